@@ -1,0 +1,86 @@
+// Shared device helpers for the sm_100a kernel library.
+//
+// Every exported launcher in this library has the C ABI
+//   extern "C" int poot_<name>(..., cudaStream_t stream)
+// and returns the cudaError_t of its launch (0 = success).  Python loads the
+// library with ctypes and passes raw device pointers, so no torch headers are
+// needed to build it and the build takes seconds.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#define POOT_API extern "C" __attribute__((visibility("default")))
+
+#ifndef POOT_SPIN_LIMIT
+// Upper bound on polls of any device-side wait (mbarrier, peer flag).  A wait
+// that runs out records a status word and returns; nothing spins forever.
+#define POOT_SPIN_LIMIT (1u << 24)
+#endif
+
+namespace poot {
+
+// Status codes written to a kernel's status word (0 = ok).
+enum Status : int {
+  kOk = 0,
+  kTimeoutProducer = 1,
+  kTimeoutMma = 2,
+  kTimeoutEpilogue = 3,
+  kTimeoutPeerFlag = 4,
+  kBadArgument = 5,
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// bf16 pair packed in a 32-bit word -> two floats (exact: bf16 is the top half of f32).
+__device__ __forceinline__ float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+
+// 16-byte streaming load that bypasses L1 (weights are read exactly once).
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+
+__device__ __forceinline__ uint4 ld_cached16(const void* p) {
+  return *reinterpret_cast<const uint4*>(p);
+}
+
+__device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
+
+template <typename T> struct Vec8;  // 8 elements = one 16-byte access for 2-byte types
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  f[0] = bf16lo(v.x); f[1] = bf16hi(v.x);
+  f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+  f[4] = bf16lo(v.z); f[5] = bf16hi(v.z);
+  f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 v;
+  v.x = pack_bf16(f[0], f[1]);
+  v.y = pack_bf16(f[2], f[3]);
+  v.z = pack_bf16(f[4], f[5]);
+  v.w = pack_bf16(f[6], f[7]);
+  return v;
+}
+
+}  // namespace poot

@@ -1,0 +1,243 @@
+// Row-wise and element-wise kernels: embedding gather, RMSNorm (with fused
+// residual add and split-K / cross-rank partial reduction), SwiGLU, casts.
+//
+// Reference behaviour covered: the fused row family (RMSNorm, crates/poot-kernelgen
+// fused.rs; op definition crates/poot-graph-ir/src/ops/norm.rs:4-29), the pointwise
+// family (SwiGLU, residual add; ops/activation.rs:94-143) and the packed bf16 row
+// gather (crates/pootc/kernels/packed/packed_bf16_row_gather.rs).
+#include "common.cuh"
+
+namespace poot {
+
+// ---------------------------------------------------------------------------
+// Embedding gather: out[t, :] = table[ids[t], :]   (bf16 rows, D % 8 == 0)
+// ---------------------------------------------------------------------------
+__global__ void embed_gather_kernel(const int* __restrict__ ids, const uint4* __restrict__ table,
+                                    uint4* __restrict__ out, int T, int D8, int vocab) {
+  int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const uint4* src = table + (size_t)id * D8;
+  uint4* dst = out + (size_t)t * D8;
+  for (int i = threadIdx.x; i < D8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm family.  One CTA per row.
+//   h_new = h (+ sum_p partial_p)             (optional residual update, written back)
+//   y     = h_new / sqrt(mean(h_new^2)+eps) * w
+// Partials are fp32 [P, T, D] (split-K slices of the producing GEMM) or bf16.
+// ---------------------------------------------------------------------------
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = (l < THREADS / 32) ? red[l] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// MAXV: 16-byte vectors per thread held in registers (D <= THREADS*8*MAXV).
+template <int THREADS, int MAXV>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,      // [T,D] input / residual stream
+               __nv_bfloat16* __restrict__ h_out,        // [T,D] updated residual (may alias x) or null
+               const float* __restrict__ partials,       // [P,T,D] fp32 or null
+               int P, size_t partial_stride,             // elements between partial slices
+               const __nv_bfloat16* __restrict__ w,      // [D]
+               __nv_bfloat16* __restrict__ y,            // [T,D] normalized output (or null)
+               int D, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const int D8 = D >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
+  float v[MAXV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int c = threadIdx.x + i * THREADS;
+    if (c < D8) {
+      uint4 raw = xr[c];
+      unpack8(raw, v[i]);
+      if (partials != nullptr) {
+        for (int p = 0; p < P; ++p) {
+          const float4* pr = reinterpret_cast<const float4*>(partials + p * partial_stride + (size_t)row * D) + 2 * c;
+          float4 a = pr[0], b = pr[1];
+          v[i][0] += a.x; v[i][1] += a.y; v[i][2] += a.z; v[i][3] += a.w;
+          v[i][4] += b.x; v[i][5] += b.y; v[i][6] += b.z; v[i][7] += b.w;
+        }
+        // The residual stream is stored in bf16: normalise what is stored.
+        uint4 packed = pack8(v[i]);
+        unpack8(packed, v[i]);
+        if (h_out != nullptr) reinterpret_cast<uint4*>(h_out + (size_t)row * D)[c] = packed;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  float tot = block_sum<THREADS>(ss, red);
+  float inv = rsqrtf(tot / (float)D + eps);
+  if (y == nullptr) return;
+  const uint4* wr = reinterpret_cast<const uint4*>(w);
+  uint4* yr = reinterpret_cast<uint4*>(y + (size_t)row * D);
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    int c = threadIdx.x + i * THREADS;
+    if (c < D8) {
+      float wf[8], o[8];
+      unpack8(wr[c], wf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * inv * wf[j];
+      yr[c] = pack8(o);
+    }
+  }
+}
+
+// out[t, j] = silu(gate) * up over an interleaved or split gate/up buffer.
+//   split layout:       gu[t, 0:F] = gate, gu[t, F:2F] = up
+//   interleaved layout: gu[t, 2j] = gate_j, gu[t, 2j+1] = up_j
+__global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                              int T, int F, int interleaved) {
+  size_t n = (size_t)T * F;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    size_t t = i / F;
+    int j = (int)(i - t * F);
+    float g, u;
+    if (interleaved) {
+      __nv_bfloat162 p = reinterpret_cast<const __nv_bfloat162*>(gu + t * 2 * F)[j];
+      g = __low2float(p); u = __high2float(p);
+    } else {
+      g = __bfloat162float(gu[t * 2 * F + j]);
+      u = __bfloat162float(gu[t * 2 * F + F + j]);
+    }
+    out[i] = __float2bfloat16(silu(g) * u);
+  }
+}
+
+__global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16(__bfloat162float(a[i]) + __bfloat162float(b[i]));
+}
+
+// h[t,:] += sum_p partial[p,t,:]   (split-K reduction without a following norm)
+__global__ void reduce_partials_kernel(const __nv_bfloat16* h, const float* partials, int P,
+                                       size_t partial_stride, __nv_bfloat16* out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float v = h ? __bfloat162float(h[i]) : 0.f;
+    for (int p = 0; p < P; ++p) v += partials[p * partial_stride + i];
+    out[i] = __float2bfloat16(v);
+  }
+}
+
+__global__ void cast_f32_bf16_kernel(const float* in, __nv_bfloat16* out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16(in[i]);
+}
+__global__ void cast_bf16_f32_kernel(const __nv_bfloat16* in, float* out, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = __bfloat162float(in[i]);
+}
+
+// Device-side step advance for chained decode: feed the sampled token back as the next input and move
+// every row one position forward (position, visible context, write slot), so consecutive graph replays
+// need no host round trip (the reference's step chain, crates/poot-executor/src/lib.rs:532-540).
+__global__ void decode_advance_kernel(const int* __restrict__ picked, int* __restrict__ tokens,
+                                      int* __restrict__ positions, int* __restrict__ slots, int* __restrict__ ctx,
+                                      const int* __restrict__ block_tables, int max_blocks,
+                                      const int* __restrict__ row_seq, int B) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B) return;
+  if (slots[i] < 0) return;  // padding row
+  tokens[i] = picked[2 * i];
+  int pos = positions[i] + 1;
+  positions[i] = pos;
+  ctx[i] = pos + 1;
+  int seq = row_seq ? row_seq[i] : i;
+  int b = pos / 16;
+  slots[i] = b < max_blocks ? block_tables[(size_t)seq * max_blocks + b] * 16 + (pos % 16) : -1;
+}
+
+}  // namespace poot
+
+using namespace poot;
+
+POOT_API int poot_decode_advance(const int* picked, int* tokens, int* positions, int* slots, int* ctx,
+                                 const int* block_tables, int max_blocks, const int* row_seq, int B, cudaStream_t s) {
+  if (B == 0) return 0;
+  decode_advance_kernel<<<(B + 127) / 128, 128, 0, s>>>(picked, tokens, positions, slots, ctx, block_tables,
+                                                        max_blocks, row_seq, B);
+  return (int)cudaGetLastError();
+}
+
+POOT_API int poot_embed_gather(const int* ids, const void* table, void* out, int T, int D, int vocab,
+                               cudaStream_t s) {
+  if (D % 8) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  embed_gather_kernel<<<T, 128, 0, s>>>(ids, (const uint4*)table, (uint4*)out, T, D / 8, vocab);
+  return (int)cudaGetLastError();
+}
+
+// x: [T,D] bf16.  partials: fp32 [P,T,D] or null.  h_out: where x+sum(partials) is stored (may equal x)
+// or null.  y: normalized output or null (reduce only).
+POOT_API int poot_rmsnorm(const void* x, void* h_out, const float* partials, int P, long long partial_stride,
+                          const void* w, void* y, int T, int D, float eps, cudaStream_t s) {
+  if (D % 8) return (int)cudaErrorInvalidValue;
+  if (T == 0) return 0;
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+  __nv_bfloat16* hb = (__nv_bfloat16*)h_out;
+  const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
+  __nv_bfloat16* yb = (__nv_bfloat16*)y;
+  int D8 = D / 8;
+  if (D8 <= 128) rmsnorm_kernel<128, 1><<<T, 128, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else if (D8 <= 256) rmsnorm_kernel<256, 1><<<T, 256, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else if (D8 <= 512) rmsnorm_kernel<512, 1><<<T, 512, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else if (D8 <= 1024) rmsnorm_kernel<512, 2><<<T, 512, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else if (D8 <= 2048) rmsnorm_kernel<512, 4><<<T, 512, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else return (int)cudaErrorInvalidValue;
+  return (int)cudaGetLastError();
+}
+
+POOT_API int poot_swiglu(const void* gu, void* out, int T, int F, int interleaved, cudaStream_t s) {
+  size_t n = (size_t)T * F;
+  if (n == 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  swiglu_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F, interleaved);
+  return (int)cudaGetLastError();
+}
+
+POOT_API int poot_add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t s) {
+  if (n == 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  add_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, (size_t)n);
+  return (int)cudaGetLastError();
+}
+
+POOT_API int poot_reduce_partials(const void* h, const float* partials, int P, long long partial_stride,
+                                  void* out, long long n, cudaStream_t s) {
+  if (n == 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  reduce_partials_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)h, partials, P, (size_t)partial_stride,
+                                                (__nv_bfloat16*)out, (size_t)n);
+  return (int)cudaGetLastError();
+}
+
+POOT_API int poot_cast_f32_bf16(const float* in, void* out, long long n, cudaStream_t s) {
+  if (n == 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_f32_bf16_kernel<<<blocks, 256, 0, s>>>(in, (__nv_bfloat16*)out, (size_t)n);
+  return (int)cudaGetLastError();
+}
+POOT_API int poot_cast_bf16_f32(const void* in, float* out, long long n, cudaStream_t s) {
+  if (n == 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  cast_bf16_f32_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)in, out, (size_t)n);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,268 @@
+// On-device token sampling: two-stage greedy argmax and the Gumbel-max family
+// (temperature + min-p, + top-k value bisection, + top-p integer-mass bisection).
+// Output per row is (token, non_finite_index): token is forced to 0 and the index of
+// the first non-finite logit is reported when any logit is NaN/Inf; otherwise -1.
+//
+// The rules are bit-compatible with the CPU oracle: maximum of
+//   logit*inv_temp + noise_scale*noise   (two roundings, no FMA; first index wins ties)
+// over the kept set  logit >= floor,  floor = max(t_k, max+floor_offset, t_p), with
+// t_k from a 30-step bisection on the count of logits >= mid and t_p from a 30-step
+// bisection over exact integer masses round(exp((l-max)*inv_temp)*2^24).
+// Noise is Gumbel(-ln(-ln u)) of u = (2*(fmix32(seed ^ idx*0x9E3779B9)>>9)+1)*2^-24.
+//
+// Reference behaviour covered: crates/pootc/kernels/sampling/{argmax_chunk,argmax_combine,
+// random_uniform,sample_gumbel_argmax_batched,sample_truncated_gumbel_argmax_batched,
+// sample_topp_gumbel_argmax_batched}.rs and crates/poot-eval/src/ops/sampling.rs:40-183.
+#include "common.cuh"
+#include <float.h>
+
+namespace poot {
+
+__device__ __forceinline__ bool finite_f32(float v) { return v >= -FLT_MAX && v <= FLT_MAX; }
+
+__device__ __forceinline__ uint32_t fmix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x85EBCA6Bu; x ^= x >> 13; x *= 0xC2B2AE35u; x ^= x >> 16;
+  return x;
+}
+__device__ __forceinline__ float uniform_at(uint32_t seed, uint32_t idx) {
+  uint32_t x = fmix32(seed ^ (idx * 0x9E3779B9u));
+  int mant = (int)(x >> 9);
+  return __fmul_rn(__fadd_rn(__fmul_rn(2.0f, (float)mant), 1.0f), 5.9604645e-8f);
+}
+
+struct Cand { float v; int i; };
+__device__ __forceinline__ Cand better(Cand a, Cand b) {
+  if (b.i >= 0 && (a.i < 0 || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
+  return a;
+}
+__device__ __forceinline__ Cand warp_best(Cand c) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    Cand t; t.v = __shfl_xor_sync(0xffffffffu, c.v, o); t.i = __shfl_xor_sync(0xffffffffu, c.i, o);
+    c = better(c, t);
+  }
+  return c;
+}
+__device__ __forceinline__ int warp_min_i(int v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+constexpr int SAMP_THREADS = 256;
+
+// Stage 1: partials[(row*groups+g)] = (best_val, best_idx, bad_idx) over one chunk.
+__global__ void __launch_bounds__(SAMP_THREADS)
+argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunk, int groups, float* __restrict__ pv,
+                    int* __restrict__ pi) {
+  __shared__ float sv[SAMP_THREADS / 32];
+  __shared__ int si[SAMP_THREADS / 32], sb[SAMP_THREADS / 32];
+  const int row = blockIdx.y, g = blockIdx.x;
+  const int start = g * chunk;
+  const int end = min(start + chunk, vocab);
+  const float* lr = logits + (size_t)row * vocab;
+  Cand best{0.f, -1};
+  int bad = vocab;
+  for (int j = start + threadIdx.x; j < end; j += SAMP_THREADS) {
+    float v = lr[j];
+    if (finite_f32(v)) { if (best.i < 0 || v > best.v) { best.v = v; best.i = j; } }
+    else if (j < bad) bad = j;
+  }
+  best = warp_best(best);
+  bad = warp_min_i(bad);
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best.v; si[w] = best.i; sb[w] = bad; }
+  __syncthreads();
+  if (w == 0) {
+    Cand c{0.f, -1}; int b = vocab;
+    if (l < SAMP_THREADS / 32) { c.v = sv[l]; c.i = si[l]; b = sb[l]; }
+    c = warp_best(c); b = warp_min_i(b);
+    if (l == 0) {
+      size_t p = (size_t)row * groups + g;
+      pv[p] = c.v; pi[p * 2] = c.i; pi[p * 2 + 1] = b;
+    }
+  }
+}
+
+__global__ void argmax_combine_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int groups, int vocab,
+                                      int* __restrict__ out) {
+  const int row = blockIdx.x, l = threadIdx.x;  // one warp
+  Cand c{0.f, -1}; int b = vocab;
+  for (int g = l; g < groups; g += 32) {
+    size_t p = (size_t)row * groups + g;
+    Cand t{pv[p], pi[p * 2]};
+    c = better(c, t);
+    b = min(b, pi[p * 2 + 1]);
+  }
+  c = warp_best(c); b = warp_min_i(b);
+  if (l == 0) {
+    bool nf = b < vocab;
+    out[row * 2] = (nf || c.i < 0) ? 0 : c.i;
+    out[row * 2 + 1] = nf ? b : -1;
+  }
+}
+
+// Block-wide helpers over SAMP_BIG threads.
+constexpr int SAMP_BIG = 1024;
+__device__ __forceinline__ float block_red_f(float v, bool is_max, float* sh) {
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  v = is_max ? warp_max(v) : -warp_max(-v);
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float r = sh[l];  // SAMP_BIG/32 == 32 entries
+  r = is_max ? warp_max(r) : -warp_max(-r);
+  __syncthreads();
+  return r;
+}
+__device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* sh) {
+  int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  unsigned long long r = sh[l];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  __syncthreads();
+  return r;
+}
+
+// rule: 1 = Gumbel (temperature+min-p), 2 = +top-k, 3 = +top-k+top-p.
+// params [rows,4] = (inv_temp, floor_offset, noise_scale, top_p); top_k [rows]; seeds [rows] (u32 bits).
+__global__ void __launch_bounds__(SAMP_BIG)
+sample_gumbel_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ params,
+                     const int* __restrict__ top_k, const int* __restrict__ seeds, int rule,
+                     int* __restrict__ out) {
+  __shared__ float shf[32];
+  __shared__ unsigned long long shu[32];
+  __shared__ int shi[32];
+  __shared__ float shv[32];
+  const int row = blockIdx.x;
+  const float* lr = logits + (size_t)row * vocab;
+  const float inv_temp = params[row * 4 + 0], floor_offset = params[row * 4 + 1];
+  const float noise_scale = params[row * 4 + 2], top_p = params[row * 4 + 3];
+  const uint32_t seed = (uint32_t)seeds[row];
+  const float MASKED = -FLT_MAX;
+
+  float mx = -FLT_MAX, mn = FLT_MAX;
+  int bad = vocab;
+  for (int j = threadIdx.x; j < vocab; j += SAMP_BIG) {
+    float v = lr[j];
+    if (finite_f32(v)) { mx = fmaxf(mx, v); if (v < mn && v != MASKED) mn = v; }
+    else if (j < bad) bad = j;
+  }
+  mx = block_red_f(mx, true, shf);
+  mn = block_red_f(mn, false, shf);
+  {
+    int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    bad = warp_min_i(bad);
+    if (l == 0) shi[w] = bad;
+    __syncthreads();
+    bad = warp_min_i(shi[l]);
+    __syncthreads();
+  }
+
+  float lo = mn;
+  if (rule >= 2) {
+    int k = top_k[row];
+    if ((float)k > 0.f) {
+      float hi = mx;
+      for (int it = 0; it < 30; ++it) {
+        float mid = __fmul_rn(__fadd_rn(lo, hi), 0.5f);
+        unsigned long long cnt = 0;
+        for (int j = threadIdx.x; j < vocab; j += SAMP_BIG) cnt += (lr[j] >= mid) ? 1ull : 0ull;
+        cnt = block_sum_u64(cnt, shu);
+        if ((float)cnt >= (float)k) lo = mid; else hi = mid;
+      }
+    }
+  }
+  const float t_k = lo;
+  const float min_p_floor = __fadd_rn(mx, floor_offset);
+  float floor_v = min_p_floor > t_k ? min_p_floor : t_k;
+  if (rule >= 3) {
+    const float floor1 = floor_v;
+    if (top_p <= 0.f) {
+      floor_v = mx;
+    } else if (top_p < 1.f) {
+      auto mass_at = [&](float th) -> unsigned long long {
+        unsigned long long m = 0;
+        for (int j = threadIdx.x; j < vocab; j += SAMP_BIG) {
+          float v = lr[j];
+          if (v >= th) m += (unsigned long long)(unsigned int)roundf(expf(__fmul_rn(__fsub_rn(v, mx), inv_temp)) * 16777216.0f);
+        }
+        return block_sum_u64(m, shu);
+      };
+      unsigned long long total = mass_at(floor1);
+      unsigned long long thresh = (unsigned long long)roundf(__fmul_rn(top_p, (float)total));
+      float tlo = floor1, thi = mx;
+      for (int it = 0; it < 30; ++it) {
+        float mid = __fmul_rn(__fadd_rn(tlo, thi), 0.5f);
+        if (mass_at(mid) >= thresh) tlo = mid; else thi = mid;
+      }
+      floor_v = floor1 > tlo ? floor1 : tlo;
+    }
+  }
+
+  Cand best{0.f, -1};
+  for (int j = threadIdx.x; j < vocab; j += SAMP_BIG) {
+    float v = lr[j];
+    if (v >= floor_v) {
+      float u = uniform_at(seed, (uint32_t)j);
+      float noise = -logf(-logf(u));
+      float pert = __fadd_rn(__fmul_rn(v, inv_temp), __fmul_rn(noise_scale, noise));
+      if (best.i < 0 || pert > best.v) { best.v = pert; best.i = j; }
+    }
+  }
+  best = warp_best(best);
+  {
+    int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    if (l == 0) { shv[w] = best.v; shi[w] = best.i; }
+    __syncthreads();
+    if (w == 0) {
+      Cand c{shv[l], shi[l]};
+      c = warp_best(c);
+      if (l == 0) {
+        bool nf = bad < vocab;
+        out[row * 2] = (nf || c.i < 0) ? 0 : c.i;
+        out[row * 2 + 1] = nf ? bad : -1;
+      }
+    }
+  }
+}
+
+__global__ void random_uniform_kernel(const int* __restrict__ seeds, int cols, float* __restrict__ out, size_t n) {
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  size_t r = i / cols;
+  out[i] = uniform_at((uint32_t)seeds[r], (uint32_t)(i - r * cols));
+}
+
+}  // namespace poot
+
+using namespace poot;
+
+// scratch: pv fp32 [rows, groups], pi int32 [rows, groups, 2]; groups = ceil(vocab / chunk).
+POOT_API int poot_argmax(const float* logits, int rows, int vocab, int chunk, float* pv, int* pi, int* out,
+                         cudaStream_t s) {
+  if (rows == 0) return 0;
+  int groups = (vocab + chunk - 1) / chunk;
+  if (groups < 1) groups = 1;
+  argmax_chunk_kernel<<<dim3(groups, rows), SAMP_THREADS, 0, s>>>(logits, vocab, chunk, groups, pv, pi);
+  argmax_combine_kernel<<<rows, 32, 0, s>>>(pv, pi, groups, vocab, out);
+  return (int)cudaGetLastError();
+}
+
+POOT_API int poot_sample_gumbel(const float* logits, int rows, int vocab, const float* params, const int* top_k,
+                                const int* seeds, int rule, int* out, cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (rule < 1 || rule > 3) return (int)cudaErrorInvalidValue;
+  sample_gumbel_kernel<<<rows, SAMP_BIG, 0, s>>>(logits, vocab, params, top_k, seeds, rule, out);
+  return (int)cudaGetLastError();
+}
+
+POOT_API int poot_random_uniform(const int* seeds, int rows, int cols, float* out, cudaStream_t s) {
+  size_t n = (size_t)rows * cols;
+  if (n == 0) return 0;
+  random_uniform_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(seeds, cols, out, n);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,317 @@
+"""PyTorch-facing wrappers over the hand-written sm_100a kernels.
+
+Every wrapper validates shapes and dtypes, allocates its output with torch when the caller passes none,
+and launches on the current CUDA stream, so all of them can be captured into a CUDA graph.  There is no
+PyTorch fallback: a tensor that is not on a CUDA device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from ._lib import check, kernels
+
+EPI_STORE, EPI_F32, EPI_RESID, EPI_SWIGLU, EPI_PARTIAL = 0, 1, 2, 3, 4
+KV_BLOCK = 16
+
+_P = c_void_p
+_SIGS = {
+    "poot_embed_gather": [_P, _P, _P, c_int, c_int, c_int, _P],
+    "poot_rmsnorm": [_P, _P, _P, c_int, c_longlong, _P, _P, c_int, c_int, c_float, _P],
+    "poot_swiglu": [_P, _P, c_int, c_int, c_int, _P],
+    "poot_add_bf16": [_P, _P, _P, c_longlong, _P],
+    "poot_reduce_partials": [_P, _P, c_int, c_longlong, _P, c_longlong, _P],
+    "poot_cast_f32_bf16": [_P, _P, c_longlong, _P],
+    "poot_cast_bf16_f32": [_P, _P, c_longlong, _P],
+    "poot_gemv_bf16": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "poot_gemm_bf16_tcgen05": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,
+                               _P, _P],
+    "poot_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_int, _P],
+    "poot_attn_paged": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float,
+                        c_float, c_int, c_int, _P],
+    "poot_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, _P],
+    "poot_argmax": [_P, c_int, c_int, c_int, _P, _P, _P, _P],
+    "poot_sample_gumbel": [_P, c_int, c_int, _P, _P, _P, c_int, _P, _P],
+    "poot_random_uniform": [_P, c_int, c_int, _P, _P],
+}
+_bound = {}
+
+
+def _fn(name: str):
+    f = _bound.get(name)
+    if f is None:
+        f = getattr(kernels(), name)
+        f.argtypes = _SIGS[name]
+        f.restype = c_int
+        _bound[name] = f
+    return f
+
+
+def register_signature(name: str, argtypes) -> None:
+    """Let other op modules of the package declare launchers that live in the same library."""
+    _SIGS[name] = argtypes
+
+
+def fn(name: str):
+    return _fn(name)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("poot_b200.ops: tensor must live on a CUDA device (no CPU fallback)")
+
+
+_status = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits set non-zero when a wait ran out."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    s = _status.get(dev)
+    if s is None:
+        s = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[dev] = s
+    return s
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait ran out; the kernel returned early and its output is invalid."""
+
+
+def check_status(device=None) -> None:
+    s = status_word(device)
+    code = int(s.item())
+    if code != 0:
+        s.zero_()
+        names = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "peer flag", 5: "bad argument"}
+        raise DeviceWaitTimeout(f"device wait timed out in {names.get(code, code)}")
+
+
+# ----------------------------------------------------------------------------------------------------------------
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(ids, table)
+    assert ids.dtype == torch.int32 and table.dtype == torch.bfloat16 and table.is_contiguous()
+    T, (V, D) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty(T, D, dtype=torch.bfloat16, device=table.device)
+    check(_fn("poot_embed_gather")(_ptr(ids), _ptr(table), _ptr(out), T, D, V, _stream()), "embed_gather")
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: Optional[torch.Tensor] = None,
+            partials: Optional[torch.Tensor] = None, h_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = rmsnorm(x + sum(partials)) * w``; the updated residual stream goes to ``h_out`` (may be ``x``)."""
+    _need_cuda(x, w)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and w.dtype == torch.bfloat16
+    T, D = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    P, stride = 0, 0
+    if partials is not None:
+        if partials.dim() == 2:
+            partials = partials.unsqueeze(0)
+        assert partials.dtype == torch.float32 and partials.shape[-2:] == (T, D)
+        assert partials.stride(2) == 1 and partials.stride(1) == D
+        P, stride = partials.shape[0], partials.stride(0)
+    check(_fn("poot_rmsnorm")(_ptr(x), _ptr(h_out), _ptr(partials), P, stride, _ptr(w), _ptr(out), T, D, float(eps),
+                              _stream()), "rmsnorm")
+    return out
+
+
+def reduce_partials(h: Optional[torch.Tensor], partials: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    P = partials.shape[0]
+    n = out.numel()
+    assert partials.stride(2) == 1 and partials.stride(1) == out.shape[1] and out.is_contiguous()
+    check(_fn("poot_reduce_partials")(_ptr(h), _ptr(partials), P, partials.stride(0), _ptr(out), n, _stream()),
+          "reduce_partials")
+    return out
+
+
+def swiglu(gu: torch.Tensor, interleaved: bool, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(gu)
+    assert gu.dtype == torch.bfloat16 and gu.is_contiguous()
+    T, F2 = gu.shape
+    if out is None:
+        out = torch.empty(T, F2 // 2, dtype=torch.bfloat16, device=gu.device)
+    check(_fn("poot_swiglu")(_ptr(gu), _ptr(out), T, F2 // 2, int(interleaved), _stream()), "swiglu")
+    return out
+
+
+def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _need_cuda(a, b)
+    if out is None:
+        out = torch.empty_like(a)
+    check(_fn("poot_add_bf16")(_ptr(a), _ptr(b), _ptr(out), a.numel(), _stream()), "add")
+    return out
+
+
+def _out_for(epi: int, M: int, N: int, device, out):
+    if out is not None:
+        return out
+    if epi == EPI_F32:
+        return torch.empty(M, N, dtype=torch.float32, device=device)
+    if epi == EPI_SWIGLU:
+        return torch.empty(M, N // 2, dtype=torch.bfloat16, device=device)
+    return torch.empty(M, N, dtype=torch.bfloat16, device=device)
+
+
+def gemv(x: torch.Tensor, W: torch.Tensor, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
+         resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Skinny GEMM ``x[M,K] @ W[N,K]^T`` for ``M <= 4`` (decode)."""
+    _need_cuda(x, W)
+    assert x.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and W.is_contiguous()
+    M, K = x.shape
+    N = W.shape[0]
+    assert W.shape[1] == K and x.stride(1) == 1
+    out = _out_for(epi, M, N, x.device, out)
+    check(_fn("poot_gemv_bf16")(epi, _ptr(x), _ptr(W), _ptr(out), _ptr(resid), M, N, K, x.stride(0), out.stride(0),
+                                _stream()), "gemv_bf16")
+    return out
+
+
+def _pick_bn(M: int, N: int) -> int:
+    m_tiles = (M + 127) // 128
+    if m_tiles * ((N + 255) // 256) >= 148:
+        return 256
+    if m_tiles * ((N + 127) // 128) >= 120:
+        return 128
+    return 64
+
+
+def gemm(x: torch.Tensor, W: torch.Tensor, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
+         resid: Optional[torch.Tensor] = None, bn: Optional[int] = None, splits: int = 1) -> torch.Tensor:
+    """tcgen05 GEMM ``x[M,K] @ W[N,K]^T``.  With ``epi == EPI_PARTIAL`` the result is fp32 ``[splits, M, N]``."""
+    _need_cuda(x, W)
+    assert x.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and W.is_contiguous()
+    M, K = x.shape
+    N = W.shape[0]
+    assert W.shape[1] == K and x.stride(1) == 1
+    if bn is None:
+        bn = _pick_bn(M, N)
+    pstride = 0
+    if epi == EPI_PARTIAL:
+        if out is None:
+            out = torch.empty(splits, M, N, dtype=torch.float32, device=x.device)
+        pstride = out.stride(0)
+        ldo = out.stride(1)
+    else:
+        out = _out_for(epi, M, N, x.device, out)
+        ldo = out.stride(0)
+    st = status_word(x.device)
+    check(_fn("poot_gemm_bf16_tcgen05")(epi, _ptr(x), _ptr(W), _ptr(out), _ptr(resid), M, N, K, x.stride(0), ldo, bn,
+                                        splits, pstride, _ptr(st), _stream()), "gemm_bf16_tcgen05")
+    return out
+
+
+def linear(x: torch.Tensor, W: torch.Tensor, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
+           resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Pick the decode GEMV (``M <= 4``) or the tensor-core GEMM."""
+    if x.shape[0] <= 4:
+        return gemv(x, W, epi, out, resid)
+    return gemm(x, W, epi, out, resid)
+
+
+def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor,
+                  positions: torch.Tensor, slots: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, Hq: int,
+                  Hkv: int, D: int, rot: Optional[int] = None, q_norm_w: Optional[torch.Tensor] = None,
+                  k_norm_w: Optional[torch.Tensor] = None, norm_eps: float = 1e-6) -> None:
+    _need_cuda(qkv, kpool)
+    T = qkv.shape[0]
+    assert qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and qkv.shape[1] == (Hq + 2 * Hkv) * D
+    assert positions.dtype == torch.int32 and slots.dtype == torch.int32
+    assert cos.dtype == torch.float32 and sin.dtype == torch.float32 and cos.is_contiguous()
+    rot = D if rot is None else rot
+    assert cos.shape[1] == rot // 2
+    check(_fn("poot_rope_kv_write")(_ptr(qkv), _ptr(q_out), _ptr(kpool), _ptr(vpool), _ptr(positions), _ptr(slots),
+                                    _ptr(cos), _ptr(sin), _ptr(q_norm_w), _ptr(k_norm_w), float(norm_eps), T, Hq, Hkv,
+                                    D, rot, cos.shape[0], 0, _stream()), "rope_kv_write")
+
+
+def attn_paged(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_tables: torch.Tensor,
+               row_seq: Optional[torch.Tensor], row_ctx: torch.Tensor, Hq: int, Hkv: int, D: int, scale: float,
+               out: Optional[torch.Tensor] = None, splits: int = 1, scratch=None, softcap: float = 0.0,
+               window: int = 0) -> torch.Tensor:
+    """Paged attention for R query rows; ``q`` is ``[R, Hq*D]``; pools are ``[blocks, Hkv, 16, D]``."""
+    _need_cuda(q, kpool, vpool)
+    R = q.shape[0]
+    assert q.dtype == torch.bfloat16 and q.stride(1) == 1
+    assert block_tables.dtype == torch.int32 and row_ctx.dtype == torch.int32
+    if out is None:
+        out = torch.empty(R, Hq * D, dtype=torch.bfloat16, device=q.device)
+    po = pml = None
+    if splits > 1:
+        if scratch is None:
+            po = torch.empty(R * Hq * splits * D, dtype=torch.float32, device=q.device)
+            pml = torch.empty(R * Hq * splits * 2, dtype=torch.float32, device=q.device)
+        else:
+            po, pml = scratch
+            assert po.numel() >= R * Hq * splits * D and pml.numel() >= R * Hq * splits * 2
+    check(_fn("poot_attn_paged")(_ptr(q), q.stride(0), _ptr(kpool), _ptr(vpool), _ptr(block_tables),
+                                 block_tables.shape[1], _ptr(row_seq), _ptr(row_ctx), _ptr(out), out.stride(0),
+                                 _ptr(po), _ptr(pml), R, Hq, Hkv, D, float(scale), float(softcap), int(window),
+                                 int(splits), _stream()), "attn_paged")
+    return out
+
+
+ARGMAX_CHUNK = 2048
+
+
+def argmax_scratch(rows: int, vocab: int, device):
+    groups = (vocab + ARGMAX_CHUNK - 1) // ARGMAX_CHUNK
+    return (torch.empty(rows * groups, dtype=torch.float32, device=device),
+            torch.empty(rows * groups * 2, dtype=torch.int32, device=device))
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, scratch=None) -> torch.Tensor:
+    """Greedy pick per row: ``out[r] = (token, non_finite_index)``."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, 2, dtype=torch.int32, device=logits.device)
+    pv, pi = scratch if scratch is not None else argmax_scratch(rows, vocab, logits.device)
+    check(_fn("poot_argmax")(_ptr(logits), rows, vocab, ARGMAX_CHUNK, _ptr(pv), _ptr(pi), _ptr(out), _stream()),
+          "argmax")
+    return out
+
+
+def sample_gumbel(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor, seeds: torch.Tensor, rule: int,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gumbel-max sampling; ``params[r] = (inv_temp, floor_offset, noise_scale, top_p)``; rule 1..3."""
+    _need_cuda(logits)
+    rows, vocab = logits.shape
+    assert params.shape == (rows, 4) and params.dtype == torch.float32
+    assert top_k.dtype == torch.int32 and seeds.dtype == torch.int32
+    if out is None:
+        out = torch.empty(rows, 2, dtype=torch.int32, device=logits.device)
+    check(_fn("poot_sample_gumbel")(_ptr(logits), rows, vocab, _ptr(params), _ptr(top_k), _ptr(seeds), rule, _ptr(out),
+                                    _stream()), "sample_gumbel")
+    return out
+
+
+def random_uniform(seeds: torch.Tensor, cols: int) -> torch.Tensor:
+    rows = seeds.numel()
+    out = torch.empty(rows, cols, dtype=torch.float32, device=seeds.device)
+    check(_fn("poot_random_uniform")(_ptr(seeds), rows, cols, _ptr(out), _stream()), "random_uniform")
+    return out
+
+
+def decode_advance(picked: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                   ctx: torch.Tensor, block_tables: torch.Tensor, row_seq: Optional[torch.Tensor], B: int) -> None:
+    """Feed sampled tokens back and advance positions / write slots on the device (chained decode)."""
+    check(_fn("poot_decode_advance")(_ptr(picked), _ptr(tokens), _ptr(positions), _ptr(slots), _ptr(ctx),
+                                     _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), B, _stream()),
+          "decode_advance")

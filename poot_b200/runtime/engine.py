@@ -1,0 +1,266 @@
+"""Per-rank device engine: static step buffers, paged KV pools, the kernel program of one step, and
+CUDA-graph capture / replay of that program.
+
+A *step* runs ``T`` query tokens (decode: one per sequence row; prefill: a chunk of one or more sequences)
+through the stack and samples one token for each of ``B`` logit rows.  All step inputs live in fixed device
+buffers that the host overwrites in place before a replay, so one captured graph per ``(T, B, sampler)`` shape
+serves every position - the record-on-first-step / replay design of the reference executor
+(crates/poot-executor/src/engine.rs:2454-2700, crates/poot-ptx-runtime/src/graph.rs:11-56), here with one
+process per GPU and no host work between kernels.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..models.config import DecoderConfig
+from ..ops import cuda_ops as K
+from .rope import rope_tables
+from .weights import DecoderWeights
+
+KV_BLOCK = K.KV_BLOCK
+
+
+@dataclass
+class StepShape:
+    tokens: int         # T: query tokens in the step
+    logit_rows: int     # B: rows that get logits + a sampled token
+    sampler: int = 0    # 0 greedy, 1..3 Gumbel family rule
+    chain: bool = False  # append the device-side advance (decode chaining)
+
+
+class KVPool:
+    """Paged K/V pools, one pair per layer: ``[num_blocks, Hkv_local, 16, D]`` bf16."""
+
+    def __init__(self, cfg: DecoderConfig, num_blocks: int, device, tp_world: int = 1):
+        self.num_blocks = num_blocks
+        self.hkv = max(cfg.n_kv_heads // tp_world, 1)
+        shape = (cfg.n_layers, 2, num_blocks, self.hkv, KV_BLOCK, cfg.head_dim)
+        self.buf = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+
+    def k(self, layer: int) -> torch.Tensor:
+        return self.buf[layer, 0]
+
+    def v(self, layer: int) -> torch.Tensor:
+        return self.buf[layer, 1]
+
+    @staticmethod
+    def bytes_per_block(cfg: DecoderConfig, tp_world: int = 1) -> int:
+        return cfg.n_layers * 2 * max(cfg.n_kv_heads // tp_world, 1) * KV_BLOCK * cfg.head_dim * 2
+
+
+class DecoderEngine:
+    """Runs the decoder program of one rank.  ``comm`` (optional) supplies the tensor-parallel collectives."""
+
+    def __init__(self, weights: DecoderWeights, num_blocks: int, max_seqs: int, max_tokens: int,
+                 max_blocks_per_seq: int, comm=None, device=None, use_graphs: bool = True):
+        cfg = weights.cfg
+        self.cfg, self.w, self.comm = cfg, weights, comm
+        self.device = torch.device(device if device is not None else weights.embed.device)
+        self.tp = weights.tp_world
+        self.hq = cfg.n_heads // self.tp
+        self.hkv = max(cfg.n_kv_heads // self.tp, 1)
+        self.max_seqs, self.max_tokens, self.max_blocks = max_seqs, max_tokens, max_blocks_per_seq
+        self.use_graphs = use_graphs
+        self.kv = KVPool(cfg, num_blocks, self.device, self.tp)
+        dev, i32 = self.device, torch.int32
+        T, D, H = max_tokens, cfg.head_dim, cfg.hidden
+        # ---- step inputs (written in place by the host, or by the advance kernel) ----
+        self.tokens = torch.zeros(T, dtype=i32, device=dev)
+        self.positions = torch.zeros(T, dtype=i32, device=dev)
+        self.slots = torch.full((T,), -1, dtype=i32, device=dev)
+        self.row_seq = torch.zeros(T, dtype=i32, device=dev)
+        self.row_ctx = torch.zeros(T, dtype=i32, device=dev)
+        self.block_tables = torch.zeros(max_seqs, max_blocks_per_seq, dtype=i32, device=dev)
+        self.logit_idx = torch.zeros(max_seqs, dtype=torch.int64, device=dev)
+        self.samp_params = torch.zeros(max_seqs, 4, dtype=torch.float32, device=dev)
+        self.samp_topk = torch.zeros(max_seqs, dtype=i32, device=dev)
+        self.samp_seeds = torch.zeros(max_seqs, dtype=i32, device=dev)
+        # ---- activations ----
+        bf = torch.bfloat16
+        ffn_local = (cfg.moe_ffn if cfg.is_moe else cfg.ffn) // (1 if cfg.is_moe else self.tp)
+        self.h = torch.zeros(T, H, dtype=bf, device=dev)
+        self.x = torch.zeros(T, H, dtype=bf, device=dev)
+        self.qkv = torch.zeros(T, (self.hq + 2 * self.hkv) * D, dtype=bf, device=dev)
+        self.q = torch.zeros(T, self.hq * D, dtype=bf, device=dev)
+        self.attn = torch.zeros(T, self.hq * D, dtype=bf, device=dev)
+        self.act = torch.zeros(T, ffn_local, dtype=bf, device=dev)
+        # split-K partial slices and split-KV scratch are only used by small steps (few tiles / few CTAs)
+        self.max_splits = 8
+        self.small_T = min(T, 256)
+        self.partials = torch.zeros(self.max_splits, self.small_T, H, dtype=torch.float32, device=dev)
+        self.hl = torch.zeros(max_seqs, H, dtype=bf, device=dev)
+        self.xl = torch.zeros(max_seqs, H, dtype=bf, device=dev)
+        self.logits = torch.zeros(max_seqs, cfg.vocab, dtype=torch.float32, device=dev)
+        self.picked = torch.zeros(max_seqs, 2, dtype=i32, device=dev)
+        self.argmax_scratch = K.argmax_scratch(max_seqs, cfg.vocab, dev)
+        self.attn_splits_max = 16
+        ts = self.small_T
+        self.attn_scratch = (torch.zeros(ts * self.hq * self.attn_splits_max * D, dtype=torch.float32, device=dev),
+                             torch.zeros(ts * self.hq * self.attn_splits_max * 2, dtype=torch.float32, device=dev))
+        cos, sin = rope_tables(cfg, cfg.max_position)
+        self.cos, self.sin = cos.to(dev), sin.to(dev)
+        self.scale = 1.0 / math.sqrt(D)
+        self._graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
+        self.launches_per_step: Dict[Tuple, int] = {}
+        self._launch_counter = 0
+
+    # ------------------------------------------------------------------ kernel program
+    def _count(self, n: int = 1):
+        self._launch_counter += n
+
+    def _linear(self, x, W, epi, out, resid=None):
+        self._count()
+        return K.linear(x, W, epi, out, resid)
+
+    def _proj_to_residual(self, x, W, T):
+        """``h += x @ W^T`` (o_proj / down_proj).  Returns pending fp32 partial slices or None.
+
+        Small-N, large-K projections at decode batch sizes do not fill 148 SMs with one K pass, so they split K
+        and leave the reduction to the next RMSNorm (which reads the residual stream anyway).
+        """
+        h = self.h[:T]
+        N, Kdim = W.shape
+        if T <= 4:
+            self._linear(x, W, K.EPI_RESID, h, h)
+            return None
+        tiles = ((T + 127) // 128) * ((N + 63) // 64)
+        if tiles < 100 and Kdim >= 1024 and T <= self.small_T:
+            splits = max(1, min(self.max_splits, 148 // tiles, Kdim // 512))
+            if splits > 1:
+                p = self.partials[:splits, :T]
+                self._count()
+                K.gemm(x, W, K.EPI_PARTIAL, out=p, bn=64, splits=splits)
+                return p
+        self._linear(x, W, K.EPI_RESID, h, h)
+        return None
+
+    def _norm(self, w, T, pending):
+        h, x = self.h[:T], self.x[:T]
+        self._count()
+        if pending is None:
+            K.rmsnorm(h, w, self.cfg.norm_eps, out=x)
+        else:
+            K.rmsnorm(h, w, self.cfg.norm_eps, out=x, partials=pending, h_out=h)
+        return x
+
+    def _attn_splits(self, T: int) -> int:
+        ctas = T * self.hkv * max(1, (self.cfg.n_rep + 3) // 4)
+        if ctas >= 148 or T > self.small_T:
+            return 1
+        return max(1, min(self.attn_splits_max, 296 // ctas))
+
+    def forward(self, shape: StepShape) -> None:
+        """Launch the whole step on the current stream (eagerly or under capture)."""
+        cfg, w = self.cfg, self.w
+        T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
+        self._launch_counter = 0
+        h = self.h[:T]
+        self._count()
+        K.embed_gather(self.tokens[:T], w.embed, out=h)
+        pending = None
+        for l, L in enumerate(w.layers):
+            x = self._norm(L.ln1, T, pending)
+            qkv = self._linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
+            self._count()
+            K.rope_kv_write(qkv, self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
+                            self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
+            splits = self._attn_splits(T)
+            self._count(2 if splits > 1 else 1)
+            K.attn_paged(self.q[:T], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:T],
+                         self.row_ctx[:T], self.hq, self.hkv, D, self.scale, out=self.attn[:T], splits=splits,
+                         scratch=self.attn_scratch, softcap=cfg.attn_softcap, window=cfg.sliding_window)
+            if self.comm is not None:
+                pending = self.comm.row_parallel(self, self.attn[:T], L.wo, T)
+            else:
+                pending = self._proj_to_residual(self.attn[:T], L.wo, T)
+            x = self._norm(L.ln2, T, pending)
+            if cfg.is_moe:
+                pending = self._moe(l, L, x, T)
+            else:
+                act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
+                if self.comm is not None:
+                    pending = self.comm.row_parallel(self, act, L.wdown, T)
+                else:
+                    pending = self._proj_to_residual(act, L.wdown, T)
+        # ---- head: gather the logit rows, final norm, LM head, sampler ----
+        if pending is not None:
+            self._count()
+            K.reduce_partials(h, pending, h)
+        hl = self.hl[:B]
+        if B == T:
+            hl = h
+        else:
+            self._count()
+            torch.index_select(h, 0, self.logit_idx[:B], out=hl)
+        self._count()
+        K.rmsnorm(hl, w.final_norm, cfg.norm_eps, out=self.xl[:B])
+        self._linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits[:B])
+        if shape.sampler == 0:
+            self._count(2)
+            K.argmax(self.logits[:B], out=self.picked[:B], scratch=self.argmax_scratch)
+        else:
+            self._count()
+            K.sample_gumbel(self.logits[:B], self.samp_params[:B], self.samp_topk[:B], self.samp_seeds[:B],
+                            shape.sampler, out=self.picked[:B])
+        if shape.chain:
+            self._count()
+            K.decode_advance(self.picked, self.tokens, self.positions, self.slots, self.row_ctx, self.block_tables,
+                             self.row_seq, B)
+
+    def _moe(self, l, L, x, T):
+        from . import moe as _moe
+        return _moe.moe_forward(self, l, L, x, T)
+
+    # ------------------------------------------------------------------ capture / replay
+    def _key(self, shape: StepShape):
+        return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain)
+
+    def prepare(self, shape: StepShape) -> None:
+        """Warm up and capture the step graph for ``shape`` (never done in the serving path afterwards)."""
+        key = self._key(shape)
+        if key in self._graphs or not self.use_graphs:
+            return
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(s):
+            self.forward(shape)  # warm-up: tensor-map cache, function attributes
+        torch.cuda.current_stream(self.device).wait_stream(s)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            self.forward(shape)
+        self._graphs[key] = g
+        self.launches_per_step[key] = self._launch_counter
+
+    def run(self, shape: StepShape) -> None:
+        """Replay (or eagerly launch) one step; inputs must already be in the static buffers."""
+        key = self._key(shape)
+        g = self._graphs.get(key)
+        if g is None and self.use_graphs:
+            self.prepare(shape)
+            g = self._graphs.get(key)
+        if g is not None:
+            g.replay()
+        else:
+            self.forward(shape)
+            self.launches_per_step[key] = self._launch_counter
+
+    # ------------------------------------------------------------------ host-side input binding
+    def bind(self, tokens, positions, slots, row_seq, row_ctx, logit_idx, block_tables=None,
+             non_blocking: bool = True) -> None:
+        """Copy one step's inputs (pinned host tensors) into the static device buffers."""
+        T = tokens.numel()
+        self.tokens[:T].copy_(tokens, non_blocking=non_blocking)
+        self.positions[:T].copy_(positions, non_blocking=non_blocking)
+        self.slots[:T].copy_(slots, non_blocking=non_blocking)
+        self.row_seq[:T].copy_(row_seq, non_blocking=non_blocking)
+        self.row_ctx[:T].copy_(row_ctx, non_blocking=non_blocking)
+        B = logit_idx.numel()
+        self.logit_idx[:B].copy_(logit_idx, non_blocking=non_blocking)
+        if block_tables is not None:
+            self.block_tables[:block_tables.shape[0], :block_tables.shape[1]].copy_(block_tables,
+                                                                                     non_blocking=non_blocking)

@@ -1,0 +1,184 @@
+"""Device-resident weights of a decoder stack in the layouts the kernels read.
+
+Layouts (all ``[out, in]`` = checkpoint order, bf16):
+
+* ``wqkv``  fused ``[q heads | k heads | v heads]`` rows (the reference keeps Q, K, V separate,
+  crates/poot-models/tests/launch_census/real_dims.tsv:69-72; fusing saves two launches per layer).
+* ``wgu``   gate and up rows interleaved (row ``2j`` = gate_j, row ``2j+1`` = up_j) so SwiGLU runs in the GEMM /
+  GEMV epilogue on adjacent accumulators.
+* tensor-parallel rank views follow the Megatron layouts of the reference's ``shard``
+  (crates/poot-graph-plan/src/passes/sharding.rs:219-251): q/k/v/gate/up split on ``out``, o/down split on ``in``,
+  embedding, head and norms replicated.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..models.config import DecoderConfig
+
+
+@dataclass
+class LayerWeights:
+    ln1: torch.Tensor
+    ln2: torch.Tensor
+    wqkv: torch.Tensor
+    wo: torch.Tensor
+    wgu: Optional[torch.Tensor] = None      # dense FFN
+    wdown: Optional[torch.Tensor] = None
+    q_norm: Optional[torch.Tensor] = None
+    k_norm: Optional[torch.Tensor] = None
+    router: Optional[torch.Tensor] = None   # [E, hidden]
+    ex_wgu: Optional[torch.Tensor] = None   # [E_local, 2F, hidden]
+    ex_wdown: Optional[torch.Tensor] = None  # [E_local, hidden, F]
+    quant: Dict[str, object] = field(default_factory=dict)  # packed (GGUF block) weights by role
+
+
+@dataclass
+class DecoderWeights:
+    cfg: DecoderConfig
+    embed: torch.Tensor
+    final_norm: torch.Tensor
+    lm_head: torch.Tensor
+    layers: List[LayerWeights]
+    tp_rank: int = 0
+    tp_world: int = 1
+    quant: Dict[str, object] = field(default_factory=dict)
+
+    def nbytes(self) -> int:
+        n = 0
+        seen = set()
+
+        def add(t):
+            nonlocal n
+            if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                n += t.numel() * t.element_size()
+
+        for t in (self.embed, self.final_norm, self.lm_head):
+            add(t)
+        for L in self.layers:
+            for v in vars(L).values():
+                add(v)
+        return n
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``[F, H]`` gate and up -> ``[2F, H]`` with rows (gate_0, up_0, gate_1, up_1, ...)."""
+    F, H = gate.shape
+    return torch.stack([gate, up], dim=1).reshape(2 * F, H).contiguous()
+
+
+def shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = w.shape[0] // world
+    return w[rank * n:(rank + 1) * n].contiguous()
+
+
+def shard_cols(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    n = w.shape[1] // world
+    return w[:, rank * n:(rank + 1) * n].contiguous()
+
+
+def fuse_qkv(wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, cfg: DecoderConfig, rank: int = 0,
+             world: int = 1) -> torch.Tensor:
+    """Fused, rank-local QKV: this rank's query heads, then its KV heads."""
+    D = cfg.head_dim
+    hq, hkv = cfg.n_heads // world, max(cfg.n_kv_heads // world, 1)
+    q = wq[rank * hq * D:(rank + 1) * hq * D]
+    kv_rank = rank * cfg.n_kv_heads // world if cfg.n_kv_heads >= world else rank % cfg.n_kv_heads
+    k = wk[kv_rank * hkv * D:(kv_rank + 1) * hkv * D]
+    v = wv[kv_rank * hkv * D:(kv_rank + 1) * hkv * D]
+    return torch.cat([q, k, v], dim=0).contiguous()
+
+
+def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02, tp_rank: int = 0, tp_world: int = 1,
+                   ep_rank: int = 0, ep_world: int = 1, dtype=torch.bfloat16) -> DecoderWeights:
+    """Random-init weights ``~N(0, std)`` generated directly in the rank-local fused layouts.
+
+    Each tensor is drawn from a generator seeded by (seed, layer, role) so a rank's shard of a weight equals the
+    same slice of the weight any other world size would draw: TP=1 and TP=8 runs compute the same model.
+    """
+    dev = torch.device(device)
+    H, D = cfg.hidden, cfg.head_dim
+
+    def draw(shape, tag: int):
+        g = torch.Generator(device=dev)
+        g.manual_seed((seed * 1000003 + tag) & 0x7fffffff)
+        return (torch.randn(shape, generator=g, device=dev, dtype=torch.float32) * std).to(dtype)
+
+    def ones(n):
+        return torch.ones(n, dtype=dtype, device=dev)
+
+    layers = []
+    for l in range(cfg.n_layers):
+        t = (l + 1) * 64
+        wq = draw((cfg.q_size, H), t + 0)
+        wk = draw((cfg.kv_size, H), t + 1)
+        wv = draw((cfg.kv_size, H), t + 2)
+        wqkv = fuse_qkv(wq, wk, wv, cfg, tp_rank, tp_world)
+        del wq, wk, wv
+        wo = shard_cols(draw((H, cfg.q_size), t + 3), tp_rank, tp_world)
+        L = LayerWeights(ln1=ones(H), ln2=ones(H), wqkv=wqkv, wo=wo)
+        if cfg.qk_norm:
+            L.q_norm, L.k_norm = ones(D), ones(D)
+        if cfg.is_moe:
+            F = cfg.moe_ffn
+            L.router = draw((cfg.n_experts, H), t + 4)
+            e_local = cfg.n_experts // ep_world
+            gus, downs = [], []
+            for e in range(ep_rank * e_local, (ep_rank + 1) * e_local):
+                g_ = draw((F, H), t + 8 + 3 * e)
+                u_ = draw((F, H), t + 9 + 3 * e)
+                gus.append(interleave_gate_up(g_, u_))
+                downs.append(draw((H, F), t + 10 + 3 * e))
+                del g_, u_
+            L.ex_wgu = torch.stack(gus)
+            L.ex_wdown = torch.stack(downs)
+        else:
+            F = cfg.ffn
+            g_ = shard_rows(draw((F, H), t + 4), tp_rank, tp_world)
+            u_ = shard_rows(draw((F, H), t + 5), tp_rank, tp_world)
+            L.wgu = interleave_gate_up(g_, u_)
+            del g_, u_
+            L.wdown = shard_cols(draw((H, F), t + 6), tp_rank, tp_world)
+        layers.append(L)
+    embed = draw((cfg.vocab, H), 1)
+    lm_head = embed if cfg.tie_embeddings else draw((cfg.vocab, H), 2)
+    return DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H), lm_head=lm_head, layers=layers, tp_rank=tp_rank,
+                          tp_world=tp_world)
+
+
+def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], device, tp_rank: int = 0,
+                       tp_world: int = 1, dtype=torch.bfloat16) -> DecoderWeights:
+    """Build device weights from canonical names (``layers.{i}.attn_q`` ... as produced by the family name tables)."""
+    dev = torch.device(device)
+
+    def get(name):
+        return tensors[name].to(device=dev, dtype=dtype)
+
+    layers = []
+    for l in range(cfg.n_layers):
+        p = f"layers.{l}."
+        wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)
+        wo = shard_cols(get(p + "attn_o"), tp_rank, tp_world)
+        L = LayerWeights(ln1=get(p + "attn_norm"), ln2=get(p + "ffn_norm"), wqkv=wqkv, wo=wo)
+        if cfg.qk_norm:
+            L.q_norm, L.k_norm = get(p + "attn_q_norm"), get(p + "attn_k_norm")
+        if cfg.is_moe:
+            L.router = get(p + "ffn_router")
+            gus, downs = [], []
+            for e in range(cfg.n_experts):
+                gus.append(interleave_gate_up(get(p + f"experts.{e}.gate"), get(p + f"experts.{e}.up")))
+                downs.append(get(p + f"experts.{e}.down"))
+            L.ex_wgu, L.ex_wdown = torch.stack(gus), torch.stack(downs)
+        else:
+            L.wgu = interleave_gate_up(shard_rows(get(p + "ffn_gate"), tp_rank, tp_world),
+                                       shard_rows(get(p + "ffn_up"), tp_rank, tp_world))
+            L.wdown = shard_cols(get(p + "ffn_down"), tp_rank, tp_world)
+        layers.append(L)
+    embed = get("embed")
+    lm_head = embed if cfg.tie_embeddings or "lm_head" not in tensors else get("lm_head")
+    return DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm"), lm_head=lm_head, layers=layers,
+                          tp_rank=tp_rank, tp_world=tp_world)

@@ -1,0 +1,111 @@
+"""Whole-model checks of the device engine against the PyTorch fp32 restatement of the stack."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _engine(cfg, batch, max_len, max_tokens, use_graphs=True, seed=0):
+    from poot_b200.runtime.engine import DecoderEngine
+    from poot_b200.runtime.session import FixedBatchSession
+    from poot_b200.runtime.weights import random_weights
+    w = random_weights(cfg, "cuda", seed=seed, std=0.05)
+    bps = (max_len + 15) // 16
+    eng = DecoderEngine(w, num_blocks=batch * bps, max_seqs=batch, max_tokens=max_tokens, max_blocks_per_seq=bps,
+                        use_graphs=use_graphs)
+    return w, eng, FixedBatchSession(eng, batch, max_len)
+
+
+def _small_cfg(**kw):
+    from poot_b200.models.config import DecoderConfig
+    base = dict(n_layers=2, hidden=256, n_heads=4, n_kv_heads=2, head_dim=64, ffn=688, vocab=2048, max_position=512)
+    base.update(kw)
+    return DecoderConfig(**base)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_prefill_logits_match_reference(graphs):
+    from poot_b200.oracle.torch_ref import forward_logits
+    from poot_b200.ops import cuda_ops as K
+    cfg = _small_cfg()
+    w, eng, sess = _engine(cfg, batch=2, max_len=64, max_tokens=64, use_graphs=graphs)
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab, (2, 24), generator=g, dtype=torch.int32)
+    picked = sess.prefill_fast(prompts)
+    K.check_status()
+    for b in range(2):
+        ref = forward_logits(w, prompts[b].cuda())[-1]
+        got = eng.logits[b]
+        assert torch.isfinite(got).all()
+        err = (got - ref).abs().max().item()
+        assert err < 0.05 * max(1.0, ref.abs().max().item()), err
+        assert picked[b, 1] == -1
+        top2 = torch.topk(ref, 2).values
+        if (top2[0] - top2[1]) > 0.05:
+            assert picked[b, 0] == int(ref.argmax())
+
+
+def test_decode_steps_equal_prefill():
+    """Decoding token by token through the paged cache gives the logits of a one-shot prefill."""
+    cfg = _small_cfg(n_heads=8, n_kv_heads=2, head_dim=128, hidden=512, ffn=1024)
+    w, eng, sess = _engine(cfg, batch=1, max_len=64, max_tokens=64)
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, cfg.vocab, (1, 20), generator=g, dtype=torch.int32)
+    sess.prefill_fast(toks)
+    full = eng.logits[0].clone()
+    w2, eng2, sess2 = _engine(cfg, batch=1, max_len=64, max_tokens=64)
+    sess2.prefill_fast(toks[:, :12])
+    for t in range(12, 20):
+        sess2.decode([int(toks[0, t])])
+    err = (eng2.logits[0] - full).abs().max().item()
+    assert err < 0.03 * max(1.0, full.abs().max().item()), err
+
+
+def test_decode_batch64_uses_tensor_core_path():
+    from poot_b200.oracle.torch_ref import forward_logits
+    from poot_b200.ops import cuda_ops as K
+    cfg = _small_cfg(hidden=512, ffn=1536, n_heads=8, n_kv_heads=2, head_dim=64)
+    B = 64
+    w, eng, sess = _engine(cfg, batch=B, max_len=32, max_tokens=B * 8)
+    g = torch.Generator().manual_seed(2)
+    prompts = torch.randint(0, cfg.vocab, (B, 8), generator=g, dtype=torch.int32)
+    sess.prefill_fast(prompts)
+    nxt = torch.randint(0, cfg.vocab, (B,), generator=g, dtype=torch.int32)
+    sess.decode(nxt.tolist())
+    K.check_status()
+    for b in (0, 31, 63):
+        seq = torch.cat([prompts[b], nxt[b:b + 1]]).cuda()
+        ref = forward_logits(w, seq)[-1]
+        err = (eng.logits[b] - ref).abs().max().item()
+        assert err < 0.05 * max(1.0, ref.abs().max().item()), (b, err)
+
+
+def test_chained_decode_matches_stepwise():
+    cfg = _small_cfg()
+    w, eng, sess = _engine(cfg, batch=2, max_len=64, max_tokens=64)
+    g = torch.Generator().manual_seed(3)
+    prompts = torch.randint(0, cfg.vocab, (2, 10), generator=g, dtype=torch.int32)
+    first = sess.prefill_fast(prompts)[:, 0].tolist()
+    toks = list(first)
+    stepwise = []
+    for _ in range(6):
+        toks = sess.decode(toks)[:, 0].tolist()
+        stepwise.append(list(toks))
+    w2, eng2, sess2 = _engine(cfg, batch=2, max_len=64, max_tokens=64)
+    first2 = sess2.prefill_fast(prompts)[:, 0].tolist()
+    assert first2 == first
+    sess2.decode_chain(first2, steps=6)
+    torch.cuda.synchronize()
+    assert eng2.picked[:2, 0].tolist() == stepwise[-1]
+
+
+def test_qk_norm_and_window_model():
+    from poot_b200.oracle.torch_ref import forward_logits
+    cfg = _small_cfg(qk_norm=True, sliding_window=8)
+    w, eng, sess = _engine(cfg, batch=1, max_len=64, max_tokens=64)
+    g = torch.Generator().manual_seed(4)
+    toks = torch.randint(0, cfg.vocab, (1, 30), generator=g, dtype=torch.int32)
+    sess.prefill_fast(toks)
+    ref = forward_logits(w, toks[0].cuda())[-1]
+    err = (eng.logits[0] - ref).abs().max().item()
+    assert err < 0.05 * max(1.0, ref.abs().max().item()), err
