@@ -45,6 +45,7 @@ attn_paged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,  // row str
   __shared__ float s_m[ATT_WARPS][NREP];
   __shared__ float s_l[ATT_WARPS][NREP];
 
+  pdl_wait(); pdl_launch();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int c = lane % LPP, g = lane / LPP;
   const int kvh = blockIdx.x / head_groups;
@@ -246,6 +247,7 @@ attn_paged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,  // row str
 // out[row, head, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
 __global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     __nv_bfloat16* __restrict__ out, int out_stride, int Hq, int D, int splits) {
+  pdl_wait(); pdl_launch();
   const int row = blockIdx.y, head = blockIdx.x;
   size_t pi = ((size_t)row * Hq + head) * splits;
   float M = -INFINITY;
@@ -273,9 +275,10 @@ static int launch_attn(const void* q, int q_stride, const void* kpool, const voi
   int hgs = n_rep / nrep_t;
   dim3 grid(Hkv * hgs, R, splits), block(ATT_WARPS * 32);
 #define POOT_ATT(NR)                                                                                        \
-  attn_paged_kernel<D, NR><<<grid, block, 0, s>>>((const __nv_bfloat16*)q, q_stride,                       \
+  err = launch_k(attn_paged_kernel<D, NR>, grid, block, 0, s, (const __nv_bfloat16*)q, q_stride,            \
       (const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, bt, max_blocks, row_seq, row_ctx,            \
       (__nv_bfloat16*)out, out_stride, part_o, part_ml, Hq, Hkv, hgs, scale, softcap, window, splits)
+  int err = 0;
   switch (nrep_t) {
     case 1: POOT_ATT(1); break;
     case 2: POOT_ATT(2); break;
@@ -283,12 +286,10 @@ static int launch_attn(const void* q, int q_stride, const void* kpool, const voi
     default: return (int)cudaErrorInvalidValue;
   }
 #undef POOT_ATT
-  int err = (int)cudaGetLastError();
   if (err) return err;
   if (splits > 1) {
-    attn_combine_kernel<<<dim3(Hq, R), D <= 128 ? D : 128, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, out_stride,
-                                                                   Hq, D, splits);
-    err = (int)cudaGetLastError();
+    err = launch_k(attn_combine_kernel, dim3(Hq, R), dim3(D <= 128 ? D : 128), 0, s, (const float*)part_o,
+                   (const float*)part_ml, (__nv_bfloat16*)out, out_stride, Hq, D, splits);
   }
   return err;
 }

@@ -83,4 +83,29 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return v;
 }
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// Every kernel of the library starts with pdl_wait() (block until the preceding kernel's memory is
+// visible; a no-op for an ordinary launch) and pdl_launch() (let the next kernel's CTAs be scheduled
+// while this one still runs).  With the library-wide switch on, launchers add the programmatic stream
+// serialization attribute, so launch latency and kernel prologues overlap the predecessor's tail.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_poot_pdl;
+
+template <typename... KArgs, typename... Args>
+inline int launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_poot_pdl ? 1 : 0;
+  return (int)cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
+
 }  // namespace poot

@@ -1,0 +1,306 @@
+// Skinny GEMM for decode batches (1 <= M <= 128 tokens):   out[M,N] = X[M,K] . W[N,K]^T
+//
+// Decode GEMMs are weight-streaming problems, so the weight is the 128-row MMA operand
+// ("swap AB"): one CTA owns 128 weight rows, the few tokens are the MMA N dimension (16..128),
+// and a deep TMA ring keeps >= 64 KB of weight bytes in flight per SM.  Small-N projections
+// (o_proj, down_proj, qkv) cannot fill 148 SMs with row tiles alone, so a thread-block cluster
+// of CK CTAs splits K for one row tile and reduces the fp32 tiles through distributed shared
+// memory: no partial buffers in HBM, and the epilogue (bf16 / fp32 store, residual add, SwiGLU
+// over interleaved gate/up rows) runs on the reduced values.
+//
+//   warp 0      TMA producer: weight tiles are requested before griddepcontrol.wait (they do not
+//               depend on the previous kernel), activation tiles after it
+//   warp 1      TMEM allocator + tcgen05.mma issuer (D[128 x BT] fp32 in TMEM)
+//   warps 2..5  TMEM -> shared fp32 tile; after the cluster barrier every CTA reduces its slab
+//               of rows over the CK peers with ld.shared::cluster and stores the result
+//
+// Reference behaviour covered: Contraction::DenseGemv / batched decode GEMM with register epilogues
+// (crates/poot-kernelgen/src/contraction/gemv.rs:1-3, contraction/mod.rs:70-84).
+#include "tc_common.cuh"
+
+namespace poot {
+
+enum { SEPI_STORE = 0, SEPI_F32 = 1, SEPI_RESID = 2, SEPI_SWIGLU = 3 };
+
+constexpr int SK_BM = 128;   // weight rows per CTA
+constexpr int SK_BK = 64;
+constexpr int SK_THREADS = 192;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
+  float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v;
+}
+
+template <int BT, int STAGES>
+struct SkinnySmem {
+  static constexpr int W_BYTES = SK_BM * SK_BK * 2;
+  static constexpr int X_BYTES = BT * SK_BK * 2;
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr int RED_BYTES = BT * SK_BM * 4;
+  static constexpr int RING = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFFSET = RING > RED_BYTES ? RING : RED_BYTES;
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;
+};
+
+template <int BT, int STAGES, int EPI>
+__global__ void __launch_bounds__(SK_THREADS)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                   void* __restrict__ out, const __nv_bfloat16* resid, int M, int N, int K, int ldo, int CK,
+                   int* __restrict__ status) {
+  using S = SkinnySmem<BT, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = tc::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t full_bar = base + S::BAR_OFFSET;
+  const uint32_t empty_bar = full_bar + STAGES * 8;
+  const uint32_t accum_bar = empty_bar + STAGES * 8;
+  const uint32_t tmem_slot = accum_bar + 8;
+  volatile uint32_t* tmem_slot_gen =
+      reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + (2 * STAGES + 1) * 8);
+  float* red = reinterpret_cast<float*>(gen_base);  // [BT][128] fp32, reuses the ring after the last MMA
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t crank = CK > 1 ? cluster_ctarank() : 0u;
+  const int row_tile = blockIdx.x / CK;
+  const int n0 = row_tile * SK_BM;
+  const int total_kt = (K + SK_BK - 1) / SK_BK;
+  const int per = (total_kt + CK - 1) / CK;
+  const int kt_begin = (int)crank * per;
+  int kt_end = kt_begin + per;
+  if (kt_end > total_kt) kt_end = total_kt;
+  const int num_kt = kt_end > kt_begin ? kt_end - kt_begin : 0;
+  constexpr uint32_t TMEM_COLS = BT < 32 ? 32 : BT;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar + 8 * s, 1); tc::mbar_init(empty_bar + 8 * s, 1); }
+    tc::mbar_init(accum_bar, 1);
+    tc::fence_barrier_init();
+    tc::fence_proxy_async();
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, TMEM_COLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_gen;
+  pdl_launch();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tc::tma_prefetch_desc(&tmW);
+      tc::tma_prefetch_desc(&tmX);
+      // Weight tiles of the first ring pass do not depend on the previous kernel's output.
+      const int pre = num_kt < STAGES ? num_kt : STAGES;
+      for (int i = 0; i < pre; ++i) {
+        tc::mbar_expect_tx(full_bar + 8 * i, S::STAGE_BYTES);
+        tc::tma_load_2d(base + i * S::STAGE_BYTES, &tmW, (kt_begin + i) * SK_BK, n0, full_bar + 8 * i);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tc::tma_load_2d(base + i * S::STAGE_BYTES + S::W_BYTES, &tmX, (kt_begin + i) * SK_BK, 0, full_bar + 8 * i);
+      int issued = pre;
+      bool ok = true;
+      for (int i = pre; i < num_kt; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+        if (!tc::mbar_wait(empty_bar + 8 * s, ph ^ 1u)) { ok = false; break; }
+        tc::mbar_expect_tx(full_bar + 8 * s, S::STAGE_BYTES);
+        const uint32_t sa = base + s * S::STAGE_BYTES;
+        const int kx = (kt_begin + i) * SK_BK;
+        tc::tma_load_2d(sa, &tmW, kx, n0, full_bar + 8 * s);
+        tc::tma_load_2d(sa + S::W_BYTES, &tmX, kx, 0, full_bar + 8 * s);
+        ++issued;
+      }
+      if (!ok) {
+        atomicExch(status, (int)kTimeoutProducer);
+        for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j)
+          tc::mbar_wait(full_bar + 8 * (j % STAGES), (uint32_t)(j / STAGES) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::idesc_bf16_f32(SK_BM, BT);
+      bool ok = true;
+      for (int i = 0; i < num_kt; ++i) {
+        const int s = i % STAGES;
+        const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
+        if (!tc::mbar_wait(full_bar + 8 * s, ph)) { ok = false; break; }
+        tc::tc_fence_after();
+        const uint32_t sa = base + s * S::STAGE_BYTES;
+        const uint64_t wdesc = tc::smem_desc_sw128(sa);
+        const uint64_t xdesc = tc::smem_desc_sw128(sa + S::W_BYTES);
+#pragma unroll
+        for (int k = 0; k < SK_BK / 16; ++k)
+          tc::mma_bf16_ss(tmem_base, wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc,
+                          (i > 0 || k > 0) ? 1u : 0u);
+        tc::tc_commit(empty_bar + 8 * s);
+      }
+      if (!ok) atomicExch(status, (int)kTimeoutMma);
+      tc::tc_commit(accum_bar);
+    }
+  } else {
+    // TMEM lane (weight row) quadrant = warp % 4; columns = tokens
+    const int quad = warp & 3;
+    bool ok = tc::mbar_wait(accum_bar, 0);
+    if (!ok && lane == 0) atomicExch(status, (int)kTimeoutEpilogue);
+    tc::tc_fence_after();
+    const int r = quad * 32 + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BT; c0 += 32) {
+      uint32_t v[32];
+      if (num_kt > 0 && ok) {
+        if (BT >= 32) {
+          tc::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+        } else {
+          // BT == 16: the allocation is 32 columns wide; the upper 16 are never written by the MMA
+          tc::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16), v);
+        }
+        tc::tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (c0 + j < BT) red[(c0 + j) * SK_BM + r] = __uint_as_float(v[j]);
+    }
+  }
+
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (CK > 1) cluster_sync_all();
+
+  // ---- reduce this CTA's slab of rows over the cluster and store ----
+  pdl_wait();
+  const int slab = SK_BM / CK;
+  const int slab0 = (int)crank * slab;
+  const uint32_t red_s = base;  // shared-window address of red[0]
+  const int Mv = M < BT ? M : BT;
+  if (EPI == SEPI_SWIGLU) {
+    const int hp = slab >> 1;
+    for (int idx = threadIdx.x; idx < hp * Mv; idx += SK_THREADS) {
+      const int p = idx % hp, tok = idx / hp;
+      const int rr = slab0 + 2 * p;
+      float g = 0.f, u = 0.f;
+      for (int c = 0; c < CK; ++c) {
+        uint32_t a = red_s + (uint32_t)((tok * SK_BM + rr) * 4);
+        if (CK > 1) a = map_to_cta(a, (uint32_t)c);
+        g += ld_dsmem_f32(a);
+        u += ld_dsmem_f32(a + 4);
+      }
+      const int n = n0 + rr;
+      if (n < N)
+        reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * ldo + (n >> 1)] = __float2bfloat16(silu(g) * u);
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < slab * Mv; idx += SK_THREADS) {
+      const int p = idx % slab, tok = idx / slab;
+      const int rr = slab0 + p;
+      float v = 0.f;
+      for (int c = 0; c < CK; ++c) {
+        uint32_t a = red_s + (uint32_t)((tok * SK_BM + rr) * 4);
+        if (CK > 1) a = map_to_cta(a, (uint32_t)c);
+        v += ld_dsmem_f32(a);
+      }
+      const int n = n0 + rr;
+      if (n < N) {
+        if (EPI == SEPI_F32) {
+          reinterpret_cast<float*>(out)[(size_t)tok * ldo + n] = v;
+        } else {
+          if (EPI == SEPI_RESID) v += __bfloat162float(resid[(size_t)tok * ldo + n]);
+          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * ldo + n] = __float2bfloat16(v);
+        }
+      }
+    }
+  }
+  if (CK > 1) cluster_sync_all();  // no CTA may exit while a peer still reads its tile
+}
+
+template <int BT, int STAGES, int EPI>
+static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid, int M, int N,
+                             int K, int ldo, int CK, int pdl, int* status, cudaStream_t s) {
+  using S = SkinnySmem<BT, STAGES>;
+  auto kern = gemm_skinny_kernel<BT, STAGES, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int row_tiles = (N + SK_BM - 1) / SK_BM;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(row_tiles * CK, 1, 1);
+  cfg.blockDim = dim3(SK_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = S::TOTAL;
+  cfg.stream = s;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (CK > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = CK; attrs[na].val.clusterDim.y = 1; attrs[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (pdl || g_poot_pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return (int)cudaLaunchKernelEx(&cfg, kern, tw, tx, out, (const __nv_bfloat16*)resid, M, N, K, ldo, CK, status);
+}
+
+template <int BT, int STAGES>
+static int launch_skinny_epi(int epi, const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid,
+                             int M, int N, int K, int ldo, int CK, int pdl, int* status, cudaStream_t s) {
+  switch (epi) {
+    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace poot
+
+using namespace poot;
+
+// X [M, ldx] bf16 with M <= 128, W [N, K] bf16, out [M, ldo].  ck = cluster size (K split): 1, 2, 4 or 8.
+// pdl != 0 launches with programmatic stream serialization (the kernel waits on its predecessor itself).
+POOT_API int poot_gemm_skinny(int epi, const void* x, const void* W, void* out, const void* resid, int M, int N, int K,
+                              int ldx, int ldo, int ck, int pdl, int* status, cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 128 || K % 8 || ldx % 8) return (int)cudaErrorInvalidValue;
+  if (ck != 1 && ck != 2 && ck != 4 && ck != 8) return (int)cudaErrorInvalidValue;
+  if (epi == SEPI_SWIGLU && (N % 2)) return (int)cudaErrorInvalidValue;
+  if (epi == SEPI_RESID && resid == nullptr) return (int)cudaErrorInvalidValue;
+  if (status == nullptr) return (int)cudaErrorInvalidValue;
+  const int bt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  CUtensorMap tw, tx;
+  int e = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)K, SK_BM);
+  if (e) return e;
+  e = make_tmap_bf16_2d(&tx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt);
+  if (e) return e;
+  switch (bt) {
+    case 16: return launch_skinny_epi<16, 6>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+    case 32: return launch_skinny_epi<32, 5>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+    case 64: return launch_skinny_epi<64, 4>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+    default: return launch_skinny_epi<128, 3>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+  }
+}

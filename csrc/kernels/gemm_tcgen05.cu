@@ -122,6 +122,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const uint32_t tmem_slot = accum_bar + 8;
   volatile uint32_t* tmem_slot_gen = reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + (2 * STAGES + 1) * 8);
 
+  pdl_wait(); pdl_launch();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.x * GEMM_BM;
   const int n0 = blockIdx.y * BN;
@@ -286,9 +287,8 @@ static int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* o
   int total_kt = (K + GEMM_BK - 1) / GEMM_BK;
   int per = (total_kt + splits - 1) / splits;
   dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN, splits);
-  kern<<<grid, GEMM_THREADS, S::TOTAL, s>>>(ta, tb, out, (const __nv_bfloat16*)resid, M, N, K, ldo, per,
-                                            partial_stride, status);
-  return (int)cudaGetLastError();
+  return launch_k(kern, grid, dim3(GEMM_THREADS), (size_t)S::TOTAL, s, ta, tb, out, (const __nv_bfloat16*)resid, M, N, K,
+                  ldo, per, partial_stride, status);
 }
 
 template <int BN, int STAGES>

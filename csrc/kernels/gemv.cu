@@ -26,6 +26,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_bf16_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ W,
                  void* __restrict__ out, const __nv_bfloat16* __restrict__ resid, int N, int K,
                  int ldx, int ldo) {
+  pdl_wait(); pdl_launch();
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int gwarp = blockIdx.x * GEMV_WARPS + warp;
@@ -111,10 +112,10 @@ static int launch_gemv(int epi, const void* x, const void* W, void* out, const v
   const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
   const __nv_bfloat16* rb = (const __nv_bfloat16*)resid;
   switch (epi) {
-    case EPI_STORE: gemv_bf16_kernel<M, EPI_STORE><<<g, b, 0, s>>>(xb, wb, out, rb, N, K, ldx, ldo); break;
-    case EPI_F32: gemv_bf16_kernel<M, EPI_F32><<<g, b, 0, s>>>(xb, wb, out, rb, N, K, ldx, ldo); break;
-    case EPI_RESID: gemv_bf16_kernel<M, EPI_RESID><<<g, b, 0, s>>>(xb, wb, out, rb, N, K, ldx, ldo); break;
-    case EPI_SWIGLU: gemv_bf16_kernel<M, EPI_SWIGLU><<<g, b, 0, s>>>(xb, wb, out, rb, N, K, ldx, ldo); break;
+    case EPI_STORE: return launch_k(gemv_bf16_kernel<M, EPI_STORE>, g, b, 0, s, (const __nv_bfloat16*)xb, (const __nv_bfloat16*)wb, out, (const __nv_bfloat16*)rb, N, K, ldx, ldo);
+    case EPI_F32: return launch_k(gemv_bf16_kernel<M, EPI_F32>, g, b, 0, s, (const __nv_bfloat16*)xb, (const __nv_bfloat16*)wb, out, (const __nv_bfloat16*)rb, N, K, ldx, ldo);
+    case EPI_RESID: return launch_k(gemv_bf16_kernel<M, EPI_RESID>, g, b, 0, s, (const __nv_bfloat16*)xb, (const __nv_bfloat16*)wb, out, (const __nv_bfloat16*)rb, N, K, ldx, ldo);
+    case EPI_SWIGLU: return launch_k(gemv_bf16_kernel<M, EPI_SWIGLU>, g, b, 0, s, (const __nv_bfloat16*)xb, (const __nv_bfloat16*)wb, out, (const __nv_bfloat16*)rb, N, K, ldx, ldo);
     default: return (int)cudaErrorInvalidValue;
   }
   return (int)cudaGetLastError();

@@ -29,6 +29,7 @@ rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict_
                const int* __restrict__ slots, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                const __nv_bfloat16* __restrict__ q_norm_w, const __nv_bfloat16* __restrict__ k_norm_w,
                float norm_eps, int T, int Hq, int Hkv, int D, int rot, int max_pos) {
+  pdl_wait(); pdl_launch();
   const int lane = threadIdx.x & 31;
   const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int heads = Hq + 2 * Hkv;
@@ -102,7 +103,7 @@ POOT_API int poot_rope_kv_write(const void* qkv, void* q_out, void* kpool, void*
   int items = T * (Hq + 2 * Hkv);
   int blocks = (items + 7) / 8;
   if (kv_dtype == 0)
-    rope_kv_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(
+    return launch_k(rope_kv_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s,
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, positions,
         slots, cos_t, sin_t, (const __nv_bfloat16*)q_norm_w, (const __nv_bfloat16*)k_norm_w, norm_eps, T, Hq, Hkv,
         D, rot, max_pos);

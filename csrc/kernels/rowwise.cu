@@ -9,11 +9,14 @@
 
 namespace poot {
 
+int g_poot_pdl = 0;
+
 // ---------------------------------------------------------------------------
 // Embedding gather: out[t, :] = table[ids[t], :]   (bf16 rows, D % 8 == 0)
 // ---------------------------------------------------------------------------
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const uint4* __restrict__ table,
                                     uint4* __restrict__ out, int T, int D8, int vocab) {
+  pdl_wait(); pdl_launch();
   int t = blockIdx.x;
   int id = ids[t];
   if (id < 0 || id >= vocab) id = 0;
@@ -51,6 +54,7 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,      // [T,D] input / residu
                __nv_bfloat16* __restrict__ y,            // [T,D] normalized output (or null)
                int D, float eps) {
   __shared__ float red[32];
+  pdl_wait(); pdl_launch();
   const int row = blockIdx.x;
   const int D8 = D >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * D);
@@ -101,6 +105,7 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x,      // [T,D] input / residu
 //   interleaved layout: gu[t, 2j] = gate_j, gu[t, 2j+1] = up_j
 __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
                               int T, int F, int interleaved) {
+  pdl_wait(); pdl_launch();
   size_t n = (size_t)T * F;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     size_t t = i / F;
@@ -118,6 +123,7 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
 }
 
 __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, size_t n) {
+  pdl_wait(); pdl_launch();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     out[i] = __float2bfloat16(__bfloat162float(a[i]) + __bfloat162float(b[i]));
 }
@@ -125,6 +131,7 @@ __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_
 // h[t,:] += sum_p partial[p,t,:]   (split-K reduction without a following norm)
 __global__ void reduce_partials_kernel(const __nv_bfloat16* h, const float* partials, int P,
                                        size_t partial_stride, __nv_bfloat16* out, size_t n) {
+  pdl_wait(); pdl_launch();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     float v = h ? __bfloat162float(h[i]) : 0.f;
     for (int p = 0; p < P; ++p) v += partials[p * partial_stride + i];
@@ -133,10 +140,12 @@ __global__ void reduce_partials_kernel(const __nv_bfloat16* h, const float* part
 }
 
 __global__ void cast_f32_bf16_kernel(const float* in, __nv_bfloat16* out, size_t n) {
+  pdl_wait(); pdl_launch();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     out[i] = __float2bfloat16(in[i]);
 }
 __global__ void cast_bf16_f32_kernel(const __nv_bfloat16* in, float* out, size_t n) {
+  pdl_wait(); pdl_launch();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
     out[i] = __bfloat162float(in[i]);
 }
@@ -148,6 +157,7 @@ __global__ void decode_advance_kernel(const int* __restrict__ picked, int* __res
                                       int* __restrict__ positions, int* __restrict__ slots, int* __restrict__ ctx,
                                       const int* __restrict__ block_tables, int max_blocks,
                                       const int* __restrict__ row_seq, int B) {
+  pdl_wait(); pdl_launch();
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= B) return;
   if (slots[i] < 0) return;  // padding row
@@ -164,10 +174,13 @@ __global__ void decode_advance_kernel(const int* __restrict__ picked, int* __res
 
 using namespace poot;
 
+POOT_API void poot_set_pdl(int on) { g_poot_pdl = on; }
+POOT_API int poot_get_pdl() { return g_poot_pdl; }
+
 POOT_API int poot_decode_advance(const int* picked, int* tokens, int* positions, int* slots, int* ctx,
                                  const int* block_tables, int max_blocks, const int* row_seq, int B, cudaStream_t s) {
   if (B == 0) return 0;
-  decode_advance_kernel<<<(B + 127) / 128, 128, 0, s>>>(picked, tokens, positions, slots, ctx, block_tables,
+  return launch_k(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, picked, tokens, positions, slots, ctx, block_tables,
                                                         max_blocks, row_seq, B);
   return (int)cudaGetLastError();
 }
@@ -176,7 +189,7 @@ POOT_API int poot_embed_gather(const int* ids, const void* table, void* out, int
                                cudaStream_t s) {
   if (D % 8) return (int)cudaErrorInvalidValue;
   if (T == 0) return 0;
-  embed_gather_kernel<<<T, 128, 0, s>>>(ids, (const uint4*)table, (uint4*)out, T, D / 8, vocab);
+  return launch_k(embed_gather_kernel, dim3(T), dim3(128), 0, s, ids, (const uint4*)table, (uint4*)out, T, D / 8, vocab);
   return (int)cudaGetLastError();
 }
 
@@ -191,11 +204,11 @@ POOT_API int poot_rmsnorm(const void* x, void* h_out, const float* partials, int
   const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
   __nv_bfloat16* yb = (__nv_bfloat16*)y;
   int D8 = D / 8;
-  if (D8 <= 128) rmsnorm_kernel<128, 1><<<T, 128, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
-  else if (D8 <= 256) rmsnorm_kernel<256, 1><<<T, 256, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
-  else if (D8 <= 512) rmsnorm_kernel<512, 1><<<T, 512, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
-  else if (D8 <= 1024) rmsnorm_kernel<512, 2><<<T, 512, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
-  else if (D8 <= 2048) rmsnorm_kernel<512, 4><<<T, 512, 0, s>>>(xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  if (D8 <= 128) return launch_k(rmsnorm_kernel<128, 1>, dim3(T), dim3(128), 0, s, xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else if (D8 <= 256) return launch_k(rmsnorm_kernel<256, 1>, dim3(T), dim3(256), 0, s, xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else if (D8 <= 512) return launch_k(rmsnorm_kernel<512, 1>, dim3(T), dim3(512), 0, s, xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else if (D8 <= 1024) return launch_k(rmsnorm_kernel<512, 2>, dim3(T), dim3(512), 0, s, xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
+  else if (D8 <= 2048) return launch_k(rmsnorm_kernel<512, 4>, dim3(T), dim3(512), 0, s, xb, hb, partials, P, (size_t)partial_stride, wb, yb, D, eps);
   else return (int)cudaErrorInvalidValue;
   return (int)cudaGetLastError();
 }
@@ -205,7 +218,7 @@ POOT_API int poot_swiglu(const void* gu, void* out, int T, int F, int interleave
   if (n == 0) return 0;
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  swiglu_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F, interleaved);
+  return launch_k(swiglu_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F, interleaved);
   return (int)cudaGetLastError();
 }
 
@@ -213,7 +226,7 @@ POOT_API int poot_add_bf16(const void* a, const void* b, void* out, long long n,
   if (n == 0) return 0;
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  add_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, (size_t)n);
+  return launch_k(add_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, (size_t)n);
   return (int)cudaGetLastError();
 }
 
@@ -222,7 +235,7 @@ POOT_API int poot_reduce_partials(const void* h, const float* partials, int P, l
   if (n == 0) return 0;
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  reduce_partials_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)h, partials, P, (size_t)partial_stride,
+  return launch_k(reduce_partials_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)h, partials, P, (size_t)partial_stride,
                                                 (__nv_bfloat16*)out, (size_t)n);
   return (int)cudaGetLastError();
 }
@@ -231,13 +244,13 @@ POOT_API int poot_cast_f32_bf16(const float* in, void* out, long long n, cudaStr
   if (n == 0) return 0;
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  cast_f32_bf16_kernel<<<blocks, 256, 0, s>>>(in, (__nv_bfloat16*)out, (size_t)n);
+  return launch_k(cast_f32_bf16_kernel, dim3(blocks), dim3(256), 0, s, in, (__nv_bfloat16*)out, (size_t)n);
   return (int)cudaGetLastError();
 }
 POOT_API int poot_cast_bf16_f32(const void* in, float* out, long long n, cudaStream_t s) {
   if (n == 0) return 0;
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
-  cast_bf16_f32_kernel<<<blocks, 256, 0, s>>>((const __nv_bfloat16*)in, out, (size_t)n);
+  return launch_k(cast_bf16_f32_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)in, out, (size_t)n);
   return (int)cudaGetLastError();
 }

@@ -57,6 +57,7 @@ argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunk, int 
                     int* __restrict__ pi) {
   __shared__ float sv[SAMP_THREADS / 32];
   __shared__ int si[SAMP_THREADS / 32], sb[SAMP_THREADS / 32];
+  pdl_wait(); pdl_launch();
   const int row = blockIdx.y, g = blockIdx.x;
   const int start = g * chunk;
   const int end = min(start + chunk, vocab);
@@ -86,6 +87,7 @@ argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunk, int 
 
 __global__ void argmax_combine_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int groups, int vocab,
                                       int* __restrict__ out) {
+  pdl_wait(); pdl_launch();
   const int row = blockIdx.x, l = threadIdx.x;  // one warp
   Cand c{0.f, -1}; int b = vocab;
   for (int g = l; g < groups; g += 32) {
@@ -137,6 +139,7 @@ sample_gumbel_kernel(const float* __restrict__ logits, int vocab, const float* _
   __shared__ unsigned long long shu[32];
   __shared__ int shi[32];
   __shared__ float shv[32];
+  pdl_wait(); pdl_launch();
   const int row = blockIdx.x;
   const float* lr = logits + (size_t)row * vocab;
   const float inv_temp = params[row * 4 + 0], floor_offset = params[row * 4 + 1];
@@ -231,6 +234,7 @@ sample_gumbel_kernel(const float* __restrict__ logits, int vocab, const float* _
 }
 
 __global__ void random_uniform_kernel(const int* __restrict__ seeds, int cols, float* __restrict__ out, size_t n) {
+  pdl_wait(); pdl_launch();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   size_t r = i / cols;
@@ -247,22 +251,20 @@ POOT_API int poot_argmax(const float* logits, int rows, int vocab, int chunk, fl
   if (rows == 0) return 0;
   int groups = (vocab + chunk - 1) / chunk;
   if (groups < 1) groups = 1;
-  argmax_chunk_kernel<<<dim3(groups, rows), SAMP_THREADS, 0, s>>>(logits, vocab, chunk, groups, pv, pi);
-  argmax_combine_kernel<<<rows, 32, 0, s>>>(pv, pi, groups, vocab, out);
-  return (int)cudaGetLastError();
+  int e = launch_k(argmax_chunk_kernel, dim3(groups, rows), dim3(SAMP_THREADS), 0, s, logits, vocab, chunk, groups, pv, pi);
+  if (e) return e;
+  return launch_k(argmax_combine_kernel, dim3(rows), dim3(32), 0, s, (const float*)pv, (const int*)pi, groups, vocab, out);
 }
 
 POOT_API int poot_sample_gumbel(const float* logits, int rows, int vocab, const float* params, const int* top_k,
                                 const int* seeds, int rule, int* out, cudaStream_t s) {
   if (rows == 0) return 0;
   if (rule < 1 || rule > 3) return (int)cudaErrorInvalidValue;
-  sample_gumbel_kernel<<<rows, SAMP_BIG, 0, s>>>(logits, vocab, params, top_k, seeds, rule, out);
-  return (int)cudaGetLastError();
+  return launch_k(sample_gumbel_kernel, dim3(rows), dim3(SAMP_BIG), 0, s, logits, vocab, params, top_k, seeds, rule, out);
 }
 
 POOT_API int poot_random_uniform(const int* seeds, int rows, int cols, float* out, cudaStream_t s) {
   size_t n = (size_t)rows * cols;
   if (n == 0) return 0;
-  random_uniform_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(seeds, cols, out, n);
-  return (int)cudaGetLastError();
+  return launch_k(random_uniform_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, s, seeds, cols, out, n);
 }

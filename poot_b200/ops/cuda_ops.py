@@ -29,6 +29,7 @@ _SIGS = {
     "poot_gemv_bf16": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "poot_gemm_bf16_tcgen05": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,
                                _P, _P],
+    "poot_gemm_skinny": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "poot_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_int, _P],
     "poot_attn_paged": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float,
@@ -216,11 +217,51 @@ def gemm(x: torch.Tensor, W: torch.Tensor, epi: int = EPI_STORE, out: Optional[t
     return out
 
 
+def skinny_cluster(N: int, Kd: int) -> int:
+    """Cluster size (K split) that fills the 148 SMs for a weight of N rows."""
+    row_tiles = (N + 127) // 128
+    ck = 1
+    while ck < 8 and row_tiles * ck < 148 and (Kd // 64) // (ck * 2) >= 4:
+        ck *= 2
+    return ck
+
+
+def gemm_skinny(x: torch.Tensor, W: torch.Tensor, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
+                resid: Optional[torch.Tensor] = None, ck: Optional[int] = None) -> torch.Tensor:
+    """Swap-AB tcgen05 GEMM for ``M <= 128`` tokens with cluster split-K reduced through DSMEM."""
+    _need_cuda(x, W)
+    assert x.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and W.is_contiguous()
+    M, Kd = x.shape
+    N = W.shape[0]
+    assert W.shape[1] == Kd and x.stride(1) == 1 and M <= 128 and epi != EPI_PARTIAL
+    if ck is None:
+        ck = skinny_cluster(N, Kd)
+    out = _out_for(epi, M, N, x.device, out)
+    st = status_word(x.device)
+    check(_fn("poot_gemm_skinny")(epi, _ptr(x), _ptr(W), _ptr(out), _ptr(resid), M, N, Kd, x.stride(0), out.stride(0),
+                                  ck, 0, _ptr(st), _stream()), "gemm_skinny")
+    return out
+
+
+GEMV_MAX_M = 4          # rows served by the SIMT GEMV; 0 routes every decode GEMM to the tensor-core kernel
+
+
+def set_pdl(on: bool) -> None:
+    """Library-wide switch: launch kernels with programmatic stream serialization."""
+    lib = kernels()
+    lib.poot_set_pdl.argtypes = [c_int]
+    lib.poot_set_pdl.restype = None
+    lib.poot_set_pdl(int(on))
+
+
 def linear(x: torch.Tensor, W: torch.Tensor, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
            resid: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Pick the decode GEMV (``M <= 4``) or the tensor-core GEMM."""
-    if x.shape[0] <= 4:
+    """Pick the decode GEMV (``M <= 4``), the skinny swap-AB GEMM (``M <= 128``) or the tiled GEMM."""
+    M = x.shape[0]
+    if M <= GEMV_MAX_M:
         return gemv(x, W, epi, out, resid)
+    if M <= 128:
+        return gemm_skinny(x, W, epi, out, resid)
     return gemm(x, W, epi, out, resid)
 
 

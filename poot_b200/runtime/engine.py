@@ -124,7 +124,7 @@ class DecoderEngine:
         """
         h = self.h[:T]
         N, Kdim = W.shape
-        if T <= 4:
+        if T <= 128:
             self._linear(x, W, K.EPI_RESID, h, h)
             return None
         tiles = ((T + 127) // 128) * ((N + 63) // 64)

@@ -93,6 +93,44 @@ def test_gemm_tcgen05(K, bn, M, N, Kd):
     K.check_status()
 
 
+@pytest.mark.parametrize("M", [1, 3, 16, 17, 64, 100, 128])
+@pytest.mark.parametrize("N,Kd,ck", [(4096, 4096, 8), (6144, 4096, 4), (1024, 14336, 8), (28672, 1024, 1), (776, 520, 2),
+                                     (256, 192, 4)])
+def test_gemm_skinny(K, M, N, Kd, ck):
+    x, W = bf(M, Kd, seed=1), bf(N, Kd, scale=0.05, seed=2)
+    ref = x.float() @ W.float().T
+    close(K.gemm_skinny(x, W, K.EPI_STORE, ck=ck), ref)
+    close(K.gemm_skinny(x, W, K.EPI_F32, ck=ck), ref, 1e-3, 1e-3)
+    res = bf(M, N, seed=3)
+    close(K.gemm_skinny(x, W, K.EPI_RESID, resid=res, ck=ck), ref + res.float())
+    close(K.gemm_skinny(x, W, K.EPI_SWIGLU, ck=ck), torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2])
+    h = res.clone()
+    K.gemm_skinny(x, W, K.EPI_RESID, out=h, resid=h)
+    close(h, ref + res.float())
+    K.check_status()
+
+
+def test_pdl_chain_matches_plain(K):
+    """A chain of dependent kernels gives the same result with programmatic dependent launch on and off."""
+    x, W1, W2 = bf(8, 1024, seed=1), bf(2048, 1024, scale=0.05, seed=2), bf(1024, 1024, scale=0.05, seed=3)
+    w = bf(1024, seed=4)
+
+    def chain():
+        a = K.gemm_skinny(x, W1, K.EPI_SWIGLU)
+        b = K.gemm_skinny(a, W2, K.EPI_RESID, resid=x)
+        return K.rmsnorm(b, w, 1e-5)
+
+    plain = chain().clone()
+    K.set_pdl(True)
+    try:
+        for _ in range(5):
+            got = chain()
+        torch.cuda.synchronize()
+    finally:
+        K.set_pdl(False)
+    assert torch.equal(plain, got)
+
+
 @pytest.mark.parametrize("splits", [2, 4, 7])
 def test_gemm_tcgen05_splitk(K, splits):
     M, N, Kd = 64, 4096, 14336
