@@ -96,6 +96,8 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--skip-bs1", action="store_true")
+    ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch between kernels")
+    ap.add_argument("--gemv-max-m", type=int, default=None, help="rows served by the SIMT GEMV (0 = tensor cores)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -125,6 +127,9 @@ def main() -> None:
         from poot_b200.parallel.tp import make_comm
         comm = make_comm(args.comm, rank, world, dev)
 
+    K.set_pdl(bool(args.pdl))
+    if args.gemv_max_m is not None:
+        K.GEMV_MAX_M = args.gemv_max_m
     cfg = PRESETS[args.model]()
     W, Ksteps, B, P = max(args.warmup, 3), args.steps, args.batch, args.prompt
     max_len = P + (W + Ksteps) * 2 + 64

@@ -1,0 +1,145 @@
+#!/usr/bin/env python
+"""Kernel bank: kernel-level cases timed on the device against their memory / compute roofline.
+
+The counterpart of the reference's performance bank (benchmarks/performance-bank/cases.json: dense and
+packed decode GEMV, batched decode GEMM, prefill GEMMs, attention, expert routing).  Each case launches
+one kernel over rotating operand copies larger than L2 (so every launch streams from HBM), captured in
+a CUDA graph so that launch overhead is not in the number, and reports microseconds per launch plus the
+achieved fraction of the measured peaks (MEASURED_PEAKS.json when present).
+
+    python benchmarks/kernel_bank.py [--case NAME ...] [--pdl 0|1] [--once]
+
+``--once`` runs each selected case a single time without timing (for use under ncu).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+from poot_b200.ops import cuda_ops as K  # noqa: E402
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+def time_graph(fns, reps=5):
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        for f in fns:
+            f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        for _ in range(reps):
+            for f in fns:
+                f()
+    g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    g.replay()
+    g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (2 * reps * len(fns))
+
+
+def rnd(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def gemm_case(M, N, Kd, kind):
+    copies = max(2, int(400e6 // (N * Kd * 2)) + 1)
+    x = rnd(M, Kd)
+    Ws = [rnd(N, Kd, scale=0.02) for _ in range(copies)]
+    outs = [torch.empty(M, N, device="cuda", dtype=torch.bfloat16) for _ in range(copies)]
+    if kind == "gemv":
+        fns = [(lambda W=W, o=o: K.gemv(x, W, K.EPI_STORE, out=o)) for W, o in zip(Ws, outs)]
+    elif kind == "skinny":
+        fns = [(lambda W=W, o=o: K.gemm_skinny(x, W, K.EPI_STORE, out=o)) for W, o in zip(Ws, outs)]
+    else:
+        fns = [(lambda W=W, o=o: K.gemm(x, W, K.EPI_STORE, out=o)) for W, o in zip(Ws, outs)]
+    return fns, N * Kd * 2 + M * Kd * 2 + M * N * 2, 2.0 * M * N * Kd
+
+
+def attn_case(B, ctx, Hq=32, Hkv=8, D=128):
+    bps = (ctx + 15) // 16
+    nb = B * bps
+    kpool, vpool = rnd(nb, Hkv, 16, D), rnd(nb, Hkv, 16, D)
+    bt = torch.randperm(nb, device="cuda").to(torch.int32).view(B, bps)
+    q = rnd(B, Hq * D)
+    row_ctx = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    out = torch.empty(B, Hq * D, device="cuda", dtype=torch.bfloat16)
+    splits = 1 if B * Hkv >= 148 else max(1, min(16, 296 // (B * Hkv)))
+    scr = (torch.empty(B * Hq * splits * D, device="cuda"), torch.empty(B * Hq * splits * 2, device="cuda"))
+    fn = lambda: K.attn_paged(q, kpool, vpool, bt, None, row_ctx, Hq, Hkv, D, 1 / math.sqrt(D), out=out,
+                              splits=splits, scratch=scr)
+    return [fn], 2 * B * ctx * Hkv * D * 2, 4.0 * B * ctx * Hq * D
+
+
+CASES = {
+    "dense-decode-gemv-qkv": lambda: gemm_case(1, 6144, 4096, "skinny"),
+    "dense-decode-gemv-o": lambda: gemm_case(1, 4096, 4096, "skinny"),
+    "dense-decode-gemv-gate-up": lambda: gemm_case(1, 28672, 4096, "skinny"),
+    "dense-decode-gemv-down": lambda: gemm_case(1, 4096, 14336, "skinny"),
+    "dense-decode-gemv-lm-head": lambda: gemm_case(1, 128256, 4096, "skinny"),
+    "simt-decode-gemv-gate-up": lambda: gemm_case(1, 28672, 4096, "gemv"),
+    "batched-decode-gemm-m8-gate-up": lambda: gemm_case(8, 28672, 4096, "skinny"),
+    "batched-decode-gemm-m64-qkv": lambda: gemm_case(64, 6144, 4096, "skinny"),
+    "batched-decode-gemm-m64-o": lambda: gemm_case(64, 4096, 4096, "skinny"),
+    "batched-decode-gemm-m64-gate-up": lambda: gemm_case(64, 28672, 4096, "skinny"),
+    "batched-decode-gemm-m64-down": lambda: gemm_case(64, 4096, 14336, "skinny"),
+    "batched-decode-gemm-m64-lm-head": lambda: gemm_case(64, 128256, 4096, "skinny"),
+    "prefill-gemm-m512-qkv": lambda: gemm_case(512, 6144, 4096, "tiled"),
+    "prefill-gemm-m512-gate-up": lambda: gemm_case(512, 28672, 4096, "tiled"),
+    "prefill-gemm-m512-down": lambda: gemm_case(512, 4096, 14336, "tiled"),
+    "prefill-gemm-m2048-gate-up": lambda: gemm_case(2048, 28672, 4096, "tiled"),
+    "prefill-gemm-m8192-k4096-n4096": lambda: gemm_case(8192, 4096, 4096, "tiled"),
+    "attention-decode-b1-ctx4096": lambda: attn_case(1, 4096),
+    "attention-decode-b64-ctx1024": lambda: attn_case(64, 1024),
+    "attention-decode-b64-ctx4096": lambda: attn_case(64, 4096),
+}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", action="append")
+    ap.add_argument("--pdl", type=int, default=1)
+    ap.add_argument("--once", action="store_true")
+    a = ap.parse_args()
+    K.set_pdl(bool(a.pdl))
+    bw, fl, src = peaks()
+    for name in (a.case or list(CASES)):
+        fns, nbytes, flops = CASES[name]()
+        if a.once:
+            for f in fns[:1]:
+                f()
+            torch.cuda.synchronize()
+            print(json.dumps({"case": name, "ran": 1}))
+            continue
+        us = time_graph(fns)
+        t_mem, t_fl = nbytes / bw * 1e6, flops / fl * 1e6
+        roof = max(t_mem, t_fl)
+        print(json.dumps({"case": name, "us": round(us, 2), "roofline_us": round(roof, 2),
+                          "bound": "memory" if t_mem >= t_fl else "compute", "frac_of_" + src: round(roof / us, 3),
+                          "GBs": round(nbytes / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 1)}), flush=True)
+        del fns
+        torch.cuda.empty_cache()
+    K.check_status()
+
+
+if __name__ == "__main__":
+    main()

@@ -39,23 +39,24 @@ __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v;
 }
 
-template <int BT, int STAGES>
+template <int BT, int STAGES, int WM>
 struct SkinnySmem {
-  static constexpr int W_BYTES = SK_BM * SK_BK * 2;
+  static constexpr int W_BYTES = WM * SK_BM * SK_BK * 2;
   static constexpr int X_BYTES = BT * SK_BK * 2;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-  static constexpr int RED_BYTES = BT * SK_BM * 4;
+  static constexpr int RED_BYTES = BT * WM * SK_BM * 4;
   static constexpr int RING = STAGES * STAGE_BYTES;
   static constexpr int BAR_OFFSET = RING > RED_BYTES ? RING : RED_BYTES;
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;
 };
 
-template <int BT, int STAGES, int EPI>
+template <int BT, int STAGES, int WM, int EPI>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    void* __restrict__ out, const __nv_bfloat16* resid, int M, int N, int K, int ldo, int CK,
                    int* __restrict__ status) {
-  using S = SkinnySmem<BT, STAGES>;
+  using S = SkinnySmem<BT, STAGES, WM>;
+  constexpr int ROWS = WM * SK_BM;  // weight rows per CTA
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = tc::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -66,19 +67,19 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const uint32_t tmem_slot = accum_bar + 8;
   volatile uint32_t* tmem_slot_gen =
       reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + (2 * STAGES + 1) * 8);
-  float* red = reinterpret_cast<float*>(gen_base);  // [BT][128] fp32, reuses the ring after the last MMA
+  float* red = reinterpret_cast<float*>(gen_base);  // [BT][ROWS] fp32, reuses the ring after the last MMA
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = CK > 1 ? cluster_ctarank() : 0u;
   const int row_tile = blockIdx.x / CK;
-  const int n0 = row_tile * SK_BM;
+  const int n0 = row_tile * ROWS;
   const int total_kt = (K + SK_BK - 1) / SK_BK;
   const int per = (total_kt + CK - 1) / CK;
   const int kt_begin = (int)crank * per;
   int kt_end = kt_begin + per;
   if (kt_end > total_kt) kt_end = total_kt;
   const int num_kt = kt_end > kt_begin ? kt_end - kt_begin : 0;
-  constexpr uint32_t TMEM_COLS = BT < 32 ? 32 : BT;
+  constexpr uint32_t TMEM_COLS = (WM * BT) < 32 ? 32 : (WM * BT);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar + 8 * s, 1); tc::mbar_init(empty_bar + 8 * s, 1); }
@@ -138,12 +139,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!tc::mbar_wait(full_bar + 8 * s, ph)) { ok = false; break; }
         tc::tc_fence_after();
         const uint32_t sa = base + s * S::STAGE_BYTES;
-        const uint64_t wdesc = tc::smem_desc_sw128(sa);
         const uint64_t xdesc = tc::smem_desc_sw128(sa + S::W_BYTES);
 #pragma unroll
-        for (int k = 0; k < SK_BK / 16; ++k)
-          tc::mma_bf16_ss(tmem_base, wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k), idesc,
-                          (i > 0 || k > 0) ? 1u : 0u);
+        for (int wm = 0; wm < WM; ++wm) {
+          const uint64_t wdesc = tc::smem_desc_sw128(sa + wm * (SK_BM * SK_BK * 2));
+#pragma unroll
+          for (int k = 0; k < SK_BK / 16; ++k)
+            tc::mma_bf16_ss(tmem_base + (uint32_t)(wm * BT), wdesc + (uint64_t)(2 * k), xdesc + (uint64_t)(2 * k),
+                            idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
         tc::tc_commit(empty_bar + 8 * s);
       }
       if (!ok) atomicExch(status, (int)kTimeoutMma);
@@ -155,25 +159,24 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     bool ok = tc::mbar_wait(accum_bar, 0);
     if (!ok && lane == 0) atomicExch(status, (int)kTimeoutEpilogue);
     tc::tc_fence_after();
-    const int r = quad * 32 + lane;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BT; c0 += 32) {
-      uint32_t v[32];
-      if (num_kt > 0 && ok) {
-        if (BT >= 32) {
-          tc::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)c0, v);
+    for (int wm = 0; wm < WM; ++wm) {
+      const int r = wm * SK_BM + quad * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BT; c0 += 32) {
+        uint32_t v[32];
+        if (num_kt > 0 && ok) {
+          // (BT == 16, WM == 1: the allocation is 32 columns wide; the upper 16 are never written by the MMA)
+          tc::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(wm * BT + c0), v);
+          tc::tmem_ld_wait();
         } else {
-          // BT == 16: the allocation is 32 columns wide; the upper 16 are never written by the MMA
-          tc::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16), v);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
-        tc::tmem_ld_wait();
-      } else {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0u;
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < BT) red[(c0 + j) * ROWS + r] = __uint_as_float(v[j]);
       }
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (c0 + j < BT) red[(c0 + j) * SK_BM + r] = __uint_as_float(v[j]);
     }
   }
 
@@ -187,7 +190,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
   // ---- reduce this CTA's slab of rows over the cluster and store ----
   pdl_wait();
-  const int slab = SK_BM / CK;
+  const int slab = ROWS / CK;
   const int slab0 = (int)crank * slab;
   const uint32_t red_s = base;  // shared-window address of red[0]
   const int Mv = M < BT ? M : BT;
@@ -198,7 +201,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int rr = slab0 + 2 * p;
       float g = 0.f, u = 0.f;
       for (int c = 0; c < CK; ++c) {
-        uint32_t a = red_s + (uint32_t)((tok * SK_BM + rr) * 4);
+        uint32_t a = red_s + (uint32_t)((tok * ROWS + rr) * 4);
         if (CK > 1) a = map_to_cta(a, (uint32_t)c);
         g += ld_dsmem_f32(a);
         u += ld_dsmem_f32(a + 4);
@@ -213,7 +216,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int rr = slab0 + p;
       float v = 0.f;
       for (int c = 0; c < CK; ++c) {
-        uint32_t a = red_s + (uint32_t)((tok * SK_BM + rr) * 4);
+        uint32_t a = red_s + (uint32_t)((tok * ROWS + rr) * 4);
         if (CK > 1) a = map_to_cta(a, (uint32_t)c);
         v += ld_dsmem_f32(a);
       }
@@ -231,18 +234,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if (CK > 1) cluster_sync_all();  // no CTA may exit while a peer still reads its tile
 }
 
-template <int BT, int STAGES, int EPI>
+template <int BT, int STAGES, int WM, int EPI>
 static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid, int M, int N,
                              int K, int ldo, int CK, int pdl, int* status, cudaStream_t s) {
-  using S = SkinnySmem<BT, STAGES>;
-  auto kern = gemm_skinny_kernel<BT, STAGES, EPI>;
+  using S = SkinnySmem<BT, STAGES, WM>;
+  auto kern = gemm_skinny_kernel<BT, STAGES, WM, EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int row_tiles = (N + SK_BM - 1) / SK_BM;
+  const int row_tiles = (N + WM * SK_BM - 1) / (WM * SK_BM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(row_tiles * CK, 1, 1);
   cfg.blockDim = dim3(SK_THREADS, 1, 1);
@@ -265,14 +268,14 @@ static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void*
   return (int)cudaLaunchKernelEx(&cfg, kern, tw, tx, out, (const __nv_bfloat16*)resid, M, N, K, ldo, CK, status);
 }
 
-template <int BT, int STAGES>
+template <int BT, int STAGES, int WM>
 static int launch_skinny_epi(int epi, const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid,
                              int M, int N, int K, int ldo, int CK, int pdl, int* status, cudaStream_t s) {
   switch (epi) {
-    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
-    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
-    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
-    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, WM, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, WM, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, WM, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, WM, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
     default: return (int)cudaErrorInvalidValue;
   }
 }
@@ -283,8 +286,9 @@ using namespace poot;
 
 // X [M, ldx] bf16 with M <= 128, W [N, K] bf16, out [M, ldo].  ck = cluster size (K split): 1, 2, 4 or 8.
 // pdl != 0 launches with programmatic stream serialization (the kernel waits on its predecessor itself).
+// wm = weight sub-tiles of 128 rows per CTA (1 or 2; 2 halves the activation re-reads from L2).
 POOT_API int poot_gemm_skinny(int epi, const void* x, const void* W, void* out, const void* resid, int M, int N, int K,
-                              int ldx, int ldo, int ck, int pdl, int* status, cudaStream_t s) {
+                              int ldx, int ldo, int ck, int wm, int pdl, int* status, cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 128 || K % 8 || ldx % 8) return (int)cudaErrorInvalidValue;
   if (ck != 1 && ck != 2 && ck != 4 && ck != 8) return (int)cudaErrorInvalidValue;
@@ -293,14 +297,23 @@ POOT_API int poot_gemm_skinny(int epi, const void* x, const void* W, void* out, 
   if (status == nullptr) return (int)cudaErrorInvalidValue;
   const int bt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap tw, tx;
-  int e = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)K, SK_BM);
+  if (wm != 1 && wm != 2) return (int)cudaErrorInvalidValue;
+  int e = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(wm * SK_BM));
   if (e) return e;
   e = make_tmap_bf16_2d(&tx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt);
   if (e) return e;
+  if (wm == 2) {
+    switch (bt) {
+      case 16: return launch_skinny_epi<16, 6, 2>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+      case 32: return launch_skinny_epi<32, 5, 2>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+      case 64: return launch_skinny_epi<64, 5, 2>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+      default: return launch_skinny_epi<128, 4, 2>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+    }
+  }
   switch (bt) {
-    case 16: return launch_skinny_epi<16, 6>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-    case 32: return launch_skinny_epi<32, 5>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-    case 64: return launch_skinny_epi<64, 4>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-    default: return launch_skinny_epi<128, 3>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+    case 16: return launch_skinny_epi<16, 6, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+    case 32: return launch_skinny_epi<32, 5, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+    case 64: return launch_skinny_epi<64, 4, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+    default: return launch_skinny_epi<128, 3, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
   }
 }

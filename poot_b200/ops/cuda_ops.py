@@ -29,7 +29,7 @@ _SIGS = {
     "poot_gemv_bf16": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "poot_gemm_bf16_tcgen05": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,
                                _P, _P],
-    "poot_gemm_skinny": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "poot_gemm_skinny": [c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "poot_rope_kv_write": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_int, _P],
     "poot_attn_paged": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float,
@@ -227,7 +227,7 @@ def skinny_cluster(N: int, Kd: int) -> int:
 
 
 def gemm_skinny(x: torch.Tensor, W: torch.Tensor, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
-                resid: Optional[torch.Tensor] = None, ck: Optional[int] = None) -> torch.Tensor:
+                resid: Optional[torch.Tensor] = None, ck: Optional[int] = None, wm: int = 1) -> torch.Tensor:
     """Swap-AB tcgen05 GEMM for ``M <= 128`` tokens with cluster split-K reduced through DSMEM."""
     _need_cuda(x, W)
     assert x.dtype == torch.bfloat16 and W.dtype == torch.bfloat16 and W.is_contiguous()
@@ -239,11 +239,11 @@ def gemm_skinny(x: torch.Tensor, W: torch.Tensor, epi: int = EPI_STORE, out: Opt
     out = _out_for(epi, M, N, x.device, out)
     st = status_word(x.device)
     check(_fn("poot_gemm_skinny")(epi, _ptr(x), _ptr(W), _ptr(out), _ptr(resid), M, N, Kd, x.stride(0), out.stride(0),
-                                  ck, 0, _ptr(st), _stream()), "gemm_skinny")
+                                  ck, wm, 0, _ptr(st), _stream()), "gemm_skinny")
     return out
 
 
-GEMV_MAX_M = 4          # rows served by the SIMT GEMV; 0 routes every decode GEMM to the tensor-core kernel
+GEMV_MAX_M = 0          # rows served by the SIMT GEMV; 0 routes every decode GEMM to the tensor-core kernel
 
 
 def set_pdl(on: bool) -> None:
