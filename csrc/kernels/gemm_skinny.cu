@@ -17,6 +17,7 @@
 // Reference behaviour covered: Contraction::DenseGemv / batched decode GEMM with register epilogues
 // (crates/poot-kernelgen/src/contraction/gemv.rs:1-3, contraction/mod.rs:70-84).
 #include "tc_common.cuh"
+#include "tp_common.cuh"
 
 namespace poot {
 
@@ -25,6 +26,11 @@ enum { SEPI_STORE = 0, SEPI_F32 = 1, SEPI_RESID = 2, SEPI_SWIGLU = 3 };
 constexpr int SK_BM = 128;   // weight rows per CTA
 constexpr int SK_BK = 64;
 constexpr int SK_THREADS = 192;
+
+// One tensor map per rank over its activation shard buffer [2 * S rows, K] (box = S rows x 64 columns).
+struct TpMaps { CUtensorMap m[TP_MAX_WORLD]; };
+
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r;
@@ -54,7 +60,7 @@ template <int BT, int STAGES, int WM, int EPI>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    void* __restrict__ out, const __nv_bfloat16* resid, int M, int N, int K, int ldo, int CK,
-                   int* __restrict__ status) {
+                   int* __restrict__ status, const __grid_constant__ TpArgs tp, const __grid_constant__ TpMaps maps) {
   using S = SkinnySmem<BT, STAGES, WM>;
   constexpr int ROWS = WM * SK_BM;  // weight rows per CTA
   extern __shared__ uint8_t smem_raw[];
@@ -108,10 +114,29 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         tc::tma_load_2d(base + i * S::STAGE_BYTES, &tmW, (kt_begin + i) * SK_BK, n0, full_bar + 8 * i);
       }
       pdl_wait();
-      for (int i = 0; i < pre; ++i)
-        tc::tma_load_2d(base + i * S::STAGE_BYTES + S::W_BYTES, &tmX, (kt_begin + i) * SK_BK, 0, full_bar + 8 * i);
-      int issued = pre;
+      const bool gather = tp.world > 1 && tp.ag_site >= 0;
+      int xrow = 0;  // row of the activation shard buffers that holds this site's data
       bool ok = true;
+      if (gather) {
+        const uint32_t target = tp_target(tp, tp.ag_site, tp.ag_sites);
+        xrow = (int)(target & 1u) * tp.S;
+        for (int r = 0; r < tp.world; ++r)
+          if (!wait_flag_ge(tp.flags_local + TP_CH_AG * TP_MAX_WORLD + r, target)) ok = false;
+        if (!ok) atomicExch(status, (int)kTimeoutPeerFlag);
+        fence_proxy_async_global();  // peers wrote the shards with ordinary stores; TMA reads them
+      }
+      // X tile of one K step: rows [r*S, (r+1)*S) come from rank r's shard (peer memory, plain TMA load)
+      auto load_x = [&](uint32_t dst, int kx, uint32_t bar) {
+        if (gather) {
+          for (int r = 0; r < tp.world; ++r)
+            tc::tma_load_2d(dst + (uint32_t)(r * tp.S * SK_BK * 2), &maps.m[r], kx, xrow, bar);
+        } else {
+          tc::tma_load_2d(dst, &tmX, kx, 0, bar);
+        }
+      };
+      for (int i = 0; i < pre; ++i)
+        load_x(base + i * S::STAGE_BYTES + S::W_BYTES, (kt_begin + i) * SK_BK, full_bar + 8 * i);
+      int issued = pre;
       for (int i = pre; i < num_kt; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
@@ -120,7 +145,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const uint32_t sa = base + s * S::STAGE_BYTES;
         const int kx = (kt_begin + i) * SK_BK;
         tc::tma_load_2d(sa, &tmW, kx, n0, full_bar + 8 * s);
-        tc::tma_load_2d(sa + S::W_BYTES, &tmX, kx, 0, full_bar + 8 * s);
+        load_x(sa + S::W_BYTES, kx, full_bar + 8 * s);
         ++issued;
       }
       if (!ok) {
@@ -193,7 +218,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int slab = ROWS / CK;
   const int slab0 = (int)crank * slab;
   const uint32_t red_s = base;  // shared-window address of red[0]
-  const int Mv = M < BT ? M : BT;
+  const bool scatter = tp.world > 1 && tp.rs_site >= 0;
+  const uint32_t rs_target = scatter ? tp_target(tp, tp.rs_site, tp.rs_sites) : 0u;
+  const int rs_parity = (int)(rs_target & 1u);
+  const int Mv = scatter ? BT : (M < BT ? M : BT);
   if (EPI == SEPI_SWIGLU) {
     const int hp = slab >> 1;
     for (int idx = threadIdx.x; idx < hp * Mv; idx += SK_THREADS) {
@@ -222,7 +250,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       const int n = n0 + rr;
       if (n < N) {
-        if (EPI == SEPI_F32) {
+        if (scatter) {
+          // reduce-scatter: token row `tok` belongs to rank tok / S; write into that rank's inbox slice for this rank
+          const int d = tok / tp.S, tl = tok - d * tp.S;
+          tp.inbox_peer[d][((size_t)((rs_parity * tp.world + tp.rank) * tp.S + tl)) * tp.ld_inbox + n] =
+              __float2bfloat16(v);
+        } else if (EPI == SEPI_F32) {
           reinterpret_cast<float*>(out)[(size_t)tok * ldo + n] = v;
         } else {
           if (EPI == SEPI_RESID) v += __bfloat162float(resid[(size_t)tok * ldo + n]);
@@ -231,12 +264,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   }
+  if (scatter) tp_signal_all(tp, TP_CH_RS, rs_target, (int)gridDim.x);
   if (CK > 1) cluster_sync_all();  // no CTA may exit while a peer still reads its tile
 }
 
 template <int BT, int STAGES, int WM, int EPI>
 static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid, int M, int N,
-                             int K, int ldo, int CK, int pdl, int* status, cudaStream_t s) {
+                             int K, int ldo, int CK, int pdl, int* status, cudaStream_t s, const TpArgs& tp,
+                             const TpMaps& maps) {
   using S = SkinnySmem<BT, STAGES, WM>;
   auto kern = gemm_skinny_kernel<BT, STAGES, WM, EPI>;
   static bool configured = false;
@@ -265,17 +300,30 @@ static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void*
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  return (int)cudaLaunchKernelEx(&cfg, kern, tw, tx, out, (const __nv_bfloat16*)resid, M, N, K, ldo, CK, status);
+  return (int)cudaLaunchKernelEx(&cfg, kern, tw, tx, out, (const __nv_bfloat16*)resid, M, N, K, ldo, CK, status, tp, maps);
 }
 
 template <int BT, int STAGES, int WM>
 static int launch_skinny_epi(int epi, const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid,
-                             int M, int N, int K, int ldo, int CK, int pdl, int* status, cudaStream_t s) {
+                             int M, int N, int K, int ldo, int CK, int pdl, int* status, cudaStream_t s,
+                             const TpArgs& tp, const TpMaps& maps) {
   switch (epi) {
-    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, WM, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
-    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, WM, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
-    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, WM, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
-    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, WM, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s);
+    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, WM, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, maps);
+    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, WM, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, maps);
+    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, WM, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, maps);
+    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, WM, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, maps);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
+static int skinny_dispatch(int epi, const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid, int M,
+                           int N, int K, int ldo, int ck, int bt, int pdl, int* status, cudaStream_t s, const TpArgs& tp,
+                           const TpMaps& maps) {
+  switch (bt) {
+    case 16: return launch_skinny_epi<16, 6, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, maps);
+    case 32: return launch_skinny_epi<32, 5, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, maps);
+    case 64: return launch_skinny_epi<64, 4, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, maps);
+    case 128: return launch_skinny_epi<128, 3, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, maps);
     default: return (int)cudaErrorInvalidValue;
   }
 }
@@ -286,34 +334,63 @@ using namespace poot;
 
 // X [M, ldx] bf16 with M <= 128, W [N, K] bf16, out [M, ldo].  ck = cluster size (K split): 1, 2, 4 or 8.
 // pdl != 0 launches with programmatic stream serialization (the kernel waits on its predecessor itself).
-// wm = weight sub-tiles of 128 rows per CTA (1 or 2; 2 halves the activation re-reads from L2).
 POOT_API int poot_gemm_skinny(int epi, const void* x, const void* W, void* out, const void* resid, int M, int N, int K,
                               int ldx, int ldo, int ck, int wm, int pdl, int* status, cudaStream_t s) {
   if (M <= 0 || N <= 0) return 0;
-  if (M > 128 || K % 8 || ldx % 8) return (int)cudaErrorInvalidValue;
+  if (M > 128 || K % 8 || ldx % 8 || wm != 1) return (int)cudaErrorInvalidValue;
   if (ck != 1 && ck != 2 && ck != 4 && ck != 8) return (int)cudaErrorInvalidValue;
   if (epi == SEPI_SWIGLU && (N % 2)) return (int)cudaErrorInvalidValue;
   if (epi == SEPI_RESID && resid == nullptr) return (int)cudaErrorInvalidValue;
   if (status == nullptr) return (int)cudaErrorInvalidValue;
   const int bt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
   CUtensorMap tw, tx;
-  if (wm != 1 && wm != 2) return (int)cudaErrorInvalidValue;
-  int e = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(wm * SK_BM));
+  int e = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)SK_BM);
   if (e) return e;
   e = make_tmap_bf16_2d(&tx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt);
   if (e) return e;
-  if (wm == 2) {
-    switch (bt) {
-      case 16: return launch_skinny_epi<16, 6, 2>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-      case 32: return launch_skinny_epi<32, 5, 2>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-      case 64: return launch_skinny_epi<64, 5, 2>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-      default: return launch_skinny_epi<128, 4, 2>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+  TpArgs tp = {};
+  tp.world = 1; tp.ag_site = -1; tp.rs_site = -1;
+  TpMaps maps = {};
+  return skinny_dispatch(epi, tw, tx, out, resid, M, N, K, ldo, ck, bt, pdl, status, s, tp, maps);
+}
+
+// Tensor-parallel form.  The step has world*S padded token rows (16, 32, 64 or 128).
+//   ag_site >= 0: X is gathered from the ranks' activation shard buffers xs_peer[r] ([2*S, K] bf16, this rank's
+//                 mapping of rank r's buffer) once rank r's flag for the site is visible; otherwise X is `x` (local).
+//   rs_site >= 0: output rows are scattered (bf16) to their owner ranks' inboxes and the site is signalled;
+//                 otherwise the epilogue `epi` writes to `out` locally.
+POOT_API int poot_gemm_skinny_tp(int epi, const void* x, const void* W, void* out, int N, int K, int ldx, int ldo,
+                                 int ck, int world, int rank, int S, int ag_site, int ag_sites, int rs_site,
+                                 int rs_sites, const int* epoch, void* flags_local, void* const* flags_peer,
+                                 void* const* inbox_peer, int ld_inbox, void* const* xs_peer, int* ticket, int* status,
+                                 cudaStream_t s) {
+  if (world < 2 || world > TP_MAX_WORLD || S % 8 || K % 8) return (int)cudaErrorInvalidValue;
+  const int bt = world * S;
+  if (bt != 16 && bt != 32 && bt != 64 && bt != 128) return (int)cudaErrorInvalidValue;
+  if (ck != 1 && ck != 2 && ck != 4 && ck != 8) return (int)cudaErrorInvalidValue;
+  if (status == nullptr || epoch == nullptr) return (int)cudaErrorInvalidValue;
+  if (rs_site >= 0 && epi != SEPI_STORE) return (int)cudaErrorInvalidValue;
+  CUtensorMap tw, tx;
+  int e = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)SK_BM);
+  if (e) return e;
+  TpMaps maps = {};
+  if (ag_site >= 0) {
+    for (int r = 0; r < world; ++r) {
+      e = make_tmap_bf16_2d(&maps.m[r], xs_peer[r], (uint64_t)(2 * S), (uint64_t)K, (uint64_t)K, (uint32_t)S);
+      if (e) return e;
     }
+    tx = maps.m[rank];
+  } else {
+    e = make_tmap_bf16_2d(&tx, x, (uint64_t)bt, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt);
+    if (e) return e;
   }
-  switch (bt) {
-    case 16: return launch_skinny_epi<16, 6, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-    case 32: return launch_skinny_epi<32, 5, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-    case 64: return launch_skinny_epi<64, 4, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
-    default: return launch_skinny_epi<128, 3, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s);
+  TpArgs tp = {};
+  tp.world = world; tp.rank = rank; tp.S = S;
+  tp.ag_site = ag_site; tp.ag_sites = ag_sites; tp.rs_site = rs_site; tp.rs_sites = rs_sites;
+  tp.ld_inbox = ld_inbox; tp.epoch = epoch; tp.flags_local = (uint32_t*)flags_local; tp.ticket = ticket;
+  for (int r = 0; r < world; ++r) {
+    tp.flags_peer[r] = (uint32_t*)flags_peer[r];
+    tp.inbox_peer[r] = inbox_peer ? (__nv_bfloat16*)inbox_peer[r] : nullptr;
   }
+  return skinny_dispatch(epi, tw, tx, out, nullptr, bt, N, K, ldo, ck, bt, 0, status, s, tp, maps);
 }

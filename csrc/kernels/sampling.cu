@@ -51,23 +51,25 @@ __device__ __forceinline__ int warp_min_i(int v) {
 
 constexpr int SAMP_THREADS = 256;
 
-// Stage 1: partials[(row*groups+g)] = (best_val, best_idx, bad_idx) over one chunk.
+// Stage 1: part[(row*groups+g)*3 ..] = (bits of best_val, best_idx, bad_idx) over one chunk of a row of
+// `vocab` logits (row pitch ld).  Indices are global: idx_offset is added (vocabulary-sharded logits), and
+// `bad_none` (the total vocabulary) stands for "no non-finite logit".
 __global__ void __launch_bounds__(SAMP_THREADS)
-argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunk, int groups, float* __restrict__ pv,
-                    int* __restrict__ pi) {
+argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int ld, int idx_offset, int bad_none, int chunk,
+                    int groups, int* __restrict__ part) {
   __shared__ float sv[SAMP_THREADS / 32];
   __shared__ int si[SAMP_THREADS / 32], sb[SAMP_THREADS / 32];
   pdl_wait(); pdl_launch();
   const int row = blockIdx.y, g = blockIdx.x;
   const int start = g * chunk;
   const int end = min(start + chunk, vocab);
-  const float* lr = logits + (size_t)row * vocab;
+  const float* lr = logits + (size_t)row * ld;
   Cand best{0.f, -1};
-  int bad = vocab;
+  int bad = bad_none;
   for (int j = start + threadIdx.x; j < end; j += SAMP_THREADS) {
     float v = lr[j];
-    if (finite_f32(v)) { if (best.i < 0 || v > best.v) { best.v = v; best.i = j; } }
-    else if (j < bad) bad = j;
+    if (finite_f32(v)) { if (best.i < 0 || v > best.v) { best.v = v; best.i = j + idx_offset; } }
+    else if (j + idx_offset < bad) bad = j + idx_offset;
   }
   best = warp_best(best);
   bad = warp_min_i(bad);
@@ -75,30 +77,32 @@ argmax_chunk_kernel(const float* __restrict__ logits, int vocab, int chunk, int 
   if (l == 0) { sv[w] = best.v; si[w] = best.i; sb[w] = bad; }
   __syncthreads();
   if (w == 0) {
-    Cand c{0.f, -1}; int b = vocab;
+    Cand c{0.f, -1}; int b = bad_none;
     if (l < SAMP_THREADS / 32) { c.v = sv[l]; c.i = si[l]; b = sb[l]; }
     c = warp_best(c); b = warp_min_i(b);
     if (l == 0) {
-      size_t p = (size_t)row * groups + g;
-      pv[p] = c.v; pi[p * 2] = c.i; pi[p * 2 + 1] = b;
+      size_t p = ((size_t)row * groups + g) * 3;
+      part[p] = __float_as_int(c.v); part[p + 1] = c.i; part[p + 2] = b;
     }
   }
 }
 
-__global__ void argmax_combine_kernel(const float* __restrict__ pv, const int* __restrict__ pi, int groups, int vocab,
-                                      int* __restrict__ out) {
+// Stage 2 over `nparts` partial tables (one per vocabulary shard), each [rows, groups, 3], part_stride ints apart.
+__global__ void argmax_combine_kernel(const int* __restrict__ part, int nparts, long long part_stride, int groups,
+                                      int bad_none, int* __restrict__ out) {
   pdl_wait(); pdl_launch();
   const int row = blockIdx.x, l = threadIdx.x;  // one warp
-  Cand c{0.f, -1}; int b = vocab;
-  for (int g = l; g < groups; g += 32) {
-    size_t p = (size_t)row * groups + g;
-    Cand t{pv[p], pi[p * 2]};
+  Cand c{0.f, -1}; int b = bad_none;
+  for (int e = l; e < nparts * groups; e += 32) {
+    const int pt = e / groups, g = e - pt * groups;
+    const int* p = part + (size_t)pt * part_stride + ((size_t)row * groups + g) * 3;
+    Cand t{__int_as_float(p[0]), p[1]};
     c = better(c, t);
-    b = min(b, pi[p * 2 + 1]);
+    b = min(b, p[2]);
   }
   c = warp_best(c); b = warp_min_i(b);
   if (l == 0) {
-    bool nf = b < vocab;
+    bool nf = b < bad_none;
     out[row * 2] = (nf || c.i < 0) ? 0 : c.i;
     out[row * 2 + 1] = nf ? b : -1;
   }
@@ -245,15 +249,29 @@ __global__ void random_uniform_kernel(const int* __restrict__ seeds, int cols, f
 
 using namespace poot;
 
-// scratch: pv fp32 [rows, groups], pi int32 [rows, groups, 2]; groups = ceil(vocab / chunk).
-POOT_API int poot_argmax(const float* logits, int rows, int vocab, int chunk, float* pv, int* pi, int* out,
-                         cudaStream_t s) {
+// part: int32 scratch [rows, groups, 3]; groups = ceil(vocab / chunk).
+POOT_API int poot_argmax_partials(const float* logits, int rows, int vocab, int ld, int idx_offset, int vocab_total,
+                                  int chunk, int* part, cudaStream_t s) {
   if (rows == 0) return 0;
   int groups = (vocab + chunk - 1) / chunk;
   if (groups < 1) groups = 1;
-  int e = launch_k(argmax_chunk_kernel, dim3(groups, rows), dim3(SAMP_THREADS), 0, s, logits, vocab, chunk, groups, pv, pi);
+  return launch_k(argmax_chunk_kernel, dim3(groups, rows), dim3(SAMP_THREADS), 0, s, logits, vocab, ld, idx_offset,
+                  vocab_total, chunk, groups, part);
+}
+
+POOT_API int poot_argmax_combine(const int* part, int nparts, long long part_stride, int rows, int groups,
+                                 int vocab_total, int* out, cudaStream_t s) {
+  if (rows == 0) return 0;
+  return launch_k(argmax_combine_kernel, dim3(rows), dim3(32), 0, s, part, nparts, part_stride, groups, vocab_total,
+                  out);
+}
+
+POOT_API int poot_argmax(const float* logits, int rows, int vocab, int chunk, int* part, int* out, cudaStream_t s) {
+  int e = poot_argmax_partials(logits, rows, vocab, vocab, 0, vocab, chunk, part, s);
   if (e) return e;
-  return launch_k(argmax_combine_kernel, dim3(rows), dim3(32), 0, s, (const float*)pv, (const int*)pi, groups, vocab, out);
+  int groups = (vocab + chunk - 1) / chunk;
+  if (groups < 1) groups = 1;
+  return poot_argmax_combine(part, 1, 0, rows, groups, vocab, out, s);
 }
 
 POOT_API int poot_sample_gumbel(const float* logits, int rows, int vocab, const float* params, const int* top_k,

@@ -1,0 +1,86 @@
+// Tensor-parallel plumbing shared by the fused compute+collective kernels.
+//
+// Ranks are processes, one per GPU.  Each rank owns a block of "symmetric" device memory that every
+// peer maps through CUDA IPC; kernels read and write peers' memory with ordinary loads/stores (and
+// non-multicast TMA loads) over NVLink.  Synchronisation uses monotone 32-bit flags in that memory:
+//
+//   flags[ch * 8 + src]   written by rank `src` (st.release.sys on the peer mapping), polled locally
+//   ch 0 = "my reduce-scatter contribution for site s has landed in your inbox"
+//   ch 1 = "my normalised activation shard for site s is ready to be gathered"
+//
+// A step of the model has a fixed number of sites per channel; a device-resident epoch counter is
+// bumped once per step, so the value to signal / wait for is (epoch-1)*sites + site + 1 and nothing
+// is ever reset between CUDA-graph replays.  Buffers are double-buffered on the parity of that value.
+// Every wait is bounded: on timeout the kernel records kTimeoutPeerFlag in the status word and goes on
+// (the step's output is then invalid, the context stays usable, the host raises a typed error).
+//
+// This replaces the reference's lowering of AllReduce / AllGather to world*(world-1) host-issued peer
+// copies per collective plus Add kernels (crates/poot-graph-plan/src/passes/sharding.rs:1165-1357,
+// crates/poot-ptx-runtime/src/context.rs:741-785).
+#pragma once
+#include "common.cuh"
+#include <cuda.h>
+
+namespace poot {
+
+constexpr int TP_MAX_WORLD = 8;
+constexpr int TP_CH_RS = 0;
+constexpr int TP_CH_AG = 1;
+constexpr long long kFlagWaitBudgetCycles = 2000000000LL;  // about 1 s
+
+struct TpArgs {
+  int world;          // 1 = not tensor parallel (all other fields unused)
+  int rank;
+  int S;              // token rows per rank (multiple of 8); padded step rows = world * S
+  int ag_site;        // >= 0: gather the X operand from the peers' activation shards for this site
+  int ag_sites;       // gather sites per step
+  int rs_site;        // >= 0: scatter the output rows to their owner ranks' inboxes for this site
+  int rs_sites;       // scatter sites per step
+  int ld_inbox;       // row pitch (elements) of an inbox slice = hidden size
+  const int* epoch;             // device step counter (>= 1 inside a step)
+  uint32_t* flags_local;        // this rank's flag block [2 * 8]
+  uint32_t* flags_peer[TP_MAX_WORLD];        // every rank's flag block (peer mappings; [rank] = local)
+  __nv_bfloat16* inbox_peer[TP_MAX_WORLD];   // every rank's inbox [2][world][S][ld_inbox] bf16
+  int* ticket;                  // local CTA-completion counter (self-resetting)
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded poll until *flag >= target (wrap-safe).  False on timeout.
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t target) {
+  if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) return true;
+  const long long t0 = clock64();
+  while ((int32_t)(ld_acquire_sys(flag) - target) < 0) {
+    if (clock64() - t0 > kFlagWaitBudgetCycles) return false;
+    __nanosleep(40);
+  }
+  return true;
+}
+
+__device__ __forceinline__ uint32_t tp_target(const TpArgs& tp, int site, int sites) {
+  return (uint32_t)(*tp.epoch - 1) * (uint32_t)sites + (uint32_t)site + 1u;
+}
+
+// Called by every CTA after its peer stores; the last CTA to arrive publishes `target` on channel `ch`
+// of every rank's flag block.  All threads of the CTA must call it (it contains a barrier).
+__device__ __forceinline__ void tp_signal_all(const TpArgs& tp, int ch, uint32_t target, int num_ctas) {
+  __threadfence_system();  // this thread's peer stores are ordered before the ticket
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = atomicAdd(tp.ticket, 1);
+    if (t == num_ctas - 1) {
+      __threadfence_system();  // cumulativity: every CTA's stores (observed through the ticket) come first
+      for (int d = 0; d < tp.world; ++d) st_release_sys(tp.flags_peer[d] + ch * TP_MAX_WORLD + tp.rank, target);
+      atomicExch(tp.ticket, 0);
+    }
+  }
+}
+
+}  // namespace poot

@@ -35,7 +35,9 @@ _SIGS = {
     "poot_attn_paged": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float,
                         c_float, c_int, c_int, _P],
     "poot_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, _P],
-    "poot_argmax": [_P, c_int, c_int, c_int, _P, _P, _P, _P],
+    "poot_argmax": [_P, c_int, c_int, c_int, _P, _P, _P],
+    "poot_argmax_partials": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
+    "poot_argmax_combine": [_P, c_int, c_longlong, c_int, c_int, c_int, _P, _P],
     "poot_sample_gumbel": [_P, c_int, c_int, _P, _P, _P, c_int, _P, _P],
     "poot_random_uniform": [_P, c_int, c_int, _P, _P],
 }
@@ -310,10 +312,13 @@ def attn_paged(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_
 ARGMAX_CHUNK = 2048
 
 
-def argmax_scratch(rows: int, vocab: int, device):
-    groups = (vocab + ARGMAX_CHUNK - 1) // ARGMAX_CHUNK
-    return (torch.empty(rows * groups, dtype=torch.float32, device=device),
-            torch.empty(rows * groups * 2, dtype=torch.int32, device=device))
+def argmax_groups(vocab: int) -> int:
+    return max(1, (vocab + ARGMAX_CHUNK - 1) // ARGMAX_CHUNK)
+
+
+def argmax_scratch(rows: int, vocab: int, device) -> torch.Tensor:
+    """int32 ``[rows, groups, 3]`` partial table ``(bits of best value, best index, first non-finite index)``."""
+    return torch.empty(rows, argmax_groups(vocab), 3, dtype=torch.int32, device=device)
 
 
 def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, scratch=None) -> torch.Tensor:
@@ -323,9 +328,24 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, scratch=Non
     rows, vocab = logits.shape
     if out is None:
         out = torch.empty(rows, 2, dtype=torch.int32, device=logits.device)
-    pv, pi = scratch if scratch is not None else argmax_scratch(rows, vocab, logits.device)
-    check(_fn("poot_argmax")(_ptr(logits), rows, vocab, ARGMAX_CHUNK, _ptr(pv), _ptr(pi), _ptr(out), _stream()),
-          "argmax")
+    part = scratch if scratch is not None else argmax_scratch(rows, vocab, logits.device)
+    check(_fn("poot_argmax")(_ptr(logits), rows, vocab, ARGMAX_CHUNK, _ptr(part), _ptr(out), _stream()), "argmax")
+    return out
+
+
+def argmax_partials(logits: torch.Tensor, idx_offset: int, vocab_total: int, part: torch.Tensor) -> torch.Tensor:
+    """Stage 1 of the greedy pick over one vocabulary shard (indices are global)."""
+    rows, vocab = logits.shape
+    check(_fn("poot_argmax_partials")(_ptr(logits), rows, vocab, logits.stride(0), idx_offset, vocab_total,
+                                      ARGMAX_CHUNK, _ptr(part), _stream()), "argmax_partials")
+    return part
+
+
+def argmax_combine(parts: torch.Tensor, rows: int, groups: int, vocab_total: int, out: torch.Tensor) -> torch.Tensor:
+    """Stage 2 over ``parts[nparts, rows, groups, 3]`` (one table per vocabulary shard)."""
+    nparts = parts.shape[0]
+    check(_fn("poot_argmax_combine")(_ptr(parts), nparts, parts.stride(0), rows, groups, vocab_total, _ptr(out),
+                                     _stream()), "argmax_combine")
     return out
 
 

@@ -1,0 +1,152 @@
+"""Tensor-parallel communication back ends of the device engine.
+
+``NcclComm`` is the baseline: a row-parallel projection writes its partial result, NCCL all-reduces it and a
+kernel adds it to the residual stream - one library collective per projection, captured in the step graph.
+
+``FusedComm`` is the product path for steps of up to 128 padded token rows (decode batches): the o_proj /
+down_proj GEMMs scatter their output tiles straight into the owner ranks' inboxes over NVLink
+(GEMM + reduce-scatter in one kernel), the consumer kernel reduces the inboxes into the token-sharded
+residual stream and normalises it (reduce + RMSNorm), and the following qkv / gate_up GEMM gathers the
+normalised shards from the peers with TMA loads inside its producer warp (all-gather + GEMM in one kernel).
+Larger steps (prefill chunks) fall back to the NCCL form.
+
+Sharding follows the reference's Megatron layouts (crates/poot-graph-plan/src/passes/sharding.rs:219-251);
+its collective lowering - every rank reads every peer's partial once, summed in rank order so all ranks get
+bit-identical results (sharding.rs:1219-1250) - is kept, but runs inside kernels instead of as
+world*(world-1) host-issued copies per collective.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import cuda_ops as K
+from ..ops._lib import check, kernels
+from .symm import SymmetricBlock
+
+_P = c_void_p
+
+
+class NcclComm:
+    """All-reduce through NCCL after a local GEMM (the baseline, not the product)."""
+
+    fused = False
+
+    def __init__(self, rank: int, world: int, device: torch.device, group=None):
+        self.rank, self.world, self.device, self.group = rank, world, device, group
+
+    def attach(self, engine) -> None:
+        T, H = engine.max_tokens, engine.cfg.hidden
+        self.partial = torch.zeros(T, H, dtype=torch.bfloat16, device=self.device)
+
+    def row_parallel(self, engine, x: torch.Tensor, W: torch.Tensor, T: int):
+        """``h += allreduce(x @ W^T)``."""
+        p = self.partial[:T]
+        engine._linear(x, W, K.EPI_STORE, p)
+        dist.all_reduce(p, group=self.group)
+        engine._count()
+        K.add(engine.h[:T], p, out=engine.h[:T])
+        return None
+
+    def all_gather(self, out: torch.Tensor, inp: torch.Tensor) -> None:
+        dist.all_gather_into_tensor(out, inp, group=self.group)
+
+
+class FusedComm(NcclComm):
+    """In-kernel NVLink reduce-scatter / all-gather fused with the projections' GEMMs."""
+
+    fused = True
+    MAX_ROWS = 128
+
+    def __init__(self, rank: int, world: int, device: torch.device, group=None, probe: bool = True):
+        super().__init__(rank, world, device, group)
+        self.probe_links = probe
+        self.block: Optional[SymmetricBlock] = None
+
+    def attach(self, engine) -> None:
+        super().attach(engine)
+        H, w = engine.cfg.hidden, self.world
+        self.H = H
+        self.s_max = self.MAX_ROWS // w
+        # layout of the symmetric block (byte offsets, 1 KiB aligned)
+        self.off_flags = 0
+        self.off_inbox = 1024
+        inbox_bytes = 2 * w * self.s_max * H * 2
+        self.off_xs = self.off_inbox + (inbox_bytes + 1023) // 1024 * 1024
+        xs_bytes = 2 * self.s_max * H * 2
+        total = self.off_xs + (xs_bytes + 1023) // 1024 * 1024
+        self.block = SymmetricBlock(total, self.rank, w, self.device, self.group)
+        if self.probe_links:
+            self.block.probe(self.group)
+        self.flags_peer = self.block.ptr_array(self.off_flags)
+        self.inbox_peer = self.block.ptr_array(self.off_inbox)
+        self.xs_peer = self.block.ptr_array(self.off_xs)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.h_shard = torch.zeros(self.s_max, H, dtype=torch.bfloat16, device=self.device)
+        L = engine.cfg.n_layers
+        self.rs_sites = 2 * L
+        self.ag_sites = 2 * L + 1
+        lib = kernels()
+        self._begin = lib.poot_tp_begin_step
+        self._begin.argtypes = [_P, _P]
+        self._norm = lib.poot_tp_norm
+        self._norm.argtypes = [_P, _P, _P, _P, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P,
+                               _P, _P, _P, _P]
+        self._gemm = lib.poot_gemm_skinny_tp
+        self._gemm.argtypes = [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, _P]
+
+    # ---- geometry -------------------------------------------------------------------------------------------
+    def rows_for(self, T: int) -> int:
+        """Padded step rows (world * S, one of 16/32/64/128) or 0 when the step is too large for the fused path."""
+        need = max(T, 8 * self.world)
+        for r in (16, 32, 64, 128):
+            if r >= need and r % (8 * self.world) == 0:
+                return r
+        return 0
+
+    # ---- launches -------------------------------------------------------------------------------------------
+    def begin_step(self) -> None:
+        check(self._begin(self.epoch.data_ptr(), K._stream()), "tp_begin_step")
+
+    def norm(self, w: torch.Tensor, S: int, eps: float, ag_site: int, rs_site: int) -> None:
+        """Reduce the inboxes of ``rs_site`` (if >= 0) into the residual shard, normalise, publish for ``ag_site``."""
+        b = self.block
+        check(self._norm(self.h_shard.data_ptr(), b.ptr(self.rank, self.off_inbox), w.data_ptr(),
+                         b.ptr(self.rank, self.off_xs), self.H, float(eps), self.world, self.rank, S, ag_site,
+                         self.ag_sites, rs_site, self.rs_sites, self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags),
+                         self.flags_peer, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
+              "tp_norm")
+
+    def gemm(self, epi: int, x: Optional[torch.Tensor], W: torch.Tensor, out: Optional[torch.Tensor], S: int,
+             ag_site: int = -1, rs_site: int = -1) -> None:
+        """Skinny GEMM with a gathered X operand (``ag_site``) and / or a scattered output (``rs_site``)."""
+        N, Kd = W.shape
+        ck = K.skinny_cluster(N, Kd)
+        ldx = x.stride(0) if x is not None else Kd
+        ldo = out.stride(0) if out is not None else self.H
+        b = self.block
+        check(self._gemm(epi, None if x is None else x.data_ptr(), W.data_ptr(), None if out is None else out.data_ptr(),
+                         N, Kd, ldx, ldo, ck, self.world, self.rank, S, ag_site, self.ag_sites, rs_site, self.rs_sites,
+                         self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer, self.inbox_peer,
+                         self.H, self.xs_peer, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(),
+                         K._stream()), "gemm_skinny_tp")
+
+    def close(self) -> None:
+        if self.block is not None:
+            torch.cuda.synchronize(self.device)
+            self.block.close()
+            self.block = None
+
+
+def make_comm(kind: str, rank: int, world: int, device: torch.device, group=None):
+    if kind == "nccl":
+        return NcclComm(rank, world, device, group)
+    if kind == "fused":
+        return FusedComm(rank, world, device, group)
+    raise ValueError(f"unknown comm kind {kind!r}")

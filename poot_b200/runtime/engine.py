@@ -67,6 +67,9 @@ class DecoderEngine:
         self.use_graphs = use_graphs
         self.kv = KVPool(cfg, num_blocks, self.device, self.tp)
         dev, i32 = self.device, torch.int32
+        if comm is not None and getattr(comm, "fused", False):
+            max_tokens = max(max_tokens, 128)  # padded rows of the fused tensor-parallel path
+            self.max_tokens = max_tokens
         T, D, H = max_tokens, cfg.head_dim, cfg.hidden
         # ---- step inputs (written in place by the host, or by the advance kernel) ----
         self.tokens = torch.zeros(T, dtype=i32, device=dev)
@@ -95,6 +98,17 @@ class DecoderEngine:
         self.hl = torch.zeros(max_seqs, H, dtype=bf, device=dev)
         self.xl = torch.zeros(max_seqs, H, dtype=bf, device=dev)
         self.logits = torch.zeros(max_seqs, cfg.vocab, dtype=torch.float32, device=dev)
+        vl = cfg.vocab // self.tp
+        if self.tp == 1:
+            self.logits_local = self.logits
+        else:
+            rows = max(max_seqs, 128)
+            self.logits_local = torch.zeros(rows, vl, dtype=torch.float32, device=dev)
+            self.logits_sel = torch.zeros(max_seqs, vl, dtype=torch.float32, device=dev)
+            self.logits_gather = torch.zeros(self.tp * max_seqs * vl, dtype=torch.float32, device=dev)
+            G = K.argmax_groups(vl)
+            self.argmax_part_local = torch.zeros(max_seqs * G * 3, dtype=torch.int32, device=dev)
+            self.argmax_part_all = torch.zeros(self.tp * max_seqs * G * 3, dtype=torch.int32, device=dev)
         self.picked = torch.zeros(max_seqs, 2, dtype=i32, device=dev)
         self.argmax_scratch = K.argmax_scratch(max_seqs, cfg.vocab, dev)
         self.attn_splits_max = 16
@@ -104,6 +118,8 @@ class DecoderEngine:
         cos, sin = rope_tables(cfg, cfg.max_position)
         self.cos, self.sin = cos.to(dev), sin.to(dev)
         self.scale = 1.0 / math.sqrt(D)
+        if comm is not None:
+            comm.attach(self)
         self._graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.launches_per_step: Dict[Tuple, int] = {}
         self._launch_counter = 0
@@ -157,6 +173,10 @@ class DecoderEngine:
         """Launch the whole step on the current stream (eagerly or under capture)."""
         cfg, w = self.cfg, self.w
         T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
+        if self.comm is not None and getattr(self.comm, "fused", False):
+            R = self.comm.rows_for(T)
+            if R:
+                return self._forward_tp_fused(shape, R)
         self._launch_counter = 0
         h = self.h[:T]
         self._count()
@@ -186,7 +206,6 @@ class DecoderEngine:
                     pending = self.comm.row_parallel(self, act, L.wdown, T)
                 else:
                     pending = self._proj_to_residual(act, L.wdown, T)
-        # ---- head: gather the logit rows, final norm, LM head, sampler ----
         if pending is not None:
             self._count()
             K.reduce_partials(h, pending, h)
@@ -198,18 +217,83 @@ class DecoderEngine:
             torch.index_select(h, 0, self.logit_idx[:B], out=hl)
         self._count()
         K.rmsnorm(hl, w.final_norm, cfg.norm_eps, out=self.xl[:B])
-        self._linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits[:B])
-        if shape.sampler == 0:
-            self._count(2)
-            K.argmax(self.logits[:B], out=self.picked[:B], scratch=self.argmax_scratch)
+        self._linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits_local[:B])
+        self._sample(shape, self.logits_local[:B])
+
+    def _sample(self, shape: StepShape, local_logits: torch.Tensor) -> None:
+        """Sampler suffix over (possibly vocabulary-sharded) logits; every rank ends with the same ``picked``."""
+        B, V = shape.logit_rows, self.cfg.vocab
+        if self.tp == 1:
+            logits = local_logits
+            if shape.sampler == 0:
+                self._count(2)
+                K.argmax(logits, out=self.picked[:B], scratch=self.argmax_scratch)
         else:
+            vl = V // self.tp
+            if shape.sampler == 0:
+                # greedy: exchange the stage-1 partial tables (a few KB), not the logits
+                G = K.argmax_groups(vl)
+                part = self.argmax_part_local[:B * G * 3].view(B, G, 3)
+                self._count()
+                K.argmax_partials(local_logits, self.w.tp_rank * vl, V, part)
+                allp = self.argmax_part_all[:self.tp * B * G * 3].view(self.tp, B, G, 3)
+                self.comm.all_gather(allp, part)
+                self._count()
+                K.argmax_combine(allp, B, G, V, self.picked[:B])
+            else:
+                gathered = self.logits_gather[:self.tp * B * vl].view(self.tp, B, vl)
+                self.comm.all_gather(gathered, local_logits.contiguous() if local_logits.stride(0) != vl else local_logits)
+                logits = self.logits[:B]
+                logits.view(B, self.tp, vl).copy_(gathered.permute(1, 0, 2))
+        if shape.sampler != 0:
             self._count()
-            K.sample_gumbel(self.logits[:B], self.samp_params[:B], self.samp_topk[:B], self.samp_seeds[:B],
-                            shape.sampler, out=self.picked[:B])
+            K.sample_gumbel(logits, self.samp_params[:B], self.samp_topk[:B], self.samp_seeds[:B], shape.sampler,
+                            out=self.picked[:B])
         if shape.chain:
             self._count()
             K.decode_advance(self.picked, self.tokens, self.positions, self.slots, self.row_ctx, self.block_tables,
                              self.row_seq, B)
+
+    def _forward_tp_fused(self, shape: StepShape, R: int) -> None:
+        """Decode-sized step on the fused tensor-parallel path: the residual stream is sharded by token rows
+        (S rows per rank, R = world * S padded rows); every projection is one kernel that also does its collective."""
+        cfg, w, comm = self.cfg, self.w, self.comm
+        T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
+        S = R // self.tp
+        r0 = w.tp_rank * S
+        self._launch_counter = 0
+        self._count(2)
+        comm.begin_step()
+        K.embed_gather(self.tokens[r0:r0 + S], w.embed, out=comm.h_shard[:S])
+        ag, rs = 0, -1
+        for l, L in enumerate(w.layers):
+            self._count(5 + (1 if self._attn_splits(R) > 1 else 0))
+            comm.norm(L.ln1, S, cfg.norm_eps, ag_site=ag, rs_site=rs)
+            comm.gemm(K.EPI_STORE, None, L.wqkv, self.qkv[:R], S, ag_site=ag)
+            K.rope_kv_write(self.qkv[:R], self.q[:R], self.kv.k(l), self.kv.v(l), self.positions[:R], self.slots[:R],
+                            self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
+            K.attn_paged(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:R], self.row_ctx[:R],
+                         self.hq, self.hkv, D, self.scale, out=self.attn[:R], splits=self._attn_splits(R),
+                         scratch=self.attn_scratch, softcap=cfg.attn_softcap, window=cfg.sliding_window)
+            rs += 1
+            comm.gemm(K.EPI_STORE, self.attn[:R], L.wo, None, S, rs_site=rs)
+            ag += 1
+            self._count(3)
+            comm.norm(L.ln2, S, cfg.norm_eps, ag_site=ag, rs_site=rs)
+            comm.gemm(K.EPI_SWIGLU, None, L.wgu, self.act[:R], S, ag_site=ag)
+            rs += 1
+            comm.gemm(K.EPI_STORE, self.act[:R], L.wdown, None, S, rs_site=rs)
+            ag += 1
+        self._count(2)
+        comm.norm(w.final_norm, S, cfg.norm_eps, ag_site=ag, rs_site=rs)
+        comm.gemm(K.EPI_F32, None, w.lm_head, self.logits_local[:R], S, ag_site=ag)
+        if B == T:
+            local = self.logits_local[:B]
+        else:
+            self._count()
+            local = self.logits_sel[:B]
+            torch.index_select(self.logits_local[:R], 0, self.logit_idx[:B], out=local)
+        self._sample(shape, local)
 
     def _moe(self, l, L, x, T):
         from . import moe as _moe
@@ -259,6 +343,14 @@ class DecoderEngine:
         self.slots[:T].copy_(slots, non_blocking=non_blocking)
         self.row_seq[:T].copy_(row_seq, non_blocking=non_blocking)
         self.row_ctx[:T].copy_(row_ctx, non_blocking=non_blocking)
+        if self.comm is not None and getattr(self.comm, "fused", False):
+            R = self.comm.rows_for(T)
+            if R > T:  # padding rows of the fused path: no KV write, empty context
+                self.tokens[T:R].zero_()
+                self.positions[T:R].zero_()
+                self.slots[T:R].fill_(-1)
+                self.row_ctx[T:R].zero_()
+                self.row_seq[T:R].zero_()
         B = logit_idx.numel()
         self.logit_idx[:B].copy_(logit_idx, non_blocking=non_blocking)
         if block_tables is not None:

@@ -146,6 +146,8 @@ def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02,
         layers.append(L)
     embed = draw((cfg.vocab, H), 1)
     lm_head = embed if cfg.tie_embeddings else draw((cfg.vocab, H), 2)
+    if tp_world > 1:
+        lm_head = shard_rows(lm_head, tp_rank, tp_world)  # vocabulary-parallel head
     return DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H), lm_head=lm_head, layers=layers, tp_rank=tp_rank,
                           tp_world=tp_world)
 
@@ -180,5 +182,7 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
         layers.append(L)
     embed = get("embed")
     lm_head = embed if cfg.tie_embeddings or "lm_head" not in tensors else get("lm_head")
+    if tp_world > 1:
+        lm_head = shard_rows(lm_head, tp_rank, tp_world)
     return DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm"), lm_head=lm_head, layers=layers,
                           tp_rank=tp_rank, tp_world=tp_world)

@@ -1,0 +1,77 @@
+"""Child process of the multi-GPU tests: one rank of a tensor-parallel run (launched by torch.distributed.run).
+
+Compares the tensor-parallel engine (NCCL baseline and fused NVLink kernels) with a single-GPU engine that
+runs the unsharded model on the same device: same greedy tokens, vocabulary-shard logits within tolerance.
+"""
+import os
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import torch
+import torch.distributed as dist
+
+
+def main():
+    kind = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from poot_b200.models.config import DecoderConfig
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.parallel.tp import make_comm
+    from poot_b200.runtime.engine import DecoderEngine
+    from poot_b200.runtime.session import FixedBatchSession
+    from poot_b200.runtime.weights import random_weights
+
+    K.set_pdl(True)
+    cfg = DecoderConfig(n_layers=3, hidden=512, n_heads=8, n_kv_heads=8 if world > 4 else 4, head_dim=64, ffn=1024,
+                        vocab=4096, max_position=256)
+    B, P, steps = int(os.environ.get("TP_TEST_BATCH", "5")), 12, 6
+    max_len, bps = 64, 4
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab, (B, P), generator=g, dtype=torch.int32)
+
+    def run(weights, comm):
+        eng = DecoderEngine(weights, num_blocks=B * bps, max_seqs=B, max_tokens=B * P, max_blocks_per_seq=bps, comm=comm)
+        sess = FixedBatchSession(eng, B, max_len)
+        toks = sess.prefill_fast(prompts)[:, 0].tolist()
+        out = [list(toks)]
+        logits = []
+        for _ in range(steps):
+            toks = sess.decode(toks)[:, 0].tolist()
+            out.append(list(toks))
+            logits.append(eng.logits_local[:B].clone())
+        K.check_status()
+        return out, logits
+
+    ref_tokens, ref_logits = run(random_weights(cfg, dev, seed=3, std=0.05), None)
+    comm = make_comm(kind, rank, world, dev)
+    tp_tokens, tp_logits = run(random_weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_world=world), comm)
+    vl = cfg.vocab // world
+    worst = 0.0
+    for a, b in zip(ref_logits, tp_logits):
+        ref = a[:, rank * vl:(rank + 1) * vl]
+        worst = max(worst, (ref - b).abs().max().item() / max(1.0, ref.abs().max().item()))
+    same = sum(int(x == y) for a, b in zip(ref_tokens, tp_tokens) for x, y in zip(a, b))
+    total = sum(len(a) for a in ref_tokens)
+    # every rank must have picked the same tokens
+    t = torch.tensor(tp_tokens, device=dev)
+    gathered = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(gathered, t)
+    agree = all(torch.equal(gathered[0], x) for x in gathered)
+    print(f"TPRESULT rank={rank} kind={kind} world={world} logits_rel_err={worst:.4f} tokens_same={same}/{total} "
+          f"ranks_agree={agree}", flush=True)
+    ok = worst < 0.06 and agree and same >= total - 2
+    if hasattr(comm, "close"):
+        dist.barrier()
+        comm.close()
+    dist.destroy_process_group()
+    sys.exit(0 if ok else 1)
+
+
+if __name__ == "__main__":
+    main()
