@@ -87,9 +87,10 @@ def fuse_qkv(wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, cfg: DecoderC
     D = cfg.head_dim
     hq, hkv = cfg.n_heads // world, max(cfg.n_kv_heads // world, 1)
     q = wq[rank * hq * D:(rank + 1) * hq * D]
-    kv_rank = rank * cfg.n_kv_heads // world if cfg.n_kv_heads >= world else rank % cfg.n_kv_heads
-    k = wk[kv_rank * hkv * D:(kv_rank + 1) * hkv * D]
-    v = wv[kv_rank * hkv * D:(kv_rank + 1) * hkv * D]
+    # first KV head of this rank; with fewer KV heads than ranks a head is replicated over world/n_kv ranks
+    k0 = rank * hkv if cfg.n_kv_heads >= world else rank * cfg.n_kv_heads // world
+    k = wk[k0 * D:(k0 + hkv) * D]
+    v = wv[k0 * D:(k0 + hkv) * D]
     return torch.cat([q, k, v], dim=0).contiguous()
 
 
