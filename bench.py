@@ -257,7 +257,14 @@ def main() -> None:
         }
         print(json.dumps(out))
     if world > 1:
-        dist.destroy_process_group()
+        # Tear-down of a process group that owns captured NCCL graphs can block; results are out, so synchronise,
+        # release the peer mappings and leave without running the destructors.
+        sys.stdout.flush()
+        dist.barrier()
+        torch.cuda.synchronize()
+        if comm is not None and hasattr(comm, "close"):
+            comm.close()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -6,7 +6,8 @@
 //  * tp_norm_kernel: the consumer side of the fused GEMM + reduce-scatter and the producer side of the
 //    fused all-gather + GEMM.  For this rank's S token rows it waits (bounded) for every rank's
 //    contribution of the previous projection, adds them in rank order to the residual stream, applies
-//    RMSNorm and publishes the normalised shard to all peers with one flag write per peer.
+//    RMSNorm and pushes the normalised rows into every rank's gather buffer (the all-gather), then
+//    publishes them with one flag write per peer.
 //  * tp_link_probe_kernel: start-up delivery check of every directed link (pattern write, read back),
 //    the counterpart of the reference's 256 B / 64 KiB / 4 MiB probe
 //    (crates/poot-ptx-runtime/src/context.rs:643-682).
@@ -25,7 +26,6 @@ __global__ void __launch_bounds__(THREADS)
 tp_norm_kernel(__nv_bfloat16* __restrict__ h_shard,            // [S, H] residual stream rows owned by this rank
                const __nv_bfloat16* __restrict__ inbox_local,  // [2][world][S][H] contributions (or unused)
                const __nv_bfloat16* __restrict__ w,            // [H]
-               __nv_bfloat16* __restrict__ xs_local,           // [2][S][H] normalised shard, gathered by peers
                int H, float eps, int* __restrict__ status, const __grid_constant__ TpArgs tp) {
   __shared__ float red[32];
   __shared__ int s_ok;
@@ -79,7 +79,8 @@ tp_norm_kernel(__nv_bfloat16* __restrict__ h_shard,            // [S, H] residua
   const float inv = rsqrtf(tot / (float)H + eps);
   const uint32_t ag_target = tp_target(tp, tp.ag_site, tp.ag_sites);
   const int out_parity = (int)(ag_target & 1u);
-  uint4* yr = reinterpret_cast<uint4*>(xs_local + ((size_t)(out_parity * tp.S + row)) * H);
+  // all-gather by push: this rank's rows go into every rank's gather buffer (16-byte peer stores, whole rows)
+  const size_t xoff = ((size_t)(out_parity * tp.world * tp.S + tp.rank * tp.S + row)) * H;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
 #pragma unroll
   for (int i = 0; i < MAXV; ++i) {
@@ -89,7 +90,8 @@ tp_norm_kernel(__nv_bfloat16* __restrict__ h_shard,            // [S, H] residua
       unpack8(wr[c], wf);
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = v[i][j] * inv * wf[j];
-      yr[c] = pack8(o);
+      const uint4 pk = pack8(o);
+      for (int d = 0; d < tp.world; ++d) reinterpret_cast<uint4*>(tp.xs_peer[d] + xoff)[c] = pk;
     }
   }
   tp_signal_all(tp, TP_CH_AG, ag_target, (int)gridDim.x);
@@ -143,23 +145,23 @@ static void fill_tp(TpArgs& tp, int world, int rank, int S, int ag_site, int ag_
 }
 
 // h_shard [S,H] += sum over ranks of inbox (when rs_site >= 0); xs_local[parity] = rmsnorm(h_shard) * w; signal ag_site.
-POOT_API int poot_tp_norm(void* h_shard, const void* inbox_local, const void* w, void* xs_local, int H, float eps,
+POOT_API int poot_tp_norm(void* h_shard, const void* inbox_local, const void* w, void* const* xs_peer, int H, float eps,
                           int world, int rank, int S, int ag_site, int ag_sites, int rs_site, int rs_sites,
                           const int* epoch, void* flags_local, void* const* flags_peer, int* ticket, int* status,
                           cudaStream_t s) {
   if (H % 8 || world < 2 || world > TP_MAX_WORLD) return (int)cudaErrorInvalidValue;
   TpArgs tp = {};
   fill_tp(tp, world, rank, S, ag_site, ag_sites, rs_site, rs_sites, epoch, flags_local, flags_peer, ticket);
+  for (int r = 0; r < world; ++r) tp.xs_peer[r] = (__nv_bfloat16*)xs_peer[r];
   __nv_bfloat16* hb = (__nv_bfloat16*)h_shard;
   const __nv_bfloat16* ib = (const __nv_bfloat16*)inbox_local;
   const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
-  __nv_bfloat16* xb = (__nv_bfloat16*)xs_local;
   const int H8 = H / 8;
-  if (H8 <= 128) return launch_k(tp_norm_kernel<128, 1>, dim3(S), dim3(128), 0, s, hb, ib, wb, xb, H, eps, status, tp);
-  if (H8 <= 256) return launch_k(tp_norm_kernel<256, 1>, dim3(S), dim3(256), 0, s, hb, ib, wb, xb, H, eps, status, tp);
-  if (H8 <= 512) return launch_k(tp_norm_kernel<512, 1>, dim3(S), dim3(512), 0, s, hb, ib, wb, xb, H, eps, status, tp);
-  if (H8 <= 1024) return launch_k(tp_norm_kernel<512, 2>, dim3(S), dim3(512), 0, s, hb, ib, wb, xb, H, eps, status, tp);
-  if (H8 <= 2048) return launch_k(tp_norm_kernel<512, 4>, dim3(S), dim3(512), 0, s, hb, ib, wb, xb, H, eps, status, tp);
+  if (H8 <= 128) return launch_k(tp_norm_kernel<128, 1>, dim3(S), dim3(128), 0, s, hb, ib, wb, H, eps, status, tp);
+  if (H8 <= 256) return launch_k(tp_norm_kernel<256, 1>, dim3(S), dim3(256), 0, s, hb, ib, wb, H, eps, status, tp);
+  if (H8 <= 512) return launch_k(tp_norm_kernel<512, 1>, dim3(S), dim3(512), 0, s, hb, ib, wb, H, eps, status, tp);
+  if (H8 <= 1024) return launch_k(tp_norm_kernel<512, 2>, dim3(S), dim3(512), 0, s, hb, ib, wb, H, eps, status, tp);
+  if (H8 <= 2048) return launch_k(tp_norm_kernel<512, 4>, dim3(S), dim3(512), 0, s, hb, ib, wb, H, eps, status, tp);
   return (int)cudaErrorInvalidValue;
 }
 

@@ -27,9 +27,6 @@ constexpr int SK_BM = 128;   // weight rows per CTA
 constexpr int SK_BK = 64;
 constexpr int SK_THREADS = 192;
 
-// One tensor map per rank over its activation shard buffer [2 * S rows, K] (box = S rows x 64 columns).
-struct TpMaps { CUtensorMap m[TP_MAX_WORLD]; };
-
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -60,7 +57,7 @@ template <int BT, int STAGES, int WM, int EPI>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    void* __restrict__ out, const __nv_bfloat16* resid, int M, int N, int K, int ldo, int CK,
-                   int* __restrict__ status, const __grid_constant__ TpArgs tp, const __grid_constant__ TpMaps maps) {
+                   int* __restrict__ status, const __grid_constant__ TpArgs tp) {
   using S = SkinnySmem<BT, STAGES, WM>;
   constexpr int ROWS = WM * SK_BM;  // weight rows per CTA
   extern __shared__ uint8_t smem_raw[];
@@ -119,21 +116,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       bool ok = true;
       if (gather) {
         const uint32_t target = tp_target(tp, tp.ag_site, tp.ag_sites);
-        xrow = (int)(target & 1u) * tp.S;
+        xrow = (int)(target & 1u) * BT;
+        // every rank pushed its normalised rows into this rank's gather buffer; wait until all have landed
         for (int r = 0; r < tp.world; ++r)
           if (!wait_flag_ge(tp.flags_local + TP_CH_AG * TP_MAX_WORLD + r, target)) ok = false;
         if (!ok) atomicExch(status, (int)kTimeoutPeerFlag);
-        fence_proxy_async_global();  // peers wrote the shards with ordinary stores; TMA reads them
+        fence_proxy_async_global();  // the rows were written with ordinary (peer) stores; TMA reads them
       }
-      // X tile of one K step: rows [r*S, (r+1)*S) come from rank r's shard (peer memory, plain TMA load)
-      auto load_x = [&](uint32_t dst, int kx, uint32_t bar) {
-        if (gather) {
-          for (int r = 0; r < tp.world; ++r)
-            tc::tma_load_2d(dst + (uint32_t)(r * tp.S * SK_BK * 2), &maps.m[r], kx, xrow, bar);
-        } else {
-          tc::tma_load_2d(dst, &tmX, kx, 0, bar);
-        }
-      };
+      auto load_x = [&](uint32_t dst, int kx, uint32_t bar) { tc::tma_load_2d(dst, &tmX, kx, xrow, bar); };
       for (int i = 0; i < pre; ++i)
         load_x(base + i * S::STAGE_BYTES + S::W_BYTES, (kt_begin + i) * SK_BK, full_bar + 8 * i);
       int issued = pre;
@@ -270,8 +260,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
 template <int BT, int STAGES, int WM, int EPI>
 static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid, int M, int N,
-                             int K, int ldo, int CK, int pdl, int* status, cudaStream_t s, const TpArgs& tp,
-                             const TpMaps& maps) {
+                             int K, int ldo, int CK, int pdl, int* status, cudaStream_t s, const TpArgs& tp) {
   using S = SkinnySmem<BT, STAGES, WM>;
   auto kern = gemm_skinny_kernel<BT, STAGES, WM, EPI>;
   static bool configured = false;
@@ -300,30 +289,29 @@ static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void*
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  return (int)cudaLaunchKernelEx(&cfg, kern, tw, tx, out, (const __nv_bfloat16*)resid, M, N, K, ldo, CK, status, tp, maps);
+  return (int)cudaLaunchKernelEx(&cfg, kern, tw, tx, out, (const __nv_bfloat16*)resid, M, N, K, ldo, CK, status, tp);
 }
 
 template <int BT, int STAGES, int WM>
 static int launch_skinny_epi(int epi, const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid,
                              int M, int N, int K, int ldo, int CK, int pdl, int* status, cudaStream_t s,
-                             const TpArgs& tp, const TpMaps& maps) {
+                             const TpArgs& tp) {
   switch (epi) {
-    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, WM, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, maps);
-    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, WM, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, maps);
-    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, WM, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, maps);
-    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, WM, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, maps);
+    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, WM, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp);
+    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, WM, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp);
+    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, WM, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp);
+    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, WM, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp);
     default: return (int)cudaErrorInvalidValue;
   }
 }
 
 static int skinny_dispatch(int epi, const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid, int M,
-                           int N, int K, int ldo, int ck, int bt, int pdl, int* status, cudaStream_t s, const TpArgs& tp,
-                           const TpMaps& maps) {
+                           int N, int K, int ldo, int ck, int bt, int pdl, int* status, cudaStream_t s, const TpArgs& tp) {
   switch (bt) {
-    case 16: return launch_skinny_epi<16, 6, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, maps);
-    case 32: return launch_skinny_epi<32, 5, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, maps);
-    case 64: return launch_skinny_epi<64, 4, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, maps);
-    case 128: return launch_skinny_epi<128, 3, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, maps);
+    case 16: return launch_skinny_epi<16, 6, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp);
+    case 32: return launch_skinny_epi<32, 5, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp);
+    case 64: return launch_skinny_epi<64, 4, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp);
+    case 128: return launch_skinny_epi<128, 3, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp);
     default: return (int)cudaErrorInvalidValue;
   }
 }
@@ -350,20 +338,19 @@ POOT_API int poot_gemm_skinny(int epi, const void* x, const void* W, void* out, 
   if (e) return e;
   TpArgs tp = {};
   tp.world = 1; tp.ag_site = -1; tp.rs_site = -1;
-  TpMaps maps = {};
-  return skinny_dispatch(epi, tw, tx, out, resid, M, N, K, ldo, ck, bt, pdl, status, s, tp, maps);
+  return skinny_dispatch(epi, tw, tx, out, resid, M, N, K, ldo, ck, bt, pdl, status, s, tp);
 }
 
 // Tensor-parallel form.  The step has world*S padded token rows (16, 32, 64 or 128).
-//   ag_site >= 0: X is gathered from the ranks' activation shard buffers xs_peer[r] ([2*S, K] bf16, this rank's
-//                 mapping of rank r's buffer) once rank r's flag for the site is visible; otherwise X is `x` (local).
+//   ag_site >= 0: X is this rank's gather buffer `x` ([2 * world*S, K] bf16, double-buffered on the site parity) into
+//                 which every rank pushed its normalised rows; the producer warp waits for all ranks' flags of the
+//                 site before its first activation load.  Otherwise X is `x` ([world*S, ldx], local data).
 //   rs_site >= 0: output rows are scattered (bf16) to their owner ranks' inboxes and the site is signalled;
 //                 otherwise the epilogue `epi` writes to `out` locally.
 POOT_API int poot_gemm_skinny_tp(int epi, const void* x, const void* W, void* out, int N, int K, int ldx, int ldo,
                                  int ck, int world, int rank, int S, int ag_site, int ag_sites, int rs_site,
                                  int rs_sites, const int* epoch, void* flags_local, void* const* flags_peer,
-                                 void* const* inbox_peer, int ld_inbox, void* const* xs_peer, int* ticket, int* status,
-                                 cudaStream_t s) {
+                                 void* const* inbox_peer, int ld_inbox, int* ticket, int* status, cudaStream_t s) {
   if (world < 2 || world > TP_MAX_WORLD || S % 8 || K % 8) return (int)cudaErrorInvalidValue;
   const int bt = world * S;
   if (bt != 16 && bt != 32 && bt != 64 && bt != 128) return (int)cudaErrorInvalidValue;
@@ -373,13 +360,9 @@ POOT_API int poot_gemm_skinny_tp(int epi, const void* x, const void* W, void* ou
   CUtensorMap tw, tx;
   int e = make_tmap_bf16_2d(&tw, W, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)SK_BM);
   if (e) return e;
-  TpMaps maps = {};
   if (ag_site >= 0) {
-    for (int r = 0; r < world; ++r) {
-      e = make_tmap_bf16_2d(&maps.m[r], xs_peer[r], (uint64_t)(2 * S), (uint64_t)K, (uint64_t)K, (uint32_t)S);
-      if (e) return e;
-    }
-    tx = maps.m[rank];
+    e = make_tmap_bf16_2d(&tx, x, (uint64_t)(2 * bt), (uint64_t)K, (uint64_t)K, (uint32_t)bt);
+    if (e) return e;
   } else {
     e = make_tmap_bf16_2d(&tx, x, (uint64_t)bt, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt);
     if (e) return e;
@@ -392,5 +375,5 @@ POOT_API int poot_gemm_skinny_tp(int epi, const void* x, const void* W, void* ou
     tp.flags_peer[r] = (uint32_t*)flags_peer[r];
     tp.inbox_peer[r] = inbox_peer ? (__nv_bfloat16*)inbox_peer[r] : nullptr;
   }
-  return skinny_dispatch(epi, tw, tx, out, nullptr, bt, N, K, ldo, ck, bt, 0, status, s, tp, maps);
+  return skinny_dispatch(epi, tw, tx, out, nullptr, bt, N, K, ldo, ck, bt, 0, status, s, tp);
 }

@@ -41,6 +41,7 @@ struct TpArgs {
   uint32_t* flags_local;        // this rank's flag block [2 * 8]
   uint32_t* flags_peer[TP_MAX_WORLD];        // every rank's flag block (peer mappings; [rank] = local)
   __nv_bfloat16* inbox_peer[TP_MAX_WORLD];   // every rank's inbox [2][world][S][ld_inbox] bf16
+  __nv_bfloat16* xs_peer[TP_MAX_WORLD];      // every rank's gather buffer [2][world*S][ld_inbox] bf16
   int* ticket;                  // local CTA-completion counter (self-resetting)
 };
 

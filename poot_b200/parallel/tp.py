@@ -6,8 +6,9 @@ kernel adds it to the residual stream - one library collective per projection, c
 ``FusedComm`` is the product path for steps of up to 128 padded token rows (decode batches): the o_proj /
 down_proj GEMMs scatter their output tiles straight into the owner ranks' inboxes over NVLink
 (GEMM + reduce-scatter in one kernel), the consumer kernel reduces the inboxes into the token-sharded
-residual stream and normalises it (reduce + RMSNorm), and the following qkv / gate_up GEMM gathers the
-normalised shards from the peers with TMA loads inside its producer warp (all-gather + GEMM in one kernel).
+residual stream and normalises it (reduce + RMSNorm), pushes the rows into every rank's gather buffer, and the following qkv / gate_up GEMM's producer
+warp waits for the ranks' flags before its first activation load (all-gather + GEMM without a separate collective;
+a remote row crosses NVLink once and is then read from local memory by every CTA).
 Larger steps (prefill chunks) fall back to the NCCL form.
 
 Sharding follows the reference's Megatron layouts (crates/poot-graph-plan/src/passes/sharding.rs:219-251);
@@ -77,7 +78,7 @@ class FusedComm(NcclComm):
         self.off_inbox = 1024
         inbox_bytes = 2 * w * self.s_max * H * 2
         self.off_xs = self.off_inbox + (inbox_bytes + 1023) // 1024 * 1024
-        xs_bytes = 2 * self.s_max * H * 2
+        xs_bytes = 2 * self.MAX_ROWS * H * 2
         total = self.off_xs + (xs_bytes + 1023) // 1024 * 1024
         self.block = SymmetricBlock(total, self.rank, w, self.device, self.group)
         if self.probe_links:
@@ -99,7 +100,7 @@ class FusedComm(NcclComm):
                                _P, _P, _P, _P]
         self._gemm = lib.poot_gemm_skinny_tp
         self._gemm.argtypes = [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P, _P]
+                               c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P]
 
     # ---- geometry -------------------------------------------------------------------------------------------
     def rows_for(self, T: int) -> int:
@@ -118,7 +119,7 @@ class FusedComm(NcclComm):
         """Reduce the inboxes of ``rs_site`` (if >= 0) into the residual shard, normalise, publish for ``ag_site``."""
         b = self.block
         check(self._norm(self.h_shard.data_ptr(), b.ptr(self.rank, self.off_inbox), w.data_ptr(),
-                         b.ptr(self.rank, self.off_xs), self.H, float(eps), self.world, self.rank, S, ag_site,
+                         self.xs_peer, self.H, float(eps), self.world, self.rank, S, ag_site,
                          self.ag_sites, rs_site, self.rs_sites, self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags),
                          self.flags_peer, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
               "tp_norm")
@@ -131,11 +132,12 @@ class FusedComm(NcclComm):
         ldx = x.stride(0) if x is not None else Kd
         ldo = out.stride(0) if out is not None else self.H
         b = self.block
-        check(self._gemm(epi, None if x is None else x.data_ptr(), W.data_ptr(), None if out is None else out.data_ptr(),
+        xptr = b.ptr(self.rank, self.off_xs) if ag_site >= 0 else x.data_ptr()
+        check(self._gemm(epi, xptr, W.data_ptr(), None if out is None else out.data_ptr(),
                          N, Kd, ldx, ldo, ck, self.world, self.rank, S, ag_site, self.ag_sites, rs_site, self.rs_sites,
                          self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer, self.inbox_peer,
-                         self.H, self.xs_peer, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(),
-                         K._stream()), "gemm_skinny_tp")
+                         self.H, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
+              "gemm_skinny_tp")
 
     def close(self) -> None:
         if self.block is not None:

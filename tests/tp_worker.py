@@ -35,14 +35,17 @@ def main():
     g = torch.Generator().manual_seed(0)
     prompts = torch.randint(0, cfg.vocab, (B, P), generator=g, dtype=torch.int32)
 
-    def run(weights, comm):
+    def run(weights, comm, forced=None):
+        """Greedy run; with ``forced`` the fed tokens are the reference's (random weights give near-tied logits,
+        so a pick may legitimately differ and must not change the rest of the comparison)."""
         eng = DecoderEngine(weights, num_blocks=B * bps, max_seqs=B, max_tokens=B * P, max_blocks_per_seq=bps, comm=comm)
         sess = FixedBatchSession(eng, B, max_len)
         toks = sess.prefill_fast(prompts)[:, 0].tolist()
         out = [list(toks)]
-        logits = []
-        for _ in range(steps):
-            toks = sess.decode(toks)[:, 0].tolist()
+        logits = [eng.logits_local[:B].clone()]
+        for i in range(steps):
+            feed = forced[i] if forced is not None else toks
+            toks = sess.decode(feed)[:, 0].tolist()
             out.append(list(toks))
             logits.append(eng.logits_local[:B].clone())
         K.check_status()
@@ -50,14 +53,20 @@ def main():
 
     ref_tokens, ref_logits = run(random_weights(cfg, dev, seed=3, std=0.05), None)
     comm = make_comm(kind, rank, world, dev)
-    tp_tokens, tp_logits = run(random_weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_world=world), comm)
+    tp_tokens, tp_logits = run(random_weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_world=world), comm,
+                               forced=ref_tokens)
     vl = cfg.vocab // world
     worst = 0.0
-    for a, b in zip(ref_logits, tp_logits):
+    same = total = 0
+    for a, b, rt, tt in zip(ref_logits, tp_logits, ref_tokens, tp_tokens):
         ref = a[:, rank * vl:(rank + 1) * vl]
         worst = max(worst, (ref - b).abs().max().item() / max(1.0, ref.abs().max().item()))
-    same = sum(int(x == y) for a, b in zip(ref_tokens, tp_tokens) for x, y in zip(a, b))
-    total = sum(len(a) for a in ref_tokens)
+        top2 = torch.topk(a, 2, dim=-1).values
+        clear = (top2[:, 0] - top2[:, 1]) > 0.05 * a.abs().max()
+        for i in range(B):
+            if bool(clear[i]):      # a pick may differ only inside a near tie of the top two logits
+                total += 1
+                same += int(rt[i] == tt[i])
     # every rank must have picked the same tokens
     t = torch.tensor(tp_tokens, device=dev)
     gathered = [torch.empty_like(t) for _ in range(world)]
@@ -65,7 +74,7 @@ def main():
     agree = all(torch.equal(gathered[0], x) for x in gathered)
     print(f"TPRESULT rank={rank} kind={kind} world={world} logits_rel_err={worst:.4f} tokens_same={same}/{total} "
           f"ranks_agree={agree}", flush=True)
-    ok = worst < 0.06 and agree and same >= total - 2
+    ok = worst < 0.06 and agree and same == total
     if hasattr(comm, "close"):
         dist.barrier()
         comm.close()
