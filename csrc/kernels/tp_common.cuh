@@ -72,12 +72,12 @@ __device__ __forceinline__ uint32_t tp_target(const TpArgs& tp, int site, int si
 // Called by every CTA after its peer stores; the last CTA to arrive publishes `target` on channel `ch`
 // of every rank's flag block.  All threads of the CTA must call it (it contains a barrier).
 __device__ __forceinline__ void tp_signal_all(const TpArgs& tp, int ch, uint32_t target, int num_ctas) {
-  __threadfence_system();  // this thread's peer stores are ordered before the ticket
-  __syncthreads();
+  __syncthreads();  // every thread's peer stores are ordered before thread 0's fence (CTA-scope barrier)
   if (threadIdx.x == 0) {
+    __threadfence_system();  // one system-scope fence per CTA: cumulative over the stores observed above
     int t = atomicAdd(tp.ticket, 1);
     if (t == num_ctas - 1) {
-      __threadfence_system();  // cumulativity: every CTA's stores (observed through the ticket) come first
+      __threadfence_system();  // every CTA's stores (observed through the ticket) come before the flags
       for (int d = 0; d < tp.world; ++d) st_release_sys(tp.flags_peer[d] + ch * TP_MAX_WORLD + tp.rank, target);
       atomicExch(tp.ticket, 0);
     }

@@ -44,14 +44,67 @@ _SIGS = {
 _bound = {}
 
 
+_timing_sink = None   # when a list: every launch is bracketed by CUDA events and appended as (name, e0, e1)
+launch_total = 0      # launchers called since import (cheap always-on counter)
+
+
 def _fn(name: str):
     f = _bound.get(name)
     if f is None:
-        f = getattr(kernels(), name)
-        f.argtypes = _SIGS[name]
-        f.restype = c_int
+        raw = getattr(kernels(), name)
+        raw.argtypes = _SIGS[name]
+        raw.restype = c_int
+
+        def f(*args, _raw=raw, _name=name):
+            global launch_total
+            launch_total += 1
+            if _timing_sink is None:
+                return _raw(*args)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = _raw(*args)
+            e1.record()
+            _timing_sink.append((_name, e0, e1))
+            return r
+
         _bound[name] = f
     return f
+
+
+def start_device_timing() -> None:
+    """Opt-in detailed device timing: bracket every launch with CUDA events (eager launches only)."""
+    global _timing_sink
+    _timing_sink = []
+
+
+def timed_region(name: str):
+    """Context manager that times a non-library region (e.g. an NCCL collective) into the same sink."""
+    class _R:
+        def __enter__(self_inner):
+            if _timing_sink is not None:
+                self_inner.e0 = torch.cuda.Event(enable_timing=True)
+                self_inner.e0.record()
+            return self_inner
+
+        def __exit__(self_inner, *exc):
+            if _timing_sink is not None:
+                e1 = torch.cuda.Event(enable_timing=True)
+                e1.record()
+                _timing_sink.append((name, self_inner.e0, e1))
+            return False
+    return _R()
+
+
+def stop_device_timing():
+    """Stop timing; returns ``{launcher name: (count, total microseconds)}`` (synchronises the device)."""
+    global _timing_sink
+    sink, _timing_sink = _timing_sink, None
+    torch.cuda.synchronize()
+    out = {}
+    for name, e0, e1 in sink or []:
+        c, t = out.get(name, (0, 0.0))
+        out[name] = (c + 1, t + e0.elapsed_time(e1) * 1e3)
+    return out
 
 
 def register_signature(name: str, argtypes) -> None:

@@ -48,13 +48,15 @@ class NcclComm:
         """``h += allreduce(x @ W^T)``."""
         p = self.partial[:T]
         engine._linear(x, W, K.EPI_STORE, p)
-        dist.all_reduce(p, group=self.group)
+        with K.timed_region("nccl_all_reduce"):
+            dist.all_reduce(p, group=self.group)
         engine._count()
         K.add(engine.h[:T], p, out=engine.h[:T])
         return None
 
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor) -> None:
-        dist.all_gather_into_tensor(out, inp, group=self.group)
+        with K.timed_region("nccl_all_gather"):
+            dist.all_gather_into_tensor(out, inp, group=self.group)
 
 
 class FusedComm(NcclComm):
@@ -92,15 +94,15 @@ class FusedComm(NcclComm):
         L = engine.cfg.n_layers
         self.rs_sites = 2 * L
         self.ag_sites = 2 * L + 1
-        lib = kernels()
-        self._begin = lib.poot_tp_begin_step
-        self._begin.argtypes = [_P, _P]
-        self._norm = lib.poot_tp_norm
-        self._norm.argtypes = [_P, _P, _P, _P, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P,
-                               _P, _P, _P, _P]
-        self._gemm = lib.poot_gemm_skinny_tp
-        self._gemm.argtypes = [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P]
+        K.register_signature("poot_tp_begin_step", [_P, _P])
+        K.register_signature("poot_tp_norm", [_P, _P, _P, _P, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                                              c_int, _P, _P, _P, _P, _P, _P])
+        K.register_signature("poot_gemm_skinny_tp", [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                     c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P,
+                                                     _P])
+        self._begin = K.fn("poot_tp_begin_step")
+        self._norm = K.fn("poot_tp_norm")
+        self._gemm = K.fn("poot_gemm_skinny_tp")
 
     # ---- geometry -------------------------------------------------------------------------------------------
     def rows_for(self, T: int) -> int:

@@ -223,6 +223,7 @@ class DecoderEngine:
     def _sample(self, shape: StepShape, local_logits: torch.Tensor) -> None:
         """Sampler suffix over (possibly vocabulary-sharded) logits; every rank ends with the same ``picked``."""
         B, V = shape.logit_rows, self.cfg.vocab
+        self.last_local_logits = local_logits  # [B, vocab / tp] of the step just launched
         if self.tp == 1:
             logits = local_logits
             if shape.sampler == 0:

@@ -42,12 +42,12 @@ def main():
         sess = FixedBatchSession(eng, B, max_len)
         toks = sess.prefill_fast(prompts)[:, 0].tolist()
         out = [list(toks)]
-        logits = [eng.logits_local[:B].clone()]
+        logits = [eng.last_local_logits[:B].clone()]
         for i in range(steps):
             feed = forced[i] if forced is not None else toks
             toks = sess.decode(feed)[:, 0].tolist()
             out.append(list(toks))
-            logits.append(eng.logits_local[:B].clone())
+            logits.append(eng.last_local_logits[:B].clone())
         K.check_status()
         return out, logits
 
