@@ -26,6 +26,7 @@ __global__ void __launch_bounds__(THREADS)
 tp_norm_kernel(__nv_bfloat16* __restrict__ h_shard,            // [S, H] residual stream rows owned by this rank
                const __nv_bfloat16* __restrict__ inbox_local,  // [2][world][S][H] contributions (or unused)
                const __nv_bfloat16* __restrict__ w,            // [H]
+               __nv_bfloat16* __restrict__ x_local,            // one-shot form: normalised rows stay local (no push)
                int H, float eps, int* __restrict__ status, const __grid_constant__ TpArgs tp) {
   __shared__ float red[32];
   __shared__ int s_ok;
@@ -77,6 +78,22 @@ tp_norm_kernel(__nv_bfloat16* __restrict__ h_shard,            // [S, H] residua
   float tot = (l < THREADS / 32) ? red[l] : 0.f;
   tot = warp_sum(tot);
   const float inv = rsqrtf(tot / (float)H + eps);
+  if (x_local != nullptr) {
+    const uint4* wr2 = reinterpret_cast<const uint4*>(w);
+    uint4* yr = reinterpret_cast<uint4*>(x_local + (size_t)row * H);
+#pragma unroll
+    for (int i = 0; i < MAXV; ++i) {
+      const int c = threadIdx.x + i * THREADS;
+      if (c < H8) {
+        float wf[8], o[8];
+        unpack8(wr2[c], wf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * inv * wf[j];
+        yr[c] = pack8(o);
+      }
+    }
+    return;
+  }
   const uint32_t ag_target = tp_target(tp, tp.ag_site, tp.ag_sites);
   const int out_parity = (int)(ag_target & 1u);
   // all-gather by push: this rank's rows go into every rank's gather buffer (16-byte peer stores, whole rows)
@@ -145,23 +162,26 @@ static void fill_tp(TpArgs& tp, int world, int rank, int S, int ag_site, int ag_
 }
 
 // h_shard [S,H] += sum over ranks of inbox (when rs_site >= 0); xs_local[parity] = rmsnorm(h_shard) * w; signal ag_site.
-POOT_API int poot_tp_norm(void* h_shard, const void* inbox_local, const void* w, void* const* xs_peer, int H, float eps,
-                          int world, int rank, int S, int ag_site, int ag_sites, int rs_site, int rs_sites,
+// x_local != null selects the one-shot form: `rows` token rows, inbox slots of S rows, output stays local.
+POOT_API int poot_tp_norm(void* h_shard, const void* inbox_local, const void* w, void* const* xs_peer, void* x_local,
+                          int rows, int H, float eps, int world, int rank, int S, int ag_site, int ag_sites, int rs_site, int rs_sites,
                           const int* epoch, void* flags_local, void* const* flags_peer, int* ticket, int* status,
                           cudaStream_t s) {
   if (H % 8 || world < 2 || world > TP_MAX_WORLD) return (int)cudaErrorInvalidValue;
   TpArgs tp = {};
   fill_tp(tp, world, rank, S, ag_site, ag_sites, rs_site, rs_sites, epoch, flags_local, flags_peer, ticket);
-  for (int r = 0; r < world; ++r) tp.xs_peer[r] = (__nv_bfloat16*)xs_peer[r];
+  for (int r = 0; r < world; ++r) tp.xs_peer[r] = xs_peer ? (__nv_bfloat16*)xs_peer[r] : nullptr;
+  __nv_bfloat16* xl = (__nv_bfloat16*)x_local;
+  const int grid = x_local ? rows : S;
   __nv_bfloat16* hb = (__nv_bfloat16*)h_shard;
   const __nv_bfloat16* ib = (const __nv_bfloat16*)inbox_local;
   const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
   const int H8 = H / 8;
-  if (H8 <= 128) return launch_k(tp_norm_kernel<128, 1>, dim3(S), dim3(128), 0, s, hb, ib, wb, H, eps, status, tp);
-  if (H8 <= 256) return launch_k(tp_norm_kernel<256, 1>, dim3(S), dim3(256), 0, s, hb, ib, wb, H, eps, status, tp);
-  if (H8 <= 512) return launch_k(tp_norm_kernel<512, 1>, dim3(S), dim3(512), 0, s, hb, ib, wb, H, eps, status, tp);
-  if (H8 <= 1024) return launch_k(tp_norm_kernel<512, 2>, dim3(S), dim3(512), 0, s, hb, ib, wb, H, eps, status, tp);
-  if (H8 <= 2048) return launch_k(tp_norm_kernel<512, 4>, dim3(S), dim3(512), 0, s, hb, ib, wb, H, eps, status, tp);
+  if (H8 <= 128) return launch_k(tp_norm_kernel<128, 1>, dim3(grid), dim3(128), 0, s, hb, ib, wb, xl, H, eps, status, tp);
+  if (H8 <= 256) return launch_k(tp_norm_kernel<256, 1>, dim3(grid), dim3(256), 0, s, hb, ib, wb, xl, H, eps, status, tp);
+  if (H8 <= 512) return launch_k(tp_norm_kernel<512, 1>, dim3(grid), dim3(512), 0, s, hb, ib, wb, xl, H, eps, status, tp);
+  if (H8 <= 1024) return launch_k(tp_norm_kernel<512, 2>, dim3(grid), dim3(512), 0, s, hb, ib, wb, xl, H, eps, status, tp);
+  if (H8 <= 2048) return launch_k(tp_norm_kernel<512, 4>, dim3(grid), dim3(512), 0, s, hb, ib, wb, xl, H, eps, status, tp);
   return (int)cudaErrorInvalidValue;
 }
 

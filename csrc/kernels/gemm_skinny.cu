@@ -211,7 +211,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const bool scatter = tp.world > 1 && tp.rs_site >= 0;
   const uint32_t rs_target = scatter ? tp_target(tp, tp.rs_site, tp.rs_sites) : 0u;
   const int rs_parity = (int)(rs_target & 1u);
-  const int Mv = scatter ? BT : (M < BT ? M : BT);
+  const int Mv = (scatter && !tp.oneshot) ? BT : (M < BT ? M : BT);
   if (EPI == SEPI_SWIGLU) {
     const int hp = slab >> 1;
     for (int idx = threadIdx.x; idx < hp * Mv; idx += SK_THREADS) {
@@ -240,7 +240,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       const int n = n0 + rr;
       if (n < N) {
-        if (scatter) {
+        if (scatter && tp.oneshot) {
+          // one-shot all-reduce: this rank's partial goes to slot `rank` of every rank's inbox
+          const __nv_bfloat16 bv = __float2bfloat16(v);
+          const size_t off = ((size_t)((rs_parity * tp.world + tp.rank) * tp.S + tok)) * tp.ld_inbox + n;
+          for (int d = 0; d < tp.world; ++d) tp.inbox_peer[d][off] = bv;
+        } else if (scatter) {
           // reduce-scatter: token row `tok` belongs to rank tok / S; write into that rank's inbox slice for this rank
           const int d = tok / tp.S, tl = tok - d * tp.S;
           tp.inbox_peer[d][((size_t)((rs_parity * tp.world + tp.rank) * tp.S + tl)) * tp.ld_inbox + n] =
@@ -350,9 +355,14 @@ POOT_API int poot_gemm_skinny(int epi, const void* x, const void* W, void* out, 
 POOT_API int poot_gemm_skinny_tp(int epi, const void* x, const void* W, void* out, int N, int K, int ldx, int ldo,
                                  int ck, int world, int rank, int S, int ag_site, int ag_sites, int rs_site,
                                  int rs_sites, const int* epoch, void* flags_local, void* const* flags_peer,
-                                 void* const* inbox_peer, int ld_inbox, int* ticket, int* status, cudaStream_t s) {
-  if (world < 2 || world > TP_MAX_WORLD || S % 8 || K % 8) return (int)cudaErrorInvalidValue;
-  const int bt = world * S;
+                                 void* const* inbox_peer, int ld_inbox, int oneshot_rows, int* ticket, int* status,
+                                 cudaStream_t s) {
+  // oneshot_rows > 0: one-shot all-reduce form over that many (unpadded) token rows; X is local, S = rows per slot.
+  if (world < 2 || world > TP_MAX_WORLD || K % 8) return (int)cudaErrorInvalidValue;
+  if (!oneshot_rows && S % 8) return (int)cudaErrorInvalidValue;
+  if (oneshot_rows && (ag_site >= 0 || oneshot_rows > S || oneshot_rows > 128)) return (int)cudaErrorInvalidValue;
+  const int M = oneshot_rows ? oneshot_rows : world * S;
+  const int bt = oneshot_rows ? (M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128))) : world * S;
   if (bt != 16 && bt != 32 && bt != 64 && bt != 128) return (int)cudaErrorInvalidValue;
   if (ck != 1 && ck != 2 && ck != 4 && ck != 8) return (int)cudaErrorInvalidValue;
   if (status == nullptr || epoch == nullptr) return (int)cudaErrorInvalidValue;
@@ -364,10 +374,11 @@ POOT_API int poot_gemm_skinny_tp(int epi, const void* x, const void* W, void* ou
     e = make_tmap_bf16_2d(&tx, x, (uint64_t)(2 * bt), (uint64_t)K, (uint64_t)K, (uint32_t)bt);
     if (e) return e;
   } else {
-    e = make_tmap_bf16_2d(&tx, x, (uint64_t)bt, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt);
+    e = make_tmap_bf16_2d(&tx, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt);
     if (e) return e;
   }
   TpArgs tp = {};
+  tp.oneshot = oneshot_rows ? 1 : 0;
   tp.world = world; tp.rank = rank; tp.S = S;
   tp.ag_site = ag_site; tp.ag_sites = ag_sites; tp.rs_site = rs_site; tp.rs_sites = rs_sites;
   tp.ld_inbox = ld_inbox; tp.epoch = epoch; tp.flags_local = (uint32_t*)flags_local; tp.ticket = ticket;
@@ -375,5 +386,5 @@ POOT_API int poot_gemm_skinny_tp(int epi, const void* x, const void* W, void* ou
     tp.flags_peer[r] = (uint32_t*)flags_peer[r];
     tp.inbox_peer[r] = inbox_peer ? (__nv_bfloat16*)inbox_peer[r] : nullptr;
   }
-  return skinny_dispatch(epi, tw, tx, out, nullptr, bt, N, K, ldo, ck, bt, 0, status, s, tp);
+  return skinny_dispatch(epi, tw, tx, out, nullptr, M, N, K, ldo, ck, bt, 0, status, s, tp);
 }

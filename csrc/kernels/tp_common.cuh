@@ -37,6 +37,7 @@ struct TpArgs {
   int rs_site;        // >= 0: scatter the output rows to their owner ranks' inboxes for this site
   int rs_sites;       // scatter sites per step
   int ld_inbox;       // row pitch (elements) of an inbox slice = hidden size
+  int oneshot;        // 1: every rank receives every rank's whole partial (one-shot all-reduce; S = rows per slot)
   const int* epoch;             // device step counter (>= 1 inside a step)
   uint32_t* flags_local;        // this rank's flag block [2 * 8]
   uint32_t* flags_peer[TP_MAX_WORLD];        // every rank's flag block (peer mappings; [rank] = local)

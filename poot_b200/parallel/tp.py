@@ -78,7 +78,7 @@ class FusedComm(NcclComm):
         # layout of the symmetric block (byte offsets, 1 KiB aligned)
         self.off_flags = 0
         self.off_inbox = 1024
-        inbox_bytes = 2 * w * self.s_max * H * 2
+        inbox_bytes = 2 * w * self.MAX_ROWS * H * 2   # one-shot form: a slot holds up to MAX_ROWS rows
         self.off_xs = self.off_inbox + (inbox_bytes + 1023) // 1024 * 1024
         xs_bytes = 2 * self.MAX_ROWS * H * 2
         total = self.off_xs + (xs_bytes + 1023) // 1024 * 1024
@@ -95,11 +95,11 @@ class FusedComm(NcclComm):
         self.rs_sites = 2 * L
         self.ag_sites = 2 * L + 1
         K.register_signature("poot_tp_begin_step", [_P, _P])
-        K.register_signature("poot_tp_norm", [_P, _P, _P, _P, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
-                                              c_int, _P, _P, _P, _P, _P, _P])
+        K.register_signature("poot_tp_norm", [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
+                                              c_int, c_int, _P, _P, _P, _P, _P, _P])
         K.register_signature("poot_gemm_skinny_tp", [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                     c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P,
-                                                     _P])
+                                                     c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, c_int, _P,
+                                                     _P, _P])
         self._begin = K.fn("poot_tp_begin_step")
         self._norm = K.fn("poot_tp_norm")
         self._gemm = K.fn("poot_gemm_skinny_tp")
@@ -117,11 +117,34 @@ class FusedComm(NcclComm):
     def begin_step(self) -> None:
         check(self._begin(self.epoch.data_ptr(), K._stream()), "tp_begin_step")
 
+    def norm_oneshot(self, h: torch.Tensor, w: torch.Tensor, x_out: torch.Tensor, rows: int, eps: float,
+                     rs_site: int) -> None:
+        """One-shot all-reduce consumer: ``h += sum_r inbox[r]`` (rank order), ``x_out = rmsnorm(h) * w``; all local."""
+        b = self.block
+        check(self._norm(h.data_ptr(), b.ptr(self.rank, self.off_inbox), w.data_ptr(), None, x_out.data_ptr(), rows,
+                         self.H, float(eps), self.world, self.rank, self.MAX_ROWS, 0, self.ag_sites, rs_site,
+                         self.rs_sites, self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer,
+                         self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()), "tp_norm")
+
+    def gemm_allreduce(self, x: torch.Tensor, W: torch.Tensor, rows: int, rs_site: int) -> None:
+        """Row-parallel projection whose epilogue writes the partial into every rank's inbox (one-shot all-reduce)."""
+        N, Kd = W.shape
+        b = self.block
+        check(self._gemm(K.EPI_STORE, x.data_ptr(), W.data_ptr(), None, N, Kd, x.stride(0), self.H,
+                         K.skinny_cluster(N, Kd), self.world, self.rank, self.MAX_ROWS, -1, self.ag_sites, rs_site,
+                         self.rs_sites, self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer,
+                         self.inbox_peer, self.H, rows, self.ticket.data_ptr(),
+                         K.status_word(self.device).data_ptr(), K._stream()), "gemm_skinny_tp")
+
+    def oneshot_ok(self, T: int) -> bool:
+        """One-shot all-reduce pays while the partial (T x hidden, sent to world-1 peers) stays small."""
+        return T <= 128 and T * (self.world - 1) <= 512
+
     def norm(self, w: torch.Tensor, S: int, eps: float, ag_site: int, rs_site: int) -> None:
         """Reduce the inboxes of ``rs_site`` (if >= 0) into the residual shard, normalise, publish for ``ag_site``."""
         b = self.block
         check(self._norm(self.h_shard.data_ptr(), b.ptr(self.rank, self.off_inbox), w.data_ptr(),
-                         self.xs_peer, self.H, float(eps), self.world, self.rank, S, ag_site,
+                         self.xs_peer, None, S, self.H, float(eps), self.world, self.rank, S, ag_site,
                          self.ag_sites, rs_site, self.rs_sites, self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags),
                          self.flags_peer, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
               "tp_norm")
@@ -138,7 +161,7 @@ class FusedComm(NcclComm):
         check(self._gemm(epi, xptr, W.data_ptr(), None if out is None else out.data_ptr(),
                          N, Kd, ldx, ldo, ck, self.world, self.rank, S, ag_site, self.ag_sites, rs_site, self.rs_sites,
                          self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer, self.inbox_peer,
-                         self.H, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
+                         self.H, 0, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
               "gemm_skinny_tp")
 
     def close(self) -> None:

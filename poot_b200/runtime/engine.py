@@ -65,6 +65,7 @@ class DecoderEngine:
         self.hkv = max(cfg.n_kv_heads // self.tp, 1)
         self.max_seqs, self.max_tokens, self.max_blocks = max_seqs, max_tokens, max_blocks_per_seq
         self.use_graphs = use_graphs
+        self.tp_mode = "auto"   # "auto": one-shot all-reduce for small steps, reduce-scatter/all-gather above; "rs_ag"
         self.kv = KVPool(cfg, num_blocks, self.device, self.tp)
         dev, i32 = self.device, torch.int32
         if comm is not None and getattr(comm, "fused", False):
@@ -174,6 +175,8 @@ class DecoderEngine:
         cfg, w = self.cfg, self.w
         T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
         if self.comm is not None and getattr(self.comm, "fused", False):
+            if self.comm.oneshot_ok(T) and self.tp_mode != "rs_ag":
+                return self._forward_tp_oneshot(shape)
             R = self.comm.rows_for(T)
             if R:
                 return self._forward_tp_fused(shape, R)
@@ -254,6 +257,50 @@ class DecoderEngine:
             self._count()
             K.decode_advance(self.picked, self.tokens, self.positions, self.slots, self.row_ctx, self.block_tables,
                              self.row_seq, B)
+
+    def _forward_tp_oneshot(self, shape: StepShape) -> None:
+        """Small steps on the fused tensor-parallel path with one-shot all-reduces: the o_proj / down_proj GEMM
+        epilogues write their partial rows into every rank's inbox over NVLink, and the next kernel (residual add +
+        RMSNorm) sums the inboxes in rank order.  One cross-rank synchronisation per projection, no library call."""
+        cfg, w, comm = self.cfg, self.w, self.comm
+        T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
+        self._launch_counter = 0
+        h, x = self.h[:T], self.x[:T]
+        self._count(3)
+        comm.begin_step()
+        K.embed_gather(self.tokens[:T], w.embed, out=h)
+        K.rmsnorm(h, w.layers[0].ln1, cfg.norm_eps, out=x)
+        rs = -1
+        for l, L in enumerate(w.layers):
+            if l > 0:
+                self._count()
+                comm.norm_oneshot(h, L.ln1, x, T, cfg.norm_eps, rs_site=rs)
+            splits = self._attn_splits(T)
+            self._count(8 + (1 if splits > 1 else 0))
+            K.linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
+            K.rope_kv_write(self.qkv[:T], self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
+                            self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
+            K.attn_paged(self.q[:T], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:T], self.row_ctx[:T],
+                         self.hq, self.hkv, D, self.scale, out=self.attn[:T], splits=splits,
+                         scratch=self.attn_scratch, softcap=cfg.attn_softcap, window=cfg.sliding_window)
+            rs += 1
+            comm.gemm_allreduce(self.attn[:T], L.wo, T, rs_site=rs)
+            comm.norm_oneshot(h, L.ln2, x, T, cfg.norm_eps, rs_site=rs)
+            K.linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
+            rs += 1
+            comm.gemm_allreduce(self.act[:T], L.wdown, T, rs_site=rs)
+        if B == T:
+            self._count()
+            comm.norm_oneshot(h, w.final_norm, self.xl[:B], T, cfg.norm_eps, rs_site=rs)
+        else:
+            # reduce into h (normalised output unused), then gather the logit rows and normalise them
+            self._count(3)
+            comm.norm_oneshot(h, w.final_norm, x, T, cfg.norm_eps, rs_site=rs)
+            torch.index_select(h, 0, self.logit_idx[:B], out=self.hl[:B])
+            K.rmsnorm(self.hl[:B], w.final_norm, cfg.norm_eps, out=self.xl[:B])
+        self._count()
+        K.linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits_local[:B])
+        self._sample(shape, self.logits_local[:B])
 
     def _forward_tp_fused(self, shape: StepShape, R: int) -> None:
         """Decode-sized step on the fused tensor-parallel path: the residual stream is sharded by token rows

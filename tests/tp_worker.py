@@ -39,6 +39,8 @@ def main():
         """Greedy run; with ``forced`` the fed tokens are the reference's (random weights give near-tied logits,
         so a pick may legitimately differ and must not change the rest of the comparison)."""
         eng = DecoderEngine(weights, num_blocks=B * bps, max_seqs=B, max_tokens=B * P, max_blocks_per_seq=bps, comm=comm)
+        if kind == "fused_rsag":
+            eng.tp_mode = "rs_ag"   # force the reduce-scatter / all-gather form even for small steps
         sess = FixedBatchSession(eng, B, max_len)
         toks = sess.prefill_fast(prompts)[:, 0].tolist()
         out = [list(toks)]
@@ -52,7 +54,7 @@ def main():
         return out, logits
 
     ref_tokens, ref_logits = run(random_weights(cfg, dev, seed=3, std=0.05), None)
-    comm = make_comm(kind, rank, world, dev)
+    comm = make_comm("fused" if kind == "fused_rsag" else kind, rank, world, dev)
     tp_tokens, tp_logits = run(random_weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_world=world), comm,
                                forced=ref_tokens)
     vl = cfg.vocab // world
