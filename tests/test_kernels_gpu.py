@@ -96,15 +96,9 @@ def test_gemm_tcgen05(K, bn, M, N, Kd):
 @pytest.mark.parametrize("M", [1, 3, 16, 17, 64, 100, 128])
 @pytest.mark.parametrize("N,Kd,ck", [(4096, 4096, 8), (6144, 4096, 4), (1024, 14336, 8), (28672, 1024, 1), (776, 520, 2),
                                      (256, 192, 4)])
-@pytest.mark.parametrize("wm", [1, 2])
-def test_gemm_skinny(K, M, N, Kd, ck, wm):
+def test_gemm_skinny(K, M, N, Kd, ck):
     x, W = bf(M, Kd, seed=1), bf(N, Kd, scale=0.05, seed=2)
     ref = x.float() @ W.float().T
-    close(K.gemm_skinny(x, W, K.EPI_STORE, ck=ck, wm=wm), ref)
-    close(K.gemm_skinny(x, W, K.EPI_SWIGLU, ck=ck, wm=wm), torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2])
-    if wm == 2:
-        K.check_status()
-        return
     close(K.gemm_skinny(x, W, K.EPI_F32, ck=ck), ref, 1e-3, 1e-3)
     res = bf(M, N, seed=3)
     close(K.gemm_skinny(x, W, K.EPI_RESID, resid=res, ck=ck), ref + res.float())
