@@ -314,3 +314,43 @@ POOT_API int poot_attn_paged(const void* q, int q_stride, const void* kpool, con
                            part_o, part_ml, R, Hq, Hkv, scale, softcap, window, splits, s);
   return (int)cudaErrorInvalidValue;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant (declared in poot_noalloc.h).  The split-KV partials go to a file-scope
+// device array instead of caller-provided scratch.  In host code `g_noalloc_scratch` is only a
+// stand-in for the symbol, not a device address: the address handed to the kernels is resolved
+// once per device with cudaGetSymbolAddress while that device is current.
+// ---------------------------------------------------------------------------------------------
+#include "poot_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[POOT_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+POOT_API int poot_attn_paged_noalloc(const void* q, int q_stride, const void* kpool, const void* vpool,
+                                     const int* block_tables, int max_blocks, const int* row_seq, const int* row_ctx,
+                                     void* out, int out_stride, int R, int Hq, int Hkv, int D, float scale,
+                                     float softcap, int window, int splits, cudaStream_t stream) {
+  if (R == 0) return 0;
+  if (R < 0 || Hq <= 0 || D <= 0 || splits < 1) return (int)cudaErrorInvalidValue;
+  const unsigned long long need = (unsigned long long)R * Hq * splits * (unsigned long long)(D + 2);
+  if (need > (unsigned long long)POOT_NOALLOC_SCRATCH_FLOATS) return (int)cudaErrorInvalidValue;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return (int)cudaErrorInvalidDevice;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    // set-up, once per device, with that device current
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_noalloc_ptr[dev] = p;
+  }
+  float* part_o = g_noalloc_ptr[dev];
+  float* part_ml = part_o + (size_t)R * Hq * splits * D;
+  return poot_attn_paged(q, q_stride, kpool, vpool, block_tables, max_blocks, row_seq, row_ctx, out, out_stride,
+                         part_o, part_ml, R, Hq, Hkv, D, scale, softcap, window, splits, stream);
+}
