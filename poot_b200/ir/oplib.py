@@ -1,0 +1,221 @@
+"""Op library: every model-level operation as a composition of primitives.
+
+These are the definitions the planner pattern-matches and the CPU oracle evaluates; device kernels are checked
+against them.  Decompositions follow crates/poot-graph-ir/src/ops/*: ``rmsnorm`` (ops/norm.rs:4-29),
+``layernorm`` (:32-75), ``linear`` (ops/linear.rs:8-19), half-split ``rope`` (ops/rope.rs:5-58), ``silu`` with a
+single division and ``swiglu`` / ``gelu`` (ops/activation.rs:94-150), masked attention and ``paged_view``
+(ops/attention.rs:7-337), causal masks from absolute positions (ops/prefill.rs), Mixtral-style routing
+(ops/moe.rs:9-431) and the sampling suffix (ops/sampling.rs:277-440).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence
+
+from ..tensor import DType
+from .builder import Builder, Traced
+
+F32, I32 = DType.F32, DType.I32
+MASK_HIDDEN = -1.0e9
+F32_MAX = 3.4028234663852886e38
+
+
+def lnot(b: Builder, x: Traced) -> Traced:
+    """Logical not of a 0/1 I32 predicate (comparisons yield I32 0/1)."""
+    return b.binary("xor", x, b.broadcast(b.scalar(1, I32), x.shape))
+
+
+# ---- normalisation ---------------------------------------------------------------------------------------------
+def rmsnorm(b: Builder, x: Traced, w: Traced, eps: float) -> Traced:
+    D = x.shape[-1]
+    sq = x * x
+    ss = sq.sum(-1, keepdim=True)
+    ms = ss * (1.0 / D)
+    den = b.unary("sqrt", ms + eps)
+    return (x / b.broadcast(den, x.shape)) * b.broadcast(w, x.shape)
+
+
+def layernorm(b: Builder, x: Traced, w: Traced, bias: Optional[Traced], eps: float) -> Traced:
+    D = x.shape[-1]
+    mean = x.sum(-1, keepdim=True) * (1.0 / D)
+    c = x - b.broadcast(mean, x.shape)
+    var = (c * c).sum(-1, keepdim=True) * (1.0 / D)
+    y = c / b.broadcast(b.unary("sqrt", var + eps), x.shape) * b.broadcast(w, x.shape)
+    return y + b.broadcast(bias, x.shape) if bias is not None else y
+
+
+def linear(b: Builder, x: Traced, w: Traced, bias: Optional[Traced] = None, precision: str = "narrow") -> Traced:
+    """``x @ w^T`` for a checkpoint-order weight ``w[out, in]``."""
+    y = b.matmul(x, b.transpose(w, (1, 0)), precision)
+    return y + b.broadcast(bias, y.shape) if bias is not None else y
+
+
+# ---- activations -----------------------------------------------------------------------------------------------
+def sigmoid(b: Builder, x: Traced) -> Traced:
+    return 1.0 / (1.0 + b.unary("exp", -x))
+
+
+def silu(b: Builder, x: Traced) -> Traced:
+    return x / (1.0 + b.unary("exp", -x))
+
+
+def swiglu(b: Builder, gate: Traced, up: Traced) -> Traced:
+    return silu(b, gate) * up
+
+
+def relu(b: Builder, x: Traced) -> Traced:
+    return b.binary("max", x, b.scalar(0.0, x.dtype))
+
+
+def gelu_tanh(b: Builder, x: Traced) -> Traced:
+    z = math.sqrt(2.0 / math.pi) * (x + 0.044715 * (x * x * x))
+    return x / (1.0 + b.unary("exp", -2.0 * z))
+
+
+def gelu_erf(b: Builder, x: Traced) -> Traced:
+    return 0.5 * x * (1.0 + b.unary("erf", x * (1.0 / math.sqrt(2.0))))
+
+
+def geglu(b: Builder, gate: Traced, up: Traced) -> Traced:
+    return gelu_tanh(b, gate) * up
+
+
+def softplus(b: Builder, x: Traced) -> Traced:
+    return b.unary("log", 1.0 + b.unary("exp", x))
+
+
+def softcap(b: Builder, x: Traced, cap: float) -> Traced:
+    return cap * b.unary("tanh", x * (1.0 / cap))
+
+
+def softmax(b: Builder, x: Traced) -> Traced:
+    m = x.max(-1, keepdim=True)
+    e = b.unary("exp", x - b.broadcast(m, x.shape))
+    return e / b.broadcast(e.sum(-1, keepdim=True), x.shape)
+
+
+# ---- rotary ----------------------------------------------------------------------------------------------------
+def rope(b: Builder, x: Traced, cos: Traced, sin: Traced, rot: Optional[int] = None) -> Traced:
+    """Half-split rotary over the leading ``rot`` channels of ``x[..., heads, D]``; ``cos``/``sin`` are
+    ``[tokens, rot]`` tables with duplicated halves, broadcast over heads."""
+    D = x.shape[-1]
+    rot = D if rot is None else rot
+    half = rot // 2
+    xr = b.slice(x, -1, 0, rot) if rot < D else x
+    x1 = b.slice(xr, -1, 0, half)
+    x2 = b.slice(xr, -1, half, half)
+    rotated = b.concat([-x2, x1], -1)
+    c = b.broadcast(b.reshape(cos, (cos.shape[0], 1, rot)), xr.shape)
+    s = b.broadcast(b.reshape(sin, (sin.shape[0], 1, rot)), xr.shape)
+    out = xr * c + rotated * s
+    if rot < D:
+        out = b.concat([out, b.slice(x, -1, rot, D - rot)], -1)
+    return out
+
+
+# ---- attention -------------------------------------------------------------------------------------------------
+def repeat_kv(b: Builder, kv: Traced, n_rep: int) -> Traced:
+    """Blocked GQA expansion ``[rows, kv_heads, S, D] -> [rows, kv_heads*n_rep, S, D]`` (q head h uses kv head h/n_rep)."""
+    if n_rep == 1:
+        return kv
+    R, H, S, D = kv.shape
+    x = b.broadcast(b.reshape(kv, (R, H, 1, S, D)), (R, H, n_rep, S, D))
+    return b.reshape(x, (R, H * n_rep, S, D))
+
+
+def causal_mask_from_pos(b: Builder, q_pos: Traced, cap: int, window: int = 0) -> Traced:
+    """Additive mask ``[rows, tokens, cap]`` from absolute query positions ``[rows, tokens]``: key j is visible to a
+    query at position p iff ``j <= p`` (and ``j > p - window`` with a sliding window)."""
+    R, T = q_pos.shape
+    keys = b.iota((R, T, cap), 2)
+    p = b.broadcast(b.reshape(q_pos, (R, T, 1)), (R, T, cap))
+    visible = b.binary("ge", p, keys)
+    if window > 0:
+        visible = b.binary("and", visible, b.binary("ge", keys, p - (window - 1)))
+    zero, hidden = b.scalar(0.0, F32), b.scalar(MASK_HIDDEN, F32)
+    return b.select(visible, b.broadcast(zero, (R, T, cap)), b.broadcast(hidden, (R, T, cap)))
+
+
+def attention_masked(b: Builder, q: Traced, k: Traced, v: Traced, mask: Traced, scale: float, n_rep: int = 1,
+                     cap: float = 0.0) -> Traced:
+    """``softmax(q k^T * scale (+softcap) + mask) v`` with ``q[rows, heads, T, D]``, ``k/v[rows, kv_heads, S, D]`` and an
+    additive ``mask[rows, T, S]``."""
+    k, v = repeat_kv(b, k, n_rep), repeat_kv(b, v, n_rep)
+    scores = b.matmul(q, b.transpose(k, (0, 1, 3, 2))) * scale
+    if cap > 0:
+        scores = softcap(b, scores, cap)
+    R, H, T, S = scores.shape
+    scores = scores + b.broadcast(b.reshape(mask, (R, 1, T, S)), scores.shape)
+    return b.matmul(softmax(b, scores), v)
+
+
+def paged_view(b: Builder, pool: Traced, read_map: Traced) -> Traced:
+    """Gather ``pool[slots, kv_heads, D]`` through ``read_map[rows, cap]`` into ``[rows, kv_heads, cap, D]``."""
+    g = b.gather(pool, read_map, 0)                 # [rows, cap, kv_heads, D]
+    return b.transpose(g, (0, 2, 1, 3))
+
+
+# ---- mixture of experts ----------------------------------------------------------------------------------------
+def canonical_router_scores(b: Builder, s: Traced) -> Traced:
+    """NaN / -inf -> f32::MIN, +inf -> f32::MAX so ranks are total (``max`` is max-number: NaN is ignored)."""
+    lo = b.broadcast(b.scalar(-F32_MAX, F32), s.shape)
+    hi = b.broadcast(b.scalar(F32_MAX, F32), s.shape)
+    return -b.binary("max", -b.binary("max", s, lo), -hi)
+
+
+def stable_descending_rank(b: Builder, s: Traced) -> Traced:
+    """``rank[r, e]`` = number of experts that sort before ``e`` (larger score, or equal score and lower index)."""
+    R, E = s.shape
+    a = b.broadcast(b.reshape(s, (R, E, 1)), (R, E, E))     # score of e
+    o = b.broadcast(b.reshape(s, (R, 1, E)), (R, E, E))     # score of other f
+    ie = b.iota((R, E, E), 1)
+    io = b.iota((R, E, E), 2)
+    gt = b.binary("ge", o, a)
+    strictly = b.binary("and", gt, lnot(b, b.binary("ge", a, o)))               # o > a
+    tie_before = b.binary("and", b.binary("and", gt, b.binary("ge", a, o)),      # o == a and f < e
+                          lnot(b, b.binary("ge", io, ie)))
+    before = b.binary("or", strictly, tie_before)
+    return b.cast(before, I32).sum(-1)
+
+
+def moe_topk_softmax(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Traced, k: int,
+                     precision: str = "narrow") -> Traced:
+    """Mixtral routing: softmax over the selected top-k logits only; experts ``w_in[E, 2F, H]`` (gate rows then up
+    rows), ``w_out[E, H, F]``; every token is evaluated by its k experts through ``indexed_matmul``."""
+    L, H = x.shape
+    E, F2, _ = w_in.shape
+    F = F2 // 2
+    scores = canonical_router_scores(b, linear(b, x, router, precision="exact"))
+    rank = stable_descending_rank(b, scores)
+    ids = b.arg_top_k(rank, k)                                              # [L, k]
+    keep = lnot(b, b.binary("ge", rank, b.broadcast(b.scalar(k, I32), rank.shape)))
+    neg = b.broadcast(b.scalar(MASK_HIDDEN, F32), scores.shape)
+    sel = b.select(keep, scores, neg)
+    m = sel.max(-1, keepdim=True)
+    ex = b.unary("exp", sel - b.broadcast(m, sel.shape)) * b.cast(keep, F32)
+    gates_all = ex / b.broadcast(ex.sum(-1, keepdim=True), ex.shape)        # [L, E]
+    flat_ids = b.reshape(ids, (L * k,))
+    gates = b.reshape(b.gather(b.reshape(gates_all, (L * E,)),
+                               b.reshape(b.iota((L, k), 0) * E, (L * k,)) + flat_ids, 0), (L * k, 1))
+    xr = b.reshape(b.broadcast(b.reshape(x, (L, 1, H)), (L, k, H)), (L * k, H))
+    gu = b.indexed_matmul(xr, b.transpose(w_in, (0, 2, 1)), flat_ids, precision)     # [L*k, 2F]
+    act = swiglu(b, b.slice(gu, -1, 0, F), b.slice(gu, -1, F, F))
+    y = b.indexed_matmul(act, b.transpose(w_out, (0, 2, 1)), flat_ids, precision) * b.broadcast(gates, (L * k, H))
+    return b.reshape(y, (L, k, H)).transpose(0, 2, 1).sum(-1)
+
+
+# ---- sampling suffix -------------------------------------------------------------------------------------------
+def sample_head(b: Builder, logits: Traced, rule: str = "greedy", seed: Optional[Traced] = None,
+                params: Optional[Traced] = None, top_k: Optional[Traced] = None, bias: Optional[Traced] = None,
+                guided_mask: Optional[Traced] = None) -> Traced:
+    """Adjusted logits (+bias, +guided mask) then ``sample_token``; Gumbel noise is ``-ln(-ln u)`` of the exact
+    uniform draw.  Returns ``[rows, 2]`` I32 ``(token, non_finite_index)``."""
+    if bias is not None:
+        logits = logits + bias
+    if guided_mask is not None:
+        logits = logits + guided_mask
+    if rule == "greedy":
+        return b.sample_token("greedy", logits)
+    u = b.random_uniform(seed, logits.shape[-1])
+    noise = -b.unary("log", -b.unary("log", u))
+    return b.sample_token(rule, logits, noise, params, top_k if rule != "gumbel" else None)
