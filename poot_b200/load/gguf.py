@@ -1,0 +1,260 @@
+"""GGUF reader and writer.
+
+Layout (crates/poot-load/src/gguf.rs:1-9): magic ``GGUF``, version, tensor count, KV count, the KV metadata, the
+tensor directory (name, dims in ggml order = innermost first, ggml type, offset), padding to
+``general.alignment`` (32), then the tensor data.  Payloads are returned as zero-copy views of a memory map; split
+shards (``-00001-of-0000N``) are merged; ggml types that exist but cannot be decoded are refused by name
+(crates/poot-load/src/gguf/format.rs:476-560).  A quantised rank-3 expert tensor becomes one packed owner per
+expert (gguf.rs:79-88).
+"""
+from __future__ import annotations
+
+import mmap
+import os
+import re
+import struct
+from dataclasses import dataclass
+from typing import Any, BinaryIO, Dict, List, Optional, Tuple
+
+import numpy as np
+
+from ..models.config import DecoderConfig, RopeScaling
+from ..quant.formats import FORMATS, GGML_REFUSED, GGML_TYPE_TO_FORMAT, UnsupportedFormat, packed_nbytes
+from ..quant.weights import PackedWeight, WeightStore
+
+MAGIC = 0x46554747
+_SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
+MAX_STRING = 1 << 28
+MAX_ARRAY = 1 << 28
+
+
+class GgufError(ValueError):
+    pass
+
+
+@dataclass
+class GgufTensorInfo:
+    name: str
+    shape: Tuple[int, ...]      # logical (outermost first)
+    ggml_type: int
+    offset: int
+
+
+class _Reader:
+    def __init__(self, buf, size):
+        self.b, self.p, self.n = buf, 0, size
+
+    def take(self, fmt: str):
+        sz = struct.calcsize(fmt)
+        if self.p + sz > self.n:
+            raise GgufError("truncated GGUF header")
+        v = struct.unpack_from(fmt, self.b, self.p)[0]
+        self.p += sz
+        return v
+
+    def string(self) -> str:
+        n = self.take("<Q")
+        if n > MAX_STRING or self.p + n > self.n:
+            raise GgufError(f"string of {n} bytes overruns the file")
+        s = bytes(self.b[self.p:self.p + n]).decode("utf-8", errors="replace")
+        self.p += n
+        return s
+
+    def value(self, t: int, depth: int = 0):
+        if t in _SCALAR:
+            return self.take(_SCALAR[t])
+        if t == 8:
+            return self.string()
+        if t == 9:
+            if depth > 2:
+                raise GgufError("array nesting too deep")
+            et, cnt = self.take("<I"), self.take("<Q")
+            if cnt > MAX_ARRAY:
+                raise GgufError(f"array of {cnt} elements")
+            if et in _SCALAR:
+                fmt = _SCALAR[et]
+                sz = struct.calcsize(fmt)
+                if self.p + sz * cnt > self.n:
+                    raise GgufError("array overruns the file")
+                arr = np.frombuffer(self.b, dtype=np.dtype(fmt[1:]).newbyteorder("<"), count=cnt, offset=self.p)
+                self.p += sz * cnt
+                return arr.tolist() if cnt <= 4096 else arr
+            return [self.value(et, depth + 1) for _ in range(cnt)]
+        raise GgufError(f"unknown metadata value type {t}")
+
+
+@dataclass
+class GgufIndex:
+    path: str
+    version: int
+    metadata: Dict[str, Any]
+    tensors: List[GgufTensorInfo]
+    data_start: int
+    alignment: int
+
+
+def read_index(path: str) -> Tuple[GgufIndex, mmap.mmap]:
+    f = open(path, "rb")
+    size = os.fstat(f.fileno()).st_size
+    if size < 24:
+        raise GgufError("file too small for a GGUF header")
+    mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
+    r = _Reader(mm, size)
+    if r.take("<I") != MAGIC:
+        raise GgufError("not a GGUF file (bad magic)")
+    version = r.take("<I")
+    if version not in (2, 3):
+        raise GgufError(f"unsupported GGUF version {version}")
+    n_tensors, n_kv = r.take("<Q"), r.take("<Q")
+    if n_tensors > 1 << 20 or n_kv > 1 << 20:
+        raise GgufError("implausible tensor / metadata count")
+    meta: Dict[str, Any] = {}
+    for _ in range(n_kv):
+        key = r.string()
+        if key in meta:
+            raise GgufError(f"duplicate metadata key {key!r}")
+        meta[key] = r.value(r.take("<I"))
+    infos = []
+    seen = set()
+    for _ in range(n_tensors):
+        name = r.string()
+        if name in seen:
+            raise GgufError(f"duplicate tensor {name!r}")
+        seen.add(name)
+        nd = r.take("<I")
+        if nd > 4:
+            raise GgufError(f"tensor {name!r} has {nd} dimensions")
+        dims = [r.take("<Q") for _ in range(nd)]
+        infos.append(GgufTensorInfo(name, tuple(reversed(dims)), r.take("<I"), r.take("<Q")))
+    align = int(meta.get("general.alignment", 32))
+    if align <= 0 or align & (align - 1):
+        raise GgufError(f"alignment {align} is not a power of two")
+    data_start = (r.p + align - 1) // align * align
+    return GgufIndex(path, version, meta, infos, data_start, align), mm
+
+
+def _format_of(info: GgufTensorInfo) -> str:
+    if info.ggml_type in GGML_REFUSED:
+        raise UnsupportedFormat(f"tensor {info.name!r}: ggml type {GGML_REFUSED[info.ggml_type]} is not supported")
+    try:
+        return GGML_TYPE_TO_FORMAT[info.ggml_type]
+    except KeyError:
+        raise UnsupportedFormat(f"tensor {info.name!r}: unknown ggml type {info.ggml_type}") from None
+
+
+def shard_paths(path: str) -> List[str]:
+    m = re.search(r"-(\d{5})-of-(\d{5})\.gguf$", path)
+    if not m:
+        return [path]
+    total = int(m.group(2))
+    return [path[:m.start()] + f"-{i:05d}-of-{total:05d}.gguf" for i in range(1, total + 1)]
+
+
+def read_gguf(path: str, check: bool = True) -> WeightStore:
+    store = WeightStore()
+    store.source = path
+    store._maps = []
+    for k, sp in enumerate(shard_paths(path)):
+        idx, mm = read_index(sp)
+        store._maps.append(mm)
+        if k == 0:
+            store.metadata = idx.metadata
+        raw = np.frombuffer(mm, dtype=np.uint8)
+        for t in idx.tensors:
+            fmt = _format_of(t)
+            n = int(np.prod(t.shape)) if t.shape else 1
+            nbytes = packed_nbytes(fmt, n)
+            lo = idx.data_start + t.offset
+            if t.offset % idx.alignment or lo + nbytes > raw.size:
+                raise GgufError(f"tensor {t.name!r} overruns the file or is misaligned")
+            payload = raw[lo:lo + nbytes]
+            if len(t.shape) == 3 and FORMATS[fmt].storage == "blocks":
+                per = nbytes // t.shape[0]
+                for e in range(t.shape[0]):
+                    store.add(PackedWeight(f"{t.name}#{e}", fmt, tuple(t.shape[1:]), payload[e * per:(e + 1) * per]))
+            else:
+                store.add(PackedWeight(t.name, fmt, tuple(t.shape), payload))
+    return store.publish(check)
+
+
+# ---- writer -----------------------------------------------------------------------------------------------------
+def _put_string(out: bytearray, s: str) -> None:
+    b = s.encode("utf-8")
+    out += struct.pack("<Q", len(b)) + b
+
+
+def _put_value(out: bytearray, v) -> None:
+    if isinstance(v, bool):
+        out += struct.pack("<I?", 7, v)
+    elif isinstance(v, int):
+        out += struct.pack("<Iq", 11, v) if v < 0 or v > 0xFFFFFFFF else struct.pack("<II", 4, v)
+    elif isinstance(v, float):
+        out += struct.pack("<If", 6, v)
+    elif isinstance(v, str):
+        out += struct.pack("<I", 8)
+        _put_string(out, v)
+    elif isinstance(v, (list, tuple, np.ndarray)):
+        v = list(v)
+        out += struct.pack("<I", 9)
+        if v and isinstance(v[0], str):
+            out += struct.pack("<IQ", 8, len(v))
+            for s in v:
+                _put_string(out, s)
+        elif v and isinstance(v[0], float):
+            out += struct.pack("<IQ", 6, len(v)) + struct.pack(f"<{len(v)}f", *v)
+        else:
+            out += struct.pack("<IQ", 5, len(v)) + struct.pack(f"<{len(v)}i", *[int(x) for x in v])
+    else:
+        raise GgufError(f"cannot encode metadata value of type {type(v)}")
+
+
+def write_gguf(path: str, metadata: Dict[str, Any], tensors: List[PackedWeight], alignment: int = 32) -> None:
+    head = bytearray(struct.pack("<IIQQ", MAGIC, 3, len(tensors), len(metadata)))
+    for k, v in metadata.items():
+        _put_string(head, k)
+        _put_value(head, v)
+    offsets, off = [], 0
+    for t in tensors:
+        offsets.append(off)
+        off = (off + t.payload.nbytes + alignment - 1) // alignment * alignment
+    for t, o in zip(tensors, offsets):
+        _put_string(head, t.name)
+        dims = list(reversed(t.shape))
+        head += struct.pack("<I", len(dims)) + struct.pack(f"<{len(dims)}Q", *dims)
+        head += struct.pack("<IQ", FORMATS[t.format].ggml_type, o)
+    pad = (-len(head)) % alignment
+    with open(path, "wb") as f:
+        f.write(head + b"\0" * pad)
+        for t in tensors:
+            raw = np.ascontiguousarray(t.payload).view(np.uint8).reshape(-1)
+            f.write(raw.tobytes())
+            f.write(b"\0" * ((-raw.nbytes) % alignment))
+
+
+# ---- metadata -> configuration ---------------------------------------------------------------------------------
+def config_from_gguf_metadata(arch: str, meta: Dict[str, Any], family: str) -> DecoderConfig:
+    def g(key, default=None):
+        return meta.get(f"{arch}.{key}", default)
+
+    H, nh = int(g("embedding_length")), int(g("attention.head_count"))
+    nkv = g("attention.head_count_kv", nh)
+    nkv = int(nkv[0] if isinstance(nkv, (list, np.ndarray)) else nkv)
+    head_dim = int(g("attention.key_length", H // nh))
+    tokens = meta.get("tokenizer.ggml.tokens")
+    vocab = int(g("vocab_size", len(tokens) if tokens is not None else 0))
+    n_exp = int(g("expert_count", 0) or 0)
+    ffn = g("feed_forward_length", 4 * H)
+    ffn = int(ffn[0] if isinstance(ffn, (list, np.ndarray)) else ffn)
+    scaling = RopeScaling()
+    if g("rope.scaling.type") in ("linear", "yarn"):
+        scaling = RopeScaling(kind=g("rope.scaling.type"), factor=float(g("rope.scaling.factor", 1.0)),
+                              original_max_position=int(g("rope.scaling.original_context_length", 8192)))
+    return DecoderConfig(
+        name=str(meta.get("general.name", family)), family="mixtral" if (family == "llama" and n_exp) else family,
+        n_layers=int(g("block_count")), hidden=H, n_heads=nh, n_kv_heads=nkv, head_dim=head_dim, ffn=ffn, vocab=vocab,
+        norm_eps=float(g("attention.layer_norm_rms_epsilon", 1e-6)), rope_theta=float(g("rope.freq_base", 10000.0)),
+        rope_dim=int(g("rope.dimension_count", head_dim)) if int(g("rope.dimension_count", head_dim)) != head_dim else None,
+        rope_scaling=scaling, max_position=int(g("context_length", 8192)),
+        tie_embeddings=False, qk_norm=family in ("qwen3", "qwen3moe", "olmo2", "olmoe"), attn_bias=family == "qwen2",
+        n_experts=n_exp, top_k=int(g("expert_used_count", 0) or 0), moe_ffn=int(g("expert_feed_forward_length", ffn)) if n_exp else 0,
+        bos_token=int(meta.get("tokenizer.ggml.bos_token_id", 1)), eos_token=int(meta.get("tokenizer.ggml.eos_token_id", 2)))

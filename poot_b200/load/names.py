@@ -1,0 +1,77 @@
+"""Checkpoint tensor names -> canonical weight roles, for HF safetensors and GGUF.
+
+Canonical names are the ones the tracer declares (``layers.{i}.attn_q`` ...).  The tables follow the reference's
+llama family (crates/poot-models/src/architectures/llama.rs:50-103): HF ``model.layers.N.self_attn.q_proj.weight``,
+Mixtral ``block_sparse_moe.gate`` / ``experts.N.w1|w3|w2``; GGUF ``blk.N.attn_q.weight``, ``ffn_gate_inp``,
+``ffn_{gate,up,down}_exps``.  GGUF llama files store Q and K rows permuted for interleaved RoPE; they are read back
+into the half-split order (``GGUF_PAIRED_QK``, llama.rs:5-8).
+"""
+from __future__ import annotations
+
+import re
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+
+HF_LAYER = {
+    "input_layernorm.weight": "attn_norm", "self_attn.q_proj.weight": "attn_q", "self_attn.k_proj.weight": "attn_k",
+    "self_attn.v_proj.weight": "attn_v", "self_attn.o_proj.weight": "attn_o", "self_attn.q_proj.bias": "attn_q_bias",
+    "self_attn.k_proj.bias": "attn_k_bias", "self_attn.v_proj.bias": "attn_v_bias", "self_attn.q_norm.weight": "attn_q_norm",
+    "self_attn.k_norm.weight": "attn_k_norm", "post_attention_layernorm.weight": "ffn_norm", "mlp.gate_proj.weight": "ffn_gate",
+    "mlp.up_proj.weight": "ffn_up", "mlp.down_proj.weight": "ffn_down", "block_sparse_moe.gate.weight": "ffn_router",
+    "mlp.gate.weight": "ffn_router",
+}
+HF_TOP = {"model.embed_tokens.weight": "embed", "model.norm.weight": "final_norm", "lm_head.weight": "lm_head"}
+HF_EXPERT = {"w1": "gate", "w3": "up", "w2": "down", "gate_proj": "gate", "up_proj": "up", "down_proj": "down"}
+
+GGUF_LAYER = {
+    "attn_norm.weight": "attn_norm", "attn_q.weight": "attn_q", "attn_k.weight": "attn_k", "attn_v.weight": "attn_v",
+    "attn_output.weight": "attn_o", "attn_q.bias": "attn_q_bias", "attn_k.bias": "attn_k_bias", "attn_v.bias": "attn_v_bias",
+    "attn_q_norm.weight": "attn_q_norm", "attn_k_norm.weight": "attn_k_norm", "ffn_norm.weight": "ffn_norm",
+    "ffn_gate.weight": "ffn_gate", "ffn_up.weight": "ffn_up", "ffn_down.weight": "ffn_down", "ffn_gate_inp.weight": "ffn_router",
+}
+GGUF_TOP = {"token_embd.weight": "embed", "output_norm.weight": "final_norm", "output.weight": "lm_head"}
+GGUF_EXPERT = {"ffn_gate_exps.weight": "gate", "ffn_up_exps.weight": "up", "ffn_down_exps.weight": "down"}
+
+
+def canonical_from_hf(name: str) -> Optional[str]:
+    if name in HF_TOP:
+        return HF_TOP[name]
+    m = re.match(r"model\.layers\.(\d+)\.(.+)$", name)
+    if not m:
+        return None
+    l, rest = m.group(1), m.group(2)
+    if rest in HF_LAYER:
+        return f"layers.{l}.{HF_LAYER[rest]}"
+    e = re.match(r"(?:block_sparse_moe|mlp)\.experts\.(\d+)\.(\w+)\.weight$", rest)
+    if e and e.group(2) in HF_EXPERT:
+        return f"layers.{l}.experts.{e.group(1)}.{HF_EXPERT[e.group(2)]}"
+    return None
+
+
+def canonical_from_gguf(name: str) -> Optional[str]:
+    if name in GGUF_TOP:
+        return GGUF_TOP[name]
+    m = re.match(r"blk\.(\d+)\.([^#]+)(?:#(\d+))?$", name)
+    if not m:
+        return None
+    l, rest, ex = m.group(1), m.group(2), m.group(3)
+    if rest in GGUF_LAYER:
+        return f"layers.{l}.{GGUF_LAYER[rest]}"
+    if rest in GGUF_EXPERT and ex is not None:
+        return f"layers.{l}.experts.{ex}.{GGUF_EXPERT[rest]}"
+    return None
+
+
+def gguf_qk_row_order(n_rows: int, n_heads: int) -> np.ndarray:
+    """Row gather that turns a GGUF (interleaved-pair) Q/K matrix back into half-split order."""
+    hd = n_rows // n_heads
+    idx = np.arange(n_rows).reshape(n_heads, hd // 2, 2)
+    return idx.transpose(0, 2, 1).reshape(-1)
+
+
+def hf_to_gguf_qk_row_order(n_rows: int, n_heads: int) -> np.ndarray:
+    """The permutation llama.cpp's converter applies to HF Q/K rows (inverse of ``gguf_qk_row_order``)."""
+    hd = n_rows // n_heads
+    idx = np.arange(n_rows).reshape(n_heads, 2, hd // 2)
+    return idx.transpose(0, 2, 1).reshape(-1)
