@@ -1,0 +1,266 @@
+// Dequant-fused decode GEMV over GGUF block-quantised weights (Q4_K, Q5_K, Q6_K, Q8_0, Q4_0) and packed
+// embedding-row gather:
+//     out[m, n] = sum_k x[m, k] * dequant(W)[n, k]          1 <= m <= 4, bf16 activations, fp32 accumulate
+// The packed blocks are read once from HBM in their checkpoint layout; decoding happens in registers.  A warp
+// walks a weight row 256 values at a time: every lane owns 8 consecutive values, so scale/min lookups are per
+// lane and the per-block sums factor as  (d*sc) * sum(q*x) - (dmin*m) * sum(x)  in the ggml product order.
+//
+// Reference behaviour covered: Contraction::Packed (crates/poot-kernelgen/src/packed/mod.rs:1-7,
+// packed/decode_plan.rs), packed row gathers (crates/pootc/kernels/packed/*.rs) and standalone dequant
+// (crates/poot-kernelgen/src/packed/kernel.rs:1-5); block layouts crates/poot-quant/src/blocks.rs:174-346.
+#include "common.cuh"
+
+namespace poot {
+
+enum QFmt { QF_Q4_0 = 2, QF_Q8_0 = 8, QF_Q4_K = 12, QF_Q5_K = 13, QF_Q6_K = 14 };
+
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ uint16_t ld16(const uint8_t* p) { return *reinterpret_cast<const uint16_t*>(p); }
+// 8 bytes from a 2-byte aligned address
+__device__ __forceinline__ void ld8_a2(const uint8_t* p, uint32_t& lo, uint32_t& hi) {
+  const uint16_t* q = reinterpret_cast<const uint16_t*>(p);
+  lo = (uint32_t)q[0] | ((uint32_t)q[1] << 16);
+  hi = (uint32_t)q[2] | ((uint32_t)q[3] << 16);
+}
+__device__ __forceinline__ void scale_min_k4(int j, const uint8_t* q, int& d, int& m) {
+  if (j < 4) { d = q[j] & 63; m = q[j + 4] & 63; }
+  else { d = (q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4); m = (q[j + 4] >> 4) | ((q[j] >> 6) << 4); }
+}
+
+template <int FMT> struct QGeom;
+template <> struct QGeom<QF_Q4_K> { static constexpr int BYTES = 144, ELEMS = 256; };
+template <> struct QGeom<QF_Q5_K> { static constexpr int BYTES = 176, ELEMS = 256; };
+template <> struct QGeom<QF_Q6_K> { static constexpr int BYTES = 210, ELEMS = 256; };
+template <> struct QGeom<QF_Q8_0> { static constexpr int BYTES = 34, ELEMS = 32; };
+template <> struct QGeom<QF_Q4_0> { static constexpr int BYTES = 18, ELEMS = 32; };
+
+// Decode the 8 consecutive values [k, k+8) of a packed row (k a multiple of 8) as
+//   value_i = scale * q[i] - offset      (offset = 0 for the symmetric formats)
+template <int FMT>
+__device__ __forceinline__ void decode8(const uint8_t* row, int k, float* q, float& scale, float& offset) {
+  if (FMT == QF_Q4_K || FMT == QF_Q5_K) {
+    const uint8_t* b = row + (size_t)(k >> 8) * QGeom<FMT>::BYTES;
+    const int e = k & 255, sub = e >> 5, j = sub >> 1, h = sub & 1, l = e & 31;
+    const uint4 head = *reinterpret_cast<const uint4*>(b);          // d, dmin, 12 scale bytes
+    const uint8_t* hb = reinterpret_cast<const uint8_t*>(&head);
+    int sc, mn;
+    scale_min_k4(sub, hb + 4, sc, mn);
+    scale = h2f((uint16_t)(head.x & 0xFFFF)) * (float)sc;
+    offset = h2f((uint16_t)(head.x >> 16)) * (float)mn;
+    const int ql_off = (FMT == QF_Q4_K ? 16 : 48) + j * 32 + l;
+    const uint2 w = *reinterpret_cast<const uint2*>(b + ql_off);
+    const uint32_t lo = h ? (w.x >> 4) : w.x, hi = h ? (w.y >> 4) : w.y;
+    uint32_t hx = 0, hy = 0;
+    if (FMT == QF_Q5_K) {
+      const uint2 qh = *reinterpret_cast<const uint2*>(b + 16 + l);
+      hx = (qh.x >> sub) & 0x01010101u; hy = (qh.y >> sub) & 0x01010101u;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      q[i] = (float)(((lo >> (8 * i)) & 0xF) | (((hx >> (8 * i)) & 1) << 4));
+      q[4 + i] = (float)(((hi >> (8 * i)) & 0xF) | (((hy >> (8 * i)) & 1) << 4));
+    }
+  } else if (FMT == QF_Q6_K) {
+    const uint8_t* b = row + (size_t)(k >> 8) * 210;
+    const int e = k & 255, n = e >> 7, g = (e >> 5) & 3, l = e & 31;
+    uint32_t lx, ly, hx, hy;
+    ld8_a2(b + n * 64 + (g & 1) * 32 + l, lx, ly);
+    ld8_a2(b + 128 + n * 32 + l, hx, hy);
+    if (g >= 2) { lx >>= 4; ly >>= 4; }
+    hx >>= 2 * g; hy >>= 2 * g;
+    const int8_t sc = (int8_t)b[192 + n * 8 + (l >> 4) + 2 * g];
+    scale = h2f(ld16(b + 208)) * (float)sc;
+    offset = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      q[i] = (float)((int)(((lx >> (8 * i)) & 0xF) | (((hx >> (8 * i)) & 3) << 4)) - 32);
+      q[4 + i] = (float)((int)(((ly >> (8 * i)) & 0xF) | (((hy >> (8 * i)) & 3) << 4)) - 32);
+    }
+  } else if (FMT == QF_Q8_0) {
+    const uint8_t* b = row + (size_t)(k >> 5) * 34;
+    uint32_t lo, hi;
+    ld8_a2(b + 2 + (k & 31), lo, hi);
+    scale = h2f(ld16(b)); offset = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      q[i] = (float)(int8_t)(lo >> (8 * i));
+      q[4 + i] = (float)(int8_t)(hi >> (8 * i));
+    }
+  } else {  // Q4_0: values 0..15 are the low nibbles of qs[0..15], 16..31 the high nibbles
+    const uint8_t* b = row + (size_t)(k >> 5) * 18;
+    const int e = k & 31;
+    uint32_t lo, hi;
+    ld8_a2(b + 2 + (e & 15), lo, hi);
+    if (e >= 16) { lo >>= 4; hi >>= 4; }
+    scale = h2f(ld16(b)); offset = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      q[i] = (float)((int)((lo >> (8 * i)) & 0xF) - 8);
+      q[4 + i] = (float)((int)((hi >> (8 * i)) & 0xF) - 8);
+    }
+  }
+}
+
+constexpr int QG_WARPS = 4;
+enum { QEPI_STORE = 0, QEPI_F32 = 1, QEPI_RESID = 2, QEPI_SWIGLU = 3 };
+
+template <int FMT, int M, int EPI>
+__global__ void __launch_bounds__(QG_WARPS * 32)
+quant_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, void* __restrict__ out,
+                  const __nv_bfloat16* __restrict__ resid, int N, int K, int ldx, int ldo) {
+  pdl_wait(); pdl_launch();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int gwarp = blockIdx.x * QG_WARPS + warp, nwarps = gridDim.x * QG_WARPS;
+  const size_t row_bytes = (size_t)(K / QGeom<FMT>::ELEMS) * QGeom<FMT>::BYTES;
+  for (int pair = gwarp; pair * 2 < N; pair += nwarps) {
+    const int n0 = pair * 2;
+    const uint8_t* r0 = W + (size_t)n0 * row_bytes;
+    const uint8_t* r1 = W + (size_t)(n0 + 1 < N ? n0 + 1 : n0) * row_bytes;
+    float acc[M][2];
+#pragma unroll
+    for (int m = 0; m < M; ++m) { acc[m][0] = 0.f; acc[m][1] = 0.f; }
+    for (int k = lane * 8; k < K; k += 256) {
+      float q0[8], q1[8], s0, o0, s1, o1;
+      decode8<FMT>(r0, k, q0, s0, o0);
+      decode8<FMT>(r1, k, q1, s1, o1);
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float xf[8];
+        unpack8(*reinterpret_cast<const uint4*>(x + (size_t)m * ldx + k), xf);
+        float d0 = 0.f, d1 = 0.f, sx = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { d0 += q0[i] * xf[i]; d1 += q1[i] * xf[i]; sx += xf[i]; }
+        acc[m][0] += s0 * d0 - o0 * sx;
+        acc[m][1] += s1 * d1 - o1 * sx;
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) { acc[m][0] = warp_sum(acc[m][0]); acc[m][1] = warp_sum(acc[m][1]); }
+    if (lane == 0) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        if (EPI == QEPI_SWIGLU) {
+          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + (n0 >> 1)] = __float2bfloat16(silu(acc[m][0]) * acc[m][1]);
+        } else {
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const int n = n0 + r;
+            if (n >= N) break;
+            float v = acc[m][r];
+            if (EPI == QEPI_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
+            else {
+              if (EPI == QEPI_RESID) v += __bfloat162float(resid[(size_t)m * ldo + n]);
+              reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16(v);
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+// out[t, :] = dequant(table[ids[t], :]) as bf16   (packed embedding rows)
+template <int FMT>
+__global__ void quant_row_gather_kernel(const int* __restrict__ ids, const uint8_t* __restrict__ table,
+                                        __nv_bfloat16* __restrict__ out, int D, int vocab) {
+  pdl_wait(); pdl_launch();
+  int id = ids[blockIdx.x];
+  if (id < 0 || id >= vocab) id = 0;
+  const size_t row_bytes = (size_t)(D / QGeom<FMT>::ELEMS) * QGeom<FMT>::BYTES;
+  const uint8_t* row = table + (size_t)id * row_bytes;
+  for (int k = threadIdx.x * 8; k < D; k += blockDim.x * 8) {
+    float q[8], s, o, v[8];
+    decode8<FMT>(row, k, q, s, o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = s * q[i] - o;
+    *reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * D + k) = pack8(v);
+  }
+}
+
+// Whole-tensor dequantisation to bf16 (formats without a fused GEMM are expanded once at load time).
+template <int FMT>
+__global__ void quant_dequant_kernel(const uint8_t* __restrict__ W, __nv_bfloat16* __restrict__ out, int N, int K) {
+  const size_t row_bytes = (size_t)(K / QGeom<FMT>::ELEMS) * QGeom<FMT>::BYTES;
+  const size_t chunks = (size_t)N * (K / 8);
+  for (size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x; c < chunks; c += (size_t)gridDim.x * blockDim.x) {
+    const size_t n = c / (K / 8);
+    const int k = (int)(c - n * (K / 8)) * 8;
+    float q[8], s, o, v[8];
+    decode8<FMT>(W + n * row_bytes, k, q, s, o);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = s * q[i] - o;
+    *reinterpret_cast<uint4*>(out + n * K + k) = pack8(v);
+  }
+}
+
+template <int FMT, int M>
+static int launch_qgemv_m(int epi, const void* x, const void* W, void* out, const void* resid, int N, int K, int ldx,
+                          int ldo, cudaStream_t s) {
+  int pairs = (N + 1) / 2, blocks = (pairs + QG_WARPS - 1) / QG_WARPS;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  dim3 g(blocks), b(QG_WARPS * 32);
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+  const uint8_t* wb = (const uint8_t*)W;
+  const __nv_bfloat16* rb = (const __nv_bfloat16*)resid;
+  switch (epi) {
+    case QEPI_STORE: return launch_k(quant_gemv_kernel<FMT, M, QEPI_STORE>, g, b, 0, s, xb, wb, out, rb, N, K, ldx, ldo);
+    case QEPI_F32: return launch_k(quant_gemv_kernel<FMT, M, QEPI_F32>, g, b, 0, s, xb, wb, out, rb, N, K, ldx, ldo);
+    case QEPI_RESID: return launch_k(quant_gemv_kernel<FMT, M, QEPI_RESID>, g, b, 0, s, xb, wb, out, rb, N, K, ldx, ldo);
+    case QEPI_SWIGLU: return launch_k(quant_gemv_kernel<FMT, M, QEPI_SWIGLU>, g, b, 0, s, xb, wb, out, rb, N, K, ldx, ldo);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+template <int FMT>
+static int launch_qgemv(int epi, const void* x, const void* W, void* out, const void* resid, int M, int N, int K,
+                        int ldx, int ldo, cudaStream_t s) {
+  switch (M) {
+    case 1: return launch_qgemv_m<FMT, 1>(epi, x, W, out, resid, N, K, ldx, ldo, s);
+    case 2: return launch_qgemv_m<FMT, 2>(epi, x, W, out, resid, N, K, ldx, ldo, s);
+    case 3: return launch_qgemv_m<FMT, 3>(epi, x, W, out, resid, N, K, ldx, ldo, s);
+    case 4: return launch_qgemv_m<FMT, 4>(epi, x, W, out, resid, N, K, ldx, ldo, s);
+    default: return (int)cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace poot
+
+using namespace poot;
+
+#define POOT_QDISPATCH(fmt, CALL)                                   \
+  switch (fmt) {                                                    \
+    case QF_Q4_K: return CALL(QF_Q4_K);                             \
+    case QF_Q5_K: return CALL(QF_Q5_K);                             \
+    case QF_Q6_K: return CALL(QF_Q6_K);                             \
+    case QF_Q8_0: return CALL(QF_Q8_0);                             \
+    case QF_Q4_0: return CALL(QF_Q4_0);                             \
+    default: return (int)cudaErrorInvalidValue;                     \
+  }
+
+// fmt = ggml type id (2 Q4_0, 8 Q8_0, 12 Q4_K, 13 Q5_K, 14 Q6_K).  x [M, ldx] bf16, W packed [N rows of K values].
+POOT_API int poot_quant_gemv(int fmt, int epi, const void* x, const void* W, void* out, const void* resid, int M, int N,
+                             int K, int ldx, int ldo, cudaStream_t s) {
+  if (K % 256 || ldx % 8 || M < 1 || M > 4) return (int)cudaErrorInvalidValue;
+  if (epi == QEPI_SWIGLU && (N & 1)) return (int)cudaErrorInvalidValue;
+#define CALL(F) launch_qgemv<F>(epi, x, W, out, resid, M, N, K, ldx, ldo, s)
+  POOT_QDISPATCH(fmt, CALL)
+#undef CALL
+}
+
+POOT_API int poot_quant_row_gather(int fmt, const int* ids, const void* table, void* out, int T, int D, int vocab,
+                                   cudaStream_t s) {
+  if (T == 0) return 0;
+  if (D % 256) return (int)cudaErrorInvalidValue;
+#define CALL(F) launch_k(quant_row_gather_kernel<F>, dim3(T), dim3(128), 0, s, ids, (const uint8_t*)table, (__nv_bfloat16*)out, D, vocab)
+  POOT_QDISPATCH(fmt, CALL)
+#undef CALL
+}
+
+POOT_API int poot_quant_dequant_bf16(int fmt, const void* W, void* out, int N, int K, cudaStream_t s) {
+  if (K % 256) return (int)cudaErrorInvalidValue;
+  long long chunks = (long long)N * (K / 8);
+  int blocks = (int)((chunks + 255) / 256 > 148 * 16 ? 148 * 16 : (chunks + 255) / 256);
+  if (blocks < 1) return 0;
+#define CALL(F) (quant_dequant_kernel<F><<<blocks, 256, 0, s>>>((const uint8_t*)W, (__nv_bfloat16*)out, N, K), (int)cudaGetLastError())
+  POOT_QDISPATCH(fmt, CALL)
+#undef CALL
+}

@@ -1,0 +1,368 @@
+"""The sequence driver: open / step / commit / release over a step engine with a paged KV cache.
+
+Mirrors the reference driver's contract (crates/poot-llm/src/driver/mod.rs:1-40, step.rs:393-1359):
+
+* ``open``    reserves a row and the KV blocks for prompt + max_tokens (nothing is ever preempted), after matching
+              the longest cached prefix of whole 16-token blocks;
+* ``step``    plans every live row - a prefill piece (``prefill_chunk`` tokens, bin-packed into a per-step token
+              budget of ``widest_piece + rows`` with one token reserved per decoding row, oldest first) or one
+              decode token - pads the plan to a prepared step shape, runs ONE engine step and returns each row's
+              sampled token (uncommitted);
+* ``commit``  appends the kept tokens to the sequence;
+* ``release`` frees the blocks and registers the prompt's full blocks in the prefix cache (not when preempted).
+
+The engine behind it is any object with the small ``StepEngine`` surface, so the same driver runs on the device
+engine, on the CPU oracle and on the recording fake used by the scheduling tests.
+"""
+from __future__ import annotations
+
+import itertools
+import time
+from dataclasses import dataclass, field
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import numpy as np
+
+from ..oracle import sampling as S
+from .kvcache import BLOCK, BASE_IDENTITY, BlockPool, OutOfBlocks, PrefixCache, blocks_for
+from .sampler import SamplingParams, step_seed
+
+
+class DriverError(RuntimeError):
+    pass
+
+
+class NoFreeRow(DriverError):
+    """Every serving row is in use."""
+
+
+class SamplerFault(DriverError):
+    """The step produced a non-finite logit for this row (typed fault; the token is not committed)."""
+
+    def __init__(self, seq_id: int, index: int):
+        super().__init__(f"sequence {seq_id}: non-finite logit at index {index}")
+        self.seq_id, self.index = seq_id, index
+
+
+@dataclass
+class StepInputs:
+    """One engine step, already padded to a prepared shape (padding rows write nothing: slot -1, context 0)."""
+    tokens: np.ndarray       # [T] int32
+    positions: np.ndarray    # [T] int32
+    slots: np.ndarray        # [T] int32, -1 = no KV write
+    row_seq: np.ndarray      # [T] int32 row of the block table
+    row_ctx: np.ndarray      # [T] int32 keys visible to the token (position + 1)
+    logit_idx: np.ndarray    # [B] int64 index into the T tokens of each row that samples
+    sampler: int             # 0 greedy, 1..3 Gumbel rule (widest needed by any row)
+    params: np.ndarray       # [B, 4] f32
+    top_k: np.ndarray        # [B] int32
+    seeds: np.ndarray        # [B] int32
+    adjust: Optional[dict] = None   # {"idx": [B, A] int32, "val": [B, A, 4] f32, "guided": {row: mask}}
+    want_logprobs: bool = False
+    live_tokens: int = 0
+    live_rows: int = 0
+
+
+@dataclass
+class RowResult:
+    seq_id: int
+    token: Optional[int]          # sampled token, or None while the prompt is still being prefilled
+    consumed: int                 # tokens of the sequence processed by this step
+    logprob: Optional[float] = None
+
+
+@dataclass
+class Sequence_:
+    id: int
+    row: int
+    tokens: List[int]
+    prompt_len: int
+    params: SamplingParams
+    blocks: List[int]
+    identity: int = BASE_IDENTITY
+    computed: int = 0             # tokens whose K/V is in the cache
+    cached_tokens: int = 0        # served from the prefix cache at open
+    generated: int = 0
+    opened_at: float = field(default_factory=time.monotonic)
+    counts: Dict[int, int] = field(default_factory=dict)   # token histogram for the penalties
+    guided: Optional[object] = None                        # constraint object with .mask(vocab) / .advance(token)
+    seed: int = 0
+
+    @property
+    def pending(self) -> int:
+        return len(self.tokens) - self.computed
+
+
+def chunk_plan(n: int, chunk: int, granule: int = 16) -> List[int]:
+    """Pieces of a prompt of ``n`` tokens: full chunks, then descending powers of two of the granule, then the rest
+    (crates/poot-llm/src/driver/chunks.rs:1-9) - a small set of distinct step shapes."""
+    out = []
+    while n >= chunk:
+        out.append(chunk)
+        n -= chunk
+    p = chunk // 2
+    while p >= granule and n > 0:
+        if n >= p:
+            out.append(p)
+            n -= p
+        p //= 2
+    if n > 0:
+        out.append(n)
+    return out
+
+
+def _bucket(n: int, cap: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return min(b, cap) if b <= cap else n
+
+
+class Driver:
+    MAX_ADJ = 1024
+
+    def __init__(self, engine, num_blocks: int, max_rows: int, max_seq_len: int, vocab: int, prefill_chunk: int = 512,
+                 prefix_caching: bool = True, eos_token: Optional[int] = None):
+        self.engine = engine
+        self.pool = BlockPool(num_blocks)
+        self.prefix = PrefixCache(self.pool) if prefix_caching else None
+        self.max_rows, self.max_seq_len, self.vocab = max_rows, max_seq_len, vocab
+        self.prefill_chunk = prefill_chunk
+        self.eos_token = eos_token
+        self.max_blocks_per_seq = blocks_for(max_seq_len)
+        self.seqs: Dict[int, Sequence_] = {}
+        self._free_rows = list(range(max_rows - 1, -1, -1))
+        self._ids = itertools.count(1)
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "prefix_hit_tokens": 0,
+                      "prefix_query_tokens": 0, "padded_tokens": 0}
+
+    # ------------------------------------------------------------------------------------------------ admission
+    def can_open(self, prompt_len: int, max_tokens: int) -> bool:
+        need = blocks_for(min(prompt_len + max_tokens, self.max_seq_len))
+        free = self.pool.available
+        return bool(self._free_rows) and need <= free + (len(self.prefix) if self.prefix is not None else 0)
+
+    def open(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, identity: int = BASE_IDENTITY,
+             guided=None) -> int:
+        params = params or SamplingParams()
+        params.validate()
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise DriverError("empty prompt")
+        if any(t < 0 or t >= self.vocab for t in prompt):
+            raise DriverError("prompt token outside the vocabulary")
+        total = len(prompt) + params.max_tokens
+        if len(prompt) >= self.max_seq_len:
+            raise DriverError(f"prompt of {len(prompt)} tokens does not fit max_seq_len {self.max_seq_len}")
+        total = min(total, self.max_seq_len)
+        if not self._free_rows:
+            raise NoFreeRow("no free serving row")
+        matched: List[int] = []
+        if self.prefix is not None:
+            matched = self.prefix.match(prompt, identity, self.max_blocks_per_seq)
+            self.stats["prefix_query_tokens"] += len(prompt)
+            self.stats["prefix_hit_tokens"] += len(matched) * BLOCK
+        need = blocks_for(total) - len(matched)
+        try:
+            if need > self.pool.available and self.prefix is not None:
+                self.prefix.evict_unused(need - self.pool.available)
+            fresh = self.pool.alloc(need)
+        except OutOfBlocks:
+            for b in matched:
+                self.pool.release(b)
+            raise
+        row = self._free_rows.pop()
+        sid = next(self._ids)
+        seq = Sequence_(sid, row, prompt, len(prompt), params, matched + fresh, identity,
+                        computed=len(matched) * BLOCK, cached_tokens=len(matched) * BLOCK, guided=guided,
+                        seed=params.seed if params.seed is not None else (sid * 2654435761) & 0x7FFFFFFF)
+        for t in prompt:
+            seq.counts[t] = seq.counts.get(t, 0) + 1
+        self.seqs[sid] = seq
+        self.engine.write_block_table(row, seq.blocks)
+        return sid
+
+    def resume(self, seq_id: int, more_tokens: Sequence[int], extra_max_tokens: int = 0) -> None:
+        """Append the next turn's tokens to a live sequence; its K/V stays (conversation mode)."""
+        seq = self.seqs[seq_id]
+        seq.tokens.extend(int(t) for t in more_tokens)
+        seq.params.max_tokens = seq.generated + extra_max_tokens if extra_max_tokens else seq.params.max_tokens
+        need = blocks_for(min(len(seq.tokens) + max(extra_max_tokens, 1), self.max_seq_len)) - len(seq.blocks)
+        if need > 0:
+            seq.blocks.extend(self.pool.alloc(need))
+            self.engine.write_block_table(seq.row, seq.blocks)
+
+    # ------------------------------------------------------------------------------------------------ stepping
+    def plan(self, seq_ids: Optional[Iterable[int]] = None):
+        """Rows of the next step: ``[(seq, piece)]`` oldest first under the token budget."""
+        live = [self.seqs[i] for i in (seq_ids if seq_ids is not None else sorted(self.seqs))]
+        live = [s for s in live if s.pending > 0]
+        decode = [s for s in live if s.pending == 1]
+        prefill = [s for s in live if s.pending > 1]
+        widest = min(max((s.pending for s in prefill), default=0), self.prefill_chunk)
+        budget = min(widest + len(live), self.engine.max_tokens)
+        rows = [(s, 1) for s in decode]
+        used = len(decode)
+        for s in prefill:                       # FIFO best-effort bin packing
+            piece = min(s.pending, self.prefill_chunk, budget - used)
+            if piece <= 0:
+                continue
+            if piece < s.pending:               # keep chunk boundaries on block multiples
+                piece = (piece // BLOCK) * BLOCK
+                if piece == 0:
+                    continue
+            rows.append((s, piece))
+            used += piece
+        rows.sort(key=lambda r: r[0].id)
+        return rows
+
+    def _slot(self, seq: Sequence_, pos: int) -> int:
+        return seq.blocks[pos // BLOCK] * BLOCK + pos % BLOCK
+
+    def build_inputs(self, rows) -> StepInputs:
+        T = sum(p for _, p in rows)
+        sampling_rows = [(s, p) for s, p in rows if p == s.pending]
+        B = len(sampling_rows)
+        Tp = _bucket(T, self.engine.max_tokens)
+        Bp = _bucket(max(B, 1), self.max_rows)
+        tokens = np.zeros(Tp, np.int32); positions = np.zeros(Tp, np.int32); slots = np.full(Tp, -1, np.int32)
+        row_seq = np.zeros(Tp, np.int32); row_ctx = np.zeros(Tp, np.int32)
+        logit_idx = np.zeros(Bp, np.int64)
+        params = np.zeros((Bp, 4), np.float32); params[:, 0] = 1.0; params[:, 1] = -1e30; params[:, 3] = 1.0
+        top_k = np.zeros(Bp, np.int32); seeds = np.zeros(Bp, np.int32)
+        rule, off, b = S.GREEDY, 0, 0
+        adjust_rows, guided_rows, want_lp = {}, {}, False
+        for s, piece in rows:
+            for i in range(piece):
+                pos = s.computed + i
+                tokens[off + i] = s.tokens[pos]
+                positions[off + i] = pos
+                slots[off + i] = self._slot(s, pos)
+                row_seq[off + i] = s.row
+                row_ctx[off + i] = pos + 1
+            if piece == s.pending:
+                logit_idx[b] = off + piece - 1
+                sp = s.params
+                rule = max(rule, sp.rule)
+                params[b] = sp.device_params()
+                top_k[b] = sp.top_k if not sp.greedy else 0
+                seeds[b] = step_seed(s.seed, s.generated)
+                if sp.needs_adjust:
+                    adjust_rows[b] = s
+                if s.guided is not None:
+                    guided_rows[b] = s.guided.mask(self.vocab)
+                want_lp = want_lp or sp.logprobs > 0
+                b += 1
+            off += piece
+        adjust = None
+        if adjust_rows or guided_rows:
+            idx = np.full((Bp, self.MAX_ADJ), -1, np.int32)
+            val = np.zeros((Bp, self.MAX_ADJ, 4), np.float32)
+            for r, s in adjust_rows.items():
+                sp = s.params
+                ents: Dict[int, List[float]] = {}
+                for t, bias in sp.logit_bias.items():
+                    ents[int(t)] = [float(bias), 1.0, 1.0, 0.0]
+                for t, c in list(s.counts.items())[-self.MAX_ADJ:]:
+                    # order of the reference: +bias, repetition on the biased value, then the additive penalties
+                    e = ents.setdefault(t, [0.0, 1.0, 1.0, 0.0])
+                    e[1] *= 1.0 / sp.repeat_penalty
+                    e[2] *= sp.repeat_penalty
+                    e[3] -= sp.presence_penalty + sp.frequency_penalty * c
+                for k, (t, e) in enumerate(list(ents.items())[:self.MAX_ADJ]):
+                    idx[r, k] = t
+                    val[r, k] = e
+            adjust = {"idx": idx, "val": val, "guided": guided_rows}
+        self.stats["padded_tokens"] += Tp - T
+        return StepInputs(tokens, positions, slots, row_seq, row_ctx, logit_idx, rule, params, top_k, seeds, adjust,
+                          want_lp, T, B)
+
+    def step(self, seq_ids: Optional[Iterable[int]] = None) -> List[RowResult]:
+        rows = self.plan(seq_ids)
+        if not rows:
+            return []
+        inp = self.build_inputs(rows)
+        picked, logprobs = self.engine.run_step(inp)
+        self.stats["steps"] += 1
+        out, b = [], 0
+        for s, piece in rows:
+            sampled = piece == s.pending
+            s.computed += piece
+            if piece > 1 or s.generated == 0 and not sampled:
+                self.stats["prefill_tokens"] += piece
+            else:
+                self.stats["decode_tokens"] += piece
+            if sampled:
+                tok, bad = int(picked[b, 0]), int(picked[b, 1])
+                lp = float(logprobs[b]) if logprobs is not None else None
+                b += 1
+                if bad >= 0:
+                    raise SamplerFault(s.id, bad)
+                out.append(RowResult(s.id, tok, piece, lp))
+            else:
+                out.append(RowResult(s.id, None, piece))
+        return out
+
+    def commit(self, seq_id: int, tokens: Sequence[int]) -> None:
+        s = self.seqs[seq_id]
+        for t in tokens:
+            if len(s.tokens) >= self.max_seq_len or len(s.tokens) >= len(s.blocks) * BLOCK:
+                raise DriverError(f"sequence {seq_id} is at its reserved capacity")
+            s.tokens.append(int(t))
+            s.counts[int(t)] = s.counts.get(int(t), 0) + 1
+            s.generated += 1
+            if s.guided is not None:
+                s.guided.advance(int(t))
+
+    def finished(self, seq_id: int, token: int) -> Optional[str]:
+        """Why the sequence ends after ``token`` was committed ("stop", "length") or None."""
+        s = self.seqs[seq_id]
+        sp = s.params
+        if not sp.ignore_eos and self.eos_token is not None and token == self.eos_token:
+            return "stop"
+        if token in sp.stop_token_ids:
+            return "stop"
+        if s.guided is not None and getattr(s.guided, "done", lambda: False)():
+            return "stop"
+        if s.generated >= sp.max_tokens or len(s.tokens) >= self.max_seq_len:
+            return "length"
+        return None
+
+    def release(self, seq_id: int, reason: str = "finished") -> dict:
+        s = self.seqs.pop(seq_id)
+        registered = 0
+        if reason == "finished" and self.prefix is not None:
+            n_full = min(s.prompt_len, s.computed) // BLOCK
+            registered = self.prefix.register(s.tokens[:n_full * BLOCK], s.blocks[:n_full], s.identity)
+        for b in s.blocks:
+            self.pool.release(b)
+        self._free_rows.append(s.row)
+        return {"registered_tokens": registered, "generated": s.generated, "cached_tokens": s.cached_tokens}
+
+    # ------------------------------------------------------------------------------------------------ convenience
+    def generate(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, on_token=None) -> List[int]:
+        sid = self.open(prompt, params)
+        out: List[int] = []
+        try:
+            while True:
+                res = [r for r in self.step([sid]) if r.seq_id == sid]
+                if not res:
+                    break
+                r = res[0]
+                if r.token is None:
+                    continue
+                self.commit(sid, [r.token])
+                out.append(r.token)
+                if on_token is not None:
+                    on_token(r.token)
+                if self.finished(sid, r.token):
+                    break
+        finally:
+            self.release(sid)
+        return out
+
+    def kv_usage(self) -> dict:
+        total = self.pool.num_blocks
+        return {"blocks_total": total, "blocks_used": total - self.pool.available,
+                "usage_ratio": (total - self.pool.available) / max(total, 1),
+                "prefix_entries": len(self.prefix) if self.prefix is not None else 0}

@@ -1,0 +1,103 @@
+"""Step engines behind the driver: the device engine adapter and the recording fake.
+
+``DeviceStepEngine`` binds a padded ``StepInputs`` into the device engine's static buffers (one pinned staging
+copy per field), replays the prepared step graph and reads back ``(token, non_finite_index)`` per sampling row -
+never the logits (crates/poot-llm/src/driver/step.rs:776, suffix.rs:255).  ``FakeStepEngine`` records every step
+and answers deterministically, which is how the scheduling and admission logic is tested without a GPU (the
+reference's recording ``ServeEngine``, crates/poot-serve/src/tests/recording_engine.rs).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import numpy as np
+
+from .driver import StepInputs
+
+
+class FakeStepEngine:
+    """Next token = (last fed token of the row + 1) mod vocab; records the steps it was asked to run."""
+
+    def __init__(self, vocab: int = 1000, max_tokens: int = 256, fail_at_step: Optional[int] = None):
+        self.vocab, self.max_tokens = vocab, max_tokens
+        self.steps: List[StepInputs] = []
+        self.block_tables = {}
+        self.fail_at_step = fail_at_step
+
+    def write_block_table(self, row: int, blocks) -> None:
+        self.block_tables[row] = list(blocks)
+
+    def run_step(self, inp: StepInputs) -> Tuple[np.ndarray, Optional[np.ndarray]]:
+        if self.fail_at_step is not None and len(self.steps) == self.fail_at_step:
+            raise RuntimeError("injected engine fault")
+        self.steps.append(inp)
+        B = len(inp.logit_idx)
+        picked = np.zeros((B, 2), np.int32)
+        picked[:, 1] = -1
+        for b in range(inp.live_rows):
+            picked[b, 0] = (int(inp.tokens[inp.logit_idx[b]]) + 1) % self.vocab
+        return picked, (np.zeros(B, np.float32) if inp.want_logprobs else None)
+
+
+class DeviceStepEngine:
+    """Adapter from ``StepInputs`` to :class:`poot_b200.runtime.engine.DecoderEngine`."""
+
+    def __init__(self, engine):
+        import torch
+        self.torch = torch
+        self.e = engine
+        self.max_tokens = engine.max_tokens
+        n = engine.max_tokens
+        pin = torch.cuda.is_available()
+
+        def buf(shape, dtype):
+            t = torch.zeros(shape, dtype=dtype)
+            return t.pin_memory() if pin else t
+
+        self.h_tokens, self.h_pos, self.h_slots = buf(n, torch.int32), buf(n, torch.int32), buf(n, torch.int32)
+        self.h_seq, self.h_ctx = buf(n, torch.int32), buf(n, torch.int32)
+        B = engine.max_seqs
+        self.h_lidx = buf(B, torch.int64)
+        self.h_params, self.h_topk, self.h_seeds = buf((B, 4), torch.float32), buf(B, torch.int32), buf(B, torch.int32)
+        self.h_picked, self.h_logprobs = buf((B, 2), torch.int32), buf(B, torch.float32)
+        self.h_bt = buf((engine.max_seqs, engine.max_blocks), torch.int32)
+
+    def write_block_table(self, row: int, blocks) -> None:
+        n = len(blocks)
+        self.h_bt[row, :n] = self.torch.as_tensor(blocks, dtype=self.torch.int32)
+        self.e.block_tables[row, :n].copy_(self.h_bt[row, :n], non_blocking=True)
+
+    def run_step(self, inp: StepInputs):
+        from ..runtime.engine import StepShape
+        torch, e = self.torch, self.e
+        T, B = len(inp.tokens), len(inp.logit_idx)
+        for dst, src in ((self.h_tokens, inp.tokens), (self.h_pos, inp.positions), (self.h_slots, inp.slots),
+                         (self.h_seq, inp.row_seq), (self.h_ctx, inp.row_ctx)):
+            dst[:T] = torch.from_numpy(src)
+        self.h_lidx[:B] = torch.from_numpy(inp.logit_idx)
+        e.bind(self.h_tokens[:T], self.h_pos[:T], self.h_slots[:T], self.h_seq[:T], self.h_ctx[:T], self.h_lidx[:B])
+        if inp.sampler != 0:
+            self.h_params[:B] = torch.from_numpy(inp.params)
+            self.h_topk[:B] = torch.from_numpy(inp.top_k)
+            self.h_seeds[:B] = torch.from_numpy(inp.seeds)
+            e.samp_params[:B].copy_(self.h_params[:B], non_blocking=True)
+            e.samp_topk[:B].copy_(self.h_topk[:B], non_blocking=True)
+            e.samp_seeds[:B].copy_(self.h_seeds[:B], non_blocking=True)
+        guided = False
+        if inp.adjust is not None:
+            if e.adj_idx is None:
+                e._alloc_adjust()
+            e.adj_idx[:B].copy_(torch.from_numpy(inp.adjust["idx"]), non_blocking=False)
+            e.adj_val[:B].copy_(torch.from_numpy(inp.adjust["val"]), non_blocking=False)
+            if inp.adjust["guided"]:
+                guided = True
+                e.guided_mask[:B].zero_()
+                for r, m in inp.adjust["guided"].items():
+                    e.guided_mask[r].copy_(torch.from_numpy(np.ascontiguousarray(m, dtype=np.float32)))
+        shape = StepShape(T, B, inp.sampler, False, inp.adjust is not None, guided, inp.want_logprobs)
+        e.run(shape)
+        self.h_picked[:B].copy_(e.picked[:B], non_blocking=True)
+        if inp.want_logprobs:
+            self.h_logprobs[:B].copy_(e.logprobs[:B], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.h_picked[:B].numpy().copy(), (self.h_logprobs[:B].numpy().copy() if inp.want_logprobs else None)

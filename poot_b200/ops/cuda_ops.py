@@ -429,3 +429,76 @@ def decode_advance(picked: torch.Tensor, tokens: torch.Tensor, positions: torch.
     check(_fn("poot_decode_advance")(_ptr(picked), _ptr(tokens), _ptr(positions), _ptr(slots), _ptr(ctx),
                                      _ptr(block_tables), block_tables.shape[1], _ptr(row_seq), B, _stream()),
           "decode_advance")
+
+
+# ---- GGUF block-quantised weights ---------------------------------------------------------------------------------
+register_signature("poot_quant_gemv", [c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
+register_signature("poot_quant_row_gather", [c_int, _P, _P, _P, c_int, c_int, c_int, _P])
+register_signature("poot_quant_dequant_bf16", [c_int, _P, _P, c_int, c_int, _P])
+QUANT_DEVICE_FORMATS = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
+
+
+class QuantWeight:
+    """A packed ``[N, K]`` weight resident on the device in its checkpoint block layout."""
+
+    def __init__(self, fmt: str, packed: torch.Tensor, N: int, K: int):
+        if fmt not in QUANT_DEVICE_FORMATS:
+            raise ValueError(f"{fmt} has no fused device kernels (expand it to bf16 at load time)")
+        assert packed.dtype == torch.uint8 and packed.is_cuda and packed.is_contiguous()
+        self.fmt, self.packed, self.N, self.K = fmt, packed, N, K
+        self.type_id = QUANT_DEVICE_FORMATS[fmt]
+        self.shape = (N, K)
+        self._scratch = None
+
+    @property
+    def device(self):
+        return self.packed.device
+
+    def nbytes(self) -> int:
+        return self.packed.numel()
+
+
+_dequant_scratch = {}
+
+
+def quant_gemv(x: torch.Tensor, W: QuantWeight, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
+               resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    M, Kd = x.shape
+    assert Kd == W.K and x.dtype == torch.bfloat16 and x.stride(1) == 1
+    out = _out_for(epi, M, W.N, x.device, out)
+    check(_fn("poot_quant_gemv")(W.type_id, epi, _ptr(x), _ptr(W.packed), _ptr(out), _ptr(resid), M, W.N, Kd,
+                                 x.stride(0), out.stride(0), _stream()), "quant_gemv")
+    return out
+
+
+def quant_row_gather(ids: torch.Tensor, W: QuantWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T = ids.numel()
+    if out is None:
+        out = torch.empty(T, W.K, dtype=torch.bfloat16, device=W.device)
+    check(_fn("poot_quant_row_gather")(W.type_id, _ptr(ids), _ptr(W.packed), _ptr(out), T, W.K, W.N, _stream()),
+          "quant_row_gather")
+    return out
+
+
+def quant_dequant(W: QuantWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(W.N, W.K, dtype=torch.bfloat16, device=W.device)
+    check(_fn("poot_quant_dequant_bf16")(W.type_id, _ptr(W.packed), _ptr(out), W.N, W.K, _stream()), "quant_dequant")
+    return out
+
+
+_plain_linear = linear
+
+
+def linear(x, W, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None):
+    """``x @ W^T`` for a bf16 weight or a packed ``QuantWeight`` (fused GEMV at decode, expand + GEMM for larger M)."""
+    if isinstance(W, QuantWeight):
+        if x.shape[0] <= 4:
+            return quant_gemv(x, W, epi, out, resid)
+        key = (W.device, W.N * W.K)
+        buf = _dequant_scratch.get(key)
+        if buf is None:
+            buf = torch.empty(W.N * W.K, dtype=torch.bfloat16, device=W.device)
+            _dequant_scratch[key] = buf
+        return _plain_linear(x, quant_dequant(W, buf.view(W.N, W.K)), epi, out, resid)
+    return _plain_linear(x, W, epi, out, resid)

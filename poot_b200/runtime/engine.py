@@ -30,6 +30,9 @@ class StepShape:
     logit_rows: int     # B: rows that get logits + a sampled token
     sampler: int = 0    # 0 greedy, 1..3 Gumbel family rule
     chain: bool = False  # append the device-side advance (decode chaining)
+    adjust: bool = False    # apply the sparse logit adjustments (bias, penalties) before sampling
+    guided: bool = False    # also add the dense guided-decoding mask
+    logprobs: bool = False  # record the picked token's log-probability
 
 
 class KVPool:
@@ -111,6 +114,8 @@ class DecoderEngine:
             self.argmax_part_local = torch.zeros(max_seqs * G * 3, dtype=torch.int32, device=dev)
             self.argmax_part_all = torch.zeros(self.tp * max_seqs * G * 3, dtype=torch.int32, device=dev)
         self.picked = torch.zeros(max_seqs, 2, dtype=i32, device=dev)
+        self.logprobs = torch.zeros(max_seqs, dtype=torch.float32, device=dev)
+        self.adj_idx = self.adj_val = self.guided_mask = None   # allocated on first use
         self.argmax_scratch = K.argmax_scratch(max_seqs, cfg.vocab, dev)
         self.attn_splits_max = 16
         ts = self.small_T
@@ -227,14 +232,13 @@ class DecoderEngine:
         """Sampler suffix over (possibly vocabulary-sharded) logits; every rank ends with the same ``picked``."""
         B, V = shape.logit_rows, self.cfg.vocab
         self.last_local_logits = local_logits  # [B, vocab / tp] of the step just launched
+        need_full = shape.sampler != 0 or shape.adjust or shape.logprobs
+        logits = None
         if self.tp == 1:
             logits = local_logits
-            if shape.sampler == 0:
-                self._count(2)
-                K.argmax(logits, out=self.picked[:B], scratch=self.argmax_scratch)
         else:
             vl = V // self.tp
-            if shape.sampler == 0:
+            if not need_full:
                 # greedy: exchange the stage-1 partial tables (a few KB), not the logits
                 G = K.argmax_groups(vl)
                 part = self.argmax_part_local[:B * G * 3].view(B, G, 3)
@@ -249,14 +253,36 @@ class DecoderEngine:
                 self.comm.all_gather(gathered, local_logits.contiguous() if local_logits.stride(0) != vl else local_logits)
                 logits = self.logits[:B]
                 logits.view(B, self.tp, vl).copy_(gathered.permute(1, 0, 2))
-        if shape.sampler != 0:
-            self._count()
-            K.sample_gumbel(logits, self.samp_params[:B], self.samp_topk[:B], self.samp_seeds[:B], shape.sampler,
-                            out=self.picked[:B])
+        if logits is not None:
+            if shape.adjust:
+                from ..ops import suffix_ops
+                self._count()
+                if self.adj_idx is None:
+                    self._alloc_adjust()
+                suffix_ops.adjust_logits(logits, self.adj_idx[:B], self.adj_val[:B],
+                                         self.guided_mask[:B] if shape.guided else None)
+            self._count(2 if shape.sampler == 0 else 1)
+            if shape.sampler == 0:
+                K.argmax(logits, out=self.picked[:B], scratch=self.argmax_scratch)
+            else:
+                K.sample_gumbel(logits, self.samp_params[:B], self.samp_topk[:B], self.samp_seeds[:B], shape.sampler,
+                                out=self.picked[:B])
+            if shape.logprobs:
+                from ..ops import suffix_ops
+                self._count()
+                suffix_ops.token_logprob(logits, self.picked[:B], out=self.logprobs[:B])
         if shape.chain:
             self._count()
             K.decode_advance(self.picked, self.tokens, self.positions, self.slots, self.row_ctx, self.block_tables,
                              self.row_seq, B)
+
+    MAX_ADJ = 1024
+
+    def _alloc_adjust(self) -> None:
+        dev = self.device
+        self.adj_idx = torch.full((self.max_seqs, self.MAX_ADJ), -1, dtype=torch.int32, device=dev)
+        self.adj_val = torch.zeros(self.max_seqs, self.MAX_ADJ, 4, dtype=torch.float32, device=dev)
+        self.guided_mask = torch.zeros(self.max_seqs, self.cfg.vocab, dtype=torch.float32, device=dev)
 
     def _forward_tp_oneshot(self, shape: StepShape) -> None:
         """Small steps on the fused tensor-parallel path with one-shot all-reduces: the o_proj / down_proj GEMM
@@ -349,7 +375,7 @@ class DecoderEngine:
 
     # ------------------------------------------------------------------ capture / replay
     def _key(self, shape: StepShape):
-        return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain)
+        return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain, shape.adjust, shape.guided, shape.logprobs)
 
     def prepare(self, shape: StepShape) -> None:
         """Warm up and capture the step graph for ``shape`` (never done in the serving path afterwards)."""

@@ -1,0 +1,55 @@
+"""Device kernels over GGUF block formats against the host codec (which is checked against hand-built blocks)."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+FMTS = ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0"]
+
+
+def _packed(fmt, N, Kd, seed=0):
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.quant import codec
+    w = (np.random.default_rng(seed).standard_normal((N, Kd)) * 0.05).astype(np.float32)
+    p = codec.quantize(fmt, w)
+    deq = codec.dequantize(fmt, p, (N, Kd))
+    return K.QuantWeight(fmt, torch.from_numpy(p).cuda(), N, Kd), torch.from_numpy(deq).cuda()
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("M", [1, 3])
+def test_quant_gemv_matches_dequantised_reference(fmt, M):
+    from poot_b200.ops import cuda_ops as K
+    N, Kd = 1026, 1024
+    W, deq = _packed(fmt, N, Kd)
+    x = (torch.randn(M, Kd, device="cuda")).to(torch.bfloat16)
+    ref = x.float() @ deq.T
+    out = K.quant_gemv(x, W, K.EPI_F32)
+    assert (out - ref).abs().max() <= 2e-3 * ref.abs().max() + 1e-3
+    res = torch.randn(M, N, device="cuda").to(torch.bfloat16)
+    o2 = K.quant_gemv(x, W, K.EPI_RESID, resid=res)
+    assert (o2.float() - (ref + res.float())).abs().max() <= 2e-2 * (ref.abs().max() + 3)
+    sw = K.quant_gemv(x, W, K.EPI_SWIGLU)
+    r2 = torch.nn.functional.silu(ref[:, 0::2]) * ref[:, 1::2]
+    assert (sw.float() - r2).abs().max() <= 2e-2 * r2.abs().max() + 1e-2
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_quant_dequant_and_row_gather_are_exact(fmt):
+    from poot_b200.ops import cuda_ops as K
+    W, deq = _packed(fmt, 300, 512, seed=3)
+    full = K.quant_dequant(W)
+    assert torch.equal(full, deq.to(torch.bfloat16))
+    ids = torch.tensor([0, 7, 299, 7], dtype=torch.int32, device="cuda")
+    rows = K.quant_row_gather(ids, W)
+    assert torch.equal(rows, deq[ids.long()].to(torch.bfloat16))
+
+
+def test_linear_dispatches_packed_weights_for_prefill_shapes():
+    from poot_b200.ops import cuda_ops as K
+    W, deq = _packed("Q4_K", 512, 1024, seed=5)
+    x = torch.randn(200, 1024, device="cuda").to(torch.bfloat16)
+    out = K.linear(x, W)
+    ref = x.float() @ deq.to(torch.bfloat16).float().T
+    assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max() + 2e-2
+    K.check_status()
