@@ -27,6 +27,18 @@ constexpr int SK_BM = 128;   // weight rows per CTA
 constexpr int SK_BK = 64;
 constexpr int SK_THREADS = 192;
 
+// Grouped (mixture-of-experts) form: blockIdx.y selects a group; a group multiplies its own X rows / columns with
+// one expert's slice of a stacked weight [experts * N, K] and writes its own output slice.
+struct GroupArgs {
+  const int* group_expert;      // group -> expert id (null: expert = group; a negative id yields zeros)
+  int w_rows_per_expert;        // N of one expert inside the stacked weight
+  int x_row_div;                // > 0: the group's X rows start at group / x_row_div
+  int x_row_mul;                // the group's X rows start at group * x_row_mul (added to the above)
+  int x_col_per_expert;         // the group's X columns (K range) start at expert * x_col_per_expert
+  long long out_group_stride;   // elements between the outputs of consecutive groups
+  const float* row_scale;       // [groups, M] factor applied to each result row (null = 1)
+};
+
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -57,7 +69,7 @@ template <int BT, int STAGES, int WM, int EPI>
 __global__ void __launch_bounds__(SK_THREADS)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    void* __restrict__ out, const __nv_bfloat16* resid, int M, int N, int K, int ldo, int CK,
-                   int* __restrict__ status, const __grid_constant__ TpArgs tp) {
+                   int* __restrict__ status, const __grid_constant__ TpArgs tp, const __grid_constant__ GroupArgs grp) {
   using S = SkinnySmem<BT, STAGES, WM>;
   constexpr int ROWS = WM * SK_BM;  // weight rows per CTA
   extern __shared__ uint8_t smem_raw[];
@@ -81,7 +93,15 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int kt_begin = (int)crank * per;
   int kt_end = kt_begin + per;
   if (kt_end > total_kt) kt_end = total_kt;
-  const int num_kt = kt_end > kt_begin ? kt_end - kt_begin : 0;
+  // grouped form: which expert's weight slice, which X rows / columns, which output slice
+  const int grp_id = blockIdx.y;
+  int expert = grp_id;
+  if (grp.group_expert != nullptr) { pdl_wait(); expert = grp.group_expert[grp_id]; }  // produced by the router kernel
+  const bool dead = expert < 0;
+  const int w_row0 = (dead ? 0 : expert) * grp.w_rows_per_expert + n0;
+  const int x_row0 = (grp.x_row_div > 0 ? grp_id / grp.x_row_div : 0) + grp_id * grp.x_row_mul;
+  const int x_col0 = (dead ? 0 : expert) * grp.x_col_per_expert;
+  const int num_kt = (dead || kt_end <= kt_begin) ? 0 : kt_end - kt_begin;
   constexpr uint32_t TMEM_COLS = (WM * BT) < 32 ? 32 : (WM * BT);
 
   if (threadIdx.x == 0) {
@@ -108,7 +128,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int pre = num_kt < STAGES ? num_kt : STAGES;
       for (int i = 0; i < pre; ++i) {
         tc::mbar_expect_tx(full_bar + 8 * i, S::STAGE_BYTES);
-        tc::tma_load_2d(base + i * S::STAGE_BYTES, &tmW, (kt_begin + i) * SK_BK, n0, full_bar + 8 * i);
+        tc::tma_load_2d(base + i * S::STAGE_BYTES, &tmW, (kt_begin + i) * SK_BK, w_row0, full_bar + 8 * i);
       }
       pdl_wait();
       const bool gather = tp.world > 1 && tp.ag_site >= 0;
@@ -123,7 +143,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!ok) atomicExch(status, (int)kTimeoutPeerFlag);
         fence_proxy_async_global();  // the rows were written with ordinary (peer) stores; TMA reads them
       }
-      auto load_x = [&](uint32_t dst, int kx, uint32_t bar) { tc::tma_load_2d(dst, &tmX, kx, xrow, bar); };
+      auto load_x = [&](uint32_t dst, int kx, uint32_t bar) {
+        tc::tma_load_2d(dst, &tmX, kx + x_col0, xrow + x_row0, bar);
+      };
       for (int i = 0; i < pre; ++i)
         load_x(base + i * S::STAGE_BYTES + S::W_BYTES, (kt_begin + i) * SK_BK, full_bar + 8 * i);
       int issued = pre;
@@ -134,7 +156,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         tc::mbar_expect_tx(full_bar + 8 * s, S::STAGE_BYTES);
         const uint32_t sa = base + s * S::STAGE_BYTES;
         const int kx = (kt_begin + i) * SK_BK;
-        tc::tma_load_2d(sa, &tmW, kx, n0, full_bar + 8 * s);
+        tc::tma_load_2d(sa, &tmW, kx, w_row0, full_bar + 8 * s);
         load_x(sa + S::W_BYTES, kx, full_bar + 8 * s);
         ++issued;
       }
@@ -212,6 +234,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const uint32_t rs_target = scatter ? tp_target(tp, tp.rs_site, tp.rs_sites) : 0u;
   const int rs_parity = (int)(rs_target & 1u);
   const int Mv = (scatter && !tp.oneshot) ? BT : (M < BT ? M : BT);
+  const size_t out_off = (size_t)grp_id * (size_t)grp.out_group_stride;
+  const float* rscale = grp.row_scale ? grp.row_scale + (size_t)grp_id * M : nullptr;
   if (EPI == SEPI_SWIGLU) {
     const int hp = slab >> 1;
     for (int idx = threadIdx.x; idx < hp * Mv; idx += SK_THREADS) {
@@ -226,7 +250,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
       const int n = n0 + rr;
       if (n < N)
-        reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * ldo + (n >> 1)] = __float2bfloat16(silu(g) * u);
+        reinterpret_cast<__nv_bfloat16*>(out)[out_off + (size_t)tok * ldo + (n >> 1)] = __float2bfloat16(silu(g) * u);
     }
   } else {
     for (int idx = threadIdx.x; idx < slab * Mv; idx += SK_THREADS) {
@@ -239,6 +263,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         v += ld_dsmem_f32(a);
       }
       const int n = n0 + rr;
+      if (rscale != nullptr) v *= rscale[tok];
       if (n < N) {
         if (scatter && tp.oneshot) {
           // one-shot all-reduce: this rank's partial goes to slot `rank` of every rank's inbox
@@ -251,10 +276,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           tp.inbox_peer[d][((size_t)((rs_parity * tp.world + tp.rank) * tp.S + tl)) * tp.ld_inbox + n] =
               __float2bfloat16(v);
         } else if (EPI == SEPI_F32) {
-          reinterpret_cast<float*>(out)[(size_t)tok * ldo + n] = v;
+          reinterpret_cast<float*>(out)[out_off + (size_t)tok * ldo + n] = v;
         } else {
-          if (EPI == SEPI_RESID) v += __bfloat162float(resid[(size_t)tok * ldo + n]);
-          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)tok * ldo + n] = __float2bfloat16(v);
+          if (EPI == SEPI_RESID) v += __bfloat162float(resid[out_off + (size_t)tok * ldo + n]);
+          reinterpret_cast<__nv_bfloat16*>(out)[out_off + (size_t)tok * ldo + n] = __float2bfloat16(v);
         }
       }
     }
@@ -265,7 +290,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
 template <int BT, int STAGES, int WM, int EPI>
 static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid, int M, int N,
-                             int K, int ldo, int CK, int pdl, int* status, cudaStream_t s, const TpArgs& tp) {
+                             int K, int ldo, int CK, int pdl, int* status, cudaStream_t s, const TpArgs& tp,
+                             const GroupArgs& grp, int groups) {
   using S = SkinnySmem<BT, STAGES, WM>;
   auto kern = gemm_skinny_kernel<BT, STAGES, WM, EPI>;
   static bool configured = false;
@@ -276,7 +302,7 @@ static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void*
   }
   const int row_tiles = (N + WM * SK_BM - 1) / (WM * SK_BM);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(row_tiles * CK, 1, 1);
+  cfg.gridDim = dim3(row_tiles * CK, groups, 1);
   cfg.blockDim = dim3(SK_THREADS, 1, 1);
   cfg.dynamicSmemBytes = S::TOTAL;
   cfg.stream = s;
@@ -294,29 +320,30 @@ static int launch_skinny_cfg(const CUtensorMap& tw, const CUtensorMap& tx, void*
   }
   cfg.attrs = attrs;
   cfg.numAttrs = na;
-  return (int)cudaLaunchKernelEx(&cfg, kern, tw, tx, out, (const __nv_bfloat16*)resid, M, N, K, ldo, CK, status, tp);
+  return (int)cudaLaunchKernelEx(&cfg, kern, tw, tx, out, (const __nv_bfloat16*)resid, M, N, K, ldo, CK, status, tp, grp);
 }
 
 template <int BT, int STAGES, int WM>
 static int launch_skinny_epi(int epi, const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid,
                              int M, int N, int K, int ldo, int CK, int pdl, int* status, cudaStream_t s,
-                             const TpArgs& tp) {
+                             const TpArgs& tp, const GroupArgs& grp, int groups) {
   switch (epi) {
-    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, WM, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp);
-    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, WM, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp);
-    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, WM, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp);
-    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, WM, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp);
+    case SEPI_STORE: return launch_skinny_cfg<BT, STAGES, WM, SEPI_STORE>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, grp, groups);
+    case SEPI_F32: return launch_skinny_cfg<BT, STAGES, WM, SEPI_F32>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, grp, groups);
+    case SEPI_RESID: return launch_skinny_cfg<BT, STAGES, WM, SEPI_RESID>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, grp, groups);
+    case SEPI_SWIGLU: return launch_skinny_cfg<BT, STAGES, WM, SEPI_SWIGLU>(tw, tx, out, resid, M, N, K, ldo, CK, pdl, status, s, tp, grp, groups);
     default: return (int)cudaErrorInvalidValue;
   }
 }
 
 static int skinny_dispatch(int epi, const CUtensorMap& tw, const CUtensorMap& tx, void* out, const void* resid, int M,
-                           int N, int K, int ldo, int ck, int bt, int pdl, int* status, cudaStream_t s, const TpArgs& tp) {
+                           int N, int K, int ldo, int ck, int bt, int pdl, int* status, cudaStream_t s, const TpArgs& tp,
+                           const GroupArgs& grp = GroupArgs{}, int groups = 1) {
   switch (bt) {
-    case 16: return launch_skinny_epi<16, 6, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp);
-    case 32: return launch_skinny_epi<32, 5, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp);
-    case 64: return launch_skinny_epi<64, 4, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp);
-    case 128: return launch_skinny_epi<128, 3, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp);
+    case 16: return launch_skinny_epi<16, 6, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, grp, groups);
+    case 32: return launch_skinny_epi<32, 5, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, grp, groups);
+    case 64: return launch_skinny_epi<64, 4, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, grp, groups);
+    case 128: return launch_skinny_epi<128, 3, 1>(epi, tw, tx, out, resid, M, N, K, ldo, ck, pdl, status, s, tp, grp, groups);
     default: return (int)cudaErrorInvalidValue;
   }
 }
@@ -387,4 +414,43 @@ POOT_API int poot_gemm_skinny_tp(int epi, const void* x, const void* W, void* ou
     tp.inbox_peer[r] = inbox_peer ? (__nv_bfloat16*)inbox_peer[r] : nullptr;
   }
   return skinny_dispatch(epi, tw, tx, out, nullptr, M, N, K, ldo, ck, bt, 0, status, s, tp);
+}
+
+// Grouped (mixture-of-experts) form over a stacked weight W [experts * N, K]: `groups` independent problems, group g
+// uses expert group_expert[g] (or g), X rows starting at g / x_row_div + g * x_row_mul, X columns starting at
+// expert * x_col_per_expert (X is [*, ldx]), and writes out + g * out_group_stride.  row_scale [groups, M] (optional)
+// multiplies each result row (the routing gate).  With tp_world > 1 and rs_site >= 0 the result goes to every rank's
+// inbox as a one-shot all-reduce contribution (expert parallelism: the combine is the reduction over experts).
+POOT_API int poot_gemm_skinny_grouped(int epi, const void* x, int x_rows, int x_cols, int ldx, const void* W,
+                                      int experts, void* out, int M, int N, int K, int ldo, int ck, int groups,
+                                      const int* group_expert, int x_row_div, int x_row_mul, int x_col_per_expert,
+                                      long long out_group_stride, const float* row_scale, int* status,
+                                      int tp_world, int tp_rank, int slot_rows, int rs_site, int rs_sites,
+                                      const int* epoch, void* flags_local, void* const* flags_peer,
+                                      void* const* inbox_peer, int ld_inbox, int* ticket, cudaStream_t s) {
+  if (M <= 0 || N <= 0 || groups <= 0) return 0;
+  if (M > 128 || K % 8 || ldx % 8) return (int)cudaErrorInvalidValue;
+  if (ck != 1 && ck != 2 && ck != 4 && ck != 8) return (int)cudaErrorInvalidValue;
+  if (status == nullptr) return (int)cudaErrorInvalidValue;
+  const int bt = M <= 16 ? 16 : (M <= 32 ? 32 : (M <= 64 ? 64 : 128));
+  CUtensorMap tw, tx;
+  int e = make_tmap_bf16_2d(&tw, W, (uint64_t)experts * (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)SK_BM);
+  if (e) return e;
+  e = make_tmap_bf16_2d(&tx, x, (uint64_t)x_rows, (uint64_t)x_cols, (uint64_t)ldx, (uint32_t)bt);
+  if (e) return e;
+  TpArgs tp = {};
+  tp.world = 1; tp.ag_site = -1; tp.rs_site = -1;
+  if (tp_world > 1 && rs_site >= 0) {
+    if (groups != 1 || epi != SEPI_STORE) return (int)cudaErrorInvalidValue;
+    tp.world = tp_world; tp.rank = tp_rank; tp.S = slot_rows; tp.oneshot = 1; tp.rs_site = rs_site; tp.rs_sites = rs_sites;
+    tp.ld_inbox = ld_inbox; tp.epoch = epoch; tp.flags_local = (uint32_t*)flags_local; tp.ticket = ticket;
+    for (int r = 0; r < tp_world; ++r) {
+      tp.flags_peer[r] = (uint32_t*)flags_peer[r];
+      tp.inbox_peer[r] = (__nv_bfloat16*)inbox_peer[r];
+    }
+  }
+  GroupArgs grp = {};
+  grp.group_expert = group_expert; grp.w_rows_per_expert = N; grp.x_row_div = x_row_div; grp.x_row_mul = x_row_mul;
+  grp.x_col_per_expert = x_col_per_expert; grp.out_group_stride = out_group_stride; grp.row_scale = row_scale;
+  return skinny_dispatch(epi, tw, tx, out, nullptr, M, N, K, ldo, ck, bt, 0, status, s, tp, grp, groups);
 }

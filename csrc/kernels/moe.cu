@@ -1,0 +1,101 @@
+// Mixture-of-experts routing and combine.
+//
+//  * moe_route: per token, canonical router scores (NaN / -inf -> f32::MIN, +inf -> f32::MAX), stable descending
+//    top-k (ties go to the lower expert index), gate weights by softmax over the selected k (Mixtral) or softmax over
+//    all experts without renormalisation; writes ids [T,k], gates [T,k] and the dense gate matrix [E,T] (0 for an
+//    unselected expert) that the grouped expert GEMM applies per row
+//    (crates/poot-graph-ir/src/ops/moe.rs:9-431, router kinds crates/poot-models/src/components/router.rs).
+//  * moe_combine: h[t] += sum over groups of the (already gate-scaled) expert outputs.
+#include "common.cuh"
+#include <float.h>
+
+namespace poot {
+
+constexpr int MOE_MAX_K = 8;
+
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int renorm,
+                                 int* __restrict__ ids, float* __restrict__ gates, float* __restrict__ dense) {
+  pdl_wait(); pdl_launch();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const float* lr = logits + (size_t)t * E;
+  int best[MOE_MAX_K];
+  float bv[MOE_MAX_K];
+  for (int j = 0; j < k; ++j) { best[j] = -1; bv[j] = -FLT_MAX; }
+  float all_max = -FLT_MAX;
+  for (int e = 0; e < E; ++e) {
+    float s = lr[e];
+    if (!(s >= -FLT_MAX)) s = -FLT_MAX;      // NaN and -inf
+    if (s > FLT_MAX) s = FLT_MAX;
+    all_max = fmaxf(all_max, s);
+    // insertion into the sorted top-k; strict '>' keeps the lower index first on ties
+    int pos = k;
+    for (int j = k - 1; j >= 0; --j) if (best[j] < 0 || s > bv[j]) pos = j;
+    if (pos < k) {
+      for (int j = k - 1; j > pos; --j) { best[j] = best[j - 1]; bv[j] = bv[j - 1]; }
+      best[pos] = e; bv[pos] = s;
+    }
+  }
+  float w[MOE_MAX_K], sum = 0.f;
+  if (renorm) {
+    for (int j = 0; j < k; ++j) { w[j] = expf(bv[j] - bv[0]); sum += w[j]; }
+  } else {
+    for (int e = 0; e < E; ++e) {
+      float s = lr[e];
+      if (!(s >= -FLT_MAX)) s = -FLT_MAX;
+      if (s > FLT_MAX) s = FLT_MAX;
+      sum += expf(s - all_max);
+    }
+    for (int j = 0; j < k; ++j) w[j] = expf(bv[j] - all_max);
+  }
+  for (int e = 0; e < E; ++e) dense[(size_t)e * T + t] = 0.f;
+  for (int j = 0; j < k; ++j) {
+    const float g = w[j] / sum;
+    ids[(size_t)t * k + j] = best[j];
+    gates[(size_t)t * k + j] = g;
+    if (best[j] >= 0) dense[(size_t)best[j] * T + t] = g;
+  }
+}
+
+// out[t, :] = (h ? h[t, :] : 0) + sum_{j < n} parts[(g0(t) + j) * gstride + row(t) * H + :]
+//   dense form (per_token == 0): g0 = 0, row = t, n = groups         parts [groups, T, H]
+//   slot form  (per_token  > 0): g0 = t * per_token, row = 0, n = per_token   parts [T * per_token, 1, H]
+__global__ void moe_combine_kernel(const __nv_bfloat16* h, const __nv_bfloat16* __restrict__ parts,
+                                   __nv_bfloat16* out, int T, int H, int groups, long long gstride, int per_token) {
+  pdl_wait(); pdl_launch();
+  const int t = blockIdx.x;
+  const int n = per_token > 0 ? per_token : groups;
+  const int g0 = per_token > 0 ? t * per_token : 0;
+  const size_t row_off = per_token > 0 ? 0 : (size_t)t * H;
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    float acc[8];
+    if (h != nullptr) unpack8(reinterpret_cast<const uint4*>(h + (size_t)t * H)[c], acc);
+    else { for (int i = 0; i < 8; ++i) acc[i] = 0.f; }
+    for (int j = 0; j < n; ++j) {
+      float f[8];
+      unpack8(reinterpret_cast<const uint4*>(parts + (size_t)(g0 + j) * gstride + row_off)[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    reinterpret_cast<uint4*>(out + (size_t)t * H)[c] = pack8(acc);
+  }
+}
+
+}  // namespace poot
+
+using namespace poot;
+
+POOT_API int poot_moe_route(const float* logits, int T, int E, int k, int renorm, int* ids, float* gates, float* dense,
+                            cudaStream_t s) {
+  if (T == 0) return 0;
+  if (k < 1 || k > MOE_MAX_K || k > E) return (int)cudaErrorInvalidValue;
+  return launch_k(moe_route_kernel, dim3((T + 63) / 64), dim3(64), 0, s, logits, T, E, k, renorm, ids, gates, dense);
+}
+
+POOT_API int poot_moe_combine(const void* h, const void* parts, void* out, int T, int H, int groups, long long gstride,
+                              int per_token, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (H % 8) return (int)cudaErrorInvalidValue;
+  return launch_k(moe_combine_kernel, dim3(T), dim3(256), 0, s, (const __nv_bfloat16*)h, (const __nv_bfloat16*)parts,
+                  (__nv_bfloat16*)out, T, H, groups, gstride, per_token);
+}

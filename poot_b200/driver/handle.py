@@ -1,0 +1,232 @@
+"""Model handle: checkpoint -> family, configuration, weight store -> device weights.
+
+``ModelHandle.load`` resolves the family from ``config.json`` (HF directory) or the GGUF header before any weight
+is read, maps the checkpoint tensor names to canonical roles, and keeps the stored tensors as zero-copy views of
+the mapped files (crates/poot-llm/src/driver/handle.rs:233; crates/poot-load/src/plan.rs:51-115).
+``device_weights`` uploads a rank's share in the layouts the kernels read: packed GGUF formats with a fused device
+GEMV stay packed (``QuantWeight``), every other stored format is expanded to bf16 once at load.
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import numpy as np
+
+from ..load import gguf, names, safetensors as st
+from ..models.config import DecoderConfig
+from ..models.model import Model
+from ..models.registry import Registry
+from ..quant import codec
+from ..quant.formats import FORMATS
+from ..quant.weights import PackedWeight, WeightStore
+
+
+@dataclass
+class ModelHandle:
+    model: Model
+    store: WeightStore
+    canonical: Dict[str, PackedWeight]     # canonical role name -> stored tensor
+    source: str
+    kind: str                              # "hf" | "gguf"
+    tokenizer_dir: Optional[str] = None
+
+    @property
+    def cfg(self) -> DecoderConfig:
+        return self.model.cfg
+
+    @staticmethod
+    def load(path: str, registry: Optional[Registry] = None) -> "ModelHandle":
+        registry = registry or Registry.builtin()
+        if os.path.isdir(path):
+            with open(os.path.join(path, "config.json")) as f:
+                model = registry.resolve_hf(json.load(f))
+            store = st.load_weight_store(path)
+            canon = {}
+            for n in store.names():
+                c = names.canonical_from_hf(n)
+                if c is not None:
+                    canon[c] = store[n]
+            return ModelHandle(model, store, canon, path, "hf", path)
+        store = gguf.read_gguf(path)
+        arch = store.metadata.get("general.architecture")
+        model = registry.resolve_gguf(arch, store.metadata)
+        canon = {}
+        for n in store.names():
+            c = names.canonical_from_gguf(n)
+            if c is None:
+                continue
+            w = store[n]
+            if arch == "llama" and c.endswith(("attn_q", "attn_k")) and len(w.shape) == 2:
+                heads = model.cfg.n_heads if c.endswith("attn_q") else model.cfg.n_kv_heads
+                w = _permute_rows(w, names.gguf_qk_row_order(w.shape[0], heads))
+            canon[c] = w
+        if "lm_head" not in canon and "embed" in canon:
+            model.cfg.tie_embeddings = True
+        return ModelHandle(model, store, canon, path, "gguf", None)
+
+    def f32(self, name: str) -> np.ndarray:
+        return self.canonical[name].to_f32()
+
+    def oracle_weights(self) -> Dict[str, np.ndarray]:
+        """Every canonical weight decoded to f32 in the tracer's layout (experts stacked gate-then-up)."""
+        c = self.cfg
+        out = {}
+        for n, w in self.canonical.items():
+            if ".experts." not in n:
+                out[n] = w.to_f32()
+        if c.is_moe:
+            for l in range(c.n_layers):
+                p = f"layers.{l}."
+                gi = np.stack([np.concatenate([self.f32(p + f"experts.{e}.gate"), self.f32(p + f"experts.{e}.up")], 0)
+                               for e in range(c.n_experts)])
+                out[p + "experts_in"] = gi
+                out[p + "experts_out"] = np.stack([self.f32(p + f"experts.{e}.down") for e in range(c.n_experts)])
+        return out
+
+
+def _permute_rows(w: PackedWeight, order: np.ndarray) -> PackedWeight:
+    d = FORMATS[w.format]
+    row_bytes = w.shape[-1] // d.block_elems * d.block_bytes
+    raw = np.ascontiguousarray(w.payload).view(np.uint8).reshape(w.shape[0], row_bytes)
+    return PackedWeight(w.name, w.format, w.shape, np.ascontiguousarray(raw[order]).reshape(-1))
+
+
+# ---- device upload ---------------------------------------------------------------------------------------------
+def _rows(w: PackedWeight, start: int, count: int) -> PackedWeight:
+    return w.rows(start, count) if FORMATS[w.format].storage != "planar" else w
+
+
+def _cat_rows(parts) -> PackedWeight:
+    fmt = parts[0].format
+    if any(p.format != fmt for p in parts):
+        raise ValueError("fused projection mixes storage formats")
+    n = sum(p.shape[0] for p in parts)
+    return PackedWeight("+".join(p.name for p in parts), fmt, (n, parts[0].shape[1]),
+                        np.concatenate([np.ascontiguousarray(p.payload).view(np.uint8).reshape(-1) for p in parts]))
+
+
+def _interleave_rows(a: PackedWeight, b: PackedWeight) -> PackedWeight:
+    d = FORMATS[a.format]
+    rb = a.shape[1] // d.block_elems * d.block_bytes
+    ra = np.ascontiguousarray(a.payload).view(np.uint8).reshape(a.shape[0], rb)
+    rbb = np.ascontiguousarray(b.payload).view(np.uint8).reshape(b.shape[0], rb)
+    return PackedWeight(a.name + "|" + b.name, a.format, (2 * a.shape[0], a.shape[1]),
+                        np.stack([ra, rbb], 1).reshape(-1))
+
+
+def to_device(w: PackedWeight, device, keep_packed: bool = True):
+    """bf16 tensor, or a ``QuantWeight`` when the format has fused device kernels."""
+    import torch
+    from ..ops import cuda_ops as K
+    d = FORMATS[w.format]
+    if keep_packed and d.device_gemv and len(w.shape) == 2 and w.shape[1] % 256 == 0:
+        raw = torch.from_numpy(np.ascontiguousarray(w.payload).view(np.uint8).reshape(-1).copy())
+        return K.QuantWeight(w.format, raw.to(device), w.shape[0], w.shape[1])
+    if w.format == "BF16":
+        t = torch.from_numpy(np.ascontiguousarray(w.payload).view(np.uint16).reshape(w.shape).copy()).view(torch.bfloat16)
+        return t.to(device)
+    return torch.from_numpy(w.to_f32()).to(device=device, dtype=torch.bfloat16)
+
+
+def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int = 1, keep_packed: bool = True):
+    """Rank-local ``DecoderWeights``: fused QKV, interleaved gate/up, Megatron shares."""
+    import torch
+    from ..runtime.weights import DecoderWeights, LayerWeights
+    c, canon = handle.cfg, handle.canonical
+    D = c.head_dim
+    hq, hkv = c.n_heads // tp_world, max(c.n_kv_heads // tp_world, 1)
+    k0 = tp_rank * hkv if c.n_kv_heads >= tp_world else tp_rank * c.n_kv_heads // tp_world
+
+    def dense(name):
+        return torch.from_numpy(canon[name].to_f32()).to(device=device, dtype=torch.bfloat16)
+
+    layers = []
+    for l in range(c.n_layers):
+        p = f"layers.{l}."
+        q, k, v = canon[p + "attn_q"], canon[p + "attn_k"], canon[p + "attn_v"]
+        if len({q.format, k.format, v.format}) == 1 and FORMATS[q.format].storage != "planar":
+            wqkv = to_device(_cat_rows([_rows(q, tp_rank * hq * D, hq * D), _rows(k, k0 * D, hkv * D),
+                                        _rows(v, k0 * D, hkv * D)]), device, keep_packed)
+        else:   # mixed formats (e.g. Q4_K_M keeps V in Q6_K): expand to bf16
+            wqkv = torch.cat([torch.from_numpy(_rows(x, s, n).to_f32()) for x, s, n in
+                              ((q, tp_rank * hq * D, hq * D), (k, k0 * D, hkv * D), (v, k0 * D, hkv * D))]
+                             ).to(device=device, dtype=torch.bfloat16)
+        o = canon[p + "attn_o"]
+        n_in = o.shape[1] // tp_world
+        wo = to_device(o.cols(tp_rank * n_in, n_in) if tp_world > 1 else o, device, keep_packed)
+        L = LayerWeights(ln1=dense(p + "attn_norm"), ln2=dense(p + "ffn_norm"), wqkv=wqkv, wo=wo)
+        if c.qk_norm:
+            L.q_norm, L.k_norm = dense(p + "attn_q_norm"), dense(p + "attn_k_norm")
+        if c.is_moe:
+            L.router = dense(p + "ffn_router")
+            gus, downs = [], []
+            for e in range(c.n_experts):
+                g, u = handle.f32(p + f"experts.{e}.gate"), handle.f32(p + f"experts.{e}.up")
+                gus.append(torch.from_numpy(np.stack([g, u], 1).reshape(2 * g.shape[0], -1)))
+                downs.append(torch.from_numpy(handle.f32(p + f"experts.{e}.down")))
+            L.ex_wgu = torch.stack(gus).to(device=device, dtype=torch.bfloat16)
+            L.ex_wdown = torch.stack(downs).to(device=device, dtype=torch.bfloat16)
+        else:
+            g, u, dn = canon[p + "ffn_gate"], canon[p + "ffn_up"], canon[p + "ffn_down"]
+            F = g.shape[0] // tp_world
+            if g.format == u.format and FORMATS[g.format].storage != "planar":
+                L.wgu = to_device(_interleave_rows(_rows(g, tp_rank * F, F), _rows(u, tp_rank * F, F)), device, keep_packed)
+            else:
+                gf, uf = _rows(g, tp_rank * F, F).to_f32(), _rows(u, tp_rank * F, F).to_f32()
+                L.wgu = torch.from_numpy(np.stack([gf, uf], 1).reshape(2 * F, -1)).to(device=device, dtype=torch.bfloat16)
+            L.wdown = to_device(dn.cols(tp_rank * F, F) if tp_world > 1 else dn, device, keep_packed)
+        layers.append(L)
+    embed = to_device(canon["embed"], device, keep_packed)
+    head = canon.get("lm_head")
+    if c.tie_embeddings or head is None:
+        lm_head = embed
+    else:
+        vl = head.shape[0] // tp_world
+        lm_head = to_device(_rows(head, tp_rank * vl, vl) if tp_world > 1 else head, device, keep_packed)
+    return DecoderWeights(cfg=c, embed=embed, final_norm=dense("final_norm"), lm_head=lm_head, layers=layers,
+                          tp_rank=tp_rank, tp_world=tp_world)
+
+
+def write_random_gguf(path: str, cfg: DecoderConfig, proj_format: str = "Q4_K", embed_format: str = "Q8_0",
+                      seed: int = 0, std: float = 0.02) -> None:
+    """A synthetic GGUF checkpoint of ``cfg`` quantised from random N(0, std) weights (projections in
+    ``proj_format``, token embeddings in ``embed_format``, norms in F32) - the benchmark's stand-in for a download."""
+    rng = np.random.default_rng(seed)
+    arch = "llama"
+    meta = {"general.architecture": arch, "general.name": cfg.name, f"{arch}.block_count": cfg.n_layers,
+            f"{arch}.embedding_length": cfg.hidden, f"{arch}.attention.head_count": cfg.n_heads,
+            f"{arch}.attention.head_count_kv": cfg.n_kv_heads, f"{arch}.feed_forward_length": cfg.ffn,
+            f"{arch}.rope.freq_base": float(cfg.rope_theta), f"{arch}.attention.layer_norm_rms_epsilon": float(cfg.norm_eps),
+            f"{arch}.context_length": cfg.max_position, f"{arch}.vocab_size": cfg.vocab,
+            f"{arch}.attention.key_length": cfg.head_dim, "tokenizer.ggml.bos_token_id": cfg.bos_token,
+            "tokenizer.ggml.eos_token_id": cfg.eos_token}
+    tensors = []
+
+    def add(name, shape, fmt, permute_heads=0):
+        w = (rng.standard_normal(shape) * std).astype(np.float32)
+        if permute_heads:
+            w = w[names.hf_to_gguf_qk_row_order(shape[0], permute_heads)]
+        if fmt == "F32":
+            tensors.append(PackedWeight(name, "F32", shape, w.view(np.uint8).reshape(-1)))
+        else:
+            tensors.append(PackedWeight(name, fmt, shape, codec.quantize(fmt, w)))
+
+    H = cfg.hidden
+    add("token_embd.weight", (cfg.vocab, H), embed_format)
+    for l in range(cfg.n_layers):
+        b = f"blk.{l}."
+        tensors.append(PackedWeight(b + "attn_norm.weight", "F32", (H,), np.ones(H, np.float32).view(np.uint8)))
+        tensors.append(PackedWeight(b + "ffn_norm.weight", "F32", (H,), np.ones(H, np.float32).view(np.uint8)))
+        add(b + "attn_q.weight", (cfg.q_size, H), proj_format, cfg.n_heads)
+        add(b + "attn_k.weight", (cfg.kv_size, H), proj_format, cfg.n_kv_heads)
+        add(b + "attn_v.weight", (cfg.kv_size, H), proj_format)
+        add(b + "attn_output.weight", (H, cfg.q_size), proj_format)
+        add(b + "ffn_gate.weight", (cfg.ffn, H), proj_format)
+        add(b + "ffn_up.weight", (cfg.ffn, H), proj_format)
+        add(b + "ffn_down.weight", (H, cfg.ffn), proj_format)
+    tensors.append(PackedWeight("output_norm.weight", "F32", (H,), np.ones(H, np.float32).view(np.uint8)))
+    add("output.weight", (cfg.vocab, H), proj_format)
+    gguf.write_gguf(path, meta, tensors)

@@ -146,10 +146,10 @@ class DecoderEngine:
         """
         h = self.h[:T]
         N, Kdim = W.shape
-        if T <= 128:
+        if T <= 128 or isinstance(W, K.QuantWeight):
             self._linear(x, W, K.EPI_RESID, h, h)
             return None
-        tiles = ((T + 127) // 128) * ((N + 63) // 64)
+        tiles =((T + 127) // 128) * ((N + 63) // 64)
         if tiles < 100 and Kdim >= 1024 and T <= self.small_T:
             splits = max(1, min(self.max_splits, 148 // tiles, Kdim // 512))
             if splits > 1:
@@ -179,16 +179,22 @@ class DecoderEngine:
         """Launch the whole step on the current stream (eagerly or under capture)."""
         cfg, w = self.cfg, self.w
         T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
-        if self.comm is not None and getattr(self.comm, "fused", False):
-            if self.comm.oneshot_ok(T) and self.tp_mode != "rs_ag":
+        packed = isinstance(w.layers[0].wqkv, K.QuantWeight) or isinstance(w.layers[0].wo, K.QuantWeight)
+        # expert parallelism with one expert per rank rides the one-shot path (the combine is the fused all-reduce)
+        moe_fusable = cfg.is_moe and w.ep_world == self.tp and w.layers[0].ex_wgu.shape[0] == 1
+        if self.comm is not None and getattr(self.comm, "fused", False) and not packed and (not cfg.is_moe or moe_fusable):
+            if self.comm.oneshot_ok(T) and (self.tp_mode != "rs_ag" or cfg.is_moe):
                 return self._forward_tp_oneshot(shape)
             R = self.comm.rows_for(T)
-            if R:
+            if R and not cfg.is_moe:
                 return self._forward_tp_fused(shape, R)
         self._launch_counter = 0
         h = self.h[:T]
         self._count()
-        K.embed_gather(self.tokens[:T], w.embed, out=h)
+        if isinstance(w.embed, K.QuantWeight):
+            K.quant_row_gather(self.tokens[:T], w.embed, out=h)
+        else:
+            K.embed_gather(self.tokens[:T], w.embed, out=h)
         pending = None
         for l, L in enumerate(w.layers):
             x = self._norm(L.ln1, T, pending)
@@ -312,9 +318,13 @@ class DecoderEngine:
             rs += 1
             comm.gemm_allreduce(self.attn[:T], L.wo, T, rs_site=rs)
             comm.norm_oneshot(h, L.ln2, x, T, cfg.norm_eps, rs_site=rs)
-            K.linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
             rs += 1
-            comm.gemm_allreduce(self.act[:T], L.wdown, T, rs_site=rs)
+            if cfg.is_moe:
+                from . import moe as _moe
+                _moe.moe_forward(self, l, L, x, T, ep=("fused", comm, rs))
+            else:
+                K.linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
+                comm.gemm_allreduce(self.act[:T], L.wdown, T, rs_site=rs)
         if B == T:
             self._count()
             comm.norm_oneshot(h, w.final_norm, self.xl[:B], T, cfg.norm_eps, rs_site=rs)
@@ -371,7 +381,9 @@ class DecoderEngine:
 
     def _moe(self, l, L, x, T):
         from . import moe as _moe
-        return _moe.moe_forward(self, l, L, x, T)
+        ep = ("nccl", self.comm) if (self.comm is not None and self.w.ep_world > 1) else None
+        _moe.moe_forward(self, l, L, x, T, ep)
+        return None
 
     # ------------------------------------------------------------------ capture / replay
     def _key(self, shape: StepShape):

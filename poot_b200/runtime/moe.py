@@ -1,0 +1,95 @@
+"""Mixture-of-experts FFN on the device engine (Mixtral / Qwen3-MoE / OLMoE style routed experts).
+
+Two regimes, both on the grouped swap-AB tcgen05 kernel over the stacked expert weights:
+
+* few (token, slot) pairs (``T * k <= E``, e.g. batch-1 decode): one group per pair reads only the experts that
+  were selected (the reference's indexed GEMV, crates/poot-kernelgen/src/contraction/indexed.rs:1-6);
+* otherwise: one group per expert runs all T tokens; the dense gate matrix (0 for an unselected expert) scales the
+  rows of the down projection, and the combine kernel adds the E outputs to the residual stream - every expert
+  weight is read exactly once per step (the reference groups rows by expert, passes/group_expert_rows.rs:1-8).
+
+Expert parallelism (one expert shard per rank, attention tensor-parallel): activations are replicated after the
+fused all-reduce, so no dispatch transfer is needed; each rank runs its local experts over all tokens and the
+gate-scaled down projection is written straight into every rank's inbox - the combine all-to-all is the one-shot
+all-reduce fused into the expert GEMM's epilogue.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import cuda_ops as K
+from ..ops import moe_ops as M
+
+
+def _buffers(eng):
+    if getattr(eng, "_moe_buf", None) is None:
+        c, dev = eng.cfg, eng.device
+        T, E, k = eng.max_tokens, c.n_experts, c.top_k
+        e_local = eng.w.layers[0].ex_wgu.shape[0]
+        F, H = c.moe_ffn, c.hidden
+        Tc = min(T, 128)
+        G = max(e_local, min(T, E) * k)
+        eng._moe_buf = {
+            "logits": torch.zeros(T, E, dtype=torch.float32, device=dev),
+            "ids": torch.zeros(T * k, dtype=torch.int32, device=dev),
+            "gates": torch.zeros(T * k, dtype=torch.float32, device=dev),
+            "dense": torch.zeros(E * T, dtype=torch.float32, device=dev),
+            "act": torch.zeros(G * Tc * F, dtype=torch.bfloat16, device=dev),
+            "parts": torch.zeros(G * Tc * H, dtype=torch.bfloat16, device=dev),
+        }
+    return eng._moe_buf
+
+
+def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
+    """``h[:T] += moe(x)``.  ``ep`` selects the expert-parallel form: ``("nccl", comm)`` reduces the local experts'
+    partial with a library all-reduce, ``("fused", comm, rs_site)`` pushes it into every rank's inbox from the GEMM
+    epilogue (returns ``"pushed"``: the caller's next reduce+norm kernel consumes it)."""
+    c = eng.cfg
+    E, k, F, H = c.n_experts, c.top_k, c.moe_ffn, c.hidden
+    buf = _buffers(eng)
+    e_local = L.ex_wgu.shape[0]
+    e0 = eng.w.ep_rank * e_local
+    logits = buf["logits"][:T]
+    eng._count(2)
+    K.linear(x, L.router, K.EPI_F32, logits)
+    ids, gates = buf["ids"][:T * k], buf["gates"][:T * k]
+    dense = buf["dense"][:E * T].view(E, T)
+    M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense)
+    h = eng.h[:T]
+    tp = (ep[1], ep[2]) if (ep is not None and ep[0] == "fused") else None
+    if ep is None and e_local == E and T * k <= E:
+        G = T * k                                             # one group per (token, slot)
+        act = buf["act"][:G * F].view(G, F)
+        parts = buf["parts"][:G * H].view(G, H)
+        eng._count(3)
+        M.gemm_grouped(K.EPI_SWIGLU, x, L.ex_wgu, act, 1, G, group_expert=ids, x_row_div=k, out_group_stride=F, ldo=F)
+        M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, parts, 1, G, group_expert=ids, x_row_mul=1, out_group_stride=H,
+                       row_scale=gates, ldo=H)
+        M.moe_combine(h, parts, h, T, H, G, H, per_token=k)
+        return None
+    # dense-over-experts regime, in token chunks of at most 128 rows
+    for t0 in range(0, T, 128):
+        n = min(128, T - t0)
+        xs = x[t0:t0 + n]
+        act = buf["act"][:e_local * n * F].view(e_local * n, F)
+        scale = dense[e0:e0 + e_local, t0:t0 + n].contiguous() if (t0 or n != T or e_local != E) else dense
+        eng._count(2)
+        M.gemm_grouped(K.EPI_SWIGLU, xs, L.ex_wgu, act, n, e_local, out_group_stride=n * F, ldo=F)
+        if tp is not None and e_local == 1 and T <= 128:
+            M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, None, n, 1, x_row_mul=n, row_scale=scale, ldo=H, tp=tp)
+            return "pushed"
+        parts = buf["parts"][:e_local * n * H].view(e_local * n, H)
+        M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, parts, n, e_local, x_row_mul=n, out_group_stride=n * H,
+                       row_scale=scale, ldo=H)
+        eng._count()
+        if ep is None:
+            M.moe_combine(h[t0:t0 + n], parts, h[t0:t0 + n], n, H, e_local, n * H)
+        else:
+            M.moe_combine(None, parts, eng.comm.partial[t0:t0 + n], n, H, e_local, n * H)
+    if ep is not None:      # library all-reduce over the ranks' expert partials, then the residual add
+        import torch.distributed as dist
+        p = eng.comm.partial[:T]
+        dist.all_reduce(p, group=eng.comm.group)
+        eng._count()
+        K.add(h, p, out=h)
+    return None

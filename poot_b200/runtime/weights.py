@@ -45,6 +45,8 @@ class DecoderWeights:
     layers: List[LayerWeights]
     tp_rank: int = 0
     tp_world: int = 1
+    ep_rank: int = 0        # expert-parallel share: this rank holds experts [ep_rank * E/ep_world, ...)
+    ep_world: int = 1
     quant: Dict[str, object] = field(default_factory=dict)
 
     def nbytes(self) -> int:
@@ -150,7 +152,7 @@ def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02,
     if tp_world > 1:
         lm_head = shard_rows(lm_head, tp_rank, tp_world)  # vocabulary-parallel head
     return DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H), lm_head=lm_head, layers=layers, tp_rank=tp_rank,
-                          tp_world=tp_world)
+                          tp_world=tp_world, ep_rank=ep_rank, ep_world=ep_world)
 
 
 def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], device, tp_rank: int = 0,

@@ -12,8 +12,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _run(kind, world, batch, port):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_TEST_BATCH=str(batch))
+def _run(kind, world, batch, port, moe=False):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TP_TEST_BATCH=str(batch), TP_TEST_MOE="1" if moe else "0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "tp_worker.py"), kind]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
@@ -34,3 +34,12 @@ def test_tp_all_gpus_matches_single_gpu(kind):
     if world == 2:
         pytest.skip("covered by the 2-GPU test")
     _run(kind, world, 7, 29543)
+
+
+@pytest.mark.parametrize("kind", ["nccl", "fused"])
+def test_expert_parallel_matches_single_gpu(kind):
+    """One expert per rank, attention tensor-parallel; the fused form pushes the gate-scaled expert output into every
+    rank's inbox from the GEMM epilogue."""
+    n = torch.cuda.device_count()
+    world = 8 if n >= 8 else (4 if n >= 4 else 2)
+    _run(kind, world, 6, 29545, moe=True)

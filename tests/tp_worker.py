@@ -30,6 +30,9 @@ def main():
     K.set_pdl(True)
     cfg = DecoderConfig(n_layers=3, hidden=512, n_heads=8, n_kv_heads=8 if world > 4 else 4, head_dim=64, ffn=1024,
                         vocab=4096, max_position=256)
+    moe = os.environ.get("TP_TEST_MOE") == "1"
+    if moe:   # expert parallel: one expert per rank, attention tensor-parallel
+        cfg.family, cfg.n_experts, cfg.top_k, cfg.moe_ffn = "mixtral", world, 2, 768
     B, P, steps = int(os.environ.get("TP_TEST_BATCH", "5")), 12, 6
     max_len, bps = 64, 4
     g = torch.Generator().manual_seed(0)
@@ -55,7 +58,8 @@ def main():
 
     ref_tokens, ref_logits = run(random_weights(cfg, dev, seed=3, std=0.05), None)
     comm = make_comm("fused" if kind == "fused_rsag" else kind, rank, world, dev)
-    tp_tokens, tp_logits = run(random_weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_world=world), comm,
+    tp_tokens, tp_logits = run(random_weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_world=world,
+                                              ep_rank=rank if moe else 0, ep_world=world if moe else 1), comm,
                                forced=ref_tokens)
     vl = cfg.vocab // world
     worst = 0.0
