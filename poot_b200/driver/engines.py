@@ -16,7 +16,8 @@ from .driver import StepInputs
 
 
 class FakeStepEngine:
-    """Next token = (last fed token of the row + 1) mod vocab; records the steps it was asked to run."""
+    """Next token = (last fed token of the row + 1) mod vocab (moved to the next token a guided mask allows);
+    records the steps it was asked to run."""
 
     def __init__(self, vocab: int = 1000, max_tokens: int = 256, fail_at_step: Optional[int] = None):
         self.vocab, self.max_tokens = vocab, max_tokens
@@ -35,7 +36,13 @@ class FakeStepEngine:
         picked = np.zeros((B, 2), np.int32)
         picked[:, 1] = -1
         for b in range(inp.live_rows):
-            picked[b, 0] = (int(inp.tokens[inp.logit_idx[b]]) + 1) % self.vocab
+            tok = (int(inp.tokens[inp.logit_idx[b]]) + 1) % self.vocab
+            mask = (inp.adjust or {}).get("guided", {}).get(b) if inp.adjust else None
+            if mask is not None:      # a guided row: the first allowed token at or after the candidate, cyclically
+                ok = np.flatnonzero(np.asarray(mask) == 0.0)
+                later = ok[ok >= tok]
+                tok = int(later[0] if len(later) else ok[0])
+            picked[b, 0] = tok
         return picked, (np.zeros(B, np.float32) if inp.want_logprobs else None)
 
 

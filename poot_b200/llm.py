@@ -1,0 +1,126 @@
+"""The call a user makes: load a checkpoint (or a random-init preset), get a driver, a tokenizer and ``generate``.
+
+Mirrors the reference's ``ModelHandle`` -> ``Driver`` pairing (crates/poot-llm/src/driver/handle.rs:233,
+crates/poot-llm/src/driver/run.rs:136-248): the handle resolves the family and weights, the driver owns rows,
+paged K/V and the prefix cache, and a step engine runs the device program.  KV capacity is sized from the device
+memory left after the weights are resident.
+"""
+from __future__ import annotations
+
+import os
+from typing import Iterable, List, Optional
+
+from .driver.driver import Driver
+from .driver.kvcache import BLOCK, blocks_for
+from .driver.sampler import SamplingParams
+from .models.config import DecoderConfig, PRESETS
+from .text.codec import ByteTokenizer, GgufTokenizer, HfTokenizer, StreamDecoder
+
+
+def _tokenizer_for(handle):
+    if handle is None:
+        return None
+    if handle.kind == "hf":
+        p = os.path.join(handle.source, "tokenizer.json")
+        if os.path.exists(p):
+            return HfTokenizer(p)
+    elif "tokenizer.ggml.tokens" in handle.store.metadata:
+        return GgufTokenizer(handle.store.metadata)
+    return None
+
+
+class LLM:
+    """A resident model with its serving driver."""
+
+    def __init__(self, cfg: DecoderConfig, driver: Driver, tokenizer, engine=None, handle=None, comm=None):
+        self.cfg, self.driver, self.tokenizer, self.engine, self.handle, self.comm = cfg, driver, tokenizer, engine, handle, comm
+
+    # ---- construction --------------------------------------------------------------------------------------------
+    @staticmethod
+    def _assemble(cfg, weights, tokenizer, rows, max_seq, prefill_chunk, kv_fraction, comm, handle, num_blocks=None,
+                  prefix_caching=True):
+        import torch
+        from .driver.engines import DeviceStepEngine
+        from .runtime.engine import DecoderEngine, KVPool
+        dev = weights.embed.device if hasattr(weights.embed, "device") else torch.device("cuda")
+        max_seq = min(max_seq, cfg.max_position)
+        if num_blocks is None:
+            free, _ = torch.cuda.mem_get_info(dev)
+            per_block = KVPool.bytes_per_block(cfg, weights.tp_world)
+            budget = int(free * kv_fraction) - (2 << 30)       # activations, logits, graphs
+            num_blocks = max(min(budget // per_block, rows * blocks_for(max_seq)), blocks_for(max_seq) + 1)
+        max_tokens = max(prefill_chunk, rows) + rows            # widest prefill piece + one decode row per sequence
+        eng = DecoderEngine(weights, num_blocks, rows, max_tokens, blocks_for(max_seq), comm=comm)
+        tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
+        eos = getattr(tokenizer, "eos", None)
+        drv = Driver(DeviceStepEngine(eng), num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
+                     prefix_caching=prefix_caching, eos_token=eos if eos is not None else cfg.eos_token)
+        return LLM(cfg, drv, tokenizer, eng, handle, comm)
+
+    @staticmethod
+    def load(path: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
+             kv_fraction: float = 0.85, keep_packed: bool = True, tp_rank: int = 0, tp_world: int = 1, comm=None,
+             num_blocks: Optional[int] = None) -> "LLM":
+        """``path``: a Hugging Face directory (config.json + safetensors) or a ``.gguf`` file."""
+        from .driver.handle import ModelHandle, device_weights
+        handle = ModelHandle.load(path)
+        weights = device_weights(handle, device, tp_rank, tp_world, keep_packed)
+        return LLM._assemble(handle.cfg, weights, _tokenizer_for(handle), rows, max_seq, prefill_chunk, kv_fraction,
+                             comm, handle, num_blocks)
+
+    @staticmethod
+    def random(preset: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
+               kv_fraction: float = 0.85, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, comm=None,
+               num_blocks: Optional[int] = None, **over) -> "LLM":
+        """Random-init weights of a named architecture (benchmarks and tests: no checkpoint on disk)."""
+        from .runtime.weights import random_weights
+        import dataclasses
+        cfg = dataclasses.replace(PRESETS[preset](), **over)
+        weights = random_weights(cfg, device, seed=seed, tp_rank=tp_rank, tp_world=tp_world)
+        return LLM._assemble(cfg, weights, None, rows, max_seq, prefill_chunk, kv_fraction, comm, None, num_blocks)
+
+    @staticmethod
+    def fake(vocab: int = 1000, rows: int = 8, max_seq: int = 512, num_blocks: int = 256, prefill_chunk: int = 64,
+             fail_at_step: Optional[int] = None) -> "LLM":
+        """A driver over the deterministic host engine (next token = last + 1): serving logic without a device."""
+        from .driver.engines import FakeStepEngine
+        tk = ByteTokenizer(vocab)
+        drv = Driver(FakeStepEngine(vocab, prefill_chunk + rows, fail_at_step), num_blocks, rows, max_seq, vocab,
+                     prefill_chunk=prefill_chunk, eos_token=tk.eos)
+        return LLM(None, drv, tk)
+
+    # ---- generation ----------------------------------------------------------------------------------------------
+    def generate_tokens(self, prompt: Iterable[int], params: Optional[SamplingParams] = None, on_token=None) -> List[int]:
+        return self.driver.generate(list(prompt), params, on_token)
+
+    def generate(self, prompt: str, params: Optional[SamplingParams] = None, on_text=None) -> str:
+        dec = StreamDecoder(self.tokenizer)
+        out: List[str] = []
+
+        def tok(t):
+            if t == self.driver.eos_token:
+                return
+            piece = dec.push(t)
+            if piece:
+                out.append(piece)
+                if on_text is not None:
+                    on_text(piece)
+
+        self.driver.generate(self.tokenizer.encode(prompt), params, tok)
+        tail = dec.flush()
+        if tail:
+            out.append(tail)
+            if on_text is not None:
+                on_text(tail)
+        return "".join(out)
+
+    def chat(self, messages: List[dict], params: Optional[SamplingParams] = None, template: Optional[str] = None,
+             on_text=None) -> str:
+        from .text.chat import render_chat
+        family = self.cfg.family if self.cfg is not None else "llama"
+        text = render_chat(messages, template, family, True)
+        return self.generate(text, params, on_text)
+
+    def close(self) -> None:
+        if self.comm is not None:
+            self.comm.close()

@@ -1,0 +1,74 @@
+"""``python -m poot_b200.serve MODEL [HOST:PORT] [--rows N] [--max-seq N] [--placement tensor:0,1,..] ...``
+
+Single placement runs in this process.  A ``tensor:`` placement is launched one process per GPU
+(``python -m torch.distributed.run --nproc-per-node N -m poot_b200.serve ...``): rank 0 owns the HTTP server, the
+scheduler and the driver; the other ranks follow the step inputs it broadcasts (website/docs/serve/tensor-parallelism.md).
+"""
+from __future__ import annotations
+
+import os
+import signal
+import sys
+import threading
+
+from .config import parse_args
+from .http import Server, ServerState
+from .metrics import Metrics
+from .scheduler import ServeEngine
+
+
+def main(argv=None) -> int:
+    try:
+        cfg = parse_args(list(sys.argv[1:] if argv is None else argv))
+    except ValueError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    from ..llm import LLM
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    comm = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
+        dist.init_process_group("nccl")
+        from ..parallel.tp import make_comm
+        comm = make_comm("fused", rank, world)
+    if cfg.model == "fake":
+        llm = LLM.fake(rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk)
+    elif cfg.model.startswith("random:"):
+        llm = LLM.random(cfg.model.split(":", 1)[1], rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
+                         kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm)
+    else:
+        llm = LLM.load(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
+                       kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm)
+    if world > 1:
+        from .follower import follow, LeaderStepEngine
+        if rank != 0:
+            follow(llm.driver.engine)
+            return 0
+        llm.driver.engine = LeaderStepEngine(llm.driver.engine)
+    template = cfg.chat_template
+    if cfg.chat_template_file:
+        with open(cfg.chat_template_file) as f:
+            template = f.read()
+    engine = ServeEngine(llm.driver, llm.tokenizer, Metrics(), cfg.max_pending_requests, cfg.max_queue_wait_secs)
+    state = ServerState(engine, cfg, cfg.model_id or os.path.basename(cfg.model.rstrip("/")) or "model",
+                        family=llm.cfg.family if llm.cfg is not None else "llama", chat_template=template)
+    server = Server(state)
+    engine.start()
+    server.start()
+    print(f"poot-b200 serving {state.model_id} on http://{cfg.addr} (rows={cfg.rows}, max_seq={cfg.max_seq})", flush=True)
+    stop = threading.Event()
+    for sig in (signal.SIGINT, signal.SIGTERM):
+        signal.signal(sig, lambda *_: stop.set())
+    stop.wait()
+    server.shutdown()
+    if world > 1:
+        llm.driver.engine.stop_followers()
+    llm.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

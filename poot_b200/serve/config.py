@@ -1,0 +1,97 @@
+"""Serve configuration: typed, strictly parsed flags (an unknown option, an unparsable or out-of-bound value stops
+start-up) - the flag set of the reference server (website/docs/serve/configuration.md:11-84;
+crates/poot-serve/src/config.rs:87-484).  Execution choices are configuration, never environment variables.
+"""
+from __future__ import annotations
+
+import argparse
+from dataclasses import dataclass, field
+from typing import List, Optional
+
+
+@dataclass
+class ServeConfig:
+    model: str = ""
+    addr: str = "127.0.0.1:8080"
+    placement: str = "single"            # single | tensor:0,1,.. | expert:0,1,..
+    rows: int = 32
+    max_seq: int = 4096
+    prefill_chunk: int = 512
+    kv_dtype: str = "bf16"
+    matmul_precision: str = "narrow"
+    chat_template: Optional[str] = None
+    chat_template_file: Optional[str] = None
+    draft_lookup: Optional[str] = None   # NGRAM:K
+    rate_limit_rpm: int = 0
+    lora_admin_key_file: Optional[str] = None
+    max_connections: int = 4096
+    max_pending_requests: int = 256
+    max_receiving_requests: int = 64
+    max_queue_wait_secs: float = 60.0
+    max_body_mib: int = 4
+    max_image_body_mib: int = 64
+    request_timeout_secs: float = 30.0
+    write_timeout_secs: float = 30.0
+    drain_timeout_secs: float = 30.0
+    device_timing: bool = False
+    timing_max_steps: int = 4096
+    prefix_cache: bool = True
+    kv_fraction: float = 0.85            # share of free device memory given to the KV pool
+    allowed_hosts: List[str] = field(default_factory=list)
+    model_id: Optional[str] = None
+
+    def validate(self) -> None:
+        def bound(name, lo, hi):
+            v = getattr(self, name)
+            if not (lo <= v <= hi):
+                raise ValueError(f"--{name.replace('_', '-')} {v} outside [{lo}, {hi}]")
+        bound("rows", 1, 1024); bound("max_seq", 128, 1 << 20); bound("prefill_chunk", 16, 8192)
+        bound("max_pending_requests", 1, 1 << 16); bound("max_body_mib", 1, 1024); bound("kv_fraction", 0.05, 0.98)
+        bound("max_queue_wait_secs", 0.1, 3600); bound("drain_timeout_secs", 0, 3600)
+        if self.kv_dtype not in ("bf16", "f16", "f32"):
+            raise ValueError(f"--kv-dtype {self.kv_dtype!r}: expected bf16, f16 or f32")
+        if self.matmul_precision not in ("exact", "narrow", "split"):
+            raise ValueError(f"--matmul-precision {self.matmul_precision!r}")
+        if not (self.placement == "single" or self.placement.startswith(("tensor:", "expert:", "pipeline:"))):
+            raise ValueError(f"--placement {self.placement!r}")
+        if self.placement.startswith("pipeline:"):
+            raise ValueError("pipeline placement is not built: use tensor:<ordinals>")
+        host, _, port = self.addr.rpartition(":")
+        if not host or not port.isdigit() or not (0 <= int(port) <= 65535):
+            raise ValueError(f"address {self.addr!r} is not host:port")
+
+    @property
+    def placement_ordinals(self) -> List[int]:
+        if self.placement == "single":
+            return [0]
+        return [int(x) for x in self.placement.split(":", 1)[1].split(",")]
+
+
+class _StrictParser(argparse.ArgumentParser):
+    def error(self, message):
+        raise ValueError(message)
+
+
+def parse_args(argv: List[str]) -> ServeConfig:
+    p = _StrictParser(prog="poot-serve", allow_abbrev=False)
+    p.add_argument("model")
+    p.add_argument("addr", nargs="?", default="127.0.0.1:8080")
+    d = ServeConfig()
+    for name, val in vars(d).items():
+        if name in ("model", "addr", "allowed_hosts"):
+            continue
+        flag = "--" + name.replace("_", "-")
+        if isinstance(val, bool):
+            p.add_argument(flag, action=argparse.BooleanOptionalAction, default=val)
+        elif isinstance(val, int):
+            p.add_argument(flag, type=int, default=val)
+        elif isinstance(val, float):
+            p.add_argument(flag, type=float, default=val)
+        else:
+            p.add_argument(flag, type=str, default=val)
+    p.add_argument("--allowed-host", action="append", default=[])
+    ns = p.parse_args(argv)
+    kw = {k: v for k, v in vars(ns).items() if k != "allowed_host"}
+    cfg = ServeConfig(**kw, allowed_hosts=ns.allowed_host)
+    cfg.validate()
+    return cfg
