@@ -193,9 +193,239 @@ __global__ void quant_dequant_kernel(const uint8_t* __restrict__ W, __nv_bfloat1
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Wide-load variants for the two formats of the quantised decode benchmark (Q4_K projections, Q8_0 embeddings).
+// One CTA of four warps owns one pair of weight rows and its warps split K; every lane fetches its weight bytes
+// with 16-byte streaming loads issued BEFORE the dependency wait (weights do not depend on the previous kernel),
+// so a whole row pair is in flight at once.  Integer levels become floats without a convert instruction: a byte
+// permute drops the level into the mantissa of a constant (128.0 as bf16<<16 for nibbles, 2^23 for bytes).
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float nib_to_f128(uint32_t masked, int i) {   // 128 + nibble (byte i of `masked`)
+  return __uint_as_float(__byte_perm(masked, 0x4300u, 0x5044u | (uint32_t)(i << 8)));
+}
+__device__ __forceinline__ float byte_to_f(uint32_t biased, int i) {     // signed level of byte i (bytes ^ 0x80)
+  return __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7440u | (uint32_t)i)) - 8388736.f;
+}
+
+template <int M, int EPI>
+__device__ __forceinline__ void qg_block_epilogue(float (&acc)[M][2], float (*red)[M][2], void* out,
+                                                  const __nv_bfloat16* resid, int n0, int N, int ldo) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int m = 0; m < M; ++m) { acc[m][0] = warp_sum(acc[m][0]); acc[m][1] = warp_sum(acc[m][1]); }
+  if (lane == 0) {
+#pragma unroll
+    for (int m = 0; m < M; ++m) { red[warp][m][0] = acc[m][0]; red[warp][m][1] = acc[m][1]; }
+  }
+  __syncthreads();
+  if (threadIdx.x < M) {
+    const int m = threadIdx.x;
+    float v0 = 0.f, v1 = 0.f;
+#pragma unroll
+    for (int w = 0; w < QG_WARPS; ++w) { v0 += red[w][m][0]; v1 += red[w][m][1]; }
+    if (EPI == QEPI_SWIGLU) {
+      reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + (n0 >> 1)] = __float2bfloat16(silu(v0) * v1);
+    } else {
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int n = n0 + r;
+        if (n >= N) break;
+        float v = r ? v1 : v0;
+        if (EPI == QEPI_F32) reinterpret_cast<float*>(out)[(size_t)m * ldo + n] = v;
+        else {
+          if (EPI == QEPI_RESID) v += __bfloat162float(resid[(size_t)m * ldo + n]);
+          reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16(v);
+        }
+      }
+    }
+  }
+}
+
+// Q4_K: a warp pass covers four 144-byte super-blocks of each row; lane = (block of the pass, 16-byte slice of its
+// 128 nibble bytes).  Slice `seg` holds values [seg*16 .. +16) of sub-block 2j in its low nibbles and the same
+// positions of sub-block 2j+1 in its high nibbles (j = seg / 2).
+struct Q4kLane { uint4 head, qs; };
+__device__ __forceinline__ void q4k_scales(const uint4& head, int j, float& a0, float& b0, float& a1, float& b1) {
+  const float d = h2f((uint16_t)(head.x & 0xFFFF)), dmin = h2f((uint16_t)(head.x >> 16));
+  int sc0, sc1, mn0, mn1;
+  if (j < 2) {
+    const int s = 16 * j;
+    sc0 = (head.y >> s) & 63; sc1 = (head.y >> (s + 8)) & 63;
+    mn0 = (head.z >> s) & 63; mn1 = (head.z >> (s + 8)) & 63;
+  } else {
+    const int s = 16 * (j - 2);
+    sc0 = ((head.w >> s) & 0xF) | (((head.y >> (s + 6)) & 3) << 4);
+    sc1 = ((head.w >> (s + 8)) & 0xF) | (((head.y >> (s + 14)) & 3) << 4);
+    mn0 = ((head.w >> (s + 4)) & 0xF) | (((head.z >> (s + 6)) & 3) << 4);
+    mn1 = ((head.w >> (s + 12)) & 0xF) | (((head.z >> (s + 14)) & 3) << 4);
+  }
+  a0 = d * (float)sc0; b0 = dmin * (float)mn0; a1 = d * (float)sc1; b1 = dmin * (float)mn1;
+}
+
+template <int M, int EPI>
+__global__ void __launch_bounds__(QG_WARPS * 32)
+q4k_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, void* __restrict__ out,
+                const __nv_bfloat16* __restrict__ resid, int N, int K, int ldx, int ldo) {
+  __shared__ float red[QG_WARPS][M][2];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane >> 3, seg = lane & 7, j = seg >> 1;
+  const int nblk = K >> 8, n0 = blockIdx.x * 2;
+  const size_t row_bytes = (size_t)nblk * 144;
+  const uint8_t* r0 = W + (size_t)n0 * row_bytes;
+  const uint8_t* r1 = W + (size_t)(n0 + 1 < N ? n0 + 1 : n0) * row_bytes;
+  Q4kLane c0, c1;
+  int b = warp * 4 + sub;
+  if (b < nblk) {
+    c0.head = ld_stream16(r0 + (size_t)b * 144); c0.qs = ld_stream16(r0 + (size_t)b * 144 + 16 + seg * 16);
+    c1.head = ld_stream16(r1 + (size_t)b * 144); c1.qs = ld_stream16(r1 + (size_t)b * 144 + 16 + seg * 16);
+  }
+  pdl_wait(); pdl_launch();
+  float acc[M][2];
+#pragma unroll
+  for (int m = 0; m < M; ++m) { acc[m][0] = 0.f; acc[m][1] = 0.f; }
+  for (; b - sub < nblk; b += QG_WARPS * 4) {
+    const bool live = b < nblk;
+    const Q4kLane u0 = c0, u1 = c1;
+    const int bn = b + QG_WARPS * 4;
+    if (bn < nblk) {   // next pass of this warp: in flight while this one is consumed
+      c0.head = ld_stream16(r0 + (size_t)bn * 144); c0.qs = ld_stream16(r0 + (size_t)bn * 144 + 16 + seg * 16);
+      c1.head = ld_stream16(r1 + (size_t)bn * 144); c1.qs = ld_stream16(r1 + (size_t)bn * 144 + 16 + seg * 16);
+    }
+    if (!live) continue;
+    float a00, b00, a01, b01, a10, b10, a11, b11;
+    q4k_scales(u0.head, j, a00, b00, a01, b01);
+    q4k_scales(u1.head, j, a10, b10, a11, b11);
+    const uint32_t w0[4] = {u0.qs.x, u0.qs.y, u0.qs.z, u0.qs.w}, w1[4] = {u1.qs.x, u1.qs.y, u1.qs.z, u1.qs.w};
+    const int k_lo = b * 256 + j * 64 + (seg & 1) * 16;
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const __nv_bfloat16* xp = x + (size_t)m * ldx + k_lo;
+      float xl[16], xh[16];
+      unpack8(*reinterpret_cast<const uint4*>(xp), xl); unpack8(*reinterpret_cast<const uint4*>(xp + 8), xl + 8);
+      unpack8(*reinterpret_cast<const uint4*>(xp + 32), xh); unpack8(*reinterpret_cast<const uint4*>(xp + 40), xh + 8);
+      float sxl = 0.f, sxh = 0.f, l0 = 0.f, h0 = 0.f, l1 = 0.f, h1 = 0.f;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t lo0 = w0[w] & 0x0F0F0F0Fu, hi0 = (w0[w] >> 4) & 0x0F0F0F0Fu;
+        const uint32_t lo1 = w1[w] & 0x0F0F0F0Fu, hi1 = (w1[w] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float xa = xl[w * 4 + i], xb = xh[w * 4 + i];
+          sxl += xa; sxh += xb;
+          l0 += nib_to_f128(lo0, i) * xa; h0 += nib_to_f128(hi0, i) * xb;
+          l1 += nib_to_f128(lo1, i) * xa; h1 += nib_to_f128(hi1, i) * xb;
+        }
+      }
+      // sum((128 + q) x) - 128 sum(x) = sum(q x);  value = a * q - b
+      acc[m][0] += a00 * (l0 - 128.f * sxl) - b00 * sxl + a01 * (h0 - 128.f * sxh) - b01 * sxh;
+      acc[m][1] += a10 * (l1 - 128.f * sxl) - b10 * sxl + a11 * (h1 - 128.f * sxh) - b11 * sxh;
+    }
+  }
+  qg_block_epilogue<M, EPI>(acc, red, out, resid, n0, N, ldo);
+}
+
+// Q8_0: a warp pass covers 32 blocks (1088 bytes) of each row, staged through shared memory because the 34-byte
+// blocks are only 2-byte aligned; lane = block of the pass.
+template <int M, int EPI>
+__global__ void __launch_bounds__(QG_WARPS * 32)
+q80_gemv_kernel(const __nv_bfloat16* __restrict__ x, const uint8_t* __restrict__ W, void* __restrict__ out,
+                const __nv_bfloat16* __restrict__ resid, int N, int K, int ldx, int ldo) {
+  __shared__ float red[QG_WARPS][M][2];
+  __shared__ __align__(16) uint8_t stage[QG_WARPS][2][1088];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nblk = K >> 5, n0 = blockIdx.x * 2;
+  const size_t row_bytes = (size_t)nblk * 34;               // K % 256 == 0: a multiple of 16 bytes
+  const uint8_t* r0 = W + (size_t)n0 * row_bytes;
+  const uint8_t* r1 = W + (size_t)(n0 + 1 < N ? n0 + 1 : n0) * row_bytes;
+  const int npass = (nblk + 31) >> 5;
+  uint4 f0[3], f1[3];
+  auto fetch = [&](int pass) {
+    const size_t base = (size_t)pass * 1088;
+    const size_t lim = row_bytes - base;                    // bytes left in the row from this pass on (multiple of 16)
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+      const size_t off = (size_t)(lane + 32 * t) * 16;
+      if (off < 1088 && off < lim) { f0[t] = ld_stream16(r0 + base + off); f1[t] = ld_stream16(r1 + base + off); }
+    }
+  };
+  if (warp < npass) fetch(warp);
+  pdl_wait(); pdl_launch();
+  float acc[M][2];
+#pragma unroll
+  for (int m = 0; m < M; ++m) { acc[m][0] = 0.f; acc[m][1] = 0.f; }
+  for (int pass = warp; pass < npass; pass += QG_WARPS) {
+    __syncwarp();
+#pragma unroll
+    for (int t = 0; t < 3; ++t) {
+      const int off = (lane + 32 * t) * 16;
+      if (off < 1088) {
+        *reinterpret_cast<uint4*>(&stage[warp][0][off]) = f0[t];
+        *reinterpret_cast<uint4*>(&stage[warp][1][off]) = f1[t];
+      }
+    }
+    __syncwarp();
+    if (pass + QG_WARPS < npass) fetch(pass + QG_WARPS);
+    const int blk = pass * 32 + lane;
+    if (blk < nblk) {
+      const uint16_t* s0 = reinterpret_cast<const uint16_t*>(&stage[warp][0][lane * 34]);
+      const uint16_t* s1 = reinterpret_cast<const uint16_t*>(&stage[warp][1][lane * 34]);
+      const float d0 = h2f(s0[0]), d1 = h2f(s1[0]);
+      uint32_t q0[8], q1[8];
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+        q0[w] = ((uint32_t)s0[1 + 2 * w] | ((uint32_t)s0[2 + 2 * w] << 16)) ^ 0x80808080u;
+        q1[w] = ((uint32_t)s1[1 + 2 * w] | ((uint32_t)s1[2 + 2 * w] << 16)) ^ 0x80808080u;
+      }
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        const __nv_bfloat16* xp = x + (size_t)m * ldx + (size_t)blk * 32;
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          float xf[8];
+          unpack8(*reinterpret_cast<const uint4*>(xp + 8 * v), xf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            t0 += byte_to_f(q0[2 * v + (i >> 2)], i & 3) * xf[i];
+            t1 += byte_to_f(q1[2 * v + (i >> 2)], i & 3) * xf[i];
+          }
+        }
+        acc[m][0] += d0 * t0; acc[m][1] += d1 * t1;
+      }
+    }
+  }
+  qg_block_epilogue<M, EPI>(acc, red, out, resid, n0, N, ldo);
+}
+
+template <int FMT, int M, int EPI> struct QKernelFor {
+  static constexpr auto fn = quant_gemv_kernel<FMT, M, EPI>;
+  static constexpr bool per_pair = false;
+};
+template <int M, int EPI> struct QKernelFor<QF_Q4_K, M, EPI> {
+  static constexpr auto fn = q4k_gemv_kernel<M, EPI>;
+  static constexpr bool per_pair = true;
+};
+template <int M, int EPI> struct QKernelFor<QF_Q8_0, M, EPI> {
+  static constexpr auto fn = q80_gemv_kernel<M, EPI>;
+  static constexpr bool per_pair = true;
+};
+
 template <int FMT, int M>
 static int launch_qgemv_m(int epi, const void* x, const void* W, void* out, const void* resid, int N, int K, int ldx,
                           int ldo, cudaStream_t s) {
+  if (QKernelFor<FMT, M, QEPI_STORE>::per_pair) {
+    dim3 g((N + 1) / 2), b(QG_WARPS * 32);
+    const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+    const uint8_t* wb = (const uint8_t*)W;
+    const __nv_bfloat16* rb = (const __nv_bfloat16*)resid;
+    switch (epi) {
+      case QEPI_STORE: return launch_k(QKernelFor<FMT, M, QEPI_STORE>::fn, g, b, 0, s, xb, wb, out, rb, N, K, ldx, ldo);
+      case QEPI_F32: return launch_k(QKernelFor<FMT, M, QEPI_F32>::fn, g, b, 0, s, xb, wb, out, rb, N, K, ldx, ldo);
+      case QEPI_RESID: return launch_k(QKernelFor<FMT, M, QEPI_RESID>::fn, g, b, 0, s, xb, wb, out, rb, N, K, ldx, ldo);
+      case QEPI_SWIGLU: return launch_k(QKernelFor<FMT, M, QEPI_SWIGLU>::fn, g, b, 0, s, xb, wb, out, rb, N, K, ldx, ldo);
+      default: return (int)cudaErrorInvalidValue;
+    }
+  }
   int pairs = (N + 1) / 2, blocks = (pairs + QG_WARPS - 1) / QG_WARPS;
   if (blocks > 148 * 8) blocks = 148 * 8;
   dim3 g(blocks), b(QG_WARPS * 32);

@@ -70,13 +70,13 @@ class LLM:
 
     @staticmethod
     def random(preset: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
-               kv_fraction: float = 0.85, seed: int = 0, tp_rank: int = 0, tp_world: int = 1, comm=None,
-               num_blocks: Optional[int] = None, **over) -> "LLM":
+               kv_fraction: float = 0.85, seed: int = 0, std: float = 0.02, tp_rank: int = 0, tp_world: int = 1,
+               comm=None, num_blocks: Optional[int] = None, **over) -> "LLM":
         """Random-init weights of a named architecture (benchmarks and tests: no checkpoint on disk)."""
         from .runtime.weights import random_weights
         import dataclasses
         cfg = dataclasses.replace(PRESETS[preset](), **over)
-        weights = random_weights(cfg, device, seed=seed, tp_rank=tp_rank, tp_world=tp_world)
+        weights = random_weights(cfg, device, seed=seed, std=std, tp_rank=tp_rank, tp_world=tp_world)
         return LLM._assemble(cfg, weights, None, rows, max_seq, prefill_chunk, kv_fraction, comm, None, num_blocks)
 
     @staticmethod

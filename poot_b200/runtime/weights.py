@@ -189,3 +189,31 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
         lm_head = shard_rows(lm_head, tp_rank, tp_world)
     return DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm"), lm_head=lm_head, layers=layers,
                           tp_rank=tp_rank, tp_world=tp_world)
+
+
+def random_quant_weights(cfg: DecoderConfig, device, proj_format: str = "Q4_K", embed_format: str = "Q8_0", seed: int = 0,
+                         std: float = 0.02, tp_rank: int = 0, tp_world: int = 1) -> DecoderWeights:
+    """Weight-only block-quantised model: the random bf16 model of :func:`random_weights`, each projection encoded
+    on the device in ``proj_format`` and the token / output embeddings in ``embed_format``; norms stay bf16.
+
+    Rank shares are cut before encoding; every cut falls on a block boundary (rows for q/k/v/gate/up, multiples of
+    the 256-value super-block along ``in`` for o/down), so a share equals the same slice of the whole packed tensor.
+    """
+    from ..ops.cuda_ops import QuantWeight
+    from ..quant.torch_quant import ENCODERS
+    if cfg.is_moe:
+        raise ValueError("quantised expert weights are not built")
+    dense = random_weights(cfg, device, seed=seed, std=std, tp_rank=tp_rank, tp_world=tp_world)
+
+    def enc(t: torch.Tensor, fmt: str) -> "QuantWeight":
+        rows, cols = t.shape
+        parts = [ENCODERS[fmt](t[r:r + 16384]) for r in range(0, rows, 16384)]   # bounded fp32 temporaries
+        return QuantWeight(fmt, torch.cat(parts).reshape(-1), rows, cols)
+
+    for L in dense.layers:
+        for role in ("wqkv", "wo", "wgu", "wdown"):
+            setattr(L, role, enc(getattr(L, role), proj_format))
+    tied = dense.lm_head is dense.embed
+    dense.embed = enc(dense.embed, embed_format)
+    dense.lm_head = dense.embed if tied else enc(dense.lm_head, embed_format)
+    return dense

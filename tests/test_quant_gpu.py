@@ -18,9 +18,9 @@ def _packed(fmt, N, Kd, seed=0):
 
 @pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("M", [1, 3])
-def test_quant_gemv_matches_dequantised_reference(fmt, M):
+@pytest.mark.parametrize("N,Kd", [(1026, 1024), (258, 5376)])
+def test_quant_gemv_matches_dequantised_reference(fmt, M, N, Kd):
     from poot_b200.ops import cuda_ops as K
-    N, Kd = 1026, 1024
     W, deq = _packed(fmt, N, Kd)
     x = (torch.randn(M, Kd, device="cuda")).to(torch.bfloat16)
     ref = x.float() @ deq.T
