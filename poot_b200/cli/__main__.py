@@ -1,0 +1,29 @@
+"""``python -m poot_b200.cli generate -m CKPT -p "..." -n 16`` (crates/poot-llm/src/bin/poot/main.rs:42-55)."""
+from __future__ import annotations
+
+import sys
+
+from .generate import main_generate
+
+USAGE = "usage: poot {generate|caption|embed} [options]   (generate --help lists the llama-cli compatible flags)"
+
+
+def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if not argv or argv[0] in ("-h", "--help"):
+        print(USAGE)
+        return 0 if argv else 2
+    cmd, rest = argv[0], argv[1:]
+    if cmd == "generate":
+        return main_generate(rest)
+    if cmd in ("caption", "embed"):
+        # The reference serves these through its vision front ends and encoder families
+        # (crates/poot-llm/src/bin/poot/main.rs:42-55); this build registers decoder-only text families.
+        print(f"error: `{cmd}` needs a vision / encoder family; only decoder text families are registered", file=sys.stderr)
+        return 2
+    print(f"error: unknown command {cmd!r}\n{USAGE}", file=sys.stderr)
+    return 2
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -32,6 +32,7 @@ class FakeStepEngine:
         if self.fail_at_step is not None and len(self.steps) == self.fail_at_step:
             raise RuntimeError("injected engine fault")
         self.steps.append(inp)
+        self._last_first = []
         B = len(inp.logit_idx)
         picked = np.zeros((B, 2), np.int32)
         picked[:, 1] = -1
@@ -43,7 +44,20 @@ class FakeStepEngine:
                 later = ok[ok >= tok]
                 tok = int(later[0] if len(later) else ok[0])
             picked[b, 0] = tok
+            self._last_first.append((int(inp.tokens[inp.logit_idx[b]]) + 1) % self.vocab)
         return picked, (np.zeros(B, np.float32) if inp.want_logprobs else None)
+
+
+    def last_logits(self, rows: int) -> np.ndarray:
+        """Synthetic logits of the last step: the favourite scores 0, every next id half a nat less."""
+        out = np.zeros((rows, self.vocab), np.float32)
+        ids = np.arange(self.vocab)
+        for b in range(rows):
+            out[b] = -0.5 * ((ids - self._last_first[b]) % self.vocab)
+        return out
+
+    def copy_block(self, src: int, dst: int) -> None:
+        self.copies = getattr(self, "copies", []) + [(src, dst)]
 
 
 class DeviceStepEngine:
@@ -108,3 +122,13 @@ class DeviceStepEngine:
             self.h_logprobs[:B].copy_(e.logprobs[:B], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self.h_picked[:B].numpy().copy(), (self.h_logprobs[:B].numpy().copy() if inp.want_logprobs else None)
+
+    def last_logits(self, rows: int) -> np.ndarray:
+        """Whole-vocabulary logits of the last step's sampling rows (single-rank engines only)."""
+        if self.e.tp != 1:
+            raise RuntimeError("ranks of a tensor-parallel engine hold vocabulary shards")
+        return self.e.logits[:rows].float().cpu().numpy()
+
+    def copy_block(self, src: int, dst: int) -> None:
+        """Copy one K/V block in every layer (a forked sequence gets its own copy of the partial last block)."""
+        self.e.kv.buf[:, :, dst].copy_(self.e.kv.buf[:, :, src])

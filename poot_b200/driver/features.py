@@ -1,0 +1,76 @@
+"""Feature composition: ONE compatibility table decides which serving features may be combined.
+
+Every pairing the engine cannot run is a row here with its reason, so a refused configuration fails at startup
+with a typed error instead of somewhere inside a step (crates/poot-llm/src/driver/features.rs:1-13).
+"""
+from __future__ import annotations
+
+from enum import Enum
+from typing import Iterable, List, Tuple
+
+
+class Feature(Enum):
+    TENSOR_PLACEMENT = "tensor placement"
+    EXPERT_PLACEMENT = "expert placement"
+    PIPELINE_PLACEMENT = "pipeline placement"
+    DRAFT_LOOKUP = "lookup drafting"
+    DRAFT_MODEL = "draft model"
+    DRAFT_MTP = "multi-token-prediction drafting"
+    BEAM = "beam search"
+    GUIDED = "guided decoding"
+    LOGPROBS = "logprobs"
+    ADAPTERS = "LoRA adapters"
+    PACKED_WEIGHTS = "packed (block-quantised) weights"
+    DEVICE_TIMING = "per-kernel device timing"
+    PREFIX_CACHE = "prefix cache"
+    RECURRENT_STATE = "recurrent state"
+    EXPERT_POOL = "pooled experts"
+
+
+class Incompatible(ValueError):
+    def __init__(self, a: Feature, b: Feature, why: str):
+        super().__init__(f"{a.value} cannot be combined with {b.value}: {why}")
+        self.pair, self.why = (a, b), why
+
+
+class Unavailable(ValueError):
+    def __init__(self, f: Feature, why: str):
+        super().__init__(f"{f.value} is not available: {why}")
+        self.feature, self.why = f, why
+
+
+F = Feature
+TABLE: List[Tuple[Feature, Feature, str]] = [
+    (F.TENSOR_PLACEMENT, F.EXPERT_PLACEMENT, "one placement per model; expert placement already shards attention over the same ranks"),
+    (F.TENSOR_PLACEMENT, F.BEAM, "beam search reads whole-vocabulary logits on the host; tensor ranks hold vocabulary shards"),
+    (F.EXPERT_PLACEMENT, F.BEAM, "beam search reads whole-vocabulary logits on the host; ranks hold vocabulary shards"),
+    (F.TENSOR_PLACEMENT, F.DEVICE_TIMING, "event brackets between launches would serialise ranks that wait on one another in-kernel"),
+    (F.EXPERT_PLACEMENT, F.DEVICE_TIMING, "event brackets between launches would serialise ranks that wait on one another in-kernel"),
+    (F.TENSOR_PLACEMENT, F.DRAFT_MODEL, "the draft model would need its own rank group"),
+    (F.DRAFT_LOOKUP, F.DRAFT_MODEL, "one draft policy per driver"),
+    (F.DRAFT_LOOKUP, F.BEAM, "speculation verifies one greedy continuation"),
+    (F.DRAFT_MODEL, F.BEAM, "speculation verifies one greedy continuation"),
+    (F.DRAFT_LOOKUP, F.GUIDED, "a constraint mask is computed one token ahead, not for k drafted positions"),
+    (F.DRAFT_MODEL, F.GUIDED, "a constraint mask is computed one token ahead, not for k drafted positions"),
+    (F.BEAM, F.GUIDED, "beams would each need a clone of the constraint state"),
+    (F.PACKED_WEIGHTS, F.EXPERT_PLACEMENT, "packed expert weights have no fused grouped kernel"),
+    (F.ADAPTERS, F.PACKED_WEIGHTS, "adapter deltas are applied to bf16 projections"),
+]
+UNAVAILABLE = {
+    F.PIPELINE_PLACEMENT: "stages over NVLink would idle all but one GPU at decode; use tensor:<ordinals>",
+    F.DRAFT_MTP: "no registered family ships multi-token-prediction heads",
+    F.RECURRENT_STATE: "no recurrent (SSM / linear-attention) family is registered",
+    F.EXPERT_POOL: "all experts stay resident in 180 GB of HBM; there is no host-side expert pool",
+}
+
+
+def check(features: Iterable[Feature]) -> None:
+    """Raises ``Unavailable`` / ``Incompatible`` for the first offending feature or pair."""
+    fs = list(dict.fromkeys(features))
+    for f in fs:
+        if f in UNAVAILABLE:
+            raise Unavailable(f, UNAVAILABLE[f])
+    have = set(fs)
+    for a, b, why in TABLE:
+        if a in have and b in have:
+            raise Incompatible(a, b, why)

@@ -1,0 +1,123 @@
+"""Speculative decoding for one greedy sequence: draft k tokens cheaply, verify them in ONE target step.
+
+Draft policies (crates/poot-llm/src/driver/speculate.rs:1-20; website/docs/serve/speculative-decoding.md):
+``LookupDraft`` proposes the continuation that followed the most recent earlier occurrence of the current n-gram
+in the sequence itself (prompt lookup); ``ModelDraft`` runs a smaller model greedily.  Verification feeds
+``[last token, d1 .. dk]`` as one piece with a logit row at each position; the accepted prefix is the run of drafts
+equal to the target's own greedy picks, plus the target's pick after it, so the output is token-for-token what
+plain greedy decoding produces.  Rejected drafts leave stale K/V in slots past the accepted length; those positions
+are rewritten when their real tokens are fed and are never visible to attention before that.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+
+from ..oracle import sampling as S
+from .driver import Driver, DriverError, StepInputs, _bucket
+from .kvcache import BLOCK
+
+
+class LookupDraft:
+    def __init__(self, ngram: int = 3, k: int = 4):
+        if ngram < 1 or k < 1:
+            raise ValueError("lookup drafting needs NGRAM >= 1 and K >= 1")
+        self.ngram, self.k = ngram, k
+
+    @staticmethod
+    def parse(text: str) -> "LookupDraft":
+        """``NGRAM:K`` as in ``--draft-lookup``."""
+        a, sep, b = text.partition(":")
+        if not sep or not a.isdigit() or not b.isdigit():
+            raise ValueError(f"--draft-lookup {text!r}: expected NGRAM:K")
+        return LookupDraft(int(a), int(b))
+
+    def propose(self, tokens: Sequence[int]) -> List[int]:
+        n = self.ngram
+        if len(tokens) <= n:
+            return []
+        key = list(tokens[-n:])
+        for start in range(len(tokens) - n - 1, -1, -1):     # most recent earlier occurrence
+            if list(tokens[start:start + n]) == key:
+                return list(tokens[start + n:start + n + self.k])
+        return []
+
+
+class ModelDraft:
+    """Greedy continuation from a smaller model behind its own driver."""
+
+    def __init__(self, draft_driver: Driver, k: int = 4):
+        self.d, self.k = draft_driver, k
+
+    def propose(self, tokens: Sequence[int]) -> List[int]:
+        from .sampler import SamplingParams
+        return self.d.generate(list(tokens), SamplingParams(max_tokens=self.k, ignore_eos=True))
+
+
+def speculative_step(d: Driver, seq_id: int, draft) -> List[int]:
+    """One verify step; returns the tokens to commit (>= 1).  The sequence must be greedy, unguided and past prefill."""
+    s = d.seqs[seq_id]
+    if not s.params.greedy or s.guided is not None or s.params.needs_adjust:
+        raise DriverError("speculation verifies plain greedy sequences only")
+    if s.pending != 1:
+        raise DriverError("speculate after the prompt is prefilled (pending must be 1)")
+    room = min(len(s.blocks) * BLOCK, d.max_seq_len) - len(s.tokens) - 1
+    room = min(room, s.params.max_tokens - s.generated - 1)
+    drafts = list(draft.propose(s.tokens))[:max(0, min(room, d.max_rows - 1, d.engine.max_tokens - 1))]
+    if any(t < 0 or t >= d.vocab for t in drafts):
+        drafts = []
+    piece = [s.tokens[-1]] + drafts
+    T, B = len(piece), len(piece)
+    Tp, Bp = _bucket(T, d.engine.max_tokens), _bucket(B, d.max_rows)
+    tokens = np.zeros(Tp, np.int32); positions = np.zeros(Tp, np.int32); slots = np.full(Tp, -1, np.int32)
+    row_seq = np.zeros(Tp, np.int32); row_ctx = np.zeros(Tp, np.int32)
+    base = s.computed
+    for i, t in enumerate(piece):
+        tokens[i], positions[i], slots[i] = t, base + i, d._slot(s, base + i)
+        row_seq[i], row_ctx[i] = s.row, base + i + 1
+    logit_idx = np.zeros(Bp, np.int64)
+    logit_idx[:B] = np.arange(T)
+    params = np.zeros((Bp, 4), np.float32); params[:, 0] = 1.0; params[:, 1] = -1e30; params[:, 3] = 1.0
+    inp = StepInputs(tokens, positions, slots, row_seq, row_ctx, logit_idx, S.GREEDY, params, np.zeros(Bp, np.int32),
+                     np.zeros(Bp, np.int32), None, False, T, B)
+    picked, _ = d.engine.run_step(inp)
+    d.stats["steps"] += 1
+    accepted = 0
+    while accepted < len(drafts) and int(picked[accepted, 0]) == drafts[accepted]:
+        accepted += 1
+    out = drafts[:accepted] + [int(picked[accepted, 0])]
+    d.stats["decode_tokens"] += 1 + accepted
+    d.stats["draft_proposed"] = d.stats.get("draft_proposed", 0) + len(drafts)
+    d.stats["draft_accepted"] = d.stats.get("draft_accepted", 0) + accepted
+    s.computed += 1 + accepted           # K/V of the fed token and of every accepted draft is final
+    # commit all but the last through the driver (each commit appends the token; the next step feeds the last one)
+    return out
+
+
+def generate_speculative(d: Driver, prompt: Sequence[int], params, draft, on_token=None) -> List[int]:
+    """Greedy generation with drafting; equals ``Driver.generate`` token for token."""
+    sid = d.open(prompt, params)
+    out: List[int] = []
+    try:
+        done = False
+        while not done:
+            s = d.seqs[sid]
+            if s.pending > 1 or s.generated == 0:
+                res = [r for r in d.step([sid]) if r.token is not None]
+                toks = [res[0].token] if res else []
+            else:
+                toks = speculative_step(d, sid, draft)
+            for k, t in enumerate(toks):
+                d.commit(sid, [t])
+                if k < len(toks) - 1:
+                    pass                      # accepted drafts: their K/V is already in the cache
+                out.append(t)
+                if on_token is not None:
+                    on_token(t)
+                if d.finished(sid, t):
+                    done = True
+                    break
+    finally:
+        d.release(sid)
+    return out

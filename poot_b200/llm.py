@@ -44,11 +44,11 @@ class LLM:
         from .runtime.engine import DecoderEngine, KVPool
         dev = weights.embed.device if hasattr(weights.embed, "device") else torch.device("cuda")
         max_seq = min(max_seq, cfg.max_position)
-        if num_blocks is None:
+        if num_blocks is None:      # capacity fit against the memory left after the weights are resident
+            from .driver import capacity
             free, _ = torch.cuda.mem_get_info(dev)
-            per_block = KVPool.bytes_per_block(cfg, weights.tp_world)
-            budget = int(free * kv_fraction) - (2 << 30)       # activations, logits, graphs
-            num_blocks = max(min(budget // per_block, rows * blocks_for(max_seq)), blocks_for(max_seq) + 1)
+            shapes = capacity.fit(cfg, free, rows, max_seq, prefill_chunk, weights.tp_world, kv_fraction=kv_fraction)
+            rows, max_seq, prefill_chunk, num_blocks = shapes.rows, shapes.max_seq, shapes.prefill_chunk, shapes.num_blocks
         max_tokens = max(prefill_chunk, rows) + rows            # widest prefill piece + one decode row per sequence
         eng = DecoderEngine(weights, num_blocks, rows, max_tokens, blocks_for(max_seq), comm=comm)
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)

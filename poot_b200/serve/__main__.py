@@ -52,7 +52,15 @@ def main(argv=None) -> int:
     if cfg.chat_template_file:
         with open(cfg.chat_template_file) as f:
             template = f.read()
-    engine = ServeEngine(llm.driver, llm.tokenizer, Metrics(), cfg.max_pending_requests, cfg.max_queue_wait_secs)
+    draft = None
+    if cfg.draft_lookup:
+        from ..driver.features import Feature, check
+        from ..driver.placement import Placement
+        from ..driver.speculate import LookupDraft
+        draft = LookupDraft.parse(cfg.draft_lookup)
+        check([Feature.DRAFT_LOOKUP, *Placement.parse(cfg.placement).features])
+    engine = ServeEngine(llm.driver, llm.tokenizer, Metrics(), cfg.max_pending_requests, cfg.max_queue_wait_secs,
+                         draft=draft)
     state = ServerState(engine, cfg, cfg.model_id or os.path.basename(cfg.model.rstrip("/")) or "model",
                         family=llm.cfg.family if llm.cfg is not None else "llama", chat_template=template)
     server = Server(state)

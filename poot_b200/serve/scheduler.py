@@ -63,7 +63,7 @@ class EngineDead(RuntimeError):
 
 class ServeEngine:
     def __init__(self, driver: Driver, tokenizer, metrics: Optional[Metrics] = None, max_pending: int = 256,
-                 max_queue_wait: float = 60.0, on_step: Optional[Callable] = None):
+                 max_queue_wait: float = 60.0, on_step: Optional[Callable] = None, draft=None):
         self.driver, self.tk = driver, tokenizer
         self.metrics = metrics or Metrics()
         self.inbox: "queue.Queue[Job]" = queue.Queue()
@@ -77,6 +77,7 @@ class ServeEngine:
         self._thread: Optional[threading.Thread] = None
         self._stop = threading.Event()
         self.on_step = on_step
+        self.draft = draft                   # draft policy (``propose(tokens)``) used while one greedy sequence is live
         self.busy_s = 0.0
         self.metrics.set("poot_slot_capacity", driver.max_rows)
 
@@ -187,6 +188,10 @@ class ServeEngine:
             self._gauges()
             return False
         t0 = time.monotonic()
+        if self.draft is not None and len(self.live) == 1 and self._speculate():
+            self.busy_s += time.monotonic() - t0
+            self._gauges()
+            return True
         try:
             results = d.step(list(self.live))
         except SamplerFault as e:                       # fails only its request
@@ -205,6 +210,25 @@ class ServeEngine:
             job = self.live[r.seq_id]
             self._commit(job, r)
         self._gauges()
+        return True
+
+    def _speculate(self) -> bool:
+        """Draft-and-verify for a lone greedy sequence (speculation gives nothing once rows batch together)."""
+        from ..driver.driver import RowResult
+        from ..driver.speculate import speculative_step
+        d = self.driver
+        sid, job = next(iter(self.live.items()))
+        s = d.seqs[sid]
+        sp = s.params
+        if s.pending != 1 or s.generated == 0 or not sp.greedy or s.guided is not None or sp.needs_adjust or sp.logprobs:
+            return False
+        toks = speculative_step(d, sid, self.draft)
+        self.metrics.inc("poot_engine_steps_total")
+        self.metrics.set("poot_batch_size", 1)
+        for t in toks:
+            self._commit(job, RowResult(sid, t, 1, None))
+            if sid not in self.live:
+                break
         return True
 
     def _commit(self, job: Job, r) -> None:

@@ -1,0 +1,115 @@
+"""Feature table, placement rules, capacity fit, speculative decoding and beam search on the host engine."""
+import numpy as np
+import pytest
+
+from poot_b200.driver import capacity
+from poot_b200.driver.beam import beam_search, fork
+from poot_b200.driver.features import Feature, Incompatible, Unavailable, check
+from poot_b200.driver.placement import Placement, PlacementError
+from poot_b200.driver.sampler import SamplingParams
+from poot_b200.driver.speculate import LookupDraft, ModelDraft, generate_speculative
+from poot_b200.llm import LLM
+from poot_b200.models.config import llama3_8b, llama3_70b, mixtral_8x7b
+
+
+def test_feature_table():
+    check([Feature.TENSOR_PLACEMENT, Feature.PREFIX_CACHE, Feature.LOGPROBS, Feature.GUIDED])
+    with pytest.raises(Incompatible) as e:
+        check([Feature.BEAM, Feature.TENSOR_PLACEMENT])
+    assert "vocabulary" in str(e.value)
+    with pytest.raises(Incompatible):
+        check([Feature.DRAFT_LOOKUP, Feature.GUIDED])
+    for f in (Feature.PIPELINE_PLACEMENT, Feature.DRAFT_MTP, Feature.RECURRENT_STATE, Feature.EXPERT_POOL):
+        with pytest.raises(Unavailable):
+            check([f])
+
+
+def test_placement_parse_and_divisibility():
+    p = Placement.parse("tensor:0,1,2,3")
+    assert p.kind == "tensor" and p.world == 4 and p.features == [Feature.TENSOR_PLACEMENT]
+    p.validate(llama3_8b())
+    Placement.parse("tensor:0,1,2,3,4,5,6,7").validate(llama3_70b())
+    Placement.parse("expert:0,1,2,3,4,5,6,7").validate(mixtral_8x7b())
+    for bad in ("tensor", "tensor:a", "tensor:0,0", "tensor:0,1,2", "ring:0,1"):
+        with pytest.raises(PlacementError):
+            Placement.parse(bad)
+    with pytest.raises(Unavailable):
+        Placement.parse("pipeline:0,1")
+    with pytest.raises(PlacementError):
+        Placement.parse("expert:0,1").validate(llama3_8b())
+    with pytest.raises(PlacementError):
+        Placement.parse("tensor:" + ",".join(map(str, range(16)))).validate(llama3_8b().__class__(**{**vars(llama3_8b()), "n_heads": 24}))
+
+
+def test_capacity_fit_halves_until_it_fits():
+    cfg = llama3_8b()
+    big = capacity.fit(cfg, free_bytes=150 << 30, rows=64, max_seq=8192)
+    assert (big.rows, big.max_seq) == (64, 8192) and big.num_blocks == 64 * 512 + 1
+    assert big.kv_bytes == big.num_blocks * capacity.kv_bytes_per_block(cfg) == big.num_blocks * 32 * 2 * 8 * 16 * 128 * 2
+    small = capacity.fit(cfg, free_bytes=1 << 30, rows=64, max_seq=8192)
+    assert small.max_seq < 8192 and small.rows == 64         # one full-length sequence must fit: the length is halved
+    assert small.planned_bytes <= (1 << 30) - capacity.RESERVE
+    assert small.num_blocks >= capacity.blocks_for(small.max_seq) + 1
+    tp = capacity.fit(cfg, free_bytes=1 << 30, rows=64, max_seq=8192, tp_world=8)
+    assert tp.max_seq == 8192 and tp.num_blocks > small.num_blocks      # a rank holds 1/8 of the KV heads
+    with pytest.raises(capacity.DoesNotFit):
+        capacity.fit(cfg, free_bytes=300 << 20, rows=4, max_seq=4096)
+    assert capacity.candidates(8, 512) == [(8, 512), (8, 256), (8, 128), (4, 128), (2, 128), (1, 128)]
+
+
+def test_lookup_drafting_equals_plain_greedy_with_fewer_steps():
+    prompt = [1] + list(range(3, 49)) + [3, 4, 5]
+    plain = LLM.fake(vocab=50).driver
+    ref = plain.generate(prompt, SamplingParams(max_tokens=30, ignore_eos=True))
+    d = LLM.fake(vocab=50).driver
+    got = generate_speculative(d, prompt, SamplingParams(max_tokens=30, ignore_eos=True), LookupDraft.parse("3:4"))
+    assert got == ref
+    assert d.stats["steps"] < plain.stats["steps"] / 2 and d.stats["draft_accepted"] > 0
+    assert d.kv_usage()["blocks_used"] == d.kv_usage()["prefix_entries"]
+    with pytest.raises(ValueError):
+        LookupDraft.parse("3")
+
+
+def test_rejected_drafts_do_not_change_the_output():
+    class WrongDraft:
+        def propose(self, tokens):
+            return [7, 7, 7]
+    prompt = [1, 10, 11, 12]
+    ref = LLM.fake(vocab=50).driver.generate(prompt, SamplingParams(max_tokens=12, ignore_eos=True))
+    d = LLM.fake(vocab=50).driver
+    assert generate_speculative(d, prompt, SamplingParams(max_tokens=12, ignore_eos=True), WrongDraft()) == ref
+    assert d.stats["draft_accepted"] <= 1 and d.stats["draft_proposed"] > 0
+
+
+def test_model_drafting_with_a_second_driver():
+    prompt = [1, 20, 21]
+    ref = LLM.fake(vocab=60).driver.generate(prompt, SamplingParams(max_tokens=10, ignore_eos=True))
+    d = LLM.fake(vocab=60).driver
+    got = generate_speculative(d, prompt, SamplingParams(max_tokens=10, ignore_eos=True), ModelDraft(LLM.fake(vocab=60).driver, 3))
+    assert got == ref and d.stats["draft_accepted"] >= 6
+
+
+def test_fork_shares_full_blocks_and_copies_the_partial_one():
+    llm = LLM.fake(vocab=100)
+    d = llm.driver
+    sid = d.open([1] + list(range(3, 23)), SamplingParams(max_tokens=8, ignore_eos=True))   # 21 tokens: 1 full block + 5
+    d.step([sid])
+    child = fork(d, sid)
+    a, b = d.seqs[sid], d.seqs[child]
+    assert a.blocks[0] == b.blocks[0] and d.pool.refcount(a.blocks[0]) == 2
+    assert a.blocks[1] != b.blocks[1] and d.engine.copies == [(a.blocks[1], b.blocks[1])]
+    assert a.row != b.row and b.tokens == a.tokens and b.computed == a.computed
+    d.release(sid, "preempted"); d.release(child, "preempted")
+    assert d.kv_usage()["blocks_used"] == 0
+
+
+def test_beam_search_orders_hypotheses_by_score():
+    d = LLM.fake(vocab=40, rows=8).driver
+    beams = beam_search(d, [1, 10], width=3, max_tokens=4, eos=-1)
+    assert len(beams) == 3
+    # the host engine's logits favour last+1, then last+2, ... half a nat apart: the best beam is the +1 chain
+    assert beams[0].tokens == [11, 12, 13, 14]
+    scores = [b.score for b in beams]
+    assert scores == sorted(scores, reverse=True) and scores[0] > scores[1]
+    assert beams[1].tokens != beams[0].tokens and len(set(map(lambda b: tuple(b.tokens), beams))) == 3
+    assert not d.seqs and d.kv_usage()["blocks_used"] == d.kv_usage()["prefix_entries"] == 0

@@ -284,3 +284,16 @@ def test_cli_flags_are_strict():
                 ["m", "--kv-dtype", "int3"]):
         with pytest.raises(ValueError):
             parse_args(bad)
+
+
+def test_lone_greedy_request_is_served_through_lookup_drafting():
+    from poot_b200.driver.speculate import LookupDraft
+    llm = LLM.fake(vocab=300, rows=4, max_seq=512, num_blocks=128, prefill_chunk=64)
+    eng = ServeEngine(llm.driver, llm.tokenizer, Metrics(), draft=LookupDraft(2, 4))
+    eng.state = "serving"
+    prompt = llm.tokenizer.encode("abcdefghij abc")          # "abc" seen before: the continuation "defg" is drafted
+    j = eng.submit(Job(prompt, SamplingParams(max_tokens=12, ignore_eos=True)))
+    for _ in range(40):
+        eng.iteration()
+    assert j.wait(1)["finish_reason"] == "length" and j.text == "defghijklmno"
+    assert llm.driver.stats["draft_accepted"] >= 4 and llm.driver.stats["steps"] < 12
