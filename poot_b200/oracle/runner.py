@@ -33,13 +33,14 @@ class OracleSession:
 
     def __init__(self, model: Model, weights: Dict[str, np.ndarray], rows: int = 1, capacity: int = 64,
                  paged: bool = True, options: Optional[EvalOptions] = None, block_order: Optional[Sequence[int]] = None,
-                 world: int = 1, rank: int = 0):
+                 world: int = 1, rank: int = 0, graph_transform=None):
         self.model, self.weights, self.rows, self.capacity, self.paged = model, weights, rows, capacity, paged
         self.options = options or EvalOptions(matmul_precision="exact")
         self.graphs: Dict[int, object] = {}
         self.state: Dict[str, np.ndarray] = {}
         self.length = 0
         self.world, self.rank = world, rank
+        self.graph_transform = graph_transform     # e.g. the planner's pass pipeline (pass-soundness checks)
         nblocks = rows * capacity // BLOCK
         order = list(block_order) if block_order is not None else list(range(nblocks))
         self.block_table = np.asarray(order, dtype=np.int32).reshape(rows, capacity // BLOCK)
@@ -48,7 +49,8 @@ class OracleSession:
     def _graph(self, tokens: int):
         if tokens not in self.graphs:
             spec = StepSpec(rows=self.rows, tokens=tokens, capacity=self.capacity, paged=self.paged, world=self.world)
-            self.graphs[tokens] = self.model.trace(spec)
+            g = self.model.trace(spec)
+            self.graphs[tokens] = self.graph_transform(g) if self.graph_transform is not None else g
         return self.graphs[tokens]
 
     def slot(self, row: int, pos: int) -> int:
@@ -103,4 +105,61 @@ class OracleSession:
             tok = int(np.argmax(logits[0]))
             out.append(tok)
             logits = self.step(np.array([[tok]], dtype=np.int32))
+        return out
+
+
+class RankWalk:
+    """Evaluate the ``world`` rank-local graphs of a tensor-parallel model in lockstep on the CPU.
+
+    Each rank runs its own :class:`OracleSession` on a thread; at an ``all_reduce`` every rank deposits its partial
+    and all of them continue with the left fold of the partials in rank order, which is the sum the device's
+    rank-ordered reduction produces (crates/poot-eval/src/ops/collective.rs:12-34; the reference's
+    ``expand_ranks`` walk, crates/poot-graph-plan/src/passes/sharding.rs:1165-1357).
+    """
+
+    def __init__(self, model: Model, weights: Dict[str, np.ndarray], world: int, rows: int = 1, capacity: int = 64,
+                 paged: bool = True, graph_transform=None):
+        import threading
+        self.world = world
+        self._barrier = threading.Barrier(world)
+        self._box: List[Optional[np.ndarray]] = [None] * world
+        self.sessions = []
+        for r in range(world):
+            opt = EvalOptions(matmul_precision="exact", collectives=self._hook(r))
+            self.sessions.append(OracleSession(model, weights, rows, capacity, paged, opt, world=world, rank=r,
+                                               graph_transform=graph_transform))
+
+    def _hook(self, rank: int):
+        def collective(op, eqn, ins):
+            self._box[rank] = ins[0]
+            self._barrier.wait()
+            if op == "all_reduce":
+                acc = self._box[0].copy()
+                for r in range(1, self.world):
+                    acc = acc + self._box[r]
+            elif op == "all_gather":
+                acc = np.concatenate(self._box, axis=eqn.attrs["axis"])
+            else:
+                raise NotImplementedError(op)
+            self._barrier.wait()         # nobody overwrites the box before every rank has read it
+            return acc
+        return collective
+
+    def step(self, tokens: np.ndarray) -> List[np.ndarray]:
+        import threading
+        out: List[Optional[np.ndarray]] = [None] * self.world
+        errs: List[BaseException] = []
+
+        def run(r):
+            try:
+                out[r] = self.sessions[r].step(tokens)
+            except BaseException as e:      # a failed rank must not leave the others waiting at the barrier
+                errs.append(e)
+                self._barrier.abort()
+
+        ts = [threading.Thread(target=run, args=(r,)) for r in range(self.world)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        if errs:
+            raise errs[0]
         return out

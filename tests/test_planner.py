@@ -1,0 +1,203 @@
+"""Planner: every pass is sound against the CPU oracle (bit-identical logits), the rewritten graph has the expected
+composites, the plan names the kernels the engine launches, buffers never overlap while live, stages recompose,
+and the rank walk of the tensor-parallel graphs matches the single-rank model."""
+import numpy as np
+import pytest
+
+from poot_b200.models.config import DecoderConfig, tiny_llama
+from poot_b200.models.model import Model, StepSpec
+from poot_b200.oracle.eval import eval_graph, EvalOptions
+from poot_b200.oracle.runner import OracleSession, RankWalk, random_weights_f32
+from poot_b200.plan import CompileOptions, Decline, compile_graph, fold_region
+from poot_b200.plan.compile import PIPELINE, run_passes
+from poot_b200.plan.planner import plan_graph
+from poot_b200.plan.refusal import Refusal
+from poot_b200.plan.staging import split_stages
+
+
+def _cfg(**kw):
+    base = dict(name="t", n_layers=2, hidden=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn=96, vocab=257, max_position=128)
+    base.update(kw)
+    return DecoderConfig(**base)
+
+
+def _logits(model, weights, transform=None, steps=3, paged=True):
+    s = OracleSession(model, weights, rows=1, capacity=32, paged=paged, graph_transform=transform)
+    rng = np.random.default_rng(1)
+    outs = [s.step(rng.integers(0, model.cfg.vocab, (1, 7)))]
+    for _ in range(steps):
+        outs.append(s.step(rng.integers(0, model.cfg.vocab, (1, 1))))
+    return outs
+
+
+@pytest.mark.parametrize("stop", PIPELINE)
+def test_every_pass_is_sound_against_the_oracle(stop):
+    model = Model(_cfg())
+    w = random_weights_f32(model, seed=0, std=0.2)
+    ref = _logits(model, w)
+    got = _logits(model, w, lambda g: run_passes(g, CompileOptions(stop_after=stop), {}, []))
+    for a, b in zip(ref, got):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(qk_norm=True), dict(attn_softcap=30.0), dict(sliding_window=8),
+                                dict(n_kv_heads=4), dict(attn_bias=True), dict(rope_dim=8)])
+def test_family_variants_compile_and_stay_exact(kw):
+    try:
+        cfg = _cfg(**kw)
+    except TypeError:
+        pytest.skip("configuration field not present")
+    model = Model(cfg)
+    w = random_weights_f32(model, seed=2, std=0.2)
+    progs = []
+
+    def tf(g):
+        p = compile_graph(g)
+        progs.append(p)
+        return p.graph
+    ref, got = _logits(model, w, steps=1), _logits(model, w, tf, steps=1)
+    for a, b in zip(ref, got):
+        assert np.array_equal(a, b)
+    s = progs[0].graph.summary()
+    assert s.get("attention") == cfg.n_layers and "exp" not in s and "matmul" not in s
+
+
+def test_contiguous_cache_graph_compiles_too():
+    model = Model(_cfg())
+    w = random_weights_f32(model, seed=3, std=0.2)
+    ref = _logits(model, w, paged=False, steps=1)
+    got = _logits(model, w, lambda g: compile_graph(g).graph, paged=False, steps=1)
+    assert all(np.array_equal(a, b) for a, b in zip(ref, got))
+
+
+def test_tiny_llama_program_summary():
+    g = Model(tiny_llama()).trace(StepSpec(rows=1, tokens=1, capacity=64))
+    p = compile_graph(g)
+    s = p.graph.summary()
+    assert s["attention"] == 2 and s["rope"] == 4 and s["fused_row"] == 5 and s["contraction_epilogue"] == 4
+    assert s["dense_contraction"] == 11 and p.log["eqns_in"] > 3 * p.log["eqns_out"] and not p.declines
+    att = next(e for e in p.graph.eqns if e.op == "attention")
+    assert att.attrs["key"] == "paged" and att.attrs["n_rep"] == 2 and abs(att.attrs["scale"] - 0.125) < 1e-12
+    norm = next(e for e in p.graph.eqns if e.op == "fused_row")
+    assert norm.attrs == {"kind": "rmsnorm", "eps": 1e-5}
+    c = p.census
+    # decode step of a 2-layer dense model: 7 projections per layer + the head, one norm kernel per RMSNorm
+    assert c["poot_gemm_skinny"] == 15 and c["poot_rmsnorm"] == 5 and c["poot_attn_paged"] == 2
+    # weights read per token: every projection once, one embedding row
+    cfg = tiny_llama()
+    per_layer = 2 * cfg.hidden * cfg.q_size + 2 * cfg.hidden * cfg.kv_size + 3 * cfg.hidden * cfg.ffn + 2 * cfg.hidden
+    expect = 4 * (cfg.n_layers * per_layer + cfg.hidden + cfg.vocab * cfg.hidden + cfg.hidden)
+    assert p.read_traffic() == expect
+
+
+def test_buffer_plan_never_overlaps_live_values():
+    g = Model(_cfg()).trace(StepSpec(rows=1, tokens=8, capacity=32))
+    p = compile_graph(g)
+    b = p.buffers
+    vals = list(b.offsets)
+    for i, u in enumerate(vals):
+        for v in vals[i + 1:]:
+            (s0, e0), (s1, e1) = b.lifetimes[u], b.lifetimes[v]
+            if e0 < s1 or e1 < s0:
+                continue
+            (o0, z0), (o1, z1) = b.offsets[u], b.offsets[v]
+            assert o0 + z0 <= o1 or o1 + z1 <= o0, (u, v)
+    assert b.arena_bytes < b.sum_bytes and all(o % 256 == 0 for o, _ in b.offsets.values())
+
+
+def test_fold_region_declines_when_a_value_escapes_early():
+    g = Model(_cfg()).trace(StepSpec(rows=1, tokens=2, capacity=32))
+    users = g.users()
+    k = next(i for i, e in enumerate(g.eqns) if e.op not in ("broadcast", "reshape") and len(users.get(e.outputs[0], [])) >= 2)
+    far = max(users[g.eqns[k].outputs[0]])
+    with pytest.raises(Decline):
+        fold_region(g.copy(), {k, far}, "fused", {"kind": "pointwise"})
+
+
+def test_planner_refuses_with_a_typed_error():
+    from poot_b200.ir.builder import Builder
+    from poot_b200.tensor import DType
+    b = Builder()
+    x = b.input("x", (4, 8), DType.F32)
+    y = b.emit("scan", [x], {"kind": "cumsum", "axis": 1})[0] if False else None
+    g = Model(_cfg()).trace(StepSpec(rows=1, tokens=1, capacity=32))
+    g.eqns[5].op = "all_to_all"
+    with pytest.raises(Refusal) as e:
+        plan_graph(g)
+    assert e.value.eqn == 5 and e.value.target == "sm_100a" and "all_to_all" in str(e.value)
+
+
+def test_stage_split_recomposes():
+    model = Model(_cfg())
+    w = random_weights_f32(model, seed=4, std=0.2)
+    g = compile_graph(model.trace(StepSpec(rows=1, tokens=3, capacity=32))).graph
+    sess = OracleSession(model, w, rows=1, capacity=32)
+    toks = np.array([[5, 6, 7]], dtype=np.int32)
+    ref = sess.step(toks)
+    cut = next(k for k, e in enumerate(g.eqns) if e.op == "attention") + 3
+    stages, bounds = split_stages(g, [cut])
+    assert len(stages) == 2 and bounds and all(b.producer == 0 and b.consumers == [1] for b in bounds)
+    s2 = OracleSession(model, w, rows=1, capacity=32)
+    s2.graphs[3] = g
+    inputs = {}
+    # feed through the session's own input builder by running stage by stage
+    carried = {}
+    full_inputs = {}
+
+    def run_stage(sg, extra):
+        s = OracleSession(model, w, rows=1, capacity=32)
+        s.graphs[3] = sg
+        orig = eval_graph
+
+        return s
+    # simple route: evaluate with explicit inputs
+    pos = np.arange(3, dtype=np.int32)[None]
+    feed = {"tokens": toks, "positions": pos, "read_map": np.arange(32, dtype=np.int32)[None],
+            "write_map": np.arange(3, dtype=np.int32)}
+    for i in g.inputs:
+        if i.storage == "const":
+            feed[i.name] = w[i.name]
+        elif i.storage == "state":
+            feed[i.name] = np.zeros(g.types[i.value].shape, np.float32)
+    opt = EvalOptions(matmul_precision="exact")
+    whole = eval_graph(g, feed, opt).outputs
+    ev0 = eval_graph(stages[0], {k: v for k, v in feed.items() if any(i.name == k for i in stages[0].inputs)}, opt).outputs
+    feed1 = {k: v for k, v in feed.items() if any(i.name == k for i in stages[1].inputs)}
+    feed1.update({b.name: ev0[b.name] for b in bounds})
+    ev1 = eval_graph(stages[1], feed1, opt).outputs
+    assert np.array_equal(ev1["logits"], whole["logits"]) and np.array_equal(whole["logits"], ref)
+    for name in whole:
+        got = ev0.get(name, ev1.get(name))
+        assert np.array_equal(got, whole[name]), name
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_rank_walk_of_the_sharded_graphs_matches_one_rank(world):
+    model = Model(_cfg(n_heads=8, n_kv_heads=4, ffn=128, vocab=256))
+    w = random_weights_f32(model, seed=5, std=0.2)
+    ref = _logits(model, w, steps=2)
+    walk = RankWalk(model, w, world, rows=1, capacity=32, graph_transform=lambda g: compile_graph(g, CompileOptions(world=world)).graph)
+    rng = np.random.default_rng(1)
+    outs = [walk.step(rng.integers(0, model.cfg.vocab, (1, 7)))]
+    for _ in range(2):
+        outs.append(walk.step(rng.integers(0, model.cfg.vocab, (1, 1))))
+    for r, per_rank in zip(ref, outs):
+        for got in per_rank:
+            assert np.allclose(got, r, rtol=1e-5, atol=1e-6)        # partial sums reassociate the K reduction
+        assert all(np.array_equal(per_rank[0], x) for x in per_rank[1:])   # every rank holds the same result
+    g0 = walk.sessions[0].graphs[1]
+    assert g0.summary().get("all_reduce") == 2 * model.cfg.n_layers
+
+
+def test_moe_graph_compiles_and_stays_exact():
+    model = Model(_cfg(n_experts=4, top_k=2, moe_ffn=32, family="mixtral"))
+    w = random_weights_f32(model, seed=6, std=0.2)
+    progs = []
+
+    def tf(g):
+        progs.append(compile_graph(g))
+        return progs[-1].graph
+    ref, got = _logits(model, w, steps=1), _logits(model, w, tf, steps=1)
+    assert all(np.array_equal(a, b) for a, b in zip(ref, got))
+    s = progs[0].graph.summary()
+    assert s["attention"] == 2 and s["fused_row"] == 5
