@@ -98,6 +98,8 @@ def main() -> None:
     ap.add_argument("--skip-bs1", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch between kernels")
     ap.add_argument("--gemv-max-m", type=int, default=None, help="rows served by the SIMT GEMV (0 = tensor cores)")
+    ap.add_argument("--dev-set", action="append", default=[], metavar="FIELD=INT",
+                    help="development only: override a model field, e.g. n_layers=2 (the JSON line is marked invalid)")
     ap.add_argument("--quant", default="none", choices=["none", "q4_k"],
                     help="q4_k: Q4_K projections + Q8_0 embeddings, batch-1 decode after a 128-token prompt")
     args = ap.parse_args()
@@ -135,13 +137,17 @@ def main() -> None:
     if args.gemv_max_m is not None:
         K.GEMV_MAX_M = args.gemv_max_m
     cfg = PRESETS[args.model]()
+    for kv in args.dev_set:
+        field, _, val = kv.partition("=")
+        setattr(cfg, field, int(val))
     W, Ksteps, B, P = max(args.warmup, 3), args.steps, args.batch, args.prompt
     max_len = P + (W + Ksteps) * 2 + 64
     bps = (max_len + 15) // 16
     if args.quant == "q4_k":
         weights = random_quant_weights(cfg, dev, "Q4_K", "Q8_0", seed=0, tp_rank=rank, tp_world=world)
     else:
-        weights = random_weights(cfg, dev, seed=0, tp_rank=rank, tp_world=world)
+        ep = world if cfg.is_moe else 1      # experts split over the ranks, attention tensor-parallel over the same ranks
+        weights = random_weights(cfg, dev, seed=0, tp_rank=rank, tp_world=world, ep_rank=rank if ep > 1 else 0, ep_world=ep)
     prefill_chunk_seqs = max(1, min(B, 2048 // P))
     eng = DecoderEngine(weights, num_blocks=B * bps + bps, max_seqs=B, max_tokens=max(prefill_chunk_seqs * P, B),
                         max_blocks_per_seq=bps, comm=comm)
@@ -253,9 +259,10 @@ def main() -> None:
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": Ksteps, "warmup": W,
             "ms_per_step": ms_dev / Ksteps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": value / PUBLISHED_DECODE_TOK_S, "dtype": "bf16", "data": "synthetic",
-            "config": {"model": cfg.name + ("" if args.quant == "none" else "-Q4_K(proj)+Q8_0(embed)"), "global_batch": B, "seq_len": P, "parallelism": f"tp{world}",
+            "config": {"model": cfg.name + ("" if args.quant == "none" else "-Q4_K(proj)+Q8_0(embed)"), "global_batch": B, "seq_len": P, "parallelism": (f"ep{world}+tp{world}(attention)" if cfg.is_moe and world > 1 else f"tp{world}"),
+                       **({"INVALID": "development run with " + ",".join(args.dev_set)} if args.dev_set else {}),
                        "comm": args.comm if world > 1 else "none",
-                       "l2": "inputs larger than L2: 16 GB of weights stream from HBM every step",
+                       "l2": f"inputs larger than L2: {weights.nbytes() / 2**30:.1f} GiB of weights per rank stream from HBM every step",
                        "kv": "paged, block 16, bf16", "decode": "CUDA graph replay per token, greedy"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": sessB.h2d_bytes(B, B),

@@ -112,10 +112,11 @@ def chunk_plan(n: int, chunk: int, granule: int = 16) -> List[int]:
 
 
 def _bucket(n: int, cap: int) -> int:
+    """Step shapes are padded to powers of two (and to the cap above the last one): few distinct captured graphs."""
     b = 1
     while b < n:
         b *= 2
-    return min(b, cap) if b <= cap else n
+    return b if b <= cap else max(cap, n)
 
 
 class Driver:
@@ -292,6 +293,10 @@ class Driver:
                 self.stats["prefill_tokens"] += piece
             else:
                 self.stats["decode_tokens"] += piece
+            if sampled and s.generated == 0 and self.prefix is not None:
+                # the prompt's K/V is complete: later arrivals may share its full blocks while this one still decodes
+                n_full = min(s.prompt_len, s.computed) // BLOCK
+                self.prefix.register(s.tokens[:n_full * BLOCK], s.blocks[:n_full], s.identity)
             if sampled:
                 tok, bad = int(picked[b, 0]), int(picked[b, 1])
                 lp = float(logprobs[b]) if logprobs is not None else None

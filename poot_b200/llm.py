@@ -49,6 +49,11 @@ class LLM:
             free, _ = torch.cuda.mem_get_info(dev)
             shapes = capacity.fit(cfg, free, rows, max_seq, prefill_chunk, weights.tp_world, kv_fraction=kv_fraction)
             rows, max_seq, prefill_chunk, num_blocks = shapes.rows, shapes.max_seq, shapes.prefill_chunk, shapes.num_blocks
+            if comm is not None:      # every rank must agree: take the smallest fit over the group
+                import torch.distributed as dist
+                t = torch.tensor([rows, max_seq, prefill_chunk, num_blocks], dtype=torch.int64, device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                rows, max_seq, prefill_chunk, num_blocks = (int(v) for v in t.tolist())
         max_tokens = max(prefill_chunk, rows) + rows            # widest prefill piece + one decode row per sequence
         eng = DecoderEngine(weights, num_blocks, rows, max_tokens, blocks_for(max_seq), comm=comm)
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)

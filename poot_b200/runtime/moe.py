@@ -51,7 +51,11 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
     e0 = eng.w.ep_rank * e_local
     logits = buf["logits"][:T]
     eng._count(2)
-    K.linear(x, L.router, K.EPI_F32, logits)
+    if T > 128 and E % 8:        # the tiled GEMM wants 8-aligned N: narrow routers go through the skinny kernel in row chunks
+        for t0 in range(0, T, 128):
+            K.linear(x[t0:t0 + 128], L.router, K.EPI_F32, logits[t0:t0 + 128])
+    else:
+        K.linear(x, L.router, K.EPI_F32, logits)
     ids, gates = buf["ids"][:T * k], buf["gates"][:T * k]
     dense = buf["dense"][:E * T].view(E, T)
     M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense)
@@ -66,6 +70,19 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
         M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, parts, 1, G, group_expert=ids, x_row_mul=1, out_group_stride=H,
                        row_scale=gates, ldo=H)
         M.moe_combine(h, parts, h, T, H, G, H, per_token=k)
+        return None
+    if ep is not None and e_local == 1 and T > 128:
+        # prefill with one expert per rank: two tiled GEMMs over all T rows (the expert's weights are read once);
+        # the gate (0 for tokens routed elsewhere) scales the activation rows before the down projection
+        act = eng.act[:T]
+        eng._count(4)
+        K.linear(x, L.ex_wgu[0], K.EPI_SWIGLU, act)
+        act.mul_(dense[e0, :T].unsqueeze(1))
+        import torch.distributed as dist
+        p = eng.comm.partial[:T]
+        K.linear(act, L.ex_wdown[0], K.EPI_STORE, p)
+        dist.all_reduce(p, group=eng.comm.group)
+        K.add(h, p, out=h)
         return None
     # dense-over-experts regime, in token chunks of at most 128 rows
     for t0 in range(0, T, 128):

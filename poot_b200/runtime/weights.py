@@ -55,6 +55,8 @@ class DecoderWeights:
 
         def add(t):
             nonlocal n
+            if hasattr(t, "packed"):          # block-quantised weight
+                t = t.packed
             if isinstance(t, torch.Tensor) and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 n += t.numel() * t.element_size()

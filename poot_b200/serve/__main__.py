@@ -33,7 +33,9 @@ def main(argv=None) -> int:
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
         dist.init_process_group("nccl")
         from ..parallel.tp import make_comm
-        comm = make_comm("fused", rank, world)
+        comm = make_comm("fused", rank, world, torch.device("cuda", torch.cuda.current_device()))
+        from .follower import init_control_group
+        init_control_group()
     if cfg.model == "fake":
         llm = LLM.fake(rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk)
     elif cfg.model.startswith("random:"):
@@ -46,7 +48,7 @@ def main(argv=None) -> int:
         from .follower import follow, LeaderStepEngine
         if rank != 0:
             follow(llm.driver.engine)
-            return 0
+            _leave(llm)
         llm.driver.engine = LeaderStepEngine(llm.driver.engine)
     template = cfg.chat_template
     if cfg.chat_template_file:
@@ -74,8 +76,21 @@ def main(argv=None) -> int:
     server.shutdown()
     if world > 1:
         llm.driver.engine.stop_followers()
+        _leave(llm)
     llm.close()
     return 0
+
+
+def _leave(llm) -> None:
+    """Multi-rank exit: meet, release the peer mappings, and leave without running the process group's destructors
+    (tearing down a group that owns captured collectives can block)."""
+    import torch
+    import torch.distributed as dist
+    torch.cuda.synchronize()
+    dist.barrier()
+    llm.close()
+    sys.stdout.flush()
+    os._exit(0)
 
 
 if __name__ == "__main__":

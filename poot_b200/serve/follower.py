@@ -13,11 +13,22 @@ from typing import List, Tuple
 import numpy as np
 
 
+_control = None
+
+
+def init_control_group():
+    """A host-side (gloo) group for the step announcements, so they never touch the GPU streams.  Collective: every
+    rank calls it once after ``init_process_group``."""
+    global _control
+    import torch.distributed as dist
+    _control = dist.new_group(backend="gloo")
+    return _control
+
+
 def _bcast_obj(obj, src: int = 0):
-    import torch
     import torch.distributed as dist
     box = [obj]
-    dist.broadcast_object_list(box, src=src)
+    dist.broadcast_object_list(box, src=src, group=_control)
     return box[0]
 
 

@@ -362,6 +362,7 @@ def make_handler(state: ServerState):
             self.send_header("Connection", "close")
             self.end_headers()
             self.connection.settimeout(cfg.write_timeout_secs)
+            self.connection.setsockopt(socket.IPPROTO_TCP, socket.TCP_NODELAY, 1)   # one small write per token
             rid = ("chatcmpl-" if chat else "cmpl-") + uuid.uuid4().hex[:24]
             obj = "chat.completion.chunk" if chat else "text_completion"
 
