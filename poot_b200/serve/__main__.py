@@ -75,7 +75,10 @@ def main(argv=None) -> int:
     stop.wait()
     server.shutdown()
     if world > 1:
-        llm.driver.engine.stop_followers()
+        try:
+            llm.driver.engine.stop_followers()
+        except RuntimeError:      # the launcher already signalled the followers: nothing left to stop
+            os._exit(0)
         _leave(llm)
     llm.close()
     return 0

@@ -410,7 +410,11 @@ class Server:
     def __init__(self, state: ServerState):
         host, _, port = state.cfg.addr.rpartition(":")
         self.state = state
-        self.httpd = ThreadingHTTPServer((host, int(port)), make_handler(state))
+        class _Listener(ThreadingHTTPServer):
+            request_queue_size = max(128, min(state.cfg.max_connections, 1024))   # a burst of connections must not be reset
+            daemon_threads = True
+
+        self.httpd = _Listener((host, int(port)), make_handler(state))
         self.httpd.handle_error = lambda request, client_address: None   # a peer that hangs up is not news
         self.httpd.daemon_threads = True
         self.thread: Optional[threading.Thread] = None
