@@ -32,6 +32,7 @@ class ModelHandle:
     source: str
     kind: str                              # "hf" | "gguf"
     tokenizer_dir: Optional[str] = None
+    adapter: Optional[str] = None          # name of the merged LoRA adapter, if any
 
     @property
     def cfg(self) -> DecoderConfig:
@@ -69,6 +70,24 @@ class ModelHandle:
 
     def f32(self, name: str) -> np.ndarray:
         return self.canonical[name].to_f32()
+
+    def apply_adapter(self, adapter) -> None:
+        """Merge a LoRA adapter into the targeted projections (``W + scale * B @ A``), replacing their stored tensors
+        by f32 ones; refused over block-quantised projections."""
+        from ..load.lora import LoraError
+        from .features import Feature, Incompatible
+        for canon in adapter.deltas:
+            if canon not in self.canonical:
+                raise LoraError(f"adapter targets {canon}, which the model does not have")
+            w = self.canonical[canon]
+            if w.format not in ("F32", "F16", "BF16"):
+                raise Incompatible(Feature.ADAPTERS, Feature.PACKED_WEIGHTS, f"{canon} is stored as {w.format}")
+            d = adapter.delta(canon)
+            if tuple(d.shape) != tuple(w.shape):
+                raise LoraError(f"{canon}: adapter delta {d.shape} does not match the weight {tuple(w.shape)}")
+            merged = (w.to_f32() + d).astype(np.float32)
+            self.canonical[canon] = PackedWeight(w.name, "F32", tuple(w.shape), merged.view(np.uint8).reshape(-1))
+        self.adapter = adapter.name
 
     def oracle_weights(self) -> Dict[str, np.ndarray]:
         """Every canonical weight decoded to f32 in the tracer's layout (experts stacked gate-then-up)."""

@@ -65,10 +65,14 @@ class LLM:
     @staticmethod
     def load(path: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
              kv_fraction: float = 0.85, keep_packed: bool = True, tp_rank: int = 0, tp_world: int = 1, comm=None,
-             num_blocks: Optional[int] = None) -> "LLM":
-        """``path``: a Hugging Face directory (config.json + safetensors) or a ``.gguf`` file."""
+             num_blocks: Optional[int] = None, lora: Optional[str] = None) -> "LLM":
+        """``path``: a Hugging Face directory (config.json + safetensors) or a ``.gguf`` file; ``lora``: a PEFT adapter
+        directory merged into the projections at load."""
         from .driver.handle import ModelHandle, device_weights
         handle = ModelHandle.load(path)
+        if lora is not None:
+            from .load.lora import load_adapter
+            handle.apply_adapter(load_adapter(lora))
         weights = device_weights(handle, device, tp_rank, tp_world, keep_packed)
         return LLM._assemble(handle.cfg, weights, _tokenizer_for(handle), rows, max_seq, prefill_chunk, kv_fraction,
                              comm, handle, num_blocks)

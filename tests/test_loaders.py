@@ -110,3 +110,95 @@ def test_name_tables_and_qk_permutation():
     fwd, inv = names.hf_to_gguf_qk_row_order(rows, heads), names.gguf_qk_row_order(rows, heads)
     w = np.arange(rows)
     assert np.array_equal(w[fwd][inv], w)
+
+
+def test_lora_adapter_loads_merges_and_refuses(tmp_path):
+    import json
+    import numpy as np
+    from poot_b200.load import lora
+    from poot_b200.load.safetensors import write_safetensors
+    from poot_b200.tensor import DType
+    rng = np.random.default_rng(0)
+    a = rng.standard_normal((4, 32)).astype(np.float32)
+    b = rng.standard_normal((48, 4)).astype(np.float32)
+    d = tmp_path / "adapter"
+    d.mkdir()
+    (d / "adapter_config.json").write_text(json.dumps({"peft_type": "LORA", "r": 4, "lora_alpha": 8}))
+    write_safetensors(str(d / "adapter_model.safetensors"), {
+        "base_model.model.model.layers.1.self_attn.q_proj.lora_A.weight": (DType.F32, a),
+        "base_model.model.model.layers.1.self_attn.q_proj.lora_B.weight": (DType.F32, b)})
+    ad = lora.load_adapter(str(d))
+    assert ad.rank == 4 and ad.scale == 2.0 and list(ad.deltas) == ["layers.1.attn_q"]
+    w = rng.standard_normal((48, 32)).astype(np.float32)
+    merged = lora.merge_into({"layers.1.attn_q": w, "layers.1.attn_k": w}, ad)
+    assert np.allclose(merged["layers.1.attn_q"], w + 2.0 * b @ a, atol=1e-5) and merged["layers.1.attn_k"] is w
+    with pytest.raises(lora.LoraError):
+        lora.merge_into({"layers.0.attn_q": w}, ad)
+    with pytest.raises(lora.LoraError):
+        lora.merge_into({"layers.1.attn_q": w[:, :16]}, ad)
+    (d / "adapter_config.json").write_text(json.dumps({"peft_type": "LORA", "r": 4, "use_dora": True}))
+    with pytest.raises(lora.LoraError):
+        lora.load_adapter(str(d))
+    (d / "adapter_config.json").write_text(json.dumps({"peft_type": "LORA", "r": 8}))
+    with pytest.raises(lora.LoraError):
+        lora.load_adapter(str(d))
+
+
+def _write_tiny_hf(dirpath, seed=0):
+    """A 2-layer Llama checkpoint in Hugging Face layout (config.json + model.safetensors)."""
+    import json
+    import numpy as np
+    from poot_b200.load.safetensors import write_safetensors
+    from poot_b200.tensor import DType
+    cfg = {"model_type": "llama", "hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4,
+           "num_key_value_heads": 2, "intermediate_size": 96, "vocab_size": 300, "rms_norm_eps": 1e-5,
+           "rope_theta": 10000.0, "max_position_embeddings": 128, "tie_word_embeddings": False, "head_dim": 16}
+    (dirpath / "config.json").write_text(json.dumps(cfg))
+    rng = np.random.default_rng(seed)
+
+    def w(*shape):
+        return (DType.F32, (rng.standard_normal(shape) * 0.1).astype(np.float32))
+    t = {"model.embed_tokens.weight": w(300, 64), "model.norm.weight": (DType.F32, np.ones(64, np.float32)),
+         "lm_head.weight": w(300, 64)}
+    for l in range(2):
+        p = f"model.layers.{l}."
+        t[p + "input_layernorm.weight"] = (DType.F32, np.ones(64, np.float32))
+        t[p + "post_attention_layernorm.weight"] = (DType.F32, np.ones(64, np.float32))
+        t[p + "self_attn.q_proj.weight"] = w(64, 64)
+        t[p + "self_attn.k_proj.weight"] = w(32, 64)
+        t[p + "self_attn.v_proj.weight"] = w(32, 64)
+        t[p + "self_attn.o_proj.weight"] = w(64, 64)
+        t[p + "mlp.gate_proj.weight"] = w(96, 64)
+        t[p + "mlp.up_proj.weight"] = w(96, 64)
+        t[p + "mlp.down_proj.weight"] = w(64, 96)
+    write_safetensors(str(dirpath / "model.safetensors"), t)
+    return cfg
+
+
+def test_model_handle_loads_hf_directory_and_merges_an_adapter(tmp_path):
+    import json
+    import numpy as np
+    from poot_b200.driver.handle import ModelHandle
+    from poot_b200.load import lora
+    from poot_b200.load.safetensors import write_safetensors
+    from poot_b200.oracle.runner import OracleSession
+    from poot_b200.tensor import DType
+    from poot_b200.weights import WeightMap
+    _write_tiny_hf(tmp_path)
+    h = ModelHandle.load(str(tmp_path))
+    assert h.kind == "hf" and h.cfg.n_layers == 2 and h.cfg.n_kv_heads == 2 and not h.cfg.tie_embeddings
+    assert WeightMap(h.canonical).missing(h.cfg) == []
+    base = OracleSession(h.model, h.oracle_weights(), capacity=32).step(np.array([[5, 9, 200]]))
+    rng = np.random.default_rng(1)
+    ad = tmp_path / "ad"
+    ad.mkdir()
+    (ad / "adapter_config.json").write_text(json.dumps({"r": 2, "lora_alpha": 4}))
+    write_safetensors(str(ad / "adapter_model.safetensors"), {
+        "base_model.model.model.layers.0.mlp.down_proj.lora_A.weight": (DType.F32, rng.standard_normal((2, 96)).astype(np.float32)),
+        "base_model.model.model.layers.0.mlp.down_proj.lora_B.weight": (DType.F32, rng.standard_normal((64, 2)).astype(np.float32))})
+    before = h.f32("layers.0.ffn_down").copy()
+    adapter = lora.load_adapter(str(ad))
+    h.apply_adapter(adapter)
+    assert h.adapter == "ad" and np.allclose(h.f32("layers.0.ffn_down"), before + adapter.delta("layers.0.ffn_down"), atol=1e-5)
+    tuned = OracleSession(h.model, h.oracle_weights(), capacity=32).step(np.array([[5, 9, 200]]))
+    assert np.isfinite(tuned).all() and np.abs(tuned - base).max() > 1e-3     # the adapter changes the logits
