@@ -34,6 +34,8 @@ _SIGS = {
                            c_int, _P],
     "poot_attn_paged": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float,
                         c_float, c_int, c_int, _P],
+    "poot_attn_flash_prefill": [_P, c_int, c_int, _P, _P, c_longlong, _P, c_int, _P, c_int, _P, c_int, c_int, c_int,
+                                c_float, c_int, _P, _P],
     "poot_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, _P],
     "poot_argmax": [_P, c_int, c_int, c_int, _P, _P, _P],
     "poot_argmax_partials": [_P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P],
@@ -360,6 +362,49 @@ def attn_paged(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_
                                  _ptr(po), _ptr(pml), R, Hq, Hkv, D, float(scale), float(softcap), int(window),
                                  int(splits), _stream()), "attn_paged")
     return out
+
+
+FLASH_MIN_TOKENS = 16      # prefill pieces at least this long go to the tensor-core kernel
+
+
+def flash_tiles(row_seq, positions, min_tokens: int = FLASH_MIN_TOKENS):
+    """Split a step's rows into tensor-core tiles and rows left to the per-row kernel.
+
+    ``row_seq`` / ``positions``: host int arrays of the step's T rows.  A *segment* is a maximal run of rows of one
+    sequence at consecutive positions; segments of at least ``min_tokens`` rows are cut into tiles of up to 128 rows
+    ``(first row, rows, block-table row, first position)``.  Returns ``(tiles [n, 4] int32, covered [T] bool)``."""
+    import numpy as np
+    seq = np.asarray(row_seq, dtype=np.int64)
+    pos = np.asarray(positions, dtype=np.int64)
+    T = seq.shape[0]
+    covered = np.zeros(T, dtype=bool)
+    if T == 0:
+        return np.zeros((0, 4), np.int32), covered
+    brk = np.flatnonzero((seq[1:] != seq[:-1]) | (pos[1:] != pos[:-1] + 1)) + 1
+    starts = np.concatenate([[0], brk])
+    ends = np.concatenate([brk, [T]])
+    tiles = []
+    for a, b in zip(starts.tolist(), ends.tolist()):
+        if b - a < min_tokens:
+            continue
+        covered[a:b] = True
+        for t0 in range(a, b, 128):
+            tiles.append((t0, min(128, b - t0), int(seq[a]), int(pos[a]) + (t0 - a)))
+    return np.asarray(tiles, dtype=np.int32).reshape(-1, 4), covered
+
+
+def attn_flash_prefill(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_tables: torch.Tensor,
+                       tiles: torch.Tensor, Hq: int, Hkv: int, scale: float, out: torch.Tensor, window: int = 0) -> None:
+    """Tensor-core causal attention over paged K/V for the rows named by ``tiles`` (``[n, 4]`` int32 on the device;
+    entries with zero rows are skipped).  head_dim 128 only; pools are ``[blocks, Hkv, 16, 128]`` bf16."""
+    _need_cuda(q, kpool, vpool)
+    assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and kpool.shape[-1] == 128 and kpool.is_contiguous()
+    assert tiles.dtype == torch.int32 and tiles.shape[1] == 4 and tiles.is_contiguous()
+    st = status_word(q.device)
+    check(_fn("poot_attn_flash_prefill")(_ptr(q), q.stride(0), q.shape[0], _ptr(kpool), _ptr(vpool), kpool.shape[0],
+                                         _ptr(block_tables), block_tables.shape[1], _ptr(tiles), tiles.shape[0],
+                                         _ptr(out), out.stride(0), Hq, Hkv, float(scale), int(window), _ptr(st),
+                                         _stream()), "attn_flash_prefill")
 
 
 ARGMAX_CHUNK = 2048

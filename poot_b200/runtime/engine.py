@@ -116,6 +116,14 @@ class DecoderEngine:
         self.picked = torch.zeros(max_seqs, 2, dtype=i32, device=dev)
         self.logprobs = torch.zeros(max_seqs, dtype=torch.float32, device=dev)
         self.adj_idx = self.adj_val = self.guided_mask = None   # allocated on first use
+        # tensor-core prefill attention: tiles cut on the host per step, rows they cover masked out of the per-row kernel
+        self.flash_ok = cfg.head_dim == 128 and cfg.attn_softcap == 0
+        self._flash_only = False      # set by bind: every row of the bound step is covered by a tile
+        self.attn_tiles = torch.zeros(self._tile_slots(T, max_seqs), 4, dtype=i32, device=dev)
+        self.row_ctx_simt = torch.zeros(T, dtype=i32, device=dev)
+        pin = torch.cuda.is_available()
+        self._h_tiles = torch.zeros(self.attn_tiles.shape, dtype=i32, pin_memory=pin)
+        self._h_ctx_simt = torch.zeros(T, dtype=i32, pin_memory=pin)
         self.argmax_scratch = K.argmax_scratch(max_seqs, cfg.vocab, dev)
         self.attn_splits_max = 16
         ts = self.small_T
@@ -169,6 +177,32 @@ class DecoderEngine:
             K.rmsnorm(h, w, self.cfg.norm_eps, out=x, partials=pending, h_out=h)
         return x
 
+    def _attention(self, l: int, R: int, T: int, B: int, count: bool = True) -> None:
+        """Attention of the step's ``R`` rows (``T`` of them live) into ``self.attn``.
+
+        Steps that carry prefill pieces (more tokens than sampling rows) run two kernels: the per-row paged kernel
+        over the rows left to it (its context length is 0 on rows the tiles cover) and the tensor-core flash kernel
+        over the tiles ``bind`` cut from the step's segments.  Pure decode steps run the per-row kernel alone."""
+        cfg, D = self.cfg, self.cfg.head_dim
+        flash = self.flash_ok and T > B
+        splits = self._attn_splits(R)
+        simt = not (flash and self._flash_only)      # every row sits in a tile: the per-row kernel has nothing to do
+        if count:
+            self._count(((2 if splits > 1 else 1) if simt else 0) + (1 if flash else 0))
+        if simt:
+            K.attn_paged(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:R],
+                         (self.row_ctx_simt if flash else self.row_ctx)[:R], self.hq, self.hkv, D, self.scale,
+                         out=self.attn[:R], splits=splits, scratch=self.attn_scratch, softcap=cfg.attn_softcap,
+                         window=cfg.sliding_window)
+        if flash:
+            K.attn_flash_prefill(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables,
+                                 self.attn_tiles[:self._tile_slots(T, B)], self.hq, self.hkv, self.scale,
+                                 out=self.attn[:R], window=cfg.sliding_window)
+
+    def _tile_slots(self, T: int, B: int) -> int:
+        """Tile slots a (T, B) step can need: full tiles plus one ragged tile per sequence."""
+        return (T + 127) // 128 + B
+
     def _attn_splits(self, T: int) -> int:
         ctas = T * self.hkv * max(1, (self.cfg.n_rep + 3) // 4)
         if ctas >= 148 or T > self.small_T:
@@ -202,11 +236,7 @@ class DecoderEngine:
             self._count()
             K.rope_kv_write(qkv, self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
                             self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
-            splits = self._attn_splits(T)
-            self._count(2 if splits > 1 else 1)
-            K.attn_paged(self.q[:T], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:T],
-                         self.row_ctx[:T], self.hq, self.hkv, D, self.scale, out=self.attn[:T], splits=splits,
-                         scratch=self.attn_scratch, softcap=cfg.attn_softcap, window=cfg.sliding_window)
+            self._attention(l, T, T, B)
             if self.comm is not None:
                 pending = self.comm.row_parallel(self, self.attn[:T], L.wo, T)
             else:
@@ -312,9 +342,7 @@ class DecoderEngine:
             K.linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
             K.rope_kv_write(self.qkv[:T], self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
                             self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
-            K.attn_paged(self.q[:T], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:T], self.row_ctx[:T],
-                         self.hq, self.hkv, D, self.scale, out=self.attn[:T], splits=splits,
-                         scratch=self.attn_scratch, softcap=cfg.attn_softcap, window=cfg.sliding_window)
+            self._attention(l, T, T, B, count=False)
             rs += 1
             comm.gemm_allreduce(self.attn[:T], L.wo, T, rs_site=rs)
             comm.norm_oneshot(h, L.ln2, x, T, cfg.norm_eps, rs_site=rs)
@@ -356,9 +384,7 @@ class DecoderEngine:
             comm.gemm(K.EPI_STORE, None, L.wqkv, self.qkv[:R], S, ag_site=ag)
             K.rope_kv_write(self.qkv[:R], self.q[:R], self.kv.k(l), self.kv.v(l), self.positions[:R], self.slots[:R],
                             self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
-            K.attn_paged(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:R], self.row_ctx[:R],
-                         self.hq, self.hkv, D, self.scale, out=self.attn[:R], splits=self._attn_splits(R),
-                         scratch=self.attn_scratch, softcap=cfg.attn_softcap, window=cfg.sliding_window)
+            self._attention(l, R, T, B, count=False)
             rs += 1
             comm.gemm(K.EPI_STORE, self.attn[:R], L.wo, None, S, rs_site=rs)
             ag += 1
@@ -387,7 +413,9 @@ class DecoderEngine:
 
     # ------------------------------------------------------------------ capture / replay
     def _key(self, shape: StepShape):
-        return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain, shape.adjust, shape.guided, shape.logprobs)
+        flash_only = self.flash_ok and shape.tokens > shape.logit_rows and self._flash_only
+        return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain, shape.adjust, shape.guided, shape.logprobs,
+                flash_only)
 
     def prepare(self, shape: StepShape) -> None:
         """Warm up and capture the step graph for ``shape`` (never done in the serving path afterwards)."""
@@ -439,6 +467,18 @@ class DecoderEngine:
                 self.row_seq[T:R].zero_()
         B = logit_idx.numel()
         self.logit_idx[:B].copy_(logit_idx, non_blocking=non_blocking)
+        if self.flash_ok and T > B:
+            tiles, covered = K.flash_tiles(row_seq.numpy(), positions.numpy())
+            n = self._tile_slots(T, B)
+            self._h_tiles[:n].zero_()
+            self._h_tiles[:tiles.shape[0]] = torch.from_numpy(tiles)
+            self._h_ctx_simt[:T] = row_ctx
+            self._h_ctx_simt[:T][torch.from_numpy(covered)] = 0
+            self._flash_only = bool(covered.all())
+            self.attn_tiles[:n].copy_(self._h_tiles[:n], non_blocking=non_blocking)
+            self.row_ctx_simt[:T].copy_(self._h_ctx_simt[:T], non_blocking=non_blocking)
+            if self.row_ctx_simt.shape[0] > T:
+                self.row_ctx_simt[T:].zero_()
         if block_tables is not None:
             self.block_tables[:block_tables.shape[0], :block_tables.shape[1]].copy_(block_tables,
                                                                                      non_blocking=non_blocking)

@@ -76,3 +76,16 @@ def test_helpers():
     r = run_contained([sys.executable, "-c", "import time; time.sleep(30)"], timeout=0.5)
     assert r.returncode == -9 and "deadline" in r.stderr
     assert run_contained([sys.executable, "-c", "print(7)"]).stdout.strip() == "7"
+
+
+def test_flash_tiles_split_rules():
+    import numpy as np
+    from poot_b200.ops import cuda_ops as K
+    seq = np.array([0] * 300 + [1] + [2] + [3] * 20 + [4] * 5)
+    pos = np.concatenate([np.arange(300), [77], [12], np.arange(40, 60), np.arange(5)])
+    tiles, covered = K.flash_tiles(seq, pos)
+    assert tiles.tolist() == [[0, 128, 0, 0], [128, 128, 0, 128], [256, 44, 0, 256], [302, 20, 3, 40]]
+    assert covered[:300].all() and not covered[300:302].any() and covered[302:322].all() and not covered[322:].any()
+    # the same sequence at non-consecutive positions is two segments
+    tiles, _ = K.flash_tiles(np.array([0] * 40), np.concatenate([np.arange(20), np.arange(100, 120)]))
+    assert tiles.tolist() == [[0, 20, 0, 0], [20, 20, 0, 100]]

@@ -273,3 +273,52 @@ def test_sample_gumbel_matches_oracle(K, rule):
     agree = (out[:, 0].numpy() == ref[:, 0]).mean()
     assert agree >= 0.75, (out, ref)
     assert (out[:, 1] == -1).all()
+
+
+@pytest.mark.parametrize("window", [0, 48])
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
+def test_flash_prefill_matches_reference_over_paged_kv(window, Hq, Hkv):
+    """Tensor-core prefill attention: several sequences, pieces that start mid-sequence, ragged tiles, shuffled pages."""
+    from poot_b200.ops import cuda_ops as K
+    torch.manual_seed(0)
+    D, nblocks, max_blocks = 128, 96, 32
+    # (block-table row, first position, tokens): a fresh 200-token prompt, a 70-token chunk continuing at 300, a short piece
+    segs = [(0, 0, 200), (1, 300, 70), (2, 5, 16), (3, 0, 129)]
+    kpool = (torch.randn(nblocks, Hkv, 16, D, device="cuda") * 0.5).to(torch.bfloat16)
+    vpool = (torch.randn(nblocks, Hkv, 16, D, device="cuda") * 0.5).to(torch.bfloat16)
+    perm = torch.randperm(nblocks)
+    bt = torch.zeros(4, max_blocks, dtype=torch.int32)
+    nxt = 0
+    for r, p0, n in segs:
+        need = (p0 + n + 15) // 16
+        bt[r, :need] = perm[nxt:nxt + need].to(torch.int32)
+        nxt += need
+    row_seq = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, _, n in segs])
+    positions = torch.cat([torch.arange(p0, p0 + n, dtype=torch.int32) for _, p0, n in segs])
+    T = row_seq.numel()
+    q = (torch.randn(T, Hq * D, device="cuda") * 0.5).to(torch.bfloat16)
+    tiles, covered = K.flash_tiles(row_seq.numpy(), positions.numpy())
+    assert covered.all() and tiles.shape[0] == 2 + 1 + 1 + 2
+    tiles_dev = torch.zeros(tiles.shape[0] + 3, 4, dtype=torch.int32, device="cuda")     # trailing empty slots are skipped
+    tiles_dev[:tiles.shape[0]] = torch.from_numpy(tiles).cuda()
+    out = torch.zeros(T, Hq * D, dtype=torch.bfloat16, device="cuda")
+    scale = D ** -0.5
+    K.attn_flash_prefill(q, kpool, vpool, bt.cuda(), tiles_dev, Hq, Hkv, scale, out, window=window)
+    torch.cuda.synchronize()
+    K.check_status()
+    n_rep = Hq // Hkv
+    worst = 0.0
+    for i in range(0, T, 7):           # a spread of rows, every segment and tile boundary included
+        r, p = int(row_seq[i]), int(positions[i])
+        ctx = p + 1
+        blocks = bt[r, :(ctx + 15) // 16].long().cuda()
+        k = kpool[blocks].permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, :ctx].float()
+        v = vpool[blocks].permute(1, 0, 2, 3).reshape(Hkv, -1, D)[:, :ctx].float()
+        lo = max(0, ctx - window) if window else 0
+        qi = q[i].float().view(Hq, D)
+        for h in range(Hq):
+            s = (k[h // n_rep, lo:] @ qi[h]) * scale
+            ref = torch.softmax(s, 0) @ v[h // n_rep, lo:]
+            worst = max(worst, (out[i].float().view(Hq, D)[h] - ref).abs().max().item())
+    assert worst < 2e-2, worst
+    assert torch.isfinite(out.float()).all()
