@@ -53,6 +53,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
 __device__ __forceinline__ float ld_dsmem_f32(uint32_t addr) {
   float v; asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory"); return v;
 }
+__device__ __forceinline__ float4 ld_dsmem_f32x4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 
 template <int BT, int STAGES, int WM>
 struct SkinnySmem {
@@ -236,7 +241,32 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int Mv = (scatter && !tp.oneshot) ? BT : (M < BT ? M : BT);
   const size_t out_off = (size_t)grp_id * (size_t)grp.out_group_stride;
   const float* rscale = grp.row_scale ? grp.row_scale + (size_t)grp_id * M : nullptr;
-  if (EPI == SEPI_SWIGLU) {
+  if (EPI == SEPI_SWIGLU && (slab & 15) == 0 && n0 + slab0 + slab <= N && (ldo & 7) == 0 &&
+      (grp.out_group_stride & 7) == 0 && ((uintptr_t)out & 15) == 0) {
+    // sixteen interleaved (gate, up) columns per thread -> eight outputs, one 16-byte store
+    const int vecs = slab >> 4;
+    for (int idx = threadIdx.x; idx < vecs * Mv; idx += SK_THREADS) {
+      const int pv = idx % vecs, tok = idx / vecs;
+      const int rr = slab0 + 16 * pv;
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = 0.f;
+      for (int c = 0; c < CK; ++c) {
+        uint32_t a = red_s + (uint32_t)((tok * ROWS + rr) * 4);
+        if (CK > 1) a = map_to_cta(a, (uint32_t)c);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const float4 t = ld_dsmem_f32x4(a + 16 * q4);
+          v[4 * q4] += t.x; v[4 * q4 + 1] += t.y; v[4 * q4 + 2] += t.z; v[4 * q4 + 3] += t.w;
+        }
+      }
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = silu(v[2 * j]) * v[2 * j + 1];
+      const int n = n0 + rr;
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + out_off + (size_t)tok * ldo + (n >> 1)) = pack8(o);
+    }
+  } else if (EPI == SEPI_SWIGLU) {
     const int hp = slab >> 1;
     for (int idx = threadIdx.x; idx < hp * Mv; idx += SK_THREADS) {
       const int p = idx % hp, tok = idx / hp;
@@ -251,6 +281,54 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       const int n = n0 + rr;
       if (n < N)
         reinterpret_cast<__nv_bfloat16*>(out)[out_off + (size_t)tok * ldo + (n >> 1)] = __float2bfloat16(silu(g) * u);
+    }
+  } else if ((slab & 7) == 0 && n0 + slab0 + slab <= N && (ldo & 7) == 0 && (grp.out_group_stride & 7) == 0 &&
+             (((uintptr_t)out | (uintptr_t)resid) & 15) == 0 && (!scatter || (tp.ld_inbox & 7) == 0)) {
+    // eight consecutive output columns per thread: 16-byte loads from the cluster's partial tiles and ONE 16-byte
+    // store per destination (a 2-byte store per element and per rank made the collective epilogue the longest
+    // part of the kernel)
+    const int vecs = slab >> 3;
+    for (int idx = threadIdx.x; idx < vecs * Mv; idx += SK_THREADS) {
+      const int pv = idx % vecs, tok = idx / vecs;
+      const int rr = slab0 + 8 * pv;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      for (int c = 0; c < CK; ++c) {
+        uint32_t a = red_s + (uint32_t)((tok * ROWS + rr) * 4);
+        if (CK > 1) a = map_to_cta(a, (uint32_t)c);
+        const float4 lo = ld_dsmem_f32x4(a), hi = ld_dsmem_f32x4(a + 16);
+        v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w;
+        v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+      }
+      const int n = n0 + rr;
+      if (rscale != nullptr) {
+        const float sc = rscale[tok];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] *= sc;
+      }
+      if (scatter && tp.oneshot) {
+        const uint4 pk = pack8(v);
+        const size_t off = ((size_t)((rs_parity * tp.world + tp.rank) * tp.S + tok)) * tp.ld_inbox + n;
+        for (int d = 0; d < tp.world; ++d) *reinterpret_cast<uint4*>(tp.inbox_peer[d] + off) = pk;
+      } else if (scatter) {
+        const int d = tok / tp.S, tl = tok - d * tp.S;
+        *reinterpret_cast<uint4*>(tp.inbox_peer[d] + ((size_t)((rs_parity * tp.world + tp.rank) * tp.S + tl)) * tp.ld_inbox + n) =
+            pack8(v);
+      } else if (EPI == SEPI_F32) {
+        float* o = reinterpret_cast<float*>(out) + out_off + (size_t)tok * ldo + n;
+        *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(v[4], v[5], v[6], v[7]);
+      } else {
+        __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + out_off + (size_t)tok * ldo + n;
+        if (EPI == SEPI_RESID) {
+          float rf[8];
+          unpack8(*reinterpret_cast<const uint4*>(resid + out_off + (size_t)tok * ldo + n), rf);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += rf[j];
+        }
+        *reinterpret_cast<uint4*>(o) = pack8(v);
+      }
     }
   } else {
     for (int idx = threadIdx.x; idx < slab * Mv; idx += SK_THREADS) {

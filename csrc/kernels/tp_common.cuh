@@ -72,13 +72,23 @@ __device__ __forceinline__ uint32_t tp_target(const TpArgs& tp, int site, int si
 
 // Called by every CTA after its peer stores; the last CTA to arrive publishes `target` on channel `ch`
 // of every rank's flag block.  All threads of the CTA must call it (it contains a barrier).
+// Acquire-release fence at system scope.  Deliberately NOT the sequentially consistent fence that
+// __threadfence_system() emits: SC fences are totally ordered across the GPU, so one per CTA serialises a few
+// hundred CTAs behind one another (measured: about 25 us per kernel); acquire-release fences only order this
+// thread's own accesses, which is all the release pattern below needs.
+__device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+
 __device__ __forceinline__ void tp_signal_all(const TpArgs& tp, int ch, uint32_t target, int num_ctas) {
   __syncthreads();  // every thread's peer stores are ordered before thread 0's fence (CTA-scope barrier)
   if (threadIdx.x == 0) {
-    __threadfence_system();  // one system-scope fence per CTA: cumulative over the stores observed above
+    // Release pattern, cumulative by the PTX memory model: this CTA's stores (ordered before thread 0 by the barrier)
+    // -> device-scope fence + ticket -> observed by the last CTA's ticket read -> ONE system-scope fence -> flags.
+    // A system-scope fence in every CTA costs tens of microseconds per kernel: the fences of a few hundred CTAs
+    // queue behind one another at the system port.
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
     int t = atomicAdd(tp.ticket, 1);
     if (t == num_ctas - 1) {
-      __threadfence_system();  // every CTA's stores (observed through the ticket) come before the flags
+      fence_acq_rel_sys();  // every CTA's stores (observed through the ticket) come before the flags
       for (int d = 0; d < tp.world; ++d) st_release_sys(tp.flags_peer[d] + ch * TP_MAX_WORLD + tp.rank, target);
       atomicExch(tp.ticket, 0);
     }
