@@ -26,7 +26,7 @@ constexpr int ATT_WARPS = 4;
 constexpr int ATT_BLOCK = 16;  // keys per pool block
 
 template <int D, int NREP>
-__global__ void __launch_bounds__(ATT_WARPS * 32)
+__global__ void __launch_bounds__(ATT_WARPS * 32, 4)   // four CTAs per SM: 592 slots, so 512 (64 rows x 8 KV heads) run as one wave
 attn_paged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,  // row stride in elements
                   const __nv_bfloat16* __restrict__ kpool, const __nv_bfloat16* __restrict__ vpool,
                   const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ row_seq,
