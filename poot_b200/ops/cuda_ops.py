@@ -138,6 +138,8 @@ _status = {}
 def status_word(device=None) -> torch.Tensor:
     """Per-device int32 word that kernels with bounded waits set non-zero when a wait ran out."""
     dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index is None:       # "cuda" and "cuda:N" must name the same word
+        dev = torch.device("cuda", torch.cuda.current_device())
     s = _status.get(dev)
     if s is None:
         s = torch.zeros(1, dtype=torch.int32, device=dev)
