@@ -100,6 +100,9 @@ def main() -> None:
     ap.add_argument("--gemv-max-m", type=int, default=None, help="rows served by the SIMT GEMV (0 = tensor cores)")
     ap.add_argument("--dev-set", action="append", default=[], metavar="FIELD=INT",
                     help="development only: override a model field, e.g. n_layers=2 (the JSON line is marked invalid)")
+    ap.add_argument("--watchdog", type=float, default=300.0,
+                    help="seconds after which a rank that is still running prints an error line and leaves "
+                         "(a rank stuck in a collective must not keep the GPUs of the whole job)")
     ap.add_argument("--quant", default="none", choices=["none", "q4_k"],
                     help="q4_k: Q4_K projections + Q8_0 embeddings, batch-1 decode after a 128-token prompt")
     args = ap.parse_args()
@@ -108,6 +111,19 @@ def main() -> None:
     if args.impl == "reference":
         reference_arm(args)
         return
+
+    def _expired():
+        # Leaving the process releases the device context; kernels of this rank that are still waiting for a peer
+        # end with it.  Rank 0 says what happened in the one-line format the caller reads.
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"metric": "decode tok/s", "value": None, "n_gpus": args.gpus,
+                              "error": f"watchdog: the run did not finish within {args.watchdog:.0f} s"}), flush=True)
+        os._exit(3)
+
+    import threading
+    dog = threading.Timer(args.watchdog, _expired)
+    dog.daemon = True
+    dog.start()
 
     import torch
     import torch.distributed as dist
@@ -283,4 +299,14 @@ def main() -> None:
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except SystemExit:
+        raise
+    except BaseException as e:      # say what failed in the one-line format, then leave without collective teardown
+        import traceback
+        traceback.print_exc()
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"metric": "decode tok/s", "value": None, "error": f"{type(e).__name__}: {e}"[:400]}), flush=True)
+        sys.stdout.flush()
+        os._exit(1)

@@ -40,7 +40,7 @@ tp_norm_kernel(__nv_bfloat16* __restrict__ h_shard,            // [S, H] residua
     if (threadIdx.x == 0) {
       bool ok = true;
       for (int r = 0; r < tp.world; ++r)
-        if (!wait_flag_ge(tp.flags_local + TP_CH_RS * TP_MAX_WORLD + r, rs_target)) ok = false;
+        if (!wait_flag_ge(tp.flags_local + TP_CH_RS * TP_MAX_WORLD + r, rs_target, status)) ok = false;
       if (!ok) atomicExch(status, (int)kTimeoutPeerFlag);
       s_ok = ok ? 1 : 0;
     }

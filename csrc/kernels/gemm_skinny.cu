@@ -144,7 +144,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         xrow = (int)(target & 1u) * BT;
         // every rank pushed its normalised rows into this rank's gather buffer; wait until all have landed
         for (int r = 0; r < tp.world; ++r)
-          if (!wait_flag_ge(tp.flags_local + TP_CH_AG * TP_MAX_WORLD + r, target)) ok = false;
+          if (!wait_flag_ge(tp.flags_local + TP_CH_AG * TP_MAX_WORLD + r, target, status)) ok = false;
         if (!ok) atomicExch(status, (int)kTimeoutPeerFlag);
         fence_proxy_async_global();  // the rows were written with ordinary (peer) stores; TMA reads them
       }

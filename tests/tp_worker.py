@@ -17,6 +17,10 @@ def main():
     kind = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
+    import threading
+    dog = threading.Timer(240.0, lambda: os._exit(3))    # a rank stuck in a collective must not keep the GPUs
+    dog.daemon = True
+    dog.start()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
