@@ -234,13 +234,15 @@ class Driver:
         rule, off, b = S.GREEDY, 0, 0
         adjust_rows, guided_rows, want_lp = {}, {}, False
         for s, piece in rows:
-            for i in range(piece):
-                pos = s.computed + i
-                tokens[off + i] = s.tokens[pos]
-                positions[off + i] = pos
-                slots[off + i] = self._slot(s, pos)
-                row_seq[off + i] = s.row
-                row_ctx[off + i] = pos + 1
+            # one vectorised fill per piece (a 512-token piece used to cost 512 trips through the interpreter)
+            p0 = s.computed
+            pos = np.arange(p0, p0 + piece, dtype=np.int32)
+            sl = slice(off, off + piece)
+            tokens[sl] = s.tokens[p0:p0 + piece]
+            positions[sl] = pos
+            slots[sl] = np.asarray(s.blocks, dtype=np.int32)[pos // BLOCK] * BLOCK + pos % BLOCK
+            row_seq[sl] = s.row
+            row_ctx[sl] = pos + 1
             if piece == s.pending:
                 logit_idx[b] = off + piece - 1
                 sp = s.params

@@ -32,6 +32,7 @@ class FakeStepEngine:
         if self.fail_at_step is not None and len(self.steps) == self.fail_at_step:
             raise RuntimeError("injected engine fault")
         self.steps.append(inp)
+        self.last_run_ms, self.last_device_ms, self.last_launches = 0.0, None, 0
         self._last_first = []
         B = len(inp.logit_idx)
         picked = np.zeros((B, 2), np.int32)
@@ -82,6 +83,10 @@ class DeviceStepEngine:
         self.h_params, self.h_topk, self.h_seeds = buf((B, 4), torch.float32), buf(B, torch.int32), buf(B, torch.int32)
         self.h_picked, self.h_logprobs = buf((B, 2), torch.int32), buf(B, torch.float32)
         self.h_bt = buf((engine.max_seqs, engine.max_blocks), torch.int32)
+        self.device_timing = False           # bracket each step with CUDA events (opt-in: it adds a synchronisation)
+        self.last_device_ms = None           # None = not measured
+        self.last_run_ms = None
+        self.last_launches = 0
 
     def write_block_table(self, row: int, blocks) -> None:
         n = len(blocks)
@@ -116,11 +121,22 @@ class DeviceStepEngine:
                 for r, m in inp.adjust["guided"].items():
                     e.guided_mask[r].copy_(torch.from_numpy(np.ascontiguousarray(m, dtype=np.float32)))
         shape = StepShape(T, B, inp.sampler, False, inp.adjust is not None, guided, inp.want_logprobs)
+        import time as _time
+        t0 = _time.perf_counter()
+        ev = None
+        if self.device_timing:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         e.run(shape)
+        if ev is not None:
+            ev[1].record()
         self.h_picked[:B].copy_(e.picked[:B], non_blocking=True)
         if inp.want_logprobs:
             self.h_logprobs[:B].copy_(e.logprobs[:B], non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        self.last_run_ms = (_time.perf_counter() - t0) * 1e3
+        self.last_device_ms = ev[0].elapsed_time(ev[1]) if ev is not None else None
+        self.last_launches = e.launches_per_step.get(e._key(shape), 0)
         return self.h_picked[:B].numpy().copy(), (self.h_logprobs[:B].numpy().copy() if inp.want_logprobs else None)
 
     def last_logits(self, rows: int) -> np.ndarray:

@@ -61,8 +61,17 @@ def main(argv=None) -> int:
         from ..driver.speculate import LookupDraft
         draft = LookupDraft.parse(cfg.draft_lookup)
         check([Feature.DRAFT_LOOKUP, *Placement.parse(cfg.placement).features])
+    timing = None
+    if cfg.device_timing:
+        from ..driver.features import Feature, check
+        from ..driver.placement import Placement
+        from ..profile import TimingOptions, TimingSnapshot
+        check([Feature.DEVICE_TIMING, *Placement.parse(cfg.placement).features])     # refused over a device group
+        timing = TimingSnapshot(TimingOptions("detailed", max_steps=cfg.timing_max_steps))
+        if hasattr(llm.driver.engine, "device_timing"):
+            llm.driver.engine.device_timing = True
     engine = ServeEngine(llm.driver, llm.tokenizer, Metrics(), cfg.max_pending_requests, cfg.max_queue_wait_secs,
-                         draft=draft)
+                         draft=draft, timing=timing)
     state = ServerState(engine, cfg, cfg.model_id or os.path.basename(cfg.model.rstrip("/")) or "model",
                         family=llm.cfg.family if llm.cfg is not None else "llama", chat_template=template)
     server = Server(state)

@@ -186,7 +186,13 @@ def make_handler(state: ServerState):
                     h = eng.health()
                     return self._send(200 if h["status"] == "serving" else 503, h)
                 if path == "/metrics":
-                    return self._send(200, eng.metrics.to_json())
+                    body = eng.metrics.to_json()
+                    if eng.timing is not None:
+                        from ..profile import Report
+                        body["device_timing"] = Report.window(eng.timing, entries=256).to_json()
+                        c = eng.timing.counters
+                        body["execution_counters"] = {"dispatches": c.dispatches, "replays": c.replays}
+                    return self._send(200, body)
                 if path == "/metrics/prometheus":
                     return self._send(200, eng.metrics.to_prometheus().encode(), "text/plain; version=0.0.4")
                 if path == "/v1/models":

@@ -63,7 +63,7 @@ class EngineDead(RuntimeError):
 
 class ServeEngine:
     def __init__(self, driver: Driver, tokenizer, metrics: Optional[Metrics] = None, max_pending: int = 256,
-                 max_queue_wait: float = 60.0, on_step: Optional[Callable] = None, draft=None):
+                 max_queue_wait: float = 60.0, on_step: Optional[Callable] = None, draft=None, timing=None):
         self.driver, self.tk = driver, tokenizer
         self.metrics = metrics or Metrics()
         self.inbox: "queue.Queue[Job]" = queue.Queue()
@@ -78,6 +78,7 @@ class ServeEngine:
         self._stop = threading.Event()
         self.on_step = on_step
         self.draft = draft                   # draft policy (``propose(tokens)``) used while one greedy sequence is live
+        self.timing = timing                 # profile.TimingSnapshot, or None: counters only
         self.busy_s = 0.0
         self.metrics.set("poot_slot_capacity", driver.max_rows)
 
@@ -199,7 +200,18 @@ class ServeEngine:
             d.release(e.seq_id, "preempted")
             self._fail(job, str(e), code=500)
             return True
-        self.busy_s += time.monotonic() - t0
+        step_s = time.monotonic() - t0
+        self.busy_s += step_s
+        if self.timing is not None:
+            eng = d.engine
+            run_ms = getattr(eng, "last_run_ms", None)
+            host = {"step": step_s * 1e3}
+            if run_ms is not None:
+                host = {"plan": max(step_s * 1e3 - run_ms, 0.0), "run": run_ms}
+            self.timing.record_step(sum(r.consumed for r in results), len(results), host,
+                                    getattr(eng, "last_device_ms", None))
+            self.timing.counters.dispatches += getattr(eng, "last_launches", 0) or 0
+            self.timing.counters.replays += 1
         m.inc("poot_engine_steps_total")
         m.set("poot_batch_size", len(results))
         if self.on_step is not None:

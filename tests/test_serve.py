@@ -297,3 +297,23 @@ def test_lone_greedy_request_is_served_through_lookup_drafting():
         eng.iteration()
     assert j.wait(1)["finish_reason"] == "length" and j.text == "defghijklmno"
     assert llm.driver.stats["draft_accepted"] >= 4 and llm.driver.stats["steps"] < 12
+
+
+def test_timing_snapshot_is_exposed_and_null_when_unmeasured():
+    from poot_b200.profile import TimingOptions, TimingSnapshot
+    llm = LLM.fake(vocab=1000, rows=4, max_seq=256, num_blocks=128, prefill_chunk=32)
+    cfg = ServeConfig(model="fake", addr="127.0.0.1:0", rows=4)
+    eng = ServeEngine(llm.driver, llm.tokenizer, Metrics(), timing=TimingSnapshot(TimingOptions("detailed", max_steps=64)))
+    srv = Server(ServerState(eng, cfg, "fake-model"))
+    eng.start(); srv.start()
+    try:
+        assert _post(srv.port, "/v1/completions", {"prompt": "a" * 40, "max_tokens": 5})[0] == 200
+        m = json.loads(_get(srv.port, "/metrics")[1])
+        t = m["device_timing"]
+        assert t["steps"] >= 5 and t["device_ms"] is None            # the host engine measures no device time: null, not 0
+        assert set(t["host_ms"]) == {"plan", "run"} and m["execution_counters"]["replays"] == t["steps"]
+    finally:
+        srv.shutdown()
+    with pytest.raises(Exception):
+        from poot_b200.driver.features import Feature, check
+        check([Feature.DEVICE_TIMING, Feature.TENSOR_PLACEMENT])
