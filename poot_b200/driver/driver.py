@@ -276,6 +276,8 @@ class Driver:
                     idx[r, k] = t
                     val[r, k] = e
             adjust = {"idx": idx, "val": val, "guided": guided_rows}
+        from ..ir.analysis import check_write_slots
+        check_write_slots(slots[:T])            # two rows writing one K/V slot in a step would race on the device
         self.stats["padded_tokens"] += Tp - T
         return StepInputs(tokens, positions, slots, row_seq, row_ctx, logit_idx, rule, params, top_k, seeds, adjust,
                           want_lp, T, B)

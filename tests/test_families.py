@@ -1,0 +1,71 @@
+"""Every supported registry family, built from a Hugging Face style config, traces, compiles and keeps the oracle's
+basic laws: decoding token by token equals one-shot prefill, and the planner's rewrite does not change a bit.
+Refused families name what is missing."""
+import numpy as np
+import pytest
+
+from poot_b200.models.registry import Registry, UnsupportedFamily
+from poot_b200.oracle.runner import OracleSession, random_weights_f32
+from poot_b200.plan import compile_graph
+
+BASE = {"hidden_size": 64, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+        "intermediate_size": 96, "vocab_size": 200, "rms_norm_eps": 1e-5, "max_position_embeddings": 128}
+FAMILIES = {
+    "llama": {"model_type": "llama", "rope_theta": 500000.0,
+              "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                               "original_max_position_embeddings": 64}},
+    "mistral": {"model_type": "mistral", "sliding_window": 8},
+    "mixtral": {"model_type": "mixtral", "num_local_experts": 4, "num_experts_per_tok": 2},
+    "qwen2": {"model_type": "qwen2", "tie_word_embeddings": True},
+    "qwen3": {"model_type": "qwen3"},
+    "olmo2": {"model_type": "olmo2"},
+    "phi3": {"model_type": "phi3"},
+    "smollm3": {"model_type": "smollm3"},
+    "granite": {"model_type": "granite", "embedding_multiplier": 12.0, "residual_multiplier": 0.22, "logits_scaling": 8.0},
+    "qwen3moe": {"model_type": "qwen3_moe", "num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 32},
+    "olmoe": {"model_type": "olmoe", "num_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 32},
+}
+
+
+@pytest.mark.parametrize("name", sorted(FAMILIES))
+def test_supported_family_traces_compiles_and_decodes(name):
+    model = Registry.builtin().resolve_hf({**BASE, **FAMILIES[name]})
+    cfg = model.cfg
+    w = random_weights_f32(model, seed=0, std=0.2)
+    rng = np.random.default_rng(3)
+    toks = rng.integers(0, cfg.vocab, (1, 12))
+    one = OracleSession(model, w, capacity=32)
+    full = one.step(toks)
+    steps = OracleSession(model, w, capacity=32)
+    steps.step(toks[:, :7])
+    for t in range(7, 12):
+        last = steps.step(toks[:, t:t + 1])
+    assert np.isfinite(full).all() and np.allclose(last, full, rtol=2e-5, atol=2e-6)
+    progs = []
+
+    def tf(g):
+        progs.append(compile_graph(g))
+        return progs[-1].graph
+    rewritten = OracleSession(model, w, capacity=32, graph_transform=tf).step(toks)
+    assert np.array_equal(rewritten, full)
+    s = progs[0].graph.summary()
+    assert s.get("attention") == cfg.n_layers and "exp" not in {k for k in s if k in ("exp",)} or cfg.is_moe
+    if cfg.sliding_window:
+        far = OracleSession(model, w, capacity=32).step(np.concatenate([rng.integers(0, cfg.vocab, (1, 4)), toks[:, 4:]], 1))
+        # with a window of 8 the last token does not see the first four positions... through one layer; with two layers
+        # information still flows, so only finiteness is asserted here
+        assert np.isfinite(far).all()
+
+
+def test_refused_families_say_what_is_missing():
+    reg = Registry.builtin()
+    for mt, word in (("gemma2", "GeGLU"), ("deepseek_v3", "latent attention"), ("nemotron_h", "Mamba2"),
+                     ("bert", "encoder"), ("qwen2_5_vl", "vision"), ("gpt_oss", "sinks")):
+        with pytest.raises(UnsupportedFamily) as e:
+            reg.resolve_hf({**BASE, "model_type": mt})
+        assert word in str(e.value)
+    with pytest.raises(UnsupportedFamily):
+        reg.resolve_hf({**BASE, "model_type": "never_heard_of_it"})
+    with pytest.raises(UnsupportedFamily):
+        reg.resolve_hf({**BASE, "model_type": "llama", "attention_bias": True})
+    assert len(reg.listed()) == 28 and len(reg.supported()) == 9

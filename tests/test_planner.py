@@ -201,3 +201,25 @@ def test_moe_graph_compiles_and_stays_exact():
     assert all(np.array_equal(a, b) for a, b in zip(ref, got))
     s = progs[0].graph.summary()
     assert s["attention"] == 2 and s["fused_row"] == 5
+
+
+def test_graph_analyses_ranges_guards_and_slots():
+    from poot_b200.ir import analysis as A
+    g = Model(_cfg()).trace(StepSpec(rows=1, tokens=4, capacity=32))
+    p = compile_graph(g)
+    assert A.dispatch_count(p.graph) < A.dispatch_count(g) / 2
+    assert 0 < A.peak_transient_bytes(p.graph) <= p.buffers.sum_bytes
+    guards = A.index_guards(g)
+    kinds = {x.op for x in guards}
+    assert kinds == {"gather", "scatter_update"} and all(x.proven for x in guards)       # declared slot ranges prove every index
+    emb = next(x for x in guards if x.extent == 257)
+    assert emb.range == (0, 256)
+    wm = next(x for x in guards if x.op == "scatter_update")
+    assert wm.range[0] == -1 and wm.allows_skip
+    # an undeclared index input cannot be proven
+    g2 = g.copy()
+    g2.input_named("tokens").range = None
+    assert any(not x.proven for x in A.index_guards(g2))
+    A.check_write_slots(np.array([3, -1, 7, -1]))
+    with pytest.raises(A.DuplicateWriteSlot):
+        A.check_write_slots(np.array([3, 7, 3]))
