@@ -223,3 +223,51 @@ def test_graph_analyses_ranges_guards_and_slots():
     A.check_write_slots(np.array([3, -1, 7, -1]))
     with pytest.raises(A.DuplicateWriteSlot):
         A.check_write_slots(np.array([3, 7, 3]))
+
+
+def test_lora_transform_matches_merged_weights_and_leaves_unadapted_rows_alone():
+    from poot_b200.plan.lora import apply_lora, lora_targets
+    model = Model(_cfg())
+    w = random_weights_f32(model, seed=7, std=0.2)
+    g = model.trace(StepSpec(rows=1, tokens=4, capacity=32, logit_rows="all"))
+    assert "layers.0.attn_q" in lora_targets(g) and "layers.1.ffn_down" in lora_targets(g) and "embed" not in lora_targets(g)
+    targets = ["layers.0.attn_q", "layers.1.ffn_down"]
+    g2 = apply_lora(g, targets, rank=2, adapters=1)
+    rng = np.random.default_rng(0)
+    feed = {"tokens": np.array([[5, 9, 100, 7]], np.int32), "positions": np.arange(4, dtype=np.int32)[None],
+            "read_map": np.arange(32, dtype=np.int32)[None], "write_map": np.arange(4, dtype=np.int32)}
+    for i in g.inputs:
+        if i.storage == "const":
+            feed[i.name] = w[i.name]
+        elif i.storage == "state":
+            feed[i.name] = np.zeros(g.types[i.value].shape, np.float32)
+    opt = EvalOptions(matmul_precision="exact")
+    base = eval_graph(g, feed, opt).outputs["logits"]
+    extra, merged = {}, dict(w)
+    for t in targets:
+        out_f, in_f = w[t].shape
+        a = np.zeros((2, in_f, 2), np.float32); b = np.zeros((2, 2, out_f), np.float32)
+        a[1], b[1] = rng.standard_normal((in_f, 2)) * 0.3, rng.standard_normal((2, out_f)) * 0.3
+        extra[t + ".lora_a"], extra[t + ".lora_b"] = a, b
+        merged[t] = w[t] + 0.5 * (a[1] @ b[1]).T
+    extra["lora.scale"] = np.array([0.0, 0.5], np.float32)
+    none = eval_graph(g2, {**feed, **extra, "lora.idx": np.zeros(4, np.int32)}, opt).outputs["logits"]
+    assert np.array_equal(none, base)                                   # index 0 = no adapter
+    on = eval_graph(g2, {**feed, **extra, "lora.idx": np.ones(4, np.int32)}, opt).outputs["logits"]
+    feed_m = {**feed, **{t: merged[t] for t in targets}}
+    ref = eval_graph(g, feed_m, opt).outputs["logits"]
+    assert np.allclose(on, ref, rtol=1e-4, atol=1e-5) and np.abs(on - base).max() > 1e-3
+    with pytest.raises(ValueError):
+        apply_lora(g, ["layers.9.attn_q"], 2, 1)
+
+
+def test_group_expert_rows_is_stable_and_block_aligned():
+    from poot_b200.plan.moe_align import group_expert_rows
+    ids = np.array([[2, 0], [2, 1], [0, 2], [2, 3]])
+    rows, tile_expert, padded = group_expert_rows(ids, 4, 4)
+    assert padded == 4 * 4 and tile_expert.tolist() == [0, 1, 2, 3]
+    assert rows[:4].tolist() == [1, 4, -1, -1]          # expert 0: flat rows 1 and 4, in order
+    assert rows[8:12].tolist() == [0, 2, 5, 6]          # expert 2 fills its tile exactly
+    assert sorted(r for r in rows.tolist() if r >= 0) == list(range(8))
+    with pytest.raises(ValueError):
+        group_expert_rows(np.array([[4]]), 4, 4)
