@@ -82,7 +82,41 @@ class ClockSampler:
 def reference_arm(args) -> None:
     print(json.dumps({"impl": "reference", "unavailable":
                       "reference is a Rust workspace (pinned nightly, LLVM 22 llc, crates.io deps, no setup.py/"
-                      "pyproject): pip install of /root/reference fails and cargo/rustc are not in the image"}))
+                      "pyproject): pip install of the reference tree fails and cargo/rustc are not in the image"}))
+
+
+def driver_e2e(eng, cfg, B, prompts, W, Ksteps, max_len, timed):
+    """Batch decode through the public serving path: ``Driver.open`` B sequences, prefill them in chunks, then time
+    ``Ksteps`` iterations of ``Driver.step`` (host planning, pinned H2D of the step inputs, graph replay, D2H of the
+    picked tokens) + ``Driver.commit``."""
+    from poot_b200.driver.driver import Driver
+    from poot_b200.driver.engines import DeviceStepEngine
+    from poot_b200.driver.sampler import SamplingParams
+    from poot_b200.ops import cuda_ops as K
+    d = Driver(DeviceStepEngine(eng), eng.kv.num_blocks, B, max_len, cfg.vocab, prefill_chunk=512, prefix_caching=False)
+    # sequences that finish prefill early keep decoding while the others are still being prefilled (one piece per
+    # step), so every sequence needs room for about B extra tokens before the timed region starts
+    budget = min(max_len - prompts.shape[1] - 1, B + W + Ksteps + 16)
+    sids = [d.open(prompts[b].tolist(), SamplingParams(max_tokens=budget, ignore_eos=True)) for b in range(B)]
+
+    def step():
+        for r in d.step(sids):
+            if r.token is not None:
+                d.commit(r.seq_id, [r.token])
+
+    guard = 0
+    while any(d.seqs[s].generated == 0 for s in sids):       # chunked prefill until every sequence has sampled once
+        step()
+        guard += 1
+        if guard > 4 * B + 64:
+            raise RuntimeError("prefill through the driver did not converge")
+    for _ in range(W):
+        step()
+    ms = timed(step, Ksteps)
+    K.check_status()
+    for s in sids:
+        d.release(s, "preempted")
+    return {"tok_s": B * Ksteps / (ms / 1e3), "ms_per_step": ms / Ksteps}
 
 
 def main() -> None:
@@ -268,6 +302,17 @@ def main() -> None:
     e2e_value = B * Ksteps / (ms_e2e / 1e3)
     K.check_status()
 
+    # ---- the same decode measured through the serving driver (open / step / commit), one GPU only ----
+    api = "FixedBatchSession.decode"
+    if world == 1:
+        try:
+            r = driver_e2e(eng, cfg, B, prompts, W, Ksteps, max_len, timed)
+            extra["e2e_session_tok_s"] = e2e_value
+            e2e_value, api = r["tok_s"], "Driver.step + Driver.commit"
+            extra["e2e_driver_ms_per_step"] = r["ms_per_step"]
+        except Exception as e:      # keep the session-level number
+            extra["e2e_driver_error"] = f"{type(e).__name__}: {e}"[:200]
+
     if rank == 0:
         out = {
             "metric": ("decode tok/s (bs1, Q4_K weights), max over ranks" if args.quant != "none" else
@@ -282,7 +327,7 @@ def main() -> None:
                        "kv": "paged, block 16, bf16", "decode": "CUDA graph replay per token, greedy"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": sessB.h2d_bytes(B, B),
-                    "d2h_bytes_per_step": B * 8},
+                    "d2h_bytes_per_step": B * 8, "api": api},
             "gpu_launches": launches,
             "extra": extra,
         }

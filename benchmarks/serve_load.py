@@ -72,7 +72,7 @@ def main():
     ap.add_argument("--port", type=int, default=8123)
     ap.add_argument("--waves", type=int, default=2)
     ap.add_argument("--startup-timeout", type=float, default=420)
-    ap.add_argument("--log", default="gpurun_out/serve_load_server.log")
+    ap.add_argument("--log", default="serve_load_server.log")
     a = ap.parse_args()
 
     serve = ["-m", "poot_b200.serve", a.model, f"127.0.0.1:{a.port}", "--rows", str(a.rows), "--max-seq", str(a.max_seq),

@@ -234,15 +234,18 @@ class Driver:
         rule, off, b = S.GREEDY, 0, 0
         adjust_rows, guided_rows, want_lp = {}, {}, False
         for s, piece in rows:
-            # one vectorised fill per piece (a 512-token piece used to cost 512 trips through the interpreter)
             p0 = s.computed
-            pos = np.arange(p0, p0 + piece, dtype=np.int32)
-            sl = slice(off, off + piece)
-            tokens[sl] = s.tokens[p0:p0 + piece]
-            positions[sl] = pos
-            slots[sl] = np.asarray(s.blocks, dtype=np.int32)[pos // BLOCK] * BLOCK + pos % BLOCK
-            row_seq[sl] = s.row
-            row_ctx[sl] = pos + 1
+            if piece == 1:       # decode row: scalar stores (a numpy slice per row would cost more than the row)
+                tokens[off], positions[off], row_seq[off], row_ctx[off] = s.tokens[p0], p0, s.row, p0 + 1
+                slots[off] = s.blocks[p0 // BLOCK] * BLOCK + p0 % BLOCK
+            else:                # prefill piece: one vectorised fill
+                pos = np.arange(p0, p0 + piece, dtype=np.int32)
+                sl = slice(off, off + piece)
+                tokens[sl] = s.tokens[p0:p0 + piece]
+                positions[sl] = pos
+                slots[sl] = np.asarray(s.blocks, dtype=np.int32)[pos // BLOCK] * BLOCK + pos % BLOCK
+                row_seq[sl] = s.row
+                row_ctx[sl] = pos + 1
             if piece == s.pending:
                 logit_idx[b] = off + piece - 1
                 sp = s.params
