@@ -46,10 +46,29 @@ class ModelHandle:
                 model = registry.resolve_hf(json.load(f))
             store = st.load_weight_store(path)
             canon = {}
+            cfg = model.cfg
             for n in store.names():
                 c = names.canonical_from_hf(n)
                 if c is not None:
                     canon[c] = store[n]
+                    continue
+                # checkpoints that store fused projections (Phi-3: qkv_proj, gate_up_proj) are cut into the
+                # canonical per-role tensors as zero-copy row views
+                fused = names.fused_hf_projection(n)
+                if fused is not None:
+                    layer, kind = fused
+                    w = store[n]
+                    p = f"layers.{layer}."
+                    if kind == "qkv":
+                        q, kv = cfg.q_size, cfg.kv_size
+                        if w.shape[0] != q + 2 * kv:
+                            raise ValueError(f"{n}: {w.shape[0]} rows, expected {q + 2 * kv} (q | k | v)")
+                        canon[p + "attn_q"], canon[p + "attn_k"], canon[p + "attn_v"] = w.rows(0, q), w.rows(q, kv), w.rows(q + kv, kv)
+                    else:
+                        half = w.shape[0] // 2
+                        if half != cfg.ffn:
+                            raise ValueError(f"{n}: {w.shape[0]} rows, expected {2 * cfg.ffn} (gate | up)")
+                        canon[p + "ffn_gate"], canon[p + "ffn_up"] = w.rows(0, half), w.rows(half, half)
             return ModelHandle(model, store, canon, path, "hf", path)
         store = gguf.read_gguf(path)
         arch = store.metadata.get("general.architecture")
@@ -177,6 +196,10 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
         n_in = o.shape[1] // tp_world
         wo = to_device(o.cols(tp_rank * n_in, n_in) if tp_world > 1 else o, device, keep_packed)
         L = LayerWeights(ln1=dense(p + "attn_norm"), ln2=dense(p + "ffn_norm"), wqkv=wqkv, wo=wo)
+        if c.attn_bias:
+            from ..runtime.weights import fuse_qkv_bias
+            L.bqkv = fuse_qkv_bias(dense(p + "attn_q_bias"), dense(p + "attn_k_bias"), dense(p + "attn_v_bias"), c,
+                                   tp_rank, tp_world)
         if c.qk_norm:
             L.q_norm, L.k_norm = dense(p + "attn_q_norm"), dense(p + "attn_k_norm")
         if c.is_moe:
@@ -205,8 +228,9 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
     else:
         vl = head.shape[0] // tp_world
         lm_head = to_device(_rows(head, tp_rank * vl, vl) if tp_world > 1 else head, device, keep_packed)
-    return DecoderWeights(cfg=c, embed=embed, final_norm=dense("final_norm"), lm_head=lm_head, layers=layers,
-                          tp_rank=tp_rank, tp_world=tp_world)
+    from ..runtime.weights import fold_scales
+    return fold_scales(DecoderWeights(cfg=c, embed=embed, final_norm=dense("final_norm"), lm_head=lm_head, layers=layers,
+                                      tp_rank=tp_rank, tp_world=tp_world))
 
 
 def write_random_gguf(path: str, cfg: DecoderConfig, proj_format: str = "Q4_K", embed_format: str = "Q8_0",

@@ -49,6 +49,14 @@ def canonical_from_hf(name: str) -> Optional[str]:
     return None
 
 
+def fused_hf_projection(name: str) -> Optional[Tuple[int, str]]:
+    """``(layer, "qkv" | "gate_up")`` for the fused projection tensors some families store (Phi-3)."""
+    m = re.match(r"model\.layers\.(\d+)\.(self_attn\.qkv_proj|mlp\.gate_up_proj)\.weight$", name)
+    if not m:
+        return None
+    return int(m.group(1)), ("qkv" if m.group(2).endswith("qkv_proj") else "gate_up")
+
+
 def canonical_from_gguf(name: str) -> Optional[str]:
     if name in GGUF_TOP:
         return GGUF_TOP[name]

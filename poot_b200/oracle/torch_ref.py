@@ -4,7 +4,9 @@ It consumes the same fused weight layouts as the engine (``DecoderWeights`` at w
 sequence with a dense causal mask, and follows the op definitions of the reference's op library: RMSNorm
 ``x / sqrt(mean(x^2)+eps) * w`` (crates/poot-graph-ir/src/ops/norm.rs:18-29), half-split RoPE (ops/rope.rs:30-58),
 ``silu(g)*u`` (ops/activation.rs:94-143), blocked GQA ``repeat_kv`` and masked softmax attention
-(ops/attention.rs:260-337), Mixtral routing (softmax over the selected top-k, ops/moe.rs).
+(ops/attention.rs:260-337), Mixtral routing (softmax over the selected top-k, ops/moe.rs).  Constant multipliers of a
+family (residual and logit scales) are already folded into the weights it is given; the embedding scale and the q/k/v
+bias are applied here as the engine applies them.
 """
 from __future__ import annotations
 
@@ -66,13 +68,18 @@ def forward_logits(w: DecoderWeights, tokens: torch.Tensor, round_bf16: bool = T
     cos, sin = rope_tables(cfg, T)
     cos, sin = cos.to(dev), sin.to(dev)
     h = w.embed[tokens.long()].float()
+    if cfg.embed_scale != 1.0:
+        h = r(h * cfg.embed_scale)
     pos = torch.arange(T, device=dev)
     mask = pos[None, :] <= pos[:, None]
     if cfg.sliding_window > 0:
         mask &= pos[None, :] > (pos[:, None] - cfg.sliding_window)
     for L in w.layers:
         x = r(rmsnorm(h, L.ln1, cfg.norm_eps))
-        qkv = r(x @ L.wqkv.float().T)
+        qkv = x @ L.wqkv.float().T
+        if L.bqkv is not None:
+            qkv = r(qkv) + L.bqkv.float()
+        qkv = r(qkv)
         q = qkv[:, :Hq * D].view(T, Hq, D)
         k = qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D)
         v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)

@@ -61,6 +61,12 @@ class DecoderEngine:
     def __init__(self, weights: DecoderWeights, num_blocks: int, max_seqs: int, max_tokens: int,
                  max_blocks_per_seq: int, comm=None, device=None, use_graphs: bool = True):
         cfg = weights.cfg
+        if cfg.final_softcap > 0:
+            from .weights import UnsupportedOnDevice
+            raise UnsupportedOnDevice("soft-capped output logits are not implemented by the device program")
+        if (cfg.residual_scale != 1.0 or cfg.logit_scale != 1.0) and not getattr(weights, "_scales_folded", False):
+            from .weights import fold_scales
+            fold_scales(weights)
         self.cfg, self.w, self.comm = cfg, weights, comm
         self.device = torch.device(device if device is not None else weights.embed.device)
         self.tp = weights.tp_world
@@ -229,10 +235,14 @@ class DecoderEngine:
             K.quant_row_gather(self.tokens[:T], w.embed, out=h)
         else:
             K.embed_gather(self.tokens[:T], w.embed, out=h)
+        if cfg.embed_scale != 1.0:
+            h.mul_(cfg.embed_scale)
         pending = None
         for l, L in enumerate(w.layers):
             x = self._norm(L.ln1, T, pending)
             qkv = self._linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
+            if L.bqkv is not None:
+                qkv.add_(L.bqkv)
             self._count()
             K.rope_kv_write(qkv, self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
                             self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
@@ -331,6 +341,8 @@ class DecoderEngine:
         self._count(3)
         comm.begin_step()
         K.embed_gather(self.tokens[:T], w.embed, out=h)
+        if cfg.embed_scale != 1.0:
+            h.mul_(cfg.embed_scale)
         K.rmsnorm(h, w.layers[0].ln1, cfg.norm_eps, out=x)
         rs = -1
         for l, L in enumerate(w.layers):
@@ -340,6 +352,8 @@ class DecoderEngine:
             splits = self._attn_splits(T)
             self._count(8 + (1 if splits > 1 else 0))
             K.linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
+            if L.bqkv is not None:
+                self.qkv[:T].add_(L.bqkv)
             K.rope_kv_write(self.qkv[:T], self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
                             self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
             self._attention(l, T, T, B, count=False)
@@ -377,11 +391,15 @@ class DecoderEngine:
         self._count(2)
         comm.begin_step()
         K.embed_gather(self.tokens[r0:r0 + S], w.embed, out=comm.h_shard[:S])
+        if cfg.embed_scale != 1.0:
+            comm.h_shard[:S].mul_(cfg.embed_scale)
         ag, rs = 0, -1
         for l, L in enumerate(w.layers):
             self._count(5 + (1 if self._attn_splits(R) > 1 else 0))
             comm.norm(L.ln1, S, cfg.norm_eps, ag_site=ag, rs_site=rs)
             comm.gemm(K.EPI_STORE, None, L.wqkv, self.qkv[:R], S, ag_site=ag)
+            if L.bqkv is not None:
+                self.qkv[:R].add_(L.bqkv)
             K.rope_kv_write(self.qkv[:R], self.q[:R], self.kv.k(l), self.kv.v(l), self.positions[:R], self.slots[:R],
                             self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
             self._attention(l, R, T, B, count=False)

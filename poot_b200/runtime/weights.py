@@ -30,6 +30,7 @@ class LayerWeights:
     wdown: Optional[torch.Tensor] = None
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
+    bqkv: Optional[torch.Tensor] = None     # fused q|k|v bias of families that have one (qwen2), rank-local
     router: Optional[torch.Tensor] = None   # [E, hidden]
     ex_wgu: Optional[torch.Tensor] = None   # [E_local, 2F, hidden]
     ex_wdown: Optional[torch.Tensor] = None  # [E_local, hidden, F]
@@ -67,6 +68,41 @@ class DecoderWeights:
             for v in vars(L).values():
                 add(v)
         return n
+
+
+class UnsupportedOnDevice(ValueError):
+    """The configuration uses a feature the device program does not implement."""
+
+
+def fold_scales(w: "DecoderWeights") -> "DecoderWeights":
+    """Fold the constant multipliers of a family into the weights they multiply, so the device program needs no extra
+    work per token: ``residual_scale`` (Granite) into the o / down projections, ``logit_scale`` into the LM head
+    (on a private copy when the head is tied to the embedding).  ``embed_scale`` stays a runtime multiply because a
+    tied head must see the unscaled table."""
+    cfg = w.cfg
+    if getattr(w, "_scales_folded", False):
+        return w
+    if cfg.residual_scale != 1.0:
+        for L in w.layers:
+            for role in ("wo", "wdown", "ex_wdown"):
+                t = getattr(L, role)
+                if t is None:
+                    continue
+                if not isinstance(t, torch.Tensor):
+                    raise UnsupportedOnDevice("residual_scale cannot be folded into block-quantised projections")
+                setattr(L, role, (t.float() * cfg.residual_scale).to(t.dtype))
+    if cfg.logit_scale != 1.0:
+        if not isinstance(w.lm_head, torch.Tensor):
+            raise UnsupportedOnDevice("logit_scale cannot be folded into a block-quantised LM head")
+        w.lm_head = (w.lm_head.float() * cfg.logit_scale).to(w.lm_head.dtype)     # a new tensor: a tied table stays as is
+    w._scales_folded = True
+    return w
+
+
+def fuse_qkv_bias(bq: torch.Tensor, bk: torch.Tensor, bv: torch.Tensor, cfg: DecoderConfig, rank: int = 0,
+                  world: int = 1) -> torch.Tensor:
+    """Rank-local fused bias in the row order of :func:`fuse_qkv`."""
+    return fuse_qkv(bq[:, None], bk[:, None], bv[:, None], cfg, rank, world)[:, 0].contiguous()
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -126,6 +162,9 @@ def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02,
         del wq, wk, wv
         wo = shard_cols(draw((H, cfg.q_size), t + 3), tp_rank, tp_world)
         L = LayerWeights(ln1=ones(H), ln2=ones(H), wqkv=wqkv, wo=wo)
+        if cfg.attn_bias:
+            L.bqkv = fuse_qkv_bias(draw((cfg.q_size,), t + 60), draw((cfg.kv_size,), t + 61), draw((cfg.kv_size,), t + 62),
+                                   cfg, tp_rank, tp_world)
         if cfg.qk_norm:
             L.q_norm, L.k_norm = ones(D), ones(D)
         if cfg.is_moe:
@@ -153,8 +192,8 @@ def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02,
     lm_head = embed if cfg.tie_embeddings else draw((cfg.vocab, H), 2)
     if tp_world > 1:
         lm_head = shard_rows(lm_head, tp_rank, tp_world)  # vocabulary-parallel head
-    return DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H), lm_head=lm_head, layers=layers, tp_rank=tp_rank,
-                          tp_world=tp_world, ep_rank=ep_rank, ep_world=ep_world)
+    return fold_scales(DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H), lm_head=lm_head, layers=layers,
+                                      tp_rank=tp_rank, tp_world=tp_world, ep_rank=ep_rank, ep_world=ep_world))
 
 
 def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], device, tp_rank: int = 0,
@@ -171,6 +210,8 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
         wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)
         wo = shard_cols(get(p + "attn_o"), tp_rank, tp_world)
         L = LayerWeights(ln1=get(p + "attn_norm"), ln2=get(p + "ffn_norm"), wqkv=wqkv, wo=wo)
+        if cfg.attn_bias:
+            L.bqkv = fuse_qkv_bias(get(p + "attn_q_bias"), get(p + "attn_k_bias"), get(p + "attn_v_bias"), cfg, tp_rank, tp_world)
         if cfg.qk_norm:
             L.q_norm, L.k_norm = get(p + "attn_q_norm"), get(p + "attn_k_norm")
         if cfg.is_moe:
@@ -189,8 +230,8 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
     lm_head = embed if cfg.tie_embeddings or "lm_head" not in tensors else get("lm_head")
     if tp_world > 1:
         lm_head = shard_rows(lm_head, tp_rank, tp_world)
-    return DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm"), lm_head=lm_head, layers=layers,
-                          tp_rank=tp_rank, tp_world=tp_world)
+    return fold_scales(DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm"), lm_head=lm_head, layers=layers,
+                                      tp_rank=tp_rank, tp_world=tp_world))
 
 
 def random_quant_weights(cfg: DecoderConfig, device, proj_format: str = "Q4_K", embed_format: str = "Q8_0", seed: int = 0,

@@ -109,3 +109,25 @@ def test_qk_norm_and_window_model():
     ref = forward_logits(w, toks[0].cuda())[-1]
     err = (eng.logits[0] - ref).abs().max().item()
     assert err < 0.05 * max(1.0, ref.abs().max().item()), err
+
+
+@pytest.mark.parametrize("kw", [dict(attn_bias=True, tie_embeddings=True),                      # qwen2-style
+                                dict(embed_scale=12.0, residual_scale=0.22, logit_scale=0.125),   # granite-style
+                                dict(head_dim=128, n_heads=4, n_kv_heads=1, hidden=512, attn_bias=True)])
+def test_bias_and_constant_multipliers(kw):
+    """q/k/v bias and the embedding scale are applied at run time, residual and logit scales are folded into the weights."""
+    from poot_b200.oracle.torch_ref import forward_logits
+    cfg = _small_cfg(**kw)
+    w, eng, sess = _engine(cfg, batch=2, max_len=64, max_tokens=64)
+    g = torch.Generator().manual_seed(6)
+    toks = torch.randint(0, cfg.vocab, (2, 21), generator=g, dtype=torch.int32)
+    sess.prefill_fast(toks)
+    for b in range(2):
+        ref = forward_logits(w, toks[b].cuda())[-1]
+        err = (eng.logits[b] - ref).abs().max().item()
+        assert err < 0.05 * max(1.0, ref.abs().max().item()), (b, err)
+    nxt = torch.randint(0, cfg.vocab, (2,), generator=g, dtype=torch.int32)
+    sess.decode(nxt.tolist())
+    ref = forward_logits(w, torch.cat([toks[0], nxt[:1]]).cuda())[-1]
+    err = (eng.logits[0] - ref).abs().max().item()
+    assert err < 0.05 * max(1.0, ref.abs().max().item()), err

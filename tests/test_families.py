@@ -69,3 +69,25 @@ def test_refused_families_say_what_is_missing():
     with pytest.raises(UnsupportedFamily):
         reg.resolve_hf({**BASE, "model_type": "llama", "attention_bias": True})
     assert len(reg.listed()) == 28 and len(reg.supported()) == 9
+
+
+@pytest.mark.parametrize("name", ["qwen2", "granite", "llama", "qwen3"])
+def test_torch_restatement_with_folded_scales_matches_the_oracle(name):
+    """The PyTorch restatement the device tests compare against (with the family's constant multipliers folded into
+    the weights, the q/k/v bias and the embedding scale applied at run time) equals the graph oracle on the CPU."""
+    import torch
+    from poot_b200.oracle.torch_ref import forward_logits
+    from poot_b200.runtime.weights import from_named_tensors
+    model = Registry.builtin().resolve_hf({**BASE, **FAMILIES[name]})
+    cfg = model.cfg
+    w = random_weights_f32(model, seed=1, std=0.2)
+    if cfg.attn_bias:
+        assert any(k.endswith("attn_q_bias") for k in w)
+    toks = np.random.default_rng(5).integers(0, cfg.vocab, (1, 10))
+    sess = OracleSession(model, w, capacity=32)
+    sess._graph = lambda T, _m=model: _m.trace(__import__("poot_b200.models.model", fromlist=["StepSpec"]).StepSpec(
+        rows=1, tokens=T, capacity=32, logit_rows="all"))
+    ref = sess.step(toks)
+    dw = from_named_tensors(cfg, {k: torch.from_numpy(v) for k, v in w.items()}, "cpu", dtype=torch.float32)
+    got = forward_logits(dw, torch.from_numpy(toks[0]).int(), round_bf16=False).numpy()
+    assert np.allclose(got, ref.reshape(got.shape), rtol=2e-4, atol=2e-5), np.abs(got - ref.reshape(got.shape)).max()

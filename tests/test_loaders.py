@@ -202,3 +202,31 @@ def test_model_handle_loads_hf_directory_and_merges_an_adapter(tmp_path):
     assert h.adapter == "ad" and np.allclose(h.f32("layers.0.ffn_down"), before + adapter.delta("layers.0.ffn_down"), atol=1e-5)
     tuned = OracleSession(h.model, h.oracle_weights(), capacity=32).step(np.array([[5, 9, 200]]))
     assert np.isfinite(tuned).all() and np.abs(tuned - base).max() > 1e-3     # the adapter changes the logits
+
+
+def test_phi3_fused_projections_are_cut_into_roles(tmp_path):
+    import json
+    import numpy as np
+    from poot_b200.driver.handle import ModelHandle
+    from poot_b200.load.safetensors import write_safetensors
+    from poot_b200.tensor import DType
+    from poot_b200.weights import WeightMap
+    cfg = {"model_type": "phi3", "hidden_size": 64, "num_hidden_layers": 1, "num_attention_heads": 4,
+           "num_key_value_heads": 2, "intermediate_size": 96, "vocab_size": 100, "max_position_embeddings": 128}
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    rng = np.random.default_rng(0)
+    qkv = rng.standard_normal((64 + 2 * 32, 64)).astype(np.float32)
+    gu = rng.standard_normal((192, 64)).astype(np.float32)
+    one = (DType.F32, np.ones(64, np.float32))
+    write_safetensors(str(tmp_path / "model.safetensors"), {
+        "model.embed_tokens.weight": (DType.F32, rng.standard_normal((100, 64)).astype(np.float32)),
+        "model.norm.weight": one, "lm_head.weight": (DType.F32, rng.standard_normal((100, 64)).astype(np.float32)),
+        "model.layers.0.input_layernorm.weight": one, "model.layers.0.post_attention_layernorm.weight": one,
+        "model.layers.0.self_attn.qkv_proj.weight": (DType.F32, qkv),
+        "model.layers.0.self_attn.o_proj.weight": (DType.F32, rng.standard_normal((64, 64)).astype(np.float32)),
+        "model.layers.0.mlp.gate_up_proj.weight": (DType.F32, gu),
+        "model.layers.0.mlp.down_proj.weight": (DType.F32, rng.standard_normal((64, 96)).astype(np.float32))})
+    h = ModelHandle.load(str(tmp_path))
+    assert WeightMap(h.canonical).missing(h.cfg) == []
+    assert np.array_equal(h.f32("layers.0.attn_q"), qkv[:64]) and np.array_equal(h.f32("layers.0.attn_v"), qkv[96:])
+    assert np.array_equal(h.f32("layers.0.ffn_gate"), gu[:96]) and np.array_equal(h.f32("layers.0.ffn_up"), gu[96:])
