@@ -45,6 +45,7 @@ class GenerateArgs:
     reverse_prompt: List[str] = field(default_factory=list)
     ignore_eos: bool = False
     backend: str = "auto"
+    lora: Optional[str] = None
     show_timings: bool = True
     verbose: bool = False
 
@@ -76,6 +77,7 @@ def parse_generate(argv: List[str]) -> GenerateArgs:
     p.add_argument("-r", "--reverse-prompt", action="append", default=[])
     p.add_argument("--ignore-eos", action="store_true")
     p.add_argument("--backend", default="auto")
+    p.add_argument("--lora", help="PEFT adapter directory merged into the projections at load")
     p.add_argument("--show-timings", action=argparse.BooleanOptionalAction, default=True)
     p.add_argument("-v", "--verbose", action="store_true")
     ns = p.parse_args(argv)
@@ -106,7 +108,7 @@ def _open(a: GenerateArgs):
     ctx = a.ctx_size or 4096
     if a.model.startswith("random:"):
         return LLM.random(a.model.split(":", 1)[1], rows=1, max_seq=ctx)
-    return LLM.load(a.model, rows=1, max_seq=ctx)
+    return LLM.load(a.model, rows=1, max_seq=ctx, lora=a.lora)
 
 
 def _template(a: GenerateArgs) -> Optional[str]:

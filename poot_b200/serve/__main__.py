@@ -43,7 +43,7 @@ def main(argv=None) -> int:
                          kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm)
     else:
         llm = LLM.load(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
-                       kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm)
+                       kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm, lora=cfg.lora)
     if world > 1:
         from .follower import follow, LeaderStepEngine
         if rank != 0:

@@ -39,6 +39,7 @@ class ServeConfig:
     kv_fraction: float = 0.85            # share of free device memory given to the KV pool
     allowed_hosts: List[str] = field(default_factory=list)
     model_id: Optional[str] = None
+    lora: Optional[str] = None           # PEFT adapter directory merged into the projections at load
 
     def validate(self) -> None:
         def bound(name, lo, hi):
