@@ -123,12 +123,15 @@ class Driver:
     MAX_ADJ = 1024
 
     def __init__(self, engine, num_blocks: int, max_rows: int, max_seq_len: int, vocab: int, prefill_chunk: int = 512,
-                 prefix_caching: bool = True, eos_token: Optional[int] = None):
+                 prefix_caching: bool = True, eos_token: Optional[int] = None, prefill_budget: Optional[int] = None):
         self.engine = engine
         self.pool = BlockPool(num_blocks)
         self.prefix = PrefixCache(self.pool) if prefix_caching else None
         self.max_rows, self.max_seq_len, self.vocab = max_rows, max_seq_len, vocab
         self.prefill_chunk = prefill_chunk
+        # prefill tokens a step may carry: one chunk (the reference's budget, widest piece + rows) unless raised, in
+        # which case several sequences' pieces share a step and the projections run at a larger, more efficient M
+        self.prefill_budget = max(prefill_budget or prefill_chunk, prefill_chunk)
         self.eos_token = eos_token
         self.max_blocks_per_seq = blocks_for(max_seq_len)
         self.seqs: Dict[int, Sequence_] = {}
@@ -201,6 +204,8 @@ class Driver:
         decode = [s for s in live if s.pending == 1]
         prefill = [s for s in live if s.pending > 1]
         widest = min(max((s.pending for s in prefill), default=0), self.prefill_chunk)
+        if self.prefill_budget > self.prefill_chunk:
+            widest = max(widest, min(sum(min(s.pending, self.prefill_chunk) for s in prefill), self.prefill_budget))
         budget = min(widest + len(live), self.engine.max_tokens)
         rows = [(s, 1) for s in decode]
         used = len(decode)

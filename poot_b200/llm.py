@@ -38,7 +38,7 @@ class LLM:
     # ---- construction --------------------------------------------------------------------------------------------
     @staticmethod
     def _assemble(cfg, weights, tokenizer, rows, max_seq, prefill_chunk, kv_fraction, comm, handle, num_blocks=None,
-                  prefix_caching=True):
+                  prefix_caching=True, prefill_budget=None):
         import torch
         from .driver.engines import DeviceStepEngine
         from .runtime.engine import DecoderEngine, KVPool
@@ -47,25 +47,29 @@ class LLM:
         if num_blocks is None:      # capacity fit against the memory left after the weights are resident
             from .driver import capacity
             free, _ = torch.cuda.mem_get_info(dev)
-            shapes = capacity.fit(cfg, free, rows, max_seq, prefill_chunk, weights.tp_world, kv_fraction=kv_fraction)
-            rows, max_seq, prefill_chunk, num_blocks = shapes.rows, shapes.max_seq, shapes.prefill_chunk, shapes.num_blocks
+            shapes = capacity.fit(cfg, free, rows, max_seq, max(prefill_chunk, prefill_budget or 0), weights.tp_world,
+                                  kv_fraction=kv_fraction)
+            rows, max_seq, num_blocks = shapes.rows, shapes.max_seq, shapes.num_blocks
+            prefill_chunk = min(prefill_chunk, max_seq)
             if comm is not None:      # every rank must agree: take the smallest fit over the group
                 import torch.distributed as dist
                 t = torch.tensor([rows, max_seq, prefill_chunk, num_blocks], dtype=torch.int64, device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
                 rows, max_seq, prefill_chunk, num_blocks = (int(v) for v in t.tolist())
-        max_tokens = max(prefill_chunk, rows) + rows            # widest prefill piece + one decode row per sequence
+        step_prefill = max(prefill_chunk, min(prefill_budget or 0, rows * prefill_chunk))
+        max_tokens = max(step_prefill, rows) + rows             # prefill tokens of a step + one decode row per sequence
         eng = DecoderEngine(weights, num_blocks, rows, max_tokens, blocks_for(max_seq), comm=comm)
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
         eos = getattr(tokenizer, "eos", None)
         drv = Driver(DeviceStepEngine(eng), num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
-                     prefix_caching=prefix_caching, eos_token=eos if eos is not None else cfg.eos_token)
+                     prefix_caching=prefix_caching, eos_token=eos if eos is not None else cfg.eos_token,
+                     prefill_budget=step_prefill)
         return LLM(cfg, drv, tokenizer, eng, handle, comm)
 
     @staticmethod
     def load(path: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
              kv_fraction: float = 0.85, keep_packed: bool = True, tp_rank: int = 0, tp_world: int = 1, comm=None,
-             num_blocks: Optional[int] = None, lora: Optional[str] = None) -> "LLM":
+             num_blocks: Optional[int] = None, lora: Optional[str] = None, prefill_budget: Optional[int] = None) -> "LLM":
         """``path``: a Hugging Face directory (config.json + safetensors) or a ``.gguf`` file; ``lora``: a PEFT adapter
         directory merged into the projections at load."""
         from .driver.handle import ModelHandle, device_weights
@@ -75,27 +79,28 @@ class LLM:
             handle.apply_adapter(load_adapter(lora))
         weights = device_weights(handle, device, tp_rank, tp_world, keep_packed)
         return LLM._assemble(handle.cfg, weights, _tokenizer_for(handle), rows, max_seq, prefill_chunk, kv_fraction,
-                             comm, handle, num_blocks)
+                             comm, handle, num_blocks, prefill_budget=prefill_budget)
 
     @staticmethod
     def random(preset: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
                kv_fraction: float = 0.85, seed: int = 0, std: float = 0.02, tp_rank: int = 0, tp_world: int = 1,
-               comm=None, num_blocks: Optional[int] = None, **over) -> "LLM":
+               comm=None, num_blocks: Optional[int] = None, prefill_budget: Optional[int] = None, **over) -> "LLM":
         """Random-init weights of a named architecture (benchmarks and tests: no checkpoint on disk)."""
         from .runtime.weights import random_weights
         import dataclasses
         cfg = dataclasses.replace(PRESETS[preset](), **over)
         weights = random_weights(cfg, device, seed=seed, std=std, tp_rank=tp_rank, tp_world=tp_world)
-        return LLM._assemble(cfg, weights, None, rows, max_seq, prefill_chunk, kv_fraction, comm, None, num_blocks)
+        return LLM._assemble(cfg, weights, None, rows, max_seq, prefill_chunk, kv_fraction, comm, None, num_blocks,
+                             prefill_budget=prefill_budget)
 
     @staticmethod
     def fake(vocab: int = 1000, rows: int = 8, max_seq: int = 512, num_blocks: int = 256, prefill_chunk: int = 64,
-             fail_at_step: Optional[int] = None) -> "LLM":
+             fail_at_step: Optional[int] = None, prefill_budget: Optional[int] = None) -> "LLM":
         """A driver over the deterministic host engine (next token = last + 1): serving logic without a device."""
         from .driver.engines import FakeStepEngine
         tk = ByteTokenizer(vocab)
-        drv = Driver(FakeStepEngine(vocab, prefill_chunk + rows, fail_at_step), num_blocks, rows, max_seq, vocab,
-                     prefill_chunk=prefill_chunk, eos_token=tk.eos)
+        drv = Driver(FakeStepEngine(vocab, max(prefill_chunk, prefill_budget or 0) + rows, fail_at_step), num_blocks, rows,
+                     max_seq, vocab, prefill_chunk=prefill_chunk, eos_token=tk.eos, prefill_budget=prefill_budget)
         return LLM(None, drv, tk)
 
     # ---- generation ----------------------------------------------------------------------------------------------

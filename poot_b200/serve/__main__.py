@@ -37,13 +37,15 @@ def main(argv=None) -> int:
         from .follower import init_control_group
         init_control_group()
     if cfg.model == "fake":
-        llm = LLM.fake(rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk)
+        llm = LLM.fake(rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, prefill_budget=cfg.prefill_budget or None)
     elif cfg.model.startswith("random:"):
         llm = LLM.random(cfg.model.split(":", 1)[1], rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
-                         kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm)
+                         kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm,
+                         prefill_budget=cfg.prefill_budget or None)
     else:
         llm = LLM.load(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
-                       kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm, lora=cfg.lora)
+                       kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm, lora=cfg.lora,
+                       prefill_budget=cfg.prefill_budget or None)
     if world > 1:
         from .follower import follow, LeaderStepEngine
         if rank != 0:

@@ -17,6 +17,7 @@ class ServeConfig:
     rows: int = 32
     max_seq: int = 4096
     prefill_chunk: int = 512
+    prefill_budget: int = 0              # prefill tokens per step; 0 = one chunk (several chunks share a step when larger)
     kv_dtype: str = "bf16"
     matmul_precision: str = "narrow"
     chat_template: Optional[str] = None

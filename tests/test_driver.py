@@ -123,3 +123,22 @@ def test_sampling_params_encode_rules_and_adjustments():
     assert row[5][0] == 2.0 and abs(row[5][1] - 1 / 1.1) < 1e-6 and abs(row[6][2] - 1.1) < 1e-6
     with pytest.raises(ValueError):
         SamplingParams(top_p=1.5).validate()
+
+
+def test_a_larger_prefill_budget_packs_several_pieces_into_one_step():
+    from poot_b200.llm import LLM
+    def steps(budget):
+        llm = LLM.fake(vocab=5000, rows=8, max_seq=1024, num_blocks=8 * 64 + 8, prefill_chunk=64, prefill_budget=budget)
+        d = llm.driver
+        sids = [d.open([1] + list(range(10 + i, 10 + i + 255)), SamplingParams(max_tokens=200, ignore_eos=True)) for i in range(8)]
+        n = 0
+        while any(d.seqs[s].generated == 0 for s in sids):
+            for r in d.step(sids):
+                if r.token is not None:
+                    d.commit(r.seq_id, [r.token])
+            n += 1
+        widest = max(len(x.tokens) for x in llm.driver.engine.steps)
+        return n, widest
+    one, w1 = steps(None)
+    four, w4 = steps(256)
+    assert four < one / 3 and w1 <= 64 + 8 and 64 + 8 < w4 <= 256 + 8
