@@ -27,11 +27,13 @@ def fold_region(g: Graph, idxs: Iterable[int], op: str, attrs: Optional[dict] = 
     while changed:
         changed = False
         rs = set(region)
-        made = {v for k in region for v in g.eqns[k].outputs}
+        made_by = {v: k for k in region for v in g.eqns[k].outputs}
         for k in list(region):
             e = g.eqns[k]
-            if e.op in ("broadcast", "reshape") and all(v not in made for v in e.inputs) and \
-                    any(u not in rs for u in users0.get(e.outputs[0], [])):
+            if e.op not in ("broadcast", "reshape") or not any(u not in rs for u in users0.get(e.outputs[0], [])):
+                continue
+            # its operands come from outside, or from shaping equations of the region (which then leave with it)
+            if all(v not in made_by or g.eqns[made_by[v]].op in ("broadcast", "reshape") for v in e.inputs):
                 region.remove(k)
                 changed = True
                 break

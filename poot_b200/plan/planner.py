@@ -100,8 +100,83 @@ def plan_eqn(g: Graph, k: int, e: Eqn, world: int = 1) -> Plan:
     raise Refusal(k, op, dt, TARGET, "unknown equation")
 
 
+ABSORBING = {"attention", "rope", "scatter_update", "dynamic_update_slice", "dense_contraction", "packed_contraction",
+             "contraction_epilogue", "matmul", "fused_row", "fused", "sample_token"}
+MOVEMENT = {"transpose", "slice", "concat", "broadcast", "iota", "cast"}
+CONTRACTIONS = {"dense_contraction", "packed_contraction", "contraction_epilogue"}
+
+
 def plan_graph(g: Graph, world: int = 1) -> List[Plan]:
-    return [plan_eqn(g, k, e, world) for k, e in enumerate(g.eqns)]
+    """Plans of every equation, then the absorptions that make the plan match the launches of the device program:
+
+    * contractions that read the same activations (q / k / v; gate / up) run as ONE GEMM over concatenated (or
+      interleaved) weight rows: the first sibling dispatches, the others are ``none``;
+    * the rotary of q and of k, the gathers of the rotary table rows and the K/V scatter are one ``rope_kv_write`` launch;
+    * movement (transpose, slice, concat, broadcast, cast) whose consumers are kernels that index their operands
+      themselves is a ``view``;
+    * attention over a prefill piece (16 rows or more, head_dim 128, no soft cap) runs on the tensor-core flash kernel.
+    """
+    plans = [plan_eqn(g, k, e, world) for k, e in enumerate(g.eqns)]
+    users = g.users()
+    prod = g.producers()
+    by_value = {i.value: i for i in g.inputs}
+    outs = {o.value for o in g.outputs}
+
+    def consumers(v, seen=None):
+        """Non-movement equations that finally read ``v`` (looking through views and movement)."""
+        seen = seen if seen is not None else set()
+        res = []
+        for u in users.get(v, []):
+            e = g.eqns[u]
+            if e.op in MOVEMENT or e.op == "reshape":
+                if u not in seen:
+                    seen.add(u)
+                    res += consumers(e.outputs[0], seen)
+            else:
+                res.append(e.op)
+        if v in outs:
+            res.append("output")
+        return res
+
+    first_by_input: Dict[int, int] = {}
+    rope_seen: Dict[tuple, int] = {}
+    for k, e in enumerate(g.eqns):
+        if e.op in CONTRACTIONS and e.attrs.get("region") != "residual_add":
+            acts = [v for v in e.inputs if not (v in by_value and by_value[v].storage == "const")]
+            x = acts[0] if acts else e.inputs[0]
+            if x in first_by_input:
+                plans[k] = Plan("none", note=f"rows concatenated into the GEMM of eqn {first_by_input[x]} (same activations)")
+            else:
+                first_by_input[x] = k
+        elif e.op == "rope":
+            key = tuple(e.inputs[1:])                 # the same cos / sin rows: q and k of one layer
+            if key in rope_seen:
+                plans[k] = Plan("none", note=f"same launch as the rotary of eqn {rope_seen[key]}")
+            else:
+                rope_seen[key] = k
+        elif e.op in ("scatter_update", "dynamic_update_slice"):
+            plans[k] = Plan("none", note="K/V rows are written by rope_kv_write through the write map")
+        elif e.op == "gather":
+            t = by_value.get(e.inputs[0])
+            if t is not None and t.computed and t.computed[0] in ("rope_cos", "rope_sin"):
+                plans[k] = Plan("none", note="rotary table rows are read inside rope_kv_write")
+            elif all(c in ABSORBING or c == "output" for c in consumers(e.outputs[0])) and \
+                    any(c == "attention" for c in consumers(e.outputs[0])):
+                plans[k] = Plan("none", note="paged K/V is read in place by the attention kernel")
+        elif e.op in MOVEMENT:
+            cs = consumers(e.outputs[0])
+            if cs and all(c in ABSORBING or c == "output" for c in cs):
+                plans[k] = Plan("view" if e.inputs else "none", note="layout handled by the consuming kernel")
+        elif e.op == "fused" and e.attrs.get("kind") == "pointwise":
+            cs = consumers(e.outputs[0])
+            if cs and all(c == "attention" for c in cs):
+                plans[k] = Plan("none", note="the mask is evaluated inside the attention kernel from positions")
+        elif e.op == "attention":
+            o = g.types[e.outputs[0]]
+            rows, d = o.shape[-2], o.shape[-1]
+            if rows >= 16 and d == 128 and not e.attrs.get("softcap"):
+                plans[k] = Plan("dispatch", ["poot_attn_flash_prefill"], plans[k].note)
+    return plans
 
 
 def launch_census(plans: List[Plan]) -> Dict[str, int]:

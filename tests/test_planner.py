@@ -81,8 +81,12 @@ def test_tiny_llama_program_summary():
     norm = next(e for e in p.graph.eqns if e.op == "fused_row")
     assert norm.attrs == {"kind": "rmsnorm", "eps": 1e-5}
     c = p.census
-    # decode step of a 2-layer dense model: 7 projections per layer + the head, one norm kernel per RMSNorm
-    assert c["poot_gemm_skinny"] == 15 and c["poot_rmsnorm"] == 5 and c["poot_attn_paged"] == 2
+    # the launches of the device program for a 2-layer dense decode step: embedding gather, per layer (norm, fused qkv
+    # GEMM, rope + K/V write, split-KV attention + combine, o_proj, norm, fused gate/up GEMM with SwiGLU, down_proj),
+    # final norm, LM head
+    assert c == {"poot_embed_gather": 1, "poot_rmsnorm": 5, "poot_gemm_skinny": 9, "poot_rope_kv_write": 2,
+                 "poot_attn_paged": 2, "poot_attn_combine": 2}
+    assert p.dispatches == 1 + 2 * 9 + 2
     # weights read per token: every projection once, one embedding row
     cfg = tiny_llama()
     per_layer = 2 * cfg.hidden * cfg.q_size + 2 * cfg.hidden * cfg.kv_size + 3 * cfg.hidden * cfg.ffn + 2 * cfg.hidden
@@ -271,3 +275,26 @@ def test_group_expert_rows_is_stable_and_block_aligned():
     assert sorted(r for r in rows.tolist() if r >= 0) == list(range(8))
     with pytest.raises(ValueError):
         group_expert_rows(np.array([[4]]), 4, 4)
+
+
+
+def test_committed_plan_digests_and_launch_census():
+    """Plan digests and launch census of the flagship configurations at their real dimensions (two layers) are pinned
+    in tests/data/plan_digests.tsv; a planner change that moves them has to regenerate the file on purpose."""
+    import os
+    from poot_b200.models.config import PRESETS
+    path = os.path.join(os.path.dirname(__file__), "data", "plan_digests.tsv")
+    rows = [l.rstrip("\n").split("\t") for l in open(path) if not l.startswith("#")]
+    assert len(rows) == 12
+    specs = {"decode-b1": lambda w: StepSpec(rows=1, tokens=1, capacity=64),
+             "prefill-512": lambda w: StepSpec(rows=1, tokens=512, capacity=512),
+             "decode-b1-tp": lambda w: StepSpec(rows=1, tokens=1, capacity=64, world=w)}
+    for name, label, n_in, n_out, digest, dispatches, census in rows:
+        cfg = PRESETS[name]()
+        cfg.n_layers = 2
+        world = 2 if name == "tiny-llama" else 8
+        g = Model(cfg).trace(specs[label](world))
+        prog = compile_graph(g, CompileOptions(world=world if label.endswith("tp") else 1))
+        got = ";".join(f"{k}={v}" for k, v in sorted(prog.census.items()))
+        assert (str(len(g.eqns)), str(len(prog.graph.eqns)), prog.graph.digest(), str(prog.dispatches), got) == \
+            (n_in, n_out, digest, dispatches, census), (name, label)
