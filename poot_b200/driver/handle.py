@@ -45,30 +45,8 @@ class ModelHandle:
             with open(os.path.join(path, "config.json")) as f:
                 model = registry.resolve_hf(json.load(f))
             store = st.load_weight_store(path)
-            canon = {}
-            cfg = model.cfg
-            for n in store.names():
-                c = names.canonical_from_hf(n)
-                if c is not None:
-                    canon[c] = store[n]
-                    continue
-                # checkpoints that store fused projections (Phi-3: qkv_proj, gate_up_proj) are cut into the
-                # canonical per-role tensors as zero-copy row views
-                fused = names.fused_hf_projection(n)
-                if fused is not None:
-                    layer, kind = fused
-                    w = store[n]
-                    p = f"layers.{layer}."
-                    if kind == "qkv":
-                        q, kv = cfg.q_size, cfg.kv_size
-                        if w.shape[0] != q + 2 * kv:
-                            raise ValueError(f"{n}: {w.shape[0]} rows, expected {q + 2 * kv} (q | k | v)")
-                        canon[p + "attn_q"], canon[p + "attn_k"], canon[p + "attn_v"] = w.rows(0, q), w.rows(q, kv), w.rows(q + kv, kv)
-                    else:
-                        half = w.shape[0] // 2
-                        if half != cfg.ffn:
-                            raise ValueError(f"{n}: {w.shape[0]} rows, expected {2 * cfg.ffn} (gate | up)")
-                        canon[p + "ffn_gate"], canon[p + "ffn_up"] = w.rows(0, half), w.rows(half, half)
+            from ..load.hf_map import map_checkpoint
+            canon = map_checkpoint(model.cfg, store)
             return ModelHandle(model, store, canon, path, "hf", path)
         store = gguf.read_gguf(path)
         arch = store.metadata.get("general.architecture")
@@ -115,13 +93,16 @@ class ModelHandle:
         for n, w in self.canonical.items():
             if ".experts." not in n:
                 out[n] = w.to_f32()
-        if c.is_moe:
-            for l in range(c.n_layers):
-                p = f"layers.{l}."
-                gi = np.stack([np.concatenate([self.f32(p + f"experts.{e}.gate"), self.f32(p + f"experts.{e}.up")], 0)
-                               for e in range(c.n_experts)])
-                out[p + "experts_in"] = gi
-                out[p + "experts_out"] = np.stack([self.f32(p + f"experts.{e}.down") for e in range(c.n_experts)])
+        for l in range(c.n_layers):
+            if not c.moe_layer(l):
+                continue
+            p = f"layers.{l}."
+            gi = np.stack([np.concatenate([self.f32(p + f"experts.{e}.gate"), self.f32(p + f"experts.{e}.up")], 0)
+                           for e in range(c.n_experts)])
+            out[p + "experts_in"] = gi
+            out[p + "experts_out"] = np.stack([self.f32(p + f"experts.{e}.down") for e in range(c.n_experts)])
+        if c.tie_embeddings:
+            out.pop("lm_head", None)
         return out
 
 

@@ -149,6 +149,58 @@ def attention_masked(b: Builder, q: Traced, k: Traced, v: Traced, mask: Traced, 
     return b.matmul(softmax(b, scores), v)
 
 
+def alibi_slopes(n_heads: int, kind: str = "bloom", bias_max: float = 8.0) -> list:
+    """Per-head ALiBi slopes.  ``bloom``: geometric series of the closest power of two, the remaining heads take the
+    odd powers of the next series (Press et al.); ``mpt``: ``2^-(i * bias_max / n2)`` over the next power of two
+    ``n2``, odd entries first when ``n_heads`` is not a power of two."""
+    if kind == "mpt":
+        n2 = 2 ** math.ceil(math.log2(n_heads))
+        sl = [1.0 / 2.0 ** (i * bias_max / n2) for i in range(1, n2 + 1)]
+        if n2 != n_heads:
+            sl = (sl[1::2] + sl[::2])[:n_heads]
+        return sl
+    cp2 = 2 ** math.floor(math.log2(n_heads))
+    base = 2.0 ** (-(2.0 ** -(math.log2(cp2) - 3)))
+    sl = [base ** i for i in range(1, cp2 + 1)]
+    if cp2 != n_heads:
+        extra = 2.0 ** (-(2.0 ** -(math.log2(2 * cp2) - 3)))
+        sl += [extra ** i for i in range(1, 1 + 2 * min(cp2, n_heads - cp2), 2)]
+    return sl
+
+
+def alibi_bias_from_pos(b: Builder, q_pos: Traced, cap: int, slopes: Sequence[float]) -> Traced:
+    """Per-head additive bias ``[rows, heads, tokens, cap]``: ``-slope[h] * (p - j)`` for a query at position p and key j
+    (softmax is shift-invariant per row, so this equals the checkpoint families' ``slope * j`` forms)."""
+    R, T = q_pos.shape
+    keys = b.iota((R, T, cap), 2)
+    p = b.broadcast(b.reshape(q_pos, (R, T, 1)), (R, T, cap))
+    rel = b.reshape(b.cast(keys - p, F32), (R, 1, T, cap))
+    return b.concat([rel * float(sl) for sl in slopes], 1)
+
+
+def attention_biased(b: Builder, q: Traced, k: Traced, v: Traced, mask: Traced, scale: float, n_rep: int = 1,
+                     cap: float = 0.0, head_bias: Optional[Traced] = None, sinks: Optional[Traced] = None) -> Traced:
+    """:func:`attention_masked` plus a per-head additive bias ``[rows, heads, T, S]`` (ALiBi) and per-head sink logits
+    ``[heads]`` that join every softmax denominator without contributing a value (ops/attention.rs ``attention_masked_sinks``)."""
+    if head_bias is None and sinks is None:
+        return attention_masked(b, q, k, v, mask, scale, n_rep, cap)
+    k, v = repeat_kv(b, k, n_rep), repeat_kv(b, v, n_rep)
+    scores = b.matmul(q, b.transpose(k, (0, 1, 3, 2))) * scale
+    if cap > 0:
+        scores = softcap(b, scores, cap)
+    R, H, T, S = scores.shape
+    if head_bias is not None:
+        scores = scores + head_bias
+    scores = scores + b.broadcast(b.reshape(mask, (R, 1, T, S)), scores.shape)
+    if sinks is None:
+        return b.matmul(softmax(b, scores), v)
+    sk = b.broadcast(b.reshape(sinks, (1, H, 1, 1)), (R, H, T, 1))
+    m = b.binary("max", scores.max(-1, keepdim=True), sk)
+    e = b.unary("exp", scores - b.broadcast(m, scores.shape))
+    den = e.sum(-1, keepdim=True) + b.unary("exp", sk - m)
+    return b.matmul(e / b.broadcast(den, scores.shape), v)
+
+
 def paged_view(b: Builder, pool: Traced, read_map: Traced) -> Traced:
     """Gather ``pool[slots, kv_heads, D]`` through ``read_map[rows, cap]`` into ``[rows, kv_heads, cap, D]``."""
     g = b.gather(pool, read_map, 0)                 # [rows, cap, kv_heads, D]
@@ -201,6 +253,90 @@ def moe_topk_softmax(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out:
     gu = b.indexed_matmul(xr, b.transpose(w_in, (0, 2, 1)), flat_ids, precision)     # [L*k, 2F]
     act = swiglu(b, b.slice(gu, -1, 0, F), b.slice(gu, -1, F, F))
     y = b.indexed_matmul(act, b.transpose(w_out, (0, 2, 1)), flat_ids, precision) * b.broadcast(gates, (L * k, H))
+    return b.reshape(y, (L, k, H)).transpose(0, 2, 1).sum(-1)
+
+
+def ffn_activation(b: Builder, gate: Traced, up: Optional[Traced], act: str = "silu", limit: float = 0.0,
+                   alpha: float = 1.702) -> Traced:
+    """``act(gate) * up`` for gated FFNs, ``act(gate)`` for plain ones.  ``limit > 0`` is the clamped form
+    ``(min(up, limit) clamped below at -limit + 1) * g * sigmoid(alpha * g)`` with ``g = min(gate, limit)``."""
+    if limit > 0:
+        lim = b.broadcast(b.scalar(limit, F32), gate.shape)
+        g = -b.binary("max", -gate, -lim)
+        u = b.binary("max", -b.binary("max", -up, -lim), -lim)
+        return (u + 1.0) * (g / (1.0 + b.unary("exp", -(g * alpha))))
+    a = {"silu": silu, "gelu_tanh": gelu_tanh, "gelu_erf": gelu_erf, "relu": relu}[act](b, gate)
+    return a * up if up is not None else a
+
+
+def _top2_sum(b: Builder, s: Traced) -> Traced:
+    """Sum of the two largest entries along the last axis (ties counted twice)."""
+    m1 = s.max(-1, keepdim=True)
+    is_max = b.binary("ge", s, b.broadcast(m1, s.shape))
+    cnt = b.cast(is_max, I32).sum(-1, keepdim=True)
+    rest = b.select(is_max, b.broadcast(b.scalar(-F32_MAX, F32), s.shape), s).max(-1, keepdim=True)
+    two = b.binary("ge", cnt, b.broadcast(b.scalar(2, I32), cnt.shape))
+    return b.reshape(m1 + b.select(two, m1, rest), s.shape[:-1])
+
+
+def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Traced, k: int, *,
+               score: str = "softmax", renorm: bool = True, router_bias: Optional[Traced] = None,
+               select_bias: Optional[Traced] = None, n_group: int = 1, topk_group: int = 1, routed_scale: float = 1.0,
+               act: str = "silu", limit: float = 0.0, alpha: float = 1.702, in_bias: Optional[Traced] = None,
+               out_bias: Optional[Traced] = None, precision: str = "narrow") -> Traced:
+    """Routed experts in every variant the shipped families use (components/router.rs, ops/moe.rs).
+
+    ``score``: ``softmax`` over all experts or ``sigmoid`` per expert.  Selection ranks ``score + select_bias`` (the
+    bias does not enter the gate), optionally restricted to the ``topk_group`` best of ``n_group`` expert groups
+    (group score = sum of its two best selection scores; experts outside are ranked as 0).  Gates are the scores at
+    the selected experts, divided by their sum when ``renorm``, times ``routed_scale``.  Experts: ``w_in[E, 2F, H]``
+    gate rows then up rows (+ ``in_bias[E, 2F]``), ``w_out[E, H, F]`` (+ ``out_bias[E, H]``)."""
+    L, H = x.shape
+    E, F2, _ = w_in.shape
+    F = F2 // 2
+    logits = linear(b, x, router, router_bias, precision="exact")
+    if score == "softmax" and renorm and select_bias is None and n_group == 1:
+        # softmax over all, pick k, renormalise == softmax over the k selected logits
+        scores = canonical_router_scores(b, logits)
+        rank = stable_descending_rank(b, scores)
+        keep = lnot(b, b.binary("ge", rank, b.broadcast(b.scalar(k, I32), rank.shape)))
+        sel = b.select(keep, scores, b.broadcast(b.scalar(MASK_HIDDEN, F32), scores.shape))
+        m = sel.max(-1, keepdim=True)
+        ex = b.unary("exp", sel - b.broadcast(m, sel.shape)) * b.cast(keep, F32)
+        gates_all = ex / b.broadcast(ex.sum(-1, keepdim=True), ex.shape)
+    else:
+        probs = softmax(b, logits) if score == "softmax" else sigmoid(b, logits)
+        choice = probs + b.broadcast(select_bias, probs.shape) if select_bias is not None else probs
+        choice = canonical_router_scores(b, choice)
+        if n_group > 1:
+            per = E // n_group
+            gs = _top2_sum(b, b.reshape(choice, (L, n_group, per)))                  # [L, G]
+            grank = stable_descending_rank(b, gs)
+            gkeep = lnot(b, b.binary("ge", grank, b.broadcast(b.scalar(topk_group, I32), grank.shape)))
+            ekeep = b.reshape(b.broadcast(b.reshape(gkeep, (L, n_group, 1)), (L, n_group, per)), (L, E))
+            choice = b.select(ekeep, choice, b.broadcast(b.scalar(0.0, F32), choice.shape))
+        rank = stable_descending_rank(b, choice)
+        keep = b.cast(lnot(b, b.binary("ge", rank, b.broadcast(b.scalar(k, I32), rank.shape))), F32)
+        picked = probs * keep
+        if renorm:
+            den = picked.sum(-1, keepdim=True)
+            if score == "sigmoid":
+                den = den + 1e-20
+            picked = picked / b.broadcast(den, picked.shape)
+        gates_all = picked * routed_scale if routed_scale != 1.0 else picked
+    ids = b.arg_top_k(rank, k)                                              # [L, k]
+    flat_ids = b.reshape(ids, (L * k,))
+    gates = b.reshape(b.gather(b.reshape(gates_all, (L * E,)),
+                               b.reshape(b.iota((L, k), 0) * E, (L * k,)) + flat_ids, 0), (L * k, 1))
+    xr = b.reshape(b.broadcast(b.reshape(x, (L, 1, H)), (L, k, H)), (L * k, H))
+    gu = b.indexed_matmul(xr, b.transpose(w_in, (0, 2, 1)), flat_ids, precision)     # [L*k, 2F]
+    if in_bias is not None:
+        gu = gu + b.gather(in_bias, flat_ids, 0)
+    a = ffn_activation(b, b.slice(gu, -1, 0, F), b.slice(gu, -1, F, F), act, limit, alpha)
+    y = b.indexed_matmul(a, b.transpose(w_out, (0, 2, 1)), flat_ids, precision)
+    if out_bias is not None:
+        y = y + b.gather(out_bias, flat_ids, 0)
+    y = y * b.broadcast(gates, (L * k, H))
     return b.reshape(y, (L, k, H)).transpose(0, 2, 1).sum(-1)
 
 

@@ -1,0 +1,232 @@
+"""Hugging Face checkpoint tensors -> canonical weight roles, per family.
+
+The tracer declares canonical names (``layers.{i}.attn_q``, ``layers.{i}.experts.{e}.gate`` ...); this module maps
+what a family's checkpoint stores onto them (the reference keeps one name table per architecture module,
+crates/poot-models/src/architectures/*.rs).  Most tensors map one to one and stay zero-copy views of the mmapped
+file.  The exceptions are rewritten once at load:
+
+* fused projections are cut into row views (Phi-3 ``qkv_proj`` / ``gate_up_proj``, MPT ``Wqkv``, the stacked
+  ``experts.gate_up_proj[E, 2F, H]`` tensors newer checkpoints use);
+* Bloom's ``query_key_value`` is stored per head as ``(q, k, v)`` triples and is de-interleaved;
+* gpt-oss experts are stored ``[E, H, 2F]`` with gate and up columns alternating; they are transposed into
+  checkpoint order (``[out, in]``) with the gate rows first;
+* Gemma norm weights are stored as ``w - 1`` and get the one added;
+* DeepSeek stores rotary channels as interleaved pairs; the rows that produce them are re-ordered into the
+  half-split order the rotary op uses (a common permutation of q and k channels leaves q.k unchanged).
+"""
+from __future__ import annotations
+
+import re
+from typing import Callable, Dict, Optional
+
+import numpy as np
+
+from ..models.config import DecoderConfig
+from ..quant.formats import descriptor
+from ..quant.weights import PackedWeight, WeightStore
+
+
+class CheckpointLayout(ValueError):
+    """A tensor the family's table expects is missing or has the wrong extent."""
+
+
+def f32_weight(name: str, a: np.ndarray) -> PackedWeight:
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return PackedWeight(name, "F32", tuple(a.shape), a.view(np.uint8).reshape(-1))
+
+
+def first_axis(w: PackedWeight, i: int) -> PackedWeight:
+    """``w[i]`` of a stacked tensor as a view (dense and block formats are contiguous per leading index)."""
+    d = descriptor(w.format)
+    if d.storage == "planar":
+        raise CheckpointLayout(f"{w.name}: stacked planar tensors are not cut")
+    inner = int(np.prod(w.shape[1:]))
+    nbytes = inner // d.block_elems * d.block_bytes
+    raw = w.payload.reshape(-1)
+    return PackedWeight(f"{w.name}[{i}]", w.format, tuple(w.shape[1:]), raw[i * nbytes:(i + 1) * nbytes])
+
+
+# llama-like layer tensors; families override single entries
+LAYER = {
+    "input_layernorm.weight": "attn_norm", "post_attention_layernorm.weight": "ffn_norm",
+    "self_attn.q_proj.weight": "attn_q", "self_attn.k_proj.weight": "attn_k", "self_attn.v_proj.weight": "attn_v",
+    "self_attn.o_proj.weight": "attn_o", "self_attn.q_proj.bias": "attn_q_bias", "self_attn.k_proj.bias": "attn_k_bias",
+    "self_attn.v_proj.bias": "attn_v_bias", "self_attn.o_proj.bias": "attn_o_bias",
+    "self_attn.q_norm.weight": "attn_q_norm", "self_attn.k_norm.weight": "attn_k_norm", "self_attn.sinks": "attn_sinks",
+    "mlp.gate_proj.weight": "ffn_gate", "mlp.up_proj.weight": "ffn_up", "mlp.down_proj.weight": "ffn_down",
+    "mlp.gate_proj.bias": "ffn_gate_bias", "mlp.up_proj.bias": "ffn_up_bias", "mlp.down_proj.bias": "ffn_down_bias",
+    "block_sparse_moe.gate.weight": "ffn_router", "mlp.gate.weight": "ffn_router", "mlp.router.weight": "ffn_router",
+    "mlp.router.bias": "ffn_router_bias", "block_sparse_moe.router.layer.weight": "ffn_router",
+    "mlp.gate.e_score_correction_bias": "ffn_router_select_bias", "mlp.e_score_correction_bias": "ffn_router_select_bias",
+    "block_sparse_moe.e_score_correction_bias": "ffn_router_select_bias",
+    "mlp.shared_experts.gate_proj.weight": "shared_gate", "mlp.shared_experts.up_proj.weight": "shared_up",
+    "mlp.shared_experts.down_proj.weight": "shared_down",
+    # multi-head latent attention
+    "self_attn.q_a_proj.weight": "attn_q_a", "self_attn.q_a_layernorm.weight": "attn_q_a_norm",
+    "self_attn.q_b_proj.weight": "attn_q_b", "self_attn.kv_a_proj_with_mqa.weight": "attn_kv_a",
+    "self_attn.kv_a_layernorm.weight": "attn_kv_a_norm", "self_attn.kv_b_proj.weight": "attn_kv_b",
+}
+# norm placement differs by block kind: the same checkpoint name means a different role
+POST_BLOCK = {"post_attention_layernorm.weight": "attn_post_norm", "post_feedforward_layernorm.weight": "ffn_post_norm"}
+SANDWICH_BLOCK = {"input_layernorm.weight": "attn_norm", "post_attention_layernorm.weight": "attn_post_norm",
+                  "pre_feedforward_layernorm.weight": "ffn_norm", "post_feedforward_layernorm.weight": "ffn_post_norm"}
+TOP = {"model.embed_tokens.weight": "embed", "model.norm.weight": "final_norm", "lm_head.weight": "lm_head"}
+EXPERT = {"w1": "gate", "w3": "up", "w2": "down", "gate_proj": "gate", "up_proj": "up", "down_proj": "down"}
+
+MPT_LAYER = {"norm_1.weight": "attn_norm", "norm_2.weight": "ffn_norm", "attn.out_proj.weight": "attn_o",
+             "ffn.up_proj.weight": "ffn_up", "ffn.down_proj.weight": "ffn_down"}
+BLOOM_LAYER = {"input_layernorm.weight": "attn_norm", "input_layernorm.bias": "attn_norm_bias",
+               "post_attention_layernorm.weight": "ffn_norm", "post_attention_layernorm.bias": "ffn_norm_bias",
+               "self_attention.dense.weight": "attn_o", "self_attention.dense.bias": "attn_o_bias",
+               "mlp.dense_h_to_4h.weight": "ffn_up", "mlp.dense_h_to_4h.bias": "ffn_up_bias",
+               "mlp.dense_4h_to_h.weight": "ffn_down", "mlp.dense_4h_to_h.bias": "ffn_down_bias"}
+BLOOM_TOP = {"transformer.word_embeddings.weight": "embed", "transformer.word_embeddings_layernorm.weight": "embed_norm",
+             "transformer.word_embeddings_layernorm.bias": "embed_norm_bias", "transformer.ln_f.weight": "final_norm",
+             "transformer.ln_f.bias": "final_norm_bias", "lm_head.weight": "lm_head"}
+
+
+def _deinterleave_rows(n: int) -> np.ndarray:
+    """Row order that turns ``(x0, y0, x1, y1, ...)`` pairs into the half-split ``(x0, x1, ..., y0, y1, ...)``."""
+    return np.concatenate([np.arange(0, n, 2), np.arange(1, n, 2)])
+
+
+def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWeight]:
+    """Canonical role name -> stored tensor for one Hugging Face checkpoint of ``cfg``'s family."""
+    if cfg.family == "mpt":
+        return _map_mpt(cfg, store)
+    if cfg.family == "bloom":
+        return _map_bloom(cfg, store)
+    table = dict(LAYER)
+    if cfg.block == "post":
+        table.update(POST_BLOCK)
+        table.pop("input_layernorm.weight")
+    elif cfg.block == "sandwich":
+        table.update(SANDWICH_BLOCK)
+    canon: Dict[str, PackedWeight] = {}
+    names = store.names()
+    for n in names:
+        w = store[n]
+        if n in TOP:
+            canon[TOP[n]] = w
+            continue
+        m = re.match(r"model\.layers\.(\d+)\.(.+)$", n)
+        if not m:
+            continue
+        l, rest = int(m.group(1)), m.group(2)
+        p = f"layers.{l}."
+        if rest in table:
+            canon[p + table[rest]] = w
+            continue
+        e = re.match(r"(?:block_sparse_moe|mlp)\.experts\.(\d+)\.(\w+)\.weight$", rest)
+        if e and e.group(2) in EXPERT:
+            canon[p + f"experts.{e.group(1)}.{EXPERT[e.group(2)]}"] = w
+            continue
+        if rest == "self_attn.qkv_proj.weight":                       # Phi-3: q | k | v rows
+            q, kv = cfg.q_size, cfg.kv_size
+            if w.shape[0] != q + 2 * kv:
+                raise CheckpointLayout(f"{n}: {w.shape[0]} rows, expected {q + 2 * kv} (q | k | v)")
+            canon[p + "attn_q"], canon[p + "attn_k"], canon[p + "attn_v"] = w.rows(0, q), w.rows(q, kv), w.rows(q + kv, kv)
+        elif rest == "mlp.gate_up_proj.weight":                       # Phi-3: gate | up rows
+            half = w.shape[0] // 2
+            if half != cfg.ffn:
+                raise CheckpointLayout(f"{n}: {w.shape[0]} rows, expected {2 * cfg.ffn} (gate | up)")
+            canon[p + "ffn_gate"], canon[p + "ffn_up"] = w.rows(0, half), w.rows(half, half)
+        elif cfg.family == "gpt_oss" and rest.startswith("mlp.experts."):
+            _gpt_oss_experts(cfg, p, rest, w, canon)
+        elif rest in ("mlp.experts.gate_up_proj", "block_sparse_moe.input_linear.weight"):   # stacked [E, 2F, H]
+            F = cfg.moe_ffn
+            if tuple(w.shape) != (cfg.n_experts, 2 * F, cfg.hidden):
+                raise CheckpointLayout(f"{n}: shape {w.shape}, expected {(cfg.n_experts, 2 * F, cfg.hidden)}")
+            for x in range(cfg.n_experts):
+                gu = first_axis(w, x)
+                canon[p + f"experts.{x}.gate"], canon[p + f"experts.{x}.up"] = gu.rows(0, F), gu.rows(F, F)
+        elif rest in ("mlp.experts.down_proj", "block_sparse_moe.output_linear.weight"):     # stacked [E, H, F]
+            for x in range(cfg.n_experts):
+                canon[p + f"experts.{x}.down"] = first_axis(w, x)
+    if cfg.norm_offset != 0.0:
+        for k in list(canon):
+            if k.endswith("norm"):
+                canon[k] = f32_weight(k, canon[k].to_f32() + cfg.norm_offset)
+    if cfg.rope_interleaved and cfg.is_mla:
+        _mla_halfsplit(cfg, canon)
+    return canon
+
+
+def _gpt_oss_experts(cfg: DecoderConfig, p: str, rest: str, w: PackedWeight, canon: Dict[str, PackedWeight]) -> None:
+    E, F = cfg.n_experts, cfg.moe_ffn
+    a = w.to_f32()
+    if rest == "mlp.experts.gate_up_proj":                 # [E, H, 2F], gate at even columns, up at odd ones
+        for x in range(E):
+            canon[p + f"experts.{x}.gate"] = f32_weight(f"{p}experts.{x}.gate", a[x][:, 0::2].T)
+            canon[p + f"experts.{x}.up"] = f32_weight(f"{p}experts.{x}.up", a[x][:, 1::2].T)
+    elif rest == "mlp.experts.gate_up_proj_bias":          # [E, 2F] alternating
+        canon[p + "experts_in_bias"] = f32_weight(p + "experts_in_bias", np.concatenate([a[:, 0::2], a[:, 1::2]], 1))
+    elif rest == "mlp.experts.down_proj":                  # [E, F, H]
+        for x in range(E):
+            canon[p + f"experts.{x}.down"] = f32_weight(f"{p}experts.{x}.down", a[x].T)
+    elif rest == "mlp.experts.down_proj_bias":
+        canon[p + "experts_out_bias"] = f32_weight(p + "experts_out_bias", a)
+
+
+def _mla_halfsplit(cfg: DecoderConfig, canon: Dict[str, PackedWeight]) -> None:
+    dn, dr, nh = cfg.qk_nope_dim, cfg.qk_rope_dim, cfg.n_heads
+    perm = _deinterleave_rows(dr)
+    for l in range(cfg.n_layers):
+        p = f"layers.{l}."
+        qn = p + ("attn_q_b" if cfg.q_lora_rank else "attn_q")
+        q = canon[qn].to_f32().reshape(nh, dn + dr, -1)
+        q = np.concatenate([q[:, :dn], q[:, dn:][:, perm]], 1).reshape(nh * (dn + dr), -1)
+        canon[qn] = f32_weight(qn, q)
+        kv = canon[p + "attn_kv_a"].to_f32()
+        kv = np.concatenate([kv[:cfg.kv_lora_rank], kv[cfg.kv_lora_rank:][perm]], 0)
+        canon[p + "attn_kv_a"] = f32_weight(p + "attn_kv_a", kv)
+
+
+def _map_mpt(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWeight]:
+    canon: Dict[str, PackedWeight] = {}
+    for n in store.names():
+        w = store[n]
+        if n == "transformer.wte.weight":
+            canon["embed"] = w
+        elif n == "transformer.norm_f.weight":
+            canon["final_norm"] = w
+        elif n == "lm_head.weight":
+            canon["lm_head"] = w
+        else:
+            m = re.match(r"transformer\.blocks\.(\d+)\.(.+)$", n)
+            if not m:
+                continue
+            p, rest = f"layers.{m.group(1)}.", m.group(2)
+            if rest in MPT_LAYER:
+                canon[p + MPT_LAYER[rest]] = w
+            elif rest == "attn.Wqkv.weight":               # q | k | v thirds
+                H = cfg.hidden
+                if w.shape[0] != 3 * H:
+                    raise CheckpointLayout(f"{n}: {w.shape[0]} rows, expected {3 * H}")
+                canon[p + "attn_q"], canon[p + "attn_k"], canon[p + "attn_v"] = w.rows(0, H), w.rows(H, H), w.rows(2 * H, H)
+    return canon
+
+
+def _map_bloom(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWeight]:
+    canon: Dict[str, PackedWeight] = {}
+    nh, D = cfg.n_heads, cfg.head_dim
+    for n in store.names():
+        w = store[n]
+        if n in BLOOM_TOP:
+            canon[BLOOM_TOP[n]] = w
+            continue
+        m = re.match(r"transformer\.h\.(\d+)\.(.+)$", n)
+        if not m:
+            continue
+        p, rest = f"layers.{m.group(1)}.", m.group(2)
+        if rest in BLOOM_LAYER:
+            canon[p + BLOOM_LAYER[rest]] = w
+        elif rest == "self_attention.query_key_value.weight":      # rows ordered [head][q|k|v][channel]
+            a = w.to_f32().reshape(nh, 3, D, -1)
+            for i, role in enumerate(("attn_q", "attn_k", "attn_v")):
+                canon[p + role] = f32_weight(p + role, a[:, i].reshape(nh * D, -1))
+        elif rest == "self_attention.query_key_value.bias":
+            a = w.to_f32().reshape(nh, 3, D)
+            for i, role in enumerate(("attn_q_bias", "attn_k_bias", "attn_v_bias")):
+                canon[p + role] = f32_weight(p + role, a[:, i].reshape(nh * D))
+    return canon

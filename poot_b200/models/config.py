@@ -52,10 +52,47 @@ class DecoderConfig:
     n_experts: int = 0
     top_k: int = 0
     moe_ffn: int = 0
-    norm_topk_prob: bool = True             # softmax over the selected k only (mixtral) vs over all then pick
+    norm_topk_prob: bool = True             # gates of the selected experts are renormalised to sum to one (mixtral); False: softmax over all, as is
     embed_scale: float = 1.0
     residual_scale: float = 1.0
     logit_scale: float = 1.0
+    # --- what differs between the standard-stack families (components/standard.rs:618-650, attention.rs, ffn.rs) ---
+    norm_kind: str = "rms"                  # rms | layer
+    norm_bias: bool = False                 # LayerNorm carries a bias (bloom)
+    block: str = "pre"                      # pre: x += f(norm(x)) | post: x += norm(f(x)) (olmo2) | sandwich: x += norm(f(norm(x)))
+    qk_norm_wide: bool = False              # with qk_norm: one RMSNorm over the whole q / k projection (olmo2, olmoe)
+    act: str = "silu"                       # silu | gelu_tanh | gelu_erf
+    gated_ffn: bool = True                  # False: down(act(up(x))) (mpt, bloom)
+    out_bias: bool = False                  # bias on the attention output projection
+    mlp_bias: bool = False                  # biases on the FFN projections
+    pos: str = "rope"                       # rope | alibi | none
+    alibi_slopes: str = "bloom"             # bloom (closest power of two + extras) | mpt
+    alibi_bias_max: float = 8.0
+    attn_scale: Optional[float] = None      # None = 1/sqrt(head_dim)
+    layer_windows: Optional[list] = None    # per-layer sliding window (0 = full); None = sliding_window everywhere
+    rope_theta_local: Optional[float] = None  # rope base of the windowed layers when it differs (gemma3)
+    embed_norm: bool = False                # LayerNorm right after the embedding (bloom)
+    attn_sinks: bool = False                # one learned logit per head joins every softmax (gpt-oss)
+    swiglu_limit: float = 0.0               # >0: clamped SwiGLU (gpt-oss): gate<=limit, |up|<=limit, (up+1)*gate*sigmoid(alpha*gate)
+    swiglu_alpha: float = 1.702
+    router: str = "softmax"                 # softmax | sigmoid
+    router_bias: bool = False               # linear bias on the router logits (gpt-oss)
+    router_select_bias: bool = False        # per-expert bias added for selection only (minimax-m2, deepseek3)
+    n_group: int = 1                        # group-limited routing (deepseek3): experts in n_group groups, keep topk_group groups
+    topk_group: int = 1
+    routed_scale: float = 1.0
+    n_shared_experts: int = 0               # always-on experts of width n_shared_experts * moe_ffn (deepseek)
+    first_dense_layers: int = 0             # leading layers with a dense FFN in a MoE model (deepseek)
+    expert_bias: bool = False               # biases on the expert projections (gpt-oss)
+    # multi-head latent attention (deepseek2/3): 0 = off
+    kv_lora_rank: int = 0
+    q_lora_rank: int = 0
+    qk_nope_dim: int = 0
+    qk_rope_dim: int = 0
+    v_head_dim: int = 0
+    norm_offset: float = 0.0                # checkpoint stores norm weights as w - offset (gemma: 1.0); added at load
+    rope_layers: Optional[list] = None      # per-layer flag: 1 = rotary applied, 0 = no position signal (smollm3 NoPE layers)
+    rope_interleaved: bool = False          # checkpoint stores rotary channels as interleaved pairs (deepseek): rows are re-ordered at load
     bos_token: int = 1
     eos_token: int = 2
 
@@ -78,6 +115,44 @@ class DecoderConfig:
     @property
     def is_moe(self) -> bool:
         return self.n_experts > 0
+
+    @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    def window_of(self, layer: int) -> int:
+        return self.sliding_window if self.layer_windows is None else int(self.layer_windows[layer])
+
+    def uses_rope(self, layer: int) -> bool:
+        return self.pos == "rope" and (self.rope_layers is None or bool(self.rope_layers[layer]))
+
+    def moe_layer(self, layer: int) -> bool:
+        return self.is_moe and layer >= self.first_dense_layers
+
+    def device_gaps(self) -> list:
+        """Features of this configuration that the device program does not implement (empty = runs on the device);
+        the CPU oracle evaluates all of them."""
+        g = []
+        if self.norm_kind != "rms": g.append("LayerNorm")
+        if self.block != "pre": g.append(f"{self.block}-norm block")
+        if self.qk_norm_wide: g.append("projection-wide q/k norm")
+        if self.act != "silu" or not self.gated_ffn: g.append(f"{self.act} {'gated' if self.gated_ffn else 'plain'} FFN")
+        if self.out_bias or self.mlp_bias or self.expert_bias: g.append("output / FFN biases")
+        if self.pos != "rope": g.append(f"{self.pos} positions")
+        if self.rope_theta_local is not None: g.append("two rope bases")
+        if self.rope_layers is not None and not all(self.rope_layers): g.append("layers without rope")
+        if self.embed_norm: g.append("embedding norm")
+        if self.attn_sinks: g.append("attention sinks")
+        if self.swiglu_limit > 0: g.append("clamped SwiGLU")
+        if self.router != "softmax" or self.router_bias or self.router_select_bias:
+            g.append("router variant")
+        if self.n_group > 1: g.append("group-limited routing")
+        if self.n_shared_experts or self.first_dense_layers: g.append("shared experts / leading dense layers")
+        if self.routed_scale != 1.0: g.append("routed scaling")
+        if self.is_mla: g.append("multi-head latent attention")
+        if self.final_softcap > 0: g.append("soft-capped logits")
+        if self.head_dim not in (64, 128): g.append(f"head_dim {self.head_dim}")
+        return g
 
     def param_count(self) -> int:
         per_layer = self.hidden * (self.q_size + 2 * self.kv_size) + self.q_size * self.hidden + 2 * self.hidden

@@ -40,6 +40,11 @@ class StepSpec:
         return self.pool_slots or self.rows * self.capacity
 
 
+def spec_rank_heads(spec: StepSpec, heads_per_rank: int) -> slice:
+    """Heads a trace covers (the tracer has no rank of its own: a sharded trace describes rank 0's share)."""
+    return slice(0, heads_per_rank)
+
+
 class Model:
     """One loaded architecture: configuration + tracer + weight-name tables."""
 
@@ -50,22 +55,69 @@ class Model:
         c = self.cfg
         H, D = c.hidden, c.head_dim
         s = {"embed": (c.vocab, H), "final_norm": (H,)}
+        norms = ["final_norm"]
+        if c.embed_norm:
+            s["embed_norm"] = (H,)
+            norms.append("embed_norm")
         if not c.tie_embeddings:
             s["lm_head"] = (c.vocab, H)
         for l in range(c.n_layers):
             p = f"layers.{l}."
-            s.update({p + "attn_norm": (H,), p + "attn_q": (c.q_size, H), p + "attn_k": (c.kv_size, H),
-                      p + "attn_v": (c.kv_size, H), p + "attn_o": (H, c.q_size), p + "ffn_norm": (H,)})
+            if c.block in ("pre", "sandwich"):
+                s[p + "attn_norm"] = (H,)
+                s[p + "ffn_norm"] = (H,)
+                norms += [p + "attn_norm", p + "ffn_norm"]
+            if c.block in ("post", "sandwich"):
+                s[p + "attn_post_norm"] = (H,)
+                s[p + "ffn_post_norm"] = (H,)
+                norms += [p + "attn_post_norm", p + "ffn_post_norm"]
+            if c.is_mla:
+                qk = c.qk_nope_dim + c.qk_rope_dim
+                if c.q_lora_rank:
+                    s.update({p + "attn_q_a": (c.q_lora_rank, H), p + "attn_q_a_norm": (c.q_lora_rank,),
+                              p + "attn_q_b": (c.n_heads * qk, c.q_lora_rank)})
+                else:
+                    s[p + "attn_q"] = (c.n_heads * qk, H)
+                s.update({p + "attn_kv_a": (c.kv_lora_rank + c.qk_rope_dim, H), p + "attn_kv_a_norm": (c.kv_lora_rank,),
+                          p + "attn_kv_b": (c.n_heads * (c.qk_nope_dim + c.v_head_dim), c.kv_lora_rank),
+                          p + "attn_o": (H, c.n_heads * c.v_head_dim)})
+            else:
+                s.update({p + "attn_q": (c.q_size, H), p + "attn_k": (c.kv_size, H), p + "attn_v": (c.kv_size, H),
+                          p + "attn_o": (H, c.q_size)})
             if c.attn_bias:
                 s.update({p + "attn_q_bias": (c.q_size,), p + "attn_k_bias": (c.kv_size,), p + "attn_v_bias": (c.kv_size,)})
+            if c.out_bias:
+                s[p + "attn_o_bias"] = (H,)
             if c.qk_norm:
-                s.update({p + "attn_q_norm": (D,), p + "attn_k_norm": (D,)})
-            if c.is_moe:
+                s.update({p + "attn_q_norm": (c.q_size if c.qk_norm_wide else D,),
+                          p + "attn_k_norm": (c.kv_size if c.qk_norm_wide else D,)})
+            if c.attn_sinks:
+                s[p + "attn_sinks"] = (c.n_heads,)
+            if c.moe_layer(l):
                 s[p + "ffn_router"] = (c.n_experts, H)
+                if c.router_bias:
+                    s[p + "ffn_router_bias"] = (c.n_experts,)
+                if c.router_select_bias:
+                    s[p + "ffn_router_select_bias"] = (c.n_experts,)
                 s[p + "experts_in"] = (c.n_experts, 2 * c.moe_ffn, H)      # gate rows then up rows
                 s[p + "experts_out"] = (c.n_experts, H, c.moe_ffn)
+                if c.expert_bias:
+                    s[p + "experts_in_bias"] = (c.n_experts, 2 * c.moe_ffn)
+                    s[p + "experts_out_bias"] = (c.n_experts, H)
+                if c.n_shared_experts:
+                    Fs = c.n_shared_experts * c.moe_ffn
+                    s.update({p + "shared_gate": (Fs, H), p + "shared_up": (Fs, H), p + "shared_down": (H, Fs)})
             else:
-                s.update({p + "ffn_gate": (c.ffn, H), p + "ffn_up": (c.ffn, H), p + "ffn_down": (H, c.ffn)})
+                if c.gated_ffn:
+                    s[p + "ffn_gate"] = (c.ffn, H)
+                s.update({p + "ffn_up": (c.ffn, H), p + "ffn_down": (H, c.ffn)})
+                if c.mlp_bias:
+                    if c.gated_ffn:
+                        s[p + "ffn_gate_bias"] = (c.ffn,)
+                    s.update({p + "ffn_up_bias": (c.ffn,), p + "ffn_down_bias": (H,)})
+        if c.norm_kind == "layer" and c.norm_bias:
+            for n in norms:
+                s[n + "_bias"] = s[n]
         return s
 
     # ------------------------------------------------------------------------------------------------------------
@@ -85,82 +137,193 @@ class Model:
                 consts[name] = b.const(name, shape or shapes[name], spec.weight_dtype).cast(F32)
             return consts[name]
 
+        def norm(x: Traced, name: str) -> Traced:
+            if c.norm_kind == "layer":
+                return O.layernorm(b, x, W(name), W(name + "_bias") if c.norm_bias else None, c.norm_eps)
+            return O.rmsnorm(b, x, W(name), c.norm_eps)
+
         tokens = b.slot("tokens", (R, T), I32, "token", range=(0, c.vocab - 1))
         positions = b.slot("positions", (R, T), I32, "pos", range=(0, c.max_position - 1))
         if spec.paged:
             read_map = b.slot("read_map", (R, cap), I32, "slot_map", range=(0, spec.slots - 1))
             write_map = b.slot("write_map", (R * T,), I32, "write_map", range=(-1, spec.slots - 1))
-        rot = c.rot
-        cos_t = b.computed("rope.cos", (c.max_position, rot), F32, "rope_cos", (rot, c.rope_theta, c.max_position, c.rope_scaling))
-        sin_t = b.computed("rope.sin", (c.max_position, rot), F32, "rope_sin", (rot, c.rope_theta, c.max_position, c.rope_scaling))
-        flat_pos = b.reshape(positions, (R * T,))
-        cos = b.gather(cos_t, flat_pos, 0)
-        sin = b.gather(sin_t, flat_pos, 0)
-        mask = O.causal_mask_from_pos(b, positions, cap, c.sliding_window)
+        rot = c.qk_rope_dim if c.is_mla else c.rot
+        rope_tables: Dict[tuple, tuple] = {}
+        flat = []
+
+        def rope_of(layer: int):
+            """cos / sin rows of this step's positions for the layer's rope base (windowed layers may use their own)."""
+            local = c.rope_theta_local is not None and c.window_of(layer) > 0
+            key = ("local",) if local else ("global",)
+            if key not in rope_tables:
+                theta, scaling = (c.rope_theta_local, type(c.rope_scaling)()) if local else (c.rope_theta, c.rope_scaling)
+                tag = "rope.local" if local else "rope"
+                ct = b.computed(tag + ".cos", (c.max_position, rot), F32, "rope_cos", (rot, theta, c.max_position, scaling))
+                st = b.computed(tag + ".sin", (c.max_position, rot), F32, "rope_sin", (rot, theta, c.max_position, scaling))
+                if not flat:
+                    flat.append(b.reshape(positions, (R * T,)))
+                rope_tables[key] = (b.gather(ct, flat[0], 0), b.gather(st, flat[0], 0))
+            return rope_tables[key]
+
+        if c.pos == "rope":
+            rope_of(0)
+        masks: Dict[int, Traced] = {}
+
+        def mask_of(layer: int) -> Traced:
+            win = c.window_of(layer)
+            if win not in masks:
+                masks[win] = O.causal_mask_from_pos(b, positions, cap, win)
+            return masks[win]
+
+        mask_of(0)
+        head_bias = None
+        if c.pos == "alibi":
+            sl = O.alibi_slopes(Hq, c.alibi_slopes, c.alibi_bias_max)
+            head_bias = O.alibi_bias_from_pos(b, positions, cap, sl[spec_rank_heads(spec, hq)])
 
         h = b.gather(W("embed"), b.reshape(tokens, (R * T,)), 0)          # [R*T, H]
         if c.embed_scale != 1.0:
             h = h * c.embed_scale
-        scale = 1.0 / math.sqrt(D)
-        for l in range(c.n_layers):
-            p = f"layers.{l}."
-            x = O.rmsnorm(b, h, W(p + "attn_norm"), c.norm_eps)
-            q = O.linear(b, x, W(p + "attn_q", (hq * D, H)), W(p + "attn_q_bias", (hq * D,)) if c.attn_bias else None)
-            k = O.linear(b, x, W(p + "attn_k", (hkv * D, H)), W(p + "attn_k_bias", (hkv * D,)) if c.attn_bias else None)
-            v = O.linear(b, x, W(p + "attn_v", (hkv * D, H)), W(p + "attn_v_bias", (hkv * D,)) if c.attn_bias else None)
-            q = b.reshape(q, (R * T, hq, D))
-            k = b.reshape(k, (R * T, hkv, D))
-            v = b.reshape(v, (R * T, hkv, D))
-            if c.qk_norm:
-                q = O.rmsnorm(b, q, W(p + "attn_q_norm"), c.norm_eps)
-                k = O.rmsnorm(b, k, W(p + "attn_k_norm"), c.norm_eps)
-            q = O.rope(b, q, cos, sin, rot)
-            k = O.rope(b, k, cos, sin, rot)
+        if c.embed_norm:
+            h = norm(h, "embed_norm")
+        scale = c.attn_scale if c.attn_scale is not None else 1.0 / math.sqrt(D)
+        rs = c.residual_scale
+
+        def kv_through_cache(p: str, k: Traced, v: Traced, dk: int, dv: int):
+            """Write this step's keys / values and read the visible window back (through the storage dtype, which keeps
+            decode-by-steps equal to one-shot prefill)."""
+            nk = k.shape[1]
             if spec.paged:
-                kp = b.state(p + "k_pool", (spec.slots, hkv, D), spec.kv_dtype, "blocked").cast(F32)
-                vp = b.state(p + "v_pool", (spec.slots, hkv, D), spec.kv_dtype, "blocked").cast(F32)
+                kp = b.state(p + "k_pool", (spec.slots, nk, dk), spec.kv_dtype, "blocked").cast(F32)
+                vp = b.state(p + "v_pool", (spec.slots, nk, dv), spec.kv_dtype, "blocked").cast(F32)
                 kp2 = b.scatter_update(kp, write_map, k)
                 vp2 = b.scatter_update(vp, write_map, v)
                 b.output(kp2.cast(spec.kv_dtype), p + "k_pool.next", "state_next", p + "k_pool")
                 b.output(vp2.cast(spec.kv_dtype), p + "v_pool.next", "state_next", p + "v_pool")
-                # reading back through the storage dtype keeps decode-by-steps equal to one-shot prefill
-                K = O.paged_view(b, kp2.cast(spec.kv_dtype).cast(F32), read_map)
-                V = O.paged_view(b, vp2.cast(spec.kv_dtype).cast(F32), read_map)
-            else:
-                kc = b.state(p + "k_cache", (R, hkv, cap, D), spec.kv_dtype, "positional", 2).cast(F32)
-                vc = b.state(p + "v_cache", (R, hkv, cap, D), spec.kv_dtype, "positional", 2).cast(F32)
-                start = b.slice(b.reshape(positions, (R * T,)), 0, 0, 1)
-                kn = b.transpose(b.reshape(k, (R, T, hkv, D)), (0, 2, 1, 3))
-                vn = b.transpose(b.reshape(v, (R, T, hkv, D)), (0, 2, 1, 3))
-                kc2 = b.dynamic_update_slice(kc, kn, start, 2)
-                vc2 = b.dynamic_update_slice(vc, vn, start, 2)
-                b.output(kc2.cast(spec.kv_dtype), p + "k_cache.next", "state_next", p + "k_cache")
-                b.output(vc2.cast(spec.kv_dtype), p + "v_cache.next", "state_next", p + "v_cache")
-                K, V = kc2.cast(spec.kv_dtype).cast(F32), vc2.cast(spec.kv_dtype).cast(F32)
+                return (O.paged_view(b, kp2.cast(spec.kv_dtype).cast(F32), read_map),
+                        O.paged_view(b, vp2.cast(spec.kv_dtype).cast(F32), read_map))
+            kc = b.state(p + "k_cache", (R, nk, cap, dk), spec.kv_dtype, "positional", 2).cast(F32)
+            vc = b.state(p + "v_cache", (R, nk, cap, dv), spec.kv_dtype, "positional", 2).cast(F32)
+            start = b.slice(b.reshape(positions, (R * T,)), 0, 0, 1)
+            kn = b.transpose(b.reshape(k, (R, T, nk, dk)), (0, 2, 1, 3))
+            vn = b.transpose(b.reshape(v, (R, T, nk, dv)), (0, 2, 1, 3))
+            kc2 = b.dynamic_update_slice(kc, kn, start, 2)
+            vc2 = b.dynamic_update_slice(vc, vn, start, 2)
+            b.output(kc2.cast(spec.kv_dtype), p + "k_cache.next", "state_next", p + "k_cache")
+            b.output(vc2.cast(spec.kv_dtype), p + "v_cache.next", "state_next", p + "v_cache")
+            return kc2.cast(spec.kv_dtype).cast(F32), vc2.cast(spec.kv_dtype).cast(F32)
+
+        def attention(l: int, x: Traced) -> Traced:
+            p = f"layers.{l}."
+            if c.is_mla:
+                return mla_attention(l, x)
+            bias = (lambda n, k_: W(p + n, (k_,))) if c.attn_bias else (lambda n, k_: None)
+            q = O.linear(b, x, W(p + "attn_q", (hq * D, H)), bias("attn_q_bias", hq * D))
+            k = O.linear(b, x, W(p + "attn_k", (hkv * D, H)), bias("attn_k_bias", hkv * D))
+            v = O.linear(b, x, W(p + "attn_v", (hkv * D, H)), bias("attn_v_bias", hkv * D))
+            if c.qk_norm and c.qk_norm_wide:
+                q = O.rmsnorm(b, q, W(p + "attn_q_norm"), c.norm_eps)
+                k = O.rmsnorm(b, k, W(p + "attn_k_norm"), c.norm_eps)
+            q = b.reshape(q, (R * T, hq, D))
+            k = b.reshape(k, (R * T, hkv, D))
+            v = b.reshape(v, (R * T, hkv, D))
+            if c.qk_norm and not c.qk_norm_wide:
+                q = O.rmsnorm(b, q, W(p + "attn_q_norm"), c.norm_eps)
+                k = O.rmsnorm(b, k, W(p + "attn_k_norm"), c.norm_eps)
+            if c.uses_rope(l):
+                cos, sin = rope_of(l)
+                q = O.rope(b, q, cos, sin, rot)
+                k = O.rope(b, k, cos, sin, rot)
+            K, V = kv_through_cache(p, k, v, D, D)
             qh = b.transpose(b.reshape(q, (R, T, hq, D)), (0, 2, 1, 3))
-            a = O.attention_masked(b, qh, K, V, mask, scale, hq // hkv, c.attn_softcap)
+            a = O.attention_biased(b, qh, K, V, mask_of(l), scale, hq // hkv, c.attn_softcap, head_bias,
+                                   W(p + "attn_sinks", (hq,)) if c.attn_sinks else None)
             a = b.reshape(b.transpose(a, (0, 2, 1, 3)), (R * T, hq * D))
             o = O.linear(b, a, W(p + "attn_o", (H, hq * D)))
             if w > 1:
                 o = b.all_reduce(o)
-            h = h + (o * c.residual_scale if c.residual_scale != 1.0 else o)
-            x = O.rmsnorm(b, h, W(p + "ffn_norm"), c.norm_eps)
-            if c.is_moe:
+            if c.out_bias:
+                o = o + b.broadcast(W(p + "attn_o_bias"), o.shape)
+            return o
+
+        def mla_attention(l: int, x: Traced) -> Traced:
+            """Multi-head latent attention in its expanded (prefill) form: queries and keys are the concatenation of a
+            per-head no-position part and a rotary part; the rotary key is one head shared by all (components/mla.rs)."""
+            p = f"layers.{l}."
+            dn, dr, dv, nh = c.qk_nope_dim, c.qk_rope_dim, c.v_head_dim, c.n_heads
+            if c.q_lora_rank:
+                qa = O.rmsnorm(b, O.linear(b, x, W(p + "attn_q_a")), W(p + "attn_q_a_norm"), c.norm_eps)
+                q = O.linear(b, qa, W(p + "attn_q_b"))
+            else:
+                q = O.linear(b, x, W(p + "attn_q"))
+            q = b.reshape(q, (R * T, nh, dn + dr))
+            kva = O.linear(b, x, W(p + "attn_kv_a"))                          # [L, kv_lora + dr]
+            ckv = O.rmsnorm(b, b.slice(kva, -1, 0, c.kv_lora_rank), W(p + "attn_kv_a_norm"), c.norm_eps)
+            k_rope = b.reshape(b.slice(kva, -1, c.kv_lora_rank, dr), (R * T, 1, dr))
+            kvb = b.reshape(O.linear(b, ckv, W(p + "attn_kv_b")), (R * T, nh, dn + dv))
+            cos, sin = rope_of(l)
+            q_rope = O.rope(b, b.slice(q, -1, dn, dr), cos, sin, dr)
+            k_rope = O.rope(b, k_rope, cos, sin, dr)
+            qf = b.concat([b.slice(q, -1, 0, dn), q_rope], -1)
+            kf = b.concat([b.slice(kvb, -1, 0, dn), b.broadcast(k_rope, (R * T, nh, dr))], -1)
+            vf = b.slice(kvb, -1, dn, dv)
+            K, V = kv_through_cache(p, kf, vf, dn + dr, dv)
+            qh = b.transpose(b.reshape(qf, (R, T, nh, dn + dr)), (0, 2, 1, 3))
+            a = O.attention_masked(b, qh, K, V, mask_of(l), scale, 1, 0.0)
+            a = b.reshape(b.transpose(a, (0, 2, 1, 3)), (R * T, nh * dv))
+            return O.linear(b, a, W(p + "attn_o"))
+
+        def dense_ffn(x: Traced, p: str, gate: str, up: str, down: str, F: int) -> Traced:
+            mb = (lambda n, k_: W(p + n, (k_,))) if c.mlp_bias else (lambda n, k_: None)
+            if c.gated_ffn:
+                g_ = O.linear(b, x, W(p + gate, (F, H)), mb(gate + "_bias", F))
+                u_ = O.linear(b, x, W(p + up, (F, H)), mb(up + "_bias", F))
+                a = O.swiglu(b, g_, u_) if c.act == "silu" else O.ffn_activation(b, g_, u_, c.act)
+            else:
+                a = O.ffn_activation(b, O.linear(b, x, W(p + up, (F, H)), mb(up + "_bias", F)), None, c.act)
+            f = O.linear(b, a, W(p + down, (H, F)))
+            if w > 1:
+                f = b.all_reduce(f)
+            if c.mlp_bias:
+                f = f + b.broadcast(W(p + down + "_bias"), f.shape)
+            return f
+
+        def ffn(l: int, x: Traced) -> Traced:
+            p = f"layers.{l}."
+            if not c.moe_layer(l):
+                return dense_ffn(x, p, "ffn_gate", "ffn_up", "ffn_down", c.ffn // w)
+            plain = (c.router == "softmax" and c.norm_topk_prob and not (c.router_bias or c.router_select_bias or c.expert_bias)
+                     and c.n_group == 1 and c.routed_scale == 1.0 and c.act == "silu" and c.swiglu_limit == 0)
+            if plain:
                 f = O.moe_topk_softmax(b, x, W(p + "ffn_router"), W(p + "experts_in"), W(p + "experts_out"), c.top_k)
             else:
-                F = c.ffn // w
-                g_ = O.linear(b, x, W(p + "ffn_gate", (F, H)))
-                u_ = O.linear(b, x, W(p + "ffn_up", (F, H)))
-                f = O.linear(b, O.swiglu(b, g_, u_), W(p + "ffn_down", (H, F)))
-                if w > 1:
-                    f = b.all_reduce(f)
-            h = h + (f * c.residual_scale if c.residual_scale != 1.0 else f)
+                f = O.moe_routed(
+                    b, x, W(p + "ffn_router"), W(p + "experts_in"), W(p + "experts_out"), c.top_k, score=c.router,
+                    renorm=c.norm_topk_prob, router_bias=W(p + "ffn_router_bias") if c.router_bias else None,
+                    select_bias=W(p + "ffn_router_select_bias") if c.router_select_bias else None, n_group=c.n_group,
+                    topk_group=c.topk_group, routed_scale=c.routed_scale, act=c.act, limit=c.swiglu_limit,
+                    alpha=c.swiglu_alpha, in_bias=W(p + "experts_in_bias") if c.expert_bias else None,
+                    out_bias=W(p + "experts_out_bias") if c.expert_bias else None)
+            if c.n_shared_experts:
+                f = f + dense_ffn(x, p, "shared_gate", "shared_up", "shared_down", c.n_shared_experts * c.moe_ffn)
+            return f
+
+        for l in range(c.n_layers):
+            p = f"layers.{l}."
+            o = attention(l, norm(h, p + "attn_norm") if c.block != "post" else h)
+            if c.block != "pre":
+                o = norm(o, p + "attn_post_norm")
+            h = h + (o * rs if rs != 1.0 else o)
+            f = ffn(l, norm(h, p + "ffn_norm") if c.block != "post" else h)
+            if c.block != "pre":
+                f = norm(f, p + "ffn_post_norm")
+            h = h + (f * rs if rs != 1.0 else f)
         h = b.reshape(h, (R, T, H))
         if spec.logit_rows == "last":
             h = b.reshape(b.slice(h, 1, T - 1, 1), (R, H))
         else:
             h = b.reshape(h, (R * T, H))
-        x = O.rmsnorm(b, h, W("final_norm"), c.norm_eps)
+        x = norm(h, "final_norm")
         head = W("embed") if c.tie_embeddings else W("lm_head")
         logits = O.linear(b, x, head)
         if c.logit_scale != 1.0:

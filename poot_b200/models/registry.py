@@ -28,66 +28,219 @@ class FamilyEntry:
     missing: Optional[str] = None     # capability that is not built when the family is refused
 
 
-def _rope_scaling(c: dict) -> RopeScaling:
-    rs = c.get("rope_scaling") or {}
+def _rope_params(c: dict, layer_type: Optional[str] = None) -> dict:
+    """Rotary settings of a header in either spelling: top-level ``rope_theta`` + ``rope_scaling`` (older
+    checkpoints) or one ``rope_parameters`` table, optionally keyed by layer type (gemma3)."""
+    rp = c.get("rope_parameters")
+    if isinstance(rp, dict):
+        if layer_type is not None and isinstance(rp.get(layer_type), dict):
+            rp = rp[layer_type]
+        elif rp and all(isinstance(v, dict) for v in rp.values()):
+            rp = rp.get("full_attention") or next(iter(rp.values()))
+        return dict(rp)
+    out = dict(c.get("rope_scaling") or {})
+    if "rope_theta" in c:
+        out["rope_theta"] = c["rope_theta"]
+    if "partial_rotary_factor" in c:
+        out["partial_rotary_factor"] = c["partial_rotary_factor"]
+    return out
+
+
+def _rope_scaling(c: dict, rs: Optional[dict] = None) -> RopeScaling:
+    rs = _rope_params(c) if rs is None else rs
     kind = rs.get("rope_type", rs.get("type", "none")) or "none"
     if kind == "default":
         kind = "none"
     return RopeScaling(kind=kind, factor=float(rs.get("factor", 1.0)),
                        low_freq_factor=float(rs.get("low_freq_factor", 1.0)),
                        high_freq_factor=float(rs.get("high_freq_factor", 4.0)),
-                       original_max_position=int(rs.get("original_max_position_embeddings",
-                                                        c.get("original_max_position_embeddings", 8192))),
-                       beta_fast=float(rs.get("beta_fast", 32.0)), beta_slow=float(rs.get("beta_slow", 1.0)),
+                       original_max_position=int(rs.get("original_max_position_embeddings") or
+                                                 c.get("original_max_position_embeddings") or 8192),
+                       beta_fast=float(rs.get("beta_fast") or 32.0), beta_slow=float(rs.get("beta_slow") or 1.0),
                        attention_factor=rs.get("attention_factor"), short_factor=rs.get("short_factor"),
                        long_factor=rs.get("long_factor"))
 
 
+def _token(v, default: int) -> int:
+    if isinstance(v, (list, tuple)):
+        v = v[0] if v else None
+    return default if v is None else int(v)
+
+
+def _windows(c: dict, n_layers: int) -> Optional[list]:
+    """Per-layer sliding windows from ``layer_types`` (``sliding_attention`` layers use ``sliding_window``)."""
+    lt, win = c.get("layer_types"), int(c.get("sliding_window") or 0)
+    if not lt or not win or not c.get("use_sliding_window", True):
+        return None
+    ws = [win if t in ("sliding_attention", "chunked_attention") else 0 for t in lt][:n_layers]
+    return ws if len(set(ws)) > 1 else None
+
+
 def _base(c: dict, family: str, **over) -> DecoderConfig:
     H, nh = c["hidden_size"], c["num_attention_heads"]
+    rp = _rope_params(c)
+    D = c.get("head_dim") or H // nh
+    prf = float(rp.get("partial_rotary_factor") or 1.0)
+    L = c["num_hidden_layers"]
+    lw = _windows(c, L)
+    win = int(c.get("sliding_window") or 0) if c.get("use_sliding_window", True) else 0
+    if lw is None and c.get("layer_types") and all(t == "full_attention" for t in c["layer_types"]):
+        win = 0
     cfg = DecoderConfig(
-        name=c.get("_name_or_path", family) or family, family=family, n_layers=c["num_hidden_layers"], hidden=H,
-        n_heads=nh, n_kv_heads=c.get("num_key_value_heads", nh), head_dim=c.get("head_dim") or H // nh,
+        name=c.get("_name_or_path", family) or family, family=family, n_layers=L, hidden=H,
+        n_heads=nh, n_kv_heads=c.get("num_key_value_heads") or nh, head_dim=D,
         ffn=c.get("intermediate_size", 4 * H), vocab=c["vocab_size"], norm_eps=float(c.get("rms_norm_eps", 1e-6)),
-        rope_theta=float(c.get("rope_theta", 10000.0)), rope_scaling=_rope_scaling(c),
+        rope_theta=float(rp.get("rope_theta", 10000.0)), rope_scaling=_rope_scaling(c, rp),
+        rope_dim=None if prf == 1.0 else int(D * prf),
         max_position=int(c.get("max_position_embeddings", 8192)), tie_embeddings=bool(c.get("tie_word_embeddings", False)),
-        sliding_window=int(c.get("sliding_window") or 0) if c.get("use_sliding_window", True) else 0,
-        bos_token=c.get("bos_token_id", 1) or 1, eos_token=(c.get("eos_token_id", 2) if isinstance(c.get("eos_token_id", 2), int) else c["eos_token_id"][0]))
+        sliding_window=0 if lw is not None else win, layer_windows=lw,
+        bos_token=_token(c.get("bos_token_id"), 1), eos_token=_token(c.get("eos_token_id"), 2))
+    if c.get("attention_bias"):
+        cfg.attn_bias = cfg.out_bias = True
+    if c.get("mlp_bias"):
+        cfg.mlp_bias = True
     for k, v in over.items():
         setattr(cfg, k, v)
     return cfg
 
 
+def _experts(c: dict) -> int:
+    return int(c.get("num_local_experts") or c.get("num_experts") or c.get("n_routed_experts") or 0)
+
+
 def _llama(c: dict) -> DecoderConfig:
-    if c.get("attention_bias") or c.get("mlp_bias"):
-        raise UnsupportedFamily("llama with attention_bias / mlp_bias")   # as the reference (llama.rs:152-156)
     cfg = _base(c, "llama")
-    if c.get("num_local_experts", 0) > 0:   # Mixtral rides the llama entry (llama.rs:136-208)
-        cfg.family, cfg.n_experts, cfg.top_k, cfg.moe_ffn = "mixtral", c["num_local_experts"], c["num_experts_per_tok"], c["intermediate_size"]
+    if _experts(c) > 0:   # Mixtral rides the llama entry (llama.rs:136-208)
+        cfg.family, cfg.n_experts, cfg.top_k, cfg.moe_ffn = "mixtral", _experts(c), c["num_experts_per_tok"], c["intermediate_size"]
     return cfg
 
 
-def _qwen2(c): return _base(c, "qwen2", attn_bias=True, sliding_window=0)
-def _qwen3(c): return _base(c, "qwen3", qk_norm=True, sliding_window=0)
-def _smollm3(c): return _base(c, "smollm3")
-def _olmo2(c): return _base(c, "olmo2", qk_norm=True)
+def _qwen2(c): return _base(c, "qwen2", attn_bias=True, out_bias=False)
+def _qwen3(c): return _base(c, "qwen3", qk_norm=True, out_bias=False)
+def _olmo2(c): return _base(c, "olmo2", qk_norm=True, qk_norm_wide=True, block="post")
 def _phi3(c): return _base(c, "phi3")
 
 
+def _smollm3(c):
+    nr = c.get("no_rope_layers")
+    return _base(c, "smollm3", rope_layers=[int(x) for x in nr] if nr and not all(nr) else None)
+
+
 def _qwen3moe(c):
-    return _base(c, "qwen3moe", qk_norm=True, sliding_window=0, n_experts=c["num_experts"], top_k=c["num_experts_per_tok"],
-                 moe_ffn=c["moe_intermediate_size"], norm_topk_prob=bool(c.get("norm_topk_prob", True)))
+    return _base(c, "qwen3moe", qk_norm=True, out_bias=False, n_experts=_experts(c), top_k=c["num_experts_per_tok"],
+                 moe_ffn=c["moe_intermediate_size"], norm_topk_prob=bool(c.get("norm_topk_prob", False)))
 
 
 def _granite(c):
-    return _base(c, "granite", embed_scale=float(c.get("embedding_multiplier", 1.0)),
-                 residual_scale=float(c.get("residual_multiplier", 1.0)),
-                 logit_scale=1.0 / float(c.get("logits_scaling", 1.0)))
+    cfg = _base(c, "granite", embed_scale=float(c.get("embedding_multiplier", 1.0)),
+                residual_scale=float(c.get("residual_multiplier", 1.0)),
+                logit_scale=1.0 / float(c.get("logits_scaling", 1.0)))
+    if c.get("attention_multiplier") is not None:
+        cfg.attn_scale = float(c["attention_multiplier"])
+    if _experts(c) > 0:   # granitemoe: top-k logits, softmax over the selected ones
+        cfg.n_experts, cfg.top_k, cfg.moe_ffn = _experts(c), c["num_experts_per_tok"], c["intermediate_size"]
+    return cfg
 
 
 def _olmoe(c):
-    return _base(c, "olmoe", qk_norm=True, n_experts=c["num_experts"], top_k=c["num_experts_per_tok"],
+    return _base(c, "olmoe", qk_norm=True, qk_norm_wide=True, n_experts=_experts(c), top_k=c["num_experts_per_tok"],
                  moe_ffn=c["intermediate_size"], norm_topk_prob=bool(c.get("norm_topk_prob", False)))
+
+
+def _gemma(c, family: str) -> DecoderConfig:
+    H = c["hidden_size"]
+    lt = c.get("layer_types")
+    L = c["num_hidden_layers"]
+    if not lt:      # older headers: gemma2 alternates starting with a windowed layer; gemma3 has one global layer in six
+        pat = int(c.get("sliding_window_pattern") or c.get("_sliding_window_pattern") or (2 if family == "gemma2" else 6))
+        lt = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention" for i in range(L)]
+    c = {**c, "layer_types": lt}
+    cfg = _base(c, family, block="sandwich", act="gelu_tanh", embed_scale=float(H) ** 0.5, norm_offset=1.0,
+                attn_scale=float(c.get("query_pre_attn_scalar") or (c.get("head_dim") or H // c["num_attention_heads"])) ** -0.5,
+                attn_softcap=float(c.get("attn_logit_softcapping") or 0.0),
+                final_softcap=float(c.get("final_logit_softcapping") or 0.0),
+                tie_embeddings=bool(c.get("tie_word_embeddings", True)))
+    if cfg.layer_windows is None and cfg.sliding_window == 0 and c.get("sliding_window") and all(t != "full_attention" for t in lt):
+        cfg.sliding_window = int(c["sliding_window"])
+    if family == "gemma3":
+        cfg.qk_norm = True
+        g = _rope_params(c, "full_attention")
+        loc = _rope_params(c, "sliding_attention")
+        cfg.rope_theta, cfg.rope_scaling = float(g.get("rope_theta", 1e6)), _rope_scaling(c, g)
+        cfg.rope_theta_local = float(c.get("rope_local_base_freq") or loc.get("rope_theta", 10000.0))
+    return cfg
+
+
+def _gemma2(c): return _gemma(c, "gemma2")
+def _gemma3(c): return _gemma(c, "gemma3")
+
+
+def _mpt(c):
+    a = c.get("attn_config") or {}
+    if not a.get("alibi", False):
+        raise UnsupportedFamily("mpt without ALiBi (learned position table)")
+    if a.get("clip_qkv") or a.get("qk_ln") or a.get("prefix_lm"):
+        raise UnsupportedFamily("mpt with clip_qkv / qk_ln / prefix_lm")
+    if not c.get("no_bias", True):
+        raise UnsupportedFamily("mpt with biases")
+    H, nh = c["d_model"], c["n_heads"]
+    return DecoderConfig(name="mpt", family="mpt", n_layers=c["n_layers"], hidden=H, n_heads=nh, n_kv_heads=nh,
+                         head_dim=H // nh, ffn=int(c.get("expansion_ratio", 4) * H), vocab=c["vocab_size"],
+                         norm_eps=float(c.get("layer_norm_epsilon", 1e-5)), max_position=int(c.get("max_seq_len", 2048)),
+                         tie_embeddings=True, norm_kind="layer", act="gelu_erf", gated_ffn=False, pos="alibi",
+                         alibi_slopes="mpt", alibi_bias_max=float(a.get("alibi_bias_max", 8)),
+                         attn_scale=a.get("softmax_scale"), logit_scale=float(c.get("logit_scale") or 1.0),
+                         bos_token=_token(c.get("bos_token_id"), 0), eos_token=_token(c.get("eos_token_id"), 0))
+
+
+def _bloom(c):
+    if c.get("apply_residual_connection_post_layernorm"):
+        raise UnsupportedFamily("bloom with the residual taken after the layer norm")
+    H, nh = c["hidden_size"], c["n_head"]
+    return DecoderConfig(name="bloom", family="bloom", n_layers=c["n_layer"], hidden=H, n_heads=nh, n_kv_heads=nh,
+                         head_dim=H // nh, ffn=4 * H, vocab=c["vocab_size"], norm_eps=float(c.get("layer_norm_epsilon", 1e-5)),
+                         max_position=int(c.get("seq_length", 2048)), tie_embeddings=True, norm_kind="layer",
+                         norm_bias=True, embed_norm=True, act="gelu_tanh", gated_ffn=False, attn_bias=True, out_bias=True,
+                         mlp_bias=True, pos="alibi", alibi_slopes="bloom",
+                         bos_token=_token(c.get("bos_token_id"), 1), eos_token=_token(c.get("eos_token_id"), 2))
+
+
+def _gpt_oss(c):
+    return _base(c, "gpt_oss", attn_bias=True, out_bias=True, attn_sinks=True, n_experts=_experts(c),
+                 top_k=c["num_experts_per_tok"], moe_ffn=c["intermediate_size"], router_bias=True, expert_bias=True,
+                 swiglu_limit=float(c.get("swiglu_limit", 7.0)), norm_topk_prob=True)
+
+
+def _minimax_m2(c):
+    return _base(c, "minimax_m2", qk_norm=True, qk_norm_wide=True, n_experts=_experts(c), top_k=c["num_experts_per_tok"],
+                 moe_ffn=c["intermediate_size"], router="sigmoid", router_select_bias=True, norm_topk_prob=True)
+
+
+def _deepseek(c, family: str) -> DecoderConfig:
+    rp = _rope_params(c)
+    if (rp.get("rope_type") or rp.get("type") or "default") not in ("default", "none"):
+        raise UnsupportedFamily(f"{family} with scaled rotary tables (the attention scale correction is not built)")
+    dn, dr = c["qk_nope_head_dim"], c["qk_rope_head_dim"]
+    v3 = family == "deepseek3"
+    method = c.get("topk_method") or ("noaux_tc" if v3 else "greedy")
+    if not v3 and method not in ("greedy",):
+        raise UnsupportedFamily(f"deepseek2 routing method {method!r}")
+    cfg = _base(c, family, kv_lora_rank=c["kv_lora_rank"], q_lora_rank=int(c.get("q_lora_rank") or 0), qk_nope_dim=dn,
+                qk_rope_dim=dr, v_head_dim=c["v_head_dim"], head_dim=dn + dr, attn_scale=float(dn + dr) ** -0.5,
+                rope_dim=None, rope_interleaved=bool(c.get("rope_interleave", True)), attn_bias=False, out_bias=False,
+                n_experts=_experts(c), top_k=int(c.get("num_experts_per_tok") or 0),
+                moe_ffn=int(c.get("moe_intermediate_size") or 0), n_shared_experts=int(c.get("n_shared_experts") or 0),
+                first_dense_layers=int(c.get("first_k_dense_replace") or 0),
+                routed_scale=float(c.get("routed_scaling_factor") or 1.0), norm_topk_prob=bool(c.get("norm_topk_prob", v3)))
+    cfg.n_kv_heads = cfg.n_heads
+    if v3:
+        cfg.router, cfg.router_select_bias = "sigmoid", True
+        cfg.n_group, cfg.topk_group = int(c.get("n_group") or 1), int(c.get("topk_group") or 1)
+    return cfg
+
+
+def _deepseek2(c): return _deepseek(c, "deepseek2")
+def _deepseek3(c): return _deepseek(c, "deepseek3")
 
 
 SHIPPED: List[FamilyEntry] = [
@@ -98,18 +251,18 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("phi3", ["phi3"], ["phi3"], _phi3),
     FamilyEntry("smollm3", ["smollm3"], ["smollm3"], _smollm3),
     FamilyEntry("granite", ["granite", "granitemoe"], ["granite"], _granite),
+    FamilyEntry("mpt", ["mpt"], ["mpt"], _mpt),
+    FamilyEntry("bloom", ["bloom"], ["bloom"], _bloom),
+    FamilyEntry("gemma3", ["gemma3", "gemma3_text"], ["gemma3"], _gemma3),
+    FamilyEntry("gemma2", ["gemma2"], ["gemma2"], _gemma2),
     FamilyEntry("qwen3moe", ["qwen3_moe"], ["qwen3moe"], _qwen3moe),
+    FamilyEntry("gpt_oss", ["gpt_oss"], ["gpt-oss"], _gpt_oss),
     FamilyEntry("olmoe", ["olmoe"], ["olmoe"], _olmoe),
+    FamilyEntry("minimax_m2", ["minimax_m2"], ["minimax-m2"], _minimax_m2),
+    FamilyEntry("deepseek2", ["deepseek_v2"], ["deepseek2"], _deepseek2),
+    FamilyEntry("deepseek3", ["deepseek_v3"], ["deepseek2"], _deepseek3),
     # families the reference ships whose mixers are not built here: refused by name
-    FamilyEntry("mpt", ["mpt"], ["mpt"], None, "ALiBi attention + LayerNorm stack"),
-    FamilyEntry("bloom", ["bloom"], ["bloom"], None, "ALiBi attention + LayerNorm stack"),
-    FamilyEntry("gemma2", ["gemma2"], ["gemma2"], None, "sandwich norms, GeGLU, logit softcap"),
-    FamilyEntry("gemma3", ["gemma3", "gemma3_text"], ["gemma3"], None, "sandwich norms, GeGLU, dual rope bases"),
     FamilyEntry("gemma4", ["gemma4"], ["gemma4"], None, "per-layer embeddings, proportional rope"),
-    FamilyEntry("gpt_oss", ["gpt_oss"], ["gpt-oss"], None, "attention sinks, MXFP4 experts, clamped SwiGLU"),
-    FamilyEntry("minimax_m2", ["minimax_m2"], ["minimax-m2"], None, "sigmoid router with bias"),
-    FamilyEntry("deepseek2", ["deepseek_v2"], ["deepseek2"], None, "multi-head latent attention"),
-    FamilyEntry("deepseek3", ["deepseek_v3"], ["deepseek2"], None, "multi-head latent attention, group-limited routing"),
     FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], None, "sparse attention indexer"),
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
     FamilyEntry("nemotron_h", ["nemotron_h"], ["nemotron_h"], None, "Mamba2 mixer"),

@@ -35,7 +35,10 @@ def rope(x, cos, sin, rot):
 def moe_ffn(cfg: DecoderConfig, L, x):
     logits = x @ L.router.float().T
     top_v, top_i = torch.topk(logits, cfg.top_k, dim=-1)  # ties: lower index first for equal values
-    gates = torch.softmax(top_v, dim=-1)
+    if cfg.norm_topk_prob:
+        gates = torch.softmax(top_v, dim=-1)
+    else:       # softmax over all experts, read at the selected ones, not renormalised
+        gates = torch.softmax(logits, dim=-1).gather(-1, top_i)
     out = torch.zeros_like(x)
     for e in range(cfg.n_experts):
         sel = (top_i == e)
@@ -71,10 +74,12 @@ def forward_logits(w: DecoderWeights, tokens: torch.Tensor, round_bf16: bool = T
     if cfg.embed_scale != 1.0:
         h = r(h * cfg.embed_scale)
     pos = torch.arange(T, device=dev)
-    mask = pos[None, :] <= pos[:, None]
-    if cfg.sliding_window > 0:
-        mask &= pos[None, :] > (pos[:, None] - cfg.sliding_window)
-    for L in w.layers:
+    causal = pos[None, :] <= pos[:, None]
+    scale = float(cfg.attn_scale) if cfg.attn_scale is not None else 1.0 / math.sqrt(D)
+    for li, L in enumerate(w.layers):
+        mask = causal
+        if cfg.window_of(li) > 0:
+            mask = causal & (pos[None, :] > (pos[:, None] - cfg.window_of(li)))
         x = r(rmsnorm(h, L.ln1, cfg.norm_eps))
         qkv = x @ L.wqkv.float().T
         if L.bqkv is not None:
@@ -90,7 +95,7 @@ def forward_logits(w: DecoderWeights, tokens: torch.Tensor, round_bf16: bool = T
         k = r(rope(k, cos, sin, cfg.rot))
         kk = k.repeat_interleave(cfg.n_rep, dim=1)
         vv = v.repeat_interleave(cfg.n_rep, dim=1)
-        s = torch.einsum("thd,shd->hts", q, kk) / math.sqrt(D)
+        s = torch.einsum("thd,shd->hts", q, kk) * scale
         if cfg.attn_softcap > 0:
             s = cfg.attn_softcap * torch.tanh(s / cfg.attn_softcap)
         s = s.masked_fill(~mask[None], float("-inf"))

@@ -61,9 +61,10 @@ class DecoderEngine:
     def __init__(self, weights: DecoderWeights, num_blocks: int, max_seqs: int, max_tokens: int,
                  max_blocks_per_seq: int, comm=None, device=None, use_graphs: bool = True):
         cfg = weights.cfg
-        if cfg.final_softcap > 0:
+        gaps = cfg.device_gaps()
+        if gaps:
             from .weights import UnsupportedOnDevice
-            raise UnsupportedOnDevice("soft-capped output logits are not implemented by the device program")
+            raise UnsupportedOnDevice(f"{cfg.family}: the device program does not implement " + ", ".join(gaps))
         if (cfg.residual_scale != 1.0 or cfg.logit_scale != 1.0) and not getattr(weights, "_scales_folded", False):
             from .weights import fold_scales
             fold_scales(weights)
@@ -137,7 +138,7 @@ class DecoderEngine:
                              torch.zeros(ts * self.hq * self.attn_splits_max * 2, dtype=torch.float32, device=dev))
         cos, sin = rope_tables(cfg, cfg.max_position)
         self.cos, self.sin = cos.to(dev), sin.to(dev)
-        self.scale = 1.0 / math.sqrt(D)
+        self.scale = float(cfg.attn_scale) if cfg.attn_scale is not None else 1.0 / math.sqrt(D)
         if comm is not None:
             comm.attach(self)
         self._graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
@@ -199,11 +200,11 @@ class DecoderEngine:
             K.attn_paged(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:R],
                          (self.row_ctx_simt if flash else self.row_ctx)[:R], self.hq, self.hkv, D, self.scale,
                          out=self.attn[:R], splits=splits, scratch=self.attn_scratch, softcap=cfg.attn_softcap,
-                         window=cfg.sliding_window)
+                         window=cfg.window_of(l))
         if flash:
             K.attn_flash_prefill(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables,
                                  self.attn_tiles[:self._tile_slots(T, B)], self.hq, self.hkv, self.scale,
-                                 out=self.attn[:R], window=cfg.sliding_window)
+                                 out=self.attn[:R], window=cfg.window_of(l))
 
     def _tile_slots(self, T: int, B: int) -> int:
         """Tile slots a (T, B) step can need: full tiles plus one ragged tile per sequence."""

@@ -24,12 +24,36 @@ FAMILIES = {
     "granite": {"model_type": "granite", "embedding_multiplier": 12.0, "residual_multiplier": 0.22, "logits_scaling": 8.0},
     "qwen3moe": {"model_type": "qwen3_moe", "num_experts": 4, "num_experts_per_tok": 2, "moe_intermediate_size": 32},
     "olmoe": {"model_type": "olmoe", "num_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 32},
+    "granitemoe": {"model_type": "granitemoe", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 32,
+                   "attention_multiplier": 0.3},
+    "gemma2": {"model_type": "gemma2", "query_pre_attn_scalar": 24, "sliding_window": 6, "attn_logit_softcapping": 5.0,
+               "final_logit_softcapping": 3.0},
+    "gemma3": {"model_type": "gemma3_text", "query_pre_attn_scalar": 24, "sliding_window": 6, "num_hidden_layers": 3,
+               "layer_types": ["sliding_attention", "sliding_attention", "full_attention"], "rope_local_base_freq": 10000.0},
+    "mpt": {"model_type": "mpt", "d_model": 64, "n_heads": 4, "n_layers": 2, "vocab_size": 200, "max_seq_len": 128,
+            "attn_config": {"alibi": True}},
+    "bloom": {"model_type": "bloom", "hidden_size": 96, "n_head": 6, "n_layer": 2, "vocab_size": 200},
+    "gpt_oss": {"model_type": "gpt_oss", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 32,
+                "sliding_window": 6, "layer_types": ["sliding_attention", "full_attention"], "attention_bias": True},
+    "minimax_m2": {"model_type": "minimax_m2", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 32},
+    "deepseek2": {"model_type": "deepseek_v2", "n_routed_experts": 8, "num_experts_per_tok": 3, "moe_intermediate_size": 32,
+                  "first_k_dense_replace": 1, "kv_lora_rank": 24, "q_lora_rank": None, "qk_rope_head_dim": 8,
+                  "qk_nope_head_dim": 16, "v_head_dim": 12, "n_shared_experts": 2, "num_key_value_heads": 4},
+    "deepseek3": {"model_type": "deepseek_v3", "n_routed_experts": 8, "num_experts_per_tok": 3, "moe_intermediate_size": 32,
+                  "first_k_dense_replace": 1, "kv_lora_rank": 24, "q_lora_rank": 32, "qk_rope_head_dim": 8,
+                  "qk_nope_head_dim": 16, "v_head_dim": 12, "n_shared_experts": 1, "n_group": 4, "topk_group": 2,
+                  "num_key_value_heads": 4},
 }
+OWN_DIMS = ("mpt", "bloom")
+
+
+def header(name):
+    return dict(FAMILIES[name]) if name in OWN_DIMS else {**BASE, **FAMILIES[name]}
 
 
 @pytest.mark.parametrize("name", sorted(FAMILIES))
 def test_supported_family_traces_compiles_and_decodes(name):
-    model = Registry.builtin().resolve_hf({**BASE, **FAMILIES[name]})
+    model = Registry.builtin().resolve_hf(header(name))
     cfg = model.cfg
     w = random_weights_f32(model, seed=0, std=0.2)
     rng = np.random.default_rng(3)
@@ -49,7 +73,8 @@ def test_supported_family_traces_compiles_and_decodes(name):
     rewritten = OracleSession(model, w, capacity=32, graph_transform=tf).step(toks)
     assert np.array_equal(rewritten, full)
     s = progs[0].graph.summary()
-    assert s.get("attention") == cfg.n_layers and "exp" not in {k for k in s if k in ("exp",)} or cfg.is_moe
+    if cfg.pos == "rope" and not cfg.attn_sinks:
+        assert s.get("attention") == cfg.n_layers       # every layer's attention chain became one composite
     if cfg.sliding_window:
         far = OracleSession(model, w, capacity=32).step(np.concatenate([rng.integers(0, cfg.vocab, (1, 4)), toks[:, 4:]], 1))
         # with a window of 8 the last token does not see the first four positions... through one layer; with two layers
@@ -59,26 +84,39 @@ def test_supported_family_traces_compiles_and_decodes(name):
 
 def test_refused_families_say_what_is_missing():
     reg = Registry.builtin()
-    for mt, word in (("gemma2", "GeGLU"), ("deepseek_v3", "latent attention"), ("nemotron_h", "Mamba2"),
-                     ("bert", "encoder"), ("qwen2_5_vl", "vision"), ("gpt_oss", "sinks")):
+    for mt, word in (("gemma4", "per-layer embeddings"), ("deepseek_v32", "sparse attention"), ("nemotron_h", "Mamba2"),
+                     ("bert", "encoder"), ("qwen2_5_vl", "vision"), ("qwen3_next", "delta-net")):
         with pytest.raises(UnsupportedFamily) as e:
             reg.resolve_hf({**BASE, "model_type": mt})
         assert word in str(e.value)
     with pytest.raises(UnsupportedFamily):
         reg.resolve_hf({**BASE, "model_type": "never_heard_of_it"})
     with pytest.raises(UnsupportedFamily):
-        reg.resolve_hf({**BASE, "model_type": "llama", "attention_bias": True})
-    assert len(reg.listed()) == 28 and len(reg.supported()) == 9
+        reg.resolve_hf({"model_type": "mpt", "d_model": 64, "n_heads": 4, "n_layers": 2, "vocab_size": 200,
+                        "attn_config": {"alibi": False}})
+    assert len(reg.listed()) == 28 and len(reg.supported()) == 17
 
 
-@pytest.mark.parametrize("name", ["qwen2", "granite", "llama", "qwen3"])
+def test_device_gaps_name_what_the_device_program_lacks():
+    """The oracle evaluates every supported family; the device program covers the pre-norm SwiGLU rope stack, and a
+    family outside it is refused on the device with the missing pieces named."""
+    reg = Registry.builtin()
+    assert reg.resolve_hf({**BASE, **FAMILIES["llama"], "head_dim": 64}).cfg.device_gaps() == []
+    assert reg.resolve_hf({**BASE, **FAMILIES["mixtral"], "head_dim": 128}).cfg.device_gaps() == []
+    for name, word in (("gemma2", "sandwich"), ("olmo2", "post-norm"), ("bloom", "LayerNorm"), ("mpt", "alibi"),
+                       ("gpt_oss", "sinks"), ("deepseek3", "latent attention"), ("minimax_m2", "router variant")):
+        gaps = reg.resolve_hf(header(name)).cfg.device_gaps()
+        assert any(word in g for g in gaps), (name, gaps)
+
+
+@pytest.mark.parametrize("name", ["qwen2", "granite", "llama", "qwen3", "mistral", "phi3", "mixtral", "qwen3moe", "granitemoe"])
 def test_torch_restatement_with_folded_scales_matches_the_oracle(name):
     """The PyTorch restatement the device tests compare against (with the family's constant multipliers folded into
     the weights, the q/k/v bias and the embedding scale applied at run time) equals the graph oracle on the CPU."""
     import torch
     from poot_b200.oracle.torch_ref import forward_logits
     from poot_b200.runtime.weights import from_named_tensors
-    model = Registry.builtin().resolve_hf({**BASE, **FAMILIES[name]})
+    model = Registry.builtin().resolve_hf(header(name))
     cfg = model.cfg
     w = random_weights_f32(model, seed=1, std=0.2)
     if cfg.attn_bias:
@@ -88,6 +126,14 @@ def test_torch_restatement_with_folded_scales_matches_the_oracle(name):
     sess._graph = lambda T, _m=model: _m.trace(__import__("poot_b200.models.model", fromlist=["StepSpec"]).StepSpec(
         rows=1, tokens=T, capacity=32, logit_rows="all"))
     ref = sess.step(toks)
-    dw = from_named_tensors(cfg, {k: torch.from_numpy(v) for k, v in w.items()}, "cpu", dtype=torch.float32)
+    named = {k: torch.from_numpy(v) for k, v in w.items()}
+    for l in range(cfg.n_layers if cfg.is_moe else 0):      # the device loader takes experts one by one
+        p = f"layers.{l}."
+        for e in range(cfg.n_experts):
+            named[p + f"experts.{e}.gate"] = named[p + "experts_in"][e, :cfg.moe_ffn]
+            named[p + f"experts.{e}.up"] = named[p + "experts_in"][e, cfg.moe_ffn:]
+            named[p + f"experts.{e}.down"] = named[p + "experts_out"][e]
+    assert cfg.device_gaps() == ["head_dim 16"]
+    dw = from_named_tensors(cfg, named, "cpu", dtype=torch.float32)
     got = forward_logits(dw, torch.from_numpy(toks[0]).int(), round_bf16=False).numpy()
     assert np.allclose(got, ref.reshape(got.shape), rtol=2e-4, atol=2e-5), np.abs(got - ref.reshape(got.shape)).max()

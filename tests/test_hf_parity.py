@@ -1,0 +1,88 @@
+"""Golden parity with the Hugging Face implementations, on the CPU.
+
+For every supported family a tiny randomly initialised ``transformers`` model is saved as a checkpoint directory
+(``config.json`` + safetensors), loaded through this package's own path (registry -> name tables -> weight store) and
+evaluated by the graph oracle; the logits of every position must equal the ``transformers`` forward pass to float
+precision.  That pins, independently of this package's own restatements, the header parsing of each family, its
+tensor-name table (fused projections, stacked experts, per-head interleaving) and the semantics of its block: norm
+placement, activations, biases, ALiBi, sliding windows per layer, two rotary bases, soft caps, attention sinks,
+router variants, shared experts, group-limited routing and multi-head latent attention."""
+import numpy as np
+import pytest
+
+transformers = pytest.importorskip("transformers")
+torch = pytest.importorskip("torch")
+
+from poot_b200.driver.handle import ModelHandle          # noqa: E402
+from poot_b200.models.model import StepSpec              # noqa: E402
+from poot_b200.oracle.runner import OracleSession        # noqa: E402
+
+BASE = dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
+            intermediate_size=96, vocab_size=200, max_position_embeddings=128)
+MLA = dict(n_routed_experts=8, num_experts_per_tok=3, moe_intermediate_size=32, first_k_dense_replace=1, kv_lora_rank=24,
+           qk_rope_head_dim=8, qk_nope_head_dim=16, v_head_dim=12, num_key_value_heads=4, head_dim=8)
+CASES = {
+    "llama": dict(model_type="llama", rms_norm_eps=1e-5),
+    "llama-biases": dict(model_type="llama", attention_bias=True, mlp_bias=True),
+    "mistral-window": dict(model_type="mistral", sliding_window=8),
+    "mixtral": dict(model_type="mixtral", num_local_experts=4, num_experts_per_tok=2),
+    "qwen2": dict(model_type="qwen2", tie_word_embeddings=True),
+    "qwen3": dict(model_type="qwen3"),
+    "olmo2": dict(model_type="olmo2"),
+    "phi3": dict(model_type="phi3", pad_token_id=0),
+    "smollm3-nope-layer": dict(model_type="smollm3", pad_token_id=0, no_rope_layers=[1, 0]),
+    "granite": dict(model_type="granite", embedding_multiplier=12.0, residual_multiplier=0.22, logits_scaling=8.0,
+                    attention_multiplier=0.2),
+    "granitemoe": dict(model_type="granitemoe", num_local_experts=4, num_experts_per_tok=2, intermediate_size=32,
+                       embedding_multiplier=3.0, residual_multiplier=0.5, logits_scaling=4.0, attention_multiplier=0.3),
+    "qwen3moe": dict(model_type="qwen3_moe", num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True),
+    "olmoe": dict(model_type="olmoe", num_experts=4, num_experts_per_tok=2, intermediate_size=32),
+    "gemma2": dict(model_type="gemma2", query_pre_attn_scalar=24, sliding_window=6, attn_logit_softcapping=5.0,
+                   final_logit_softcapping=3.0),
+    "gemma3": dict(model_type="gemma3_text", query_pre_attn_scalar=24, sliding_window=6, num_hidden_layers=3,
+                   layer_types=["sliding_attention", "sliding_attention", "full_attention"]),
+    "mpt": dict(model_type="mpt", d_model=64, n_heads=4, n_layers=2, vocab_size=200, max_seq_len=128),
+    "mpt-6-heads": dict(model_type="mpt", d_model=96, n_heads=6, n_layers=2, vocab_size=200, max_seq_len=128),
+    "bloom": dict(model_type="bloom", hidden_size=64, n_head=4, n_layer=2, vocab_size=200),
+    "bloom-6-heads": dict(model_type="bloom", hidden_size=96, n_head=6, n_layer=2, vocab_size=200),
+    "gpt_oss": dict(model_type="gpt_oss", num_local_experts=4, num_experts_per_tok=2, intermediate_size=32, sliding_window=6,
+                    layer_types=["sliding_attention", "full_attention"],
+                    rope_parameters={"rope_type": "default", "rope_theta": 10000.0}),
+    "minimax_m2": dict(model_type="minimax_m2", num_local_experts=4, num_experts_per_tok=2, intermediate_size=32),
+    "deepseek2": dict(model_type="deepseek_v2", q_lora_rank=None, n_shared_experts=2, **MLA),
+    "deepseek3": dict(model_type="deepseek_v3", q_lora_rank=32, n_shared_experts=1, n_group=4, topk_group=2, **MLA),
+}
+OWN_DIMS = ("mpt", "bloom")      # families whose headers do not use the llama field names
+
+
+def build(case: dict):
+    from transformers import AutoConfig, AutoModelForCausalLM
+    over = dict(case)
+    mt = over.pop("model_type")
+    d = over if mt in OWN_DIMS else {**BASE, **over}
+    cfg = AutoConfig.for_model(mt, **d)
+    torch.manual_seed(0)
+    m = AutoModelForCausalLM.from_config(cfg, attn_implementation="eager").float().eval()
+    with torch.no_grad():          # default initialisation is too tame to show a wrong norm or a wrong bias
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+            else:
+                p.mul_(4.0)
+    return m, d["vocab_size"]
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_logits_equal_the_hugging_face_forward(name, tmp_path):
+    m, vocab = build(CASES[name])
+    toks = torch.randint(0, vocab, (1, 12), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = m(toks).logits[0].numpy()
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    h = ModelHandle.load(str(tmp_path))
+    sess = OracleSession(h.model, h.oracle_weights(), capacity=32)
+    sess._graph = lambda T: h.model.trace(StepSpec(rows=1, tokens=T, capacity=32, logit_rows="all"))
+    got = sess.step(toks.numpy()).reshape(ref.shape)
+    assert np.isfinite(got).all()
+    err = np.abs(got - ref).max() / np.abs(ref).max()
+    assert err < 2e-5, err
