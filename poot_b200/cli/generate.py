@@ -96,8 +96,9 @@ def parse_generate(argv: List[str]) -> GenerateArgs:
         raise ValueError("sampling or context option out of range")
     if len(a.reverse_prompt) > 16:
         raise ValueError("at most 16 reverse prompts")
-    if a.backend not in ("auto", "b200", "cuda", "fake"):
-        raise ValueError(f"--backend {a.backend!r}: this build has one device backend (b200 / cuda / auto) and `fake`")
+    if a.backend not in ("auto", "b200", "cuda", "fake", "oracle"):
+        raise ValueError(f"--backend {a.backend!r}: this build has one device backend (b200 / cuda / auto), the CPU "
+                         "`oracle` and `fake`")
     return a
 
 
@@ -108,6 +109,8 @@ def _open(a: GenerateArgs):
     ctx = a.ctx_size or 4096
     if a.model.startswith("random:"):
         return LLM.random(a.model.split(":", 1)[1], rows=1, max_seq=ctx)
+    if a.backend == "oracle":
+        return LLM.oracle(a.model, rows=1, max_seq=ctx, num_blocks=(ctx + 15) // 16 + 1, lora=a.lora)
     return LLM.load(a.model, rows=1, max_seq=ctx, lora=a.lora)
 
 

@@ -128,6 +128,9 @@ class Driver:
         self.pool = BlockPool(num_blocks)
         self.prefix = PrefixCache(self.pool) if prefix_caching else None
         self.max_rows, self.max_seq_len, self.vocab = max_rows, max_seq_len, vocab
+        if prefill_chunk < BLOCK:
+            # a piece that does not finish its prompt is cut on a block boundary; a chunk below one block could never advance
+            raise DriverError(f"prefill_chunk {prefill_chunk} is smaller than the K/V block of {BLOCK} tokens")
         self.prefill_chunk = prefill_chunk
         # prefill tokens a step may carry: one chunk (the reference's budget, widest piece + rows) unless raised, in
         # which case several sequences' pieces share a step and the projections run at a larger, more efficient M

@@ -148,3 +148,121 @@ class DeviceStepEngine:
     def copy_block(self, src: int, dst: int) -> None:
         """Copy one K/V block in every layer (a forked sequence gets its own copy of the partial last block)."""
         self.e.kv.buf[:, :, dst].copy_(self.e.kv.buf[:, :, src])
+
+
+class OracleStepEngine:
+    """The CPU oracle behind the driver: every supported family runs end to end on the host.
+
+    A step's ragged token list is cut into its per-sequence segments; each segment is one evaluation of the family's
+    traced graph (``rows=1``, ``tokens=len(segment)``) whose paged K/V pools are this engine's state, read through
+    the sequence's block table and written at the step's slots - the same maps the device program gets.  Sampling,
+    logit adjustment and log-probabilities follow the rules the device kernels implement
+    (crates/poot-eval/src/ops/sampling.rs:61-183).  This is the reference's ``poot-eval`` used as an executor: slow,
+    exact in f32, and independent of any device kernel.
+    """
+
+    def __init__(self, model, weights, num_blocks: int, max_seqs: int, max_tokens: int, max_blocks_per_seq: int,
+                 options=None, graph_transform=None):
+        from ..oracle.eval import EvalOptions
+        from .kvcache import BLOCK
+        self.model, self.weights = model, weights
+        self.block = BLOCK
+        self.num_blocks, self.max_seqs, self.max_tokens, self.max_blocks = num_blocks, max_seqs, max_tokens, max_blocks_per_seq
+        self.options = options or EvalOptions(matmul_precision="exact")
+        self.graph_transform = graph_transform
+        self.block_tables = np.zeros((max_seqs, max_blocks_per_seq), np.int32)
+        self.state = {}
+        self.graphs = {}
+        self.steps = 0
+        self._logits: Optional[np.ndarray] = None
+        self.last_run_ms, self.last_device_ms, self.last_launches = None, None, 0
+
+    def write_block_table(self, row: int, blocks) -> None:
+        self.block_tables[row, :len(blocks)] = np.asarray(blocks, np.int32)
+
+    def _graph(self, tokens: int, capacity: int):
+        key = (tokens, capacity)
+        if key not in self.graphs:
+            from ..models.model import StepSpec
+            g = self.model.trace(StepSpec(rows=1, tokens=tokens, capacity=capacity, paged=True,
+                                          pool_slots=self.num_blocks * self.block))
+            self.graphs[key] = self.graph_transform(g) if self.graph_transform is not None else g
+        return self.graphs[key]
+
+    def _segment(self, row: int, tokens: np.ndarray, positions: np.ndarray, slots: np.ndarray, ctx: int) -> np.ndarray:
+        from ..oracle.eval import eval_graph
+        blocks = max(1, -(-ctx // self.block))
+        cap_blocks = 1
+        while cap_blocks < blocks:
+            cap_blocks *= 2
+        cap_blocks = min(cap_blocks, self.max_blocks)
+        cap = cap_blocks * self.block
+        g = self._graph(len(tokens), cap)
+        bt = self.block_tables[row, :cap_blocks].astype(np.int64)
+        read = (bt[:, None] * self.block + np.arange(self.block)[None, :]).reshape(1, cap).astype(np.int32)
+        inputs = {"tokens": tokens.reshape(1, -1).astype(np.int32), "positions": positions.reshape(1, -1).astype(np.int32),
+                  "read_map": read, "write_map": slots.astype(np.int32)}
+        for i in g.inputs:
+            if i.storage == "const":
+                inputs[i.name] = self.weights[i.name]
+            elif i.storage == "state":
+                if i.name not in self.state:
+                    self.state[i.name] = np.zeros(g.types[i.value].shape, dtype=np.float32)
+                inputs[i.name] = self.state[i.name]
+        ev = eval_graph(g, inputs, self.options)
+        for o in g.outputs:
+            if o.role == "state_next":
+                self.state[o.state_of] = ev.outputs[o.name]
+        return ev.outputs["logits"][0]
+
+    def run_step(self, inp: StepInputs):
+        import time as _time
+        from ..oracle.sampling import sample_rows
+        t0 = _time.perf_counter()
+        T, B = inp.live_tokens or len(inp.tokens), len(inp.logit_idx)
+        vocab = self.model.cfg.vocab
+        logits = np.zeros((B, vocab), np.float32)
+        want = {int(i): b for b, i in enumerate(inp.logit_idx[:inp.live_rows])}
+        start = 0
+        while start < T:
+            row = int(inp.row_seq[start])
+            end = start + 1
+            while end < T and int(inp.row_seq[end]) == row and int(inp.positions[end]) == int(inp.positions[end - 1]) + 1:
+                end += 1
+            if int(inp.row_ctx[start]) > 0:       # padding tokens have no context and write nothing
+                out = self._segment(row, inp.tokens[start:end], inp.positions[start:end], inp.slots[start:end],
+                                    int(inp.row_ctx[end - 1]))
+                if end - 1 in want:
+                    logits[want[end - 1]] = out
+            start = end
+        if inp.adjust is not None:
+            idx, val = inp.adjust["idx"], inp.adjust["val"]
+            for b in range(inp.live_rows):
+                for t, v in zip(idx[b], val[b]):
+                    if 0 <= t < vocab:
+                        l = np.float32(logits[b, t] + v[0])
+                        logits[b, t] = np.float32((l * v[1] if l > 0 else l * v[2]) + v[3])
+                m = inp.adjust["guided"].get(b)
+                if m is not None:
+                    m = np.asarray(m, np.float32)
+                    fmin = np.finfo(np.float32).min
+                    logits[b] = np.where(m <= fmin, fmin, logits[b] + m).astype(np.float32)
+        picked = sample_rows(logits, inp.params, inp.top_k, inp.seeds, inp.sampler)
+        lp = None
+        if inp.want_logprobs:
+            mx = logits.max(-1, keepdims=True)
+            lse = mx[:, 0] + np.log(np.exp(logits - mx).sum(-1))
+            lp = (logits[np.arange(B), picked[:, 0]] - lse).astype(np.float32)
+        self._logits = logits
+        self.steps += 1
+        self.last_run_ms = (_time.perf_counter() - t0) * 1e3
+        return picked, lp
+
+    def last_logits(self, rows: int) -> np.ndarray:
+        return self._logits[:rows]
+
+    def copy_block(self, src: int, dst: int) -> None:
+        b = self.block
+        for name, pool in self.state.items():
+            if name.endswith(("k_pool", "v_pool")):
+                pool[dst * b:(dst + 1) * b] = pool[src * b:(src + 1) * b]

@@ -103,6 +103,35 @@ class LLM:
                      max_seq, vocab, prefill_chunk=prefill_chunk, eos_token=tk.eos, prefill_budget=prefill_budget)
         return LLM(None, drv, tk)
 
+    @staticmethod
+    def oracle(path: str, rows: int = 4, max_seq: int = 512, num_blocks: int = 128, prefill_chunk: int = 64,
+               lora: Optional[str] = None, prefill_budget: Optional[int] = None) -> "LLM":
+        """A checkpoint served by the CPU oracle: every supported family end to end on the host, in f32, through the
+        same driver (paged K/V, prefix cache, sampling rules) as the device engine.  Slow; meant for checking a
+        family or a checkpoint without a device."""
+        from .driver.engines import OracleStepEngine
+        from .driver.handle import ModelHandle
+        handle = ModelHandle.load(path)
+        if lora is not None:
+            from .load.lora import load_adapter
+            handle.apply_adapter(load_adapter(lora))
+        return LLM.oracle_from(handle.model, handle.oracle_weights(), _tokenizer_for(handle), rows, max_seq, num_blocks,
+                               prefill_chunk, handle, prefill_budget)
+
+    @staticmethod
+    def oracle_from(model, weights, tokenizer=None, rows: int = 4, max_seq: int = 512, num_blocks: int = 128,
+                    prefill_chunk: int = 64, handle=None, prefill_budget: Optional[int] = None) -> "LLM":
+        from .driver.engines import OracleStepEngine
+        cfg = model.cfg
+        max_seq = min(max_seq, cfg.max_position)
+        step_prefill = max(prefill_chunk, min(prefill_budget or 0, rows * prefill_chunk))
+        eng = OracleStepEngine(model, weights, num_blocks, rows, step_prefill + rows, blocks_for(max_seq))
+        tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
+        eos = getattr(tokenizer, "eos", None)
+        drv = Driver(eng, num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
+                     eos_token=eos if eos is not None else cfg.eos_token, prefill_budget=step_prefill)
+        return LLM(cfg, drv, tokenizer, None, handle, None)
+
     # ---- generation ----------------------------------------------------------------------------------------------
     def generate_tokens(self, prompt: Iterable[int], params: Optional[SamplingParams] = None, on_token=None) -> List[int]:
         return self.driver.generate(list(prompt), params, on_token)

@@ -27,6 +27,12 @@ def main(argv=None) -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     comm = None
+    if cfg.backend not in ("b200", "cuda", "auto", "oracle"):
+        print(f"poot-serve: --backend {cfg.backend!r}: this build has the device backend (b200) and `oracle`", file=sys.stderr)
+        return 2
+    if cfg.backend == "oracle" and world > 1:
+        print("poot-serve: the oracle backend runs in one process", file=sys.stderr)
+        return 2
     if world > 1:
         import torch
         import torch.distributed as dist
@@ -42,6 +48,9 @@ def main(argv=None) -> int:
         llm = LLM.random(cfg.model.split(":", 1)[1], rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
                          kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm,
                          prefill_budget=cfg.prefill_budget or None)
+    elif cfg.backend == "oracle":
+        llm = LLM.oracle(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, lora=cfg.lora,
+                         num_blocks=cfg.rows * ((cfg.max_seq + 15) // 16) + 8, prefill_budget=cfg.prefill_budget or None)
     else:
         llm = LLM.load(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
                        kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm, lora=cfg.lora,

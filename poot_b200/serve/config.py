@@ -41,6 +41,7 @@ class ServeConfig:
     allowed_hosts: List[str] = field(default_factory=list)
     model_id: Optional[str] = None
     lora: Optional[str] = None           # PEFT adapter directory merged into the projections at load
+    backend: str = "b200"                # b200 (the device engine) | oracle (the CPU graph evaluator; every family, slow)
 
     def validate(self) -> None:
         def bound(name, lo, hi):
