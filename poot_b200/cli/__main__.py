@@ -16,10 +16,13 @@ def main(argv=None) -> int:
     cmd, rest = argv[0], argv[1:]
     if cmd == "generate":
         return main_generate(rest)
-    if cmd in ("caption", "embed"):
-        # The reference serves these through its vision front ends and encoder families
-        # (crates/poot-llm/src/bin/poot/main.rs:42-55); this build registers decoder-only text families.
-        print(f"error: `{cmd}` needs a vision / encoder family; only decoder text families are registered", file=sys.stderr)
+    if cmd == "embed":
+        from .embed import main_embed
+        return main_embed(rest)
+    if cmd == "caption":
+        # The reference serves this through its vision front ends (crates/poot-llm/src/bin/poot/main.rs:42-55);
+        # this build registers text families only.
+        print("error: `caption` needs a vision family; only text families are registered", file=sys.stderr)
         return 2
     print(f"error: unknown command {cmd!r}\n{USAGE}", file=sys.stderr)
     return 2

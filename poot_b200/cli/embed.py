@@ -1,0 +1,40 @@
+"""``poot embed {similarity|rerank|cross} MODEL_DIR TEXT...`` (crates/poot-llm/src/bin/poot/embed.rs:1-80).
+
+``similarity`` prints the cosine of each later text to the first; ``rerank`` ranks the documents after the query by
+the cosine of their embeddings; ``cross`` ranks them by a cross-encoder's relevance logit."""
+from __future__ import annotations
+
+import sys
+from typing import List
+
+USAGE = "usage: poot embed {similarity|rerank|cross} MODEL_DIR TEXT [TEXT ...]"
+
+
+def main_embed(argv: List[str], out=None) -> int:
+    out = out or sys.stdout
+    if len(argv) < 3 or argv[0] not in ("similarity", "rerank", "cross"):
+        print(USAGE, file=sys.stderr)
+        return 2
+    mode, path, texts = argv[0], argv[1], argv[2:]
+    from ..embed import Embedder, EmbedError
+    try:
+        emb = Embedder.load(path)
+        if mode == "similarity":
+            vec, _ = emb.embed(texts)
+            print("pooling mean", file=out)
+            for t, v in zip(texts[1:], vec[1:]):
+                print(f"{float(v @ vec[0]):+.3f}  {t}", file=out)
+            return 0
+        if len(texts) < 2:
+            print("error: a query and at least one document", file=sys.stderr)
+            return 2
+        if (mode == "cross") != bool(emb.cfg.labels):
+            raise EmbedError("`cross` needs a cross-encoder checkpoint; `rerank` an embedding encoder")
+        scores, _ = emb.rerank(texts[0], texts[1:])
+        order = sorted(range(len(scores)), key=lambda i: (-float(scores[i]), i))
+        for rank, i in enumerate(order):
+            print(f"{rank + 1}. {float(scores[i]):+.3f}  {texts[1 + i]}", file=out)
+        return 0
+    except (EmbedError, FileNotFoundError, ValueError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2

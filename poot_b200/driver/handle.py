@@ -93,6 +93,8 @@ class ModelHandle:
         for n, w in self.canonical.items():
             if ".experts." not in n:
                 out[n] = w.to_f32()
+        if getattr(self.model, "kind", "decoder") == "encoder":
+            return out
         for l in range(c.n_layers):
             if not c.moe_layer(l):
                 continue

@@ -90,8 +90,32 @@ def _deinterleave_rows(n: int) -> np.ndarray:
     return np.concatenate([np.arange(0, n, 2), np.arange(1, n, 2)])
 
 
+BERT_TOP = {"embeddings.word_embeddings.weight": "embed", "embeddings.position_embeddings.weight": "embed_pos",
+            "embeddings.token_type_embeddings.weight": "embed_type", "embeddings.LayerNorm.weight": "embed_norm",
+            "embeddings.LayerNorm.bias": "embed_norm_bias", "pooler.dense.weight": "pooler", "pooler.dense.bias": "pooler_bias",
+            "classifier.weight": "classifier", "classifier.bias": "classifier_bias"}
+BERT_LAYER = {"attention.self.query": "attn_q", "attention.self.key": "attn_k", "attention.self.value": "attn_v",
+              "attention.output.dense": "attn_o", "attention.output.LayerNorm": "attn_post_norm",
+              "intermediate.dense": "ffn_up", "output.dense": "ffn_down", "output.LayerNorm": "ffn_post_norm"}
+
+
+def _map_bert(cfg, store: WeightStore) -> Dict[str, PackedWeight]:
+    canon: Dict[str, PackedWeight] = {}
+    for n in store.names():
+        short = n[5:] if n.startswith("bert.") else n
+        if short in BERT_TOP:
+            canon[BERT_TOP[short]] = store[n]
+            continue
+        m = re.match(r"encoder\.layer\.(\d+)\.(.+)\.(weight|bias)$", short)
+        if m and m.group(2) in BERT_LAYER:
+            canon[f"layers.{m.group(1)}.{BERT_LAYER[m.group(2)]}" + ("_bias" if m.group(3) == "bias" else "")] = store[n]
+    return canon
+
+
 def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWeight]:
     """Canonical role name -> stored tensor for one Hugging Face checkpoint of ``cfg``'s family."""
+    if cfg.family == "bert":
+        return _map_bert(cfg, store)
     if cfg.family == "mpt":
         return _map_mpt(cfg, store)
     if cfg.family == "bloom":

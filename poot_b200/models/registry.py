@@ -26,6 +26,7 @@ class FamilyEntry:
     gguf_archs: List[str]
     from_hf: Optional[Callable[[dict], DecoderConfig]]
     missing: Optional[str] = None     # capability that is not built when the family is refused
+    kind: str = "decoder"             # decoder (standard stack) | encoder (embeddings / rerank scores)
 
 
 def _rope_params(c: dict, layer_type: Optional[str] = None) -> dict:
@@ -243,6 +244,21 @@ def _deepseek2(c): return _deepseek(c, "deepseek2")
 def _deepseek3(c): return _deepseek(c, "deepseek3")
 
 
+def _bert(c):
+    from .encoder import EncoderConfig
+    if (c.get("position_embedding_type") or "absolute") != "absolute":
+        raise UnsupportedFamily("bert with relative position embeddings")
+    act = {"gelu": "gelu_erf", "gelu_new": "gelu_tanh", "gelu_pytorch_tanh": "gelu_tanh", "relu": "relu"}.get(c.get("hidden_act", "gelu"))
+    if act is None:
+        raise UnsupportedFamily(f"bert activation {c.get('hidden_act')!r}")
+    arch = " ".join(c.get("architectures") or [])
+    labels = len(c.get("id2label") or {}) or int(c.get("num_labels") or 0) if "SequenceClassification" in arch else 0
+    return EncoderConfig(n_layers=c["num_hidden_layers"], hidden=c["hidden_size"], n_heads=c["num_attention_heads"],
+                         ffn=c["intermediate_size"], vocab=c["vocab_size"], max_position=c.get("max_position_embeddings", 512),
+                         type_vocab=c.get("type_vocab_size", 2), norm_eps=float(c.get("layer_norm_eps", 1e-12)), act=act,
+                         labels=labels, pad_token=int(c.get("pad_token_id") or 0))
+
+
 SHIPPED: List[FamilyEntry] = [
     FamilyEntry("qwen2", ["qwen2"], ["qwen2"], _qwen2),
     FamilyEntry("llama", ["llama", "mistral", "mixtral"], ["llama"], _llama),
@@ -261,12 +277,12 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("minimax_m2", ["minimax_m2"], ["minimax-m2"], _minimax_m2),
     FamilyEntry("deepseek2", ["deepseek_v2"], ["deepseek2"], _deepseek2),
     FamilyEntry("deepseek3", ["deepseek_v3"], ["deepseek2"], _deepseek3),
+    FamilyEntry("bert", ["bert"], ["bert"], _bert, kind="encoder"),
     # families the reference ships whose mixers are not built here: refused by name
     FamilyEntry("gemma4", ["gemma4"], ["gemma4"], None, "per-layer embeddings, proportional rope"),
     FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], None, "sparse attention indexer"),
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
     FamilyEntry("nemotron_h", ["nemotron_h"], ["nemotron_h"], None, "Mamba2 mixer"),
-    FamilyEntry("bert", ["bert"], ["bert"], None, "bidirectional encoder"),
     FamilyEntry("idefics3", ["idefics3"], [], None, "vision tower"),
     FamilyEntry("qwen3next", ["qwen3_next"], ["qwen3next"], None, "gated delta-net mixer"),
     FamilyEntry("qwen38", ["qwen3_8"], ["qwen38"], None, "gated delta-net mixer"),
@@ -290,6 +306,9 @@ class Registry:
             if mt in e.hf_types:
                 if e.from_hf is None:
                     raise UnsupportedFamily(f"family {e.name!r} needs {e.missing}, which this build does not have")
+                if e.kind == "encoder":
+                    from .encoder import EncoderModel
+                    return EncoderModel(e.from_hf(config))
                 return Model(e.from_hf(config))
         raise UnsupportedFamily(f"no family for model_type {mt!r}")
 

@@ -42,6 +42,8 @@ def main(argv=None) -> int:
         comm = make_comm("fused", rank, world, torch.device("cuda", torch.cuda.current_device()))
         from .follower import init_control_group
         init_control_group()
+    if _is_encoder_checkpoint(cfg.model):
+        return _serve_encoder(cfg)
     if cfg.model == "fake":
         llm = LLM.fake(rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, prefill_budget=cfg.prefill_budget or None)
     elif cfg.model.startswith("random:"):
@@ -101,6 +103,32 @@ def main(argv=None) -> int:
             os._exit(0)
         _leave(llm)
     llm.close()
+    return 0
+
+
+def _is_encoder_checkpoint(path: str) -> bool:
+    import json
+    header = os.path.join(path, "config.json")
+    if not os.path.isfile(header):
+        return False
+    with open(header) as f:
+        return json.load(f).get("model_type") in ("bert",)
+
+
+def _serve_encoder(cfg) -> int:
+    """An encoder checkpoint serves ``/v1/embeddings`` and ``/v1/rerank`` (evaluated by the CPU oracle)."""
+    from ..embed import Embedder, EmbedEngine
+    emb = Embedder.load(cfg.model)
+    engine = EmbedEngine(emb, Metrics())
+    state = ServerState(engine, cfg, cfg.model_id or emb.name, family="bert")
+    server = Server(state)
+    server.start()
+    print(f"poot-b200 serving encoder {state.model_id} on http://{cfg.addr}", flush=True)
+    stop = threading.Event()
+    for sig in (signal.SIGINT, signal.SIGTERM):
+        signal.signal(sig, lambda *_: stop.set())
+    stop.wait()
+    server.shutdown()
     return 0
 
 

@@ -1,7 +1,7 @@
 """OpenAI-compatible HTTP/1.1 server on the standard library (the reference server is std-only too).
 
 Surface (website/docs/serve/api.md:33-76): ``POST /v1/completions``, ``POST /v1/chat/completions`` (JSON or SSE),
-``POST /v1/embeddings`` and ``/v1/rerank`` (refused with an OpenAI-shaped error: no encoder family is built),
+``POST /v1/embeddings`` and ``/v1/rerank`` (served when the model is an encoder checkpoint; refused otherwise),
 ``GET /v1/models[/{id}]``, ``/health``, ``/metrics``, ``/metrics/prometheus``, ``GET/POST/DELETE /v1/lora_adapters``
 (admin key).  Hardening: 64 KiB header cap, body caps, Host policy, per-minute rate limit, bounded pending queue
 (429 + Retry-After), request / write timeouts, clamps (``max_tokens`` <= 32768, <= 16 stop strings, <= 10 000
@@ -110,6 +110,7 @@ class ServerState:
             with open(cfg.lora_admin_key_file) as f:
                 self.admin_key = f.read().strip()
         self.adapters: Dict[str, dict] = {}
+        self.embedder = getattr(engine, "embedder", None)    # set when the served model is an encoder
 
 
 def make_handler(state: ServerState):
@@ -222,13 +223,78 @@ def make_handler(state: ServerState):
             except ApiError as e:
                 self._error(e)
 
+        # ---- encoder routes ---------------------------------------------------------------------------------
+        def _encoder_call(self, fn):
+            from ..embed import EmbedError
+            try:
+                return eng.run(fn)
+            except EmbedError as e:
+                raise ApiError(400, str(e))
+            except RuntimeError as e:
+                raise ApiError(503, str(e), "service_unavailable")
+
+        def _embeddings(self, req: dict) -> dict:
+            inp = req.get("input")
+            if isinstance(inp, str):
+                inp = [inp]
+            if not isinstance(inp, list) or not inp or len(inp) > 2048:
+                raise ApiError(400, "`input` must be a string, a list of strings or a list of token-id lists (at most 2048)")
+            fmt = req.get("encoding_format", "float")
+            if fmt not in ("float", "base64"):
+                raise ApiError(400, "`encoding_format` must be float or base64")
+            pooling = req.get("pooling", "mean")
+            emb = state.embedder
+            if all(isinstance(x, str) for x in inp):
+                vec, n = self._encoder_call(lambda: emb.embed(inp, pooling, bool(req.get("normalize", True))))
+            elif all(isinstance(x, list) and x and all(isinstance(t, int) and 0 <= t < emb.cfg.vocab for t in x) for x in inp):
+                vec = self._encoder_call(lambda: emb.embed_ids(inp, pooling, bool(req.get("normalize", True))))
+                n = sum(len(x) for x in inp)
+            else:
+                raise ApiError(400, "`input` mixes strings and token lists, or names a token outside the vocabulary")
+            dims = req.get("dimensions")
+            if dims is not None:
+                if not isinstance(dims, int) or not (0 < dims <= vec.shape[1]):
+                    raise ApiError(400, f"`dimensions` must be between 1 and {vec.shape[1]}")
+                vec = vec[:, :dims]
+            def one(v):
+                if fmt == "base64":
+                    import base64
+                    return base64.b64encode(v.astype("<f4").tobytes()).decode()
+                return [float(x) for x in v]
+            return {"object": "list", "model": state.model_id,
+                    "data": [{"object": "embedding", "index": i, "embedding": one(v)} for i, v in enumerate(vec)],
+                    "usage": {"prompt_tokens": n, "total_tokens": n}}
+
+        def _rerank(self, req: dict) -> dict:
+            q, docs = req.get("query"), req.get("documents")
+            if not isinstance(q, str) or not isinstance(docs, list) or not docs or len(docs) > 1024:
+                raise ApiError(400, "`query` must be a string and `documents` a non-empty list (at most 1024)")
+            texts = [d if isinstance(d, str) else d.get("text") if isinstance(d, dict) else None for d in docs]
+            if any(not isinstance(t, str) for t in texts):
+                raise ApiError(400, "every document must be a string or an object with a `text` field")
+            top_n = req.get("top_n", len(texts))
+            if not isinstance(top_n, int) or top_n < 1:
+                raise ApiError(400, "`top_n` must be a positive integer")
+            scores, n = self._encoder_call(lambda: state.embedder.rerank(q, texts))
+            order = sorted(range(len(texts)), key=lambda i: (-float(scores[i]), i))[:top_n]
+            res = [{"index": i, "relevance_score": float(scores[i]),
+                    **({"document": {"text": texts[i]}} if req.get("return_documents") else {})} for i in order]
+            return {"model": state.model_id, "results": res, "usage": {"prompt_tokens": n, "total_tokens": n}}
+
         def do_POST(self):
             try:
                 self._check_head()
                 path = self.path.split("?")[0]
                 if path in ("/v1/embeddings", "/v1/rerank"):
+                    req = self._body()
+                    if state.embedder is None:
+                        raise ApiError(400, "the served model is a decoder: no embedding / rerank head is available")
+                    if not state.limiter.allow():
+                        raise ApiError(429, "rate limit exceeded", "rate_limit_error", retry_after=60)
+                    return self._send(200, self._embeddings(req) if path == "/v1/embeddings" else self._rerank(req))
+                if state.embedder is not None and path in ("/v1/completions", "/v1/chat/completions"):
                     self._body()
-                    raise ApiError(400, "the served model is a decoder: no embedding / rerank head is available")
+                    raise ApiError(400, "the served model is an encoder: it embeds and scores, it does not generate")
                 if path == "/v1/lora_adapters":
                     self._admin()
                     req = self._body()

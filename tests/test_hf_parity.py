@@ -132,3 +132,117 @@ def test_cli_generates_from_a_checkpoint_on_the_oracle_backend(tmp_path):
     r = run_generate(parse_generate(["-m", str(tmp_path), "--backend", "oracle", "-p", "ab", "-n", "4", "--temp", "0",
                                      "--no-chat-template", "--ignore-eos"]), out=out)
     assert r["generated"] == 4
+
+
+# ---- encoders --------------------------------------------------------------------------------------------------
+BERT = dict(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128, vocab_size=300,
+            max_position_embeddings=64, type_vocab_size=2)
+
+
+def _bert(cls, tmp_path, **kw):
+    from transformers import BertConfig
+    torch.manual_seed(0)
+    m = cls(BertConfig(**BERT, **kw)).float().eval()
+    with torch.no_grad():
+        for p in m.parameters():
+            if p.dim() == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+            else:
+                p.mul_(3.0)
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    return m
+
+
+def test_bert_hidden_states_equal_hugging_face_and_ignore_padding(tmp_path):
+    from transformers import BertModel
+    from poot_b200.embed import Embedder
+    m = _bert(BertModel, tmp_path)
+    emb = Embedder.load(str(tmp_path))
+    g = torch.Generator().manual_seed(3)
+    a, b = torch.randint(1, 300, (1, 11), generator=g), torch.randint(1, 300, (1, 5), generator=g)
+    with torch.no_grad():
+        ra = m(a).last_hidden_state[0].numpy()
+        rb = m(b).last_hidden_state[0].numpy()
+    hid = emb.forward([a[0].tolist(), b[0].tolist()])          # one right-padded batch
+    assert np.abs(hid[0, :11] - ra).max() < 1e-4 * np.abs(ra).max()
+    assert np.abs(hid[1, :5] - rb).max() < 1e-4 * np.abs(rb).max()
+    vec = emb.embed_ids([a[0].tolist(), b[0].tolist()])
+    want = ra.mean(0) / np.linalg.norm(ra.mean(0))
+    assert np.allclose(vec[0], want, atol=1e-5) and abs(np.linalg.norm(vec[1]) - 1) < 1e-5
+
+
+def test_bert_cross_encoder_scores_and_http_routes(tmp_path):
+    import json
+    import urllib.request
+    from transformers import BertForSequenceClassification
+    from poot_b200.embed import Embedder, EmbedEngine
+    from poot_b200.serve.config import ServeConfig
+    from poot_b200.serve.http import Server, ServerState
+    from poot_b200.serve.metrics import Metrics
+    m = _bert(BertForSequenceClassification, tmp_path, num_labels=1)
+    emb = Embedder.load(str(tmp_path))
+    assert emb.cfg.labels == 1
+    ids, types = emb.tk.encode("what is a kernel", "a function that runs on the device")
+    with torch.no_grad():
+        want = m(torch.tensor([ids]), token_type_ids=torch.tensor([types])).logits[0, 0].item()
+    scores, _ = emb.rerank("what is a kernel", ["a function that runs on the device", "bread"])
+    assert abs(float(scores[0]) - want) < 1e-4 * max(1.0, abs(want))
+    cfg = ServeConfig(model=str(tmp_path), addr="127.0.0.1:0")
+    server = Server(ServerState(EmbedEngine(emb, Metrics()), cfg, "tiny-cross-encoder", family="bert"))
+    server.start()
+    try:
+        def post(path, body):
+            req = urllib.request.Request(f"http://127.0.0.1:{server.port}{path}", json.dumps(body).encode(),
+                                         {"Content-Type": "application/json"})
+            try:
+                with urllib.request.urlopen(req, timeout=30) as r:
+                    return r.status, json.loads(r.read())
+            except urllib.error.HTTPError as e:
+                return e.code, json.loads(e.read())
+        st, body = post("/v1/rerank", {"query": "what is a kernel", "documents": ["a function that runs on the device", {"text": "bread"}],
+                                       "return_documents": True})
+        assert st == 200 and len(body["results"]) == 2
+        top = body["results"][0]
+        assert abs(top["relevance_score"] - float(scores[top["index"]])) < 1e-6 and "text" in top["document"]
+        assert body["results"][0]["relevance_score"] >= body["results"][1]["relevance_score"]
+        st, body = post("/v1/embeddings", {"input": "x"})
+        assert st == 400 and "classifier" in body["error"]["message"]
+        st, body = post("/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}]})
+        assert st == 400 and "encoder" in body["error"]["message"]
+    finally:
+        server.shutdown()
+
+
+def test_embeddings_route_and_cli(tmp_path, capsys):
+    import base64
+    import json
+    import urllib.request
+    from transformers import BertModel
+    from poot_b200.cli.__main__ import main
+    from poot_b200.embed import Embedder, EmbedEngine
+    from poot_b200.serve.config import ServeConfig
+    from poot_b200.serve.http import Server, ServerState
+    from poot_b200.serve.metrics import Metrics
+    _bert(BertModel, tmp_path)
+    emb = Embedder.load(str(tmp_path))
+    server = Server(ServerState(EmbedEngine(emb, Metrics()), ServeConfig(model=str(tmp_path), addr="127.0.0.1:0"), "tiny-bert", family="bert"))
+    server.start()
+    try:
+        def post(body):
+            req = urllib.request.Request(f"http://127.0.0.1:{server.port}/v1/embeddings", json.dumps(body).encode(),
+                                         {"Content-Type": "application/json"})
+            with urllib.request.urlopen(req, timeout=30) as r:
+                return json.loads(r.read())
+        r = post({"input": ["alpha", "beta gamma"], "model": "tiny-bert"})
+        want, n = emb.embed(["alpha", "beta gamma"])
+        assert r["usage"]["prompt_tokens"] == n and len(r["data"]) == 2
+        assert np.allclose(r["data"][1]["embedding"], want[1], atol=1e-6)
+        r64 = post({"input": "alpha", "encoding_format": "base64", "dimensions": 16})
+        v = np.frombuffer(base64.b64decode(r64["data"][0]["embedding"]), "<f4")
+        assert v.shape == (16,) and np.allclose(v, want[0][:16], atol=1e-6)
+    finally:
+        server.shutdown()
+    assert main(["embed", "similarity", str(tmp_path), "alpha", "alpha", "zz top"]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert lines[0].startswith("pooling") and lines[1].startswith("+1.000") and len(lines) == 3
+    assert main(["embed", "cross", str(tmp_path), "q", "d"]) == 2      # not a cross-encoder
