@@ -202,17 +202,22 @@ class OracleStepEngine:
         read = (bt[:, None] * self.block + np.arange(self.block)[None, :]).reshape(1, cap).astype(np.int32)
         inputs = {"tokens": tokens.reshape(1, -1).astype(np.int32), "positions": positions.reshape(1, -1).astype(np.int32),
                   "read_map": read, "write_map": slots.astype(np.int32)}
+        fresh = int(positions[0]) == 0        # a sequence's first segment starts its recurrences from zero
+        keys = {}
         for i in g.inputs:
             if i.storage == "const":
                 inputs[i.name] = self.weights[i.name]
             elif i.storage == "state":
-                if i.name not in self.state:
-                    self.state[i.name] = np.zeros(g.types[i.value].shape, dtype=np.float32)
-                inputs[i.name] = self.state[i.name]
+                # paged pools are shared by every sequence; recurrent state (conv taps, scan carry) belongs to the row
+                key = (row, i.name) if getattr(i, "state_role", None) == "recurrent" else i.name
+                if key not in self.state or (isinstance(key, tuple) and fresh):
+                    self.state[key] = np.zeros(g.types[i.value].shape, dtype=np.float32)
+                inputs[i.name] = self.state[key]
+                keys[i.name] = key
         ev = eval_graph(g, inputs, self.options)
         for o in g.outputs:
             if o.role == "state_next":
-                self.state[o.state_of] = ev.outputs[o.name]
+                self.state[keys[o.state_of]] = ev.outputs[o.name]
         return ev.outputs["logits"][0]
 
     def run_step(self, inp: StepInputs):
@@ -264,5 +269,5 @@ class OracleStepEngine:
     def copy_block(self, src: int, dst: int) -> None:
         b = self.block
         for name, pool in self.state.items():
-            if name.endswith(("k_pool", "v_pool")):
+            if isinstance(name, str) and name.endswith(("k_pool", "v_pool")):
                 pool[dst * b:(dst + 1) * b] = pool[src * b:(src + 1) * b]

@@ -96,11 +96,14 @@ class ModelHandle:
         if getattr(self.model, "kind", "decoder") == "encoder":
             return out
         for l in range(c.n_layers):
-            if not c.moe_layer(l):
+            if not (c.has_ffn(l) and c.moe_layer(l)):
                 continue
             p = f"layers.{l}."
-            gi = np.stack([np.concatenate([self.f32(p + f"experts.{e}.gate"), self.f32(p + f"experts.{e}.up")], 0)
-                           for e in range(c.n_experts)])
+            if c.gated_ffn:
+                gi = np.stack([np.concatenate([self.f32(p + f"experts.{e}.gate"), self.f32(p + f"experts.{e}.up")], 0)
+                               for e in range(c.n_experts)])
+            else:
+                gi = np.stack([self.f32(p + f"experts.{e}.up") for e in range(c.n_experts)])
             out[p + "experts_in"] = gi
             out[p + "experts_out"] = np.stack([self.f32(p + f"experts.{e}.down") for e in range(c.n_experts)])
         if c.tie_embeddings:

@@ -145,7 +145,23 @@ def infer(op: str, attrs: Dict[str, Any], ins: List[TensorType], body=None) -> L
         (rank,) = ins     # stable descending rank [rows, E] -> ids [rows, k]
         return [TensorType((rank.shape[0], attrs["k"]), I32)]
     if op == "scan":
-        return [TensorType(tuple(attrs["shape"]), ins[0].dtype)]
+        fam = attrs.get("family")
+        first = ins[0]
+        if fam not in ("delta_rule", "ssd") or first.rank != 4 or first.shape[0] != 1 or any(t.dtype != F32 for t in ins):
+            raise GraphError(f"scan: family {fam!r}, lead operand {first.shape}")
+        _, h, l, w = first.shape
+        if fam == "delta_rule":
+            want = [(1, h, l, w), (1, h, l, w), (1, h, l, w), (1, h, l, 1), (1, h, l, 1), (1, h, w, w)]
+            rows = w
+        else:
+            n = ins[1].shape[3] if ins[1].rank == 4 else 0
+            want = [(1, h, l, w), (1, h, l, n), (1, h, l, n), (1, h, l, 1), (1, h, 1, 1), (1, h, 1, 1), (1, h, n, w)]
+            rows = n
+        if len(ins) != len(want) or any(tuple(t.shape) != s_ for t, s_ in zip(ins, want)) or rows == 0:
+            raise GraphError(f"scan {fam}: operands {[tuple(t.shape) for t in ins]}, expected {want}")
+        if tuple(attrs["shape"]) != (1, h, l + rows, w):
+            raise GraphError("scan: packed shape does not match the operands")
+        return [TensorType((1, h, l + rows, w), F32)]
     if op == "random_uniform":
         (seed,) = ins
         return [TensorType(tuple(seed.shape) + (attrs["cols"],), F32)]

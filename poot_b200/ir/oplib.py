@@ -84,6 +84,42 @@ def softplus(b: Builder, x: Traced) -> Traced:
     return b.unary("log", 1.0 + b.unary("exp", x))
 
 
+def softplus_stable(b: Builder, x: Traced) -> Traced:
+    """``max(x, 0) + log(1 + exp(-|x|))``: softplus without overflow for large arguments."""
+    zero = b.broadcast(b.scalar(0.0, F32), x.shape)
+    ax = b.binary("max", x, -x)
+    return b.binary("max", x, zero) + b.unary("log", 1.0 + b.unary("exp", -ax))
+
+
+def l2norm(b: Builder, x: Traced, eps: float = 1e-6) -> Traced:
+    return x / b.broadcast(b.unary("sqrt", (x * x).sum(-1, keepdim=True) + eps), x.shape)
+
+
+def causal_conv1d(b: Builder, x: Traced, state: Traced, w: Traced, bias: Optional[Traced] = None):
+    """Depthwise causal convolution of ``x[L, C]`` continuing from ``state[K-1, C]`` (the previous K-1 inputs) with
+    taps ``w[C, K]``: ``y[t] = sum_k w[:, k] * xp[t + k]`` over ``xp = state ++ x``.  Returns ``(y, next_state)``
+    (ops/ssm.rs causal conv1d)."""
+    L, C = x.shape
+    K = w.shape[1]
+    xp = b.concat([state, x], 0)
+    y = None
+    for k in range(K):
+        tap = b.broadcast(b.reshape(b.slice(w, 1, k, 1), (1, C)), (L, C))
+        term = b.slice(xp, 0, k, L) * tap
+        y = term if y is None else y + term
+    if bias is not None:
+        y = y + b.broadcast(bias, (L, C))
+    return y, b.slice(xp, 0, L, K - 1)
+
+
+def gated_rmsnorm(b: Builder, y: Traced, z: Traced, w: Traced, eps: float, gate_first: bool) -> Traced:
+    """RMSNorm over the last axis combined with a SiLU gate: ``norm(y * silu(z)) * w`` (Mamba2) or
+    ``norm(y) * w * silu(z)`` (gated delta net)."""
+    if gate_first:
+        return rmsnorm(b, y * silu(b, z), w, eps)
+    return rmsnorm(b, y, w, eps) * silu(b, z)
+
+
 def softcap(b: Builder, x: Traced, cap: float) -> Traced:
     return cap * b.unary("tanh", x * (1.0 / cap))
 
@@ -265,7 +301,8 @@ def ffn_activation(b: Builder, gate: Traced, up: Optional[Traced], act: str = "s
         g = -b.binary("max", -gate, -lim)
         u = b.binary("max", -b.binary("max", -up, -lim), -lim)
         return (u + 1.0) * (g / (1.0 + b.unary("exp", -(g * alpha))))
-    a = {"silu": silu, "gelu_tanh": gelu_tanh, "gelu_erf": gelu_erf, "relu": relu}[act](b, gate)
+    a = {"silu": silu, "gelu_tanh": gelu_tanh, "gelu_erf": gelu_erf, "relu": relu,
+         "relu2": lambda b_, x: relu(b_, x) * relu(b_, x)}[act](b, gate)
     return a * up if up is not None else a
 
 
@@ -283,17 +320,18 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
                score: str = "softmax", renorm: bool = True, router_bias: Optional[Traced] = None,
                select_bias: Optional[Traced] = None, n_group: int = 1, topk_group: int = 1, routed_scale: float = 1.0,
                act: str = "silu", limit: float = 0.0, alpha: float = 1.702, in_bias: Optional[Traced] = None,
-               out_bias: Optional[Traced] = None, precision: str = "narrow") -> Traced:
+               out_bias: Optional[Traced] = None, gated: bool = True, precision: str = "narrow") -> Traced:
     """Routed experts in every variant the shipped families use (components/router.rs, ops/moe.rs).
 
     ``score``: ``softmax`` over all experts or ``sigmoid`` per expert.  Selection ranks ``score + select_bias`` (the
     bias does not enter the gate), optionally restricted to the ``topk_group`` best of ``n_group`` expert groups
     (group score = sum of its two best selection scores; experts outside are ranked as 0).  Gates are the scores at
     the selected experts, divided by their sum when ``renorm``, times ``routed_scale``.  Experts: ``w_in[E, 2F, H]``
-    gate rows then up rows (+ ``in_bias[E, 2F]``), ``w_out[E, H, F]`` (+ ``out_bias[E, H]``)."""
+    gate rows then up rows (+ ``in_bias[E, 2F]``), ``w_out[E, H, F]`` (+ ``out_bias[E, H]``); with ``gated=False``
+    ``w_in[E, F, H]`` and the expert is ``down(act(up(x)))``."""
     L, H = x.shape
     E, F2, _ = w_in.shape
-    F = F2 // 2
+    F = F2 // 2 if gated else F2
     logits = linear(b, x, router, router_bias, precision="exact")
     if score == "softmax" and renorm and select_bias is None and n_group == 1:
         # softmax over all, pick k, renormalise == softmax over the k selected logits
@@ -332,7 +370,8 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
     gu = b.indexed_matmul(xr, b.transpose(w_in, (0, 2, 1)), flat_ids, precision)     # [L*k, 2F]
     if in_bias is not None:
         gu = gu + b.gather(in_bias, flat_ids, 0)
-    a = ffn_activation(b, b.slice(gu, -1, 0, F), b.slice(gu, -1, F, F), act, limit, alpha)
+    a = ffn_activation(b, b.slice(gu, -1, 0, F), b.slice(gu, -1, F, F), act, limit, alpha) if gated else \
+        ffn_activation(b, gu, None, act)
     y = b.indexed_matmul(a, b.transpose(w_out, (0, 2, 1)), flat_ids, precision)
     if out_bias is not None:
         y = y + b.gather(out_bias, flat_ids, 0)

@@ -128,8 +128,11 @@ class LLM:
         eng = OracleStepEngine(model, weights, num_blocks, rows, step_prefill + rows, blocks_for(max_seq))
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
         eos = getattr(tokenizer, "eos", None)
+        # a prefix hit skips tokens; a recurrent layer's state after those tokens is not in the K/V cache, so recurrent
+        # families run without the prefix cache (the reference snapshots recurrent state instead)
         drv = Driver(eng, num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
-                     eos_token=eos if eos is not None else cfg.eos_token, prefill_budget=step_prefill)
+                     prefix_caching=not cfg.is_recurrent, eos_token=eos if eos is not None else cfg.eos_token,
+                     prefill_budget=step_prefill)
         return LLM(cfg, drv, tokenizer, None, handle, None)
 
     # ---- generation ----------------------------------------------------------------------------------------------

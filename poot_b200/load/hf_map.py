@@ -61,6 +61,8 @@ LAYER = {
     "block_sparse_moe.e_score_correction_bias": "ffn_router_select_bias",
     "mlp.shared_experts.gate_proj.weight": "shared_gate", "mlp.shared_experts.up_proj.weight": "shared_up",
     "mlp.shared_experts.down_proj.weight": "shared_down",
+    "mlp.shared_expert.gate_proj.weight": "shared_gate", "mlp.shared_expert.up_proj.weight": "shared_up",
+    "mlp.shared_expert.down_proj.weight": "shared_down", "mlp.shared_expert_gate.weight": "shared_expert_gate",
     # multi-head latent attention
     "self_attn.q_a_proj.weight": "attn_q_a", "self_attn.q_a_layernorm.weight": "attn_q_a_norm",
     "self_attn.q_b_proj.weight": "attn_q_b", "self_attn.kv_a_proj_with_mqa.weight": "attn_kv_a",
@@ -116,6 +118,8 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
     """Canonical role name -> stored tensor for one Hugging Face checkpoint of ``cfg``'s family."""
     if cfg.family == "bert":
         return _map_bert(cfg, store)
+    if cfg.family == "nemotron_h":
+        return _map_nemotron_h(cfg, store)
     if cfg.family == "mpt":
         return _map_mpt(cfg, store)
     if cfg.family == "bloom":
@@ -138,6 +142,8 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
             continue
         l, rest = int(m.group(1)), m.group(2)
         p = f"layers.{l}."
+        if cfg.family == "qwen3next" and _qwen3next_tensor(cfg, p, rest, w, canon):
+            continue
         if rest in table:
             canon[p + table[rest]] = w
             continue
@@ -173,6 +179,91 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
                 canon[k] = f32_weight(k, canon[k].to_f32() + cfg.norm_offset)
     if cfg.rope_interleaved and cfg.is_mla:
         _mla_halfsplit(cfg, canon)
+    return canon
+
+
+def _qwen3next_tensor(cfg: DecoderConfig, p: str, rest: str, w: PackedWeight, canon: Dict[str, PackedWeight]) -> bool:
+    """Tensors of the gated attention and gated delta-net layers that are stored fused (crates/poot-models/src/
+    architectures/qwen3next.rs): ``q_proj`` carries ``[head][query | gate]`` rows; ``in_proj_qkvz`` is grouped per key
+    head as ``[q | k | v of the group's value heads | z of them]`` and ``in_proj_ba`` as ``[b | a]``."""
+    nk, nv, Dg, D = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.head_dim
+    if rest == "self_attn.q_proj.weight":
+        a = w.to_f32().reshape(cfg.n_heads, 2, D, -1)
+        canon[p + "attn_q"] = f32_weight(p + "attn_q", a[:, 0].reshape(cfg.n_heads * D, -1))
+        canon[p + "attn_gate"] = f32_weight(p + "attn_gate", a[:, 1].reshape(cfg.n_heads * D, -1))
+        return True
+    if rest == "linear_attn.in_proj_qkvz.weight":
+        r = nv // nk
+        a = w.to_f32().reshape(nk, 2 * Dg + 2 * r * Dg, -1)
+        cuts = {"gdn_q": (0, Dg), "gdn_k": (Dg, Dg), "gdn_v": (2 * Dg, r * Dg), "gdn_z": (2 * Dg + r * Dg, r * Dg)}
+        for role, (o, n) in cuts.items():
+            canon[p + role] = f32_weight(p + role, a[:, o:o + n].reshape(nk * n, -1))
+        return True
+    if rest == "linear_attn.in_proj_ba.weight":
+        r = nv // nk
+        a = w.to_f32().reshape(nk, 2 * r, -1)
+        canon[p + "gdn_b"] = f32_weight(p + "gdn_b", a[:, :r].reshape(nv, -1))
+        canon[p + "gdn_a"] = f32_weight(p + "gdn_a", a[:, r:].reshape(nv, -1))
+        return True
+    simple = {"linear_attn.dt_bias": "gdn_dt_bias", "linear_attn.A_log": "gdn_a_log", "linear_attn.norm.weight": "gdn_gate_norm_w",
+              "linear_attn.out_proj.weight": "gdn_o"}
+    if rest in simple:
+        canon[p + simple[rest]] = w
+        return True
+    if rest == "linear_attn.conv1d.weight":                # [C, 1, K]
+        a = w.to_f32()
+        canon[p + "gdn_conv"] = f32_weight(p + "gdn_conv", a.reshape(a.shape[0], a.shape[-1]))
+        return True
+    return False
+
+
+NEMOTRON_MIXER = {"mixer.dt_bias": "ssm_dt_bias", "mixer.A_log": "ssm_a_log", "mixer.D": "ssm_d", "mixer.conv1d.bias": "ssm_conv_bias",
+                  "mixer.norm.weight": "ssm_gate_norm_w", "mixer.out_proj.weight": "ssm_o",
+                  "mixer.q_proj.weight": "attn_q", "mixer.k_proj.weight": "attn_k", "mixer.v_proj.weight": "attn_v",
+                  "mixer.o_proj.weight": "attn_o", "mixer.up_proj.weight": "ffn_up", "mixer.down_proj.weight": "ffn_down",
+                  "mixer.gate.weight": "ffn_router", "mixer.gate.e_score_correction_bias": "ffn_router_select_bias",
+                  "mixer.shared_experts.up_proj.weight": "shared_up", "mixer.shared_experts.down_proj.weight": "shared_down"}
+
+
+def _map_nemotron_h(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWeight]:
+    canon: Dict[str, PackedWeight] = {}
+    I = cfg.ssm_heads * cfg.ssm_head_dim
+    C = I + 2 * cfg.ssm_groups * cfg.ssm_state
+    top = {"embeddings.weight": "embed", "embedding.weight": "embed", "norm_f.weight": "final_norm"}
+    for n in store.names():
+        w = store[n]
+        if n == "lm_head.weight":
+            canon["lm_head"] = w
+            continue
+        short = re.sub(r"^(model|backbone)\.", "", n)
+        if short in top:
+            canon[top[short]] = w
+            continue
+        m = re.match(r"layers\.(\d+)\.(.+)$", short)
+        if not m:
+            continue
+        l, rest = int(m.group(1)), m.group(2)
+        p = f"layers.{l}."
+        if rest == "norm.weight":          # one norm per block: it feeds the block's mixer, or its FFN when it has none
+            canon[p + ("attn_norm" if cfg.mixer_of(l) != "none" else "ffn_norm")] = w
+        elif rest in NEMOTRON_MIXER:
+            canon[p + NEMOTRON_MIXER[rest]] = w
+        elif rest == "mixer.in_proj.weight":               # z | (x | B | C) | dt rows
+            if w.shape[0] != I + C + cfg.ssm_heads:
+                raise CheckpointLayout(f"{n}: {w.shape[0]} rows, expected {I + C + cfg.ssm_heads}")
+            canon[p + "ssm_in_z"], canon[p + "ssm_in_x"], canon[p + "ssm_in_dt"] = w.rows(0, I), w.rows(I, C), w.rows(I + C, cfg.ssm_heads)
+        elif rest == "mixer.conv1d.weight":
+            a = w.to_f32()
+            canon[p + "ssm_conv"] = f32_weight(p + "ssm_conv", a.reshape(a.shape[0], a.shape[-1]))
+        elif re.match(r"mixer\.experts\.(\d+)\.(up|down)_proj\.weight$", rest):
+            e = re.match(r"mixer\.experts\.(\d+)\.(up|down)_proj\.weight$", rest)
+            canon[p + f"experts.{e.group(1)}.{e.group(2)}"] = w
+        elif rest == "mixer.experts.up_proj":
+            for x in range(cfg.n_experts):
+                canon[p + f"experts.{x}.up"] = first_axis(w, x)
+        elif rest == "mixer.experts.down_proj":
+            for x in range(cfg.n_experts):
+                canon[p + f"experts.{x}.down"] = first_axis(w, x)
     return canon
 
 

