@@ -133,7 +133,8 @@ class DeviceStepEngine:
         self.h_picked[:B].copy_(e.picked[:B], non_blocking=True)
         if inp.want_logprobs:
             self.h_logprobs[:B].copy_(e.logprobs[:B], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if e.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
         self.last_run_ms = (_time.perf_counter() - t0) * 1e3
         self.last_device_ms = ev[0].elapsed_time(ev[1]) if ev is not None else None
         self.last_launches = e.launches_per_step.get(e._key(shape), 0)

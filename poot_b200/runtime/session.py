@@ -109,7 +109,8 @@ class FixedBatchSession:
         e.bind(self.h_tokens[:T], self.h_pos[:T], self.h_slots[:T], self.h_seq[:T], self.h_ctx[:T], self.h_lidx[:B])
         e.run(shape)
         self.h_picked[:B].copy_(e.picked[:B], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if e.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
         return self.h_picked[:B]
 
     # ---- chained decode: N replays with no host round trip in between --------------------------------

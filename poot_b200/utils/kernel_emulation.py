@@ -1,0 +1,323 @@
+"""Host restatements of the device kernels' entry points, for checking the engine's program on a machine
+without a GPU.
+
+``with emulated_kernels():`` replaces the functions of ``ops.cuda_ops`` / ``ops.moe_ops`` / ``ops.suffix_ops`` by
+PyTorch code over CPU tensors with the same signatures, buffer layouts and rounding points (fp32 accumulation, bf16
+stores where the kernels store bf16).  A ``DecoderEngine(device="cpu", use_graphs=False)`` built inside the block
+then runs its unmodified kernel program - buffer binding, the order of launches, epilogue choices, K/V paging,
+chained decode, the sampler suffix - and can be compared with the fp32 restatement of the model.  This is a test
+harness only: nothing selects it automatically, the engine never falls back to it, and on a GPU box the ops keep
+failing loudly when the CUDA library is missing.  What it cannot check is the kernels themselves; those are
+compared with PyTorch references on the device.
+"""
+from __future__ import annotations
+
+import math
+from contextlib import contextmanager
+from typing import Optional
+
+import numpy as np
+import torch
+
+from ..ops import cuda_ops as K
+
+BF = torch.bfloat16
+
+
+def _bf(x: torch.Tensor) -> torch.Tensor:
+    return x.to(BF)
+
+
+def embed_gather(ids, table, out=None):
+    r = table[ids.long()]
+    if out is None:
+        return r.clone()
+    out.copy_(r)
+    return out
+
+
+def rmsnorm(x, w, eps, out=None, partials=None, h_out=None):
+    h = x.float()
+    if partials is not None:
+        p = partials if partials.dim() == 3 else partials.unsqueeze(0)
+        h = _bf(h + p.float().sum(0)).float()
+        if h_out is not None:
+            h_out.copy_(_bf(h))
+    y = h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps) * w.float()
+    if out is None:
+        return _bf(y)
+    out.copy_(_bf(y))
+    return out
+
+
+def reduce_partials(h, partials, out):
+    s = partials.float().sum(0)
+    if h is not None:
+        s = s + h.float()
+    out.copy_(_bf(s))
+    return out
+
+
+def swiglu(gu, interleaved, out=None):
+    g = gu.float()
+    F = g.shape[1] // 2
+    a = torch.nn.functional.silu(g[:, 0::2]) * g[:, 1::2] if interleaved else torch.nn.functional.silu(g[:, :F]) * g[:, F:]
+    if out is None:
+        return _bf(a)
+    out.copy_(_bf(a))
+    return out
+
+
+def add(a, b, out=None):
+    r = _bf(a.float() + b.float())
+    if out is None:
+        return r
+    out.copy_(r)
+    return out
+
+
+def _epilogue(y: torch.Tensor, epi: int, out, resid):
+    """``y`` fp32 ``[M, N]`` -> the epilogue's stored form."""
+    if epi == K.EPI_F32:
+        r = y
+    elif epi == K.EPI_SWIGLU:
+        r = _bf(torch.nn.functional.silu(y[:, 0::2]) * y[:, 1::2])
+    elif epi == K.EPI_RESID:
+        r = _bf(y + resid.float())
+    else:
+        r = _bf(y)
+    if out is None:
+        return r.clone()
+    out.copy_(r)
+    return out
+
+
+def linear(x, W, epi=K.EPI_STORE, out=None, resid=None):
+    if isinstance(W, K.QuantWeight):
+        raise NotImplementedError("packed weights are not emulated")
+    return _epilogue(x.float() @ W.float().T, epi, out, resid)
+
+
+def gemm(x, W, epi=K.EPI_STORE, out=None, resid=None, bn=None, splits=1):
+    if epi == K.EPI_PARTIAL:        # split-K partial slices: the sum over slices is the product
+        y = x.float() @ W.float().T
+        if out is None:
+            out = torch.zeros(splits, *y.shape, dtype=torch.float32)
+        out.zero_()
+        Kd = x.shape[1]
+        step = -(-Kd // splits)
+        for s in range(splits):
+            out[s].copy_(x[:, s * step:(s + 1) * step].float() @ W[:, s * step:(s + 1) * step].float().T)
+        return out
+    return linear(x, W, epi, out, resid)
+
+
+def gemm_skinny(x, W, epi=K.EPI_STORE, out=None, resid=None, ck=None, wm=1):
+    assert x.shape[0] <= 128
+    return linear(x, W, epi, out, resid)
+
+
+def gemv(x, W, epi=K.EPI_STORE, out=None, resid=None):
+    return linear(x, W, epi, out, resid)
+
+
+def rope_kv_write(qkv, q_out, kpool, vpool, positions, slots, cos, sin, Hq, Hkv, D, rot=None, q_norm_w=None,
+                  k_norm_w=None, norm_eps=1e-6):
+    T = qkv.shape[0]
+    rot = D if rot is None else rot
+    half = rot // 2
+    x = qkv.float()
+    q = x[:, :Hq * D].reshape(T, Hq, D)
+    k = x[:, Hq * D:(Hq + Hkv) * D].reshape(T, Hkv, D)
+    v = x[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+
+    def norm(t, w):
+        return t if w is None else t / torch.sqrt((t * t).mean(-1, keepdim=True) + norm_eps) * w.float()
+
+    def rope(t):
+        c = cos[positions.long()].unsqueeze(1)      # [T, 1, half]
+        s = sin[positions.long()].unsqueeze(1)
+        a, b = t[..., :half], t[..., half:rot]
+        return torch.cat([a * c - b * s, b * c + a * s, t[..., rot:]], -1)
+
+    q, k = rope(norm(q, q_norm_w)), rope(norm(k, k_norm_w))
+    q_out.copy_(_bf(q.reshape(T, Hq * D)))
+    live = slots >= 0
+    if live.any():
+        sl = slots[live].long()
+        kpool[sl // K.KV_BLOCK, :, sl % K.KV_BLOCK] = _bf(k[live])
+        vpool[sl // K.KV_BLOCK, :, sl % K.KV_BLOCK] = _bf(v[live])
+
+
+def _attend(qrow: torch.Tensor, kpool, vpool, blocks: torch.Tensor, first_key: int, n_keys: int, Hq: int, Hkv: int,
+            D: int, scale: float, softcap: float) -> torch.Tensor:
+    """One query row ``[Hq, D]`` over keys ``first_key .. n_keys-1`` of the sequence whose block list is ``blocks``."""
+    pos = torch.arange(first_key, n_keys)
+    blk = blocks[(pos // K.KV_BLOCK).long()].long()
+    kk = kpool[blk, :, (pos % K.KV_BLOCK).long()].float()      # [S, Hkv, D]
+    vv = vpool[blk, :, (pos % K.KV_BLOCK).long()].float()
+    rep = Hq // Hkv
+    kk, vv = kk.repeat_interleave(rep, 1), vv.repeat_interleave(rep, 1)
+    s = torch.einsum("hd,shd->hs", qrow.float(), kk) * scale
+    if softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
+    return torch.einsum("hs,shd->hd", torch.softmax(s, -1), vv)
+
+
+def attn_paged(q, kpool, vpool, block_tables, row_seq, row_ctx, Hq, Hkv, D, scale, out=None, splits=1, scratch=None,
+               softcap=0.0, window=0):
+    R = q.shape[0]
+    if out is None:
+        out = torch.zeros(R, Hq * D, dtype=BF)
+    for r in range(R):
+        ctx = int(row_ctx[r])
+        if ctx <= 0:
+            continue
+        seq = int(row_seq[r]) if row_seq is not None else r
+        first = ctx - window if (window > 0 and ctx > window) else 0
+        o = _attend(q[r].reshape(Hq, D), kpool, vpool, block_tables[seq], first, ctx, Hq, Hkv, D, scale, softcap)
+        out[r].copy_(_bf(o.reshape(-1)))
+    return out
+
+
+def attn_flash_prefill(q, kpool, vpool, block_tables, tiles, Hq, Hkv, scale, out, window=0):
+    D = kpool.shape[-1]
+    for first_row, rows, seq, first_pos in tiles.tolist():
+        for i in range(rows):
+            ctx = first_pos + i + 1
+            first = ctx - window if (window > 0 and ctx > window) else 0
+            o = _attend(q[first_row + i].reshape(Hq, D), kpool, vpool, block_tables[seq], first, ctx, Hq, Hkv, D, scale, 0.0)
+            out[first_row + i].copy_(_bf(o.reshape(-1)))
+
+
+def argmax_scratch(rows, vocab, device):
+    return torch.zeros(rows, K.argmax_groups(vocab), 3, dtype=torch.int32)
+
+
+def argmax(logits, out=None, scratch=None):
+    from ..oracle.sampling import GREEDY, sample_rows
+    r = torch.from_numpy(sample_rows(logits.float().numpy(), None, None, None, GREEDY))
+    if out is None:
+        return r
+    out.copy_(r)
+    return out
+
+
+def sample_gumbel(logits, params, top_k, seeds, rule, out=None):
+    from ..oracle.sampling import sample_rows
+    r = torch.from_numpy(sample_rows(logits.float().numpy(), params.numpy(), top_k.numpy(), seeds.numpy(), rule))
+    if out is None:
+        return r
+    out.copy_(r)
+    return out
+
+
+def decode_advance(picked, tokens, positions, slots, ctx, block_tables, row_seq, B):
+    maxb = block_tables.shape[1]
+    for i in range(B):
+        if int(slots[i]) < 0:
+            continue
+        tokens[i] = picked[i, 0]
+        pos = int(positions[i]) + 1
+        positions[i] = pos
+        ctx[i] = pos + 1
+        seq = int(row_seq[i]) if row_seq is not None else i
+        b = pos // K.KV_BLOCK
+        slots[i] = int(block_tables[seq, b]) * K.KV_BLOCK + pos % K.KV_BLOCK if b < maxb else -1
+
+
+def adjust_logits(logits, idx, val, guided=None):
+    fmin = torch.finfo(torch.float32).min
+    for r in range(logits.shape[0]):
+        for t, v in zip(idx[r].tolist(), val[r].tolist()):
+            if 0 <= t < logits.shape[1]:
+                l = float(logits[r, t]) + v[0]
+                logits[r, t] = (l * v[1] if l > 0 else l * v[2]) + v[3]
+        if guided is not None:
+            m = guided[r]
+            logits[r] = torch.where(m <= fmin, torch.full_like(m, fmin), torch.where(m != 0, logits[r] + m, logits[r]))
+
+
+def token_logprob(logits, picked, out=None):
+    lp = torch.log_softmax(logits.float(), -1)[torch.arange(logits.shape[0]), picked[:, 0].long()]
+    if out is None:
+        return lp
+    out.copy_(lp)
+    return out
+
+
+def moe_route(logits, k, renorm, ids, gates, dense):
+    T, E = logits.shape
+    s = torch.nan_to_num(logits.float(), nan=torch.finfo(torch.float32).min, posinf=torch.finfo(torch.float32).max,
+                         neginf=torch.finfo(torch.float32).min)
+    order = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :k]       # ties: lower index first
+    top = s.gather(-1, order)
+    g = torch.softmax(top, -1) if renorm else torch.softmax(s, -1).gather(-1, order)
+    ids.view(T, k).copy_(order.to(torch.int32))
+    gates.view(T, k).copy_(g)
+    d = dense.view(E, T)
+    d.zero_()
+    d.T.scatter_(1, order, g)
+
+
+def moe_combine(h, parts, out, T, H, groups, gstride, per_token=0):
+    p = parts.reshape(-1).float()
+    acc = torch.zeros(T, H) if h is None else h.float().clone()
+    if per_token:      # group g belongs to token g / per_token
+        for g in range(groups):
+            acc[g // per_token] += p[g * gstride:g * gstride + H]
+    else:
+        for g in range(groups):
+            acc += p[g * gstride:g * gstride + T * H].view(T, H)
+    out.copy_(_bf(acc))
+
+
+def gemm_grouped(epi, x, W, out, M, groups, group_expert=None, x_row_div=0, x_row_mul=0, x_col_per_expert=0,
+                 out_group_stride=0, row_scale=None, ldo=None, K_dim=None, tp=None):
+    if tp is not None:
+        raise NotImplementedError("peer pushes are not emulated")
+    E, N, Kw = W.shape
+    Kd = K_dim or Kw
+    n_out = N // 2 if epi == K.EPI_SWIGLU else N
+    flat = out.reshape(-1)
+    for g in range(groups):
+        e = int(group_expert[g]) if group_expert is not None else g
+        row0 = (g // x_row_div if x_row_div > 0 else 0) + g * x_row_mul
+        col0 = e * x_col_per_expert
+        if e < 0:
+            y = torch.zeros(M, N)
+        else:
+            y = x[row0:row0 + M, col0:col0 + Kd].float() @ W[e].float().T
+        if row_scale is not None:
+            y = y * row_scale.reshape(-1)[g * M:(g + 1) * M].float().unsqueeze(1)
+        r = _bf(torch.nn.functional.silu(y[:, 0::2]) * y[:, 1::2]) if epi == K.EPI_SWIGLU else _bf(y)
+        for m in range(M):
+            o = g * out_group_stride + m * ldo
+            flat[o:o + n_out] = r[m]
+
+
+_status = torch.zeros(1, dtype=torch.int32)
+
+
+@contextmanager
+def emulated_kernels():
+    """Run the engine's kernel program against the host restatements above (tests only)."""
+    from ..ops import moe_ops, suffix_ops
+    table = {
+        K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
+                linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
+                attn_paged=attn_paged, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
+                argmax=argmax, sample_gumbel=sample_gumbel, decode_advance=decode_advance,
+                status_word=lambda device=None: _status, check_status=lambda device=None: None),
+        moe_ops: dict(moe_route=moe_route, moe_combine=moe_combine, gemm_grouped=gemm_grouped),
+        suffix_ops: dict(adjust_logits=adjust_logits, token_logprob=token_logprob),
+    }
+    saved = {(mod, name): getattr(mod, name) for mod, fns in table.items() for name in fns}
+    try:
+        for mod, fns in table.items():
+            for name, fn in fns.items():
+                setattr(mod, name, fn)
+        yield
+    finally:
+        for (mod, name), fn in saved.items():
+            setattr(mod, name, fn)
