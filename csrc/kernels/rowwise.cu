@@ -122,6 +122,42 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
   }
 }
 
+// act(gate) * up for gated FFNs whose activation is not SiLU (GeGLU): act 0 = SiLU, 1 = GELU (tanh form), 2 = GELU (erf).
+__global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                 int T, int F, int interleaved, int act) {
+  pdl_wait(); pdl_launch();
+  size_t n = (size_t)T * F;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    size_t t = i / F;
+    int j = (int)(i - t * F);
+    float g, u;
+    if (interleaved) {
+      __nv_bfloat162 p = reinterpret_cast<const __nv_bfloat162*>(gu + t * 2 * F)[j];
+      g = __low2float(p); u = __high2float(p);
+    } else {
+      g = __bfloat162float(gu[t * 2 * F + j]);
+      u = __bfloat162float(gu[t * 2 * F + F + j]);
+    }
+    float a;
+    if (act == 1) {
+      const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+      a = g / (1.f + __expf(-2.f * z));
+    } else if (act == 2) {
+      a = 0.5f * g * (1.f + erff(g * 0.7071067811865475f));
+    } else {
+      a = silu(g);
+    }
+    out[i] = __float2bfloat16(a * u);
+  }
+}
+
+// x = cap * tanh(x / cap) in place over fp32 logits
+__global__ void softcap_f32_kernel(float* __restrict__ x, size_t n, float cap, float inv_cap) {
+  pdl_wait(); pdl_launch();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
 __global__ void add_kernel(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, size_t n) {
   pdl_wait(); pdl_launch();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
@@ -220,6 +256,24 @@ POOT_API int poot_swiglu(const void* gu, void* out, int T, int F, int interleave
   if (blocks > 148 * 16) blocks = 148 * 16;
   return launch_k(swiglu_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F, interleaved);
   return (int)cudaGetLastError();
+}
+
+POOT_API int poot_gated_act(const void* gu, void* out, int T, int F, int interleaved, int act, cudaStream_t s) {
+  size_t n = (size_t)T * F;
+  if (n == 0) return 0;
+  if (act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch_k(gated_act_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F,
+                  interleaved, act);
+}
+
+POOT_API int poot_softcap_f32(void* x, long long n, float cap, cudaStream_t s) {
+  if (n == 0) return 0;
+  if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch_k(softcap_f32_kernel, dim3(blocks), dim3(256), 0, s, (float*)x, (size_t)n, cap, 1.f / cap);
 }
 
 POOT_API int poot_add_bf16(const void* a, const void* b, void* out, long long n, cudaStream_t s) {

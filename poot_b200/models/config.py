@@ -160,18 +160,22 @@ class DecoderConfig:
     def moe_layer(self, layer: int) -> bool:
         return self.is_moe and layer >= self.first_dense_layers and not (self.dense_layers and layer in self.dense_layers)
 
+    @property
+    def plain_block(self) -> bool:
+        """The pre-norm SwiGLU rope layer the fused tensor-parallel programs are written for."""
+        return (self.block == "pre" and self.act == "silu" and not self.qk_norm_wide and self.rope_theta_local is None
+                and (self.rope_layers is None or all(self.rope_layers)) and self.final_softcap == 0)
+
     def device_gaps(self) -> list:
         """Features of this configuration that the device program does not implement (empty = runs on the device);
         the CPU oracle evaluates all of them."""
         g = []
         if self.norm_kind != "rms": g.append("LayerNorm")
-        if self.block != "pre": g.append(f"{self.block}-norm block")
-        if self.qk_norm_wide: g.append("projection-wide q/k norm")
-        if self.act != "silu" or not self.gated_ffn: g.append(f"{self.act} {'gated' if self.gated_ffn else 'plain'} FFN")
+        if self.block != "pre" and self.is_moe: g.append(f"{self.block}-norm block with routed experts")
+        if not self.gated_ffn or self.act not in ("silu", "gelu_tanh", "gelu_erf"): g.append(f"{self.act} {'gated' if self.gated_ffn else 'plain'} FFN")
+        if self.act != "silu" and self.is_moe: g.append(f"{self.act} experts")
         if self.out_bias or self.mlp_bias or self.expert_bias: g.append("output / FFN biases")
         if self.pos != "rope": g.append(f"{self.pos} positions")
-        if self.rope_theta_local is not None: g.append("two rope bases")
-        if self.rope_layers is not None and not all(self.rope_layers): g.append("layers without rope")
         if self.embed_norm: g.append("embedding norm")
         if self.attn_sinks: g.append("attention sinks")
         if self.swiglu_limit > 0: g.append("clamped SwiGLU")
@@ -184,7 +188,6 @@ class DecoderConfig:
         if self.is_recurrent: g.append("recurrent mixers (Mamba2 / gated delta net scans)")
         if self.layer_kinds is not None and not self.is_recurrent or self.layer_ffn is not None: g.append("single-mixer blocks")
         if self.attn_gate or self.shared_expert_gate: g.append("gated attention output / gated shared expert")
-        if self.final_softcap > 0: g.append("soft-capped logits")
         if self.head_dim not in (64, 128): g.append(f"head_dim {self.head_dim}")
         return g
 

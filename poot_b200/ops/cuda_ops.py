@@ -22,6 +22,8 @@ _SIGS = {
     "poot_embed_gather": [_P, _P, _P, c_int, c_int, c_int, _P],
     "poot_rmsnorm": [_P, _P, _P, c_int, c_longlong, _P, _P, c_int, c_int, c_float, _P],
     "poot_swiglu": [_P, _P, c_int, c_int, c_int, _P],
+    "poot_gated_act": [_P, _P, c_int, c_int, c_int, c_int, _P],
+    "poot_softcap_f32": [_P, c_longlong, c_float, _P],
     "poot_add_bf16": [_P, _P, _P, c_longlong, _P],
     "poot_reduce_partials": [_P, _P, c_int, c_longlong, _P, c_longlong, _P],
     "poot_cast_f32_bf16": [_P, _P, c_longlong, _P],
@@ -208,6 +210,28 @@ def swiglu(gu: torch.Tensor, interleaved: bool, out: Optional[torch.Tensor] = No
         out = torch.empty(T, F2 // 2, dtype=torch.bfloat16, device=gu.device)
     check(_fn("poot_swiglu")(_ptr(gu), _ptr(out), T, F2 // 2, int(interleaved), _stream()), "swiglu")
     return out
+
+
+GATED_ACTS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2}
+
+
+def gated_act(gu: torch.Tensor, interleaved: bool, act: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``act(gate) * up`` over a ``[T, 2F]`` projection output (GeGLU and the other gated FFNs that are not SwiGLU)."""
+    _need_cuda(gu)
+    assert gu.dtype == torch.bfloat16 and gu.is_contiguous()
+    T, F2 = gu.shape
+    if out is None:
+        out = torch.empty(T, F2 // 2, dtype=torch.bfloat16, device=gu.device)
+    check(_fn("poot_gated_act")(_ptr(gu), _ptr(out), T, F2 // 2, int(interleaved), GATED_ACTS[act], _stream()), "gated_act")
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``x = cap * tanh(x / cap)`` in place (fp32 logits)."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    check(_fn("poot_softcap_f32")(_ptr(x), x.numel(), float(cap), _stream()), "softcap")
+    return x
 
 
 def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

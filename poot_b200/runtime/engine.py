@@ -138,6 +138,25 @@ class DecoderEngine:
                              torch.zeros(ts * self.hq * self.attn_splits_max * 2, dtype=torch.float32, device=dev))
         cos, sin = rope_tables(cfg, cfg.max_position)
         self.cos, self.sin = cos.to(dev), sin.to(dev)
+        self.cos_local = self.sin_local = self.cos_none = self.sin_none = None
+        if cfg.rope_theta_local is not None:     # windowed layers rotate with their own base and no scaling
+            import dataclasses
+            from ..models.config import RopeScaling
+            c2, s2 = rope_tables(dataclasses.replace(cfg, rope_theta=cfg.rope_theta_local, rope_scaling=RopeScaling()),
+                                 cfg.max_position)
+            self.cos_local, self.sin_local = c2.to(dev), s2.to(dev)
+        if cfg.rope_layers is not None and not all(cfg.rope_layers):   # layers without a position signal: the identity rotation
+            self.cos_none, self.sin_none = torch.ones_like(self.cos), torch.zeros_like(self.sin)
+        if not cfg.plain_block:
+            if comm is not None:
+                from .weights import UnsupportedOnDevice
+                raise UnsupportedOnDevice(f"{cfg.family}: tensor parallelism is built for the pre-norm SwiGLU rope layer only")
+            self.proj = torch.zeros(T, H, dtype=bf, device=dev)          # projection output waiting for its post norm
+            if cfg.act != "silu":
+                self.gu = torch.zeros(T, 2 * ffn_local, dtype=bf, device=dev)
+            if cfg.qk_norm_wide:
+                self.qn = torch.zeros(T, self.hq * D, dtype=bf, device=dev)
+                self.kn = torch.zeros(T, self.hkv * D, dtype=bf, device=dev)
         self.scale = float(cfg.attn_scale) if cfg.attn_scale is not None else 1.0 / math.sqrt(D)
         if comm is not None:
             comm.attach(self)
@@ -239,25 +258,40 @@ class DecoderEngine:
         if cfg.embed_scale != 1.0:
             h.mul_(cfg.embed_scale)
         pending = None
+        post = cfg.block != "pre"           # a norm sits between each projection and its residual add
         for l, L in enumerate(w.layers):
-            x = self._norm(L.ln1, T, pending)
+            x = h if cfg.block == "post" else self._norm(L.ln1, T, pending)
             qkv = self._linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
             if L.bqkv is not None:
                 qkv.add_(L.bqkv)
+            qn, kn = L.q_norm, L.k_norm
+            if cfg.qk_norm_wide:            # one norm over the whole q / k projection: done here, not per head in the rope kernel
+                self._wide_qk_norm(qkv, L, T)
+                qn = kn = None
+            cos, sin = self._rope_tables_of(l)
             self._count()
             K.rope_kv_write(qkv, self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
-                            self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
+                            cos, sin, self.hq, self.hkv, D, cfg.rot, qn, kn, cfg.norm_eps)
             self._attention(l, T, T, B)
-            if self.comm is not None:
+            if post:
+                self._proj_post_norm(self.attn[:T], L.wo, L.post1, T)
+            elif self.comm is not None:
                 pending = self.comm.row_parallel(self, self.attn[:T], L.wo, T)
             else:
                 pending = self._proj_to_residual(self.attn[:T], L.wo, T)
-            x = self._norm(L.ln2, T, pending)
+            x = h if cfg.block == "post" else self._norm(L.ln2, T, pending)
             if cfg.is_moe:
                 pending = self._moe(l, L, x, T)
             else:
-                act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
-                if self.comm is not None:
+                if cfg.act == "silu":
+                    act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
+                else:                       # GeGLU: plain projection, then the gated activation over adjacent (gate, up) pairs
+                    gu = self._linear(x, L.wgu, K.EPI_STORE, self.gu[:T])
+                    self._count()
+                    act = K.gated_act(gu, True, cfg.act, out=self.act[:T])
+                if post:
+                    self._proj_post_norm(act, L.wdown, L.post2, T)
+                elif self.comm is not None:
                     pending = self.comm.row_parallel(self, act, L.wdown, T)
                 else:
                     pending = self._proj_to_residual(act, L.wdown, T)
@@ -273,7 +307,38 @@ class DecoderEngine:
         self._count()
         K.rmsnorm(hl, w.final_norm, cfg.norm_eps, out=self.xl[:B])
         self._linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits_local[:B])
+        if cfg.final_softcap > 0:
+            self._count()
+            K.softcap_(self.logits_local[:B], cfg.final_softcap)
         self._sample(shape, self.logits_local[:B])
+
+    def _rope_tables_of(self, l: int):
+        cfg = self.cfg
+        if self.cos_none is not None and not cfg.rope_layers[l]:
+            return self.cos_none, self.sin_none
+        if self.cos_local is not None and cfg.window_of(l) > 0:
+            return self.cos_local, self.sin_local
+        return self.cos, self.sin
+
+    def _proj_post_norm(self, x, W, norm_w, T: int) -> None:
+        """``h += rmsnorm(x @ W^T) * norm_w`` (post-norm and sandwich blocks): projection, norm, residual add."""
+        h, p = self.h[:T], self.proj[:T]
+        self._linear(x, W, K.EPI_STORE, p)
+        self._count(2)
+        K.rmsnorm(p, norm_w, self.cfg.norm_eps, out=p)
+        K.add(h, p, out=h)
+
+    def _wide_qk_norm(self, qkv, L, T: int) -> None:
+        """RMSNorm over the whole q projection and over the whole k projection of the fused qkv rows."""
+        nq, nk = self.hq * self.cfg.head_dim, self.hkv * self.cfg.head_dim
+        qn, kn = self.qn[:T], self.kn[:T]
+        qn.copy_(qkv[:, :nq])
+        kn.copy_(qkv[:, nq:nq + nk])
+        self._count(6)
+        K.rmsnorm(qn, L.q_norm, self.cfg.norm_eps, out=qn)
+        K.rmsnorm(kn, L.k_norm, self.cfg.norm_eps, out=kn)
+        qkv[:, :nq].copy_(qn)
+        qkv[:, nq:nq + nk].copy_(kn)
 
     def _sample(self, shape: StepShape, local_logits: torch.Tensor) -> None:
         """Sampler suffix over (possibly vocabulary-sharded) logits; every rank ends with the same ``picked``."""

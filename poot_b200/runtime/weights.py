@@ -31,6 +31,8 @@ class LayerWeights:
     q_norm: Optional[torch.Tensor] = None
     k_norm: Optional[torch.Tensor] = None
     bqkv: Optional[torch.Tensor] = None     # fused q|k|v bias of families that have one (qwen2), rank-local
+    post1: Optional[torch.Tensor] = None    # norm applied to the attention output before the residual add (post / sandwich blocks)
+    post2: Optional[torch.Tensor] = None    # the same for the FFN output
     router: Optional[torch.Tensor] = None   # [E, hidden]
     ex_wgu: Optional[torch.Tensor] = None   # [E_local, 2F, hidden]
     ex_wdown: Optional[torch.Tensor] = None  # [E_local, hidden, F]
@@ -82,6 +84,8 @@ def fold_scales(w: "DecoderWeights") -> "DecoderWeights":
     cfg = w.cfg
     if getattr(w, "_scales_folded", False):
         return w
+    if cfg.residual_scale != 1.0 and cfg.block != "pre":
+        raise UnsupportedOnDevice("residual_scale with a norm between the projection and the residual add")
     if cfg.residual_scale != 1.0:
         for L in w.layers:
             for role in ("wo", "wdown", "ex_wdown"):
@@ -209,7 +213,10 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
         p = f"layers.{l}."
         wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)
         wo = shard_cols(get(p + "attn_o"), tp_rank, tp_world)
-        L = LayerWeights(ln1=get(p + "attn_norm"), ln2=get(p + "ffn_norm"), wqkv=wqkv, wo=wo)
+        pre = cfg.block in ("pre", "sandwich")
+        L = LayerWeights(ln1=get(p + "attn_norm") if pre else None, ln2=get(p + "ffn_norm") if pre else None, wqkv=wqkv, wo=wo)
+        if cfg.block in ("post", "sandwich"):
+            L.post1, L.post2 = get(p + "attn_post_norm"), get(p + "ffn_post_norm")
         if cfg.attn_bias:
             L.bqkv = fuse_qkv_bias(get(p + "attn_q_bias"), get(p + "attn_k_bias"), get(p + "attn_v_bias"), cfg, tp_rank, tp_world)
         if cfg.qk_norm:

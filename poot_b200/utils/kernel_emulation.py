@@ -68,6 +68,24 @@ def swiglu(gu, interleaved, out=None):
     return out
 
 
+def gated_act(gu, interleaved, act, out=None):
+    g = gu.float()
+    F = g.shape[1] // 2
+    gate, up = (g[:, 0::2], g[:, 1::2]) if interleaved else (g[:, :F], g[:, F:])
+    fn = {"silu": torch.nn.functional.silu, "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
+          "gelu_erf": torch.nn.functional.gelu}[act]
+    r = _bf(fn(gate) * up)
+    if out is None:
+        return r
+    out.copy_(r)
+    return out
+
+
+def softcap_(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
+    return x
+
+
 def add(a, b, out=None):
     r = _bf(a.float() + b.float())
     if out is None:
@@ -305,6 +323,7 @@ def emulated_kernels():
     from ..ops import moe_ops, suffix_ops
     table = {
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
+                gated_act=gated_act, softcap_=softcap_,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
                 attn_paged=attn_paged, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
                 argmax=argmax, sample_gumbel=sample_gumbel, decode_advance=decode_advance,

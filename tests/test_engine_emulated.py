@@ -86,13 +86,13 @@ def test_chained_decode_equals_stepwise_decode():
 def test_device_gaps_are_refused_by_the_engine():
     from poot_b200.runtime.engine import DecoderEngine
     from poot_b200.runtime.weights import UnsupportedOnDevice, random_weights
-    cfg = _cfg(final_softcap=30.0)
+    cfg = _cfg(attn_sinks=True)
     with emulated_kernels():
         w = random_weights(_cfg(), "cpu", seed=0)
         w.cfg = cfg
         with pytest.raises(UnsupportedOnDevice) as e:
             DecoderEngine(w, 8, 1, 16, 4, device="cpu", use_graphs=False)
-    assert "soft-capped" in str(e.value)
+    assert "sinks" in str(e.value)
 
 
 def test_serving_driver_over_the_emulated_engine_matches_greedy_reference():
@@ -149,3 +149,60 @@ def test_long_prefill_takes_the_tiled_split_k_route(kw):
             ref = forward_logits(w, prompts[b])[-1]
             err = (eng.logits[b] - ref).abs().max().item()
             assert err < 0.03 * max(1.0, ref.abs().max().item()), err
+
+
+HF_BASE = {"hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 64,
+           "intermediate_size": 384, "vocab_size": 512, "rms_norm_eps": 1e-5, "max_position_embeddings": 128}
+HF_FAMILIES = {
+    "gemma2": {"model_type": "gemma2", "query_pre_attn_scalar": 48, "sliding_window": 8, "attn_logit_softcapping": 1.0,
+               "final_logit_softcapping": 10.0},
+    "gemma3": {"model_type": "gemma3_text", "query_pre_attn_scalar": 48, "sliding_window": 8, "num_hidden_layers": 3,
+               "layer_types": ["sliding_attention", "sliding_attention", "full_attention"], "rope_local_base_freq": 10000.0,
+               "rope_theta": 1000000.0},
+    "olmo2": {"model_type": "olmo2"},
+    "olmoe": {"model_type": "olmoe", "num_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
+    "smollm3-nope-layer": {"model_type": "smollm3", "no_rope_layers": [1, 0]},
+    "granite": {"model_type": "granite", "embedding_multiplier": 6.0, "residual_multiplier": 0.5, "logits_scaling": 4.0,
+                "attention_multiplier": 0.1},
+}
+
+
+@pytest.mark.parametrize("name", sorted(HF_FAMILIES))
+def test_family_blocks_on_the_engine_match_the_graph_oracle(name):
+    """Families beyond the plain pre-norm SwiGLU layer (sandwich and post norms, GeGLU, soft caps, two rope bases,
+    projection-wide q/k norms, layers without rope): the engine's program against the graph oracle, which is itself
+    checked against the Hugging Face implementations."""
+    from poot_b200.models.model import StepSpec
+    from poot_b200.models.registry import Registry
+    from poot_b200.oracle.runner import OracleSession, random_weights_f32
+    from poot_b200.runtime.engine import DecoderEngine
+    from poot_b200.runtime.session import FixedBatchSession
+    from poot_b200.runtime.weights import from_named_tensors
+    model = Registry.builtin().resolve_hf({**HF_BASE, **HF_FAMILIES[name]})
+    cfg = model.cfg
+    assert cfg.device_gaps() == [], cfg.device_gaps()
+    w = random_weights_f32(model, seed=2, std=0.08)
+    for k in w:
+        if k.endswith("norm"):
+            w[k] = (1.0 + 0.1 * np.random.default_rng(len(k)).standard_normal(w[k].shape)).astype(np.float32)
+    w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}     # what the device will hold
+    named = {k: torch.from_numpy(v) for k, v in w.items()}
+    for l in range(cfg.n_layers if cfg.is_moe else 0):
+        p = f"layers.{l}."
+        for e in range(cfg.n_experts):
+            named[p + f"experts.{e}.gate"] = named[p + "experts_in"][e, :cfg.moe_ffn]
+            named[p + f"experts.{e}.up"] = named[p + "experts_in"][e, cfg.moe_ffn:]
+            named[p + f"experts.{e}.down"] = named[p + "experts_out"][e]
+    toks = np.random.default_rng(7).integers(0, cfg.vocab, (1, 23))
+    sess = OracleSession(model, w, capacity=32)
+    ref = torch.from_numpy(sess.step(toks))[0]
+    with emulated_kernels():
+        dw = from_named_tensors(cfg, named, "cpu")
+        eng = DecoderEngine(dw, num_blocks=4, max_seqs=1, max_tokens=32, max_blocks_per_seq=2, device="cpu", use_graphs=False)
+        s = FixedBatchSession(eng, 1, 32)
+        s.prefill_fast(torch.from_numpy(toks[:, :20]).int())
+        for t in range(20, 23):
+            s.decode([int(toks[0, t])])
+        got = eng.logits[0]
+    err = (got - ref).abs().max().item()
+    assert err < 0.02 * max(1.0, ref.abs().max().item()), (name, err, ref.abs().max().item())
