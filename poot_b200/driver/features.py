@@ -54,10 +54,13 @@ TABLE: List[Tuple[Feature, Feature, str]] = [
     (F.DRAFT_MODEL, F.GUIDED, "a constraint mask is computed one token ahead, not for k drafted positions"),
     (F.BEAM, F.GUIDED, "beams would each need a clone of the constraint state"),
     (F.PACKED_WEIGHTS, F.EXPERT_PLACEMENT, "packed expert weights have no fused grouped kernel"),
+    (F.PIPELINE_PLACEMENT, F.TENSOR_PLACEMENT, "one placement per model: stages are not themselves tensor-parallel groups"),
+    (F.PIPELINE_PLACEMENT, F.EXPERT_PLACEMENT, "one placement per model: stages are not themselves expert-parallel groups"),
+    (F.PIPELINE_PLACEMENT, F.DEVICE_TIMING, "per-launch device spans are recorded on one device"),
+    (F.PIPELINE_PLACEMENT, F.BEAM, "a fork copies K/V blocks on every stage; only the leader's copy is wired"),
     (F.ADAPTERS, F.PACKED_WEIGHTS, "adapter deltas are applied to bf16 projections"),
 ]
 UNAVAILABLE = {
-    F.PIPELINE_PLACEMENT: "stages over NVLink would idle all but one GPU at decode; use tensor:<ordinals>",
     F.DRAFT_MTP: "no registered family ships multi-token-prediction heads",
     F.RECURRENT_STATE: "no recurrent (SSM / linear-attention) family is registered",
     F.EXPERT_POOL: "all experts stay resident in 180 GB of HBM; there is no host-side expert pool",

@@ -155,7 +155,7 @@ def to_device(w: PackedWeight, device, keep_packed: bool = True):
     return torch.from_numpy(w.to_f32()).to(device=device, dtype=torch.bfloat16)
 
 
-def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int = 1, keep_packed: bool = True):
+def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int = 1, keep_packed: bool = True, stage=None):
     """Rank-local ``DecoderWeights``: fused QKV, interleaved gate/up, Megatron shares."""
     import torch
     from ..runtime.weights import DecoderWeights, LayerWeights
@@ -168,7 +168,9 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
         return torch.from_numpy(canon[name].to_f32()).to(device=device, dtype=torch.bfloat16)
 
     layers = []
-    for l in range(c.n_layers):
+    from ..runtime.weights import StageSpec
+    st = stage or StageSpec.whole(c)
+    for l in range(st.l0, st.l1):
         p = f"layers.{l}."
         q, k, v = canon[p + "attn_q"], canon[p + "attn_k"], canon[p + "attn_v"]
         if len({q.format, k.format, v.format}) == 1 and FORMATS[q.format].storage != "planar":
@@ -181,7 +183,10 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
         o = canon[p + "attn_o"]
         n_in = o.shape[1] // tp_world
         wo = to_device(o.cols(tp_rank * n_in, n_in) if tp_world > 1 else o, device, keep_packed)
-        L = LayerWeights(ln1=dense(p + "attn_norm"), ln2=dense(p + "ffn_norm"), wqkv=wqkv, wo=wo)
+        pre = c.block in ("pre", "sandwich")
+        L = LayerWeights(ln1=dense(p + "attn_norm") if pre else None, ln2=dense(p + "ffn_norm") if pre else None, wqkv=wqkv, wo=wo)
+        if c.block in ("post", "sandwich"):
+            L.post1, L.post2 = dense(p + "attn_post_norm"), dense(p + "ffn_post_norm")
         if c.attn_bias:
             from ..runtime.weights import fuse_qkv_bias
             L.bqkv = fuse_qkv_bias(dense(p + "attn_q_bias"), dense(p + "attn_k_bias"), dense(p + "attn_v_bias"), c,
@@ -207,16 +212,20 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
                 L.wgu = torch.from_numpy(np.stack([gf, uf], 1).reshape(2 * F, -1)).to(device=device, dtype=torch.bfloat16)
             L.wdown = to_device(dn.cols(tp_rank * F, F) if tp_world > 1 else dn, device, keep_packed)
         layers.append(L)
-    embed = to_device(canon["embed"], device, keep_packed)
     head = canon.get("lm_head")
-    if c.tie_embeddings or head is None:
+    tied = c.tie_embeddings or head is None
+    embed = to_device(canon["embed"], device, keep_packed) if (st.first or (st.last and tied)) else None
+    lm_head = None
+    if st.last and tied:
         lm_head = embed
-    else:
+    elif st.last:
         vl = head.shape[0] // tp_world
         lm_head = to_device(_rows(head, tp_rank * vl, vl) if tp_world > 1 else head, device, keep_packed)
+    if not st.first:
+        embed = None
     from ..runtime.weights import fold_scales
-    return fold_scales(DecoderWeights(cfg=c, embed=embed, final_norm=dense("final_norm"), lm_head=lm_head, layers=layers,
-                                      tp_rank=tp_rank, tp_world=tp_world))
+    return fold_scales(DecoderWeights(cfg=c, embed=embed, final_norm=dense("final_norm") if st.last else None,
+                                      lm_head=lm_head, layers=layers, tp_rank=tp_rank, tp_world=tp_world, stage=stage))
 
 
 def write_random_gguf(path: str, cfg: DecoderConfig, proj_format: str = "Q4_K", embed_format: str = "Q8_0",

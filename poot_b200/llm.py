@@ -17,6 +17,17 @@ from .models.config import DecoderConfig, PRESETS
 from .text.codec import ByteTokenizer, GgufTokenizer, HfTokenizer, StreamDecoder
 
 
+def _stage_and_link(cfg, pp_rank: int, pp_world: int, link):
+    """This process's layer range of a pipeline over ``pp_world`` processes, and the link to its neighbours."""
+    if pp_world <= 1:
+        return None, None
+    from .driver.placement import pipeline_cuts
+    from .parallel.pipeline import PipelineLink
+    from .runtime.weights import StageSpec
+    l0, l1 = pipeline_cuts(cfg, pp_world)[pp_rank]
+    return StageSpec(pp_rank, pp_world, l0, l1), (link or PipelineLink(pp_rank, pp_world))
+
+
 def _tokenizer_for(handle):
     if handle is None:
         return None
@@ -38,11 +49,11 @@ class LLM:
     # ---- construction --------------------------------------------------------------------------------------------
     @staticmethod
     def _assemble(cfg, weights, tokenizer, rows, max_seq, prefill_chunk, kv_fraction, comm, handle, num_blocks=None,
-                  prefix_caching=True, prefill_budget=None):
+                  prefix_caching=True, prefill_budget=None, link=None):
         import torch
         from .driver.engines import DeviceStepEngine
         from .runtime.engine import DecoderEngine, KVPool
-        dev = weights.embed.device if hasattr(weights.embed, "device") else torch.device("cuda")
+        dev = weights.layers[0].wo.device
         max_seq = min(max_seq, cfg.max_position)
         if num_blocks is None:      # capacity fit against the memory left after the weights are resident
             from .driver import capacity
@@ -51,14 +62,16 @@ class LLM:
                                   kv_fraction=kv_fraction)
             rows, max_seq, num_blocks = shapes.rows, shapes.max_seq, shapes.num_blocks
             prefill_chunk = min(prefill_chunk, max_seq)
-            if comm is not None:      # every rank must agree: take the smallest fit over the group
+            if comm is not None or link is not None:      # every rank must agree: take the smallest fit over the group
                 import torch.distributed as dist
                 t = torch.tensor([rows, max_seq, prefill_chunk, num_blocks], dtype=torch.int64, device=dev)
                 dist.all_reduce(t, op=dist.ReduceOp.MIN)
                 rows, max_seq, prefill_chunk, num_blocks = (int(v) for v in t.tolist())
         step_prefill = max(prefill_chunk, min(prefill_budget or 0, rows * prefill_chunk))
         max_tokens = max(step_prefill, rows) + rows             # prefill tokens of a step + one decode row per sequence
-        eng = DecoderEngine(weights, num_blocks, rows, max_tokens, blocks_for(max_seq), comm=comm)
+        # pipeline stages launch eagerly: their steps contain point-to-point transfers whose capture is not relied on
+        eng = DecoderEngine(weights, num_blocks, rows, max_tokens, blocks_for(max_seq), comm=comm, link=link,
+                            use_graphs=link is None and dev.type == "cuda")
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
         eos = getattr(tokenizer, "eos", None)
         drv = Driver(DeviceStepEngine(eng), num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
@@ -69,29 +82,34 @@ class LLM:
     @staticmethod
     def load(path: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
              kv_fraction: float = 0.85, keep_packed: bool = True, tp_rank: int = 0, tp_world: int = 1, comm=None,
-             num_blocks: Optional[int] = None, lora: Optional[str] = None, prefill_budget: Optional[int] = None) -> "LLM":
+             num_blocks: Optional[int] = None, lora: Optional[str] = None, prefill_budget: Optional[int] = None,
+             pp_rank: int = 0, pp_world: int = 1, link=None) -> "LLM":
         """``path``: a Hugging Face directory (config.json + safetensors) or a ``.gguf`` file; ``lora``: a PEFT adapter
-        directory merged into the projections at load."""
+        directory merged into the projections at load; ``pp_rank`` / ``pp_world``: this process's stage of a layer
+        pipeline (it loads only its layers)."""
         from .driver.handle import ModelHandle, device_weights
         handle = ModelHandle.load(path)
         if lora is not None:
             from .load.lora import load_adapter
             handle.apply_adapter(load_adapter(lora))
-        weights = device_weights(handle, device, tp_rank, tp_world, keep_packed)
+        stage, link = _stage_and_link(handle.cfg, pp_rank, pp_world, link)
+        weights = device_weights(handle, device, tp_rank, tp_world, keep_packed, stage=stage)
         return LLM._assemble(handle.cfg, weights, _tokenizer_for(handle), rows, max_seq, prefill_chunk, kv_fraction,
-                             comm, handle, num_blocks, prefill_budget=prefill_budget)
+                             comm, handle, num_blocks, prefill_budget=prefill_budget, link=link)
 
     @staticmethod
     def random(preset: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
                kv_fraction: float = 0.85, seed: int = 0, std: float = 0.02, tp_rank: int = 0, tp_world: int = 1,
-               comm=None, num_blocks: Optional[int] = None, prefill_budget: Optional[int] = None, **over) -> "LLM":
+               comm=None, num_blocks: Optional[int] = None, prefill_budget: Optional[int] = None, pp_rank: int = 0,
+               pp_world: int = 1, link=None, **over) -> "LLM":
         """Random-init weights of a named architecture (benchmarks and tests: no checkpoint on disk)."""
         from .runtime.weights import random_weights
         import dataclasses
         cfg = dataclasses.replace(PRESETS[preset](), **over)
-        weights = random_weights(cfg, device, seed=seed, std=std, tp_rank=tp_rank, tp_world=tp_world)
+        stage, link = _stage_and_link(cfg, pp_rank, pp_world, link)
+        weights = random_weights(cfg, device, seed=seed, std=std, tp_rank=tp_rank, tp_world=tp_world, stage=stage)
         return LLM._assemble(cfg, weights, None, rows, max_seq, prefill_chunk, kv_fraction, comm, None, num_blocks,
-                             prefill_budget=prefill_budget)
+                             prefill_budget=prefill_budget, link=link)
 
     @staticmethod
     def fake(vocab: int = 1000, rows: int = 8, max_seq: int = 512, num_blocks: int = 256, prefill_chunk: int = 64,

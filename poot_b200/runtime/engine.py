@@ -38,10 +38,10 @@ class StepShape:
 class KVPool:
     """Paged K/V pools, one pair per layer: ``[num_blocks, Hkv_local, 16, D]`` bf16."""
 
-    def __init__(self, cfg: DecoderConfig, num_blocks: int, device, tp_world: int = 1):
+    def __init__(self, cfg: DecoderConfig, num_blocks: int, device, tp_world: int = 1, n_layers: Optional[int] = None):
         self.num_blocks = num_blocks
         self.hkv = max(cfg.n_kv_heads // tp_world, 1)
-        shape = (cfg.n_layers, 2, num_blocks, self.hkv, KV_BLOCK, cfg.head_dim)
+        shape = (cfg.n_layers if n_layers is None else n_layers, 2, num_blocks, self.hkv, KV_BLOCK, cfg.head_dim)
         self.buf = torch.zeros(shape, dtype=torch.bfloat16, device=device)
 
     def k(self, layer: int) -> torch.Tensor:
@@ -59,8 +59,16 @@ class DecoderEngine:
     """Runs the decoder program of one rank.  ``comm`` (optional) supplies the tensor-parallel collectives."""
 
     def __init__(self, weights: DecoderWeights, num_blocks: int, max_seqs: int, max_tokens: int,
-                 max_blocks_per_seq: int, comm=None, device=None, use_graphs: bool = True):
+                 max_blocks_per_seq: int, comm=None, device=None, use_graphs: bool = True, link=None):
         cfg = weights.cfg
+        self.stage = weights.stage          # None, or this rank's layer range of a pipeline
+        self.link = link                    # hand-off of the residual stream between stages
+        if self.stage is not None and self.stage.count > 1:
+            from .weights import UnsupportedOnDevice
+            if link is None:
+                raise ValueError("a pipeline stage needs a link to its neighbours")
+            if comm is not None:
+                raise UnsupportedOnDevice("pipeline stages are not themselves tensor-parallel groups")
         gaps = cfg.device_gaps()
         if gaps:
             from .weights import UnsupportedOnDevice
@@ -69,14 +77,14 @@ class DecoderEngine:
             from .weights import fold_scales
             fold_scales(weights)
         self.cfg, self.w, self.comm = cfg, weights, comm
-        self.device = torch.device(device if device is not None else weights.embed.device)
+        self.device = torch.device(device if device is not None else weights.layers[0].wo.device)
         self.tp = weights.tp_world
         self.hq = cfg.n_heads // self.tp
         self.hkv = max(cfg.n_kv_heads // self.tp, 1)
         self.max_seqs, self.max_tokens, self.max_blocks = max_seqs, max_tokens, max_blocks_per_seq
         self.use_graphs = use_graphs
         self.tp_mode = "auto"   # "auto": one-shot all-reduce for small steps, reduce-scatter/all-gather above; "rs_ag"
-        self.kv = KVPool(cfg, num_blocks, self.device, self.tp)
+        self.kv = KVPool(cfg, num_blocks, self.device, self.tp, n_layers=len(weights.layers))
         dev, i32 = self.device, torch.int32
         if comm is not None and getattr(comm, "fused", False):
             max_tokens = max(max_tokens, 128)  # padded rows of the fused tensor-parallel path
@@ -219,11 +227,11 @@ class DecoderEngine:
             K.attn_paged(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:R],
                          (self.row_ctx_simt if flash else self.row_ctx)[:R], self.hq, self.hkv, D, self.scale,
                          out=self.attn[:R], splits=splits, scratch=self.attn_scratch, softcap=cfg.attn_softcap,
-                         window=cfg.window_of(l))
+                         window=cfg.window_of(self.w.layer0 + l))
         if flash:
             K.attn_flash_prefill(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables,
                                  self.attn_tiles[:self._tile_slots(T, B)], self.hq, self.hkv, self.scale,
-                                 out=self.attn[:R], window=cfg.window_of(l))
+                                 out=self.attn[:R], window=cfg.window_of(self.w.layer0 + l))
 
     def _tile_slots(self, T: int, B: int) -> int:
         """Tile slots a (T, B) step can need: full tiles plus one ragged tile per sequence."""
@@ -250,13 +258,19 @@ class DecoderEngine:
                 return self._forward_tp_fused(shape, R)
         self._launch_counter = 0
         h = self.h[:T]
-        self._count()
-        if isinstance(w.embed, K.QuantWeight):
-            K.quant_row_gather(self.tokens[:T], w.embed, out=h)
+        staged = self.stage is not None and self.stage.count > 1
+        if staged and shape.chain:
+            raise ValueError("chained decode feeds tokens back on one device; a pipeline's sampler and embedding are on different stages")
+        if staged and not self.stage.first:
+            self.link.recv_hidden(h)             # the residual stream as the previous stage left it
         else:
-            K.embed_gather(self.tokens[:T], w.embed, out=h)
-        if cfg.embed_scale != 1.0:
-            h.mul_(cfg.embed_scale)
+            self._count()
+            if isinstance(w.embed, K.QuantWeight):
+                K.quant_row_gather(self.tokens[:T], w.embed, out=h)
+            else:
+                K.embed_gather(self.tokens[:T], w.embed, out=h)
+            if cfg.embed_scale != 1.0:
+                h.mul_(cfg.embed_scale)
         pending = None
         post = cfg.block != "pre"           # a norm sits between each projection and its residual add
         for l, L in enumerate(w.layers):
@@ -268,7 +282,7 @@ class DecoderEngine:
             if cfg.qk_norm_wide:            # one norm over the whole q / k projection: done here, not per head in the rope kernel
                 self._wide_qk_norm(qkv, L, T)
                 qn = kn = None
-            cos, sin = self._rope_tables_of(l)
+            cos, sin = self._rope_tables_of(w.layer0 + l)
             self._count()
             K.rope_kv_write(qkv, self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
                             cos, sin, self.hq, self.hkv, D, cfg.rot, qn, kn, cfg.norm_eps)
@@ -298,6 +312,11 @@ class DecoderEngine:
         if pending is not None:
             self._count()
             K.reduce_partials(h, pending, h)
+        if staged and not self.stage.last:
+            self.link.send_hidden(h)
+            if self.stage.first:                 # the driver's rank: wait for the last stage's sampled tokens
+                self.link.return_picked(self.picked[:B], self.logprobs[:B] if shape.logprobs else None)
+            return
         hl = self.hl[:B]
         if B == T:
             hl = h
@@ -311,6 +330,8 @@ class DecoderEngine:
             self._count()
             K.softcap_(self.logits_local[:B], cfg.final_softcap)
         self._sample(shape, self.logits_local[:B])
+        if staged:
+            self.link.return_picked(self.picked[:B], self.logprobs[:B] if shape.logprobs else None)
 
     def _rope_tables_of(self, l: int):
         cfg = self.cfg

@@ -39,6 +39,28 @@ class LayerWeights:
     quant: Dict[str, object] = field(default_factory=dict)  # packed (GGUF block) weights by role
 
 
+@dataclass(frozen=True)
+class StageSpec:
+    """One stage of a layer pipeline: layers ``[l0, l1)`` of the model on this rank; the token embedding lives on the
+    first stage, the final norm and the head on the last (crates/poot-llm/src/driver/placement.rs:1-16)."""
+    index: int
+    count: int
+    l0: int
+    l1: int
+
+    @property
+    def first(self) -> bool:
+        return self.index == 0
+
+    @property
+    def last(self) -> bool:
+        return self.index == self.count - 1
+
+    @staticmethod
+    def whole(cfg: DecoderConfig) -> "StageSpec":
+        return StageSpec(0, 1, 0, cfg.n_layers)
+
+
 @dataclass
 class DecoderWeights:
     cfg: DecoderConfig
@@ -51,6 +73,11 @@ class DecoderWeights:
     ep_rank: int = 0        # expert-parallel share: this rank holds experts [ep_rank * E/ep_world, ...)
     ep_world: int = 1
     quant: Dict[str, object] = field(default_factory=dict)
+    stage: Optional[StageSpec] = None      # None = the whole model; else ``layers`` holds layers [stage.l0, stage.l1)
+
+    @property
+    def layer0(self) -> int:
+        return 0 if self.stage is None else self.stage.l0
 
     def nbytes(self) -> int:
         n = 0
@@ -65,7 +92,8 @@ class DecoderWeights:
                 n += t.numel() * t.element_size()
 
         for t in (self.embed, self.final_norm, self.lm_head):
-            add(t)
+            if t is not None:
+                add(t)
         for L in self.layers:
             for v in vars(L).values():
                 add(v)
@@ -95,7 +123,7 @@ def fold_scales(w: "DecoderWeights") -> "DecoderWeights":
                 if not isinstance(t, torch.Tensor):
                     raise UnsupportedOnDevice("residual_scale cannot be folded into block-quantised projections")
                 setattr(L, role, (t.float() * cfg.residual_scale).to(t.dtype))
-    if cfg.logit_scale != 1.0:
+    if cfg.logit_scale != 1.0 and w.lm_head is not None:
         if not isinstance(w.lm_head, torch.Tensor):
             raise UnsupportedOnDevice("logit_scale cannot be folded into a block-quantised LM head")
         w.lm_head = (w.lm_head.float() * cfg.logit_scale).to(w.lm_head.dtype)     # a new tensor: a tied table stays as is
@@ -139,7 +167,7 @@ def fuse_qkv(wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, cfg: DecoderC
 
 
 def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02, tp_rank: int = 0, tp_world: int = 1,
-                   ep_rank: int = 0, ep_world: int = 1, dtype=torch.bfloat16) -> DecoderWeights:
+                   ep_rank: int = 0, ep_world: int = 1, dtype=torch.bfloat16, stage: Optional[StageSpec] = None) -> DecoderWeights:
     """Random-init weights ``~N(0, std)`` generated directly in the rank-local fused layouts.
 
     Each tensor is drawn from a generator seeded by (seed, layer, role) so a rank's shard of a weight equals the
@@ -157,7 +185,8 @@ def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02,
         return torch.ones(n, dtype=dtype, device=dev)
 
     layers = []
-    for l in range(cfg.n_layers):
+    st = stage or StageSpec.whole(cfg)
+    for l in range(st.l0, st.l1):
         t = (l + 1) * 64
         wq = draw((cfg.q_size, H), t + 0)
         wk = draw((cfg.kv_size, H), t + 1)
@@ -192,16 +221,21 @@ def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02,
             del g_, u_
             L.wdown = shard_cols(draw((H, F), t + 6), tp_rank, tp_world)
         layers.append(L)
-    embed = draw((cfg.vocab, H), 1)
-    lm_head = embed if cfg.tie_embeddings else draw((cfg.vocab, H), 2)
-    if tp_world > 1:
-        lm_head = shard_rows(lm_head, tp_rank, tp_world)  # vocabulary-parallel head
-    return fold_scales(DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H), lm_head=lm_head, layers=layers,
-                                      tp_rank=tp_rank, tp_world=tp_world, ep_rank=ep_rank, ep_world=ep_world))
+    embed = draw((cfg.vocab, H), 1) if (st.first or (st.last and cfg.tie_embeddings)) else None
+    lm_head = None
+    if st.last:
+        lm_head = embed if cfg.tie_embeddings else draw((cfg.vocab, H), 2)
+        if tp_world > 1:
+            lm_head = shard_rows(lm_head, tp_rank, tp_world)  # vocabulary-parallel head
+    if not st.first:
+        embed = None
+    return fold_scales(DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H) if st.last else None, lm_head=lm_head,
+                                      layers=layers, tp_rank=tp_rank, tp_world=tp_world, ep_rank=ep_rank, ep_world=ep_world,
+                                      stage=stage))
 
 
 def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], device, tp_rank: int = 0,
-                       tp_world: int = 1, dtype=torch.bfloat16) -> DecoderWeights:
+                       tp_world: int = 1, dtype=torch.bfloat16, stage: Optional[StageSpec] = None) -> DecoderWeights:
     """Build device weights from canonical names (``layers.{i}.attn_q`` ... as produced by the family name tables)."""
     dev = torch.device(device)
 
@@ -209,7 +243,8 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
         return tensors[name].to(device=dev, dtype=dtype)
 
     layers = []
-    for l in range(cfg.n_layers):
+    st = stage or StageSpec.whole(cfg)
+    for l in range(st.l0, st.l1):
         p = f"layers.{l}."
         wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)
         wo = shard_cols(get(p + "attn_o"), tp_rank, tp_world)
@@ -233,12 +268,17 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
                                        shard_rows(get(p + "ffn_up"), tp_rank, tp_world))
             L.wdown = shard_cols(get(p + "ffn_down"), tp_rank, tp_world)
         layers.append(L)
-    embed = get("embed")
-    lm_head = embed if cfg.tie_embeddings or "lm_head" not in tensors else get("lm_head")
-    if tp_world > 1:
-        lm_head = shard_rows(lm_head, tp_rank, tp_world)
-    return fold_scales(DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm"), lm_head=lm_head, layers=layers,
-                                      tp_rank=tp_rank, tp_world=tp_world))
+    tied = cfg.tie_embeddings or "lm_head" not in tensors
+    embed = get("embed") if (st.first or (st.last and tied)) else None
+    lm_head = None
+    if st.last:
+        lm_head = embed if tied else get("lm_head")
+        if tp_world > 1:
+            lm_head = shard_rows(lm_head, tp_rank, tp_world)
+    if not st.first:
+        embed = None
+    return fold_scales(DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm") if st.last else None,
+                                      lm_head=lm_head, layers=layers, tp_rank=tp_rank, tp_world=tp_world, stage=stage))
 
 
 def random_quant_weights(cfg: DecoderConfig, device, proj_format: str = "Q4_K", embed_format: str = "Q8_0", seed: int = 0,

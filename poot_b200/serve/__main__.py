@@ -33,13 +33,18 @@ def main(argv=None) -> int:
     if cfg.backend == "oracle" and world > 1:
         print("poot-serve: the oracle backend runs in one process", file=sys.stderr)
         return 2
+    pp = 1
     if world > 1:
         import torch
         import torch.distributed as dist
+        from ..driver.placement import Placement
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
         dist.init_process_group("nccl")
-        from ..parallel.tp import make_comm
-        comm = make_comm("fused", rank, world, torch.device("cuda", torch.cuda.current_device()))
+        if Placement.parse(cfg.placement).kind == "pipeline":     # one stage per process: layers split, no collectives
+            pp = world
+        else:
+            from ..parallel.tp import make_comm
+            comm = make_comm("fused", rank, world, torch.device("cuda", torch.cuda.current_device()))
         from .follower import init_control_group
         init_control_group()
     if _is_encoder_checkpoint(cfg.model):
@@ -48,15 +53,16 @@ def main(argv=None) -> int:
         llm = LLM.fake(rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, prefill_budget=cfg.prefill_budget or None)
     elif cfg.model.startswith("random:"):
         llm = LLM.random(cfg.model.split(":", 1)[1], rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
-                         kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm,
-                         prefill_budget=cfg.prefill_budget or None)
+                         kv_fraction=cfg.kv_fraction, tp_rank=rank if pp == 1 else 0, tp_world=world if pp == 1 else 1,
+                         comm=comm, prefill_budget=cfg.prefill_budget or None, pp_rank=rank if pp > 1 else 0, pp_world=pp)
     elif cfg.backend == "oracle":
         llm = LLM.oracle(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, lora=cfg.lora,
                          num_blocks=cfg.rows * ((cfg.max_seq + 15) // 16) + 8, prefill_budget=cfg.prefill_budget or None)
     else:
         llm = LLM.load(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
-                       kv_fraction=cfg.kv_fraction, tp_rank=rank, tp_world=world, comm=comm, lora=cfg.lora,
-                       prefill_budget=cfg.prefill_budget or None)
+                       kv_fraction=cfg.kv_fraction, tp_rank=rank if pp == 1 else 0, tp_world=world if pp == 1 else 1,
+                       comm=comm, lora=cfg.lora, prefill_budget=cfg.prefill_budget or None,
+                       pp_rank=rank if pp > 1 else 0, pp_world=pp)
     if world > 1:
         from .follower import follow, LeaderStepEngine
         if rank != 0:

@@ -13,7 +13,7 @@ from typing import List, Optional
 class ServeConfig:
     model: str = ""
     addr: str = "127.0.0.1:8080"
-    placement: str = "single"            # single | tensor:0,1,.. | expert:0,1,..
+    placement: str = "single"            # single | tensor:0,1,.. | expert:0,1,.. | pipeline:0,1,..
     rows: int = 32
     max_seq: int = 4096
     prefill_chunk: int = 512
@@ -57,8 +57,6 @@ class ServeConfig:
             raise ValueError(f"--matmul-precision {self.matmul_precision!r}")
         if not (self.placement == "single" or self.placement.startswith(("tensor:", "expert:", "pipeline:"))):
             raise ValueError(f"--placement {self.placement!r}")
-        if self.placement.startswith("pipeline:"):
-            raise ValueError("pipeline placement is not built: use tensor:<ordinals>")
         host, _, port = self.addr.rpartition(":")
         if not host or not port.isdigit() or not (0 <= int(port) <= 65535):
             raise ValueError(f"address {self.addr!r} is not host:port")

@@ -19,7 +19,7 @@ def test_feature_table():
     assert "vocabulary" in str(e.value)
     with pytest.raises(Incompatible):
         check([Feature.DRAFT_LOOKUP, Feature.GUIDED])
-    for f in (Feature.PIPELINE_PLACEMENT, Feature.DRAFT_MTP, Feature.RECURRENT_STATE, Feature.EXPERT_POOL):
+    for f in (Feature.DRAFT_MTP, Feature.RECURRENT_STATE, Feature.EXPERT_POOL):
         with pytest.raises(Unavailable):
             check([f])
 
@@ -33,8 +33,17 @@ def test_placement_parse_and_divisibility():
     for bad in ("tensor", "tensor:a", "tensor:0,0", "tensor:0,1,2", "ring:0,1"):
         with pytest.raises(PlacementError):
             Placement.parse(bad)
-    with pytest.raises(Unavailable):
-        Placement.parse("pipeline:0,1")
+    pp = Placement.parse("pipeline:0,1,2")
+    assert pp.kind == "pipeline" and pp.world == 3 and pp.features == [Feature.PIPELINE_PLACEMENT]
+    pp.validate(llama3_8b())
+    from poot_b200.driver.placement import pipeline_cuts
+    cuts = pipeline_cuts(llama3_70b(), 8)
+    assert cuts[0][0] == 0 and cuts[-1][1] == 80 and all(a < b for a, b in cuts) and all(cuts[i][1] == cuts[i + 1][0] for i in range(7))
+    # the embedding sits on the first stage and the head on the last: they carry fewer layers than the middle stages
+    sizes = [b - a for a, b in cuts]
+    assert sizes[0] < max(sizes) and sizes[-1] < max(sizes) and max(sizes) - min(sizes) <= 2
+    with pytest.raises(Incompatible):
+        check([Feature.PIPELINE_PLACEMENT, Feature.TENSOR_PLACEMENT])
     with pytest.raises(PlacementError):
         Placement.parse("expert:0,1").validate(llama3_8b())
     with pytest.raises(PlacementError):

@@ -206,3 +206,53 @@ def test_family_blocks_on_the_engine_match_the_graph_oracle(name):
         got = eng.logits[0]
     err = (got - ref).abs().max().item()
     assert err < 0.02 * max(1.0, ref.abs().max().item()), (name, err, ref.abs().max().item())
+
+
+def test_pipeline_stages_reproduce_the_single_device_run():
+    """Three pipeline stages (one thread each, queues as links) over the emulated kernels: the first stage embeds and
+    gets the sampled tokens back, the middle stage only transforms the residual stream, the last stage samples; the
+    logits and tokens equal the unsplit engine's, for a prefill step and decode steps through each stage's own K/V."""
+    import threading
+    from poot_b200.driver.placement import Placement, pipeline_cuts
+    from poot_b200.parallel.pipeline import LocalLink
+    from poot_b200.runtime.engine import DecoderEngine
+    from poot_b200.runtime.session import FixedBatchSession
+    from poot_b200.runtime.weights import StageSpec, random_weights
+    cfg = _cfg(n_layers=5, layer_windows=[0, 6, 0, 6, 0])
+    cuts = pipeline_cuts(cfg, 3)
+    assert [b - a for a, b in cuts] in ([1, 2, 2], [2, 2, 1], [2, 1, 2]) and cuts[0][0] == 0 and cuts[-1][1] == 5
+    Placement.parse("pipeline:0,1,2").validate(cfg)
+    g = torch.Generator().manual_seed(11)
+    prompts = torch.randint(0, cfg.vocab, (2, 18), generator=g, dtype=torch.int32)
+    nxt = torch.randint(0, cfg.vocab, (2, 2), generator=g, dtype=torch.int32)
+
+    def drive(sess):
+        out = [sess.prefill_fast(prompts).clone()]
+        for t in range(2):
+            out.append(sess.decode(nxt[:, t].tolist()).clone())
+        return out
+
+    with emulated_kernels():
+        _, whole, s = _engine(cfg, 2, 64, 48)
+        want = drive(s)
+        want_logits = whole.logits[:2].clone()
+        queues, engines, results = {}, [], {}
+        for i, (l0, l1) in enumerate(cuts):
+            st = StageSpec(i, 3, l0, l1)
+            w = random_weights(cfg, "cpu", seed=0, std=0.05, stage=st)
+            assert len(w.layers) == l1 - l0 and (w.embed is not None) == st.first and (w.lm_head is not None) == st.last
+            engines.append(DecoderEngine(w, num_blocks=9, max_seqs=2, max_tokens=48, max_blocks_per_seq=4, device="cpu",
+                                         use_graphs=False, link=LocalLink(queues, i, 3)))
+
+        def stage(i):
+            results[i] = drive(FixedBatchSession(engines[i], 2, 64))
+        threads = [threading.Thread(target=stage, args=(i,)) for i in range(3)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=120)
+        assert sorted(results) == [0, 1, 2]
+    for a, b in zip(results[0], want):            # the driver's stage holds the tokens the last stage sampled
+        assert torch.equal(a, b)
+    assert torch.equal(engines[2].logits[:2], want_logits)
+    assert engines[0].kv.buf.shape[0] == cuts[0][1] - cuts[0][0] and engines[0].link.sent_bytes > 0

@@ -280,7 +280,7 @@ def test_cli_flags_are_strict():
     cfg = parse_args(["model.gguf", "127.0.0.1:9000", "--rows", "64", "--max-seq", "8192", "--no-prefix-cache",
                       "--placement", "tensor:0,1,2,3", "--allowed-host", "a", "--allowed-host", "b"])
     assert cfg.rows == 64 and cfg.placement_ordinals == [0, 1, 2, 3] and not cfg.prefix_cache and cfg.allowed_hosts == ["a", "b"]
-    for bad in (["m", "--rows", "0"], ["m", "--bogus"], ["m", "--placement", "pipeline:0,1"], ["m", "nohost"],
+    for bad in (["m", "--rows", "0"], ["m", "--bogus"], ["m", "--placement", "ring:0,1"], ["m", "nohost"],
                 ["m", "--kv-dtype", "int3"]):
         with pytest.raises(ValueError):
             parse_args(bad)

@@ -43,3 +43,18 @@ def test_expert_parallel_matches_single_gpu(kind):
     n = torch.cuda.device_count()
     world = 8 if n >= 8 else (4 if n >= 4 else 2)
     _run(kind, world, 6, 29545, moe=True)
+
+
+@pytest.mark.xfail(strict=False, reason="pipeline stages over NCCL point-to-point: not yet run on devices")
+def test_pipeline_two_stages_match_single_gpu():
+    """Layer pipeline over two GPUs: stage hand-off by NCCL send / recv, rank 0 drives, rank 1 follows."""
+    import json
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", POOT_PP_CUDA="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29547", str(ROOT / "tests" / "pp_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert out["ok"], out
