@@ -56,7 +56,8 @@ class NcclComm:
 
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor) -> None:
         with K.timed_region("nccl_all_gather"):
-            dist.all_gather_into_tensor(out, inp, group=self.group)
+            # flat views: the same bytes, and the form every backend of the process group accepts
+            dist.all_gather_into_tensor(out.view(-1), inp.reshape(-1), group=self.group)
 
 
 class FusedComm(NcclComm):

@@ -221,6 +221,44 @@ def argmax(logits, out=None, scratch=None):
     return out
 
 
+def argmax_partials(logits, idx_offset, vocab_total, part):
+    """Stage 1 over one vocabulary shard: per (row, chunk) the best finite value (as its bit pattern), its global index
+    and the first non-finite global index (``vocab_total`` when there is none)."""
+    rows, vocab = logits.shape
+    chunk = K.ARGMAX_CHUNK
+    x = logits.float()
+    for g in range(part.shape[1]):
+        seg = x[:, g * chunk:(g + 1) * chunk]
+        fin = torch.isfinite(seg)
+        masked = torch.where(fin, seg, torch.full_like(seg, -float("inf")))
+        best = masked.argmax(-1)                                        # first maximum
+        val = masked.gather(-1, best[:, None])[:, 0]
+        any_fin = fin.any(-1)
+        part[:, g, 0] = torch.where(any_fin, val, torch.zeros_like(val)).view(torch.int32)
+        part[:, g, 1] = torch.where(any_fin, best + idx_offset + g * chunk, torch.full_like(best, -1)).to(torch.int32)
+        bad = torch.where(fin, torch.full_like(seg, float(vocab_total)),
+                          (torch.arange(seg.shape[1]) + idx_offset + g * chunk).float().expand_as(seg)).min(-1).values
+        part[:, g, 2] = bad.to(torch.int32)
+    return part
+
+
+def argmax_combine(parts, rows, groups, vocab_total, out):
+    p = parts.reshape(-1, rows, groups, 3).permute(1, 0, 2, 3).reshape(rows, -1, 3)
+    for r in range(rows):
+        vals = p[r, :, 0].contiguous().view(torch.float32)
+        idx = p[r, :, 1]
+        live = idx >= 0
+        bad = int(p[r, :, 2].min())
+        tok = 0
+        if live.any():
+            v = torch.where(live, vals, torch.full_like(vals, -float("inf")))
+            m = v.max()
+            tok = int(idx[(v == m) & live].min())
+        out[r, 0] = 0 if bad < vocab_total else tok
+        out[r, 1] = bad if bad < vocab_total else -1
+    return out
+
+
 def sample_gumbel(logits, params, top_k, seeds, rule, out=None):
     from ..oracle.sampling import sample_rows
     r = torch.from_numpy(sample_rows(logits.float().numpy(), params.numpy(), top_k.numpy(), seeds.numpy(), rule))
@@ -326,7 +364,8 @@ def emulated_kernels():
                 gated_act=gated_act, softcap_=softcap_,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
                 attn_paged=attn_paged, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
-                argmax=argmax, sample_gumbel=sample_gumbel, decode_advance=decode_advance,
+                argmax=argmax, argmax_partials=argmax_partials, argmax_combine=argmax_combine,
+                sample_gumbel=sample_gumbel, decode_advance=decode_advance,
                 status_word=lambda device=None: _status, check_status=lambda device=None: None),
         moe_ops: dict(moe_route=moe_route, moe_combine=moe_combine, gemm_grouped=gemm_grouped),
         suffix_ops: dict(adjust_logits=adjust_logits, token_logprob=token_logprob),
