@@ -256,3 +256,36 @@ def test_pipeline_stages_reproduce_the_single_device_run():
         assert torch.equal(a, b)
     assert torch.equal(engines[2].logits[:2], want_logits)
     assert engines[0].kv.buf.shape[0] == cuts[0][1] - cuts[0][0] and engines[0].link.sent_bytes > 0
+
+
+def test_bench_driver_path_runs_on_the_emulated_engine():
+    """The benchmark's end-to-end arm (Driver.open / step / commit over DeviceStepEngine) on a tiny model: chunked
+    prefill of the whole batch, warm-up, timed steps, release."""
+    import importlib.util
+    import os
+    import time
+    spec = importlib.util.spec_from_file_location("poot_bench", os.path.join(os.path.dirname(__file__), "..", "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    cfg = _cfg()
+    calls = []
+
+    def timed(fn, n):
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        calls.append(n)
+        return (time.perf_counter() - t0) * 1e3
+
+    with emulated_kernels():
+        B, P = 3, 40
+        max_len = P + 64
+        bps = (max_len + 15) // 16
+        from poot_b200.runtime.engine import DecoderEngine
+        from poot_b200.runtime.weights import random_weights
+        w = random_weights(cfg, "cpu", seed=0, std=0.05)
+        eng = DecoderEngine(w, num_blocks=B * bps + bps, max_seqs=B, max_tokens=512 + B, max_blocks_per_seq=bps, device="cpu",
+                            use_graphs=False)
+        prompts = torch.randint(0, cfg.vocab, (B, P), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+        r = bench.driver_e2e(eng, cfg, B, prompts, 2, 3, max_len, timed)
+    assert calls == [3] and r["tok_s"] > 0 and r["ms_per_step"] > 0

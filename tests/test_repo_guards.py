@@ -1,0 +1,107 @@
+"""Repository guards (the reference keeps the same kind under scripts/: dependency direction, no baked paths;
+website/docs/develop/test.md:78-89): layering of the package, nothing in the product depends on scratch folders or
+on the test-only kernel emulation, sources carry no machine paths, every registered kernel signature is exported by
+a CUDA source, and every closed-call name stays out of the tree."""
+import ast
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "poot_b200")
+
+# a package may import the packages listed for it (and itself); lower layers never reach up
+LAYERS = {
+    "tensor": set(), "target": {"tensor"}, "quant": {"tensor", "ops"}, "weights": {"tensor", "quant"},
+    "load": {"tensor", "quant", "weights", "models"}, "ir": {"tensor", "quant"}, "oracle": {"tensor", "quant", "ir", "models", "runtime"},
+    "models": {"tensor", "ir", "load"}, "plan": {"tensor", "ir", "quant", "target", "models", "oracle"},
+    "ops": set(), "profile": {"target", "ops"}, "text": set(),
+    "runtime": {"models", "ops", "quant", "parallel", "tensor"}, "parallel": {"ops", "runtime"},
+    "utils": {"ops", "oracle", "runtime", "models", "tensor"},
+    "driver": {"models", "runtime", "ops", "load", "quant", "ir", "oracle", "text", "tensor", "profile", "parallel"},
+    "serve": {"driver", "text", "profile", "models", "parallel", "runtime", "ops"}, "cli": {"driver", "text", "models"},
+}
+TOP = {"llm": None, "embed": None, "build": None, "__init__": None}     # facades at the package root may import anything
+
+
+def _py_files(base):
+    for d, dirs, files in os.walk(base):
+        dirs[:] = [x for x in dirs if x not in ("__pycache__", "lib")]
+        for f in files:
+            if f.endswith(".py"):
+                yield os.path.join(d, f)
+
+
+def _imports(path):
+    tree = ast.parse(open(path).read(), path)
+    rel = os.path.relpath(path, PKG).split(os.sep)
+    for node in ast.walk(tree):
+        if isinstance(node, ast.ImportFrom):
+            if node.level:           # relative: resolve against the file's package
+                base = rel[:-1]
+                up = node.level - 1
+                base = base[:len(base) - up] if up else base
+                mod = base + (node.module.split(".") if node.module else [])
+                yield ".".join(["poot_b200"] + mod)
+            elif node.module:
+                yield node.module
+        elif isinstance(node, ast.Import):
+            for a in node.names:
+                yield a.name
+
+
+def test_package_layering():
+    bad = []
+    for path in _py_files(PKG):
+        rel = os.path.relpath(path, PKG).split(os.sep)
+        me = rel[0] if len(rel) > 1 else rel[0][:-3]
+        if me in TOP:
+            continue
+        assert me in LAYERS, f"package {me!r} is not in the layer table"
+        for mod in _imports(path):
+            parts = mod.split(".")
+            if parts[0] != "poot_b200" or len(parts) < 2:
+                continue
+            dep = parts[1]
+            if dep == me or dep in TOP and dep != "__init__":
+                if dep in ("llm", "embed") and me != "cli" and me != "serve":
+                    bad.append((os.path.relpath(path, ROOT), mod))
+                continue
+            if dep not in LAYERS[me]:
+                bad.append((os.path.relpath(path, ROOT), mod))
+    assert not bad, bad
+
+
+def test_product_does_not_depend_on_scratch_or_on_the_kernel_emulation():
+    for path in list(_py_files(PKG)) + [os.path.join(ROOT, "bench.py"), os.path.join(ROOT, "__graft_entry__.py")]:
+        src = open(path).read()
+        assert not re.search(r"(^|[^a-z])_work([^a-z]|$)", src), path
+        if not path.endswith(os.path.join("utils", "kernel_emulation.py")):
+            assert "kernel_emulation" not in src, f"{path}: the host emulation is a test harness, nothing in the product selects it"
+
+
+def test_sources_carry_no_machine_paths_or_closed_calls():
+    pat = re.compile(r"/root/|/home/[a-z]|cudaMemcpy(3D)?BatchAsync|cuMemcpy(3D)?BatchAsync|multicast::cluster")
+    hits = []
+    for base, exts in ((PKG, (".py",)), (os.path.join(ROOT, "csrc"), (".cu", ".cuh", ".cpp", ".h")),
+                       (os.path.join(ROOT, "benchmarks"), (".py",)), (os.path.join(ROOT, "tests"), (".py",))):
+        for d, dirs, files in os.walk(base):
+            dirs[:] = [x for x in dirs if x != "__pycache__"]
+            for f in files:
+                if f.endswith(exts) and f != "test_repo_guards.py":
+                    for i, line in enumerate(open(os.path.join(d, f), errors="replace"), 1):
+                        if pat.search(line):
+                            hits.append((os.path.relpath(os.path.join(d, f), ROOT), i, line.strip()[:80]))
+    assert not hits, hits
+
+
+def test_every_registered_kernel_entry_is_exported_by_a_source():
+    from poot_b200.ops import cuda_ops, moe_ops, suffix_ops  # noqa: F401  (registration happens at import)
+    names = set(cuda_ops._SIGS) if hasattr(cuda_ops, "_SIGS") else set()
+    exported = set()
+    for d, _, files in os.walk(os.path.join(ROOT, "csrc")):
+        for f in files:
+            if f.endswith((".cu", ".cpp")):
+                exported |= set(re.findall(r"POOT_API\s+[\w\s\*]+?\b(poot_\w+)\s*\(", open(os.path.join(d, f)).read()))
+    assert names, "the signature table was not found"
+    missing = sorted(n for n in names if n not in exported)
+    assert not missing, missing
