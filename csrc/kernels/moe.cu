@@ -13,31 +13,44 @@ namespace poot {
 
 constexpr int MOE_MAX_K = 8;
 
-__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int renorm,
+// mode 0: softmax gates (over the k selected logits when renorm, else over all experts, not renormalised).
+// mode 1: sigmoid scores; experts are ranked by score + select_bias[e] (the bias does not enter the gate), gates are
+//         the selected scores, divided by their sum (+1e-20) when renorm.  Both: gates are multiplied by `scale`.
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int renorm, int mode,
+                                 const float* __restrict__ select_bias, float scale,
                                  int* __restrict__ ids, float* __restrict__ gates, float* __restrict__ dense) {
   pdl_wait(); pdl_launch();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   const float* lr = logits + (size_t)t * E;
   int best[MOE_MAX_K];
-  float bv[MOE_MAX_K];
-  for (int j = 0; j < k; ++j) { best[j] = -1; bv[j] = -FLT_MAX; }
+  float bv[MOE_MAX_K];      // the value experts are ranked by
+  float sv[MOE_MAX_K];      // the score that becomes the gate (mode 1)
+  for (int j = 0; j < k; ++j) { best[j] = -1; bv[j] = -FLT_MAX; sv[j] = 0.f; }
   float all_max = -FLT_MAX;
   for (int e = 0; e < E; ++e) {
     float s = lr[e];
     if (!(s >= -FLT_MAX)) s = -FLT_MAX;      // NaN and -inf
     if (s > FLT_MAX) s = FLT_MAX;
     all_max = fmaxf(all_max, s);
+    float score = s, rankv = s;
+    if (mode == 1) {
+      score = 1.f / (1.f + expf(-s));
+      rankv = score + (select_bias ? select_bias[e] : 0.f);
+    }
     // insertion into the sorted top-k; strict '>' keeps the lower index first on ties
     int pos = k;
-    for (int j = k - 1; j >= 0; --j) if (best[j] < 0 || s > bv[j]) pos = j;
+    for (int j = k - 1; j >= 0; --j) if (best[j] < 0 || rankv > bv[j]) pos = j;
     if (pos < k) {
-      for (int j = k - 1; j > pos; --j) { best[j] = best[j - 1]; bv[j] = bv[j - 1]; }
-      best[pos] = e; bv[pos] = s;
+      for (int j = k - 1; j > pos; --j) { best[j] = best[j - 1]; bv[j] = bv[j - 1]; sv[j] = sv[j - 1]; }
+      best[pos] = e; bv[pos] = rankv; sv[pos] = score;
     }
   }
   float w[MOE_MAX_K], sum = 0.f;
-  if (renorm) {
+  if (mode == 1) {
+    for (int j = 0; j < k; ++j) { w[j] = sv[j]; sum += sv[j]; }
+    sum = renorm ? sum + 1e-20f : 1.f;
+  } else if (renorm) {
     for (int j = 0; j < k; ++j) { w[j] = expf(bv[j] - bv[0]); sum += w[j]; }
   } else {
     for (int e = 0; e < E; ++e) {
@@ -50,7 +63,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
   }
   for (int e = 0; e < E; ++e) dense[(size_t)e * T + t] = 0.f;
   for (int j = 0; j < k; ++j) {
-    const float g = w[j] / sum;
+    const float g = w[j] / sum * scale;
     ids[(size_t)t * k + j] = best[j];
     gates[(size_t)t * k + j] = g;
     if (best[j] >= 0) dense[(size_t)best[j] * T + t] = g;
@@ -89,7 +102,18 @@ POOT_API int poot_moe_route(const float* logits, int T, int E, int k, int renorm
                             cudaStream_t s) {
   if (T == 0) return 0;
   if (k < 1 || k > MOE_MAX_K || k > E) return (int)cudaErrorInvalidValue;
-  return launch_k(moe_route_kernel, dim3((T + 63) / 64), dim3(64), 0, s, logits, T, E, k, renorm, ids, gates, dense);
+  return launch_k(moe_route_kernel, dim3((T + 63) / 64), dim3(64), 0, s, logits, T, E, k, renorm, 0,
+                  (const float*)nullptr, 1.f, ids, gates, dense);
+}
+
+// Router variants: mode 1 = sigmoid scores with an optional selection-only bias [E]; gates times `scale`.
+POOT_API int poot_moe_route_ex(const float* logits, int T, int E, int k, int renorm, int mode, const float* select_bias,
+                               float scale, int* ids, float* gates, float* dense, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (k < 1 || k > MOE_MAX_K || k > E || mode < 0 || mode > 1) return (int)cudaErrorInvalidValue;
+  if (mode == 0 && select_bias != nullptr) return (int)cudaErrorInvalidValue;
+  return launch_k(moe_route_kernel, dim3((T + 63) / 64), dim3(64), 0, s, logits, T, E, k, renorm, mode, select_bias, scale,
+                  ids, gates, dense);
 }
 
 POOT_API int poot_moe_combine(const void* h, const void* parts, void* out, int T, int H, int groups, long long gstride,

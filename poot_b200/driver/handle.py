@@ -195,6 +195,8 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
             L.q_norm, L.k_norm = dense(p + "attn_q_norm"), dense(p + "attn_k_norm")
         if c.is_moe:
             L.router = dense(p + "ffn_router")
+            if c.router_select_bias:
+                L.select_bias = torch.from_numpy(handle.f32(p + "ffn_router_select_bias")).to(device=device, dtype=torch.float32)
             gus, downs = [], []
             for e in range(c.n_experts):
                 g, u = handle.f32(p + f"experts.{e}.gate"), handle.f32(p + f"experts.{e}.up")

@@ -179,11 +179,10 @@ class DecoderConfig:
         if self.embed_norm: g.append("embedding norm")
         if self.attn_sinks: g.append("attention sinks")
         if self.swiglu_limit > 0: g.append("clamped SwiGLU")
-        if self.router != "softmax" or self.router_bias or self.router_select_bias:
-            g.append("router variant")
+        if self.router_bias or (self.router == "softmax" and self.router_select_bias): g.append("router variant")
         if self.n_group > 1: g.append("group-limited routing")
-        if self.n_shared_experts or self.first_dense_layers: g.append("shared experts / leading dense layers")
-        if self.routed_scale != 1.0: g.append("routed scaling")
+        if self.shared_width or self.first_dense_layers or self.dense_layers: g.append("shared experts / dense layers in a routed model")
+        if self.is_moe and self.top_k > 8: g.append("more than 8 experts per token")
         if self.is_mla: g.append("multi-head latent attention")
         if self.is_recurrent: g.append("recurrent mixers (Mamba2 / gated delta net scans)")
         if self.layer_kinds is not None and not self.is_recurrent or self.layer_ffn is not None: g.append("single-mixer blocks")

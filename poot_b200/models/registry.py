@@ -362,6 +362,10 @@ SHIPPED: List[FamilyEntry] = [
 ]
 
 
+# families whose GGUF metadata and tensor names the generic llama-style reader covers completely
+GGUF_FAMILIES = ("llama", "qwen2", "qwen3", "qwen3moe", "phi3")
+
+
 class Registry:
     def __init__(self, entries: Optional[List[FamilyEntry]] = None):
         self.entries = list(entries if entries is not None else SHIPPED)
@@ -388,6 +392,11 @@ class Registry:
             if arch in e.gguf_archs:
                 if e.from_hf is None:
                     raise UnsupportedFamily(f"family {e.name!r} needs {e.missing}, which this build does not have")
+                if e.name not in GGUF_FAMILIES:
+                    # the GGUF header of these families carries fields (norm placement, soft caps, window patterns,
+                    # multipliers, router kinds) that only their Hugging Face header table reads here
+                    raise UnsupportedFamily(f"family {e.name!r}: no GGUF header / tensor-name table; load the Hugging Face "
+                                            "checkpoint directory (config.json + safetensors) instead")
                 return Model(config_from_gguf_metadata(arch, meta, e.name))
         raise UnsupportedFamily(f"no family for GGUF architecture {arch!r}")
 

@@ -58,7 +58,8 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
         K.linear(x, L.router, K.EPI_F32, logits)
     ids, gates = buf["ids"][:T * k], buf["gates"][:T * k]
     dense = buf["dense"][:E * T].view(E, T)
-    M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense)
+    M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense, mode=c.router, select_bias=L.select_bias,
+                scale=c.routed_scale)
     h = eng.h[:T]
     tp = (ep[1], ep[2]) if (ep is not None and ep[0] == "fused") else None
     if ep is None and e_local == E and T * k <= E:

@@ -34,6 +34,7 @@ class LayerWeights:
     post1: Optional[torch.Tensor] = None    # norm applied to the attention output before the residual add (post / sandwich blocks)
     post2: Optional[torch.Tensor] = None    # the same for the FFN output
     router: Optional[torch.Tensor] = None   # [E, hidden]
+    select_bias: Optional[torch.Tensor] = None   # [E] fp32, added to the router scores for selection only
     ex_wgu: Optional[torch.Tensor] = None   # [E_local, 2F, hidden]
     ex_wdown: Optional[torch.Tensor] = None  # [E_local, hidden, F]
     quant: Dict[str, object] = field(default_factory=dict)  # packed (GGUF block) weights by role
@@ -258,6 +259,8 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             L.q_norm, L.k_norm = get(p + "attn_q_norm"), get(p + "attn_k_norm")
         if cfg.is_moe:
             L.router = get(p + "ffn_router")
+            if cfg.router_select_bias:
+                L.select_bias = tensors[p + "ffn_router_select_bias"].to(device=dev, dtype=torch.float32).contiguous()
             gus, downs = [], []
             for e in range(cfg.n_experts):
                 gus.append(interleave_gate_up(get(p + f"experts.{e}.gate"), get(p + f"experts.{e}.up")))

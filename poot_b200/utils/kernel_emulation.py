@@ -302,13 +302,22 @@ def token_logprob(logits, picked, out=None):
     return out
 
 
-def moe_route(logits, k, renorm, ids, gates, dense):
+def moe_route(logits, k, renorm, ids, gates, dense, mode="softmax", select_bias=None, scale=1.0):
     T, E = logits.shape
     s = torch.nan_to_num(logits.float(), nan=torch.finfo(torch.float32).min, posinf=torch.finfo(torch.float32).max,
                          neginf=torch.finfo(torch.float32).min)
-    order = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :k]       # ties: lower index first
-    top = s.gather(-1, order)
-    g = torch.softmax(top, -1) if renorm else torch.softmax(s, -1).gather(-1, order)
+    if mode == "sigmoid":
+        score = torch.sigmoid(s)
+        rankv = score + (select_bias.float() if select_bias is not None else 0.0)
+        order = torch.sort(rankv, dim=-1, descending=True, stable=True).indices[:, :k]
+        g = score.gather(-1, order)
+        if renorm:
+            g = g / (g.sum(-1, keepdim=True) + 1e-20)
+    else:
+        order = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :k]       # ties: lower index first
+        top = s.gather(-1, order)
+        g = torch.softmax(top, -1) if renorm else torch.softmax(s, -1).gather(-1, order)
+    g = g * scale
     ids.view(T, k).copy_(order.to(torch.int32))
     gates.view(T, k).copy_(g)
     d = dense.view(E, T)

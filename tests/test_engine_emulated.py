@@ -162,6 +162,7 @@ HF_FAMILIES = {
     "olmo2": {"model_type": "olmo2"},
     "olmoe": {"model_type": "olmoe", "num_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
     "smollm3-nope-layer": {"model_type": "smollm3", "no_rope_layers": [1, 0]},
+    "minimax_m2": {"model_type": "minimax_m2", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
     "granite": {"model_type": "granite", "embedding_multiplier": 6.0, "residual_multiplier": 0.5, "logits_scaling": 4.0,
                 "attention_multiplier": 0.1},
 }
@@ -183,6 +184,8 @@ def test_family_blocks_on_the_engine_match_the_graph_oracle(name):
     assert cfg.device_gaps() == [], cfg.device_gaps()
     w = random_weights_f32(model, seed=2, std=0.08)
     for k in w:
+        if k.endswith("select_bias"):
+            w[k] = (0.3 * np.random.default_rng(1).standard_normal(w[k].shape)).astype(np.float32)
         if k.endswith("norm"):
             w[k] = (1.0 + 0.1 * np.random.default_rng(len(k)).standard_normal(w[k].shape)).astype(np.float32)
     w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}     # what the device will hold

@@ -57,3 +57,20 @@ def test_mixtral_like_model_matches_reference(batch, prompt):
     ref = forward_logits(w, torch.cat([toks[0], nxt[:1]]).cuda())[-1]
     err = (eng.logits[0] - ref).abs().max().item() / max(1.0, ref.abs().max().item())
     assert err < 0.06, err
+
+
+@pytest.mark.xfail(strict=False, reason="router variant: not yet run on a device")
+def test_sigmoid_router_with_selection_bias_matches_the_host_restatement():
+    from poot_b200.ops import moe_ops as M
+    from poot_b200.utils import kernel_emulation as emu
+    g = torch.Generator().manual_seed(0)
+    T, E, k = 37, 64, 6
+    logits = torch.randn(T, E, generator=g) * 2
+    bias = torch.randn(E, generator=g) * 0.3
+    for renorm in (True, False):
+        want = [torch.zeros(T * k, dtype=torch.int32), torch.zeros(T * k), torch.zeros(E * T)]
+        emu.moe_route(logits, k, renorm, *want, mode="sigmoid", select_bias=bias, scale=2.5)
+        got = [torch.zeros(T * k, dtype=torch.int32, device="cuda"), torch.zeros(T * k, device="cuda"), torch.zeros(E * T, device="cuda")]
+        M.moe_route(logits.cuda(), k, renorm, *got, mode="sigmoid", select_bias=bias.cuda(), scale=2.5)
+        assert torch.equal(got[0].cpu(), want[0])
+        assert torch.allclose(got[1].cpu(), want[1], rtol=1e-5, atol=1e-6) and torch.allclose(got[2].cpu(), want[2], rtol=1e-5, atol=1e-6)
