@@ -72,7 +72,8 @@ LAYER = {
 POST_BLOCK = {"post_attention_layernorm.weight": "attn_post_norm", "post_feedforward_layernorm.weight": "ffn_post_norm"}
 SANDWICH_BLOCK = {"input_layernorm.weight": "attn_norm", "post_attention_layernorm.weight": "attn_post_norm",
                   "pre_feedforward_layernorm.weight": "ffn_norm", "post_feedforward_layernorm.weight": "ffn_post_norm"}
-TOP = {"model.embed_tokens.weight": "embed", "model.norm.weight": "final_norm", "lm_head.weight": "lm_head"}
+TOP = {"model.embed_tokens.weight": "embed", "model.norm.weight": "final_norm", "lm_head.weight": "lm_head",
+       "model.language_model.embed_tokens.weight": "embed", "model.language_model.norm.weight": "final_norm"}
 EXPERT = {"w1": "gate", "w3": "up", "w2": "down", "gate_proj": "gate", "up_proj": "up", "down_proj": "down"}
 
 MPT_LAYER = {"norm_1.weight": "attn_norm", "norm_2.weight": "ffn_norm", "attn.out_proj.weight": "attn_o",
@@ -137,12 +138,12 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
         if n in TOP:
             canon[TOP[n]] = w
             continue
-        m = re.match(r"model\.layers\.(\d+)\.(.+)$", n)
+        m = re.match(r"model\.(?:language_model\.)?layers\.(\d+)\.(.+)$", n)
         if not m:
             continue
         l, rest = int(m.group(1)), m.group(2)
         p = f"layers.{l}."
-        if cfg.family == "qwen3next" and _qwen3next_tensor(cfg, p, rest, w, canon):
+        if cfg.family in ("qwen3next", "qwen38_27b") and _qwen3next_tensor(cfg, p, rest, w, canon):
             continue
         if rest in table:
             canon[p + table[rest]] = w
@@ -205,7 +206,12 @@ def _qwen3next_tensor(cfg: DecoderConfig, p: str, rest: str, w: PackedWeight, ca
         canon[p + "gdn_b"] = f32_weight(p + "gdn_b", a[:, :r].reshape(nv, -1))
         canon[p + "gdn_a"] = f32_weight(p + "gdn_a", a[:, r:].reshape(nv, -1))
         return True
-    simple = {"linear_attn.dt_bias": "gdn_dt_bias", "linear_attn.A_log": "gdn_a_log", "linear_attn.norm.weight": "gdn_gate_norm_w",
+    if rest == "linear_attn.in_proj_qkv.weight":        # Qwen3.5 spelling: q | k | v rows, one projection per quantity
+        kd = nk * Dg
+        canon[p + "gdn_q"], canon[p + "gdn_k"], canon[p + "gdn_v"] = w.rows(0, kd), w.rows(kd, kd), w.rows(2 * kd, nv * Dg)
+        return True
+    simple = {"linear_attn.in_proj_z.weight": "gdn_z", "linear_attn.in_proj_b.weight": "gdn_b", "linear_attn.in_proj_a.weight": "gdn_a",
+              "linear_attn.dt_bias": "gdn_dt_bias", "linear_attn.A_log": "gdn_a_log", "linear_attn.norm.weight": "gdn_gate_norm_w",
               "linear_attn.out_proj.weight": "gdn_o"}
     if rest in simple:
         canon[p + simple[rest]] = w

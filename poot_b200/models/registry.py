@@ -314,6 +314,15 @@ def _qwen3next(c):
     return cfg
 
 
+def _qwen35(c):
+    """Qwen3.5 text tower (``qwen3_5_text``, or ``qwen3_5`` with the tower's header nested under ``text_config``): the
+    Qwen3-Next body with a dense gated FFN where Qwen3-Next routes (architectures/qwen38_27b.rs:1-12)."""
+    c = c.get("text_config") or c
+    cfg = _qwen3next(c)
+    cfg.family = "qwen38_27b"
+    return cfg
+
+
 def _bert(c):
     from .encoder import EncoderConfig
     if (c.get("position_embedding_type") or "absolute") != "absolute":
@@ -349,15 +358,15 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("deepseek3", ["deepseek_v3"], ["deepseek2"], _deepseek3),
     FamilyEntry("nemotron_h", ["nemotron_h"], ["nemotron_h"], _nemotron_h),
     FamilyEntry("qwen3next", ["qwen3_next"], ["qwen3next"], _qwen3next),
+    FamilyEntry("qwen38_27b", ["qwen3_5", "qwen3_5_text"], ["qwen35"], _qwen35),
     FamilyEntry("bert", ["bert"], ["bert"], _bert, kind="encoder"),
     # families the reference ships whose mixers are not built here: refused by name
     FamilyEntry("gemma4", ["gemma4"], ["gemma4"], None, "per-layer embeddings, proportional rope"),
     FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], None, "sparse attention indexer"),
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
     FamilyEntry("idefics3", ["idefics3"], [], None, "vision tower"),
-    FamilyEntry("qwen38", ["qwen3_8"], ["qwen38"], None, "gated delta-net mixer"),
-    FamilyEntry("qwen38_27b", ["qwen3_8_27b"], ["qwen38"], None, "gated delta-net mixer"),
-    FamilyEntry("glm53_flash", ["glm5_flash"], ["glm53"], None, "kimi delta attention"),
+    FamilyEntry("qwen38", ["qwen4_exp"], ["qwen4exp"], None, "block-indexed sparse attention, hyper-connection residual streams, n-gram embeddings"),
+    FamilyEntry("glm53_flash", ["glm5_flash"], ["glm53"], None, "kimi delta attention, hyper-connection residual streams"),
     FamilyEntry("qwen_vl", ["qwen2_5_vl"], ["qwen2vl"], None, "vision tower, sectioned mRoPE"),
 ]
 

@@ -100,7 +100,7 @@ def test_supported_family_traces_compiles_and_decodes(name):
 def test_refused_families_say_what_is_missing():
     reg = Registry.builtin()
     for mt, word in (("gemma4", "per-layer embeddings"), ("deepseek_v32", "sparse attention"), ("glm5_flash", "delta attention"),
-                     ("idefics3", "vision"), ("qwen2_5_vl", "vision"), ("qwen3_8", "delta-net")):
+                     ("idefics3", "vision"), ("qwen2_5_vl", "vision"), ("qwen4_exp", "hyper-connection")):
         with pytest.raises(UnsupportedFamily) as e:
             reg.resolve_hf({**BASE, "model_type": mt})
         assert word in str(e.value)
@@ -109,7 +109,7 @@ def test_refused_families_say_what_is_missing():
     with pytest.raises(UnsupportedFamily):
         reg.resolve_hf({"model_type": "mpt", "d_model": 64, "n_heads": 4, "n_layers": 2, "vocab_size": 200,
                         "attn_config": {"alibi": False}})
-    assert len(reg.listed()) == 28 and len(reg.supported()) == 20
+    assert len(reg.listed()) == 28 and len(reg.supported()) == 21
 
 
 def test_device_gaps_name_what_the_device_program_lacks():
@@ -154,3 +154,12 @@ def test_torch_restatement_with_folded_scales_matches_the_oracle(name):
     dw = from_named_tensors(cfg, named, "cpu", dtype=torch.float32)
     got = forward_logits(dw, torch.from_numpy(toks[0]).int(), round_bf16=False).numpy()
     assert np.allclose(got, ref.reshape(got.shape), rtol=2e-4, atol=2e-5), np.abs(got - ref.reshape(got.shape)).max()
+
+
+def test_supported_models_page_is_current():
+    """docs/supported-models.md is generated from the registry; regenerate it with
+    ``python -m poot_b200.models.support_matrix > docs/supported-models.md`` when a family changes."""
+    import os
+    from poot_b200.models.support_matrix import render
+    path = os.path.join(os.path.dirname(__file__), "..", "docs", "supported-models.md")
+    assert open(path).read() == render()

@@ -62,6 +62,8 @@ CASES = {
                       linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4,
                       num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, shared_expert_intermediate_size=48,
                       _tol=1e-4),
+    "qwen3_5": dict(model_type="qwen3_5_text", layer_types=["linear_attention", "full_attention"], linear_num_value_heads=4,
+                    linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4, _tol=1e-4),
 }
 OWN_DIMS = ("mpt", "bloom")      # families whose headers do not use the llama field names
 
