@@ -61,6 +61,7 @@ class StepInputs:
     want_logprobs: bool = False
     live_tokens: int = 0
     live_rows: int = 0
+    adapter_rows: Optional[np.ndarray] = None   # [T] int32 adapter slot of every token row (-1 = none); None = no row uses one
 
 
 @dataclass
@@ -87,6 +88,7 @@ class Sequence_:
     counts: Dict[int, int] = field(default_factory=dict)   # token histogram for the penalties
     guided: Optional[object] = None                        # constraint object with .mask(vocab) / .advance(token)
     seed: int = 0
+    adapter_slot: int = -1                                 # resident LoRA adapter of the sequence (-1 = base model)
 
     @property
     def pending(self) -> int:
@@ -150,8 +152,12 @@ class Driver:
         return bool(self._free_rows) and need <= free + (len(self.prefix) if self.prefix is not None else 0)
 
     def open(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, identity: int = BASE_IDENTITY,
-             guided=None) -> int:
+             guided=None, adapter_slot: int = -1) -> int:
+        """``adapter_slot``: slot of a resident LoRA adapter the sequence runs with (-1 = the base model).  K/V computed
+        under one adapter is not valid under another, so the prefix-cache identity is taken per slot."""
         params = params or SamplingParams()
+        if adapter_slot >= 0 and identity == BASE_IDENTITY:
+            identity = (BASE_IDENTITY ^ (0x9E3779B97F4A7C15 * (adapter_slot + 1))) & 0xFFFFFFFFFFFFFFFF
         params.validate()
         prompt = [int(t) for t in prompt]
         if not prompt:
@@ -183,6 +189,7 @@ class Driver:
         seq = Sequence_(sid, row, prompt, len(prompt), params, matched + fresh, identity,
                         computed=len(matched) * BLOCK, cached_tokens=len(matched) * BLOCK, guided=guided,
                         seed=params.seed if params.seed is not None else (sid * 2654435761) & 0x7FFFFFFF)
+        seq.adapter_slot = int(adapter_slot)
         for t in prompt:
             seq.counts[t] = seq.counts.get(t, 0) + 1
         self.seqs[sid] = seq
@@ -241,8 +248,11 @@ class Driver:
         top_k = np.zeros(Bp, np.int32); seeds = np.zeros(Bp, np.int32)
         rule, off, b = S.GREEDY, 0, 0
         adjust_rows, guided_rows, want_lp = {}, {}, False
+        adapter_rows = np.full(Tp, -1, np.int32) if any(s.adapter_slot >= 0 for s, _ in rows) else None
         for s, piece in rows:
             p0 = s.computed
+            if adapter_rows is not None:
+                adapter_rows[off:off + piece] = s.adapter_slot
             if piece == 1:       # decode row: scalar stores (a numpy slice per row would cost more than the row)
                 tokens[off], positions[off], row_seq[off], row_ctx[off] = s.tokens[p0], p0, s.row, p0 + 1
                 slots[off] = s.blocks[p0 // BLOCK] * BLOCK + p0 % BLOCK
@@ -291,7 +301,7 @@ class Driver:
         check_write_slots(slots[:T])            # two rows writing one K/V slot in a step would race on the device
         self.stats["padded_tokens"] += Tp - T
         return StepInputs(tokens, positions, slots, row_seq, row_ctx, logit_idx, rule, params, top_k, seeds, adjust,
-                          want_lp, T, B)
+                          want_lp, T, B, adapter_rows)
 
     def step(self, seq_ids: Optional[Iterable[int]] = None) -> List[RowResult]:
         rows = self.plan(seq_ids)

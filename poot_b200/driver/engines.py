@@ -120,7 +120,12 @@ class DeviceStepEngine:
                 e.guided_mask[:B].zero_()
                 for r, m in inp.adjust["guided"].items():
                     e.guided_mask[r].copy_(torch.from_numpy(np.ascontiguousarray(m, dtype=np.float32)))
-        shape = StepShape(T, B, inp.sampler, False, inp.adjust is not None, guided, inp.want_logprobs)
+        lora = False
+        if inp.adapter_rows is not None:
+            if e.lora is None:
+                raise RuntimeError("a sequence names an adapter slot but the engine has no adapter bank")
+            lora = e.lora.bind_rows(inp.adapter_rows, T)
+        shape = StepShape(T, B, inp.sampler, False, inp.adjust is not None, guided, inp.want_logprobs, lora)
         import time as _time
         t0 = _time.perf_counter()
         ev = None

@@ -33,6 +33,7 @@ class StepShape:
     adjust: bool = False    # apply the sparse logit adjustments (bias, penalties) before sampling
     guided: bool = False    # also add the dense guided-decoding mask
     logprobs: bool = False  # record the picked token's log-probability
+    lora: bool = False      # some row of the step selects a resident adapter (adds the per-row low-rank terms)
 
 
 class KVPool:
@@ -168,9 +169,25 @@ class DecoderEngine:
         self.scale = float(cfg.attn_scale) if cfg.attn_scale is not None else 1.0 / math.sqrt(D)
         if comm is not None:
             comm.attach(self)
+        self.lora = None                    # bank of resident adapters, created by enable_adapters()
         self._graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.launches_per_step: Dict[Tuple, int] = {}
         self._launch_counter = 0
+
+    def enable_adapters(self, slots: int = 8, max_rank: int = 64):
+        """Create the bank of resident LoRA adapters (per-row selection); see ``runtime/lora_bank.py``."""
+        from .lora_bank import LoraBank, LoraBankError
+        if self.comm is not None or (self.stage is not None and self.stage.count > 1):
+            raise LoraBankError("per-row adapters are built for the single-device engine")
+        if isinstance(self.w.layers[0].wqkv, K.QuantWeight):
+            raise LoraBankError("per-row adapters need bf16 projections")
+        self.lora = LoraBank(self.cfg, len(self.w.layers), slots, max_rank, self.max_tokens, self.device)
+        if getattr(self, "gu", None) is None:
+            ffn_local = self.cfg.ffn // self.tp
+            self.gu = torch.zeros(self.max_tokens, 2 * ffn_local, dtype=torch.bfloat16, device=self.device)
+        if getattr(self, "proj", None) is None:
+            self.proj = torch.zeros(self.max_tokens, self.cfg.hidden, dtype=torch.bfloat16, device=self.device)
+        return self.lora
 
     # ------------------------------------------------------------------ kernel program
     def _count(self, n: int = 1):
@@ -272,12 +289,15 @@ class DecoderEngine:
             if cfg.embed_scale != 1.0:
                 h.mul_(cfg.embed_scale)
         pending = None
+        lora = shape.lora and self.lora is not None
         post = cfg.block != "pre"           # a norm sits between each projection and its residual add
         for l, L in enumerate(w.layers):
             x = h if cfg.block == "post" else self._norm(L.ln1, T, pending)
             qkv = self._linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
             if L.bqkv is not None:
                 qkv.add_(L.bqkv)
+            if lora:
+                self.lora.apply(self, "qkv", l, x, qkv, T)
             qn, kn = L.q_norm, L.k_norm
             if cfg.qk_norm_wide:            # one norm over the whole q / k projection: done here, not per head in the rope kernel
                 self._wide_qk_norm(qkv, L, T)
@@ -288,27 +308,33 @@ class DecoderEngine:
                             cos, sin, self.hq, self.hkv, D, cfg.rot, qn, kn, cfg.norm_eps)
             self._attention(l, T, T, B)
             if post:
-                self._proj_post_norm(self.attn[:T], L.wo, L.post1, T)
+                self._proj_post_norm(self.attn[:T], L.wo, L.post1, T, ("o", l) if lora else None)
             elif self.comm is not None:
                 pending = self.comm.row_parallel(self, self.attn[:T], L.wo, T)
             else:
                 pending = self._proj_to_residual(self.attn[:T], L.wo, T)
+                if lora:
+                    self.lora.apply(self, "o", l, self.attn[:T], h, T)
             x = h if cfg.block == "post" else self._norm(L.ln2, T, pending)
             if cfg.is_moe:
                 pending = self._moe(l, L, x, T)
             else:
-                if cfg.act == "silu":
+                if cfg.act == "silu" and not lora:
                     act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
-                else:                       # GeGLU: plain projection, then the gated activation over adjacent (gate, up) pairs
+                else:                       # plain projection (+ adapter term), then the gated activation over (gate, up) pairs
                     gu = self._linear(x, L.wgu, K.EPI_STORE, self.gu[:T])
+                    if lora:
+                        self.lora.apply(self, "gu", l, x, gu, T)
                     self._count()
                     act = K.gated_act(gu, True, cfg.act, out=self.act[:T])
                 if post:
-                    self._proj_post_norm(act, L.wdown, L.post2, T)
+                    self._proj_post_norm(act, L.wdown, L.post2, T, ("down", l) if lora else None)
                 elif self.comm is not None:
                     pending = self.comm.row_parallel(self, act, L.wdown, T)
                 else:
                     pending = self._proj_to_residual(act, L.wdown, T)
+                    if lora:
+                        self.lora.apply(self, "down", l, act, h, T)
         if pending is not None:
             self._count()
             K.reduce_partials(h, pending, h)
@@ -341,10 +367,12 @@ class DecoderEngine:
             return self.cos_local, self.sin_local
         return self.cos, self.sin
 
-    def _proj_post_norm(self, x, W, norm_w, T: int) -> None:
+    def _proj_post_norm(self, x, W, norm_w, T: int, adapter_site=None) -> None:
         """``h += rmsnorm(x @ W^T) * norm_w`` (post-norm and sandwich blocks): projection, norm, residual add."""
         h, p = self.h[:T], self.proj[:T]
         self._linear(x, W, K.EPI_STORE, p)
+        if adapter_site is not None:
+            self.lora.apply(self, adapter_site[0], adapter_site[1], x, p, T)
         self._count(2)
         K.rmsnorm(p, norm_w, self.cfg.norm_eps, out=p)
         K.add(h, p, out=h)
@@ -520,7 +548,7 @@ class DecoderEngine:
     def _key(self, shape: StepShape):
         flash_only = self.flash_ok and shape.tokens > shape.logit_rows and self._flash_only
         return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain, shape.adjust, shape.guided, shape.logprobs,
-                flash_only)
+                flash_only, shape.lora)
 
     def prepare(self, shape: StepShape) -> None:
         """Warm up and capture the step graph for ``shape`` (never done in the serving path afterwards)."""

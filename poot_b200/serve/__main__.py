@@ -63,6 +63,11 @@ def main(argv=None) -> int:
                        kv_fraction=cfg.kv_fraction, tp_rank=rank if pp == 1 else 0, tp_world=world if pp == 1 else 1,
                        comm=comm, lora=cfg.lora, prefill_budget=cfg.prefill_budget or None,
                        pp_rank=rank if pp > 1 else 0, pp_world=pp)
+    if cfg.lora_slots > 0:
+        if world > 1 or llm.engine is None:
+            print("poot-serve: --lora-slots needs the single-device engine", file=sys.stderr)
+            return 2
+        llm.engine.enable_adapters(cfg.lora_slots, cfg.lora_max_rank)
     if world > 1:
         from .follower import follow, LeaderStepEngine
         if rank != 0:

@@ -41,6 +41,8 @@ class ServeConfig:
     allowed_hosts: List[str] = field(default_factory=list)
     model_id: Optional[str] = None
     lora: Optional[str] = None           # PEFT adapter directory merged into the projections at load
+    lora_slots: int = 0                  # > 0: resident adapters selected per request (POST /v1/lora_adapters, `model` = name)
+    lora_max_rank: int = 64
     backend: str = "b200"                # b200 (the device engine) | oracle (the CPU graph evaluator; every family, slow)
 
     def validate(self) -> None:

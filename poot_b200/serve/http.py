@@ -197,7 +197,9 @@ def make_handler(state: ServerState):
                 if path == "/metrics/prometheus":
                     return self._send(200, eng.metrics.to_prometheus().encode(), "text/plain; version=0.0.4")
                 if path == "/v1/models":
-                    return self._send(200, {"object": "list", "data": [self._model_obj()]})
+                    return self._send(200, {"object": "list", "data": [self._model_obj()] + [
+                        {"id": a["id"], "object": "model", "created": a["created"], "owned_by": "poot-b200", "parent": state.model_id}
+                        for a in state.adapters.values()]})
                 if path.startswith("/v1/models/"):
                     if path[len("/v1/models/"):] != state.model_id:
                         raise ApiError(404, "model not found", "not_found_error")
@@ -217,11 +219,35 @@ def make_handler(state: ServerState):
                     name = self.path[len("/v1/lora_adapters/"):]
                     if name not in state.adapters:
                         raise ApiError(404, "adapter not found", "not_found_error")
+                    if eng.adapter_in_use(state.adapters[name]["slot"]):
+                        raise ApiError(409, f"adapter {name!r} is in use by live requests", "conflict_error")
+                    eng.adapter_call(lambda bank: bank.unload(name))
                     del state.adapters[name]
                     return self._send(200, {"deleted": True, "id": name})
                 raise ApiError(404, "no route", "not_found_error")
             except ApiError as e:
                 self._error(e)
+
+        def _load_adapter(self, req: dict) -> dict:
+            """``POST /v1/lora_adapters {"name": ..., "path": ...}``: make a PEFT adapter resident; requests select it by
+            naming it as their ``model``."""
+            from ..load.lora import LoraError, load_adapter
+            from ..runtime.lora_bank import LoraBankError
+            name, path_ = req.get("name"), req.get("path")
+            if not isinstance(name, str) or not name or not isinstance(path_, str) or not path_:
+                raise ApiError(400, "`name` and `path` are required strings")
+            if name == state.model_id or name in state.adapters:
+                raise ApiError(409, f"the name {name!r} is already served", "conflict_error")
+            try:
+                adapter = load_adapter(path_, name)
+                slot = eng.adapter_call(lambda bank: bank.load(adapter))
+            except LookupError as e:
+                raise ApiError(400, f"adapter {name!r}: {e}") from None
+            except (LoraError, LoraBankError, FileNotFoundError) as e:
+                raise ApiError(400, f"adapter {name!r}: {e}") from None
+            state.adapters[name] = {"id": name, "object": "lora_adapter", "slot": slot, "rank": adapter.rank, "path": path_,
+                                    "created": int(time.time())}
+            return state.adapters[name]
 
         # ---- encoder routes ---------------------------------------------------------------------------------
         def _encoder_call(self, fn):
@@ -297,14 +323,16 @@ def make_handler(state: ServerState):
                     raise ApiError(400, "the served model is an encoder: it embeds and scores, it does not generate")
                 if path == "/v1/lora_adapters":
                     self._admin()
-                    req = self._body()
-                    raise ApiError(400, f"adapter {req.get('name')!r}: LoRA serving is not enabled for this model")
+                    return self._send(200, self._load_adapter(self._body()))
                 if path not in ("/v1/completions", "/v1/chat/completions"):
                     raise ApiError(404, f"no route {path}", "not_found_error")
                 if not state.limiter.allow():
                     raise ApiError(429, "rate limit exceeded", "rate_limit_error", retry_after=60)
                 req = self._body()
-                if req.get("model") not in (None, state.model_id):
+                adapter_slot = -1
+                if req.get("model") in state.adapters:       # a resident adapter is addressed as a model of its own
+                    adapter_slot = state.adapters[req["model"]]["slot"]
+                elif req.get("model") not in (None, state.model_id):
                     raise ApiError(404, f"model {req.get('model')!r} is not served", "not_found_error", "model")
                 n = req.get("n", 1)
                 if isinstance(n, bool) or not isinstance(n, int) or not (1 <= n <= 16):
@@ -319,7 +347,8 @@ def make_handler(state: ServerState):
                         g = None
                         if guided_spec is not None:
                             g = guided_mod.build_constraint(guided_spec, eng.tk, eng.driver.eos_token, tools)
-                        jobs.append(eng.submit(Job(prompt_ids, sp, stream=bool(req.get("stream")), guided=g)))
+                        jobs.append(eng.submit(Job(prompt_ids, sp, stream=bool(req.get("stream")), guided=g,
+                                                   adapter_slot=adapter_slot)))
                 except queue.Full:
                     for j in jobs:
                         j.cancelled.set()

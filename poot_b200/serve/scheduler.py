@@ -29,6 +29,7 @@ class Job:
     params: SamplingParams
     stream: bool = False
     guided: Optional[object] = None
+    adapter_slot: int = -1             # resident LoRA adapter the request selected (-1 = base model)
     id: int = 0
     created: float = field(default_factory=time.monotonic)
     events: "queue.Queue" = field(default_factory=lambda: queue.Queue(maxsize=4096))
@@ -80,6 +81,7 @@ class ServeEngine:
         self.draft = draft                   # draft policy (``propose(tokens)``) used while one greedy sequence is live
         self.timing = timing                 # profile.TimingSnapshot, or None: counters only
         self.busy_s = 0.0
+        self._admin: "queue.Queue" = queue.Queue()
         self.metrics.set("poot_slot_capacity", driver.max_rows)
 
     # ---- submission (any thread) -------------------------------------------------------------------------------
@@ -101,6 +103,39 @@ class ServeEngine:
         self.metrics.inc("poot_requests_total")
         self.inbox.put(job)
         return job
+
+    # ---- resident adapters (admin thread; serialised with the engine thread by the admin queue) -----------------
+    @property
+    def adapter_bank(self):
+        inner = getattr(self.driver.engine, "inner", self.driver.engine)
+        return getattr(getattr(inner, "e", None), "lora", None)
+
+    def adapter_call(self, fn):
+        """Run ``fn(bank)`` on the engine thread between two steps (the bank must not change under a running step)."""
+        if self.adapter_bank is None:
+            raise LookupError("adapter serving is not enabled (start the server with --lora-slots N)")
+        box: "queue.Queue" = queue.Queue(maxsize=1)
+        self._admin.put((fn, box))
+        if self._thread is None or not self._thread.is_alive():       # no engine thread (tests drive iteration() themselves)
+            self._run_admin()
+        ok, val = box.get(timeout=60)
+        if not ok:
+            raise val
+        return val
+
+    def _run_admin(self) -> None:
+        while True:
+            try:
+                fn, box = self._admin.get_nowait()
+            except queue.Empty:
+                return
+            try:
+                box.put((True, fn(self.adapter_bank)))
+            except Exception as e:      # reported to the admin caller, the engine keeps serving
+                box.put((False, e))
+
+    def adapter_in_use(self, slot: int) -> bool:
+        return any(j.adapter_slot == slot for j in list(self.live.values()) + list(self.waiting))
 
     # ---- lifecycle ---------------------------------------------------------------------------------------------
     def start(self) -> None:
@@ -143,6 +178,7 @@ class ServeEngine:
     # ---- one loop iteration ------------------------------------------------------------------------------------
     def iteration(self) -> bool:
         d, m = self.driver, self.metrics
+        self._run_admin()
         while True:                                     # intake
             try:
                 self.waiting.append(self.inbox.get_nowait())
@@ -168,7 +204,7 @@ class ServeEngine:
         while self.waiting and self.state in ("serving", "draining"):   # admit oldest first
             job = self.waiting[0]
             try:
-                sid = d.open(job.prompt_tokens, job.params, guided=job.guided)
+                sid = d.open(job.prompt_tokens, job.params, guided=job.guided, adapter_slot=job.adapter_slot)
             except (NoFreeRow, OutOfBlocks):
                 if not self.live and not d.seqs:        # can never fit
                     self.waiting.pop(0)

@@ -292,3 +292,182 @@ def test_bench_driver_path_runs_on_the_emulated_engine():
         prompts = torch.randint(0, cfg.vocab, (B, P), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
         r = bench.driver_e2e(eng, cfg, B, prompts, 2, 3, max_len, timed)
     assert calls == [3] and r["tok_s"] > 0 and r["ms_per_step"] > 0
+
+
+def make_adapter(cfg, rng, name, r, roles):
+    from poot_b200.load.lora import LoraAdapter
+    d = {}
+    for l in range(cfg.n_layers):
+        for role, (o, i) in roles.items():
+            d[f"layers.{l}.{role}"] = ((rng.standard_normal((r, i)) * 0.2).astype(np.float32),
+                                        (rng.standard_normal((o, r)) * 0.2).astype(np.float32))
+    return LoraAdapter(name, r, 0.5, d)
+
+
+def adapter_roles(cfg):
+    H, F = cfg.hidden, cfg.ffn
+    return {"attn_q": (cfg.q_size, H), "attn_k": (cfg.kv_size, H), "attn_v": (cfg.kv_size, H), "attn_o": (H, cfg.q_size),
+            "ffn_gate": (F, H), "ffn_up": (F, H), "ffn_down": (H, F)}
+
+
+def merged_weights(cfg, w, ad):
+    """Reference: the engine's fused layouts with the adapter's delta merged in."""
+    import copy
+    m = copy.deepcopy(w)
+    q, kv = cfg.q_size, cfg.kv_size
+    for l, L in enumerate(m.layers):
+        p = f"layers.{l}."
+        dl = lambda role: torch.from_numpy(ad.delta(p + role)).to(L.wo.device) if (p + role) in ad.deltas else None
+        wqkv = L.wqkv.float()
+        for role, (a, b) in (("attn_q", (0, q)), ("attn_k", (q, q + kv)), ("attn_v", (q + kv, q + 2 * kv))):
+            if dl(role) is not None:
+                wqkv[a:b] += dl(role)
+        L.wqkv = wqkv.to(torch.bfloat16)
+        if dl("attn_o") is not None:
+            L.wo = (L.wo.float() + dl("attn_o")).to(torch.bfloat16)
+        wgu = L.wgu.float()
+        if dl("ffn_gate") is not None:
+            wgu[0::2] += dl("ffn_gate")
+        if dl("ffn_up") is not None:
+            wgu[1::2] += dl("ffn_up")
+        L.wgu = wgu.to(torch.bfloat16)
+        if dl("ffn_down") is not None:
+            L.wdown = (L.wdown.float() + dl("ffn_down")).to(torch.bfloat16)
+    return m
+
+
+def test_rows_of_one_step_use_different_resident_adapters():
+    """Two sequences in the same steps, one per adapter, a third without any: each row's logits equal the model whose
+    projections carry that adapter's merged delta (prefill and decode through the bank's grouped contractions)."""
+    from poot_b200.oracle.torch_ref import forward_logits
+    cfg = _cfg()
+    rng = np.random.default_rng(0)
+    every = adapter_roles(cfg)
+    ad_a = make_adapter(cfg, rng, "a", 8, every)
+    ad_b = make_adapter(cfg, rng, "b", 4, {"attn_q": every["attn_q"], "attn_v": every["attn_v"], "ffn_down": every["ffn_down"]})
+    merged = lambda w_, ad: merged_weights(cfg, w_, ad)
+
+    with emulated_kernels():
+        w, eng, sess = _engine(cfg, batch=3, max_len=64, max_tokens=96)
+        bank = eng.enable_adapters(slots=4, max_rank=8)
+        sa, sb = bank.load(ad_a), bank.load(ad_b)
+        assert (sa, sb) == (0, 1) and bank.slot_of("b") == 1
+        g = torch.Generator().manual_seed(0)
+        prompts = torch.randint(0, cfg.vocab, (3, 17), generator=g, dtype=torch.int32)
+        slots = [sa, sb, -1]
+        T = 3 * 17
+        assert bank.bind_rows(np.repeat(np.array(slots, np.int32), 17), T)
+        from poot_b200.runtime.engine import StepShape
+        # prefill with adapters: the session binds the inputs, the step shape carries the adapter flag
+        B, L = prompts.shape
+        pos = torch.arange(L, dtype=torch.int32).repeat(B)
+        seq = torch.arange(B, dtype=torch.int32).repeat_interleave(L)
+        sess.h_tokens[:T] = prompts.reshape(-1)
+        sess.h_pos[:T], sess.h_seq[:T] = pos, seq
+        blk = sess.block_tables_host[seq.long(), (pos // 16).long()]
+        sess.h_slots[:T] = blk * 16 + pos % 16
+        sess.h_ctx[:T] = pos + 1
+        sess.h_lidx[:B] = torch.arange(B, dtype=torch.int64) * L + (L - 1)
+        sess.lengths = [L] * B
+        sess._step(StepShape(T, B, 0, lora=True))
+        refs = [merged(w, ad_a), merged(w, ad_b), w]
+        for b in range(3):
+            ref = forward_logits(refs[b], prompts[b])[-1]
+            err = (eng.logits[b] - ref).abs().max().item()
+            assert err < 0.03 * max(1.0, ref.abs().max().item()), ("prefill", b, err)
+        # the adapter matters: row 0 differs from the base model by more than the tolerance
+        base = forward_logits(w, prompts[0])[-1]
+        assert (eng.logits[0] - base).abs().max().item() > 0.1 * base.abs().max().item()
+        # one decode step, one row per sequence
+        nxt = torch.randint(0, cfg.vocab, (3,), generator=g, dtype=torch.int32)
+        bank.bind_rows(np.array(slots, np.int32), 3)
+        sess._bind_decode_inputs(nxt.tolist())
+        sess.len_t = sess.len_t + 1
+        sess._step(StepShape(3, 3, 0, lora=True))
+        for b in range(3):
+            ref = forward_logits(refs[b], torch.cat([prompts[b], nxt[b:b + 1]]))[-1]
+            err = (eng.logits[b] - ref).abs().max().item()
+            assert err < 0.03 * max(1.0, ref.abs().max().item()), ("decode", b, err)
+        bank.unload("a")
+        assert bank.names[:2] == [None, "b"]
+
+
+def test_server_loads_adapters_and_requests_select_them_by_model_name(tmp_path):
+    """HTTP server over the emulated engine: ``POST /v1/lora_adapters`` makes a PEFT directory resident, a request whose
+    ``model`` names it decodes with it (and differs from the base model's answer), the adapter shows up under
+    ``/v1/models``, cannot be deleted twice, and a sequence opened under it does not share prefix-cache blocks with the
+    base model."""
+    import json
+    import urllib.request
+    from poot_b200.driver.driver import Driver
+    from poot_b200.driver.engines import DeviceStepEngine
+    from poot_b200.load import safetensors as st
+    from poot_b200.runtime.engine import DecoderEngine
+    from poot_b200.runtime.weights import random_weights
+    from poot_b200.serve.config import ServeConfig
+    from poot_b200.serve.http import Server, ServerState
+    from poot_b200.serve.metrics import Metrics
+    from poot_b200.serve.scheduler import ServeEngine
+    from poot_b200.tensor import DType
+    from poot_b200.text.codec import ByteTokenizer
+    cfg = _cfg(vocab=300)
+    rng = np.random.default_rng(0)
+    d = tmp_path / "adapter"
+    d.mkdir()
+    (d / "adapter_config.json").write_text(json.dumps({"peft_type": "LORA", "r": 4, "lora_alpha": 16}))
+    tensors = {}
+    for l in range(cfg.n_layers):
+        for mod, (o, i) in (("self_attn.q_proj", (cfg.q_size, cfg.hidden)), ("mlp.down_proj", (cfg.hidden, cfg.ffn))):
+            tensors[f"base_model.model.model.layers.{l}.{mod}.lora_A.weight"] = (DType.F32, (rng.standard_normal((4, i)) * 0.3).astype(np.float32))
+            tensors[f"base_model.model.model.layers.{l}.{mod}.lora_B.weight"] = (DType.F32, (rng.standard_normal((o, 4)) * 0.3).astype(np.float32))
+    st.write_safetensors(str(d / "adapter_model.safetensors"), tensors)
+    key = tmp_path / "key"
+    key.write_text("sesame")
+    with emulated_kernels():
+        w = random_weights(cfg, "cpu", seed=1, std=0.05)
+        eng = DecoderEngine(w, num_blocks=24, max_seqs=2, max_tokens=34, max_blocks_per_seq=8, device="cpu", use_graphs=False)
+        eng.enable_adapters(slots=2, max_rank=8)
+        tk = ByteTokenizer(cfg.vocab)
+        drv = Driver(DeviceStepEngine(eng), 24, 2, 128, cfg.vocab, prefill_chunk=32, eos_token=tk.eos)
+        serve = ServeEngine(drv, tk, Metrics())
+        scfg = ServeConfig(model="tiny", addr="127.0.0.1:0", lora_admin_key_file=str(key))
+        server = Server(ServerState(serve, scfg, "tiny"))
+        serve.start()
+        server.start()
+        try:
+            def call(method, path, body=None, admin=False):
+                req = urllib.request.Request(f"http://127.0.0.1:{server.port}{path}", None if body is None else json.dumps(body).encode(),
+                                             {"Content-Type": "application/json", **({"Authorization": "Bearer sesame"} if admin else {})},
+                                             method=method)
+                try:
+                    with urllib.request.urlopen(req, timeout=60) as r:
+                        return r.status, json.loads(r.read())
+                except urllib.error.HTTPError as e:
+                    return e.code, json.loads(e.read())
+            st_, _ = call("POST", "/v1/lora_adapters", {"name": "tuned", "path": str(d)})
+            assert st_ in (401, 403)                                   # admin key required
+            st_, body = call("POST", "/v1/lora_adapters", {"name": "tuned", "path": str(d)}, admin=True)
+            assert st_ == 200 and body["slot"] == 0 and body["rank"] == 4, body
+            st_, body = call("POST", "/v1/lora_adapters", {"name": "tuned", "path": str(d)}, admin=True)
+            assert st_ == 409
+            st_, models = call("GET", "/v1/models")
+            assert [m["id"] for m in models["data"]] == ["tiny", "tuned"]
+            ask = {"prompt": "the quick brown fox jumps", "max_tokens": 6, "temperature": 0, "ignore_eos": True}
+            st_, base = call("POST", "/v1/completions", {**ask, "model": "tiny"})
+            st_, tuned = call("POST", "/v1/completions", {**ask, "model": "tuned"})
+            st_, base2 = call("POST", "/v1/completions", ask)
+            assert st_ == 200 and base["choices"][0]["text"] == base2["choices"][0]["text"]
+            assert tuned["choices"][0]["text"] != base["choices"][0]["text"]
+            assert base2["usage"].get("prompt_tokens_details", {}).get("cached_tokens", 0) >= 16     # same identity: shared prefix
+            assert tuned["usage"].get("prompt_tokens_details", {}).get("cached_tokens", 0) == 0      # other identity: none
+            st_, _ = call("POST", "/v1/completions", {**ask, "model": "nobody"})
+            assert st_ == 404
+            st_, _ = call("DELETE", "/v1/lora_adapters/tuned", admin=True)
+            assert st_ == 200
+            st_, _ = call("DELETE", "/v1/lora_adapters/tuned", admin=True)
+            assert st_ == 404
+            st_, _ = call("POST", "/v1/completions", {**ask, "model": "tuned"})
+            assert st_ == 404
+        finally:
+            server.shutdown()
+            serve.drain(5)

@@ -170,3 +170,47 @@ def test_family_blocks_match_the_graph_oracle(name):
     K.check_status()
     err = (eng.logits[0].cpu() - ref).abs().max().item()
     assert err < 0.03 * max(1.0, ref.abs().max().item()), (name, err)
+
+
+@pytest.mark.xfail(strict=False, reason="per-row adapters through the grouped GEMM: not yet run on a device")
+def test_rows_with_and_without_a_resident_adapter():
+    """Device twin of the host-emulated adapter check: one decode step of three rows (adapter a, adapter b, none)."""
+    import numpy as np
+    from test_engine_emulated import adapter_roles, make_adapter, merged_weights
+    from poot_b200.oracle.torch_ref import forward_logits
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.runtime.engine import StepShape
+    cfg = _small_cfg()
+    w, eng, sess = _engine(cfg, batch=3, max_len=64, max_tokens=96, use_graphs=False)
+    bank = eng.enable_adapters(slots=4, max_rank=8)
+    rng = np.random.default_rng(0)
+    every = adapter_roles(cfg)
+    ads = [make_adapter(cfg, rng, "a", 8, every), make_adapter(cfg, rng, "b", 4, {"attn_q": every["attn_q"], "ffn_down": every["ffn_down"]})]
+    slots = [bank.load(ads[0]), bank.load(ads[1]), -1]
+    g = torch.Generator().manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab, (3, 17), generator=g, dtype=torch.int32)
+    sess.prefill_fast(prompts)           # base-model prefill only fills positions; the checked step recomputes row by row below
+    refs = [merged_weights(cfg, w, ads[0]), merged_weights(cfg, w, ads[1]), w]
+    # a fresh session so that every row's K/V is computed under its own adapter
+    w2, eng2, s2 = _engine(cfg, batch=3, max_len=64, max_tokens=96, use_graphs=False)
+    bank2 = eng2.enable_adapters(slots=4, max_rank=8)
+    for a in ads:
+        bank2.load(a)
+    T = 3 * 17
+    bank2.bind_rows(np.repeat(np.array(slots, np.int32), 17), T)
+    B, L = prompts.shape
+    pos = torch.arange(L, dtype=torch.int32).repeat(B)
+    seq = torch.arange(B, dtype=torch.int32).repeat_interleave(L)
+    s2.h_tokens[:T] = prompts.reshape(-1)
+    s2.h_pos[:T], s2.h_seq[:T] = pos, seq
+    blk = s2.block_tables_host[seq.long(), (pos // 16).long()]
+    s2.h_slots[:T] = blk * 16 + pos % 16
+    s2.h_ctx[:T] = pos + 1
+    s2.h_lidx[:B] = torch.arange(B, dtype=torch.int64) * L + (L - 1)
+    s2.lengths = [L] * B
+    s2._step(StepShape(T, B, 0, lora=True))
+    K.check_status()
+    for b in range(3):
+        ref = forward_logits(refs[b], prompts[b].cuda())[-1]
+        err = (eng2.logits[b] - ref).abs().max().item()
+        assert err < 0.05 * max(1.0, ref.abs().max().item()), (b, err)
