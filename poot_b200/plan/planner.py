@@ -176,7 +176,79 @@ def plan_graph(g: Graph, world: int = 1) -> List[Plan]:
             rows, d = o.shape[-2], o.shape[-1]
             if rows >= 16 and d == 128 and not e.attrs.get("softcap"):
                 plans[k] = Plan("dispatch", ["poot_attn_flash_prefill"], plans[k].note)
+    _absorb_routed_experts(g, plans, users, prod)
     return plans
+
+
+def _absorb_routed_experts(g: Graph, plans: List[Plan], users, prod) -> None:
+    """A routed-experts block is five launches on the device: the router GEMM, ``moe_route`` (canonical scores, stable
+    top-k, gates, the dense gate matrix), two grouped expert GEMMs (the activation is the first one's epilogue, the
+    gate scaling the second one's) and ``moe_combine`` (which also adds into the residual stream).  Everything between
+    the router logits and the weighted sum - score canonicalisation, ranks, masks, the softmax over the selected
+    logits, gate gathers, the row broadcast, the activation - is evaluated inside those kernels, so those equations
+    are ``none`` here.  Literal broadcasts shared by the blocks of several layers are absorbed once every user of
+    theirs is inside some block."""
+    blocks = []
+    for k, e in enumerate(g.eqns):
+        if e.op != "arg_top_k":
+            continue
+        # forward slice from the selected ids up to the weighted sum over the k slots
+        region, frontier, end = set(), [k], None
+        while frontier:
+            i = frontier.pop()
+            for v in g.eqns[i].outputs:
+                for u in users.get(v, []):
+                    if u in region:
+                        continue
+                    region.add(u)
+                    ue = g.eqns[u]
+                    if ue.op == "reduce" and any(g.eqns[prod[x]].op == "transpose" for x in ue.inputs if x in prod) and \
+                            any(r in region and g.eqns[r].op == "indexed_matmul" for r in range(u)):
+                        end = u if end is None else min(end, u)
+                        continue
+                    frontier.append(u)
+        if end is None:
+            continue
+        region = {i for i in region if i <= end}
+        anc, frontier = set(), [end, k] + sorted(region)
+        while frontier:                                  # every ancestor up to the router GEMM / the block's input
+            i = frontier.pop()
+            for v in g.eqns[i].inputs:
+                j = prod.get(v)
+                if j is None or j in anc or j in region:
+                    continue
+                if g.eqns[j].op in CONTRACTIONS or g.eqns[j].op in ("matmul", "fused_row", "attention", "add"):
+                    continue
+                anc.add(j)
+                frontier.append(j)
+        blocks.append((k, end, region, anc))
+    if not blocks:
+        return
+    fixed = set().union(*[r | {end, k} for k, end, r, _ in blocks])
+    back = set().union(*[a for _, _, _, a in blocks]) - fixed
+    changed = True
+    while changed:                                       # keep the ancestors whose every use stays inside some block
+        changed = False
+        inside = fixed | back
+        for j in list(back):
+            if not all(u in inside for o in g.eqns[j].outputs for u in users.get(o, [])):
+                back.discard(j)
+                changed = True
+    for k, end, region, anc in blocks:
+        grouped = 0
+        for i in sorted(region | (anc & back)):
+            op = g.eqns[i].op
+            if i == end:
+                plans[i] = Plan("dispatch", ["poot_moe_combine"], "sum of the gate-scaled expert outputs into the residual stream")
+            elif op == "indexed_matmul":
+                grouped += 1
+                note = "SwiGLU in the epilogue" if grouped == 1 else "gate scaling in the epilogue"
+                plans[i] = Plan("dispatch", ["poot_gemm_skinny_grouped"], note)
+            elif i != k:
+                plans[i] = Plan("none", note=f"evaluated inside the routed-experts kernels (route of eqn {k})")
+        for u in users.get(g.eqns[end].outputs[0], []):  # the residual add is moe_combine's accumulate
+            if g.eqns[u].op == "add" or g.eqns[u].attrs.get("region") == "residual_add":
+                plans[u] = Plan("none", note="the combine kernel adds into the residual stream")
 
 
 def launch_census(plans: List[Plan]) -> Dict[str, int]:

@@ -471,3 +471,20 @@ def test_server_loads_adapters_and_requests_select_them_by_model_name(tmp_path):
         finally:
             server.shutdown()
             serve.drain(5)
+
+
+@pytest.mark.parametrize("kw", [{}, dict(n_experts=4, top_k=2, moe_ffn=128)], ids=["dense", "moe"])
+def test_planner_launch_census_equals_the_engine_launch_count(kw):
+    """The planner's dispatch count for a decode step equals what the engine launches for it (the engine adds the
+    two-stage greedy pick, which the traced graph exports logits for instead)."""
+    from poot_b200.models.model import Model, StepSpec
+    from poot_b200.plan import compile_graph
+    from poot_b200.runtime.engine import StepShape
+    cfg = _cfg(**kw)
+    prog = compile_graph(Model(cfg).trace(StepSpec(rows=2, tokens=1, capacity=64)))
+    with emulated_kernels():
+        _, eng, sess = _engine(cfg, 2, 64, 32)
+        sess.prefill_fast(torch.randint(0, cfg.vocab, (2, 9), generator=torch.Generator().manual_seed(0), dtype=torch.int32))
+        sess.decode([1, 2])
+        launched = eng.launches_per_step[eng._key(StepShape(2, 2, 0))]
+    assert launched - 2 == prog.dispatches, (launched, prog.census)
