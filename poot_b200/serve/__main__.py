@@ -78,7 +78,25 @@ def main(argv=None) -> int:
     if cfg.chat_template_file:
         with open(cfg.chat_template_file) as f:
             template = f.read()
+    from ..driver.features import Feature as _F, check as _check
+    if cfg.draft_mtp:
+        _check([_F.DRAFT_MTP])           # typed refusal: no registered family ships multi-token-prediction heads
+    if cfg.expert_pool:
+        _check([_F.EXPERT_POOL])         # typed refusal: experts stay resident in HBM
+    if cfg.check_ranges and llm.cfg is not None:
+        _prove_ranges(llm.cfg, cfg)
     draft = None
+    if cfg.draft_model:
+        from ..driver.placement import Placement
+        from ..driver.speculate import ModelDraft
+        _check([_F.DRAFT_MODEL, *Placement.parse(cfg.placement).features])
+        path, _, k = cfg.draft_model.rpartition(":")
+        small = (LLM.oracle(path, rows=1, max_seq=cfg.max_seq) if cfg.backend == "oracle" else
+                 LLM.load(path, rows=1, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, kv_fraction=0.05))
+        if small.cfg.vocab != llm.cfg.vocab:
+            print("poot-serve: the draft model's vocabulary differs from the served model's", file=sys.stderr)
+            return 2
+        draft = ModelDraft(small.driver, int(k))
     if cfg.draft_lookup:
         from ..driver.features import Feature, check
         from ..driver.placement import Placement
@@ -91,7 +109,9 @@ def main(argv=None) -> int:
         from ..driver.placement import Placement
         from ..profile import TimingOptions, TimingSnapshot
         check([Feature.DEVICE_TIMING, *Placement.parse(cfg.placement).features])     # refused over a device group
-        timing = TimingSnapshot(TimingOptions("detailed", max_steps=cfg.timing_max_steps))
+        timing = TimingSnapshot(TimingOptions("detailed", max_steps=cfg.timing_max_steps,
+                                              max_dispatch_records=cfg.timing_max_dispatch_records,
+                                              sample_every=cfg.timing_sample_every))
         if hasattr(llm.driver.engine, "device_timing"):
             llm.driver.engine.device_timing = True
     engine = ServeEngine(llm.driver, llm.tokenizer, Metrics(), cfg.max_pending_requests, cfg.max_queue_wait_secs,
@@ -115,6 +135,18 @@ def main(argv=None) -> int:
         _leave(llm)
     llm.close()
     return 0
+
+
+def _prove_ranges(model_cfg, cfg) -> None:
+    """``--check-ranges``: trace the decode and prefill step graphs and prove every index (token ids, positions, slot
+    maps, expert ids) inside its extent before the server accepts a request; an unproven index stops startup."""
+    from ..ir.analysis import index_guards
+    from ..models.model import Model, StepSpec
+    for tokens in (1, min(cfg.prefill_chunk, 64)):
+        g = Model(model_cfg).trace(StepSpec(rows=1, tokens=tokens, capacity=64))
+        bad = [x for x in index_guards(g) if not x.proven]
+        if bad:
+            raise SystemExit(f"poot-serve: --check-ranges: {len(bad)} index uses are not proven in range, first: {bad[0]}")
 
 
 def _is_encoder_checkpoint(path: str) -> bool:

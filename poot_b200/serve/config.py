@@ -23,6 +23,10 @@ class ServeConfig:
     chat_template: Optional[str] = None
     chat_template_file: Optional[str] = None
     draft_lookup: Optional[str] = None   # NGRAM:K
+    draft_model: Optional[str] = None    # PATH:K - a smaller checkpoint proposes K tokens per verify step
+    draft_mtp: int = 0                   # K tokens from the checkpoint's own multi-token-prediction heads (refused: no family ships them)
+    expert_pool: int = 0                 # resident expert rows of a host-paged expert pool (refused: experts stay resident)
+    check_ranges: bool = False           # prove every index of the step graphs in range before serving
     rate_limit_rpm: int = 0
     lora_admin_key_file: Optional[str] = None
     max_connections: int = 4096
@@ -36,6 +40,9 @@ class ServeConfig:
     drain_timeout_secs: float = 30.0
     device_timing: bool = False
     timing_max_steps: int = 4096
+    timing_max_dispatch_records: int = 65536
+    timing_max_in_flight_queries: int = 64
+    timing_sample_every: int = 1
     prefix_cache: bool = True
     kv_fraction: float = 0.85            # share of free device memory given to the KV pool
     allowed_hosts: List[str] = field(default_factory=list)
@@ -53,6 +60,15 @@ class ServeConfig:
         bound("rows", 1, 1024); bound("max_seq", 128, 1 << 20); bound("prefill_chunk", 16, 8192)
         bound("max_pending_requests", 1, 1 << 16); bound("max_body_mib", 1, 1024); bound("kv_fraction", 0.05, 0.98)
         bound("max_queue_wait_secs", 0.1, 3600); bound("drain_timeout_secs", 0, 3600)
+        bound("timing_max_steps", 1, 1 << 24); bound("timing_max_dispatch_records", 1, 1 << 28)
+        bound("timing_max_in_flight_queries", 1, 1 << 16); bound("timing_sample_every", 1, 1 << 20)
+        bound("draft_mtp", 0, 16); bound("expert_pool", 0, 1 << 16)
+        if sum(x is not None and x != 0 for x in (self.draft_lookup, self.draft_model, self.draft_mtp or None)) > 1:
+            raise ValueError("one draft policy: --draft-lookup, --draft-model or --draft-mtp")
+        if self.draft_model is not None:
+            path, sep, k = self.draft_model.rpartition(":")
+            if not sep or not path or not k.isdigit() or not (1 <= int(k) <= 16):
+                raise ValueError(f"--draft-model {self.draft_model!r}: expected PATH:K with K in [1, 16]")
         if self.kv_dtype not in ("bf16", "f16", "f32"):
             raise ValueError(f"--kv-dtype {self.kv_dtype!r}: expected bf16, f16 or f32")
         if self.matmul_precision not in ("exact", "narrow", "split"):

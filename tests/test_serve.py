@@ -317,3 +317,25 @@ def test_timing_snapshot_is_exposed_and_null_when_unmeasured():
     with pytest.raises(Exception):
         from poot_b200.driver.features import Feature, check
         check([Feature.DEVICE_TIMING, Feature.TENSOR_PLACEMENT])
+
+
+def test_flags_for_draft_policies_pools_and_range_checks():
+    from poot_b200.driver.features import Feature, Unavailable, check
+    from poot_b200.models.config import mixtral_8x7b, tiny_llama
+    from poot_b200.serve.__main__ import _prove_ranges
+    cfg = parse_args(["m", "--draft-model", "/models/small:4", "--check-ranges", "--timing-sample-every", "2",
+                      "--timing-max-dispatch-records", "1000"])
+    assert cfg.draft_model == "/models/small:4" and cfg.check_ranges and cfg.timing_sample_every == 2
+    for bad in (["m", "--draft-model", "no-count"], ["m", "--draft-model", "p:4", "--draft-lookup", "3:4"], ["m", "--draft-mtp", "99"],
+                ["m", "--timing-sample-every", "0"]):
+        with pytest.raises(ValueError):
+            parse_args(bad)
+    for f in (Feature.DRAFT_MTP, Feature.EXPERT_POOL):           # accepted by the parser, refused typed at startup
+        with pytest.raises(Unavailable):
+            check([f])
+    c = tiny_llama()
+    c.n_layers = 1
+    _prove_ranges(c, cfg)
+    m = mixtral_8x7b()
+    m.n_layers, m.hidden, m.moe_ffn, m.ffn, m.n_heads, m.n_kv_heads, m.head_dim, m.vocab = 1, 128, 64, 64, 2, 1, 64, 512
+    _prove_ranges(m, cfg)                                        # expert ids are proven in range too
