@@ -54,6 +54,14 @@ TABLE: List[Tuple[Feature, Feature, str]] = [
     (F.DRAFT_MODEL, F.GUIDED, "a constraint mask is computed one token ahead, not for k drafted positions"),
     (F.BEAM, F.GUIDED, "beams would each need a clone of the constraint state"),
     (F.PACKED_WEIGHTS, F.EXPERT_PLACEMENT, "packed expert weights have no fused grouped kernel"),
+    (F.RECURRENT_STATE, F.PREFIX_CACHE, "a prefix hit skips tokens; the recurrent state after them is not in the K/V cache"),
+    (F.RECURRENT_STATE, F.DRAFT_LOOKUP, "a rejected draft would need the recurrent state rolled back; state snapshots are not built"),
+    (F.RECURRENT_STATE, F.DRAFT_MODEL, "a rejected draft would need the recurrent state rolled back; state snapshots are not built"),
+    (F.RECURRENT_STATE, F.BEAM, "a fork would need a copy of the recurrent state; only K/V blocks are copied"),
+    (F.RECURRENT_STATE, F.TENSOR_PLACEMENT, "recurrent mixers run on the host evaluator, in one process"),
+    (F.ADAPTERS, F.TENSOR_PLACEMENT, "the adapter bank is built for the single-device engine"),
+    (F.ADAPTERS, F.EXPERT_PLACEMENT, "the adapter bank is built for the single-device engine"),
+    (F.ADAPTERS, F.PIPELINE_PLACEMENT, "the adapter bank is built for the single-device engine"),
     (F.PIPELINE_PLACEMENT, F.TENSOR_PLACEMENT, "one placement per model: stages are not themselves tensor-parallel groups"),
     (F.PIPELINE_PLACEMENT, F.EXPERT_PLACEMENT, "one placement per model: stages are not themselves expert-parallel groups"),
     (F.PIPELINE_PLACEMENT, F.DEVICE_TIMING, "per-launch device spans are recorded on one device"),
@@ -62,7 +70,6 @@ TABLE: List[Tuple[Feature, Feature, str]] = [
 ]
 UNAVAILABLE = {
     F.DRAFT_MTP: "no registered family ships multi-token-prediction heads",
-    F.RECURRENT_STATE: "no recurrent (SSM / linear-attention) family is registered",
     F.EXPERT_POOL: "all experts stay resident in 180 GB of HBM; there is no host-side expert pool",
 }
 

@@ -148,6 +148,8 @@ class LLM:
         eos = getattr(tokenizer, "eos", None)
         # a prefix hit skips tokens; a recurrent layer's state after those tokens is not in the K/V cache, so recurrent
         # families run without the prefix cache (the reference snapshots recurrent state instead)
+        from .driver.features import Feature, check
+        check([Feature.RECURRENT_STATE] if cfg.is_recurrent else [])
         drv = Driver(eng, num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
                      prefix_caching=not cfg.is_recurrent, eos_token=eos if eos is not None else cfg.eos_token,
                      prefill_budget=step_prefill)

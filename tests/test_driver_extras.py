@@ -19,7 +19,13 @@ def test_feature_table():
     assert "vocabulary" in str(e.value)
     with pytest.raises(Incompatible):
         check([Feature.DRAFT_LOOKUP, Feature.GUIDED])
-    for f in (Feature.DRAFT_MTP, Feature.RECURRENT_STATE, Feature.EXPERT_POOL):
+    check([Feature.RECURRENT_STATE, Feature.GUIDED, Feature.LOGPROBS])       # recurrent families serve; what they exclude is typed
+    for other in (Feature.PREFIX_CACHE, Feature.DRAFT_LOOKUP, Feature.BEAM):
+        with pytest.raises(Incompatible):
+            check([Feature.RECURRENT_STATE, other])
+    with pytest.raises(Incompatible):
+        check([Feature.ADAPTERS, Feature.TENSOR_PLACEMENT])
+    for f in (Feature.DRAFT_MTP, Feature.EXPERT_POOL):
         with pytest.raises(Unavailable):
             check([f])
 
