@@ -160,6 +160,11 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
     import torch
     from ..runtime.weights import DecoderWeights, LayerWeights
     c, canon = handle.cfg, handle.canonical
+    if c.layer_kinds is not None or c.attn_gate or c.qk_norm_wide or c.router_select_bias:
+        # hybrid stacks and the less common layer variants go through the canonical-name builder (dense bf16)
+        from ..runtime.weights import from_named_tensors
+        named = {n: torch.from_numpy(np.ascontiguousarray(w.to_f32())) for n, w in canon.items()}
+        return from_named_tensors(c, named, device, tp_rank, tp_world, stage=stage)
     D = c.head_dim
     hq, hkv = c.n_heads // tp_world, max(c.n_kv_heads // tp_world, 1)
     k0 = tp_rank * hkv if c.n_kv_heads >= tp_world else tp_rank * c.n_kv_heads // tp_world

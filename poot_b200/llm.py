@@ -74,6 +74,10 @@ class LLM:
                             use_graphs=link is None and dev.type == "cuda")
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
         eos = getattr(tokenizer, "eos", None)
+        if cfg.is_recurrent:
+            from .driver.features import Feature, check
+            check([Feature.RECURRENT_STATE] + ([Feature.TENSOR_PLACEMENT] if comm is not None else []))
+            prefix_caching = False         # a prefix hit skips tokens whose recurrent state is not cached
         drv = Driver(DeviceStepEngine(eng), num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
                      prefix_caching=prefix_caching, eos_token=eos if eos is not None else cfg.eos_token,
                      prefill_budget=step_prefill)

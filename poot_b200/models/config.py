@@ -164,7 +164,8 @@ class DecoderConfig:
     def plain_block(self) -> bool:
         """The pre-norm SwiGLU rope layer the fused tensor-parallel programs are written for."""
         return (self.block == "pre" and self.act == "silu" and not self.qk_norm_wide and self.rope_theta_local is None
-                and (self.rope_layers is None or all(self.rope_layers)) and self.final_softcap == 0)
+                and (self.rope_layers is None or all(self.rope_layers)) and self.final_softcap == 0
+                and self.layer_kinds is None and not self.attn_gate)
 
     def device_gaps(self) -> list:
         """Features of this configuration that the device program does not implement (empty = runs on the device);
@@ -184,9 +185,10 @@ class DecoderConfig:
         if self.shared_width or self.first_dense_layers or self.dense_layers: g.append("shared experts / dense layers in a routed model")
         if self.is_moe and self.top_k > 8: g.append("more than 8 experts per token")
         if self.is_mla: g.append("multi-head latent attention")
-        if self.is_recurrent: g.append("recurrent mixers (Mamba2 / gated delta net scans)")
-        if self.layer_kinds is not None and not self.is_recurrent or self.layer_ffn is not None: g.append("single-mixer blocks")
-        if self.attn_gate or self.shared_expert_gate: g.append("gated attention output / gated shared expert")
+        if self.layer_kinds is not None and any(k == "mamba" for k in self.layer_kinds): g.append("Mamba2 mixer")
+        if self.layer_kinds is not None and any(k == "none" for k in self.layer_kinds) or self.layer_ffn is not None: g.append("single-mixer blocks")
+        if self.shared_expert_gate: g.append("gated shared expert")
+        if self.gdn_k_heads and self.gdn_head_dim not in (64, 128): g.append(f"delta-net head width {self.gdn_head_dim}")
         if self.head_dim not in (64, 128): g.append(f"head_dim {self.head_dim}")
         return g
 

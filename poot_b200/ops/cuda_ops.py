@@ -24,6 +24,10 @@ _SIGS = {
     "poot_swiglu": [_P, _P, c_int, c_int, c_int, _P],
     "poot_gated_act": [_P, _P, c_int, c_int, c_int, c_int, _P],
     "poot_softcap_f32": [_P, c_longlong, c_float, _P],
+    "poot_causal_conv_silu": [_P, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, c_int, _P, _P],
+    "poot_gdn_scan": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
+    "poot_gated_rmsnorm": [_P, _P, c_int, c_int, _P, c_float, _P, c_int, c_int, c_int, _P],
+    "poot_sigmoid_mul": [_P, _P, c_longlong, _P],
     "poot_add_bf16": [_P, _P, _P, c_longlong, _P],
     "poot_reduce_partials": [_P, _P, c_int, c_longlong, _P, c_longlong, _P],
     "poot_cast_f32_bf16": [_P, _P, c_longlong, _P],
@@ -417,6 +421,71 @@ def flash_tiles(row_seq, positions, min_tokens: int = FLASH_MIN_TOKENS):
         for t0 in range(a, b, 128):
             tiles.append((t0, min(128, b - t0), int(seq[a]), int(pos[a]) + (t0 - a)))
     return np.asarray(tiles, dtype=np.int32).reshape(-1, 4), covered
+
+
+def step_segments(row_seq, positions, row_ctx):
+    """The sequence pieces of a step: maximal runs of live rows (context > 0) of one sequence at consecutive positions,
+    as ``[n, 4]`` int32 ``(first row, rows, block-table row, first position)``."""
+    import numpy as np
+    seq = np.asarray(row_seq, dtype=np.int64)
+    pos = np.asarray(positions, dtype=np.int64)
+    live = np.asarray(row_ctx) > 0
+    out, t, T = [], 0, seq.shape[0]
+    while t < T:
+        if not live[t]:
+            t += 1
+            continue
+        e = t + 1
+        while e < T and live[e] and seq[e] == seq[t] and pos[e] == pos[e - 1] + 1:
+            e += 1
+        out.append((t, e - t, int(seq[t]), int(pos[t])))
+        t = e
+    return np.asarray(out, dtype=np.int32).reshape(-1, 4)
+
+
+def causal_conv_silu(x: torch.Tensor, col0: int, C: int, w: torch.Tensor, state: torch.Tensor, segs: torch.Tensor,
+                     out: torch.Tensor) -> torch.Tensor:
+    """Depthwise causal convolution + SiLU over columns ``[col0, col0 + C)`` of ``x[T, ld]`` (bf16), per sequence piece
+    of ``segs``, continuing from and updating ``state[rows, K-1, C]`` (fp32; a piece at position 0 starts from zeros)."""
+    _need_cuda(x, state)
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.dtype == torch.float32 and w.is_contiguous()
+    assert state.dtype == torch.float32 and state.is_contiguous() and segs.dtype == torch.int32 and out.is_contiguous()
+    Kc = w.shape[1]
+    check(_fn("poot_causal_conv_silu")(_ptr(x), x.stride(0), col0, C, Kc, _ptr(w), _ptr(state), state.shape[0], _ptr(segs),
+                                       segs.shape[0], _ptr(out), _stream()), "causal_conv_silu")
+    return out
+
+
+def gdn_scan(qkv: torch.Tensor, ba: torch.Tensor, b_col: int, a_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             state: torch.Tensor, segs: torch.Tensor, out: torch.Tensor, nk: int, nv: int, D: int) -> torch.Tensor:
+    """Gated delta rule over each sequence piece (crates/poot-graph-ir/src/ops/ssm.rs).  ``qkv[T, (2 nk + nv) D]`` holds
+    q | k | v after the convolution; ``ba[T, ld]`` holds the raw b and a projections at columns ``b_col`` / ``a_col``;
+    q and k are normalised to unit length, q scaled by ``D^-1/2``, ``g = -exp(a_log) softplus(a + dt_bias)``,
+    ``beta = sigmoid(b)``; ``state[rows, nv, D, D]`` fp32 is read (unless the piece starts at position 0) and updated."""
+    _need_cuda(qkv, state)
+    assert qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and ba.dtype == torch.bfloat16 and ba.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous() and out.is_contiguous() and D in (64, 128)
+    check(_fn("poot_gdn_scan")(_ptr(qkv), _ptr(ba), ba.stride(0), b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state),
+                               state.shape[0], _ptr(segs), segs.shape[0], _ptr(out), nk, nv, D, _stream()), "gdn_scan")
+    return out
+
+
+def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, z_col: int, w: torch.Tensor, eps: float, out: torch.Tensor,
+                  heads: int, D: int) -> torch.Tensor:
+    """``out = rmsnorm_D(y) * w * silu(z)`` per head; ``z`` is read at columns ``[z_col, z_col + heads * D)`` of its rows."""
+    _need_cuda(y, z)
+    assert y.dtype == torch.bfloat16 and y.is_contiguous() and z.stride(1) == 1 and w.dtype == torch.bfloat16
+    check(_fn("poot_gated_rmsnorm")(_ptr(y), _ptr(z), z.stride(0), z_col, _ptr(w), float(eps), _ptr(out), y.shape[0], heads, D,
+                                    _stream()), "gated_rmsnorm")
+    return out
+
+
+def sigmoid_mul(a: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """``a *= sigmoid(g)`` elementwise (bf16, same shape)."""
+    _need_cuda(a, g)
+    assert a.dtype == torch.bfloat16 and a.is_contiguous() and g.is_contiguous() and a.shape == g.shape
+    check(_fn("poot_sigmoid_mul")(_ptr(a), _ptr(g), a.numel(), _stream()), "sigmoid_mul")
+    return a
 
 
 def attn_flash_prefill(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_tables: torch.Tensor,

@@ -85,7 +85,8 @@ class DecoderEngine:
         self.max_seqs, self.max_tokens, self.max_blocks = max_seqs, max_tokens, max_blocks_per_seq
         self.use_graphs = use_graphs
         self.tp_mode = "auto"   # "auto": one-shot all-reduce for small steps, reduce-scatter/all-gather above; "rs_ag"
-        self.kv = KVPool(cfg, num_blocks, self.device, self.tp, n_layers=len(weights.layers))
+        self.kv = KVPool(cfg, num_blocks, self.device, self.tp,
+                         n_layers=sum(1 for i in range(len(weights.layers)) if cfg.mixer_of(weights.layer0 + i) == "attention") or 1)
         dev, i32 = self.device, torch.int32
         if comm is not None and getattr(comm, "fused", False):
             max_tokens = max(max_tokens, 128)  # padded rows of the fused tensor-parallel path
@@ -156,6 +157,24 @@ class DecoderEngine:
             self.cos_local, self.sin_local = c2.to(dev), s2.to(dev)
         if cfg.rope_layers is not None and not all(cfg.rope_layers):   # layers without a position signal: the identity rotation
             self.cos_none, self.sin_none = torch.ones_like(self.cos), torch.zeros_like(self.sin)
+        # attention layers own K/V pool entries; recurrent layers own state entries
+        kinds = [cfg.mixer_of(weights.layer0 + i) for i in range(len(weights.layers))]
+        self._kv_of = {i: n for n, i in enumerate(i for i, k in enumerate(kinds) if k == "attention")}
+        self._gdn_of = {i: n for n, i in enumerate(i for i, k in enumerate(kinds) if k == "gdn")}
+        if self._gdn_of:
+            nk, nv, Dg, Kc = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.gdn_conv
+            C = (2 * nk + nv) * Dg
+            self.gdn_C, self.gdn_N = C, C + nv * Dg + 2 * nv
+            self.gdn_in = torch.zeros(T, self.gdn_N, dtype=bf, device=dev)
+            self.gdn_conv_out = torch.zeros(T, C, dtype=bf, device=dev)
+            self.gdn_y = torch.zeros(T, nv * Dg, dtype=bf, device=dev)
+            self.gdn_conv_state = torch.zeros(len(self._gdn_of), max_seqs, Kc - 1, C, dtype=torch.float32, device=dev)
+            self.gdn_state = torch.zeros(len(self._gdn_of), max_seqs, nv, Dg, Dg, dtype=torch.float32, device=dev)
+            # one segment per sequence piece of the step: (first row, rows, sequence row, first position); zero rows = unused
+            self.seg_table = torch.zeros(max_seqs, 4, dtype=i32, device=dev)
+            self._h_segs = torch.zeros(max_seqs, 4, dtype=i32, pin_memory=torch.cuda.is_available())
+        if cfg.attn_gate:
+            self.gate = torch.zeros(T, self.hq * D, dtype=bf, device=dev)
         if not cfg.plain_block:
             if comm is not None:
                 from .weights import UnsupportedOnDevice
@@ -241,12 +260,12 @@ class DecoderEngine:
         if count:
             self._count(((2 if splits > 1 else 1) if simt else 0) + (1 if flash else 0))
         if simt:
-            K.attn_paged(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables, self.row_seq[:R],
+            K.attn_paged(self.q[:R], self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables, self.row_seq[:R],
                          (self.row_ctx_simt if flash else self.row_ctx)[:R], self.hq, self.hkv, D, self.scale,
                          out=self.attn[:R], splits=splits, scratch=self.attn_scratch, softcap=cfg.attn_softcap,
                          window=cfg.window_of(self.w.layer0 + l))
         if flash:
-            K.attn_flash_prefill(self.q[:R], self.kv.k(l), self.kv.v(l), self.block_tables,
+            K.attn_flash_prefill(self.q[:R], self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables,
                                  self.attn_tiles[:self._tile_slots(T, B)], self.hq, self.hkv, self.scale,
                                  out=self.attn[:R], window=cfg.window_of(self.w.layer0 + l))
 
@@ -293,6 +312,12 @@ class DecoderEngine:
         post = cfg.block != "pre"           # a norm sits between each projection and its residual add
         for l, L in enumerate(w.layers):
             x = h if cfg.block == "post" else self._norm(L.ln1, T, pending)
+            if L.kind == "gdn":
+                pending = self._gdn_mixer(l, L, x, T)
+                x = self._norm(L.ln2, T, pending)
+                act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
+                pending = self._proj_to_residual(act, L.wdown, T)
+                continue
             qkv = self._linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
             if L.bqkv is not None:
                 qkv.add_(L.bqkv)
@@ -304,9 +329,14 @@ class DecoderEngine:
                 qn = kn = None
             cos, sin = self._rope_tables_of(w.layer0 + l)
             self._count()
-            K.rope_kv_write(qkv, self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
+            kvl = self._kv_of[l]
+            K.rope_kv_write(qkv, self.q[:T], self.kv.k(kvl), self.kv.v(kvl), self.positions[:T], self.slots[:T],
                             cos, sin, self.hq, self.hkv, D, cfg.rot, qn, kn, cfg.norm_eps)
             self._attention(l, T, T, B)
+            if L.wgate is not None:             # gated attention: the output is scaled by sigmoid of a projection of the layer input
+                gate = self._linear(x, L.wgate, K.EPI_STORE, self.gate[:T])
+                self._count()
+                K.sigmoid_mul(self.attn[:T], gate)
             if post:
                 self._proj_post_norm(self.attn[:T], L.wo, L.post1, T, ("o", l) if lora else None)
             elif self.comm is not None:
@@ -358,6 +388,21 @@ class DecoderEngine:
         self._sample(shape, self.logits_local[:B])
         if staged:
             self.link.return_picked(self.picked[:B], self.logprobs[:B] if shape.logprobs else None)
+
+    def _gdn_mixer(self, l: int, L, x, T: int):
+        """Gated delta net layer (components/gdn.rs): one GEMM for q | k | v | z | b | a, causal conv + SiLU over
+        (q | k | v) continuing each sequence's conv window, the gated delta rule over each sequence's state matrices,
+        RMSNorm gated by SiLU(z), out-projection into the residual stream."""
+        cfg, gi = self.cfg, self._gdn_of[l]
+        nk, nv, Dg = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim
+        C = self.gdn_C
+        proj = self._linear(x, L.wqkv, K.EPI_STORE, self.gdn_in[:T])
+        self._count(3)
+        K.causal_conv_silu(proj, 0, C, L.gdn["conv"], self.gdn_conv_state[gi], self.seg_table, self.gdn_conv_out[:T])
+        K.gdn_scan(self.gdn_conv_out[:T], proj, C + nv * Dg, C + nv * Dg + nv, L.gdn["dt_bias"], L.gdn["a_log"],
+                   self.gdn_state[gi], self.seg_table, self.gdn_y[:T], nk, nv, Dg)
+        K.gated_rmsnorm(self.gdn_y[:T], proj, C, L.gdn["gate_norm"], cfg.norm_eps, self.gdn_y[:T], nv, Dg)
+        return self._proj_to_residual(self.gdn_y[:T], L.wo, T)
 
     def _rope_tables_of(self, l: int):
         cfg = self.cfg
@@ -600,6 +645,13 @@ class DecoderEngine:
                 self.row_seq[T:R].zero_()
         B = logit_idx.numel()
         self.logit_idx[:B].copy_(logit_idx, non_blocking=non_blocking)
+        if self._gdn_of:
+            segs = K.step_segments(row_seq.numpy(), positions.numpy(), row_ctx.numpy())
+            if segs.shape[0] > self._h_segs.shape[0]:
+                raise ValueError("a step carries more sequence pieces than the engine has rows")
+            self._h_segs.zero_()
+            self._h_segs[:segs.shape[0]] = torch.from_numpy(segs)
+            self.seg_table.copy_(self._h_segs, non_blocking=non_blocking)
         if self.flash_ok and T > B:
             tiles, covered = K.flash_tiles(row_seq.numpy(), positions.numpy())
             n = self._tile_slots(T, B)

@@ -33,6 +33,9 @@ class LayerWeights:
     bqkv: Optional[torch.Tensor] = None     # fused q|k|v bias of families that have one (qwen2), rank-local
     post1: Optional[torch.Tensor] = None    # norm applied to the attention output before the residual add (post / sandwich blocks)
     post2: Optional[torch.Tensor] = None    # the same for the FFN output
+    wgate: Optional[torch.Tensor] = None    # attention output gate projection [q_size, hidden] (gated attention)
+    kind: str = "attention"                 # token mixer of the layer: attention | gdn
+    gdn: Optional[Dict[str, torch.Tensor]] = None   # gated delta net: w_in (q|k|v|z|b|a rows), conv [C, K], dt_bias, a_log, gate_norm
     router: Optional[torch.Tensor] = None   # [E, hidden]
     select_bias: Optional[torch.Tensor] = None   # [E] fp32, added to the router scores for selection only
     ex_wgu: Optional[torch.Tensor] = None   # [E_local, 2F, hidden]
@@ -247,15 +250,25 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
     st = stage or StageSpec.whole(cfg)
     for l in range(st.l0, st.l1):
         p = f"layers.{l}."
-        wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)
-        wo = shard_cols(get(p + "attn_o"), tp_rank, tp_world)
         pre = cfg.block in ("pre", "sandwich")
-        L = LayerWeights(ln1=get(p + "attn_norm") if pre else None, ln2=get(p + "ffn_norm") if pre else None, wqkv=wqkv, wo=wo)
+        if cfg.mixer_of(l) == "gdn":
+            # one GEMM for every projection of the layer: q | k | v | z | b | a rows
+            w_in = torch.cat([get(p + r) for r in ("gdn_q", "gdn_k", "gdn_v", "gdn_z", "gdn_b", "gdn_a")], 0).contiguous()
+            f32 = lambda n: tensors[p + n].to(device=dev, dtype=torch.float32).contiguous()
+            L = LayerWeights(ln1=get(p + "attn_norm"), ln2=get(p + "ffn_norm"), wqkv=w_in, wo=get(p + "gdn_o"), kind="gdn",
+                             gdn={"conv": f32("gdn_conv"), "dt_bias": f32("gdn_dt_bias"), "a_log": f32("gdn_a_log"),
+                                  "gate_norm": get(p + "gdn_gate_norm_w")})
+        else:
+            wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)
+            wo = shard_cols(get(p + "attn_o"), tp_rank, tp_world)
+            L = LayerWeights(ln1=get(p + "attn_norm") if pre else None, ln2=get(p + "ffn_norm") if pre else None, wqkv=wqkv, wo=wo)
+            if cfg.attn_gate:
+                L.wgate = shard_rows(get(p + "attn_gate"), tp_rank, tp_world)
         if cfg.block in ("post", "sandwich"):
             L.post1, L.post2 = get(p + "attn_post_norm"), get(p + "ffn_post_norm")
         if cfg.attn_bias:
             L.bqkv = fuse_qkv_bias(get(p + "attn_q_bias"), get(p + "attn_k_bias"), get(p + "attn_v_bias"), cfg, tp_rank, tp_world)
-        if cfg.qk_norm:
+        if cfg.qk_norm and L.kind == "attention":
             L.q_norm, L.k_norm = get(p + "attn_q_norm"), get(p + "attn_k_norm")
         if cfg.is_moe:
             L.router = get(p + "ffn_router")

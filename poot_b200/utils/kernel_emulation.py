@@ -86,6 +86,60 @@ def softcap_(x, cap):
     return x
 
 
+def causal_conv_silu(x, col0, C, w, state, segs, out):
+    Kc = w.shape[1]
+    for first, n, seq, pos0 in segs.tolist():
+        if n == 0:
+            continue
+        prev = torch.zeros(Kc - 1, C) if pos0 == 0 else state[seq].clone()
+        xp = torch.cat([prev, x[first:first + n, col0:col0 + C].float()], 0)
+        acc = sum(xp[k:k + n] * w[:, k] for k in range(Kc))
+        out[first:first + n] = _bf(torch.nn.functional.silu(acc))
+        state[seq] = xp[n:]
+    return out
+
+
+def gdn_scan(qkv, ba, b_col, a_col, dt_bias, a_log, state, segs, out, nk, nv, D):
+    rep = nv // nk
+    for first, n, seq, pos0 in segs.tolist():
+        if n == 0:
+            continue
+        S = torch.zeros(nv, D, D) if pos0 == 0 else state[seq].clone()
+        x = qkv[first:first + n].float()
+        q = x[:, :nk * D].reshape(n, nk, D)
+        k = x[:, nk * D:2 * nk * D].reshape(n, nk, D)
+        v = x[:, 2 * nk * D:].reshape(n, nv, D)
+        unit = lambda t: t / torch.sqrt((t * t).sum(-1, keepdim=True) + 1e-6)
+        q = unit(q).repeat_interleave(rep, 1) * (D ** -0.5)
+        k = unit(k).repeat_interleave(rep, 1)
+        b = ba[first:first + n, b_col:b_col + nv].float()
+        a = ba[first:first + n, a_col:a_col + nv].float()
+        beta = torch.sigmoid(b)
+        g = -torch.exp(a_log.float()) * torch.nn.functional.softplus(a + dt_bias.float())
+        for t in range(n):
+            S = S * torch.exp(g[t])[:, None, None]
+            kv = torch.einsum("hk,hkv->hv", k[t], S)
+            d = (v[t] - kv) * beta[t][:, None]
+            S = S + k[t][:, :, None] * d[:, None, :]
+            out[first + t] = _bf(torch.einsum("hk,hkv->hv", q[t], S).reshape(-1))
+        state[seq] = S
+    return out
+
+
+def gated_rmsnorm(y, z, z_col, w, eps, out, heads, D):
+    T = y.shape[0]
+    yy = y.float().reshape(T, heads, D)
+    zz = z[:, z_col:z_col + heads * D].float().reshape(T, heads, D)
+    r = yy / torch.sqrt((yy * yy).mean(-1, keepdim=True) + eps) * w.float() * torch.nn.functional.silu(zz)
+    out.copy_(_bf(r.reshape(T, heads * D)))
+    return out
+
+
+def sigmoid_mul(a, g):
+    a.copy_(_bf(a.float() * torch.sigmoid(g.float())))
+    return a
+
+
 def add(a, b, out=None):
     r = _bf(a.float() + b.float())
     if out is None:
@@ -370,7 +424,8 @@ def emulated_kernels():
     from ..ops import moe_ops, suffix_ops
     table = {
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
-                gated_act=gated_act, softcap_=softcap_,
+                gated_act=gated_act, softcap_=softcap_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan,
+                gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
                 attn_paged=attn_paged, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
                 argmax=argmax, argmax_partials=argmax_partials, argmax_combine=argmax_combine,

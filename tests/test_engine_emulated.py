@@ -162,6 +162,9 @@ HF_FAMILIES = {
     "olmo2": {"model_type": "olmo2"},
     "olmoe": {"model_type": "olmoe", "num_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
     "smollm3-nope-layer": {"model_type": "smollm3", "no_rope_layers": [1, 0]},
+    "qwen3_5": {"model_type": "qwen3_5_text", "num_hidden_layers": 4, "layer_types": ["linear_attention", "full_attention"] * 2,
+                "linear_num_value_heads": 4, "linear_num_key_heads": 2, "linear_key_head_dim": 64, "linear_value_head_dim": 64,
+                "linear_conv_kernel_dim": 4, "rope_parameters": {"rope_theta": 10000.0, "partial_rotary_factor": 0.5, "rope_type": "default"}},
     "minimax_m2": {"model_type": "minimax_m2", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
     "granite": {"model_type": "granite", "embedding_multiplier": 6.0, "residual_multiplier": 0.5, "logits_scaling": 4.0,
                 "attention_multiplier": 0.1},
@@ -186,8 +189,10 @@ def test_family_blocks_on_the_engine_match_the_graph_oracle(name):
     for k in w:
         if k.endswith("select_bias"):
             w[k] = (0.3 * np.random.default_rng(1).standard_normal(w[k].shape)).astype(np.float32)
-        if k.endswith("norm"):
+        if k.endswith(("norm", "norm_w")):
             w[k] = (1.0 + 0.1 * np.random.default_rng(len(k)).standard_normal(w[k].shape)).astype(np.float32)
+        if k.endswith("gdn_a_log"):
+            w[k] = np.log(np.random.default_rng(3).uniform(0.5, 4.0, w[k].shape)).astype(np.float32)
     w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}     # what the device will hold
     named = {k: torch.from_numpy(v) for k, v in w.items()}
     for l in range(cfg.n_layers if cfg.is_moe else 0):

@@ -105,3 +105,37 @@ def test_every_registered_kernel_entry_is_exported_by_a_source():
     assert names, "the signature table was not found"
     missing = sorted(n for n in names if n not in exported)
     assert not missing, missing
+
+
+def test_ctypes_signatures_match_the_c_declarations():
+    """Every registered ctypes signature has the parameter kinds, in order, of the exported C function: a pointer (or
+    stream) for a pointer, ``int`` / ``long long`` / ``float`` for themselves.  A kernel entry whose argument list
+    changed without its binding (or the other way round) fails here, not on a device."""
+    import ctypes
+    from poot_b200.ops import cuda_ops, moe_ops, suffix_ops  # noqa: F401
+    from poot_b200.parallel import tp  # noqa: F401  (registers the comm launchers)
+    decl = {}
+    for d, _, files in os.walk(os.path.join(ROOT, "csrc", "kernels")):
+        for f in files:
+            if f.endswith(".cu"):
+                src = open(os.path.join(d, f)).read()
+                for m in re.finditer(r"POOT_API\s+int\s+(poot_\w+)\s*\(([^)]*)\)", src):
+                    decl[m.group(1)] = m.group(2)
+
+    def kind(param: str):
+        p = param.strip()
+        if "*" in p or p.startswith("cudaStream_t"):
+            return ctypes.c_void_p
+        base = re.sub(r"\b(const|unsigned)\b", "", p).split()
+        ty = " ".join(base[:-1]) if len(base) > 1 else base[0]
+        return {"int": ctypes.c_int, "long long": ctypes.c_longlong, "float": ctypes.c_float, "size_t": ctypes.c_size_t,
+                "uint32_t": ctypes.c_uint32}.get(ty, ty)
+
+    bad = []
+    for name, sig in cuda_ops._SIGS.items():
+        if name not in decl:
+            continue                       # exported-by-a-source is checked above
+        want = [kind(p) for p in decl[name].split(",") if p.strip()]
+        if list(sig) != want:
+            bad.append((name, [getattr(t, "__name__", t) for t in sig], [getattr(t, "__name__", t) for t in want]))
+    assert not bad, bad
