@@ -275,3 +275,15 @@ def write_random_gguf(path: str, cfg: DecoderConfig, proj_format: str = "Q4_K", 
     tensors.append(PackedWeight("output_norm.weight", "F32", (H,), np.ones(H, np.float32).view(np.uint8)))
     add("output.weight", (cfg.vocab, H), proj_format)
     gguf.write_gguf(path, meta, tensors)
+
+
+def prove_step_ranges(cfg: DecoderConfig, prefill_chunk: int = 64) -> None:
+    """Trace the decode and prefill step graphs and prove every index (token ids, positions, slot maps, expert ids)
+    inside its extent; raises ``ValueError`` naming the first unproven use."""
+    from ..ir.analysis import index_guards
+    from ..models.model import Model, StepSpec
+    for tokens in (1, min(prefill_chunk, 64)):
+        g = Model(cfg).trace(StepSpec(rows=1, tokens=tokens, capacity=64))
+        bad = [x for x in index_guards(g) if not x.proven]
+        if bad:
+            raise ValueError(f"{len(bad)} index uses are not proven in range, first: {bad[0]}")

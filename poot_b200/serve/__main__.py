@@ -138,15 +138,12 @@ def main(argv=None) -> int:
 
 
 def _prove_ranges(model_cfg, cfg) -> None:
-    """``--check-ranges``: trace the decode and prefill step graphs and prove every index (token ids, positions, slot
-    maps, expert ids) inside its extent before the server accepts a request; an unproven index stops startup."""
-    from ..ir.analysis import index_guards
-    from ..models.model import Model, StepSpec
-    for tokens in (1, min(cfg.prefill_chunk, 64)):
-        g = Model(model_cfg).trace(StepSpec(rows=1, tokens=tokens, capacity=64))
-        bad = [x for x in index_guards(g) if not x.proven]
-        if bad:
-            raise SystemExit(f"poot-serve: --check-ranges: {len(bad)} index uses are not proven in range, first: {bad[0]}")
+    """``--check-ranges``: an unproven index of the step graphs stops startup."""
+    from ..driver.handle import prove_step_ranges
+    try:
+        prove_step_ranges(model_cfg, cfg.prefill_chunk)
+    except ValueError as e:
+        raise SystemExit(f"poot-serve: --check-ranges: {e}") from None
 
 
 def _is_encoder_checkpoint(path: str) -> bool:
