@@ -11,7 +11,7 @@
 
 namespace poot {
 
-constexpr int MOE_MAX_K = 8;
+constexpr int MOE_MAX_K = 16;
 
 // mode 0: softmax gates (over the k selected logits when renorm, else over all experts, not renormalised).
 // mode 1: sigmoid scores; experts are ranked by score + select_bias[e] (the bias does not enter the gate), gates are

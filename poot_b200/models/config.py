@@ -182,12 +182,11 @@ class DecoderConfig:
         if self.swiglu_limit > 0: g.append("clamped SwiGLU")
         if self.router_bias or (self.router == "softmax" and self.router_select_bias): g.append("router variant")
         if self.n_group > 1: g.append("group-limited routing")
-        if self.shared_width or self.first_dense_layers or self.dense_layers: g.append("shared experts / dense layers in a routed model")
-        if self.is_moe and self.top_k > 8: g.append("more than 8 experts per token")
+        if self.shared_width and (not self.gated_ffn or self.act != "silu"): g.append("shared expert that is not a SwiGLU FFN")
+        if self.is_moe and self.top_k > 16: g.append("more than 16 experts per token")
         if self.is_mla: g.append("multi-head latent attention")
         if self.layer_kinds is not None and any(k == "mamba" for k in self.layer_kinds): g.append("Mamba2 mixer")
         if self.layer_kinds is not None and any(k == "none" for k in self.layer_kinds) or self.layer_ffn is not None: g.append("single-mixer blocks")
-        if self.shared_expert_gate: g.append("gated shared expert")
         if self.gdn_k_heads and self.gdn_head_dim not in (64, 128): g.append(f"delta-net head width {self.gdn_head_dim}")
         if self.head_dim not in (64, 128): g.append(f"head_dim {self.head_dim}")
         return g

@@ -106,6 +106,8 @@ class DecoderEngine:
         # ---- activations ----
         bf = torch.bfloat16
         ffn_local = (cfg.moe_ffn if cfg.is_moe else cfg.ffn) // (1 if cfg.is_moe else self.tp)
+        if cfg.is_moe and (cfg.first_dense_layers or cfg.dense_layers):      # leading dense layers of a routed model
+            ffn_local = max(ffn_local, cfg.ffn)
         self.h = torch.zeros(T, H, dtype=bf, device=dev)
         self.x = torch.zeros(T, H, dtype=bf, device=dev)
         self.qkv = torch.zeros(T, (self.hq + 2 * self.hkv) * D, dtype=bf, device=dev)
@@ -285,7 +287,7 @@ class DecoderEngine:
         T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
         packed = isinstance(w.layers[0].wqkv, K.QuantWeight) or isinstance(w.layers[0].wo, K.QuantWeight)
         # expert parallelism with one expert per rank rides the one-shot path (the combine is the fused all-reduce)
-        moe_fusable = cfg.is_moe and w.ep_world == self.tp and w.layers[0].ex_wgu.shape[0] == 1
+        moe_fusable = cfg.is_moe and w.ep_world == self.tp and w.layers[0].ex_wgu is not None and w.layers[0].ex_wgu.shape[0] == 1
         if self.comm is not None and getattr(self.comm, "fused", False) and not packed and (not cfg.is_moe or moe_fusable):
             if self.comm.oneshot_ok(T) and (self.tp_mode != "rs_ag" or cfg.is_moe):
                 return self._forward_tp_oneshot(shape)
@@ -315,8 +317,11 @@ class DecoderEngine:
             if L.kind == "gdn":
                 pending = self._gdn_mixer(l, L, x, T)
                 x = self._norm(L.ln2, T, pending)
-                act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
-                pending = self._proj_to_residual(act, L.wdown, T)
+                if cfg.moe_layer(w.layer0 + l):
+                    pending = self._moe(l, L, x, T)
+                else:
+                    act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
+                    pending = self._proj_to_residual(act, L.wdown, T)
                 continue
             qkv = self._linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
             if L.bqkv is not None:
@@ -346,7 +351,7 @@ class DecoderEngine:
                 if lora:
                     self.lora.apply(self, "o", l, self.attn[:T], h, T)
             x = h if cfg.block == "post" else self._norm(L.ln2, T, pending)
-            if cfg.is_moe:
+            if cfg.moe_layer(w.layer0 + l):
                 pending = self._moe(l, L, x, T)
             else:
                 if cfg.act == "silu" and not lora:
@@ -587,6 +592,8 @@ class DecoderEngine:
         from . import moe as _moe
         ep = ("nccl", self.comm) if (self.comm is not None and self.w.ep_world > 1) else None
         _moe.moe_forward(self, l, L, x, T, ep)
+        if L.sh_wgu is not None:
+            _moe.shared_expert(self, L, x, T)
         return None
 
     # ------------------------------------------------------------------ capture / replay

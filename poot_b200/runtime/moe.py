@@ -25,7 +25,7 @@ def _buffers(eng):
     if getattr(eng, "_moe_buf", None) is None:
         c, dev = eng.cfg, eng.device
         T, E, k = eng.max_tokens, c.n_experts, c.top_k
-        e_local = eng.w.layers[0].ex_wgu.shape[0]
+        e_local = next(L_.ex_wgu.shape[0] for L_ in eng.w.layers if L_.ex_wgu is not None)
         F, H = c.moe_ffn, c.hidden
         Tc = min(T, 128)
         G = max(e_local, min(T, E) * k)
@@ -38,6 +38,25 @@ def _buffers(eng):
             "parts": torch.zeros(G * Tc * H, dtype=torch.bfloat16, device=dev),
         }
     return eng._moe_buf
+
+
+def shared_expert(eng, L, x: torch.Tensor, T: int) -> None:
+    """``h[:T] += shared(x)``: the always-on expert of families that have one (a dense SwiGLU FFN), optionally scaled per
+    token by ``sigmoid(x . w)`` (the scale is applied to the activation rows, which the down projection carries through)."""
+    c = eng.cfg
+    if getattr(eng, "_sh_act", None) is None:
+        eng._sh_act = torch.zeros(eng.max_tokens, c.shared_width, dtype=torch.bfloat16, device=eng.device)
+        eng._sh_gate = torch.zeros(eng.max_tokens, 8, dtype=torch.float32, device=eng.device)
+    act = eng._sh_act[:T]
+    eng._count(2)
+    K.linear(x, L.sh_wgu, K.EPI_SWIGLU, act)
+    if L.sh_gate is not None:
+        eng._count(2)
+        g = eng._sh_gate[:T]
+        K.linear(x, L.sh_gate, K.EPI_F32, g)
+        act.mul_(torch.sigmoid(g[:, :1]).to(act.dtype))
+    h = eng.h[:T]
+    K.linear(act, L.sh_wdown, K.EPI_RESID, h, h)
 
 
 def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):

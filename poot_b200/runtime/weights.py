@@ -38,6 +38,9 @@ class LayerWeights:
     gdn: Optional[Dict[str, torch.Tensor]] = None   # gated delta net: w_in (q|k|v|z|b|a rows), conv [C, K], dt_bias, a_log, gate_norm
     router: Optional[torch.Tensor] = None   # [E, hidden]
     select_bias: Optional[torch.Tensor] = None   # [E] fp32, added to the router scores for selection only
+    sh_wgu: Optional[torch.Tensor] = None   # always-on (shared) expert: interleaved gate/up rows, down projection
+    sh_wdown: Optional[torch.Tensor] = None
+    sh_gate: Optional[torch.Tensor] = None  # [8, hidden]: row 0 is the shared expert's sigmoid gate, the rest zero padding
     ex_wgu: Optional[torch.Tensor] = None   # [E_local, 2F, hidden]
     ex_wdown: Optional[torch.Tensor] = None  # [E_local, hidden, F]
     quant: Dict[str, object] = field(default_factory=dict)  # packed (GGUF block) weights by role
@@ -270,10 +273,16 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             L.bqkv = fuse_qkv_bias(get(p + "attn_q_bias"), get(p + "attn_k_bias"), get(p + "attn_v_bias"), cfg, tp_rank, tp_world)
         if cfg.qk_norm and L.kind == "attention":
             L.q_norm, L.k_norm = get(p + "attn_q_norm"), get(p + "attn_k_norm")
-        if cfg.is_moe:
+        if cfg.moe_layer(l):
             L.router = get(p + "ffn_router")
             if cfg.router_select_bias:
                 L.select_bias = tensors[p + "ffn_router_select_bias"].to(device=dev, dtype=torch.float32).contiguous()
+            if cfg.shared_width:
+                L.sh_wgu = interleave_gate_up(get(p + "shared_gate"), get(p + "shared_up"))
+                L.sh_wdown = get(p + "shared_down")
+                if cfg.shared_expert_gate:
+                    L.sh_gate = torch.zeros(8, cfg.hidden, dtype=dtype, device=dev)
+                    L.sh_gate[0] = get(p + "shared_expert_gate")[0]
             gus, downs = [], []
             for e in range(cfg.n_experts):
                 gus.append(interleave_gate_up(get(p + f"experts.{e}.gate"), get(p + f"experts.{e}.up")))

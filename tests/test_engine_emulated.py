@@ -165,6 +165,10 @@ HF_FAMILIES = {
     "qwen3_5": {"model_type": "qwen3_5_text", "num_hidden_layers": 4, "layer_types": ["linear_attention", "full_attention"] * 2,
                 "linear_num_value_heads": 4, "linear_num_key_heads": 2, "linear_key_head_dim": 64, "linear_value_head_dim": 64,
                 "linear_conv_kernel_dim": 4, "rope_parameters": {"rope_theta": 10000.0, "partial_rotary_factor": 0.5, "rope_type": "default"}},
+    "qwen3next": {"model_type": "qwen3_next", "num_hidden_layers": 2, "layer_types": ["linear_attention", "full_attention"],
+                  "linear_num_value_heads": 4, "linear_num_key_heads": 2, "linear_key_head_dim": 64, "linear_value_head_dim": 64,
+                  "num_experts": 16, "num_experts_per_tok": 10, "moe_intermediate_size": 64, "shared_expert_intermediate_size": 128,
+                  "partial_rotary_factor": 0.25},
     "minimax_m2": {"model_type": "minimax_m2", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
     "granite": {"model_type": "granite", "embedding_multiplier": 6.0, "residual_multiplier": 0.5, "logits_scaling": 4.0,
                 "attention_multiplier": 0.1},

@@ -136,7 +136,7 @@ def test_bias_and_constant_multipliers(kw):
 
 
 @pytest.mark.xfail(strict=False, reason="new device paths: not yet run on a device")
-@pytest.mark.parametrize("name", ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "minimax_m2", "qwen3_5"])
+@pytest.mark.parametrize("name", ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "minimax_m2", "qwen3_5", "qwen3next"])
 def test_family_blocks_match_the_graph_oracle(name):
     """The device twin of the host-emulated check: sandwich / post norms, GeGLU, soft caps, two rope bases,
     projection-wide q/k norms and layers without rope on the real kernels, against the graph oracle."""
