@@ -188,7 +188,7 @@ class DecoderConfig:
         if self.layer_kinds is not None and any(k == "mamba" for k in self.layer_kinds): g.append("Mamba2 mixer")
         if self.layer_kinds is not None and any(k == "none" for k in self.layer_kinds) or self.layer_ffn is not None: g.append("single-mixer blocks")
         if self.gdn_k_heads and self.gdn_head_dim not in (64, 128): g.append(f"delta-net head width {self.gdn_head_dim}")
-        if self.head_dim not in (64, 128): g.append(f"head_dim {self.head_dim}")
+        if self.head_dim % 32 or not (32 <= self.head_dim <= 512): g.append(f"head_dim {self.head_dim}")
         return g
 
     def param_count(self) -> int:

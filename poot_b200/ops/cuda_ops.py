@@ -40,6 +40,8 @@ _SIGS = {
                            c_int, _P],
     "poot_attn_paged": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float,
                         c_float, c_int, c_int, _P],
+    "poot_attn_general": [_P, c_int, _P, _P, c_int, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                          c_float, c_int, _P, _P, _P],
     "poot_attn_flash_prefill": [_P, c_int, c_int, _P, _P, c_longlong, _P, c_int, _P, c_int, _P, c_int, c_int, c_int,
                                 c_float, c_int, _P, _P],
     "poot_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, _P],
@@ -391,6 +393,22 @@ def attn_paged(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_
                                  block_tables.shape[1], _ptr(row_seq), _ptr(row_ctx), _ptr(out), out.stride(0),
                                  _ptr(po), _ptr(pml), R, Hq, Hkv, D, float(scale), float(softcap), int(window),
                                  int(splits), _stream()), "attn_paged")
+    return out
+
+
+def attn_general(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_tables: torch.Tensor,
+                 row_seq: Optional[torch.Tensor], row_ctx: torch.Tensor, Hq: int, Hkv: int, Dk: int, Dv: int, scale: float,
+                 out: torch.Tensor, softcap: float = 0.0, window: int = 0, alibi: Optional[torch.Tensor] = None,
+                 sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paged attention for the shapes the tuned kernels do not serve: key width ``Dk`` and value width ``Dv`` (multiples of
+    32 up to 512), optional per-head ALiBi slopes and sink logits (fp32 ``[Hq]``).  Pools are ``[blocks, Hkv, 16, pool_d]``."""
+    _need_cuda(q, kpool, vpool)
+    assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and kpool.is_contiguous() and vpool.is_contiguous()
+    assert kpool.shape == vpool.shape and block_tables.dtype == torch.int32 and row_ctx.dtype == torch.int32
+    check(_fn("poot_attn_general")(_ptr(q), q.stride(0), _ptr(kpool), _ptr(vpool), kpool.shape[-1], _ptr(block_tables),
+                                   block_tables.shape[1], _ptr(row_seq), _ptr(row_ctx), _ptr(out), out.stride(0), q.shape[0], Hq,
+                                   Hkv, Dk, Dv, float(scale), float(softcap), int(window), _ptr(alibi), _ptr(sinks), _stream()),
+          "attn_general")
     return out
 
 

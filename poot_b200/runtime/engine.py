@@ -136,6 +136,7 @@ class DecoderEngine:
         self.logprobs = torch.zeros(max_seqs, dtype=torch.float32, device=dev)
         self.adj_idx = self.adj_val = self.guided_mask = None   # allocated on first use
         # tensor-core prefill attention: tiles cut on the host per step, rows they cover masked out of the per-row kernel
+        self.attn_general = cfg.head_dim not in (64, 128)     # e.g. head_dim 256: served by the general attention kernel
         self.flash_ok = cfg.head_dim == 128 and cfg.attn_softcap == 0
         self._flash_only = False      # set by bind: every row of the bound step is covered by a tile
         self.attn_tiles = torch.zeros(self._tile_slots(T, max_seqs), 4, dtype=i32, device=dev)
@@ -256,6 +257,14 @@ class DecoderEngine:
         over the rows left to it (its context length is 0 on rows the tiles cover) and the tensor-core flash kernel
         over the tiles ``bind`` cut from the step's segments.  Pure decode steps run the per-row kernel alone."""
         cfg, D = self.cfg, self.cfg.head_dim
+        if self.attn_general:
+            # head widths the tuned kernels do not serve: the general kernel over every live row
+            if count:
+                self._count()
+            K.attn_general(self.q[:R], self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables, self.row_seq[:R],
+                           self.row_ctx[:R], self.hq, self.hkv, D, D, self.scale, self.attn[:R], softcap=cfg.attn_softcap,
+                           window=cfg.window_of(self.w.layer0 + l))
+            return
         flash = self.flash_ok and T > B
         splits = self._attn_splits(R)
         simt = not (flash and self._flash_only)      # every row sits in a tile: the per-row kernel has nothing to do

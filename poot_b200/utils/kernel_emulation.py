@@ -252,6 +252,33 @@ def attn_paged(q, kpool, vpool, block_tables, row_seq, row_ctx, Hq, Hkv, D, scal
     return out
 
 
+def attn_general(q, kpool, vpool, block_tables, row_seq, row_ctx, Hq, Hkv, Dk, Dv, scale, out, softcap=0.0, window=0,
+                 alibi=None, sinks=None):
+    rep = Hq // Hkv
+    for r in range(q.shape[0]):
+        ctx = int(row_ctx[r])
+        if ctx <= 0:
+            continue
+        seq = int(row_seq[r]) if row_seq is not None else r
+        first = ctx - window if (window > 0 and ctx > window) else 0
+        pos = torch.arange(first, ctx)
+        blk = block_tables[seq][(pos // K.KV_BLOCK).long()].long()
+        kk = kpool[blk, :, (pos % K.KV_BLOCK).long()][..., :Dk].float().repeat_interleave(rep, 1)     # [S, Hq, Dk]
+        vv = vpool[blk, :, (pos % K.KV_BLOCK).long()][..., :Dv].float().repeat_interleave(rep, 1)
+        s = torch.einsum("hd,shd->hs", q[r, :Hq * Dk].reshape(Hq, Dk).float(), kk) * scale
+        if softcap > 0:
+            s = softcap * torch.tanh(s / softcap)
+        if alibi is not None:
+            s = s + alibi.float()[:, None] * (pos - (ctx - 1)).float()[None, :]
+        if sinks is not None:
+            full = torch.cat([s, sinks.float()[:, None]], 1)
+            p = torch.softmax(full, -1)[:, :-1]
+        else:
+            p = torch.softmax(s, -1)
+        out[r, :Hq * Dv] = _bf(torch.einsum("hs,shd->hd", p, vv).reshape(-1))
+    return out
+
+
 def attn_flash_prefill(q, kpool, vpool, block_tables, tiles, Hq, Hkv, scale, out, window=0):
     D = kpool.shape[-1]
     for first_row, rows, seq, first_pos in tiles.tolist():
@@ -427,7 +454,7 @@ def emulated_kernels():
                 gated_act=gated_act, softcap_=softcap_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
-                attn_paged=attn_paged, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
+                attn_paged=attn_paged, attn_general=attn_general, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
                 argmax=argmax, argmax_partials=argmax_partials, argmax_combine=argmax_combine,
                 sample_gumbel=sample_gumbel, decode_advance=decode_advance,
                 status_word=lambda device=None: _status, check_status=lambda device=None: None),

@@ -31,6 +31,7 @@ def _engine(cfg, batch, max_len, max_tokens, seed=0):
 VARIANTS = {
     "llama": {},
     "head-dim-128-flash-tiles": dict(n_heads=2, n_kv_heads=1, head_dim=128, hidden=256),
+    "head-dim-256-general-attention": dict(n_heads=2, n_kv_heads=1, head_dim=256, hidden=256, sliding_window=12, attn_softcap=30.0),
     "qk-norm-window": dict(qk_norm=True, sliding_window=8),
     "per-layer-windows": dict(layer_windows=[6, 0]),
     "scale-override-softcap": dict(attn_scale=0.2, attn_softcap=20.0),

@@ -390,3 +390,28 @@ def test_gdn_kernels_match_their_host_restatements(D):
     want = (a.float() * torch.sigmoid(gt.float()))
     got = K.sigmoid_mul(a.cuda(), gt.cuda())
     assert tol(got, want)
+
+
+@pytest.mark.xfail(strict=False, reason="general attention kernel: not yet run on a device")
+@pytest.mark.parametrize("Dk,Dv,extras", [(256, 256, False), (192, 128, False), (64, 64, True)])
+def test_general_attention_matches_its_host_restatement(Dk, Dv, extras):
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.utils import kernel_emulation as emu
+    g = torch.Generator().manual_seed(0)
+    Hq, Hkv, blocks, R = 4, 2, 12, 5
+    pd = max(Dk, Dv)
+    kpool = (torch.randn(blocks, Hkv, 16, pd, generator=g) * 0.5).to(torch.bfloat16)
+    vpool = (torch.randn(blocks, Hkv, 16, pd, generator=g) * 0.5).to(torch.bfloat16)
+    bt = torch.tensor([[3, 1, 7, 0], [5, 2, 9, 11]], dtype=torch.int32)
+    row_seq = torch.tensor([0, 0, 1, 1, 0], dtype=torch.int32)
+    row_ctx = torch.tensor([1, 37, 64, 20, 0], dtype=torch.int32)
+    q = (torch.randn(R, Hq * Dk, generator=g) * 0.5).to(torch.bfloat16)
+    alibi = torch.tensor([0.5, 0.25, 0.125, 0.0625]) if extras else None
+    sinks = torch.randn(Hq, generator=g) if extras else None
+    for window, cap in ((0, 0.0), (9, 5.0)):
+        want = torch.zeros(R, Hq * Dv, dtype=torch.bfloat16)
+        emu.attn_general(q, kpool, vpool, bt, row_seq, row_ctx, Hq, Hkv, Dk, Dv, 0.11, want, cap, window, alibi, sinks)
+        got = torch.zeros(R, Hq * Dv, dtype=torch.bfloat16, device="cuda")
+        K.attn_general(q.cuda(), kpool.cuda(), vpool.cuda(), bt.cuda(), row_seq.cuda(), row_ctx.cuda(), Hq, Hkv, Dk, Dv, 0.11, got,
+                       cap, window, None if alibi is None else alibi.cuda(), None if sinks is None else sinks.cuda())
+        assert (got.float().cpu() - want.float()).abs().max().item() < 0.02
