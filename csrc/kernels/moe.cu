@@ -12,17 +12,43 @@
 namespace poot {
 
 constexpr int MOE_MAX_K = 16;
+constexpr int MOE_MAX_GROUPS = 32;
 
 // mode 0: softmax gates (over the k selected logits when renorm, else over all experts, not renormalised).
 // mode 1: sigmoid scores; experts are ranked by score + select_bias[e] (the bias does not enter the gate), gates are
 //         the selected scores, divided by their sum (+1e-20) when renorm.  Both: gates are multiplied by `scale`.
 __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int k, int renorm, int mode,
-                                 const float* __restrict__ select_bias, float scale,
+                                 const float* __restrict__ select_bias, float scale, int n_group, int topk_group,
                                  int* __restrict__ ids, float* __restrict__ gates, float* __restrict__ dense) {
   pdl_wait(); pdl_launch();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   const float* lr = logits + (size_t)t * E;
+  // Group-limited routing (mode 1): experts form n_group groups; a group's score is the sum of its two best selection
+  // values; only the topk_group best groups (lower index first on ties) stay eligible, the others rank as 0.
+  unsigned keep_groups = 0xffffffffu;
+  const int per = n_group > 1 ? E / n_group : E;
+  if (n_group > 1) {
+    float gs[MOE_MAX_GROUPS];
+    for (int g = 0; g < n_group; ++g) {
+      float b1 = -FLT_MAX, b2 = -FLT_MAX;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        float s = lr[e];
+        if (!(s >= -FLT_MAX)) s = -FLT_MAX;
+        if (s > FLT_MAX) s = FLT_MAX;
+        const float v = 1.f / (1.f + expf(-s)) + (select_bias ? select_bias[e] : 0.f);
+        if (v > b1) { b2 = b1; b1 = v; } else if (v > b2) { b2 = v; }
+      }
+      gs[g] = b1 + b2;
+    }
+    keep_groups = 0u;
+    for (int n = 0; n < topk_group; ++n) {
+      int bg = -1; float bvv = -FLT_MAX;
+      for (int g = 0; g < n_group; ++g)
+        if (!((keep_groups >> g) & 1u) && (bg < 0 || gs[g] > bvv)) { bg = g; bvv = gs[g]; }
+      if (bg >= 0) keep_groups |= 1u << bg;
+    }
+  }
   int best[MOE_MAX_K];
   float bv[MOE_MAX_K];      // the value experts are ranked by
   float sv[MOE_MAX_K];      // the score that becomes the gate (mode 1)
@@ -37,6 +63,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
     if (mode == 1) {
       score = 1.f / (1.f + expf(-s));
       rankv = score + (select_bias ? select_bias[e] : 0.f);
+      if (n_group > 1 && !((keep_groups >> (e / per)) & 1u)) rankv = 0.f;
     }
     // insertion into the sorted top-k; strict '>' keeps the lower index first on ties
     int pos = k;
@@ -103,17 +130,20 @@ POOT_API int poot_moe_route(const float* logits, int T, int E, int k, int renorm
   if (T == 0) return 0;
   if (k < 1 || k > MOE_MAX_K || k > E) return (int)cudaErrorInvalidValue;
   return launch_k(moe_route_kernel, dim3((T + 63) / 64), dim3(64), 0, s, logits, T, E, k, renorm, 0,
-                  (const float*)nullptr, 1.f, ids, gates, dense);
+                  (const float*)nullptr, 1.f, 1, 1, ids, gates, dense);
 }
 
 // Router variants: mode 1 = sigmoid scores with an optional selection-only bias [E]; gates times `scale`.
 POOT_API int poot_moe_route_ex(const float* logits, int T, int E, int k, int renorm, int mode, const float* select_bias,
-                               float scale, int* ids, float* gates, float* dense, cudaStream_t s) {
+                               float scale, int n_group, int topk_group, int* ids, float* gates, float* dense, cudaStream_t s) {
   if (T == 0) return 0;
   if (k < 1 || k > MOE_MAX_K || k > E || mode < 0 || mode > 1) return (int)cudaErrorInvalidValue;
-  if (mode == 0 && select_bias != nullptr) return (int)cudaErrorInvalidValue;
+  if (mode == 0 && (select_bias != nullptr || n_group > 1)) return (int)cudaErrorInvalidValue;
+  if (n_group < 1 || n_group > MOE_MAX_GROUPS || E % n_group || topk_group < 1 || topk_group > n_group ||
+      (n_group > 1 && E / n_group < 2))
+    return (int)cudaErrorInvalidValue;
   return launch_k(moe_route_kernel, dim3((T + 63) / 64), dim3(64), 0, s, logits, T, E, k, renorm, mode, select_bias, scale,
-                  ids, gates, dense);
+                  n_group, topk_group, ids, gates, dense);
 }
 
 POOT_API int poot_moe_combine(const void* h, const void* parts, void* out, int T, int H, int groups, long long gstride,

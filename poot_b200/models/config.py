@@ -165,7 +165,7 @@ class DecoderConfig:
         """The pre-norm SwiGLU rope layer the fused tensor-parallel programs are written for."""
         return (self.block == "pre" and self.act == "silu" and not self.qk_norm_wide and self.rope_theta_local is None
                 and (self.rope_layers is None or all(self.rope_layers)) and self.final_softcap == 0
-                and self.layer_kinds is None and not self.attn_gate)
+                and self.layer_kinds is None and not self.attn_gate and not self.is_mla)
 
     def device_gaps(self) -> list:
         """Features of this configuration that the device program does not implement (empty = runs on the device);
@@ -181,10 +181,11 @@ class DecoderConfig:
         if self.attn_sinks: g.append("attention sinks")
         if self.swiglu_limit > 0: g.append("clamped SwiGLU")
         if self.router_bias or (self.router == "softmax" and self.router_select_bias): g.append("router variant")
-        if self.n_group > 1: g.append("group-limited routing")
+        if self.n_group > 32 or (self.n_group > 1 and self.router != "sigmoid"): g.append("group-limited routing outside the sigmoid router")
         if self.shared_width and (not self.gated_ffn or self.act != "silu"): g.append("shared expert that is not a SwiGLU FFN")
         if self.is_moe and self.top_k > 16: g.append("more than 16 experts per token")
-        if self.is_mla: g.append("multi-head latent attention")
+        if self.is_mla and (self.qk_rope_dim % 2 or (self.qk_nope_dim + self.qk_rope_dim) % 32 or self.v_head_dim % 32):
+            g.append("latent attention head widths that are not multiples of 32")
         if self.layer_kinds is not None and any(k == "mamba" for k in self.layer_kinds): g.append("Mamba2 mixer")
         if self.layer_kinds is not None and any(k == "none" for k in self.layer_kinds) or self.layer_ffn is not None: g.append("single-mixer blocks")
         if self.gdn_k_heads and self.gdn_head_dim not in (64, 128): g.append(f"delta-net head width {self.gdn_head_dim}")

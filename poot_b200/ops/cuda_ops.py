@@ -40,6 +40,7 @@ _SIGS = {
                            c_int, _P],
     "poot_attn_paged": [_P, c_int, _P, _P, _P, c_int, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, c_float,
                         c_float, c_int, c_int, _P],
+    "poot_mla_qkv_write": [_P, _P, _P, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "poot_attn_general": [_P, c_int, _P, _P, c_int, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                           c_float, c_int, _P, _P, _P],
     "poot_attn_flash_prefill": [_P, c_int, c_int, _P, _P, c_longlong, _P, c_int, _P, c_int, _P, c_int, c_int, c_int,
@@ -394,6 +395,20 @@ def attn_paged(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_
                                  _ptr(po), _ptr(pml), R, Hq, Hkv, D, float(scale), float(softcap), int(window),
                                  int(splits), _stream()), "attn_paged")
     return out
+
+
+def mla_qkv_write(q: torch.Tensor, kvb: torch.Tensor, kva: torch.Tensor, rope_col: int, q_out: torch.Tensor, kpool: torch.Tensor,
+                  vpool: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nh: int,
+                  dn: int, dr: int, dv: int) -> None:
+    """Latent attention, expanded form: rotate the rotary parts, write the query rows ``[T, nh * (dn + dr)]`` and the key
+    ``[no-position | shared rotary]`` and value rows into the pools (rows ``dn + dr`` wide; a value uses the first ``dv``)."""
+    _need_cuda(q, kpool)
+    T = q.shape[0]
+    assert q.is_contiguous() and kvb.is_contiguous() and kva.stride(1) == 1 and q_out.is_contiguous()
+    assert kpool.shape[-1] == dn + dr and cos.shape[1] == dr // 2 and cos.dtype == torch.float32
+    check(_fn("poot_mla_qkv_write")(_ptr(q), _ptr(kvb), _ptr(kva), kva.stride(0), rope_col, _ptr(q_out), _ptr(kpool), _ptr(vpool),
+                                    _ptr(positions), _ptr(slots), _ptr(cos), _ptr(sin), T, nh, dn, dr, dv, cos.shape[0], _stream()),
+          "mla_qkv_write")
 
 
 def attn_general(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_tables: torch.Tensor,

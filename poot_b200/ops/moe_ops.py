@@ -12,7 +12,7 @@ from ._lib import check
 
 _P = c_void_p
 K.register_signature("poot_moe_route", [_P, c_int, c_int, c_int, c_int, _P, _P, _P, _P])
-K.register_signature("poot_moe_route_ex", [_P, c_int, c_int, c_int, c_int, c_int, _P, c_float, _P, _P, _P, _P])
+K.register_signature("poot_moe_route_ex", [_P, c_int, c_int, c_int, c_int, c_int, _P, c_float, c_int, c_int, _P, _P, _P, _P])
 K.register_signature("poot_moe_combine", [_P, _P, _P, c_int, c_int, c_int, c_longlong, c_int, _P])
 K.register_signature("poot_gemm_skinny_grouped",
                      [c_int, _P, c_int, c_int, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int,
@@ -20,18 +20,20 @@ K.register_signature("poot_gemm_skinny_grouped",
 
 
 def moe_route(logits: torch.Tensor, k: int, renorm: bool, ids: torch.Tensor, gates: torch.Tensor, dense: torch.Tensor,
-              mode: str = "softmax", select_bias: Optional[torch.Tensor] = None, scale: float = 1.0):
+              mode: str = "softmax", select_bias: Optional[torch.Tensor] = None, scale: float = 1.0, n_group: int = 1,
+              topk_group: int = 1):
     """``logits[T,E]`` fp32 -> ``ids[T,k]`` i32, ``gates[T,k]`` f32, ``dense[E,T]`` f32 (0 where unselected).
     ``mode="sigmoid"``: per-expert sigmoid scores, ranked with ``select_bias[E]`` added (selection only), gates = the
     selected scores (over their sum when ``renorm``); every gate is multiplied by ``scale``."""
     T, E = logits.shape
-    if mode == "softmax" and select_bias is None and scale == 1.0:
+    if mode == "softmax" and select_bias is None and scale == 1.0 and n_group == 1:
         check(K.fn("poot_moe_route")(logits.data_ptr(), T, E, k, int(renorm), ids.data_ptr(), gates.data_ptr(),
                                      dense.data_ptr(), K._stream()), "moe_route")
         return
     assert select_bias is None or (select_bias.dtype == torch.float32 and select_bias.numel() == E)
     check(K.fn("poot_moe_route_ex")(logits.data_ptr(), T, E, k, int(renorm), {"softmax": 0, "sigmoid": 1}[mode],
-                                    None if select_bias is None else select_bias.data_ptr(), float(scale), ids.data_ptr(),
+                                    None if select_bias is None else select_bias.data_ptr(), float(scale), int(n_group),
+                                    int(topk_group), ids.data_ptr(),
                                     gates.data_ptr(), dense.data_ptr(), K._stream()), "moe_route_ex")
 
 

@@ -136,7 +136,7 @@ class DecoderEngine:
         self.logprobs = torch.zeros(max_seqs, dtype=torch.float32, device=dev)
         self.adj_idx = self.adj_val = self.guided_mask = None   # allocated on first use
         # tensor-core prefill attention: tiles cut on the host per step, rows they cover masked out of the per-row kernel
-        self.attn_general = cfg.head_dim not in (64, 128)     # e.g. head_dim 256: served by the general attention kernel
+        self.attn_general = cfg.head_dim not in (64, 128) or cfg.is_mla   # e.g. head_dim 256: served by the general attention kernel
         self.flash_ok = cfg.head_dim == 128 and cfg.attn_softcap == 0
         self._flash_only = False      # set by bind: every row of the bound step is covered by a tile
         self.attn_tiles = torch.zeros(self._tile_slots(T, max_seqs), 4, dtype=i32, device=dev)
@@ -149,7 +149,8 @@ class DecoderEngine:
         ts = self.small_T
         self.attn_scratch = (torch.zeros(ts * self.hq * self.attn_splits_max * D, dtype=torch.float32, device=dev),
                              torch.zeros(ts * self.hq * self.attn_splits_max * 2, dtype=torch.float32, device=dev))
-        cos, sin = rope_tables(cfg, cfg.max_position)
+        import dataclasses as _dc
+        cos, sin = rope_tables(_dc.replace(cfg, rope_dim=cfg.qk_rope_dim) if cfg.is_mla else cfg, cfg.max_position)
         self.cos, self.sin = cos.to(dev), sin.to(dev)
         self.cos_local = self.sin_local = self.cos_none = self.sin_none = None
         if cfg.rope_theta_local is not None:     # windowed layers rotate with their own base and no scaling
@@ -163,6 +164,13 @@ class DecoderEngine:
         # attention layers own K/V pool entries; recurrent layers own state entries
         kinds = [cfg.mixer_of(weights.layer0 + i) for i in range(len(weights.layers))]
         self._kv_of = {i: n for n, i in enumerate(i for i, k in enumerate(kinds) if k == "attention")}
+        if cfg.is_mla:
+            dq = cfg.qk_nope_dim + cfg.qk_rope_dim
+            self.mla_q = torch.zeros(T, cfg.n_heads * dq, dtype=bf, device=dev)
+            self.mla_qa = torch.zeros(T, max(cfg.q_lora_rank, 8), dtype=bf, device=dev)
+            self.mla_kva = torch.zeros(T, cfg.kv_lora_rank + cfg.qk_rope_dim, dtype=bf, device=dev)
+            self.mla_ckv = torch.zeros(T, cfg.kv_lora_rank, dtype=bf, device=dev)
+            self.mla_kvb = torch.zeros(T, cfg.n_heads * (cfg.qk_nope_dim + cfg.v_head_dim), dtype=bf, device=dev)
         self._gdn_of = {i: n for n, i in enumerate(i for i, k in enumerate(kinds) if k == "gdn")}
         if self._gdn_of:
             nk, nv, Dg, Kc = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.gdn_conv
@@ -323,6 +331,15 @@ class DecoderEngine:
         post = cfg.block != "pre"           # a norm sits between each projection and its residual add
         for l, L in enumerate(w.layers):
             x = h if cfg.block == "post" else self._norm(L.ln1, T, pending)
+            if L.kind == "mla":
+                pending = self._mla_mixer(l, L, x, T)
+                x = self._norm(L.ln2, T, pending)
+                if cfg.moe_layer(w.layer0 + l):
+                    pending = self._moe(l, L, x, T)
+                else:
+                    act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
+                    pending = self._proj_to_residual(act, L.wdown, T)
+                continue
             if L.kind == "gdn":
                 pending = self._gdn_mixer(l, L, x, T)
                 x = self._norm(L.ln2, T, pending)
@@ -402,6 +419,33 @@ class DecoderEngine:
         self._sample(shape, self.logits_local[:B])
         if staged:
             self.link.return_picked(self.picked[:B], self.logprobs[:B] if shape.logprobs else None)
+
+    def _mla_mixer(self, l: int, L, x, T: int):
+        """Multi-head latent attention in its expanded form (components/mla.rs): low-rank query and key/value
+        projections with their norms, the rotary on the rotary parts only, keys ``[no-position | shared rotary]`` and
+        values written to the paged pools, attention with key width ``dn + dr`` and value width ``dv``, out-projection."""
+        cfg, m = self.cfg, L.mla
+        nh, dn, dr, dv = cfg.n_heads, cfg.qk_nope_dim, cfg.qk_rope_dim, cfg.v_head_dim
+        if "q_a" in m:
+            qa = self._linear(x, m["q_a"], K.EPI_STORE, self.mla_qa[:T, :cfg.q_lora_rank])
+            self._count()
+            K.rmsnorm(qa, m["q_a_norm"], cfg.norm_eps, out=qa)
+            q = self._linear(qa, m["q_b"], K.EPI_STORE, self.q[:T])
+        else:
+            q = self._linear(x, m["q"], K.EPI_STORE, self.q[:T])
+        kva = self._linear(x, m["kv_a"], K.EPI_STORE, self.mla_kva[:T])
+        ckv = self.mla_ckv[:T]
+        ckv.copy_(kva[:, :cfg.kv_lora_rank])
+        self._count(3)
+        K.rmsnorm(ckv, m["kv_a_norm"], cfg.norm_eps, out=ckv)
+        kvb = self._linear(ckv, m["kv_b"], K.EPI_STORE, self.mla_kvb[:T])
+        kvl = self._kv_of[l]
+        K.mla_qkv_write(q, kvb, kva, cfg.kv_lora_rank, self.mla_q[:T], self.kv.k(kvl), self.kv.v(kvl), self.positions[:T],
+                        self.slots[:T], self.cos, self.sin, nh, dn, dr, dv)
+        attn = self.attn[:T, :nh * dv]
+        K.attn_general(self.mla_q[:T], self.kv.k(kvl), self.kv.v(kvl), self.block_tables, self.row_seq[:T], self.row_ctx[:T],
+                       nh, nh, dn + dr, dv, self.scale, attn, window=cfg.window_of(self.w.layer0 + l))
+        return self._proj_to_residual(attn, L.wo, T)
 
     def _gdn_mixer(self, l: int, L, x, T: int):
         """Gated delta net layer (components/gdn.rs): one GEMM for q | k | v | z | b | a, causal conv + SiLU over

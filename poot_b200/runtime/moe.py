@@ -78,7 +78,7 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
     ids, gates = buf["ids"][:T * k], buf["gates"][:T * k]
     dense = buf["dense"][:E * T].view(E, T)
     M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense, mode=c.router, select_bias=L.select_bias,
-                scale=c.routed_scale)
+                scale=c.routed_scale, n_group=c.n_group, topk_group=c.topk_group)
     h = eng.h[:T]
     tp = (ep[1], ep[2]) if (ep is not None and ep[0] == "fused") else None
     if ep is None and e_local == E and T * k <= E:

@@ -34,7 +34,8 @@ class LayerWeights:
     post1: Optional[torch.Tensor] = None    # norm applied to the attention output before the residual add (post / sandwich blocks)
     post2: Optional[torch.Tensor] = None    # the same for the FFN output
     wgate: Optional[torch.Tensor] = None    # attention output gate projection [q_size, hidden] (gated attention)
-    kind: str = "attention"                 # token mixer of the layer: attention | gdn
+    kind: str = "attention"                 # token mixer of the layer: attention | gdn | mla
+    mla: Optional[Dict[str, torch.Tensor]] = None   # latent attention: q_a, q_a_norm, q_b (or q), kv_a, kv_a_norm, kv_b
     gdn: Optional[Dict[str, torch.Tensor]] = None   # gated delta net: w_in (q|k|v|z|b|a rows), conv [C, K], dt_bias, a_log, gate_norm
     router: Optional[torch.Tensor] = None   # [E, hidden]
     select_bias: Optional[torch.Tensor] = None   # [E] fp32, added to the router scores for selection only
@@ -261,6 +262,13 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             L = LayerWeights(ln1=get(p + "attn_norm"), ln2=get(p + "ffn_norm"), wqkv=w_in, wo=get(p + "gdn_o"), kind="gdn",
                              gdn={"conv": f32("gdn_conv"), "dt_bias": f32("gdn_dt_bias"), "a_log": f32("gdn_a_log"),
                                   "gate_norm": get(p + "gdn_gate_norm_w")})
+        elif cfg.is_mla:
+            m = {"kv_a": get(p + "attn_kv_a"), "kv_a_norm": get(p + "attn_kv_a_norm"), "kv_b": get(p + "attn_kv_b")}
+            if cfg.q_lora_rank:
+                m.update({"q_a": get(p + "attn_q_a"), "q_a_norm": get(p + "attn_q_a_norm"), "q_b": get(p + "attn_q_b")})
+            else:
+                m["q"] = get(p + "attn_q")
+            L = LayerWeights(ln1=get(p + "attn_norm"), ln2=get(p + "ffn_norm"), wqkv=m["kv_a"], wo=get(p + "attn_o"), kind="mla", mla=m)
         else:
             wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)
             wo = shard_cols(get(p + "attn_o"), tp_rank, tp_world)

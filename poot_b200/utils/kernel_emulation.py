@@ -252,6 +252,27 @@ def attn_paged(q, kpool, vpool, block_tables, row_seq, row_ctx, Hq, Hkv, D, scal
     return out
 
 
+def mla_qkv_write(q, kvb, kva, rope_col, q_out, kpool, vpool, positions, slots, cos, sin, nh, dn, dr, dv):
+    T, half = q.shape[0], dr // 2
+    c = cos[positions.long()].unsqueeze(1)
+    s = sin[positions.long()].unsqueeze(1)
+
+    def rot(t):
+        a, b = t[..., :half], t[..., half:]
+        return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+    qq = q.float().reshape(T, nh, dn + dr)
+    q_out.copy_(_bf(torch.cat([qq[..., :dn], rot(qq[..., dn:])], -1).reshape(T, -1)))
+    kb = kvb.float().reshape(T, nh, dn + dv)
+    kr = rot(kva[:, rope_col:rope_col + dr].float().reshape(T, 1, dr)).expand(T, nh, dr)
+    kfull = torch.cat([kb[..., :dn], kr], -1)
+    live = slots >= 0
+    if live.any():
+        sl = slots[live].long()
+        kpool[sl // K.KV_BLOCK, :, sl % K.KV_BLOCK] = _bf(kfull[live])
+        vpool[sl // K.KV_BLOCK, :, sl % K.KV_BLOCK, :dv] = _bf(kb[live][..., dn:])
+
+
 def attn_general(q, kpool, vpool, block_tables, row_seq, row_ctx, Hq, Hkv, Dk, Dv, scale, out, softcap=0.0, window=0,
                  alibi=None, sinks=None):
     rep = Hq // Hkv
@@ -383,13 +404,18 @@ def token_logprob(logits, picked, out=None):
     return out
 
 
-def moe_route(logits, k, renorm, ids, gates, dense, mode="softmax", select_bias=None, scale=1.0):
+def moe_route(logits, k, renorm, ids, gates, dense, mode="softmax", select_bias=None, scale=1.0, n_group=1, topk_group=1):
     T, E = logits.shape
     s = torch.nan_to_num(logits.float(), nan=torch.finfo(torch.float32).min, posinf=torch.finfo(torch.float32).max,
                          neginf=torch.finfo(torch.float32).min)
     if mode == "sigmoid":
         score = torch.sigmoid(s)
         rankv = score + (select_bias.float() if select_bias is not None else 0.0)
+        if n_group > 1:
+            gs = rankv.reshape(T, n_group, E // n_group).topk(2, dim=-1).values.sum(-1)
+            gorder = torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :topk_group]
+            keep = torch.zeros(T, n_group, dtype=torch.bool).scatter_(1, gorder, True)
+            rankv = torch.where(keep.repeat_interleave(E // n_group, 1), rankv, torch.zeros_like(rankv))
         order = torch.sort(rankv, dim=-1, descending=True, stable=True).indices[:, :k]
         g = score.gather(-1, order)
         if renorm:
@@ -454,7 +480,7 @@ def emulated_kernels():
                 gated_act=gated_act, softcap_=softcap_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
-                attn_paged=attn_paged, attn_general=attn_general, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
+                attn_paged=attn_paged, attn_general=attn_general, mla_qkv_write=mla_qkv_write, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
                 argmax=argmax, argmax_partials=argmax_partials, argmax_combine=argmax_combine,
                 sample_gumbel=sample_gumbel, decode_advance=decode_advance,
                 status_word=lambda device=None: _status, check_status=lambda device=None: None),

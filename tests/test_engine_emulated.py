@@ -170,6 +170,12 @@ HF_FAMILIES = {
                   "linear_num_value_heads": 4, "linear_num_key_heads": 2, "linear_key_head_dim": 64, "linear_value_head_dim": 64,
                   "num_experts": 16, "num_experts_per_tok": 10, "moe_intermediate_size": 64, "shared_expert_intermediate_size": 128,
                   "partial_rotary_factor": 0.25},
+    "deepseek2": {"model_type": "deepseek_v2", "n_routed_experts": 8, "num_experts_per_tok": 3, "moe_intermediate_size": 64,
+                  "first_k_dense_replace": 1, "kv_lora_rank": 64, "q_lora_rank": None, "qk_rope_head_dim": 32,
+                  "qk_nope_head_dim": 64, "v_head_dim": 64, "n_shared_experts": 2, "num_key_value_heads": 4},
+    "deepseek3": {"model_type": "deepseek_v3", "n_routed_experts": 8, "num_experts_per_tok": 3, "moe_intermediate_size": 64,
+                  "first_k_dense_replace": 1, "kv_lora_rank": 64, "q_lora_rank": 96, "qk_rope_head_dim": 32, "qk_nope_head_dim": 64,
+                  "v_head_dim": 64, "n_shared_experts": 1, "n_group": 4, "topk_group": 2, "num_key_value_heads": 4},
     "minimax_m2": {"model_type": "minimax_m2", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
     "granite": {"model_type": "granite", "embedding_multiplier": 6.0, "residual_multiplier": 0.5, "logits_scaling": 4.0,
                 "attention_multiplier": 0.1},
@@ -200,7 +206,7 @@ def test_family_blocks_on_the_engine_match_the_graph_oracle(name):
             w[k] = np.log(np.random.default_rng(3).uniform(0.5, 4.0, w[k].shape)).astype(np.float32)
     w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}     # what the device will hold
     named = {k: torch.from_numpy(v) for k, v in w.items()}
-    for l in range(cfg.n_layers if cfg.is_moe else 0):
+    for l in [l for l in range(cfg.n_layers) if cfg.has_ffn(l) and cfg.moe_layer(l)]:
         p = f"layers.{l}."
         for e in range(cfg.n_experts):
             named[p + f"experts.{e}.gate"] = named[p + "experts_in"][e, :cfg.moe_ffn]

@@ -136,7 +136,7 @@ def test_bias_and_constant_multipliers(kw):
 
 
 @pytest.mark.xfail(strict=False, reason="new device paths: not yet run on a device")
-@pytest.mark.parametrize("name", ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "minimax_m2", "qwen3_5", "qwen3next"])
+@pytest.mark.parametrize("name", ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "minimax_m2", "qwen3_5", "qwen3next", "deepseek2", "deepseek3"])
 def test_family_blocks_match_the_graph_oracle(name):
     """The device twin of the host-emulated check: sandwich / post norms, GeGLU, soft caps, two rope bases,
     projection-wide q/k norms and layers without rope on the real kernels, against the graph oracle."""
@@ -153,7 +153,7 @@ def test_family_blocks_match_the_graph_oracle(name):
     w = random_weights_f32(model, seed=2, std=0.08)
     w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}
     named = {k: torch.from_numpy(v) for k, v in w.items()}
-    for l in range(cfg.n_layers if cfg.is_moe else 0):
+    for l in [l for l in range(cfg.n_layers) if cfg.has_ffn(l) and cfg.moe_layer(l)]:
         p = f"layers.{l}."
         for e in range(cfg.n_experts):
             named[p + f"experts.{e}.gate"] = named[p + "experts_in"][e, :cfg.moe_ffn]

@@ -121,7 +121,7 @@ def test_device_gaps_name_what_the_device_program_lacks():
     for name in ("gemma2", "gemma3", "olmo2", "olmoe", "smollm3", "granitemoe", "minimax_m2", "qwen3next"):      # only the tiny test head width is in the way
         assert all("16" in g for g in reg.resolve_hf(header(name)).cfg.device_gaps()), name
     for name, word in (("nemotron_h", "Mamba2"), ("bloom", "LayerNorm"), ("mpt", "alibi"),
-                       ("gpt_oss", "sinks"), ("deepseek3", "latent attention"), ("deepseek3", "group-limited")):
+                       ("gpt_oss", "sinks"), ("nemotron_h", "single-mixer")):
         gaps = reg.resolve_hf(header(name)).cfg.device_gaps()
         assert any(word in g for g in gaps), (name, gaps)
 

@@ -415,3 +415,35 @@ def test_general_attention_matches_its_host_restatement(Dk, Dv, extras):
         K.attn_general(q.cuda(), kpool.cuda(), vpool.cuda(), bt.cuda(), row_seq.cuda(), row_ctx.cuda(), Hq, Hkv, Dk, Dv, 0.11, got,
                        cap, window, None if alibi is None else alibi.cuda(), None if sinks is None else sinks.cuda())
         assert (got.float().cpu() - want.float()).abs().max().item() < 0.02
+
+
+@pytest.mark.xfail(strict=False, reason="latent attention assembly and group-limited routing: not yet run on a device")
+def test_mla_assembly_and_group_limited_router_match_their_host_restatements():
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.ops import moe_ops as M
+    from poot_b200.utils import kernel_emulation as emu
+    g = torch.Generator().manual_seed(0)
+    T, nh, dn, dr, dv, rk, blocks = 9, 4, 64, 32, 64, 48, 6
+    q = torch.randn(T, nh * (dn + dr), generator=g).to(torch.bfloat16)
+    kvb = torch.randn(T, nh * (dn + dv), generator=g).to(torch.bfloat16)
+    kva = torch.randn(T, rk + dr, generator=g).to(torch.bfloat16)
+    pos = torch.arange(3, 3 + T, dtype=torch.int32)
+    slots = torch.tensor([5, 6, 7, -1, 40, 41, 42, 43, 90], dtype=torch.int32)
+    ang = torch.arange(64)[:, None] * (1.0 / 10000 ** (torch.arange(dr // 2) / (dr // 2)))[None]
+    cos, sin = torch.cos(ang).float(), torch.sin(ang).float()
+    ref = [torch.zeros(T, nh * (dn + dr), dtype=torch.bfloat16), torch.zeros(blocks, nh, 16, dn + dr, dtype=torch.bfloat16),
+           torch.zeros(blocks, nh, 16, dn + dr, dtype=torch.bfloat16)]
+    emu.mla_qkv_write(q, kvb, kva, rk, ref[0], ref[1], ref[2], pos, slots, cos, sin, nh, dn, dr, dv)
+    dev = [torch.zeros_like(t).cuda() for t in ref]
+    K.mla_qkv_write(q.cuda(), kvb.cuda(), kva.cuda(), rk, dev[0], dev[1], dev[2], pos.cuda(), slots.cuda(), cos.cuda(), sin.cuda(),
+                    nh, dn, dr, dv)
+    for a, b in zip(dev, ref):
+        assert (a.float().cpu() - b.float()).abs().max().item() < 0.02
+    E, k = 32, 6
+    logits = torch.randn(21, E, generator=g) * 2
+    bias = torch.randn(E, generator=g) * 0.2
+    want = [torch.zeros(21 * k, dtype=torch.int32), torch.zeros(21 * k), torch.zeros(E * 21)]
+    emu.moe_route(logits, k, True, *want, mode="sigmoid", select_bias=bias, scale=2.5, n_group=8, topk_group=3)
+    got = [torch.zeros(21 * k, dtype=torch.int32, device="cuda"), torch.zeros(21 * k, device="cuda"), torch.zeros(E * 21, device="cuda")]
+    M.moe_route(logits.cuda(), k, True, *got, mode="sigmoid", select_bias=bias.cuda(), scale=2.5, n_group=8, topk_group=3)
+    assert torch.equal(got[0].cpu(), want[0]) and torch.allclose(got[1].cpu(), want[1], rtol=1e-5, atol=1e-6)
