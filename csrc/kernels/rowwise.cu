@@ -122,9 +122,10 @@ __global__ void swiglu_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat1
   }
 }
 
-// act(gate) * up for gated FFNs whose activation is not SiLU (GeGLU): act 0 = SiLU, 1 = GELU (tanh form), 2 = GELU (erf).
+// act(gate) * up for gated FFNs whose activation is not plain SiLU: act 0 = SiLU, 1 = GELU (tanh form), 2 = GELU (erf),
+// 3 = clamped SwiGLU.
 __global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
-                                 int T, int F, int interleaved, int act) {
+                                 int T, int F, int interleaved, int act, float limit, float alpha) {
   pdl_wait(); pdl_launch();
   size_t n = (size_t)T * F;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
@@ -144,6 +145,10 @@ __global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bflo
       a = g / (1.f + __expf(-2.f * z));
     } else if (act == 2) {
       a = 0.5f * g * (1.f + erff(g * 0.7071067811865475f));
+    } else if (act == 3) {          // clamped SwiGLU: gate <= limit, |up| <= limit, (up + 1) * gate * sigmoid(alpha * gate)
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit) + 1.f;
+      a = g / (1.f + __expf(-alpha * g));
     } else {
       a = silu(g);
     }
@@ -258,14 +263,15 @@ POOT_API int poot_swiglu(const void* gu, void* out, int T, int F, int interleave
   return (int)cudaGetLastError();
 }
 
-POOT_API int poot_gated_act(const void* gu, void* out, int T, int F, int interleaved, int act, cudaStream_t s) {
+POOT_API int poot_gated_act(const void* gu, void* out, int T, int F, int interleaved, int act, float limit, float alpha,
+                            cudaStream_t s) {
   size_t n = (size_t)T * F;
   if (n == 0) return 0;
-  if (act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+  if (act < 0 || act > 3 || (act == 3 && !(limit > 0.f))) return (int)cudaErrorInvalidValue;
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   return launch_k(gated_act_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F,
-                  interleaved, act);
+                  interleaved, act, limit, alpha);
 }
 
 POOT_API int poot_softcap_f32(void* x, long long n, float cap, cudaStream_t s) {

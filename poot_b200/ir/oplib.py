@@ -12,7 +12,7 @@ from __future__ import annotations
 import math
 from typing import Optional, Sequence
 
-from ..tensor import DType
+from ..tensor import DType, alibi_slopes  # noqa: F401  (re-exported: callers take it from the op library)
 from .builder import Builder, Traced
 
 F32, I32 = DType.F32, DType.I32
@@ -183,25 +183,6 @@ def attention_masked(b: Builder, q: Traced, k: Traced, v: Traced, mask: Traced, 
     R, H, T, S = scores.shape
     scores = scores + b.broadcast(b.reshape(mask, (R, 1, T, S)), scores.shape)
     return b.matmul(softmax(b, scores), v)
-
-
-def alibi_slopes(n_heads: int, kind: str = "bloom", bias_max: float = 8.0) -> list:
-    """Per-head ALiBi slopes.  ``bloom``: geometric series of the closest power of two, the remaining heads take the
-    odd powers of the next series (Press et al.); ``mpt``: ``2^-(i * bias_max / n2)`` over the next power of two
-    ``n2``, odd entries first when ``n_heads`` is not a power of two."""
-    if kind == "mpt":
-        n2 = 2 ** math.ceil(math.log2(n_heads))
-        sl = [1.0 / 2.0 ** (i * bias_max / n2) for i in range(1, n2 + 1)]
-        if n2 != n_heads:
-            sl = (sl[1::2] + sl[::2])[:n_heads]
-        return sl
-    cp2 = 2 ** math.floor(math.log2(n_heads))
-    base = 2.0 ** (-(2.0 ** -(math.log2(cp2) - 3)))
-    sl = [base ** i for i in range(1, cp2 + 1)]
-    if cp2 != n_heads:
-        extra = 2.0 ** (-(2.0 ** -(math.log2(2 * cp2) - 3)))
-        sl += [extra ** i for i in range(1, 1 + 2 * min(cp2, n_heads - cp2), 2)]
-    return sl
 
 
 def alibi_bias_from_pos(b: Builder, q_pos: Traced, cap: int, slopes: Sequence[float]) -> Traced:

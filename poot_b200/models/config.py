@@ -165,7 +165,8 @@ class DecoderConfig:
         """The pre-norm SwiGLU rope layer the fused tensor-parallel programs are written for."""
         return (self.block == "pre" and self.act == "silu" and not self.qk_norm_wide and self.rope_theta_local is None
                 and (self.rope_layers is None or all(self.rope_layers)) and self.final_softcap == 0
-                and self.layer_kinds is None and not self.attn_gate and not self.is_mla)
+                and self.layer_kinds is None and not self.attn_gate and not self.is_mla and not self.attn_sinks
+                and not self.out_bias and not self.expert_bias and self.swiglu_limit == 0 and not self.router_bias)
 
     def device_gaps(self) -> list:
         """Features of this configuration that the device program does not implement (empty = runs on the device);
@@ -175,12 +176,12 @@ class DecoderConfig:
         if self.block != "pre" and self.is_moe: g.append(f"{self.block}-norm block with routed experts")
         if not self.gated_ffn or self.act not in ("silu", "gelu_tanh", "gelu_erf"): g.append(f"{self.act} {'gated' if self.gated_ffn else 'plain'} FFN")
         if self.act != "silu" and self.is_moe: g.append(f"{self.act} experts")
-        if self.out_bias or self.mlp_bias or self.expert_bias: g.append("output / FFN biases")
+        if self.mlp_bias: g.append("dense FFN biases")
+        if self.out_bias and self.block != "pre": g.append("output bias with a post norm")
         if self.pos != "rope": g.append(f"{self.pos} positions")
         if self.embed_norm: g.append("embedding norm")
-        if self.attn_sinks: g.append("attention sinks")
-        if self.swiglu_limit > 0: g.append("clamped SwiGLU")
-        if self.router_bias or (self.router == "softmax" and self.router_select_bias): g.append("router variant")
+        if self.swiglu_limit > 0 and not self.is_moe: g.append("clamped SwiGLU in a dense FFN")
+        if self.router == "softmax" and self.router_select_bias: g.append("router variant")
         if self.n_group > 32 or (self.n_group > 1 and self.router != "sigmoid"): g.append("group-limited routing outside the sigmoid router")
         if self.shared_width and (not self.gated_ffn or self.act != "silu"): g.append("shared expert that is not a SwiGLU FFN")
         if self.is_moe and self.top_k > 16: g.append("more than 16 experts per token")

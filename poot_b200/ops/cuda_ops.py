@@ -22,7 +22,7 @@ _SIGS = {
     "poot_embed_gather": [_P, _P, _P, c_int, c_int, c_int, _P],
     "poot_rmsnorm": [_P, _P, _P, c_int, c_longlong, _P, _P, c_int, c_int, c_float, _P],
     "poot_swiglu": [_P, _P, c_int, c_int, c_int, _P],
-    "poot_gated_act": [_P, _P, c_int, c_int, c_int, c_int, _P],
+    "poot_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_float, c_float, _P],
     "poot_softcap_f32": [_P, c_longlong, c_float, _P],
     "poot_causal_conv_silu": [_P, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, c_int, _P, _P],
     "poot_gdn_scan": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
@@ -219,17 +219,20 @@ def swiglu(gu: torch.Tensor, interleaved: bool, out: Optional[torch.Tensor] = No
     return out
 
 
-GATED_ACTS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2}
+GATED_ACTS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2, "swiglu_clamped": 3}
 
 
-def gated_act(gu: torch.Tensor, interleaved: bool, act: str, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``act(gate) * up`` over a ``[T, 2F]`` projection output (GeGLU and the other gated FFNs that are not SwiGLU)."""
+def gated_act(gu: torch.Tensor, interleaved: bool, act: str, out: Optional[torch.Tensor] = None, limit: float = 0.0,
+              alpha: float = 1.702) -> torch.Tensor:
+    """``act(gate) * up`` over a ``[T, 2F]`` projection output (GeGLU and the other gated FFNs that are not SwiGLU);
+    ``swiglu_clamped``: ``(clamp(up, +-limit) + 1) * g * sigmoid(alpha * g)`` with ``g = min(gate, limit)``."""
     _need_cuda(gu)
     assert gu.dtype == torch.bfloat16 and gu.is_contiguous()
     T, F2 = gu.shape
     if out is None:
         out = torch.empty(T, F2 // 2, dtype=torch.bfloat16, device=gu.device)
-    check(_fn("poot_gated_act")(_ptr(gu), _ptr(out), T, F2 // 2, int(interleaved), GATED_ACTS[act], _stream()), "gated_act")
+    check(_fn("poot_gated_act")(_ptr(gu), _ptr(out), T, F2 // 2, int(interleaved), GATED_ACTS[act], float(limit), float(alpha),
+                                _stream()), "gated_act")
     return out
 
 

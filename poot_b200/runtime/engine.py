@@ -136,7 +136,13 @@ class DecoderEngine:
         self.logprobs = torch.zeros(max_seqs, dtype=torch.float32, device=dev)
         self.adj_idx = self.adj_val = self.guided_mask = None   # allocated on first use
         # tensor-core prefill attention: tiles cut on the host per step, rows they cover masked out of the per-row kernel
-        self.attn_general = cfg.head_dim not in (64, 128) or cfg.is_mla   # e.g. head_dim 256: served by the general attention kernel
+        # head_dim 256, latent attention, sink logits and ALiBi are served by the general attention kernel
+        self.attn_general = cfg.head_dim not in (64, 128) or cfg.is_mla or cfg.attn_sinks or cfg.pos == "alibi"
+        self.alibi = None
+        if cfg.pos == "alibi":
+            from ..tensor import alibi_slopes
+            sl = alibi_slopes(cfg.n_heads, cfg.alibi_slopes, cfg.alibi_bias_max)
+            self.alibi = torch.tensor(sl[weights.tp_rank * self.hq:(weights.tp_rank + 1) * self.hq], dtype=torch.float32, device=dev)
         self.flash_ok = cfg.head_dim == 128 and cfg.attn_softcap == 0
         self._flash_only = False      # set by bind: every row of the bound step is covered by a tile
         self.attn_tiles = torch.zeros(self._tile_slots(T, max_seqs), 4, dtype=i32, device=dev)
@@ -271,7 +277,7 @@ class DecoderEngine:
                 self._count()
             K.attn_general(self.q[:R], self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables, self.row_seq[:R],
                            self.row_ctx[:R], self.hq, self.hkv, D, D, self.scale, self.attn[:R], softcap=cfg.attn_softcap,
-                           window=cfg.window_of(self.w.layer0 + l))
+                           window=cfg.window_of(self.w.layer0 + l), alibi=self.alibi, sinks=self.w.layers[l].sinks)
             return
         flash = self.flash_ok and T > B
         splits = self._attn_splits(R)
@@ -376,6 +382,8 @@ class DecoderEngine:
                 pending = self._proj_to_residual(self.attn[:T], L.wo, T)
                 if lora:
                     self.lora.apply(self, "o", l, self.attn[:T], h, T)
+                if L.bo is not None:
+                    h.add_(L.bo)
             x = h if cfg.block == "post" else self._norm(L.ln2, T, pending)
             if cfg.moe_layer(w.layer0 + l):
                 pending = self._moe(l, L, x, T)

@@ -35,6 +35,8 @@ def _buffers(eng):
             "gates": torch.zeros(T * k, dtype=torch.float32, device=dev),
             "dense": torch.zeros(E * T, dtype=torch.float32, device=dev),
             "act": torch.zeros(G * Tc * F, dtype=torch.bfloat16, device=dev),
+            "gu": (torch.zeros(G * Tc * 2 * F, dtype=torch.bfloat16, device=dev)
+                   if (c.expert_bias or c.swiglu_limit > 0 or c.act != "silu") else None),
             "parts": torch.zeros(G * Tc * H, dtype=torch.bfloat16, device=dev),
         }
     return eng._moe_buf
@@ -59,6 +61,18 @@ def shared_expert(eng, L, x: torch.Tensor, T: int) -> None:
     K.linear(act, L.sh_wdown, K.EPI_RESID, h, h)
 
 
+def _expert_act(eng, L, gu: torch.Tensor, act: torch.Tensor, expert_of_row: torch.Tensor) -> None:
+    """Bias of each row's expert (when the family has one) and the gated activation over the (gate, up) pairs."""
+    c = eng.cfg
+    if L.ex_bgu is not None:
+        gu.add_(L.ex_bgu[expert_of_row])
+    eng._count()
+    if c.swiglu_limit > 0:
+        K.gated_act(gu, True, "swiglu_clamped", out=act, limit=c.swiglu_limit, alpha=c.swiglu_alpha)
+    else:
+        K.gated_act(gu, True, c.act, out=act)
+
+
 def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
     """``h[:T] += moe(x)``.  ``ep`` selects the expert-parallel form: ``("nccl", comm)`` reduces the local experts'
     partial with a library all-reduce, ``("fused", comm, rs_site)`` pushes it into every rank's inbox from the GEMM
@@ -75,6 +89,8 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
             K.linear(x[t0:t0 + 128], L.router, K.EPI_F32, logits[t0:t0 + 128])
     else:
         K.linear(x, L.router, K.EPI_F32, logits)
+    if L.router_bias is not None:
+        logits.add_(L.router_bias)
     ids, gates = buf["ids"][:T * k], buf["gates"][:T * k]
     dense = buf["dense"][:E * T].view(E, T)
     M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense, mode=c.router, select_bias=L.select_bias,
@@ -86,9 +102,16 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
         act = buf["act"][:G * F].view(G, F)
         parts = buf["parts"][:G * H].view(G, H)
         eng._count(3)
-        M.gemm_grouped(K.EPI_SWIGLU, x, L.ex_wgu, act, 1, G, group_expert=ids, x_row_div=k, out_group_stride=F, ldo=F)
+        if buf["gu"] is None:
+            M.gemm_grouped(K.EPI_SWIGLU, x, L.ex_wgu, act, 1, G, group_expert=ids, x_row_div=k, out_group_stride=F, ldo=F)
+        else:           # biased / clamped experts: plain projection, bias of the group's expert, then the activation
+            gu = buf["gu"][:G * 2 * F].view(G, 2 * F)
+            M.gemm_grouped(K.EPI_STORE, x, L.ex_wgu, gu, 1, G, group_expert=ids, x_row_div=k, out_group_stride=2 * F, ldo=2 * F)
+            _expert_act(eng, L, gu, act, ids.long())
         M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, parts, 1, G, group_expert=ids, x_row_mul=1, out_group_stride=H,
                        row_scale=gates, ldo=H)
+        if L.ex_bdown is not None:
+            parts.add_((L.ex_bdown[ids.long()].float() * gates[:, None]).to(parts.dtype))
         M.moe_combine(h, parts, h, T, H, G, H, per_token=k)
         return None
     if ep is not None and e_local == 1 and T > 128:
@@ -111,13 +134,21 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
         act = buf["act"][:e_local * n * F].view(e_local * n, F)
         scale = dense[e0:e0 + e_local, t0:t0 + n].contiguous() if (t0 or n != T or e_local != E) else dense
         eng._count(2)
-        M.gemm_grouped(K.EPI_SWIGLU, xs, L.ex_wgu, act, n, e_local, out_group_stride=n * F, ldo=F)
+        if buf["gu"] is None:
+            M.gemm_grouped(K.EPI_SWIGLU, xs, L.ex_wgu, act, n, e_local, out_group_stride=n * F, ldo=F)
+        else:
+            gu = buf["gu"][:e_local * n * 2 * F].view(e_local * n, 2 * F)
+            M.gemm_grouped(K.EPI_STORE, xs, L.ex_wgu, gu, n, e_local, out_group_stride=n * 2 * F, ldo=2 * F)
+            _expert_act(eng, L, gu, act, torch.arange(e0, e0 + e_local, device=gu.device).repeat_interleave(n))
         if tp is not None and e_local == 1 and T <= 128:
             M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, None, n, 1, x_row_mul=n, row_scale=scale, ldo=H, tp=tp)
             return "pushed"
         parts = buf["parts"][:e_local * n * H].view(e_local * n, H)
         M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, parts, n, e_local, x_row_mul=n, out_group_stride=n * H,
                        row_scale=scale, ldo=H)
+        if L.ex_bdown is not None:      # the bias is part of the expert's output, so it is scaled by the row's gate too
+            sc = dense[e0:e0 + e_local, t0:t0 + n].reshape(e_local * n, 1)
+            parts.add_((L.ex_bdown[e0:e0 + e_local].float().repeat_interleave(n, 0) * sc).to(parts.dtype))
         eng._count()
         if ep is None:
             M.moe_combine(h[t0:t0 + n], parts, h[t0:t0 + n], n, H, e_local, n * H)

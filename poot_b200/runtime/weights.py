@@ -34,6 +34,11 @@ class LayerWeights:
     post1: Optional[torch.Tensor] = None    # norm applied to the attention output before the residual add (post / sandwich blocks)
     post2: Optional[torch.Tensor] = None    # the same for the FFN output
     wgate: Optional[torch.Tensor] = None    # attention output gate projection [q_size, hidden] (gated attention)
+    bo: Optional[torch.Tensor] = None       # bias of the attention output projection
+    sinks: Optional[torch.Tensor] = None    # [heads] fp32 sink logits joining every softmax denominator
+    router_bias: Optional[torch.Tensor] = None    # [E] fp32 added to the router logits
+    ex_bgu: Optional[torch.Tensor] = None   # [E, 2F] expert gate/up biases in the interleaved row order of ex_wgu
+    ex_bdown: Optional[torch.Tensor] = None  # [E, hidden] expert down-projection biases
     kind: str = "attention"                 # token mixer of the layer: attention | gdn | mla
     mla: Optional[Dict[str, torch.Tensor]] = None   # latent attention: q_a, q_a_norm, q_b (or q), kv_a, kv_a_norm, kv_b
     gdn: Optional[Dict[str, torch.Tensor]] = None   # gated delta net: w_in (q|k|v|z|b|a rows), conv [C, K], dt_bias, a_log, gate_norm
@@ -275,6 +280,10 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             L = LayerWeights(ln1=get(p + "attn_norm") if pre else None, ln2=get(p + "ffn_norm") if pre else None, wqkv=wqkv, wo=wo)
             if cfg.attn_gate:
                 L.wgate = shard_rows(get(p + "attn_gate"), tp_rank, tp_world)
+            if cfg.out_bias:
+                L.bo = get(p + "attn_o_bias")
+            if cfg.attn_sinks:
+                L.sinks = tensors[p + "attn_sinks"].to(device=dev, dtype=torch.float32).contiguous()
         if cfg.block in ("post", "sandwich"):
             L.post1, L.post2 = get(p + "attn_post_norm"), get(p + "ffn_post_norm")
         if cfg.attn_bias:
@@ -285,6 +294,13 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             L.router = get(p + "ffn_router")
             if cfg.router_select_bias:
                 L.select_bias = tensors[p + "ffn_router_select_bias"].to(device=dev, dtype=torch.float32).contiguous()
+            if cfg.router_bias:
+                L.router_bias = tensors[p + "ffn_router_bias"].to(device=dev, dtype=torch.float32).contiguous()
+            if cfg.expert_bias:
+                b = get(p + "experts_in_bias")                       # [E, 2F]: gate half then up half
+                F_ = cfg.moe_ffn
+                L.ex_bgu = torch.stack([b[:, :F_], b[:, F_:]], dim=2).reshape(b.shape[0], 2 * F_).contiguous()
+                L.ex_bdown = get(p + "experts_out_bias")
             if cfg.shared_width:
                 L.sh_wgu = interleave_gate_up(get(p + "shared_gate"), get(p + "shared_up"))
                 L.sh_wdown = get(p + "shared_down")

@@ -7,6 +7,8 @@ carrier the loaders, the oracle and the executors exchange.  Storage dtypes with
 """
 from __future__ import annotations
 
+import math
+
 import enum
 from dataclasses import dataclass
 from typing import Sequence, Tuple
@@ -174,3 +176,23 @@ class HostTensor:
     def view(self, start_row: int, rows: int) -> "HostTensor":
         """A zero-copy view of a run of leading-axis rows (``HostView`` of the reference)."""
         return HostTensor((rows,) + tuple(self.shape[1:]), self.dtype, self.data[start_row:start_row + rows])
+
+
+# ---- position helpers shared by the tracer and the device engine ------------------------------------------------
+def alibi_slopes(n_heads: int, kind: str = "bloom", bias_max: float = 8.0) -> list:
+    """Per-head ALiBi slopes.  ``bloom``: geometric series of the closest power of two, the remaining heads take the
+    odd powers of the next series (Press et al.); ``mpt``: ``2^-(i * bias_max / n2)`` over the next power of two
+    ``n2``, odd entries first when ``n_heads`` is not a power of two."""
+    if kind == "mpt":
+        n2 = 2 ** math.ceil(math.log2(n_heads))
+        sl = [1.0 / 2.0 ** (i * bias_max / n2) for i in range(1, n2 + 1)]
+        if n2 != n_heads:
+            sl = (sl[1::2] + sl[::2])[:n_heads]
+        return sl
+    cp2 = 2 ** math.floor(math.log2(n_heads))
+    base = 2.0 ** (-(2.0 ** -(math.log2(cp2) - 3)))
+    sl = [base ** i for i in range(1, cp2 + 1)]
+    if cp2 != n_heads:
+        extra = 2.0 ** (-(2.0 ** -(math.log2(2 * cp2) - 3)))
+        sl += [extra ** i for i in range(1, 1 + 2 * min(cp2, n_heads - cp2), 2)]
+    return sl

@@ -68,13 +68,17 @@ def swiglu(gu, interleaved, out=None):
     return out
 
 
-def gated_act(gu, interleaved, act, out=None):
+def gated_act(gu, interleaved, act, out=None, limit=0.0, alpha=1.702):
     g = gu.float()
     F = g.shape[1] // 2
     gate, up = (g[:, 0::2], g[:, 1::2]) if interleaved else (g[:, :F], g[:, F:])
-    fn = {"silu": torch.nn.functional.silu, "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
-          "gelu_erf": torch.nn.functional.gelu}[act]
-    r = _bf(fn(gate) * up)
+    if act == "swiglu_clamped":
+        gate = gate.clamp(max=limit)
+        r = _bf((up.clamp(-limit, limit) + 1.0) * gate * torch.sigmoid(alpha * gate))
+    else:
+        fn = {"silu": torch.nn.functional.silu, "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
+              "gelu_erf": torch.nn.functional.gelu}[act]
+        r = _bf(fn(gate) * up)
     if out is None:
         return r
     out.copy_(r)
