@@ -156,6 +156,52 @@ __global__ void gated_act_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bflo
   }
 }
 
+// LayerNorm over the last axis: (x - mean) * rsqrt(var + eps) * w (+ b).  One CTA of 256 threads per row.
+__global__ void __launch_bounds__(256)
+layernorm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
+                 float eps, __nv_bfloat16* __restrict__ out, int D) {
+  __shared__ float red[2][8];
+  pdl_wait(); pdl_launch();
+  const __nv_bfloat16* xr = x + (size_t)blockIdx.x * D;
+  __nv_bfloat16* o = out + (size_t)blockIdx.x * D;
+  float s = 0.f, ss = 0.f;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) { const float v = __bfloat162float(xr[i]); s += v; ss += v * v; }
+  s = warp_sum(s); ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) { red[0][threadIdx.x >> 5] = s; red[1][threadIdx.x >> 5] = ss; }
+  __syncthreads();
+  s = 0.f; ss = 0.f;
+  for (int i = 0; i < 8; ++i) { s += red[0][i]; ss += red[1][i]; }
+  const float mean = s / (float)D;
+  const float var = fmaxf(ss / (float)D - mean * mean, 0.f);
+  const float inv = rsqrtf(var + eps);
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = (__bfloat162float(xr[i]) - mean) * inv * __bfloat162float(w[i]);
+    if (b != nullptr) v += __bfloat162float(b[i]);
+    o[i] = __float2bfloat16(v);
+  }
+}
+
+// x = act(x) in place over bf16: 1 = GELU (tanh form), 2 = GELU (erf), 4 = squared ReLU, 0 = SiLU
+__global__ void act_bf16_kernel(__nv_bfloat16* __restrict__ x, size_t n, int act) {
+  pdl_wait(); pdl_launch();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float g = __bfloat162float(x[i]);
+    float a;
+    if (act == 1) {
+      const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+      a = g / (1.f + __expf(-2.f * z));
+    } else if (act == 2) {
+      a = 0.5f * g * (1.f + erff(g * 0.7071067811865475f));
+    } else if (act == 4) {
+      const float r = fmaxf(g, 0.f);
+      a = r * r;
+    } else {
+      a = silu(g);
+    }
+    x[i] = __float2bfloat16(a);
+  }
+}
+
 // x = cap * tanh(x / cap) in place over fp32 logits
 __global__ void softcap_f32_kernel(float* __restrict__ x, size_t n, float cap, float inv_cap) {
   pdl_wait(); pdl_launch();
@@ -272,6 +318,21 @@ POOT_API int poot_gated_act(const void* gu, void* out, int T, int F, int interle
   if (blocks > 148 * 16) blocks = 148 * 16;
   return launch_k(gated_act_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, F,
                   interleaved, act, limit, alpha);
+}
+
+POOT_API int poot_layernorm(const void* x, const void* w, const void* b, float eps, void* out, int T, int D, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (D < 1) return (int)cudaErrorInvalidValue;
+  return launch_k(layernorm_kernel, dim3(T), dim3(256), 0, s, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                  (const __nv_bfloat16*)b, eps, (__nv_bfloat16*)out, D);
+}
+
+POOT_API int poot_act_bf16(void* x, long long n, int act, cudaStream_t s) {
+  if (n == 0) return 0;
+  if (act != 0 && act != 1 && act != 2 && act != 4) return (int)cudaErrorInvalidValue;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch_k(act_bf16_kernel, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16*)x, (size_t)n, act);
 }
 
 POOT_API int poot_softcap_f32(void* x, long long n, float cap, cudaStream_t s) {

@@ -166,20 +166,20 @@ class DecoderConfig:
         return (self.block == "pre" and self.act == "silu" and not self.qk_norm_wide and self.rope_theta_local is None
                 and (self.rope_layers is None or all(self.rope_layers)) and self.final_softcap == 0
                 and self.layer_kinds is None and not self.attn_gate and not self.is_mla and not self.attn_sinks
-                and not self.out_bias and not self.expert_bias and self.swiglu_limit == 0 and not self.router_bias)
+                and not self.out_bias and not self.expert_bias and self.swiglu_limit == 0 and not self.router_bias
+                and self.norm_kind == "rms" and self.gated_ffn and self.pos == "rope" and not self.embed_norm)
 
     def device_gaps(self) -> list:
         """Features of this configuration that the device program does not implement (empty = runs on the device);
         the CPU oracle evaluates all of them."""
         g = []
-        if self.norm_kind != "rms": g.append("LayerNorm")
+        if self.norm_kind != "rms" and self.block != "pre": g.append("LayerNorm with a post norm")
         if self.block != "pre" and self.is_moe: g.append(f"{self.block}-norm block with routed experts")
-        if not self.gated_ffn or self.act not in ("silu", "gelu_tanh", "gelu_erf"): g.append(f"{self.act} {'gated' if self.gated_ffn else 'plain'} FFN")
+        if self.gated_ffn and self.act not in ("silu", "gelu_tanh", "gelu_erf"): g.append(f"{self.act} gated FFN")
+        if not self.gated_ffn and self.is_moe: g.append("experts without a gate")
         if self.act != "silu" and self.is_moe: g.append(f"{self.act} experts")
-        if self.mlp_bias: g.append("dense FFN biases")
+        if self.mlp_bias and self.gated_ffn: g.append("biases of a gated dense FFN")
         if self.out_bias and self.block != "pre": g.append("output bias with a post norm")
-        if self.pos != "rope": g.append(f"{self.pos} positions")
-        if self.embed_norm: g.append("embedding norm")
         if self.swiglu_limit > 0 and not self.is_moe: g.append("clamped SwiGLU in a dense FFN")
         if self.router == "softmax" and self.router_select_bias: g.append("router variant")
         if self.n_group > 32 or (self.n_group > 1 and self.router != "sigmoid"): g.append("group-limited routing outside the sigmoid router")

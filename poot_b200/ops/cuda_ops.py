@@ -24,6 +24,8 @@ _SIGS = {
     "poot_swiglu": [_P, _P, c_int, c_int, c_int, _P],
     "poot_gated_act": [_P, _P, c_int, c_int, c_int, c_int, c_float, c_float, _P],
     "poot_softcap_f32": [_P, c_longlong, c_float, _P],
+    "poot_layernorm": [_P, _P, _P, c_float, _P, c_int, c_int, _P],
+    "poot_act_bf16": [_P, c_longlong, c_int, _P],
     "poot_causal_conv_silu": [_P, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, c_int, _P, _P],
     "poot_gdn_scan": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
     "poot_gated_rmsnorm": [_P, _P, c_int, c_int, _P, c_float, _P, c_int, c_int, c_int, _P],
@@ -234,6 +236,27 @@ def gated_act(gu: torch.Tensor, interleaved: bool, act: str, out: Optional[torch
     check(_fn("poot_gated_act")(_ptr(gu), _ptr(out), T, F2 // 2, int(interleaved), GATED_ACTS[act], float(limit), float(alpha),
                                 _stream()), "gated_act")
     return out
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``(x - mean) / sqrt(var + eps) * w (+ b)`` over the last axis (bf16)."""
+    _need_cuda(x, w)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and w.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty_like(x)
+    check(_fn("poot_layernorm")(_ptr(x), _ptr(w), _ptr(b), float(eps), _ptr(out), x.shape[0], x.shape[1], _stream()), "layernorm")
+    return out
+
+
+PLAIN_ACTS = {"silu": 0, "gelu_tanh": 1, "gelu_erf": 2, "relu2": 4}
+
+
+def act_(x: torch.Tensor, act: str) -> torch.Tensor:
+    """``x = act(x)`` in place (bf16): the activation of FFNs without a gate."""
+    _need_cuda(x)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    check(_fn("poot_act_bf16")(_ptr(x), x.numel(), PLAIN_ACTS[act], _stream()), "act")
+    return x
 
 
 def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:

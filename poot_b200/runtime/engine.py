@@ -165,7 +165,7 @@ class DecoderEngine:
             c2, s2 = rope_tables(dataclasses.replace(cfg, rope_theta=cfg.rope_theta_local, rope_scaling=RopeScaling()),
                                  cfg.max_position)
             self.cos_local, self.sin_local = c2.to(dev), s2.to(dev)
-        if cfg.rope_layers is not None and not all(cfg.rope_layers):   # layers without a position signal: the identity rotation
+        if cfg.pos != "rope" or (cfg.rope_layers is not None and not all(cfg.rope_layers)):   # no position signal: the identity rotation
             self.cos_none, self.sin_none = torch.ones_like(self.cos), torch.zeros_like(self.sin)
         # attention layers own K/V pool entries; recurrent layers own state entries
         kinds = [cfg.mixer_of(weights.layer0 + i) for i in range(len(weights.layers))]
@@ -255,9 +255,15 @@ class DecoderEngine:
         self._linear(x, W, K.EPI_RESID, h, h)
         return None
 
-    def _norm(self, w, T, pending):
+    def _norm(self, w, T, pending, bias=None):
         h, x = self.h[:T], self.x[:T]
         self._count()
+        if self.cfg.norm_kind == "layer":
+            if pending is not None:
+                self._count()
+                K.reduce_partials(h, pending, h)
+            K.layernorm(h, w, bias, self.cfg.norm_eps, out=x)
+            return x
         if pending is None:
             K.rmsnorm(h, w, self.cfg.norm_eps, out=x)
         else:
@@ -332,11 +338,14 @@ class DecoderEngine:
                 K.embed_gather(self.tokens[:T], w.embed, out=h)
             if cfg.embed_scale != 1.0:
                 h.mul_(cfg.embed_scale)
+            if w.embed_norm is not None:
+                self._count()
+                K.layernorm(h, w.embed_norm, w.embed_norm_b, cfg.norm_eps, out=h)
         pending = None
         lora = shape.lora and self.lora is not None
         post = cfg.block != "pre"           # a norm sits between each projection and its residual add
         for l, L in enumerate(w.layers):
-            x = h if cfg.block == "post" else self._norm(L.ln1, T, pending)
+            x = h if cfg.block == "post" else self._norm(L.ln1, T, pending, L.ln1_b)
             if L.kind == "mla":
                 pending = self._mla_mixer(l, L, x, T)
                 x = self._norm(L.ln2, T, pending)
@@ -384,9 +393,18 @@ class DecoderEngine:
                     self.lora.apply(self, "o", l, self.attn[:T], h, T)
                 if L.bo is not None:
                     h.add_(L.bo)
-            x = h if cfg.block == "post" else self._norm(L.ln2, T, pending)
+            x = h if cfg.block == "post" else self._norm(L.ln2, T, pending, L.ln2_b)
             if cfg.moe_layer(w.layer0 + l):
                 pending = self._moe(l, L, x, T)
+            elif not cfg.gated_ffn:             # down(act(up(x) + b) ) + b: no gate
+                up = self._linear(x, L.wgu, K.EPI_STORE, self.act[:T])
+                if L.bgu is not None:
+                    up.add_(L.bgu)
+                self._count()
+                K.act_(up, cfg.act)
+                pending = self._proj_to_residual(up, L.wdown, T)
+                if L.bdown is not None:
+                    h.add_(L.bdown)
             else:
                 if cfg.act == "silu" and not lora:
                     act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
@@ -419,7 +437,10 @@ class DecoderEngine:
             self._count()
             torch.index_select(h, 0, self.logit_idx[:B], out=hl)
         self._count()
-        K.rmsnorm(hl, w.final_norm, cfg.norm_eps, out=self.xl[:B])
+        if cfg.norm_kind == "layer":
+            K.layernorm(hl, w.final_norm, w.final_norm_b, cfg.norm_eps, out=self.xl[:B])
+        else:
+            K.rmsnorm(hl, w.final_norm, cfg.norm_eps, out=self.xl[:B])
         self._linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits_local[:B])
         if cfg.final_softcap > 0:
             self._count()
@@ -472,7 +493,7 @@ class DecoderEngine:
 
     def _rope_tables_of(self, l: int):
         cfg = self.cfg
-        if self.cos_none is not None and not cfg.rope_layers[l]:
+        if self.cos_none is not None and (cfg.pos != "rope" or not cfg.rope_layers[l]):
             return self.cos_none, self.sin_none
         if self.cos_local is not None and cfg.window_of(l) > 0:
             return self.cos_local, self.sin_local

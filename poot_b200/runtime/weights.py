@@ -35,6 +35,10 @@ class LayerWeights:
     post2: Optional[torch.Tensor] = None    # the same for the FFN output
     wgate: Optional[torch.Tensor] = None    # attention output gate projection [q_size, hidden] (gated attention)
     bo: Optional[torch.Tensor] = None       # bias of the attention output projection
+    ln1_b: Optional[torch.Tensor] = None    # LayerNorm biases (families whose norms carry one)
+    ln2_b: Optional[torch.Tensor] = None
+    bgu: Optional[torch.Tensor] = None      # dense FFN biases: gate/up (interleaved like wgu, or up only) and down
+    bdown: Optional[torch.Tensor] = None
     sinks: Optional[torch.Tensor] = None    # [heads] fp32 sink logits joining every softmax denominator
     router_bias: Optional[torch.Tensor] = None    # [E] fp32 added to the router logits
     ex_bgu: Optional[torch.Tensor] = None   # [E, 2F] expert gate/up biases in the interleaved row order of ex_wgu
@@ -87,6 +91,9 @@ class DecoderWeights:
     ep_world: int = 1
     quant: Dict[str, object] = field(default_factory=dict)
     stage: Optional[StageSpec] = None      # None = the whole model; else ``layers`` holds layers [stage.l0, stage.l1)
+    final_norm_b: Optional[torch.Tensor] = None
+    embed_norm: Optional[torch.Tensor] = None     # LayerNorm right after the embedding (bloom), with its bias
+    embed_norm_b: Optional[torch.Tensor] = None
 
     @property
     def layer0(self) -> int:
@@ -312,10 +319,17 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
                 gus.append(interleave_gate_up(get(p + f"experts.{e}.gate"), get(p + f"experts.{e}.up")))
                 downs.append(get(p + f"experts.{e}.down"))
             L.ex_wgu, L.ex_wdown = torch.stack(gus), torch.stack(downs)
-        else:
+        elif cfg.gated_ffn:
             L.wgu = interleave_gate_up(shard_rows(get(p + "ffn_gate"), tp_rank, tp_world),
                                        shard_rows(get(p + "ffn_up"), tp_rank, tp_world))
             L.wdown = shard_cols(get(p + "ffn_down"), tp_rank, tp_world)
+        else:                                   # down(act(up(x))): no gate
+            L.wgu = shard_rows(get(p + "ffn_up"), tp_rank, tp_world)
+            L.wdown = shard_cols(get(p + "ffn_down"), tp_rank, tp_world)
+            if cfg.mlp_bias:
+                L.bgu, L.bdown = get(p + "ffn_up_bias"), get(p + "ffn_down_bias")
+        if cfg.norm_kind == "layer" and cfg.norm_bias:
+            L.ln1_b, L.ln2_b = get(p + "attn_norm_bias"), get(p + "ffn_norm_bias")
         layers.append(L)
     tied = cfg.tie_embeddings or "lm_head" not in tensors
     embed = get("embed") if (st.first or (st.last and tied)) else None
@@ -326,8 +340,14 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             lm_head = shard_rows(lm_head, tp_rank, tp_world)
     if not st.first:
         embed = None
-    return fold_scales(DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm") if st.last else None,
-                                      lm_head=lm_head, layers=layers, tp_rank=tp_rank, tp_world=tp_world, stage=stage))
+    dw = DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm") if st.last else None,
+                        lm_head=lm_head, layers=layers, tp_rank=tp_rank, tp_world=tp_world, stage=stage)
+    if cfg.norm_kind == "layer" and cfg.norm_bias and st.last:
+        dw.final_norm_b = get("final_norm_bias")
+    if cfg.embed_norm and st.first:
+        dw.embed_norm = get("embed_norm")
+        dw.embed_norm_b = get("embed_norm_bias") if cfg.norm_bias else None
+    return fold_scales(dw)
 
 
 def random_quant_weights(cfg: DecoderConfig, device, proj_format: str = "Q4_K", embed_format: str = "Q8_0", seed: int = 0,

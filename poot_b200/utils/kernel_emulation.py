@@ -85,6 +85,26 @@ def gated_act(gu, interleaved, act, out=None, limit=0.0, alpha=1.702):
     return out
 
 
+def layernorm(x, w, b, eps, out=None):
+    h = x.float()
+    mean = h.mean(-1, keepdim=True)
+    var = ((h - mean) ** 2).mean(-1, keepdim=True)
+    y = (h - mean) / torch.sqrt(var + eps) * w.float()
+    if b is not None:
+        y = y + b.float()
+    if out is None:
+        return _bf(y)
+    out.copy_(_bf(y))
+    return out
+
+
+def act_(x, act):
+    fn = {"silu": torch.nn.functional.silu, "gelu_tanh": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
+          "gelu_erf": torch.nn.functional.gelu, "relu2": lambda t: torch.relu(t) ** 2}[act]
+    x.copy_(_bf(fn(x.float())))
+    return x
+
+
 def softcap_(x, cap):
     x.copy_(cap * torch.tanh(x / cap))
     return x
@@ -481,7 +501,7 @@ def emulated_kernels():
     from ..ops import moe_ops, suffix_ops
     table = {
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
-                gated_act=gated_act, softcap_=softcap_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan,
+                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
                 attn_paged=attn_paged, attn_general=attn_general, mla_qkv_write=mla_qkv_write, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,

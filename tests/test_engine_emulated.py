@@ -87,13 +87,13 @@ def test_chained_decode_equals_stepwise_decode():
 def test_device_gaps_are_refused_by_the_engine():
     from poot_b200.runtime.engine import DecoderEngine
     from poot_b200.runtime.weights import UnsupportedOnDevice, random_weights
-    cfg = _cfg(norm_kind="layer")
+    cfg = _cfg(layer_kinds=["mamba", "attention"])
     with emulated_kernels():
         w = random_weights(_cfg(), "cpu", seed=0)
         w.cfg = cfg
         with pytest.raises(UnsupportedOnDevice) as e:
             DecoderEngine(w, 8, 1, 16, 4, device="cpu", use_graphs=False)
-    assert "LayerNorm" in str(e.value)
+    assert "Mamba2" in str(e.value)
 
 
 def test_serving_driver_over_the_emulated_engine_matches_greedy_reference():
@@ -180,6 +180,9 @@ HF_FAMILIES = {
                 "layer_types": ["sliding_attention", "full_attention"], "attention_bias": True,
                 "rope_parameters": {"rope_type": "yarn", "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False,
                                     "original_max_position_embeddings": 32, "rope_theta": 10000.0}},
+    "mpt": {"model_type": "mpt", "d_model": 256, "n_heads": 4, "n_layers": 2, "vocab_size": 512, "max_seq_len": 128,
+            "attn_config": {"alibi": True}},
+    "bloom": {"model_type": "bloom", "hidden_size": 384, "n_head": 6, "n_layer": 2, "vocab_size": 512},
     "minimax_m2": {"model_type": "minimax_m2", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
     "granite": {"model_type": "granite", "embedding_multiplier": 6.0, "residual_multiplier": 0.5, "logits_scaling": 4.0,
                 "attention_multiplier": 0.1},
@@ -197,7 +200,7 @@ def test_family_blocks_on_the_engine_match_the_graph_oracle(name):
     from poot_b200.runtime.engine import DecoderEngine
     from poot_b200.runtime.session import FixedBatchSession
     from poot_b200.runtime.weights import from_named_tensors
-    model = Registry.builtin().resolve_hf({**HF_BASE, **HF_FAMILIES[name]})
+    model = Registry.builtin().resolve_hf(HF_FAMILIES[name] if name in ("mpt", "bloom") else {**HF_BASE, **HF_FAMILIES[name]})
     cfg = model.cfg
     assert cfg.device_gaps() == [], cfg.device_gaps()
     w = random_weights_f32(model, seed=2, std=0.08)

@@ -136,7 +136,7 @@ def test_bias_and_constant_multipliers(kw):
 
 
 @pytest.mark.xfail(strict=False, reason="new device paths: not yet run on a device")
-@pytest.mark.parametrize("name", ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "minimax_m2", "qwen3_5", "qwen3next", "deepseek2", "deepseek3", "gpt_oss"])
+@pytest.mark.parametrize("name", ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "minimax_m2", "qwen3_5", "qwen3next", "deepseek2", "deepseek3", "gpt_oss", "mpt", "bloom"])
 def test_family_blocks_match_the_graph_oracle(name):
     """The device twin of the host-emulated check: sandwich / post norms, GeGLU, soft caps, two rope bases,
     projection-wide q/k norms and layers without rope on the real kernels, against the graph oracle."""
@@ -148,7 +148,7 @@ def test_family_blocks_match_the_graph_oracle(name):
     from poot_b200.runtime.engine import DecoderEngine
     from poot_b200.runtime.session import FixedBatchSession
     from poot_b200.runtime.weights import from_named_tensors
-    model = Registry.builtin().resolve_hf({**HF_BASE, **HF_FAMILIES[name]})
+    model = Registry.builtin().resolve_hf(HF_FAMILIES[name] if name in ("mpt", "bloom") else {**HF_BASE, **HF_FAMILIES[name]})
     cfg = model.cfg
     w = random_weights_f32(model, seed=2, std=0.08)
     w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}

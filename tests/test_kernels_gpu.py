@@ -447,3 +447,21 @@ def test_mla_assembly_and_group_limited_router_match_their_host_restatements():
     got = [torch.zeros(21 * k, dtype=torch.int32, device="cuda"), torch.zeros(21 * k, device="cuda"), torch.zeros(E * 21, device="cuda")]
     M.moe_route(logits.cuda(), k, True, *got, mode="sigmoid", select_bias=bias.cuda(), scale=2.5, n_group=8, topk_group=3)
     assert torch.equal(got[0].cpu(), want[0]) and torch.allclose(got[1].cpu(), want[1], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.xfail(strict=False, reason="LayerNorm, plain activations and the clamped SwiGLU: not yet run on a device")
+def test_layernorm_plain_activations_and_clamped_swiglu():
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.utils import kernel_emulation as emu
+    g = torch.Generator().manual_seed(0)
+    x = (torch.randn(19, 384, generator=g) * 2 + 0.5).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(384, generator=g)).to(torch.bfloat16)
+    b = (0.1 * torch.randn(384, generator=g)).to(torch.bfloat16)
+    close = lambda a, r: (a.float().cpu() - r.float()).abs().max().item() <= 0.02 * r.float().abs().max().item() + 2e-3
+    for bias in (b, None):
+        assert close(K.layernorm(x.cuda(), w.cuda(), None if bias is None else bias.cuda(), 1e-5), emu.layernorm(x, w, bias, 1e-5))
+    for act in ("silu", "gelu_tanh", "gelu_erf", "relu2"):
+        assert close(K.act_(x.clone().cuda(), act), emu.act_(x.clone(), act))
+    gu = (torch.randn(11, 2 * 96, generator=g) * 6).to(torch.bfloat16)
+    assert close(K.gated_act(gu.cuda(), True, "swiglu_clamped", limit=7.0, alpha=1.702),
+                 emu.gated_act(gu, True, "swiglu_clamped", limit=7.0, alpha=1.702))
