@@ -18,8 +18,8 @@ __device__ __forceinline__ float bf2f(__nv_bfloat16 v) { return __bfloat162float
 
 template <int KC>
 __global__ void causal_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int col0, int C,
-                                        const float* __restrict__ w, float* __restrict__ state, int state_rows,
-                                        const int* __restrict__ segs, __nv_bfloat16* __restrict__ out) {
+                                        const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ state,
+                                        int state_rows, const int* __restrict__ segs, __nv_bfloat16* __restrict__ out) {
   pdl_wait(); pdl_launch();
   const int s = blockIdx.y;
   const int first = segs[4 * s], n = segs[4 * s + 1], seq = segs[4 * s + 2], pos0 = segs[4 * s + 3];
@@ -33,9 +33,10 @@ __global__ void causal_conv_silu_kernel(const __nv_bfloat16* __restrict__ x, int
   float wk[KC];
 #pragma unroll
   for (int k = 0; k < KC; ++k) wk[k] = w[(size_t)c * KC + k];
+  const float b0 = bias ? bias[c] : 0.f;
   for (int i = 0; i < n; ++i) {
     const float v = bf2f(x[(size_t)(first + i) * ldx + col0 + c]);
-    float acc = wk[KC - 1] * v;
+    float acc = b0 + wk[KC - 1] * v;
 #pragma unroll
     for (int k = 0; k < KC - 1; ++k) acc += wk[k] * win[k];
 #pragma unroll
@@ -111,23 +112,71 @@ __global__ void __launch_bounds__(D) gdn_scan_kernel(const __nv_bfloat16* __rest
   for (int i = 0; i < D; ++i) St[(size_t)i * D + j] = S[i * D + j];
 }
 
+// Mamba2 selective state-space recurrence per head: h <- exp(dt A) h + dt B (x) x;  y = C.h + D x, with dt = softplus(raw + bias).
+// grid (heads, pieces), block P threads: thread p owns column p of the head's state h[N][P] (shared memory).
+// xbc [T, C] holds x (heads * P) | B (groups * N) | C (groups * N) after the convolution; dt_raw is read from `dtm` at dt_col.
+template <int P>
+__global__ void __launch_bounds__(P) ssd_scan_kernel(const __nv_bfloat16* __restrict__ xbc, const __nv_bfloat16* __restrict__ dtm,
+                                                     int ldd, int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                                     const float* __restrict__ dskip, float* __restrict__ state, int state_rows,
+                                                     const int* __restrict__ segs, __nv_bfloat16* __restrict__ out, int nh, int groups, int N) {
+  extern __shared__ float sm[];
+  float* H = sm;                            // [N][P]
+  float* Bs = H + (size_t)N * P;            // [N]
+  float* Cs = Bs + N;                       // [N]
+  pdl_wait(); pdl_launch();
+  const int s = blockIdx.y, h = blockIdx.x, p = threadIdx.x;
+  const int first = segs[4 * s], n = segs[4 * s + 1], seq = segs[4 * s + 2], pos0 = segs[4 * s + 3];
+  if (n <= 0 || seq < 0 || seq >= state_rows) return;
+  float* St = state + ((size_t)seq * nh + h) * N * P;
+  for (int i = 0; i < N; ++i) H[i * P + p] = pos0 == 0 ? 0.f : St[(size_t)i * P + p];
+  const int I = nh * P, g = h / (nh / groups);
+  const size_t C = (size_t)I + 2 * (size_t)groups * N;
+  const float A = -__expf(a_log[h]), bias = dt_bias[h], Dh = dskip[h];
+  for (int t = 0; t < n; ++t) {
+    const size_t row = (size_t)first + t;
+    const __nv_bfloat16* r = xbc + row * C;
+    __syncthreads();                        // the previous row's readers are done with Bs / Cs
+    for (int i = p; i < N; i += P) { Bs[i] = bf2f(r[I + g * N + i]); Cs[i] = bf2f(r[I + groups * N + g * N + i]); }
+    __syncthreads();
+    const float xv = bf2f(r[h * P + p]);
+    const float raw = bf2f(dtm[row * ldd + dt_col + h]) + bias;
+    const float dt = raw > 20.f ? raw : log1pf(__expf(raw));
+    const float dA = __expf(dt * A), dx = dt * xv;
+    float y = 0.f;
+    for (int i = 0; i < N; ++i) {
+      const float hv = dA * H[i * P + p] + Bs[i] * dx;
+      H[i * P + p] = hv;
+      y += Cs[i] * hv;
+    }
+    out[row * (size_t)I + h * P + p] = __float2bfloat16(y + Dh * xv);
+  }
+  for (int i = 0; i < N; ++i) St[(size_t)i * P + p] = H[i * P + p];
+}
+
 // grid (rows, ceil(heads / 8)), block 256: one warp per (row, head)
 __global__ void gated_rmsnorm_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ z, int ldz, int z_col,
-                                     const __nv_bfloat16* __restrict__ w, float eps, __nv_bfloat16* __restrict__ out,
-                                     int T, int heads, int D) {
+                                     const __nv_bfloat16* __restrict__ w, int w_per_head, float eps, int gate_first,
+                                     __nv_bfloat16* __restrict__ out, int T, int heads, int D) {
   pdl_wait(); pdl_launch();
   const int t = blockIdx.x, h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= heads) return;
   const __nv_bfloat16* yr = y + ((size_t)t * heads + h) * D;
   const __nv_bfloat16* zr = z + (size_t)t * ldz + z_col + (size_t)h * D;
   __nv_bfloat16* o = out + ((size_t)t * heads + h) * D;
+  // gate_first: norm(y * silu(z)) * w (Mamba2, one norm per channel group); else norm(y) * w * silu(z) (gated delta net)
+  const __nv_bfloat16* wr = w + (w_per_head ? (size_t)h * D : 0);
   float ss = 0.f;
-  for (int i = lane; i < D; i += 32) { const float v = bf2f(yr[i]); ss += v * v; }
+  for (int i = lane; i < D; i += 32) {
+    float v = bf2f(yr[i]);
+    if (gate_first) v *= silu(bf2f(zr[i]));
+    ss += v * v;
+  }
   ss = warp_sum(ss);
   const float inv = rsqrtf(ss / (float)D + eps);
   for (int i = lane; i < D; i += 32) {
-    const float v = bf2f(yr[i]), g = bf2f(zr[i]);
-    o[i] = __float2bfloat16(v * inv * bf2f(w[i]) * silu(g));
+    const float v = bf2f(yr[i]), g = silu(bf2f(zr[i]));
+    o[i] = __float2bfloat16(gate_first ? v * g * inv * bf2f(wr[i]) : v * inv * bf2f(wr[i]) * g);
   }
 }
 
@@ -141,17 +190,17 @@ __global__ void sigmoid_mul_kernel(__nv_bfloat16* __restrict__ a, const __nv_bfl
 
 using namespace poot;
 
-POOT_API int poot_causal_conv_silu(const void* x, int ldx, int col0, int C, int Kc, const float* w, float* state, int state_rows,
-                                   const int* segs, int n_segs, void* out, cudaStream_t s) {
+POOT_API int poot_causal_conv_silu(const void* x, int ldx, int col0, int C, int Kc, const float* w, const float* bias, float* state,
+                                   int state_rows, const int* segs, int n_segs, void* out, cudaStream_t s) {
   if (n_segs == 0 || C == 0) return 0;
   if (Kc < 2 || Kc > 4 || col0 < 0 || ldx < col0 + C) return (int)cudaErrorInvalidValue;
   dim3 grid((C + 127) / 128, n_segs), block(128);
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
   __nv_bfloat16* ob = (__nv_bfloat16*)out;
   switch (Kc) {
-    case 2: return launch_k(causal_conv_silu_kernel<2>, grid, block, 0, s, xb, ldx, col0, C, w, state, state_rows, segs, ob);
-    case 3: return launch_k(causal_conv_silu_kernel<3>, grid, block, 0, s, xb, ldx, col0, C, w, state, state_rows, segs, ob);
-    default: return launch_k(causal_conv_silu_kernel<4>, grid, block, 0, s, xb, ldx, col0, C, w, state, state_rows, segs, ob);
+    case 2: return launch_k(causal_conv_silu_kernel<2>, grid, block, 0, s, xb, ldx, col0, C, w, bias, state, state_rows, segs, ob);
+    case 3: return launch_k(causal_conv_silu_kernel<3>, grid, block, 0, s, xb, ldx, col0, C, w, bias, state, state_rows, segs, ob);
+    default: return launch_k(causal_conv_silu_kernel<4>, grid, block, 0, s, xb, ldx, col0, C, w, bias, state, state_rows, segs, ob);
   }
 }
 
@@ -179,12 +228,40 @@ POOT_API int poot_gdn_scan(const void* qkv, const void* ba, int ldb, int b_col, 
   return (int)cudaErrorInvalidValue;
 }
 
-POOT_API int poot_gated_rmsnorm(const void* y, const void* z, int ldz, int z_col, const void* w, float eps, void* out, int T,
-                                int heads, int D, cudaStream_t s) {
+template <int P>
+static int launch_ssd_scan(const void* xbc, const void* dtm, int ldd, int dt_col, const float* dt_bias, const float* a_log,
+                           const float* dskip, float* state, int state_rows, const int* segs, int n_segs, void* out, int nh,
+                           int groups, int N, cudaStream_t s) {
+  const size_t smem = ((size_t)N * P + 2 * (size_t)N) * sizeof(float);
+  if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(ssd_scan_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  return launch_k(ssd_scan_kernel<P>, dim3(nh, n_segs), dim3(P), smem, s, (const __nv_bfloat16*)xbc, (const __nv_bfloat16*)dtm, ldd,
+                  dt_col, dt_bias, a_log, dskip, state, state_rows, segs, (__nv_bfloat16*)out, nh, groups, N);
+}
+
+POOT_API int poot_ssd_scan(const void* xbc, const void* dtm, int ldd, int dt_col, const float* dt_bias, const float* a_log,
+                           const float* dskip, float* state, int state_rows, const int* segs, int n_segs, void* out, int nh,
+                           int groups, int N, int P, cudaStream_t s) {
+  if (n_segs == 0) return 0;
+  if (nh < 1 || groups < 1 || nh % groups || N < 1 || dt_col < 0) return (int)cudaErrorInvalidValue;
+  if (P == 64) return launch_ssd_scan<64>(xbc, dtm, ldd, dt_col, dt_bias, a_log, dskip, state, state_rows, segs, n_segs, out, nh, groups, N, s);
+  if (P == 128) return launch_ssd_scan<128>(xbc, dtm, ldd, dt_col, dt_bias, a_log, dskip, state, state_rows, segs, n_segs, out, nh, groups, N, s);
+  if (P == 32) return launch_ssd_scan<32>(xbc, dtm, ldd, dt_col, dt_bias, a_log, dskip, state, state_rows, segs, n_segs, out, nh, groups, N, s);
+  return (int)cudaErrorInvalidValue;
+}
+
+POOT_API int poot_gated_rmsnorm(const void* y, const void* z, int ldz, int z_col, const void* w, int w_per_head, float eps,
+                                int gate_first, void* out, int T, int heads, int D, cudaStream_t s) {
   if (T == 0) return 0;
   if (heads < 1 || D < 1 || z_col < 0) return (int)cudaErrorInvalidValue;
   return launch_k(gated_rmsnorm_kernel, dim3(T, (heads + 7) / 8), dim3(256), 0, s, (const __nv_bfloat16*)y,
-                  (const __nv_bfloat16*)z, ldz, z_col, (const __nv_bfloat16*)w, eps, (__nv_bfloat16*)out, T, heads, D);
+                  (const __nv_bfloat16*)z, ldz, z_col, (const __nv_bfloat16*)w, w_per_head, eps, gate_first, (__nv_bfloat16*)out, T,
+                  heads, D);
 }
 
 POOT_API int poot_sigmoid_mul(void* a, const void* g, long long n, cudaStream_t s) {

@@ -176,19 +176,18 @@ class DecoderConfig:
         if self.norm_kind != "rms" and self.block != "pre": g.append("LayerNorm with a post norm")
         if self.block != "pre" and self.is_moe: g.append(f"{self.block}-norm block with routed experts")
         if self.gated_ffn and self.act not in ("silu", "gelu_tanh", "gelu_erf"): g.append(f"{self.act} gated FFN")
-        if not self.gated_ffn and self.is_moe: g.append("experts without a gate")
-        if self.act != "silu" and self.is_moe: g.append(f"{self.act} experts")
+        if self.is_moe and self.act not in ("silu", "relu2", "gelu_tanh", "gelu_erf"): g.append(f"{self.act} experts")
         if self.mlp_bias and self.gated_ffn: g.append("biases of a gated dense FFN")
         if self.out_bias and self.block != "pre": g.append("output bias with a post norm")
         if self.swiglu_limit > 0 and not self.is_moe: g.append("clamped SwiGLU in a dense FFN")
         if self.router == "softmax" and self.router_select_bias: g.append("router variant")
         if self.n_group > 32 or (self.n_group > 1 and self.router != "sigmoid"): g.append("group-limited routing outside the sigmoid router")
-        if self.shared_width and (not self.gated_ffn or self.act != "silu"): g.append("shared expert that is not a SwiGLU FFN")
+        if self.shared_width and self.gated_ffn and self.act != "silu": g.append("gated shared expert that is not SwiGLU")
         if self.is_moe and self.top_k > 16: g.append("more than 16 experts per token")
         if self.is_mla and (self.qk_rope_dim % 2 or (self.qk_nope_dim + self.qk_rope_dim) % 32 or self.v_head_dim % 32):
             g.append("latent attention head widths that are not multiples of 32")
-        if self.layer_kinds is not None and any(k == "mamba" for k in self.layer_kinds): g.append("Mamba2 mixer")
-        if self.layer_kinds is not None and any(k == "none" for k in self.layer_kinds) or self.layer_ffn is not None: g.append("single-mixer blocks")
+        if self.ssm_heads and self.ssm_head_dim not in (32, 64, 128): g.append(f"Mamba2 head width {self.ssm_head_dim}")
+        if self.ssm_heads and self.ssm_conv not in (2, 3, 4): g.append(f"conv width {self.ssm_conv}")
         if self.gdn_k_heads and self.gdn_head_dim not in (64, 128): g.append(f"delta-net head width {self.gdn_head_dim}")
         if self.head_dim % 32 or not (32 <= self.head_dim <= 512): g.append(f"head_dim {self.head_dim}")
         return g

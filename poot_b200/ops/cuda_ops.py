@@ -26,9 +26,10 @@ _SIGS = {
     "poot_softcap_f32": [_P, c_longlong, c_float, _P],
     "poot_layernorm": [_P, _P, _P, c_float, _P, c_int, c_int, _P],
     "poot_act_bf16": [_P, c_longlong, c_int, _P],
-    "poot_causal_conv_silu": [_P, c_int, c_int, c_int, c_int, _P, _P, c_int, _P, c_int, _P, _P],
+    "poot_causal_conv_silu": [_P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, _P],
+    "poot_ssd_scan": [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "poot_gdn_scan": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
-    "poot_gated_rmsnorm": [_P, _P, c_int, c_int, _P, c_float, _P, c_int, c_int, c_int, _P],
+    "poot_gated_rmsnorm": [_P, _P, c_int, c_int, _P, c_int, c_float, c_int, _P, c_int, c_int, c_int, _P],
     "poot_sigmoid_mul": [_P, _P, c_longlong, _P],
     "poot_add_bf16": [_P, _P, _P, c_longlong, _P],
     "poot_reduce_partials": [_P, _P, c_int, c_longlong, _P, c_longlong, _P],
@@ -503,15 +504,15 @@ def step_segments(row_seq, positions, row_ctx):
 
 
 def causal_conv_silu(x: torch.Tensor, col0: int, C: int, w: torch.Tensor, state: torch.Tensor, segs: torch.Tensor,
-                     out: torch.Tensor) -> torch.Tensor:
+                     out: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Depthwise causal convolution + SiLU over columns ``[col0, col0 + C)`` of ``x[T, ld]`` (bf16), per sequence piece
     of ``segs``, continuing from and updating ``state[rows, K-1, C]`` (fp32; a piece at position 0 starts from zeros)."""
     _need_cuda(x, state)
     assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.dtype == torch.float32 and w.is_contiguous()
     assert state.dtype == torch.float32 and state.is_contiguous() and segs.dtype == torch.int32 and out.is_contiguous()
     Kc = w.shape[1]
-    check(_fn("poot_causal_conv_silu")(_ptr(x), x.stride(0), col0, C, Kc, _ptr(w), _ptr(state), state.shape[0], _ptr(segs),
-                                       segs.shape[0], _ptr(out), _stream()), "causal_conv_silu")
+    check(_fn("poot_causal_conv_silu")(_ptr(x), x.stride(0), col0, C, Kc, _ptr(w), _ptr(bias), _ptr(state), state.shape[0],
+                                       _ptr(segs), segs.shape[0], _ptr(out), _stream()), "causal_conv_silu")
     return out
 
 
@@ -530,12 +531,30 @@ def gdn_scan(qkv: torch.Tensor, ba: torch.Tensor, b_col: int, a_col: int, dt_bia
 
 
 def gated_rmsnorm(y: torch.Tensor, z: torch.Tensor, z_col: int, w: torch.Tensor, eps: float, out: torch.Tensor,
-                  heads: int, D: int) -> torch.Tensor:
-    """``out = rmsnorm_D(y) * w * silu(z)`` per head; ``z`` is read at columns ``[z_col, z_col + heads * D)`` of its rows."""
+                  heads: int, D: int, gate_first: bool = False) -> torch.Tensor:
+    """``out = rmsnorm_D(y) * w * silu(z)`` per head (``w[D]`` shared by the heads), or with ``gate_first``
+    ``rmsnorm_D(y * silu(z)) * w`` per channel group (``w[heads * D]``); ``z`` is read at columns
+    ``[z_col, z_col + heads * D)`` of its rows."""
     _need_cuda(y, z)
     assert y.dtype == torch.bfloat16 and y.is_contiguous() and z.stride(1) == 1 and w.dtype == torch.bfloat16
-    check(_fn("poot_gated_rmsnorm")(_ptr(y), _ptr(z), z.stride(0), z_col, _ptr(w), float(eps), _ptr(out), y.shape[0], heads, D,
-                                    _stream()), "gated_rmsnorm")
+    per_head = int(w.numel() == heads * D and heads > 1)
+    assert w.numel() in (D, heads * D)
+    check(_fn("poot_gated_rmsnorm")(_ptr(y), _ptr(z), z.stride(0), z_col, _ptr(w), per_head, float(eps), int(gate_first), _ptr(out),
+                                    y.shape[0], heads, D, _stream()), "gated_rmsnorm")
+    return out
+
+
+def ssd_scan(xbc: torch.Tensor, dtm: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor, dskip: torch.Tensor,
+             state: torch.Tensor, segs: torch.Tensor, out: torch.Tensor, nh: int, groups: int, N: int, P: int) -> torch.Tensor:
+    """Mamba2 selective state-space recurrence over each sequence piece (crates/poot-graph-ir/src/ops/ssm.rs):
+    ``xbc[T, nh P + 2 groups N]`` holds x | B | C after the convolution, the raw time steps are columns
+    ``[dt_col, dt_col + nh)`` of ``dtm``; ``state[rows, nh, N, P]`` fp32 is read (unless the piece starts at position 0)
+    and updated; ``out[T, nh P]``."""
+    _need_cuda(xbc, state)
+    assert xbc.dtype == torch.bfloat16 and xbc.is_contiguous() and dtm.stride(1) == 1 and state.dtype == torch.float32
+    assert state.is_contiguous() and out.is_contiguous() and P in (32, 64, 128)
+    check(_fn("poot_ssd_scan")(_ptr(xbc), _ptr(dtm), dtm.stride(0), dt_col, _ptr(dt_bias), _ptr(a_log), _ptr(dskip), _ptr(state),
+                               state.shape[0], _ptr(segs), segs.shape[0], _ptr(out), nh, groups, N, P, _stream()), "ssd_scan")
     return out
 
 

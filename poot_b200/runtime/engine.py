@@ -190,6 +190,20 @@ class DecoderEngine:
             # one segment per sequence piece of the step: (first row, rows, sequence row, first position); zero rows = unused
             self.seg_table = torch.zeros(max_seqs, 4, dtype=i32, device=dev)
             self._h_segs = torch.zeros(max_seqs, 4, dtype=i32, pin_memory=torch.cuda.is_available())
+        self._ssm_of = {i: n for n, i in enumerate(i for i, k in enumerate(kinds) if k == "mamba")}
+        if self._ssm_of:
+            nhm, P, N, G, Kc = cfg.ssm_heads, cfg.ssm_head_dim, cfg.ssm_state, cfg.ssm_groups, cfg.ssm_conv
+            I = nhm * P
+            C = I + 2 * G * N
+            self.ssm_I, self.ssm_C = I, C
+            self.ssm_in = torch.zeros(T, -(-(I + C + nhm) // 8) * 8, dtype=bf, device=dev)
+            self.ssm_conv_out = torch.zeros(T, C, dtype=bf, device=dev)
+            self.ssm_y = torch.zeros(T, I, dtype=bf, device=dev)
+            self.ssm_conv_state = torch.zeros(len(self._ssm_of), max_seqs, Kc - 1, C, dtype=torch.float32, device=dev)
+            self.ssm_state = torch.zeros(len(self._ssm_of), max_seqs, nhm, N, P, dtype=torch.float32, device=dev)
+            if not self._gdn_of:
+                self.seg_table = torch.zeros(max_seqs, 4, dtype=i32, device=dev)
+                self._h_segs = torch.zeros(max_seqs, 4, dtype=i32, pin_memory=torch.cuda.is_available())
         if cfg.attn_gate:
             self.gate = torch.zeros(T, self.hq * D, dtype=bf, device=dev)
         if not cfg.plain_block:
@@ -345,6 +359,9 @@ class DecoderEngine:
         lora = shape.lora and self.lora is not None
         post = cfg.block != "pre"           # a norm sits between each projection and its residual add
         for l, L in enumerate(w.layers):
+            if cfg.layer_ffn is not None:       # blocks of one mixer each (a token mixer OR an FFN), each behind its own norm
+                pending = self._single_mixer_block(l, L, T, B, pending)
+                continue
             x = h if cfg.block == "post" else self._norm(L.ln1, T, pending, L.ln1_b)
             if L.kind == "mla":
                 pending = self._mla_mixer(l, L, x, T)
@@ -448,6 +465,53 @@ class DecoderEngine:
         self._sample(shape, self.logits_local[:B])
         if staged:
             self.link.return_picked(self.picked[:B], self.logprobs[:B] if shape.logprobs else None)
+
+    def _single_mixer_block(self, l: int, L, T: int, B: int, pending):
+        """One block of a stack whose blocks hold a single mixer (nemotron-h): Mamba2, plain attention, a dense FFN or
+        routed experts, always as ``h += mixer(norm(h))``."""
+        cfg, w, D = self.cfg, self.w, self.cfg.head_dim
+        if L.kind == "mamba":
+            pending = self._mamba_mixer(l, L, self._norm(L.ln1, T, pending), T)
+        elif L.kind == "attention":
+            x = self._norm(L.ln1, T, pending)
+            qkv = self._linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
+            cos, sin = self._rope_tables_of(w.layer0 + l)
+            kvl = self._kv_of[l]
+            self._count()
+            K.rope_kv_write(qkv, self.q[:T], self.kv.k(kvl), self.kv.v(kvl), self.positions[:T], self.slots[:T], cos, sin,
+                            self.hq, self.hkv, D, cfg.rot, None, None, cfg.norm_eps)
+            self._attention(l, T, T, B)
+            pending = self._proj_to_residual(self.attn[:T], L.wo, T)
+        if cfg.has_ffn(w.layer0 + l):
+            x = self._norm(L.ln2, T, pending)
+            if cfg.moe_layer(w.layer0 + l):
+                pending = self._moe(l, L, x, T)
+            else:
+                up = self._linear(x, L.wgu, K.EPI_STORE, self.act[:T])
+                if L.bgu is not None:
+                    up.add_(L.bgu)
+                self._count()
+                K.act_(up, cfg.act)
+                pending = self._proj_to_residual(up, L.wdown, T)
+                if L.bdown is not None:
+                    self.h[:T].add_(L.bdown)
+        return pending
+
+    def _mamba_mixer(self, l: int, L, x, T: int):
+        """Mamba2 layer (components/mamba2.rs): one GEMM for z | (x | B | C) | dt, causal conv + SiLU continuing each
+        sequence's window, the selective state-space recurrence over each sequence's state, the gated RMSNorm within
+        channel groups, out-projection into the residual stream."""
+        cfg, si = self.cfg, self._ssm_of[l]
+        I, C = self.ssm_I, self.ssm_C
+        proj = self._linear(x, L.wqkv, K.EPI_STORE, self.ssm_in[:T])
+        self._count(3)
+        K.causal_conv_silu(proj, I, C, L.ssm["conv"], self.ssm_conv_state[si], self.seg_table, self.ssm_conv_out[:T],
+                           bias=L.ssm["conv_bias"])
+        K.ssd_scan(self.ssm_conv_out[:T], proj, I + C, L.ssm["dt_bias"], L.ssm["a_log"], L.ssm["d"], self.ssm_state[si],
+                   self.seg_table, self.ssm_y[:T], cfg.ssm_heads, cfg.ssm_groups, cfg.ssm_state, cfg.ssm_head_dim)
+        G = cfg.ssm_groups
+        K.gated_rmsnorm(self.ssm_y[:T], proj, 0, L.ssm["gate_norm"], cfg.norm_eps, self.ssm_y[:T], G, I // G, gate_first=True)
+        return self._proj_to_residual(self.ssm_y[:T], L.wo, T)
 
     def _mla_mixer(self, l: int, L, x, T: int):
         """Multi-head latent attention in its expanded form (components/mla.rs): low-rank query and key/value
@@ -734,7 +798,7 @@ class DecoderEngine:
                 self.row_seq[T:R].zero_()
         B = logit_idx.numel()
         self.logit_idx[:B].copy_(logit_idx, non_blocking=non_blocking)
-        if self._gdn_of:
+        if self._gdn_of or self._ssm_of:
             segs = K.step_segments(row_seq.numpy(), positions.numpy(), row_ctx.numpy())
             if segs.shape[0] > self._h_segs.shape[0]:
                 raise ValueError("a step carries more sequence pieces than the engine has rows")

@@ -36,7 +36,7 @@ def _buffers(eng):
             "dense": torch.zeros(E * T, dtype=torch.float32, device=dev),
             "act": torch.zeros(G * Tc * F, dtype=torch.bfloat16, device=dev),
             "gu": (torch.zeros(G * Tc * 2 * F, dtype=torch.bfloat16, device=dev)
-                   if (c.expert_bias or c.swiglu_limit > 0 or c.act != "silu") else None),
+                   if (c.expert_bias or c.swiglu_limit > 0 or c.act != "silu" or not c.gated_ffn) else None),
             "parts": torch.zeros(G * Tc * H, dtype=torch.bfloat16, device=dev),
         }
     return eng._moe_buf
@@ -51,7 +51,12 @@ def shared_expert(eng, L, x: torch.Tensor, T: int) -> None:
         eng._sh_gate = torch.zeros(eng.max_tokens, 8, dtype=torch.float32, device=eng.device)
     act = eng._sh_act[:T]
     eng._count(2)
-    K.linear(x, L.sh_wgu, K.EPI_SWIGLU, act)
+    if c.gated_ffn:
+        K.linear(x, L.sh_wgu, K.EPI_SWIGLU, act)
+    else:
+        eng._count()
+        K.linear(x, L.sh_wgu, K.EPI_STORE, act)
+        K.act_(act, c.act)
     if L.sh_gate is not None:
         eng._count(2)
         g = eng._sh_gate[:T]
@@ -67,7 +72,10 @@ def _expert_act(eng, L, gu: torch.Tensor, act: torch.Tensor, expert_of_row: torc
     if L.ex_bgu is not None:
         gu.add_(L.ex_bgu[expert_of_row])
     eng._count()
-    if c.swiglu_limit > 0:
+    if not c.gated_ffn:                 # experts without a gate: act(up(x))
+        act.copy_(gu)
+        K.act_(act, c.act)
+    elif c.swiglu_limit > 0:
         K.gated_act(gu, True, "swiglu_clamped", out=act, limit=c.swiglu_limit, alpha=c.swiglu_alpha)
     else:
         K.gated_act(gu, True, c.act, out=act)
@@ -105,8 +113,9 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
         if buf["gu"] is None:
             M.gemm_grouped(K.EPI_SWIGLU, x, L.ex_wgu, act, 1, G, group_expert=ids, x_row_div=k, out_group_stride=F, ldo=F)
         else:           # biased / clamped experts: plain projection, bias of the group's expert, then the activation
-            gu = buf["gu"][:G * 2 * F].view(G, 2 * F)
-            M.gemm_grouped(K.EPI_STORE, x, L.ex_wgu, gu, 1, G, group_expert=ids, x_row_div=k, out_group_stride=2 * F, ldo=2 * F)
+            W2 = L.ex_wgu.shape[1]          # 2F with a gate, F without
+            gu = buf["gu"][:G * W2].view(G, W2)
+            M.gemm_grouped(K.EPI_STORE, x, L.ex_wgu, gu, 1, G, group_expert=ids, x_row_div=k, out_group_stride=W2, ldo=W2)
             _expert_act(eng, L, gu, act, ids.long())
         M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, parts, 1, G, group_expert=ids, x_row_mul=1, out_group_stride=H,
                        row_scale=gates, ldo=H)
@@ -137,8 +146,9 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
         if buf["gu"] is None:
             M.gemm_grouped(K.EPI_SWIGLU, xs, L.ex_wgu, act, n, e_local, out_group_stride=n * F, ldo=F)
         else:
-            gu = buf["gu"][:e_local * n * 2 * F].view(e_local * n, 2 * F)
-            M.gemm_grouped(K.EPI_STORE, xs, L.ex_wgu, gu, n, e_local, out_group_stride=n * 2 * F, ldo=2 * F)
+            W2 = L.ex_wgu.shape[1]
+            gu = buf["gu"][:e_local * n * W2].view(e_local * n, W2)
+            M.gemm_grouped(K.EPI_STORE, xs, L.ex_wgu, gu, n, e_local, out_group_stride=n * W2, ldo=W2)
             _expert_act(eng, L, gu, act, torch.arange(e0, e0 + e_local, device=gu.device).repeat_interleave(n))
         if tp is not None and e_local == 1 and T <= 128:
             M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, None, n, 1, x_row_mul=n, row_scale=scale, ldo=H, tp=tp)

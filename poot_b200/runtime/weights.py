@@ -43,7 +43,8 @@ class LayerWeights:
     router_bias: Optional[torch.Tensor] = None    # [E] fp32 added to the router logits
     ex_bgu: Optional[torch.Tensor] = None   # [E, 2F] expert gate/up biases in the interleaved row order of ex_wgu
     ex_bdown: Optional[torch.Tensor] = None  # [E, hidden] expert down-projection biases
-    kind: str = "attention"                 # token mixer of the layer: attention | gdn | mla
+    kind: str = "attention"                 # token mixer of the layer: attention | gdn | mla | mamba | none (FFN-only block)
+    ssm: Optional[Dict[str, torch.Tensor]] = None   # Mamba2: conv [C, K], conv_bias, dt_bias, a_log, d (fp32), gate_norm (bf16)
     mla: Optional[Dict[str, torch.Tensor]] = None   # latent attention: q_a, q_a_norm, q_b (or q), kv_a, kv_a_norm, kv_b
     gdn: Optional[Dict[str, torch.Tensor]] = None   # gated delta net: w_in (q|k|v|z|b|a rows), conv [C, K], dt_bias, a_log, gate_norm
     router: Optional[torch.Tensor] = None   # [E, hidden]
@@ -274,6 +275,19 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             L = LayerWeights(ln1=get(p + "attn_norm"), ln2=get(p + "ffn_norm"), wqkv=w_in, wo=get(p + "gdn_o"), kind="gdn",
                              gdn={"conv": f32("gdn_conv"), "dt_bias": f32("gdn_dt_bias"), "a_log": f32("gdn_a_log"),
                                   "gate_norm": get(p + "gdn_gate_norm_w")})
+        elif cfg.mixer_of(l) == "mamba":
+            # one GEMM for z | (x | B | C) | dt; rows padded to a multiple of 8 for the tiled GEMM's output alignment
+            w_in = torch.cat([get(p + r) for r in ("ssm_in_z", "ssm_in_x", "ssm_in_dt")], 0)
+            pad = (-w_in.shape[0]) % 8
+            if pad:
+                w_in = torch.cat([w_in, torch.zeros(pad, w_in.shape[1], dtype=dtype, device=dev)], 0)
+            f32 = lambda n: tensors[p + n].to(device=dev, dtype=torch.float32).contiguous()
+            L = LayerWeights(ln1=get(p + "attn_norm"), ln2=None, wqkv=w_in.contiguous(), wo=get(p + "ssm_o"), kind="mamba",
+                             ssm={"conv": f32("ssm_conv"), "conv_bias": f32("ssm_conv_bias") if cfg.ssm_conv_bias else None,
+                                  "dt_bias": f32("ssm_dt_bias"), "a_log": f32("ssm_a_log"), "d": f32("ssm_d"),
+                                  "gate_norm": get(p + "ssm_gate_norm_w")})
+        elif cfg.mixer_of(l) == "none":
+            L = LayerWeights(ln1=None, ln2=None, wqkv=None, wo=None, kind="none")
         elif cfg.is_mla:
             m = {"kv_a": get(p + "attn_kv_a"), "kv_a_norm": get(p + "attn_kv_a_norm"), "kv_b": get(p + "attn_kv_b")}
             if cfg.q_lora_rank:
@@ -284,7 +298,8 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
         else:
             wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)
             wo = shard_cols(get(p + "attn_o"), tp_rank, tp_world)
-            L = LayerWeights(ln1=get(p + "attn_norm") if pre else None, ln2=get(p + "ffn_norm") if pre else None, wqkv=wqkv, wo=wo)
+            L = LayerWeights(ln1=get(p + "attn_norm") if pre else None,
+                             ln2=get(p + "ffn_norm") if (pre and cfg.has_ffn(l)) else None, wqkv=wqkv, wo=wo)
             if cfg.attn_gate:
                 L.wgate = shard_rows(get(p + "attn_gate"), tp_rank, tp_world)
             if cfg.out_bias:
@@ -297,7 +312,11 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             L.bqkv = fuse_qkv_bias(get(p + "attn_q_bias"), get(p + "attn_k_bias"), get(p + "attn_v_bias"), cfg, tp_rank, tp_world)
         if cfg.qk_norm and L.kind == "attention":
             L.q_norm, L.k_norm = get(p + "attn_q_norm"), get(p + "attn_k_norm")
-        if cfg.moe_layer(l):
+        if cfg.has_ffn(l) and L.ln2 is None and cfg.block != "post":
+            L.ln2 = get(p + "ffn_norm")
+        if not cfg.has_ffn(l):
+            pass
+        elif cfg.moe_layer(l):
             L.router = get(p + "ffn_router")
             if cfg.router_select_bias:
                 L.select_bias = tensors[p + "ffn_router_select_bias"].to(device=dev, dtype=torch.float32).contiguous()
@@ -309,14 +328,15 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
                 L.ex_bgu = torch.stack([b[:, :F_], b[:, F_:]], dim=2).reshape(b.shape[0], 2 * F_).contiguous()
                 L.ex_bdown = get(p + "experts_out_bias")
             if cfg.shared_width:
-                L.sh_wgu = interleave_gate_up(get(p + "shared_gate"), get(p + "shared_up"))
+                L.sh_wgu = interleave_gate_up(get(p + "shared_gate"), get(p + "shared_up")) if cfg.gated_ffn else get(p + "shared_up")
                 L.sh_wdown = get(p + "shared_down")
                 if cfg.shared_expert_gate:
                     L.sh_gate = torch.zeros(8, cfg.hidden, dtype=dtype, device=dev)
                     L.sh_gate[0] = get(p + "shared_expert_gate")[0]
             gus, downs = [], []
             for e in range(cfg.n_experts):
-                gus.append(interleave_gate_up(get(p + f"experts.{e}.gate"), get(p + f"experts.{e}.up")))
+                gus.append(interleave_gate_up(get(p + f"experts.{e}.gate"), get(p + f"experts.{e}.up")) if cfg.gated_ffn
+                           else get(p + f"experts.{e}.up"))
                 downs.append(get(p + f"experts.{e}.down"))
             L.ex_wgu, L.ex_wdown = torch.stack(gus), torch.stack(downs)
         elif cfg.gated_ffn:

@@ -110,7 +110,7 @@ def softcap_(x, cap):
     return x
 
 
-def causal_conv_silu(x, col0, C, w, state, segs, out):
+def causal_conv_silu(x, col0, C, w, state, segs, out, bias=None):
     Kc = w.shape[1]
     for first, n, seq, pos0 in segs.tolist():
         if n == 0:
@@ -118,6 +118,8 @@ def causal_conv_silu(x, col0, C, w, state, segs, out):
         prev = torch.zeros(Kc - 1, C) if pos0 == 0 else state[seq].clone()
         xp = torch.cat([prev, x[first:first + n, col0:col0 + C].float()], 0)
         acc = sum(xp[k:k + n] * w[:, k] for k in range(Kc))
+        if bias is not None:
+            acc = acc + bias.float()
         out[first:first + n] = _bf(torch.nn.functional.silu(acc))
         state[seq] = xp[n:]
     return out
@@ -150,12 +152,37 @@ def gdn_scan(qkv, ba, b_col, a_col, dt_bias, a_log, state, segs, out, nk, nv, D)
     return out
 
 
-def gated_rmsnorm(y, z, z_col, w, eps, out, heads, D):
+def gated_rmsnorm(y, z, z_col, w, eps, out, heads, D, gate_first=False):
     T = y.shape[0]
     yy = y.float().reshape(T, heads, D)
-    zz = z[:, z_col:z_col + heads * D].float().reshape(T, heads, D)
-    r = yy / torch.sqrt((yy * yy).mean(-1, keepdim=True) + eps) * w.float() * torch.nn.functional.silu(zz)
+    zz = torch.nn.functional.silu(z[:, z_col:z_col + heads * D].float().reshape(T, heads, D))
+    ww = w.float().reshape(heads, D) if w.numel() == heads * D else w.float()
+    if gate_first:
+        v = yy * zz
+        r = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * ww
+    else:
+        r = yy / torch.sqrt((yy * yy).mean(-1, keepdim=True) + eps) * ww * zz
     out.copy_(_bf(r.reshape(T, heads * D)))
+    return out
+
+
+def ssd_scan(xbc, dtm, dt_col, dt_bias, a_log, dskip, state, segs, out, nh, groups, N, P):
+    I, rep = nh * P, nh // groups
+    for first, n, seq, pos0 in segs.tolist():
+        if n == 0:
+            continue
+        H = torch.zeros(nh, N, P) if pos0 == 0 else state[seq].clone()
+        r = xbc[first:first + n].float()
+        x = r[:, :I].reshape(n, nh, P)
+        B = r[:, I:I + groups * N].reshape(n, groups, N).repeat_interleave(rep, 1)
+        C = r[:, I + groups * N:].reshape(n, groups, N).repeat_interleave(rep, 1)
+        dt = torch.nn.functional.softplus(dtm[first:first + n, dt_col:dt_col + nh].float() + dt_bias.float())
+        A = -torch.exp(a_log.float())
+        for t in range(n):
+            H = torch.exp(dt[t] * A)[:, None, None] * H + (dt[t][:, None] * B[t])[:, :, None] * x[t][:, None, :]
+            y = torch.einsum("hn,hnp->hp", C[t], H) + dskip.float()[:, None] * x[t]
+            out[first + t] = _bf(y.reshape(-1))
+        state[seq] = H
     return out
 
 
@@ -501,7 +528,7 @@ def emulated_kernels():
     from ..ops import moe_ops, suffix_ops
     table = {
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
-                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan,
+                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, ssd_scan=ssd_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
                 attn_paged=attn_paged, attn_general=attn_general, mla_qkv_write=mla_qkv_write, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,

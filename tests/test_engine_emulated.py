@@ -87,13 +87,13 @@ def test_chained_decode_equals_stepwise_decode():
 def test_device_gaps_are_refused_by_the_engine():
     from poot_b200.runtime.engine import DecoderEngine
     from poot_b200.runtime.weights import UnsupportedOnDevice, random_weights
-    cfg = _cfg(layer_kinds=["mamba", "attention"])
+    cfg = _cfg(mlp_bias=True)
     with emulated_kernels():
         w = random_weights(_cfg(), "cpu", seed=0)
         w.cfg = cfg
         with pytest.raises(UnsupportedOnDevice) as e:
             DecoderEngine(w, 8, 1, 16, 4, device="cpu", use_graphs=False)
-    assert "Mamba2" in str(e.value)
+    assert "biases of a gated dense FFN" in str(e.value)
 
 
 def test_serving_driver_over_the_emulated_engine_matches_greedy_reference():
@@ -183,6 +183,9 @@ HF_FAMILIES = {
     "mpt": {"model_type": "mpt", "d_model": 256, "n_heads": 4, "n_layers": 2, "vocab_size": 512, "max_seq_len": 128,
             "attn_config": {"alibi": True}},
     "bloom": {"model_type": "bloom", "hidden_size": 384, "n_head": 6, "n_layer": 2, "vocab_size": 512},
+    "nemotron_h": {"model_type": "nemotron_h", "hybrid_override_pattern": "M-*E", "mamba_num_heads": 4, "mamba_head_dim": 32,
+                   "ssm_state_size": 16, "n_groups": 2, "conv_kernel": 4, "n_routed_experts": 4, "num_experts_per_tok": 2,
+                   "moe_intermediate_size": 64, "moe_shared_expert_intermediate_size": 96, "layer_norm_epsilon": 1e-5},
     "minimax_m2": {"model_type": "minimax_m2", "num_local_experts": 4, "num_experts_per_tok": 2, "intermediate_size": 128},
     "granite": {"model_type": "granite", "embedding_multiplier": 6.0, "residual_multiplier": 0.5, "logits_scaling": 4.0,
                 "attention_multiplier": 0.1},
@@ -209,7 +212,7 @@ def test_family_blocks_on_the_engine_match_the_graph_oracle(name):
             w[k] = (0.3 * np.random.default_rng(1).standard_normal(w[k].shape)).astype(np.float32)
         if k.endswith(("norm", "norm_w")):
             w[k] = (1.0 + 0.1 * np.random.default_rng(len(k)).standard_normal(w[k].shape)).astype(np.float32)
-        if k.endswith("gdn_a_log"):
+        if k.endswith(("gdn_a_log", "ssm_a_log")):
             w[k] = np.log(np.random.default_rng(3).uniform(0.5, 4.0, w[k].shape)).astype(np.float32)
     w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}     # what the device will hold
     named = {k: torch.from_numpy(v) for k, v in w.items()}
@@ -217,7 +220,7 @@ def test_family_blocks_on_the_engine_match_the_graph_oracle(name):
         p = f"layers.{l}."
         for e in range(cfg.n_experts):
             named[p + f"experts.{e}.gate"] = named[p + "experts_in"][e, :cfg.moe_ffn]
-            named[p + f"experts.{e}.up"] = named[p + "experts_in"][e, cfg.moe_ffn:]
+            named[p + f"experts.{e}.up"] = named[p + "experts_in"][e, cfg.moe_ffn:] if cfg.gated_ffn else named[p + "experts_in"][e]
             named[p + f"experts.{e}.down"] = named[p + "experts_out"][e]
     # routed experts make the model discontinuous: where two router scores nearly tie, bf16 rounding can pick the other
     # expert and move the logits by several percent; the token seed of such a family avoids a near-tie on its last steps

@@ -136,7 +136,7 @@ def test_bias_and_constant_multipliers(kw):
 
 
 @pytest.mark.xfail(strict=False, reason="new device paths: not yet run on a device")
-@pytest.mark.parametrize("name", ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "minimax_m2", "qwen3_5", "qwen3next", "deepseek2", "deepseek3", "gpt_oss", "mpt", "bloom"])
+@pytest.mark.parametrize("name", ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "minimax_m2", "qwen3_5", "qwen3next", "deepseek2", "deepseek3", "gpt_oss", "mpt", "bloom", "nemotron_h"])
 def test_family_blocks_match_the_graph_oracle(name):
     """The device twin of the host-emulated check: sandwich / post norms, GeGLU, soft caps, two rope bases,
     projection-wide q/k norms and layers without rope on the real kernels, against the graph oracle."""
@@ -157,7 +157,7 @@ def test_family_blocks_match_the_graph_oracle(name):
         p = f"layers.{l}."
         for e in range(cfg.n_experts):
             named[p + f"experts.{e}.gate"] = named[p + "experts_in"][e, :cfg.moe_ffn]
-            named[p + f"experts.{e}.up"] = named[p + "experts_in"][e, cfg.moe_ffn:]
+            named[p + f"experts.{e}.up"] = named[p + "experts_in"][e, cfg.moe_ffn:] if cfg.gated_ffn else named[p + "experts_in"][e]
             named[p + f"experts.{e}.down"] = named[p + "experts_out"][e]
     # routed experts make the model discontinuous: where two router scores nearly tie, bf16 rounding can pick the other
     # expert and move the logits by several percent; the token seed of such a family avoids a near-tie on its last steps
