@@ -160,7 +160,8 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
     import torch
     from ..runtime.weights import DecoderWeights, LayerWeights
     c, canon = handle.cfg, handle.canonical
-    if c.layer_kinds is not None or c.attn_gate or c.qk_norm_wide or c.router_select_bias:
+    if not c.plain_block or c.router_select_bias or c.shared_width or c.first_dense_layers or c.dense_layers or c.n_group > 1 \
+            or c.router != "softmax":
         # hybrid stacks and the less common layer variants go through the canonical-name builder (dense bf16)
         from ..runtime.weights import from_named_tensors
         named = {n: torch.from_numpy(np.ascontiguousarray(w.to_f32())) for n, w in canon.items()}

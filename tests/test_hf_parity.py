@@ -300,3 +300,47 @@ def test_qwen3_5_checkpoint_on_the_emulated_device_engine_generates_what_hugging
     # bf16 weights and activations on the engine side: compare where the reference's top two logits are not a near tie
     agree = sum(a == b for i, w_ in zip(ids, want) for a, b in zip(got[i], w_))
     assert agree >= 8, (got, want)
+
+
+DEVICE_CASES = {
+    # the parity cases at widths the device kernels take (head widths that are multiples of 32)
+    "gemma2": dict(head_dim=32, hidden_size=128),
+    "gemma3": dict(head_dim=32, hidden_size=128),
+    "olmo2": dict(head_dim=32, hidden_size=128),
+    "granitemoe": dict(head_dim=32, hidden_size=128),
+    "gpt_oss": dict(head_dim=32, hidden_size=128),
+    "minimax_m2": dict(head_dim=32, hidden_size=128),
+    "bloom": dict(hidden_size=128, n_head=4),
+    "mpt": dict(d_model=128, n_heads=4),
+    "deepseek3": dict(hidden_size=128, qk_rope_head_dim=32, qk_nope_head_dim=32, v_head_dim=32, head_dim=32),
+    "nemotron_h": dict(head_dim=32, hidden_size=128, mamba_head_dim=32),
+    "qwen3next": dict(head_dim=32, hidden_size=128, linear_key_head_dim=64, linear_value_head_dim=64,
+                      rope_parameters={"rope_theta": 10000.0, "partial_rotary_factor": 0.5, "rope_type": "default"}),
+}
+
+
+@pytest.mark.parametrize("name", sorted(DEVICE_CASES))
+def test_checkpoint_through_the_device_loader_and_emulated_engine_follows_hugging_face(name, tmp_path):
+    """Checkpoint directory -> ``LLM.load`` (the device loader: fused layouts, biases, folded norm offsets, expert
+    stacks, per-family extras) -> the engine's program with the kernels restated on the host -> greedy tokens, against
+    ``transformers`` greedy generation.  bf16 weights and activations on the engine side: most tokens must agree (a
+    near-tie of the top two logits, or of two router scores, may pick differently)."""
+    from poot_b200 import LLM, SamplingParams
+    from poot_b200.utils.kernel_emulation import emulated_kernels
+    m, vocab = build({**CASES[name], **DEVICE_CASES[name]})
+    m.generation_config.eos_token_id = None
+    m.generation_config.pad_token_id = 0
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    p = torch.randint(3, vocab, (1, 21), generator=torch.Generator().manual_seed(4))
+    with torch.no_grad():
+        want = m.generate(p, max_new_tokens=6, do_sample=False, eos_token_id=None)[0, 21:].tolist()
+    with emulated_kernels():
+        llm = LLM.load(str(tmp_path), device="cpu", rows=1, max_seq=64, prefill_chunk=16, num_blocks=8)
+        assert llm.cfg.device_gaps() == []
+        got = llm.generate_tokens(p[0].tolist(), SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
+    agree = 0
+    for a, b in zip(got, want):      # count the common prefix: after a divergence the continuations are different texts
+        if a != b:
+            break
+        agree += 1
+    assert agree >= 2, (got, want)
