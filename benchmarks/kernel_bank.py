@@ -90,6 +90,90 @@ def attn_case(B, ctx, Hq=32, Hkv=8, D=128):
     return [fn], 2 * B * ctx * Hkv * D * 2, 4.0 * B * ctx * Hq * D
 
 
+def general_attn_case(B, ctx, Hq, Hkv, Dk, Dv):
+    """The general attention kernel (head widths the tuned kernels do not take: 256, or 192 / 128 latent attention)."""
+    bps = (ctx + 15) // 16
+    nb = B * bps
+    pd = max(Dk, Dv)
+    kpool, vpool = rnd(nb, Hkv, 16, pd), rnd(nb, Hkv, 16, pd)
+    bt = torch.randperm(nb, device="cuda").to(torch.int32).view(B, bps)
+    q = rnd(B, Hq * Dk)
+    row_ctx = torch.full((B,), ctx, dtype=torch.int32, device="cuda")
+    out = torch.empty(B, Hq * Dv, device="cuda", dtype=torch.bfloat16)
+    fn = lambda: K.attn_general(q, kpool, vpool, bt, None, row_ctx, Hq, Hkv, Dk, Dv, 1 / math.sqrt(Dk), out)
+    return [fn], B * ctx * Hkv * (Dk + Dv) * 2, 2.0 * B * ctx * Hq * (Dk + Dv)
+
+
+def segments(n_seq, rows_each):
+    segs = torch.zeros(n_seq, 4, dtype=torch.int32)
+    for i in range(n_seq):
+        segs[i] = torch.tensor([i * rows_each, rows_each, i, 16 if rows_each == 1 else 0])
+    return segs.cuda()
+
+
+def gdn_case(n_seq, rows_each, nk=16, nv=48, D=128):
+    """Gated delta rule over ``n_seq`` sequence pieces (decode: one row each; prefill: ``rows_each`` rows)."""
+    T = n_seq * rows_each
+    C = (2 * nk + nv) * D
+    qkv, ba = rnd(T, C, scale=0.3), rnd(T, 2 * nv, scale=0.3)
+    state = torch.zeros(n_seq, nv, D, D, device="cuda")
+    out = torch.empty(T, nv * D, device="cuda", dtype=torch.bfloat16)
+    dtb, alog = torch.zeros(nv, device="cuda"), torch.zeros(nv, device="cuda")
+    segs = segments(n_seq, rows_each)
+    fn = lambda: K.gdn_scan(qkv, ba, 0, nv, dtb, alog, state, segs, out, nk, nv, D)
+    return [fn], 2 * n_seq * nv * D * D * 4 + T * C * 2, 6.0 * T * nv * D * D
+
+
+def ssd_case(n_seq, rows_each, nh=128, G=8, N=128, P=64):
+    """Mamba2 recurrence over ``n_seq`` sequence pieces."""
+    T = n_seq * rows_each
+    I = nh * P
+    C = I + 2 * G * N
+    xbc, dtm = rnd(T, C, scale=0.3), rnd(T, nh, scale=0.3)
+    state = torch.zeros(n_seq, nh, N, P, device="cuda")
+    out = torch.empty(T, I, device="cuda", dtype=torch.bfloat16)
+    z = torch.zeros(nh, device="cuda")
+    segs = segments(n_seq, rows_each)
+    fn = lambda: K.ssd_scan(xbc, dtm, 0, z, z, z, state, segs, out, nh, G, N, P)
+    return [fn], 2 * n_seq * nh * N * P * 4 + T * C * 2, 4.0 * T * nh * N * P
+
+
+def conv_case(n_seq, rows_each, C=10240, Kc=4):
+    T = n_seq * rows_each
+    x = rnd(T, C)
+    w = torch.randn(C, Kc, device="cuda")
+    state = torch.zeros(n_seq, Kc - 1, C, device="cuda")
+    out = torch.empty(T, C, device="cuda", dtype=torch.bfloat16)
+    segs = segments(n_seq, rows_each)
+    fn = lambda: K.causal_conv_silu(x, 0, C, w, state, segs, out)
+    return [fn], 2 * T * C * 2 + 2 * n_seq * (Kc - 1) * C * 4, 2.0 * T * C * Kc
+
+
+def flash_case(rows, Hq=32, Hkv=8, D=128):
+    """Tensor-core prefill attention of one sequence of ``rows`` tokens."""
+    import numpy as np
+    bps = (rows + 15) // 16
+    kpool, vpool = rnd(bps, Hkv, 16, D), rnd(bps, Hkv, 16, D)
+    bt = torch.arange(bps, device="cuda", dtype=torch.int32).view(1, bps)
+    q = rnd(rows, Hq * D)
+    out = torch.empty(rows, Hq * D, device="cuda", dtype=torch.bfloat16)
+    tiles, _ = K.flash_tiles(np.zeros(rows, np.int32), np.arange(rows, dtype=np.int32))
+    tl = torch.from_numpy(tiles).cuda()
+    fn = lambda: K.attn_flash_prefill(q, kpool, vpool, bt, tl, Hq, Hkv, 1 / math.sqrt(D), out)
+    return [fn], 2 * rows * Hkv * D * 2 + 2 * rows * Hq * D * 2, 2.0 * rows * rows * Hq * D      # causal: half of 4 L^2 H D
+
+
+def route_case(T, E, k, mode):
+    from poot_b200.ops import moe_ops as M
+    logits = torch.randn(T, E, device="cuda")
+    ids, gates = torch.zeros(T * k, dtype=torch.int32, device="cuda"), torch.zeros(T * k, device="cuda")
+    dense = torch.zeros(E * T, device="cuda")
+    bias = torch.zeros(E, device="cuda") if mode == "sigmoid" else None
+    fn = lambda: M.moe_route(logits, k, True, ids, gates, dense, mode=mode, select_bias=bias, n_group=8 if mode == "sigmoid" else 1,
+                             topk_group=4 if mode == "sigmoid" else 1)
+    return [fn], T * E * 8, 0.0
+
+
 CASES = {
     "dense-decode-gemv-qkv": lambda: gemm_case(1, 6144, 4096, "skinny"),
     "dense-decode-gemv-o": lambda: gemm_case(1, 4096, 4096, "skinny"),
@@ -111,6 +195,18 @@ CASES = {
     "attention-decode-b1-ctx4096": lambda: attn_case(1, 4096),
     "attention-decode-b64-ctx1024": lambda: attn_case(64, 1024),
     "attention-decode-b64-ctx4096": lambda: attn_case(64, 4096),
+    "prefill-attention-2048": lambda: flash_case(2048),
+    "prefill-attention-8192": lambda: flash_case(8192),
+    "attention-general-d256-b64-ctx1024": lambda: general_attn_case(64, 1024, 8, 4, 256, 256),
+    "attention-general-latent-b16-ctx1024": lambda: general_attn_case(16, 1024, 128, 128, 192, 128),
+    "scan-delta-rule-decode-b64": lambda: gdn_case(64, 1),
+    "scan-delta-rule-prefill-512": lambda: gdn_case(1, 512),
+    "scan-ssd-decode-b64": lambda: ssd_case(64, 1),
+    "scan-ssd-prefill-512": lambda: ssd_case(1, 512),
+    "causal-conv-decode-b64": lambda: conv_case(64, 1),
+    "causal-conv-prefill-512": lambda: conv_case(1, 512),
+    "expert-routing-softmax-512x128-top8": lambda: route_case(512, 128, 8, "softmax"),
+    "expert-routing-sigmoid-groups-512x256-top8": lambda: route_case(512, 256, 8, "sigmoid"),
 }
 
 
