@@ -20,10 +20,8 @@ def main(argv=None) -> int:
         from .embed import main_embed
         return main_embed(rest)
     if cmd == "caption":
-        # The reference serves this through its vision front ends (crates/poot-llm/src/bin/poot/main.rs:42-55);
-        # this build registers text families only.
-        print("error: `caption` needs a vision family; only text families are registered", file=sys.stderr)
-        return 2
+        from .caption import main_caption
+        return main_caption(rest)
     print(f"error: unknown command {cmd!r}\n{USAGE}", file=sys.stderr)
     return 2
 

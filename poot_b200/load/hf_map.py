@@ -17,6 +17,7 @@ file.  The exceptions are rewritten once at load:
 from __future__ import annotations
 
 import re
+from dataclasses import replace
 from typing import Callable, Dict, Optional
 
 import numpy as np
@@ -115,8 +116,54 @@ def _map_bert(cfg, store: WeightStore) -> Dict[str, PackedWeight]:
     return canon
 
 
+VISION_TOP = {"embeddings.patch_embedding.bias": "patch_embed_bias", "embeddings.position_embedding.weight": "pos_embed",
+              "post_layernorm.weight": "post_norm", "post_layernorm.bias": "post_norm_bias"}
+VISION_LAYER = {"layer_norm1": "attn_norm", "layer_norm2": "ffn_norm", "self_attn.q_proj": "attn_q", "self_attn.k_proj": "attn_k",
+                "self_attn.v_proj": "attn_v", "self_attn.out_proj": "attn_o", "mlp.fc1": "ffn_up", "mlp.fc2": "ffn_down"}
+
+
+class _Renamed:
+    """A weight store seen through a name prefix swap (a text stack nested one level down in a multimodal checkpoint)."""
+
+    def __init__(self, store: WeightStore, old: str, new: str):
+        self.store = store
+        self.inner = {(new + n[len(old):] if n.startswith(old) else n): n for n in store.names()}
+
+    def names(self):
+        return list(self.inner)
+
+    def __getitem__(self, name: str) -> PackedWeight:
+        return self.store[self.inner[name]]
+
+
+def _map_vision(store: WeightStore) -> Dict[str, PackedWeight]:
+    """Vision tower and connector tensors of an Idefics3 / SmolVLM checkpoint (``model.vision_model.*``,
+    ``model.connector.*``); the patch convolution ``[out, C, p, p]`` flattens to a matrix over flattened patches."""
+    canon: Dict[str, PackedWeight] = {}
+    for n in store.names():
+        if n == "model.connector.modality_projection.proj.weight":
+            canon["vision.projector"] = store[n]
+            continue
+        if not n.startswith("model.vision_model."):
+            continue
+        short = n[len("model.vision_model."):]
+        if short == "embeddings.patch_embedding.weight":
+            w = store[n].to_f32()
+            canon["vision.patch_embed"] = f32_weight("vision.patch_embed", w.reshape(w.shape[0], -1))
+        elif short in VISION_TOP:
+            canon["vision." + VISION_TOP[short]] = store[n]
+        else:
+            m = re.match(r"encoder\.layers\.(\d+)\.(.+)\.(weight|bias)$", short)
+            if m and m.group(2) in VISION_LAYER:
+                canon[f"vision.layers.{m.group(1)}.{VISION_LAYER[m.group(2)]}" + ("_bias" if m.group(3) == "bias" else "")] = store[n]
+    return canon
+
+
 def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWeight]:
     """Canonical role name -> stored tensor for one Hugging Face checkpoint of ``cfg``'s family."""
+    if cfg.family == "idefics3":
+        text = replace(cfg, family="llama")
+        return {**_map_vision(store), **map_checkpoint(text, _Renamed(store, "model.text_model.", "model."))}
     if cfg.family == "bert":
         return _map_bert(cfg, store)
     if cfg.family == "nemotron_h":

@@ -34,6 +34,7 @@ class StepSpec:
     weight_dtype: DType = DType.F32
     sampler: Optional[str] = None  # None = export logits; greedy | gumbel | gumbel_top_k | gumbel_top_k_top_p
     world: int = 1                # tensor-parallel world (the tracer emits all_reduce at the Megatron points)
+    embeds: bool = False          # rows of other modalities replace the embeddings of flagged tokens (image rows of a VLM)
 
     @property
     def slots(self) -> int:
@@ -208,6 +209,11 @@ class Model:
             head_bias = O.alibi_bias_from_pos(b, positions, cap, sl[spec_rank_heads(spec, hq)])
 
         h = b.gather(W("embed"), b.reshape(tokens, (R * T,)), 0)          # [R*T, H]
+        if spec.embeds:
+            # rows computed outside the text stack (a vision connector's output) stand in for flagged tokens' embeddings
+            rows_in = b.slot("embed_rows", (R * T, H), F32, "activation")
+            flagged = b.slot("embed_flags", (R * T,), I32, "activation", range=(0, 1))
+            h = b.select(b.broadcast(b.reshape(flagged, (R * T, 1)), (R * T, H)), rows_in, h)
         if c.embed_scale != 1.0:
             h = h * c.embed_scale
         if c.embed_norm:

@@ -26,7 +26,7 @@ class FamilyEntry:
     gguf_archs: List[str]
     from_hf: Optional[Callable[[dict], DecoderConfig]]
     missing: Optional[str] = None     # capability that is not built when the family is refused
-    kind: str = "decoder"             # decoder (standard stack) | encoder (embeddings / rerank scores)
+    kind: str = "decoder"             # decoder (standard stack) | encoder (embeddings / rerank scores) | vlm (vision tower + decoder)
 
 
 def _rope_params(c: dict, layer_type: Optional[str] = None) -> dict:
@@ -323,6 +323,28 @@ def _qwen35(c):
     return cfg
 
 
+def _idefics3(c):
+    """Idefics3 / SmolVLM: a llama text stack behind a SigLIP-style vision tower and a pixel-shuffle connector."""
+    from .vision import VisionConfig
+    t, v = dict(c.get("text_config") or {}), dict(c.get("vision_config") or {})
+    if (t.get("model_type") or "llama") != "llama":
+        raise UnsupportedFamily(f"idefics3 over a {t.get('model_type')!r} text stack")
+    t.setdefault("tie_word_embeddings", c.get("tie_word_embeddings", False))
+    text = _llama(t)
+    text.family = "idefics3"
+    act = {"gelu_pytorch_tanh": "gelu_tanh", "gelu_new": "gelu_tanh", "gelu": "gelu_erf"}.get(v.get("hidden_act", "gelu_pytorch_tanh"))
+    if act is None:
+        raise UnsupportedFamily(f"idefics3 vision activation {v.get('hidden_act')!r}")
+    vision = VisionConfig(hidden=v.get("hidden_size", 1152), ffn=v.get("intermediate_size", 3072),
+                          n_layers=v.get("num_hidden_layers", 12), n_heads=v.get("num_attention_heads", 16),
+                          channels=v.get("num_channels", 3), image_size=v.get("image_size", 224), patch=v.get("patch_size", 32),
+                          norm_eps=float(v.get("layer_norm_eps", 1e-6)), act=act, scale=int(c.get("scale_factor", 2)),
+                          text_hidden=text.hidden)
+    if vision.per_side % vision.scale:
+        raise UnsupportedFamily(f"idefics3: {vision.per_side} patches per side do not fold by {vision.scale}")
+    return text, vision, int(c.get("image_token_id", 128257))
+
+
 def _bert(c):
     from .encoder import EncoderConfig
     if (c.get("position_embedding_type") or "absolute") != "absolute":
@@ -360,11 +382,11 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("qwen3next", ["qwen3_next"], ["qwen3next"], _qwen3next),
     FamilyEntry("qwen38_27b", ["qwen3_5", "qwen3_5_text"], ["qwen35"], _qwen35),
     FamilyEntry("bert", ["bert"], ["bert"], _bert, kind="encoder"),
+    FamilyEntry("idefics3", ["idefics3", "smolvlm"], [], _idefics3, kind="vlm"),
     # families the reference ships whose mixers are not built here: refused by name
     FamilyEntry("gemma4", ["gemma4"], ["gemma4"], None, "per-layer embeddings, proportional rope"),
     FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], None, "sparse attention indexer"),
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
-    FamilyEntry("idefics3", ["idefics3"], [], None, "vision tower"),
     FamilyEntry("qwen38", ["qwen4_exp"], ["qwen4exp"], None, "block-indexed sparse attention, hyper-connection residual streams, n-gram embeddings"),
     FamilyEntry("glm53_flash", ["glm5_flash"], ["glm53"], None, "kimi delta attention, hyper-connection residual streams"),
     FamilyEntry("qwen_vl", ["qwen2_5_vl"], ["qwen2vl"], None, "vision tower, sectioned mRoPE"),
@@ -392,6 +414,10 @@ class Registry:
                 if e.kind == "encoder":
                     from .encoder import EncoderModel
                     return EncoderModel(e.from_hf(config))
+                if e.kind == "vlm":
+                    from .vision import VisionLanguageModel, VisionTower
+                    text, vision, image_token = e.from_hf(config)
+                    return VisionLanguageModel(Model(text), VisionTower(vision), image_token)
                 return Model(e.from_hf(config))
         raise UnsupportedFamily(f"no family for model_type {mt!r}")
 

@@ -30,6 +30,11 @@ SAMPLES = {
     "qwen38_27b": dict(model_type="qwen3_5_text", linear_num_value_heads=48, linear_num_key_heads=16, linear_key_head_dim=128,
                        linear_value_head_dim=128),
     "bert": dict(model_type="bert", num_attention_heads=12, intermediate_size=3072, hidden_size=768),
+    "idefics3": dict(model_type="idefics3", text_config=dict(model_type="llama", hidden_size=2048, num_hidden_layers=4,
+                                                             num_attention_heads=32, num_key_value_heads=32, intermediate_size=8192,
+                                                             vocab_size=49155),
+                     vision_config=dict(hidden_size=1152, intermediate_size=4304, num_hidden_layers=27, num_attention_heads=16,
+                                        image_size=384, patch_size=14), scale_factor=3, image_token_id=49153),
 }
 BASE = dict(hidden_size=4096, num_hidden_layers=4, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
             intermediate_size=14336, vocab_size=32000, max_position_embeddings=8192)
@@ -49,6 +54,10 @@ def rows():
         model = reg.resolve_hf(header)
         if e.kind == "encoder":
             out.append((e.name, ", ".join(e.hf_types), "oracle", "no", "-", "embeddings and rerank scores on the host evaluator"))
+            continue
+        if e.kind == "vlm":
+            out.append((e.name, ", ".join(e.hf_types), "oracle", "no", "text only",
+                        "image rows in place of embeddings (the text stack alone runs on the device); `caption` evaluates on the host"))
             continue
         gaps = model.cfg.device_gaps()
         device = "yes" if not gaps else "no"

@@ -30,7 +30,9 @@ FAMILY_DEFAULT = {"llama": "llama3", "mistral": "mistral", "mixtral": "mistral",
 
 def render_chat(messages: List[dict], template: Optional[str] = None, family: str = "llama",
                 add_generation_prompt: bool = True, bos_token: str = "", eos_token: str = "",
-                tools: Optional[list] = None) -> str:
+                tools: Optional[list] = None, keep_parts: bool = False) -> str:
+    """``keep_parts`` hands list-valued message contents to the template as they are (multimodal templates walk the
+    parts and write a placeholder per image); otherwise a list collapses to the concatenation of its text parts."""
     from jinja2 import TemplateError as JTE
     from jinja2.sandbox import ImmutableSandboxedEnvironment
     for m in messages:
@@ -47,9 +49,9 @@ def render_chat(messages: List[dict], template: Optional[str] = None, family: st
     norm = []
     for m in messages:
         c = m.get("content")
-        if isinstance(c, list):
+        if isinstance(c, list) and not keep_parts:
             c = "".join(p.get("text", "") for p in c if isinstance(p, dict) and p.get("type") == "text")
-        norm.append({**m, "content": c or ""})
+        norm.append({**m, "content": c if (keep_parts and isinstance(c, list)) else (c or "")})
     try:
         out = env.from_string(src).render(messages=norm, add_generation_prompt=add_generation_prompt,
                                           bos_token=bos_token, eos_token=eos_token, tools=tools)

@@ -1,0 +1,159 @@
+"""Vision-language generation: image frames through the vision tower, their rows in place of the image tokens'
+embeddings, then ordinary decoding (crates/poot-llm/src/bin/poot/caption.rs:38-120; the front-end session of
+crates/poot-models/src/multimodal/front_end.rs).
+
+``VisionLLM.load(dir)`` opens an Idefics3 / SmolVLM checkpoint.  ``prepare`` turns a question and a decoded image into
+prompt tokens and normalised frames; ``generate`` encodes the frames once, prefills the prompt with the image rows
+bound to the flagged positions and decodes greedily.  Both graphs (tower and text stack) evaluate on the CPU oracle:
+the device engine has no binding for rows that replace embeddings yet, so a vision checkpoint is refused there."""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+
+from .driver.handle import ModelHandle
+from .models.image_prep import ImagePrep, image_prompt, preprocess
+from .models.vision import patchify, position_ids
+from .oracle.eval import EvalOptions, eval_graph
+from .oracle.runner import BLOCK, OracleSession
+from .text.chat import render_chat
+from .text.codec import StreamDecoder, load_tokenizer
+
+# the template SmolVLM checkpoints ship, used when a checkpoint directory carries none
+VLM_TEMPLATE = ("<|im_start|>{% for message in messages %}{{message['role'] | capitalize}}"
+                "{% if message['content'][0]['type'] == 'image' %}{{':'}}{% else %}{{': '}}{% endif %}"
+                "{% for line in message['content'] %}{% if line['type'] == 'text' %}{{line['text']}}"
+                "{% elif line['type'] == 'image' %}{{ '<image>' }}{% endif %}{% endfor %}<end_of_utterance>\n{% endfor %}"
+                "{% if add_generation_prompt %}{{ 'Assistant:' }}{% endif %}")
+
+
+class NotVisionModel(ValueError):
+    """The checkpoint's family has no vision front end."""
+
+
+class VisionLLM:
+    def __init__(self, handle: ModelHandle, tokenizer=None, template: Optional[str] = None):
+        if getattr(handle.model, "kind", "decoder") != "vlm":
+            raise NotVisionModel("the checkpoint is not a vision-language model: its family has no front end")
+        self.handle, self.model = handle, handle.model
+        self.vision = self.model.vision
+        self.weights = handle.oracle_weights()
+        self.tokenizer, self.template = tokenizer, template
+        self.prep = ImagePrep.from_dir(handle.source, self.vision.cfg.image_size)
+        self._towers = {}
+        self.eos: List[int] = []                      # end tokens of generation_config.json, beside the tokenizer's
+
+    @staticmethod
+    def load(path: str) -> "VisionLLM":
+        import json
+        import os
+        handle = ModelHandle.load(path)
+        tok, template = None, None
+        if os.path.exists(os.path.join(path, "tokenizer.json")):
+            tok = load_tokenizer(handle)
+        for name, key in (("chat_template.json", "chat_template"), ("tokenizer_config.json", "chat_template")):
+            f = os.path.join(path, name)
+            if template is None and os.path.exists(f):
+                with open(f) as fh:
+                    template = json.load(fh).get(key)
+        f = os.path.join(path, "chat_template.jinja")
+        if template is None and os.path.exists(f):
+            with open(f) as fh:
+                template = fh.read()
+        vlm = VisionLLM(handle, tok, template)
+        f = os.path.join(path, "generation_config.json")
+        if os.path.exists(f):
+            with open(f) as fh:
+                e = json.load(fh).get("eos_token_id")
+            vlm.eos = [int(x) for x in (e if isinstance(e, list) else [e]) if x is not None]
+        return vlm
+
+    # ---- vision tower ----------------------------------------------------------------------------------------------
+    def encode_images(self, pixels: np.ndarray) -> np.ndarray:
+        """``pixels[frames, C, S, S]`` (normalised) -> ``[frames * rows_per_image, text_hidden]``."""
+        c = self.vision.cfg
+        pixels = np.asarray(pixels, dtype=np.float32)
+        n, ch, h, w = pixels.shape
+        if (ch, h, w) != (c.channels, c.image_size, c.image_size):
+            raise ValueError(f"frames of {(ch, h, w)}; the tower takes {(c.channels, c.image_size, c.image_size)}")
+        if n not in self._towers:
+            self._towers[n] = self.vision.trace(n)
+        g = self._towers[n]
+        inputs = {"patches": patchify(pixels, c.patch),
+                  "pos_ids": np.tile(position_ids(c, c.per_side, c.per_side)[None, :], (n, 1))}
+        for i in g.inputs:
+            if i.storage == "const":
+                inputs[i.name] = self.weights[i.name]
+        return eval_graph(g, inputs, EvalOptions(matmul_precision="exact")).outputs["image_rows"]
+
+    # ---- prompt ----------------------------------------------------------------------------------------------------
+    def prepare(self, question: str, image) -> tuple:
+        """``(prompt tokens, frames)`` for one user turn holding ``image`` (a PIL image) and ``question``."""
+        if self.tokenizer is None:
+            raise ValueError("the checkpoint directory has no tokenizer.json")
+        frames = preprocess(image, self.prep)
+        text = render_chat([{"role": "user", "content": [{"type": "image"}, {"type": "text", "text": question}]}],
+                           self.template or VLM_TEMPLATE, family="idefics3", keep_parts=True)
+        expanded = image_prompt(self.prep, frames.rows, frames.cols, self.vision.cfg.rows_per_image)
+        text = text.replace(self.prep.image_token, expanded, 1)
+        return self.tokenizer.encode(text, add_bos=False), frames.pixels
+
+    # ---- generation ------------------------------------------------------------------------------------------------
+    def _session(self, length: int) -> OracleSession:
+        cap = -(-length // BLOCK) * BLOCK
+        return OracleSession(self.model, self.weights, rows=1, capacity=cap, paged=True)
+
+    def prefill(self, sess: OracleSession, tokens: Sequence[int], pixels: Optional[np.ndarray]) -> np.ndarray:
+        """Feed the whole prompt; returns the last position's logits ``[1, vocab]``."""
+        toks = np.asarray(tokens, dtype=np.int32).reshape(1, -1)
+        flags = (toks[0] == self.model.image_token).astype(np.int32)
+        if pixels is None or len(pixels) == 0:
+            if flags.any():
+                raise ValueError("the prompt holds image tokens but no image was given")
+            return sess.step(toks)
+        rows = self.encode_images(pixels)
+        if int(flags.sum()) != rows.shape[0]:
+            raise ValueError(f"the prompt holds {int(flags.sum())} image tokens; the frames give {rows.shape[0]} rows")
+        full = np.zeros((toks.shape[1], rows.shape[1]), dtype=np.float32)
+        full[flags.astype(bool)] = rows
+        return sess.step(toks, embed_rows=full, embed_flags=flags)
+
+    def generate(self, tokens: Sequence[int], pixels: Optional[np.ndarray], max_new: int = 64,
+                 eos: Optional[Sequence[int]] = None, on_token: Optional[Callable[[int], None]] = None) -> List[int]:
+        """Greedy continuation of ``tokens`` (which hold one image token per image row)."""
+        sess = self._session(len(tokens) + max_new)
+        logits = self.prefill(sess, tokens, pixels)
+        stop = set(eos or ())
+        out: List[int] = []
+        for i in range(max_new):
+            tok = int(np.argmax(logits[0]))
+            if tok in stop:
+                break
+            out.append(tok)
+            if on_token is not None:
+                on_token(tok)
+            if i + 1 < max_new:
+                logits = sess.step(np.array([[tok]], dtype=np.int32))
+        return out
+
+    def caption(self, image, question: str = "Can you describe this image?", max_new: int = 64,
+                on_piece: Optional[Callable[[str], None]] = None) -> str:
+        tokens, pixels = self.prepare(question, image)
+        dec = StreamDecoder(self.tokenizer)
+        pieces: List[str] = []
+
+        def emit(tok: int):
+            piece = dec.push(tok)
+            if piece:
+                pieces.append(piece)
+                if on_piece is not None:
+                    on_piece(piece)
+        eos = [t for t in (getattr(self.tokenizer, "eos", None), self.handle.cfg.eos_token, *self.eos) if t is not None]
+        self.generate(tokens, pixels, max_new, eos, emit)
+        tail = dec.flush()
+        if tail:
+            pieces.append(tail)
+            if on_piece is not None:
+                on_piece(tail)
+        return "".join(pieces)

@@ -100,7 +100,7 @@ def test_supported_family_traces_compiles_and_decodes(name):
 def test_refused_families_say_what_is_missing():
     reg = Registry.builtin()
     for mt, word in (("gemma4", "per-layer embeddings"), ("deepseek_v32", "sparse attention"), ("glm5_flash", "delta attention"),
-                     ("idefics3", "vision"), ("qwen2_5_vl", "vision"), ("qwen4_exp", "hyper-connection")):
+                     ("qwen2_5_vl", "vision"), ("qwen4_exp", "hyper-connection")):
         with pytest.raises(UnsupportedFamily) as e:
             reg.resolve_hf({**BASE, "model_type": mt})
         assert word in str(e.value)
@@ -109,7 +109,7 @@ def test_refused_families_say_what_is_missing():
     with pytest.raises(UnsupportedFamily):
         reg.resolve_hf({"model_type": "mpt", "d_model": 64, "n_heads": 4, "n_layers": 2, "vocab_size": 200,
                         "attn_config": {"alibi": False}})
-    assert len(reg.listed()) == 28 and len(reg.supported()) == 21
+    assert len(reg.listed()) == 28 and len(reg.supported()) == 22
 
 
 def test_device_gaps_name_what_the_device_program_lacks():
@@ -139,7 +139,7 @@ def test_torch_restatement_with_folded_scales_matches_the_oracle(name):
         assert any(k.endswith("attn_q_bias") for k in w)
     toks = np.random.default_rng(5).integers(0, cfg.vocab, (1, 10))
     sess = OracleSession(model, w, capacity=32)
-    sess._graph = lambda T, _m=model: _m.trace(__import__("poot_b200.models.model", fromlist=["StepSpec"]).StepSpec(
+    sess._graph = lambda T, embeds=False, _m=model: _m.trace(__import__("poot_b200.models.model", fromlist=["StepSpec"]).StepSpec(
         rows=1, tokens=T, capacity=32, logit_rows="all"))
     ref = sess.step(toks)
     named = {k: torch.from_numpy(v) for k, v in w.items()}

@@ -94,7 +94,7 @@ def test_logits_equal_the_hugging_face_forward(name, tmp_path):
     m.save_pretrained(str(tmp_path), safe_serialization=True)
     h = ModelHandle.load(str(tmp_path))
     sess = OracleSession(h.model, h.oracle_weights(), capacity=32)
-    sess._graph = lambda T: h.model.trace(StepSpec(rows=1, tokens=T, capacity=32, logit_rows="all"))
+    sess._graph = lambda T, embeds=False: h.model.trace(StepSpec(rows=1, tokens=T, capacity=32, logit_rows="all"))
     got = sess.step(toks.numpy()).reshape(ref.shape)
     assert np.isfinite(got).all()
     err = np.abs(got - ref).max() / np.abs(ref).max()

@@ -142,7 +142,7 @@ def test_stage_split_recomposes():
     stages, bounds = split_stages(g, [cut])
     assert len(stages) == 2 and bounds and all(b.producer == 0 and b.consumers == [1] for b in bounds)
     s2 = OracleSession(model, w, rows=1, capacity=32)
-    s2.graphs[3] = g
+    s2.graphs[(3, False)] = g
     inputs = {}
     # feed through the session's own input builder by running stage by stage
     carried = {}
@@ -150,7 +150,7 @@ def test_stage_split_recomposes():
 
     def run_stage(sg, extra):
         s = OracleSession(model, w, rows=1, capacity=32)
-        s.graphs[3] = sg
+        s.graphs[(3, False)] = sg
         orig = eval_graph
 
         return s
@@ -189,7 +189,7 @@ def test_rank_walk_of_the_sharded_graphs_matches_one_rank(world):
         for got in per_rank:
             assert np.allclose(got, r, rtol=1e-5, atol=1e-6)        # partial sums reassociate the K reduction
         assert all(np.array_equal(per_rank[0], x) for x in per_rank[1:])   # every rank holds the same result
-    g0 = walk.sessions[0].graphs[1]
+    g0 = walk.sessions[0].graphs[(1, False)]
     assert g0.summary().get("all_reduce") == 2 * model.cfg.n_layers
 
 

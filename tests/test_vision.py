@@ -1,0 +1,181 @@
+"""Vision-language family (Idefics3 / SmolVLM): tower + connector + text stack against the Hugging Face implementation,
+image preprocessing against its processor, prompt expansion, and the ``caption`` command end to end."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+transformers = pytest.importorskip("transformers")
+PIL = pytest.importorskip("PIL")
+
+from poot_b200.models.image_prep import ImagePrep, image_prompt, preprocess, resize_for_encoder, resize_longest, split_geometry
+from poot_b200.models.vision import VisionConfig, patchify, position_ids
+from poot_b200.vlm import NotVisionModel, VisionLLM
+
+SPECIALS = ["<|im_start|>", "<end_of_utterance>", "<fake_token_around_image>", "<global-img>", "<image>"] + \
+           [f"<row_{r}_col_{c}>" for r in range(1, 4) for c in range(1, 4)]
+
+
+def _tokenizer(path):
+    """Byte-level tokenizer (256 byte tokens) with the front end's marker tokens added behind them."""
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers
+    alphabet = pre_tokenizers.ByteLevel.alphabet()
+    vocab = {ch: i for i, ch in enumerate(sorted(alphabet))}
+    tk = Tokenizer(models.BPE(vocab=vocab, merges=[]))
+    tk.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tk.decoder = decoders.ByteLevel()
+    tk.add_special_tokens(SPECIALS)
+    tk.save(os.path.join(path, "tokenizer.json"))
+    with open(os.path.join(path, "tokenizer_config.json"), "w") as f:
+        json.dump({"eos_token": "<end_of_utterance>"}, f)
+    return tk
+
+
+@pytest.fixture(scope="module")
+def checkpoint(tmp_path_factory):
+    from transformers import Idefics3Config, Idefics3ForConditionalGeneration
+    d = str(tmp_path_factory.mktemp("idefics3"))
+    tk = _tokenizer(d)
+    image_token = tk.token_to_id("<image>")
+    torch.manual_seed(0)
+    cfg = Idefics3Config(
+        text_config=dict(model_type="llama", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=2, vocab_size=tk.get_vocab_size(), max_position_embeddings=512, rms_norm_eps=1e-5),
+        vision_config=dict(hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, image_size=32,
+                           patch_size=8, num_channels=3),
+        scale_factor=2, image_token_id=image_token, pad_token_id=0)
+    hf = Idefics3ForConditionalGeneration(cfg).eval()
+    for p in hf.parameters():                                   # biases and norms away from their constant init
+        if p.ndim == 1:
+            p.data.add_(torch.randn_like(p) * 0.05)
+    hf.save_pretrained(d, safe_serialization=True)
+    with open(os.path.join(d, "preprocessor_config.json"), "w") as f:
+        json.dump({"size": {"longest_edge": 64}, "max_image_size": {"longest_edge": 32}, "do_image_splitting": True,
+                   "image_mean": [0.5] * 3, "image_std": [0.5] * 3, "rescale_factor": 1 / 255}, f)
+    return d, hf, image_token
+
+
+def test_logits_and_greedy_continuation_match_transformers(checkpoint):
+    d, hf, image_token = checkpoint
+    vlm = VisionLLM.load(d)
+    rpi = vlm.vision.cfg.rows_per_image
+    assert rpi == 4 and vlm.model.image_token == image_token
+    rng = np.random.default_rng(0)
+    pixels = rng.standard_normal((2, 3, 32, 32)).astype(np.float32)
+    tokens = [5, 6] + [image_token] * rpi + [7] + [image_token] * rpi + [8, 9, 10]
+    with torch.no_grad():
+        out = hf(input_ids=torch.tensor([tokens]), pixel_values=torch.tensor(pixels)[None],
+                 attention_mask=torch.ones(1, len(tokens), dtype=torch.long))
+    want = out.logits[0, -1].numpy()
+    sess = vlm._session(len(tokens))
+    got = vlm.prefill(sess, tokens, pixels)[0]
+    assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    # the image rows matter: the same tokens without them give different logits
+    plain = vlm._session(len(tokens)).step(np.asarray([tokens], dtype=np.int32))[0]
+    assert np.abs(plain - want).max() > 1e-3
+    with torch.no_grad():
+        gen = hf.generate(input_ids=torch.tensor([tokens]), pixel_values=torch.tensor(pixels)[None],
+                          attention_mask=torch.ones(1, len(tokens), dtype=torch.long), max_new_tokens=6, do_sample=False,
+                          eos_token_id=None, pad_token_id=0)
+    assert vlm.generate(tokens, pixels, max_new=6) == gen[0, len(tokens):].tolist()
+
+
+def test_image_rows_must_match_the_image_tokens(checkpoint):
+    d, _, image_token = checkpoint
+    vlm = VisionLLM.load(d)
+    pixels = np.zeros((1, 3, 32, 32), dtype=np.float32)
+    with pytest.raises(ValueError, match="image tokens"):
+        vlm.prefill(vlm._session(16), [1, image_token, 2], pixels)
+    with pytest.raises(ValueError, match="no image"):
+        vlm.prefill(vlm._session(16), [1, image_token, 2], None)
+    with pytest.raises(ValueError, match="tower takes"):
+        vlm.encode_images(np.zeros((1, 3, 16, 16), dtype=np.float32))
+
+
+def test_position_ids_and_patch_order():
+    c = VisionConfig(image_size=32, patch=8)
+    assert position_ids(c, 4, 4).tolist() == list(range(16))            # a full square image: the identity
+    assert position_ids(c, 2, 2).tolist() == [0, 2, 8, 10]              # a smaller grid lands on every other bucket
+    x = np.arange(2 * 3 * 16 * 16, dtype=np.float32).reshape(2, 3, 16, 16)
+    p = patchify(x, 8)
+    assert p.shape == (2, 4, 192)
+    conv = torch.nn.functional.unfold(torch.tensor(x), kernel_size=8, stride=8).transpose(1, 2).numpy()
+    assert np.array_equal(p, conv)
+    ragged = np.arange(3 * 20 * 20, dtype=np.float32).reshape(1, 3, 20, 20)          # 20 / 8: the last 4 pixels are dropped
+    conv = torch.nn.functional.unfold(torch.tensor(ragged), kernel_size=8, stride=8).transpose(1, 2).numpy()
+    assert np.array_equal(patchify(ragged, 8), conv)
+
+
+@pytest.mark.parametrize("hw", [(300, 500), (640, 200), (40, 40), (31, 77)])
+def test_preprocessing_matches_the_reference_processor(hw):
+    from PIL import Image
+    from transformers.models.idefics3.image_processing_pil_idefics3 import Idefics3ImageProcessorPil
+    from transformers.models.idefics3.processing_idefics3 import get_image_prompt_string
+    rng = np.random.default_rng(1)
+    img = Image.fromarray(rng.integers(0, 255, (*hw, 3), dtype=np.uint8))
+    for tile, longest in ((64, 256), (32, 50)):
+        ip = Idefics3ImageProcessorPil(size={"longest_edge": longest}, max_image_size={"longest_edge": tile},
+                                       image_mean=[0.5] * 3, image_std=[0.5] * 3)
+        out = ip(images=[img], return_tensors="np", return_row_col_info=True)
+        prep = ImagePrep(longest_edge=longest, tile=tile)
+        fr = preprocess(img, prep)
+        assert (fr.rows, fr.cols) == (out["rows"][0][0], out["cols"][0][0])
+        assert fr.pixels.shape == out["pixel_values"][0].shape
+        assert np.abs(fr.pixels - out["pixel_values"][0]).max() < 1e-6
+        want = get_image_prompt_string(fr.rows, fr.cols, 4, "<fake_token_around_image>", "<image>", "<global-img>")
+        assert image_prompt(prep, fr.rows, fr.cols, 4) == want
+
+
+def test_resize_geometry():
+    assert resize_longest(300, 500, 100) == (60, 100)
+    assert resize_longest(501, 100, 100) == (100, 20)               # odd short edge rounds up to even
+    assert resize_for_encoder(60, 100, 32) == (96, 128)
+    assert split_geometry(96, 128, 32) == (3, 4) and split_geometry(32, 32, 32) == (0, 0)
+    one = preprocess(__import__("PIL.Image", fromlist=["x"]).new("RGB", (20, 20)), ImagePrep(longest_edge=32, tile=32))
+    assert one.pixels.shape == (1, 3, 32, 32) and (one.rows, one.cols) == (0, 0)
+    unsplit = preprocess(__import__("PIL.Image", fromlist=["x"]).new("L", (90, 50)), ImagePrep(longest_edge=64, tile=32, split=False))
+    assert unsplit.pixels.shape == (1, 3, 32, 32)
+
+
+def test_caption_command_end_to_end(checkpoint, tmp_path, capsys):
+    from PIL import Image
+    from poot_b200.cli.__main__ import main
+    d, hf, image_token = checkpoint
+    rng = np.random.default_rng(2)
+    path = str(tmp_path / "picture.png")
+    img = Image.fromarray(rng.integers(0, 255, (40, 60, 3), dtype=np.uint8))
+    img.save(path)
+    vlm = VisionLLM.load(d)
+    tokens, pixels = vlm.prepare("What is this?", img)
+    # 60x40 scales to 64x44 -> rounds up to 64x64 -> 2x2 tiles plus the global frame
+    assert pixels.shape == (5, 3, 32, 32) and tokens.count(image_token) == 5 * vlm.vision.cfg.rows_per_image
+    text = vlm.tokenizer.tk.decode(tokens, skip_special_tokens=False)
+    assert text.startswith("<|im_start|>User:<fake_token_around_image><row_1_col_1><image>") and text.endswith("Assistant:")
+    assert "<global-img>" in text and "What is this?<end_of_utterance>" in text
+    with torch.no_grad():
+        gen = hf.generate(input_ids=torch.tensor([tokens]), pixel_values=torch.tensor(pixels)[None],
+                          attention_mask=torch.ones(1, len(tokens), dtype=torch.long), max_new_tokens=5, do_sample=False,
+                          eos_token_id=None, pad_token_id=0)
+    want = gen[0, len(tokens):].tolist()
+    assert vlm.generate(tokens, pixels, max_new=5) == want
+    assert main(["caption", d, path, "What is this?", "-n", "5"]) == 0
+    out = capsys.readouterr().out
+    eos = vlm.tokenizer.eos
+    shown = want[:want.index(eos)] if eos in want else want
+    from poot_b200.text.codec import StreamDecoder
+    dec = StreamDecoder(vlm.tokenizer)
+    streamed = "".join(dec.push(t) for t in shown) + dec.flush()
+    assert out == streamed + "\n"
+    assert main(["caption", d, str(tmp_path / "missing.png")]) == 1
+    assert main(["caption", d]) == 2
+
+
+def test_text_checkpoints_have_no_front_end(tmp_path):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    d = str(tmp_path / "llama")
+    LlamaForCausalLM(LlamaConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2,
+                                 num_key_value_heads=2, vocab_size=64)).save_pretrained(d, safe_serialization=True)
+    with pytest.raises(NotVisionModel):
+        VisionLLM.load(d)
