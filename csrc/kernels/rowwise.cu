@@ -202,6 +202,20 @@ __global__ void act_bf16_kernel(__nv_bfloat16* __restrict__ x, size_t n, int act
   }
 }
 
+// h[t, :] = rows[t, :] for the rows whose flag is set (rows of another modality in place of token embeddings);
+// 16-byte chunks, D a multiple of 8
+__global__ void replace_rows_kernel(__nv_bfloat16* __restrict__ h, const __nv_bfloat16* __restrict__ rows,
+                                    const int* __restrict__ flags, int T, int D) {
+  pdl_wait(); pdl_launch();
+  const int chunks = D / 8;
+  const size_t total = (size_t)T * chunks;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / chunks);
+    if (flags[t] == 0) continue;
+    reinterpret_cast<uint4*>(h)[i] = reinterpret_cast<const uint4*>(rows)[i];
+  }
+}
+
 // x = cap * tanh(x / cap) in place over fp32 logits
 __global__ void softcap_f32_kernel(float* __restrict__ x, size_t n, float cap, float inv_cap) {
   pdl_wait(); pdl_launch();
@@ -333,6 +347,16 @@ POOT_API int poot_act_bf16(void* x, long long n, int act, cudaStream_t s) {
   int blocks = (int)((n + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   return launch_k(act_bf16_kernel, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16*)x, (size_t)n, act);
+}
+
+POOT_API int poot_replace_rows(void* h, const void* rows, const int* flags, int T, int D, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (D < 8 || D % 8 != 0) return (int)cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(rows)) & 15) return (int)cudaErrorInvalidValue;
+  size_t total = (size_t)T * (D / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch_k(replace_rows_kernel, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16*)h, (const __nv_bfloat16*)rows, flags, T, D);
 }
 
 POOT_API int poot_softcap_f32(void* x, long long n, float cap, cudaStream_t s) {

@@ -1,6 +1,7 @@
 """``caption MODEL_DIR IMAGE [QUESTION]``: caption an image with a vision-language checkpoint
 (crates/poot-llm/src/bin/poot/caption.rs:26-37: positional checkpoint directory, image file and question, 64 greedy
-tokens streamed to stdout).  The image is decoded with Pillow; an animated file contributes its first frame."""
+tokens streamed to stdout; ``--backend`` picks the text stack's executor as the reference's device flags do).  The
+image is decoded with Pillow; an animated file contributes its first frame."""
 from __future__ import annotations
 
 import argparse
@@ -22,9 +23,13 @@ def parse_caption(argv: List[str]) -> argparse.Namespace:
     p.add_argument("image")
     p.add_argument("question", nargs="?", default=DEFAULT_QUESTION)
     p.add_argument("-n", "--predict", type=int, default=MAX_NEW)
+    p.add_argument("--backend", default="auto", choices=("auto", "device", "oracle"))
+    p.add_argument("-c", "--ctx-size", type=int, default=0, help="text window (0: 8192 on the device, 2048 on the oracle)")
     a = p.parse_args(argv)
     if a.predict <= 0:
         raise ValueError("--predict must be positive")
+    if a.ctx_size < 0:
+        raise ValueError("--ctx-size must not be negative")
     return a
 
 
@@ -43,8 +48,13 @@ def main_caption(argv: List[str]) -> int:
     except Exception as e:                                  # unreadable or undecodable file
         print(f"error: decode {args.image}: {e}", file=sys.stderr)
         return 1
+    backend = args.backend
+    if backend == "auto":
+        import torch
+        backend = "device" if torch.cuda.is_available() else "oracle"
+    ctx = args.ctx_size or (8192 if backend == "device" else 2048)
     try:
-        vlm = VisionLLM.load(args.model_dir)
+        vlm = VisionLLM.load(args.model_dir, backend=backend, rows=1, max_seq=ctx)
     except (NotVisionModel, UnsupportedFamily, FileNotFoundError) as e:
         print(f"error: {e}", file=sys.stderr)
         return 1

@@ -62,6 +62,8 @@ class StepInputs:
     live_tokens: int = 0
     live_rows: int = 0
     adapter_rows: Optional[np.ndarray] = None   # [T] int32 adapter slot of every token row (-1 = none); None = no row uses one
+    embed_flags: Optional[np.ndarray] = None    # [T] int32, 1 = the token's embedding is replaced by its row of embed_rows
+    embed_rows: Optional[np.ndarray] = None     # [T, hidden] f32 (rows without a flag are zero); None = no token is replaced
 
 
 @dataclass
@@ -89,6 +91,8 @@ class Sequence_:
     guided: Optional[object] = None                        # constraint object with .mask(vocab) / .advance(token)
     seed: int = 0
     adapter_slot: int = -1                                 # resident LoRA adapter of the sequence (-1 = base model)
+    embed_pos: Optional[np.ndarray] = None                 # sorted prompt positions whose embeddings are replaced ...
+    embed_rows: Optional[np.ndarray] = None                # ... by these rows [len(embed_pos), hidden] (image rows of a VLM)
 
     @property
     def pending(self) -> int:
@@ -152,12 +156,25 @@ class Driver:
         return bool(self._free_rows) and need <= free + (len(self.prefix) if self.prefix is not None else 0)
 
     def open(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, identity: int = BASE_IDENTITY,
-             guided=None, adapter_slot: int = -1) -> int:
+             guided=None, adapter_slot: int = -1, embeds=None) -> int:
         """``adapter_slot``: slot of a resident LoRA adapter the sequence runs with (-1 = the base model).  K/V computed
-        under one adapter is not valid under another, so the prefix-cache identity is taken per slot."""
+        under one adapter is not valid under another, so the prefix-cache identity is taken per slot.
+        ``embeds``: ``(positions, rows[len(positions), hidden])``: rows of another modality that replace the embeddings
+        of those prompt tokens (crates/poot-llm/src/driver: ``generate_with_inputs``).  The tokens at those positions are
+        placeholders that say nothing about the rows, so the prefix-cache identity also covers the rows' content."""
         params = params or SamplingParams()
+        embed_pos = embed_rows = None
+        if embeds is not None:
+            embed_pos = np.asarray(embeds[0], dtype=np.int64).reshape(-1)
+            embed_rows = np.ascontiguousarray(embeds[1], dtype=np.float32).reshape(len(embed_pos), -1)
+            if len(embed_pos) and (np.any(np.diff(embed_pos) <= 0) or embed_pos[0] < 0 or embed_pos[-1] >= len(prompt)):
+                raise DriverError("embedding rows must name distinct prompt positions in ascending order")
         if adapter_slot >= 0 and identity == BASE_IDENTITY:
             identity = (BASE_IDENTITY ^ (0x9E3779B97F4A7C15 * (adapter_slot + 1))) & 0xFFFFFFFFFFFFFFFF
+        if embed_pos is not None and len(embed_pos):
+            import zlib
+            digest = zlib.crc32(embed_rows.tobytes(), zlib.crc32(embed_pos.tobytes()))
+            identity = (identity ^ (0xC2B2AE3D27D4EB4F * (digest + 1))) & 0xFFFFFFFFFFFFFFFF
         params.validate()
         prompt = [int(t) for t in prompt]
         if not prompt:
@@ -190,6 +207,7 @@ class Driver:
                         computed=len(matched) * BLOCK, cached_tokens=len(matched) * BLOCK, guided=guided,
                         seed=params.seed if params.seed is not None else (sid * 2654435761) & 0x7FFFFFFF)
         seq.adapter_slot = int(adapter_slot)
+        seq.embed_pos, seq.embed_rows = embed_pos, embed_rows
         for t in prompt:
             seq.counts[t] = seq.counts.get(t, 0) + 1
         self.seqs[sid] = seq
@@ -249,10 +267,20 @@ class Driver:
         rule, off, b = S.GREEDY, 0, 0
         adjust_rows, guided_rows, want_lp = {}, {}, False
         adapter_rows = np.full(Tp, -1, np.int32) if any(s.adapter_slot >= 0 for s, _ in rows) else None
+        embed_flags = embed_vals = None
         for s, piece in rows:
             p0 = s.computed
             if adapter_rows is not None:
                 adapter_rows[off:off + piece] = s.adapter_slot
+            if s.embed_pos is not None and p0 < s.prompt_len:
+                lo, hi = np.searchsorted(s.embed_pos, (p0, p0 + piece))
+                if hi > lo:
+                    if embed_flags is None:
+                        embed_flags = np.zeros(Tp, np.int32)
+                        embed_vals = np.zeros((Tp, s.embed_rows.shape[1]), np.float32)
+                    at = off + (s.embed_pos[lo:hi] - p0)
+                    embed_flags[at] = 1
+                    embed_vals[at] = s.embed_rows[lo:hi]
             if piece == 1:       # decode row: scalar stores (a numpy slice per row would cost more than the row)
                 tokens[off], positions[off], row_seq[off], row_ctx[off] = s.tokens[p0], p0, s.row, p0 + 1
                 slots[off] = s.blocks[p0 // BLOCK] * BLOCK + p0 % BLOCK
@@ -301,7 +329,7 @@ class Driver:
         check_write_slots(slots[:T])            # two rows writing one K/V slot in a step would race on the device
         self.stats["padded_tokens"] += Tp - T
         return StepInputs(tokens, positions, slots, row_seq, row_ctx, logit_idx, rule, params, top_k, seeds, adjust,
-                          want_lp, T, B, adapter_rows)
+                          want_lp, T, B, adapter_rows, embed_flags, embed_vals)
 
     def step(self, seq_ids: Optional[Iterable[int]] = None) -> List[RowResult]:
         rows = self.plan(seq_ids)
@@ -370,8 +398,8 @@ class Driver:
         return {"registered_tokens": registered, "generated": s.generated, "cached_tokens": s.cached_tokens}
 
     # ------------------------------------------------------------------------------------------------ convenience
-    def generate(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, on_token=None) -> List[int]:
-        sid = self.open(prompt, params)
+    def generate(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, on_token=None, embeds=None) -> List[int]:
+        sid = self.open(prompt, params, embeds=embeds)
         out: List[int] = []
         try:
             while True:

@@ -125,7 +125,10 @@ class DeviceStepEngine:
             if e.lora is None:
                 raise RuntimeError("a sequence names an adapter slot but the engine has no adapter bank")
             lora = e.lora.bind_rows(inp.adapter_rows, T)
-        shape = StepShape(T, B, inp.sampler, False, inp.adjust is not None, guided, inp.want_logprobs, lora)
+        embeds = inp.embed_flags is not None
+        if embeds:
+            e.bind_embeds(torch.from_numpy(inp.embed_flags[:T]), torch.from_numpy(inp.embed_rows[:T]))
+        shape = StepShape(T, B, inp.sampler, False, inp.adjust is not None, guided, inp.want_logprobs, lora, embeds)
         import time as _time
         t0 = _time.perf_counter()
         ev = None
@@ -186,16 +189,17 @@ class OracleStepEngine:
     def write_block_table(self, row: int, blocks) -> None:
         self.block_tables[row, :len(blocks)] = np.asarray(blocks, np.int32)
 
-    def _graph(self, tokens: int, capacity: int):
-        key = (tokens, capacity)
+    def _graph(self, tokens: int, capacity: int, embeds: bool = False):
+        key = (tokens, capacity, embeds)
         if key not in self.graphs:
             from ..models.model import StepSpec
             g = self.model.trace(StepSpec(rows=1, tokens=tokens, capacity=capacity, paged=True,
-                                          pool_slots=self.num_blocks * self.block))
+                                          pool_slots=self.num_blocks * self.block, embeds=embeds))
             self.graphs[key] = self.graph_transform(g) if self.graph_transform is not None else g
         return self.graphs[key]
 
-    def _segment(self, row: int, tokens: np.ndarray, positions: np.ndarray, slots: np.ndarray, ctx: int) -> np.ndarray:
+    def _segment(self, row: int, tokens: np.ndarray, positions: np.ndarray, slots: np.ndarray, ctx: int,
+                 embed_flags: Optional[np.ndarray] = None, embed_rows: Optional[np.ndarray] = None) -> np.ndarray:
         from ..oracle.eval import eval_graph
         blocks = max(1, -(-ctx // self.block))
         cap_blocks = 1
@@ -203,11 +207,14 @@ class OracleStepEngine:
             cap_blocks *= 2
         cap_blocks = min(cap_blocks, self.max_blocks)
         cap = cap_blocks * self.block
-        g = self._graph(len(tokens), cap)
+        embeds = embed_flags is not None and bool(embed_flags.any())
+        g = self._graph(len(tokens), cap, embeds)
         bt = self.block_tables[row, :cap_blocks].astype(np.int64)
         read = (bt[:, None] * self.block + np.arange(self.block)[None, :]).reshape(1, cap).astype(np.int32)
         inputs = {"tokens": tokens.reshape(1, -1).astype(np.int32), "positions": positions.reshape(1, -1).astype(np.int32),
                   "read_map": read, "write_map": slots.astype(np.int32)}
+        if embeds:
+            inputs["embed_flags"], inputs["embed_rows"] = embed_flags.astype(np.int32), embed_rows.astype(np.float32)
         fresh = int(positions[0]) == 0        # a sequence's first segment starts its recurrences from zero
         keys = {}
         for i in g.inputs:
@@ -241,8 +248,10 @@ class OracleStepEngine:
             while end < T and int(inp.row_seq[end]) == row and int(inp.positions[end]) == int(inp.positions[end - 1]) + 1:
                 end += 1
             if int(inp.row_ctx[start]) > 0:       # padding tokens have no context and write nothing
+                ef = inp.embed_flags[start:end] if inp.embed_flags is not None else None
+                er = inp.embed_rows[start:end] if inp.embed_flags is not None else None
                 out = self._segment(row, inp.tokens[start:end], inp.positions[start:end], inp.slots[start:end],
-                                    int(inp.row_ctx[end - 1]))
+                                    int(inp.row_ctx[end - 1]), ef, er)
                 if end - 1 in want:
                     logits[want[end - 1]] = out
             start = end

@@ -160,8 +160,10 @@ class LLM:
         return LLM(cfg, drv, tokenizer, None, handle, None)
 
     # ---- generation ----------------------------------------------------------------------------------------------
-    def generate_tokens(self, prompt: Iterable[int], params: Optional[SamplingParams] = None, on_token=None) -> List[int]:
-        return self.driver.generate(list(prompt), params, on_token)
+    def generate_tokens(self, prompt: Iterable[int], params: Optional[SamplingParams] = None, on_token=None,
+                        embeds=None) -> List[int]:
+        """``embeds``: ``(positions, rows)`` replacing the embeddings of those prompt tokens (image rows of a VLM)."""
+        return self.driver.generate(list(prompt), params, on_token, embeds=embeds)
 
     def generate(self, prompt: str, params: Optional[SamplingParams] = None, on_text=None) -> str:
         dec = StreamDecoder(self.tokenizer)

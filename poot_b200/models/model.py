@@ -209,13 +209,13 @@ class Model:
             head_bias = O.alibi_bias_from_pos(b, positions, cap, sl[spec_rank_heads(spec, hq)])
 
         h = b.gather(W("embed"), b.reshape(tokens, (R * T,)), 0)          # [R*T, H]
+        if c.embed_scale != 1.0:
+            h = h * c.embed_scale
         if spec.embeds:
             # rows computed outside the text stack (a vision connector's output) stand in for flagged tokens' embeddings
             rows_in = b.slot("embed_rows", (R * T, H), F32, "activation")
             flagged = b.slot("embed_flags", (R * T,), I32, "activation", range=(0, 1))
             h = b.select(b.broadcast(b.reshape(flagged, (R * T, 1)), (R * T, H)), rows_in, h)
-        if c.embed_scale != 1.0:
-            h = h * c.embed_scale
         if c.embed_norm:
             h = norm(h, "embed_norm")
         scale = c.attn_scale if c.attn_scale is not None else 1.0 / math.sqrt(D)

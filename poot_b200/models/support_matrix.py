@@ -56,8 +56,8 @@ def rows():
             out.append((e.name, ", ".join(e.hf_types), "oracle", "no", "-", "embeddings and rerank scores on the host evaluator"))
             continue
         if e.kind == "vlm":
-            out.append((e.name, ", ".join(e.hf_types), "oracle", "no", "text only",
-                        "image rows in place of embeddings (the text stack alone runs on the device); `caption` evaluates on the host"))
+            out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "text stack",
+                        "a device program for the vision tower (it is evaluated on the host, once per image)"))
             continue
         gaps = model.cfg.device_gaps()
         device = "yes" if not gaps else "no"

@@ -26,6 +26,7 @@ _SIGS = {
     "poot_softcap_f32": [_P, c_longlong, c_float, _P],
     "poot_layernorm": [_P, _P, _P, c_float, _P, c_int, c_int, _P],
     "poot_act_bf16": [_P, c_longlong, c_int, _P],
+    "poot_replace_rows": [_P, _P, _P, c_int, c_int, _P],
     "poot_causal_conv_silu": [_P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, _P],
     "poot_ssd_scan": [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "poot_gdn_scan": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
@@ -258,6 +259,16 @@ def act_(x: torch.Tensor, act: str) -> torch.Tensor:
     assert x.dtype == torch.bfloat16 and x.is_contiguous()
     check(_fn("poot_act_bf16")(_ptr(x), x.numel(), PLAIN_ACTS[act], _stream()), "act")
     return x
+
+
+def replace_rows_(h: torch.Tensor, rows: torch.Tensor, flags: torch.Tensor) -> torch.Tensor:
+    """``h[t] = rows[t]`` where ``flags[t] != 0`` (bf16 ``[T, D]``, int32 ``[T]``): rows of another modality (a vision
+    connector's output) in place of the token embeddings."""
+    _need_cuda(h, rows, flags)
+    assert h.dtype == rows.dtype == torch.bfloat16 and flags.dtype == torch.int32
+    assert h.is_contiguous() and rows.is_contiguous() and h.shape == rows.shape and flags.numel() == h.shape[0]
+    check(_fn("poot_replace_rows")(_ptr(h), _ptr(rows), _ptr(flags), h.shape[0], h.shape[1], _stream()), "replace_rows")
+    return h
 
 
 def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:

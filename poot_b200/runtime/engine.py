@@ -34,6 +34,7 @@ class StepShape:
     guided: bool = False    # also add the dense guided-decoding mask
     logprobs: bool = False  # record the picked token's log-probability
     lora: bool = False      # some row of the step selects a resident adapter (adds the per-row low-rank terms)
+    embeds: bool = False    # rows of another modality replace the embeddings of flagged tokens (``bind_embeds``)
 
 
 class KVPool:
@@ -220,9 +221,23 @@ class DecoderEngine:
         if comm is not None:
             comm.attach(self)
         self.lora = None                    # bank of resident adapters, created by enable_adapters()
+        self.embed_rows = self.embed_flags = None   # staging of rows that replace embeddings, created by bind_embeds()
         self._graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.launches_per_step: Dict[Tuple, int] = {}
         self._launch_counter = 0
+
+    def bind_embeds(self, flags: torch.Tensor, rows: torch.Tensor) -> None:
+        """Stage the rows that replace token embeddings in the next step: ``flags[T]`` int32 (1 = replace) and
+        ``rows[T, hidden]`` (any float dtype; rows without a flag are ignored).  The buffers have fixed addresses, so a
+        captured step graph replays over them."""
+        if self.tp != 1 or (self.stage is not None and not self.stage.first):
+            raise ValueError("rows in place of embeddings: single-rank engines and the first pipeline stage only")
+        if self.embed_rows is None:
+            self.embed_rows = torch.zeros(self.max_tokens, self.cfg.hidden, dtype=torch.bfloat16, device=self.device)
+            self.embed_flags = torch.zeros(self.max_tokens, dtype=torch.int32, device=self.device)
+        T = flags.numel()
+        self.embed_flags[:T].copy_(flags, non_blocking=True)
+        self.embed_rows[:T].copy_(rows, non_blocking=True)
 
     def enable_adapters(self, slots: int = 8, max_rank: int = 64):
         """Create the bank of resident LoRA adapters (per-row selection); see ``runtime/lora_bank.py``."""
@@ -352,6 +367,9 @@ class DecoderEngine:
                 K.embed_gather(self.tokens[:T], w.embed, out=h)
             if cfg.embed_scale != 1.0:
                 h.mul_(cfg.embed_scale)
+            if shape.embeds:
+                self._count()
+                K.replace_rows_(h, self.embed_rows[:T], self.embed_flags[:T])
             if w.embed_norm is not None:
                 self._count()
                 K.layernorm(h, w.embed_norm, w.embed_norm_b, cfg.norm_eps, out=h)
@@ -746,7 +764,7 @@ class DecoderEngine:
     def _key(self, shape: StepShape):
         flash_only = self.flash_ok and shape.tokens > shape.logit_rows and self._flash_only
         return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain, shape.adjust, shape.guided, shape.logprobs,
-                flash_only, shape.lora)
+                flash_only, shape.lora, shape.embeds)
 
     def prepare(self, shape: StepShape) -> None:
         """Warm up and capture the step graph for ``shape`` (never done in the serving path afterwards)."""

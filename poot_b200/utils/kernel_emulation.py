@@ -105,6 +105,12 @@ def act_(x, act):
     return x
 
 
+def replace_rows_(h, rows, flags):
+    sel = flags.bool()
+    h[sel] = rows[sel]
+    return h
+
+
 def softcap_(x, cap):
     x.copy_(cap * torch.tanh(x / cap))
     return x
@@ -528,7 +534,7 @@ def emulated_kernels():
     from ..ops import moe_ops, suffix_ops
     table = {
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
-                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, ssd_scan=ssd_scan,
+                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, replace_rows_=replace_rows_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, ssd_scan=ssd_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
                 attn_paged=attn_paged, attn_general=attn_general, mla_qkv_write=mla_qkv_write, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,

@@ -3,9 +3,11 @@ embeddings, then ordinary decoding (crates/poot-llm/src/bin/poot/caption.rs:38-1
 crates/poot-models/src/multimodal/front_end.rs).
 
 ``VisionLLM.load(dir)`` opens an Idefics3 / SmolVLM checkpoint.  ``prepare`` turns a question and a decoded image into
-prompt tokens and normalised frames; ``generate`` encodes the frames once, prefills the prompt with the image rows
-bound to the flagged positions and decodes greedily.  Both graphs (tower and text stack) evaluate on the CPU oracle:
-the device engine has no binding for rows that replace embeddings yet, so a vision checkpoint is refused there."""
+prompt tokens and normalised frames; ``generate`` encodes the frames once and opens a sequence on the text driver
+whose image-token positions carry the image rows (``Driver.open(..., embeds=)``), so chunked prefill, the paged K/V
+cache, the prefix cache (keyed on the rows' content) and sampling are the ordinary ones.  ``backend="oracle"`` runs the
+text stack on the host evaluator, ``backend="device"`` on the B200 engine; the vision tower is evaluated on the host
+in both (one pass per image)."""
 from __future__ import annotations
 
 from typing import Callable, List, Optional, Sequence
@@ -16,6 +18,7 @@ from .driver.handle import ModelHandle
 from .models.image_prep import ImagePrep, image_prompt, preprocess
 from .models.vision import patchify, position_ids
 from .oracle.eval import EvalOptions, eval_graph
+from .driver.sampler import SamplingParams
 from .oracle.runner import BLOCK, OracleSession
 from .text.chat import render_chat
 from .text.codec import StreamDecoder, load_tokenizer
@@ -33,22 +36,33 @@ class NotVisionModel(ValueError):
 
 
 class VisionLLM:
-    def __init__(self, handle: ModelHandle, tokenizer=None, template: Optional[str] = None):
+    def __init__(self, handle: ModelHandle, tokenizer=None, template: Optional[str] = None, llm=None):
         if getattr(handle.model, "kind", "decoder") != "vlm":
             raise NotVisionModel("the checkpoint is not a vision-language model: its family has no front end")
         self.handle, self.model = handle, handle.model
         self.vision = self.model.vision
         self.weights = handle.oracle_weights()
         self.tokenizer, self.template = tokenizer, template
+        self.llm = llm                                # text driver (None: a bare oracle session per call)
         self.prep = ImagePrep.from_dir(handle.source, self.vision.cfg.image_size)
         self._towers = {}
         self.eos: List[int] = []                      # end tokens of generation_config.json, beside the tokenizer's
 
     @staticmethod
-    def load(path: str) -> "VisionLLM":
+    def load(path: str, backend: str = "oracle", device="cuda", rows: int = 4, max_seq: int = 8192,
+             prefill_chunk: int = 256, num_blocks: Optional[int] = None) -> "VisionLLM":
+        """``max_seq`` / ``prefill_chunk`` default to the reference's caption window (8192 positions, pieces of 256)."""
         import json
         import os
-        handle = ModelHandle.load(path)
+        from .llm import LLM
+        if backend == "oracle":
+            llm = LLM.oracle(path, rows=rows, max_seq=max_seq, num_blocks=num_blocks or (rows * max_seq // BLOCK),
+                             prefill_chunk=prefill_chunk)
+        elif backend == "device":
+            llm = LLM.load(path, device=device, rows=rows, max_seq=max_seq, prefill_chunk=prefill_chunk, num_blocks=num_blocks)
+        else:
+            raise ValueError(f"backend {backend!r}: oracle or device")
+        handle = llm.handle
         tok, template = None, None
         if os.path.exists(os.path.join(path, "tokenizer.json")):
             tok = load_tokenizer(handle)
@@ -61,7 +75,7 @@ class VisionLLM:
         if template is None and os.path.exists(f):
             with open(f) as fh:
                 template = fh.read()
-        vlm = VisionLLM(handle, tok, template)
+        vlm = VisionLLM(handle, tok, template, llm)
         f = os.path.join(path, "generation_config.json")
         if os.path.exists(f):
             with open(f) as fh:
@@ -119,22 +133,58 @@ class VisionLLM:
         full[flags.astype(bool)] = rows
         return sess.step(toks, embed_rows=full, embed_flags=flags)
 
+    def image_inputs(self, tokens: Sequence[int], pixels: Optional[np.ndarray]):
+        """``(positions, rows)`` for ``Driver.open(..., embeds=)``: the prompt's image-token positions and the rows the
+        frames give, checked to agree in number."""
+        toks = np.asarray(tokens, dtype=np.int64).reshape(-1)
+        at = np.nonzero(toks == self.model.image_token)[0]
+        if pixels is None or len(pixels) == 0:
+            if len(at):
+                raise ValueError("the prompt holds image tokens but no image was given")
+            return None
+        rows = self.encode_images(pixels)
+        if len(at) != rows.shape[0]:
+            raise ValueError(f"the prompt holds {len(at)} image tokens; the frames give {rows.shape[0]} rows")
+        return at, rows
+
     def generate(self, tokens: Sequence[int], pixels: Optional[np.ndarray], max_new: int = 64,
                  eos: Optional[Sequence[int]] = None, on_token: Optional[Callable[[int], None]] = None) -> List[int]:
-        """Greedy continuation of ``tokens`` (which hold one image token per image row)."""
-        sess = self._session(len(tokens) + max_new)
-        logits = self.prefill(sess, tokens, pixels)
+        """Greedy continuation of ``tokens`` (which hold one image token per image row); stops before a token of ``eos``."""
         stop = set(eos or ())
-        out: List[int] = []
-        for i in range(max_new):
-            tok = int(np.argmax(logits[0]))
-            if tok in stop:
-                break
-            out.append(tok)
-            if on_token is not None:
-                on_token(tok)
-            if i + 1 < max_new:
-                logits = sess.step(np.array([[tok]], dtype=np.int32))
+        if self.llm is None:
+            sess = self._session(len(tokens) + max_new)
+            logits = self.prefill(sess, tokens, pixels)
+            out: List[int] = []
+            for i in range(max_new):
+                tok = int(np.argmax(logits[0]))
+                if tok in stop:
+                    break
+                out.append(tok)
+                if on_token is not None:
+                    on_token(tok)
+                if i + 1 < max_new:
+                    logits = sess.step(np.array([[tok]], dtype=np.int32))
+            return out
+        drv = self.llm.driver
+        params = SamplingParams(temperature=0.0, max_tokens=max_new, ignore_eos=True)
+        sid = drv.open(list(tokens), params, embeds=self.image_inputs(tokens, pixels))
+        out = []
+        try:
+            while len(out) < max_new:
+                res = [r for r in drv.step([sid]) if r.seq_id == sid]
+                if not res:
+                    break
+                if res[0].token is None:
+                    continue
+                tok = int(res[0].token)
+                if tok in stop:
+                    break
+                drv.commit(sid, [tok])
+                out.append(tok)
+                if on_token is not None:
+                    on_token(tok)
+        finally:
+            drv.release(sid)
         return out
 
     def caption(self, image, question: str = "Can you describe this image?", max_new: int = 64,

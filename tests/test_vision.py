@@ -41,7 +41,7 @@ def checkpoint(tmp_path_factory):
     image_token = tk.token_to_id("<image>")
     torch.manual_seed(0)
     cfg = Idefics3Config(
-        text_config=dict(model_type="llama", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+        text_config=dict(model_type="llama", hidden_size=128, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
                          num_key_value_heads=2, vocab_size=tk.get_vocab_size(), max_position_embeddings=512, rms_norm_eps=1e-5),
         vision_config=dict(hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, image_size=32,
                            patch_size=8, num_channels=3),
@@ -170,6 +170,64 @@ def test_caption_command_end_to_end(checkpoint, tmp_path, capsys):
     assert out == streamed + "\n"
     assert main(["caption", d, str(tmp_path / "missing.png")]) == 1
     assert main(["caption", d]) == 2
+
+
+def _hf_greedy(hf, tokens, pixels, n):
+    with torch.no_grad():
+        gen = hf.generate(input_ids=torch.tensor([tokens]), pixel_values=torch.tensor(pixels)[None],
+                          attention_mask=torch.ones(1, len(tokens), dtype=torch.long), max_new_tokens=n, do_sample=False,
+                          eos_token_id=None, pad_token_id=0)
+    return gen[0, len(tokens):].tolist()
+
+
+def test_image_rows_through_the_driver_chunked_prefill_and_prefix_cache(checkpoint):
+    """Image rows ride the ordinary driver: prefill in pieces of 16 tokens cuts the image runs across steps, and the
+    prefix cache tells two images behind identical placeholder tokens apart."""
+    d, hf, image_token = checkpoint
+    vlm = VisionLLM.load(d, backend="oracle", rows=2, max_seq=128, prefill_chunk=16, num_blocks=32)
+    rpi = vlm.vision.cfg.rows_per_image
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((5, 3, 32, 32)).astype(np.float32)
+    b = rng.standard_normal((5, 3, 32, 32)).astype(np.float32)
+    tokens = [5, 6, 7] + [image_token] * (3 * rpi) + [9] + [image_token] * (2 * rpi) + list(range(20, 33))
+    assert len(tokens) > 32                                         # at least two full blocks can be shared
+    want_a, want_b = _hf_greedy(hf, tokens, a, 5), _hf_greedy(hf, tokens, b, 5)
+    assert want_a != want_b
+    drv = vlm.llm.driver
+    assert vlm.generate(tokens, a, max_new=5) == want_a
+    hits = drv.stats["prefix_hit_tokens"]
+    assert vlm.generate(tokens, b, max_new=5) == want_b             # same tokens, other image: no shared prefix
+    assert drv.stats["prefix_hit_tokens"] == hits
+    assert vlm.generate(tokens, a, max_new=5) == want_a             # the first image again: its blocks are reused
+    assert drv.stats["prefix_hit_tokens"] >= hits + 32
+    from poot_b200.driver.driver import DriverError
+    with pytest.raises(DriverError, match="ascending"):
+        drv.open(tokens, embeds=(np.array([4, 3]), np.zeros((2, 128), np.float32)))
+
+
+def test_image_rows_on_the_emulated_device_engine(checkpoint):
+    """The device engine's program (kernels restated on the host, bf16): the staged rows replace the image tokens'
+    embeddings after the gather, in chunked prefill too."""
+    from poot_b200.utils.kernel_emulation import emulated_kernels
+    d, hf, image_token = checkpoint
+    rpi = 4
+    rng = np.random.default_rng(4)
+    pixels = rng.standard_normal((3, 3, 32, 32)).astype(np.float32)
+    tokens = [5, 6] + [image_token] * (3 * rpi) + [8, 9, 10, 11, 12, 13, 14]
+    want = _hf_greedy(hf, tokens, pixels, 6)
+    with emulated_kernels():
+        vlm = VisionLLM.load(d, backend="device", device="cpu", rows=1, max_seq=64, prefill_chunk=16, num_blocks=8)
+        got = vlm.generate(tokens, pixels, max_new=6)
+        eng = vlm.llm.engine
+        assert any(k[-1] for k in eng.launches_per_step), "no step ran with rows in place of embeddings"
+        blind = vlm.llm.generate_tokens(tokens, __import__("poot_b200").SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
+    agree = 0
+    for x, y in zip(got, want):
+        if x != y:
+            break
+        agree += 1
+    assert agree >= 2, (got, want)
+    assert blind != got                                               # without the rows the continuation is another one
 
 
 def test_text_checkpoints_have_no_front_end(tmp_path):
