@@ -118,6 +118,10 @@ def main(argv=None) -> int:
                          draft=draft, timing=timing)
     state = ServerState(engine, cfg, cfg.model_id or os.path.basename(cfg.model.rstrip("/")) or "model",
                         family=llm.cfg.family if llm.cfg is not None else "llama", chat_template=template)
+    handle = getattr(llm, "handle", None)
+    if handle is not None and getattr(handle.model, "kind", "decoder") == "vlm" and world == 1:
+        from ..vlm import VisionLLM
+        state.vision = VisionLLM(handle, llm.tokenizer, template, llm)     # /v1/chat/completions takes image_url parts
     server = Server(state)
     engine.start()
     server.start()

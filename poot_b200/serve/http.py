@@ -111,6 +111,7 @@ class ServerState:
                 self.admin_key = f.read().strip()
         self.adapters: Dict[str, dict] = {}
         self.embedder = getattr(engine, "embedder", None)    # set when the served model is an encoder
+        self.vision = None                                   # vision front end (tower + preprocessing) of a served VLM
 
 
 def make_handler(state: ServerState):
@@ -338,7 +339,9 @@ def make_handler(state: ServerState):
                 if isinstance(n, bool) or not isinstance(n, int) or not (1 <= n <= 16):
                     raise ApiError(400, "n must be an integer in [1, 16]", param="n")
                 chat = path.endswith("chat/completions")
+                self._embeds = None
                 prompt_ids, guided_spec, tools = self._prompt(req, chat)
+                embeds = self._embeds
                 params = sampling_from_request(req)
                 jobs: List[Job] = []
                 try:
@@ -348,7 +351,7 @@ def make_handler(state: ServerState):
                         if guided_spec is not None:
                             g = guided_mod.build_constraint(guided_spec, eng.tk, eng.driver.eos_token, tools)
                         jobs.append(eng.submit(Job(prompt_ids, sp, stream=bool(req.get("stream")), guided=g,
-                                                   adapter_slot=adapter_slot)))
+                                                   adapter_slot=adapter_slot, embeds=embeds)))
                 except queue.Full:
                     for j in jobs:
                         j.cancelled.set()
@@ -395,12 +398,14 @@ def make_handler(state: ServerState):
                 msgs = req.get("messages")
                 if not isinstance(msgs, list) or not msgs:
                     raise ApiError(400, "messages must be a non-empty list", param="messages")
-                try:
-                    text = chat_mod.render_chat(msgs, state.chat_template, state.family, True, state.bos_text,
-                                                state.eos_text, tools)
-                except chat_mod.TemplateError as ex:
-                    raise ApiError(400, str(ex), param="messages") from None
-                ids = eng.tk.encode(text, add_bos=not text.startswith(state.bos_text) if state.bos_text else True)
+                ids = self._image_prompt(msgs)
+                if ids is None:
+                    try:
+                        text = chat_mod.render_chat(msgs, state.chat_template, state.family, True, state.bos_text,
+                                                    state.eos_text, tools)
+                    except chat_mod.TemplateError as ex:
+                        raise ApiError(400, str(ex), param="messages") from None
+                    ids = eng.tk.encode(text, add_bos=not text.startswith(state.bos_text) if state.bos_text else True)
             else:
                 p = req.get("prompt")
                 if isinstance(p, list) and p and all(isinstance(t, int) and not isinstance(t, bool) for t in p):
@@ -414,6 +419,28 @@ def make_handler(state: ServerState):
             if len(ids) >= eng.driver.max_seq_len:
                 raise ApiError(400, f"prompt of {len(ids)} tokens exceeds the context of {eng.driver.max_seq_len}")
             return ids, guided_spec, tools
+
+        _embeds = None
+
+        def _image_prompt(self, msgs) -> Optional[List[int]]:
+            """Messages with image parts: prompt tokens with the image placeholders expanded, and the image rows staged
+            for the job (``self._embeds``).  ``None`` when no message holds an image."""
+            self._embeds = None
+            has = any(isinstance(m, dict) and isinstance(m.get("content"), list) and
+                      any(isinstance(p, dict) and p.get("type") in ("image_url", "image") for p in m["content"]) for m in msgs)
+            if not has:
+                return None
+            if state.vision is None:
+                raise ApiError(400, "the served model takes no images: it has no vision front end", param="messages")
+            try:
+                if any(isinstance(p, dict) and p.get("type") == "image" for m in msgs if isinstance(m.get("content"), list)
+                       for p in m["content"]):
+                    raise ValueError("image parts are sent as image_url with a data: URL")
+                ids, pixels = state.vision.prepare_messages(msgs, state.chat_template)
+                self._embeds = state.vision.image_inputs(ids, pixels)
+            except (ValueError, chat_mod.TemplateError) as ex:
+                raise ApiError(400, str(ex), param="messages") from None
+            return ids
 
         def _usage(self, jobs):
             p = len(jobs[0].prompt_tokens)

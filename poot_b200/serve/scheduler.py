@@ -30,6 +30,7 @@ class Job:
     stream: bool = False
     guided: Optional[object] = None
     adapter_slot: int = -1             # resident LoRA adapter the request selected (-1 = base model)
+    embeds: Optional[tuple] = None     # (positions, rows): rows that replace the embeddings of those prompt tokens (image rows)
     id: int = 0
     created: float = field(default_factory=time.monotonic)
     events: "queue.Queue" = field(default_factory=lambda: queue.Queue(maxsize=4096))
@@ -204,7 +205,8 @@ class ServeEngine:
         while self.waiting and self.state in ("serving", "draining"):   # admit oldest first
             job = self.waiting[0]
             try:
-                sid = d.open(job.prompt_tokens, job.params, guided=job.guided, adapter_slot=job.adapter_slot)
+                sid = d.open(job.prompt_tokens, job.params, guided=job.guided, adapter_slot=job.adapter_slot,
+                             embeds=job.embeds)
             except (NoFreeRow, OutOfBlocks):
                 if not self.live and not d.seqs:        # can never fit
                     self.waiting.pop(0)

@@ -31,6 +31,40 @@ VLM_TEMPLATE = ("<|im_start|>{% for message in messages %}{{message['role'] | ca
                 "{% if add_generation_prompt %}{{ 'Assistant:' }}{% endif %}")
 
 
+MAX_IMAGE_BYTES = 32 * 1024 * 1024
+MAX_IMAGE_PIXELS = 64 * 1024 * 1024
+
+
+def image_from_data_url(url):
+    """Decode a ``data:image/...;base64,`` URL into a PIL image; anything else (a remote URL, an oversized or
+    undecodable payload) is a ``ValueError``."""
+    import base64
+    import binascii
+    import io
+    if not isinstance(url, str) or not url.startswith("data:"):
+        raise ValueError("image_url must be a data: URL (base64); remote URLs are not fetched")
+    head, sep, payload = url[5:].partition(",")
+    if not sep or not head.endswith(";base64"):
+        raise ValueError("image_url must be base64-encoded (data:image/png;base64,...)")
+    if len(payload) > MAX_IMAGE_BYTES * 4 // 3 + 4:
+        raise ValueError("image payload exceeds the size limit")
+    try:
+        raw = base64.b64decode(payload, validate=True)
+    except (binascii.Error, ValueError):
+        raise ValueError("image payload is not valid base64") from None
+    from PIL import Image
+    try:
+        img = Image.open(io.BytesIO(raw))
+        if img.size[0] * img.size[1] > MAX_IMAGE_PIXELS:
+            raise ValueError("image exceeds the pixel limit")
+        img.load()
+    except ValueError:
+        raise
+    except Exception as e:
+        raise ValueError(f"image payload does not decode: {e}") from None
+    return img
+
+
 class NotVisionModel(ValueError):
     """The checkpoint's family has no vision front end."""
 
@@ -41,7 +75,8 @@ class VisionLLM:
             raise NotVisionModel("the checkpoint is not a vision-language model: its family has no front end")
         self.handle, self.model = handle, handle.model
         self.vision = self.model.vision
-        self.weights = handle.oracle_weights()
+        self.vision_weights = {n: w.to_f32() for n, w in handle.canonical.items() if n.startswith("vision.")}
+        self._weights = None
         self.tokenizer, self.template = tokenizer, template
         self.llm = llm                                # text driver (None: a bare oracle session per call)
         self.prep = ImagePrep.from_dir(handle.source, self.vision.cfg.image_size)
@@ -83,6 +118,13 @@ class VisionLLM:
             vlm.eos = [int(x) for x in (e if isinstance(e, list) else [e]) if x is not None]
         return vlm
 
+    @property
+    def weights(self):
+        """Every weight in f32 for bare oracle sessions (decoded on first use; the served paths never need it)."""
+        if self._weights is None:
+            self._weights = self.handle.oracle_weights()
+        return self._weights
+
     # ---- vision tower ----------------------------------------------------------------------------------------------
     def encode_images(self, pixels: np.ndarray) -> np.ndarray:
         """``pixels[frames, C, S, S]`` (normalised) -> ``[frames * rows_per_image, text_hidden]``."""
@@ -98,7 +140,7 @@ class VisionLLM:
                   "pos_ids": np.tile(position_ids(c, c.per_side, c.per_side)[None, :], (n, 1))}
         for i in g.inputs:
             if i.storage == "const":
-                inputs[i.name] = self.weights[i.name]
+                inputs[i.name] = self.vision_weights[i.name]
         return eval_graph(g, inputs, EvalOptions(matmul_precision="exact")).outputs["image_rows"]
 
     # ---- prompt ----------------------------------------------------------------------------------------------------
@@ -112,6 +154,44 @@ class VisionLLM:
         expanded = image_prompt(self.prep, frames.rows, frames.cols, self.vision.cfg.rows_per_image)
         text = text.replace(self.prep.image_token, expanded, 1)
         return self.tokenizer.encode(text, add_bos=False), frames.pixels
+
+    def prepare_messages(self, messages: List[dict], template: Optional[str] = None) -> tuple:
+        """Chat messages whose contents hold image parts -> ``(prompt tokens, frames of every image in order)``.
+        An image part is ``{"type": "image_url", "image_url": {"url": "data:image/...;base64,..."}}`` (or ``{"type":
+        "image", "image": <PIL image>}``); only ``data:`` URLs are read (the server fetches nothing)."""
+        if self.tokenizer is None:
+            raise ValueError("the checkpoint directory has no tokenizer.json")
+        images, shaped = [], []
+        for m in messages:
+            c = m.get("content") if isinstance(m, dict) else None
+            if isinstance(c, str):
+                shaped.append({**m, "content": [{"type": "text", "text": c}]})
+                continue
+            parts = []
+            for part in c or []:
+                kind = part.get("type") if isinstance(part, dict) else None
+                if kind == "text":
+                    parts.append({"type": "text", "text": str(part.get("text", ""))})
+                elif kind == "image_url":
+                    images.append(image_from_data_url((part.get("image_url") or {}).get("url")))
+                    parts.append({"type": "image"})
+                elif kind == "image":
+                    images.append(part.get("image"))
+                    parts.append({"type": "image"})
+                else:
+                    raise ValueError(f"content part of type {kind!r}: text and image_url parts are read")
+            shaped.append({**m, "content": parts})
+        text = render_chat(shaped, template or self.template or VLM_TEMPLATE, family="idefics3", keep_parts=True)
+        pieces = text.split(self.prep.image_token)
+        if len(pieces) != len(images) + 1:
+            raise ValueError(f"the template wrote {len(pieces) - 1} image placeholders for {len(images)} images")
+        out, frames = pieces[0], []
+        for img, tail in zip(images, pieces[1:]):
+            fr = preprocess(img, self.prep)
+            frames.append(fr.pixels)
+            out += image_prompt(self.prep, fr.rows, fr.cols, self.vision.cfg.rows_per_image) + tail
+        pixels = np.concatenate(frames, 0) if frames else None
+        return self.tokenizer.encode(out, add_bos=False), pixels
 
     # ---- generation ------------------------------------------------------------------------------------------------
     def _session(self, length: int) -> OracleSession:

@@ -230,6 +230,57 @@ def test_image_rows_on_the_emulated_device_engine(checkpoint):
     assert blind != got                                               # without the rows the continuation is another one
 
 
+def test_chat_completions_take_image_url_parts(checkpoint):
+    """An OpenAI-style chat request with a base64 ``image_url`` part: the server expands the placeholder, runs the tower
+    and opens the sequence with the image rows; the completion is the one ``transformers`` generates for that prompt."""
+    import base64
+    import http.client
+    import io
+    from PIL import Image
+    from poot_b200.llm import LLM
+    from poot_b200.serve import Metrics, ServeConfig, ServeEngine, Server, ServerState
+    d, hf, image_token = checkpoint
+    llm = LLM.oracle(d, rows=2, max_seq=256, num_blocks=40, prefill_chunk=32)
+    cfg = ServeConfig(model=d, addr="127.0.0.1:0", rows=2)
+    eng = ServeEngine(llm.driver, llm.tokenizer, Metrics(), 8, cfg.max_queue_wait_secs)
+    state = ServerState(eng, cfg, "tiny-vlm", family="idefics3")
+    state.vision = VisionLLM(llm.handle, llm.tokenizer, None, llm)
+    srv = Server(state)
+    eng.start()
+    srv.start()
+
+    def post(body):
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=60)
+        c.request("POST", "/v1/chat/completions", json.dumps(body).encode(), {"Content-Type": "application/json"})
+        r = c.getresponse()
+        out = r.status, json.loads(r.read())
+        c.close()
+        return out
+    try:
+        img = Image.fromarray(np.random.default_rng(6).integers(0, 255, (30, 30, 3), dtype=np.uint8))
+        buf = io.BytesIO()
+        img.save(buf, format="PNG")
+        url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+        msgs = [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}}, {"type": "text", "text": "What?"}]}]
+        tokens, pixels = state.vision.prepare_messages(msgs)
+        want = _hf_greedy(hf, tokens, pixels, 4)
+        st, body = post({"messages": msgs, "max_tokens": 4, "temperature": 0, "ignore_eos": True})
+        assert st == 200, body
+        assert body["usage"]["prompt_tokens"] == len(tokens) and body["usage"]["completion_tokens"] == 4
+        from poot_b200.text.codec import StreamDecoder
+        eos = llm.driver.eos_token
+        assert body["choices"][0]["message"]["content"] == llm.tokenizer.decode([t for t in want if t != eos])
+        st, body = post({"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "https://example.com/a.png"}}]}]})
+        assert st == 400 and "data: URL" in body["error"]["message"]
+        st, body = post({"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}}]}]})
+        assert st == 400 and "decode" in body["error"]["message"]
+        state.vision = None
+        st, body = post({"messages": msgs, "max_tokens": 2})
+        assert st == 400 and "no vision front end" in body["error"]["message"]
+    finally:
+        srv.shutdown()
+
+
 def test_text_checkpoints_have_no_front_end(tmp_path):
     from transformers import LlamaConfig, LlamaForCausalLM
     d = str(tmp_path / "llama")
