@@ -54,6 +54,12 @@ class NcclComm:
         K.add(engine.h[:T], p, out=engine.h[:T])
         return None
 
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        """Sum ``t`` over the ranks in place (a projection's partial that a norm consumes before the residual add)."""
+        with K.timed_region("nccl_all_reduce"):
+            dist.all_reduce(t, group=self.group)
+        return t
+
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor) -> None:
         with K.timed_region("nccl_all_gather"):
             # flat views: the same bytes, and the form every backend of the process group accepts

@@ -209,8 +209,15 @@ class DecoderEngine:
             self.gate = torch.zeros(T, self.hq * D, dtype=bf, device=dev)
         if not cfg.plain_block:
             if comm is not None:
+                # the fused programs are written for the pre-norm SwiGLU rope layer; other attention stacks shard the
+                # Megatron way over the library collectives.  Latent attention and recurrent mixers have no sharding rule
+                # (crates/poot-graph-plan/src/passes/sharding.rs:86-96: ``NoRule``).
                 from .weights import UnsupportedOnDevice
-                raise UnsupportedOnDevice(f"{cfg.family}: tensor parallelism is built for the pre-norm SwiGLU rope layer only")
+                if getattr(comm, "fused", False):
+                    raise UnsupportedOnDevice(f"{cfg.family}: the fused tensor-parallel programs are built for the pre-norm "
+                                              "SwiGLU rope layer only; shard this family over the library collectives")
+                if cfg.is_mla or cfg.layer_kinds is not None or cfg.attn_gate:
+                    raise UnsupportedOnDevice(f"{cfg.family}: no sharding rule for latent attention, gated attention or recurrent mixers")
             self.proj = torch.zeros(T, H, dtype=bf, device=dev)          # projection output waiting for its post norm
             if cfg.act != "silu":
                 self.gu = torch.zeros(T, 2 * ffn_local, dtype=bf, device=dev)
@@ -422,6 +429,8 @@ class DecoderEngine:
                 self._proj_post_norm(self.attn[:T], L.wo, L.post1, T, ("o", l) if lora else None)
             elif self.comm is not None:
                 pending = self.comm.row_parallel(self, self.attn[:T], L.wo, T)
+                if L.bo is not None:            # the bias joins the reduced sum once
+                    h.add_(L.bo)
             else:
                 pending = self._proj_to_residual(self.attn[:T], L.wo, T)
                 if lora:
@@ -437,7 +446,8 @@ class DecoderEngine:
                     up.add_(L.bgu)
                 self._count()
                 K.act_(up, cfg.act)
-                pending = self._proj_to_residual(up, L.wdown, T)
+                pending = (self.comm.row_parallel(self, up, L.wdown, T) if self.comm is not None
+                           else self._proj_to_residual(up, L.wdown, T))
                 if L.bdown is not None:
                     h.add_(L.bdown)
             else:
@@ -510,7 +520,8 @@ class DecoderEngine:
                     up.add_(L.bgu)
                 self._count()
                 K.act_(up, cfg.act)
-                pending = self._proj_to_residual(up, L.wdown, T)
+                pending = (self.comm.row_parallel(self, up, L.wdown, T) if self.comm is not None
+                           else self._proj_to_residual(up, L.wdown, T))
                 if L.bdown is not None:
                     self.h[:T].add_(L.bdown)
         return pending
@@ -587,6 +598,8 @@ class DecoderEngine:
         self._linear(x, W, K.EPI_STORE, p)
         if adapter_site is not None:
             self.lora.apply(self, adapter_site[0], adapter_site[1], x, p, T)
+        if self.comm is not None:                # a row-parallel projection: the norm needs the sum over the ranks
+            self.comm.all_reduce(p)
         self._count(2)
         K.rmsnorm(p, norm_w, self.cfg.norm_eps, out=p)
         K.add(h, p, out=h)
@@ -597,6 +610,16 @@ class DecoderEngine:
         qn, kn = self.qn[:T], self.kn[:T]
         qn.copy_(qkv[:, :nq])
         kn.copy_(qkv[:, nq:nq + nk])
+        if self.comm is not None:
+            # the norm spans the heads of every rank: mean squares are summed over the ranks, then each rank scales
+            # its own channels (library-collective path; plain tensor arithmetic, two small all-reduces per layer)
+            for t, wt, width in ((qn, L.q_norm, nq * self.tp), (kn, L.k_norm, nk * self.tp)):
+                ss = t.float().pow(2).sum(-1, keepdim=True)
+                self.comm.all_reduce(ss)
+                t.copy_((t.float() * torch.rsqrt(ss / width + self.cfg.norm_eps) * wt.float()).to(t.dtype))
+            qkv[:, :nq].copy_(qn)
+            qkv[:, nq:nq + nk].copy_(kn)
+            return
         self._count(6)
         K.rmsnorm(qn, L.q_norm, self.cfg.norm_eps, out=qn)
         K.rmsnorm(kn, L.k_norm, self.cfg.norm_eps, out=kn)

@@ -304,14 +304,18 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
                 L.wgate = shard_rows(get(p + "attn_gate"), tp_rank, tp_world)
             if cfg.out_bias:
                 L.bo = get(p + "attn_o_bias")
-            if cfg.attn_sinks:
-                L.sinks = tensors[p + "attn_sinks"].to(device=dev, dtype=torch.float32).contiguous()
+            if cfg.attn_sinks:                   # one sink logit per query head: a rank keeps its heads'
+                hq = cfg.n_heads // tp_world
+                L.sinks = tensors[p + "attn_sinks"][tp_rank * hq:(tp_rank + 1) * hq].to(device=dev, dtype=torch.float32).contiguous()
         if cfg.block in ("post", "sandwich"):
             L.post1, L.post2 = get(p + "attn_post_norm"), get(p + "ffn_post_norm")
         if cfg.attn_bias:
             L.bqkv = fuse_qkv_bias(get(p + "attn_q_bias"), get(p + "attn_k_bias"), get(p + "attn_v_bias"), cfg, tp_rank, tp_world)
         if cfg.qk_norm and L.kind == "attention":
             L.q_norm, L.k_norm = get(p + "attn_q_norm"), get(p + "attn_k_norm")
+            if cfg.qk_norm_wide and tp_world > 1:     # a weight per projection channel: a rank keeps its heads' channels
+                L.q_norm = shard_rows(L.q_norm, tp_rank, tp_world)
+                L.k_norm = shard_rows(L.k_norm, tp_rank, tp_world)
         if cfg.has_ffn(l) and L.ln2 is None and cfg.block != "post":
             L.ln2 = get(p + "ffn_norm")
         if not cfg.has_ffn(l):
@@ -347,7 +351,7 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
             L.wgu = shard_rows(get(p + "ffn_up"), tp_rank, tp_world)
             L.wdown = shard_cols(get(p + "ffn_down"), tp_rank, tp_world)
             if cfg.mlp_bias:
-                L.bgu, L.bdown = get(p + "ffn_up_bias"), get(p + "ffn_down_bias")
+                L.bgu, L.bdown = shard_rows(get(p + "ffn_up_bias"), tp_rank, tp_world), get(p + "ffn_down_bias")
         if cfg.norm_kind == "layer" and cfg.norm_bias:
             L.ln1_b, L.ln2_b = get(p + "attn_norm_bias"), get(p + "ffn_norm_bias")
         layers.append(L)

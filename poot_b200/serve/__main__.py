@@ -44,7 +44,7 @@ def main(argv=None) -> int:
             pp = world
         else:
             from ..parallel.tp import make_comm
-            comm = make_comm("fused", rank, world, torch.device("cuda", torch.cuda.current_device()))
+            comm = make_comm(_comm_kind(cfg.model), rank, world, torch.device("cuda", torch.cuda.current_device()))
         from .follower import init_control_group
         init_control_group()
     if _is_encoder_checkpoint(cfg.model):
@@ -139,6 +139,22 @@ def main(argv=None) -> int:
         _leave(llm)
     llm.close()
     return 0
+
+
+def _comm_kind(model: str) -> str:
+    """The fused GEMM + NVLink programs are written for the pre-norm SwiGLU rope layer; a checkpoint of another
+    attention stack shards the same way over the library collectives."""
+    import json
+    path = os.path.join(model, "config.json")
+    if not os.path.isfile(path):
+        return "fused"
+    from ..models.registry import Registry, UnsupportedFamily
+    try:
+        with open(path) as f:
+            cfg = Registry.builtin().resolve_hf(json.load(f)).cfg
+    except (UnsupportedFamily, KeyError, ValueError):
+        return "fused"                   # the load that follows reports what is wrong with the checkpoint
+    return "fused" if getattr(cfg, "plain_block", True) else "nccl"
 
 
 def _prove_ranges(model_cfg, cfg) -> None:

@@ -58,3 +58,21 @@ def test_pipeline_two_stages_match_single_gpu():
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert out["ok"], out
+
+
+@pytest.mark.xfail(strict=False, reason="tensor-parallel shares of the families beyond the plain layer: not yet run on devices")
+def test_tensor_parallel_families_match_single_gpu():
+    """Two GPUs over NCCL (library collectives) with the real kernels: the gathered logits of every family equal one
+    GPU's within bf16 noise."""
+    import json
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    families = ["gemma2", "gemma3", "olmo2", "olmoe", "smollm3-nope-layer", "granite", "mpt", "bloom", "gpt_oss", "minimax_m2"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", POOT_TP_CUDA="1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29549", str(ROOT / "tests" / "tp_family_worker.py"), *families]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=str(ROOT / "tests"))
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    out = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    for rank_flags in out["ranks"]:
+        assert all(ok for ok, _ in rank_flags.values()), out
