@@ -99,6 +99,8 @@ class ModelHandle:
             if not (c.has_ffn(l) and c.moe_layer(l)):
                 continue
             p = f"layers.{l}."
+            if p + "experts_in" in out:          # the family's checkpoint stores the experts stacked in this layout
+                continue
             if c.gated_ffn:
                 gi = np.stack([np.concatenate([self.f32(p + f"experts.{e}.gate"), self.f32(p + f"experts.{e}.up")], 0)
                                for e in range(c.n_experts)])
@@ -160,6 +162,11 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
     import torch
     from ..runtime.weights import DecoderWeights, LayerWeights
     c, canon = handle.cfg, handle.canonical
+    gaps = c.device_gaps()
+    if gaps:                 # refused before any tensor is read: the loader below knows the device program's layouts only
+        from ..runtime.weights import UnsupportedOnDevice
+        raise UnsupportedOnDevice(f"{c.family}: the device program lacks " + "; ".join(gaps) +
+                                  " (the CPU oracle evaluates this checkpoint: --backend oracle)")
     if not c.plain_block or c.router_select_bias or c.shared_width or c.first_dense_layers or c.dense_layers or c.n_group > 1 \
             or c.router != "softmax":
         # hybrid stacks and the less common layer variants go through the canonical-name builder (dense bf16)

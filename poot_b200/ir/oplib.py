@@ -301,7 +301,8 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
                score: str = "softmax", renorm: bool = True, router_bias: Optional[Traced] = None,
                select_bias: Optional[Traced] = None, n_group: int = 1, topk_group: int = 1, routed_scale: float = 1.0,
                act: str = "silu", limit: float = 0.0, alpha: float = 1.702, in_bias: Optional[Traced] = None,
-               out_bias: Optional[Traced] = None, gated: bool = True, precision: str = "narrow") -> Traced:
+               out_bias: Optional[Traced] = None, gated: bool = True, precision: str = "narrow",
+               router_x: Optional[Traced] = None, expert_scale: Optional[Traced] = None) -> Traced:
     """Routed experts in every variant the shipped families use (components/router.rs, ops/moe.rs).
 
     ``score``: ``softmax`` over all experts or ``sigmoid`` per expert.  Selection ranks ``score + select_bias`` (the
@@ -309,11 +310,12 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
     (group score = sum of its two best selection scores; experts outside are ranked as 0).  Gates are the scores at
     the selected experts, divided by their sum when ``renorm``, times ``routed_scale``.  Experts: ``w_in[E, 2F, H]``
     gate rows then up rows (+ ``in_bias[E, 2F]``), ``w_out[E, H, F]`` (+ ``out_bias[E, H]``); with ``gated=False``
-    ``w_in[E, F, H]`` and the expert is ``down(act(up(x)))``."""
+    ``w_in[E, F, H]`` and the expert is ``down(act(up(x)))``.  ``router_x``: the router reads these rows instead of
+    the experts' input; ``expert_scale[E]`` multiplies the gate of each expert after the renormalisation."""
     L, H = x.shape
     E, F2, _ = w_in.shape
     F = F2 // 2 if gated else F2
-    logits = linear(b, x, router, router_bias, precision="exact")
+    logits = linear(b, router_x if router_x is not None else x, router, router_bias, precision="exact")
     if score == "softmax" and renorm and select_bias is None and n_group == 1:
         # softmax over all, pick k, renormalise == softmax over the k selected logits
         scores = canonical_router_scores(b, logits)
@@ -343,6 +345,8 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
                 den = den + 1e-20
             picked = picked / b.broadcast(den, picked.shape)
         gates_all = picked * routed_scale if routed_scale != 1.0 else picked
+    if expert_scale is not None:
+        gates_all = gates_all * b.broadcast(b.reshape(expert_scale, (1, E)), gates_all.shape)
     ids = b.arg_top_k(rank, k)                                              # [L, k]
     flat_ids = b.reshape(ids, (L * k,))
     gates = b.reshape(b.gather(b.reshape(gates_all, (L * E,)),

@@ -159,8 +159,50 @@ def _map_vision(store: WeightStore) -> Dict[str, PackedWeight]:
     return canon
 
 
+GEMMA4_TOP = {"embed_tokens.weight": "embed", "norm.weight": "final_norm", "embed_tokens_per_layer.weight": "ple_embed",
+              "per_layer_model_projection.weight": "ple_model_proj", "per_layer_projection_norm.weight": "ple_proj_norm"}
+GEMMA4_LAYER = {"input_layernorm.weight": "attn_norm", "post_attention_layernorm.weight": "attn_post_norm",
+                "pre_feedforward_layernorm.weight": "ffn_norm", "post_feedforward_layernorm.weight": "ffn_post_norm",
+                "self_attn.q_proj.weight": "attn_q", "self_attn.k_proj.weight": "attn_k", "self_attn.v_proj.weight": "attn_v",
+                "self_attn.o_proj.weight": "attn_o", "self_attn.q_norm.weight": "attn_q_norm", "self_attn.k_norm.weight": "attn_k_norm",
+                "mlp.gate_proj.weight": "ffn_gate", "mlp.up_proj.weight": "ffn_up", "mlp.down_proj.weight": "ffn_down",
+                "layer_scalar": "layer_scalar", "per_layer_input_gate.weight": "ple_gate", "per_layer_projection.weight": "ple_proj",
+                "post_per_layer_input_norm.weight": "ple_post_norm", "router.proj.weight": "ffn_router", "router.scale": "ffn_router_scale",
+                "router.per_expert_scale": "ffn_expert_scale", "experts.gate_up_proj": "experts_in", "experts.down_proj": "experts_out",
+                "post_feedforward_layernorm_1.weight": "ffn_post_norm_1", "post_feedforward_layernorm_2.weight": "ffn_post_norm_2",
+                "pre_feedforward_layernorm_2.weight": "ffn_norm_2"}
+
+
+def _map_gemma4(cfg, store: WeightStore) -> Dict[str, PackedWeight]:
+    """Gemma 4 text tensors (``model.*`` of a text checkpoint, ``model.language_model.*`` of a multimodal one).  The
+    experts are stored stacked in the tracer's own layout; K/V projections of layers that share another layer's K/V
+    are present in the file and unused."""
+    canon: Dict[str, PackedWeight] = {}
+    for n in store.names():
+        m = re.match(r"model\.(?:language_model\.)?(.+)$", n)
+        if n == "lm_head.weight":
+            canon["lm_head"] = store[n]
+        if not m:
+            continue
+        rest = m.group(1)
+        if rest in GEMMA4_TOP:
+            canon[GEMMA4_TOP[rest]] = store[n]
+            continue
+        lm = re.match(r"layers\.(\d+)\.(.+)$", rest)
+        if lm and lm.group(2) in GEMMA4_LAYER:
+            l, role = int(lm.group(1)), GEMMA4_LAYER[lm.group(2)]
+            if role in ("attn_k", "attn_v", "attn_k_norm") and cfg.kv_source(l) is not None:
+                continue
+            if role == "attn_v" and cfg.value_is_key(l):
+                continue
+            canon[f"layers.{l}.{role}"] = store[n]
+    return canon
+
+
 def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWeight]:
     """Canonical role name -> stored tensor for one Hugging Face checkpoint of ``cfg``'s family."""
+    if cfg.family == "gemma4":
+        return _map_gemma4(cfg, store)
     if cfg.family == "idefics3":
         text = replace(cfg, family="llama")
         return {**_map_vision(store), **map_checkpoint(text, _Renamed(store, "model.text_model.", "model."))}

@@ -14,8 +14,9 @@ from typing import Optional
 @dataclass
 class RopeScaling:
     """RoPE frequency scaling (crates/poot-graph-ir/src/rope_table.rs:64-150)."""
-    kind: str = "none"  # none | linear | dynamic | yarn | longrope | llama3
+    kind: str = "none"  # none | linear | dynamic | yarn | longrope | llama3 | proportional
     factor: float = 1.0
+    proportion: float = 1.0          # proportional: share of the head's channel pairs that rotate (the rest keep frequency 0)
     low_freq_factor: float = 1.0
     high_freq_factor: float = 4.0
     original_max_position: int = 8192

@@ -26,7 +26,7 @@ class FamilyEntry:
     gguf_archs: List[str]
     from_hf: Optional[Callable[[dict], DecoderConfig]]
     missing: Optional[str] = None     # capability that is not built when the family is refused
-    kind: str = "decoder"             # decoder (standard stack) | encoder (embeddings / rerank scores) | vlm (vision tower + decoder)
+    kind: str = "decoder"             # decoder (standard stack) | encoder (embeddings / rerank scores) | vlm (vision tower + decoder) | gemma4 (own tracer)
 
 
 def _rope_params(c: dict, layer_type: Optional[str] = None) -> dict:
@@ -174,6 +174,43 @@ def _gemma(c, family: str) -> DecoderConfig:
 
 def _gemma2(c): return _gemma(c, "gemma2")
 def _gemma3(c): return _gemma(c, "gemma3")
+
+
+def _gemma4(c):
+    """Gemma 4 text stack (``gemma4_text``, or the text part of a multimodal ``gemma4`` header)."""
+    from .gemma4 import Gemma4Config
+    c = c.get("text_config") or c
+    if c.get("use_bidirectional_attention") == "all":
+        raise UnsupportedFamily("gemma4 with bidirectional attention over every token")
+    L, H = c["num_hidden_layers"], c["hidden_size"]
+    lt = list(c.get("layer_types") or ["full_attention"] * L)[:L]
+    win = int(c.get("sliding_window") or 0)
+    rp = c.get("rope_parameters") or {}
+    full, local = dict(rp.get("full_attention") or {}), dict(rp.get("sliding_attention") or {})
+    if full.get("rope_type", "default") not in ("default", "proportional") or local.get("rope_type", "default") != "default":
+        raise UnsupportedFamily(f"gemma4 rope types {full.get('rope_type')!r} / {local.get('rope_type')!r}")
+    act = {"gelu_pytorch_tanh": "gelu_tanh", "gelu_new": "gelu_tanh", "gelu": "gelu_erf", "silu": "silu"}.get(
+        c.get("hidden_activation", "gelu_pytorch_tanh"))
+    if act is None:
+        raise UnsupportedFamily(f"gemma4 activation {c.get('hidden_activation')!r}")
+    moe = bool(c.get("enable_moe_block"))
+    cap = c.get("final_logit_softcapping")
+    return Gemma4Config(
+        name="gemma4", family="gemma4", n_layers=L, hidden=H, n_heads=c["num_attention_heads"],
+        n_kv_heads=c.get("num_key_value_heads") or c["num_attention_heads"], head_dim=c.get("head_dim") or H // c["num_attention_heads"],
+        ffn=c["intermediate_size"], vocab=c["vocab_size"], norm_eps=float(c.get("rms_norm_eps", 1e-6)), act=act,
+        rope_theta=float(full.get("rope_theta", 1000000.0)), rope_theta_local=float(local.get("rope_theta", 10000.0)),
+        rope_proportion=float(full.get("partial_rotary_factor", 1.0)) if full.get("rope_type") == "proportional" else 1.0,
+        max_position=int(c.get("max_position_embeddings", 131072)), tie_embeddings=bool(c.get("tie_word_embeddings", True)),
+        layer_windows=[win if t == "sliding_attention" else 0 for t in lt], block="sandwich", qk_norm=True,
+        final_softcap=float(cap) if cap else 0.0, embed_scale=float(H) ** 0.5,
+        global_head_dim=int(c.get("global_head_dim") or 0), n_global_kv_heads=int(c.get("num_global_key_value_heads") or 0),
+        k_eq_v=bool(c.get("attention_k_eq_v")), kv_shared_layers=int(c.get("num_kv_shared_layers") or 0),
+        double_wide_mlp=bool(c.get("use_double_wide_mlp")), ple_dim=int(c.get("hidden_size_per_layer_input") or 0),
+        ple_vocab=int(c.get("vocab_size_per_layer_input") or c["vocab_size"]), moe_block=moe,
+        n_experts=int(c.get("num_experts") or 0) if moe else 0, top_k=int(c.get("top_k_experts") or 0) if moe else 0,
+        moe_ffn=int(c.get("moe_intermediate_size") or 0) if moe else 0,
+        bos_token=_token(c.get("bos_token_id"), 2), eos_token=_token(c.get("eos_token_id"), 1))
 
 
 def _mpt(c):
@@ -372,6 +409,7 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("bloom", ["bloom"], ["bloom"], _bloom),
     FamilyEntry("gemma3", ["gemma3", "gemma3_text"], ["gemma3"], _gemma3),
     FamilyEntry("gemma2", ["gemma2"], ["gemma2"], _gemma2),
+    FamilyEntry("gemma4", ["gemma4", "gemma4_text"], ["gemma4"], _gemma4, kind="gemma4"),
     FamilyEntry("qwen3moe", ["qwen3_moe"], ["qwen3moe"], _qwen3moe),
     FamilyEntry("gpt_oss", ["gpt_oss"], ["gpt-oss"], _gpt_oss),
     FamilyEntry("olmoe", ["olmoe"], ["olmoe"], _olmoe),
@@ -384,7 +422,6 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("bert", ["bert"], ["bert"], _bert, kind="encoder"),
     FamilyEntry("idefics3", ["idefics3", "smolvlm"], [], _idefics3, kind="vlm"),
     # families the reference ships whose mixers are not built here: refused by name
-    FamilyEntry("gemma4", ["gemma4"], ["gemma4"], None, "per-layer embeddings, proportional rope"),
     FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], None, "sparse attention indexer"),
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
     FamilyEntry("qwen38", ["qwen4_exp"], ["qwen4exp"], None, "block-indexed sparse attention, hyper-connection residual streams, n-gram embeddings"),
@@ -414,6 +451,9 @@ class Registry:
                 if e.kind == "encoder":
                     from .encoder import EncoderModel
                     return EncoderModel(e.from_hf(config))
+                if e.kind == "gemma4":
+                    from .gemma4 import Gemma4Model
+                    return Gemma4Model(e.from_hf(config))
                 if e.kind == "vlm":
                     from .vision import VisionLanguageModel, VisionTower
                     text, vision, image_token = e.from_hf(config)

@@ -29,6 +29,9 @@ SAMPLES = {
                       shared_expert_intermediate_size=512),
     "qwen38_27b": dict(model_type="qwen3_5_text", linear_num_value_heads=48, linear_num_key_heads=16, linear_key_head_dim=128,
                        linear_value_head_dim=128),
+    "gemma4": dict(model_type="gemma4_text", head_dim=256, global_head_dim=512, hidden_size_per_layer_input=256, num_kv_shared_layers=2,
+                   vocab_size_per_layer_input=32000, sliding_window=512,
+                   layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
     "bert": dict(model_type="bert", num_attention_heads=12, intermediate_size=3072, hidden_size=768),
     "idefics3": dict(model_type="idefics3", text_config=dict(model_type="llama", hidden_size=2048, num_hidden_layers=4,
                                                              num_attention_heads=32, num_key_value_heads=32, intermediate_size=8192,

@@ -28,6 +28,9 @@ def inv_frequencies(dim: int, theta: float, scaling: Optional[RopeScaling], posi
     if kind == "dynamic" and positions > sc.original_max_position:
         base = base * ((sc.factor * positions / sc.original_max_position) - (sc.factor - 1.0)) ** (dim / (dim - 2.0))
     inv = base ** (-2.0 * j / dim)
+    if kind == "proportional":
+        # the table spans the whole head; only the first ``proportion`` of the (i, i + dim/2) pairs rotate
+        inv = np.where(j < int(sc.proportion * dim // 2), inv, 0.0)
     if kind == "linear" and sc.factor > 0:
         inv = inv / sc.factor
     elif kind == "llama3":
@@ -58,9 +61,6 @@ def inv_frequencies(dim: int, theta: float, scaling: Optional[RopeScaling], posi
             att = math.sqrt(1.0 + math.log(positions / sc.original_max_position) / math.log(sc.original_max_position))
         if sc.attention_factor is not None:
             att = sc.attention_factor
-    elif kind == "proportional":
-        rotated = int(sc.factor)
-        inv = np.where(j < rotated, inv, 0.0)
     if freq_factors is not None and kind not in ("yarn",) and not (kind == "longrope" and (sc.short_factor or sc.long_factor)):
         inv = inv / np.asarray(freq_factors, dtype=np.float64)
     return inv, float(att)

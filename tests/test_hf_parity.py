@@ -41,6 +41,24 @@ CASES = {
                    final_logit_softcapping=3.0),
     "gemma3": dict(model_type="gemma3_text", query_pre_attn_scalar=24, sliding_window=6, num_hidden_layers=3,
                    layer_types=["sliding_attention", "sliding_attention", "full_attention"]),
+    # gemma4: head width by layer type, proportional rope, scores without a scale, weightless v norm, layer scalars ...
+    "gemma4": dict(model_type="gemma4_text", num_hidden_layers=4, global_head_dim=32, sliding_window=6, vocab_size_per_layer_input=200,
+                   layer_types=["sliding_attention", "full_attention"] * 2, hidden_size_per_layer_input=0, pad_token_id=0, _scale=2.0),
+    # ... per-layer embeddings, the last two layers attending over the K/V of layers 0 / 1, double-width FFNs there
+    "gemma4-per-layer-embeddings-shared-kv": dict(
+        model_type="gemma4_text", num_hidden_layers=4, global_head_dim=32, sliding_window=6, vocab_size_per_layer_input=200,
+        layer_types=["sliding_attention", "full_attention"] * 2, hidden_size_per_layer_input=8, num_kv_shared_layers=2,
+        use_double_wide_mlp=True, pad_token_id=0, _scale=2.0),
+    # ... full-attention layers whose value is the key projection, on one K/V head; capped logits
+    "gemma4-value-is-key": dict(model_type="gemma4_text", num_hidden_layers=4, global_head_dim=32, sliding_window=6,
+                                vocab_size_per_layer_input=200, layer_types=["sliding_attention", "full_attention"] * 2,
+                                hidden_size_per_layer_input=0, attention_k_eq_v=True, num_global_key_value_heads=1,
+                                final_logit_softcapping=30.0, pad_token_id=0, _scale=2.0),
+    # ... a dense FFN plus routed experts in every layer, the router on the un-normed residual, per-expert gate scales
+    "gemma4-moe": dict(model_type="gemma4_text", num_hidden_layers=4, global_head_dim=32, sliding_window=6,
+                       vocab_size_per_layer_input=200, layer_types=["sliding_attention", "full_attention"] * 2,
+                       hidden_size_per_layer_input=0, enable_moe_block=True, num_experts=4, top_k_experts=2,
+                       moe_intermediate_size=48, pad_token_id=0, _scale=2.0),
     "mpt": dict(model_type="mpt", d_model=64, n_heads=4, n_layers=2, vocab_size=200, max_seq_len=128),
     "mpt-6-heads": dict(model_type="mpt", d_model=96, n_heads=6, n_layers=2, vocab_size=200, max_seq_len=128),
     "bloom": dict(model_type="bloom", hidden_size=64, n_head=4, n_layer=2, vocab_size=200),
@@ -101,7 +119,8 @@ def test_logits_equal_the_hugging_face_forward(name, tmp_path):
     assert err < CASES[name].get("_tol", 2e-5), err
 
 
-@pytest.mark.parametrize("name", ["llama", "gemma3", "bloom", "deepseek3", "gpt_oss", "qwen3next", "nemotron_h"])
+@pytest.mark.parametrize("name", ["llama", "gemma3", "bloom", "deepseek3", "gpt_oss", "qwen3next", "nemotron_h",
+                                  "gemma4-per-layer-embeddings-shared-kv"])
 def test_driver_over_the_oracle_engine_generates_what_hugging_face_generates(name, tmp_path):
     """End to end on the host: checkpoint directory -> ``LLM.oracle`` -> driver (paged K/V through block tables,
     chunked prefill, two sequences in flight) gives the greedy continuation ``transformers`` gives."""
