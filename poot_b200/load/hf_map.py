@@ -199,8 +199,48 @@ def _map_gemma4(cfg, store: WeightStore) -> Dict[str, PackedWeight]:
     return canon
 
 
+QWEN_VISION_LAYER = {"norm1.weight": "attn_norm", "norm2.weight": "ffn_norm", "attn.proj.weight": "attn_o", "attn.proj.bias": "attn_o_bias",
+                     "mlp.gate_proj.weight": "ffn_gate", "mlp.gate_proj.bias": "ffn_gate_bias", "mlp.up_proj.weight": "ffn_up",
+                     "mlp.up_proj.bias": "ffn_up_bias", "mlp.down_proj.weight": "ffn_down", "mlp.down_proj.bias": "ffn_down_bias"}
+QWEN_VISION_TOP = {"merger.ln_q.weight": "merger_norm", "merger.mlp.0.weight": "merger_fc1", "merger.mlp.0.bias": "merger_fc1_bias",
+                   "merger.mlp.2.weight": "merger_fc2", "merger.mlp.2.bias": "merger_fc2_bias"}
+
+
+def _map_qwen_vision(store: WeightStore) -> Dict[str, PackedWeight]:
+    """Vision tower tensors of a Qwen2.5-VL checkpoint (``model.visual.*``, older files ``visual.*``): the patch
+    convolution ``[out, C, t, p, p]`` flattens to a matrix, the fused ``qkv`` rows are cut into thirds."""
+    canon: Dict[str, PackedWeight] = {}
+    for n in store.names():
+        m = re.match(r"(?:model\.)?visual\.(.+)$", n)
+        if not m:
+            continue
+        short = m.group(1)
+        if short == "patch_embed.proj.weight":
+            w = store[n].to_f32()
+            canon["vision.patch_embed"] = f32_weight("vision.patch_embed", w.reshape(w.shape[0], -1))
+        elif short in QWEN_VISION_TOP:
+            canon["vision." + QWEN_VISION_TOP[short]] = store[n]
+        else:
+            b = re.match(r"blocks\.(\d+)\.(.+)$", short)
+            if not b:
+                continue
+            p, rest = f"vision.layers.{b.group(1)}.", b.group(2)
+            if rest in QWEN_VISION_LAYER:
+                canon[p + QWEN_VISION_LAYER[rest]] = store[n]
+            elif rest in ("attn.qkv.weight", "attn.qkv.bias"):
+                w = store[n].to_f32()
+                third = w.shape[0] // 3
+                tail = "_bias" if rest.endswith("bias") else ""
+                for i, role in enumerate(("attn_q", "attn_k", "attn_v")):
+                    canon[p + role + tail] = f32_weight(p + role + tail, np.ascontiguousarray(w[i * third:(i + 1) * third]))
+    return canon
+
+
 def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWeight]:
     """Canonical role name -> stored tensor for one Hugging Face checkpoint of ``cfg``'s family."""
+    if cfg.family == "qwen_vl":
+        text = replace(cfg, family="qwen2")
+        return {**_map_qwen_vision(store), **map_checkpoint(text, store)}
     if cfg.family == "gemma4":
         return _map_gemma4(cfg, store)
     if cfg.family == "idefics3":

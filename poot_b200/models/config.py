@@ -111,6 +111,7 @@ class DecoderConfig:
     norm_offset: float = 0.0                # checkpoint stores norm weights as w - offset (gemma: 1.0); added at load
     rope_layers: Optional[list] = None      # per-layer flag: 1 = rotary applied, 0 = no position signal (smollm3 NoPE layers)
     rope_interleaved: bool = False          # checkpoint stores rotary channels as interleaved pairs (deepseek): rows are re-ordered at load
+    mrope_sections: Optional[list] = None   # channel pairs of the time / row / column rotary streams (Qwen2.5-VL); None: one stream
     bos_token: int = 1
     eos_token: int = 2
 

@@ -146,3 +146,84 @@ def image_prompt(prep: ImagePrep, rows: int, cols: int, rows_per_image: int) -> 
             text += f"{prep.fake_token}<row_{r + 1}_col_{c + 1}>{run}"
         text += "\n"
     return text + f"\n{prep.fake_token}{prep.global_token}{run}{prep.fake_token}"
+
+
+# ---- Qwen2.5-VL ----------------------------------------------------------------------------------------------------
+CLIP_MEAN = (0.48145466, 0.4578275, 0.40821073)
+CLIP_STD = (0.26862954, 0.26130258, 0.27577711)
+
+
+@dataclass
+class QwenImagePrep:
+    """Preprocessing of the Qwen2.5-VL front end (crates/poot-models/src/multimodal/qwen_vl/processor): resize both
+    edges to multiples of ``patch * merge`` within a pixel budget (bicubic), normalise, and lay the pixels out as one
+    row per ``temporal x patch x patch`` patch in (frame, merged row, merged column, row in cell, column in cell) order."""
+    patch: int = 14
+    merge: int = 2
+    temporal: int = 2
+    min_pixels: int = 56 * 56
+    max_pixels: int = 28 * 28 * 1280
+    rescale: float = 1.0 / 255.0
+    mean: Tuple[float, ...] = CLIP_MEAN
+    std: Tuple[float, ...] = CLIP_STD
+    image_token: str = "<|image_pad|>"
+
+    @staticmethod
+    def from_dir(path: str, patch: int, merge: int, temporal: int) -> "QwenImagePrep":
+        p = QwenImagePrep(patch=patch, merge=merge, temporal=temporal, min_pixels=(2 * patch * merge) ** 2,
+                          max_pixels=(patch * merge) ** 2 * 1280)
+        f = os.path.join(path, "preprocessor_config.json")
+        if os.path.exists(f):
+            with open(f) as fh:
+                c = json.load(fh)
+            size = c.get("size") or {}
+            p.min_pixels = int(c.get("min_pixels") or size.get("shortest_edge") or p.min_pixels)
+            p.max_pixels = int(c.get("max_pixels") or size.get("longest_edge") or p.max_pixels)
+            p.rescale = float(c.get("rescale_factor", p.rescale))
+            p.mean = tuple(c.get("image_mean", p.mean))
+            p.std = tuple(c.get("image_std", p.std))
+            for key, want in (("patch_size", patch), ("merge_size", merge), ("temporal_patch_size", temporal)):
+                if key in c and int(c[key]) != want:
+                    raise ValueError(f"preprocessor {key} {c[key]} does not fit the vision tower's {want}")
+        return p
+
+
+def smart_resize(h: int, w: int, factor: int, min_pixels: int, max_pixels: int) -> Tuple[int, int]:
+    """``(height, width)``: both multiples of ``factor``, the area inside ``[min_pixels, max_pixels]``, aspect kept as
+    closely as that allows."""
+    if max(h, w) / min(h, w) > 200:
+        raise ValueError(f"aspect ratio of a {h}x{w} image exceeds 200")
+    hb, wb = round(h / factor) * factor, round(w / factor) * factor
+    if hb * wb > max_pixels:
+        beta = math.sqrt(h * w / max_pixels)
+        hb = max(factor, math.floor(h / beta / factor) * factor)
+        wb = max(factor, math.floor(w / beta / factor) * factor)
+    elif hb * wb < min_pixels:
+        beta = math.sqrt(min_pixels / (h * w))
+        hb, wb = math.ceil(h * beta / factor) * factor, math.ceil(w * beta / factor) * factor
+    return hb, wb
+
+
+@dataclass
+class QwenImages:
+    patches: np.ndarray                 # [sum t*h*w, C * temporal * patch * patch] f32
+    grids: List[Tuple[int, int, int]]   # (t, h, w) patches of every image
+
+    def rows(self, merge: int) -> List[int]:
+        return [t * h * w // (merge * merge) for t, h, w in self.grids]
+
+
+def qwen_preprocess(img, prep: QwenImagePrep) -> QwenImages:
+    """One still image (a PIL image): a single temporal step made of ``temporal`` copies of the frame."""
+    from PIL import Image
+    img = img.convert("RGB")
+    w, h = img.size
+    hb, wb = smart_resize(h, w, prep.patch * prep.merge, prep.min_pixels, prep.max_pixels)
+    img = img.resize((wb, hb), Image.BICUBIC)
+    a = np.asarray(img, dtype=np.float32).transpose(2, 0, 1) * np.float32(prep.rescale)
+    a = (a - np.asarray(prep.mean, np.float32)[:, None, None]) / np.asarray(prep.std, np.float32)[:, None, None]
+    p, m, tp = prep.patch, prep.merge, prep.temporal
+    gh, gw = hb // p, wb // p
+    x = np.broadcast_to(a[None], (tp, 3, hb, wb)).reshape(1, tp, 3, gh // m, m, p, gw // m, m, p)
+    x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)
+    return QwenImages(np.ascontiguousarray(x).reshape(gh * gw, 3 * tp * p * p), [(1, gh, gw)])

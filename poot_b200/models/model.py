@@ -35,6 +35,7 @@ class StepSpec:
     sampler: Optional[str] = None  # None = export logits; greedy | gumbel | gumbel_top_k | gumbel_top_k_top_p
     world: int = 1                # tensor-parallel world (the tracer emits all_reduce at the Megatron points)
     embeds: bool = False          # rows of other modalities replace the embeddings of flagged tokens (image rows of a VLM)
+    mrope: bool = False           # three rotary position streams (time, row, column) bind per token: ``rope_positions[3, R*T]``
 
     @property
     def slots(self) -> int:
@@ -189,7 +190,22 @@ class Model:
                 st = b.computed(tag + ".sin", (c.max_position, rot), F32, "rope_sin", (rot, theta, c.max_position, scaling))
                 if not flat:
                     flat.append(b.reshape(positions, (R * T,)))
-                rope_tables[key] = (b.gather(ct, flat[0], 0), b.gather(st, flat[0], 0))
+                if spec.mrope and c.mrope_sections:
+                    # sectioned rotary: channel pairs [0, s0) turn with the time stream, [s0, s0 + s1) with the row
+                    # stream, the rest with the column stream (multimodal/mrope.rs); text tokens carry three equal values
+                    streams = b.slot("rope_positions", (3, R * T), I32, "pos", range=(0, c.max_position - 1))
+                    per = [(b.gather(ct, b.reshape(b.slice(streams, 0, i, 1), (R * T,)), 0),
+                            b.gather(st, b.reshape(b.slice(streams, 0, i, 1), (R * T,)), 0)) for i in range(3)]
+                    half, cuts, at = rot // 2, [], 0
+                    for i, n in enumerate(c.mrope_sections):
+                        cuts.append((i % 3, at, n))
+                        at += n
+                    if at != half:
+                        raise ValueError(f"mrope sections {c.mrope_sections} do not cover {half} channel pairs")
+                    pieces = lambda k: [b.slice(per[i][k], -1, base + a0, n) for base in (0, half) for i, a0, n in cuts]
+                    rope_tables[key] = (b.concat(pieces(0), -1), b.concat(pieces(1), -1))
+                else:
+                    rope_tables[key] = (b.gather(ct, flat[0], 0), b.gather(st, flat[0], 0))
             return rope_tables[key]
 
         if c.pos == "rope" and c.mixer_of(0) == "attention":

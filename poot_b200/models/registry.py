@@ -382,6 +382,35 @@ def _idefics3(c):
     return text, vision, int(c.get("image_token_id", 128257))
 
 
+def _qwen_vl(c):
+    """Qwen2.5-VL: a Qwen2 text stack with sectioned rotary positions behind a windowed-attention vision tower."""
+    from .vision import QwenVisionConfig
+    t = dict(c.get("text_config") or c)
+    v = dict(c.get("vision_config") or {})
+    t.setdefault("tie_word_embeddings", c.get("tie_word_embeddings", False))
+    rp = t.get("rope_parameters") or t.get("rope_scaling") or {}
+    sections = rp.get("mrope_section")
+    if not sections:
+        raise UnsupportedFamily("qwen2_5_vl header without mrope_section")
+    plain = {k: x for k, x in t.items() if k not in ("rope_scaling", "rope_parameters")}
+    plain["rope_theta"] = rp.get("rope_theta", t.get("rope_theta", 1000000.0))
+    plain["use_sliding_window"] = False
+    text = _base(plain, "qwen_vl", attn_bias=True, out_bias=False)
+    text.mrope_sections = [int(x) for x in sections]
+    act = {"silu": "silu", "gelu_pytorch_tanh": "gelu_tanh", "gelu": "gelu_erf"}.get(v.get("hidden_act", "silu"))
+    if act is None:
+        raise UnsupportedFamily(f"qwen2_5_vl vision activation {v.get('hidden_act')!r}")
+    vision = QwenVisionConfig(hidden=v.get("hidden_size", 1280), ffn=v.get("intermediate_size", 3420), n_layers=v.get("depth", 32),
+                              n_heads=v.get("num_heads", 16), channels=v.get("in_channels", v.get("in_chans", 3)),
+                              patch=v.get("patch_size", 14), temporal=v.get("temporal_patch_size", 2),
+                              merge=v.get("spatial_merge_size", 2), window=v.get("window_size", 112),
+                              full_layers=tuple(v.get("fullatt_block_indexes", (7, 15, 23, 31))),
+                              out_hidden=v.get("out_hidden_size", text.hidden), act=act)
+    if vision.out_hidden != text.hidden:
+        raise UnsupportedFamily("qwen2_5_vl: the merger's output width differs from the text width")
+    return text, vision, int(c.get("image_token_id", 151655))
+
+
 def _bert(c):
     from .encoder import EncoderConfig
     if (c.get("position_embedding_type") or "absolute") != "absolute":
@@ -421,12 +450,12 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("qwen38_27b", ["qwen3_5", "qwen3_5_text"], ["qwen35"], _qwen35),
     FamilyEntry("bert", ["bert"], ["bert"], _bert, kind="encoder"),
     FamilyEntry("idefics3", ["idefics3", "smolvlm"], [], _idefics3, kind="vlm"),
+    FamilyEntry("qwen_vl", ["qwen2_5_vl"], [], _qwen_vl, kind="vlm"),
     # families the reference ships whose mixers are not built here: refused by name
     FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], None, "sparse attention indexer"),
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
     FamilyEntry("qwen38", ["qwen4_exp"], ["qwen4exp"], None, "block-indexed sparse attention, hyper-connection residual streams, n-gram embeddings"),
     FamilyEntry("glm53_flash", ["glm5_flash"], ["glm53"], None, "kimi delta attention, hyper-connection residual streams"),
-    FamilyEntry("qwen_vl", ["qwen2_5_vl"], ["qwen2vl"], None, "vision tower, sectioned mRoPE"),
 ]
 
 
@@ -455,9 +484,10 @@ class Registry:
                     from .gemma4 import Gemma4Model
                     return Gemma4Model(e.from_hf(config))
                 if e.kind == "vlm":
-                    from .vision import VisionLanguageModel, VisionTower
+                    from .vision import QwenVisionConfig, QwenVisionTower, VisionLanguageModel, VisionTower
                     text, vision, image_token = e.from_hf(config)
-                    return VisionLanguageModel(Model(text), VisionTower(vision), image_token)
+                    tower = QwenVisionTower(vision) if isinstance(vision, QwenVisionConfig) else VisionTower(vision)
+                    return VisionLanguageModel(Model(text), tower, image_token)
                 return Model(e.from_hf(config))
         raise UnsupportedFamily(f"no family for model_type {mt!r}")
 

@@ -29,6 +29,12 @@ SAMPLES = {
                       shared_expert_intermediate_size=512),
     "qwen38_27b": dict(model_type="qwen3_5_text", linear_num_value_heads=48, linear_num_key_heads=16, linear_key_head_dim=128,
                        linear_value_head_dim=128),
+    "qwen_vl": dict(model_type="qwen2_5_vl", text_config=dict(hidden_size=2048, num_hidden_layers=4, num_attention_heads=16,
+                                                              num_key_value_heads=2, intermediate_size=11008, vocab_size=151936,
+                                                              rope_parameters={"rope_type": "default", "mrope_section": [16, 24, 24],
+                                                                               "rope_theta": 1000000.0}),
+                    vision_config=dict(depth=32, hidden_size=1280, intermediate_size=3420, num_heads=16, out_hidden_size=2048),
+                    image_token_id=151655),
     "gemma4": dict(model_type="gemma4_text", head_dim=256, global_head_dim=512, hidden_size_per_layer_input=256, num_kv_shared_layers=2,
                    vocab_size_per_layer_input=32000, sliding_window=512,
                    layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
@@ -57,6 +63,11 @@ def rows():
         model = reg.resolve_hf(header)
         if e.kind == "encoder":
             out.append((e.name, ", ".join(e.hf_types), "oracle", "no", "-", "embeddings and rerank scores on the host evaluator"))
+            continue
+        if e.kind == "vlm" and model.cfg.mrope_sections:
+            out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "text stack",
+                        "a device program for the vision tower; three rotary position streams per token in the driver "
+                        "(images run through `caption` / `VisionLLM` on the host evaluator)"))
             continue
         if e.kind == "vlm":
             out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "text stack",

@@ -157,3 +157,157 @@ class VisionLanguageModel:
 
     def trace(self, spec):
         return self.text.trace(spec)
+
+
+# ---- Qwen2.5-VL ----------------------------------------------------------------------------------------------------
+@dataclass
+class QwenVisionConfig:
+    """Vision tower of Qwen2.5-VL (crates/poot-models/src/multimodal/qwen_vl/tower.rs): patches of
+    ``temporal x patch x patch`` pixels, 2-D rotary positions, attention inside windows of merged patches except on the
+    ``full_layers``, RMSNorm, biased SwiGLU, and a merger that folds ``merge x merge`` patches into one text row."""
+    hidden: int = 64
+    ffn: int = 128
+    n_layers: int = 2
+    n_heads: int = 4
+    channels: int = 3
+    patch: int = 14
+    temporal: int = 2
+    merge: int = 2
+    window: int = 112                      # pixels
+    full_layers: tuple = (1,)
+    out_hidden: int = 64
+    act: str = "silu"
+    norm_eps: float = 1e-6
+    rope_theta: float = 10000.0
+
+    @property
+    def patch_dim(self) -> int:
+        return self.channels * self.temporal * self.patch * self.patch
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.n_heads
+
+    @property
+    def unit(self) -> int:
+        return self.merge * self.merge
+
+
+def qwen_vision_inputs(cfg: QwenVisionConfig, grids) -> Dict[str, np.ndarray]:
+    """Host-side inputs of the tower for images of ``grids = [(t, h, w), ...]`` patches, in the processor's patch order
+    (frame, merged row, merged column, row in the merge cell, column in the merge cell): rotary tables from each patch's
+    (row, column), and the two additive masks - patches of one frame see each other on the full layers, patches of one
+    window of ``window / merge / patch`` merged cells on the others."""
+    rows, cols, frame_id, window_id = [], [], [], []
+    m, vws = cfg.merge, max(cfg.window // cfg.merge // cfg.patch, 1)
+    frames = windows = 0
+    for t, h, w in grids:
+        lh, lw = h // m, w // m
+        r = np.arange(h)[:, None].repeat(w, 1).reshape(lh, m, lw, m).transpose(0, 2, 1, 3).reshape(-1)
+        c = np.arange(w)[None, :].repeat(h, 0).reshape(lh, m, lw, m).transpose(0, 2, 1, 3).reshape(-1)
+        wh = -(-lh // vws)
+        win = ((r // m) // vws) * (-(-lw // vws)) + (c // m) // vws
+        for f in range(t):
+            rows.append(r); cols.append(c)
+            frame_id.append(np.full(h * w, frames + f))
+            window_id.append(windows + f * wh * (-(-lw // vws)) + win)
+        frames += t
+        windows += t * wh * (-(-lw // vws))
+    rows, cols = np.concatenate(rows), np.concatenate(cols)
+    frame_id, window_id = np.concatenate(frame_id), np.concatenate(window_id)
+    quarter = cfg.head_dim // 4
+    inv = 1.0 / (cfg.rope_theta ** (np.arange(0, cfg.head_dim // 2, 2, dtype=np.float32) / np.float32(cfg.head_dim // 2)))
+    ang = np.concatenate([rows[:, None].astype(np.float32) * inv[None, :quarter], cols[:, None].astype(np.float32) * inv[None, :quarter]], 1)
+    ang = np.concatenate([ang, ang], 1)
+    hidden = np.float32(O.MASK_HIDDEN)
+    return {"rope_cos": np.cos(ang).astype(np.float32), "rope_sin": np.sin(ang).astype(np.float32),
+            "mask_full": np.where(frame_id[:, None] == frame_id[None, :], np.float32(0), hidden)[None].astype(np.float32),
+            "mask_window": np.where(window_id[:, None] == window_id[None, :], np.float32(0), hidden)[None].astype(np.float32)}
+
+
+class QwenVisionTower:
+    def __init__(self, cfg: QwenVisionConfig):
+        self.cfg = cfg
+
+    def weight_shapes(self) -> Dict[str, tuple]:
+        c = self.cfg
+        H, U = c.hidden, c.hidden * c.unit
+        s = {"vision.patch_embed": (H, c.patch_dim), "vision.merger_norm": (H,), "vision.merger_fc1": (U, U),
+             "vision.merger_fc1_bias": (U,), "vision.merger_fc2": (c.out_hidden, U), "vision.merger_fc2_bias": (c.out_hidden,)}
+        for l in range(c.n_layers):
+            p = f"vision.layers.{l}."
+            for r, shape in (("attn_q", (H, H)), ("attn_k", (H, H)), ("attn_v", (H, H)), ("attn_o", (H, H)),
+                             ("ffn_gate", (c.ffn, H)), ("ffn_up", (c.ffn, H)), ("ffn_down", (H, c.ffn))):
+                s[p + r], s[p + r + "_bias"] = shape, (shape[0],)
+            s[p + "attn_norm"], s[p + "ffn_norm"] = (H,), (H,)
+        return s
+
+    def trace(self, patches: int, weight_dtype: DType = DType.F32) -> Graph:
+        """``patches[N, patch_dim]`` + the inputs of ``qwen_vision_inputs`` -> ``image_rows[N / merge^2, out_hidden]``."""
+        c = self.cfg
+        b = Builder()
+        N, H, nh, D = patches, c.hidden, c.n_heads, c.head_dim
+        shapes = self.weight_shapes()
+        consts = {}
+
+        def W(name):
+            if name not in consts:
+                consts[name] = b.const(name, shapes[name], weight_dtype).cast(F32)
+            return consts[name]
+
+        x = b.slot("patches", (N, c.patch_dim), F32, "activation")
+        cos = b.slot("rope_cos", (N, D), F32, "activation")
+        sin = b.slot("rope_sin", (N, D), F32, "activation")
+        masks = {True: b.slot("mask_full", (1, N, N), F32, "activation"), False: b.slot("mask_window", (1, N, N), F32, "activation")}
+        h = O.linear(b, x, W("vision.patch_embed"), precision="exact")
+        scale = 1.0 / math.sqrt(D)
+        for l in range(c.n_layers):
+            p = f"vision.layers.{l}."
+            y = O.rmsnorm(b, h, W(p + "attn_norm"), c.norm_eps)
+            q = O.rope(b, b.reshape(O.linear(b, y, W(p + "attn_q"), W(p + "attn_q_bias")), (N, nh, D)), cos, sin, D)
+            k = O.rope(b, b.reshape(O.linear(b, y, W(p + "attn_k"), W(p + "attn_k_bias")), (N, nh, D)), cos, sin, D)
+            v = b.reshape(O.linear(b, y, W(p + "attn_v"), W(p + "attn_v_bias")), (N, nh, D))
+            heads = lambda t: b.transpose(b.reshape(t, (1, N, nh, D)), (0, 2, 1, 3))
+            a = O.attention_masked(b, heads(q), heads(k), heads(v), masks[l in c.full_layers], scale)
+            a = b.reshape(b.transpose(a, (0, 2, 1, 3)), (N, H))
+            h = h + O.linear(b, a, W(p + "attn_o"), W(p + "attn_o_bias"))
+            y = O.rmsnorm(b, h, W(p + "ffn_norm"), c.norm_eps)
+            g = O.ffn_activation(b, O.linear(b, y, W(p + "ffn_gate"), W(p + "ffn_gate_bias")),
+                                 O.linear(b, y, W(p + "ffn_up"), W(p + "ffn_up_bias")), c.act)
+            h = h + O.linear(b, g, W(p + "ffn_down"), W(p + "ffn_down_bias"))
+        m = b.reshape(O.rmsnorm(b, h, W("vision.merger_norm"), c.norm_eps), (N // c.unit, H * c.unit))
+        m = O.gelu_erf(b, O.linear(b, m, W("vision.merger_fc1"), W("vision.merger_fc1_bias")))
+        b.output(O.linear(b, m, W("vision.merger_fc2"), W("vision.merger_fc2_bias")), "image_rows", "result")
+        return b.finish()
+
+
+def mrope_positions(tokens, image_token: int, grids, merge: int) -> np.ndarray:
+    """Rotary position streams ``[3, len(tokens)]`` (time, row, column) of a prompt whose runs of ``image_token`` stand
+    for the images of ``grids = [(t, h, w), ...]`` patches (multimodal/mrope.rs; ``get_rope_index``): text tokens count
+    up with three equal values; an image starting at ``s`` gives ``(s, s + row, s + column)`` per merged cell; the text
+    after it continues at ``s + max(rows, columns)`` of merged cells."""
+    toks = np.asarray(tokens).reshape(-1)
+    out = np.zeros((3, len(toks)), dtype=np.int32)
+    i, nxt, image = 0, 0, 0
+    while i < len(toks):
+        if toks[i] != image_token:
+            out[:, i] = nxt
+            nxt += 1
+            i += 1
+            continue
+        if image >= len(grids):
+            raise ValueError("more image runs in the prompt than images")
+        t, h, w = grids[image]
+        lh, lw = h // merge, w // merge
+        n = t * lh * lw
+        if not np.all(toks[i:i + n] == image_token) or len(toks[i:i + n]) != n:
+            raise ValueError(f"image {image}: the prompt holds fewer than {n} image tokens in a run")
+        out[0, i:i + n] = nxt                   # frames of one image share the start (no time interval between them)
+        out[1, i:i + n] = nxt + np.tile(np.repeat(np.arange(lh), lw), t)
+        out[2, i:i + n] = nxt + np.tile(np.tile(np.arange(lw), lh), t)
+        nxt += max(lh, lw)
+        i += n
+        image += 1
+    if image != len(grids):
+        raise ValueError(f"{len(grids)} images for {image} image runs in the prompt")
+    return out

@@ -46,11 +46,11 @@ class OracleSession:
         self.block_table = np.asarray(order, dtype=np.int32).reshape(rows, capacity // BLOCK)
         self.last_logits: Optional[np.ndarray] = None
 
-    def _graph(self, tokens: int, embeds: bool = False):
-        key = (tokens, embeds)
+    def _graph(self, tokens: int, embeds: bool = False, mrope: bool = False):
+        key = (tokens, embeds, mrope) if mrope else (tokens, embeds)
         if key not in self.graphs:
             spec = StepSpec(rows=self.rows, tokens=tokens, capacity=self.capacity, paged=self.paged, world=self.world,
-                            embeds=embeds)
+                            embeds=embeds, mrope=mrope)
             g = self.model.trace(spec)
             self.graphs[key] = self.graph_transform(g) if self.graph_transform is not None else g
         return self.graphs[key]
@@ -59,14 +59,18 @@ class OracleSession:
         return int(self.block_table[row, pos // BLOCK]) * BLOCK + pos % BLOCK
 
     def step(self, tokens: np.ndarray, embed_rows: Optional[np.ndarray] = None,
-             embed_flags: Optional[np.ndarray] = None) -> np.ndarray:
+             embed_flags: Optional[np.ndarray] = None, rope_positions: Optional[np.ndarray] = None) -> np.ndarray:
         """Feed ``tokens[rows, T]`` at the current position; returns logits ``[rows, vocab]`` of the last token.
-        ``embed_rows[rows * T, hidden]`` replace the embeddings of the tokens whose ``embed_flags`` entry is 1."""
+        ``embed_rows[rows * T, hidden]`` replace the embeddings of the tokens whose ``embed_flags`` entry is 1;
+        ``rope_positions[3, rows * T]`` are the rotary position streams of a sectioned-rope model (the K/V index of a
+        token stays its place in the sequence)."""
         tokens = np.asarray(tokens, dtype=np.int32).reshape(self.rows, -1)
         T = tokens.shape[1]
-        g = self._graph(T, embed_rows is not None)
+        g = self._graph(T, embed_rows is not None, True) if rope_positions is not None else self._graph(T, embed_rows is not None)
         pos = np.arange(self.length, self.length + T, dtype=np.int32)[None, :].repeat(self.rows, 0)
         inputs: Dict[str, np.ndarray] = {"tokens": tokens, "positions": pos}
+        if rope_positions is not None:
+            inputs["rope_positions"] = np.asarray(rope_positions, dtype=np.int32).reshape(3, self.rows * T)
         if embed_rows is not None:
             inputs["embed_rows"] = np.asarray(embed_rows, dtype=np.float32).reshape(self.rows * T, -1)
             inputs["embed_flags"] = np.asarray(embed_flags, dtype=np.int32).reshape(self.rows * T)

@@ -15,8 +15,8 @@ from typing import Callable, List, Optional, Sequence
 import numpy as np
 
 from .driver.handle import ModelHandle
-from .models.image_prep import ImagePrep, image_prompt, preprocess
-from .models.vision import patchify, position_ids
+from .models.image_prep import ImagePrep, QwenImagePrep, QwenImages, image_prompt, preprocess, qwen_preprocess
+from .models.vision import QwenVisionTower, mrope_positions, patchify, position_ids, qwen_vision_inputs
 from .oracle.eval import EvalOptions, eval_graph
 from .driver.sampler import SamplingParams
 from .oracle.runner import BLOCK, OracleSession
@@ -30,6 +30,14 @@ VLM_TEMPLATE = ("<|im_start|>{% for message in messages %}{{message['role'] | ca
                 "{% elif line['type'] == 'image' %}{{ '<image>' }}{% endif %}{% endfor %}<end_of_utterance>\n{% endfor %}"
                 "{% if add_generation_prompt %}{{ 'Assistant:' }}{% endif %}")
 
+
+# Qwen2.5-VL's template: ChatML turns, an image part written as one padded placeholder between the vision markers
+QWEN_VL_TEMPLATE = ("{% for message in messages %}{% if loop.first and message['role'] != 'system' %}<|im_start|>system\n"
+                    "You are a helpful assistant.<|im_end|>\n{% endif %}<|im_start|>{{ message['role'] }}\n"
+                    "{% if message['content'] is string %}{{ message['content'] }}{% else %}{% for part in message['content'] %}"
+                    "{% if part['type'] == 'image' %}<|vision_start|><|image_pad|><|vision_end|>"
+                    "{% elif part['type'] == 'text' %}{{ part['text'] }}{% endif %}{% endfor %}{% endif %}<|im_end|>\n{% endfor %}"
+                    "{% if add_generation_prompt %}<|im_start|>assistant\n{% endif %}")
 
 MAX_IMAGE_BYTES = 32 * 1024 * 1024
 MAX_IMAGE_PIXELS = 64 * 1024 * 1024
@@ -79,8 +87,15 @@ class VisionLLM:
         self._weights = None
         self.tokenizer, self.template = tokenizer, template
         self.llm = llm                                # text driver (None: a bare oracle session per call)
-        self.prep = ImagePrep.from_dir(handle.source, self.vision.cfg.image_size)
+        self.qwen = isinstance(self.vision, QwenVisionTower)      # sectioned rotary positions, patches of any grid
+        if self.qwen:
+            vc = self.vision.cfg
+            self.prep = QwenImagePrep.from_dir(handle.source, vc.patch, vc.merge, vc.temporal)
+            self.llm = None              # the serving driver binds one position per token; this family needs three
+        else:
+            self.prep = ImagePrep.from_dir(handle.source, self.vision.cfg.image_size)
         self._towers = {}
+        self.rope_delta = 0                           # rotary position minus sequence index after the last prefilled prompt
         self.eos: List[int] = []                      # end tokens of generation_config.json, beside the tokenizer's
 
     @staticmethod
@@ -127,8 +142,19 @@ class VisionLLM:
 
     # ---- vision tower ----------------------------------------------------------------------------------------------
     def encode_images(self, pixels: np.ndarray) -> np.ndarray:
-        """``pixels[frames, C, S, S]`` (normalised) -> ``[frames * rows_per_image, text_hidden]``."""
+        """``pixels[frames, C, S, S]`` (normalised) -> ``[frames * rows_per_image, text_hidden]``; for Qwen2.5-VL the
+        flattened patches and grids of ``QwenImages`` -> one row per merged cell."""
         c = self.vision.cfg
+        if self.qwen:
+            n = pixels.patches.shape[0]
+            if n not in self._towers:
+                self._towers[n] = self.vision.trace(n)
+            g = self._towers[n]
+            inputs = {"patches": np.asarray(pixels.patches, dtype=np.float32), **qwen_vision_inputs(c, pixels.grids)}
+            for i in g.inputs:
+                if i.storage == "const":
+                    inputs[i.name] = self.vision_weights[i.name]
+            return eval_graph(g, inputs, EvalOptions(matmul_precision="exact")).outputs["image_rows"]
         pixels = np.asarray(pixels, dtype=np.float32)
         n, ch, h, w = pixels.shape
         if (ch, h, w) != (c.channels, c.image_size, c.image_size):
@@ -146,14 +172,8 @@ class VisionLLM:
     # ---- prompt ----------------------------------------------------------------------------------------------------
     def prepare(self, question: str, image) -> tuple:
         """``(prompt tokens, frames)`` for one user turn holding ``image`` (a PIL image) and ``question``."""
-        if self.tokenizer is None:
-            raise ValueError("the checkpoint directory has no tokenizer.json")
-        frames = preprocess(image, self.prep)
-        text = render_chat([{"role": "user", "content": [{"type": "image"}, {"type": "text", "text": question}]}],
-                           self.template or VLM_TEMPLATE, family="idefics3", keep_parts=True)
-        expanded = image_prompt(self.prep, frames.rows, frames.cols, self.vision.cfg.rows_per_image)
-        text = text.replace(self.prep.image_token, expanded, 1)
-        return self.tokenizer.encode(text, add_bos=False), frames.pixels
+        return self.prepare_messages([{"role": "user", "content": [{"type": "image", "image": image},
+                                                                  {"type": "text", "text": question}]}])
 
     def prepare_messages(self, messages: List[dict], template: Optional[str] = None) -> tuple:
         """Chat messages whose contents hold image parts -> ``(prompt tokens, frames of every image in order)``.
@@ -181,16 +201,25 @@ class VisionLLM:
                 else:
                     raise ValueError(f"content part of type {kind!r}: text and image_url parts are read")
             shaped.append({**m, "content": parts})
-        text = render_chat(shaped, template or self.template or VLM_TEMPLATE, family="idefics3", keep_parts=True)
+        default = QWEN_VL_TEMPLATE if self.qwen else VLM_TEMPLATE
+        text = render_chat(shaped, template or self.template or default, family=self.handle.cfg.family, keep_parts=True)
         pieces = text.split(self.prep.image_token)
         if len(pieces) != len(images) + 1:
             raise ValueError(f"the template wrote {len(pieces) - 1} image placeholders for {len(images)} images")
-        out, frames = pieces[0], []
+        out, frames, grids = pieces[0], [], []
         for img, tail in zip(images, pieces[1:]):
-            fr = preprocess(img, self.prep)
-            frames.append(fr.pixels)
-            out += image_prompt(self.prep, fr.rows, fr.cols, self.vision.cfg.rows_per_image) + tail
+            if self.qwen:
+                one = qwen_preprocess(img, self.prep)
+                frames.append(one.patches)
+                grids += one.grids
+                out += self.prep.image_token * one.rows(self.vision.cfg.merge)[0] + tail
+            else:
+                fr = preprocess(img, self.prep)
+                frames.append(fr.pixels)
+                out += image_prompt(self.prep, fr.rows, fr.cols, self.vision.cfg.rows_per_image) + tail
         pixels = np.concatenate(frames, 0) if frames else None
+        if self.qwen and frames:
+            pixels = QwenImages(pixels, grids)
         return self.tokenizer.encode(out, add_bos=False), pixels
 
     # ---- generation ------------------------------------------------------------------------------------------------
@@ -202,20 +231,29 @@ class VisionLLM:
         """Feed the whole prompt; returns the last position's logits ``[1, vocab]``."""
         toks = np.asarray(tokens, dtype=np.int32).reshape(1, -1)
         flags = (toks[0] == self.model.image_token).astype(np.int32)
-        if pixels is None or len(pixels) == 0:
+        none = pixels is None or (not self.qwen and len(pixels) == 0)
+        rope = None
+        if self.qwen:
+            # three rotary streams per token; the decode steps after this prompt continue at ``index + rope_delta``
+            rope = mrope_positions(toks[0], self.model.image_token, [] if none else pixels.grids, self.vision.cfg.merge)
+            self.rope_delta = int(rope.max()) + 1 - toks.shape[1]
+        if none:
             if flags.any():
                 raise ValueError("the prompt holds image tokens but no image was given")
-            return sess.step(toks)
+            return sess.step(toks, rope_positions=rope)
         rows = self.encode_images(pixels)
         if int(flags.sum()) != rows.shape[0]:
             raise ValueError(f"the prompt holds {int(flags.sum())} image tokens; the frames give {rows.shape[0]} rows")
         full = np.zeros((toks.shape[1], rows.shape[1]), dtype=np.float32)
         full[flags.astype(bool)] = rows
-        return sess.step(toks, embed_rows=full, embed_flags=flags)
+        return sess.step(toks, embed_rows=full, embed_flags=flags, rope_positions=rope)
 
     def image_inputs(self, tokens: Sequence[int], pixels: Optional[np.ndarray]):
         """``(positions, rows)`` for ``Driver.open(..., embeds=)``: the prompt's image-token positions and the rows the
         frames give, checked to agree in number."""
+        if self.qwen:
+            raise ValueError("this family's sectioned rotary positions are not bound by the serving driver; "
+                             "its images run through VisionLLM.generate / `caption`")
         toks = np.asarray(tokens, dtype=np.int64).reshape(-1)
         at = np.nonzero(toks == self.model.image_token)[0]
         if pixels is None or len(pixels) == 0:
@@ -243,7 +281,8 @@ class VisionLLM:
                 if on_token is not None:
                     on_token(tok)
                 if i + 1 < max_new:
-                    logits = sess.step(np.array([[tok]], dtype=np.int32))
+                    rope = np.full((3, 1), sess.length + self.rope_delta, np.int32) if self.qwen else None
+                    logits = sess.step(np.array([[tok]], dtype=np.int32), rope_positions=rope)
             return out
         drv = self.llm.driver
         params = SamplingParams(temperature=0.0, max_tokens=max_new, ignore_eos=True)

@@ -288,3 +288,141 @@ def test_text_checkpoints_have_no_front_end(tmp_path):
                                  num_key_value_heads=2, vocab_size=64)).save_pretrained(d, safe_serialization=True)
     with pytest.raises(NotVisionModel):
         VisionLLM.load(d)
+
+
+# ---- Qwen2.5-VL ----------------------------------------------------------------------------------------------------
+QWEN_SPECIALS = ["<|im_start|>", "<|im_end|>", "<|vision_start|>", "<|vision_end|>", "<|image_pad|>", "<|video_pad|>"]
+
+
+@pytest.fixture(scope="module")
+def qwen_checkpoint(tmp_path_factory):
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers
+    from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    d = str(tmp_path_factory.mktemp("qwen_vl"))
+    vocab = {ch: i for i, ch in enumerate(sorted(pre_tokenizers.ByteLevel.alphabet()))}
+    tk = Tokenizer(models.BPE(vocab=vocab, merges=[]))
+    tk.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False)
+    tk.decoder = decoders.ByteLevel()
+    tk.add_special_tokens(QWEN_SPECIALS)
+    tk.save(os.path.join(d, "tokenizer.json"))
+    with open(os.path.join(d, "tokenizer_config.json"), "w") as f:
+        json.dump({"eos_token": "<|im_end|>"}, f)
+    ids = {t: tk.token_to_id(t) for t in QWEN_SPECIALS}
+    torch.manual_seed(0)
+    cfg = Qwen2_5_VLConfig(
+        text_config=dict(hidden_size=64, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         vocab_size=tk.get_vocab_size(), max_position_embeddings=512,
+                         rope_parameters={"rope_type": "default", "mrope_section": [2, 3, 3], "rope_theta": 10000.0}),
+        # one position token per second: this transformers version multiplies an image's start position by the rate
+        vision_config=dict(depth=3, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4,
+                           spatial_merge_size=2, temporal_patch_size=2, window_size=16, fullatt_block_indexes=[1],
+                           out_hidden_size=64, tokens_per_second=1),
+        image_token_id=ids["<|image_pad|>"], video_token_id=ids["<|video_pad|>"], vision_start_token_id=ids["<|vision_start|>"],
+        vision_end_token_id=ids["<|vision_end|>"])
+    hf = Qwen2_5_VLForConditionalGeneration(cfg).eval()
+    for p in hf.parameters():
+        if p.ndim == 1:
+            p.data.add_(torch.randn_like(p) * 0.1)
+    hf.save_pretrained(d, safe_serialization=True)
+    with open(os.path.join(d, "preprocessor_config.json"), "w") as f:
+        json.dump({"size": {"shortest_edge": 16 * 16, "longest_edge": 8 * 8 * 40}, "patch_size": 4, "merge_size": 2,
+                   "temporal_patch_size": 2}, f)
+    return d, hf, ids
+
+
+def _qwen_greedy(hf, tokens, images, image_token, n):
+    ids = torch.tensor([tokens])
+    with torch.no_grad():
+        gen = hf.generate(input_ids=ids, pixel_values=torch.tensor(images.patches), image_grid_thw=torch.tensor(images.grids),
+                          attention_mask=torch.ones_like(ids), mm_token_type_ids=(ids == image_token).long(), max_new_tokens=n,
+                          do_sample=False, eos_token_id=None, pad_token_id=0)
+    return gen[0, len(tokens):].tolist()
+
+
+def test_qwen_vl_tower_logits_and_generation_match_transformers(qwen_checkpoint):
+    from poot_b200.models.image_prep import QwenImages
+    d, hf, ids = qwen_checkpoint
+    vlm = VisionLLM.load(d)
+    IMG = ids["<|image_pad|>"]
+    assert vlm.qwen and vlm.model.image_token == IMG and vlm.handle.cfg.mrope_sections == [2, 3, 3]
+    grids = [(1, 8, 12), (1, 4, 6)]                  # two images: 6 windows of 2x2 merged cells, and 2x... a ragged edge
+    n = sum(t * h * w for t, h, w in grids)
+    images = QwenImages(np.random.default_rng(0).standard_normal((n, vlm.vision.cfg.patch_dim)).astype(np.float32), grids)
+    with torch.no_grad():
+        want_rows = hf.model.visual(torch.tensor(images.patches), grid_thw=torch.tensor(grids)).pooler_output.numpy()
+    rows = vlm.encode_images(images)
+    assert rows.shape == (24 + 6, 64) and np.abs(rows - want_rows).max() < 1e-5
+    tokens = [5, 6, ids["<|vision_start|>"]] + [IMG] * 24 + [ids["<|vision_end|>"], 7, ids["<|vision_start|>"]] + [IMG] * 6 + \
+             [ids["<|vision_end|>"], 8, 9, 10, 11]
+    t = torch.tensor([tokens])
+    with torch.no_grad():
+        out = hf(input_ids=t, pixel_values=torch.tensor(images.patches), image_grid_thw=torch.tensor(grids),
+                 attention_mask=torch.ones_like(t), mm_token_type_ids=(t == IMG).long())
+    want = out.logits[0, -1].numpy()
+    got = vlm.prefill(vlm._session(len(tokens)), tokens, images)[0]
+    assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    assert vlm.rope_delta == (2 + 1 + 6 + 2 + 1 + 3 + 5) - len(tokens)          # an image advances by its longer merged edge
+    assert vlm.generate(tokens, images, max_new=6) == _qwen_greedy(hf, tokens, images, IMG, 6)
+    # without images the three streams are equal and the stack is the plain Qwen2 one
+    plain = [5, 6, 7, 8, 9, 10]
+    with torch.no_grad():
+        want = hf(input_ids=torch.tensor([plain])).logits[0, -1].numpy()
+    assert np.abs(vlm.prefill(vlm._session(16), plain, None)[0] - want).max() < 1e-5
+    with pytest.raises(ValueError, match="serving driver"):
+        vlm.image_inputs(tokens, images)
+
+
+def test_mrope_positions():
+    from poot_b200.models.vision import mrope_positions
+    I = 99
+    pos = mrope_positions([1, 2] + [I] * 6 + [3, 4], I, [(1, 4, 6)], 2)          # 2 x 3 merged cells starting at 2
+    assert pos[0].tolist() == [0, 1, 2, 2, 2, 2, 2, 2, 5, 6]
+    assert pos[1].tolist() == [0, 1, 2, 2, 2, 3, 3, 3, 5, 6]
+    assert pos[2].tolist() == [0, 1, 2, 3, 4, 2, 3, 4, 5, 6]
+    assert mrope_positions([4, 5, 6], I, [], 2).tolist() == [[0, 1, 2]] * 3
+    with pytest.raises(ValueError, match="fewer than"):
+        mrope_positions([1] + [I] * 5, I, [(1, 4, 6)], 2)
+    with pytest.raises(ValueError, match="more image runs"):
+        mrope_positions([I] * 6 + [1] + [I] * 6, I, [(1, 4, 6)], 2)
+    with pytest.raises(ValueError, match="2 images for 1"):
+        mrope_positions([I] * 6, I, [(1, 4, 6), (1, 4, 6)], 2)
+
+
+@pytest.mark.parametrize("hw", [(300, 500), (64, 40), (1000, 900), (30, 31)])
+def test_qwen_preprocessing_matches_the_reference_processor(hw):
+    from PIL import Image
+    from transformers.models.qwen2_vl.image_processing_pil_qwen2_vl import Qwen2VLImageProcessorPil
+    from poot_b200.models.image_prep import QwenImagePrep, qwen_preprocess, smart_resize
+    img = Image.fromarray(np.random.default_rng(0).integers(0, 255, (*hw, 3), dtype=np.uint8))
+    for patch, lo, hi in ((14, 56 * 56, 28 * 28 * 1280), (4, 16 * 16, 8 * 8 * 40)):
+        ip = Qwen2VLImageProcessorPil(patch_size=patch, merge_size=2, temporal_patch_size=2, size={"shortest_edge": lo, "longest_edge": hi})
+        out = ip(images=[img], return_tensors="np")
+        got = qwen_preprocess(img, QwenImagePrep(patch=patch, min_pixels=lo, max_pixels=hi))
+        assert got.grids == [tuple(int(x) for x in out["image_grid_thw"][0])]
+        assert got.patches.shape == out["pixel_values"].shape and np.abs(got.patches - out["pixel_values"]).max() < 2e-6
+    assert smart_resize(30, 31, 28, 56 * 56, 10 ** 6) == (56, 84) and smart_resize(1000, 900, 8, 256, 2560) == (48, 48)
+    with pytest.raises(ValueError, match="aspect"):
+        smart_resize(10, 2001, 28, 1, 10 ** 9)
+
+
+def test_qwen_caption_command(qwen_checkpoint, tmp_path, capsys):
+    from PIL import Image
+    from poot_b200.cli.__main__ import main
+    from poot_b200.text.codec import StreamDecoder
+    d, hf, ids = qwen_checkpoint
+    path = str(tmp_path / "picture.png")
+    img = Image.fromarray(np.random.default_rng(3).integers(0, 255, (40, 60, 3), dtype=np.uint8))
+    img.save(path)
+    vlm = VisionLLM.load(d)
+    tokens, images = vlm.prepare("What is this?", img)
+    assert images.grids == [(1, 10, 16)] and tokens.count(ids["<|image_pad|>"]) == 40
+    text = vlm.tokenizer.tk.decode(tokens, skip_special_tokens=False)
+    assert "<|im_start|>user\n<|vision_start|><|image_pad|>" in text and text.endswith("What is this?<|im_end|>\n<|im_start|>assistant\n")
+    want = _qwen_greedy(hf, tokens, images, ids["<|image_pad|>"], 5)
+    assert vlm.generate(tokens, images, max_new=5) == want
+    assert main(["caption", d, path, "What is this?", "-n", "5", "--backend", "oracle"]) == 0
+    out = capsys.readouterr().out
+    eos = vlm.tokenizer.eos
+    shown = want[:want.index(eos)] if eos in want else want
+    dec = StreamDecoder(vlm.tokenizer)
+    assert out == "".join(dec.push(t) for t in shown) + dec.flush() + "\n"
