@@ -68,6 +68,9 @@ LAYER = {
     "self_attn.q_a_proj.weight": "attn_q_a", "self_attn.q_a_layernorm.weight": "attn_q_a_norm",
     "self_attn.q_b_proj.weight": "attn_q_b", "self_attn.kv_a_proj_with_mqa.weight": "attn_kv_a",
     "self_attn.kv_a_layernorm.weight": "attn_kv_a_norm", "self_attn.kv_b_proj.weight": "attn_kv_b",
+    # sparse attention indexer
+    "self_attn.indexer.wq_b.weight": "idx_q", "self_attn.indexer.wk.weight": "idx_k", "self_attn.indexer.k_norm.weight": "idx_k_norm",
+    "self_attn.indexer.k_norm.bias": "idx_k_norm_bias", "self_attn.indexer.weights_proj.weight": "idx_weights",
 }
 # norm placement differs by block kind: the same checkpoint name means a different role
 POST_BLOCK = {"post_attention_layernorm.weight": "attn_post_norm", "post_feedforward_layernorm.weight": "ffn_post_norm"}

@@ -111,6 +111,10 @@ class DecoderConfig:
     norm_offset: float = 0.0                # checkpoint stores norm weights as w - offset (gemma: 1.0); added at load
     rope_layers: Optional[list] = None      # per-layer flag: 1 = rotary applied, 0 = no position signal (smollm3 NoPE layers)
     rope_interleaved: bool = False          # checkpoint stores rotary channels as interleaved pairs (deepseek): rows are re-ordered at load
+    latent_norm_eps: Optional[float] = None  # epsilon of the norms inside latent attention (None: norm_eps)
+    index_topk: int = 0                     # sparse attention: keys each query keeps, picked by the indexer (0: dense attention)
+    index_n_heads: int = 0
+    index_head_dim: int = 0
     mrope_sections: Optional[list] = None   # channel pairs of the time / row / column rotary streams (Qwen2.5-VL); None: one stream
     bos_token: int = 1
     eos_token: int = 2
@@ -171,10 +175,15 @@ class DecoderConfig:
                 and not self.out_bias and not self.expert_bias and self.swiglu_limit == 0 and not self.router_bias
                 and self.norm_kind == "rms" and self.gated_ffn and self.pos == "rope" and not self.embed_norm)
 
+    @property
+    def mla_eps(self) -> float:
+        return self.norm_eps if self.latent_norm_eps is None else self.latent_norm_eps
+
     def device_gaps(self) -> list:
         """Features of this configuration that the device program does not implement (empty = runs on the device);
         the CPU oracle evaluates all of them."""
         g = []
+        if self.index_topk: g.append("sparse attention indexer")
         if self.norm_kind != "rms" and self.block != "pre": g.append("LayerNorm with a post norm")
         if self.block != "pre" and self.is_moe: g.append(f"{self.block}-norm block with routed experts")
         if self.gated_ffn and self.act not in ("silu", "gelu_tanh", "gelu_erf"): g.append(f"{self.act} gated FFN")

@@ -101,6 +101,10 @@ class Model:
                 s.update({p + "attn_kv_a": (c.kv_lora_rank + c.qk_rope_dim, H), p + "attn_kv_a_norm": (c.kv_lora_rank,),
                           p + "attn_kv_b": (c.n_heads * (c.qk_nope_dim + c.v_head_dim), c.kv_lora_rank),
                           p + "attn_o": (H, c.n_heads * c.v_head_dim)})
+                if c.index_topk:
+                    s.update({p + "idx_q": (c.index_n_heads * c.index_head_dim, c.q_lora_rank), p + "idx_k": (c.index_head_dim, H),
+                              p + "idx_k_norm": (c.index_head_dim,), p + "idx_k_norm_bias": (c.index_head_dim,),
+                              p + "idx_weights": (c.index_n_heads, H)})
             elif kind == "attention":
                 s.update({p + "attn_q": (c.q_size, H), p + "attn_k": (c.kv_size, H), p + "attn_v": (c.kv_size, H),
                           p + "attn_o": (H, c.q_size)})
@@ -296,19 +300,47 @@ class Model:
                 o = o + b.broadcast(W(p + "attn_o_bias"), o.shape)
             return o
 
+        def sparse_mask(p: str, x: Traced, q_resid: Traced, cos: Traced, sin: Traced, mask: Traced) -> Traced:
+            """Sparse attention indexer (components/dsa.rs): a light multi-head scorer over its own cached keys ranks the
+            visible keys of every query, ``score[t, s] = sum_h w[t, h] * relu(q[t, h] . k[s]) / sqrt(Di)``; the
+            ``index_topk`` best stay visible to the main attention.  The rotary part leads each indexer head and is
+            rotated half-split."""
+            ni, Di, dr = c.index_n_heads, c.index_head_dim, c.qk_rope_dim
+            q = b.reshape(O.linear(b, q_resid, W(p + "idx_q")), (R * T, ni, Di))
+            q = b.concat([O.rope(b, b.slice(q, -1, 0, dr), cos, sin, dr), b.slice(q, -1, dr, Di - dr)], -1)
+            k = O.layernorm(b, O.linear(b, x, W(p + "idx_k")), W(p + "idx_k_norm"), W(p + "idx_k_norm_bias"), 1e-6)
+            k = b.reshape(k, (R * T, 1, Di))
+            k = b.concat([O.rope(b, b.slice(k, -1, 0, dr), cos, sin, dr), b.slice(k, -1, dr, Di - dr)], -1)
+            if not spec.paged:
+                raise ValueError("the sparse attention indexer is traced over paged pools")
+            pool = b.state(p + "idx_pool", (spec.slots, 1, Di), spec.kv_dtype, "blocked").cast(F32)
+            pool2 = b.scatter_update(pool, write_map, k)
+            b.output(pool2.cast(spec.kv_dtype), p + "idx_pool.next", "state_next", p + "idx_pool")
+            keys = O.paged_view(b, pool2.cast(spec.kv_dtype).cast(F32), read_map)            # [R, 1, cap, Di]
+            qh = b.transpose(b.reshape(q, (R, T, ni, Di)), (0, 2, 1, 3))                        # [R, ni, T, Di]
+            kt = b.broadcast(b.transpose(keys, (0, 1, 3, 2)), (R, ni, Di, cap))
+            dots = O.relu(b, b.matmul(qh, kt, "exact") * (Di ** -0.5))                          # [R, ni, T, cap]
+            wts = O.linear(b, x, W(p + "idx_weights"), precision="exact") * (ni ** -0.5)        # [R*T, ni]
+            wts = b.transpose(b.reshape(wts, (R, T, ni)), (0, 2, 1))
+            score = (dots * b.broadcast(b.reshape(wts, (R, ni, T, 1)), dots.shape)).transpose(0, 2, 3, 1).sum(-1) + mask
+            rank = b.reshape(O.stable_descending_rank(b, b.reshape(score, (R * T, cap))), (R, T, cap))
+            keep = O.lnot(b, b.binary("ge", rank, b.broadcast(b.scalar(c.index_topk, I32), rank.shape)))
+            return b.select(keep, mask, b.broadcast(b.scalar(O.MASK_HIDDEN, F32), mask.shape))
+
         def mla_attention(l: int, x: Traced) -> Traced:
             """Multi-head latent attention in its expanded (prefill) form: queries and keys are the concatenation of a
             per-head no-position part and a rotary part; the rotary key is one head shared by all (components/mla.rs)."""
             p = f"layers.{l}."
             dn, dr, dv, nh = c.qk_nope_dim, c.qk_rope_dim, c.v_head_dim, c.n_heads
             if c.q_lora_rank:
-                qa = O.rmsnorm(b, O.linear(b, x, W(p + "attn_q_a")), W(p + "attn_q_a_norm"), c.norm_eps)
+                qa = O.rmsnorm(b, O.linear(b, x, W(p + "attn_q_a")), W(p + "attn_q_a_norm"), c.mla_eps)
                 q = O.linear(b, qa, W(p + "attn_q_b"))
             else:
+                qa = None
                 q = O.linear(b, x, W(p + "attn_q"))
             q = b.reshape(q, (R * T, nh, dn + dr))
             kva = O.linear(b, x, W(p + "attn_kv_a"))                          # [L, kv_lora + dr]
-            ckv = O.rmsnorm(b, b.slice(kva, -1, 0, c.kv_lora_rank), W(p + "attn_kv_a_norm"), c.norm_eps)
+            ckv = O.rmsnorm(b, b.slice(kva, -1, 0, c.kv_lora_rank), W(p + "attn_kv_a_norm"), c.mla_eps)
             k_rope = b.reshape(b.slice(kva, -1, c.kv_lora_rank, dr), (R * T, 1, dr))
             kvb = b.reshape(O.linear(b, ckv, W(p + "attn_kv_b")), (R * T, nh, dn + dv))
             cos, sin = rope_of(l)
@@ -319,7 +351,10 @@ class Model:
             vf = b.slice(kvb, -1, dn, dv)
             K, V = kv_through_cache(p, kf, vf, dn + dr, dv)
             qh = b.transpose(b.reshape(qf, (R, T, nh, dn + dr)), (0, 2, 1, 3))
-            a = O.attention_masked(b, qh, K, V, mask_of(l), scale, 1, 0.0)
+            mask = mask_of(l)
+            if c.index_topk:
+                mask = sparse_mask(p, x, qa, cos, sin, mask)
+            a = O.attention_masked(b, qh, K, V, mask, scale, 1, 0.0)
             a = b.reshape(b.transpose(a, (0, 2, 1, 3)), (R * T, nh * dv))
             return O.linear(b, a, W(p + "attn_o"))
 

@@ -271,9 +271,37 @@ def _deepseek(c, family: str) -> DecoderConfig:
                 first_dense_layers=int(c.get("first_k_dense_replace") or 0),
                 routed_scale=float(c.get("routed_scaling_factor") or 1.0), norm_topk_prob=bool(c.get("norm_topk_prob", v3)))
     cfg.n_kv_heads = cfg.n_heads
+    cfg.latent_norm_eps = 1e-6          # the norms of the low-rank query / key-value projections keep their own epsilon
     if v3:
         cfg.router, cfg.router_select_bias = "sigmoid", True
         cfg.n_group, cfg.topk_group = int(c.get("n_group") or 1), int(c.get("topk_group") or 1)
+    return cfg
+
+
+def _with_indexer(cfg: DecoderConfig, c: dict) -> DecoderConfig:
+    """Sparse attention fields of DeepSeek-V3.2 style headers (``index_topk`` / ``index_n_heads`` / ``index_head_dim``)."""
+    cfg.index_topk, cfg.index_n_heads = int(c.get("index_topk") or 0), int(c.get("index_n_heads") or 0)
+    cfg.index_head_dim = int(c.get("index_head_dim") or 0)
+    if cfg.index_topk and not cfg.q_lora_rank:
+        raise UnsupportedFamily("a sparse attention indexer needs the low-rank query projection it reads")
+    if cfg.index_topk and cfg.index_head_dim < cfg.qk_rope_dim:
+        raise UnsupportedFamily("indexer heads narrower than the rotary part")
+    return cfg
+
+
+def _deepseek32(c):
+    cfg = _with_indexer(_deepseek(c, "deepseek3"), c)
+    cfg.family = "deepseek32"
+    return cfg
+
+
+def _glm_moe_dsa(c):
+    """GLM with latent attention and the sparse attention indexer: DeepSeek-V3 style stack, half-split rotary, dense or
+    routed FFN by ``mlp_layer_types``."""
+    cfg = _with_indexer(_deepseek({**c, "rope_interleave": False, "first_k_dense_replace": 0}, "deepseek3"), c)
+    cfg.family = "glm_moe_dsa"
+    kinds = list(c.get("mlp_layer_types") or [])[:cfg.n_layers]
+    cfg.dense_layers = [i for i, k in enumerate(kinds) if k == "dense"] or None
     return cfg
 
 
@@ -445,6 +473,8 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("minimax_m2", ["minimax_m2"], ["minimax-m2"], _minimax_m2),
     FamilyEntry("deepseek2", ["deepseek_v2"], ["deepseek2"], _deepseek2),
     FamilyEntry("deepseek3", ["deepseek_v3"], ["deepseek2"], _deepseek3),
+    FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], _deepseek32),
+    FamilyEntry("glm_moe_dsa", ["glm_moe_dsa"], [], _glm_moe_dsa),
     FamilyEntry("nemotron_h", ["nemotron_h"], ["nemotron_h"], _nemotron_h),
     FamilyEntry("qwen3next", ["qwen3_next"], ["qwen3next"], _qwen3next),
     FamilyEntry("qwen38_27b", ["qwen3_5", "qwen3_5_text"], ["qwen35"], _qwen35),
@@ -452,7 +482,6 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("idefics3", ["idefics3", "smolvlm"], [], _idefics3, kind="vlm"),
     FamilyEntry("qwen_vl", ["qwen2_5_vl"], [], _qwen_vl, kind="vlm"),
     # families the reference ships whose mixers are not built here: refused by name
-    FamilyEntry("deepseek32", ["deepseek_v32"], ["deepseek32"], None, "sparse attention indexer"),
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
     FamilyEntry("qwen38", ["qwen4_exp"], ["qwen4exp"], None, "block-indexed sparse attention, hyper-connection residual streams, n-gram embeddings"),
     FamilyEntry("glm53_flash", ["glm5_flash"], ["glm53"], None, "kimi delta attention, hyper-connection residual streams"),

@@ -23,6 +23,13 @@ SAMPLES = {
     "deepseek3": dict(model_type="deepseek_v3", n_routed_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048, kv_lora_rank=512,
                       q_lora_rank=1536, qk_rope_head_dim=64, qk_nope_head_dim=128, v_head_dim=128, n_shared_experts=1, n_group=8,
                       topk_group=4, first_k_dense_replace=3),
+    "deepseek32": dict(model_type="deepseek_v32", n_routed_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048, kv_lora_rank=512,
+                       q_lora_rank=1536, qk_rope_head_dim=64, qk_nope_head_dim=128, v_head_dim=128, n_shared_experts=1, n_group=8,
+                       topk_group=4, first_k_dense_replace=3, index_topk=2048, index_n_heads=64, index_head_dim=128),
+    "glm_moe_dsa": dict(model_type="glm_moe_dsa", n_routed_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048,
+                        kv_lora_rank=512, q_lora_rank=2048, qk_rope_head_dim=64, qk_nope_head_dim=192, v_head_dim=256,
+                        n_shared_experts=1, mlp_layer_types=["dense", "sparse", "sparse", "sparse"], index_topk=2048,
+                        index_n_heads=32, index_head_dim=128),
     "nemotron_h": dict(model_type="nemotron_h", hybrid_override_pattern="M-M*", mamba_num_heads=128, mamba_head_dim=64, ssm_state_size=128, n_groups=8),
     "qwen3next": dict(model_type="qwen3_next", linear_num_value_heads=32, linear_num_key_heads=16, linear_key_head_dim=128,
                       linear_value_head_dim=128, num_experts=512, num_experts_per_tok=10, moe_intermediate_size=512,

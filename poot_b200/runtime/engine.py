@@ -551,7 +551,7 @@ class DecoderEngine:
         if "q_a" in m:
             qa = self._linear(x, m["q_a"], K.EPI_STORE, self.mla_qa[:T, :cfg.q_lora_rank])
             self._count()
-            K.rmsnorm(qa, m["q_a_norm"], cfg.norm_eps, out=qa)
+            K.rmsnorm(qa, m["q_a_norm"], cfg.mla_eps, out=qa)
             q = self._linear(qa, m["q_b"], K.EPI_STORE, self.q[:T])
         else:
             q = self._linear(x, m["q"], K.EPI_STORE, self.q[:T])
@@ -559,7 +559,7 @@ class DecoderEngine:
         ckv = self.mla_ckv[:T]
         ckv.copy_(kva[:, :cfg.kv_lora_rank])
         self._count(3)
-        K.rmsnorm(ckv, m["kv_a_norm"], cfg.norm_eps, out=ckv)
+        K.rmsnorm(ckv, m["kv_a_norm"], cfg.mla_eps, out=ckv)
         kvb = self._linear(ckv, m["kv_b"], K.EPI_STORE, self.mla_kvb[:T])
         kvl = self._kv_of[l]
         K.mla_qkv_write(q, kvb, kva, cfg.kv_lora_rank, self.mla_q[:T], self.kv.k(kvl), self.kv.v(kvl), self.positions[:T],

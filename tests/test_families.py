@@ -43,6 +43,10 @@ FAMILIES = {
                   "first_k_dense_replace": 1, "kv_lora_rank": 24, "q_lora_rank": 32, "qk_rope_head_dim": 8,
                   "qk_nope_head_dim": 16, "v_head_dim": 12, "n_shared_experts": 1, "n_group": 4, "topk_group": 2,
                   "num_key_value_heads": 4},
+    "deepseek32": {"model_type": "deepseek_v32", "n_routed_experts": 8, "num_experts_per_tok": 3, "moe_intermediate_size": 32,
+                   "first_k_dense_replace": 1, "kv_lora_rank": 24, "q_lora_rank": 32, "qk_rope_head_dim": 8,
+                   "qk_nope_head_dim": 16, "v_head_dim": 12, "n_shared_experts": 1, "n_group": 4, "topk_group": 2,
+                   "num_key_value_heads": 4, "index_topk": 6, "index_n_heads": 4, "index_head_dim": 16},
     "nemotron_h": {"model_type": "nemotron_h", "hybrid_override_pattern": "M-*E", "mamba_num_heads": 4, "mamba_head_dim": 16,
                    "ssm_state_size": 8, "n_groups": 2, "conv_kernel": 4, "n_routed_experts": 4, "num_experts_per_tok": 2,
                    "moe_intermediate_size": 32, "moe_shared_expert_intermediate_size": 48, "layer_norm_epsilon": 1e-5},
@@ -99,7 +103,7 @@ def test_supported_family_traces_compiles_and_decodes(name):
 
 def test_refused_families_say_what_is_missing():
     reg = Registry.builtin()
-    for mt, word in (("deepseek_v32", "sparse attention"), ("glm5_flash", "delta attention"),
+    for mt, word in (("deepseek_v4", "compressed attention"), ("glm5_flash", "delta attention"),
                      ("qwen4_exp", "hyper-connection")):
         with pytest.raises(UnsupportedFamily) as e:
             reg.resolve_hf({**BASE, "model_type": mt})
@@ -109,7 +113,7 @@ def test_refused_families_say_what_is_missing():
     with pytest.raises(UnsupportedFamily):
         reg.resolve_hf({"model_type": "mpt", "d_model": 64, "n_heads": 4, "n_layers": 2, "vocab_size": 200,
                         "attn_config": {"alibi": False}})
-    assert len(reg.listed()) == 28 and len(reg.supported()) == 24
+    assert len(reg.listed()) == 29 and len(reg.supported()) == 26
 
 
 def test_device_gaps_name_what_the_device_program_lacks():

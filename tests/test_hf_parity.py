@@ -41,6 +41,13 @@ CASES = {
                    final_logit_softcapping=3.0),
     "gemma3": dict(model_type="gemma3_text", query_pre_attn_scalar=24, sliding_window=6, num_hidden_layers=3,
                    layer_types=["sliding_attention", "sliding_attention", "full_attention"]),
+    # latent attention behind the sparse attention indexer: every query keeps its 5 best-scored keys (DeepSeek-V3.2's
+    # mechanism; six indexer heads keep exact zero ties of the rectified scores out of the cut)
+    "glm_moe_dsa": dict(model_type="glm_moe_dsa", num_hidden_layers=3, q_lora_rank=32, kv_lora_rank=24, qk_rope_head_dim=8,
+                        qk_nope_head_dim=16, v_head_dim=12, num_key_value_heads=4, head_dim=8, n_routed_experts=8,
+                        num_experts_per_tok=3, moe_intermediate_size=32, n_shared_experts=1, n_group=2, topk_group=1,
+                        mlp_layer_types=["dense", "sparse", "sparse"], index_topk=5, index_n_heads=6, index_head_dim=16,
+                        routed_scaling_factor=2.5, pad_token_id=0, _scale=3.0),
     # gemma4: head width by layer type, proportional rope, scores without a scale, weightless v norm, layer scalars ...
     "gemma4": dict(model_type="gemma4_text", num_hidden_layers=4, global_head_dim=32, sliding_window=6, vocab_size_per_layer_input=200,
                    layer_types=["sliding_attention", "full_attention"] * 2, hidden_size_per_layer_input=0, pad_token_id=0, _scale=2.0),
@@ -120,7 +127,7 @@ def test_logits_equal_the_hugging_face_forward(name, tmp_path):
 
 
 @pytest.mark.parametrize("name", ["llama", "gemma3", "bloom", "deepseek3", "gpt_oss", "qwen3next", "nemotron_h",
-                                  "gemma4-per-layer-embeddings-shared-kv"])
+                                  "gemma4-per-layer-embeddings-shared-kv", "glm_moe_dsa"])
 def test_driver_over_the_oracle_engine_generates_what_hugging_face_generates(name, tmp_path):
     """End to end on the host: checkpoint directory -> ``LLM.oracle`` -> driver (paged K/V through block tables,
     chunked prefill, two sequences in flight) gives the greedy continuation ``transformers`` gives."""
