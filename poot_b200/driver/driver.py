@@ -64,6 +64,7 @@ class StepInputs:
     adapter_rows: Optional[np.ndarray] = None   # [T] int32 adapter slot of every token row (-1 = none); None = no row uses one
     embed_flags: Optional[np.ndarray] = None    # [T] int32, 1 = the token's embedding is replaced by its row of embed_rows
     embed_rows: Optional[np.ndarray] = None     # [T, hidden] f32 (rows without a flag are zero); None = no token is replaced
+    rope_positions: Optional[np.ndarray] = None  # [3, T] int32 rotary position streams (time, row, column); None = the positions
 
 
 @dataclass
@@ -93,6 +94,8 @@ class Sequence_:
     adapter_slot: int = -1                                 # resident LoRA adapter of the sequence (-1 = base model)
     embed_pos: Optional[np.ndarray] = None                 # sorted prompt positions whose embeddings are replaced ...
     embed_rows: Optional[np.ndarray] = None                # ... by these rows [len(embed_pos), hidden] (image rows of a VLM)
+    rope_prefix: Optional[np.ndarray] = None               # [3, prompt_len] rotary position streams of the prompt (sectioned rope)
+    rope_delta: int = 0                                    # rotary position minus sequence index for every later token
 
     @property
     def pending(self) -> int:
@@ -156,12 +159,15 @@ class Driver:
         return bool(self._free_rows) and need <= free + (len(self.prefix) if self.prefix is not None else 0)
 
     def open(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, identity: int = BASE_IDENTITY,
-             guided=None, adapter_slot: int = -1, embeds=None) -> int:
+             guided=None, adapter_slot: int = -1, embeds=None, rope_positions=None) -> int:
         """``adapter_slot``: slot of a resident LoRA adapter the sequence runs with (-1 = the base model).  K/V computed
         under one adapter is not valid under another, so the prefix-cache identity is taken per slot.
         ``embeds``: ``(positions, rows[len(positions), hidden])``: rows of another modality that replace the embeddings
         of those prompt tokens (crates/poot-llm/src/driver: ``generate_with_inputs``).  The tokens at those positions are
-        placeholders that say nothing about the rows, so the prefix-cache identity also covers the rows' content."""
+        placeholders that say nothing about the rows, so the prefix-cache identity also covers the rows' content.
+        ``rope_positions[3, len(prompt)]``: the prompt's rotary position streams under a sectioned rope (an image's
+        tokens carry (start, start + row, start + column)); later tokens continue one past the largest value.  A token's
+        K/V slot and causal order stay its index in the sequence."""
         params = params or SamplingParams()
         embed_pos = embed_rows = None
         if embeds is not None:
@@ -169,12 +175,20 @@ class Driver:
             embed_rows = np.ascontiguousarray(embeds[1], dtype=np.float32).reshape(len(embed_pos), -1)
             if len(embed_pos) and (np.any(np.diff(embed_pos) <= 0) or embed_pos[0] < 0 or embed_pos[-1] >= len(prompt)):
                 raise DriverError("embedding rows must name distinct prompt positions in ascending order")
+        rope_prefix = None
+        if rope_positions is not None:
+            rope_prefix = np.ascontiguousarray(rope_positions, dtype=np.int32).reshape(3, -1)
+            if rope_prefix.shape[1] != len(prompt) or rope_prefix.min() < 0:
+                raise DriverError("rotary position streams must give three non-negative values per prompt token")
         if adapter_slot >= 0 and identity == BASE_IDENTITY:
             identity = (BASE_IDENTITY ^ (0x9E3779B97F4A7C15 * (adapter_slot + 1))) & 0xFFFFFFFFFFFFFFFF
         if embed_pos is not None and len(embed_pos):
             import zlib
             digest = zlib.crc32(embed_rows.tobytes(), zlib.crc32(embed_pos.tobytes()))
             identity = (identity ^ (0xC2B2AE3D27D4EB4F * (digest + 1))) & 0xFFFFFFFFFFFFFFFF
+        if rope_prefix is not None:
+            import zlib
+            identity = (identity ^ (0x165667B19E3779F9 * (zlib.crc32(rope_prefix.tobytes()) + 1))) & 0xFFFFFFFFFFFFFFFF
         params.validate()
         prompt = [int(t) for t in prompt]
         if not prompt:
@@ -208,6 +222,8 @@ class Driver:
                         seed=params.seed if params.seed is not None else (sid * 2654435761) & 0x7FFFFFFF)
         seq.adapter_slot = int(adapter_slot)
         seq.embed_pos, seq.embed_rows = embed_pos, embed_rows
+        if rope_prefix is not None:
+            seq.rope_prefix, seq.rope_delta = rope_prefix, int(rope_prefix.max()) + 1 - len(prompt)
         for t in prompt:
             seq.counts[t] = seq.counts.get(t, 0) + 1
         self.seqs[sid] = seq
@@ -268,8 +284,15 @@ class Driver:
         adjust_rows, guided_rows, want_lp = {}, {}, False
         adapter_rows = np.full(Tp, -1, np.int32) if any(s.adapter_slot >= 0 for s, _ in rows) else None
         embed_flags = embed_vals = None
+        rope_pos = np.zeros((3, Tp), np.int32) if any(s.rope_prefix is not None for s, _ in rows) else None
         for s, piece in rows:
             p0 = s.computed
+            if rope_pos is not None:
+                idx = np.arange(p0, p0 + piece)
+                n_pre = 0 if s.rope_prefix is None else max(0, min(piece, s.rope_prefix.shape[1] - p0))
+                if n_pre:
+                    rope_pos[:, off:off + n_pre] = s.rope_prefix[:, p0:p0 + n_pre]
+                rope_pos[:, off + n_pre:off + piece] = idx[n_pre:] + s.rope_delta
             if adapter_rows is not None:
                 adapter_rows[off:off + piece] = s.adapter_slot
             if s.embed_pos is not None and p0 < s.prompt_len:
@@ -329,7 +352,7 @@ class Driver:
         check_write_slots(slots[:T])            # two rows writing one K/V slot in a step would race on the device
         self.stats["padded_tokens"] += Tp - T
         return StepInputs(tokens, positions, slots, row_seq, row_ctx, logit_idx, rule, params, top_k, seeds, adjust,
-                          want_lp, T, B, adapter_rows, embed_flags, embed_vals)
+                          want_lp, T, B, adapter_rows, embed_flags, embed_vals, rope_pos)
 
     def step(self, seq_ids: Optional[Iterable[int]] = None) -> List[RowResult]:
         rows = self.plan(seq_ids)
@@ -398,8 +421,9 @@ class Driver:
         return {"registered_tokens": registered, "generated": s.generated, "cached_tokens": s.cached_tokens}
 
     # ------------------------------------------------------------------------------------------------ convenience
-    def generate(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, on_token=None, embeds=None) -> List[int]:
-        sid = self.open(prompt, params, embeds=embeds)
+    def generate(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, on_token=None, embeds=None,
+                 rope_positions=None) -> List[int]:
+        sid = self.open(prompt, params, embeds=embeds, rope_positions=rope_positions)
         out: List[int] = []
         try:
             while True:

@@ -128,7 +128,10 @@ class DeviceStepEngine:
         embeds = inp.embed_flags is not None
         if embeds:
             e.bind_embeds(torch.from_numpy(inp.embed_flags[:T]), torch.from_numpy(inp.embed_rows[:T]))
-        shape = StepShape(T, B, inp.sampler, False, inp.adjust is not None, guided, inp.want_logprobs, lora, embeds)
+        mrope = inp.rope_positions is not None
+        if mrope:
+            e.bind_rope_streams(torch.from_numpy(inp.rope_positions[:, :T]))
+        shape = StepShape(T, B, inp.sampler, False, inp.adjust is not None, guided, inp.want_logprobs, lora, embeds, mrope)
         import time as _time
         t0 = _time.perf_counter()
         ev = None
@@ -189,17 +192,18 @@ class OracleStepEngine:
     def write_block_table(self, row: int, blocks) -> None:
         self.block_tables[row, :len(blocks)] = np.asarray(blocks, np.int32)
 
-    def _graph(self, tokens: int, capacity: int, embeds: bool = False):
-        key = (tokens, capacity, embeds)
+    def _graph(self, tokens: int, capacity: int, embeds: bool = False, mrope: bool = False):
+        key = (tokens, capacity, embeds, mrope)
         if key not in self.graphs:
             from ..models.model import StepSpec
             g = self.model.trace(StepSpec(rows=1, tokens=tokens, capacity=capacity, paged=True,
-                                          pool_slots=self.num_blocks * self.block, embeds=embeds))
+                                          pool_slots=self.num_blocks * self.block, embeds=embeds, mrope=mrope))
             self.graphs[key] = self.graph_transform(g) if self.graph_transform is not None else g
         return self.graphs[key]
 
     def _segment(self, row: int, tokens: np.ndarray, positions: np.ndarray, slots: np.ndarray, ctx: int,
-                 embed_flags: Optional[np.ndarray] = None, embed_rows: Optional[np.ndarray] = None) -> np.ndarray:
+                 embed_flags: Optional[np.ndarray] = None, embed_rows: Optional[np.ndarray] = None,
+                 rope_positions: Optional[np.ndarray] = None) -> np.ndarray:
         from ..oracle.eval import eval_graph
         blocks = max(1, -(-ctx // self.block))
         cap_blocks = 1
@@ -208,11 +212,14 @@ class OracleStepEngine:
         cap_blocks = min(cap_blocks, self.max_blocks)
         cap = cap_blocks * self.block
         embeds = embed_flags is not None and bool(embed_flags.any())
-        g = self._graph(len(tokens), cap, embeds)
+        mrope = rope_positions is not None and bool(getattr(self.model.cfg, "mrope_sections", None))
+        g = self._graph(len(tokens), cap, embeds, mrope)
         bt = self.block_tables[row, :cap_blocks].astype(np.int64)
         read = (bt[:, None] * self.block + np.arange(self.block)[None, :]).reshape(1, cap).astype(np.int32)
         inputs = {"tokens": tokens.reshape(1, -1).astype(np.int32), "positions": positions.reshape(1, -1).astype(np.int32),
                   "read_map": read, "write_map": slots.astype(np.int32)}
+        if mrope:
+            inputs["rope_positions"] = np.ascontiguousarray(rope_positions, dtype=np.int32)
         if embeds:
             inputs["embed_flags"], inputs["embed_rows"] = embed_flags.astype(np.int32), embed_rows.astype(np.float32)
         fresh = int(positions[0]) == 0        # a sequence's first segment starts its recurrences from zero
@@ -251,7 +258,8 @@ class OracleStepEngine:
                 ef = inp.embed_flags[start:end] if inp.embed_flags is not None else None
                 er = inp.embed_rows[start:end] if inp.embed_flags is not None else None
                 out = self._segment(row, inp.tokens[start:end], inp.positions[start:end], inp.slots[start:end],
-                                    int(inp.row_ctx[end - 1]), ef, er)
+                                    int(inp.row_ctx[end - 1]), ef, er,
+                                    inp.rope_positions[:, start:end] if inp.rope_positions is not None else None)
                 if end - 1 in want:
                     logits[want[end - 1]] = out
             start = end

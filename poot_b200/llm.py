@@ -161,9 +161,10 @@ class LLM:
 
     # ---- generation ----------------------------------------------------------------------------------------------
     def generate_tokens(self, prompt: Iterable[int], params: Optional[SamplingParams] = None, on_token=None,
-                        embeds=None) -> List[int]:
-        """``embeds``: ``(positions, rows)`` replacing the embeddings of those prompt tokens (image rows of a VLM)."""
-        return self.driver.generate(list(prompt), params, on_token, embeds=embeds)
+                        embeds=None, rope_positions=None) -> List[int]:
+        """``embeds``: ``(positions, rows)`` replacing the embeddings of those prompt tokens (image rows of a VLM);
+        ``rope_positions[3, len(prompt)]``: the prompt's rotary position streams under a sectioned rope."""
+        return self.driver.generate(list(prompt), params, on_token, embeds=embeds, rope_positions=rope_positions)
 
     def generate(self, prompt: str, params: Optional[SamplingParams] = None, on_text=None) -> str:
         dec = StreamDecoder(self.tokenizer)

@@ -73,8 +73,7 @@ def rows():
             continue
         if e.kind == "vlm" and model.cfg.mrope_sections:
             out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "text stack",
-                        "a device program for the vision tower; three rotary position streams per token in the driver "
-                        "(images run through `caption` / `VisionLLM` on the host evaluator)"))
+                        "a device program for the vision tower (it is evaluated on the host, once per image)"))
             continue
         if e.kind == "vlm":
             out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "text stack",

@@ -35,6 +35,7 @@ class StepShape:
     logprobs: bool = False  # record the picked token's log-probability
     lora: bool = False      # some row of the step selects a resident adapter (adds the per-row low-rank terms)
     embeds: bool = False    # rows of another modality replace the embeddings of flagged tokens (``bind_embeds``)
+    mrope: bool = False     # sectioned rotary: the step's cos / sin rows were assembled per token (``bind_rope_streams``)
 
 
 class KVPool:
@@ -229,6 +230,7 @@ class DecoderEngine:
             comm.attach(self)
         self.lora = None                    # bank of resident adapters, created by enable_adapters()
         self.embed_rows = self.embed_flags = None   # staging of rows that replace embeddings, created by bind_embeds()
+        self.rope_cos_tok = self.rope_sin_tok = None  # per-token rotary rows of a sectioned rope, created by bind_rope_streams()
         self._graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.launches_per_step: Dict[Tuple, int] = {}
         self._launch_counter = 0
@@ -245,6 +247,30 @@ class DecoderEngine:
         T = flags.numel()
         self.embed_flags[:T].copy_(flags, non_blocking=True)
         self.embed_rows[:T].copy_(rows, non_blocking=True)
+
+    def bind_rope_streams(self, streams: torch.Tensor) -> None:
+        """Stage the rotary rows of the next step under a sectioned rope: ``streams[3, T]`` int32 are the (time, row,
+        column) positions of every token; channel pair ``j`` of a token's row is read from the table at the position of
+        the stream that owns ``j``.  The rows land in fixed buffers indexed by the token's place in the step, so the
+        rotary kernel reads them with positions ``0..T-1`` and a captured step graph replays over them."""
+        cfg = self.cfg
+        if not cfg.mrope_sections:
+            raise ValueError(f"{cfg.family}: rotary position streams need a sectioned rope")
+        half = cfg.rot // 2
+        if self.rope_cos_tok is None:
+            dev = self.device
+            self.rope_cos_tok = torch.zeros(self.max_tokens, half, dtype=torch.float32, device=dev)
+            self.rope_sin_tok = torch.zeros(self.max_tokens, half, dtype=torch.float32, device=dev)
+            self.rope_iota = torch.arange(self.max_tokens, dtype=torch.int32, device=dev)
+            owner = [i % 3 for i, n in enumerate(cfg.mrope_sections) for _ in range(n)]
+            if len(owner) != half:
+                raise ValueError(f"mrope sections {cfg.mrope_sections} do not cover {half} channel pairs")
+            self._rope_owner = torch.tensor(owner, dtype=torch.long, device=dev).view(1, 1, half)
+        T = streams.shape[1]
+        idx = streams.to(device=self.device, dtype=torch.long)                       # [3, T]
+        own = self._rope_owner.expand(1, T, half)
+        self.rope_cos_tok[:T].copy_(self.cos[idx].gather(0, own)[0])
+        self.rope_sin_tok[:T].copy_(self.sin[idx].gather(0, own)[0])
 
     def enable_adapters(self, slots: int = 8, max_rank: int = 64):
         """Create the bank of resident LoRA adapters (per-row selection); see ``runtime/lora_bank.py``."""
@@ -416,9 +442,12 @@ class DecoderEngine:
                 self._wide_qk_norm(qkv, L, T)
                 qn = kn = None
             cos, sin = self._rope_tables_of(w.layer0 + l)
+            rope_at = self.positions[:T]
+            if shape.mrope:                     # rows assembled per token by bind_rope_streams: row t is token t's
+                cos, sin, rope_at = self.rope_cos_tok, self.rope_sin_tok, self.rope_iota[:T]
             self._count()
             kvl = self._kv_of[l]
-            K.rope_kv_write(qkv, self.q[:T], self.kv.k(kvl), self.kv.v(kvl), self.positions[:T], self.slots[:T],
+            K.rope_kv_write(qkv, self.q[:T], self.kv.k(kvl), self.kv.v(kvl), rope_at, self.slots[:T],
                             cos, sin, self.hq, self.hkv, D, cfg.rot, qn, kn, cfg.norm_eps)
             self._attention(l, T, T, B)
             if L.wgate is not None:             # gated attention: the output is scaled by sigmoid of a projection of the layer input
@@ -787,7 +816,7 @@ class DecoderEngine:
     def _key(self, shape: StepShape):
         flash_only = self.flash_ok and shape.tokens > shape.logit_rows and self._flash_only
         return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain, shape.adjust, shape.guided, shape.logprobs,
-                flash_only, shape.lora, shape.embeds)
+                flash_only, shape.lora, shape.embeds, shape.mrope)
 
     def prepare(self, shape: StepShape) -> None:
         """Warm up and capture the step graph for ``shape`` (never done in the serving path afterwards)."""

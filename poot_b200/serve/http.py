@@ -339,9 +339,9 @@ def make_handler(state: ServerState):
                 if isinstance(n, bool) or not isinstance(n, int) or not (1 <= n <= 16):
                     raise ApiError(400, "n must be an integer in [1, 16]", param="n")
                 chat = path.endswith("chat/completions")
-                self._embeds = None
+                self._embeds = self._rope = None
                 prompt_ids, guided_spec, tools = self._prompt(req, chat)
-                embeds = self._embeds
+                embeds, rope_positions = self._embeds, self._rope
                 params = sampling_from_request(req)
                 jobs: List[Job] = []
                 try:
@@ -351,7 +351,7 @@ def make_handler(state: ServerState):
                         if guided_spec is not None:
                             g = guided_mod.build_constraint(guided_spec, eng.tk, eng.driver.eos_token, tools)
                         jobs.append(eng.submit(Job(prompt_ids, sp, stream=bool(req.get("stream")), guided=g,
-                                                   adapter_slot=adapter_slot, embeds=embeds)))
+                                                   adapter_slot=adapter_slot, embeds=embeds, rope_positions=rope_positions)))
                 except queue.Full:
                     for j in jobs:
                         j.cancelled.set()
@@ -420,12 +420,12 @@ def make_handler(state: ServerState):
                 raise ApiError(400, f"prompt of {len(ids)} tokens exceeds the context of {eng.driver.max_seq_len}")
             return ids, guided_spec, tools
 
-        _embeds = None
+        _embeds = _rope = None
 
         def _image_prompt(self, msgs) -> Optional[List[int]]:
             """Messages with image parts: prompt tokens with the image placeholders expanded, and the image rows staged
             for the job (``self._embeds``).  ``None`` when no message holds an image."""
-            self._embeds = None
+            self._embeds = self._rope = None
             has = any(isinstance(m, dict) and isinstance(m.get("content"), list) and
                       any(isinstance(p, dict) and p.get("type") in ("image_url", "image") for p in m["content"]) for m in msgs)
             if not has:
@@ -438,6 +438,7 @@ def make_handler(state: ServerState):
                     raise ValueError("image parts are sent as image_url with a data: URL")
                 ids, pixels = state.vision.prepare_messages(msgs, state.chat_template)
                 self._embeds = state.vision.image_inputs(ids, pixels)
+                self._rope = state.vision.rope_inputs(ids, pixels)
             except (ValueError, chat_mod.TemplateError) as ex:
                 raise ApiError(400, str(ex), param="messages") from None
             return ids

@@ -31,6 +31,7 @@ class Job:
     guided: Optional[object] = None
     adapter_slot: int = -1             # resident LoRA adapter the request selected (-1 = base model)
     embeds: Optional[tuple] = None     # (positions, rows): rows that replace the embeddings of those prompt tokens (image rows)
+    rope_positions: Optional[object] = None   # [3, prompt] rotary position streams of a sectioned rope (None: the positions)
     id: int = 0
     created: float = field(default_factory=time.monotonic)
     events: "queue.Queue" = field(default_factory=lambda: queue.Queue(maxsize=4096))
@@ -206,7 +207,7 @@ class ServeEngine:
             job = self.waiting[0]
             try:
                 sid = d.open(job.prompt_tokens, job.params, guided=job.guided, adapter_slot=job.adapter_slot,
-                             embeds=job.embeds)
+                             embeds=job.embeds, rope_positions=job.rope_positions)
             except (NoFreeRow, OutOfBlocks):
                 if not self.live and not d.seqs:        # can never fit
                     self.waiting.pop(0)

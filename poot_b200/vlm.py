@@ -91,7 +91,6 @@ class VisionLLM:
         if self.qwen:
             vc = self.vision.cfg
             self.prep = QwenImagePrep.from_dir(handle.source, vc.patch, vc.merge, vc.temporal)
-            self.llm = None              # the serving driver binds one position per token; this family needs three
         else:
             self.prep = ImagePrep.from_dir(handle.source, self.vision.cfg.image_size)
         self._towers = {}
@@ -251,12 +250,9 @@ class VisionLLM:
     def image_inputs(self, tokens: Sequence[int], pixels: Optional[np.ndarray]):
         """``(positions, rows)`` for ``Driver.open(..., embeds=)``: the prompt's image-token positions and the rows the
         frames give, checked to agree in number."""
-        if self.qwen:
-            raise ValueError("this family's sectioned rotary positions are not bound by the serving driver; "
-                             "its images run through VisionLLM.generate / `caption`")
         toks = np.asarray(tokens, dtype=np.int64).reshape(-1)
         at = np.nonzero(toks == self.model.image_token)[0]
-        if pixels is None or len(pixels) == 0:
+        if pixels is None or (not self.qwen and len(pixels) == 0):
             if len(at):
                 raise ValueError("the prompt holds image tokens but no image was given")
             return None
@@ -264,6 +260,14 @@ class VisionLLM:
         if len(at) != rows.shape[0]:
             raise ValueError(f"the prompt holds {len(at)} image tokens; the frames give {rows.shape[0]} rows")
         return at, rows
+
+    def rope_inputs(self, tokens: Sequence[int], pixels) -> Optional[np.ndarray]:
+        """Rotary position streams ``[3, len(tokens)]`` for ``Driver.open(..., rope_positions=)`` under a sectioned rope
+        (``None`` for families with one position per token)."""
+        if not self.qwen:
+            return None
+        grids = [] if pixels is None else pixels.grids
+        return mrope_positions(np.asarray(tokens).reshape(-1), self.model.image_token, grids, self.vision.cfg.merge)
 
     def generate(self, tokens: Sequence[int], pixels: Optional[np.ndarray], max_new: int = 64,
                  eos: Optional[Sequence[int]] = None, on_token: Optional[Callable[[int], None]] = None) -> List[int]:
@@ -286,7 +290,8 @@ class VisionLLM:
             return out
         drv = self.llm.driver
         params = SamplingParams(temperature=0.0, max_tokens=max_new, ignore_eos=True)
-        sid = drv.open(list(tokens), params, embeds=self.image_inputs(tokens, pixels))
+        sid = drv.open(list(tokens), params, embeds=self.image_inputs(tokens, pixels),
+                       rope_positions=self.rope_inputs(tokens, pixels))
         out = []
         try:
             while len(out) < max_new:

@@ -219,7 +219,7 @@ def test_image_rows_on_the_emulated_device_engine(checkpoint):
         vlm = VisionLLM.load(d, backend="device", device="cpu", rows=1, max_seq=64, prefill_chunk=16, num_blocks=8)
         got = vlm.generate(tokens, pixels, max_new=6)
         eng = vlm.llm.engine
-        assert any(k[-1] for k in eng.launches_per_step), "no step ran with rows in place of embeddings"
+        assert any(k[-2] for k in eng.launches_per_step), "no step ran with rows in place of embeddings"
         blind = vlm.llm.generate_tokens(tokens, __import__("poot_b200").SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
     agree = 0
     for x, y in zip(got, want):
@@ -368,8 +368,10 @@ def test_qwen_vl_tower_logits_and_generation_match_transformers(qwen_checkpoint)
     with torch.no_grad():
         want = hf(input_ids=torch.tensor([plain])).logits[0, -1].numpy()
     assert np.abs(vlm.prefill(vlm._session(16), plain, None)[0] - want).max() < 1e-5
-    with pytest.raises(ValueError, match="serving driver"):
-        vlm.image_inputs(tokens, images)
+    # through the serving driver: chunked prefill cuts the image runs, decode continues at index + delta
+    served = VisionLLM.load(d, backend="oracle", rows=2, max_seq=128, prefill_chunk=16, num_blocks=32)
+    assert served.llm is not None and served.generate(tokens, images, max_new=6) == _qwen_greedy(hf, tokens, images, IMG, 6)
+    assert served.generate(plain, None, max_new=4) == vlm.generate(plain, None, max_new=4)
 
 
 def test_mrope_positions():
@@ -426,3 +428,51 @@ def test_qwen_caption_command(qwen_checkpoint, tmp_path, capsys):
     shown = want[:want.index(eos)] if eos in want else want
     dec = StreamDecoder(vlm.tokenizer)
     assert out == "".join(dec.push(t) for t in shown) + dec.flush() + "\n"
+
+
+def test_qwen_vl_images_on_the_emulated_device_engine(tmp_path):
+    """The device engine's program under a sectioned rope: the per-token rotary rows staged by ``bind_rope_streams``
+    (time / row / column streams by channel section) and the image rows staged by ``bind_embeds``, in chunked prefill
+    and decode, against ``transformers`` greedy generation (bf16 on the engine side: the first tokens must agree)."""
+    from transformers import Qwen2_5_VLConfig, Qwen2_5_VLForConditionalGeneration
+    from poot_b200.models.image_prep import QwenImages
+    from poot_b200.utils.kernel_emulation import emulated_kernels
+    torch.manual_seed(0)
+    cfg = Qwen2_5_VLConfig(
+        text_config=dict(hidden_size=128, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                         vocab_size=300, max_position_embeddings=256,
+                         rope_parameters={"rope_type": "default", "mrope_section": [4, 6, 6], "rope_theta": 10000.0}),
+        vision_config=dict(depth=2, hidden_size=32, intermediate_size=48, num_heads=2, in_channels=3, patch_size=4,
+                           spatial_merge_size=2, temporal_patch_size=2, window_size=16, fullatt_block_indexes=[1],
+                           out_hidden_size=128, tokens_per_second=1),
+        image_token_id=290, video_token_id=291, vision_start_token_id=292, vision_end_token_id=293)
+    hf = Qwen2_5_VLForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for p in hf.parameters():
+            if p.ndim == 1:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = str(tmp_path)
+    hf.save_pretrained(d, safe_serialization=True)
+    grids = [(1, 8, 12)]
+    images = QwenImages(np.random.default_rng(5).standard_normal((96, 96)).astype(np.float32), grids)
+    tokens = [5, 6, 292] + [290] * 24 + [293, 8, 9, 10, 11, 12]
+    want = _qwen_greedy(hf, tokens, images, 290, 6)
+    with emulated_kernels():
+        vlm = VisionLLM.load(d, backend="device", device="cpu", rows=1, max_seq=64, prefill_chunk=16, num_blocks=8)
+        got = vlm.generate(tokens, images, max_new=6)
+        keys = list(vlm.llm.engine.launches_per_step)
+        assert any(k[-1] and k[-2] for k in keys) and any(k[-1] and not k[-2] for k in keys)   # image chunks, then plain ones
+        eng = vlm.llm.engine
+        streams = torch.tensor([[3, 3, 3, 9], [3, 4, 5, 9], [7, 3, 2, 9]], dtype=torch.int32)
+        eng.bind_rope_streams(streams)
+        owner = [0] * 4 + [1] * 6 + [2] * 6                                  # sections [4, 6, 6] of the 16 channel pairs
+        for t in range(4):
+            for j in (0, 3, 4, 9, 10, 15):
+                assert eng.rope_cos_tok[t, j] == eng.cos[int(streams[owner[j], t]), j]
+                assert eng.rope_sin_tok[t, j] == eng.sin[int(streams[owner[j], t]), j]
+    agree = 0
+    for x, y in zip(got, want):
+        if x != y:
+            break
+        agree += 1
+    assert agree >= 2, (got, want)
