@@ -239,8 +239,9 @@ class DecoderEngine:
         """Stage the rows that replace token embeddings in the next step: ``flags[T]`` int32 (1 = replace) and
         ``rows[T, hidden]`` (any float dtype; rows without a flag are ignored).  The buffers have fixed addresses, so a
         captured step graph replays over them."""
-        if self.tp != 1 or (self.stage is not None and not self.stage.first):
-            raise ValueError("rows in place of embeddings: single-rank engines and the first pipeline stage only")
+        if getattr(self.comm, "fused", False) or (self.stage is not None and not self.stage.first):
+            raise ValueError("rows in place of embeddings: not in the fused tensor-parallel programs, and on the first "
+                             "pipeline stage only")
         if self.embed_rows is None:
             self.embed_rows = torch.zeros(self.max_tokens, self.cfg.hidden, dtype=torch.bfloat16, device=self.device)
             self.embed_flags = torch.zeros(self.max_tokens, dtype=torch.int32, device=self.device)
@@ -256,6 +257,8 @@ class DecoderEngine:
         cfg = self.cfg
         if not cfg.mrope_sections:
             raise ValueError(f"{cfg.family}: rotary position streams need a sectioned rope")
+        if getattr(self.comm, "fused", False):
+            raise ValueError("rotary position streams are not read by the fused tensor-parallel programs")
         half = cfg.rot // 2
         if self.rope_cos_tok is None:
             dev = self.device
