@@ -48,9 +48,26 @@ class Embedder:
         self.cfg = model.cfg
         self.graphs = {}
         self.lock = threading.Lock()
+        self.engine = None               # device program (runtime/encoder_engine.py); None: the host evaluator
+
+    def to_device(self, device="cuda", max_tokens: int = 4096, max_rows: int = 64) -> "Embedder":
+        """Run the encoder on the B200 engine (bf16) instead of the host evaluator."""
+        import torch
+        from .runtime.encoder_engine import EncoderEngine
+        tensors = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in self.weights.items()}
+        self.engine = EncoderEngine(self.cfg, tensors, device, max_tokens, max_rows)
+        return self
 
     @staticmethod
-    def load(path: str) -> "Embedder":
+    def load(path: str, backend: str = "oracle", device="cuda") -> "Embedder":
+        """``backend``: ``oracle`` (host evaluator, f32) or ``device`` (the B200 engine, bf16)."""
+        if backend not in ("oracle", "device"):
+            raise EmbedError(f"backend {backend!r}: oracle or device")
+        emb = Embedder._load(path)
+        return emb.to_device(device) if backend == "device" else emb
+
+    @staticmethod
+    def _load(path: str) -> "Embedder":
         from .driver.handle import ModelHandle
         handle = ModelHandle.load(path)
         if getattr(handle.model, "kind", "decoder") != "encoder":
@@ -78,6 +95,15 @@ class Embedder:
         longest = max(len(x) for x in ids)
         if longest > c.max_position:
             raise EmbedError(f"input of {longest} tokens exceeds the model's {c.max_position} positions")
+        if self.engine is not None:
+            with self.lock:
+                if c.labels:
+                    return self.engine.scores(ids, types).cpu().numpy()
+                rows = self.engine.forward(ids, types)
+                hid = np.zeros((R, longest, c.hidden), np.float32)
+                for r, x in enumerate(rows):
+                    hid[r, :x.shape[0]] = x.cpu().numpy()
+                return hid
         T = min(-(-longest // 16) * 16, c.max_position)
         tok = np.full((R, T), c.pad_token, np.int32)
         typ = np.zeros((R, T), np.int32)
@@ -140,7 +166,7 @@ class EmbedEngine:
     def health(self) -> dict:
         h = {"status": self.state}
         if self.state == "serving":
-            h.update({"backend": "oracle", "kind": "encoder", "max_seq": self.embedder.cfg.max_position})
+            h.update({"backend": "oracle" if self.embedder.engine is None else "b200", "kind": "encoder", "max_seq": self.embedder.cfg.max_position})
         return h
 
     def run(self, fn):

@@ -69,7 +69,7 @@ def rows():
             header = {"vocab_size": 32000, "hidden_size": 4096, **header}
         model = reg.resolve_hf(header)
         if e.kind == "encoder":
-            out.append((e.name, ", ".join(e.hf_types), "oracle", "no", "-", "embeddings and rerank scores on the host evaluator"))
+            out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "yes", "- (embeddings and rerank scores; head widths that are multiples of 32)"))
             continue
         if e.kind == "vlm" and model.cfg.mrope_sections:
             out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "text stack",

@@ -176,9 +176,14 @@ def _is_encoder_checkpoint(path: str) -> bool:
 
 
 def _serve_encoder(cfg) -> int:
-    """An encoder checkpoint serves ``/v1/embeddings`` and ``/v1/rerank`` (evaluated by the CPU oracle)."""
+    """An encoder checkpoint serves ``/v1/embeddings`` and ``/v1/rerank``: on the device engine, or on the host evaluator
+    with ``--backend oracle`` (and when no device is present)."""
     from ..embed import Embedder, EmbedEngine
-    emb = Embedder.load(cfg.model)
+    backend = "oracle"
+    if cfg.backend != "oracle":
+        import torch
+        backend = "device" if torch.cuda.is_available() else "oracle"
+    emb = Embedder.load(cfg.model, backend=backend)
     engine = EmbedEngine(emb, Metrics())
     state = ServerState(engine, cfg, cfg.model_id or emb.name, family="bert")
     server = Server(state)

@@ -516,3 +516,41 @@ def test_planner_launch_census_equals_the_engine_launch_count(kw):
         sess.decode([1, 2])
         launched = eng.launches_per_step[eng._key(StepShape(2, 2, 0))]
     assert launched - 2 == prog.dispatches, (launched, prog.census)
+
+
+def test_encoder_engine_matches_the_graph_oracle(tmp_path):
+    """BERT on the device engine's kernels (restated on the host): ragged batch, K/V of each sequence in its own pool
+    blocks, every token seeing its whole sequence; hidden states, pooled embeddings and a cross-encoder's scores against
+    the graph oracle, which is itself checked against the Hugging Face model."""
+    from poot_b200.embed import Embedder, PairTokenizer
+    from poot_b200.models.encoder import EncoderConfig, EncoderModel
+    from poot_b200.oracle.runner import random_weights_f32
+    from poot_b200.text.codec import ByteTokenizer
+    for labels in (0, 1):
+        cfg = EncoderConfig(n_layers=2, hidden=128, n_heads=4, ffn=256, vocab=300, max_position=64, labels=labels)
+        model = EncoderModel(cfg)
+        w = random_weights_f32(model, seed=3, std=0.08)
+        for k in w:
+            if k.endswith("_bias"):
+                w[k] = (0.1 * np.random.default_rng(len(k)).standard_normal(w[k].shape)).astype(np.float32)
+        w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in w.items()}
+        tk = PairTokenizer(ByteTokenizer(cfg.vocab), cfg.vocab - 2, cfg.vocab - 1)
+        rng = np.random.default_rng(1)
+        ids = [rng.integers(3, 290, n).tolist() for n in (21, 5, 33)]          # ragged, across K/V block boundaries
+        types = [[0] * (len(x) // 2) + [1] * (len(x) - len(x) // 2) for x in ids]
+        host = Embedder(model, w, tk)
+        want = host.forward(ids, types)
+        with emulated_kernels():
+            dev = Embedder(model, w, tk).to_device("cpu", max_tokens=128, max_rows=4)
+            got = dev.forward(ids, types)
+            assert dev.engine.launches == 6 + 13 * cfg.n_layers
+            if labels:
+                assert got.shape == (3, 1) and np.abs(got - want).max() < 0.03 * max(1.0, np.abs(want).max())
+                continue
+            for r, x in enumerate(ids):
+                err = np.abs(got[r, :len(x)] - want[r, :len(x)]).max()
+                assert err < 0.03 * max(1.0, np.abs(want[r, :len(x)]).max()), (r, err)
+            e_dev, e_host = dev.embed_ids(ids), host.embed_ids(ids)
+            assert np.abs((e_dev * e_host).sum(-1) - 1.0).max() < 2e-3          # the same directions
+            with pytest.raises(ValueError, match="exceed"):
+                dev.forward([list(range(3, 60))] * 3)

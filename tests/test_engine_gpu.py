@@ -216,3 +216,23 @@ def test_rows_with_and_without_a_resident_adapter():
         ref = forward_logits(refs[b], prompts[b].cuda())[-1]
         err = (eng2.logits[b] - ref).abs().max().item()
         assert err < 0.05 * max(1.0, ref.abs().max().item()), (b, err)
+
+
+@pytest.mark.xfail(strict=False, reason="the encoder program (BERT) on the device engine: not yet run on a device")
+def test_encoder_engine_matches_the_graph_oracle_on_the_device():
+    import numpy as np
+    from poot_b200.embed import Embedder, PairTokenizer
+    from poot_b200.models.encoder import EncoderConfig, EncoderModel
+    from poot_b200.oracle.runner import random_weights_f32
+    from poot_b200.text.codec import ByteTokenizer
+    cfg = EncoderConfig(n_layers=2, hidden=384, n_heads=12, ffn=1536, vocab=1000, max_position=128)
+    model = EncoderModel(cfg)
+    w = {k: torch.from_numpy(v).to(torch.bfloat16).float().numpy() for k, v in random_weights_f32(model, seed=3, std=0.05).items()}
+    tk = PairTokenizer(ByteTokenizer(cfg.vocab), cfg.vocab - 2, cfg.vocab - 1)
+    rng = np.random.default_rng(1)
+    ids = [rng.integers(3, 990, n).tolist() for n in (21, 5, 97, 64)]
+    want = Embedder(model, w, tk).forward(ids)
+    got = Embedder(model, w, tk).to_device("cuda", max_tokens=256, max_rows=4).forward(ids)
+    for r, x in enumerate(ids):
+        err = np.abs(got[r, :len(x)] - want[r, :len(x)]).max()
+        assert err < 0.03 * max(1.0, np.abs(want[r, :len(x)]).max()), (r, err)
