@@ -174,6 +174,35 @@ def route_case(T, E, k, mode):
     return [fn], T * E * 8, 0.0
 
 
+def replace_rows_case(T, D, share=0.5):
+    """Image rows in place of token embeddings: half of the rows flagged, so half of ``rows`` is read and written."""
+    h, rows = rnd(T, D), rnd(T, D)
+    flags = (torch.rand(T, device="cuda") < share).to(torch.int32)
+    fn = lambda: K.replace_rows_(h, rows, flags)
+    return [fn], int(2 * T * D * 2 * share) + T * 4, 0.0
+
+
+def encoder_case(n_seq, length, hidden=384, heads=12, ffn=1536, layers=6):
+    """A MiniLM-sized BERT encoder over a ragged batch through ``runtime/encoder_engine.py`` (the whole program: it is timed
+    eagerly inside one graph capture like the kernels; bytes = the weights once, flops = the projections)."""
+    from poot_b200.models.encoder import EncoderConfig, EncoderModel
+    from poot_b200.runtime.encoder_engine import EncoderEngine
+    cfg = EncoderConfig(n_layers=layers, hidden=hidden, n_heads=heads, ffn=ffn, vocab=30522, max_position=512)
+    shapes = EncoderModel(cfg).weight_shapes()
+    tensors = {k: torch.randn(*v) * 0.02 for k, v in shapes.items()}
+    eng = EncoderEngine(cfg, tensors, "cuda", max_tokens=n_seq * length, max_rows=n_seq)
+    seqs = [list(range(3, 3 + length))] * n_seq
+    N = n_seq * length
+    eng._bind(seqs, None)                        # the host layout once; the timed part is the device program
+
+    def fn():
+        eng._bind = lambda s, t: (N, [length] * n_seq)
+        eng.forward(seqs)
+    wbytes = sum(int(torch.tensor(v).prod()) * 2 for k, v in shapes.items() if k.startswith("layers."))
+    flops = 2.0 * N * layers * (4 * hidden * hidden + 2 * hidden * ffn) + 4.0 * layers * n_seq * length * length * hidden
+    return [fn], wbytes, flops
+
+
 CASES = {
     "dense-decode-gemv-qkv": lambda: gemm_case(1, 6144, 4096, "skinny"),
     "dense-decode-gemv-o": lambda: gemm_case(1, 4096, 4096, "skinny"),
@@ -205,6 +234,8 @@ CASES = {
     "scan-ssd-prefill-512": lambda: ssd_case(1, 512),
     "causal-conv-decode-b64": lambda: conv_case(64, 1),
     "causal-conv-prefill-512": lambda: conv_case(1, 512),
+    "replace-rows-1377x2048": lambda: replace_rows_case(1377, 2048),
+    "encoder-minilm-b32-len128": lambda: encoder_case(32, 128),
     "expert-routing-softmax-512x128-top8": lambda: route_case(512, 128, 8, "softmax"),
     "expert-routing-sigmoid-groups-512x256-top8": lambda: route_case(512, 256, 8, "sigmoid"),
 }
