@@ -76,8 +76,8 @@ def rows():
                         "a device program for the vision tower (it is evaluated on the host, once per image)"))
             continue
         if e.kind == "vlm":
-            out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "text stack",
-                        "a device program for the vision tower (it is evaluated on the host, once per image)"))
+            out.append((e.name, ", ".join(e.hf_types), "oracle + device", "no", "yes",
+                        "vision towers whose heads are not multiples of 32 wide run on the host evaluator"))
             continue
         gaps = model.cfg.device_gaps()
         device = "yes" if not gaps else "no"

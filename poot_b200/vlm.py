@@ -94,6 +94,7 @@ class VisionLLM:
         else:
             self.prep = ImagePrep.from_dir(handle.source, self.vision.cfg.image_size)
         self._towers = {}
+        self.vision_engine = None                     # device program of the tower (runtime/vision_engine.py); None: host evaluator
         self.rope_delta = 0                           # rotary position minus sequence index after the last prefilled prompt
         self.eos: List[int] = []                      # end tokens of generation_config.json, beside the tokenizer's
 
@@ -125,12 +126,25 @@ class VisionLLM:
             with open(f) as fh:
                 template = fh.read()
         vlm = VisionLLM(handle, tok, template, llm)
+        if backend == "device" and not vlm.qwen:
+            vlm.tower_to_device(device)
         f = os.path.join(path, "generation_config.json")
         if os.path.exists(f):
             with open(f) as fh:
                 e = json.load(fh).get("eos_token_id")
             vlm.eos = [int(x) for x in (e if isinstance(e, list) else [e]) if x is not None]
         return vlm
+
+    def tower_to_device(self, device="cuda", max_frames: int = 17) -> bool:
+        """Run the vision tower on the device engine when its head width allows it; otherwise it stays on the host."""
+        import torch
+        from .runtime.vision_engine import VisionEngine
+        try:
+            tensors = {k: torch.from_numpy(np.ascontiguousarray(v)) for k, v in self.vision_weights.items()}
+            self.vision_engine = VisionEngine(self.vision.cfg, tensors, device, max_frames)
+        except ValueError:
+            self.vision_engine = None
+        return self.vision_engine is not None
 
     @property
     def weights(self):
@@ -158,6 +172,8 @@ class VisionLLM:
         n, ch, h, w = pixels.shape
         if (ch, h, w) != (c.channels, c.image_size, c.image_size):
             raise ValueError(f"frames of {(ch, h, w)}; the tower takes {(c.channels, c.image_size, c.image_size)}")
+        if self.vision_engine is not None and n <= self.vision_engine.max_frames:
+            return self.vision_engine.forward(pixels).float().cpu().numpy()
         if n not in self._towers:
             self._towers[n] = self.vision.trace(n)
         g = self._towers[n]

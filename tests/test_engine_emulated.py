@@ -554,3 +554,36 @@ def test_encoder_engine_matches_the_graph_oracle(tmp_path):
             assert np.abs((e_dev * e_host).sum(-1) - 1.0).max() < 2e-3          # the same directions
             with pytest.raises(ValueError, match="exceed"):
                 dev.forward([list(range(3, 60))] * 3)
+
+
+def test_vision_engine_matches_the_graph_oracle():
+    """The SmolVLM vision tower and connector on the device engine's kernels (restated on the host) against the traced
+    tower evaluated by the oracle: patch GEMM + position rows, pre-norm blocks with whole-frame attention, final norm,
+    pixel shuffle, projection."""
+    from poot_b200.models.vision import VisionConfig, VisionTower, patchify, position_ids
+    from poot_b200.oracle.eval import EvalOptions, eval_graph
+    from poot_b200.runtime.vision_engine import VisionEngine
+    cfg = VisionConfig(hidden=128, ffn=256, n_layers=2, n_heads=4, image_size=48, patch=8, scale=2, text_hidden=96)
+    tower = VisionTower(cfg)
+    rng = np.random.default_rng(0)
+    w = {}
+    for k, shape in tower.weight_shapes().items():
+        v = rng.standard_normal(shape) * (0.1 if k.endswith("_bias") else 0.06)
+        if k.endswith("norm"):
+            v = 1.0 + 0.1 * rng.standard_normal(shape)
+        w[k] = torch.from_numpy(v.astype(np.float32)).to(torch.bfloat16).float().numpy()
+    pixels = rng.standard_normal((3, 3, 48, 48)).astype(np.float32)
+    g = tower.trace(3)
+    inputs = {"patches": patchify(pixels, 8), "pos_ids": np.tile(position_ids(cfg, 6, 6)[None], (3, 1))}
+    inputs.update({i.name: w[i.name] for i in g.inputs if i.storage == "const"})
+    want = eval_graph(g, inputs, EvalOptions(matmul_precision="exact")).outputs["image_rows"]
+    with emulated_kernels():
+        eng = VisionEngine(cfg, {k: torch.from_numpy(v) for k, v in w.items()}, "cpu", max_frames=4)
+        got = eng.forward(pixels).float().numpy()
+        assert eng.launches == 4 + 13 * cfg.n_layers + 3
+        with pytest.raises(ValueError, match="frames exceed"):
+            eng.forward(np.zeros((5, 3, 48, 48), np.float32))
+    assert got.shape == want.shape == (3 * 9, 96)
+    assert np.abs(got - want).max() < 0.03 * max(1.0, np.abs(want).max())
+    with pytest.raises(ValueError, match="multiples of 32"):
+        VisionEngine(VisionConfig(hidden=48, n_heads=4), {}, "cpu")

@@ -43,7 +43,7 @@ def checkpoint(tmp_path_factory):
     cfg = Idefics3Config(
         text_config=dict(model_type="llama", hidden_size=128, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
                          num_key_value_heads=2, vocab_size=tk.get_vocab_size(), max_position_embeddings=512, rms_norm_eps=1e-5),
-        vision_config=dict(hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, image_size=32,
+        vision_config=dict(hidden_size=128, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4, image_size=32,
                            patch_size=8, num_channels=3),
         scale_factor=2, image_token_id=image_token, pad_token_id=0)
     hf = Idefics3ForConditionalGeneration(cfg).eval()
@@ -217,7 +217,9 @@ def test_image_rows_on_the_emulated_device_engine(checkpoint):
     want = _hf_greedy(hf, tokens, pixels, 6)
     with emulated_kernels():
         vlm = VisionLLM.load(d, backend="device", device="cpu", rows=1, max_seq=64, prefill_chunk=16, num_blocks=8)
+        assert vlm.vision_engine is not None                      # 32-wide heads: the tower runs on the engine too
         got = vlm.generate(tokens, pixels, max_new=6)
+        assert vlm.vision_engine.launches == 4 + 13 * 2 + 3
         eng = vlm.llm.engine
         assert any(k[-2] for k in eng.launches_per_step), "no step ran with rows in place of embeddings"
         blind = vlm.llm.generate_tokens(tokens, __import__("poot_b200").SamplingParams(max_tokens=6, temperature=0.0, ignore_eos=True))
