@@ -236,3 +236,25 @@ def test_encoder_engine_matches_the_graph_oracle_on_the_device():
     for r, x in enumerate(ids):
         err = np.abs(got[r, :len(x)] - want[r, :len(x)]).max()
         assert err < 0.03 * max(1.0, np.abs(want[r, :len(x)]).max()), (r, err)
+
+
+@pytest.mark.xfail(strict=False, reason="the vision tower program on the device engine: not yet run on a device")
+def test_vision_engine_matches_the_graph_oracle_on_the_device():
+    import numpy as np
+    from poot_b200.models.vision import VisionConfig, VisionTower, patchify, position_ids
+    from poot_b200.oracle.eval import EvalOptions, eval_graph
+    from poot_b200.runtime.vision_engine import VisionEngine
+    cfg = VisionConfig(hidden=256, ffn=512, n_layers=2, n_heads=4, image_size=128, patch=16, scale=4, text_hidden=192)
+    tower = VisionTower(cfg)
+    rng = np.random.default_rng(0)
+    w = {}
+    for k, shape in tower.weight_shapes().items():
+        v = 1.0 + 0.1 * rng.standard_normal(shape) if k.endswith("norm") else rng.standard_normal(shape) * 0.05
+        w[k] = torch.from_numpy(v.astype(np.float32)).to(torch.bfloat16).float().numpy()
+    pixels = rng.standard_normal((2, 3, 128, 128)).astype(np.float32)
+    g = tower.trace(2)
+    inputs = {"patches": patchify(pixels, 16), "pos_ids": np.tile(position_ids(cfg, 8, 8)[None], (2, 1))}
+    inputs.update({i.name: w[i.name] for i in g.inputs if i.storage == "const"})
+    want = eval_graph(g, inputs, EvalOptions(matmul_precision="exact")).outputs["image_rows"]
+    got = VisionEngine(cfg, {k: torch.from_numpy(v) for k, v in w.items()}, "cuda", max_frames=2).forward(pixels).float().cpu().numpy()
+    assert np.abs(got - want).max() < 0.03 * max(1.0, np.abs(want).max())

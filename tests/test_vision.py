@@ -376,6 +376,46 @@ def test_qwen_vl_tower_logits_and_generation_match_transformers(qwen_checkpoint)
     assert served.generate(plain, None, max_new=4) == vlm.generate(plain, None, max_new=4)
 
 
+def test_qwen_vl_chat_completions_with_an_image(qwen_checkpoint):
+    """The served path of the sectioned-rope family: an ``image_url`` part becomes image rows and three rotary position
+    streams on the scheduler's job; the completion is the one ``transformers`` generates."""
+    import base64
+    import http.client
+    import io
+    from PIL import Image
+    from poot_b200.llm import LLM
+    from poot_b200.serve import Metrics, ServeConfig, ServeEngine, Server, ServerState
+    d, hf, ids = qwen_checkpoint
+    llm = LLM.oracle(d, rows=2, max_seq=256, num_blocks=40, prefill_chunk=32)
+    cfg = ServeConfig(model=d, addr="127.0.0.1:0", rows=2)
+    eng = ServeEngine(llm.driver, llm.tokenizer, Metrics(), 8, cfg.max_queue_wait_secs)
+    state = ServerState(eng, cfg, "tiny-qwen-vl", family="qwen_vl")
+    state.vision = VisionLLM(llm.handle, llm.tokenizer, None, llm)
+    srv = Server(state)
+    eng.start()
+    srv.start()
+    try:
+        img = Image.fromarray(np.random.default_rng(8).integers(0, 255, (24, 40, 3), dtype=np.uint8))
+        buf = io.BytesIO()
+        img.save(buf, format="PNG")
+        url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+        msgs = [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}}, {"type": "text", "text": "What?"}]}]
+        tokens, images = state.vision.prepare_messages(msgs)
+        want = _qwen_greedy(hf, tokens, images, ids["<|image_pad|>"], 4)
+        c = http.client.HTTPConnection("127.0.0.1", srv.port, timeout=60)
+        c.request("POST", "/v1/chat/completions", json.dumps({"messages": msgs, "max_tokens": 4, "temperature": 0, "ignore_eos": True}).encode(),
+                  {"Content-Type": "application/json"})
+        r = c.getresponse()
+        body = json.loads(r.read())
+        c.close()
+        assert r.status == 200, body
+        assert body["usage"]["prompt_tokens"] == len(tokens)
+        eos = llm.driver.eos_token
+        assert body["choices"][0]["message"]["content"] == llm.tokenizer.decode([t for t in want if t != eos])
+    finally:
+        srv.shutdown()
+
+
 def test_mrope_positions():
     from poot_b200.models.vision import mrope_positions
     I = 99
