@@ -36,6 +36,10 @@ def fork(d: Driver, seq_id: int) -> int:
     n = Sequence_(sid, row, list(s.tokens), s.prompt_len, copy.copy(s.params), s.blocks[:full] + fresh, s.identity,
                   computed=s.computed, cached_tokens=s.cached_tokens, generated=s.generated, counts=dict(s.counts),
                   seed=s.seed)
+    # what the sequence runs under travels with the fork: its resident adapter, the rows that stand in for prompt
+    # embeddings (a fork taken mid-prompt still has them ahead) and the rotary offset of a sectioned rope
+    n.adapter_slot, n.embed_pos, n.embed_rows = s.adapter_slot, s.embed_pos, s.embed_rows
+    n.rope_prefix, n.rope_delta = s.rope_prefix, s.rope_delta
     d.seqs[sid] = n
     d.engine.write_block_table(row, n.blocks)
     return sid

@@ -118,6 +118,24 @@ def test_fork_shares_full_blocks_and_copies_the_partial_one():
     assert d.kv_usage()["blocks_used"] == d.kv_usage()["prefix_entries"] == 1
 
 
+def test_fork_carries_the_adapter_the_embedding_rows_and_the_rotary_offset():
+    import numpy as np
+    d = LLM.fake(vocab=100).driver
+    prompt = [1] + list(range(3, 23))
+    rope = np.stack([np.arange(21), np.arange(21), np.arange(21)]).astype(np.int32)
+    rope[:, 5:] += 7                                          # an image earlier in the prompt pushed the positions on
+    sid = d.open(prompt, SamplingParams(max_tokens=4, ignore_eos=True), adapter_slot=2,
+                 embeds=(np.array([2, 3]), np.ones((2, 8), np.float32)), rope_positions=rope)
+    d.step([sid])
+    child = fork(d, sid)
+    a, b = d.seqs[sid], d.seqs[child]
+    assert b.adapter_slot == 2 and b.rope_delta == a.rope_delta == 7 and b.embed_pos is a.embed_pos and b.identity == a.identity
+    d.commit(child, [50])
+    inp = d.build_inputs(d.plan([child]))
+    assert inp.rope_positions[:, 0].tolist() == [21 + 7] * 3 and inp.adapter_rows[0] == 2 and inp.embed_flags is None
+    d.release(sid, "preempted"); d.release(child, "preempted")
+
+
 def test_beam_search_orders_hypotheses_by_score():
     d = LLM.fake(vocab=40, rows=8).driver
     beams = beam_search(d, [1, 10], width=3, max_tokens=4, eos=-1)
