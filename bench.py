@@ -29,9 +29,11 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-# Published numbers of the reference that are closest in kind (single stream bf16 decode of its largest dense
-# bf16 model, qwen3-4b at ISL 128 on an RTX PRO 6000 Blackwell): decode tok/s.  No B200 / Llama-3-8B number exists.
-PUBLISHED_DECODE_TOK_S = 112.9
+# The reference publishes no Llama-3-8B, no batch > 1 and no B200 number, so ``vs_baseline`` is null.  For context
+# only, ``extra`` carries the ratio of the batch-1 decode rate to the reference's closest published cell: single-stream
+# bf16 decode of its largest dense bf16 model (qwen3-4b, ISL 128) on an RTX PRO 6000 Blackwell.  Different model,
+# different GPU: not a like-for-like comparison.
+PUBLISHED_BS1_DECODE_TOK_S_QWEN3_4B_RTXPRO6000 = 112.9
 
 
 class ClockSampler:
@@ -128,7 +130,10 @@ def main() -> None:
     ap.add_argument("--model", default="llama-3-8b")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt", type=int, default=512)
-    ap.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"],
+                    help="collectives of a tensor-parallel run: the in-kernel NVLink programs (fused) or the library's "
+                         "(nccl); auto = the package default (poot_b200.parallel.tp.DEFAULT_COMM)")
+    ap.add_argument("--nvls", type=int, default=0, help="1: let the library use in-switch (multicast) reductions")
     ap.add_argument("--skip-bs1", action="store_true")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch between kernels")
     ap.add_argument("--gemv-max-m", type=int, default=None, help="rows served by the SIMT GEMV (0 = tensor cores)")
@@ -146,18 +151,19 @@ def main() -> None:
         reference_arm(args)
         return
 
-    def _expired():
-        # Leaving the process releases the device context; kernels of this rank that are still waiting for a peer
-        # end with it.  Rank 0 says what happened in the one-line format the caller reads.
-        if int(os.environ.get("RANK", "0")) == 0:
-            print(json.dumps({"metric": "decode tok/s", "value": None, "n_gpus": args.gpus,
-                              "error": f"watchdog: the run did not finish within {args.watchdog:.0f} s"}), flush=True)
-        os._exit(3)
+    # Every way out of a multi-rank run (watchdog, SIGTERM, an exception) first makes this rank's kernels stop waiting
+    # for peers and the device go idle, and only then leaves the process (poot_b200/parallel/teardown.py).
+    from poot_b200.parallel import teardown
 
-    import threading
-    dog = threading.Timer(args.watchdog, _expired)
-    dog.daemon = True
-    dog.start()
+    def _say(code: int) -> None:
+        if code != 0 and int(os.environ.get("RANK", "0")) == 0:
+            print(json.dumps({"metric": "decode tok/s", "value": None, "n_gpus": args.gpus,
+                              "error": f"run ended early with code {code} (watchdog {args.watchdog:.0f} s, signal or fault); "
+                                       "the device was drained before exit"}), flush=True)
+
+    dog = teardown.install(watchdog_seconds=args.watchdog, on_exit=_say)
+    if not args.nvls:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
     import torch
     import torch.distributed as dist
@@ -180,8 +186,11 @@ def main() -> None:
     comm = None
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-        from poot_b200.parallel.tp import make_comm
+        from poot_b200.parallel.tp import DEFAULT_COMM, make_comm
+        if args.comm == "auto":
+            args.comm = DEFAULT_COMM
         comm = make_comm(args.comm, rank, world, dev)
+        teardown.set_comm(comm)
 
     K.set_pdl(bool(args.pdl))
     if args.gemv_max_m is not None:
@@ -319,7 +328,7 @@ def main() -> None:
                        "decode tok/s (bs64; bs1 and prefill tok/s in extra), max over ranks"),
             "value": value, "unit": "tok/s", "n_gpus": world, "steps": Ksteps, "warmup": W,
             "ms_per_step": ms_dev / Ksteps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": value / PUBLISHED_DECODE_TOK_S, "dtype": "bf16", "data": "synthetic",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"model": cfg.name + ("" if args.quant == "none" else "-Q4_K(proj)+Q8_0(embed)"), "global_batch": B, "seq_len": P, "parallelism": (f"ep{world}+tp{world}(attention)" if cfg.is_moe and world > 1 else f"tp{world}"),
                        **({"INVALID": "development run with " + ",".join(args.dev_set)} if args.dev_set else {}),
                        "comm": args.comm if world > 1 else "none",
@@ -331,10 +340,18 @@ def main() -> None:
             "gpu_launches": launches,
             "extra": extra,
         }
+        if "decode_tok_s_bs1" in extra:
+            extra["bs1_vs_reference_published_qwen3_4b_rtxpro6000"] = (
+                extra["decode_tok_s_bs1"] / PUBLISHED_BS1_DECODE_TOK_S_QWEN3_4B_RTXPRO6000)
+        if world > 1 and args.comm != "fused":
+            out["config"]["note"] = ("library collectives (the baseline path); the fused GEMM + NVLink programs are "
+                                     "selected with --comm fused")
         print(json.dumps(out))
+    if dog is not None:
+        dog.cancel()
     if world > 1:
-        # Tear-down of a process group that owns captured NCCL graphs can block; results are out, so synchronise,
-        # release the peer mappings and leave without running the destructors.
+        # Tear-down of a process group that owns captured NCCL graphs can block; results are out, so meet, go idle,
+        # release the peer mappings (close() drains the device first) and leave without running the destructors.
         sys.stdout.flush()
         dist.barrier()
         torch.cuda.synchronize()
@@ -348,10 +365,12 @@ if __name__ == "__main__":
         main()
     except SystemExit:
         raise
-    except BaseException as e:      # say what failed in the one-line format, then leave without collective teardown
+    except BaseException as e:      # say what failed in the one-line format, drain the device, then leave
         import traceback
         traceback.print_exc()
         if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps({"metric": "decode tok/s", "value": None, "error": f"{type(e).__name__}: {e}"[:400]}), flush=True)
         sys.stdout.flush()
-        os._exit(1)
+        from poot_b200.parallel import teardown as _td
+        _td._state["on_exit"] = None
+        _td.drain_and_exit(1)

@@ -161,26 +161,58 @@ HOST_API int poot_prefix_register(void* c, void* p, uint64_t identity, const uin
   return covered;
 }
 
-// Drop entries whose block only the cache still references (least recently used first) until `want` blocks
-// were freed (want <= 0: all of them).  Returns the number of blocks returned to the pool.
+// Drop entries whose block only the cache still references until `want` blocks were freed (want <= 0: all of them).
+// Order: leaves of the prefix chains first, least recently used first among them.  A match stamps a chain's blocks in
+// prefix order, so a parent always carries an older stamp than its children; evicting by stamp alone would take the
+// parent and leave children that can never be matched again (the match stops at the missing parent) yet still hold
+// blocks.  An entry becomes evictable when no cached entry names it as parent.  Returns the blocks returned to the pool.
 HOST_API int poot_prefix_evict_unused(void* c, void* p, int want) {
   PrefixCache* pc = (PrefixCache*)c;
   Pool* pool = (Pool*)p;
-  std::vector<std::pair<uint64_t, Key>> cand;
+  std::unordered_map<Key, int, KeyHash> children;
+  for (auto& kv : pc->cached) children[Key{kv.second.parent, kv.first.identity}] += 1;  // the root key names no entry
+  using Cand = std::pair<uint64_t, Key>;
+  auto later = [](const Cand& a, const Cand& b) { return a.first > b.first; };
+  std::vector<Cand> heap;
+  auto evictable = [&](const Key& k, const Entry& e) {
+    auto ch = children.find(k);
+    return pool->refs[e.block] == 1 && (ch == children.end() || ch->second <= 0);
+  };
   for (auto& kv : pc->cached)
-    if (pool->refs[kv.second.block] == 1) cand.push_back({kv.second.last_use, kv.first});
-  std::sort(cand.begin(), cand.end(), [](auto& a, auto& b) { return a.first < b.first; });
+    if (evictable(kv.first, kv.second)) heap.push_back({kv.second.last_use, kv.first});
+  std::make_heap(heap.begin(), heap.end(), later);
   int freed = 0;
-  for (auto& c2 : cand) {
-    if (want > 0 && freed >= want) break;
-    auto it = pc->cached.find(c2.second);
+  while (!heap.empty() && !(want > 0 && freed >= want)) {
+    std::pop_heap(heap.begin(), heap.end(), later);
+    Key k = heap.back().second;
+    heap.pop_back();
+    auto it = pc->cached.find(k);
     if (it == pc->cached.end()) continue;
-    int b = it->second.block;
+    const Key parent{it->second.parent, k.identity};
+    const int b = it->second.block;
     pc->cached.erase(it);
     if (--pool->refs[b] == 0) pool->free_list.push_back(b);
     ++freed;
+    auto ch = children.find(parent);
+    if (ch != children.end() && --ch->second <= 0) {
+      auto pit = pc->cached.find(parent);
+      if (pit != pc->cached.end() && !(pit->first == k) && evictable(pit->first, pit->second)) {
+        heap.push_back({pit->second.last_use, pit->first});
+        std::push_heap(heap.begin(), heap.end(), later);
+      }
+    }
   }
   return freed;
+}
+
+// Number of cached blocks that only the cache references: what evict_unused() could return to the pool.
+HOST_API int poot_prefix_count_unused(void* c, void* p) {
+  PrefixCache* pc = (PrefixCache*)c;
+  Pool* pool = (Pool*)p;
+  int n = 0;
+  for (auto& kv : pc->cached)
+    if (pool->refs[kv.second.block] == 1) ++n;
+  return n;
 }
 
 // Remove every entry of one weights identity (an adapter that was unloaded).

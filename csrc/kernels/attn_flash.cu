@@ -143,7 +143,7 @@ attn_flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         ++issued_v;
       }
       if (!ok) {
-        atomicExch(status, (int)kTimeoutProducer);
+        ctl_fail(status, (int)kTimeoutProducer);
         // let the copies already in flight land before the CTA can exit
         for (int j = (issued_k > 2 ? issued_k - 2 : 0); j < issued_k; ++j)
           tc::mbar_wait(full_k + 8 * (j & 1), (uint32_t)(j >> 1) & 1u);
@@ -182,7 +182,7 @@ attn_flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
         tc::tc_commit(bar_o);
         tc::tc_commit(empty_v + 8 * s);
       }
-      if (!ok) atomicExch(status, (int)kTimeoutMma);
+      if (!ok) ctl_fail(status, (int)kTimeoutMma);
     }
   } else {
     // ---------------- softmax: thread <-> query row (tensor-memory lane) ----------------
@@ -265,7 +265,7 @@ attn_flash_prefill_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_
       }
       tc::tc_fence_before();
     }
-    if (!ok && lane == 0) atomicExch(status, (int)kTimeoutEpilogue);
+    if (!ok && lane == 0) ctl_fail(status, (int)kTimeoutEpilogue);
     if (ok && row < n_tok) {
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* orow = out + (size_t)(tok0 + row) * out_stride + (size_t)head * FA_D;

@@ -304,6 +304,7 @@ POOT_API int poot_attn_paged(const void* q, int q_stride, const void* kpool, con
                              float* part_o, float* part_ml, int R, int Hq, int Hkv, int D, float scale, float softcap,
                              int window, int splits, cudaStream_t s) {
   if (R == 0) return 0;
+  if (R < 0 || Hq <= 0 || Hkv <= 0) return (int)cudaErrorInvalidValue;   // before the modulo: Hkv == 0 must not trap the host
   if (splits < 1 || Hq % Hkv) return (int)cudaErrorInvalidValue;
   if (splits > 1 && (part_o == nullptr || part_ml == nullptr)) return (int)cudaErrorInvalidValue;
   if (D == 128)
@@ -335,7 +336,7 @@ POOT_API int poot_attn_paged_noalloc(const void* q, int q_stride, const void* kp
                                      void* out, int out_stride, int R, int Hq, int Hkv, int D, float scale,
                                      float softcap, int window, int splits, cudaStream_t stream) {
   if (R == 0) return 0;
-  if (R < 0 || Hq <= 0 || D <= 0 || splits < 1) return (int)cudaErrorInvalidValue;
+  if (R < 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || D <= 0 || splits < 1) return (int)cudaErrorInvalidValue;
   const unsigned long long need = (unsigned long long)R * Hq * splits * (unsigned long long)(D + 2);
   if (need > (unsigned long long)POOT_NOALLOC_SCRATCH_FLOATS) return (int)cudaErrorInvalidValue;
   int dev = 0;

@@ -2,7 +2,10 @@
 //
 //  * poot_symm_* / poot_ipc_*: device allocations exported to the peer processes through CUDA IPC
 //    (one process per GPU; every rank maps every other rank's block once at start-up).
-//  * tp_begin_step: bumps the device-resident epoch once per model step (first node of the step graph).
+//  * tp_begin_step: bumps the device-resident epoch once per model step (first node of the step graph) and
+//    writes the step's deadline into the control block: the waits of one step share one budget.
+//  * tp_argmax_exchange_kernel: the greedy pick over a vocabulary-parallel head without a library collective;
+//    every rank pushes its stage-1 table into the peers' exchange areas and combines what it received.
 //  * tp_norm_kernel: the consumer side of the fused GEMM + reduce-scatter and the producer side of the
 //    fused all-gather + GEMM.  For this rank's S token rows it waits (bounded) for every rank's
 //    contribution of the previous projection, adds them in rank order to the residual stream, applies
@@ -12,13 +15,76 @@
 //    the counterpart of the reference's 256 B / 64 KiB / 4 MiB probe
 //    (crates/poot-ptx-runtime/src/context.rs:643-682).
 #include "tp_common.cuh"
+#include "argmax_common.cuh"
 #include <cstring>
 
 namespace poot {
 
-__global__ void tp_begin_step_kernel(int* epoch) {
+__global__ void tp_begin_step_kernel(int* epoch, int* status) {
   pdl_wait(); pdl_launch();
-  if (threadIdx.x == 0 && blockIdx.x == 0) *epoch += 1;
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    *epoch += 1;
+    if (status != nullptr) {
+      const unsigned long long budget = *reinterpret_cast<const volatile unsigned long long*>(status + 6);
+      *reinterpret_cast<volatile unsigned long long*>(status + 2) = budget ? global_ns() + budget : 0ull;
+    }
+  }
+}
+
+// Greedy pick over vocabulary shards.  grid = rows, one warp per row.  `part_local` is this rank's stage-1 table
+// [rows, groups, 3] (value bits, global index, first non-finite index).  Each CTA copies its row's slice into every
+// peer's exchange area, the last CTA to finish publishes the exchange number on channel TP_CH_AX, then each CTA
+// waits (bounded) for the peers' tables of the same exchange and reduces all of them for its row.  The exchange
+// number lives in `ax_count` (device memory, read by every CTA before its ticket, advanced by the last CTA), the
+// areas are double-buffered on its parity: a rank can only reach exchange n + 2 after every peer has signalled
+// something later than its own combine of exchange n, because each step in between waits on all peers.
+__global__ void __launch_bounds__(32)
+tp_argmax_exchange_kernel(const int* __restrict__ part_local, int rows, int groups, int ax_cap, int bad_none,
+                          int* __restrict__ out, int* ax_count, int* __restrict__ status,
+                          const __grid_constant__ TpArgs tp) {
+  __shared__ int s_ok;
+  pdl_wait(); pdl_launch();
+  const int row = blockIdx.x, l = threadIdx.x;
+  const uint32_t target = (uint32_t)*reinterpret_cast<const volatile int*>(ax_count) + 1u;
+  const int parity = (int)(target & 1u);
+  const int n = groups * 3;
+  const int* src = part_local + (size_t)row * n;
+  const size_t slot = (size_t)(parity * tp.world + tp.rank) * ax_cap + (size_t)row * n;
+  for (int d = 0; d < tp.world; ++d) {
+    if (d == tp.rank) continue;
+    int* dst = tp.ax_peer[d] + slot;
+    for (int e = l; e < n; e += 32) dst[e] = src[e];
+  }
+  tp_signal_all(tp, TP_CH_AX, target, (int)gridDim.x, status, ax_count);
+  if (l == 0) {
+    bool ok = true;
+    for (int r = 0; r < tp.world && ok; ++r) {
+      if (r == tp.rank) continue;
+      int why = tp_wait_flag(tp.flags_local, tp.world, TP_CH_AX, r, target, status);
+      if (why == 0 && ld_acquire_sys(tp.flags_local + TP_CH_POISON * TP_MAX_WORLD + r) != 0u) why = (int)kPeerFailed;
+      if (why != 0) { ctl_fail(status, why, (1 << 20) + r); ok = false; }
+    }
+    s_ok = ok ? 1 : 0;
+  }
+  __syncthreads();
+  Cand c{0.f, -1}; int b = bad_none;
+  if (s_ok) {
+    for (int e = l; e < tp.world * groups; e += 32) {
+      const int pt = e / groups, g = e - pt * groups;
+      const int* p = (pt == tp.rank) ? src + g * 3
+                                     : tp.ax_peer[tp.rank] + (size_t)(parity * tp.world + pt) * ax_cap + (size_t)row * n + g * 3;
+      // peers wrote these words: read them past L1
+      Cand t{__int_as_float(__ldcg(p)), __ldcg(p + 1)};
+      c = better(c, t);
+      b = min(b, __ldcg(p + 2));
+    }
+  }
+  c = warp_best(c); b = warp_min_i(b);
+  if (l == 0) {
+    const bool nf = b < bad_none;
+    out[row * 2] = (nf || c.i < 0) ? 0 : c.i;
+    out[row * 2 + 1] = nf ? b : -1;
+  }
 }
 
 template <int THREADS, int MAXV>
@@ -37,13 +103,8 @@ tp_norm_kernel(__nv_bfloat16* __restrict__ h_shard,            // [S, H] residua
   uint32_t rs_target = 0;
   if (has_in) {
     rs_target = tp_target(tp, tp.rs_site, tp.rs_sites);
-    if (threadIdx.x == 0) {
-      bool ok = true;
-      for (int r = 0; r < tp.world; ++r)
-        if (!wait_flag_ge(tp.flags_local + TP_CH_RS * TP_MAX_WORLD + r, rs_target, status)) ok = false;
-      if (!ok) atomicExch(status, (int)kTimeoutPeerFlag);
-      s_ok = ok ? 1 : 0;
-    }
+    if (threadIdx.x == 0)
+      s_ok = tp_wait_all(tp.flags_local, tp.world, TP_CH_RS, rs_target, tp.rs_site, status) ? 1 : 0;
     __syncthreads();
   }
   const int in_parity = (int)(rs_target & 1u);
@@ -111,7 +172,7 @@ tp_norm_kernel(__nv_bfloat16* __restrict__ h_shard,            // [S, H] residua
       for (int d = 0; d < tp.world; ++d) reinterpret_cast<uint4*>(tp.xs_peer[d] + xoff)[c] = pk;
     }
   }
-  tp_signal_all(tp, TP_CH_AG, ag_target, (int)gridDim.x);
+  tp_signal_all(tp, TP_CH_AG, ag_target, (int)gridDim.x, status);
 }
 
 // Writes a pattern of n 32-bit words into `dst` (a peer mapping) / checks it in local memory.
@@ -149,9 +210,48 @@ POOT_API int poot_ipc_open(const void* handle, void** out) {
 }
 POOT_API int poot_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 
-POOT_API int poot_tp_begin_step(int* epoch, cudaStream_t s) {
-  return launch_k(tp_begin_step_kernel, dim3(1), dim3(32), 0, s, epoch);
+// First kernel of a tensor-parallel step: epoch += 1, control block deadline = now + the block's step budget.
+POOT_API int poot_tp_begin_step(int* epoch, int* status, cudaStream_t s) {
+  return launch_k(tp_begin_step_kernel, dim3(1), dim3(32), 0, s, epoch, status);
 }
+
+// Greedy pick over `world` vocabulary shards through the symmetric block (no library collective).
+//   part_local [rows, groups, 3] int32, ax_peer[r] = rank r's exchange area [2][world][ax_cap] int32 with
+//   rows * groups * 3 <= ax_cap, ax_count = device counter of exchanges done, out [rows, 2] int32.
+POOT_API int poot_tp_argmax_exchange(const int* part_local, int rows, int groups, int ax_cap, int vocab_total, int* out,
+                                     int* ax_count, int world, int rank, void* flags_local, void* const* flags_peer,
+                                     void* const* ax_peer, int* ticket, int* status, cudaStream_t s) {
+  if (rows <= 0) return 0;
+  if (world < 2 || world > TP_MAX_WORLD || groups < 1 || (long long)rows * groups * 3 > (long long)ax_cap)
+    return (int)cudaErrorInvalidValue;
+  if (status == nullptr || ax_count == nullptr || ticket == nullptr) return (int)cudaErrorInvalidValue;
+  TpArgs tp = {};
+  tp.world = world; tp.rank = rank; tp.ag_site = -1; tp.rs_site = -1;
+  tp.flags_local = (uint32_t*)flags_local; tp.ticket = ticket;
+  for (int r = 0; r < world; ++r) { tp.flags_peer[r] = (uint32_t*)flags_peer[r]; tp.ax_peer[r] = (int*)ax_peer[r]; }
+  return launch_k(tp_argmax_exchange_kernel, dim3(rows), dim3(32), 0, s, part_local, rows, groups, ax_cap, vocab_total,
+                  out, ax_count, status, tp);
+}
+
+// ---- control block: host-mapped abort word -------------------------------------------------------------------
+// The abort word lives in pinned host memory that the device reads through its mapped address, so the host can
+// set it while kernels are running (a store to device memory from the host would need a stream).
+POOT_API int poot_abort_word_alloc(int** host_ptr_out, void** device_ptr_out) {
+  int* h = nullptr;
+  cudaError_t e = cudaHostAlloc((void**)&h, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+  if (e != cudaSuccess) return (int)e;
+  *h = 0;
+  void* d = nullptr;
+  e = cudaHostGetDevicePointer(&d, h, 0);
+  if (e != cudaSuccess) { cudaFreeHost(h); return (int)e; }
+  *host_ptr_out = h;
+  *device_ptr_out = d;
+  return 0;
+}
+POOT_API void poot_abort_word_set(int* host_ptr, int value) {
+  __atomic_store_n(host_ptr, value, __ATOMIC_SEQ_CST);
+}
+POOT_API int poot_abort_word_free(int* host_ptr) { return (int)cudaFreeHost(host_ptr); }
 
 static void fill_tp(TpArgs& tp, int world, int rank, int S, int ag_site, int ag_sites, int rs_site, int rs_sites,
                     const int* epoch, void* flags_local, void* const* flags_peer, int* ticket) {

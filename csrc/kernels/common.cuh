@@ -29,7 +29,59 @@ enum Status : int {
   kTimeoutEpilogue = 3,
   kTimeoutPeerFlag = 4,
   kBadArgument = 5,
+  kAborted = 6,        // the host set the abort word while a wait was pending
+  kStepDeadline = 7,   // the step's deadline passed while a wait was pending
+  kPeerFailed = 8,     // another rank published a failure (poison word) for the current step
 };
+
+// ---- control block -----------------------------------------------------------------------------
+// Every launcher takes an `int* status`.  It points at a 16-word block in device memory, one per device:
+//
+//   [0]     first failure of a bounded wait (a Status code); written with compare-and-swap from 0, so the
+//           first cause stays and later, consequential failures do not overwrite it
+//   [1]     detail of that failure (site index, peer rank or ring slot; -1 when there is none)
+//   [2..3]  step deadline: a %globaltimer value (ns).  0 = none.  Set by the step's first kernel; every wait on
+//           another rank gives up once it has passed, so the waits of one step share ONE budget
+//   [4..5]  device-visible address of a host-mapped abort word (0 = none).  The host sets that word to make every
+//           pending and future wait return at once (drain before exit, signal handlers, watchdogs)
+//   [6..7]  the budget (ns) that the step's first kernel adds to %globaltimer to form the deadline (0 = none)
+//   [8]     number of waits that gave up since the block was last cleared (diagnostic)
+//
+// A block whose words 1.. are zero behaves like the old single status word.
+constexpr int kCtlWords = 16;
+
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool ctl_failed(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
+// Record a failure; only the first one of a step is kept.
+__device__ __forceinline__ void ctl_fail(int* status, int code, int detail = -1) {
+  if (status == nullptr) return;
+  if (atomicCAS(status, 0, code) == 0) reinterpret_cast<volatile int*>(status)[1] = detail;
+  atomicAdd(status + 8, 1);
+}
+__device__ __forceinline__ unsigned long long ctl_deadline(const int* status) {
+  return status == nullptr ? 0ull : *reinterpret_cast<const volatile unsigned long long*>(status + 2);
+}
+__device__ __forceinline__ bool ctl_host_abort(const int* status) {
+  if (status == nullptr) return false;
+  const unsigned long long a = *reinterpret_cast<const volatile unsigned long long*>(status + 4);
+  return a != 0ull && *reinterpret_cast<const volatile int*>(a) != 0;
+}
+// Why a pending wait should stop now (0 = keep waiting).  `slack_ns` is added to the step deadline: waits that
+// depend on another wait of the same kernel get a later limit than the wait they depend on.
+__device__ __forceinline__ int ctl_stop_reason(const int* status, unsigned long long slack_ns = 0ull) {
+  if (status == nullptr) return 0;
+  if (*reinterpret_cast<const volatile int*>(status) != 0) return *reinterpret_cast<const volatile int*>(status);
+  if (ctl_host_abort(status)) return (int)kAborted;
+  const unsigned long long d = ctl_deadline(status);
+  if (d != 0ull && global_ns() > d + slack_ns) return (int)kStepDeadline;
+  return 0;
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

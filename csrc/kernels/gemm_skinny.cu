@@ -89,6 +89,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       reinterpret_cast<volatile uint32_t*>(gen_base + S::BAR_OFFSET + (2 * STAGES + 1) * 8);
   float* red = reinterpret_cast<float*>(gen_base);  // [BT][ROWS] fp32, reuses the ring after the last MMA
 
+  __shared__ volatile int s_cta_fail;   // raised by the producer warp when it gives up on its ring
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t crank = CK > 1 ? cluster_ctarank() : 0u;
   const int row_tile = blockIdx.x / CK;
@@ -110,6 +111,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   constexpr uint32_t TMEM_COLS = (WM * BT) < 32 ? 32 : (WM * BT);
 
   if (threadIdx.x == 0) {
+    s_cta_fail = 0;
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar + 8 * s, 1); tc::mbar_init(empty_bar + 8 * s, 1); }
     tc::mbar_init(accum_bar, 1);
     tc::fence_barrier_init();
@@ -142,10 +144,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       if (gather) {
         const uint32_t target = tp_target(tp, tp.ag_site, tp.ag_sites);
         xrow = (int)(target & 1u) * BT;
-        // every rank pushed its normalised rows into this rank's gather buffer; wait until all have landed
-        for (int r = 0; r < tp.world; ++r)
-          if (!wait_flag_ge(tp.flags_local + TP_CH_AG * TP_MAX_WORLD + r, target, status)) ok = false;
-        if (!ok) atomicExch(status, (int)kTimeoutPeerFlag);
+        // Every rank pushed its normalised rows into this rank's gather buffer; wait until all have landed.  If a
+        // flag does not arrive the cause is recorded and the kernel goes on over whatever the buffer holds: the
+        // ring keeps moving, the kernel ends at once and the host sees the failure with the step's result.
+        tp_wait_all(tp.flags_local, tp.world, TP_CH_AG, target, tp.ag_site, status);
         fence_proxy_async_global();  // the rows were written with ordinary (peer) stores; TMA reads them
       }
       auto load_x = [&](uint32_t dst, int kx, uint32_t bar) {
@@ -166,7 +168,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         ++issued;
       }
       if (!ok) {
-        atomicExch(status, (int)kTimeoutProducer);
+        s_cta_fail = 1;
+        ctl_fail(status, (int)kTimeoutProducer, issued);
+        // let the copies already in flight land before the CTA can exit
         for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j)
           tc::mbar_wait(full_bar + 8 * (j % STAGES), (uint32_t)(j / STAGES) & 1u);
       }
@@ -178,7 +182,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int i = 0; i < num_kt; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-        if (!tc::mbar_wait(full_bar + 8 * s, ph)) { ok = false; break; }
+        // The first tile arrives only after the producer has passed griddepcontrol.wait and, in the gathered form,
+        // its wait for the peers' flags: that wait's limit is the later one.  Once one tile has landed, the rest
+        // depends on this CTA's own copies only.
+        const bool arrived = (i == 0) ? tc::mbar_wait_dependent(full_bar + 8 * s, ph, status, &s_cta_fail)
+                                      : tc::mbar_wait(full_bar + 8 * s, ph);
+        if (!arrived) { ok = false; break; }
         tc::tc_fence_after();
         const uint32_t sa = base + s * S::STAGE_BYTES;
         const uint64_t xdesc = tc::smem_desc_sw128(sa + S::W_BYTES);
@@ -192,22 +201,25 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
         tc::tc_commit(empty_bar + 8 * s);
       }
-      if (!ok) atomicExch(status, (int)kTimeoutMma);
+      if (!ok) ctl_fail(status, (int)kTimeoutMma);
       tc::tc_commit(accum_bar);
     }
   } else {
     // TMEM lane (weight row) quadrant = warp % 4; columns = tokens
     const int quad = warp & 3;
-    bool ok = tc::mbar_wait(accum_bar, 0);
-    if (!ok && lane == 0) atomicExch(status, (int)kTimeoutEpilogue);
+    // (one verdict per warp: the tensor-memory loads below are warp-wide instructions)
+    const bool ok = __all_sync(0xffffffffu, tc::mbar_wait_dependent(accum_bar, 0, status, nullptr));
+    if (!ok && lane == 0) ctl_fail(status, (int)kTimeoutEpilogue);
     tc::tc_fence_after();
 #pragma unroll 1
-    for (int wm = 0; wm < WM; ++wm) {
+    // A wait that ran out leaves the ring in an unknown state (copies may still be landing in it): the partial
+    // tile is then not written at all, the step is already marked invalid.
+    for (int wm = 0; ok && wm < WM; ++wm) {
       const int r = wm * SK_BM + quad * 32 + lane;
 #pragma unroll 1
       for (int c0 = 0; c0 < BT; c0 += 32) {
         uint32_t v[32];
-        if (num_kt > 0 && ok) {
+        if (num_kt > 0) {
           // (BT == 16, WM == 1: the allocation is 32 columns wide; the upper 16 are never written by the MMA)
           tc::tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(wm * BT + c0), v);
           tc::tmem_ld_wait();
@@ -362,7 +374,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       }
     }
   }
-  if (scatter) tp_signal_all(tp, TP_CH_RS, rs_target, (int)gridDim.x);
+  if (scatter) tp_signal_all(tp, TP_CH_RS, rs_target, (int)gridDim.x, status);
   if (CK > 1) cluster_sync_all();  // no CTA may exit while a peer still reads its tile
 }
 

@@ -166,7 +166,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         ++issued;
       }
       if (!ok) {
-        atomicExch(status, (int)kTimeoutProducer);
+        ctl_fail(status, (int)kTimeoutProducer);
         // let the copies already in flight land before the CTA can exit
         for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j)
           tc::mbar_wait(full_bar + 8 * (j % STAGES), (uint32_t)(j / STAGES) & 1u);
@@ -192,15 +192,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
         tc::tc_commit(empty_bar + 8 * s);
       }
-      if (!ok) atomicExch(status, (int)kTimeoutMma);
+      if (!ok) ctl_fail(status, (int)kTimeoutMma);
       tc::tc_commit(accum_bar);  // arrives once every MMA issued above has completed
     }
   } else {
     // ---- epilogue warps: TMEM lane quadrant = warp % 4 ----
     const int quad = warp & 3;
     const int row = m0 + quad * 32 + lane;
-    bool ok = tc::mbar_wait(accum_bar, 0);
-    if (!ok && lane == 0) atomicExch(status, (int)kTimeoutEpilogue);
+    const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(accum_bar, 0));  // one verdict per warp (warp-wide loads below)
+    if (!ok && lane == 0) ctl_fail(status, (int)kTimeoutEpilogue);
     tc::tc_fence_after();
     if (ok) {
 #pragma unroll 1

@@ -30,7 +30,10 @@ extern "C" {
 //
 // The call performs no cudaMalloc, cudaFree or any other allocating routine.  The first call on a
 // device resolves the array's device address (cudaGetSymbolAddress) and caches it for that device;
-// make that first call outside of any stream capture.  All calls share the one array, which keeps
+// make that first call outside of any stream capture.  Host threads may make their first calls at
+// the same time: each resolves the same address and stores the same value.  Head counts that are
+// not positive, or query heads that are not a multiple of the K/V heads, return
+// cudaErrorInvalidValue (1) like every other bad request.  All calls share the one array, which keeps
 // the previous call's contents: the kernels overwrite every partial they later read, so nothing has
 // to be cleared, but two calls that run concurrently on the GPU (different streams, or graphs that
 // overlap) race on it - serialise them.

@@ -14,6 +14,7 @@
 // random_uniform,sample_gumbel_argmax_batched,sample_truncated_gumbel_argmax_batched,
 // sample_topp_gumbel_argmax_batched}.rs and crates/poot-eval/src/ops/sampling.rs:40-183.
 #include "common.cuh"
+#include "argmax_common.cuh"
 #include <float.h>
 
 namespace poot {
@@ -28,25 +29,6 @@ __device__ __forceinline__ float uniform_at(uint32_t seed, uint32_t idx) {
   uint32_t x = fmix32(seed ^ (idx * 0x9E3779B9u));
   int mant = (int)(x >> 9);
   return __fmul_rn(__fadd_rn(__fmul_rn(2.0f, (float)mant), 1.0f), 5.9604645e-8f);
-}
-
-struct Cand { float v; int i; };
-__device__ __forceinline__ Cand better(Cand a, Cand b) {
-  if (b.i >= 0 && (a.i < 0 || b.v > a.v || (b.v == a.v && b.i < a.i))) return b;
-  return a;
-}
-__device__ __forceinline__ Cand warp_best(Cand c) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    Cand t; t.v = __shfl_xor_sync(0xffffffffu, c.v, o); t.i = __shfl_xor_sync(0xffffffffu, c.i, o);
-    c = better(c, t);
-  }
-  return c;
-}
-__device__ __forceinline__ int warp_min_i(int v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
 }
 
 constexpr int SAMP_THREADS = 256;

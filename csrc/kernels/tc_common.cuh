@@ -43,12 +43,40 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false on timeout.
+// Bounded wait on a barrier that only this CTA's own copies and MMAs complete: false after kWaitBudgetCycles.
+// Callers start such a wait only after griddepcontrol.wait, so a predecessor that is itself waiting (on another
+// rank, up to its step deadline) cannot make it run out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   if (mbar_try(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try(bar, parity)) {
     if (clock64() - t0 > kWaitBudgetCycles) return false;
+  }
+  return true;
+}
+
+// Bounded wait on a barrier whose completion depends on something that may legitimately last until the step
+// deadline: the kernel before this one (it may be waiting for another rank; this kernel's producer warp sits in
+// griddepcontrol.wait meanwhile), or the producer warp's own wait for peers' flags.  Its limit is later than those
+// by construction: the step deadline plus kDependentSlackNs, or kLongWaitCycles when the control block carries no
+// deadline.  It ends early only when the CTA-local failure flag is raised (the producer gave up on its ring).  It
+// deliberately does not end on a recorded failure or on the host's abort word: the waits on other ranks do, their
+// kernels then run to the end at once, and this barrier completes in the normal way microseconds later; stopping
+// here as well would stall the ring and turn one failure into a slow drain.
+constexpr unsigned long long kDependentSlackNs = 250000000ull;   // 0.25 s
+constexpr long long kLongWaitCycles = 20000000000LL;              // about 10 s
+__device__ __forceinline__ bool mbar_wait_dependent(uint32_t bar, uint32_t parity, const int* status,
+                                                    const volatile int* cta_fail) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  unsigned tries = 0;
+  while (!mbar_try(bar, parity)) {
+    if ((++tries & 255u) == 0) {
+      if (cta_fail != nullptr && *cta_fail != 0) return false;
+      const unsigned long long d = ctl_deadline(status);
+      if (d != 0ull && global_ns() > d + kDependentSlackNs) return false;
+      if (clock64() - t0 > kLongWaitCycles) return false;
+    }
   }
   return true;
 }

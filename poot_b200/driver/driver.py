@@ -133,6 +133,11 @@ class Driver:
 
     def __init__(self, engine, num_blocks: int, max_rows: int, max_seq_len: int, vocab: int, prefill_chunk: int = 512,
                  prefix_caching: bool = True, eos_token: Optional[int] = None, prefill_budget: Optional[int] = None):
+        # every step is a guarded transaction: validation before launch, NeedsReset after a failure, Poisoned when the
+        # clean-up fails too (runtime/lifecycle.py)
+        from ..runtime.lifecycle import GuardedStepEngine, StepLimits
+        if not isinstance(engine, GuardedStepEngine):
+            engine = GuardedStepEngine(engine, StepLimits.of(engine, vocab), on_reset=self._drop_everything)
         self.engine = engine
         self.pool = BlockPool(num_blocks)
         self.prefix = PrefixCache(self.pool) if prefix_caching else None
@@ -156,7 +161,7 @@ class Driver:
     def can_open(self, prompt_len: int, max_tokens: int) -> bool:
         need = blocks_for(min(prompt_len + max_tokens, self.max_seq_len))
         free = self.pool.available
-        return bool(self._free_rows) and need <= free + (len(self.prefix) if self.prefix is not None else 0)
+        return bool(self._free_rows) and need <= free + (self.prefix.reclaimable() if self.prefix is not None else 0)
 
     def open(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, identity: int = BASE_IDENTITY,
              guided=None, adapter_slot: int = -1, embeds=None, rope_positions=None) -> int:
@@ -383,6 +388,20 @@ class Driver:
             else:
                 out.append(RowResult(s.id, None, piece))
         return out
+
+    def reset(self) -> None:
+        """Complete reset after a failed step (``NeedsReset``): the engine restores its state and every open sequence,
+        its blocks and the prefix cache are dropped, because K/V written by the failed step cannot be trusted."""
+        self.engine.reset()
+
+    def _drop_everything(self) -> None:
+        for sid in list(self.seqs):
+            s = self.seqs.pop(sid)
+            for b in s.blocks:
+                self.pool.release(b)
+            self._free_rows.append(s.row)
+        if self.prefix is not None:
+            self.prefix.evict_unused(0)
 
     def commit(self, seq_id: int, tokens: Sequence[int]) -> None:
         s = self.seqs[seq_id]

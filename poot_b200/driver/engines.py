@@ -83,6 +83,8 @@ class DeviceStepEngine:
         self.h_params, self.h_topk, self.h_seeds = buf((B, 4), torch.float32), buf(B, torch.int32), buf(B, torch.int32)
         self.h_picked, self.h_logprobs = buf((B, 2), torch.int32), buf(B, torch.float32)
         self.h_bt = buf((engine.max_seqs, engine.max_blocks), torch.int32)
+        self.h_status = buf(16, torch.int32)   # the device control block, read back with every step's result
+        self.status_hook = None                # tests: callable returning (code, detail) in place of the device's block
         self.device_timing = False           # bracket each step with CUDA events (opt-in: it adds a synchronisation)
         self.last_device_ms = None           # None = not measured
         self.last_run_ms = None
@@ -144,12 +146,68 @@ class DeviceStepEngine:
         self.h_picked[:B].copy_(e.picked[:B], non_blocking=True)
         if inp.want_logprobs:
             self.h_logprobs[:B].copy_(e.logprobs[:B], non_blocking=True)
-        if e.device.type == "cuda":
+        on_device = e.device.type == "cuda"
+        if on_device:
+            # the control block rides the same stream as the result: no extra synchronisation
+            from ..ops import cuda_ops as K
+            self.h_status.copy_(K.status_word(e.device), non_blocking=True)
             torch.cuda.current_stream().synchronize()
+        self._raise_on_failed_wait(on_device)
         self.last_run_ms = (_time.perf_counter() - t0) * 1e3
         self.last_device_ms = ev[0].elapsed_time(ev[1]) if ev is not None else None
         self.last_launches = e.launches_per_step.get(e._key(shape), 0)
         return self.h_picked[:B].numpy().copy(), (self.h_logprobs[:B].numpy().copy() if inp.want_logprobs else None)
+
+    def abort(self) -> None:
+        """Watchdog / signal-handler hook: every pending and future wait on another rank gives up at once."""
+        if self.e.device.type == "cuda":
+            from ..ops import cuda_ops as K
+            K.request_abort(self.e.device)
+
+    def abort_cleanup(self) -> None:
+        """Clean-up after a failed step: make pending waits give up, let the device go idle, clear the control block."""
+        if self.e.device.type != "cuda":
+            return
+        from ..ops import cuda_ops as K
+        K.request_abort(self.e.device)
+        try:
+            self.torch.cuda.synchronize(self.e.device)
+        finally:
+            K.clear_abort(self.e.device)
+        st = K.status_word(self.e.device)
+        st[0:4].zero_()
+        st[8:9].zero_()
+
+    def reset_state(self) -> None:
+        """The engine's part of a complete reset: recurrent and convolution state start from zero, the K/V pool's
+        contents are dropped by the owner (its blocks return to the free list), and a tensor-parallel group starts its
+        cross-rank counters over together."""
+        e = self.e
+        for name in ("gdn_state", "gdn_conv_state", "ssm_state", "ssm_conv_state"):
+            t = getattr(e, name, None)
+            if t is not None:
+                t.zero_()
+        comm = getattr(e, "comm", None)
+        if comm is not None and hasattr(comm, "reset"):
+            comm.reset()
+
+    def _raise_on_failed_wait(self, on_device: bool) -> None:
+        """A wait that gave up inside the step makes its tokens invalid: they must not reach a client.  The typed
+        error leaves through the scheduler's guard, which fails the live requests and marks the engine dead."""
+        if self.status_hook is not None:
+            code, detail = self.status_hook()
+        elif on_device:
+            code, detail = int(self.h_status[0]), int(self.h_status[1])
+        else:
+            return
+        if code != 0:
+            from ..ops import cuda_ops as K
+            if on_device and self.status_hook is None:
+                st = K.status_word(self.e.device)
+                st[0:2].zero_()
+                st[8:9].zero_()
+            raise K.DeviceWaitTimeout(f"device wait timed out in {K.describe_status(code, detail)}; the step's "
+                                      "tokens were discarded", code, detail)
 
     def last_logits(self, rows: int) -> np.ndarray:
         """Whole-vocabulary logits of the last step's sampling rows (single-rank engines only)."""

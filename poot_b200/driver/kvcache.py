@@ -44,6 +44,7 @@ def _lib():
         lib.poot_prefix_register.argtypes = [P, P, c_uint64, P, c_int, P, c_int]
         lib.poot_prefix_evict_unused.argtypes = [P, P, c_int]
         lib.poot_prefix_drop_identity.argtypes = [P, P, c_uint64]
+        lib.poot_prefix_count_unused.argtypes = [P, P]
         lib.poot_chain_hash.argtypes = [c_uint64, P]
         lib.poot_chain_hash.restype = c_uint64
         lib.poot_chain_root.restype = c_uint64
@@ -131,6 +132,10 @@ class PrefixCache:
         blk = np.ascontiguousarray(blocks, dtype=np.int32)
         return self.lib.poot_prefix_register(self.h, self.pool.h, identity, toks.ctypes.data, len(toks),
                                              blk.ctypes.data, len(blk))
+
+    def reclaimable(self) -> int:
+        """Cached blocks that no live sequence shares: what ``evict_unused`` can give back."""
+        return self.lib.poot_prefix_count_unused(self.h, self.pool.h)
 
     def evict_unused(self, want: int = 0) -> int:
         return self.lib.poot_prefix_evict_unused(self.h, self.pool.h, want)

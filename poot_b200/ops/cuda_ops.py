@@ -146,31 +146,105 @@ def _need_cuda(*ts):
 
 
 _status = {}
+_abort = {}            # device -> (host pointer of the mapped abort word, device-visible address)
+CTL_WORDS = 16         # control block: [0] first failure, [1] detail, [2:4] deadline ns, [4:6] abort-word address,
+                       # [6:8] step budget ns, [8] waits given up (csrc/kernels/common.cuh)
+DEFAULT_STEP_BUDGET_S = 5.0
+
+STATUS_NAMES = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "peer flag", 5: "bad argument",
+                6: "host abort", 7: "step deadline", 8: "peer failed"}
+
+
+def _canon(device=None) -> torch.device:
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    if dev.index is None:       # "cuda" and "cuda:N" must name the same block
+        dev = torch.device("cuda", torch.cuda.current_device())
+    return dev
 
 
 def status_word(device=None) -> torch.Tensor:
-    """Per-device int32 word that kernels with bounded waits set non-zero when a wait ran out."""
-    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-    if dev.index is None:       # "cuda" and "cuda:N" must name the same word
-        dev = torch.device("cuda", torch.cuda.current_device())
+    """Per-device control block (``CTL_WORDS`` int32 words) that every launcher receives as its ``status`` pointer.
+
+    Word 0 is the first failure of a bounded wait since the block was last cleared; the block also carries the
+    step deadline, the step budget and the address of a host-mapped abort word (see ``request_abort``)."""
+    dev = _canon(device)
     s = _status.get(dev)
     if s is None:
-        s = torch.zeros(1, dtype=torch.int32, device=dev)
+        s = torch.zeros(CTL_WORDS, dtype=torch.int32, device=dev)
         _status[dev] = s
+        lib = kernels()
+        lib.poot_abort_word_alloc.argtypes = [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)]
+        lib.poot_abort_word_set.argtypes = [c_void_p, c_int]
+        lib.poot_abort_word_set.restype = None
+        hp, dp = c_void_p(), c_void_p()
+        with torch.cuda.device(dev):
+            check(lib.poot_abort_word_alloc(ctypes.byref(hp), ctypes.byref(dp)), "abort_word_alloc")
+        _abort[dev] = (hp.value, dp.value)
+        s[4:6].copy_(torch.tensor([dp.value], dtype=torch.int64).view(torch.int32))
+        set_step_budget(DEFAULT_STEP_BUDGET_S, dev)
     return s
+
+
+def set_step_budget(seconds: float, device=None) -> None:
+    """Budget shared by all cross-rank waits of one tensor-parallel step (0 = no deadline: each wait has its own
+    limit of about a second)."""
+    s = _status.get(_canon(device))
+    if s is None:
+        s = status_word(device)
+    ns = int(max(0.0, seconds) * 1e9)
+    s[6:8].copy_(torch.tensor([ns], dtype=torch.int64).view(torch.int32))
+    s[2:4].zero_()      # a deadline left by an earlier step must not end the waits of a program that sets none
+
+
+def request_abort(device=None) -> None:
+    """Host side of the abort word: every pending and future cross-rank wait on the device gives up at once, so
+    queued kernels run to their end and ``torch.cuda.synchronize`` returns.  Plain host store (async-signal-safe
+    once the block exists); it works while kernels are running.  Call ``clear_abort`` before using the device again."""
+    devs = [_canon(device)] if device is not None else list(_abort)
+    for d in devs:
+        if d in _abort:
+            kernels().poot_abort_word_set(_abort[d][0], 1)
+
+
+def clear_abort(device=None) -> None:
+    devs = [_canon(device)] if device is not None else list(_abort)
+    for d in devs:
+        if d in _abort:
+            kernels().poot_abort_word_set(_abort[d][0], 0)
 
 
 class DeviceWaitTimeout(RuntimeError):
     """A bounded device-side wait ran out; the kernel returned early and its output is invalid."""
 
+    def __init__(self, message: str, code: int = 0, detail: int = -1):
+        super().__init__(message)
+        self.code, self.detail = code, detail
+
+
+def read_status(device=None):
+    """``(code, detail, waits_given_up)`` of the control block (synchronises the device)."""
+    words = status_word(device)[:9].tolist()
+    return words[0], words[1], words[8]
+
+
+def describe_status(code: int, detail: int) -> str:
+    what = STATUS_NAMES.get(code, str(code))
+    if code in (4, 7, 8) and detail >= 0:
+        if detail >= (1 << 20):
+            return f"{what} (greedy-pick exchange, waiting for rank {detail - (1 << 20)})"
+        return f"{what} (site {detail // 16}, waiting for rank {detail % 16})"
+    return what
+
 
 def check_status(device=None) -> None:
-    s = status_word(device)
-    code = int(s.item())
+    """Raise ``DeviceWaitTimeout`` if a wait gave up since the last check; the failure words are cleared."""
+    code, detail, gave_up = read_status(device)
     if code != 0:
-        s.zero_()
-        names = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue", 4: "peer flag", 5: "bad argument"}
-        raise DeviceWaitTimeout(f"device wait timed out in {names.get(code, code)}")
+        s = status_word(device)
+        s[0:2].zero_()
+        s[8:9].zero_()
+        raise DeviceWaitTimeout(f"device wait timed out in {describe_status(code, detail)}"
+                                f" ({gave_up} wait(s) gave up)", code, detail)
 
 
 # ----------------------------------------------------------------------------------------------------------------

@@ -65,6 +65,16 @@ class NcclComm:
             # flat views: the same bytes, and the form every backend of the process group accepts
             dist.all_gather_into_tensor(out.view(-1), inp.reshape(-1), group=self.group)
 
+    def rendezvous(self) -> None:
+        """Host rendezvous of all ranks with the device idle on both sides: everything queued so far has finished
+        on every rank when this returns.  Called before the first launch of any program whose kernels wait on other
+        ranks, so no rank can start such a program seconds ahead of its peers."""
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
 
 class FusedComm(NcclComm):
     """In-kernel NVLink reduce-scatter / all-gather fused with the projections' GEMMs."""
@@ -88,20 +98,29 @@ class FusedComm(NcclComm):
         inbox_bytes = 2 * w * self.MAX_ROWS * H * 2   # one-shot form: a slot holds up to MAX_ROWS rows
         self.off_xs = self.off_inbox + (inbox_bytes + 1023) // 1024 * 1024
         xs_bytes = 2 * self.MAX_ROWS * H * 2
-        total = self.off_xs + (xs_bytes + 1023) // 1024 * 1024
+        self.off_ax = self.off_xs + (xs_bytes + 1023) // 1024 * 1024
+        # greedy-pick exchange: [2][world][ax_cap] int32, one stage-1 table [rows, groups, 3] per rank and parity
+        self.ax_cap = engine.max_seqs * K.argmax_groups(max(1, engine.cfg.vocab // w)) * 3
+        ax_bytes = 2 * w * self.ax_cap * 4
+        total = self.off_ax + (ax_bytes + 1023) // 1024 * 1024
         self.block = SymmetricBlock(total, self.rank, w, self.device, self.group)
         if self.probe_links:
             self.block.probe(self.group)
         self.flags_peer = self.block.ptr_array(self.off_flags)
         self.inbox_peer = self.block.ptr_array(self.off_inbox)
         self.xs_peer = self.block.ptr_array(self.off_xs)
+        self.ax_peer = self.block.ptr_array(self.off_ax)
+        self.ax_count = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.h_shard = torch.zeros(self.s_max, H, dtype=torch.bfloat16, device=self.device)
         L = engine.cfg.n_layers
         self.rs_sites = 2 * L
         self.ag_sites = 2 * L + 1
-        K.register_signature("poot_tp_begin_step", [_P, _P])
+        K.register_signature("poot_tp_begin_step", [_P, _P, _P])
+        K.register_signature("poot_tp_argmax_exchange", [_P, c_int, c_int, c_int, c_int, _P, _P, c_int, c_int, _P, _P, _P,
+                                                         _P, _P, _P])
+        self._exchange = K.fn("poot_tp_argmax_exchange")
         K.register_signature("poot_tp_norm", [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
                                               c_int, c_int, _P, _P, _P, _P, _P, _P])
         K.register_signature("poot_gemm_skinny_tp", [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -122,7 +141,18 @@ class FusedComm(NcclComm):
 
     # ---- launches -------------------------------------------------------------------------------------------
     def begin_step(self) -> None:
-        check(self._begin(self.epoch.data_ptr(), K._stream()), "tp_begin_step")
+        """First launch of a fused step: advances the epoch and starts the step's wait budget."""
+        check(self._begin(self.epoch.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()), "tp_begin_step")
+
+    def argmax_exchange(self, part: torch.Tensor, rows: int, groups: int, vocab_total: int, out: torch.Tensor) -> None:
+        """Greedy pick over the ranks' vocabulary shards: push this rank's stage-1 table ``part`` [rows, groups, 3]
+        into every peer's exchange area and combine the tables received, in one kernel and without a library
+        collective (a fused step's graph holds no library collective at all)."""
+        b = self.block
+        check(self._exchange(part.data_ptr(), rows, groups, self.ax_cap, vocab_total, out.data_ptr(),
+                             self.ax_count.data_ptr(), self.world, self.rank, b.ptr(self.rank, self.off_flags),
+                             self.flags_peer, self.ax_peer, self.ticket.data_ptr(),
+                             K.status_word(self.device).data_ptr(), K._stream()), "tp_argmax_exchange")
 
     def norm_oneshot(self, h: torch.Tensor, w: torch.Tensor, x_out: torch.Tensor, rows: int, eps: float,
                      rs_site: int) -> None:
@@ -171,14 +201,43 @@ class FusedComm(NcclComm):
                          self.H, 0, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
               "gemm_skinny_tp")
 
+    def reset(self) -> None:
+        """Collective restart of the cross-rank protocol after a failed step: every rank drains, all meet, each zeroes
+        its own block (flags, poison words, inboxes) and its counters, all meet again.  Between the two meetings no rank
+        launches anything, so no rank can see a half-cleared peer."""
+        self.drain()
+        K.clear_abort(self.device)
+        self.rendezvous()
+        self.block.local_tensor(0, (self.block.nbytes,), torch.uint8).zero_()
+        self.epoch.zero_()
+        self.ticket.zero_()
+        self.ax_count.zero_()
+        self.rendezvous()
+
+    def drain(self) -> None:
+        """Make every kernel of this rank that is waiting on a peer give up (host abort word), then wait for the
+        device to go idle.  After this no kernel of this rank is resident, so the process can unmap peers' memory and
+        exit without tearing a context down under a waiting kernel."""
+        K.request_abort(self.device)
+        torch.cuda.synchronize(self.device)
+
     def close(self) -> None:
         if self.block is not None:
-            torch.cuda.synchronize(self.device)
+            self.drain()
             self.block.close()
             self.block = None
+            K.clear_abort(self.device)
+
+
+# What "auto" means wherever a tensor-parallel group is built without an explicit choice.  The fused programs are the
+# product path; they are selected explicitly (``--comm fused``) until they have been re-validated on more than two
+# GPUs with the step deadline, abort word and rendezvous rules in place.
+DEFAULT_COMM = "nccl"
 
 
 def make_comm(kind: str, rank: int, world: int, device: torch.device, group=None):
+    if kind == "auto":
+        kind = DEFAULT_COMM
     if kind == "nccl":
         return NcclComm(rank, world, device, group)
     if kind == "fused":

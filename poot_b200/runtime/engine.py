@@ -375,19 +375,38 @@ class DecoderEngine:
             return 1
         return max(1, min(self.attn_splits_max, 296 // ctas))
 
+    def _fused_shape(self, shape: StepShape) -> bool:
+        """Whether this step runs one of the fused tensor-parallel programs (kernels that wait on other ranks).
+
+        A step is either fused or it rides the library collectives, never both: a fused step's graph holds no library
+        collective (the greedy pick is exchanged through the symmetric block), and a step that needs the full logits on
+        every rank (sampling rules, logit adjustments, log-probabilities) takes the library path as a whole."""
+        cfg, w, comm = self.cfg, self.w, self.comm
+        if comm is None or not getattr(comm, "fused", False):
+            return False
+        if shape.sampler != 0 or shape.adjust or shape.logprobs:
+            return False
+        if isinstance(w.layers[0].wqkv, K.QuantWeight) or isinstance(w.layers[0].wo, K.QuantWeight):
+            return False
+        T = shape.tokens
+        if cfg.is_moe:
+            # expert parallelism with one expert per rank rides the one-shot path (the combine is the fused all-reduce)
+            fusable = w.ep_world == self.tp and w.layers[0].ex_wgu is not None and w.layers[0].ex_wgu.shape[0] == 1
+            return bool(fusable and comm.oneshot_ok(T))
+        if comm.oneshot_ok(T) and self.tp_mode != "rs_ag":
+            return True
+        return bool(comm.rows_for(T))
+
     def forward(self, shape: StepShape) -> None:
         """Launch the whole step on the current stream (eagerly or under capture)."""
         cfg, w = self.cfg, self.w
         T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
-        packed = isinstance(w.layers[0].wqkv, K.QuantWeight) or isinstance(w.layers[0].wo, K.QuantWeight)
-        # expert parallelism with one expert per rank rides the one-shot path (the combine is the fused all-reduce)
-        moe_fusable = cfg.is_moe and w.ep_world == self.tp and w.layers[0].ex_wgu is not None and w.layers[0].ex_wgu.shape[0] == 1
-        if self.comm is not None and getattr(self.comm, "fused", False) and not packed and (not cfg.is_moe or moe_fusable):
+        self._fused_step = False
+        if self._fused_shape(shape):
+            self._fused_step = True
             if self.comm.oneshot_ok(T) and (self.tp_mode != "rs_ag" or cfg.is_moe):
                 return self._forward_tp_oneshot(shape)
-            R = self.comm.rows_for(T)
-            if R and not cfg.is_moe:
-                return self._forward_tp_fused(shape, R)
+            return self._forward_tp_fused(shape, self.comm.rows_for(T))
         self._launch_counter = 0
         h = self.h[:T]
         staged = self.stage is not None and self.stage.count > 1
@@ -674,10 +693,14 @@ class DecoderEngine:
                 part = self.argmax_part_local[:B * G * 3].view(B, G, 3)
                 self._count()
                 K.argmax_partials(local_logits, self.w.tp_rank * vl, V, part)
-                allp = self.argmax_part_all[:self.tp * B * G * 3].view(self.tp, B, G, 3)
-                self.comm.all_gather(allp, part)
-                self._count()
-                K.argmax_combine(allp, B, G, V, self.picked[:B])
+                if getattr(self, "_fused_step", False):
+                    self._count()
+                    self.comm.argmax_exchange(part, B, G, V, self.picked[:B])
+                else:
+                    allp = self.argmax_part_all[:self.tp * B * G * 3].view(self.tp, B, G, 3)
+                    self.comm.all_gather(allp, part)
+                    self._count()
+                    K.argmax_combine(allp, B, G, V, self.picked[:B])
             else:
                 gathered = self.logits_gather[:self.tp * B * vl].view(self.tp, B, vl)
                 self.comm.all_gather(gathered, local_logits.contiguous() if local_logits.stride(0) != vl else local_logits)
@@ -826,17 +849,28 @@ class DecoderEngine:
         key = self._key(shape)
         if key in self._graphs or not self.use_graphs:
             return
+        # A program whose kernels wait on other ranks starts on every rank together: host rendezvous with the devices
+        # idle before the eager warm-up forward, and again before the first replay of the captured graph.  Without it
+        # a rank that finished its set-up seconds earlier would sit in device-side waits while its peers are still
+        # building tensor maps, and would run out of its step budget for no fault of any rank.
+        multi = self.comm is not None and self.tp > 1
+        if multi:
+            self.comm.rendezvous()
         s = torch.cuda.Stream(device=self.device)
         s.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(s):
             self.forward(shape)  # warm-up: tensor-map cache, function attributes
         torch.cuda.current_stream(self.device).wait_stream(s)
         torch.cuda.synchronize(self.device)
+        if multi:
+            K.check_status(self.device)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s):
             self.forward(shape)
         self._graphs[key] = g
         self.launches_per_step[key] = self._launch_counter
+        if multi:
+            self.comm.rendezvous()
 
     def run(self, shape: StepShape) -> None:
         """Replay (or eagerly launch) one step; inputs must already be in the static buffers."""

@@ -44,9 +44,13 @@ def main(argv=None) -> int:
             pp = world
         else:
             from ..parallel.tp import make_comm
-            comm = make_comm(_comm_kind(cfg.model), rank, world, torch.device("cuda", torch.cuda.current_device()))
+            kind = _comm_kind(cfg.model) if cfg.comm == "auto" else cfg.comm
+            comm = make_comm(kind, rank, world, torch.device("cuda", torch.cuda.current_device()))
+        from ..ops import cuda_ops as _K
+        _K.set_step_budget(cfg.device_step_budget_secs)
         from .follower import init_control_group
-        init_control_group()
+        init_control_group(ready_deadline=cfg.ready_deadline_secs, step_deadline=max(cfg.step_deadline_secs, 1.0),
+                           heartbeat_timeout=cfg.rank_heartbeat_timeout_secs)
     if _is_encoder_checkpoint(cfg.model):
         return _serve_encoder(cfg)
     if cfg.model == "fake":
@@ -71,8 +75,10 @@ def main(argv=None) -> int:
     if world > 1:
         from .follower import follow, LeaderStepEngine
         if rank != 0:
-            follow(llm.driver.engine)
-            _leave(llm)
+            _drain_on_signal()
+            cause = follow(llm.driver.engine)
+            print(f"poot-serve rank {rank}: leaving ({cause})", file=sys.stderr, flush=True)
+            _leave(llm, collective=cause == "shutdown")
         llm.driver.engine = LeaderStepEngine(llm.driver.engine)
     template = cfg.chat_template
     if cfg.chat_template_file:
@@ -115,7 +121,7 @@ def main(argv=None) -> int:
         if hasattr(llm.driver.engine, "device_timing"):
             llm.driver.engine.device_timing = True
     engine = ServeEngine(llm.driver, llm.tokenizer, Metrics(), cfg.max_pending_requests, cfg.max_queue_wait_secs,
-                         draft=draft, timing=timing)
+                         draft=draft, timing=timing, step_deadline=cfg.step_deadline_secs or None)
     state = ServerState(engine, cfg, cfg.model_id or os.path.basename(cfg.model.rstrip("/")) or "model",
                         family=llm.cfg.family if llm.cfg is not None else "llama", chat_template=template)
     handle = getattr(llm, "handle", None)
@@ -132,11 +138,9 @@ def main(argv=None) -> int:
     stop.wait()
     server.shutdown()
     if world > 1:
-        try:
-            llm.driver.engine.stop_followers()
-        except RuntimeError:      # the launcher already signalled the followers: nothing left to stop
-            os._exit(0)
-        _leave(llm)
+        clean = engine.state != "dead"
+        llm.driver.engine.stop_followers("shutdown" if clean else (engine.cause or "engine dead"))
+        _leave(llm, collective=clean)
     llm.close()
     return 0
 
@@ -146,15 +150,16 @@ def _comm_kind(model: str) -> str:
     attention stack shards the same way over the library collectives."""
     import json
     path = os.path.join(model, "config.json")
+    from ..parallel.tp import DEFAULT_COMM
     if not os.path.isfile(path):
-        return "fused"
+        return DEFAULT_COMM
     from ..models.registry import Registry, UnsupportedFamily
     try:
         with open(path) as f:
             cfg = Registry.builtin().resolve_hf(json.load(f)).cfg
     except (UnsupportedFamily, KeyError, ValueError):
-        return "fused"                   # the load that follows reports what is wrong with the checkpoint
-    return "fused" if getattr(cfg, "plain_block", True) else "nccl"
+        return DEFAULT_COMM              # the load that follows reports what is wrong with the checkpoint
+    return DEFAULT_COMM if getattr(cfg, "plain_block", True) else "nccl"
 
 
 def _prove_ranges(model_cfg, cfg) -> None:
@@ -197,15 +202,38 @@ def _serve_encoder(cfg) -> int:
     return 0
 
 
-def _leave(llm) -> None:
-    """Multi-rank exit: meet, release the peer mappings, and leave without running the process group's destructors
-    (tearing down a group that owns captured collectives can block)."""
+def _drain_on_signal() -> None:
+    """A follower that is told to terminate must not exit under a kernel that is waiting for a peer: the handler sets
+    the abort word, waits for the device to go idle and only then leaves."""
+    def handler(*_):
+        import torch
+        from ..ops import cuda_ops as K
+        K.request_abort()
+        try:
+            torch.cuda.synchronize()
+        finally:
+            os._exit(0)
+    for sig in (signal.SIGINT, signal.SIGTERM):
+        signal.signal(sig, handler)
+
+
+def _leave(llm, collective: bool = True) -> None:
+    """Multi-rank exit.  First make sure no kernel of this rank is resident: set the abort word (any wait on another
+    rank returns at once) and synchronise.  After a clean stop the ranks then meet at a barrier before they release the
+    peer mappings; after a failure there is no barrier, because a rank may be gone.  The process then leaves without
+    running the process group's destructors (tearing down a group that owns captured collectives can block)."""
     import torch
     import torch.distributed as dist
+    from ..ops import cuda_ops as K
+    K.request_abort()
     torch.cuda.synchronize()
-    dist.barrier()
+    if collective:
+        K.clear_abort()
+        dist.barrier()
+        torch.cuda.synchronize()
     llm.close()
     sys.stdout.flush()
+    sys.stderr.flush()
     os._exit(0)
 
 

@@ -38,6 +38,11 @@ class ServeConfig:
     request_timeout_secs: float = 30.0
     write_timeout_secs: float = 30.0
     drain_timeout_secs: float = 30.0
+    step_deadline_secs: float = 30.0     # a step still running after this is declared lost: the engine goes dead (0 = off)
+    device_step_budget_secs: float = 5.0  # budget shared by all cross-rank waits inside one step's kernels
+    ready_deadline_secs: float = 5.0     # multi-rank: every follower must say it is about to launch a step within this
+    rank_heartbeat_timeout_secs: float = 3.0
+    comm: str = "auto"                   # auto | fused | nccl: collectives of a tensor-parallel group
     device_timing: bool = False
     timing_max_steps: int = 4096
     timing_max_dispatch_records: int = 65536
@@ -60,6 +65,10 @@ class ServeConfig:
         bound("rows", 1, 1024); bound("max_seq", 128, 1 << 20); bound("prefill_chunk", 16, 8192)
         bound("max_pending_requests", 1, 1 << 16); bound("max_body_mib", 1, 1024); bound("kv_fraction", 0.05, 0.98)
         bound("max_queue_wait_secs", 0.1, 3600); bound("drain_timeout_secs", 0, 3600)
+        bound("step_deadline_secs", 0, 3600); bound("device_step_budget_secs", 0, 600)
+        bound("ready_deadline_secs", 0.05, 600); bound("rank_heartbeat_timeout_secs", 0.2, 600)
+        if self.comm not in ("auto", "fused", "nccl"):
+            raise ValueError(f"--comm {self.comm!r}: expected auto, fused or nccl")
         bound("timing_max_steps", 1, 1 << 24); bound("timing_max_dispatch_records", 1, 1 << 28)
         bound("timing_max_in_flight_queries", 1, 1 << 16); bound("timing_sample_every", 1, 1 << 20)
         bound("draft_mtp", 0, 16); bound("expert_pool", 0, 1 << 16)

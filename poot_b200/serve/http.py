@@ -9,6 +9,7 @@ Surface (website/docs/serve/api.md:33-76): ``POST /v1/completions``, ``POST /v1/
 """
 from __future__ import annotations
 
+import hmac
 import json
 import queue
 import socket
@@ -371,7 +372,7 @@ def make_handler(state: ServerState):
         # ---- helpers ----------------------------------------------------------------------------------------
         def _admin(self):
             auth = self.headers.get("Authorization", "")
-            if state.admin_key is None or auth != f"Bearer {state.admin_key}":
+            if state.admin_key is None or not hmac.compare_digest(auth.encode(), f"Bearer {state.admin_key}".encode()):
                 raise ApiError(401, "admin key required", "authentication_error")
 
         def _model_obj(self):

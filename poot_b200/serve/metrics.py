@@ -44,7 +44,8 @@ class Metrics:
     COUNTERS = ("poot_requests_total", "poot_requests_completed_total", "poot_requests_cancelled_total",
                 "poot_requests_errored_total", "poot_requests_rejected_total", "poot_prompt_tokens_total",
                 "poot_completion_tokens_total", "poot_prefix_cache_hit_tokens_total",
-                "poot_prefix_cache_query_tokens_total", "poot_engine_steps_total", "poot_engine_compiles_total")
+                "poot_prefix_cache_query_tokens_total", "poot_engine_steps_total", "poot_engine_compiles_total",
+                "poot_step_deadline_exceeded_total")
     GAUGES = ("poot_inflight_requests", "poot_queue_depth", "poot_batch_size", "poot_slot_capacity",
               "poot_kv_usage_ratio", "poot_kv_blocks_used", "poot_kv_blocks_total", "poot_prefix_hit_rate",
               "poot_gpu_active_ratio", "poot_weight_bytes", "poot_kv_bytes", "poot_uptime_seconds")

@@ -66,7 +66,8 @@ class EngineDead(RuntimeError):
 
 class ServeEngine:
     def __init__(self, driver: Driver, tokenizer, metrics: Optional[Metrics] = None, max_pending: int = 256,
-                 max_queue_wait: float = 60.0, on_step: Optional[Callable] = None, draft=None, timing=None):
+                 max_queue_wait: float = 60.0, on_step: Optional[Callable] = None, draft=None, timing=None,
+                 step_deadline: Optional[float] = None):
         self.driver, self.tk = driver, tokenizer
         self.metrics = metrics or Metrics()
         self.inbox: "queue.Queue[Job]" = queue.Queue()
@@ -84,6 +85,10 @@ class ServeEngine:
         self.timing = timing                 # profile.TimingSnapshot, or None: counters only
         self.busy_s = 0.0
         self._admin: "queue.Queue" = queue.Queue()
+        # step-deadline watchdog: a step that is still running after this many seconds is declared lost
+        self.step_deadline = step_deadline
+        self._step_started: Optional[float] = None
+        self._watchdog: Optional[threading.Thread] = None
         self.metrics.set("poot_slot_capacity", driver.max_rows)
 
     # ---- submission (any thread) -------------------------------------------------------------------------------
@@ -144,6 +149,30 @@ class ServeEngine:
         self.state = "serving"
         self._thread = threading.Thread(target=self._run_guarded, name="poot-engine", daemon=True)
         self._thread.start()
+        if self.step_deadline:
+            self._watchdog = threading.Thread(target=self._watch_steps, name="poot-step-watchdog", daemon=True)
+            self._watchdog.start()
+
+    def _watch_steps(self) -> None:
+        """A step that outlives ``step_deadline`` cannot be interrupted from here, but the engine can be told to give
+        up: ``abort()`` sets the device's abort word (every wait on another rank returns at once) and, on a multi-rank
+        engine, tells the followers to stop.  The engine is dead from then on: requests in flight fail, new ones get
+        503 with the cause, and the blocked step ends with a typed error when its kernels have drained."""
+        while not self._stop.is_set() and self.state != "dead":
+            t0 = self._step_started
+            if t0 is not None and time.monotonic() - t0 > self.step_deadline:
+                self.state, self.cause = "dead", f"fault: a step exceeded its deadline of {self.step_deadline:.1f} s"
+                self.metrics.inc("poot_step_deadline_exceeded_total")
+                abort = getattr(self.driver.engine, "abort", None)
+                if abort is not None:
+                    try:
+                        abort()
+                    except Exception:
+                        traceback.print_exc()
+                for job in list(self.live.values()) + list(self.waiting):
+                    self._fail(job, "engine fault: step deadline exceeded")
+                return
+            self._stop.wait(min(0.05, self.step_deadline / 4))
 
     def drain(self, timeout: float = 30.0) -> None:
         """Stop admitting, let live requests finish (bounded), then stop the thread."""
@@ -160,7 +189,8 @@ class ServeEngine:
         try:
             self.run()
         except Exception as e:   # a fault, not a refusal: the engine is dead from here on
-            self.state, self.cause = "dead", f"fault: {e}"
+            if self.state != "dead":     # the watchdog may have named the cause already
+                self.state, self.cause = "dead", f"fault: {e}"
             traceback.print_exc()
             for job in list(self.live.values()) + self.waiting:
                 self._fail(job, "engine fault")
@@ -232,6 +262,7 @@ class ServeEngine:
             self.busy_s += time.monotonic() - t0
             self._gauges()
             return True
+        self._step_started = t0
         try:
             results = d.step(list(self.live))
         except SamplerFault as e:                       # fails only its request
@@ -239,6 +270,10 @@ class ServeEngine:
             d.release(e.seq_id, "preempted")
             self._fail(job, str(e), code=500)
             return True
+        finally:
+            self._step_started = None
+        if self.state == "dead":                        # the watchdog gave this step up: its tokens are not committed
+            raise EngineDead(self.cause or "engine is dead")
         step_s = time.monotonic() - t0
         self.busy_s += step_s
         if self.timing is not None:

@@ -525,7 +525,7 @@ def gemm_grouped(epi, x, W, out, M, groups, group_expert=None, x_row_div=0, x_ro
             flat[o:o + n_out] = r[m]
 
 
-_status = torch.zeros(1, dtype=torch.int32)
+_status = torch.zeros(16, dtype=torch.int32)
 
 
 @contextmanager

@@ -1,0 +1,271 @@
+"""Host restatement of the fused tensor-parallel kernels, with the ranks as threads of one process (tests only).
+
+``EmulatedFusedComm`` offers what ``parallel.tp.FusedComm`` offers the engine, but its "symmetric memory" is a set of
+host tensors that all rank threads share, and each launch is a Python function that does what the kernel does, in the
+kernel's order: write the partial rows into the peers' inboxes, publish the site's flag (and the poison word when this
+rank has recorded a failure), wait for the peers' flags under the rules of ``csrc/kernels/tp_common.cuh`` - a recorded
+failure, the host's abort word, the step deadline and a peer's poison word each end a wait - then reduce in rank order.
+
+So the engine's unmodified fused programs (site numbering, flag targets across steps, buffer parity, the greedy-pick
+exchange) run at any world size without a GPU, and the failure rules can be driven from the host: a rank thread that
+never starts, a stall longer than the step budget, an abort while a wait is pending.  With fewer GPUs than ranks this
+is also the only form in which kernels that wait on one another may be run at all.  Nothing in the product selects it.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from typing import List, Optional
+
+import torch
+
+from ..ops import cuda_ops as K
+from . import kernel_emulation as E
+
+CH_RS, CH_AG, CH_POISON, CH_AX = 0, 1, 2, 3
+MAX_ROWS = 128
+OK, TIMEOUT_PEER_FLAG, ABORTED, STEP_DEADLINE, PEER_FAILED = 0, 4, 6, 7, 8
+NO_DEADLINE_BUDGET_S = 1.0
+
+
+class EmulatedGroup:
+    """What the ranks of one node share: every rank's flag block, inbox, gather buffer, exchange area, control block."""
+
+    def __init__(self, world: int, hidden: int, ax_cap: int = 4096):
+        self.world, self.H, self.ax_cap = world, hidden, ax_cap
+        self.flags = torch.zeros(world, 4, 8, dtype=torch.int64)
+        self.inbox = [torch.zeros(2, world, MAX_ROWS, hidden, dtype=torch.bfloat16) for _ in range(world)]
+        self.xs = [torch.zeros(2, MAX_ROWS, hidden, dtype=torch.bfloat16) for _ in range(world)]
+        self.ax = [torch.zeros(2, world, ax_cap, dtype=torch.int32) for _ in range(world)]
+        # control blocks: first failure, detail, deadline (monotonic seconds; 0 = none), abort word, step budget
+        self.ctl = [dict(code=0, detail=-1, deadline=0.0, abort=0, budget=5.0, gave_up=0) for _ in range(world)]
+        self.barrier = threading.Barrier(world)
+        self.lock = threading.Lock()
+
+    # ---- control block rules (csrc/kernels/common.cuh) ---------------------------------------------------------
+    def fail(self, rank: int, code: int, detail: int = -1) -> None:
+        with self.lock:
+            c = self.ctl[rank]
+            if c["code"] == 0:                  # first cause only
+                c["code"], c["detail"] = code, detail
+            c["gave_up"] += 1
+
+    def stop_reason(self, rank: int) -> int:
+        c = self.ctl[rank]
+        if c["code"] != 0:
+            return c["code"]
+        if c["abort"]:
+            return ABORTED
+        if c["deadline"] and time.monotonic() > c["deadline"]:
+            return STEP_DEADLINE
+        return 0
+
+    def request_abort(self, rank: Optional[int] = None) -> None:
+        for r in (range(self.world) if rank is None else [rank]):
+            self.ctl[r]["abort"] = 1
+
+    def status(self, rank: int):
+        c = self.ctl[rank]
+        return c["code"], c["detail"]
+
+    def clear(self, rank: int) -> None:
+        self.ctl[rank].update(code=0, detail=-1, gave_up=0)
+
+    # ---- flags (csrc/kernels/tp_common.cuh) ----------------------------------------------------------------------
+    def wait_flag(self, rank: int, ch: int, src: int, target: int) -> int:
+        f = self.flags[rank, ch]
+        if int(f[src]) >= target:
+            return 0
+        why = self.stop_reason(rank)
+        if why:
+            return why
+        has_deadline = bool(self.ctl[rank]["deadline"])
+        t0 = time.monotonic()
+        while int(f[src]) < target:
+            if bool((self.flags[rank, CH_POISON, :self.world] != 0).any()):
+                return PEER_FAILED
+            why = self.stop_reason(rank)
+            if why:
+                return why
+            if not has_deadline and time.monotonic() - t0 > NO_DEADLINE_BUDGET_S:
+                return TIMEOUT_PEER_FLAG
+            time.sleep(0.0002)
+        return 0
+
+    def wait_all(self, rank: int, ch: int, target: int, site: int, skip_self: bool = False) -> bool:
+        for r in range(self.world):             # a peer that gave up ran ahead and published every flag: its poison word tells
+            if int(self.flags[rank, CH_POISON, r]) != 0:
+                self.fail(rank, PEER_FAILED, site * 16 + r)
+                return False
+        for r in range(self.world):
+            if skip_self and r == rank:
+                continue
+            why = self.wait_flag(rank, ch, r, target)
+            if why:
+                self.fail(rank, why, site * 16 + r)
+                return False
+        return True
+
+    def signal_all(self, rank: int, ch: int, target: int) -> None:
+        code = self.ctl[rank]["code"]
+        for d in range(self.world):
+            if code and d != rank:
+                self.flags[d, CH_POISON, rank] = code
+            self.flags[d, ch, rank] = target
+
+
+class EmulatedFusedComm:
+    fused = True
+    MAX_ROWS = MAX_ROWS
+
+    def __init__(self, rank: int, group: EmulatedGroup):
+        self.rank, self.world, self.g = rank, group.world, group
+        self.device = torch.device("cpu")
+        self.epoch = 0
+        self.ax_count = 0
+        self.block = None
+        self.log: List[tuple] = []          # (kind, site, target) of every cross-rank launch, for the tests
+
+    def attach(self, engine) -> None:
+        H = engine.cfg.hidden
+        assert H == self.g.H
+        self.H = H
+        self.s_max = MAX_ROWS // self.world
+        self.h_shard = torch.zeros(self.s_max, H, dtype=torch.bfloat16)
+        L = engine.cfg.n_layers
+        self.rs_sites, self.ag_sites = 2 * L, 2 * L + 1
+        self.partial = torch.zeros(engine.max_tokens, H, dtype=torch.bfloat16)
+
+    # ---- geometry (same rules as FusedComm) ----------------------------------------------------------------------
+    def rows_for(self, T: int) -> int:
+        need = max(T, 8 * self.world)
+        for r in (16, 32, 64, 128):
+            if r >= need and r % (8 * self.world) == 0:
+                return r
+        return 0
+
+    def oneshot_ok(self, T: int) -> bool:
+        return T <= 128 and T * (self.world - 1) <= 512
+
+    def _target(self, site: int, sites: int) -> int:
+        return (self.epoch - 1) * sites + site + 1
+
+    # ---- launches --------------------------------------------------------------------------------------------------
+    def rendezvous(self) -> None:
+        self.g.barrier.wait(timeout=60)
+
+    def begin_step(self) -> None:
+        self.epoch += 1
+        c = self.g.ctl[self.rank]
+        c["deadline"] = time.monotonic() + c["budget"] if c["budget"] else 0.0
+
+    def gemm_allreduce(self, x, W, rows: int, rs_site: int) -> None:
+        y = E._bf(x[:rows].float() @ W.float().T)
+        target = self._target(rs_site, self.rs_sites)
+        for d in range(self.world):
+            self.g.inbox[d][target & 1, self.rank, :rows] = y
+        self.log.append(("rs", rs_site, target))
+        self.g.signal_all(self.rank, CH_RS, target)
+
+    def _reduce(self, h, rows: int, rs_site: int, slot_rows_from=None):
+        target = self._target(rs_site, self.rs_sites)
+        self.g.wait_all(self.rank, CH_RS, target, rs_site)
+        v = h[:rows].float()
+        for r in range(self.world):             # rank order: every rank computes the same sums
+            v = v + self.g.inbox[self.rank][target & 1, r, :rows].float()
+        h[:rows] = E._bf(v)
+
+    def norm_oneshot(self, h, w, x_out, rows: int, eps: float, rs_site: int) -> None:
+        if rs_site >= 0:
+            self._reduce(h, rows, rs_site)
+        E.rmsnorm(h[:rows], w, eps, out=x_out[:rows])
+
+    def norm(self, w, S: int, eps: float, ag_site: int, rs_site: int) -> None:
+        if rs_site >= 0:
+            self._reduce(self.h_shard, S, rs_site)
+        y = E.rmsnorm(self.h_shard[:S], w, eps)
+        target = self._target(ag_site, self.ag_sites)
+        for d in range(self.world):
+            self.g.xs[d][target & 1, self.rank * S:(self.rank + 1) * S] = y
+        self.log.append(("ag", ag_site, target))
+        self.g.signal_all(self.rank, CH_AG, target)
+
+    def gemm(self, epi, x, W, out, S: int, ag_site: int = -1, rs_site: int = -1) -> None:
+        R = self.world * S
+        if ag_site >= 0:
+            target = self._target(ag_site, self.ag_sites)
+            self.g.wait_all(self.rank, CH_AG, target, ag_site)
+            X = self.g.xs[self.rank][target & 1, :R]
+        else:
+            X = x[:R]
+        y = X.float() @ W.float().T
+        if rs_site >= 0:
+            target = self._target(rs_site, self.rs_sites)
+            yb = E._bf(y)
+            for d in range(self.world):         # token row t belongs to rank t // S
+                self.g.inbox[d][target & 1, self.rank, :S] = yb[d * S:(d + 1) * S]
+            self.log.append(("rs", rs_site, target))
+            self.g.signal_all(self.rank, CH_RS, target)
+        else:
+            E._epilogue(y, epi, out[:R], None)
+
+    def argmax_exchange(self, part, rows: int, groups: int, vocab_total: int, out) -> None:
+        target = self.ax_count + 1
+        n = rows * groups * 3
+        flat = part.reshape(-1)[:n]
+        for d in range(self.world):
+            if d != self.rank:
+                self.g.ax[d][target & 1, self.rank, :n] = flat
+        self.g.signal_all(self.rank, CH_AX, target)
+        self.ax_count = target
+        ok = True
+        for r in range(self.world):
+            if r == self.rank:
+                continue
+            why = self.g.wait_flag(self.rank, CH_AX, r, target)
+            if not why and int(self.g.flags[self.rank, CH_POISON, r]) != 0:
+                why = PEER_FAILED
+            if why:
+                self.g.fail(self.rank, why, (1 << 20) + r)
+                ok = False
+                break
+        if not ok:
+            out[:rows, 0], out[:rows, 1] = 0, -1
+            return
+        tables = [flat if r == self.rank else self.g.ax[self.rank][target & 1, r, :n] for r in range(self.world)]
+        E.argmax_combine(torch.stack(tables).view(self.world, rows, groups, 3), rows, groups, vocab_total, out)
+
+    # ---- the library-collective interface, for steps that are not fused (prefill chunks, sampling rules) ----------
+    def _exchange_host(self, t: torch.Tensor) -> List[torch.Tensor]:
+        box = self.g.__dict__.setdefault("_box", [None] * self.world)
+        box[self.rank] = t.clone()
+        self.g.barrier.wait(timeout=60)
+        got = [b.clone() for b in box]
+        self.g.barrier.wait(timeout=60)
+        return got
+
+    def row_parallel(self, engine, x, W, T: int):
+        p = self.partial[:T]
+        engine._linear(x, W, K.EPI_STORE, p)
+        self.all_reduce(p)
+        engine._count()
+        K.add(engine.h[:T], p, out=engine.h[:T])
+        return None
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        parts = self._exchange_host(t)
+        acc = parts[0].float()
+        for p in parts[1:]:
+            acc = acc + p.float()
+        t.copy_(acc.to(t.dtype))
+        return t
+
+    def all_gather(self, out: torch.Tensor, inp: torch.Tensor) -> None:
+        parts = self._exchange_host(inp)
+        out.view(self.world, -1).copy_(torch.stack([p.reshape(-1) for p in parts]))
+
+    def drain(self) -> None:
+        self.g.request_abort(self.rank)
+
+    def close(self) -> None:
+        pass

@@ -13,7 +13,7 @@ def test_peer_flag_wait_runs_out_and_is_reported():
     from poot_b200.ops import cuda_ops as K
     from poot_b200.ops._lib import check
     _P = c_void_p
-    K.register_signature("poot_tp_begin_step", [_P, _P])
+    K.register_signature("poot_tp_begin_step", [_P, _P, _P])
     K.register_signature("poot_tp_norm", [_P, _P, _P, _P, _P, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
                                           c_int, c_int, _P, _P, _P, _P, _P, _P])
     dev = torch.device("cuda")
@@ -28,15 +28,18 @@ def test_peer_flag_wait_runs_out_and_is_reported():
     fp = (c_void_p * world)(*[f.data_ptr() for f in flags])
     st = K.status_word(dev)
     K.check_status()
-    check(K.fn("poot_tp_begin_step")(epoch.data_ptr(), K._stream()), "begin")
+    K.set_step_budget(0.5, dev)                      # the waits of this "step" share half a second
+    check(K.fn("poot_tp_begin_step")(epoch.data_ptr(), st.data_ptr(), K._stream()), "begin")
     t0 = time.time()
     check(K.fn("poot_tp_norm")(h.data_ptr(), inbox.data_ptr(), w.data_ptr(), None, x.data_ptr(), rows, H, 1e-5, world, 0,
                                128, 0, 3, 0, 2, epoch.data_ptr(), flags[0].data_ptr(), fp, ticket.data_ptr(),
                                st.data_ptr(), K._stream()), "tp_norm")
     torch.cuda.synchronize()
     waited = time.time() - t0
-    assert 0.3 < waited < 10.0                       # the wait was bounded: about a second per missing peer
-    with pytest.raises(K.DeviceWaitTimeout, match="peer flag"):
+    K.set_step_budget(K.DEFAULT_STEP_BUDGET_S, dev)
+    assert 0.3 < waited < 5.0                        # the wait ended at the step deadline
+    with pytest.raises(K.DeviceWaitTimeout, match="step deadline") as err:
         K.check_status()
+    assert err.value.code == 7 and err.value.detail == 0      # site 0, rank 0's flag never came
     K.check_status()                                 # the word was cleared by the report
     assert float(torch.ones(8, device=dev).sum()) == 8.0        # the context is still usable

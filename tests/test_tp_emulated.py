@@ -1,0 +1,164 @@
+"""The fused tensor-parallel programs of the engine with the ranks as threads over host restatements of the kernels
+(``utils/tp_emulation.py``): token parity with one rank at world 2, 4 and 8 in both collective forms, the flag targets
+across steps, and the failure rules of the waits - host abort, step deadline, poison - driven from the host."""
+import threading
+import time
+
+import pytest
+import torch
+
+from poot_b200.models.config import DecoderConfig
+from poot_b200.runtime.engine import DecoderEngine
+from poot_b200.runtime.session import FixedBatchSession
+from poot_b200.runtime.weights import random_weights
+from poot_b200.utils.kernel_emulation import emulated_kernels
+from poot_b200.utils.tp_emulation import (ABORTED, PEER_FAILED, STEP_DEADLINE, EmulatedFusedComm, EmulatedGroup)
+
+
+def _cfg(world):
+    return DecoderConfig(n_layers=2, hidden=256, n_heads=8, n_kv_heads=8 if world > 4 else 4, head_dim=64, ffn=512,
+                         vocab=4096, max_position=256)
+
+
+def _prompts(cfg, B=2, P=9):
+    g = torch.Generator().manual_seed(5)
+    return torch.randint(0, cfg.vocab, (B, P), generator=g, dtype=torch.int32)
+
+
+def _rank_program(cfg, rank, world, comm, mode, steps, out, before_step=None):
+    w = random_weights(cfg, "cpu", seed=0, std=0.05, tp_rank=rank, tp_world=world)
+    eng = DecoderEngine(w, num_blocks=9, max_seqs=2, max_tokens=48, max_blocks_per_seq=4, comm=comm, device="cpu",
+                        use_graphs=False)
+    if mode == "rs_ag":
+        eng.tp_mode = "rs_ag"
+    s = FixedBatchSession(eng, 2, 64)
+    toks = [s.prefill_fast(_prompts(cfg)).clone()]
+    for i in range(steps):
+        if before_step is not None:
+            before_step(rank, i)
+        toks.append(s.decode(toks[-1][:, 0].tolist()).clone())
+    out[rank] = torch.stack(toks)
+
+
+def _run_group(cfg, world, mode, steps=3, before_step=None, budget=5.0):
+    group = EmulatedGroup(world, cfg.hidden)
+    for c in group.ctl:
+        c["budget"] = budget
+    comms = [EmulatedFusedComm(r, group) for r in range(world)]
+    out, errs = {}, {}
+
+    def body(r):
+        try:
+            _rank_program(cfg, r, world, comms[r], mode, steps, out, before_step)
+        except Exception as e:       # a thread's failure must fail the test, not vanish
+            errs[r] = e
+    threads = [threading.Thread(target=body, args=(r,), daemon=True) for r in range(world)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=180)
+    assert not any(t.is_alive() for t in threads), "a rank thread did not finish"
+    return group, comms, out, errs
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("mode", ["oneshot", "rs_ag"])
+def test_fused_programs_match_one_rank_at_every_world_size(world, mode):
+    cfg = _cfg(world)
+    with emulated_kernels():
+        ref = {}
+        _rank_program(cfg, 0, 1, None, "oneshot", 3, ref)
+        group, comms, out, errs = _run_group(cfg, world, mode)
+    assert not errs, errs
+    for r in range(world):
+        assert torch.equal(out[r][:, :, 0], ref[0][:, :, 0]), (r, out[r][:, :, 0], ref[0][:, :, 0])
+        assert group.status(r) == (0, -1)
+    # one epoch per step; flag targets never repeat and grow by one per site inside a step
+    L = cfg.n_layers
+    assert all(c.epoch == 4 for c in comms)
+    rs_targets = [t for k, _, t in comms[0].log if k == "rs"]
+    assert rs_targets == sorted(set(rs_targets)) and len(rs_targets) == 4 * 2 * L
+    assert rs_targets[-1] == 4 * 2 * L
+    if mode == "rs_ag":                              # the 18-token prefill and the decode steps both ride the sharded form
+        ag_targets = [t for k, _, t in comms[0].log if k == "ag"]
+        assert len(ag_targets) == 4 * (2 * L + 1) and ag_targets == sorted(set(ag_targets))
+    assert all(c.ax_count == 4 for c in comms)       # one greedy-pick exchange per step, no library collective
+
+
+def test_host_abort_ends_a_pending_wait_at_once():
+    """Rank 1 never starts its second decode step.  Rank 0 sits in a wait with a long budget; the host sets the abort
+    word and the wait returns within milliseconds, the first cause says so, and later waits do not wait at all."""
+    cfg = _cfg(2)
+    gate = threading.Event()
+    holder = {}
+
+    def before(rank, i):
+        if rank == 1 and i == 1:
+            gate.wait(timeout=30)                     # stays out of the step until the test lets it go
+
+    def aborter():
+        time.sleep(0.5)
+        holder["t_abort"] = time.monotonic()
+        holder["group"].request_abort(0)
+        time.sleep(0.3)
+        holder["group"].request_abort(1)
+        gate.set()
+
+    with emulated_kernels():
+        group = EmulatedGroup(2, cfg.hidden)
+        for c in group.ctl:
+            c["budget"] = 60.0
+        holder["group"] = group
+        comms = [EmulatedFusedComm(r, group) for r in range(2)]
+        out = {}
+        ts = [threading.Thread(target=_rank_program, args=(cfg, r, 2, comms[r], "oneshot", 3, out, before), daemon=True)
+              for r in range(2)]
+        threading.Thread(target=aborter, daemon=True).start()
+        t0 = time.monotonic()
+        for t in ts:
+            t.start()
+        ts[0].join(timeout=60)
+        done0 = time.monotonic()
+        ts[1].join(timeout=60)
+    assert not ts[0].is_alive() and not ts[1].is_alive()
+    assert done0 - holder["t_abort"] < 2.0            # not the 60 s budget
+    code, detail = group.status(0)
+    assert code == ABORTED and detail % 16 == 1       # it was waiting for rank 1
+    assert group.ctl[0]["gave_up"] >= 1
+
+
+def test_the_waits_of_one_step_share_one_deadline_and_the_failure_reaches_the_peer():
+    """Rank 1 stalls for longer than the step budget before its second decode step.  Rank 0 gives up at the deadline
+    (once: the later waits of the step return at once), publishes its failure with its next signal, and rank 1, when it
+    finally runs the step, stops waiting as soon as it sees the poison word."""
+    cfg = _cfg(2)
+
+    def before(rank, i):
+        if rank == 1 and i == 1:
+            time.sleep(1.2)
+
+    with emulated_kernels():
+        t0 = time.monotonic()
+        group, comms, out, errs = _run_group(cfg, 2, "oneshot", steps=2, before_step=before, budget=0.4)
+        took = time.monotonic() - t0
+    assert not errs, errs
+    assert group.status(0)[0] == STEP_DEADLINE
+    assert group.status(1)[0] in (PEER_FAILED, STEP_DEADLINE)
+    assert group.ctl[0]["gave_up"] <= 2 * cfg.n_layers + 2
+    assert took < 10.0                                # one budget, not one per site
+
+
+def test_device_adapter_turns_the_emulated_status_into_a_typed_error():
+    from poot_b200.driver.engines import DeviceStepEngine
+    from poot_b200.ops.cuda_ops import DeviceWaitTimeout
+    cfg = _cfg(2)
+    with emulated_kernels():
+        group = EmulatedGroup(2, cfg.hidden)
+        w = random_weights(cfg, "cpu", seed=0, std=0.05, tp_rank=0, tp_world=2)
+        eng = DecoderEngine(w, num_blocks=9, max_seqs=2, max_tokens=48, max_blocks_per_seq=4,
+                            comm=EmulatedFusedComm(0, group), device="cpu", use_graphs=False)
+        dev = DeviceStepEngine(eng)
+        dev.status_hook = lambda: group.status(0)
+        group.fail(0, STEP_DEADLINE, 3 * 16 + 1)
+        with pytest.raises(DeviceWaitTimeout, match=r"step deadline \(site 3, waiting for rank 1\)"):
+            dev._raise_on_failed_wait(False)

@@ -66,3 +66,6 @@ def test_noalloc_rejects_requests_beyond_the_built_in_scratch():
     # 4096 rows x 32 heads x 16 splits x 130 floats is far beyond 2 Mi floats: refused before any launch
     code = f(None, 0, None, None, None, 0, None, None, None, 0, 4096, 32, 8, 128, 1.0, 0.0, 0, 16, None)
     assert code == 1
+    # head counts that cannot be divided are refused the same way, not by a trap on the host
+    for hq, hkv in ((32, 0), (32, -8), (32, 5), (0, 8)):
+        assert f(None, 0, None, None, None, 0, None, None, None, 0, 4, hq, hkv, 128, 1.0, 0.0, 0, 2, None) == 1

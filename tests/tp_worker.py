@@ -17,10 +17,9 @@ def main():
     kind = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ["LOCAL_RANK"])
-    import threading
-    dog = threading.Timer(240.0, lambda: os._exit(3))    # a rank stuck in a collective must not keep the GPUs
-    dog.daemon = True
-    dog.start()
+    # watchdog and signals leave through a drain: no exit under a kernel that still waits for a peer
+    from poot_b200.parallel import teardown
+    teardown.install(watchdog_seconds=240.0)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
@@ -62,6 +61,7 @@ def main():
 
     ref_tokens, ref_logits = run(random_weights(cfg, dev, seed=3, std=0.05), None)
     comm = make_comm("fused" if kind == "fused_rsag" else kind, rank, world, dev)
+    teardown.set_comm(comm)
     tp_tokens, tp_logits = run(random_weights(cfg, dev, seed=3, std=0.05, tp_rank=rank, tp_world=world,
                                               ep_rank=rank if moe else 0, ep_world=world if moe else 1), comm,
                                forced=ref_tokens)
