@@ -203,6 +203,77 @@ def encoder_case(n_seq, length, hidden=384, heads=12, ffn=1536, layers=6):
     return [fn], wbytes, flops
 
 
+def quant_decode_case(layers=4):
+    """Eager batch-1 decode steps of the Q4_K / Q8_0 Llama-3-8B stack cut to ``layers`` layers (a launch list shows
+    the share of the packed GEMV, attention and the row kernels); bytes = the packed weights of those layers."""
+    from poot_b200.models.config import PRESETS
+    from poot_b200.runtime.engine import DecoderEngine
+    from poot_b200.runtime.session import FixedBatchSession
+    from poot_b200.runtime.weights import random_quant_weights
+    cfg = PRESETS["llama-3-8b"]()
+    cfg.n_layers = layers
+    w = random_quant_weights(cfg, "cuda", seed=0)
+    max_len = 768
+    bps = max_len // 16
+    eng = DecoderEngine(w, num_blocks=bps, max_seqs=1, max_tokens=128, max_blocks_per_seq=bps, use_graphs=False)
+    s = FixedBatchSession(eng, 1, max_len)
+    s.len_t = torch.full((1,), 200, dtype=torch.int32)
+    return [lambda: s.decode([1])], w.nbytes(), 0.0
+
+
+def tp_oneshot_pair_case(world=2, T=64, H=4096, Kl=7168):
+    """The fused row-parallel GEMM + one-shot all-reduce + reduce/RMSNorm pair of a tensor-parallel decode step with
+    every rank of the group emulated on ONE GPU (a profiler captures single-GPU programs only): each rank has its own
+    flag block, inbox, step counter and weight shard in this GPU's memory, so the "peer" stores land locally.  Launch
+    order per round: every rank's step-begin, every rank's GEMM, then every rank's reduce+norm - a kernel that waits on
+    flags is enqueued on the same stream after the kernels that set them, so nothing waits on a later launch.  One call
+    of the returned function is one round; the time reported is per kernel launch (2 * world + world launches a round)."""
+    from ctypes import c_float, c_int, c_void_p
+    from poot_b200.ops._lib import check
+    P = c_void_p
+    K.register_signature("poot_tp_begin_step", [P, P, P])
+    K.register_signature("poot_tp_norm", [P, P, P, P, P, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, P, P, P, P, P, P])
+    K.register_signature("poot_gemm_skinny_tp", [c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                 c_int, c_int, c_int, c_int, c_int, P, P, P, P, c_int, c_int, P, P, P])
+    begin, norm, gemm = K.fn("poot_tp_begin_step"), K.fn("poot_tp_norm"), K.fn("poot_gemm_skinny_tp")
+    MAX_ROWS, RS_SITES, AG_SITES = 128, 1, 2
+    dev = torch.device("cuda")
+    flags = [torch.zeros(256, dtype=torch.int32, device=dev) for _ in range(world)]
+    inbox = [torch.zeros(2 * world * MAX_ROWS * H, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    epoch = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(world)]
+    ticket = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(world)]
+    copies = 3          # rotate weight copies so that every launch streams cold weights (inputs larger than L2)
+    W = [[rnd(H, Kl, scale=0.02) for _ in range(copies)] for _ in range(world)]
+    x = [rnd(T, Kl, scale=0.5) for _ in range(world)]
+    h = [torch.zeros(T, H, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    wn = torch.ones(H, dtype=torch.bfloat16, device=dev)
+    xo = [torch.zeros(T, H, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    fpeer = (c_void_p * world)(*[f.data_ptr() for f in flags])
+    ipeer = (c_void_p * world)(*[b.data_ptr() for b in inbox])
+    st = K.status_word(dev)
+    ck = K.skinny_cluster(H, Kl)
+    it = [0]
+
+    def one_round():
+        s = K._stream()
+        c = it[0] % copies
+        it[0] += 1
+        for r in range(world):
+            check(begin(epoch[r].data_ptr(), st.data_ptr(), s), "begin")
+        for r in range(world):
+            check(gemm(K.EPI_STORE, x[r].data_ptr(), W[r][c].data_ptr(), None, H, Kl, Kl, H, ck, world, r, MAX_ROWS, -1,
+                       AG_SITES, 0, RS_SITES, epoch[r].data_ptr(), flags[r].data_ptr(), fpeer, ipeer, H, T,
+                       ticket[r].data_ptr(), st.data_ptr(), s), "gemm_skinny_tp")
+        for r in range(world):
+            check(norm(h[r].data_ptr(), inbox[r].data_ptr(), wn.data_ptr(), None, xo[r].data_ptr(), T, H, 1e-5, world, r,
+                       MAX_ROWS, 0, AG_SITES, 0, RS_SITES, epoch[r].data_ptr(), flags[r].data_ptr(), fpeer,
+                       ticket[r].data_ptr(), st.data_ptr(), s), "tp_norm")
+    # per launch: the weight shard streams once per GEMM; the reduce reads world partial tiles
+    per_round_bytes = world * (H * Kl * 2 + T * Kl * 2 + (world + 1) * T * H * 2 + T * H * 2)
+    return [one_round], per_round_bytes, 2.0 * world * T * H * Kl
+
+
 CASES = {
     "dense-decode-gemv-qkv": lambda: gemm_case(1, 6144, 4096, "skinny"),
     "dense-decode-gemv-o": lambda: gemm_case(1, 4096, 4096, "skinny"),
@@ -236,6 +307,8 @@ CASES = {
     "causal-conv-prefill-512": lambda: conv_case(1, 512),
     "replace-rows-1377x2048": lambda: replace_rows_case(1377, 2048),
     "encoder-minilm-b32-len128": lambda: encoder_case(32, 128),
+    "quant-decode-steps-q4k-4-layers": lambda: quant_decode_case(4),
+    "tp-oneshot-gemm-norm-pair-emulated-w2-m64": lambda: tp_oneshot_pair_case(2, 64, 4096, 7168),
     "expert-routing-softmax-512x128-top8": lambda: route_case(512, 128, 8, "softmax"),
     "expert-routing-sigmoid-groups-512x256-top8": lambda: route_case(512, 256, 8, "sigmoid"),
 }
