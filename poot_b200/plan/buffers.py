@@ -24,6 +24,24 @@ class BufferPlan:
     sum_bytes: int                           # what separate allocations would take
 
 
+def first_fit(items, placed=None):
+    """Place ``(key, size, start, end)`` intervals, in the order given, at the lowest offset no live interval holds.
+    Returns ``({key: (offset, size)}, arena size, placed)``; ``placed`` (``[offset, size, start, end]`` lists) can be
+    handed back in to continue a layout.  Shared by the value-level buffer plan and the launch program's arena."""
+    placed = [] if placed is None else placed
+    offsets = {}
+    for key, size, s, t in items:
+        busy = sorted((o, o + z) for o, z, a, b in placed if not (b < s or t < a))
+        off = 0
+        for lo, hi in busy:
+            if off + size <= lo:
+                break
+            off = max(off, hi)
+        placed.append([off, size, s, t])
+        offsets[key] = (off, size)
+    return offsets, max((o + z for o, z, _, _ in placed), default=0), placed
+
+
 def plan_buffers(g: Graph, plans: List[Plan]) -> BufferPlan:
     last_use: Dict[int, int] = {}
     for k, e in enumerate(g.eqns):
@@ -46,18 +64,6 @@ def plan_buffers(g: Graph, plans: List[Plan]) -> BufferPlan:
             life[v] = (k, last_use.get(v, k))
     # first-fit by decreasing size over the interval graph
     order = sorted(life, key=lambda v: (-g.types[v].nbytes, life[v][0]))
-    placed: List[Tuple[int, int, int, int]] = []      # (offset, size, start, end)
-    offsets: Dict[int, Tuple[int, int]] = {}
-    for v in order:
-        size = (g.types[v].nbytes + ALIGN - 1) // ALIGN * ALIGN
-        s, t = life[v]
-        busy = sorted((o, o + z) for o, z, a, b in placed if not (b < s or t < a))
-        off = 0
-        for lo, hi in busy:
-            if off + size <= lo:
-                break
-            off = max(off, hi)
-        placed.append((off, size, s, t))
-        offsets[v] = (off, size)
-    arena = max((o + z for o, z, _, _ in placed), default=0)
+    items = [(v, (g.types[v].nbytes + ALIGN - 1) // ALIGN * ALIGN, life[v][0], life[v][1]) for v in order]
+    offsets, arena, placed = first_fit(items)
     return BufferPlan(offsets, life, arena, sum(z for _, z, _, _ in placed))

@@ -138,18 +138,50 @@ def plan_graph(g: Graph, world: int = 1) -> List[Plan]:
             res.append("output")
         return res
 
+    def bias_operand(e: Eqn) -> bool:
+        """A ``residual_add`` epilogue whose extra operand is a bias row broadcast over the step's rows (not an
+        activation): the contraction still merges with its siblings, the bias is added to the merged rows."""
+        if e.op != "contraction_epilogue" or len(e.inputs) < 3:
+            return False
+        v, hops = e.inputs[2], 0
+        while hops < 8:
+            i = by_value.get(v)
+            if i is not None:
+                return i.storage == "const" and i.name.endswith("_bias")
+            j = prod.get(v)
+            if j is None or g.eqns[j].op not in ("broadcast", "reshape", "cast") or not g.eqns[j].inputs:
+                return False
+            v, hops = g.eqns[j].inputs[0], hops + 1
+        return False
+
     first_by_input: Dict[int, int] = {}
     rope_seen: Dict[tuple, int] = {}
     for k, e in enumerate(g.eqns):
-        if e.op in CONTRACTIONS and e.attrs.get("region") != "residual_add":
+        if e.op == "fused_row" and e.attrs.get("kind") == "rmsnorm":
+            names = [by_value[v].name for v in e.inputs if v in by_value and by_value[v].storage == "const"]
+            if names and names[-1].endswith(("_q_norm", "_k_norm")) and set(consumers(e.outputs[0])) <= {"rope"}:
+                plans[k] = Plan("none", note="the per-head q / k norm is evaluated inside rope_kv_write")
+            continue
+        if e.op in CONTRACTIONS and (e.attrs.get("region") != "residual_add" or bias_operand(e)):
             acts = [v for v in e.inputs if not (v in by_value and by_value[v].storage == "const")]
             x = acts[0] if acts else e.inputs[0]
             if x in first_by_input:
                 plans[k] = Plan("none", note=f"rows concatenated into the GEMM of eqn {first_by_input[x]} (same activations)")
             else:
                 first_by_input[x] = k
+                if bias_operand(e):
+                    plans[k] = Plan("dispatch", plans[k].kernels + ["poot_add"], "bias row added to the merged rows")
         elif e.op == "rope":
-            key = tuple(e.inputs[1:])                 # the same cos / sin rows: q and k of one layer
+            # q and k of one layer come out of the same merged projection: one launch rotates both and writes K/V
+            src, hops = e.inputs[0], 0
+            while src in prod and hops < 16 and g.eqns[prod[src]].op not in CONTRACTIONS and g.eqns[prod[src]].inputs:
+                src, hops = g.eqns[prod[src]].inputs[0], hops + 1
+            j = prod.get(src)
+            if j is not None and g.eqns[j].op in CONTRACTIONS:
+                acts = [v for v in g.eqns[j].inputs if not (v in by_value and by_value[v].storage == "const")]
+                key = ("proj", first_by_input.get(acts[0] if acts else g.eqns[j].inputs[0], j))
+            else:
+                key = ("rows",) + tuple(e.inputs[1:])
             if key in rope_seen:
                 plans[k] = Plan("none", note=f"same launch as the rotary of eqn {rope_seen[key]}")
             else:

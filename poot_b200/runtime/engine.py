@@ -228,6 +228,11 @@ class DecoderEngine:
         self.scale = float(cfg.attn_scale) if cfg.attn_scale is not None else 1.0 / math.sqrt(D)
         if comm is not None:
             comm.attach(self)
+        # Families whose layer the planner lowers completely run the compiled plan's launch list (runtime/program.py);
+        # everything else keeps the hand-sequenced program below.
+        self.program = None
+        from .program import ProgramExecutor
+        self.program = ProgramExecutor.build_for(self)
         self.lora = None                    # bank of resident adapters, created by enable_adapters()
         self.embed_rows = self.embed_flags = None   # staging of rows that replace embeddings, created by bind_embeds()
         self.rope_cos_tok = self.rope_sin_tok = None  # per-token rotary rows of a sectioned rope, created by bind_rope_streams()
@@ -298,16 +303,18 @@ class DecoderEngine:
         self._count()
         return K.linear(x, W, epi, out, resid)
 
-    def _proj_to_residual(self, x, W, T):
-        """``h += x @ W^T`` (o_proj / down_proj).  Returns pending fp32 partial slices or None.
+    def _proj_to_residual(self, x, W, T, h=None, out=None):
+        """``out = h + x @ W^T`` (o_proj / down_proj; in place on the residual stream ``self.h`` by default).  Returns
+        pending fp32 partial slices (the caller's next norm adds them to ``h``) or None.
 
         Small-N, large-K projections at decode batch sizes do not fill 148 SMs with one K pass, so they split K
         and leave the reduction to the next RMSNorm (which reads the residual stream anyway).
         """
-        h = self.h[:T]
+        h = self.h[:T] if h is None else h
+        out = h if out is None else out
         N, Kdim = W.shape
         if T <= 128 or isinstance(W, K.QuantWeight):
-            self._linear(x, W, K.EPI_RESID, h, h)
+            self._linear(x, W, K.EPI_RESID, out, h)
             return None
         tiles =((T + 127) // 128) * ((N + 63) // 64)
         if tiles < 100 and Kdim >= 1024 and T <= self.small_T:
@@ -317,7 +324,7 @@ class DecoderEngine:
                 self._count()
                 K.gemm(x, W, K.EPI_PARTIAL, out=p, bn=64, splits=splits)
                 return p
-        self._linear(x, W, K.EPI_RESID, h, h)
+        self._linear(x, W, K.EPI_RESID, out, h)
         return None
 
     def _norm(self, w, T, pending, bias=None):
@@ -335,19 +342,21 @@ class DecoderEngine:
             K.rmsnorm(h, w, self.cfg.norm_eps, out=x, partials=pending, h_out=h)
         return x
 
-    def _attention(self, l: int, R: int, T: int, B: int, count: bool = True) -> None:
+    def _attention(self, l: int, R: int, T: int, B: int, count: bool = True, q=None, out=None) -> None:
         """Attention of the step's ``R`` rows (``T`` of them live) into ``self.attn``.
 
         Steps that carry prefill pieces (more tokens than sampling rows) run two kernels: the per-row paged kernel
         over the rows left to it (its context length is 0 on rows the tiles cover) and the tensor-core flash kernel
         over the tiles ``bind`` cut from the step's segments.  Pure decode steps run the per-row kernel alone."""
         cfg, D = self.cfg, self.cfg.head_dim
+        q = self.q[:R] if q is None else q
+        out = self.attn[:R] if out is None else out
         if self.attn_general:
             # head widths the tuned kernels do not serve: the general kernel over every live row
             if count:
                 self._count()
-            K.attn_general(self.q[:R], self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables, self.row_seq[:R],
-                           self.row_ctx[:R], self.hq, self.hkv, D, D, self.scale, self.attn[:R], softcap=cfg.attn_softcap,
+            K.attn_general(q, self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables, self.row_seq[:R],
+                           self.row_ctx[:R], self.hq, self.hkv, D, D, self.scale, out, softcap=cfg.attn_softcap,
                            window=cfg.window_of(self.w.layer0 + l), alibi=self.alibi, sinks=self.w.layers[l].sinks)
             return
         flash = self.flash_ok and T > B
@@ -356,14 +365,14 @@ class DecoderEngine:
         if count:
             self._count(((2 if splits > 1 else 1) if simt else 0) + (1 if flash else 0))
         if simt:
-            K.attn_paged(self.q[:R], self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables, self.row_seq[:R],
+            K.attn_paged(q, self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables, self.row_seq[:R],
                          (self.row_ctx_simt if flash else self.row_ctx)[:R], self.hq, self.hkv, D, self.scale,
-                         out=self.attn[:R], splits=splits, scratch=self.attn_scratch, softcap=cfg.attn_softcap,
+                         out=out, splits=splits, scratch=self.attn_scratch, softcap=cfg.attn_softcap,
                          window=cfg.window_of(self.w.layer0 + l))
         if flash:
-            K.attn_flash_prefill(self.q[:R], self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables,
+            K.attn_flash_prefill(q, self.kv.k(self._kv_of[l]), self.kv.v(self._kv_of[l]), self.block_tables,
                                  self.attn_tiles[:self._tile_slots(T, B)], self.hq, self.hkv, self.scale,
-                                 out=self.attn[:R], window=cfg.window_of(self.w.layer0 + l))
+                                 out=out, window=cfg.window_of(self.w.layer0 + l))
 
     def _tile_slots(self, T: int, B: int) -> int:
         """Tile slots a (T, B) step can need: full tiles plus one ragged tile per sequence."""
@@ -402,6 +411,8 @@ class DecoderEngine:
         cfg, w = self.cfg, self.w
         T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
         self._fused_step = False
+        if self.program is not None and self.program.accepts(shape):
+            return self.program.run(shape)      # the plain decoder layer: a walk over the compiled plan's launch list
         if self._fused_shape(shape):
             self._fused_step = True
             if self.comm.oneshot_ok(T) and (self.tp_mode != "rs_ag" or cfg.is_moe):
@@ -830,12 +841,12 @@ class DecoderEngine:
             torch.index_select(self.logits_local[:R], 0, self.logit_idx[:B], out=local)
         self._sample(shape, local)
 
-    def _moe(self, l, L, x, T):
+    def _moe(self, l, L, x, T, h=None):
         from . import moe as _moe
         ep = ("nccl", self.comm) if (self.comm is not None and self.w.ep_world > 1) else None
-        _moe.moe_forward(self, l, L, x, T, ep)
+        _moe.moe_forward(self, l, L, x, T, ep, h=h)
         if L.sh_wgu is not None:
-            _moe.shared_expert(self, L, x, T)
+            _moe.shared_expert(self, L, x, T, h=h)
         return None
 
     # ------------------------------------------------------------------ capture / replay

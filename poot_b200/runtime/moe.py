@@ -42,7 +42,7 @@ def _buffers(eng):
     return eng._moe_buf
 
 
-def shared_expert(eng, L, x: torch.Tensor, T: int) -> None:
+def shared_expert(eng, L, x: torch.Tensor, T: int, h=None) -> None:
     """``h[:T] += shared(x)``: the always-on expert of families that have one (a dense SwiGLU FFN), optionally scaled per
     token by ``sigmoid(x . w)`` (the scale is applied to the activation rows, which the down projection carries through)."""
     c = eng.cfg
@@ -62,7 +62,7 @@ def shared_expert(eng, L, x: torch.Tensor, T: int) -> None:
         g = eng._sh_gate[:T]
         K.linear(x, L.sh_gate, K.EPI_F32, g)
         act.mul_(torch.sigmoid(g[:, :1]).to(act.dtype))
-    h = eng.h[:T]
+    h = eng.h[:T] if h is None else h
     K.linear(act, L.sh_wdown, K.EPI_RESID, h, h)
 
 
@@ -81,7 +81,7 @@ def _expert_act(eng, L, gu: torch.Tensor, act: torch.Tensor, expert_of_row: torc
         K.gated_act(gu, True, c.act, out=act)
 
 
-def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
+def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
     """``h[:T] += moe(x)``.  ``ep`` selects the expert-parallel form: ``("nccl", comm)`` reduces the local experts'
     partial with a library all-reduce, ``("fused", comm, rs_site)`` pushes it into every rank's inbox from the GEMM
     epilogue (returns ``"pushed"``: the caller's next reduce+norm kernel consumes it)."""
@@ -103,7 +103,7 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None):
     dense = buf["dense"][:E * T].view(E, T)
     M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense, mode=c.router, select_bias=L.select_bias,
                 scale=c.routed_scale, n_group=c.n_group, topk_group=c.topk_group)
-    h = eng.h[:T]
+    h = eng.h[:T] if h is None else h
     tp = (ep[1], ep[2]) if (ep is not None and ep[0] == "fused") else None
     if ep is None and e_local == E and T * k <= E:
         G = T * k                                             # one group per (token, slot)
