@@ -15,7 +15,7 @@ LAYERS = {
     "load": {"tensor", "quant", "weights", "models"}, "ir": {"tensor", "quant"}, "oracle": {"tensor", "quant", "ir", "models", "runtime"},
     "models": {"tensor", "ir", "load"}, "plan": {"tensor", "ir", "quant", "target", "models", "oracle"},
     "ops": set(), "profile": {"target", "ops"}, "text": set(),
-    "runtime": {"models", "ops", "quant", "parallel", "tensor"}, "parallel": {"ops", "runtime"},
+    "runtime": {"models", "ops", "quant", "parallel", "tensor", "plan"}, "parallel": {"ops", "runtime"},
     "utils": {"ops", "oracle", "runtime", "models", "tensor"},
     "driver": {"models", "runtime", "ops", "load", "quant", "ir", "oracle", "text", "tensor", "profile", "parallel"},
     "serve": {"driver", "text", "profile", "models", "parallel", "runtime", "ops", "load"}, "cli": {"driver", "text", "models"},
