@@ -106,11 +106,21 @@ struct GemmSmem {
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;  // +1024 for base alignment
 };
 
-template <int BN, int STAGES, int EPI>
+// Grouped form (mixture of experts over rows grouped by expert): row tile blockIdx.x belongs to expert
+// tile_expert[blockIdx.x] of a stacked weight [experts * N, K]; a negative entry is an unused tile (nothing is stored).
+// row_scale (optional) multiplies each stored row (the routing gate of the down projection).
+struct TileGroups {
+  const int* tile_expert;
+  int w_rows_per_expert;
+  const float* row_scale;
+};
+
+template <int BN, int STAGES, int EPI, bool GROUPED = false>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          void* __restrict__ out, const __nv_bfloat16* __restrict__ resid, int M, int N, int K,
-                         int ldo, int k_tiles_per_split, long long partial_stride, int* __restrict__ status) {
+                         int ldo, int k_tiles_per_split, long long partial_stride, int* __restrict__ status,
+                         const TileGroups grp) {
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = tc::smem_u32(smem_raw);
@@ -131,7 +141,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   const int kt_begin = split * k_tiles_per_split;
   int kt_end = kt_begin + k_tiles_per_split;
   if (kt_end > total_k_tiles) kt_end = total_k_tiles;
-  const int num_kt = kt_end > kt_begin ? kt_end - kt_begin : 0;
+  int num_kt = kt_end > kt_begin ? kt_end - kt_begin : 0;
+  int w_n0 = n0;            // row of the weight operand this tile starts at
+  bool dead = false;        // grouped form: a row tile no expert owns
+  if (GROUPED) {
+    const int ex = grp.tile_expert[blockIdx.x];
+    dead = ex < 0;
+    w_n0 = (dead ? 0 : ex) * grp.w_rows_per_expert + n0;
+    if (dead) num_kt = 0;
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar + 8 * s, 1); tc::mbar_init(empty_bar + 8 * s, 1); }
@@ -162,7 +180,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         const uint32_t sa = base + s * S::STAGE_BYTES;
         const int kx = (kt_begin + i) * GEMM_BK;
         tc::tma_load_2d(sa, &tmA, kx, m0, full_bar + 8 * s);
-        tc::tma_load_2d(sa + S::A_BYTES, &tmB, kx, n0, full_bar + 8 * s);
+        tc::tma_load_2d(sa + S::A_BYTES, &tmB, kx, w_n0, full_bar + 8 * s);
         ++issued;
       }
       if (!ok) {
@@ -202,7 +220,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(accum_bar, 0));  // one verdict per warp (warp-wide loads below)
     if (!ok && lane == 0) ctl_fail(status, (int)kTimeoutEpilogue);
     tc::tc_fence_after();
-    if (ok) {
+    if (ok && !dead) {
+      const float rs = (GROUPED && grp.row_scale != nullptr && row < M) ? grp.row_scale[row] : 1.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -250,6 +269,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 float f[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[8 * v + j]);
+                if (GROUPED) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) f[j] *= rs;
+                }
                 if (EPI == GEPI_RESID) {
                   float rf[8];
                   unpack8(*reinterpret_cast<const uint4*>(rrow + 8 * v), rf);
@@ -288,7 +311,7 @@ static int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* o
   int per = (total_kt + splits - 1) / splits;
   dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN, splits);
   return launch_k(kern, grid, dim3(GEMM_THREADS), (size_t)S::TOTAL, s, ta, tb, out, (const __nv_bfloat16*)resid, M, N, K,
-                  ldo, per, partial_stride, status);
+                  ldo, per, partial_stride, status, TileGroups{nullptr, 0, nullptr});
 }
 
 template <int BN, int STAGES>
@@ -304,9 +327,46 @@ static int launch_gemm_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb
   }
 }
 
+template <int BN, int STAGES, int EPI>
+static int launch_gemm_grouped_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int M, int N, int K, int ldo,
+                                   const TileGroups& grp, int* status, cudaStream_t s) {
+  using S = GemmSmem<BN, STAGES>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, EPI, true>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int total_kt = (K + GEMM_BK - 1) / GEMM_BK;
+  dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN, 1);
+  return launch_k(kern, grid, dim3(GEMM_THREADS), (size_t)S::TOTAL, s, ta, tb, out, (const __nv_bfloat16*)nullptr, M, N, K,
+                  ldo, total_kt, 0LL, status, grp);
+}
+
 }  // namespace poot
 
 using namespace poot;
+
+// Grouped tiled GEMM over rows grouped by expert (see moe_align): X [M, ldx] with M = tiles * 128 grouped rows, stacked
+// weight W [experts * N, K], out [M, ldo]; row tile t multiplies with expert tile_expert[t] (negative: unused, nothing is
+// stored).  epi 0 (bf16 store, optional row_scale [M]) or 3 (SwiGLU over interleaved gate / up rows).  N % 128 == 0.
+POOT_API int poot_gemm_grouped_tiled(int epi, const void* x, const void* W, void* out, int M, int N, int K, int ldx,
+                                     int ldo, int experts, const int* tile_expert, const float* row_scale, int* status,
+                                     cudaStream_t s) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M % GEMM_BM || N % 128 || K % 8 || ldx % 8 || ldo % 8 || experts < 1) return (int)cudaErrorInvalidValue;
+  if (epi != GEPI_STORE && epi != GEPI_SWIGLU) return (int)cudaErrorInvalidValue;
+  if (tile_expert == nullptr || status == nullptr) return (int)cudaErrorInvalidValue;
+  CUtensorMap ta, tb;
+  int e = make_tmap_bf16_2d(&ta, x, (uint64_t)M, (uint64_t)K, (uint64_t)ldx, GEMM_BM);
+  if (e) return e;
+  e = make_tmap_bf16_2d(&tb, W, (uint64_t)experts * (uint64_t)N, (uint64_t)K, (uint64_t)K, 128u);
+  if (e) return e;
+  TileGroups grp{tile_expert, N, row_scale};
+  if (epi == GEPI_SWIGLU) return launch_gemm_grouped_cfg<128, 3, GEPI_SWIGLU>(ta, tb, out, M, N, K, ldo, grp, status, s);
+  return launch_gemm_grouped_cfg<128, 3, GEPI_STORE>(ta, tb, out, M, N, K, ldo, grp, status, s);
+}
 
 // X [M, ldx] bf16 (ldx >= K), W [N, K] bf16, out [M, ldo].
 //   epi 0 bf16 store, 1 fp32 store, 2 bf16 residual add (resid has the layout of out),

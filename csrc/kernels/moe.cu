@@ -6,6 +6,12 @@
 //    unselected expert) that the grouped expert GEMM applies per row
 //    (crates/poot-graph-ir/src/ops/moe.rs:9-431, router kinds crates/poot-models/src/components/router.rs).
 //  * moe_combine: h[t] += sum over groups of the (already gate-scaled) expert outputs.
+//  * moe_align / moe_gather_rows / moe_scatter_combine: row grouping by expert.  The (token, slot) rows routed to
+//    one expert are made contiguous and every expert's run is padded to a whole row tile, so a grouped GEMM walks
+//    tiles that each belong to exactly one expert and every expert multiplies only its own rows at any token count
+//    (the reference's group_expert_rows pass and grouped indexed contraction:
+//    crates/poot-graph-plan/src/passes/group_expert_rows.rs:1-8, crates/poot-kernelgen/src/contraction/indexed.rs:1-6).
+//    With an expert-parallel shard (experts [e0, e0 + e_local) on this rank) rows routed elsewhere are left out.
 #include "common.cuh"
 #include <float.h>
 
@@ -121,9 +127,129 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* h, const __nv_bfloat16* 
   }
 }
 
+// Block-aligned grouping of (token, slot) rows by expert.  One CTA.
+//   ids [n]            expert of every flat row (token * k + slot); ids outside [e0, e0 + e_local) are skipped
+//   pos [n]            out: position of the row in the grouped order, -1 when skipped
+//   sorted_rows [cap]  out: flat row at each grouped position, -1 for padding (cap = max_tiles * block)
+//   tile_expert [max_tiles]  out: local expert of each row tile, -1 for tiles beyond the last used one
+//   n_tiles            out: tiles in use
+// The order of rows inside one expert's run follows the arrival of the atomics; every row's result is independent
+// of its position inside the tile, so the step's output does not depend on that order.
+constexpr int MOE_ALIGN_THREADS = 1024;
+constexpr int MOE_ALIGN_MAX_E = 1024;
+
+__global__ void __launch_bounds__(MOE_ALIGN_THREADS)
+moe_align_kernel(const int* __restrict__ ids, int n, int e0, int e_local, int block, int max_tiles,
+                 int* __restrict__ pos, int* __restrict__ sorted_rows, int* __restrict__ tile_expert,
+                 int* __restrict__ n_tiles) {
+  __shared__ int counts[MOE_ALIGN_MAX_E];
+  __shared__ int starts[MOE_ALIGN_MAX_E];
+  __shared__ int cursor[MOE_ALIGN_MAX_E];
+  __shared__ int s_tiles;
+  pdl_wait(); pdl_launch();
+  for (int e = threadIdx.x; e < e_local; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i] - e0;
+    if (e >= 0 && e < e_local) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tiles = 0;
+    for (int e = 0; e < e_local; ++e) {
+      starts[e] = tiles * block;
+      int t = (counts[e] + block - 1) / block;
+      if (tiles + t > max_tiles) t = max_tiles - tiles;   // cannot happen when max_tiles >= ceil(n / block) + e_local
+      for (int j = 0; j < t; ++j) tile_expert[tiles + j] = e;
+      tiles += t;
+    }
+    for (int j = tiles; j < max_tiles; ++j) tile_expert[j] = -1;
+    s_tiles = tiles;
+    *n_tiles = tiles;
+  }
+  for (int p = threadIdx.x; p < max_tiles * block; p += blockDim.x) sorted_rows[p] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int e = ids[i] - e0;
+    int p = -1;
+    if (e >= 0 && e < e_local) {
+      const int slot = atomicAdd(&cursor[e], 1);
+      p = starts[e] + slot;
+      if (p < s_tiles * block) sorted_rows[p] = i; else p = -1;
+    }
+    pos[i] = p;
+  }
+}
+
+// xs[p, :] = x[sorted_rows[p] / k, :] (zeros for padding rows), gate_sorted[p] = gates[sorted_rows[p]] (0 for padding).
+// One CTA per grouped row; rows of tiles that are not in use are left alone.
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int* __restrict__ sorted_rows,
+                                       const float* __restrict__ gates, const int* __restrict__ n_tiles, int block, int k,
+                                       int H, __nv_bfloat16* __restrict__ xs, float* __restrict__ gate_sorted) {
+  pdl_wait(); pdl_launch();
+  const int p = blockIdx.x;
+  if (p >= *n_tiles * block) return;
+  const int i = sorted_rows[p];
+  uint4* dst = reinterpret_cast<uint4*>(xs + (size_t)p * H);
+  if (i < 0) {
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = make_uint4(0u, 0u, 0u, 0u);
+    if (threadIdx.x == 0) gate_sorted[p] = 0.f;
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(i / k) * ldx);
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) dst[c] = src[c];
+  if (threadIdx.x == 0) gate_sorted[p] = gates[i];
+}
+
+// out[t, :] = (h ? h[t, :] : 0) + sum over the token's k slots of y[pos[t * k + j], :] (slots with pos < 0 are other
+// ranks' experts).  y rows are already gate-scaled by the down projection's epilogue.  Slots add in slot order.
+__global__ void moe_scatter_combine_kernel(const __nv_bfloat16* h, const __nv_bfloat16* __restrict__ y,
+                                           const int* __restrict__ pos, __nv_bfloat16* out, int T, int H, int k) {
+  pdl_wait(); pdl_launch();
+  const int t = blockIdx.x;
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    float acc[8];
+    if (h != nullptr) unpack8(reinterpret_cast<const uint4*>(h + (size_t)t * H)[c], acc);
+    else { for (int i = 0; i < 8; ++i) acc[i] = 0.f; }
+    for (int j = 0; j < k; ++j) {
+      const int p = pos[(size_t)t * k + j];
+      if (p < 0) continue;
+      float f[8];
+      unpack8(reinterpret_cast<const uint4*>(y + (size_t)p * H)[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    reinterpret_cast<uint4*>(out + (size_t)t * H)[c] = pack8(acc);
+  }
+}
+
 }  // namespace poot
 
 using namespace poot;
+
+// Row grouping: see moe_align_kernel.  max_tiles must be at least ceil(n / block) + e_local.
+POOT_API int poot_moe_align(const int* ids, int n, int e0, int e_local, int block, int max_tiles, int* pos,
+                            int* sorted_rows, int* tile_expert, int* n_tiles, cudaStream_t s) {
+  if (n < 0 || e_local < 1 || e_local > MOE_ALIGN_MAX_E || block < 1 || max_tiles < 1) return (int)cudaErrorInvalidValue;
+  if ((long long)max_tiles < ((long long)n + block - 1) / block + e_local) return (int)cudaErrorInvalidValue;
+  return launch_k(moe_align_kernel, dim3(1), dim3(MOE_ALIGN_THREADS), 0, s, ids, n, e0, e_local, block, max_tiles, pos,
+                  sorted_rows, tile_expert, n_tiles);
+}
+
+POOT_API int poot_moe_gather_rows(const void* x, int ldx, const int* sorted_rows, const float* gates, const int* n_tiles,
+                                  int block, int max_tiles, int k, int H, void* xs, float* gate_sorted, cudaStream_t s) {
+  if (H % 8 || ldx % 8 || k < 1) return (int)cudaErrorInvalidValue;
+  return launch_k(moe_gather_rows_kernel, dim3(max_tiles * block), dim3(128), 0, s, (const __nv_bfloat16*)x, ldx,
+                  sorted_rows, gates, n_tiles, block, k, H, (__nv_bfloat16*)xs, gate_sorted);
+}
+
+POOT_API int poot_moe_scatter_combine(const void* h, const void* y, const int* pos, void* out, int T, int H, int k,
+                                      cudaStream_t s) {
+  if (T == 0) return 0;
+  if (H % 8 || k < 1) return (int)cudaErrorInvalidValue;
+  return launch_k(moe_scatter_combine_kernel, dim3(T), dim3(256), 0, s, (const __nv_bfloat16*)h, (const __nv_bfloat16*)y,
+                  pos, (__nv_bfloat16*)out, T, H, k);
+}
 
 POOT_API int poot_moe_route(const float* logits, int T, int E, int k, int renorm, int* ids, float* gates, float* dense,
                             cudaStream_t s) {

@@ -19,6 +19,63 @@ K.register_signature("poot_gemm_skinny_grouped",
                       c_int, c_int, c_longlong, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P])
 
 
+K.register_signature("poot_moe_align", [_P, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, _P])
+K.register_signature("poot_moe_gather_rows", [_P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, _P, _P, _P])
+K.register_signature("poot_moe_scatter_combine", [_P, _P, _P, _P, c_int, c_int, c_int, _P])
+K.register_signature("poot_gemm_grouped_tiled", [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P])
+
+
+def group_block(rows: int, experts: int) -> int:
+    """Row tile of the grouped form for ``rows`` routed (token, slot) rows over ``experts`` experts: the smallest MMA
+    token width that holds an average expert's rows, so padding stays below one tile per expert."""
+    avg = max(1, rows // max(experts, 1))
+    for b in (16, 32, 64):
+        if avg <= b:
+            return b
+    return 128
+
+
+def group_capacity(rows: int, experts: int, block: int) -> int:
+    """Upper bound on row tiles: every expert's run is padded to a whole tile."""
+    return (rows + block - 1) // block + experts
+
+
+def moe_align(ids: torch.Tensor, e0: int, e_local: int, block: int, max_tiles: int, pos: torch.Tensor,
+              sorted_rows: torch.Tensor, tile_expert: torch.Tensor, n_tiles: torch.Tensor) -> None:
+    """Group the flat (token, slot) rows ``ids[n]`` by expert over this rank's experts ``[e0, e0 + e_local)``: ``pos[n]``
+    (grouped position or -1), ``sorted_rows[max_tiles * block]`` (flat row or -1), ``tile_expert[max_tiles]`` (local expert
+    of each tile or -1), ``n_tiles[1]``."""
+    check(K.fn("poot_moe_align")(ids.data_ptr(), ids.numel(), e0, e_local, block, max_tiles, pos.data_ptr(),
+                                 sorted_rows.data_ptr(), tile_expert.data_ptr(), n_tiles.data_ptr(), K._stream()), "moe_align")
+
+
+def moe_gather_rows(x: torch.Tensor, sorted_rows: torch.Tensor, gates: torch.Tensor, n_tiles: torch.Tensor, block: int,
+                    max_tiles: int, k: int, xs: torch.Tensor, gate_sorted: torch.Tensor) -> None:
+    """``xs[p] = x[sorted_rows[p] // k]`` and ``gate_sorted[p] = gates[sorted_rows[p]]`` (zeros on padding rows)."""
+    check(K.fn("poot_moe_gather_rows")(x.data_ptr(), x.stride(0), sorted_rows.data_ptr(), gates.data_ptr(), n_tiles.data_ptr(),
+                                       block, max_tiles, k, x.shape[1], xs.data_ptr(), gate_sorted.data_ptr(), K._stream()),
+          "moe_gather_rows")
+
+
+def moe_scatter_combine(h: Optional[torch.Tensor], y: torch.Tensor, pos: torch.Tensor, out: torch.Tensor, T: int, H: int,
+                        k: int) -> None:
+    """``out[t] = (h[t] or 0) + sum_j y[pos[t * k + j]]`` over the slots with ``pos >= 0``."""
+    check(K.fn("poot_moe_scatter_combine")(None if h is None else h.data_ptr(), y.data_ptr(), pos.data_ptr(), out.data_ptr(),
+                                           T, H, k, K._stream()), "moe_scatter_combine")
+
+
+def gemm_grouped_tiled(epi: int, x: torch.Tensor, W: torch.Tensor, out: torch.Tensor, tile_expert: torch.Tensor,
+                       row_scale: Optional[torch.Tensor] = None) -> None:
+    """Tiled tcgen05 GEMM over rows grouped by expert in tiles of 128: ``x[M, K]`` with ``M = tiles * 128``, stacked
+    ``W[E, N, K]``; tile ``t`` multiplies with expert ``tile_expert[t]`` (negative: unused)."""
+    E, N, Kd = W.shape
+    st = K.status_word(x.device)
+    check(K.fn("poot_gemm_grouped_tiled")(epi, x.data_ptr(), W.data_ptr(), out.data_ptr(), x.shape[0], N, Kd, x.stride(0),
+                                          out.stride(0), E, tile_expert.data_ptr(),
+                                          None if row_scale is None else row_scale.data_ptr(), st.data_ptr(), K._stream()),
+          "gemm_grouped_tiled")
+
+
 def moe_route(logits: torch.Tensor, k: int, renorm: bool, ids: torch.Tensor, gates: torch.Tensor, dense: torch.Tensor,
               mode: str = "softmax", select_bias: Optional[torch.Tensor] = None, scale: float = 1.0, n_group: int = 1,
               topk_group: int = 1):

@@ -256,7 +256,7 @@ def _moe_blocks(g: Graph, plans) -> Dict[int, dict]:
     blocks: Dict[int, dict] = {}
     disp = [k for k, p in enumerate(plans) if p.kind == "dispatch"]
     for idx, k in enumerate(disp):
-        if plans[k].kernels != ["poot_moe_route"]:
+        if not plans[k].kernels or plans[k].kernels[0] != "poot_moe_route":
             continue
         # the router GEMM is the dispatch just before, the grouped GEMMs and the combine follow
         router = disp[idx - 1]
@@ -266,7 +266,7 @@ def _moe_blocks(g: Graph, plans) -> Dict[int, dict]:
         tail = []
         for j in disp[idx + 1:]:
             tail.append(j)
-            if plans[j].kernels == ["poot_moe_combine"]:
+            if plans[j].kernels in (["poot_moe_combine"], ["poot_moe_scatter_combine"]):
                 break
         comb = tail[-1]
         out = g.eqns[comb].outputs[0]

@@ -268,10 +268,19 @@ def _absorb_routed_experts(g: Graph, plans: List[Plan], users, prod) -> None:
                 changed = True
     for k, end, region, anc in blocks:
         grouped = 0
+        # few (token, slot) rows: one group per row reads only the selected experts.  More rows than experts: the rows
+        # are grouped by expert on the device first (align + gather), and the combine scatters back per token.
+        sel = g.types[g.eqns[k].inputs[0]]
+        rows_k = (sel.numel // sel.shape[-1]) * g.eqns[k].attrs.get("k", 1)
+        by_rows = rows_k > sel.shape[-1]
+        if by_rows:
+            plans[k] = Plan("dispatch", ["poot_moe_route", "poot_moe_align", "poot_moe_gather_rows"],
+                            "routing, block-aligned grouping of the rows by expert, gather into the grouped order")
         for i in sorted(region | (anc & back)):
             op = g.eqns[i].op
             if i == end:
-                plans[i] = Plan("dispatch", ["poot_moe_combine"], "sum of the gate-scaled expert outputs into the residual stream")
+                plans[i] = Plan("dispatch", ["poot_moe_scatter_combine" if by_rows else "poot_moe_combine"],
+                                "sum of the gate-scaled expert outputs into the residual stream")
             elif op == "indexed_matmul":
                 grouped += 1
                 note = "SwiGLU in the epilogue" if grouped == 1 else "gate scaling in the epilogue"

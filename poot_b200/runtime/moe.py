@@ -4,14 +4,17 @@ Two regimes, both on the grouped swap-AB tcgen05 kernel over the stacked expert 
 
 * few (token, slot) pairs (``T * k <= E``, e.g. batch-1 decode): one group per pair reads only the experts that
   were selected (the reference's indexed GEMV, crates/poot-kernelgen/src/contraction/indexed.rs:1-6);
-* otherwise: one group per expert runs all T tokens; the dense gate matrix (0 for an unselected expert) scales the
-  rows of the down projection, and the combine kernel adds the E outputs to the residual stream - every expert
-  weight is read exactly once per step (the reference groups rows by expert, passes/group_expert_rows.rs:1-8).
+* otherwise the rows are grouped by expert on the device (``moe_align``: block-aligned runs, one expert per row tile),
+  gathered into that order, multiplied by two grouped GEMMs that walk the tiles (the swap-AB kernel for tiles of up to
+  64 rows, the tiled tcgen05 kernel for tiles of 128), and scattered back with a sum over each token's slots - every
+  expert multiplies its own rows only, so the FLOPs are the routed FLOPs at any token count (the reference's
+  group_expert_rows pass and grouped indexed contraction, passes/group_expert_rows.rs:1-8, contraction/indexed.rs:1-6).
 
-Expert parallelism (one expert shard per rank, attention tensor-parallel): activations are replicated after the
-fused all-reduce, so no dispatch transfer is needed; each rank runs its local experts over all tokens and the
-gate-scaled down projection is written straight into every rank's inbox - the combine all-to-all is the one-shot
-all-reduce fused into the expert GEMM's epilogue.
+Expert parallelism (an expert shard per rank, attention tensor-parallel): activations are replicated after the
+attention block's all-reduce, so "dispatch" is a selection, not a transfer - each rank groups only the rows routed to
+its own experts (any number of local experts) and the ranks' partial sums meet in one all-reduce.  In decode-sized
+steps with one expert per rank the gate-scaled down projection is written straight into every rank's inbox from the
+GEMM epilogue (the combine is the one-shot all-reduce fused into the expert GEMM).
 """
 from __future__ import annotations
 
@@ -123,51 +126,84 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
             parts.add_((L.ex_bdown[ids.long()].float() * gates[:, None]).to(parts.dtype))
         M.moe_combine(h, parts, h, T, H, G, H, per_token=k)
         return None
-    if ep is not None and e_local == 1 and T > 128:
-        # prefill with one expert per rank: two tiled GEMMs over all T rows (the expert's weights are read once);
-        # the gate (0 for tokens routed elsewhere) scales the activation rows before the down projection
-        act = eng.act[:T]
-        eng._count(4)
-        K.linear(x, L.ex_wgu[0], K.EPI_SWIGLU, act)
-        act.mul_(dense[e0, :T].unsqueeze(1))
-        import torch.distributed as dist
-        p = eng.comm.partial[:T]
-        K.linear(act, L.ex_wdown[0], K.EPI_STORE, p)
-        dist.all_reduce(p, group=eng.comm.group)
-        K.add(h, p, out=h)
-        return None
-    # dense-over-experts regime, in token chunks of at most 128 rows
-    for t0 in range(0, T, 128):
-        n = min(128, T - t0)
-        xs = x[t0:t0 + n]
-        act = buf["act"][:e_local * n * F].view(e_local * n, F)
-        scale = dense[e0:e0 + e_local, t0:t0 + n].contiguous() if (t0 or n != T or e_local != E) else dense
+    if tp is not None and e_local == 1 and T <= 128:
+        # decode-sized step with one expert per rank: the expert runs the step's rows with its gate column as the row
+        # scale and its epilogue pushes the result into every rank's inbox (the combine is the fused all-reduce)
+        act = buf["act"][:T * F].view(T, F)
+        scale = dense[e0:e0 + 1, :T].contiguous()
         eng._count(2)
-        if buf["gu"] is None:
-            M.gemm_grouped(K.EPI_SWIGLU, xs, L.ex_wgu, act, n, e_local, out_group_stride=n * F, ldo=F)
-        else:
-            W2 = L.ex_wgu.shape[1]
-            gu = buf["gu"][:e_local * n * W2].view(e_local * n, W2)
-            M.gemm_grouped(K.EPI_STORE, xs, L.ex_wgu, gu, n, e_local, out_group_stride=n * W2, ldo=W2)
-            _expert_act(eng, L, gu, act, torch.arange(e0, e0 + e_local, device=gu.device).repeat_interleave(n))
-        if tp is not None and e_local == 1 and T <= 128:
-            M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, None, n, 1, x_row_mul=n, row_scale=scale, ldo=H, tp=tp)
-            return "pushed"
-        parts = buf["parts"][:e_local * n * H].view(e_local * n, H)
-        M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, parts, n, e_local, x_row_mul=n, out_group_stride=n * H,
-                       row_scale=scale, ldo=H)
-        if L.ex_bdown is not None:      # the bias is part of the expert's output, so it is scaled by the row's gate too
-            sc = dense[e0:e0 + e_local, t0:t0 + n].reshape(e_local * n, 1)
-            parts.add_((L.ex_bdown[e0:e0 + e_local].float().repeat_interleave(n, 0) * sc).to(parts.dtype))
-        eng._count()
-        if ep is None:
-            M.moe_combine(h[t0:t0 + n], parts, h[t0:t0 + n], n, H, e_local, n * H)
-        else:
-            M.moe_combine(None, parts, eng.comm.partial[t0:t0 + n], n, H, e_local, n * H)
-    if ep is not None:      # library all-reduce over the ranks' expert partials, then the residual add
-        import torch.distributed as dist
-        p = eng.comm.partial[:T]
-        dist.all_reduce(p, group=eng.comm.group)
-        eng._count()
-        K.add(h, p, out=h)
+        M.gemm_grouped(K.EPI_SWIGLU, x, L.ex_wgu, act, T, 1, out_group_stride=T * F, ldo=F)
+        M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, None, T, 1, x_row_mul=T, row_scale=scale, ldo=H, tp=tp)
+        return "pushed"
+    # Row-grouped regime: the (token, slot) rows of every local expert are made contiguous and padded to whole row
+    # tiles (moe_align), the activations are gathered into that order, and two grouped GEMMs walk the tiles - each
+    # expert multiplies its own rows only, at any token count and for any number of local experts.
+    n = T * k
+    block = M.group_block(n, E)
+    max_tiles = M.group_capacity(n, e_local, block)
+    cap = max_tiles * block
+    g = _group_buffers(eng, cap, max_tiles, n)
+    pos, sorted_rows, tile_expert, n_tiles = g["pos"][:n], g["sorted_rows"][:cap], g["tile_expert"][:max_tiles], g["n_tiles"]
+    xs, gate_s = g["xs"][:cap], g["gate"][:cap]
+    act, y = g["act"][:cap], g["y"][:cap]
+    eng._count(4)
+    M.moe_align(ids, e0, e_local, block, max_tiles, pos, sorted_rows, tile_expert, n_tiles)
+    M.moe_gather_rows(x, sorted_rows, gates, n_tiles, block, max_tiles, k, xs, gate_s)
+    plain = buf["gu"] is None
+    tiled = block == 128 and L.ex_wgu.shape[1] % 128 == 0 and H % 128 == 0
+    W2 = L.ex_wgu.shape[1]
+    if plain:
+        up_out, up_epi = act, K.EPI_SWIGLU
+    else:               # biased / clamped / non-SwiGLU experts: plain projection, the tile's expert bias, then the activation
+        up_out, up_epi = g["gu"][:cap], K.EPI_STORE
+    if tiled:
+        M.gemm_grouped_tiled(up_epi, xs, L.ex_wgu, up_out, tile_expert)
+    else:
+        M.gemm_grouped(up_epi, xs, L.ex_wgu, up_out, block, max_tiles, group_expert=tile_expert, x_row_mul=block,
+                       out_group_stride=block * up_out.shape[1], ldo=up_out.shape[1])
+    if not plain:
+        expert_of_row = (tile_expert.clamp(min=0) + e0).repeat_interleave(block).long()
+        _expert_act(eng, L, up_out, act, expert_of_row)
+    if tiled:
+        M.gemm_grouped_tiled(K.EPI_STORE, act, L.ex_wdown, y, tile_expert, row_scale=gate_s)
+    else:
+        M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, y, block, max_tiles, group_expert=tile_expert, x_row_mul=block,
+                       out_group_stride=block * H, row_scale=gate_s, ldo=H)
+    if L.ex_bdown is not None:      # the bias is part of the expert's output, so it is scaled by the row's gate too
+        expert_of_row = (tile_expert.clamp(min=0) + e0).repeat_interleave(block).long()
+        y.add_((L.ex_bdown[expert_of_row].float() * gate_s[:, None]).to(y.dtype))
+    eng._count()
+    if ep is None:
+        M.moe_scatter_combine(h, y, pos, h, T, H, k)
+        return None
+    # expert parallel over the library collectives: this rank's experts' share of every token, summed over the ranks
+    import torch.distributed as dist
+    p = eng.comm.partial[:T]
+    M.moe_scatter_combine(None, y, pos, p, T, H, k)
+    dist.all_reduce(p, group=eng.comm.group)
+    eng._count()
+    K.add(h, p, out=h)
     return None
+
+
+def _group_buffers(eng, cap: int, max_tiles: int, n: int):
+    """Scratch of the row-grouped regime, grown to the largest step seen (steps are captured per shape, so a buffer
+    that a captured graph uses is never replaced: growth only happens before the first capture of a larger shape)."""
+    c, dev = eng.cfg, eng.device
+    g = getattr(eng, "_moe_group", None)
+    if g is None or g["cap"] < cap or g["tiles"] < max_tiles or g["n"] < n:
+        F, H = c.moe_ffn, c.hidden
+        W2 = next(L_.ex_wgu.shape[1] for L_ in eng.w.layers if L_.ex_wgu is not None)
+        need_gu = c.expert_bias or c.swiglu_limit > 0 or c.act != "silu" or not c.gated_ffn
+        g = {"cap": cap, "tiles": max_tiles, "n": n,
+             "pos": torch.zeros(n, dtype=torch.int32, device=dev),
+             "sorted_rows": torch.zeros(cap, dtype=torch.int32, device=dev),
+             "tile_expert": torch.zeros(max_tiles, dtype=torch.int32, device=dev),
+             "n_tiles": torch.zeros(1, dtype=torch.int32, device=dev),
+             "xs": torch.zeros(cap, H, dtype=torch.bfloat16, device=dev),
+             "gate": torch.zeros(cap, dtype=torch.float32, device=dev),
+             "act": torch.zeros(cap, F, dtype=torch.bfloat16, device=dev),
+             "gu": torch.zeros(cap, W2, dtype=torch.bfloat16, device=dev) if need_gu else None,
+             "y": torch.zeros(cap, H, dtype=torch.bfloat16, device=dev)}
+        eng._moe_group = g
+    return g

@@ -525,6 +525,53 @@ def gemm_grouped(epi, x, W, out, M, groups, group_expert=None, x_row_div=0, x_ro
             flat[o:o + n_out] = r[m]
 
 
+def moe_align(ids, e0, e_local, block, max_tiles, pos, sorted_rows, tile_expert, n_tiles):
+    from ..plan.moe_align import group_expert_rows
+    flat = ids.reshape(-1).long()
+    local = (flat >= e0) & (flat < e0 + e_local)
+    idx = torch.nonzero(local).reshape(-1)
+    rows, tiles, padded = group_expert_rows((flat[idx] - e0).numpy(), e_local, block)
+    sorted_rows.fill_(-1)
+    pos.fill_(-1)
+    tile_expert.fill_(-1)
+    n_tiles[0] = padded // block
+    if padded:
+        sr = torch.from_numpy(rows)
+        live = sr >= 0
+        mapped = torch.where(live, idx[sr.clamp(min=0)], torch.full_like(sr, -1))
+        sorted_rows[:padded] = mapped.to(sorted_rows.dtype)
+        pos[mapped[live]] = torch.nonzero(live).reshape(-1).to(pos.dtype)
+        tile_expert[:padded // block] = torch.from_numpy(tiles)
+
+
+def moe_gather_rows(x, sorted_rows, gates, n_tiles, block, max_tiles, k, xs, gate_sorted):
+    n = int(n_tiles[0]) * block
+    sr = sorted_rows[:n].long()
+    live = sr >= 0
+    xs[:n] = torch.where(live[:, None], x[(sr.clamp(min=0) // k)], torch.zeros_like(xs[:n]))
+    gate_sorted[:n] = torch.where(live, gates.reshape(-1)[sr.clamp(min=0)], torch.zeros_like(gate_sorted[:n]))
+
+
+def moe_scatter_combine(h, y, pos, out, T, H, k):
+    acc = h[:T].float().clone() if h is not None else torch.zeros(T, H)
+    p = pos[:T * k].view(T, k).long()
+    for j in range(k):                                      # slot order, as the kernel adds
+        live = p[:, j] >= 0
+        acc = acc + torch.where(live[:, None], y[p[:, j].clamp(min=0)].float(), torch.zeros(T, H))
+    out[:T].copy_(_bf(acc))
+
+
+def gemm_grouped_tiled(epi, x, W, out, tile_expert, row_scale=None):
+    for t, ex in enumerate(tile_expert.tolist()):
+        if ex < 0:
+            continue
+        rows = slice(t * 128, (t + 1) * 128)
+        y = x[rows].float() @ W[ex].float().T
+        if row_scale is not None:
+            y = y * row_scale[rows].reshape(-1, 1)
+        _epilogue(y, epi, out[rows], None)
+
+
 _status = torch.zeros(16, dtype=torch.int32)
 
 
@@ -541,7 +588,9 @@ def emulated_kernels():
                 argmax=argmax, argmax_partials=argmax_partials, argmax_combine=argmax_combine,
                 sample_gumbel=sample_gumbel, decode_advance=decode_advance,
                 status_word=lambda device=None: _status, check_status=lambda device=None: None),
-        moe_ops: dict(moe_route=moe_route, moe_combine=moe_combine, gemm_grouped=gemm_grouped),
+        moe_ops: dict(moe_route=moe_route, moe_combine=moe_combine, gemm_grouped=gemm_grouped, moe_align=moe_align,
+                      moe_gather_rows=moe_gather_rows, moe_scatter_combine=moe_scatter_combine,
+                      gemm_grouped_tiled=gemm_grouped_tiled),
         suffix_ops: dict(adjust_logits=adjust_logits, token_logprob=token_logprob),
     }
     saved = {(mod, name): getattr(mod, name) for mod, fns in table.items() for name in fns}

@@ -518,6 +518,27 @@ def test_planner_launch_census_equals_the_engine_launch_count(kw):
     assert launched - 2 == prog.dispatches, (launched, prog.census)
 
 
+def test_planner_census_of_the_row_grouped_expert_regime():
+    """More (token, slot) rows than experts: routing, align and gather, two grouped GEMMs, scatter-combine."""
+    from poot_b200.models.model import Model, StepSpec
+    from poot_b200.plan import compile_graph
+    from poot_b200.runtime.engine import StepShape
+    cfg = _cfg(n_experts=4, top_k=2, moe_ffn=128)
+    prog = compile_graph(Model(cfg).trace(StepSpec(rows=1, tokens=18, capacity=64, paged=True, pool_slots=128)))
+    L = cfg.n_layers
+    moe = {k: v for k, v in prog.census.items() if "moe" in k or "grouped" in k}
+    assert moe == {"poot_moe_route": L, "poot_moe_align": L, "poot_moe_gather_rows": L, "poot_gemm_skinny_grouped": 2 * L,
+                   "poot_moe_scatter_combine": L}
+    counts = {}
+    with emulated_kernels():
+        for name, c in (("moe", cfg), ("dense", _cfg())):
+            _, eng, sess = _engine(c, 2, 64, 48)
+            sess.prefill_fast(torch.randint(0, c.vocab, (2, 9), generator=torch.Generator().manual_seed(0), dtype=torch.int32))
+            counts[name] = eng.launches_per_step[eng._key(StepShape(18, 2, 0))]
+    # a routed block is the router GEMM + six launches where the dense FFN has two
+    assert counts["moe"] - counts["dense"] == L * (7 - 2), counts
+
+
 def test_encoder_engine_matches_the_graph_oracle(tmp_path):
     """BERT on the device engine's kernels (restated on the host): ragged batch, K/V of each sequence in its own pool
     blocks, every token seeing its whole sequence; hidden states, pooled embeddings and a cross-encoder's scores against

@@ -23,12 +23,14 @@ def test_pipeline_ranks_generate_what_one_process_generates(world):
     assert out["sent_bytes"] > 0
 
 
-def test_tensor_parallel_ranks_over_the_library_collectives_match_one_process():
-    """Two ranks over gloo with emulated kernels: Megatron shares, all-reduce after the row-parallel projections,
-    expert-parallel MoE, vocabulary-parallel head with the greedy pick merged from per-shard partial tables."""
+@pytest.mark.parametrize("world", [2, 4])
+def test_tensor_parallel_ranks_over_the_library_collectives_match_one_process(world):
+    """Ranks over gloo with emulated kernels: Megatron shares, all-reduce after the row-parallel projections,
+    expert-parallel MoE with two experts per rank (each rank groups only its own experts' rows), vocabulary-parallel
+    head with the greedy pick merged from per-shard partial tables."""
     worker = os.path.join(os.path.dirname(__file__), "tp_cpu_worker.py")
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", str(29700 + os.getpid() % 200), worker]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29700 + world + os.getpid() % 200), worker]
     r = subprocess.run(cmd, env=dict(os.environ, OMP_NUM_THREADS="2", CUDA_VISIBLE_DEVICES=""), capture_output=True,
                        text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-3000:]

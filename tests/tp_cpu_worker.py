@@ -37,9 +37,11 @@ def main() -> int:
     rank, world = dist.get_rank(), dist.get_world_size()
     results = {}
     with emulated_kernels():
-        for name, kw in (("dense", {}), ("moe", dict(n_experts=4, top_k=2, moe_ffn=128))):
-            cfg = DecoderConfig(n_layers=2, hidden=128, n_heads=4, n_kv_heads=2, head_dim=64, ffn=256, vocab=4096,
-                                max_position=256, **kw)
+        # two experts per rank: each rank groups only the rows routed to its own experts (row-grouped regime at prefill,
+        # one group per (token, slot) never applies under expert parallelism)
+        for name, kw in (("dense", {}), ("moe", dict(n_experts=2 * world, top_k=2, moe_ffn=128))):
+            cfg = DecoderConfig(n_layers=2, hidden=128, n_heads=max(4, world), n_kv_heads=2 if world <= 2 else world, head_dim=64,
+                                ffn=256, vocab=4096, max_position=256, **kw)
             got, eng = run(cfg, rank, world, NcclComm(rank, world, torch.device("cpu")))
             eng.samp_params[:2] = torch.tensor([[1.0, -1e30, 1.0, 1.0]] * 2)
             want, ref = run(cfg, 0, 1, None)
