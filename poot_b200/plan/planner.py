@@ -284,7 +284,9 @@ def _absorb_routed_experts(g: Graph, plans: List[Plan], users, prod) -> None:
             elif op == "indexed_matmul":
                 grouped += 1
                 note = "SwiGLU in the epilogue" if grouped == 1 else "gate scaling in the epilogue"
-                plans[i] = Plan("dispatch", ["poot_gemm_skinny_grouped"], note)
+                # tiles of 128 grouped rows (an average expert has more than 64 rows) go through the tiled tcgen05 kernel
+                tiled = by_rows and rows_k // sel.shape[-1] > 64
+                plans[i] = Plan("dispatch", ["poot_gemm_grouped_tiled" if tiled else "poot_gemm_skinny_grouped"], note)
             elif i != k:
                 plans[i] = Plan("none", note=f"evaluated inside the routed-experts kernels (route of eqn {k})")
         for u in users.get(g.eqns[end].outputs[0], []):  # the residual add is moe_combine's accumulate
