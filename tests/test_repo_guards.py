@@ -16,7 +16,7 @@ LAYERS = {
     "models": {"tensor", "ir", "load"}, "plan": {"tensor", "ir", "quant", "target", "models", "oracle"},
     "ops": set(), "profile": {"target", "ops"}, "text": set(),
     "runtime": {"models", "ops", "quant", "parallel", "tensor", "plan"}, "parallel": {"ops", "runtime"},
-    "utils": {"ops", "oracle", "runtime", "models", "tensor"},
+    "utils": {"ops", "oracle", "runtime", "models", "tensor", "plan"},
     "driver": {"models", "runtime", "ops", "load", "quant", "ir", "oracle", "text", "tensor", "profile", "parallel"},
     "serve": {"driver", "text", "profile", "models", "parallel", "runtime", "ops", "load"}, "cli": {"driver", "text", "models"},
 }
