@@ -738,7 +738,9 @@ def decode_advance(picked: torch.Tensor, tokens: torch.Tensor, positions: torch.
 register_signature("poot_quant_gemv", [c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P])
 register_signature("poot_quant_row_gather", [c_int, _P, _P, _P, c_int, c_int, c_int, _P])
 register_signature("poot_quant_dequant_bf16", [c_int, _P, _P, c_int, c_int, _P])
-QUANT_DEVICE_FORMATS = {"Q4_0": 2, "Q8_0": 8, "Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
+# block formats with dequant-fused device kernels (name -> ggml type id, the id the launchers take)
+QUANT_DEVICE_FORMATS = {"Q4_0": 2, "Q4_1": 3, "Q5_0": 6, "Q5_1": 7, "Q8_0": 8, "Q2_K": 10, "Q3_K": 11, "Q4_K": 12,
+                        "Q5_K": 13, "Q6_K": 14, "IQ4_NL": 20, "IQ4_XS": 23, "MXFP4": 39}
 
 
 class QuantWeight:

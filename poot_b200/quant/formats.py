@@ -33,18 +33,18 @@ class FormatDescriptor:
 _F = FormatDescriptor
 FORMATS: Dict[str, FormatDescriptor] = {f.name: f for f in [
     _F("F32", "dense", 1, 4, 0), _F("F16", "dense", 1, 2, 1, encode=True), _F("BF16", "dense", 1, 2, 30),
-    _F("Q4_0", "blocks", 32, 18, 2, encode=True, device_gemv=True), _F("Q4_1", "blocks", 32, 20, 3, encode=True),
-    _F("Q5_0", "blocks", 32, 22, 6, encode=True), _F("Q5_1", "blocks", 32, 24, 7, encode=True),
+    _F("Q4_0", "blocks", 32, 18, 2, encode=True, device_gemv=True), _F("Q4_1", "blocks", 32, 20, 3, encode=True, device_gemv=True),
+    _F("Q5_0", "blocks", 32, 22, 6, encode=True, device_gemv=True), _F("Q5_1", "blocks", 32, 24, 7, encode=True, device_gemv=True),
     _F("Q8_0", "blocks", 32, 34, 8, encode=True, device_gemv=True),
-    _F("Q2_K", "blocks", 256, 84, 10, encode=True), _F("Q3_K", "blocks", 256, 110, 11, encode=True),
+    _F("Q2_K", "blocks", 256, 84, 10, encode=True, device_gemv=True), _F("Q3_K", "blocks", 256, 110, 11, encode=True, device_gemv=True),
     _F("Q4_K", "blocks", 256, 144, 12, encode=True, device_gemv=True),
     _F("Q5_K", "blocks", 256, 176, 13, encode=True, device_gemv=True),
     _F("Q6_K", "blocks", 256, 210, 14, encode=True, device_gemv=True),
-    _F("IQ4_NL", "blocks", 32, 18, 20), _F("IQ4_XS", "blocks", 256, 136, 23),
+    _F("IQ4_NL", "blocks", 32, 18, 20, device_gemv=True), _F("IQ4_XS", "blocks", 256, 136, 23, device_gemv=True),
     _F("IQ2_XS", "blocks", 256, 74, 17, decode=False, note="codebook grid not reproduced"),
     _F("IQ3_XXS", "blocks", 256, 98, 18, decode=False, note="codebook grid not reproduced"),
     _F("IQ3_S", "blocks", 256, 110, 21, decode=False, note="codebook grid not reproduced"),
-    _F("MXFP4", "blocks", 32, 17, 39, encode=True),
+    _F("MXFP4", "blocks", 32, 17, 39, encode=True, device_gemv=True),
     _F("E4M3_CHANNEL", "planar", note="fp8 weight + per-output-channel f32 scale", encode=True),
     _F("E4M3_BLOCK128", "planar", note="fp8 weight + 128x128 block scales", encode=True),
     _F("E2M1_ROW32", "planar", note="fp4 codes + e8m0 scale per 32 values of a row", encode=True),

@@ -92,3 +92,47 @@ def test_packed_row_and_column_views():
     assert np.array_equal(pw.cols(256, 256).to_f32(), full[:, 256:])
     with pytest.raises(ValueError):
         pw.cols(100, 256)
+
+
+def _random_blocks(fmt, rows, K, seed=3):
+    """Packed rows of ``fmt``: encoded from random weights where an encoder exists, otherwise random bytes with
+    finite f16 scale fields (IQ4_NL / IQ4_XS have a decoder only)."""
+    rng = np.random.default_rng(seed)
+    d = FORMATS[fmt]
+    if d.encode:
+        return codec.quantize(fmt, (rng.standard_normal((rows, K)) * 0.05).astype(np.float32)).reshape(rows, -1)
+    raw = rng.integers(0, 256, size=(rows, K // d.block_elems, d.block_bytes), dtype=np.uint8)
+    scale = (rng.standard_normal((rows, K // d.block_elems)) * 0.01).astype(np.float16).view(np.uint8).reshape(rows, -1, 2)
+    raw[:, :, 0:2] = scale
+    return raw.reshape(rows, -1)
+
+
+DEVICE_BLOCK_FORMATS = [n for n, f in FORMATS.items() if f.storage == "blocks" and f.device_gemv]
+
+
+@pytest.mark.parametrize("fmt", DEVICE_BLOCK_FORMATS)
+def test_device_block_decoders_equal_the_host_codec(fmt):
+    """The block decoders that the device kernels run are also built for the host (the same source): every value of
+    every format equals the host codec's, so a wrong nibble order, bit plane or scale index cannot hide until a GPU run."""
+    import ctypes
+    from poot_b200.ops._lib import kernels
+    from poot_b200.ops.cuda_ops import QUANT_DEVICE_FORMATS
+    lib = kernels()
+    f = lib.poot_quant_decode8_host
+    f.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+    f.restype = ctypes.c_int
+    assert len(DEVICE_BLOCK_FORMATS) == 13 and set(DEVICE_BLOCK_FORMATS) == set(QUANT_DEVICE_FORMATS)
+    rows, K = 3, 1024
+    packed = np.ascontiguousarray(_random_blocks(fmt, rows, K))
+    want = codec.dequantize(fmt, packed, (rows, K))
+    got = np.zeros((rows, K), np.float32)
+    out8 = np.zeros(8, np.float32)
+    for r in range(rows):
+        row = np.ascontiguousarray(packed[r])
+        for k in range(0, K, 8):
+            assert f(QUANT_DEVICE_FORMATS[fmt], row.ctypes.data, k, out8.ctypes.data) == 0
+            got[r, k:k + 8] = out8
+    # the kernels factor a block as scale * q - offset in f32; the host codec multiplies in a slightly different order
+    assert np.allclose(got, want, rtol=2e-6, atol=1e-7), (fmt, np.abs(got - want).max())
+    assert f(QUANT_DEVICE_FORMATS[fmt], packed.ctypes.data, 4, out8.ctypes.data) == 1      # k must be a multiple of 8
+    assert f(99, packed.ctypes.data, 0, out8.ctypes.data) == 1

@@ -4,21 +4,28 @@ import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
-FMTS = ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0"]
+FMTS = ["Q4_K", "Q5_K", "Q6_K", "Q8_0", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q2_K", "Q3_K", "IQ4_NL", "IQ4_XS", "MXFP4"]
 
 
 def _packed(fmt, N, Kd, seed=0):
     from poot_b200.ops import cuda_ops as K
     from poot_b200.quant import codec
-    w = (np.random.default_rng(seed).standard_normal((N, Kd)) * 0.05).astype(np.float32)
-    p = codec.quantize(fmt, w)
+    from poot_b200.quant.formats import FORMATS
+    rng = np.random.default_rng(seed)
+    d = FORMATS[fmt]
+    if d.encode:
+        p = codec.quantize(fmt, (rng.standard_normal((N, Kd)) * 0.05).astype(np.float32))
+    else:           # decoder-only formats (IQ4_NL, IQ4_XS): random code bytes under finite f16 block scales
+        raw = rng.integers(0, 256, size=(N, Kd // d.block_elems, d.block_bytes), dtype=np.uint8)
+        raw[:, :, 0:2] = (rng.standard_normal((N, Kd // d.block_elems)) * 0.01).astype(np.float16).view(np.uint8).reshape(N, -1, 2)
+        p = raw.reshape(-1)
     deq = codec.dequantize(fmt, p, (N, Kd))
     return K.QuantWeight(fmt, torch.from_numpy(p).cuda(), N, Kd), torch.from_numpy(deq).cuda()
 
 
 @pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("M", [1, 3])
-@pytest.mark.parametrize("N,Kd", [(1026, 1024), (258, 5376)])
+@pytest.mark.parametrize("N,Kd", [(1026, 1024), (258, 5376), (36, 14336)])     # 14336 = the down projection's K of Llama-3-8B
 def test_quant_gemv_matches_dequantised_reference(fmt, M, N, Kd):
     from poot_b200.ops import cuda_ops as K
     W, deq = _packed(fmt, N, Kd)
