@@ -3,9 +3,12 @@
 Constraint kinds of the reference (crates/poot-text/src/guided.rs, src/grammar.rs:1-6): a fixed ``choice`` list, a
 ``regex``, a ``json_schema`` (compiled to a regex for the supported subset), free-form ``json`` (a pushdown prefix
 acceptor), a ``GBNF`` grammar (the stack machine llama.cpp uses) and a forced tool call (a JSON-schema constraint
-built from the tool's parameters).  A constraint is a character-level acceptor with ``clone`` / ``feed``; the mask
-of a step marks every token whose text keeps the acceptor alive (0 = allowed, ``f32::MIN`` = excluded, the
-``MASKED_LOGIT`` of the sampling rules).  Hostile inputs are bounded: pattern length, grammar size, nesting depth.
+built from the tool's parameters).  Every kind becomes a machine stepped over *bytes*: choice, regex, schema and tool
+constraints a dense byte DFA (``text/automata.py``), free-form JSON and GBNF a stack machine whose states are immutable
+values.  The mask of a step (0 = allowed, ``f32::MIN`` = excluded, the ``MASKED_LOGIT`` of the sampling rules) is the
+cached allowed-token set of the machine's current state; a state's set is computed once, by a pruned walk of the
+vocabulary's byte trie.  Hostile inputs are bounded: pattern length, automaton size and build work, grammar size,
+nesting depth.
 """
 from __future__ import annotations
 
@@ -24,224 +27,6 @@ class ConstraintError(ValueError):
     pass
 
 
-# ---- acceptors -------------------------------------------------------------------------------------------------
-class RegexAcceptor:
-    def __init__(self, pattern: str, text: str = ""):
-        import regex
-        if len(pattern) > MAX_PATTERN:
-            raise ConstraintError("regex too long")
-        try:
-            self.rx = regex.compile(pattern, flags=regex.DOTALL)
-        except regex.error as e:
-            raise ConstraintError(f"bad regex: {e}") from None
-        self.text = text
-
-    def clone(self):
-        c = object.__new__(RegexAcceptor)
-        c.rx, c.text = self.rx, self.text
-        return c
-
-    def feed(self, s: str) -> bool:
-        self.text += s
-        return self.rx.fullmatch(self.text, partial=True) is not None
-
-    def complete(self) -> bool:
-        return self.rx.fullmatch(self.text) is not None
-
-
-class ChoiceAcceptor:
-    def __init__(self, choices: Sequence[str], text: str = ""):
-        if not choices:
-            raise ConstraintError("empty choice list")
-        self.choices, self.text = list(choices), text
-
-    def clone(self):
-        return ChoiceAcceptor(self.choices, self.text)
-
-    def feed(self, s: str) -> bool:
-        self.text += s
-        return any(c.startswith(self.text) for c in self.choices)
-
-    def complete(self) -> bool:
-        return self.text in self.choices
-
-
-class JsonAcceptor:
-    """Prefix acceptor of one JSON value (RFC 8259) with a nesting bound."""
-
-    def __init__(self):
-        self.stack: List[str] = ["value"]     # what is expected next, innermost last
-        self.buf = ""                         # scalar being read
-        self.mode = None                      # None | "str" | "esc" | "num" | "lit"
-        self.lit = ""
-        self.uni = 0
-
-    def clone(self):
-        c = JsonAcceptor()
-        c.stack, c.buf, c.mode, c.lit, c.uni = list(self.stack), self.buf, self.mode, self.lit, self.uni
-        return c
-
-    def complete(self) -> bool:
-        if self.mode == "num":
-            return self._num_done(self.buf) and self.stack == ["value_done_pending"]
-        return not self.stack and self.mode is None
-
-    @staticmethod
-    def _num_ok_prefix(s: str) -> bool:
-        import re
-        return re.fullmatch(r"-?(0|[1-9]\d*)?(\.\d*)?([eE][+-]?\d*)?", s) is not None and s != ""
-
-    @staticmethod
-    def _num_done(s: str) -> bool:
-        import re
-        return re.fullmatch(r"-?(0|[1-9]\d*)(\.\d+)?([eE][+-]?\d+)?", s) is not None
-
-    def _value_done(self):
-        while self.stack and self.stack[-1] in ("value", "value_done_pending"):
-            self.stack.pop()
-            break
-
-    def feed(self, s: str) -> bool:
-        for ch in s:
-            if not self._feed1(ch):
-                return False
-        return True
-
-    def _feed1(self, ch: str) -> bool:
-        if self.mode == "str":
-            if ch == "\\":
-                self.mode = "esc"
-            elif ch == '"':
-                self.mode = None
-                self._after_string()
-            elif ord(ch) < 0x20:
-                return False
-            return True
-        if self.mode == "esc":
-            if ch == "u":
-                self.mode, self.uni = "uni", 4
-            elif ch in '"\\/bfnrt':
-                self.mode = "str"
-            else:
-                return False
-            return True
-        if self.mode == "uni":
-            if ch not in "0123456789abcdefABCDEF":
-                return False
-            self.uni -= 1
-            if self.uni == 0:
-                self.mode = "str"
-            return True
-        if self.mode == "lit":
-            self.buf += ch
-            if not self.lit.startswith(self.buf):
-                return False
-            if self.buf == self.lit:
-                self.mode = None
-                self._close_value()
-            return True
-        if self.mode == "num":
-            if self._num_ok_prefix(self.buf + ch):
-                self.buf += ch
-                return True
-            if not self._num_done(self.buf):
-                return False
-            self.mode = None
-            self.stack.pop()          # value_done_pending
-            self._close_value(pop=False)
-            return self._feed1(ch)
-        if ch in " \t\r\n":
-            return True
-        if not self.stack:
-            return False
-        top = self.stack[-1]
-        if top == "value" or top == "value_or_end_array":
-            if top == "value_or_end_array":
-                if ch == "]":
-                    self.stack.pop()
-                    self._close_value(pop=False)
-                    return True
-                self.stack[-1] = "array_next"
-                self.stack.append("value")
-            return self._start_value(ch)
-        if top == "key_or_end":
-            if ch == "}":
-                self.stack.pop()
-                self._close_value(pop=False)
-                return True
-            if ch == '"':
-                self.stack[-1] = "colon"
-                self.mode = "str"
-                self.stack.append("keystr")
-                return True
-            return False
-        if top == "key":
-            if ch == '"':
-                self.stack[-1] = "colon"
-                self.mode = "str"
-                self.stack.append("keystr")
-                return True
-            return False
-        if top == "colon":
-            if ch == ":":
-                self.stack[-1] = "object_next"
-                self.stack.append("value")
-                return True
-            return False
-        if top == "object_next":
-            if ch == ",":
-                self.stack[-1] = "key"
-                return True
-            if ch == "}":
-                self.stack.pop()
-                self._close_value(pop=False)
-                return True
-            return False
-        if top == "array_next":
-            if ch == ",":
-                self.stack.append("value")
-                return True
-            if ch == "]":
-                self.stack.pop()
-                self._close_value(pop=False)
-                return True
-            return False
-        return False
-
-    def _after_string(self):
-        if self.stack and self.stack[-1] == "keystr":
-            self.stack.pop()
-        else:
-            self._close_value()
-
-    def _close_value(self, pop: bool = True):
-        if pop and self.stack and self.stack[-1] == "value":
-            self.stack.pop()
-
-    def _start_value(self, ch: str) -> bool:
-        if len(self.stack) > MAX_DEPTH:
-            return False
-        if ch == "{":
-            self.stack[-1] = "key_or_end"
-            return True
-        if ch == "[":
-            self.stack[-1] = "value_or_end_array"
-            return True
-        if ch == '"':
-            self.mode = "str"
-            return True
-        if ch in "-0123456789":
-            self.mode, self.buf = "num", ch
-            self.stack[-1] = "value_done_pending"
-            return True
-        for lit in ("true", "false", "null"):
-            if ch == lit[0]:
-                self.mode, self.lit, self.buf = "lit", lit, ch
-                return True
-        return False
-
-
-# ---- JSON schema -> regex (supported subset) -------------------------------------------------------------------
 _WS = r"[ \n\t]*"
 _STR = r'"(?:[^"\\\x00-\x1f]|\\["\\/bfnrt]|\\u[0-9a-fA-F]{4})*"'
 _NUM = r"-?(?:0|[1-9][0-9]*)(?:\.[0-9]+)?(?:[eE][+-]?[0-9]+)?"
@@ -513,70 +298,256 @@ class GbnfAcceptor:
         return () in self.stacks
 
 
-# ---- constraint (acceptor + tokenizer) -------------------------------------------------------------------------
-class Constraint:
-    def __init__(self, acceptor, tokenizer, eos_token: Optional[int] = None):
-        self.acc, self.tk, self.eos = acceptor, tokenizer, eos_token
-        self._texts: Optional[List[str]] = None
-        self._by_first: Dict[str, List[int]] = {}
+# ---- byte-level machines ----------------------------------------------------------------------------------------
+JSON_GRAMMAR = r"""
+root   ::= ws value ws
+value  ::= object | array | string | number | "true" | "false" | "null"
+object ::= "{" ws ( string ws ":" ws value ws ( "," ws string ws ":" ws value ws )* )? "}"
+array  ::= "[" ws ( value ws ( "," ws value ws )* )? "]"
+string ::= "\"" ( [^"\\\x00-\x1f] | "\\" ( ["\\/bfnrt] | "u" hex hex hex hex ) )* "\""
+hex    ::= [0-9a-fA-F]
+number ::= "-"? ( "0" | [1-9] [0-9]* ) ( "." [0-9]+ )? ( [eE] [-+]? [0-9]+ )?
+ws     ::= [ \t\n\r]*
+"""
 
-    def _table(self, vocab: int) -> List[str]:
-        if self._texts is None:
-            self._texts = []
-            for t in range(vocab):
-                try:
-                    s = self.tk.token_bytes(t).decode("utf-8")
-                except UnicodeDecodeError:
-                    s = ""
-                self._texts.append(s)
-                if s:
-                    self._by_first.setdefault(s[0], []).append(t)
-        return self._texts
+
+class DfaMachine:
+    """A regex / choice / schema constraint as a byte DFA; its states are small integers."""
+
+    def __init__(self, dfa):
+        self.dfa = dfa
+
+    def start(self):
+        return 0
+
+    def step(self, state, byte: int):
+        ns = int(self.dfa.table[state, byte])
+        return None if ns < 0 else ns
+
+    def complete(self, state) -> bool:
+        return bool(self.dfa.accepting[state])
+
+    def can_continue(self, state) -> bool:
+        return bool((self.dfa.table[state] >= 0).any())
+
+    def allowed(self, trie, state):
+        return trie.walk_dfa(self.dfa, state)
+
+
+class GbnfMachine:
+    """The grammar's stack machine stepped over bytes.  A state is ``(set of stacks, bytes of an unfinished UTF-8
+    character)``; both parts are immutable, so states are dictionary keys and stepping never copies an acceptor.  A
+    character that is still incomplete is admissible when some stack top matches a character of the code-point range
+    its bytes leave open."""
+
+    def __init__(self, grammar: "Gbnf"):
+        self.g = grammar
+        self._helper = GbnfAcceptor(grammar, stacks=set())
+
+    def start(self):
+        return (frozenset(GbnfAcceptor(self.g).stacks), b"")
+
+    @staticmethod
+    def _open_range(prefix: bytes):
+        b0, n = prefix[0], len(prefix)
+        if 0xC2 <= b0 <= 0xDF:
+            need, cp, bits = 2, b0 & 0x1F, 6
+        elif 0xE0 <= b0 <= 0xEF:
+            need, cp, bits = 3, b0 & 0x0F, 12
+        elif 0xF0 <= b0 <= 0xF4:
+            need, cp, bits = 4, b0 & 0x07, 18
+        else:
+            return None
+        for c in prefix[1:]:
+            if c & 0xC0 != 0x80:
+                return None
+            bits -= 6
+            cp = (cp << 6) | (c & 0x3F)
+        if n > need:
+            return None
+        lo = cp << bits
+        hi = lo | ((1 << bits) - 1)
+        # a sequence of this length encodes only code points above the shorter forms (no overlong encodings)
+        floor, ceil = {2: (0x80, 0x7FF), 3: (0x800, 0xFFFF), 4: (0x10000, 0x10FFFF)}[need]
+        lo, hi = max(lo, floor), min(hi, ceil)
+        if lo > hi:
+            return None
+        return need, lo, hi
+
+    @staticmethod
+    def _matches_some(el, lo: int, hi: int) -> bool:
+        _, neg, ranges = el
+        rs = sorted((ord(a), ord(b)) for a, b in ranges)
+        if not neg:
+            return any(a <= hi and b >= lo for a, b in rs)
+        cur = lo                                    # negated class: some code point of [lo, hi] outside every range
+        for a, b in rs:
+            if a > cur:
+                break
+            cur = max(cur, b + 1)
+            if cur > hi:
+                return False
+        return cur <= hi
+
+    def _feed_char(self, stacks, ch: str):
+        nxt: set = set()
+        for st in stacks:
+            if st and GbnfAcceptor._match(st[-1], ch):
+                self._helper._expand(st[:-1], nxt, 0)
+        nxt = {st for st in nxt if len(st) <= 4 * MAX_DEPTH}      # nesting bound: deeper derivations are refused
+        return (frozenset(nxt), b"") if nxt else None
+
+    def step(self, state, byte: int):
+        stacks, pend = state
+        if not pend and byte < 0x80:
+            return self._feed_char(stacks, chr(byte))
+        pend = pend + bytes([byte])
+        rng = self._open_range(pend)
+        if rng is None:
+            return None
+        need, lo, hi = rng
+        if len(pend) == need:
+            try:
+                ch = pend.decode("utf-8")
+            except UnicodeDecodeError:
+                return None
+            return self._feed_char(stacks, ch)
+        if not any(st and self._matches_some(st[-1], lo, hi) for st in stacks):
+            return None
+        return (stacks, pend)
+
+    def complete(self, state) -> bool:
+        return not state[1] and () in state[0]
+
+    def can_continue(self, state) -> bool:
+        return bool(state[1]) or any(st for st in state[0])
+
+    def allowed(self, trie, state):
+        return trie.walk(state, self.step)
+
+
+# ---- constraint (machine + tokenizer) ----------------------------------------------------------------------------
+_DFA_CACHE: Dict[tuple, tuple] = {}     # (kind, pattern) -> (machine, {tokenizer id: StateMasks})
+_DFA_CACHE_CAP = 64
+
+
+def _vocab_trie(tokenizer):
+    """The tokenizer's byte trie, built once and kept on the tokenizer."""
+    trie = getattr(tokenizer, "_guided_trie", None)
+    if trie is None:
+        from .automata import TokenTrie
+        toks = []
+        for t in range(tokenizer.vocab_size()):
+            try:
+                toks.append(bytes(tokenizer.token_bytes(t)))
+            except Exception:
+                toks.append(b"")
+        trie = TokenTrie(toks)
+        try:
+            tokenizer._guided_trie = trie
+        except AttributeError:
+            pass
+    return trie
+
+
+class Constraint:
+    """The state of one request under a constraint: the machine's current state, advanced by every committed token.
+
+    ``mask`` looks the state's allowed-token set up in a cache shared by every request with the same pattern and
+    tokenizer; a state seen for the first time costs one pruned walk of the vocabulary trie, a state seen before costs
+    a dictionary lookup (crates/poot-text/src/guided.rs:261-350).  Tokens are bytes: a token holding half of a UTF-8
+    character is allowed exactly when the machine can take those bytes."""
+
+    def __init__(self, machine, tokenizer, eos_token: Optional[int] = None, masks=None):
+        from .automata import StateMasks
+        self.m, self.tk, self.eos = machine, tokenizer, eos_token
+        self.state = machine.start()
+        self.masks = masks if masks is not None else StateMasks()
+        self._bytes: Optional[List[bytes]] = None
+
+    def clone(self) -> "Constraint":
+        c = Constraint(self.m, self.tk, self.eos, self.masks)
+        c.state = self.state
+        return c
+
+    def _allowed(self, vocab: int) -> np.ndarray:
+        trie = _vocab_trie(self.tk)
+        st = self.state
+        packed = self.masks.get(st, lambda: np.packbits(self.m.allowed(trie, st)))
+        a = np.unpackbits(packed, count=trie.n_tokens).astype(bool)
+        if len(a) < vocab:
+            a = np.concatenate([a, np.zeros(vocab - len(a), bool)])
+        return a[:vocab]
 
     def mask(self, vocab: int) -> np.ndarray:
-        texts = self._table(vocab)
-        m = np.full(vocab, MASKED, dtype=np.float32)
-        for first, toks in self._by_first.items():
-            if not self.acc.clone().feed(first):
-                continue                                   # no token starting with this character can continue
-            for t in toks:
-                s = texts[t]
-                if len(s) == 1 or self.acc.clone().feed(s):
-                    m[t] = 0.0
-        if self.eos is not None and self.acc.complete():
-            m[self.eos] = 0.0
+        m = np.where(self._allowed(vocab), np.float32(0.0), np.float32(MASKED)).astype(np.float32)
+        if self.eos is not None and self.eos < vocab:
+            m[self.eos] = 0.0 if self.m.complete(self.state) else MASKED
         return m
+
+    def feed_bytes(self, data: bytes) -> bool:
+        """Advance over raw bytes (tests, prefilled text).  False when the machine dies; the state is then unchanged."""
+        st = self.state
+        for b in data:
+            st = self.m.step(st, b)
+            if st is None:
+                return False
+        self.state = st
+        return True
 
     def advance(self, token: int) -> None:
         if token == self.eos:
             return
-        texts = self._table(max(self.tk.vocab_size(), token + 1))
-        self.acc.feed(texts[token])
+        self.feed_bytes(bytes(self.tk.token_bytes(token)))
 
     def done(self) -> bool:
-        """True when the text is complete and no token could extend it."""
-        if not self.acc.complete():
-            return False
-        texts = self._texts or []
-        return not any(self.acc.clone().feed(c) for c in self._by_first)
+        """True when the text is complete and nothing could extend it."""
+        return self.m.complete(self.state) and not self.m.can_continue(self.state)
+
+
+def _cached_dfa(kind: str, pattern: str, build):
+    key = (kind, pattern)
+    hit = _DFA_CACHE.get(key)
+    if hit is None:
+        if len(_DFA_CACHE) >= _DFA_CACHE_CAP:
+            _DFA_CACHE.clear()
+        hit = _DFA_CACHE[key] = (build(), {})
+    return hit
+
+
+def _regex_machine(pattern: str):
+    from .automata import AutomatonError, ByteDfa
+    if len(pattern) > MAX_PATTERN:
+        raise ConstraintError("regex too long")
+    try:
+        return DfaMachine(ByteDfa.from_regex(pattern))
+    except AutomatonError as e:
+        raise ConstraintError(str(e)) from None
 
 
 def build_constraint(spec: dict, tokenizer, eos_token: Optional[int] = None, tools: Optional[list] = None) -> Constraint:
     """``spec`` = {"choice": [...]} | {"regex": "..."} | {"json_schema": {...}} | {"json": true} | {"grammar": "..."} |
     {"tool": name-or-None}."""
+    from .automata import ByteDfa, StateMasks
     if "choice" in spec:
-        acc = ChoiceAcceptor(spec["choice"])
+        if not spec["choice"]:
+            raise ConstraintError("empty choice list")
+        key = "\x00".join(spec["choice"])
+        machine, per_tok = _cached_dfa("choice", key, lambda: DfaMachine(ByteDfa.from_literals([c.encode("utf-8") for c in spec["choice"]])))
     elif "regex" in spec:
-        acc = RegexAcceptor(spec["regex"])
+        machine, per_tok = _cached_dfa("regex", spec["regex"], lambda: _regex_machine(spec["regex"]))
     elif "json_schema" in spec:
-        acc = RegexAcceptor(schema_to_regex(spec["json_schema"]))
+        pattern = schema_to_regex(spec["json_schema"])
+        machine, per_tok = _cached_dfa("regex", pattern, lambda: _regex_machine(pattern))
     elif spec.get("json"):
-        acc = JsonAcceptor()
+        machine, per_tok = _cached_dfa("gbnf", JSON_GRAMMAR, lambda: GbnfMachine(Gbnf(JSON_GRAMMAR)))
     elif "grammar" in spec:
-        acc = GbnfAcceptor(Gbnf(spec["grammar"]))
+        machine, per_tok = _cached_dfa("gbnf", spec["grammar"], lambda: GbnfMachine(Gbnf(spec["grammar"])))
     elif "tool" in spec:
         from .tools import forced_tool_schema
-        acc = RegexAcceptor(schema_to_regex(forced_tool_schema(tools or [], spec["tool"])))
+        pattern = schema_to_regex(forced_tool_schema(tools or [], spec["tool"]))
+        machine, per_tok = _cached_dfa("regex", pattern, lambda: _regex_machine(pattern))
     else:
         raise ConstraintError("unknown constraint kind")
-    return Constraint(acc, tokenizer, eos_token)
+    masks = per_tok.setdefault(id(tokenizer), StateMasks())     # shared by every request with this pattern and tokenizer
+    return Constraint(machine, tokenizer, eos_token, masks)

@@ -14,7 +14,7 @@ LAYERS = {
     "tensor": set(), "target": {"tensor"}, "quant": {"tensor", "ops"}, "weights": {"tensor", "quant"},
     "load": {"tensor", "quant", "weights", "models"}, "ir": {"tensor", "quant"}, "oracle": {"tensor", "quant", "ir", "models", "runtime"},
     "models": {"tensor", "ir", "load"}, "plan": {"tensor", "ir", "quant", "target", "models", "oracle"},
-    "ops": set(), "profile": {"target", "ops"}, "text": set(),
+    "ops": set(), "profile": {"target", "ops"}, "text": {"ops"},
     "runtime": {"models", "ops", "quant", "parallel", "tensor", "plan"}, "parallel": {"ops", "runtime"},
     "utils": {"ops", "oracle", "runtime", "models", "tensor", "plan"},
     "driver": {"models", "runtime", "ops", "load", "quant", "ir", "oracle", "text", "tensor", "profile", "parallel"},

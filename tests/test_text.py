@@ -56,10 +56,10 @@ def test_chat_templates_render_and_refuse_hostile_templates():
     ("[1,]", False, False), ('"unterminated', True, False), ("tru", True, False), ("truth", False, False), ("-0.5", True, True),
     ("01", False, False), ("[" * 100, False, False)])
 def test_json_prefix_acceptor(text, ok, complete):
-    a = guided.JsonAcceptor()
-    assert a.feed(text) == ok
+    c = guided.build_constraint({"json": True}, ByteTokenizer(300, eos=2), eos_token=2)
+    assert c.feed_bytes(text.encode()) == ok
     if ok:
-        assert a.complete() == complete
+        assert c.m.complete(c.state) == complete
 
 
 def test_schema_regex_and_choice_and_regex_constraints():
