@@ -158,6 +158,34 @@ class DeviceStepEngine:
         self.last_launches = e.launches_per_step.get(e._key(shape), 0)
         return self.h_picked[:B].numpy().copy(), (self.h_logprobs[:B].numpy().copy() if inp.want_logprobs else None)
 
+    # ---- recurrent state: snapshot / restore of sequence rows (speculative rollback) ---------------------------------
+    _STATE_NAMES = ("gdn_state", "gdn_conv_state", "ssm_state", "ssm_conv_state")
+
+    @property
+    def has_recurrent_state(self) -> bool:
+        return any(getattr(self.e, n, None) is not None for n in self._STATE_NAMES)
+
+    def snapshot_rows(self, rows) -> None:
+        """Copy the recurrent state of the sequence rows ``rows`` into the shadow set.  Folding a token into a recurrent
+        state is not invertible, so a speculative round keeps a copy of the rows it verifies and a partial accept copies
+        them back and replays the kept tokens (crates/poot-llm/src/driver/snapshot.rs:1-17).  K/V needs no copy: a slot
+        past the committed length is overwritten before it is ever visible."""
+        torch = self.torch
+        idx = torch.as_tensor(list(rows), dtype=torch.long, device=self.e.device)
+        if getattr(self, "_shadow", None) is None:
+            self._shadow = {n: torch.zeros_like(getattr(self.e, n)) for n in self._STATE_NAMES
+                            if getattr(self.e, n, None) is not None}
+        for n, sh in self._shadow.items():
+            sh.index_copy_(1, idx, getattr(self.e, n).index_select(1, idx))
+
+    def restore_rows(self, rows) -> None:
+        torch = self.torch
+        if getattr(self, "_shadow", None) is None:
+            raise RuntimeError("restore_rows without a snapshot")
+        idx = torch.as_tensor(list(rows), dtype=torch.long, device=self.e.device)
+        for n, sh in self._shadow.items():
+            getattr(self.e, n).index_copy_(1, idx, sh.index_select(1, idx))
+
     def abort(self) -> None:
         """Watchdog / signal-handler hook: every pending and future wait on another rank gives up at once."""
         if self.e.device.type == "cuda":

@@ -55,8 +55,6 @@ TABLE: List[Tuple[Feature, Feature, str]] = [
     (F.BEAM, F.GUIDED, "beams would each need a clone of the constraint state"),
     (F.PACKED_WEIGHTS, F.EXPERT_PLACEMENT, "packed expert weights have no fused grouped kernel"),
     (F.RECURRENT_STATE, F.PREFIX_CACHE, "a prefix hit skips tokens; the recurrent state after them is not in the K/V cache"),
-    (F.RECURRENT_STATE, F.DRAFT_LOOKUP, "a rejected draft would need the recurrent state rolled back; state snapshots are not built"),
-    (F.RECURRENT_STATE, F.DRAFT_MODEL, "a rejected draft would need the recurrent state rolled back; state snapshots are not built"),
     (F.RECURRENT_STATE, F.BEAM, "a fork would need a copy of the recurrent state; only K/V blocks are copied"),
     (F.RECURRENT_STATE, F.TENSOR_PLACEMENT, "recurrent mixers run on the host evaluator, in one process"),
     (F.ADAPTERS, F.TENSOR_PLACEMENT, "the adapter bank is built for the single-device engine"),

@@ -6,7 +6,10 @@ in the sequence itself (prompt lookup); ``ModelDraft`` runs a smaller model gree
 ``[last token, d1 .. dk]`` as one piece with a logit row at each position; the accepted prefix is the run of drafts
 equal to the target's own greedy picks, plus the target's pick after it, so the output is token-for-token what
 plain greedy decoding produces.  Rejected drafts leave stale K/V in slots past the accepted length; those positions
-are rewritten when their real tokens are fed and are never visible to attention before that.
+are rewritten when their real tokens are fed and are never visible to attention before that.  Recurrent state is
+different: a rejected draft has been folded into it and cannot be taken out again, so on a model with recurrent
+mixers the round snapshots the sequence's state rows before the verify step and, after a partial accept, restores them
+and replays the kept tokens (crates/poot-llm/src/driver/snapshot.rs:1-17).
 """
 from __future__ import annotations
 
@@ -81,11 +84,30 @@ def speculative_step(d: Driver, seq_id: int, draft) -> List[int]:
     params = np.zeros((Bp, 4), np.float32); params[:, 0] = 1.0; params[:, 1] = -1e30; params[:, 3] = 1.0
     inp = StepInputs(tokens, positions, slots, row_seq, row_ctx, logit_idx, S.GREEDY, params, np.zeros(Bp, np.int32),
                      np.zeros(Bp, np.int32), None, False, T, B)
+    recurrent = bool(drafts) and bool(getattr(d.engine, "has_recurrent_state", False))
+    if recurrent:
+        d.engine.snapshot_rows([s.row])
     picked, _ = d.engine.run_step(inp)
     d.stats["steps"] += 1
     accepted = 0
     while accepted < len(drafts) and int(picked[accepted, 0]) == drafts[accepted]:
         accepted += 1
+    if recurrent and accepted < len(drafts):
+        # the rejected drafts were folded into the recurrent state: take the rows back and replay what is kept
+        d.engine.restore_rows([s.row])
+        keep = 1 + accepted
+        Tk = _bucket(keep, d.engine.max_tokens)
+        rt = np.zeros(Tk, np.int32); rp = np.zeros(Tk, np.int32); rs = np.full(Tk, -1, np.int32)
+        rq = np.zeros(Tk, np.int32); rc = np.zeros(Tk, np.int32)
+        rt[:keep], rp[:keep], rs[:keep], rq[:keep], rc[:keep] = tokens[:keep], positions[:keep], slots[:keep], row_seq[:keep], row_ctx[:keep]
+        li = np.zeros(_bucket(1, d.max_rows), np.int64)
+        li[0] = keep - 1
+        Bk = len(li)
+        pk = np.zeros((Bk, 4), np.float32); pk[:, 0] = 1.0; pk[:, 1] = -1e30; pk[:, 3] = 1.0
+        d.engine.run_step(StepInputs(rt, rp, rs, rq, rc, li, S.GREEDY, pk, np.zeros(Bk, np.int32), np.zeros(Bk, np.int32),
+                                     None, False, keep, 1))
+        d.stats["steps"] += 1
+        d.stats["draft_replays"] = d.stats.get("draft_replays", 0) + 1
     out = drafts[:accepted] + [int(picked[accepted, 0])]
     d.stats["decode_tokens"] += 1 + accepted
     d.stats["draft_proposed"] = d.stats.get("draft_proposed", 0) + len(drafts)

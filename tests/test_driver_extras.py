@@ -20,9 +20,10 @@ def test_feature_table():
     with pytest.raises(Incompatible):
         check([Feature.DRAFT_LOOKUP, Feature.GUIDED])
     check([Feature.RECURRENT_STATE, Feature.GUIDED, Feature.LOGPROBS])       # recurrent families serve; what they exclude is typed
-    for other in (Feature.PREFIX_CACHE, Feature.DRAFT_LOOKUP, Feature.BEAM):
+    for other in (Feature.PREFIX_CACHE, Feature.BEAM):
         with pytest.raises(Incompatible):
             check([Feature.RECURRENT_STATE, other])
+    check([Feature.RECURRENT_STATE, Feature.DRAFT_LOOKUP])       # the round snapshots and restores the state rows
     with pytest.raises(Incompatible):
         check([Feature.ADAPTERS, Feature.TENSOR_PLACEMENT])
     for f in (Feature.DRAFT_MTP, Feature.EXPERT_POOL):
@@ -146,3 +147,54 @@ def test_beam_search_orders_hypotheses_by_score():
     assert scores == sorted(scores, reverse=True) and scores[0] > scores[1]
     assert beams[1].tokens != beams[0].tokens and len(set(map(lambda b: tuple(b.tokens), beams))) == 3
     assert not d.seqs and d.kv_usage()["blocks_used"] == d.kv_usage()["prefix_entries"]
+
+
+def test_speculation_on_a_recurrent_hybrid_rolls_its_state_back():
+    """A model with gated-delta-net layers: a rejected draft has been folded into the recurrent state, so the verify
+    round snapshots the sequence's state rows, restores them after a partial accept and replays the kept tokens; the
+    output equals plain greedy decoding token for token."""
+    import numpy as np
+    import torch
+    from poot_b200.driver.driver import Driver
+    from poot_b200.driver.engines import DeviceStepEngine
+    from poot_b200.driver.sampler import SamplingParams
+    from poot_b200.driver.speculate import generate_speculative
+    from poot_b200.models.registry import Registry
+    from poot_b200.oracle.runner import random_weights_f32
+    from poot_b200.runtime.engine import DecoderEngine
+    from poot_b200.runtime.weights import from_named_tensors
+    from poot_b200.utils.kernel_emulation import emulated_kernels
+    from test_engine_emulated import HF_BASE, HF_FAMILIES
+    model = Registry.builtin().resolve_hf({**HF_BASE, **HF_FAMILIES["qwen3_5"]})
+    cfg = model.cfg
+    w = random_weights_f32(model, seed=2, std=0.08)
+    for k in w:
+        if k.endswith("gdn_a_log"):
+            w[k] = np.log(np.random.default_rng(3).uniform(0.5, 4.0, w[k].shape)).astype(np.float32)
+    named = {k: torch.from_numpy(v).to(torch.bfloat16).float() for k, v in w.items()}
+
+    class Wrong:
+        """Drafts that are right for one token and then wrong: every round is a partial accept."""
+
+        def __init__(self, truth):
+            self.truth, self.n = truth, 0
+
+        def propose(self, tokens):
+            done = len(tokens) - 6
+            nxt = self.truth[done:done + 1]
+            self.n += 1
+            return list(nxt) + [(nxt[0] + 1) % cfg.vocab if nxt else 0, 3] if nxt else []
+
+    prompt = [5, 9, 11, 200, 17, 3]
+    sp = SamplingParams(max_tokens=9, temperature=0.0, ignore_eos=True)
+    with emulated_kernels():
+        def driver():
+            eng = DecoderEngine(from_named_tensors(cfg, named, "cpu"), num_blocks=8, max_seqs=4, max_tokens=32,
+                                max_blocks_per_seq=4, device="cpu", use_graphs=False)
+            return Driver(DeviceStepEngine(eng), 8, 4, 64, cfg.vocab, prefill_chunk=16, prefix_caching=False)
+        want = driver().generate(prompt, sp)
+        d = driver()
+        assert d.engine.has_recurrent_state
+        got = generate_speculative(d, prompt, sp, Wrong(want))
+    assert got == want
+    assert d.stats["draft_replays"] >= 2 and d.stats["draft_accepted"] >= 2
