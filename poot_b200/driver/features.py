@@ -65,10 +65,13 @@ TABLE: List[Tuple[Feature, Feature, str]] = [
     (F.PIPELINE_PLACEMENT, F.DEVICE_TIMING, "per-launch device spans are recorded on one device"),
     (F.PIPELINE_PLACEMENT, F.BEAM, "a fork copies K/V blocks on every stage; only the leader's copy is wired"),
     (F.ADAPTERS, F.PACKED_WEIGHTS, "adapter deltas are applied to bf16 projections"),
+    (F.EXPERT_POOL, F.TENSOR_PLACEMENT, "the expert pool is built for the single-device engine"),
+    (F.EXPERT_POOL, F.EXPERT_PLACEMENT, "an expert-parallel group keeps its experts resident on their ranks"),
+    (F.EXPERT_POOL, F.PIPELINE_PLACEMENT, "the expert pool is built for the single-device engine"),
+    (F.EXPERT_POOL, F.PACKED_WEIGHTS, "packed expert weights have no fused grouped kernel"),
 ]
 UNAVAILABLE = {
     F.DRAFT_MTP: "no registered family ships multi-token-prediction heads",
-    F.EXPERT_POOL: "all experts stay resident in 180 GB of HBM; there is no host-side expert pool",
 }
 
 

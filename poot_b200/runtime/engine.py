@@ -296,6 +296,54 @@ class DecoderEngine:
         return self.lora
 
     # ------------------------------------------------------------------ kernel program
+    def host_embedding(self) -> int:
+        """Keep the token-embedding table in host memory.  A table that only a row gather reads never needs to be a
+        device buffer: a step needs ``T`` of its rows, never the table.  The table moves to pinned host memory; ``bind``
+        - which knows the step's token ids on the host - copies the *stored* bytes of the rows the step gathers into a
+        small device slot (a packed table's rows stay packed: they are decoded by the same row-gather kernel, over the
+        slot), and the step's embed launch reads row ``t`` of the slot for token ``t``.  Returns the device bytes freed.
+        Refused for a table that is also the output head (it has a second reader), for a tensor-parallel rank and for
+        chained decode, whose tokens never visit the host.  The reference's hosted gather sites:
+        crates/poot-graph-plan/src/passes/hosted_gather.rs:1-8."""
+        w = self.w
+        if w.embed is None or w.lm_head is w.embed:
+            raise ValueError("the embedding table is also the output head: not a gather-only table")
+        if self.comm is not None or (self.stage is not None and self.stage.count > 1):
+            raise ValueError("hosted embedding rows are built for the single-device engine")
+        pin = self.device.type == "cuda"
+        T = self.max_tokens
+        if isinstance(w.embed, K.QuantWeight):
+            q = w.embed
+            row_bytes = q.packed.numel() // q.N
+            host = q.packed.view(q.N, row_bytes).cpu()
+            slot = torch.zeros(T, row_bytes, dtype=torch.uint8, device=self.device)
+            freed = q.packed.numel()
+            w.embed = K.QuantWeight(q.fmt, slot.view(-1), T, q.K) if self.device.type == "cuda" else q
+            self._hosted = {"table": host.pin_memory() if pin else host, "slot": slot, "packed": True,
+                            "stage": torch.zeros(T, row_bytes, dtype=torch.uint8, pin_memory=pin)}
+        else:
+            host = w.embed.cpu()
+            freed = w.embed.numel() * w.embed.element_size()
+            slot = torch.zeros(T, host.shape[1], dtype=host.dtype, device=self.device)
+            w.embed = slot
+            self._hosted = {"table": host.pin_memory() if pin else host, "slot": slot, "packed": False,
+                            "stage": torch.zeros(T, host.shape[1], dtype=host.dtype, pin_memory=pin)}
+        self.embed_iota = torch.arange(T, dtype=torch.int32, device=self.device)
+        self._graphs.clear()
+        return freed
+
+    def _embed_ids(self, T: int, lo: int = 0) -> torch.Tensor:
+        """Row ids of the embed launch: the step's tokens, or 0..T-1 over the hosted slot."""
+        if getattr(self, "_hosted", None) is not None:
+            return self.embed_iota[lo:lo + T]
+        return self.tokens[lo:lo + T]
+
+    def enable_expert_pool(self, slots: int, manager) -> None:
+        """Pooled experts: ``slots`` resident experts per routed layer, the rest in pinned host memory (runtime/moe.py)."""
+        from .moe import enable_expert_pool
+        enable_expert_pool(self, slots, manager)
+        self._graphs.clear()
+
     def _count(self, n: int = 1):
         self._launch_counter += n
 
@@ -411,6 +459,8 @@ class DecoderEngine:
         cfg, w = self.cfg, self.w
         T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
         self._fused_step = False
+        if shape.chain and getattr(self, "_hosted", None) is not None:
+            raise ValueError("chained decode feeds tokens back on the device; hosted embedding rows are copied from the host")
         if self.program is not None and self.program.accepts(shape):
             return self.program.run(shape)      # the plain decoder layer: a walk over the compiled plan's launch list
         if self._fused_shape(shape):
@@ -428,9 +478,9 @@ class DecoderEngine:
         else:
             self._count()
             if isinstance(w.embed, K.QuantWeight):
-                K.quant_row_gather(self.tokens[:T], w.embed, out=h)
+                K.quant_row_gather(self._embed_ids(T), w.embed, out=h)
             else:
-                K.embed_gather(self.tokens[:T], w.embed, out=h)
+                K.embed_gather(self._embed_ids(T), w.embed, out=h)
             if cfg.embed_scale != 1.0:
                 h.mul_(cfg.embed_scale)
             if shape.embeds:
@@ -902,6 +952,11 @@ class DecoderEngine:
         """Copy one step's inputs (pinned host tensors) into the static device buffers."""
         T = tokens.numel()
         self.tokens[:T].copy_(tokens, non_blocking=non_blocking)
+        hosted = getattr(self, "_hosted", None)
+        if hosted is not None:                  # the rows this step gathers, as stored, into the device slot
+            rows = hosted["stage"][:T]
+            torch.index_select(hosted["table"], 0, tokens.long().clamp(0, hosted["table"].shape[0] - 1), out=rows)
+            hosted["slot"][:T].copy_(rows, non_blocking=non_blocking)
         self.positions[:T].copy_(positions, non_blocking=non_blocking)
         self.slots[:T].copy_(slots, non_blocking=non_blocking)
         self.row_seq[:T].copy_(row_seq, non_blocking=non_blocking)

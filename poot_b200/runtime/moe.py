@@ -45,6 +45,49 @@ def _buffers(eng):
     return eng._moe_buf
 
 
+def enable_expert_pool(eng, slots: int, manager) -> None:
+    """Keep only ``slots`` experts of every routed layer on the device.  The stored expert tables move to pinned host
+    memory, the device holds a pool ``[slots, ...]`` per table and an ``[E]`` map from expert id to pool row; each routed
+    layer is cut at its router: the host reads the step's expert ids, ``manager.sync`` (an LRU residency manager: the
+    driver's ``ExpertResidency``) names the rows to refill, the experts' bytes are copied as stored, and the layer runs
+    its row-grouped program over the pool through the map.  Steps are launched eagerly (the cut is a host
+    synchronisation, which a captured graph cannot hold).  The reference's pool transform and residency manager:
+    crates/poot-graph-plan/src/passes/pool.rs:1-7, crates/poot-llm/src/driver/expert_residency.rs:1-14."""
+    c = eng.cfg
+    if not c.is_moe:
+        raise ValueError("an expert pool needs routed experts")
+    if c.expert_bias or eng.comm is not None:
+        raise ValueError("the expert pool is built for unbiased experts on the single-device engine")
+    if not (c.top_k <= slots < c.n_experts):
+        raise ValueError(f"a pool of {slots} rows must hold a token's {c.top_k} experts and be smaller than the {c.n_experts} experts")
+    pin = eng.device.type == "cuda"
+    for L in eng.w.layers:
+        if L.ex_wgu is None:
+            continue
+        host = (L.ex_wgu.cpu(), L.ex_wdown.cpu())
+        L.ex_host = tuple(t.pin_memory() if pin else t for t in host)
+        L.ex_wgu = torch.zeros(slots, *L.ex_wgu.shape[1:], dtype=L.ex_wgu.dtype, device=eng.device)
+        L.ex_wdown = torch.zeros(slots, *L.ex_wdown.shape[1:], dtype=L.ex_wdown.dtype, device=eng.device)
+        L.ex_map = torch.full((c.n_experts,), -1, dtype=torch.int32, device=eng.device)
+    eng.expert_pool = (slots, manager)
+    eng.use_graphs = False
+    eng._moe_buf = None
+
+
+def _pool_sync(eng, l: int, L, ids: torch.Tensor) -> torch.Tensor:
+    """The host sync of a pooled routed layer: make the step's experts resident, return the ids as pool rows."""
+    slots, mgr = eng.expert_pool
+    E = eng.cfg.n_experts
+    nbytes = sum(t[0].numel() * t[0].element_size() for t in L.ex_host)
+    fills, emap, changed = mgr.sync((id(eng), l), ids.cpu().tolist(), E, slots, nbytes)
+    for row, ex in fills:                                   # the stored bytes of each missing expert, as stored
+        L.ex_wgu[row].copy_(L.ex_host[0][ex], non_blocking=True)
+        L.ex_wdown[row].copy_(L.ex_host[1][ex], non_blocking=True)
+    if changed:
+        L.ex_map.copy_(torch.tensor(emap, dtype=torch.int32))
+    return L.ex_map[ids.long()].contiguous()
+
+
 def shared_expert(eng, L, x: torch.Tensor, T: int, h=None) -> None:
     """``h[:T] += shared(x)``: the always-on expert of families that have one (a dense SwiGLU FFN), optionally scaled per
     token by ``sigmoid(x . w)`` (the scale is applied to the activation rows, which the down projection carries through)."""
@@ -108,7 +151,11 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
                 scale=c.routed_scale, n_group=c.n_group, topk_group=c.topk_group)
     h = eng.h[:T] if h is None else h
     tp = (ep[1], ep[2]) if (ep is not None and ep[0] == "fused") else None
-    if ep is None and e_local == E and T * k <= E:
+    pooled = getattr(eng, "expert_pool", None) is not None
+    if pooled:
+        eng._count()
+        ids = _pool_sync(eng, l, L, ids)                    # expert ids -> pool rows; the layer below reads the pool
+    if ep is None and e_local == E and T * k <= E and not pooled:
         G = T * k                                             # one group per (token, slot)
         act = buf["act"][:G * F].view(G, F)
         parts = buf["parts"][:G * H].view(G, H)

@@ -139,10 +139,11 @@ class ProgramExecutor:
             if l.op == "embed":
                 e._count()
                 h = buf[l.out][:T]
-                if isinstance(bound, K.QuantWeight):
-                    K.quant_row_gather(e.tokens[:T], bound, out=h)
+                table = e.w.embed               # (rebound when the table moved to the host: the slot of gathered rows)
+                if isinstance(table, K.QuantWeight):
+                    K.quant_row_gather(e._embed_ids(T), table, out=h)
                 else:
-                    K.embed_gather(e.tokens[:T], bound, out=h)
+                    K.embed_gather(e._embed_ids(T), table, out=h)
             elif l.op == "rmsnorm":
                 out = buf[l.out][:rows]
                 e._count()

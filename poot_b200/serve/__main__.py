@@ -87,8 +87,24 @@ def main(argv=None) -> int:
     from ..driver.features import Feature as _F, check as _check
     if cfg.draft_mtp:
         _check([_F.DRAFT_MTP])           # typed refusal: no registered family ships multi-token-prediction heads
+    if cfg.host_embedding:
+        if world > 1 or llm.engine is None:
+            print("poot-serve: --host-embedding needs the single-device engine", file=sys.stderr)
+            return 2
+        try:
+            freed = llm.engine.host_embedding()
+        except ValueError as e:
+            print(f"poot-serve: --host-embedding: {e}", file=sys.stderr)
+            return 2
+        print(f"poot-serve: embedding table hosted, {freed / 2**20:.0f} MiB of device memory freed", file=sys.stderr)
     if cfg.expert_pool:
-        _check([_F.EXPERT_POOL])         # typed refusal: experts stay resident in HBM
+        from ..driver.placement import Placement as _Pl
+        from ..driver.expert_residency import ExpertResidency
+        _check([_F.EXPERT_POOL, *_Pl.parse(cfg.placement).features])
+        if llm.engine is None:
+            print("poot-serve: --expert-pool needs the device engine", file=sys.stderr)
+            return 2
+        llm.engine.enable_expert_pool(cfg.expert_pool, ExpertResidency())
     if cfg.check_ranges and llm.cfg is not None:
         _prove_ranges(llm.cfg, cfg)
     draft = None

@@ -26,9 +26,11 @@ def test_feature_table():
     check([Feature.RECURRENT_STATE, Feature.DRAFT_LOOKUP])       # the round snapshots and restores the state rows
     with pytest.raises(Incompatible):
         check([Feature.ADAPTERS, Feature.TENSOR_PLACEMENT])
-    for f in (Feature.DRAFT_MTP, Feature.EXPERT_POOL):
-        with pytest.raises(Unavailable):
-            check([f])
+    with pytest.raises(Unavailable):
+        check([Feature.DRAFT_MTP])
+    check([Feature.EXPERT_POOL, Feature.PREFIX_CACHE])
+    with pytest.raises(Incompatible):
+        check([Feature.EXPERT_POOL, Feature.EXPERT_PLACEMENT])
 
 
 def test_placement_parse_and_divisibility():
@@ -198,3 +200,99 @@ def test_speculation_on_a_recurrent_hybrid_rolls_its_state_back():
         got = generate_speculative(d, prompt, sp, Wrong(want))
     assert got == want
     assert d.stats["draft_replays"] >= 2 and d.stats["draft_accepted"] >= 2
+
+
+def test_expert_residency_manager_follows_the_lru_contract():
+    from poot_b200.driver.expert_residency import ExpertIdOutOfRange, ExpertResidency, PoolTooSmall
+    m = ExpertResidency()
+    fills, emap, changed = m.sync("L0", [3, 1, 3], experts=8, slots=3)
+    assert fills == [(0, 3), (1, 1)] and emap == [-1, 1, -1, 0, -1, -1, -1, -1] and changed     # free rows first
+    fills, emap, changed = m.sync("L0", [1, 3], 8, 3)
+    assert fills == [] and not changed                                                          # all hits
+    fills, _, _ = m.sync("L0", [5], 8, 3)
+    assert fills == [(2, 5)]
+    fills, emap, _ = m.sync("L0", [1, 7], 8, 3)        # 1 is pinned; 3 was needed least recently of the unpinned rows
+    assert fills == [(0, 7)] and emap[3] == -1 and emap[7] == 0 and emap[1] == 1
+    assert m.counters.refills == 4 and m.counters.evictions == 1 and m.counters.syncs == 4 and m.counters.id_reads == 8
+    _, other, _ = m.sync("L1", [0], 8, 3)              # another layer has its own LRU
+    assert other[0] == 0
+    with pytest.raises(PoolTooSmall):
+        m.sync("L0", [0, 1, 2, 3], 8, 3)
+    with pytest.raises(ExpertIdOutOfRange):
+        m.sync("L0", [8], 8, 3)
+    m.reset()
+    assert m.counters.syncs == 0 and not m.sites
+
+
+def test_pooled_experts_generate_what_resident_experts_generate():
+    """Six resident experts of eight per layer, the rest in host memory: the routed layers are cut at the router, the
+    manager refills pool rows, and the tokens equal the engine that keeps every expert on the device."""
+    import torch
+    from poot_b200.driver.expert_residency import ExpertResidency
+    from poot_b200.models.config import DecoderConfig
+    from poot_b200.runtime.engine import DecoderEngine
+    from poot_b200.runtime.session import FixedBatchSession
+    from poot_b200.runtime.weights import random_weights
+    from poot_b200.utils.kernel_emulation import emulated_kernels
+    cfg = DecoderConfig(n_layers=2, hidden=128, n_heads=4, n_kv_heads=2, head_dim=64, ffn=256, vocab=512, max_position=256,
+                        n_experts=8, top_k=2, moe_ffn=64)
+    prompts = torch.randint(0, cfg.vocab, (1, 3), generator=torch.Generator().manual_seed(4), dtype=torch.int32)
+
+    def run(pool):
+        eng = DecoderEngine(random_weights(cfg, "cpu", seed=1, std=0.05), num_blocks=8, max_seqs=1, max_tokens=32,
+                            max_blocks_per_seq=4, device="cpu", use_graphs=False)
+        mgr = None
+        if pool:
+            mgr = ExpertResidency()
+            eng.enable_expert_pool(pool, mgr)
+            assert eng.w.layers[0].ex_wgu.shape[0] == pool and eng.w.layers[0].ex_host[0].shape[0] == 8
+        s = FixedBatchSession(eng, 1, 64)
+        out = [s.prefill_fast(prompts).clone()]
+        for _ in range(12):
+            out.append(s.decode(out[-1][:, 0].tolist()).clone())
+        return torch.stack(out), mgr
+
+    with emulated_kernels():
+        want, _ = run(0)
+        got, mgr = run(6)
+    assert torch.equal(got, want)
+    c = mgr.counters
+    assert c.syncs == 13 * cfg.n_layers and c.refills >= 6 and c.refill_bytes > 0
+    with emulated_kernels(), pytest.raises(ValueError):
+        eng = DecoderEngine(random_weights(cfg, "cpu", seed=1, std=0.05), num_blocks=8, max_seqs=1, max_tokens=32,
+                            max_blocks_per_seq=4, device="cpu", use_graphs=False)
+        eng.enable_expert_pool(8, ExpertResidency())             # not smaller than the experts
+
+
+def test_hosted_embedding_rows_are_copied_at_bind_and_change_nothing():
+    """The token-embedding table in host memory: bind copies the rows a step gathers into a device slot; tokens equal."""
+    import torch
+    from poot_b200.models.config import DecoderConfig
+    from poot_b200.runtime.engine import DecoderEngine, StepShape
+    from poot_b200.runtime.session import FixedBatchSession
+    from poot_b200.runtime.weights import random_weights
+    from poot_b200.utils.kernel_emulation import emulated_kernels
+    cfg = DecoderConfig(n_layers=2, hidden=128, n_heads=4, n_kv_heads=2, head_dim=64, ffn=256, vocab=512, max_position=256)
+    prompts = torch.randint(0, cfg.vocab, (2, 11), generator=torch.Generator().manual_seed(4), dtype=torch.int32)
+
+    def run(hosted):
+        eng = DecoderEngine(random_weights(cfg, "cpu", seed=1, std=0.05), num_blocks=16, max_seqs=2, max_tokens=32,
+                            max_blocks_per_seq=4, device="cpu", use_graphs=False)
+        freed = eng.host_embedding() if hosted else 0
+        s = FixedBatchSession(eng, 2, 64)
+        out = [s.prefill_fast(prompts).clone()]
+        for _ in range(4):
+            out.append(s.decode(out[-1][:, 0].tolist()).clone())
+        return torch.stack(out), eng, freed
+
+    with emulated_kernels():
+        want, _, _ = run(False)
+        got, eng, freed = run(True)
+        assert torch.equal(got, want)
+        assert freed == cfg.vocab * cfg.hidden * 2 and eng.w.embed.shape == (32, cfg.hidden)      # the device holds a slot, not the table
+        with pytest.raises(ValueError, match="chained decode"):
+            eng.forward(StepShape(2, 2, 0, chain=True))
+        tied = DecoderEngine(random_weights(DecoderConfig(**{**cfg.__dict__, "tie_embeddings": True}), "cpu", seed=1), num_blocks=4,
+                             max_seqs=1, max_tokens=16, max_blocks_per_seq=2, device="cpu", use_graphs=False)
+        with pytest.raises(ValueError, match="output head"):
+            tied.host_embedding()
