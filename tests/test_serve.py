@@ -330,9 +330,10 @@ def test_flags_for_draft_policies_pools_and_range_checks():
                 ["m", "--timing-sample-every", "0"]):
         with pytest.raises(ValueError):
             parse_args(bad)
-    for f in (Feature.DRAFT_MTP, Feature.EXPERT_POOL):           # accepted by the parser, refused typed at startup
-        with pytest.raises(Unavailable):
-            check([f])
+    with pytest.raises(Unavailable):                             # accepted by the parser, refused typed at startup
+        check([Feature.DRAFT_MTP])
+    assert parse_args(["m", "--expert-pool", "6", "--host-embedding"]).expert_pool == 6
+    check([Feature.EXPERT_POOL])                                 # pooled experts are served (single-device engine)
     c = tiny_llama()
     c.n_layers = 1
     _prove_ranges(c, cfg)
