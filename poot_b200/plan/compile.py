@@ -17,6 +17,9 @@ class CompileOptions:
     fuse: bool = True
     attention: bool = True
     stop_after: Optional[str] = None       # name of the last pass to run (pass-soundness tests walk the pipeline)
+    precision: Optional[str] = None        # exact | narrow | split: run select_operand_precision + store_narrowed_activations
+    check_ranges: bool = False             # add the range witnesses of the narrowed operands (--check-ranges)
+    limits: Optional[object] = None        # numerics.Limits: legalize against these device limits
 
 
 @dataclass
@@ -90,6 +93,16 @@ def compile_graph(graph: Graph, options: Optional[CompileOptions] = None) -> Pro
     log: Dict[str, object] = {"eqns_in": len(graph.eqns)}
     declines: list = []
     g = run_passes(graph, opt, log, declines)
+    if opt.stop_after is None:
+        from . import numerics
+        if opt.limits is not None:
+            log["legalize"] = numerics.legalize(g, opt.limits)
+        if opt.precision is not None:
+            log["select_operand_precision"] = numerics.select_operand_precision(g, opt.precision, opt.world)
+            log["store_narrowed_activations"] = numerics.store_narrowed_activations(g)
+        if opt.check_ranges:
+            log["check_narrow_ranges"] = len(numerics.check_narrow_ranges(g))
+        g.validate()
     log["eqns_out"] = len(g.eqns)
     plans = plan_graph(g, opt.world)
     return Program(g, plans, plan_buffers(g, plans), log, declines)

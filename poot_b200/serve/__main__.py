@@ -72,6 +72,20 @@ def main(argv=None) -> int:
             print("poot-serve: --lora-slots needs the single-device engine", file=sys.stderr)
             return 2
         llm.engine.enable_adapters(cfg.lora_slots, cfg.lora_max_rank)
+    if world > 1 and pp == 1 and llm.cfg is not None and llm.engine is not None:
+        # the group's plan - placement without duplication, the step's communication rows against the links'
+        # capabilities, every device's own byte total - is admitted before the first step (plan/multi_device.py)
+        import torch
+        from ..driver.placement import Placement as _Pl
+        from ..plan.multi_device import MultiDeviceError, Topology, plan_tensor_parallel
+        ords = list(_Pl.parse(cfg.placement).ordinals) if cfg.placement != "single" else list(range(world))
+        total = torch.cuda.get_device_properties(torch.cuda.current_device()).total_memory
+        try:
+            plan_tensor_parallel(llm.cfg, Topology.nvswitch(ords, total), cfg.rows, llm.engine.kv.num_blocks, cfg.rows,
+                                 comm="fused" if getattr(comm, "fused", False) else "nccl").validate()
+        except MultiDeviceError as e:
+            print(f"poot-serve: placement {cfg.placement}: {e}", file=sys.stderr)
+            return 2
     if world > 1:
         from .follower import follow, LeaderStepEngine
         if rank != 0:
