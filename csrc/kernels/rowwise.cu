@@ -271,6 +271,68 @@ __global__ void decode_advance_kernel(const int* __restrict__ picked, int* __res
   slots[i] = b < max_blocks ? block_tables[(size_t)seq * max_blocks + b] * 16 + (pos % 16) : -1;
 }
 
+// ---- small pointwise and movement kernels the layer programs need between the large ones ------------------------
+// x[t, :] += bias[:]   (bf16 rows with pitch ldx, bf16 or f32 bias; also the f32 form for router logits)
+template <typename XT, typename BT>
+__global__ void bias_add_kernel(XT* __restrict__ x, const BT* __restrict__ bias, int T, int N, int ldx) {
+  pdl_wait(); pdl_launch();
+  const size_t total = (size_t)T * N;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / N), n = (int)(i - (size_t)t * N);
+    XT* p = x + (size_t)t * ldx + n;
+    *p = (XT)((float)*p + (float)bias[n]);
+  }
+}
+
+// x *= s
+__global__ void scale_bf16_kernel(__nv_bfloat16* __restrict__ x, size_t n, float s) {
+  pdl_wait(); pdl_launch();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = __float2bfloat16(__bfloat162float(x[i]) * s);
+}
+
+// out[b, :] = src[idx[b], :]  moved in chunks of type C (16, 4 or 2 bytes: the widest that divides the row and both
+// pitches); idx is int64.  An index outside [0, rows) copies row 0 (the step is refused on the host before it can
+// name one).
+template <typename C>
+__global__ void gather_rows_kernel(const uint8_t* __restrict__ src, long long src_pitch, int rows,
+                                   const long long* __restrict__ idx, uint8_t* __restrict__ out, long long out_pitch,
+                                   int row_bytes) {
+  pdl_wait(); pdl_launch();
+  long long r = idx[blockIdx.x];
+  if (r < 0 || r >= rows) r = 0;
+  const C* s = reinterpret_cast<const C*>(src + (size_t)r * src_pitch);
+  C* d = reinterpret_cast<C*>(out + (size_t)blockIdx.x * out_pitch);
+  for (int c = threadIdx.x; c < row_bytes / (int)sizeof(C); c += blockDim.x) d[c] = s[c];
+}
+
+// x[t, :] *= sigmoid(g[t * ldg])   (the per-token gate of a shared expert)
+__global__ void sigmoid_gate_rows_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ g, int ldg, int T, int N) {
+  pdl_wait(); pdl_launch();
+  const size_t total = (size_t)T * N;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / N);
+    const float s = 1.f / (1.f + __expf(-g[(size_t)t * ldg]));
+    x[i] = __float2bfloat16(__bfloat162float(x[i]) * s);
+  }
+}
+
+// x[r, :] += table[idx[r / div] + e0, :] * (gate ? gate[r] : 1): the bias of each row's expert.  Rows of a padding
+// tile (idx < 0) are left alone.
+__global__ void bias_add_indexed_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ table,
+                                        const int* __restrict__ idx, int div, int e0, int experts,
+                                        const float* __restrict__ gate, int R, int N) {
+  pdl_wait(); pdl_launch();
+  const size_t total = (size_t)R * N;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / N), n = (int)(i - (size_t)r * N);
+    const int e = idx[r / div];
+    if (e < 0 || e + e0 >= experts) continue;
+    const float b = __bfloat162float(table[(size_t)(e + e0) * N + n]) * (gate ? gate[r] : 1.f);
+    x[i] = __float2bfloat16(__bfloat162float(x[i]) + b);
+  }
+}
+
 }  // namespace poot
 
 using namespace poot;
@@ -398,4 +460,64 @@ POOT_API int poot_cast_bf16_f32(const void* in, float* out, long long n, cudaStr
   if (blocks > 148 * 16) blocks = 148 * 16;
   return launch_k(cast_bf16_f32_kernel, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)in, out, (size_t)n);
   return (int)cudaGetLastError();
+}
+
+// bias dtype: 0 bf16, 1 f32.  x dtype: 0 bf16, 1 f32 (the f32 form takes an f32 bias only).
+POOT_API int poot_bias_add(void* x, const void* bias, int T, int N, int ldx, int x_f32, int bias_f32, cudaStream_t s) {
+  if (T == 0 || N == 0) return 0;
+  size_t total = (size_t)T * N;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (x_f32) {
+    if (!bias_f32) return (int)cudaErrorInvalidValue;
+    return launch_k(bias_add_kernel<float, float>, dim3(blocks), dim3(256), 0, s, (float*)x, (const float*)bias, T, N, ldx);
+  }
+  if (bias_f32)
+    return launch_k(bias_add_kernel<__nv_bfloat16, float>, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16*)x, (const float*)bias, T, N, ldx);
+  return launch_k(bias_add_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16*)x,
+                  (const __nv_bfloat16*)bias, T, N, ldx);
+}
+
+POOT_API int poot_scale_bf16(void* x, long long n, float scale, cudaStream_t s) {
+  if (n == 0) return 0;
+  int blocks = (int)((n + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch_k(scale_bf16_kernel, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16*)x, (size_t)n, scale);
+}
+
+POOT_API int poot_gather_rows(const void* src, long long src_pitch, int rows, const long long* idx, void* out,
+                              long long out_pitch, int n_out, int row_bytes, cudaStream_t s) {
+  if (n_out == 0) return 0;
+  const uintptr_t all = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out) | (uintptr_t)src_pitch |
+                        (uintptr_t)out_pitch | (uintptr_t)row_bytes;
+  const dim3 g(n_out), b(128);
+  if (all % 16 == 0)
+    return launch_k(gather_rows_kernel<uint4>, g, b, 0, s, (const uint8_t*)src, src_pitch, rows, idx, (uint8_t*)out,
+                    out_pitch, row_bytes);
+  if (all % 4 == 0)
+    return launch_k(gather_rows_kernel<uint32_t>, g, b, 0, s, (const uint8_t*)src, src_pitch, rows, idx, (uint8_t*)out,
+                    out_pitch, row_bytes);
+  if (all % 2 == 0)
+    return launch_k(gather_rows_kernel<uint16_t>, g, b, 0, s, (const uint8_t*)src, src_pitch, rows, idx, (uint8_t*)out,
+                    out_pitch, row_bytes);
+  return (int)cudaErrorInvalidValue;
+}
+
+POOT_API int poot_sigmoid_gate_rows(void* x, const float* g, int ldg, int T, int N, cudaStream_t s) {
+  if (T == 0 || N == 0) return 0;
+  size_t total = (size_t)T * N;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch_k(sigmoid_gate_rows_kernel, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16*)x, g, ldg, T, N);
+}
+
+POOT_API int poot_bias_add_indexed(void* x, const void* table, const int* idx, int div, int e0, int experts,
+                                   const float* gate, int R, int N, cudaStream_t s) {
+  if (R == 0 || N == 0) return 0;
+  if (div <= 0) return (int)cudaErrorInvalidValue;
+  size_t total = (size_t)R * N;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  return launch_k(bias_add_indexed_kernel, dim3(blocks), dim3(256), 0, s, (__nv_bfloat16*)x, (const __nv_bfloat16*)table,
+                  idx, div, e0, experts, gate, R, N);
 }

@@ -33,6 +33,11 @@ _SIGS = {
     "poot_gated_rmsnorm": [_P, _P, c_int, c_int, _P, c_int, c_float, c_int, _P, c_int, c_int, c_int, _P],
     "poot_sigmoid_mul": [_P, _P, c_longlong, _P],
     "poot_add_bf16": [_P, _P, _P, c_longlong, _P],
+    "poot_bias_add": [_P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "poot_bias_add_indexed": [_P, _P, _P, c_int, c_int, c_int, _P, c_int, c_int, _P],
+    "poot_scale_bf16": [_P, c_longlong, c_float, _P],
+    "poot_gather_rows": [_P, c_longlong, c_int, _P, _P, c_longlong, c_int, c_int, _P],
+    "poot_sigmoid_gate_rows": [_P, _P, c_int, c_int, c_int, _P],
     "poot_reduce_partials": [_P, _P, c_int, c_longlong, _P, c_longlong, _P],
     "poot_cast_f32_bf16": [_P, _P, c_longlong, _P],
     "poot_cast_bf16_f32": [_P, _P, c_longlong, _P],
@@ -359,6 +364,67 @@ def add(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) ->
         out = torch.empty_like(a)
     check(_fn("poot_add_bf16")(_ptr(a), _ptr(b), _ptr(out), a.numel(), _stream()), "add")
     return out
+
+
+def bias_add_(x: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """``x[t, :] += bias`` in place.  ``x`` is a bf16 or f32 matrix whose rows may be a column slice of a wider
+    buffer (unit inner stride); ``bias`` is bf16 or f32 (an f32 ``x`` takes an f32 bias)."""
+    _need_cuda(x, bias)
+    assert x.dim() == 2 and x.stride(1) == 1 and bias.is_contiguous() and bias.numel() == x.shape[1]
+    assert x.dtype in (torch.bfloat16, torch.float32) and bias.dtype in (torch.bfloat16, torch.float32)
+    T, N = x.shape
+    check(_fn("poot_bias_add")(_ptr(x), _ptr(bias), T, N, x.stride(0) if T > 1 else N,
+                               int(x.dtype == torch.float32), int(bias.dtype == torch.float32), _stream()), "bias_add")
+    return x
+
+
+def bias_add_indexed_(x: torch.Tensor, table: torch.Tensor, idx: torch.Tensor, div: int = 1, e0: int = 0,
+                      gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x[r] += table[idx[r // div] + e0] * (gate[r] if gate is given else 1)`` in place; rows whose index is negative
+    are left alone.  ``x`` and ``table`` are contiguous bf16, ``idx`` int32, ``gate`` f32."""
+    _need_cuda(x, table, idx)
+    assert x.dtype == table.dtype == torch.bfloat16 and x.is_contiguous() and table.is_contiguous()
+    assert idx.dtype == torch.int32 and idx.is_contiguous() and table.shape[1] == x.shape[1]
+    R, N = x.shape
+    assert idx.numel() * div >= R
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.is_contiguous() and gate.numel() >= R
+    check(_fn("poot_bias_add_indexed")(_ptr(x), _ptr(table), _ptr(idx), int(div), int(e0), table.shape[0],
+                                       _ptr(gate) if gate is not None else None, R, N, _stream()), "bias_add_indexed")
+    return x
+
+
+def scale_(x: torch.Tensor, s: float) -> torch.Tensor:
+    """``x *= s`` in place (bf16, contiguous)."""
+    _need_cuda(x)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous()
+    check(_fn("poot_scale_bf16")(_ptr(x), x.numel(), float(s), _stream()), "scale")
+    return x
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[b] = src[idx[b]]`` for 2-D tensors of one dtype (16-byte chunks when rows and pitches allow, narrower otherwise); ``idx`` is int64
+    with ``out.shape[0]`` entries read."""
+    _need_cuda(src, idx, out)
+    assert src.dim() == 2 and out.dim() == 2 and src.dtype == out.dtype and src.shape[1] == out.shape[1]
+    assert src.stride(1) == 1 and out.stride(1) == 1 and idx.dtype == torch.int64 and idx.is_contiguous()
+    assert idx.numel() >= out.shape[0]
+    es = src.element_size()
+    B = out.shape[0]
+    check(_fn("poot_gather_rows")(_ptr(src), src.stride(0) * es, src.shape[0], _ptr(idx), _ptr(out),
+                                  (out.stride(0) if B > 1 else out.shape[1]) * es, B, src.shape[1] * es, _stream()),
+          "gather_rows")
+    return out
+
+
+def sigmoid_gate_rows_(x: torch.Tensor, g: torch.Tensor) -> torch.Tensor:
+    """``x[t, :] *= sigmoid(g[t, 0])`` in place: ``x`` bf16 contiguous ``[T, N]``, ``g`` f32 ``[T, >=1]``."""
+    _need_cuda(x, g)
+    assert x.dtype == torch.bfloat16 and x.is_contiguous() and g.dtype == torch.float32 and g.dim() == 2
+    assert g.shape[0] == x.shape[0] and g.stride(1) == 1
+    check(_fn("poot_sigmoid_gate_rows")(_ptr(x), _ptr(g), g.stride(0), x.shape[0], x.shape[1], _stream()),
+          "sigmoid_gate_rows")
+    return x
 
 
 def _out_for(epi: int, M: int, N: int, device, out):

@@ -482,7 +482,7 @@ class DecoderEngine:
             else:
                 K.embed_gather(self._embed_ids(T), w.embed, out=h)
             if cfg.embed_scale != 1.0:
-                h.mul_(cfg.embed_scale)
+                K.scale_(h, cfg.embed_scale)
             if shape.embeds:
                 self._count()
                 K.replace_rows_(h, self.embed_rows[:T], self.embed_flags[:T])
@@ -517,7 +517,7 @@ class DecoderEngine:
                 continue
             qkv = self._linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
             if L.bqkv is not None:
-                qkv.add_(L.bqkv)
+                K.bias_add_(qkv, L.bqkv)
             if lora:
                 self.lora.apply(self, "qkv", l, x, qkv, T)
             qn, kn = L.q_norm, L.k_norm
@@ -542,26 +542,26 @@ class DecoderEngine:
             elif self.comm is not None:
                 pending = self.comm.row_parallel(self, self.attn[:T], L.wo, T)
                 if L.bo is not None:            # the bias joins the reduced sum once
-                    h.add_(L.bo)
+                    K.bias_add_(h, L.bo)
             else:
                 pending = self._proj_to_residual(self.attn[:T], L.wo, T)
                 if lora:
                     self.lora.apply(self, "o", l, self.attn[:T], h, T)
                 if L.bo is not None:
-                    h.add_(L.bo)
+                    K.bias_add_(h, L.bo)
             x = h if cfg.block == "post" else self._norm(L.ln2, T, pending, L.ln2_b)
             if cfg.moe_layer(w.layer0 + l):
                 pending = self._moe(l, L, x, T)
             elif not cfg.gated_ffn:             # down(act(up(x) + b) ) + b: no gate
                 up = self._linear(x, L.wgu, K.EPI_STORE, self.act[:T])
                 if L.bgu is not None:
-                    up.add_(L.bgu)
+                    K.bias_add_(up, L.bgu)
                 self._count()
                 K.act_(up, cfg.act)
                 pending = (self.comm.row_parallel(self, up, L.wdown, T) if self.comm is not None
                            else self._proj_to_residual(up, L.wdown, T))
                 if L.bdown is not None:
-                    h.add_(L.bdown)
+                    K.bias_add_(h, L.bdown)
             else:
                 if cfg.act == "silu" and not lora:
                     act = self._linear(x, L.wgu, K.EPI_SWIGLU, self.act[:T])
@@ -592,7 +592,7 @@ class DecoderEngine:
             hl = h
         else:
             self._count()
-            torch.index_select(h, 0, self.logit_idx[:B], out=hl)
+            K.gather_rows(h, self.logit_idx[:B], hl)
         self._count()
         if cfg.norm_kind == "layer":
             K.layernorm(hl, w.final_norm, w.final_norm_b, cfg.norm_eps, out=self.xl[:B])
@@ -629,13 +629,13 @@ class DecoderEngine:
             else:
                 up = self._linear(x, L.wgu, K.EPI_STORE, self.act[:T])
                 if L.bgu is not None:
-                    up.add_(L.bgu)
+                    K.bias_add_(up, L.bgu)
                 self._count()
                 K.act_(up, cfg.act)
                 pending = (self.comm.row_parallel(self, up, L.wdown, T) if self.comm is not None
                            else self._proj_to_residual(up, L.wdown, T))
                 if L.bdown is not None:
-                    self.h[:T].add_(L.bdown)
+                    K.bias_add_(self.h[:T], L.bdown)
         return pending
 
     def _mamba_mixer(self, l: int, L, x, T: int):
@@ -810,7 +810,7 @@ class DecoderEngine:
         comm.begin_step()
         K.embed_gather(self.tokens[:T], w.embed, out=h)
         if cfg.embed_scale != 1.0:
-            h.mul_(cfg.embed_scale)
+            K.scale_(h, cfg.embed_scale)
         K.rmsnorm(h, w.layers[0].ln1, cfg.norm_eps, out=x)
         rs = -1
         for l, L in enumerate(w.layers):
@@ -821,7 +821,7 @@ class DecoderEngine:
             self._count(8 + (1 if splits > 1 else 0))
             K.linear(x, L.wqkv, K.EPI_STORE, self.qkv[:T])
             if L.bqkv is not None:
-                self.qkv[:T].add_(L.bqkv)
+                K.bias_add_(self.qkv[:T], L.bqkv)
             K.rope_kv_write(self.qkv[:T], self.q[:T], self.kv.k(l), self.kv.v(l), self.positions[:T], self.slots[:T],
                             self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
             self._attention(l, T, T, B, count=False)
@@ -842,7 +842,7 @@ class DecoderEngine:
             # reduce into h (normalised output unused), then gather the logit rows and normalise them
             self._count(3)
             comm.norm_oneshot(h, w.final_norm, x, T, cfg.norm_eps, rs_site=rs)
-            torch.index_select(h, 0, self.logit_idx[:B], out=self.hl[:B])
+            K.gather_rows(h, self.logit_idx[:B], self.hl[:B])
             K.rmsnorm(self.hl[:B], w.final_norm, cfg.norm_eps, out=self.xl[:B])
         self._count()
         K.linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits_local[:B])
@@ -860,14 +860,14 @@ class DecoderEngine:
         comm.begin_step()
         K.embed_gather(self.tokens[r0:r0 + S], w.embed, out=comm.h_shard[:S])
         if cfg.embed_scale != 1.0:
-            comm.h_shard[:S].mul_(cfg.embed_scale)
+            K.scale_(comm.h_shard[:S], cfg.embed_scale)
         ag, rs = 0, -1
         for l, L in enumerate(w.layers):
             self._count(5 + (1 if self._attn_splits(R) > 1 else 0))
             comm.norm(L.ln1, S, cfg.norm_eps, ag_site=ag, rs_site=rs)
             comm.gemm(K.EPI_STORE, None, L.wqkv, self.qkv[:R], S, ag_site=ag)
             if L.bqkv is not None:
-                self.qkv[:R].add_(L.bqkv)
+                K.bias_add_(self.qkv[:R], L.bqkv)
             K.rope_kv_write(self.qkv[:R], self.q[:R], self.kv.k(l), self.kv.v(l), self.positions[:R], self.slots[:R],
                             self.cos, self.sin, self.hq, self.hkv, D, cfg.rot, L.q_norm, L.k_norm, cfg.norm_eps)
             self._attention(l, R, T, B, count=False)
@@ -888,7 +888,7 @@ class DecoderEngine:
         else:
             self._count()
             local = self.logits_sel[:B]
-            torch.index_select(self.logits_local[:R], 0, self.logit_idx[:B], out=local)
+            K.gather_rows(self.logits_local[:R], self.logit_idx[:B], local)
         self._sample(shape, local)
 
     def _moe(self, l, L, x, T, h=None):

@@ -107,16 +107,18 @@ def shared_expert(eng, L, x: torch.Tensor, T: int, h=None) -> None:
         eng._count(2)
         g = eng._sh_gate[:T]
         K.linear(x, L.sh_gate, K.EPI_F32, g)
-        act.mul_(torch.sigmoid(g[:, :1]).to(act.dtype))
+        K.sigmoid_gate_rows_(act, g)
     h = eng.h[:T] if h is None else h
     K.linear(act, L.sh_wdown, K.EPI_RESID, h, h)
 
 
-def _expert_act(eng, L, gu: torch.Tensor, act: torch.Tensor, expert_of_row: torch.Tensor) -> None:
-    """Bias of each row's expert (when the family has one) and the gated activation over the (gate, up) pairs."""
+def _expert_act(eng, L, gu: torch.Tensor, act: torch.Tensor, idx: torch.Tensor, div: int, e0: int) -> None:
+    """Bias of each row's expert (``idx[row // div] + e0``, when the family has one) and the gated activation over the
+    (gate, up) pairs."""
     c = eng.cfg
     if L.ex_bgu is not None:
-        gu.add_(L.ex_bgu[expert_of_row])
+        eng._count()
+        K.bias_add_indexed_(gu, L.ex_bgu, idx, div, e0)
     eng._count()
     if not c.gated_ffn:                 # experts without a gate: act(up(x))
         act.copy_(gu)
@@ -144,7 +146,7 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
     else:
         K.linear(x, L.router, K.EPI_F32, logits)
     if L.router_bias is not None:
-        logits.add_(L.router_bias)
+        K.bias_add_(logits, L.router_bias)
     ids, gates = buf["ids"][:T * k], buf["gates"][:T * k]
     dense = buf["dense"][:E * T].view(E, T)
     M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense, mode=c.router, select_bias=L.select_bias,
@@ -166,11 +168,12 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
             W2 = L.ex_wgu.shape[1]          # 2F with a gate, F without
             gu = buf["gu"][:G * W2].view(G, W2)
             M.gemm_grouped(K.EPI_STORE, x, L.ex_wgu, gu, 1, G, group_expert=ids, x_row_div=k, out_group_stride=W2, ldo=W2)
-            _expert_act(eng, L, gu, act, ids.long())
+            _expert_act(eng, L, gu, act, ids, 1, 0)
         M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, parts, 1, G, group_expert=ids, x_row_mul=1, out_group_stride=H,
                        row_scale=gates, ldo=H)
         if L.ex_bdown is not None:
-            parts.add_((L.ex_bdown[ids.long()].float() * gates[:, None]).to(parts.dtype))
+            eng._count()
+            K.bias_add_indexed_(parts, L.ex_bdown, ids, 1, 0, gate=gates)
         M.moe_combine(h, parts, h, T, H, G, H, per_token=k)
         return None
     if tp is not None and e_local == 1 and T <= 128:
@@ -209,16 +212,15 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
         M.gemm_grouped(up_epi, xs, L.ex_wgu, up_out, block, max_tiles, group_expert=tile_expert, x_row_mul=block,
                        out_group_stride=block * up_out.shape[1], ldo=up_out.shape[1])
     if not plain:
-        expert_of_row = (tile_expert.clamp(min=0) + e0).repeat_interleave(block).long()
-        _expert_act(eng, L, up_out, act, expert_of_row)
+        _expert_act(eng, L, up_out, act, tile_expert, block, e0)
     if tiled:
         M.gemm_grouped_tiled(K.EPI_STORE, act, L.ex_wdown, y, tile_expert, row_scale=gate_s)
     else:
         M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, y, block, max_tiles, group_expert=tile_expert, x_row_mul=block,
                        out_group_stride=block * H, row_scale=gate_s, ldo=H)
     if L.ex_bdown is not None:      # the bias is part of the expert's output, so it is scaled by the row's gate too
-        expert_of_row = (tile_expert.clamp(min=0) + e0).repeat_interleave(block).long()
-        y.add_((L.ex_bdown[expert_of_row].float() * gate_s[:, None]).to(y.dtype))
+        eng._count()
+        K.bias_add_indexed_(y, L.ex_bdown, tile_expert, block, e0, gate=gate_s)
     eng._count()
     if ep is None:
         M.moe_scatter_combine(h, y, pos, h, T, H, k)

@@ -168,7 +168,7 @@ class ProgramExecutor:
                     W, bias = bound if isinstance(bound, tuple) else (bound, None)
                     out = e._linear(x, W, K.EPI_STORE, buf[l.out][:rows])
                     if bias is not None:
-                        out.add_(bias)
+                        K.bias_add_(out, bias)
             elif l.op == "rope_kv":
                 L = w.layers[l.layer - w.layer0]
                 cos, sin = e._rope_tables_of(l.layer)
@@ -190,7 +190,7 @@ class ProgramExecutor:
                     alias[l.out] = buf[l.x]
                 else:
                     e._count()
-                    torch.index_select(buf[l.x][:T], 0, e.logit_idx[:B], out=buf[l.out][:B])
+                    K.gather_rows(buf[l.x][:T], e.logit_idx[:B], buf[l.out][:B])
             else:                               # pragma: no cover - lower() only emits the kinds above
                 raise LoweringRefused(l.op)
         flush()

@@ -205,6 +205,37 @@ def add(a, b, out=None):
     return out
 
 
+def bias_add_(x, bias):
+    x.copy_((x.float() + bias.float()).to(x.dtype))
+    return x
+
+
+def bias_add_indexed_(x, table, idx, div=1, e0=0, gate=None):
+    R = x.shape[0]
+    e = idx.long().repeat_interleave(div)[:R]
+    live = (e >= 0) & (e + e0 < table.shape[0])
+    b = table[(e + e0).clamp(0, table.shape[0] - 1)].float()
+    if gate is not None:
+        b = b * gate[:R, None]
+    x.copy_(torch.where(live[:, None], _bf(x.float() + b), x))
+    return x
+
+
+def scale_(x, s):
+    x.copy_(_bf(x.float() * s))
+    return x
+
+
+def gather_rows(src, idx, out):
+    out.copy_(src[idx[:out.shape[0]].clamp(0, src.shape[0] - 1)])
+    return out
+
+
+def sigmoid_gate_rows_(x, g):
+    x.copy_(_bf(x.float() * torch.sigmoid(g[:, :1])))
+    return x
+
+
 def _epilogue(y: torch.Tensor, epi: int, out, resid):
     """``y`` fp32 ``[M, N]`` -> the epilogue's stored form."""
     if epi == K.EPI_F32:
@@ -583,6 +614,8 @@ def emulated_kernels():
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
                 gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, replace_rows_=replace_rows_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, ssd_scan=ssd_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
+                bias_add_=bias_add_, bias_add_indexed_=bias_add_indexed_, scale_=scale_, gather_rows=gather_rows,
+                sigmoid_gate_rows_=sigmoid_gate_rows_,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
                 attn_paged=attn_paged, attn_general=attn_general, mla_qkv_write=mla_qkv_write, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
                 argmax=argmax, argmax_partials=argmax_partials, argmax_combine=argmax_combine,
