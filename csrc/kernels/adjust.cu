@@ -19,6 +19,7 @@ __global__ void adjust_logits_kernel(float* __restrict__ logits, int vocab, cons
   // entries of a row name distinct tokens, so the sparse pass has no write conflicts
   for (int i = threadIdx.x; i < max_adj; i += blockDim.x) {
     const int t = idx[(size_t)row * max_adj + i];
+    if (t >= 0) POOT_IN_RANGE(t, vocab, kSiteLogitIndex);      // a negative id ends the row's list
     if (t < 0 || t >= vocab) continue;
     const float* v = val + ((size_t)row * max_adj + i) * 4;
     float l = lr[t] + v[0];
@@ -57,6 +58,7 @@ __global__ void token_logprob_kernel(const float* __restrict__ logits, int vocab
   s = warp_sum(l < (blockDim.x >> 5) ? red[l] : 0.f);
   if (threadIdx.x == 0) {
     const int t = picked[row * 2];
+    POOT_IN_RANGE(t, vocab, kSiteTokenId);
     out[row] = (t >= 0 && t < vocab) ? lr[t] - mx - logf(s) : 0.f;
   }
 }

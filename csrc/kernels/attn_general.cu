@@ -39,7 +39,8 @@ attn_general_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
   const float slope = alibi ? alibi[h] : 0.f;
   float m = -FLT_MAX, l = 0.f;
   for (int j = first + w; j < ctx; j += AG_WARPS) {
-    const int blk = block_tables[(size_t)seq * max_blocks + (j >> 4)];
+    int blk = block_tables[(size_t)seq * max_blocks + (j >> 4)];
+    if (!POOT_IN_RANGE(j >> 4, max_blocks, kSitePosition) || !POOT_IN_RANGE(blk, POOT_LIMIT(kLimPoolBlocks), kSiteBlockId)) blk = 0;
     const size_t base = (((size_t)blk * Hkv + kvh) * 16 + (j & 15)) * pool_d;
     const __nv_bfloat16* kr = kpool + base;
     const __nv_bfloat16* vr = vpool + base;

@@ -89,7 +89,8 @@ attn_paged_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,  // row str
   const int hl = lane % NREP;
 
   for (int b = nb_begin + warp; b < nb_end; b += ATT_WARPS) {
-    const int blk = bt[b];
+    int blk = bt[b];
+    if (!POOT_IN_RANGE(blk, POOT_LIMIT(kLimPoolBlocks), kSiteBlockId)) blk = 0;
     const int pbase = b * ATT_BLOCK;
     const size_t boff = ((size_t)blk * Hkv + kvh) * ATT_BLOCK * D;
     const uint4* kb = reinterpret_cast<const uint4*>(kpool + boff);

@@ -160,4 +160,65 @@ inline int launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, 
   return (int)cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
 }
 
+// ---- checked build ---------------------------------------------------------------------------------------------
+// With -DPOOT_DEBUG_BOUNDS every data-dependent index a kernel reads from device memory (token ids, K/V slots, block
+// ids, expert ids, row maps) is compared with its bound before use.  An index outside it is not trapped on: the
+// kernel records {site, source line, index, bound} - the first record wins - substitutes a safe index and carries
+// on, so the context stays usable and the host reads the record after the step (poot_debug_bounds_read).  Bounds a
+// kernel is not given as an argument (pool slots, pool blocks, recurrent-state rows) are set once from the host
+// (poot_debug_bounds_limit).  The record and the limits are per translation unit; each unit registers its accessors
+// in one host-side list, which the two entry points walk.  A release build compiles every check away.
+enum BoundsSite {
+  kSiteTokenId = 1, kSiteKvSlot = 2, kSiteBlockId = 3, kSitePosition = 4, kSiteExpertId = 5, kSiteRowMap = 6,
+  kSiteLogitIndex = 7, kSiteSeqRow = 8, kSiteStateRow = 9, kSiteGatherRow = 10,
+};
+enum BoundsLimit { kLimPoolSlots = 0, kLimPoolBlocks = 1, kLimStateRows = 2, kLimCount = 4 };
+
+#ifdef POOT_DEBUG_BOUNDS
+}  // namespace poot
+#include <vector>
+namespace poot {
+namespace dbg {
+static __device__ int g_fault[4];
+static __device__ long long g_limit[kLimCount];
+struct Unit {
+  int (*read)(int*);
+  int (*clear)();
+  int (*limit)(int, long long);
+};
+inline std::vector<Unit>& units() {
+  static std::vector<Unit> u;
+  return u;
+}
+static int unit_read(int* out4) { return (int)cudaMemcpyFromSymbol(out4, g_fault, sizeof(int) * 4); }
+static int unit_clear() {
+  const int z[4] = {0, 0, 0, 0};
+  return (int)cudaMemcpyToSymbol(g_fault, z, sizeof(z));
+}
+static int unit_limit(int which, long long v) {
+  return (int)cudaMemcpyToSymbol(g_limit, &v, sizeof(v), sizeof(long long) * which);
+}
+static const int unit_registered = (units().push_back(Unit{unit_read, unit_clear, unit_limit}), 0);
+
+__device__ __forceinline__ bool in_range(long long i, long long n, int site, int line) {
+  if (i >= 0 && i < n) return true;
+  if (atomicCAS(&g_fault[0], 0, site) == 0) {
+    g_fault[1] = line;
+    g_fault[2] = (int)(i < -2147483647LL ? -2147483647LL : (i > 2147483647LL ? 2147483647LL : i));
+    g_fault[3] = (int)(n > 2147483647LL ? 2147483647LL : n);
+  }
+  return false;
+}
+__device__ __forceinline__ long long limit(int which) {
+  const long long v = g_limit[which];
+  return v > 0 ? v : 0x7fffffffffffffffLL;
+}
+}  // namespace dbg
+#define POOT_IN_RANGE(i, n, site) (::poot::dbg::in_range((long long)(i), (long long)(n), (site), __LINE__))
+#define POOT_LIMIT(which) (::poot::dbg::limit(which))
+#else
+#define POOT_IN_RANGE(i, n, site) (true)
+#define POOT_LIMIT(which) (0x7fffffffffffffffLL)
+#endif
+
 }  // namespace poot

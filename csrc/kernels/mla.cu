@@ -37,6 +37,7 @@ mla_qkv_write_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
   }
   const int slot = slots[t];
   if (slot < 0) return;
+  if (!POOT_IN_RANGE(slot, POOT_LIMIT(kLimPoolSlots), kSiteKvSlot)) return;
   const size_t base = (((size_t)(slot / KV_BLOCK) * nh + h) * KV_BLOCK + (slot % KV_BLOCK)) * dq;
   const __nv_bfloat16* kb = kvb + ((size_t)t * nh + h) * (dn + dv);
   __nv_bfloat16* kd = kpool + base;

@@ -280,7 +280,7 @@ __global__ void quant_row_gather_kernel(const int* __restrict__ ids, const uint8
                                         __nv_bfloat16* __restrict__ out, int D, int vocab) {
   pdl_wait(); pdl_launch();
   int id = ids[blockIdx.x];
-  if (id < 0 || id >= vocab) id = 0;
+  if (!POOT_IN_RANGE(id, vocab, kSiteTokenId) || id < 0 || id >= vocab) id = 0;
   const size_t row_bytes = (size_t)(D / QGeom<FMT>::ELEMS) * QGeom<FMT>::BYTES;
   const uint8_t* row = table + (size_t)id * row_bytes;
   for (int k = threadIdx.x * 8; k < D; k += blockDim.x * 8) {

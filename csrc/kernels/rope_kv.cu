@@ -41,6 +41,7 @@ rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict_
   if (h >= Hq + Hkv) {  // V head: plain copy into the pool
     int slot = slots[t];
     if (slot < 0) return;
+    if (!POOT_IN_RANGE(slot, POOT_LIMIT(kLimPoolSlots), kSiteKvSlot)) return;
     int kvh = h - Hq - Hkv;
     KV* dst = vpool + (((size_t)(slot / KV_BLOCK) * Hkv + kvh) * KV_BLOCK + (slot % KV_BLOCK)) * D;
     for (int d = lane; d < D; d += 32) dst[d] = to_kv<KV>(__bfloat162float(src[d]));
@@ -49,7 +50,11 @@ rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict_
 
   const bool is_q = h < Hq;
   int slot = 0;
-  if (!is_q) { slot = slots[t]; if (slot < 0) return; }
+  if (!is_q) {
+    slot = slots[t];
+    if (slot < 0) return;
+    if (!POOT_IN_RANGE(slot, POOT_LIMIT(kLimPoolSlots), kSiteKvSlot)) return;
+  }
   const __nv_bfloat16* nw = is_q ? q_norm_w : k_norm_w;
   float inv = 1.f;
   if (nw != nullptr) {
@@ -59,6 +64,7 @@ rope_kv_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict_
     inv = rsqrtf(ss / (float)D + norm_eps);
   }
   int pos = positions[t];
+  POOT_IN_RANGE(pos, max_pos, kSitePosition);
   if (pos < 0) pos = 0;
   if (pos >= max_pos) pos = max_pos - 1;
   const int half = rot >> 1;

@@ -19,7 +19,7 @@ __global__ void embed_gather_kernel(const int* __restrict__ ids, const uint4* __
   pdl_wait(); pdl_launch();
   int t = blockIdx.x;
   int id = ids[t];
-  if (id < 0 || id >= vocab) id = 0;
+  if (!POOT_IN_RANGE(id, vocab, kSiteTokenId) || id < 0 || id >= vocab) id = 0;
   const uint4* src = table + (size_t)id * D8;
   uint4* dst = out + (size_t)t * D8;
   for (int i = threadIdx.x; i < D8; i += blockDim.x) dst[i] = src[i];
@@ -268,7 +268,10 @@ __global__ void decode_advance_kernel(const int* __restrict__ picked, int* __res
   ctx[i] = pos + 1;
   int seq = row_seq ? row_seq[i] : i;
   int b = pos / 16;
-  slots[i] = b < max_blocks ? block_tables[(size_t)seq * max_blocks + b] * 16 + (pos % 16) : -1;
+  POOT_IN_RANGE(b, max_blocks, kSitePosition);      // a row that outgrew its block table: release writes slot -1
+  int blk = b < max_blocks ? block_tables[(size_t)seq * max_blocks + b] : 0;
+  if (!POOT_IN_RANGE(blk, POOT_LIMIT(kLimPoolBlocks), kSiteBlockId)) blk = 0;
+  slots[i] = b < max_blocks ? blk * 16 + (pos % 16) : -1;
 }
 
 // ---- small pointwise and movement kernels the layer programs need between the large ones ------------------------
@@ -300,7 +303,7 @@ __global__ void gather_rows_kernel(const uint8_t* __restrict__ src, long long sr
                                    int row_bytes) {
   pdl_wait(); pdl_launch();
   long long r = idx[blockIdx.x];
-  if (r < 0 || r >= rows) r = 0;
+  if (!POOT_IN_RANGE(r, rows, kSiteGatherRow) || r < 0 || r >= rows) r = 0;
   const C* s = reinterpret_cast<const C*>(src + (size_t)r * src_pitch);
   C* d = reinterpret_cast<C*>(out + (size_t)blockIdx.x * out_pitch);
   for (int c = threadIdx.x; c < row_bytes / (int)sizeof(C); c += blockDim.x) d[c] = s[c];
@@ -327,6 +330,7 @@ __global__ void bias_add_indexed_kernel(__nv_bfloat16* __restrict__ x, const __n
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int r = (int)(i / N), n = (int)(i - (size_t)r * N);
     const int e = idx[r / div];
+    if (e >= 0) POOT_IN_RANGE(e + e0, experts, kSiteExpertId);      // a negative id marks a padding tile
     if (e < 0 || e + e0 >= experts) continue;
     const float b = __bfloat162float(table[(size_t)(e + e0) * N + n]) * (gate ? gate[r] : 1.f);
     x[i] = __float2bfloat16(__bfloat162float(x[i]) + b);

@@ -56,21 +56,27 @@ def _run(cmd, verbose):
     return r.stdout + r.stderr
 
 
-def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
+def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool = False,
+                  debug_bounds: bool = False) -> Path:
+    """``debug_bounds``: the checked flavour (``-DPOOT_DEBUG_BOUNDS``: every data-dependent index is compared with its
+    bound and a miss is recorded for the host instead of trapping), built beside the release library as
+    ``libpoot_kernels_dbg.so`` and loaded instead of it when ``POOT_DEBUG_BOUNDS=1`` is in the environment."""
     src_dir = CSRC / "kernels"
     sources = sorted(src_dir.glob("*.cu"))
     headers = sorted(src_dir.glob("*.cuh")) + sorted(src_dir.glob("*.h"))
-    OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    obj_dir = OBJ_DIR.parent / "obj_dbg" if debug_bounds else OBJ_DIR
+    obj_dir.mkdir(parents=True, exist_ok=True)
     LIB_DIR.mkdir(parents=True, exist_ok=True)
-    out = LIB_DIR / "libpoot_kernels.so"
+    out = LIB_DIR / ("libpoot_kernels_dbg.so" if debug_bounds else "libpoot_kernels.so")
     nvcc = _nvcc()
     jobs = []
     objs = []
+    extra = ["-DPOOT_DEBUG_BOUNDS"] if debug_bounds else []
     for s in sources:
-        o = OBJ_DIR / (s.stem + ".o")
+        o = obj_dir / (s.stem + ".o")
         objs.append(o)
         if force or _newer(o, [s, *headers]):
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(src_dir), "-c", str(s), "-o", str(o)]
+            cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(src_dir), "-c", str(s), "-o", str(o)]
             if ptxas_info:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)
@@ -108,13 +114,19 @@ def build_host(verbose: bool = False, force: bool = False) -> Path:
     return out
 
 
-def build_all(verbose: bool = False, force: bool = False) -> None:
+def build_kernels_checked(verbose: bool = False, force: bool = False) -> Path:
+    return build_kernels(verbose, force, debug_bounds=True)
+
+
+def build_all(verbose: bool = False, force: bool = False, checked: bool = False) -> None:
     build_host(verbose, force)
     build_kernels(verbose, force)
+    if checked:
+        build_kernels_checked(verbose, force)
 
 
 if __name__ == "__main__":
-    build_all(verbose="-v" in sys.argv, force="-f" in sys.argv)
+    build_all(verbose="-v" in sys.argv, force="-f" in sys.argv, checked="--checked" in sys.argv)
     if "--ptxas" in sys.argv:
         build_kernels(verbose=False, force=True, ptxas_info=True)
     print("built:", *(p.name for p in LIB_DIR.glob("*.so")))

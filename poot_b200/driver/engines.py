@@ -86,6 +86,13 @@ class DeviceStepEngine:
         self.h_status = buf(16, torch.int32)   # the device control block, read back with every step's result
         self.status_hook = None                # tests: callable returning (code, detail) in place of the device's block
         self.device_timing = False           # bracket each step with CUDA events (opt-in: it adds a synchronisation)
+        self.bounds_checked = False          # the checked kernel library is loaded: read its record after every step
+        if pin and engine.device.type == "cuda":
+            from ..ops import cuda_ops as K
+            if K.bounds_checking():
+                self.bounds_checked = True
+                K.set_bounds_limits(pool_slots=engine.kv.num_blocks * 16, pool_blocks=engine.kv.num_blocks,
+                                    state_rows=engine.max_seqs)
         self.last_device_ms = None           # None = not measured
         self.last_run_ms = None
         self.last_launches = 0
@@ -222,6 +229,9 @@ class DeviceStepEngine:
     def _raise_on_failed_wait(self, on_device: bool) -> None:
         """A wait that gave up inside the step makes its tokens invalid: they must not reach a client.  The typed
         error leaves through the scheduler's guard, which fails the live requests and marks the engine dead."""
+        if self.bounds_checked and on_device:
+            from ..ops import cuda_ops as K
+            K.check_bounds()                   # raises DeviceIndexOutOfRange: the step's tokens are discarded
         if self.status_hook is not None:
             code, detail = self.status_hook()
         elif on_device:

@@ -7,6 +7,7 @@ still be loaded (the CUDA runtime is linked statically) but no launcher may be c
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
@@ -36,12 +37,16 @@ def _load(name: str, builder: str):
 
 
 def kernels() -> ctypes.CDLL:
-    """The CUDA kernel library (``libpoot_kernels.so``)."""
+    """The CUDA kernel library: ``libpoot_kernels.so``, or its checked flavour ``libpoot_kernels_dbg.so`` (bounds
+    checks on every data-dependent index, recorded for the host) when ``POOT_DEBUG_BOUNDS=1`` is set."""
     global _kernels
     if _kernels is None:
         with _lock:
             if _kernels is None:
-                _kernels = _load("libpoot_kernels.so", "build_kernels")
+                if os.environ.get("POOT_DEBUG_BOUNDS", "0") not in ("", "0"):
+                    _kernels = _load("libpoot_kernels_dbg.so", "build_kernels_checked")
+                else:
+                    _kernels = _load("libpoot_kernels.so", "build_kernels")
     return _kernels
 
 

@@ -252,6 +252,51 @@ def check_status(device=None) -> None:
                                 f" ({gave_up} wait(s) gave up)", code, detail)
 
 
+# ---- checked build ------------------------------------------------------------------------------------------------
+BOUNDS_SITES = {1: "token id", 2: "K/V slot", 3: "K/V block id", 4: "position", 5: "expert id", 6: "row map",
+                7: "logit index", 8: "sequence row", 9: "recurrent-state row", 10: "gathered row"}
+BOUNDS_LIMITS = {"pool_slots": 0, "pool_blocks": 1, "state_rows": 2}
+
+
+class DeviceIndexOutOfRange(RuntimeError):
+    """The checked kernel library saw a data-dependent index outside its bound (the kernel substituted a safe index
+    and carried on; the step's results are not to be used)."""
+
+    def __init__(self, site: int, line: int, index: int, bound: int):
+        super().__init__(f"device index out of range: {BOUNDS_SITES.get(site, f'site {site}')} {index} outside "
+                         f"[0, {bound}) (kernel source line {line})")
+        self.site, self.line, self.index, self.bound = site, line, index, bound
+
+
+def _dbg(name: str, argtypes):
+    f = getattr(kernels(), name)            # host-only entry points: not launches, so not counted as such
+    f.argtypes, f.restype = argtypes, c_int
+    return f
+
+
+def bounds_checking() -> bool:
+    """True when the loaded kernel library is the checked flavour (``POOT_DEBUG_BOUNDS=1`` at import)."""
+    return bool(_dbg("poot_debug_bounds_enabled", [])())
+
+
+def set_bounds_limits(**limits: int) -> None:
+    """Bounds the kernels are not given as arguments: ``pool_slots``, ``pool_blocks``, ``state_rows``."""
+    for name, v in limits.items():
+        check(_dbg("poot_debug_bounds_limit", [c_int, c_longlong])(BOUNDS_LIMITS[name], int(v)), "debug_bounds_limit")
+
+
+def check_bounds() -> None:
+    """Raise ``DeviceIndexOutOfRange`` for the first recorded fault (and clear the record).  Synchronises the device;
+    a no-op on the release library."""
+    if not bounds_checking():
+        return
+    out = (c_int * 4)()
+    check(_dbg("poot_debug_bounds_read", [_P])(out), "debug_bounds_read")
+    if out[0] != 0:
+        check(_dbg("poot_debug_bounds_clear", [])(), "debug_bounds_clear")
+        raise DeviceIndexOutOfRange(out[0], out[1], out[2], out[3])
+
+
 # ----------------------------------------------------------------------------------------------------------------
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _need_cuda(ids, table)

@@ -27,7 +27,10 @@ import torch.distributed as dist
 
 from ..ops import cuda_ops as K
 from ..ops._lib import check, kernels
+from .guarded_layout import CommBufferOverrun, GuardedLayout
 from .symm import SymmetricBlock
+
+FLAG_BYTES = 4 * 8 * 4             # four channels of eight int32 flag words (tp_common.cuh: TP_FLAG_WORDS)
 
 _P = c_void_p
 
@@ -92,20 +95,20 @@ class FusedComm(NcclComm):
         H, w = engine.cfg.hidden, self.world
         self.H = H
         self.s_max = self.MAX_ROWS // w
-        # layout of the symmetric block (byte offsets, 1 KiB aligned)
-        self.off_flags = 0
-        self.off_inbox = 1024
+        # layout of the symmetric block: 1 KiB aligned regions, each followed by guard words that check_guards() reads
         inbox_bytes = 2 * w * self.MAX_ROWS * H * 2   # one-shot form: a slot holds up to MAX_ROWS rows
-        self.off_xs = self.off_inbox + (inbox_bytes + 1023) // 1024 * 1024
         xs_bytes = 2 * self.MAX_ROWS * H * 2
-        self.off_ax = self.off_xs + (xs_bytes + 1023) // 1024 * 1024
         # greedy-pick exchange: [2][world][ax_cap] int32, one stage-1 table [rows, groups, 3] per rank and parity
         self.ax_cap = engine.max_seqs * K.argmax_groups(max(1, engine.cfg.vocab // w)) * 3
         ax_bytes = 2 * w * self.ax_cap * 4
-        total = self.off_ax + (ax_bytes + 1023) // 1024 * 1024
-        self.block = SymmetricBlock(total, self.rank, w, self.device, self.group)
+        self.layout = GuardedLayout([("flags", FLAG_BYTES), ("inbox", inbox_bytes), ("xs", xs_bytes), ("ax", ax_bytes)])
+        self.off_flags, self.off_inbox = self.layout.offset("flags"), self.layout.offset("inbox")
+        self.off_xs, self.off_ax = self.layout.offset("xs"), self.layout.offset("ax")
+        self.block = SymmetricBlock(self.layout.total, self.rank, w, self.device, self.group)
         if self.probe_links:
-            self.block.probe(self.group)
+            self.block.probe(self.group)                  # leaves the block zeroed
+        self._write_guards()
+        self.last_overrun: Optional[CommBufferOverrun] = None
         self.flags_peer = self.block.ptr_array(self.off_flags)
         self.inbox_peer = self.block.ptr_array(self.off_inbox)
         self.xs_peer = self.block.ptr_array(self.off_xs)
@@ -201,6 +204,19 @@ class FusedComm(NcclComm):
                          self.H, 0, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
               "gemm_skinny_tp")
 
+    def _write_guards(self) -> None:
+        def store(off, words):
+            self.block.local_tensor(off, (len(words),), torch.int32).copy_(torch.tensor(words, dtype=torch.int32))
+        self.layout.write(self.rank, store)
+        torch.cuda.synchronize(self.device)
+
+    def check_guards(self) -> None:
+        """Read the guard words behind every region of this rank's block (host read after a device sync); raises
+        ``CommBufferOverrun`` naming the region a store ran past.  Called at close, before a reset clears the block,
+        and by debug runs after a step."""
+        torch.cuda.synchronize(self.device)
+        self.layout.check(self.rank, lambda off, n: self.block.local_tensor(off, (n,), torch.int32).cpu().tolist())
+
     def reset(self) -> None:
         """Collective restart of the cross-rank protocol after a failed step: every rank drains, all meet, each zeroes
         its own block (flags, poison words, inboxes) and its counters, all meet again.  Between the two meetings no rank
@@ -208,7 +224,12 @@ class FusedComm(NcclComm):
         self.drain()
         K.clear_abort(self.device)
         self.rendezvous()
+        try:                            # what the failed step left behind is evidence: look before clearing it
+            self.check_guards()
+        except CommBufferOverrun as e:
+            self.last_overrun = e
         self.block.local_tensor(0, (self.block.nbytes,), torch.uint8).zero_()
+        self._write_guards()
         self.epoch.zero_()
         self.ticket.zero_()
         self.ax_count.zero_()
@@ -224,9 +245,16 @@ class FusedComm(NcclComm):
     def close(self) -> None:
         if self.block is not None:
             self.drain()
+            overrun = self.last_overrun
+            try:
+                self.check_guards()
+            except CommBufferOverrun as e:
+                overrun = e
             self.block.close()
             self.block = None
             K.clear_abort(self.device)
+            if overrun is not None:
+                raise overrun
 
 
 # What "auto" means wherever a tensor-parallel group is built without an explicit choice.  The fused programs are the
