@@ -65,6 +65,7 @@ class StepInputs:
     embed_flags: Optional[np.ndarray] = None    # [T] int32, 1 = the token's embedding is replaced by its row of embed_rows
     embed_rows: Optional[np.ndarray] = None     # [T, hidden] f32 (rows without a flag are zero); None = no token is replaced
     rope_positions: Optional[np.ndarray] = None  # [3, T] int32 rotary position streams (time, row, column); None = the positions
+    carry: Optional[np.ndarray] = None          # [T, hidden] f32: the hidden-state carry a multi-token-prediction layer reads
 
 
 @dataclass
@@ -152,6 +153,7 @@ class Driver:
         self.eos_token = eos_token
         self.max_blocks_per_seq = blocks_for(max_seq_len)
         self.seqs: Dict[int, Sequence_] = {}
+        self.after_step = None      # hook run after every step with the spans it wrote (a multi-token-prediction draft catches up)
         self._free_rows = list(range(max_rows - 1, -1, -1))
         self._ids = itertools.count(1)
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "prefix_hit_tokens": 0,
@@ -367,8 +369,11 @@ class Driver:
         picked, logprobs = self.engine.run_step(inp)
         self.stats["steps"] += 1
         out, b = [], 0
+        spans, off = [], 0
         for s, piece in rows:
             sampled = piece == s.pending
+            spans.append([s, s.computed, piece, off, list(s.tokens[s.computed + 1:s.computed + piece + 1])])
+            off += piece
             s.computed += piece
             if piece > 1 or s.generated == 0 and not sampled:
                 self.stats["prefill_tokens"] += piece
@@ -384,9 +389,13 @@ class Driver:
                 b += 1
                 if bad >= 0:
                     raise SamplerFault(s.id, bad)
+                spans[-1][4].append(tok)
                 out.append(RowResult(s.id, tok, piece, lp))
             else:
                 out.append(RowResult(s.id, None, piece))
+        if self.after_step is not None:
+            # (sequence, first position, positions written, offset of its rows in the step, the token after each position)
+            self.after_step(self, [tuple(sp) for sp in spans])
         return out
 
     def reset(self) -> None:

@@ -84,6 +84,8 @@ class DeviceStepEngine:
         self.h_picked, self.h_logprobs = buf((B, 2), torch.int32), buf(B, torch.float32)
         self.h_bt = buf((engine.max_seqs, engine.max_blocks), torch.int32)
         self.h_status = buf(16, torch.int32)   # the device control block, read back with every step's result
+        self.h_carry = None                    # host copy of the hidden-state carry, made when the engine exports one
+        self.last_hidden = None
         self.status_hook = None                # tests: callable returning (code, detail) in place of the device's block
         self.device_timing = False           # bracket each step with CUDA events (opt-in: it adds a synchronisation)
         self.bounds_checked = False          # the checked kernel library is loaded: read its record after every step
@@ -96,6 +98,23 @@ class DeviceStepEngine:
         self.last_device_ms = None           # None = not measured
         self.last_run_ms = None
         self.last_launches = 0
+
+    @property
+    def carry(self) -> bool:
+        """The engine leaves every token row's closing hidden state in ``last_hidden`` after a step."""
+        return self.e.carry
+
+    @property
+    def block_tables(self):
+        return self.e.block_tables
+
+    @block_tables.setter
+    def block_tables(self, tables) -> None:
+        """Read another engine's block tables (a multi-token-prediction layer addresses its cache through the target's);
+        set before the first step, which captures the tensor's address."""
+        if tuple(tables.shape) != tuple(self.e.block_tables.shape):
+            raise ValueError("block tables of different geometry cannot be shared")
+        self.e.block_tables = tables
 
     def write_block_table(self, row: int, blocks) -> None:
         n = len(blocks)
@@ -134,6 +153,8 @@ class DeviceStepEngine:
             if e.lora is None:
                 raise RuntimeError("a sequence names an adapter slot but the engine has no adapter bank")
             lora = e.lora.bind_rows(inp.adapter_rows, T)
+        if inp.carry is not None:
+            e.bind_carry(torch.from_numpy(np.ascontiguousarray(inp.carry[:T])), torch.from_numpy(inp.positions[:T]))
         embeds = inp.embed_flags is not None
         if embeds:
             e.bind_embeds(torch.from_numpy(inp.embed_flags[:T]), torch.from_numpy(inp.embed_rows[:T]))
@@ -153,6 +174,12 @@ class DeviceStepEngine:
         self.h_picked[:B].copy_(e.picked[:B], non_blocking=True)
         if inp.want_logprobs:
             self.h_logprobs[:B].copy_(e.logprobs[:B], non_blocking=True)
+        if e.carry:
+            if self.h_carry is None:
+                self.h_carry = torch.zeros(e.max_tokens, e.cfg.hidden, dtype=torch.bfloat16)
+                if torch.cuda.is_available():
+                    self.h_carry = self.h_carry.pin_memory()
+            self.h_carry[:T].copy_(e.carry_out[:T], non_blocking=True)
         on_device = e.device.type == "cuda"
         if on_device:
             # the control block rides the same stream as the result: no extra synchronisation
@@ -160,6 +187,8 @@ class DeviceStepEngine:
             self.h_status.copy_(K.status_word(e.device), non_blocking=True)
             torch.cuda.current_stream().synchronize()
         self._raise_on_failed_wait(on_device)
+        if e.carry:
+            self.last_hidden = self.h_carry[:T].float().numpy()
         self.last_run_ms = (_time.perf_counter() - t0) * 1e3
         self.last_device_ms = ev[0].elapsed_time(ev[1]) if ev is not None else None
         self.last_launches = e.launches_per_step.get(e._key(shape), 0)
@@ -270,7 +299,9 @@ class OracleStepEngine:
     """
 
     def __init__(self, model, weights, num_blocks: int, max_seqs: int, max_tokens: int, max_blocks_per_seq: int,
-                 options=None, graph_transform=None):
+                 options=None, graph_transform=None, carry: bool = False):
+        """``carry``: every step also keeps the closing-norm hidden state of each of its tokens (``last_hidden``), the
+        input of a multi-token-prediction layer; the graphs are then traced with a logit row at every position."""
         from ..oracle.eval import EvalOptions
         from .kvcache import BLOCK
         self.model, self.weights = model, weights
@@ -283,6 +314,8 @@ class OracleStepEngine:
         self.graphs = {}
         self.steps = 0
         self._logits: Optional[np.ndarray] = None
+        self.carry = carry or bool(getattr(model.cfg, "mtp_head", False))
+        self.last_hidden: Optional[np.ndarray] = None
         self.last_run_ms, self.last_device_ms, self.last_launches = None, None, 0
 
     def write_block_table(self, row: int, blocks) -> None:
@@ -293,13 +326,15 @@ class OracleStepEngine:
         if key not in self.graphs:
             from ..models.model import StepSpec
             g = self.model.trace(StepSpec(rows=1, tokens=tokens, capacity=capacity, paged=True,
-                                          pool_slots=self.num_blocks * self.block, embeds=embeds, mrope=mrope))
+                                          pool_slots=self.num_blocks * self.block, embeds=embeds, mrope=mrope,
+                                          carry=self.carry, logit_rows="all" if self.carry else "last"))
             self.graphs[key] = self.graph_transform(g) if self.graph_transform is not None else g
         return self.graphs[key]
 
     def _segment(self, row: int, tokens: np.ndarray, positions: np.ndarray, slots: np.ndarray, ctx: int,
                  embed_flags: Optional[np.ndarray] = None, embed_rows: Optional[np.ndarray] = None,
-                 rope_positions: Optional[np.ndarray] = None) -> np.ndarray:
+                 rope_positions: Optional[np.ndarray] = None, carry: Optional[np.ndarray] = None):
+        """Logits of the segment's last token; with ``carry`` engines ``(logits, hidden)`` of every token."""
         from ..oracle.eval import eval_graph
         blocks = max(1, -(-ctx // self.block))
         cap_blocks = 1
@@ -318,6 +353,10 @@ class OracleStepEngine:
             inputs["rope_positions"] = np.ascontiguousarray(rope_positions, dtype=np.int32)
         if embeds:
             inputs["embed_flags"], inputs["embed_rows"] = embed_flags.astype(np.int32), embed_rows.astype(np.float32)
+        if getattr(self.model.cfg, "mtp_head", False):
+            if carry is None:
+                raise ValueError("a multi-token-prediction layer steps over a hidden-state carry")
+            inputs["carry"] = np.ascontiguousarray(carry, dtype=np.float32)
         fresh = int(positions[0]) == 0        # a sequence's first segment starts its recurrences from zero
         keys = {}
         for i in g.inputs:
@@ -334,6 +373,8 @@ class OracleStepEngine:
         for o in g.outputs:
             if o.role == "state_next":
                 self.state[keys[o.state_of]] = ev.outputs[o.name]
+        if self.carry:
+            return ev.outputs["logits"], ev.outputs["hidden"]
         return ev.outputs["logits"][0]
 
     def run_step(self, inp: StepInputs):
@@ -344,6 +385,7 @@ class OracleStepEngine:
         vocab = self.model.cfg.vocab
         logits = np.zeros((B, vocab), np.float32)
         want = {int(i): b for b, i in enumerate(inp.logit_idx[:inp.live_rows])}
+        hidden = np.zeros((T, self.model.cfg.hidden), np.float32) if self.carry else None
         start = 0
         while start < T:
             row = int(inp.row_seq[start])
@@ -355,8 +397,14 @@ class OracleStepEngine:
                 er = inp.embed_rows[start:end] if inp.embed_flags is not None else None
                 out = self._segment(row, inp.tokens[start:end], inp.positions[start:end], inp.slots[start:end],
                                     int(inp.row_ctx[end - 1]), ef, er,
-                                    inp.rope_positions[:, start:end] if inp.rope_positions is not None else None)
-                if end - 1 in want:
+                                    inp.rope_positions[:, start:end] if inp.rope_positions is not None else None,
+                                    inp.carry[start:end] if inp.carry is not None else None)
+                if self.carry:
+                    seg_logits, hidden[start:end] = out
+                    for i in range(start, end):
+                        if i in want:
+                            logits[want[i]] = seg_logits[i - start]
+                elif end - 1 in want:
                     logits[want[end - 1]] = out
             start = end
         if inp.adjust is not None:
@@ -378,6 +426,7 @@ class OracleStepEngine:
             lse = mx[:, 0] + np.log(np.exp(logits - mx).sum(-1))
             lp = (logits[np.arange(B), picked[:, 0]] - lse).astype(np.float32)
         self._logits = logits
+        self.last_hidden = hidden
         self.steps += 1
         self.last_run_ms = (_time.perf_counter() - t0) * 1e3
         return picked, lp

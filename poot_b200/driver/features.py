@@ -48,6 +48,15 @@ TABLE: List[Tuple[Feature, Feature, str]] = [
     (F.EXPERT_PLACEMENT, F.DEVICE_TIMING, "event brackets between launches would serialise ranks that wait on one another in-kernel"),
     (F.TENSOR_PLACEMENT, F.DRAFT_MODEL, "the draft model would need its own rank group"),
     (F.DRAFT_LOOKUP, F.DRAFT_MODEL, "one draft policy per driver"),
+    (F.DRAFT_MTP, F.DRAFT_LOOKUP, "one draft policy per driver"),
+    (F.DRAFT_MTP, F.DRAFT_MODEL, "one draft policy per driver"),
+    (F.DRAFT_MTP, F.BEAM, "speculation verifies one greedy continuation"),
+    (F.DRAFT_MTP, F.GUIDED, "a constraint mask is computed one token ahead, not for k drafted positions"),
+    (F.DRAFT_MTP, F.PREFIX_CACHE, "the layer's cache entry of a block's last position depends on the token after it"),
+    (F.DRAFT_MTP, F.ADAPTERS, "the layer reads the base model's hidden state"),
+    (F.DRAFT_MTP, F.TENSOR_PLACEMENT, "the layer runs on the single-device engine"),
+    (F.DRAFT_MTP, F.EXPERT_PLACEMENT, "the layer runs on the single-device engine"),
+    (F.DRAFT_MTP, F.PIPELINE_PLACEMENT, "the layer runs on the single-device engine"),
     (F.DRAFT_LOOKUP, F.BEAM, "speculation verifies one greedy continuation"),
     (F.DRAFT_MODEL, F.BEAM, "speculation verifies one greedy continuation"),
     (F.DRAFT_LOOKUP, F.GUIDED, "a constraint mask is computed one token ahead, not for k drafted positions"),
@@ -70,9 +79,14 @@ TABLE: List[Tuple[Feature, Feature, str]] = [
     (F.EXPERT_POOL, F.PIPELINE_PLACEMENT, "the expert pool is built for the single-device engine"),
     (F.EXPERT_POOL, F.PACKED_WEIGHTS, "packed expert weights have no fused grouped kernel"),
 ]
-UNAVAILABLE = {
-    F.DRAFT_MTP: "no registered family ships multi-token-prediction heads",
-}
+UNAVAILABLE: dict = {}      # features no build of the engine offers (none at present); a model that lacks what a feature
+#                             needs is refused where the model is known (``require_mtp``)
+
+
+def require_mtp(cfg) -> None:
+    """Typed refusal of multi-token-prediction drafting on a model whose checkpoint stores no such layer."""
+    if getattr(cfg, "mtp_layers", 0) < 1:
+        raise Unavailable(F.DRAFT_MTP, f"{getattr(cfg, 'family', 'this model')} stores no multi-token-prediction layer")
 
 
 def check(features: Iterable[Feature]) -> None:

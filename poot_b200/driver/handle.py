@@ -86,30 +86,76 @@ class ModelHandle:
             self.canonical[canon] = PackedWeight(w.name, "F32", tuple(w.shape), merged.view(np.uint8).reshape(-1))
         self.adapter = adapter.name
 
+    def _stack_experts(self, out: Dict[str, np.ndarray], p: str) -> None:
+        c = self.cfg
+        if p + "experts_in" in out:          # the family's checkpoint stores the experts stacked in this layout
+            return
+        if c.gated_ffn:
+            gi = np.stack([np.concatenate([self.f32(p + f"experts.{e}.gate"), self.f32(p + f"experts.{e}.up")], 0)
+                           for e in range(c.n_experts)])
+        else:
+            gi = np.stack([self.f32(p + f"experts.{e}.up") for e in range(c.n_experts)])
+        out[p + "experts_in"] = gi
+        out[p + "experts_out"] = np.stack([self.f32(p + f"experts.{e}.down") for e in range(c.n_experts)])
+
     def oracle_weights(self) -> Dict[str, np.ndarray]:
         """Every canonical weight decoded to f32 in the tracer's layout (experts stacked gate-then-up)."""
         c = self.cfg
         out = {}
+        tail = f"layers.{c.n_layers}."          # a multi-token-prediction layer's block: ``mtp_oracle_weights``
         for n, w in self.canonical.items():
-            if ".experts." not in n:
+            if ".experts." not in n and not n.startswith(tail) and not n.startswith("mtp."):
                 out[n] = w.to_f32()
         if getattr(self.model, "kind", "decoder") == "encoder":
             return out
         for l in range(c.n_layers):
-            if not (c.has_ffn(l) and c.moe_layer(l)):
-                continue
-            p = f"layers.{l}."
-            if p + "experts_in" in out:          # the family's checkpoint stores the experts stacked in this layout
-                continue
-            if c.gated_ffn:
-                gi = np.stack([np.concatenate([self.f32(p + f"experts.{e}.gate"), self.f32(p + f"experts.{e}.up")], 0)
-                               for e in range(c.n_experts)])
-            else:
-                gi = np.stack([self.f32(p + f"experts.{e}.up") for e in range(c.n_experts)])
-            out[p + "experts_in"] = gi
-            out[p + "experts_out"] = np.stack([self.f32(p + f"experts.{e}.down") for e in range(c.n_experts)])
+            if c.has_ffn(l) and c.moe_layer(l):
+                self._stack_experts(out, f"layers.{l}.")
         if c.tie_embeddings:
             out.pop("lm_head", None)
+        return out
+
+    @property
+    def has_mtp(self) -> bool:
+        """The configuration names a multi-token-prediction layer AND the checkpoint stores it (conversions often
+        drop it)."""
+        return self.cfg.mtp_layers > 0 and "mtp.eh_proj" in self.canonical
+
+    def mtp_named(self) -> Dict[str, PackedWeight]:
+        """Canonical names of the multi-token-prediction layer as a one-layer model (block renamed to layer 0, its
+        closing norm as ``final_norm``, the target's embedding and head)."""
+        c = self.cfg
+        if not self.has_mtp:
+            raise KeyError(f"{self.source} stores no multi-token-prediction layer")
+        tail = f"layers.{c.n_layers}."
+        out = {"layers.0." + n[len(tail):]: w for n, w in self.canonical.items() if n.startswith(tail)}
+        for n in ("mtp.enorm", "mtp.hnorm", "mtp.eh_proj"):
+            out[n] = self.canonical[n]
+        out["final_norm"], out["embed"] = self.canonical["mtp.head_norm"], self.canonical["embed"]
+        if not c.tie_embeddings and "lm_head" in self.canonical:
+            out["lm_head"] = self.canonical["lm_head"]
+        return out
+
+    def mtp_oracle_weights(self) -> Dict[str, np.ndarray]:
+        """The multi-token-prediction layer as the one-layer model ``models.config.mtp_config`` describes: its block
+        renamed to layer 0, its closing norm as ``final_norm``, the target's embedding and head."""
+        from ..models.config import mtp_config
+        c = self.cfg
+        if not self.has_mtp:
+            raise KeyError(f"{self.source} stores no multi-token-prediction layer")
+        tail = f"layers.{c.n_layers}."
+        out = {"layers.0." + n[len(tail):]: w.to_f32() for n, w in self.canonical.items()
+               if n.startswith(tail) and ".experts." not in n}
+        if mtp_config(c).moe_layer(0):
+            src = {}
+            self._stack_experts(src, tail)
+            out.update({"layers.0." + k[len(tail):]: v for k, v in src.items()})
+        for n in ("mtp.enorm", "mtp.hnorm", "mtp.eh_proj"):
+            out[n] = self.f32(n)
+        out["final_norm"] = self.f32("mtp.head_norm")
+        out["embed"] = self.f32("embed")
+        if not c.tie_embeddings:
+            out["lm_head"] = self.f32("lm_head")
         return out
 
 
@@ -155,6 +201,17 @@ def to_device(w: PackedWeight, device, keep_packed: bool = True):
         t = torch.from_numpy(np.ascontiguousarray(w.payload).view(np.uint16).reshape(w.shape).copy()).view(torch.bfloat16)
         return t.to(device)
     return torch.from_numpy(w.to_f32()).to(device=device, dtype=torch.bfloat16)
+
+
+def mtp_device_weights(handle: ModelHandle, device, target=None):
+    """Device weights of the checkpoint's multi-token-prediction layer (dense bf16, canonical-name builder); with
+    ``target`` given the layer uses the target's embedding and head tensors instead of copies."""
+    import torch
+    from ..models.config import mtp_config
+    from ..runtime.weights import from_named_tensors, share_tables
+    named = {n: torch.from_numpy(np.ascontiguousarray(w.to_f32())) for n, w in handle.mtp_named().items()}
+    w = from_named_tensors(mtp_config(handle.cfg), named, device)
+    return share_tables(w, target) if target is not None else w
 
 
 def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int = 1, keep_packed: bool = True, stage=None):

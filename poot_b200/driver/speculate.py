@@ -58,6 +58,109 @@ class ModelDraft:
         return self.d.generate(list(tokens), SamplingParams(max_tokens=self.k, ignore_eos=True))
 
 
+class MtpDraft:
+    """Drafts from the served model's own multi-token-prediction layer (crates/poot-llm/src/driver/speculate.rs:20-33).
+
+    The layer is a one-block model of its own (``models.config.mtp_config``) behind ``runner``, a step engine that
+    shares the target's block tables, so its K/V for a position lives at the slot the target uses for it.  At position
+    ``p`` it reads the target's closing hidden state of ``p`` and the token that follows ``p``, and guesses the token
+    after that.  After every target step the layer runs over the positions the step wrote (``catch_up``): its cache
+    then holds every committed position, and the last position's pick is the first draft of the sequence's next round.
+    The round's other ``k - 1`` drafts are one-token chain steps, each fed the draft before it and the layer's own
+    closing state of the step before (the post-norm state: recycling the pre-norm one lowers acceptance).  Chain steps
+    write cache entries past the committed prefix; they are masked by the context length until the next catch-up, which
+    starts at the query position, overwrites them.  A sequence whose last result was not committed whole proposes
+    nothing for a round.
+    """
+
+    def __init__(self, runner, k: int = 1):
+        if k < 1:
+            raise ValueError("multi-token-prediction drafting needs K >= 1")
+        self.runner, self.k = runner, k
+        self.next = {}              # seq id -> (position of the round's query token, query token, first draft, hidden row)
+        self.stats = {"catch_up_steps": 0, "chain_steps": 0}
+
+    def attach(self, d: Driver) -> "MtpDraft":
+        """Share the target's block tables and run after each of its steps."""
+        inner = getattr(d.engine, "inner", d.engine)
+        if not getattr(inner, "carry", False):
+            raise DriverError("the target engine exports no hidden-state carry for its multi-token-prediction layer")
+        if hasattr(inner, "block_tables") and hasattr(self.runner, "block_tables"):
+            self.runner.block_tables = inner.block_tables
+        d.after_step = self.catch_up
+        return self
+
+    def _run(self, d: Driver, spans, carry_rows: np.ndarray, sample: Sequence[bool]):
+        """One step of the layer over ``spans`` = (sequence, first position, count, tokens after).  Returns the picks of
+        the sampling spans' last rows and the layer's closing hidden state of every row."""
+        T = sum(n for _, _, n, _ in spans)
+        B = max(1, sum(bool(x) for x in sample))
+        Tp, Bp = _bucket(T, self.runner.max_tokens), _bucket(B, d.max_rows)
+        tokens = np.zeros(Tp, np.int32); positions = np.zeros(Tp, np.int32); slots = np.full(Tp, -1, np.int32)
+        row_seq = np.zeros(Tp, np.int32); row_ctx = np.zeros(Tp, np.int32)
+        carry = np.zeros((Tp, carry_rows.shape[1]), np.float32)
+        carry[:T] = carry_rows
+        logit_idx = np.zeros(Bp, np.int64)
+        off = b = 0
+        for (s, p0, n, after), want in zip(spans, sample):
+            for i in range(n):
+                pos = p0 + i
+                tokens[off + i], positions[off + i], slots[off + i] = after[i], pos, d._slot(s, pos)
+                row_seq[off + i], row_ctx[off + i] = s.row, pos + 1
+            if want:
+                logit_idx[b] = off + n - 1
+                b += 1
+            off += n
+        params = np.zeros((Bp, 4), np.float32); params[:, 0] = 1.0; params[:, 1] = -1e30; params[:, 3] = 1.0
+        inp = StepInputs(tokens, positions, slots, row_seq, row_ctx, logit_idx, S.GREEDY, params, np.zeros(Bp, np.int32),
+                         np.zeros(Bp, np.int32), None, False, T, max(b, 1), carry=carry)
+        picked, _ = self.runner.run_step(inp)
+        return picked, self.runner.last_hidden
+
+    def catch_up(self, d: Driver, spans) -> None:
+        """Run the layer over the positions a target step just wrote.  ``spans``: (sequence, first position, count,
+        offset of the span's rows in the step, the token after each position - one short when the step did not sample)."""
+        hidden = getattr(d.engine, "last_hidden", None)
+        if hidden is None:
+            return
+        for sid in [i for i in self.next if i not in d.seqs]:
+            del self.next[sid]
+        rows, carry, sample = [], [], []
+        for s, p0, n, off, after in spans:
+            self.next.pop(s.id, None)
+            m = min(n, len(after))           # a prefill piece that ends the known tokens without a sample: last row waits
+            if m <= 0:
+                continue
+            rows.append((s, p0, m, after[:m]))
+            carry.append(np.asarray(hidden[off:off + m], np.float32))
+            sample.append(m == n and len(s.tokens) == p0 + n)      # the step sampled this row's next token
+        if not rows:
+            return
+        picked, own = self._run(d, rows, np.concatenate(carry, 0), sample)
+        self.stats["catch_up_steps"] += 1
+        off = b = 0
+        for (s, p0, m, after), want in zip(rows, sample):
+            if want:
+                self.next[s.id] = (p0 + m, int(after[-1]), int(picked[b, 0]), np.array(own[off + m - 1], np.float32))
+                b += 1
+            off += m
+
+    def propose_for(self, d: Driver, s, limit: int) -> List[int]:
+        st = self.next.pop(s.id, None)
+        if st is None or limit < 1:
+            return []
+        pos, query, first, hid = st
+        if s.computed != pos or len(s.tokens) != pos + 1 or s.tokens[-1] != query:
+            return []                        # the result the draft followed was not committed whole
+        drafts = [first]
+        while len(drafts) < min(self.k, limit):
+            picked, own = self._run(d, [(s, pos + len(drafts) - 1, 1, [drafts[-1]])], hid[None, :], [True])
+            self.stats["chain_steps"] += 1
+            drafts.append(int(picked[0, 0]))
+            hid = np.array(own[0], np.float32)
+        return drafts
+
+
 def speculative_step(d: Driver, seq_id: int, draft) -> List[int]:
     """One verify step; returns the tokens to commit (>= 1).  The sequence must be greedy, unguided and past prefill."""
     s = d.seqs[seq_id]
@@ -67,7 +170,8 @@ def speculative_step(d: Driver, seq_id: int, draft) -> List[int]:
         raise DriverError("speculate after the prompt is prefilled (pending must be 1)")
     room = min(len(s.blocks) * BLOCK, d.max_seq_len) - len(s.tokens) - 1
     room = min(room, s.params.max_tokens - s.generated - 1)
-    drafts = list(draft.propose(s.tokens))[:max(0, min(room, d.max_rows - 1, d.engine.max_tokens - 1))]
+    limit = max(0, min(room, d.max_rows - 1, d.engine.max_tokens - 1))
+    drafts = draft.propose_for(d, s, limit) if hasattr(draft, "propose_for") else list(draft.propose(s.tokens))[:limit]
     if any(t < 0 or t >= d.vocab for t in drafts):
         drafts = []
     piece = [s.tokens[-1]] + drafts
@@ -109,6 +213,15 @@ def speculative_step(d: Driver, seq_id: int, draft) -> List[int]:
         d.stats["steps"] += 1
         d.stats["draft_replays"] = d.stats.get("draft_replays", 0) + 1
     out = drafts[:accepted] + [int(picked[accepted, 0])]
+    if hasattr(draft, "catch_up"):
+        # the verify step wrote positions base .. base + accepted for good; the layer catches up over them, fed the
+        # accepted drafts and the target's own pick as the tokens that follow
+        keep_tokens = s.tokens
+        s.tokens = s.tokens + out[:-1]                  # what the sequence will hold once the caller commits the result
+        try:
+            draft.catch_up(d, [(s, base, 1 + accepted, 0, list(out))])
+        finally:
+            s.tokens = keep_tokens
     d.stats["decode_tokens"] += 1 + accepted
     d.stats["draft_proposed"] = d.stats.get("draft_proposed", 0) + len(drafts)
     d.stats["draft_accepted"] = d.stats.get("draft_accepted", 0) + accepted

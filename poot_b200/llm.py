@@ -45,11 +45,14 @@ class LLM:
 
     def __init__(self, cfg: DecoderConfig, driver: Driver, tokenizer, engine=None, handle=None, comm=None):
         self.cfg, self.driver, self.tokenizer, self.engine, self.handle, self.comm = cfg, driver, tokenizer, engine, handle, comm
+        self.draft = None           # draft policy of the model itself (its multi-token-prediction layer), when it has one
 
     # ---- construction --------------------------------------------------------------------------------------------
     @staticmethod
     def _assemble(cfg, weights, tokenizer, rows, max_seq, prefill_chunk, kv_fraction, comm, handle, num_blocks=None,
-                  prefix_caching=True, prefill_budget=None, link=None):
+                  prefix_caching=True, prefill_budget=None, link=None, mtp=None):
+        """``mtp``: ``(device weights of the model's multi-token-prediction layer, k)``; the layer gets a one-block engine
+        of its own whose K/V pool is addressed through the target's block tables."""
         import torch
         from .driver.engines import DeviceStepEngine
         from .runtime.engine import DecoderEngine, KVPool
@@ -70,8 +73,14 @@ class LLM:
         step_prefill = max(prefill_chunk, min(prefill_budget or 0, rows * prefill_chunk))
         max_tokens = max(step_prefill, rows) + rows             # prefill tokens of a step + one decode row per sequence
         # pipeline stages launch eagerly: their steps contain point-to-point transfers whose capture is not relied on
+        if mtp is not None:
+            from .driver.features import Feature, check as _check, require_mtp
+            require_mtp(cfg)
+            _check([Feature.DRAFT_MTP] + ([Feature.TENSOR_PLACEMENT] if comm is not None else [])
+                   + ([Feature.PIPELINE_PLACEMENT] if link is not None else []))
+            prefix_caching = False     # a block's last position in the layer's cache depends on the token after it
         eng = DecoderEngine(weights, num_blocks, rows, max_tokens, blocks_for(max_seq), comm=comm, link=link,
-                            use_graphs=link is None and dev.type == "cuda")
+                            use_graphs=link is None and dev.type == "cuda", carry=mtp is not None)
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
         eos = getattr(tokenizer, "eos", None)
         if cfg.is_recurrent:
@@ -81,13 +90,21 @@ class LLM:
         drv = Driver(DeviceStepEngine(eng), num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
                      prefix_caching=prefix_caching, eos_token=eos if eos is not None else cfg.eos_token,
                      prefill_budget=step_prefill)
-        return LLM(cfg, drv, tokenizer, eng, handle, comm)
+        llm = LLM(cfg, drv, tokenizer, eng, handle, comm)
+        if mtp is not None:
+            from .driver.speculate import MtpDraft
+            layer_weights, k = mtp
+            layer = DecoderEngine(layer_weights, num_blocks, rows, max_tokens, blocks_for(max_seq),
+                                  use_graphs=dev.type == "cuda")
+            llm.mtp_engine = layer
+            llm.draft = MtpDraft(DeviceStepEngine(layer), k).attach(drv)
+        return llm
 
     @staticmethod
     def load(path: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
              kv_fraction: float = 0.85, keep_packed: bool = True, tp_rank: int = 0, tp_world: int = 1, comm=None,
              num_blocks: Optional[int] = None, lora: Optional[str] = None, prefill_budget: Optional[int] = None,
-             pp_rank: int = 0, pp_world: int = 1, link=None) -> "LLM":
+             pp_rank: int = 0, pp_world: int = 1, link=None, draft_mtp: int = 0) -> "LLM":
         """``path``: a Hugging Face directory (config.json + safetensors) or a ``.gguf`` file; ``lora``: a PEFT adapter
         directory merged into the projections at load; ``pp_rank`` / ``pp_world``: this process's stage of a layer
         pipeline (it loads only its layers)."""
@@ -98,22 +115,38 @@ class LLM:
             handle.apply_adapter(load_adapter(lora))
         stage, link = _stage_and_link(handle.cfg, pp_rank, pp_world, link)
         weights = device_weights(handle, device, tp_rank, tp_world, keep_packed, stage=stage)
+        mtp = None
+        if draft_mtp:
+            from .driver.features import Feature, Unavailable, require_mtp
+            from .driver.handle import mtp_device_weights
+            require_mtp(handle.cfg)
+            if not handle.has_mtp:
+                raise Unavailable(Feature.DRAFT_MTP, f"{path} does not store the model's multi-token-prediction layer")
+            mtp = (mtp_device_weights(handle, device, weights), draft_mtp)
         return LLM._assemble(handle.cfg, weights, _tokenizer_for(handle), rows, max_seq, prefill_chunk, kv_fraction,
-                             comm, handle, num_blocks, prefill_budget=prefill_budget, link=link)
+                             comm, handle, num_blocks, prefill_budget=prefill_budget, link=link, mtp=mtp)
 
     @staticmethod
     def random(preset: str, device="cuda", rows: int = 32, max_seq: int = 4096, prefill_chunk: int = 512,
                kv_fraction: float = 0.85, seed: int = 0, std: float = 0.02, tp_rank: int = 0, tp_world: int = 1,
                comm=None, num_blocks: Optional[int] = None, prefill_budget: Optional[int] = None, pp_rank: int = 0,
-               pp_world: int = 1, link=None, **over) -> "LLM":
-        """Random-init weights of a named architecture (benchmarks and tests: no checkpoint on disk)."""
-        from .runtime.weights import random_weights
+               pp_world: int = 1, link=None, draft_mtp: int = 0, **over) -> "LLM":
+        """Random-init weights of a named architecture (benchmarks and tests: no checkpoint on disk).  ``draft_mtp``:
+        also draw a multi-token-prediction layer (the configuration must name one: ``mtp_layers=1``) and draft with it."""
+        from .runtime.weights import random_weights, share_tables
         import dataclasses
         cfg = dataclasses.replace(PRESETS[preset](), **over)
         stage, link = _stage_and_link(cfg, pp_rank, pp_world, link)
+        if draft_mtp:
+            from .driver.features import require_mtp
+            require_mtp(cfg)                    # refused before a byte of weights is drawn
         weights = random_weights(cfg, device, seed=seed, std=std, tp_rank=tp_rank, tp_world=tp_world, stage=stage)
+        mtp = None
+        if draft_mtp:
+            from .models.config import mtp_config
+            mtp = (share_tables(random_weights(mtp_config(cfg), device, seed=seed + 1, std=std), weights), draft_mtp)
         return LLM._assemble(cfg, weights, None, rows, max_seq, prefill_chunk, kv_fraction, comm, None, num_blocks,
-                             prefill_budget=prefill_budget, link=link)
+                             prefill_budget=prefill_budget, link=link, mtp=mtp)
 
     @staticmethod
     def fake(vocab: int = 1000, rows: int = 8, max_seq: int = 512, num_blocks: int = 256, prefill_chunk: int = 64,
@@ -127,7 +160,7 @@ class LLM:
 
     @staticmethod
     def oracle(path: str, rows: int = 4, max_seq: int = 512, num_blocks: int = 128, prefill_chunk: int = 64,
-               lora: Optional[str] = None, prefill_budget: Optional[int] = None) -> "LLM":
+               lora: Optional[str] = None, prefill_budget: Optional[int] = None, draft_mtp: int = 0) -> "LLM":
         """A checkpoint served by the CPU oracle: every supported family end to end on the host, in f32, through the
         same driver (paged K/V, prefix cache, sampling rules) as the device engine.  Slow; meant for checking a
         family or a checkpoint without a device."""
@@ -137,17 +170,27 @@ class LLM:
         if lora is not None:
             from .load.lora import load_adapter
             handle.apply_adapter(load_adapter(lora))
+        mtp = None
+        if draft_mtp:
+            from .driver.features import Feature, Unavailable, require_mtp
+            require_mtp(handle.cfg)
+            if not handle.has_mtp:
+                raise Unavailable(Feature.DRAFT_MTP, f"{path} does not store the model's multi-token-prediction layer")
+            mtp = (handle.mtp_oracle_weights(), draft_mtp)
         return LLM.oracle_from(handle.model, handle.oracle_weights(), _tokenizer_for(handle), rows, max_seq, num_blocks,
-                               prefill_chunk, handle, prefill_budget)
+                               prefill_chunk, handle, prefill_budget, mtp=mtp)
 
     @staticmethod
     def oracle_from(model, weights, tokenizer=None, rows: int = 4, max_seq: int = 512, num_blocks: int = 128,
-                    prefill_chunk: int = 64, handle=None, prefill_budget: Optional[int] = None) -> "LLM":
+                    prefill_chunk: int = 64, handle=None, prefill_budget: Optional[int] = None, mtp=None) -> "LLM":
+        """``mtp``: ``(weights of the multi-token-prediction layer, k)``: the layer drafts ``k`` tokens per round for a
+        lone greedy sequence (``LLM.draft``); the model's configuration must store such a layer."""
         from .driver.engines import OracleStepEngine
         cfg = model.cfg
         max_seq = min(max_seq, cfg.max_position)
         step_prefill = max(prefill_chunk, min(prefill_budget or 0, rows * prefill_chunk))
-        eng = OracleStepEngine(model, weights, num_blocks, rows, step_prefill + rows, blocks_for(max_seq))
+        eng = OracleStepEngine(model, weights, num_blocks, rows, step_prefill + rows, blocks_for(max_seq),
+                               carry=mtp is not None)
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
         eos = getattr(tokenizer, "eos", None)
         # a prefix hit skips tokens; a recurrent layer's state after those tokens is not in the K/V cache, so recurrent
@@ -155,15 +198,34 @@ class LLM:
         from .driver.features import Feature, check
         check([Feature.RECURRENT_STATE] if cfg.is_recurrent else [])
         drv = Driver(eng, num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk,
-                     prefix_caching=not cfg.is_recurrent, eos_token=eos if eos is not None else cfg.eos_token,
-                     prefill_budget=step_prefill)
-        return LLM(cfg, drv, tokenizer, None, handle, None)
+                     prefix_caching=not cfg.is_recurrent and mtp is None,
+                     eos_token=eos if eos is not None else cfg.eos_token, prefill_budget=step_prefill)
+        llm = LLM(cfg, drv, tokenizer, None, handle, None)
+        if mtp is not None:
+            # a block's last position depends on the token after it, so prefix reuse is off under this policy
+            from .driver.features import Feature
+            from .driver.speculate import MtpDraft
+            from .models.config import mtp_config
+            from .models.model import Model
+            from .driver.features import require_mtp
+            require_mtp(cfg)
+            check([Feature.DRAFT_MTP] + ([Feature.RECURRENT_STATE] if cfg.is_recurrent else []))
+            mtp_weights, k = mtp
+            layer = Model(mtp_config(cfg))
+            runner = OracleStepEngine(layer, mtp_weights, num_blocks, rows, step_prefill + rows, blocks_for(max_seq))
+            llm.draft = MtpDraft(runner, k).attach(drv)
+        return llm
 
     # ---- generation ----------------------------------------------------------------------------------------------
     def generate_tokens(self, prompt: Iterable[int], params: Optional[SamplingParams] = None, on_token=None,
                         embeds=None, rope_positions=None) -> List[int]:
         """``embeds``: ``(positions, rows)`` replacing the embeddings of those prompt tokens (image rows of a VLM);
         ``rope_positions[3, len(prompt)]``: the prompt's rotary position streams under a sectioned rope."""
+        p = params or SamplingParams()
+        if (self.draft is not None and embeds is None and rope_positions is None and p.greedy and not p.needs_adjust
+                and not p.logprobs):
+            from .driver.speculate import generate_speculative
+            return generate_speculative(self.driver, list(prompt), p, self.draft, on_token)
         return self.driver.generate(list(prompt), params, on_token, embeds=embeds, rope_positions=rope_positions)
 
     def generate(self, prompt: str, params: Optional[SamplingParams] = None, on_text=None) -> str:

@@ -78,6 +78,11 @@ SANDWICH_BLOCK = {"input_layernorm.weight": "attn_norm", "post_attention_layerno
                   "pre_feedforward_layernorm.weight": "ffn_norm", "post_feedforward_layernorm.weight": "ffn_post_norm"}
 TOP = {"model.embed_tokens.weight": "embed", "model.norm.weight": "final_norm", "lm_head.weight": "lm_head",
        "model.language_model.embed_tokens.weight": "embed", "model.language_model.norm.weight": "final_norm"}
+# tensors a checkpoint stores for its multi-token-prediction layer beside that layer's block (DeepSeek-V3 layout:
+# ``model.layers.<n_layers>.*``); the block's own tensors map like any layer's
+MTP = {"enorm.weight": "mtp.enorm", "hnorm.weight": "mtp.hnorm", "eh_proj.weight": "mtp.eh_proj",
+       "shared_head.norm.weight": "mtp.head_norm", "shared_head.head.weight": "mtp.lm_head",
+       "embed_tokens.weight": "mtp.embed"}
 EXPERT = {"w1": "gate", "w3": "up", "w2": "down", "gate_proj": "gate", "up_proj": "up", "down_proj": "down"}
 
 MPT_LAYER = {"norm_1.weight": "attn_norm", "norm_2.weight": "ffn_norm", "attn.out_proj.weight": "attn_o",
@@ -279,6 +284,9 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
             continue
         if rest in table:
             canon[p + table[rest]] = w
+            continue
+        if l == cfg.n_layers and cfg.mtp_layers and rest in MTP:
+            canon[MTP[rest]] = w
             continue
         e = re.match(r"(?:block_sparse_moe|mlp)\.experts\.(\d+)\.(\w+)\.weight$", rest)
         if e and e.group(2) in EXPERT:

@@ -95,6 +95,10 @@ class DecoderConfig:
     layer_kinds: Optional[list] = None      # "attention" | "mamba" | "gdn" | "none" per layer; None = attention everywhere
     layer_ffn: Optional[list] = None        # 1 = the layer has an FFN after its mixer; None = every layer has one
     dense_layers: Optional[list] = None     # layers of a MoE model whose FFN is dense (besides the leading first_dense_layers)
+    # multi-token prediction: layers the checkpoint stores after the text stack, each guessing one token further ahead
+    # from a position's closing hidden state and the token that follows it (DeepSeek-V3 ``num_nextn_predict_layers``)
+    mtp_layers: int = 0
+    mtp_head: bool = False                  # this configuration IS such a layer (``mtp_config``): its input mixes a carry in
     ssm_heads: int = 0                      # Mamba2: heads, head width, state size, B/C groups, conv taps
     ssm_head_dim: int = 0
     ssm_state: int = 0
@@ -214,6 +218,21 @@ class DecoderConfig:
 
     def to_dict(self) -> dict:
         return asdict(self)
+
+
+def mtp_config(cfg: DecoderConfig) -> DecoderConfig:
+    """The configuration of ``cfg``'s multi-token-prediction layer as a one-layer model of its own: the block has the
+    kind the layer after the text stack would have (attention mixer; routed FFN when the stack's last layers are), its
+    closing norm is the layer's ``shared_head.norm`` and its embedding and head are the target's."""
+    from dataclasses import replace
+    if cfg.mtp_layers < 1:
+        raise ValueError(f"{cfg.family} stores no multi-token-prediction layer")
+    n = cfg.n_layers
+    moe = cfg.is_moe and n >= cfg.first_dense_layers
+    win = cfg.layer_windows[-1] if getattr(cfg, "layer_windows", None) else None
+    return replace(cfg, name=cfg.name + "-mtp", n_layers=1, first_dense_layers=0 if moe else 1, dense_layers=None,
+                   layer_kinds=None, layer_ffn=None, layer_windows=[win] if win is not None else None, mtp_layers=0,
+                   mtp_head=True)
 
 
 def tiny_llama() -> DecoderConfig:

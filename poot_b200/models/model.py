@@ -34,6 +34,8 @@ class StepSpec:
     weight_dtype: DType = DType.F32
     sampler: Optional[str] = None  # None = export logits; greedy | gumbel | gumbel_top_k | gumbel_top_k_top_p
     world: int = 1                # tensor-parallel world (the tracer emits all_reduce at the Megatron points)
+    carry: bool = False           # also export the closing-norm hidden state of the logit rows ("hidden"): what a
+    #                               multi-token-prediction layer reads and a chain of its steps recycles
     embeds: bool = False          # rows of other modalities replace the embeddings of flagged tokens (image rows of a VLM)
     mrope: bool = False           # three rotary position streams (time, row, column) bind per token: ``rope_positions[3, R*T]``
 
@@ -63,6 +65,9 @@ class Model:
             norms.append("embed_norm")
         if not c.tie_embeddings:
             s["lm_head"] = (c.vocab, H)
+        if c.mtp_head:
+            s.update({"mtp.enorm": (H,), "mtp.hnorm": (H,), "mtp.eh_proj": (H, 2 * H)})
+            norms += ["mtp.enorm", "mtp.hnorm"]
         for l in range(c.n_layers):
             p = f"layers.{l}."
             kind, has_ffn = c.mixer_of(l), c.has_ffn(l)
@@ -238,6 +243,15 @@ class Model:
             h = b.select(b.broadcast(b.reshape(flagged, (R * T, 1)), (R * T, H)), rows_in, h)
         if c.embed_norm:
             h = norm(h, "embed_norm")
+        if c.mtp_head:
+            # multi-token-prediction input: the embedding of the token that FOLLOWS a position (zeroed at absolute
+            # position 0) and the target's closing hidden state of that position, each under its own norm, embedding
+            # first, mapped back to the width (DeepSeek-V3 section 2.2; crates/poot-models/src/architectures/
+            # glm53_flash/mtp.rs:9-13)
+            carry = b.slot("carry", (R * T, H), F32, "activation")
+            first = b.binary("ge", b.broadcast(b.scalar(0, I32), (R * T, 1)), b.reshape(positions, (R * T, 1)))   # pos == 0
+            h = b.select(b.broadcast(first, (R * T, H)), b.broadcast(b.scalar(0.0, F32), (R * T, H)), h)
+            h = O.linear(b, b.concat([norm(h, "mtp.enorm"), norm(carry, "mtp.hnorm")], -1), W("mtp.eh_proj"))
         scale = c.attn_scale if c.attn_scale is not None else 1.0 / math.sqrt(D)
         rs = c.residual_scale
 
@@ -490,6 +504,8 @@ class Model:
         else:
             h = b.reshape(h, (R * T, H))
         x = norm(h, "final_norm")
+        if spec.carry or c.mtp_head:
+            b.output(x, "hidden", "export")
         head = W("embed") if c.tie_embeddings else W("lm_head")
         logits = O.linear(b, x, head)
         if c.logit_scale != 1.0:

@@ -273,6 +273,7 @@ def _deepseek(c, family: str) -> DecoderConfig:
     cfg.n_kv_heads = cfg.n_heads
     cfg.latent_norm_eps = 1e-6          # the norms of the low-rank query / key-value projections keep their own epsilon
     if v3:
+        cfg.mtp_layers = int(c.get("num_nextn_predict_layers") or 0)     # used only when the checkpoint stores the layer
         cfg.router, cfg.router_select_bias = "sigmoid", True
         cfg.n_group, cfg.topk_group = int(c.get("n_group") or 1), int(c.get("topk_group") or 1)
     return cfg

@@ -62,7 +62,11 @@ class DecoderEngine:
     """Runs the decoder program of one rank.  ``comm`` (optional) supplies the tensor-parallel collectives."""
 
     def __init__(self, weights: DecoderWeights, num_blocks: int, max_seqs: int, max_tokens: int,
-                 max_blocks_per_seq: int, comm=None, device=None, use_graphs: bool = True, link=None):
+                 max_blocks_per_seq: int, comm=None, device=None, use_graphs: bool = True, link=None,
+                 carry: bool = False):
+        """``carry``: every step also leaves the closing-norm hidden state of each of its token rows in ``carry_out``
+        (what the model's multi-token-prediction layer reads).  An engine built over such a layer's own weights
+        (``cfg.mtp_head``) reads ``carry_in`` beside its tokens and always exports its own closing state."""
         cfg = weights.cfg
         self.stage = weights.stage          # None, or this rank's layer range of a pipeline
         self.link = link                    # hand-off of the residual stream between stages
@@ -231,8 +235,24 @@ class DecoderEngine:
         # Families whose layer the planner lowers completely run the compiled plan's launch list (runtime/program.py);
         # everything else keeps the hand-sequenced program below.
         self.program = None
+        self.carry = bool(carry or cfg.mtp_head)
+        self.carry_out = self.carry_in = None
+        if self.carry:
+            if comm is not None or (self.stage is not None and self.stage.count > 1):
+                raise ValueError("the hidden-state carry is exported by the single-device engine")
+            self.carry_out = torch.zeros(max_tokens, cfg.hidden, dtype=torch.bfloat16, device=self.device)
+        if cfg.mtp_head:
+            if getattr(weights, "mtp", None) is None:
+                raise ValueError("weights of a multi-token-prediction layer carry its input norms and projection")
+            H_ = cfg.hidden
+            self.carry_in = torch.zeros(max_tokens, H_, dtype=torch.bfloat16, device=self.device)
+            self.mtp_e = torch.zeros(max_tokens, H_, dtype=torch.bfloat16, device=self.device)
+            self.mtp_c = torch.zeros(max_tokens, H_, dtype=torch.bfloat16, device=self.device)
+            self.mtp_zero = torch.zeros(max_tokens, H_, dtype=torch.bfloat16, device=self.device)
+            self.mtp_first = torch.zeros(max_tokens, dtype=torch.int32, device=self.device)   # 1 = absolute position 0
         from .program import ProgramExecutor
-        self.program = ProgramExecutor.build_for(self)
+        if not self.carry:
+            self.program = ProgramExecutor.build_for(self)
         self.lora = None                    # bank of resident adapters, created by enable_adapters()
         self.embed_rows = self.embed_flags = None   # staging of rows that replace embeddings, created by bind_embeds()
         self.rope_cos_tok = self.rope_sin_tok = None  # per-token rotary rows of a sectioned rope, created by bind_rope_streams()
@@ -253,6 +273,15 @@ class DecoderEngine:
         T = flags.numel()
         self.embed_flags[:T].copy_(flags, non_blocking=True)
         self.embed_rows[:T].copy_(rows, non_blocking=True)
+
+    def bind_carry(self, rows: torch.Tensor, positions: torch.Tensor) -> None:
+        """Stage the hidden-state carry of the next step of a multi-token-prediction layer: ``rows[T, hidden]`` (any
+        float dtype) and the step's positions (the embedding at absolute position 0 is zeroed)."""
+        if self.carry_in is None:
+            raise ValueError("this engine is not a multi-token-prediction layer")
+        T = rows.shape[0]
+        self.carry_in[:T].copy_(rows, non_blocking=True)
+        self.mtp_first[:T].copy_((positions[:T] == 0).to(torch.int32), non_blocking=True)
 
     def bind_rope_streams(self, streams: torch.Tensor) -> None:
         """Stage the rotary rows of the next step under a sectioned rope: ``streams[3, T]`` int32 are the (time, row,
@@ -489,6 +518,16 @@ class DecoderEngine:
             if w.embed_norm is not None:
                 self._count()
                 K.layernorm(h, w.embed_norm, w.embed_norm_b, cfg.norm_eps, out=h)
+            if cfg.mtp_head:
+                # h = eh_proj . [enorm(embedding of the token after the position, zero at position 0) ; hnorm(carry)],
+                # as two projections over the halves of eh_proj, the second accumulating onto the first
+                m = w.mtp
+                self._count(3)
+                K.replace_rows_(h, self.mtp_zero[:T], self.mtp_first[:T])
+                K.rmsnorm(h, m["enorm"], cfg.norm_eps, out=self.mtp_e[:T])
+                K.rmsnorm(self.carry_in[:T], m["hnorm"], cfg.norm_eps, out=self.mtp_c[:T])
+                self._linear(self.mtp_e[:T], m["we"], K.EPI_STORE, h)
+                self._linear(self.mtp_c[:T], m["wh"], K.EPI_RESID, h, h)
         pending = None
         lora = shape.lora and self.lora is not None
         post = cfg.block != "pre"           # a norm sits between each projection and its residual add
@@ -587,18 +626,32 @@ class DecoderEngine:
             if self.stage.first:                 # the driver's rank: wait for the last stage's sampled tokens
                 self.link.return_picked(self.picked[:B], self.logprobs[:B] if shape.logprobs else None)
             return
-        hl = self.hl[:B]
-        if B == T:
-            hl = h
-        else:
+        xl = self.xl[:B]
+        if self.carry:
+            # the closing norm runs over every token row (the carry), the logit rows are gathered from its output
             self._count()
-            K.gather_rows(h, self.logit_idx[:B], hl)
-        self._count()
-        if cfg.norm_kind == "layer":
-            K.layernorm(hl, w.final_norm, w.final_norm_b, cfg.norm_eps, out=self.xl[:B])
+            if cfg.norm_kind == "layer":
+                K.layernorm(h, w.final_norm, w.final_norm_b, cfg.norm_eps, out=self.carry_out[:T])
+            else:
+                K.rmsnorm(h, w.final_norm, cfg.norm_eps, out=self.carry_out[:T])
+            if B == T:
+                xl = self.carry_out[:T]
+            else:
+                self._count()
+                K.gather_rows(self.carry_out[:T], self.logit_idx[:B], xl)
         else:
-            K.rmsnorm(hl, w.final_norm, cfg.norm_eps, out=self.xl[:B])
-        self._linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits_local[:B])
+            hl = self.hl[:B]
+            if B == T:
+                hl = h
+            else:
+                self._count()
+                K.gather_rows(h, self.logit_idx[:B], hl)
+            self._count()
+            if cfg.norm_kind == "layer":
+                K.layernorm(hl, w.final_norm, w.final_norm_b, cfg.norm_eps, out=xl)
+            else:
+                K.rmsnorm(hl, w.final_norm, cfg.norm_eps, out=xl)
+        self._linear(xl, w.lm_head, K.EPI_F32, self.logits_local[:B])
         if cfg.final_softcap > 0:
             self._count()
             K.softcap_(self.logits_local[:B], cfg.final_softcap)

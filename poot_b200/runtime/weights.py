@@ -95,6 +95,9 @@ class DecoderWeights:
     final_norm_b: Optional[torch.Tensor] = None
     embed_norm: Optional[torch.Tensor] = None     # LayerNorm right after the embedding (bloom), with its bias
     embed_norm_b: Optional[torch.Tensor] = None
+    # a multi-token-prediction layer's input side: {"enorm", "hnorm"} norm weights and the two halves of its projection
+    # {"we": eh_proj[:, :H] over the token embedding, "wh": eh_proj[:, H:] over the hidden-state carry}
+    mtp: Optional[Dict[str, torch.Tensor]] = None
 
     @property
     def layer0(self) -> int:
@@ -187,6 +190,20 @@ def fuse_qkv(wq: torch.Tensor, wk: torch.Tensor, wv: torch.Tensor, cfg: DecoderC
     return torch.cat([q, k, v], dim=0).contiguous()
 
 
+def mtp_input_weights(enorm: torch.Tensor, hnorm: torch.Tensor, eh_proj: torch.Tensor) -> Dict[str, torch.Tensor]:
+    """The input side of a multi-token-prediction layer in the engine's layout: ``eh_proj[H, 2H]`` multiplies
+    ``[enorm(embedding) ; hnorm(carry)]``; it is kept as its two halves so the concatenation never materialises."""
+    H = eh_proj.shape[0]
+    return {"enorm": enorm.contiguous(), "hnorm": hnorm.contiguous(), "we": eh_proj[:, :H].contiguous(),
+            "wh": eh_proj[:, H:].contiguous()}
+
+
+def share_tables(layer: DecoderWeights, target: DecoderWeights) -> DecoderWeights:
+    """A multi-token-prediction layer embeds and un-embeds with the target's own tables (no second copy on the device)."""
+    layer.embed, layer.lm_head = target.embed, target.lm_head
+    return layer
+
+
 def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02, tp_rank: int = 0, tp_world: int = 1,
                    ep_rank: int = 0, ep_world: int = 1, dtype=torch.bfloat16, stage: Optional[StageSpec] = None) -> DecoderWeights:
     """Random-init weights ``~N(0, std)`` generated directly in the rank-local fused layouts.
@@ -250,9 +267,13 @@ def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02,
             lm_head = shard_rows(lm_head, tp_rank, tp_world)  # vocabulary-parallel head
     if not st.first:
         embed = None
-    return fold_scales(DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H) if st.last else None, lm_head=lm_head,
-                                      layers=layers, tp_rank=tp_rank, tp_world=tp_world, ep_rank=ep_rank, ep_world=ep_world,
-                                      stage=stage))
+    dw = DecoderWeights(cfg=cfg, embed=embed, final_norm=ones(H) if st.last else None, lm_head=lm_head,
+                        layers=layers, tp_rank=tp_rank, tp_world=tp_world, ep_rank=ep_rank, ep_world=ep_world,
+                        stage=stage)
+    if cfg.mtp_head:
+        eh = draw((H, 2 * H), 3)
+        dw.mtp = mtp_input_weights(ones(H), ones(H), eh)
+    return fold_scales(dw)
 
 
 def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], device, tp_rank: int = 0,
@@ -366,6 +387,8 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
         embed = None
     dw = DecoderWeights(cfg=cfg, embed=embed, final_norm=get("final_norm") if st.last else None,
                         lm_head=lm_head, layers=layers, tp_rank=tp_rank, tp_world=tp_world, stage=stage)
+    if cfg.mtp_head:
+        dw.mtp = mtp_input_weights(get("mtp.enorm"), get("mtp.hnorm"), get("mtp.eh_proj"))
     if cfg.norm_kind == "layer" and cfg.norm_bias and st.last:
         dw.final_norm_b = get("final_norm_bias")
     if cfg.embed_norm and st.first:

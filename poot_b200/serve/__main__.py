@@ -53,20 +53,40 @@ def main(argv=None) -> int:
                            heartbeat_timeout=cfg.rank_heartbeat_timeout_secs)
     if _is_encoder_checkpoint(cfg.model):
         return _serve_encoder(cfg)
+    from ..driver.features import Incompatible as _Inc, Unavailable as _Unav
+    mtp_k = cfg.draft_mtp
+    if mtp_k and (world > 1 or cfg.model == "fake" or cfg.lora or cfg.lora_slots):
+        print("poot-serve: --draft-mtp runs on the single-device engine, without adapters", file=sys.stderr)
+        return 2
+    try:
+        llm = _open_model(cfg, rank, world, pp, comm, mtp_k)
+    except (_Unav, _Inc) as e:
+        print(f"poot-serve: {e}", file=sys.stderr)
+        return 2
+    return _serve(cfg, llm, rank, world, pp, comm)
+
+
+def _open_model(cfg, rank: int, world: int, pp: int, comm, mtp_k: int):
+    from ..llm import LLM
     if cfg.model == "fake":
-        llm = LLM.fake(rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, prefill_budget=cfg.prefill_budget or None)
-    elif cfg.model.startswith("random:"):
-        llm = LLM.random(cfg.model.split(":", 1)[1], rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
-                         kv_fraction=cfg.kv_fraction, tp_rank=rank if pp == 1 else 0, tp_world=world if pp == 1 else 1,
-                         comm=comm, prefill_budget=cfg.prefill_budget or None, pp_rank=rank if pp > 1 else 0, pp_world=pp)
-    elif cfg.backend == "oracle":
-        llm = LLM.oracle(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, lora=cfg.lora,
-                         num_blocks=cfg.rows * ((cfg.max_seq + 15) // 16) + 8, prefill_budget=cfg.prefill_budget or None)
-    else:
-        llm = LLM.load(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
-                       kv_fraction=cfg.kv_fraction, tp_rank=rank if pp == 1 else 0, tp_world=world if pp == 1 else 1,
-                       comm=comm, lora=cfg.lora, prefill_budget=cfg.prefill_budget or None,
-                       pp_rank=rank if pp > 1 else 0, pp_world=pp)
+        return LLM.fake(rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, prefill_budget=cfg.prefill_budget or None)
+    if cfg.model.startswith("random:"):
+        return LLM.random(cfg.model.split(":", 1)[1], rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
+                          kv_fraction=cfg.kv_fraction, tp_rank=rank if pp == 1 else 0, tp_world=world if pp == 1 else 1,
+                          comm=comm, prefill_budget=cfg.prefill_budget or None, pp_rank=rank if pp > 1 else 0, pp_world=pp,
+                          draft_mtp=mtp_k)
+    if cfg.backend == "oracle":
+        return LLM.oracle(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, lora=cfg.lora,
+                          num_blocks=cfg.rows * ((cfg.max_seq + 15) // 16) + 8, prefill_budget=cfg.prefill_budget or None,
+                          draft_mtp=mtp_k)
+    return LLM.load(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk,
+                    kv_fraction=cfg.kv_fraction, tp_rank=rank if pp == 1 else 0, tp_world=world if pp == 1 else 1,
+                    comm=comm, lora=cfg.lora, prefill_budget=cfg.prefill_budget or None,
+                    pp_rank=rank if pp > 1 else 0, pp_world=pp, draft_mtp=mtp_k)
+
+
+def _serve(cfg, llm, rank: int, world: int, pp: int, comm) -> int:
+    from ..llm import LLM
     if cfg.lora_slots > 0:
         if world > 1 or llm.engine is None:
             print("poot-serve: --lora-slots needs the single-device engine", file=sys.stderr)
@@ -99,8 +119,7 @@ def main(argv=None) -> int:
         with open(cfg.chat_template_file) as f:
             template = f.read()
     from ..driver.features import Feature as _F, check as _check
-    if cfg.draft_mtp:
-        _check([_F.DRAFT_MTP])           # typed refusal: no registered family ships multi-token-prediction heads
+    draft = llm.draft                    # --draft-mtp: the model's own multi-token-prediction layer, attached at load
     if cfg.host_embedding:
         if world > 1 or llm.engine is None:
             print("poot-serve: --host-embedding needs the single-device engine", file=sys.stderr)
@@ -121,7 +140,6 @@ def main(argv=None) -> int:
         llm.engine.enable_expert_pool(cfg.expert_pool, ExpertResidency())
     if cfg.check_ranges and llm.cfg is not None:
         _prove_ranges(llm.cfg, cfg)
-    draft = None
     if cfg.draft_model:
         from ..driver.placement import Placement
         from ..driver.speculate import ModelDraft

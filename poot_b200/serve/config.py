@@ -24,7 +24,7 @@ class ServeConfig:
     chat_template_file: Optional[str] = None
     draft_lookup: Optional[str] = None   # NGRAM:K
     draft_model: Optional[str] = None    # PATH:K - a smaller checkpoint proposes K tokens per verify step
-    draft_mtp: int = 0                   # K tokens from the checkpoint's own multi-token-prediction heads (refused: no family ships them)
+    draft_mtp: int = 0                   # K tokens from the checkpoint's own multi-token-prediction heads (the checkpoint must store the layer)
     expert_pool: int = 0                 # > 0: resident experts per routed layer; the other experts stay in pinned host memory
     host_embedding: bool = False         # keep the token-embedding table in host memory; a step copies the rows it gathers
     check_ranges: bool = False           # prove every index of the step graphs in range before serving

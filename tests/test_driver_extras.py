@@ -26,8 +26,11 @@ def test_feature_table():
     check([Feature.RECURRENT_STATE, Feature.DRAFT_LOOKUP])       # the round snapshots and restores the state rows
     with pytest.raises(Incompatible):
         check([Feature.ADAPTERS, Feature.TENSOR_PLACEMENT])
+    check([Feature.DRAFT_MTP])                   # offered; a model without the layer is refused where the model is known
     with pytest.raises(Unavailable):
-        check([Feature.DRAFT_MTP])
+        from poot_b200.driver.features import require_mtp
+        from poot_b200.models.config import tiny_llama
+        require_mtp(tiny_llama())
     check([Feature.EXPERT_POOL, Feature.PREFIX_CACHE])
     with pytest.raises(Incompatible):
         check([Feature.EXPERT_POOL, Feature.EXPERT_PLACEMENT])

@@ -330,8 +330,11 @@ def test_flags_for_draft_policies_pools_and_range_checks():
                 ["m", "--timing-sample-every", "0"]):
         with pytest.raises(ValueError):
             parse_args(bad)
-    with pytest.raises(Unavailable):                             # accepted by the parser, refused typed at startup
-        check([Feature.DRAFT_MTP])
+    with pytest.raises(Unavailable):                             # accepted by the parser, refused typed where the model is known
+        from poot_b200.driver.features import require_mtp
+        require_mtp(tiny_llama())
+    from poot_b200.serve.__main__ import main as serve_main
+    assert serve_main(["random:tiny-llama", "127.0.0.1:0", "--draft-mtp", "2", "--backend", "oracle"]) == 2
     assert parse_args(["m", "--expert-pool", "6", "--host-embedding"]).expert_pool == 6
     check([Feature.EXPERT_POOL])                                 # pooled experts are served (single-device engine)
     c = tiny_llama()
