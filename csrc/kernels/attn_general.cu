@@ -2,7 +2,8 @@
 // not be equal), causal window, score soft cap, per-head ALiBi slopes, per-head sink logits.  It serves the shapes the
 // tuned kernels do not (head_dim 256, split key / value widths): one CTA of four warps per (query row, head); the warps
 // take every fourth key and keep online-softmax partials that are merged through shared memory.  Correctness path, not
-// a fast one: no split over the keys across CTAs, no tensor cores.
+// a fast one: no split over the keys across CTAs, no tensor cores.  With a selection list (the output of the sparse
+// attention indexer) a row attends to the listed key positions only.
 //
 // K / V pools are [blocks, kv heads, 16, pool_d]; a row holds the key (Dk used) or the value (Dv used).
 #include "common.cuh"
@@ -18,7 +19,7 @@ attn_general_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
                     const __nv_bfloat16* __restrict__ vpool, int pool_d, const int* __restrict__ block_tables, int max_blocks,
                     const int* __restrict__ row_seq, const int* __restrict__ row_ctx, __nv_bfloat16* __restrict__ out,
                     int out_stride, int Hq, int Hkv, int Dk, int Dv, float scale, float softcap, int window,
-                    const float* __restrict__ alibi, const float* __restrict__ sinks) {
+                    const float* __restrict__ alibi, const float* __restrict__ sinks, const int* __restrict__ sel, int sel_k) {
   __shared__ float sm_m[AG_WARPS], sm_l[AG_WARPS];
   __shared__ float sm_o[AG_WARPS][AG_MAXD];
   pdl_wait(); pdl_launch();
@@ -38,7 +39,11 @@ attn_general_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
   }
   const float slope = alibi ? alibi[h] : 0.f;
   float m = -FLT_MAX, l = 0.f;
-  for (int j = first + w; j < ctx; j += AG_WARPS) {
+  // with a selection list the row attends to the listed positions only (ascending, -1 after the last kept)
+  const int n_iter = sel ? sel_k : ctx - first;
+  for (int it = w; it < n_iter; it += AG_WARPS) {
+    const int j = sel ? sel[(size_t)r * sel_k + it] : first + it;
+    if (j < 0 || j >= ctx) continue;
     int blk = block_tables[(size_t)seq * max_blocks + (j >> 4)];
     if (!POOT_IN_RANGE(j >> 4, max_blocks, kSitePosition) || !POOT_IN_RANGE(blk, POOT_LIMIT(kLimPoolBlocks), kSiteBlockId)) blk = 0;
     const size_t base = (((size_t)blk * Hkv + kvh) * 16 + (j & 15)) * pool_d;
@@ -89,11 +94,12 @@ using namespace poot;
 POOT_API int poot_attn_general(const void* q, int q_stride, const void* kpool, const void* vpool, int pool_d,
                                const int* block_tables, int max_blocks, const int* row_seq, const int* row_ctx, void* out,
                                int out_stride, int R, int Hq, int Hkv, int Dk, int Dv, float scale, float softcap, int window,
-                               const float* alibi, const float* sinks, cudaStream_t s) {
+                               const float* alibi, const float* sinks, const int* sel, int sel_k, cudaStream_t s) {
   if (R == 0) return 0;
   if (Dk % 32 || Dv % 32 || Dk < 32 || Dv < 32 || Dk > AG_MAXD || Dv > AG_MAXD || pool_d < Dk || pool_d < Dv || Hkv < 1 || Hq % Hkv)
     return (int)cudaErrorInvalidValue;
+  if (sel != nullptr && sel_k < 1) return (int)cudaErrorInvalidValue;
   return launch_k(attn_general_kernel, dim3(R, Hq), dim3(AG_WARPS * 32), 0, s, (const __nv_bfloat16*)q, q_stride,
                   (const __nv_bfloat16*)kpool, (const __nv_bfloat16*)vpool, pool_d, block_tables, max_blocks, row_seq, row_ctx,
-                  (__nv_bfloat16*)out, out_stride, Hq, Hkv, Dk, Dv, scale, softcap, window, alibi, sinks);
+                  (__nv_bfloat16*)out, out_stride, Hq, Hkv, Dk, Dv, scale, softcap, window, alibi, sinks, sel, sel_k);
 }

@@ -37,7 +37,8 @@ class ServingShapes:
 
 def kv_bytes_per_block(cfg: DecoderConfig, tp_world: int = 1, kv_itemsize: int = 2) -> int:
     hkv = max(cfg.n_kv_heads // tp_world, 1)
-    return cfg.n_layers * 2 * hkv * BLOCK * cfg.head_dim * kv_itemsize
+    index = cfg.n_layers * BLOCK * cfg.index_head_dim * 2 if cfg.index_topk else 0    # the sparse indexer's own key pool
+    return cfg.n_layers * 2 * hkv * BLOCK * cfg.head_dim * kv_itemsize + index
 
 
 def plan_bytes(cfg: DecoderConfig, rows: int, max_seq: int, prefill_chunk: int, num_blocks: int, tp_world: int = 1,

@@ -285,6 +285,8 @@ class DeviceStepEngine:
     def copy_block(self, src: int, dst: int) -> None:
         """Copy one K/V block in every layer (a forked sequence gets its own copy of the partial last block)."""
         self.e.kv.buf[:, :, dst].copy_(self.e.kv.buf[:, :, src])
+        if getattr(self.e, "idx_pool", None) is not None:        # the sparse indexer's keys of the block travel with it
+            self.e.idx_pool[:, dst].copy_(self.e.idx_pool[:, src])
 
 
 class OracleStepEngine:

@@ -187,7 +187,8 @@ class DecoderConfig:
         """Features of this configuration that the device program does not implement (empty = runs on the device);
         the CPU oracle evaluates all of them."""
         g = []
-        if self.index_topk: g.append("sparse attention indexer")
+        if self.index_topk and (self.index_n_heads > 64 or self.index_head_dim > 256 or self.index_head_dim < self.qk_rope_dim):
+            g.append("sparse attention indexer beyond 64 heads of width 256")
         if self.norm_kind != "rms" and self.block != "pre": g.append("LayerNorm with a post norm")
         if self.block != "pre" and self.is_moe: g.append(f"{self.block}-norm block with routed experts")
         if self.gated_ffn and self.act not in ("silu", "gelu_tanh", "gelu_erf"): g.append(f"{self.act} gated FFN")

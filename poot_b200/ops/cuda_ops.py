@@ -51,7 +51,11 @@ _SIGS = {
                         c_float, c_int, c_int, _P],
     "poot_mla_qkv_write": [_P, _P, _P, c_int, c_int, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "poot_attn_general": [_P, c_int, _P, _P, c_int, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                          c_float, c_int, _P, _P, _P],
+                          c_float, c_int, _P, _P, _P, c_int, _P],
+    "poot_index_k_write": [_P, _P, _P, c_float, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, _P],
+    "poot_index_q_rope": [_P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "poot_index_scores": [_P, _P, c_int, _P, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P],
+    "poot_index_select": [_P, c_int, _P, _P, c_int, c_int, _P],
     "poot_attn_flash_prefill": [_P, c_int, c_int, _P, _P, c_longlong, _P, c_int, _P, c_int, _P, c_int, c_int, c_int,
                                 c_float, c_int, _P, _P],
     "poot_decode_advance": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, _P],
@@ -637,17 +641,69 @@ def mla_qkv_write(q: torch.Tensor, kvb: torch.Tensor, kva: torch.Tensor, rope_co
 def attn_general(q: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_tables: torch.Tensor,
                  row_seq: Optional[torch.Tensor], row_ctx: torch.Tensor, Hq: int, Hkv: int, Dk: int, Dv: int, scale: float,
                  out: torch.Tensor, softcap: float = 0.0, window: int = 0, alibi: Optional[torch.Tensor] = None,
-                 sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 sinks: Optional[torch.Tensor] = None, sel: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Paged attention for the shapes the tuned kernels do not serve: key width ``Dk`` and value width ``Dv`` (multiples of
-    32 up to 512), optional per-head ALiBi slopes and sink logits (fp32 ``[Hq]``).  Pools are ``[blocks, Hkv, 16, pool_d]``."""
+    32 up to 512), optional per-head ALiBi slopes and sink logits (fp32 ``[Hq]``).  Pools are ``[blocks, Hkv, 16, pool_d]``.
+    ``sel[rows, k]`` int32 (ascending key positions, -1 after the last) restricts each row to the listed keys."""
     _need_cuda(q, kpool, vpool)
+    if sel is not None:
+        assert sel.dtype == torch.int32 and sel.is_contiguous() and sel.shape[0] >= q.shape[0]
     assert q.dtype == torch.bfloat16 and q.stride(1) == 1 and kpool.is_contiguous() and vpool.is_contiguous()
     assert kpool.shape == vpool.shape and block_tables.dtype == torch.int32 and row_ctx.dtype == torch.int32
     check(_fn("poot_attn_general")(_ptr(q), q.stride(0), _ptr(kpool), _ptr(vpool), kpool.shape[-1], _ptr(block_tables),
                                    block_tables.shape[1], _ptr(row_seq), _ptr(row_ctx), _ptr(out), out.stride(0), q.shape[0], Hq,
-                                   Hkv, Dk, Dv, float(scale), float(softcap), int(window), _ptr(alibi), _ptr(sinks), _stream()),
+                                   Hkv, Dk, Dv, float(scale), float(softcap), int(window), _ptr(alibi), _ptr(sinks), _ptr(sel),
+                                   sel.shape[1] if sel is not None else 0, _stream()),
           "attn_general")
     return out
+
+
+# ---- sparse attention indexer ---------------------------------------------------------------------------------------
+def index_k_write(kraw: torch.Tensor, norm_w: torch.Tensor, norm_b: Optional[torch.Tensor], eps: float,
+                  positions: torch.Tensor, slots: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, pool: torch.Tensor,
+                  dr: int) -> None:
+    """Indexer keys of a step: ``LayerNorm(kraw)`` with the rotary on the leading ``dr`` channels (half-split), written
+    to ``pool[blocks, 16, Di]`` at the tokens' slots."""
+    _need_cuda(kraw, pool)
+    T, Di = kraw.shape
+    assert kraw.dtype == torch.bfloat16 and kraw.is_contiguous() and pool.is_contiguous() and pool.shape[-1] == Di
+    assert cos.dtype == torch.float32 and (dr == 0 or cos.shape[1] == dr // 2)
+    check(_fn("poot_index_k_write")(_ptr(kraw), _ptr(norm_w), _ptr(norm_b), float(eps), _ptr(positions), _ptr(slots), _ptr(cos),
+                                    _ptr(sin), _ptr(pool), T, Di, dr, cos.shape[0], _stream()), "index_k_write")
+
+
+def index_q_rope(q: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, ni: int, Di: int,
+                 dr: int) -> torch.Tensor:
+    """The rotary on the leading ``dr`` channels of each indexer query head, in place: ``q[T, ni * Di]``."""
+    _need_cuda(q)
+    assert q.dtype == torch.bfloat16 and q.is_contiguous() and q.shape[1] == ni * Di
+    check(_fn("poot_index_q_rope")(_ptr(q), _ptr(positions), _ptr(cos), _ptr(sin), q.shape[0], ni, Di, dr, cos.shape[0],
+                                   _stream()), "index_q_rope")
+    return q
+
+
+def index_scores(q: torch.Tensor, w: torch.Tensor, pool: torch.Tensor, block_tables: torch.Tensor,
+                 row_seq: Optional[torch.Tensor], row_ctx: torch.Tensor, scores: torch.Tensor, ni: int, Di: int,
+                 max_ctx: int, scale: float) -> torch.Tensor:
+    """``scores[r, j] = sum_h w[r, h] * relu(q[r, h] . key[j] * scale)`` for every visible key ``j < row_ctx[r]``;
+    entries at and beyond a row's context are left as they were.  ``w`` is f32 ``[rows, >= ni]``."""
+    _need_cuda(q, w, pool, scores)
+    assert q.dtype == torch.bfloat16 and q.is_contiguous() and w.dtype == torch.float32 and w.stride(1) == 1
+    assert scores.dtype == torch.float32 and scores.stride(1) == 1 and scores.shape[1] >= max_ctx
+    check(_fn("poot_index_scores")(_ptr(q), _ptr(w), w.stride(0), _ptr(pool), _ptr(block_tables), block_tables.shape[1],
+                                   _ptr(row_seq), _ptr(row_ctx), _ptr(scores), scores.stride(0), q.shape[0], ni, Di,
+                                   int(max_ctx), float(scale), _stream()), "index_scores")
+    return scores
+
+
+def index_select(scores: torch.Tensor, row_ctx: torch.Tensor, sel: torch.Tensor) -> torch.Tensor:
+    """Per row the ``sel.shape[1]`` best of its ``row_ctx[r]`` scores (ties at the cut: lowest position first), as
+    ascending positions with -1 after the last kept; a row with no more scores than that keeps them all."""
+    _need_cuda(scores, sel)
+    assert scores.dtype == torch.float32 and sel.dtype == torch.int32 and sel.is_contiguous()
+    check(_fn("poot_index_select")(_ptr(scores), scores.stride(0), _ptr(row_ctx), _ptr(sel), sel.shape[0], sel.shape[1],
+                                   _stream()), "index_select")
+    return sel
 
 
 FLASH_MIN_TOKENS = 16      # prefill pieces at least this long go to the tensor-core kernel

@@ -183,6 +183,16 @@ class DecoderEngine:
             self.mla_kva = torch.zeros(T, cfg.kv_lora_rank + cfg.qk_rope_dim, dtype=bf, device=dev)
             self.mla_ckv = torch.zeros(T, cfg.kv_lora_rank, dtype=bf, device=dev)
             self.mla_kvb = torch.zeros(T, cfg.n_heads * (cfg.qk_nope_dim + cfg.v_head_dim), dtype=bf, device=dev)
+            if cfg.index_topk:
+                # sparse attention indexer: its own key pool per attention layer, the step's indexer queries, raw keys and
+                # head weights, one score per (row, visible position) and the kept positions of every row
+                ni, Di = cfg.index_n_heads, cfg.index_head_dim
+                self.idx_pool = torch.zeros(max(len(self._kv_of), 1), num_blocks, 16, Di, dtype=bf, device=dev)
+                self.idx_q = torch.zeros(T, ni * Di, dtype=bf, device=dev)
+                self.idx_kraw = torch.zeros(T, Di, dtype=bf, device=dev)
+                self.idx_w = torch.zeros(T, (ni + 7) // 8 * 8, dtype=torch.float32, device=dev)
+                self.idx_scores = torch.zeros(T, max_blocks_per_seq * 16, dtype=torch.float32, device=dev)
+                self.idx_sel = torch.full((T, cfg.index_topk), -1, dtype=i32, device=dev)
         self._gdn_of = {i: n for n, i in enumerate(i for i, k in enumerate(kinds) if k == "gdn")}
         if self._gdn_of:
             nk, nv, Dg, Kc = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.gdn_conv
@@ -730,9 +740,27 @@ class DecoderEngine:
         K.mla_qkv_write(q, kvb, kva, cfg.kv_lora_rank, self.mla_q[:T], self.kv.k(kvl), self.kv.v(kvl), self.positions[:T],
                         self.slots[:T], self.cos, self.sin, nh, dn, dr, dv)
         attn = self.attn[:T, :nh * dv]
+        sel = self._index_select(kvl, m, x, qa, T) if cfg.index_topk else None
         K.attn_general(self.mla_q[:T], self.kv.k(kvl), self.kv.v(kvl), self.block_tables, self.row_seq[:T], self.row_ctx[:T],
-                       nh, nh, dn + dr, dv, self.scale, attn, window=cfg.window_of(self.w.layer0 + l))
+                       nh, nh, dn + dr, dv, self.scale, attn, window=cfg.window_of(self.w.layer0 + l), sel=sel)
         return self._proj_to_residual(attn, L.wo, T)
+
+    def _index_select(self, kvl: int, m, x, qa, T: int):
+        """Sparse attention indexer (components/dsa.rs): score every visible key of every row with the light multi-head
+        scorer over the layer's index pool and keep each row's ``index_topk`` best; the result is the selection list
+        the attention kernel walks."""
+        cfg = self.cfg
+        ni, Di, dr = cfg.index_n_heads, cfg.index_head_dim, cfg.qk_rope_dim
+        iq = self._linear(qa, m["idx_q"], K.EPI_STORE, self.idx_q[:T])
+        kraw = self._linear(x, m["idx_k"], K.EPI_STORE, self.idx_kraw[:T])
+        w = self._linear(x, m["idx_w"], K.EPI_F32, self.idx_w[:T])
+        self._count(4)
+        K.index_q_rope(iq, self.positions[:T], self.cos, self.sin, ni, Di, dr)
+        K.index_k_write(kraw, m["idx_k_norm"], m["idx_k_norm_bias"], 1e-6, self.positions[:T], self.slots[:T], self.cos,
+                        self.sin, self.idx_pool[kvl], dr)
+        K.index_scores(iq, w, self.idx_pool[kvl], self.block_tables, self.row_seq[:T], self.row_ctx[:T], self.idx_scores[:T],
+                       ni, Di, self.idx_scores.shape[1], Di ** -0.5)
+        return K.index_select(self.idx_scores[:T], self.row_ctx[:T], self.idx_sel[:T])
 
     def _gdn_mixer(self, l: int, L, x, T: int):
         """Gated delta net layer (components/gdn.rs): one GEMM for q | k | v | z | b | a, causal conv + SiLU over

@@ -315,6 +315,16 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
                 m.update({"q_a": get(p + "attn_q_a"), "q_a_norm": get(p + "attn_q_a_norm"), "q_b": get(p + "attn_q_b")})
             else:
                 m["q"] = get(p + "attn_q")
+            if cfg.index_topk:
+                # sparse attention indexer: its query heads read the low-rank query, its key and head weights the layer
+                # input; the head-weight rows carry the 1/sqrt(heads) factor and are padded to a multiple of 8 rows
+                ni = cfg.index_n_heads
+                wts = tensors[p + "idx_weights"].to(device=dev, dtype=torch.float32) * (ni ** -0.5)
+                pad = (-ni) % 8
+                if pad:
+                    wts = torch.cat([wts, torch.zeros(pad, wts.shape[1], dtype=torch.float32, device=dev)], 0)
+                m.update({"idx_q": get(p + "idx_q"), "idx_k": get(p + "idx_k"), "idx_k_norm": get(p + "idx_k_norm"),
+                          "idx_k_norm_bias": get(p + "idx_k_norm_bias"), "idx_w": wts.to(dtype).contiguous()})
             L = LayerWeights(ln1=get(p + "attn_norm"), ln2=get(p + "ffn_norm"), wqkv=m["kv_a"], wo=get(p + "attn_o"), kind="mla", mla=m)
         else:
             wqkv = fuse_qkv(get(p + "attn_q"), get(p + "attn_k"), get(p + "attn_v"), cfg, tp_rank, tp_world)

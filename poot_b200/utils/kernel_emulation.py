@@ -362,7 +362,7 @@ def mla_qkv_write(q, kvb, kva, rope_col, q_out, kpool, vpool, positions, slots, 
 
 
 def attn_general(q, kpool, vpool, block_tables, row_seq, row_ctx, Hq, Hkv, Dk, Dv, scale, out, softcap=0.0, window=0,
-                 alibi=None, sinks=None):
+                 alibi=None, sinks=None, sel=None):
     rep = Hq // Hkv
     for r in range(q.shape[0]):
         ctx = int(row_ctx[r])
@@ -371,6 +371,9 @@ def attn_general(q, kpool, vpool, block_tables, row_seq, row_ctx, Hq, Hkv, Dk, D
         seq = int(row_seq[r]) if row_seq is not None else r
         first = ctx - window if (window > 0 and ctx > window) else 0
         pos = torch.arange(first, ctx)
+        if sel is not None:
+            pos = sel[r].long()
+            pos = pos[(pos >= 0) & (pos < ctx)]
         blk = block_tables[seq][(pos // K.KV_BLOCK).long()].long()
         kk = kpool[blk, :, (pos % K.KV_BLOCK).long()][..., :Dk].float().repeat_interleave(rep, 1)     # [S, Hq, Dk]
         vv = vpool[blk, :, (pos % K.KV_BLOCK).long()][..., :Dv].float().repeat_interleave(rep, 1)
@@ -386,6 +389,68 @@ def attn_general(q, kpool, vpool, block_tables, row_seq, row_ctx, Hq, Hkv, Dk, D
             p = torch.softmax(s, -1)
         out[r, :Hq * Dv] = _bf(torch.einsum("hs,shd->hd", p, vv).reshape(-1))
     return out
+
+
+def _half_rope(x, cos_row, sin_row, dr):
+    """Half-split rotary on the leading ``dr`` channels of the last axis."""
+    half = dr // 2
+    x1, x2 = x[..., :half], x[..., half:dr]
+    return torch.cat([x1 * cos_row - x2 * sin_row, x2 * cos_row + x1 * sin_row, x[..., dr:]], -1)
+
+
+def index_k_write(kraw, norm_w, norm_b, eps, positions, slots, cos, sin, pool, dr):
+    T, Di = kraw.shape
+    x = kraw.float()
+    mean = x.mean(-1, keepdim=True)
+    var = ((x - mean) ** 2).mean(-1, keepdim=True)
+    y = (x - mean) * torch.rsqrt(var + eps) * norm_w.float() + (norm_b.float() if norm_b is not None else 0.0)
+    y = _bf(y).float()                                      # the kernel rounds the normalised row before rotating it
+    flat = pool.view(-1, Di)
+    for t in range(T):
+        slot = int(slots[t])
+        if slot < 0:
+            continue
+        p = min(max(int(positions[t]), 0), cos.shape[0] - 1)
+        flat[slot] = _bf(_half_rope(y[t], cos[p], sin[p], dr)) if dr else _bf(y[t])
+
+
+def index_q_rope(q, positions, cos, sin, ni, Di, dr):
+    if dr == 0:
+        return q
+    T = q.shape[0]
+    p = positions[:T].long().clamp(0, cos.shape[0] - 1)
+    x = q.view(T, ni, Di).float()
+    q.copy_(_bf(_half_rope(x, cos[p][:, None, :], sin[p][:, None, :], dr)).view(T, ni * Di))
+    return q
+
+
+def index_scores(q, w, pool, block_tables, row_seq, row_ctx, scores, ni, Di, max_ctx, scale):
+    flat = pool.view(-1, Di)
+    for r in range(q.shape[0]):
+        ctx = int(row_ctx[r])
+        if ctx <= 0:
+            continue
+        seq = int(row_seq[r]) if row_seq is not None else r
+        pos = torch.arange(ctx)
+        keys = flat[block_tables[seq][(pos // K.KV_BLOCK).long()].long() * K.KV_BLOCK + pos % K.KV_BLOCK].float()   # [ctx, Di]
+        dots = torch.relu(q[r].view(ni, Di).float() @ keys.T * scale)                                                # [ni, ctx]
+        scores[r, :ctx] = (w[r, :ni].float()[:, None] * dots).sum(0)
+    return scores
+
+
+def index_select(scores, row_ctx, sel):
+    k = sel.shape[1]
+    sel.fill_(-1)
+    for r in range(sel.shape[0]):
+        n = max(int(row_ctx[r]), 0)
+        if n <= k:
+            sel[r, :n] = torch.arange(n, dtype=sel.dtype)
+            continue
+        s = scores[r, :n].float().clone()
+        s[torch.isnan(s) | (s == float("-inf"))] = torch.finfo(torch.float32).min
+        order = torch.sort(s, descending=True, stable=True).indices[:k]        # ties: lowest position first
+        sel[r] = torch.sort(order).values.to(sel.dtype)
+    return sel
 
 
 def attn_flash_prefill(q, kpool, vpool, block_tables, tiles, Hq, Hkv, scale, out, window=0):
@@ -617,6 +682,8 @@ def emulated_kernels():
                 bias_add_=bias_add_, bias_add_indexed_=bias_add_indexed_, scale_=scale_, gather_rows=gather_rows,
                 sigmoid_gate_rows_=sigmoid_gate_rows_,
                 linear=linear, gemm=gemm, gemm_skinny=gemm_skinny, gemv=gemv, rope_kv_write=rope_kv_write,
+                index_k_write=index_k_write, index_q_rope=index_q_rope, index_scores=index_scores,
+                index_select=index_select,
                 attn_paged=attn_paged, attn_general=attn_general, mla_qkv_write=mla_qkv_write, attn_flash_prefill=attn_flash_prefill, argmax_scratch=argmax_scratch,
                 argmax=argmax, argmax_partials=argmax_partials, argmax_combine=argmax_combine,
                 sample_gumbel=sample_gumbel, decode_advance=decode_advance,

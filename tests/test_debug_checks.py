@@ -50,8 +50,7 @@ def test_checked_library_registers_every_translation_unit():
     from poot_b200 import build
     lib_dir = build.LIB_DIR
     dbg = lib_dir / "libpoot_kernels_dbg.so"
-    if not dbg.exists():
-        build.build_kernels_checked()
+    build.build_kernels_checked()            # rebuilds only what is older than its sources
     checked, release = ctypes.CDLL(str(dbg)), ctypes.CDLL(str(lib_dir / "libpoot_kernels.so"))
     assert checked.poot_debug_bounds_enabled() == 1 and release.poot_debug_bounds_enabled() == 0
     n_units = len(list((build.CSRC / "kernels").glob("*.cu")))

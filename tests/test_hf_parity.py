@@ -339,6 +339,10 @@ DEVICE_CASES = {
     "bloom": dict(hidden_size=128, n_head=4),
     "mpt": dict(d_model=128, n_heads=4),
     "deepseek3": dict(hidden_size=128, qk_rope_head_dim=32, qk_nope_head_dim=32, v_head_dim=32, head_dim=32),
+    # latent attention behind the sparse indexer on the device program: index keys in their own paged pool, scores over the
+    # visible keys, exact top-k selection, attention over the kept positions only
+    "glm_moe_dsa": dict(hidden_size=128, qk_rope_head_dim=32, qk_nope_head_dim=32, v_head_dim=32, head_dim=32,
+                        kv_lora_rank=32, index_head_dim=32),
     "nemotron_h": dict(head_dim=32, hidden_size=128, mamba_head_dim=32),
     "qwen3next": dict(head_dim=32, hidden_size=128, linear_key_head_dim=64, linear_value_head_dim=64,
                       rope_parameters={"rope_theta": 10000.0, "partial_rotary_factor": 0.5, "rope_type": "default"}),
@@ -370,3 +374,44 @@ def test_checkpoint_through_the_device_loader_and_emulated_engine_follows_huggin
             break
         agree += 1
     assert agree >= 2, (got, want)
+
+
+def test_sparse_indexer_on_the_device_program_keeps_the_positions_hugging_face_keeps(tmp_path):
+    """First layer of the sparse-attention family through the engine's kernel program (host restatements): the
+    positions the indexer keeps for each of 16 prompt rows are exactly the ones ``transformers``' indexer keeps (deeper
+    layers see bf16-rounded inputs, where a near-tie at the cut may fall the other way)."""
+    from poot_b200 import LLM, SamplingParams
+    from poot_b200.utils import kernel_emulation as emu
+    m, vocab = build({**CASES["glm_moe_dsa"], **DEVICE_CASES["glm_moe_dsa"]})
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    p = torch.randint(3, vocab, (1, 16), generator=torch.Generator().manual_seed(4))
+    kept = {}
+    indexer = m.model.layers[0].self_attn.indexer
+    forward = indexer.forward
+
+    def spy_hf(*a, **k):
+        kept["hf"] = forward(*a, **k)
+        return kept["hf"]
+
+    indexer.forward = spy_hf
+    with torch.no_grad():
+        m(p)
+    select = emu.index_select
+
+    def spy_device(scores, row_ctx, sel):
+        out = select(scores, row_ctx, sel)
+        kept.setdefault("device", sel.clone())
+        return out
+
+    emu.index_select = spy_device
+    try:
+        with emu.emulated_kernels():
+            llm = LLM.load(str(tmp_path), device="cpu", rows=1, max_seq=64, prefill_chunk=16, num_blocks=8)
+            sid = llm.driver.open(p[0].tolist(), SamplingParams(max_tokens=2, temperature=0.0, ignore_eos=True))
+            llm.driver.step([sid])
+    finally:
+        emu.index_select = select
+    for t in range(16):
+        want = sorted(x for x in kept["hf"][0, t].tolist() if 0 <= x <= t)
+        got = [x for x in kept["device"][t].tolist() if x >= 0]
+        assert got == want, (t, got, want)
