@@ -13,6 +13,7 @@
 //    crates/poot-graph-plan/src/passes/group_expert_rows.rs:1-8, crates/poot-kernelgen/src/contraction/indexed.rs:1-6).
 //    With an expert-parallel shard (experts [e0, e0 + e_local) on this rank) rows routed elsewhere are left out.
 #include "common.cuh"
+#include "tp_common.cuh"
 #include <float.h>
 
 namespace poot {
@@ -223,6 +224,35 @@ __global__ void moe_scatter_combine_kernel(const __nv_bfloat16* h, const __nv_bf
   }
 }
 
+// Expert-parallel combine for decode-sized steps, fused with the one-shot all-reduce: this rank's share of every token
+// (the gate-scaled outputs of its own experts, summed in slot order; zero for a token none of them serves) is written
+// straight into every rank's inbox slot for this rank, then the reduce-scatter channel is signalled.  The consumer is
+// the same reduce + norm kernel that follows a row-parallel GEMM.  One CTA per token row; every CTA signals.
+__global__ void moe_scatter_combine_push_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pos, int T, int H,
+                                                int k, TpArgs tp, int* status) {
+  pdl_wait(); pdl_launch();
+  const int t = blockIdx.x;
+  const uint32_t target = tp_target(tp, tp.rs_site, tp.rs_sites);
+  const int parity = (int)(target & 1u);
+  const size_t row = ((size_t)((parity * tp.world + tp.rank) * tp.S + t)) * tp.ld_inbox;
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      const int p = pos[(size_t)t * k + j];
+      if (p < 0) continue;
+      float f[8];
+      unpack8(reinterpret_cast<const uint4*>(y + (size_t)p * H)[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    const uint4 pk = pack8(acc);
+    for (int d = 0; d < tp.world; ++d) *reinterpret_cast<uint4*>(tp.inbox_peer[d] + row + (size_t)c * 8) = pk;
+  }
+  tp_signal_all(tp, TP_CH_RS, target, gridDim.x, status);
+}
+
 }  // namespace poot
 
 using namespace poot;
@@ -278,4 +308,23 @@ POOT_API int poot_moe_combine(const void* h, const void* parts, void* out, int T
   if (H % 8) return (int)cudaErrorInvalidValue;
   return launch_k(moe_combine_kernel, dim3(T), dim3(256), 0, s, (const __nv_bfloat16*)h, (const __nv_bfloat16*)parts,
                   (__nv_bfloat16*)out, T, H, groups, gstride, per_token);
+}
+
+// Combine + one-shot push (see moe_scatter_combine_push_kernel).  slot_rows: rows of one inbox slot; T <= slot_rows.
+POOT_API int poot_moe_scatter_combine_push(const void* y, const int* pos, int T, int H, int k, int tp_world, int tp_rank,
+                                           int slot_rows, int rs_site, int rs_sites, const int* epoch, void* flags_local,
+                                           void* const* flags_peer, void* const* inbox_peer, int ld_inbox, int* ticket,
+                                           int* status, cudaStream_t s) {
+  if (T <= 0) return (int)cudaErrorInvalidValue;      // every rank must signal: an empty step has no push to skip
+  if (H % 8 || ld_inbox % 8 || ld_inbox < H || k < 1 || T > slot_rows) return (int)cudaErrorInvalidValue;
+  if (tp_world < 2 || tp_world > TP_MAX_WORLD || tp_rank < 0 || tp_rank >= tp_world || rs_site < 0 || status == nullptr)
+    return (int)cudaErrorInvalidValue;
+  TpArgs tp = {};
+  tp.world = tp_world; tp.rank = tp_rank; tp.S = slot_rows; tp.oneshot = 1; tp.ag_site = -1; tp.rs_site = rs_site;
+  tp.rs_sites = rs_sites; tp.ld_inbox = ld_inbox; tp.epoch = epoch; tp.flags_local = (uint32_t*)flags_local; tp.ticket = ticket;
+  for (int r = 0; r < tp_world; ++r) {
+    tp.flags_peer[r] = (uint32_t*)flags_peer[r];
+    tp.inbox_peer[r] = (__nv_bfloat16*)inbox_peer[r];
+  }
+  return launch_k(moe_scatter_combine_push_kernel, dim3(T), dim3(256), 0, s, (const __nv_bfloat16*)y, pos, T, H, k, tp, status);
 }

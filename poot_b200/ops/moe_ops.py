@@ -100,6 +100,19 @@ def moe_combine(h: Optional[torch.Tensor], parts: torch.Tensor, out: torch.Tenso
                                    gstride, per_token, K._stream()), "moe_combine")
 
 
+def moe_scatter_combine_push(y: torch.Tensor, pos: torch.Tensor, T: int, H: int, k: int, tp) -> None:
+    """The expert-parallel combine of a decode-sized step fused with the one-shot all-reduce: this rank's share of every
+    token goes straight into every rank's inbox; ``tp = (comm, rs_site)``.  The next reduce + norm kernel consumes it."""
+    comm, rs_site = tp
+    b = comm.block
+    K.register_signature("poot_moe_scatter_combine_push", [_P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                           _P, _P, _P, _P, c_int, _P, _P, _P])
+    check(K.fn("poot_moe_scatter_combine_push")(
+        y.data_ptr(), pos.data_ptr(), T, H, k, comm.world, comm.rank, comm.MAX_ROWS, rs_site, comm.rs_sites,
+        comm.epoch.data_ptr(), b.ptr(comm.rank, comm.off_flags), comm.flags_peer, comm.inbox_peer, comm.H,
+        comm.ticket.data_ptr(), K.status_word(y.device).data_ptr(), K._stream()), "moe_scatter_combine_push")
+
+
 def gemm_grouped(epi: int, x: torch.Tensor, W: torch.Tensor, out: Optional[torch.Tensor], M: int, groups: int,
                  group_expert: Optional[torch.Tensor] = None, x_row_div: int = 0, x_row_mul: int = 0,
                  x_col_per_expert: int = 0, out_group_stride: int = 0, row_scale: Optional[torch.Tensor] = None,

@@ -486,8 +486,9 @@ class DecoderEngine:
             return False
         T = shape.tokens
         if cfg.is_moe:
-            # expert parallelism with one expert per rank rides the one-shot path (the combine is the fused all-reduce)
-            fusable = w.ep_world == self.tp and w.layers[0].ex_wgu is not None and w.layers[0].ex_wgu.shape[0] == 1
+            # expert parallelism rides the one-shot path: the experts' combine is the fused all-reduce (one expert per
+            # rank pushes from its GEMM epilogue, several per rank from the combine kernel)
+            fusable = w.ep_world == self.tp and w.layers[0].ex_wgu is not None
             return bool(fusable and comm.oneshot_ok(T))
         if comm.oneshot_ok(T) and self.tp_mode != "rs_ag":
             return True

@@ -225,6 +225,11 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
     if ep is None:
         M.moe_scatter_combine(h, y, pos, h, T, H, k)
         return None
+    if tp is not None:
+        # any number of experts per rank, decode-sized step: the combine writes this rank's share of every token into
+        # every rank's inbox (no library collective in the step)
+        M.moe_scatter_combine_push(y, pos, T, H, k, tp)
+        return "pushed"
     # expert parallel over the library collectives: this rank's experts' share of every token, summed over the ranks
     import torch.distributed as dist
     p = eng.comm.partial[:T]

@@ -600,7 +600,15 @@ def moe_combine(h, parts, out, T, H, groups, gstride, per_token=0):
 def gemm_grouped(epi, x, W, out, M, groups, group_expert=None, x_row_div=0, x_row_mul=0, x_col_per_expert=0,
                  out_group_stride=0, row_scale=None, ldo=None, K_dim=None, tp=None):
     if tp is not None:
-        raise NotImplementedError("peer pushes are not emulated")
+        # one group whose result goes to every rank's inbox: compute it into a scratch, then push through the comm
+        comm, rs_site = tp
+        if not hasattr(comm, "push_rows"):
+            raise NotImplementedError("peer pushes are emulated over utils.tp_emulation only")
+        scratch = torch.zeros(M, W.shape[1], dtype=torch.bfloat16)
+        gemm_grouped(epi, x, W, scratch, M, groups, group_expert, x_row_div, x_row_mul, x_col_per_expert, 0, row_scale,
+                     W.shape[1], K_dim)
+        comm.push_rows(scratch, M, rs_site)
+        return
     E, N, Kw = W.shape
     Kd = K_dim or Kw
     n_out = N // 2 if epi == K.EPI_SWIGLU else N
@@ -657,6 +665,13 @@ def moe_scatter_combine(h, y, pos, out, T, H, k):
     out[:T].copy_(_bf(acc))
 
 
+def moe_scatter_combine_push(y, pos, T, H, k, tp):
+    comm, rs_site = tp
+    part = torch.zeros(T, H, dtype=torch.bfloat16)
+    moe_scatter_combine(None, y, pos, part, T, H, k)
+    comm.push_rows(part, T, rs_site)
+
+
 def gemm_grouped_tiled(epi, x, W, out, tile_expert, row_scale=None):
     for t, ex in enumerate(tile_expert.tolist()):
         if ex < 0:
@@ -690,6 +705,7 @@ def emulated_kernels():
                 status_word=lambda device=None: _status, check_status=lambda device=None: None),
         moe_ops: dict(moe_route=moe_route, moe_combine=moe_combine, gemm_grouped=gemm_grouped, moe_align=moe_align,
                       moe_gather_rows=moe_gather_rows, moe_scatter_combine=moe_scatter_combine,
+                      moe_scatter_combine_push=moe_scatter_combine_push,
                       gemm_grouped_tiled=gemm_grouped_tiled),
         suffix_ops: dict(adjust_logits=adjust_logits, token_logprob=token_logprob),
     }

@@ -123,6 +123,7 @@ class EmulatedFusedComm:
         self.device = torch.device("cpu")
         self.epoch = 0
         self.ax_count = 0
+        self.library_collectives = 0
         self.block = None
         self.log: List[tuple] = []          # (kind, site, target) of every cross-rank launch, for the tests
 
@@ -164,6 +165,14 @@ class EmulatedFusedComm:
         target = self._target(rs_site, self.rs_sites)
         for d in range(self.world):
             self.g.inbox[d][target & 1, self.rank, :rows] = y
+        self.log.append(("rs", rs_site, target))
+        self.g.signal_all(self.rank, CH_RS, target)
+
+    def push_rows(self, y, rows: int, rs_site: int) -> None:
+        """A producer that is not the row-parallel GEMM (the expert-parallel combine) sends its partial rows the same way."""
+        target = self._target(rs_site, self.rs_sites)
+        for d in range(self.world):
+            self.g.inbox[d][target & 1, self.rank, :rows] = y[:rows]
         self.log.append(("rs", rs_site, target))
         self.g.signal_all(self.rank, CH_RS, target)
 
@@ -253,6 +262,7 @@ class EmulatedFusedComm:
         return None
 
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        self.library_collectives += 1           # what a step on the library path would hand to NCCL
         parts = self._exchange_host(t)
         acc = parts[0].float()
         for p in parts[1:]:
@@ -261,6 +271,7 @@ class EmulatedFusedComm:
         return t
 
     def all_gather(self, out: torch.Tensor, inp: torch.Tensor) -> None:
+        self.library_collectives += 1
         parts = self._exchange_host(inp)
         out.view(self.world, -1).copy_(torch.stack([p.reshape(-1) for p in parts]))
 

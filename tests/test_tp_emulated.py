@@ -162,3 +162,55 @@ def test_device_adapter_turns_the_emulated_status_into_a_typed_error():
         group.fail(0, STEP_DEADLINE, 3 * 16 + 1)
         with pytest.raises(DeviceWaitTimeout, match=r"step deadline \(site 3, waiting for rank 1\)"):
             dev._raise_on_failed_wait(False)
+
+
+def _moe_rank_program(cfg, rank, world, comm, steps, out):
+    w = random_weights(cfg, "cpu", seed=0, std=0.05, tp_rank=rank, tp_world=world, ep_rank=rank, ep_world=world)
+    eng = DecoderEngine(w, num_blocks=9, max_seqs=2, max_tokens=48, max_blocks_per_seq=4, comm=comm, device="cpu",
+                        use_graphs=False)
+    s = FixedBatchSession(eng, 2, 64)
+    toks = [s.prefill_fast(_prompts(cfg)).clone()]
+    for _ in range(steps):
+        toks.append(s.decode(toks[-1][:, 0].tolist()).clone())
+    out[rank] = torch.stack(toks)
+    return eng
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_steps_are_fused_for_one_or_several_experts_per_rank(world):
+    """Four routed experts over 2 ranks (two per rank: the combine kernel pushes) and over 4 ranks (one per rank: the
+    down projection's epilogue pushes): tokens equal the single-rank run, and no step used a library collective."""
+    cfg = DecoderConfig(n_layers=2, hidden=256, n_heads=8, n_kv_heads=4, head_dim=64, ffn=512, vocab=4096, max_position=256,
+                        n_experts=4, top_k=2, moe_ffn=128)
+    with emulated_kernels():
+        ref = {}
+        _moe_rank_program(cfg, 0, 1, None, 3, ref)
+        group = EmulatedGroup(world, cfg.hidden)
+        for c in group.ctl:
+            c["budget"] = 5.0
+        comms = [EmulatedFusedComm(r, group) for r in range(world)]
+        out, errs = {}, {}
+
+        def body(r):
+            try:
+                _moe_rank_program(cfg, r, world, comms[r], 3, out)
+            except Exception as e:
+                errs[r] = e
+        threads = [threading.Thread(target=body, args=(r,), daemon=True) for r in range(world)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=180)
+        assert not any(t.is_alive() for t in threads), "a rank thread did not finish"
+    assert not errs, errs
+    for r in range(world):
+        # every rank reduces the same inbox rows in the same order: the ranks agree bit for bit with one another ...
+        assert torch.equal(out[r], out[0]) and group.status(r) == (0, -1)
+    # ... and with one rank up to the rounding of the per-rank partial sums (bf16 partials added in rank order instead
+    # of one f32 sum over the token's experts): the prompt's token and the first decoded token are the same
+    assert torch.equal(out[0][:2, :, 0], ref[0][:2, :, 0]), (out[0][:, :, 0], ref[0][:, :, 0])
+    assert (out[0][:, :, 0] == ref[0][:, :, 0]).float().mean() >= 0.75
+    L = cfg.n_layers
+    rs_targets = [t for k, _, t in comms[0].log if k == "rs"]
+    assert len(rs_targets) == 4 * 2 * L and rs_targets == sorted(set(rs_targets))     # attention + experts, every step
+    assert all(c.ax_count == 4 for c in comms) and all(c.library_collectives == 0 for c in comms)
