@@ -332,7 +332,9 @@ class Driver:
                 if sp.needs_adjust:
                     adjust_rows[b] = s
                 if s.guided is not None:
-                    guided_rows[b] = s.guided.mask(self.vocab)
+                    # an engine with a late-input point builds the mask while the device runs the model body
+                    guided_rows[b] = ((lambda g=s.guided: g.mask(self.vocab)) if getattr(self.engine, "late_inputs", False)
+                                      else s.guided.mask(self.vocab))
                 want_lp = want_lp or sp.logprobs > 0
                 b += 1
             off += piece

@@ -88,6 +88,8 @@ class DeviceStepEngine:
         self.last_hidden = None
         self.status_hook = None                # tests: callable returning (code, detail) in place of the device's block
         self.device_timing = False           # bracket each step with CUDA events (opt-in: it adds a synchronisation)
+        self.late_inputs = True              # guided-decoding masks may arrive as callables: built at the step's late-input point
+        self.late_steps = 0
         self.bounds_checked = False          # the checked kernel library is loaded: read its record after every step
         if pin and engine.device.type == "cuda":
             from ..ops import cuda_ops as K
@@ -138,6 +140,7 @@ class DeviceStepEngine:
             e.samp_topk[:B].copy_(self.h_topk[:B], non_blocking=True)
             e.samp_seeds[:B].copy_(self.h_seeds[:B], non_blocking=True)
         guided = False
+        late = None
         if inp.adjust is not None:
             if e.adj_idx is None:
                 e._alloc_adjust()
@@ -145,9 +148,18 @@ class DeviceStepEngine:
             e.adj_val[:B].copy_(torch.from_numpy(inp.adjust["val"]), non_blocking=False)
             if inp.adjust["guided"]:
                 guided = True
-                e.guided_mask[:B].zero_()
-                for r, m in inp.adjust["guided"].items():
-                    e.guided_mask[r].copy_(torch.from_numpy(np.ascontiguousarray(m, dtype=np.float32)))
+                rows = inp.adjust["guided"]
+
+                def bind_masks():
+                    e.guided_mask[:B].zero_()
+                    for r, m in rows.items():
+                        m = m() if callable(m) else m           # built now: the model body is already on the device
+                        e.guided_mask[r].copy_(torch.from_numpy(np.ascontiguousarray(m, dtype=np.float32)))
+
+                if any(callable(m) for m in rows.values()):
+                    late = bind_masks
+                else:
+                    bind_masks()
         lora = False
         if inp.adapter_rows is not None:
             if e.lora is None:
@@ -168,7 +180,11 @@ class DeviceStepEngine:
         if self.device_timing:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
-        e.run(shape)
+        if late is not None:
+            e.run_late(shape, late)
+            self.late_steps += 1
+        else:
+            e.run(shape)
         if ev is not None:
             ev[1].record()
         self.h_picked[:B].copy_(e.picked[:B], non_blocking=True)

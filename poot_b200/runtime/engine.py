@@ -266,6 +266,8 @@ class DecoderEngine:
         self.lora = None                    # bank of resident adapters, created by enable_adapters()
         self.embed_rows = self.embed_flags = None   # staging of rows that replace embeddings, created by bind_embeds()
         self.rope_cos_tok = self.rope_sin_tok = None  # per-token rotary rows of a sectioned rope, created by bind_rope_streams()
+        self._stage: Optional[str] = None    # "body" / "suffix" while one stage of a cut step is launched (run_late)
+        self._suffix_in: Dict[Tuple, torch.Tensor] = {}     # the logits view each cut shape's suffix reads
         self._graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.launches_per_step: Dict[Tuple, int] = {}
         self._launch_counter = 0
@@ -498,6 +500,9 @@ class DecoderEngine:
         """Launch the whole step on the current stream (eagerly or under capture)."""
         cfg, w = self.cfg, self.w
         T, B, D = shape.tokens, shape.logit_rows, cfg.head_dim
+        if self._stage == "suffix":             # second stage of a step cut at its late-input point: the sampler suffix only
+            self._launch_counter = 0
+            return self._sample(shape, self._suffix_in[self._key(shape)])
         self._fused_step = False
         if shape.chain and getattr(self, "_hosted", None) is not None:
             raise ValueError("chained decode feeds tokens back on the device; hosted embedding rows are copied from the host")
@@ -824,6 +829,9 @@ class DecoderEngine:
         """Sampler suffix over (possibly vocabulary-sharded) logits; every rank ends with the same ``picked``."""
         B, V = shape.logit_rows, self.cfg.vocab
         self.last_local_logits = local_logits  # [B, vocab / tp] of the step just launched
+        if self._stage == "body":               # first stage of a cut step: everything up to the logits
+            self._suffix_in[self._key(shape)] = local_logits
+            return
         need_full = shape.sampler != 0 or shape.adjust or shape.logprobs
         logits = None
         if self.tp == 1:
@@ -987,11 +995,22 @@ class DecoderEngine:
         return (shape.tokens, shape.logit_rows, shape.sampler, shape.chain, shape.adjust, shape.guided, shape.logprobs,
                 flash_only, shape.lora, shape.embeds, shape.mrope)
 
-    def prepare(self, shape: StepShape) -> None:
-        """Warm up and capture the step graph for ``shape`` (never done in the serving path afterwards)."""
-        key = self._key(shape)
+    def prepare(self, shape: StepShape, stage: Optional[str] = None) -> None:
+        """Warm up and capture the step graph for ``shape`` (never done in the serving path afterwards).  ``stage``:
+        one of the two stages of a step cut at its late-input point (``run_late``), captured as a graph of its own."""
+        key = self._key(shape) + ((stage,) if stage else ())
         if key in self._graphs or not self.use_graphs:
             return
+        if stage:
+            self._stage = stage
+            try:
+                self._capture(shape, key)
+            finally:
+                self._stage = None
+            return
+        self._capture(shape, key)
+
+    def _capture(self, shape: StepShape, key) -> None:
         # A program whose kernels wait on other ranks starts on every rank together: host rendezvous with the devices
         # idle before the eager warm-up forward, and again before the first replay of the captured graph.  Without it
         # a rank that finished its set-up seconds earlier would sit in device-side waits while its peers are still
@@ -1015,18 +1034,33 @@ class DecoderEngine:
         if multi:
             self.comm.rendezvous()
 
-    def run(self, shape: StepShape) -> None:
+    def run(self, shape: StepShape, stage: Optional[str] = None) -> None:
         """Replay (or eagerly launch) one step; inputs must already be in the static buffers."""
-        key = self._key(shape)
+        key = self._key(shape) + ((stage,) if stage else ())
         g = self._graphs.get(key)
         if g is None and self.use_graphs:
-            self.prepare(shape)
+            self.prepare(shape, stage)
             g = self._graphs.get(key)
         if g is not None:
             g.replay()
-        else:
+            return
+        self._stage = stage
+        try:
             self.forward(shape)
-            self.launches_per_step[key] = self._launch_counter
+        finally:
+            self._stage = None
+        self.launches_per_step[key] = self._launch_counter
+
+    def run_late(self, shape: StepShape, late) -> None:
+        """A step cut at its late-input point (crates/poot-executor/src/engine.rs "late_after"): the stages before the
+        point are enqueued - everything up to the logits - then ``late()`` builds and binds what only the rest reads
+        (the guided-decoding masks, the sparse logit adjustments) while the device is busy with the model body, then
+        the sampler suffix is enqueued.  Each stage is its own captured graph."""
+        if shape.chain:
+            raise ValueError("a chained step feeds itself on the device; it has no late-input point")
+        self.run(shape, "body")
+        late()
+        self.run(shape, "suffix")
 
     # ------------------------------------------------------------------ host-side input binding
     def bind(self, tokens, positions, slots, row_seq, row_ctx, logit_idx, block_tables=None,

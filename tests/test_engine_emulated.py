@@ -608,3 +608,54 @@ def test_vision_engine_matches_the_graph_oracle():
     assert np.abs(got - want).max() < 0.03 * max(1.0, np.abs(want).max())
     with pytest.raises(ValueError, match="multiples of 32"):
         VisionEngine(VisionConfig(hidden=48, n_heads=4), {}, "cpu")
+
+
+def test_guided_steps_are_cut_at_the_late_input_point():
+    """A guided sequence on the device step engine: the mask arrives as a callable, the engine launches the model body,
+    builds and binds the mask, then launches the sampler suffix; the constrained output is what the eager mask gives."""
+    from poot_b200 import LLM, SamplingParams
+    from poot_b200.text.guided import build_constraint
+    over = dict(n_layers=2, hidden=128, n_heads=4, n_kv_heads=2, head_dim=64, ffn=256, vocab=512, max_position=256)
+
+    def run(late: bool):
+        llm = LLM.random("tiny-llama", device="cpu", rows=2, max_seq=64, prefill_chunk=16, num_blocks=16, std=0.08, **over)
+        d = llm.driver
+        inner = d.engine.inner
+        inner.late_inputs = late
+        order = []
+        e = inner.e
+        body, sample = e.forward, e._sample
+
+        def spy_forward(shape):
+            order.append("forward:" + str(e._stage))
+            return body(shape)
+
+        e.forward = spy_forward
+        g = build_constraint({"choice": ["yes", "no", "maybe"]}, llm.tokenizer, d.eos_token)
+        mask = g.mask
+
+        def spy_mask(vocab):
+            order.append("mask")
+            return mask(vocab)
+
+        g.mask = spy_mask
+        sid = d.open(llm.tokenizer.encode("answer:"), SamplingParams(max_tokens=8), guided=g)
+        out = []
+        for _ in range(8):
+            r = d.step([sid])[0]
+            d.commit(sid, [r.token])
+            if d.finished(sid, r.token):
+                if r.token != d.eos_token:
+                    out.append(r.token)
+                break
+            out.append(r.token)
+        d.release(sid)
+        return llm.tokenizer.decode(out), order, inner.late_steps
+
+    with emulated_kernels():
+        text_late, order_late, n_late = run(True)
+        text_eager, order_eager, n_eager = run(False)
+    assert text_late == text_eager and text_late in ("yes", "no", "maybe")
+    assert n_late > 0 and n_eager == 0
+    assert order_late[:3] == ["forward:body", "mask", "forward:suffix"]       # the mask is built between the stages
+    assert order_eager[:2] == ["mask", "forward:None"]
