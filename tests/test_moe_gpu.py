@@ -28,6 +28,7 @@ def test_moe_route_matches_topk_softmax():
     assert 2 not in ids[4].tolist()
 
 
+@pytest.mark.first_device_run          # steps with more rows than experts ride the row-grouped kernels
 @pytest.mark.parametrize("batch,prompt", [(1, 9), (12, 6), (2, 100)])
 def test_mixtral_like_model_matches_reference(batch, prompt):
     from poot_b200.models.config import DecoderConfig

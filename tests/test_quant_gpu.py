@@ -23,6 +23,7 @@ def _packed(fmt, N, Kd, seed=0):
     return K.QuantWeight(fmt, torch.from_numpy(p).cuda(), N, Kd), torch.from_numpy(deq).cuda()
 
 
+@pytest.mark.first_device_run          # eight of the formats' decoders have not run on a device
 @pytest.mark.parametrize("fmt", FMTS)
 @pytest.mark.parametrize("M", [1, 3])
 @pytest.mark.parametrize("N,Kd", [(1026, 1024), (258, 5376), (36, 14336)])     # 14336 = the down projection's K of Llama-3-8B
@@ -41,6 +42,7 @@ def test_quant_gemv_matches_dequantised_reference(fmt, M, N, Kd):
     assert (sw.float() - r2).abs().max() <= 2e-2 * r2.abs().max() + 1e-2
 
 
+@pytest.mark.first_device_run
 @pytest.mark.parametrize("fmt", FMTS)
 def test_quant_dequant_and_row_gather_are_exact(fmt):
     from poot_b200.ops import cuda_ops as K
