@@ -116,6 +116,7 @@ def test_expert_parallel_shards_group_only_their_own_rows_and_sum_to_the_whole()
 
 
 @pytest.mark.gpu
+@pytest.mark.first_device_run
 @pytest.mark.parametrize("T,E,k", [(1, 8, 2), (64, 8, 2), (1024, 8, 2), (64, 128, 8), (1024, 128, 8)])
 def test_row_grouped_experts_on_the_device(T, E, k):
     """The device kernels (align, gather, grouped swap-AB and tiled tcgen05 GEMMs, scatter-combine) against the fp32
@@ -132,6 +133,7 @@ def test_row_grouped_experts_on_the_device(T, E, k):
 
 
 @pytest.mark.gpu
+@pytest.mark.first_device_run
 def test_expert_shard_on_the_device_leaves_other_ranks_rows_out():
     from poot_b200.ops import cuda_ops as K, moe_ops as M
     T, E, k = 96, 8, 2
