@@ -43,8 +43,10 @@ class ModelHandle:
         registry = registry or Registry.builtin()
         if os.path.isdir(path):
             with open(os.path.join(path, "config.json")) as f:
-                model = registry.resolve_hf(json.load(f))
-            store = st.load_weight_store(path)
+                hf_config = json.load(f)
+            model = registry.resolve_hf(hf_config)
+            from ..load.planar import planar_view
+            store = planar_view(st.load_weight_store(path), hf_config)    # fp8 / GPTQ / AWQ linears become planar weights
             from ..load.hf_map import map_checkpoint
             canon = map_checkpoint(model.cfg, store)
             return ModelHandle(model, store, canon, path, "hf", path)
@@ -168,7 +170,21 @@ def _permute_rows(w: PackedWeight, order: np.ndarray) -> PackedWeight:
 
 # ---- device upload ---------------------------------------------------------------------------------------------
 def _rows(w: PackedWeight, start: int, count: int) -> PackedWeight:
-    return w.rows(start, count) if FORMATS[w.format].storage != "planar" else w
+    if FORMATS[w.format].storage == "planar":
+        if start == 0 and count == w.shape[0]:
+            return w
+        from ..load.planar import planar_take_rows
+        return planar_take_rows(w, np.arange(start, start + count))
+    return w.rows(start, count)
+
+
+def _planar(w: PackedWeight) -> bool:
+    return FORMATS[w.format].storage == "planar"
+
+
+def _dense_f32(w: PackedWeight) -> PackedWeight:
+    a = np.ascontiguousarray(w.to_f32(), dtype=np.float32)
+    return PackedWeight(w.name, "F32", tuple(a.shape), a.view(np.uint8).reshape(-1))
 
 
 def _cat_rows(parts) -> PackedWeight:
@@ -194,6 +210,11 @@ def to_device(w: PackedWeight, device, keep_packed: bool = True):
     import torch
     from ..ops import cuda_ops as K
     d = FORMATS[w.format]
+    if d.storage == "planar":
+        if keep_packed and w.format in K.PLANAR_DEVICE_FORMATS and len(w.shape) == 2:
+            ops = {k: torch.from_numpy(np.array(v)).to(device) for k, v in w.planar.items()}     # a copy: the mapped file is read-only
+            return K.PlanarWeight(w.format, ops, w.shape[0], w.shape[1], w.group)
+        return torch.from_numpy(w.to_f32()).to(device=device, dtype=torch.bfloat16)
     if keep_packed and d.device_gemv and len(w.shape) == 2 and w.shape[1] % 256 == 0:
         raw = torch.from_numpy(np.ascontiguousarray(w.payload).view(np.uint8).reshape(-1).copy())
         return K.QuantWeight(w.format, raw.to(device), w.shape[0], w.shape[1])
@@ -233,6 +254,10 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
     D = c.head_dim
     hq, hkv = c.n_heads // tp_world, max(c.n_kv_heads // tp_world, 1)
     k0 = tp_rank * hkv if c.n_kv_heads >= tp_world else tp_rank * c.n_kv_heads // tp_world
+    if tp_world > 1 and any(_planar(w) for w in canon.values()):
+        # planar quantised linears are cut along K for the row-parallel projections, which their group layouts do not
+        # allow in general: a device group runs them decoded
+        canon = {n: (_dense_f32(w) if _planar(w) else w) for n, w in canon.items()}
 
     def dense(name):
         return torch.from_numpy(canon[name].to_f32()).to(device=device, dtype=torch.bfloat16)
@@ -243,7 +268,16 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
     for l in range(st.l0, st.l1):
         p = f"layers.{l}."
         q, k, v = canon[p + "attn_q"], canon[p + "attn_k"], canon[p + "attn_v"]
-        if len({q.format, k.format, v.format}) == 1 and FORMATS[q.format].storage != "planar":
+        wqkv = None
+        if len({q.format, k.format, v.format}) == 1 and _planar(q) and keep_packed:
+            try:                # one planar weight over q | k | v rows, still packed
+                from ..load.planar import planar_cat_rows
+                wqkv = to_device(planar_cat_rows([q, k, v]), device, keep_packed)
+            except ValueError:
+                wqkv = None     # parts that do not line up with the format's groups: decoded below
+        if wqkv is not None:
+            pass
+        elif len({q.format, k.format, v.format}) == 1 and not _planar(q):
             wqkv = to_device(_cat_rows([_rows(q, tp_rank * hq * D, hq * D), _rows(k, k0 * D, hkv * D),
                                         _rows(v, k0 * D, hkv * D)]), device, keep_packed)
         else:   # mixed formats (e.g. Q4_K_M keeps V in Q6_K): expand to bf16
@@ -277,7 +311,17 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
         else:
             g, u, dn = canon[p + "ffn_gate"], canon[p + "ffn_up"], canon[p + "ffn_down"]
             F = g.shape[0] // tp_world
-            if g.format == u.format and FORMATS[g.format].storage != "planar":
+            wgu = None
+            if g.format == u.format and _planar(g) and keep_packed:
+                try:            # gate and up rows interleaved inside the packed form (codes, scales, zero points move together)
+                    from ..load.planar import planar_cat_rows, planar_take_rows
+                    order = np.stack([np.arange(F), F + np.arange(F)], 1).reshape(-1)
+                    wgu = to_device(planar_take_rows(planar_cat_rows([g, u]), order), device, keep_packed)
+                except ValueError:
+                    wgu = None
+            if wgu is not None:
+                L.wgu = wgu
+            elif g.format == u.format and not _planar(g):
                 L.wgu = to_device(_interleave_rows(_rows(g, tp_rank * F, F), _rows(u, tp_rank * F, F)), device, keep_packed)
             else:
                 gf, uf = _rows(g, tp_rank * F, F).to_f32(), _rows(u, tp_rank * F, F).to_f32()

@@ -962,8 +962,83 @@ def quant_dequant(W: QuantWeight, out: Optional[torch.Tensor] = None) -> torch.T
 _plain_linear = linear
 
 
+PLANAR_DEVICE_FORMATS = {"E4M3_CHANNEL": 0, "E4M3_BLOCK128": 1, "E2M1_ROW32": 2, "GPTQ": 3, "AWQ": 4}
+_SIGS["poot_planar_gemv"] = [c_int, c_int, _P, c_int, _P, _P, _P, _P, c_int, _P, _P, c_int, c_int, c_int, c_int, _P]
+_SIGS["poot_planar_dequant"] = [c_int, _P, _P, _P, _P, c_int, _P, c_int, c_int, _P]
+
+
+class PlanarWeight:
+    """A ``[N, K]`` weight resident on the device as the tensors its safetensors checkpoint stores (codes, scales,
+    zero points): fp8 with per-channel or 128 x 128 block scales, fp4 rows of 32, GPTQ and AWQ int4."""
+
+    def __init__(self, fmt: str, ops: dict, N: int, K: int, group: int = 128):
+        if fmt not in PLANAR_DEVICE_FORMATS:
+            raise ValueError(f"{fmt} is not a planar format with device kernels")
+        self.fmt, self.type_id, self.N, self.K, self.group = fmt, PLANAR_DEVICE_FORMATS[fmt], N, K, group
+        self.shape = (N, K)
+        if fmt in ("GPTQ", "AWQ"):
+            self.w, self.zeros = ops["qweight"].contiguous(), ops["qzeros"].contiguous()
+            self.scale = ops["scales"].to(torch.float32).contiguous()
+            g = ops.get("g_idx")
+            self.g_idx = None if g is None or fmt == "AWQ" else g.to(torch.int32).contiguous()
+        else:
+            self.w, self.zeros, self.g_idx = ops["weight"].contiguous(), None, None
+            sc = ops["weight_scale_inv"] if fmt == "E4M3_BLOCK128" else ops["weight_scale"]
+            self.scale = (sc if fmt == "E2M1_ROW32" else sc.to(torch.float32).reshape(-1) if fmt == "E4M3_CHANNEL"
+                          else sc.to(torch.float32)).contiguous()
+
+    @property
+    def device(self):
+        return self.w.device
+
+    def tensors(self):
+        return [t for t in (self.w, self.scale, self.zeros, self.g_idx) if t is not None]
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.tensors())
+
+
+def planar_gemv(x: torch.Tensor, W: PlanarWeight, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
+                resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x[M <= 4, K] @ W^T`` decoded from the checkpoint's own tensors inside the product."""
+    _need_cuda(x, W.w)
+    M, Kd = x.shape
+    assert Kd == W.K and x.dtype == torch.bfloat16 and x.stride(1) == 1 and epi in (EPI_STORE, EPI_F32, EPI_RESID)
+    out = _out_for(epi, M, W.N, x.device, out)
+    check(_fn("poot_planar_gemv")(W.type_id, {EPI_STORE: 0, EPI_F32: 1, EPI_RESID: 2}[epi], _ptr(x), x.stride(0), _ptr(W.w),
+                                  _ptr(W.scale), _ptr(W.zeros), _ptr(W.g_idx), W.group, _ptr(out), _ptr(resid), out.stride(0),
+                                  M, W.N, Kd, _stream()), "planar_gemv")
+    return out
+
+
+def planar_dequant(W: PlanarWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The whole weight as bf16 ``[N, K]``."""
+    _need_cuda(W.w)
+    if out is None:
+        out = torch.empty(W.N, W.K, dtype=torch.bfloat16, device=W.device)
+    check(_fn("poot_planar_dequant")(W.type_id, _ptr(W.w), _ptr(W.scale), _ptr(W.zeros), _ptr(W.g_idx), W.group, _ptr(out),
+                                     W.N, W.K, _stream()), "planar_dequant")
+    return out
+
+
 def linear(x, W, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None, resid: Optional[torch.Tensor] = None):
-    """``x @ W^T`` for a bf16 weight or a packed ``QuantWeight`` (fused GEMV at decode, expand + GEMM for larger M)."""
+    """``x @ W^T`` for a bf16 weight, a packed ``QuantWeight`` or a ``PlanarWeight`` (fused GEMV at decode, expand + GEMM
+    for larger M)."""
+    if isinstance(W, PlanarWeight):
+        if x.shape[0] <= 4 and epi in (EPI_STORE, EPI_F32, EPI_RESID):
+            return planar_gemv(x, W, epi, out, resid)
+        if x.shape[0] <= 4 and epi == EPI_SWIGLU:           # interleaved (gate, up) rows: product, then the gated activation
+            key = (W.device, "gu", W.N)
+            gu = _dequant_scratch.get(key)
+            if gu is None:
+                gu = _dequant_scratch[key] = torch.empty(4, W.N, dtype=torch.bfloat16, device=W.device)
+            return swiglu(planar_gemv(x, W, EPI_STORE, gu[:x.shape[0]]), True, out)
+        key = (W.device, W.N * W.K)
+        buf = _dequant_scratch.get(key)
+        if buf is None:
+            buf = torch.empty(W.N * W.K, dtype=torch.bfloat16, device=W.device)
+            _dequant_scratch[key] = buf
+        return _plain_linear(x, planar_dequant(W, buf.view(W.N, W.K)), epi, out, resid)
     if isinstance(W, QuantWeight):
         if x.shape[0] <= 4:
             return quant_gemv(x, W, epi, out, resid)

@@ -45,11 +45,11 @@ FORMATS: Dict[str, FormatDescriptor] = {f.name: f for f in [
     _F("IQ3_XXS", "blocks", 256, 98, 18, decode=False, note="codebook grid not reproduced"),
     _F("IQ3_S", "blocks", 256, 110, 21, decode=False, note="codebook grid not reproduced"),
     _F("MXFP4", "blocks", 32, 17, 39, encode=True, device_gemv=True),
-    _F("E4M3_CHANNEL", "planar", note="fp8 weight + per-output-channel f32 scale", encode=True),
-    _F("E4M3_BLOCK128", "planar", note="fp8 weight + 128x128 block scales", encode=True),
-    _F("E2M1_ROW32", "planar", note="fp4 codes + e8m0 scale per 32 values of a row", encode=True),
-    _F("GPTQ", "planar", note="int4 qweight/qzeros/scales (+g_idx for act-order)", encode=True),
-    _F("AWQ", "planar", note="int4 qweight/qzeros/scales in AWQ nibble order", encode=True),
+    _F("E4M3_CHANNEL", "planar", device_gemv=True, note="fp8 weight + per-output-channel f32 scale", encode=True),
+    _F("E4M3_BLOCK128", "planar", device_gemv=True, note="fp8 weight + 128x128 block scales", encode=True),
+    _F("E2M1_ROW32", "planar", device_gemv=True, note="fp4 codes + e8m0 scale per 32 values of a row", encode=True),
+    _F("GPTQ", "planar", device_gemv=True, note="int4 qweight/qzeros/scales (+g_idx for act-order)", encode=True),
+    _F("AWQ", "planar", device_gemv=True, note="int4 qweight/qzeros/scales in AWQ nibble order", encode=True),
 ]}
 GGML_TYPE_TO_FORMAT = {f.ggml_type: f.name for f in FORMATS.values() if f.ggml_type is not None}
 # ggml types that exist but are refused by name (as the reference's type table does, crates/poot-load/src/gguf/format.rs:476-520)

@@ -22,6 +22,7 @@ class PackedWeight:
     shape: Tuple[int, ...]       # logical shape (rows = out features, last axis = K)
     payload: np.ndarray          # raw bytes (uint8 view) for dense / block formats
     planar: Optional[Dict[str, np.ndarray]] = None
+    group: int = 128             # int4 planar formats: values per (scale, zero point) along K
 
     @property
     def nbytes(self) -> int:
@@ -32,7 +33,7 @@ class PackedWeight:
     def to_f32(self) -> np.ndarray:
         d = descriptor(self.format)
         if d.storage == "planar":
-            return codec.dequantize_planar(self.format, self.planar)
+            return codec.dequantize_planar(self.format, self.planar, self.group)
         return codec.dequantize(self.format, self.payload, self.shape)
 
     def rows(self, start: int, count: int) -> "PackedWeight":

@@ -252,9 +252,32 @@ def _epilogue(y: torch.Tensor, epi: int, out, resid):
     return out
 
 
+def _planar_f32(W) -> torch.Tensor:
+    """The decoded weight of a ``PlanarWeight`` through the host codec (cached on the object)."""
+    w = getattr(W, "_emulated_f32", None)
+    if w is None:
+        from ..quant import codec
+        np_ = lambda t: None if t is None else t.cpu().numpy()
+        if W.fmt in ("GPTQ", "AWQ"):
+            ops = {"qweight": np_(W.w), "qzeros": np_(W.zeros), "scales": np_(W.scale)}
+            if W.g_idx is not None:
+                ops["g_idx"] = np_(W.g_idx)
+        else:
+            key = "weight_scale_inv" if W.fmt == "E4M3_BLOCK128" else "weight_scale"
+            ops = {"weight": np_(W.w), key: np_(W.scale)}
+        w = torch.from_numpy(codec.dequantize_planar(W.fmt, ops, W.group).astype("float32"))
+        W._emulated_f32 = w
+    return w
+
+
 def linear(x, W, epi=K.EPI_STORE, out=None, resid=None):
     if isinstance(W, K.QuantWeight):
         raise NotImplementedError("packed weights are not emulated")
+    if isinstance(W, K.PlanarWeight):
+        w = _planar_f32(W)
+        if x.shape[0] > 4:              # larger steps decode the weight to bf16 first and multiply with the dense GEMM
+            w = _bf(w).float()
+        return _epilogue(x.float() @ w.T, epi, out, resid)
     return _epilogue(x.float() @ W.float().T, epi, out, resid)
 
 

@@ -1,0 +1,158 @@
+"""Quantised safetensors checkpoints (fp8 per-channel and 128 x 128 block scales, GPTQ, AWQ): the loader assembles one
+planar weight per linear, the oracle decodes it, and the device loader keeps it packed (fused q|k|v and interleaved
+gate|up included) for the dequant-fused kernels, checked here on their host restatements."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from poot_b200.load.planar import PlanarView, planar_cat_rows, planar_take_rows
+from poot_b200.quant import codec
+from poot_b200.quant.formats import UnsupportedFormat
+from poot_b200.quant.weights import PackedWeight
+
+FMTS = ["E4M3_CHANNEL", "E4M3_BLOCK128", "E2M1_ROW32", "GPTQ", "AWQ"]
+
+
+def _pw(fmt, w, group=32, name="w"):
+    ops = codec.quantize_planar(fmt, w, group)
+    if fmt == "GPTQ":
+        ops.pop("g_idx")
+    return PackedWeight(name, fmt, w.shape, np.zeros(0, np.uint8), planar=ops, group=group)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+def test_row_surgery_keeps_the_decoded_values(fmt):
+    rng = np.random.default_rng(0)
+    a, b = rng.standard_normal((128, 64)).astype(np.float32), rng.standard_normal((256, 64)).astype(np.float32)
+    pa, pb = _pw(fmt, a), _pw(fmt, b)
+    cat = planar_cat_rows([pa, pb])
+    assert cat.shape == (384, 64)
+    np.testing.assert_array_equal(cat.to_f32(), np.concatenate([pa.to_f32(), pb.to_f32()]))
+    order = np.arange(384).reshape(3, 128)[[2, 0, 1]].reshape(-1)             # whole aligned blocks: every format allows it
+    np.testing.assert_array_equal(planar_take_rows(cat, order).to_f32(), cat.to_f32()[order])
+    inter = np.stack([np.arange(128), 128 + np.arange(128)], 1).reshape(-1)   # gate / up interleave
+    two = planar_cat_rows([pa, _pw(fmt, b[:128])])
+    if fmt == "E4M3_BLOCK128":
+        with pytest.raises(ValueError):
+            planar_take_rows(two, inter)
+    else:
+        np.testing.assert_array_equal(planar_take_rows(two, inter).to_f32(), two.to_f32()[inter])
+    with pytest.raises(ValueError):
+        planar_cat_rows([pa, _pw("E4M3_CHANNEL" if fmt != "E4M3_CHANNEL" else "AWQ", b)])
+
+
+def _quantised_checkpoint(tmp_path, method, block=False):
+    """A tiny llama directory whose linears are stored the way ``method`` stores them."""
+    from safetensors.torch import save_file
+    from transformers import AutoConfig, AutoModelForCausalLM
+    cfg = AutoConfig.for_model("llama", hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                               num_key_value_heads=2, head_dim=32, vocab_size=320, max_position_embeddings=128,
+                               tie_word_embeddings=False)
+    torch.manual_seed(0)
+    m = AutoModelForCausalLM.from_config(cfg).float().eval()
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    sd = {k: v.clone() for k, v in m.state_dict().items()}
+    out, ref = {}, {}
+    for k, v in sd.items():
+        if not (k.endswith("proj.weight")):
+            out[k] = v
+            continue
+        stem = k[:-len(".weight")]
+        w = v.numpy()
+        if method == "fp8":
+            fmt = "E4M3_BLOCK128" if block else "E4M3_CHANNEL"
+            ops = codec.quantize_planar(fmt, w)
+            out[k] = torch.from_numpy(ops["weight"]).view(torch.float8_e4m3fn)
+            if block:
+                out[stem + ".weight_scale_inv"] = torch.from_numpy(ops["weight_scale_inv"])
+            else:
+                out[stem + ".weight_scale"] = torch.from_numpy(ops["weight_scale"]).reshape(-1, 1)
+        else:
+            fmt = method.upper()
+            ops = codec.quantize_planar(fmt, w, 32)
+            out[stem + ".qweight"] = torch.from_numpy(np.ascontiguousarray(ops["qweight"]))
+            out[stem + ".qzeros"] = torch.from_numpy(np.ascontiguousarray(ops["qzeros"]))
+            out[stem + ".scales"] = torch.from_numpy(np.ascontiguousarray(ops["scales"])).to(torch.float16).contiguous()
+            ops["scales"] = out[stem + ".scales"].float().numpy()
+            if method == "gptq":
+                out[stem + ".g_idx"] = torch.from_numpy(ops["g_idx"])
+        ref[k] = codec.dequantize_planar(fmt, ops, 32)
+    save_file(out, str(tmp_path / "model.safetensors"), metadata={"format": "pt"})
+    hf = json.loads((tmp_path / "config.json").read_text())
+    hf["quantization_config"] = ({"quant_method": "fp8", **({"weight_block_size": [128, 128]} if block else {})}
+                                 if method == "fp8" else {"quant_method": method, "bits": 4, "group_size": 32, "version": "gemm"})
+    (tmp_path / "config.json").write_text(json.dumps(hf))
+    with torch.no_grad():                  # the reference model: the same architecture over the decoded weights
+        for k, w in ref.items():
+            sd[k].copy_(torch.from_numpy(w))
+    m.load_state_dict(sd)
+    return m
+
+
+@pytest.mark.parametrize("method,block", [("fp8", False), ("fp8", True), ("gptq", False), ("awq", False)])
+def test_quantised_checkpoint_loads_and_generates(method, block, tmp_path):
+    from poot_b200 import LLM, SamplingParams
+    from poot_b200.driver.handle import ModelHandle
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.utils.kernel_emulation import emulated_kernels
+    m = _quantised_checkpoint(tmp_path, method, block)
+    h = ModelHandle.load(str(tmp_path))
+    fmt = {"fp8": "E4M3_BLOCK128" if block else "E4M3_CHANNEL", "gptq": "GPTQ", "awq": "AWQ"}[method]
+    assert h.canonical["layers.0.attn_q"].format == fmt and h.canonical["embed"].format in ("F32", "BF16", "F16")
+    assert not any(n.endswith(("qzeros", "scales", "weight_scale", "weight_scale_inv")) for n in h.canonical)
+    p = torch.randint(3, 320, (1, 19), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want_logits = m(p).logits[0, -1].numpy()
+        want = m.generate(p, max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)[0, 19:].tolist()
+    llm = LLM.oracle(str(tmp_path), rows=1, max_seq=64, num_blocks=8, prefill_chunk=32)
+    got = llm.generate_tokens(p[0].tolist(), SamplingParams(max_tokens=6, ignore_eos=True))
+    assert got == want
+    got_logits = llm.driver.engine.last_logits(1)[0]
+    with emulated_kernels():
+        dev = LLM.load(str(tmp_path), device="cpu", rows=1, max_seq=64, prefill_chunk=32, num_blocks=8)
+        L = dev.engine.w.layers[0]
+        packed = [isinstance(x, K.PlanarWeight) for x in (L.wqkv, L.wo, L.wgu, L.wdown)]
+        # fused q|k|v and the interleaved gate|up stay packed; under 128 x 128 block scales rows cannot interleave and
+        # this model's 64-row k / v parts do not fill a block, so those two are decoded there
+        blocked = fmt == "E4M3_BLOCK128"
+        assert packed == [not blocked, True, not blocked, True], packed
+        if not blocked:
+            assert L.wqkv.N == 128 + 2 * 64 and L.wqkv.nbytes() < 0.6 * L.wqkv.N * L.wqkv.K * 2
+        toks = dev.generate_tokens(p[0].tolist(), SamplingParams(max_tokens=6, ignore_eos=True))
+    agree = sum(1 for a, b in zip(toks, want) if a == b)
+    assert toks[0] == want[0] and agree >= 4, (toks, want)
+
+
+def test_unsupported_quantisation_methods_are_typed_refusals():
+    class Store:
+        def names(self): return []
+    for q in ({"quant_method": "bitsandbytes"}, {"quant_method": "gptq", "bits": 8}, {"quant_method": "awq", "version": "gemv"},
+              {"quant_method": "fp8", "weight_block_size": [64, 64]}, {"quant_method": "gptq", "bits": 4, "group_size": -1}):
+        with pytest.raises(UnsupportedFormat):
+            PlanarView(Store(), q)
+
+
+@pytest.mark.gpu
+@pytest.mark.xfail(strict=False, reason="new kernels: not yet run on a device")
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("M", [1, 4])
+def test_planar_gemv_and_dequant_match_the_host_codec(fmt, M):
+    from poot_b200.ops import cuda_ops as K
+    rng = np.random.default_rng(3)
+    N, Kd, group = 264, 1024, 128
+    w = (rng.standard_normal((N, Kd)) * 0.05).astype(np.float32)
+    ops = codec.quantize_planar(fmt, w, group)
+    ref = torch.from_numpy(codec.dequantize_planar(fmt, ops, group))
+    dev_ops = {k: torch.from_numpy(np.ascontiguousarray(v)).cuda() for k, v in ops.items()}
+    W = K.PlanarWeight(fmt, dev_ops, N, Kd, group)
+    deq = K.planar_dequant(W).float().cpu()
+    assert (deq - ref).abs().max().item() <= 0.01 * ref.abs().max().item()
+    x = (torch.randn(M, Kd, generator=torch.Generator().manual_seed(0)) * 0.5).to(torch.bfloat16)
+    want = x.float() @ ref.T
+    got = K.planar_gemv(x.cuda(), W, K.EPI_F32).cpu()
+    assert (got - want).abs().max().item() <= 2e-3 * max(1.0, want.abs().max().item())
+    res = torch.randn(M, N).to(torch.bfloat16)
+    got = K.planar_gemv(x.cuda(), W, K.EPI_RESID, resid=res.cuda()).float().cpu()
+    assert (got - (want + res.float())).abs().max().item() <= 0.02 * max(1.0, want.abs().max().item())

@@ -16,7 +16,7 @@ LAYERS = {
     "models": {"tensor", "ir", "load"}, "plan": {"tensor", "ir", "quant", "target", "models", "oracle"},
     "ops": set(), "profile": {"target", "ops"}, "text": {"ops"},
     "runtime": {"models", "ops", "quant", "parallel", "tensor", "plan"}, "parallel": {"ops", "runtime"},
-    "utils": {"ops", "oracle", "runtime", "models", "tensor", "plan"},
+    "utils": {"ops", "oracle", "runtime", "models", "tensor", "plan", "quant"},
     "driver": {"models", "runtime", "ops", "load", "quant", "ir", "oracle", "text", "tensor", "profile", "parallel"},
     "serve": {"driver", "text", "profile", "models", "parallel", "runtime", "ops", "load", "plan"}, "cli": {"driver", "text", "models"},
 }
