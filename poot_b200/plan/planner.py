@@ -95,7 +95,15 @@ def plan_eqn(g: Graph, k: int, e: Eqn, world: int = 1) -> Plan:
     if op in ("add", "sub", "mul", "div", "max", "neg", "exp", "tanh", "sqrt", "recip", "select", "ge", "and", "or",
               "xor", "log", "erf", "not", "geu", "remu", "shl", "shr", "clz", "reduce"):
         return Plan("dispatch", ["elementwise"], "unfused primitive")
-    if op in ("scan", "block_top_k", "selected_attention", "packed_dequant", "all_to_all", "side_output"):
+    if op == "scan":
+        # recurrences over a sequence's own state rows: the gated delta rule (D x D state per head) and the Mamba2
+        # recurrence (N x P state per head); the state update and the output come out of one launch per layer
+        kind = e.attrs.get("family")
+        kernel = {"delta_rule": "poot_gdn_scan", "ssd": "poot_ssd_scan"}.get(kind)
+        if kernel is None:
+            raise Refusal(k, op, dt, TARGET, f"no kernel for the {kind!r} recurrence")
+        return Plan("dispatch", [kernel], f"{kind}: state carried per (sequence, head) in shared memory")
+    if op in ("block_top_k", "selected_attention", "packed_dequant", "all_to_all", "side_output"):
         raise Refusal(k, op, dt, TARGET, "no kernel family for this equation")
     raise Refusal(k, op, dt, TARGET, "unknown equation")
 

@@ -298,3 +298,29 @@ def test_committed_plan_digests_and_launch_census():
         got = ";".join(f"{k}={v}" for k, v in sorted(prog.census.items()))
         assert (str(len(g.eqns)), str(len(prog.graph.eqns)), prog.graph.digest(), str(prog.dispatches), got) == \
             (n_in, n_out, digest, dispatches, census), (name, label)
+
+
+@pytest.mark.parametrize("kinds,extra,kernel", [
+    (["gdn", "attention"], dict(gdn_k_heads=2, gdn_v_heads=4, gdn_head_dim=64, gdn_conv=4), "poot_gdn_scan"),
+    (["mamba", "attention"], dict(ssm_heads=4, ssm_head_dim=32, ssm_state=16, ssm_groups=2, ssm_conv=4), "poot_ssd_scan"),
+])
+def test_hybrid_stacks_plan_their_recurrence_on_the_scan_kernels(kinds, extra, kernel):
+    """The ``scan`` equation of a gated delta net or Mamba2 layer gets its kernel (one launch per recurrent layer); an
+    unknown recurrence is a typed refusal."""
+    import collections
+    from poot_b200.models.config import DecoderConfig
+    from poot_b200.models.model import Model, StepSpec
+    from poot_b200.plan.compile import compile_graph
+    cfg = DecoderConfig(n_layers=2, hidden=128, n_heads=4, n_kv_heads=2, head_dim=32, ffn=256, vocab=320, max_position=128,
+                        layer_kinds=kinds, **extra)
+    for T in (1, 8):
+        g = Model(cfg).trace(StepSpec(rows=1, tokens=T, capacity=32, paged=True, pool_slots=64))
+        prog = compile_graph(g)
+        census = collections.Counter(k for p in prog.plans if p.kind == "dispatch" for k in p.kernels)
+        assert census[kernel] == 1 and census["poot_attn_paged"] == 1 and census["poot_rope_kv_write"] == 1
+    from poot_b200.plan.planner import plan_eqn
+    scan = next(e for e in g.eqns if e.op == "scan")
+    import dataclasses
+    odd = dataclasses.replace(scan, attrs={**scan.attrs, "family": "prefix_sum"})
+    with pytest.raises(Refusal):
+        plan_eqn(g, 0, odd)
