@@ -31,6 +31,14 @@ __global__ void tp_begin_step_kernel(int* epoch, int* status) {
   }
 }
 
+// Last kernel of a tensor-parallel step: the step deadline is cleared, so kernels of steps that do not start with
+// tp_begin_step (steps on the library collectives, single-rank work on the same device) never read a stale one.
+__global__ void tp_end_step_kernel(int* status) {
+  pdl_wait(); pdl_launch();
+  if (threadIdx.x == 0 && blockIdx.x == 0 && status != nullptr)
+    *reinterpret_cast<volatile unsigned long long*>(status + 2) = 0ull;
+}
+
 // Greedy pick over vocabulary shards.  grid = rows, one warp per row.  `part_local` is this rank's stage-1 table
 // [rows, groups, 3] (value bits, global index, first non-finite index).  Each CTA copies its row's slice into every
 // peer's exchange area, the last CTA to finish publishes the exchange number on channel TP_CH_AX, then each CTA
@@ -213,6 +221,10 @@ POOT_API int poot_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 // First kernel of a tensor-parallel step: epoch += 1, control block deadline = now + the block's step budget.
 POOT_API int poot_tp_begin_step(int* epoch, int* status, cudaStream_t s) {
   return launch_k(tp_begin_step_kernel, dim3(1), dim3(32), 0, s, epoch, status);
+}
+
+POOT_API int poot_tp_end_step(int* status, cudaStream_t s) {
+  return launch_k(tp_end_step_kernel, dim3(1), dim3(32), 0, s, status);
 }
 
 // Greedy pick over `world` vocabulary shards through the symmetric block (no library collective).

@@ -129,7 +129,9 @@ class FusedComm(NcclComm):
         K.register_signature("poot_gemm_skinny_tp", [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                                      c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, c_int, _P,
                                                      _P, _P])
+        K.register_signature("poot_tp_end_step", [_P, _P])
         self._begin = K.fn("poot_tp_begin_step")
+        self._end = K.fn("poot_tp_end_step")
         self._norm = K.fn("poot_tp_norm")
         self._gemm = K.fn("poot_gemm_skinny_tp")
 
@@ -146,6 +148,11 @@ class FusedComm(NcclComm):
     def begin_step(self) -> None:
         """First launch of a fused step: advances the epoch and starts the step's wait budget."""
         check(self._begin(self.epoch.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()), "tp_begin_step")
+
+    def end_step(self) -> None:
+        """Last launch of a fused step: clears the step deadline, so a later step that does not begin with
+        ``begin_step`` (one on the library collectives) is not judged against a deadline that has passed."""
+        check(self._end(K.status_word(self.device).data_ptr(), K._stream()), "tp_end_step")
 
     def argmax_exchange(self, part: torch.Tensor, rows: int, groups: int, vocab_total: int, out: torch.Tensor) -> None:
         """Greedy pick over the ranks' vocabulary shards: push this rank's stage-1 table ``part`` [rows, groups, 3]

@@ -937,6 +937,8 @@ class DecoderEngine:
         self._count()
         K.linear(self.xl[:B], w.lm_head, K.EPI_F32, self.logits_local[:B])
         self._sample(shape, self.logits_local[:B])
+        self._count()
+        comm.end_step()
 
     def _forward_tp_fused(self, shape: StepShape, R: int) -> None:
         """Decode-sized step on the fused tensor-parallel path: the residual stream is sharded by token rows
@@ -980,6 +982,8 @@ class DecoderEngine:
             local = self.logits_sel[:B]
             K.gather_rows(self.logits_local[:R], self.logit_idx[:B], local)
         self._sample(shape, local)
+        self._count()
+        comm.end_step()
 
     def _moe(self, l, L, x, T, h=None):
         from . import moe as _moe

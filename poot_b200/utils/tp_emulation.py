@@ -160,6 +160,9 @@ class EmulatedFusedComm:
         c = self.g.ctl[self.rank]
         c["deadline"] = time.monotonic() + c["budget"] if c["budget"] else 0.0
 
+    def end_step(self) -> None:
+        self.g.ctl[self.rank]["deadline"] = 0.0
+
     def gemm_allreduce(self, x, W, rows: int, rs_site: int) -> None:
         y = E._bf(x[:rows].float() @ W.float().T)
         target = self._target(rs_site, self.rs_sites)
