@@ -96,15 +96,12 @@ def device_identity(llm) -> Dict[str, object]:
 
 
 def memory_classes(llm) -> Optional[Dict[str, int]]:
-    eng = llm.engine
-    if eng is None:
+    """Bytes by class as the engine counts its own buffers (weights, K/V and recurrent state, workspace, staging)."""
+    if llm.engine is None:
         return None
-    kv = sum(int(t.numel() * t.element_size()) for t in (getattr(eng.pool, "k", None), getattr(eng.pool, "v", None))
-             if t is not None) if getattr(eng, "pool", None) is not None else 0
-    import torch
-    total = int(torch.cuda.memory_allocated()) if torch.cuda.is_available() else 0
-    w = int(eng.w.nbytes()) if hasattr(eng.w, "nbytes") else 0
-    return {"weights_bytes": w, "kv_bytes": kv, "workspace_bytes": max(0, total - w - kv), "staging_bytes": 0}
+    from poot_b200.profile.memory import account
+    inner = getattr(llm.driver.engine, "inner", llm.driver.engine)
+    return account(llm.engine, inner).classes()
 
 
 def run_cell(model: str, scenario: str, isl: int, osl: int, repeat: int = 1, requests: int = 1, rows: int = 1,

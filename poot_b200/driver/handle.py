@@ -215,12 +215,12 @@ def to_device(w: PackedWeight, device, keep_packed: bool = True):
             ops = {k: torch.from_numpy(np.array(v)).to(device) for k, v in w.planar.items()}     # a copy: the mapped file is read-only
             return K.PlanarWeight(w.format, ops, w.shape[0], w.shape[1], w.group)
         return torch.from_numpy(w.to_f32()).to(device=device, dtype=torch.bfloat16)
+    from ..runtime.upload import upload       # stored bytes go to the device through the pinned ring, as stored
     if keep_packed and d.device_gemv and len(w.shape) == 2 and w.shape[1] % 256 == 0:
-        raw = torch.from_numpy(np.ascontiguousarray(w.payload).view(np.uint8).reshape(-1).copy())
-        return K.QuantWeight(w.format, raw.to(device), w.shape[0], w.shape[1])
+        raw = upload(np.ascontiguousarray(w.payload).view(np.uint8).reshape(-1), device, torch.uint8)
+        return K.QuantWeight(w.format, raw, w.shape[0], w.shape[1])
     if w.format == "BF16":
-        t = torch.from_numpy(np.ascontiguousarray(w.payload).view(np.uint16).reshape(w.shape).copy()).view(torch.bfloat16)
-        return t.to(device)
+        return upload(np.ascontiguousarray(w.payload).view(np.uint16).reshape(w.shape), device, torch.bfloat16)
     return torch.from_numpy(w.to_f32()).to(device=device, dtype=torch.bfloat16)
 
 

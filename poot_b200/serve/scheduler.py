@@ -81,6 +81,7 @@ class ServeEngine:
         self._thread: Optional[threading.Thread] = None
         self._stop = threading.Event()
         self.on_step = on_step
+        self._memory_roles = None
         self.draft = draft                   # draft policy (``propose(tokens)``) used while one greedy sequence is live
         self.timing = timing                 # profile.TimingSnapshot, or None: counters only
         self.busy_s = 0.0
@@ -399,6 +400,15 @@ class ServeEngine:
         m.set("poot_kv_blocks_total", kv["blocks_total"])
         up = max(time.time() - m.started, 1e-9)
         m.set("poot_gpu_active_ratio", min(1.0, self.busy_s / up))
+        if self._memory_roles is None:          # bytes by buffer role: fixed once the engine is built, counted once
+            self._memory_roles = {}
+            inner = getattr(d.engine, "inner", d.engine)
+            eng = getattr(inner, "e", None)
+            if eng is not None and hasattr(eng, "kv"):
+                from ..profile.memory import account
+                self._memory_roles = account(eng, inner).bytes_by_role
+            for role, n in self._memory_roles.items():
+                m.set(f"poot_memory_{role}_bytes", n)
 
     def health(self) -> dict:
         h = {"status": self.state}
