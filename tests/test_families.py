@@ -77,12 +77,14 @@ def test_supported_family_traces_compiles_and_decodes(name):
         last = steps.step(toks[:, t:t + 1])
     assert np.isfinite(full).all() and np.allclose(last, full, rtol=2e-5, atol=1e-5)
     if cfg.is_recurrent:
-        # the recurrence has no device kernel family yet: the planner says so with a typed refusal naming the equation
+        # the recurrence is planned on its scan kernel, one launch per recurrent layer, and the rewritten graph still
+        # evaluates to the same logits
         from poot_b200.models.model import StepSpec
-        from poot_b200.plan.refusal import Refusal
-        with pytest.raises(Refusal) as e:
-            compile_graph(model.trace(StepSpec(rows=1, tokens=4, capacity=32)))
-        assert e.value.op == "scan"
+        prog = compile_graph(model.trace(StepSpec(rows=1, tokens=4, capacity=32)))
+        scans = [k for p in prog.plans if p.kind == "dispatch" for k in p.kernels if k in ("poot_gdn_scan", "poot_ssd_scan")]
+        assert len(scans) == sum(1 for k in cfg.layer_kinds if k in ("gdn", "mamba"))
+        rewritten = OracleSession(model, w, capacity=32, graph_transform=lambda g: compile_graph(g).graph).step(toks)
+        assert np.allclose(rewritten, full, rtol=2e-5, atol=1e-5)
         return
     progs = []
 
