@@ -141,3 +141,20 @@ def test_ctypes_signatures_match_the_c_declarations():
         if list(sig) != want:
             bad.append((name, [getattr(t, "__name__", t) for t in sig], [getattr(t, "__name__", t) for t in want]))
     assert not bad, bad
+
+
+def test_every_typed_error_is_named_by_a_test():
+    """Variant coverage: an exception class the package defines must appear by name in some test, so a refusal or
+    failure path nobody exercises cannot be added silently (the reference's ``scripts/check-variant-coverage.py``)."""
+    import re
+    pat = re.compile(r"(Error|Exception|Refus\w*|Unavailable|Incompatible|Fault|Timeout|Lost|Failed|Missing|Overrun|"
+                     r"NeedsReset|Poisoned|Validation|OutOfRange|TooSmall|Exceeded|Layout)$")
+    classes = {}
+    for path in _py_files(PKG):
+        for node in ast.walk(ast.parse(open(path).read(), path)):
+            if isinstance(node, ast.ClassDef) and pat.search(node.name) and node.bases:
+                classes[node.name] = os.path.relpath(path, ROOT)
+    here = os.path.dirname(__file__)
+    tests = "".join(open(os.path.join(here, f)).read() for f in os.listdir(here) if f.endswith(".py"))
+    missing = sorted((c, p) for c, p in classes.items() if not re.search(r"\b" + c + r"\b", tests))
+    assert len(classes) > 30 and not missing, missing
