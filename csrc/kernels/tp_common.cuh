@@ -12,6 +12,7 @@
 // bumped once per step, so the value to signal / wait for is (epoch-1)*sites + site + 1 and nothing
 // is ever reset between CUDA-graph replays.  Buffers are double-buffered on the parity of that value.
 //
+//   ch 3 = greedy-pick exchange, ch 4 / 5 = expert-parallel dispatch / combine (ep_exchange.cu)
 //   ch 2 = poison: flags[2 * 8 + src] != 0 means rank `src` recorded a failure; it is published with the rank's
 //          next signal, and every wait on this rank that sees it gives up with kPeerFailed, so one rank's failure
 //          reaches all ranks within one site instead of leaving them to compute on stale inboxes
@@ -36,7 +37,9 @@ constexpr int TP_CH_RS = 0;
 constexpr int TP_CH_AG = 1;
 constexpr int TP_CH_POISON = 2;
 constexpr int TP_CH_AX = 3;       // "my greedy-pick partial table of exchange n has landed in your exchange area"
-constexpr int TP_FLAG_WORDS = 4 * TP_MAX_WORLD;
+constexpr int TP_CH_EPD = 4;      // "the rows of exchange n that I route to your experts have landed in your receive area"
+constexpr int TP_CH_EPC = 5;      // "your rows of exchange n, through my experts, have landed in your combine area"
+constexpr int TP_FLAG_WORDS = 6 * TP_MAX_WORLD;
 // Limit of one wait when the control block carries no step deadline (plain kernel tests): about 1 s.
 constexpr long long kFlagWaitBudgetCycles = 2000000000LL;
 

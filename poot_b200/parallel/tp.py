@@ -30,7 +30,7 @@ from ..ops._lib import check, kernels
 from .guarded_layout import CommBufferOverrun, GuardedLayout
 from .symm import SymmetricBlock
 
-FLAG_BYTES = 4 * 8 * 4             # four channels of eight int32 flag words (tp_common.cuh: TP_FLAG_WORDS)
+FLAG_BYTES = 6 * 8 * 4             # six channels of eight int32 flag words (tp_common.cuh: TP_FLAG_WORDS)
 
 _P = c_void_p
 
@@ -101,7 +101,16 @@ class FusedComm(NcclComm):
         # greedy-pick exchange: [2][world][ax_cap] int32, one stage-1 table [rows, groups, 3] per rank and parity
         self.ax_cap = engine.max_seqs * K.argmax_groups(max(1, engine.cfg.vocab // w)) * 3
         ax_bytes = 2 * w * self.ax_cap * 4
-        self.layout = GuardedLayout([("flags", FLAG_BYTES), ("inbox", inbox_bytes), ("xs", xs_bytes), ("ax", ax_bytes)])
+        regions = [("flags", FLAG_BYTES), ("inbox", inbox_bytes), ("xs", xs_bytes), ("ax", ax_bytes)]
+        self.ep_cap = 0
+        cfg = engine.cfg
+        if cfg.is_moe and getattr(engine.w, "ep_world", 1) == w:
+            # expert-parallel exchange over a token-sharded stream: receive area [2][world][cap][H] with its metadata
+            # and counts, combine area [2][cap][H]; cap = a rank's (token, slot) rows of the largest sharded step
+            self.ep_cap = self.s_max * cfg.top_k
+            regions += [("ep_recv", 2 * w * self.ep_cap * H * 2), ("ep_meta", 2 * w * self.ep_cap * 16),
+                        ("ep_count", 2 * w * 4), ("ep_back", 2 * self.ep_cap * H * 2)]
+        self.layout = GuardedLayout(regions)
         self.off_flags, self.off_inbox = self.layout.offset("flags"), self.layout.offset("inbox")
         self.off_xs, self.off_ax = self.layout.offset("xs"), self.layout.offset("ax")
         self.block = SymmetricBlock(self.layout.total, self.rank, w, self.device, self.group)
@@ -113,6 +122,21 @@ class FusedComm(NcclComm):
         self.inbox_peer = self.block.ptr_array(self.off_inbox)
         self.xs_peer = self.block.ptr_array(self.off_xs)
         self.ax_peer = self.block.ptr_array(self.off_ax)
+        if self.ep_cap:
+            i32 = dict(dtype=torch.int32, device=self.device)
+            self.ep_peers = [self.block.ptr_array(self.layout.offset(n)) for n in ("ep_recv", "ep_meta", "ep_count", "ep_back")]
+            self.ep_sites = engine.cfg.n_layers
+            self.ep_dest, self.ep_dpos = torch.zeros(self.ep_cap, **i32), torch.zeros(self.ep_cap, **i32)
+            self.ep_counts = torch.zeros(8, **i32)
+            self.ep_ids = torch.zeros(w * self.ep_cap, **i32)
+            self.ep_gate = torch.zeros(w * self.ep_cap, dtype=torch.float32, device=self.device)
+            ep_common = [c_int] * 9 + [_P] * 9
+            K.register_signature("poot_ep_plan", [_P, c_int, c_int, c_int, _P, _P, _P, _P])
+            K.register_signature("poot_ep_dispatch", [_P, c_int, _P, _P, _P, _P, _P] + ep_common)
+            K.register_signature("poot_ep_mask", [_P, _P, _P, _P] + ep_common)
+            K.register_signature("poot_ep_gather", [_P, _P, _P, _P, c_int, c_int, _P, _P] + ep_common)
+            K.register_signature("poot_ep_combine", [_P, _P, _P] + ep_common)
+            K.register_signature("poot_ep_finish", [_P, _P] + ep_common)
         self.ax_count = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.ticket = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -210,6 +234,57 @@ class FusedComm(NcclComm):
                          self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer, self.inbox_peer,
                          self.H, 0, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
               "gemm_skinny_tp")
+
+    # ---- expert-parallel exchange over the token-sharded stream (csrc/kernels/ep_exchange.cu) ---------------------------
+    def norm_local(self, w: torch.Tensor, x_out: torch.Tensor, S: int, eps: float, rs_site: int) -> None:
+        """Reduce the inboxes of ``rs_site`` (if >= 0) into the residual shard and normalise this rank's own rows into
+        ``x_out``; nothing is published (the expert exchange sends each row only where its experts are)."""
+        b = self.block
+        check(self._norm(self.h_shard.data_ptr(), b.ptr(self.rank, self.off_inbox), w.data_ptr(), None, x_out.data_ptr(), S,
+                         self.H, float(eps), self.world, self.rank, S, 0, self.ag_sites, rs_site, self.rs_sites,
+                         self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer,
+                         self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()), "tp_norm")
+
+    def _ep_common(self, S: int, k: int, e_local: int, site: int):
+        b = self.block
+        return (self.world, self.rank, S, k, self.ep_cap, self.H, e_local, site, self.ep_sites, self.epoch.data_ptr(),
+                b.ptr(self.rank, self.off_flags), self.flags_peer, *self.ep_peers, self.ticket.data_ptr(),
+                K.status_word(self.device).data_ptr(), K._stream())
+
+    def _ep_local(self, name: str) -> int:
+        return self.block.ptr(self.rank, self.layout.offset(name))
+
+    def ep_dispatch(self, x: torch.Tensor, ids: torch.Tensor, gates: torch.Tensor, S: int, k: int, e_local: int,
+                    site: int) -> None:
+        """Send every (token, slot) row of this rank's ``S`` tokens to the rank that holds its expert."""
+        n = S * k
+        check(K.fn("poot_ep_plan")(ids.data_ptr(), n, e_local, self.world, self.ep_dest.data_ptr(), self.ep_dpos.data_ptr(),
+                                   self.ep_counts.data_ptr(), K._stream()), "ep_plan")
+        check(K.fn("poot_ep_dispatch")(x.data_ptr(), x.stride(0), ids.data_ptr(), gates.data_ptr(), self.ep_dest.data_ptr(),
+                                       self.ep_dpos.data_ptr(), self.ep_counts.data_ptr(), *self._ep_common(S, k, e_local, site)),
+              "ep_dispatch")
+
+    def ep_mask(self, S: int, k: int, e_local: int, site: int):
+        """Wait for every rank's rows; returns ``(expert ids or -1, gates)`` over the ``world * cap`` receive slots."""
+        check(K.fn("poot_ep_mask")(self._ep_local("ep_meta"), self._ep_local("ep_count"), self.ep_ids.data_ptr(),
+                                   self.ep_gate.data_ptr(), *self._ep_common(S, k, e_local, site)), "ep_mask")
+        return self.ep_ids, self.ep_gate
+
+    def ep_gather(self, sorted_rows, n_tiles, block: int, max_tiles: int, xs, gate_sorted, S: int, k: int, e_local: int,
+                  site: int) -> None:
+        check(K.fn("poot_ep_gather")(self._ep_local("ep_recv"), sorted_rows.data_ptr(), self.ep_gate.data_ptr(),
+                                     n_tiles.data_ptr(), block, max_tiles, xs.data_ptr(), gate_sorted.data_ptr(),
+                                     *self._ep_common(S, k, e_local, site)), "ep_gather")
+
+    def ep_combine(self, y: torch.Tensor, pos: torch.Tensor, S: int, k: int, e_local: int, site: int) -> None:
+        """Send every result row back to the rank that owns its token."""
+        check(K.fn("poot_ep_combine")(y.data_ptr(), pos.data_ptr(), self._ep_local("ep_meta"),
+                                      *self._ep_common(S, k, e_local, site)), "ep_combine")
+
+    def ep_finish(self, S: int, k: int, e_local: int, site: int) -> None:
+        """Wait for every rank's results and add each token's ``k`` rows to the residual shard, in slot order."""
+        check(K.fn("poot_ep_finish")(self.h_shard.data_ptr(), self._ep_local("ep_back"),
+                                     *self._ep_common(S, k, e_local, site)), "ep_finish")
 
     def _write_guards(self) -> None:
         def store(off, words):

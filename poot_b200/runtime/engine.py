@@ -491,6 +491,8 @@ class DecoderEngine:
             # expert parallelism rides the one-shot path: the experts' combine is the fused all-reduce (one expert per
             # rank pushes from its GEMM epilogue, several per rank from the combine kernel)
             fusable = w.ep_world == self.tp and w.layers[0].ex_wgu is not None
+            if fusable and self.tp_mode == "rs_ag" and getattr(comm, "ep_cap", 0) and w.layers[0].sh_wgu is None:
+                return bool(comm.rows_for(T))        # token-sharded stream: experts reached by dispatch / combine exchanges
             return bool(fusable and comm.oneshot_ok(T))
         if comm.oneshot_ok(T) and self.tp_mode != "rs_ag":
             return True
@@ -510,7 +512,7 @@ class DecoderEngine:
             return self.program.run(shape)      # the plain decoder layer: a walk over the compiled plan's launch list
         if self._fused_shape(shape):
             self._fused_step = True
-            if self.comm.oneshot_ok(T) and (self.tp_mode != "rs_ag" or cfg.is_moe):
+            if self.comm.oneshot_ok(T) and (self.tp_mode != "rs_ag" or (cfg.is_moe and not getattr(self.comm, "ep_cap", 0))):
                 return self._forward_tp_oneshot(shape)
             return self._forward_tp_fused(shape, self.comm.rows_for(T))
         self._launch_counter = 0
@@ -953,10 +955,10 @@ class DecoderEngine:
         K.embed_gather(self.tokens[r0:r0 + S], w.embed, out=comm.h_shard[:S])
         if cfg.embed_scale != 1.0:
             K.scale_(comm.h_shard[:S], cfg.embed_scale)
-        ag, rs = 0, -1
+        ag, rs, pending_rs = 0, -1, -1       # pending_rs: the reduce-scatter site whose inboxes the next norm still has to add
         for l, L in enumerate(w.layers):
             self._count(5 + (1 if self._attn_splits(R) > 1 else 0))
-            comm.norm(L.ln1, S, cfg.norm_eps, ag_site=ag, rs_site=rs)
+            comm.norm(L.ln1, S, cfg.norm_eps, ag_site=ag, rs_site=pending_rs)
             comm.gemm(K.EPI_STORE, None, L.wqkv, self.qkv[:R], S, ag_site=ag)
             if L.bqkv is not None:
                 K.bias_add_(self.qkv[:R], L.bqkv)
@@ -966,14 +968,27 @@ class DecoderEngine:
             rs += 1
             comm.gemm(K.EPI_STORE, self.attn[:R], L.wo, None, S, rs_site=rs)
             ag += 1
+            if cfg.moe_layer(w.layer0 + l):
+                # routed experts over the token-sharded stream: this rank's rows are normalised locally, each goes to
+                # the ranks of its experts and its results come back (no all-gather, no reduce-scatter at this site)
+                from . import moe as _moe
+                x_own = self.x[:S]
+                self._count()
+                comm.norm_local(L.ln2, x_own, S, cfg.norm_eps, rs_site=rs)
+                _moe.moe_forward_sharded(self, l, L, x_own, S, comm, site=l)
+                rs += 1
+                ag += 1
+                pending_rs = -1
+                continue
             self._count(3)
             comm.norm(L.ln2, S, cfg.norm_eps, ag_site=ag, rs_site=rs)
             comm.gemm(K.EPI_SWIGLU, None, L.wgu, self.act[:R], S, ag_site=ag)
             rs += 1
             comm.gemm(K.EPI_STORE, self.act[:R], L.wdown, None, S, rs_site=rs)
             ag += 1
+            pending_rs = rs
         self._count(2)
-        comm.norm(w.final_norm, S, cfg.norm_eps, ag_site=ag, rs_site=rs)
+        comm.norm(w.final_norm, S, cfg.norm_eps, ag_site=ag, rs_site=pending_rs)
         comm.gemm(K.EPI_F32, None, w.lm_head, self.logits_local[:R], S, ag_site=ag)
         if B == T:
             local = self.logits_local[:B]

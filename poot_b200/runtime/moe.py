@@ -240,6 +240,55 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
     return None
 
 
+def moe_forward_sharded(eng, l: int, L, x: torch.Tensor, S: int, comm, site: int) -> None:
+    """Routed experts over a token-sharded residual stream (the reduce-scatter form of tensor parallelism with the experts
+    split over the same ranks): ``x[S, H]`` are THIS rank's normalised rows.  Router and top-k run on them; every
+    (token, slot) row is dispatched to the rank that holds its expert; that rank groups what it received by expert, runs
+    the two grouped GEMMs and sends each result row back; the owner adds its tokens' ``k`` rows to its residual shard
+    (``comm.h_shard``).  Dispatch and combine are the all-to-all exchanges of ``csrc/kernels/ep_exchange.cu``."""
+    c = eng.cfg
+    E, k, F, H = c.n_experts, c.top_k, c.moe_ffn, c.hidden
+    buf = _buffers(eng)
+    e_local = L.ex_wgu.shape[0]
+    e0 = eng.w.ep_rank * e_local
+    logits = buf["logits"][:S]
+    eng._count(2)
+    K.linear(x, L.router, K.EPI_F32, logits)
+    if L.router_bias is not None:
+        eng._count()
+        K.bias_add_(logits, L.router_bias)
+    ids, gates = buf["ids"][:S * k], buf["gates"][:S * k]
+    dense = buf["dense"][:E * S].view(E, S)
+    M.moe_route(logits, k, c.norm_topk_prob, ids, gates, dense, mode=c.router, select_bias=L.select_bias,
+                scale=c.routed_scale, n_group=c.n_group, topk_group=c.topk_group)
+    eng._count(3)
+    comm.ep_dispatch(x, ids, gates, S, k, e_local, site)                 # plan + peer stores + flags
+    rids, _ = comm.ep_mask(S, k, e_local, site)                          # waits for every rank's rows
+    n = comm.world * comm.ep_cap
+    block = M.group_block(comm.world * S * k // comm.world, e_local)     # a rank receives S * k rows on average
+    max_tiles = M.group_capacity(n, e_local, block)
+    cap = max_tiles * block
+    g = _group_buffers(eng, cap, max_tiles, n)
+    pos, sorted_rows, tile_expert, n_tiles = g["pos"][:n], g["sorted_rows"][:cap], g["tile_expert"][:max_tiles], g["n_tiles"]
+    xs, gate_s, act, y = g["xs"][:cap], g["gate"][:cap], g["act"][:cap], g["y"][:cap]
+    eng._count(6)
+    M.moe_align(rids, e0, e_local, block, max_tiles, pos, sorted_rows, tile_expert, n_tiles)
+    comm.ep_gather(sorted_rows, n_tiles, block, max_tiles, xs, gate_s, S, k, e_local, site)
+    plain = buf["gu"] is None
+    up_out, up_epi = (act, K.EPI_SWIGLU) if plain else (g["gu"][:cap], K.EPI_STORE)
+    M.gemm_grouped(up_epi, xs, L.ex_wgu, up_out, block, max_tiles, group_expert=tile_expert, x_row_mul=block,
+                   out_group_stride=block * up_out.shape[1], ldo=up_out.shape[1])
+    if not plain:
+        _expert_act(eng, L, up_out, act, tile_expert, block, e0)
+    M.gemm_grouped(K.EPI_STORE, act, L.ex_wdown, y, block, max_tiles, group_expert=tile_expert, x_row_mul=block,
+                   out_group_stride=block * H, row_scale=gate_s, ldo=H)
+    if L.ex_bdown is not None:
+        eng._count()
+        K.bias_add_indexed_(y, L.ex_bdown, tile_expert, block, e0, gate=gate_s)
+    comm.ep_combine(y, pos, S, k, e_local, site)                         # peer stores + flags
+    comm.ep_finish(S, k, e_local, site)                                  # waits, then h_shard += the tokens' k rows
+
+
 def _group_buffers(eng, cap: int, max_tiles: int, n: int):
     """Scratch of the row-grouped regime, grown to the largest step seen (steps are captured per shape, so a buffer
     that a captured graph uses is never replaced: growth only happens before the first capture of a larger shape)."""

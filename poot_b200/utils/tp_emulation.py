@@ -22,7 +22,7 @@ import torch
 from ..ops import cuda_ops as K
 from . import kernel_emulation as E
 
-CH_RS, CH_AG, CH_POISON, CH_AX = 0, 1, 2, 3
+CH_RS, CH_AG, CH_POISON, CH_AX, CH_EPD, CH_EPC = 0, 1, 2, 3, 4, 5
 MAX_ROWS = 128
 OK, TIMEOUT_PEER_FLAG, ABORTED, STEP_DEADLINE, PEER_FAILED = 0, 4, 6, 7, 8
 NO_DEADLINE_BUDGET_S = 1.0
@@ -33,7 +33,7 @@ class EmulatedGroup:
 
     def __init__(self, world: int, hidden: int, ax_cap: int = 4096):
         self.world, self.H, self.ax_cap = world, hidden, ax_cap
-        self.flags = torch.zeros(world, 4, 8, dtype=torch.int64)
+        self.flags = torch.zeros(world, 6, 8, dtype=torch.int64)
         self.inbox = [torch.zeros(2, world, MAX_ROWS, hidden, dtype=torch.bfloat16) for _ in range(world)]
         self.xs = [torch.zeros(2, MAX_ROWS, hidden, dtype=torch.bfloat16) for _ in range(world)]
         self.ax = [torch.zeros(2, world, ax_cap, dtype=torch.int32) for _ in range(world)]
@@ -41,6 +41,18 @@ class EmulatedGroup:
         self.ctl = [dict(code=0, detail=-1, deadline=0.0, abort=0, budget=5.0, gave_up=0) for _ in range(world)]
         self.barrier = threading.Barrier(world)
         self.lock = threading.Lock()
+        self.ep_recv = self.ep_meta = self.ep_gatev = self.ep_count = self.ep_back = None
+
+    def ensure_ep(self, cap: int) -> None:
+        """Receive and combine areas of the expert-parallel exchange (first rank to attach a routed model makes them)."""
+        with self.lock:
+            if self.ep_recv is None:
+                w, H = self.world, self.H
+                self.ep_recv = [torch.zeros(2, w, cap, H, dtype=torch.bfloat16) for _ in range(w)]
+                self.ep_meta = [torch.zeros(2, w, cap, 4, dtype=torch.int32) for _ in range(w)]
+                self.ep_gatev = [torch.zeros(2, w, cap, dtype=torch.float32) for _ in range(w)]
+                self.ep_count = [torch.zeros(2, w, dtype=torch.int32) for _ in range(w)]
+                self.ep_back = [torch.zeros(2, cap, H, dtype=torch.bfloat16) for _ in range(w)]
 
     # ---- control block rules (csrc/kernels/common.cuh) ---------------------------------------------------------
     def fail(self, rank: int, code: int, detail: int = -1) -> None:
@@ -136,6 +148,10 @@ class EmulatedFusedComm:
         L = engine.cfg.n_layers
         self.rs_sites, self.ag_sites = 2 * L, 2 * L + 1
         self.partial = torch.zeros(engine.max_tokens, H, dtype=torch.bfloat16)
+        self.ep_cap, self.ep_sites = 0, L
+        if engine.cfg.is_moe and getattr(engine.w, "ep_world", 1) == self.world:
+            self.ep_cap = self.s_max * engine.cfg.top_k
+            self.g.ensure_ep(self.ep_cap)
 
     # ---- geometry (same rules as FusedComm) ----------------------------------------------------------------------
     def rows_for(self, T: int) -> int:
@@ -178,6 +194,84 @@ class EmulatedFusedComm:
             self.g.inbox[d][target & 1, self.rank, :rows] = y[:rows]
         self.log.append(("rs", rs_site, target))
         self.g.signal_all(self.rank, CH_RS, target)
+
+    # ---- expert-parallel exchange over the token-sharded stream ------------------------------------------------------
+    def norm_local(self, w, x_out, S: int, eps: float, rs_site: int) -> None:
+        if rs_site >= 0:
+            self._reduce(self.h_shard, S, rs_site)
+        E.rmsnorm(self.h_shard[:S], w, eps, out=x_out[:S])
+
+    def _ep_target(self, site: int) -> int:
+        return (self.epoch - 1) * self.ep_sites + site + 1
+
+    def ep_dispatch(self, x, ids, gates, S: int, k: int, e_local: int, site: int) -> None:
+        target = self._ep_target(site)
+        par, g = target & 1, self.g
+        counts = [0] * self.world
+        for i in range(S * k):
+            d = int(ids[i]) // e_local
+            p = counts[d]
+            counts[d] += 1
+            g.ep_recv[d][par, self.rank, p] = x[i // k]
+            g.ep_meta[d][par, self.rank, p] = torch.tensor([int(ids[i]), i, 0, 0], dtype=torch.int32)
+            g.ep_gatev[d][par, self.rank, p] = gates[i]
+        for d in range(self.world):
+            g.ep_count[d][par, self.rank] = counts[d]
+        self.log.append(("epd", site, target))
+        g.signal_all(self.rank, CH_EPD, target)
+
+    def ep_mask(self, S: int, k: int, e_local: int, site: int):
+        target = self._ep_target(site)
+        par, g = target & 1, self.g
+        ok = g.wait_all(self.rank, CH_EPD, target, site)
+        cap = self.ep_cap
+        ids = torch.full((self.world * cap,), -1, dtype=torch.int32)
+        gate = torch.zeros(self.world * cap, dtype=torch.float32)
+        if ok:
+            for src in range(self.world):
+                n = int(g.ep_count[self.rank][par, src])
+                ids[src * cap:src * cap + n] = g.ep_meta[self.rank][par, src, :n, 0]
+                gate[src * cap:src * cap + n] = g.ep_gatev[self.rank][par, src, :n]
+        self.ep_ids, self.ep_gate = ids, gate
+        return ids, gate
+
+    def ep_gather(self, sorted_rows, n_tiles, block: int, max_tiles: int, xs, gate_sorted, S: int, k: int, e_local: int,
+                  site: int) -> None:
+        par = self._ep_target(site) & 1
+        flat = self.g.ep_recv[self.rank][par].reshape(self.world * self.ep_cap, -1)
+        for p in range(int(n_tiles[0]) * block):
+            i = int(sorted_rows[p])
+            if i < 0:
+                xs[p].zero_()
+                gate_sorted[p] = 0.0
+            else:
+                xs[p] = flat[i]
+                gate_sorted[p] = self.ep_gate[i]
+
+    def ep_combine(self, y, pos, S: int, k: int, e_local: int, site: int) -> None:
+        target = self._ep_target(site)
+        par, g, cap = target & 1, self.g, self.ep_cap
+        for idx in range(self.world * cap):
+            p = int(pos[idx])
+            if p < 0:
+                continue
+            src = idx // cap
+            row = int(g.ep_meta[self.rank][par, src, idx - src * cap, 1])
+            g.ep_back[src][par, row] = y[p]
+        self.log.append(("epc", site, target))
+        g.signal_all(self.rank, CH_EPC, target)
+
+    def ep_finish(self, S: int, k: int, e_local: int, site: int) -> None:
+        target = self._ep_target(site)
+        par = target & 1
+        if not self.g.wait_all(self.rank, CH_EPC, target, site):
+            return
+        back = self.g.ep_back[self.rank][par]
+        for t in range(S):
+            v = self.h_shard[t].float()
+            for j in range(k):
+                v = v + back[t * k + j].float()
+            self.h_shard[t] = E._bf(v)
 
     def _reduce(self, h, rows: int, rs_site: int, slot_rows_from=None):
         target = self._target(rs_site, self.rs_sites)
