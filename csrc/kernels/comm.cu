@@ -31,6 +31,25 @@ __global__ void tp_begin_step_kernel(int* epoch, int* status) {
   }
 }
 
+// out[b, :] = gathered rows [idx[b], :] of this rank's gather buffer for site ag_site, after every rank's rows have
+// landed (the head of a prefill-sized step needs the few sampling rows, not all of them).  grid = rows, 128 threads.
+__global__ void __launch_bounds__(128)
+tp_gather_rows_kernel(const __nv_bfloat16* __restrict__ xs_local, const long long* __restrict__ idx,
+                      __nv_bfloat16* __restrict__ out, int H, int* status, const __grid_constant__ TpArgs tp) {
+  __shared__ int s_ok;
+  pdl_wait(); pdl_launch();
+  const uint32_t target = tp_target(tp, tp.ag_site, tp.ag_sites);
+  if (threadIdx.x == 0) s_ok = tp_wait_all(tp.flags_local, tp.world, TP_CH_AG, target, tp.ag_site, status) ? 1 : 0;
+  __syncthreads();
+  const int R = tp.world * tp.S;
+  long long r = idx[blockIdx.x];
+  if (!POOT_IN_RANGE(r, R, kSiteGatherRow) || r < 0 || r >= R) r = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(xs_local + ((size_t)(target & 1u) * R + (size_t)r) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * H);
+  for (int c = threadIdx.x; c < H / 8; c += blockDim.x)
+    dst[c] = s_ok ? __ldcg(src + c) : make_uint4(0u, 0u, 0u, 0u);      // written by peers: never from L1
+}
+
 // Last kernel of a tensor-parallel step: the step deadline is cleared, so kernels of steps that do not start with
 // tp_begin_step (steps on the library collectives, single-rank work on the same device) never read a stale one.
 __global__ void tp_end_step_kernel(int* status) {
@@ -221,6 +240,18 @@ POOT_API int poot_ipc_close(void* p) { return (int)cudaIpcCloseMemHandle(p); }
 // First kernel of a tensor-parallel step: epoch += 1, control block deadline = now + the block's step budget.
 POOT_API int poot_tp_begin_step(int* epoch, int* status, cudaStream_t s) {
   return launch_k(tp_begin_step_kernel, dim3(1), dim3(32), 0, s, epoch, status);
+}
+
+POOT_API int poot_tp_gather_rows(const void* xs_local, const long long* idx, void* out, int rows, int H, int world, int rank,
+                                 int S, int ag_site, int ag_sites, const int* epoch, void* flags_local, int* status,
+                                 cudaStream_t s) {
+  if (rows == 0) return 0;
+  if (H % 8 || world < 1 || world > TP_MAX_WORLD || ag_site < 0 || status == nullptr) return (int)cudaErrorInvalidValue;
+  TpArgs tp = {};
+  tp.world = world; tp.rank = rank; tp.S = S; tp.ag_site = ag_site; tp.ag_sites = ag_sites; tp.rs_site = -1; tp.epoch = epoch;
+  tp.flags_local = (uint32_t*)flags_local;
+  return launch_k(tp_gather_rows_kernel, dim3(rows), dim3(128), 0, s, (const __nv_bfloat16*)xs_local, idx,
+                  (__nv_bfloat16*)out, H, status, tp);
 }
 
 POOT_API int poot_tp_end_step(int* status, cudaStream_t s) {

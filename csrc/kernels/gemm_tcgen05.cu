@@ -17,7 +17,9 @@
 // crates/poot-graph-plan/src/passes/fuse.rs ContractionEpilogue).  The reference lowers this
 // family to wmma m16n16k16 for sm_80; this file is the sm_100a design.
 #include "tc_common.cuh"
+#include "tp_common.cuh"
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 #include <cstring>
 
@@ -115,13 +117,25 @@ struct TileGroups {
   const float* row_scale;
 };
 
-template <int BN, int STAGES, int EPI, bool GROUPED = false>
+// Tensor-parallel form (prefill-sized steps of the token-sharded program, more than 128 padded rows): the policy type
+// carries the peer pointers.  With ag_site >= 0 the X operand is this rank's gather buffer [2][world * S][K] (every rank
+// pushed its normalised rows into it): the producer waits for the ranks' flags of the site, then loads tiles of the
+// buffer half the site's parity names (plain TMA loads of local memory, no multicast).  With rs_site >= 0 the bf16
+// result is not stored locally: each output row goes to the inbox of the rank that owns the token row
+// (row / S), into this rank's slot, and the last CTA publishes the site's flag - GEMM + reduce-scatter in one kernel;
+// the consumer is the same reduce + norm kernel as for decode-sized steps.
+struct NoTp {};
+__device__ __forceinline__ void gemm_fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+
+template <int BN, int STAGES, int EPI, bool GROUPED = false, typename TP = NoTp>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          void* __restrict__ out, const __nv_bfloat16* __restrict__ resid, int M, int N, int K,
                          int ldo, int k_tiles_per_split, long long partial_stride, int* __restrict__ status,
-                         const TileGroups grp) {
+                         const TileGroups grp, const __grid_constant__ TP tp) {
+  constexpr bool kTp = !std::is_same<TP, NoTp>::value;
   using S = GemmSmem<BN, STAGES>;
+  __shared__ volatile int s_cta_fail;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = tc::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -152,6 +166,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   }
 
   if (threadIdx.x == 0) {
+    s_cta_fail = 0;
     for (int s = 0; s < STAGES; ++s) { tc::mbar_init(full_bar + 8 * s, 1); tc::mbar_init(empty_bar + 8 * s, 1); }
     tc::mbar_init(accum_bar, 1);
     tc::fence_barrier_init();
@@ -172,6 +187,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       tc::tma_prefetch_desc(&tmB);
       int issued = 0;
       bool ok = true;
+      int a_row0 = m0;
+      if constexpr (kTp) {
+        if (tp.world > 1 && tp.ag_site >= 0) {
+          const uint32_t target = tp_target(tp, tp.ag_site, tp.ag_sites);
+          a_row0 = (int)(target & 1u) * (tp.world * tp.S) + m0;
+          // If a flag does not arrive the cause is recorded and the kernel goes on over whatever the buffer holds: the
+          // ring keeps moving, the kernel ends at once and the host sees the failure with the step's result.
+          tp_wait_all(tp.flags_local, tp.world, TP_CH_AG, target, tp.ag_site, status);
+          gemm_fence_proxy_async_global();   // the rows were written with ordinary (peer) stores; TMA reads them
+        }
+      }
       for (int i = 0; i < num_kt; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
@@ -179,11 +205,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         tc::mbar_expect_tx(full_bar + 8 * s, S::STAGE_BYTES);
         const uint32_t sa = base + s * S::STAGE_BYTES;
         const int kx = (kt_begin + i) * GEMM_BK;
-        tc::tma_load_2d(sa, &tmA, kx, m0, full_bar + 8 * s);
+        tc::tma_load_2d(sa, &tmA, kx, a_row0, full_bar + 8 * s);
         tc::tma_load_2d(sa + S::A_BYTES, &tmB, kx, w_n0, full_bar + 8 * s);
         ++issued;
       }
       if (!ok) {
+        s_cta_fail = 1;
         ctl_fail(status, (int)kTimeoutProducer);
         // let the copies already in flight land before the CTA can exit
         for (int j = (issued > STAGES ? issued - STAGES : 0); j < issued; ++j)
@@ -197,7 +224,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       for (int i = 0; i < num_kt; ++i) {
         const int s = i % STAGES;
         const uint32_t ph = (uint32_t)(i / STAGES) & 1u;
-        if (!tc::mbar_wait(full_bar + 8 * s, ph)) { ok = false; break; }
+        // gathered form: the first tile arrives only after the producer's wait for the peers' flags, whose limit is the
+        // step deadline; this wait's limit is the later one
+        const bool arrived = (kTp && i == 0) ? tc::mbar_wait_dependent(full_bar + 8 * s, ph, status, &s_cta_fail)
+                                             : tc::mbar_wait(full_bar + 8 * s, ph);
+        if (!arrived) { ok = false; break; }
         tc::tc_fence_after();
         const uint32_t sa = base + s * S::STAGE_BYTES;
         const uint64_t adesc = tc::smem_desc_sw128(sa);
@@ -217,9 +248,21 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     // ---- epilogue warps: TMEM lane quadrant = warp % 4 ----
     const int quad = warp & 3;
     const int row = m0 + quad * 32 + lane;
-    const bool ok = __all_sync(0xffffffffu, tc::mbar_wait(accum_bar, 0));  // one verdict per warp (warp-wide loads below)
+    // one verdict per warp (the tensor-memory loads below are warp-wide instructions)
+    const bool ok = __all_sync(0xffffffffu, kTp ? tc::mbar_wait_dependent(accum_bar, 0, status, nullptr)
+                                               : tc::mbar_wait(accum_bar, 0));
     if (!ok && lane == 0) ctl_fail(status, (int)kTimeoutEpilogue);
     tc::tc_fence_after();
+    bool scatter = false;
+    __nv_bfloat16* peer_row = nullptr;       // this output row in its owner's inbox (scattered form)
+    if constexpr (kTp) {
+      scatter = tp.world > 1 && tp.rs_site >= 0 && EPI == GEPI_STORE;
+      if (scatter && row < M) {
+        const int parity = (int)(tp_target(tp, tp.rs_site, tp.rs_sites) & 1u);
+        const int owner = row / tp.S, local = row - owner * tp.S;
+        peer_row = tp.inbox_peer[owner] + ((size_t)((parity * tp.world + tp.rank) * tp.S + local)) * tp.ld_inbox;
+      }
+    }
     if (ok && !dead) {
       const float rs = (GROUPED && grp.row_scale != nullptr && row < M) ? grp.row_scale[row] : 1.f;
 #pragma unroll 1
@@ -261,7 +304,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
               }
             }
           } else {
-            __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldo + n;
+            __nv_bfloat16* orow = scatter ? peer_row + n : reinterpret_cast<__nv_bfloat16*>(out) + (size_t)row * ldo + n;
             const __nv_bfloat16* rrow = resid + (size_t)row * ldo + n;
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -294,6 +337,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     __syncwarp();
     tc::tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
   }
+  if constexpr (kTp) {
+    // every CTA arrives (all threads: the call contains a barrier); the last one publishes the site's flag everywhere
+    if (tp.world > 1 && tp.rs_site >= 0 && EPI == GEPI_STORE)
+      tp_signal_all(tp, TP_CH_RS, tp_target(tp, tp.rs_site, tp.rs_sites), (int)(gridDim.x * gridDim.y * gridDim.z), status);
+  }
 }
 
 template <int BN, int STAGES, int EPI>
@@ -311,7 +359,7 @@ static int launch_gemm_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* o
   int per = (total_kt + splits - 1) / splits;
   dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN, splits);
   return launch_k(kern, grid, dim3(GEMM_THREADS), (size_t)S::TOTAL, s, ta, tb, out, (const __nv_bfloat16*)resid, M, N, K,
-                  ldo, per, partial_stride, status, TileGroups{nullptr, 0, nullptr});
+                  ldo, per, partial_stride, status, TileGroups{nullptr, 0, nullptr}, NoTp{});
 }
 
 template <int BN, int STAGES>
@@ -341,7 +389,25 @@ static int launch_gemm_grouped_cfg(const CUtensorMap& ta, const CUtensorMap& tb,
   const int total_kt = (K + GEMM_BK - 1) / GEMM_BK;
   dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN, 1);
   return launch_k(kern, grid, dim3(GEMM_THREADS), (size_t)S::TOTAL, s, ta, tb, out, (const __nv_bfloat16*)nullptr, M, N, K,
-                  ldo, total_kt, 0LL, status, grp);
+                  ldo, total_kt, 0LL, status, grp, NoTp{});
+}
+
+template <int EPI>
+static int launch_gemm_tp_cfg(const CUtensorMap& ta, const CUtensorMap& tb, void* out, int M, int N, int K, int ldo,
+                              const TpArgs& tp, int* status, cudaStream_t s) {
+  constexpr int BN = 128, STAGES = 3;
+  using S = GemmSmem<BN, STAGES>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, STAGES, EPI, false, TpArgs>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int total_kt = (K + GEMM_BK - 1) / GEMM_BK;
+  dim3 grid((M + GEMM_BM - 1) / GEMM_BM, (N + BN - 1) / BN, 1);
+  return launch_k(kern, grid, dim3(GEMM_THREADS), (size_t)S::TOTAL, s, ta, tb, out, (const __nv_bfloat16*)nullptr, M, N, K,
+                  ldo, total_kt, 0LL, status, TileGroups{nullptr, 0, nullptr}, tp);
 }
 
 }  // namespace poot
@@ -393,5 +459,42 @@ POOT_API int poot_gemm_bf16_tcgen05(int epi, const void* x, const void* W, void*
     case 128: return launch_gemm_epi<128, 3>(epi, ta, tb, out, resid, M, N, K, ldo, splits, partial_stride, status, s);
     case 256: return launch_gemm_epi<256, 4>(epi, ta, tb, out, resid, M, N, K, ldo, splits, partial_stride, status, s);
     default: return (int)cudaErrorInvalidValue;
+  }
+}
+
+// Tiled GEMM of the token-sharded tensor-parallel program for steps above 128 padded rows (see the policy comment at
+// the kernel).  M = world * S padded rows, a multiple of 128.
+//   ag_site >= 0: `x` is this rank's gather buffer [2 * M, K] bf16 (double-buffered on the site's parity, row pitch ldx).
+//   rs_site >= 0: epi must be 0; the result rows go to the owner ranks' inboxes [2][world][S][ld_inbox] and `out` is unused.
+//   epi 0 bf16 store, 1 fp32 store (logits), 3 SwiGLU.
+POOT_API int poot_gemm_tiled_tp(int epi, const void* x, const void* W, void* out, int N, int K, int ldx, int ldo,
+                                int tp_world, int tp_rank, int S_rows, int ag_site, int ag_sites, int rs_site, int rs_sites,
+                                const int* epoch, void* flags_local, void* const* flags_peer, void* const* inbox_peer,
+                                int ld_inbox, int* ticket, int* status, cudaStream_t s) {
+  const int M = tp_world * S_rows;
+  if (tp_world < 2 || tp_world > TP_MAX_WORLD || tp_rank < 0 || tp_rank >= tp_world || S_rows < 1 || M % GEMM_BM)
+    return (int)cudaErrorInvalidValue;
+  if (N <= 0 || N % 8 || K % 8 || ldx % 8 || status == nullptr || epoch == nullptr || ticket == nullptr)
+    return (int)cudaErrorInvalidValue;
+  if (epi != GEPI_STORE && epi != GEPI_F32 && epi != GEPI_SWIGLU) return (int)cudaErrorInvalidValue;
+  if (rs_site >= 0 && (epi != GEPI_STORE || inbox_peer == nullptr || ld_inbox % 8 || ld_inbox < N)) return (int)cudaErrorInvalidValue;
+  if (rs_site < 0 && (out == nullptr || ldo % (epi == GEPI_F32 ? 4 : 8))) return (int)cudaErrorInvalidValue;
+  if (epi == GEPI_SWIGLU && N % 16) return (int)cudaErrorInvalidValue;
+  TpArgs tp = {};
+  tp.world = tp_world; tp.rank = tp_rank; tp.S = S_rows; tp.ag_site = ag_site; tp.ag_sites = ag_sites; tp.rs_site = rs_site;
+  tp.rs_sites = rs_sites; tp.ld_inbox = ld_inbox; tp.epoch = epoch; tp.flags_local = (uint32_t*)flags_local; tp.ticket = ticket;
+  for (int r = 0; r < tp_world; ++r) {
+    tp.flags_peer[r] = (uint32_t*)flags_peer[r];
+    tp.inbox_peer[r] = inbox_peer ? (__nv_bfloat16*)inbox_peer[r] : nullptr;
+  }
+  CUtensorMap ta, tb;
+  int e = make_tmap_bf16_2d(&ta, x, (uint64_t)(ag_site >= 0 ? 2 * M : M), (uint64_t)K, (uint64_t)ldx, GEMM_BM);
+  if (e) return e;
+  e = make_tmap_bf16_2d(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128u);
+  if (e) return e;
+  switch (epi) {
+    case GEPI_STORE: return launch_gemm_tp_cfg<GEPI_STORE>(ta, tb, out, M, N, K, ldo, tp, status, s);
+    case GEPI_F32: return launch_gemm_tp_cfg<GEPI_F32>(ta, tb, out, M, N, K, ldo, tp, status, s);
+    default: return launch_gemm_tp_cfg<GEPI_SWIGLU>(ta, tb, out, M, N, K, ldo, tp, status, s);
   }
 }

@@ -83,7 +83,8 @@ class FusedComm(NcclComm):
     """In-kernel NVLink reduce-scatter / all-gather fused with the projections' GEMMs."""
 
     fused = True
-    MAX_ROWS = 128
+    MAX_ROWS = 128                 # rows of a one-shot slot, and the largest step the skinny (swap-AB) kernels serve
+    MAX_SHARD_ROWS = 4096          # largest padded step of the token-sharded program (tiled GEMMs above 128 rows)
 
     def __init__(self, rank: int, world: int, device: torch.device, group=None, probe: bool = True):
         super().__init__(rank, world, device, group)
@@ -94,10 +95,13 @@ class FusedComm(NcclComm):
         super().attach(engine)
         H, w = engine.cfg.hidden, self.world
         self.H = H
-        self.s_max = self.MAX_ROWS // w
+        # the sharded program serves steps up to max_rows padded rows: what the engine's buffers hold, in whole 128-row tiles
+        self.max_rows = max(self.MAX_ROWS, min(self.MAX_SHARD_ROWS, engine.max_tokens // 128 * 128))
+        self.s_max = self.max_rows // w
         # layout of the symmetric block: 1 KiB aligned regions, each followed by guard words that check_guards() reads
-        inbox_bytes = 2 * w * self.MAX_ROWS * H * 2   # one-shot form: a slot holds up to MAX_ROWS rows
-        xs_bytes = 2 * self.MAX_ROWS * H * 2
+        # inbox: one-shot form [2][world][MAX_ROWS][H] or sharded form [2][world][S][H] with world * S <= max_rows
+        inbox_bytes = 2 * max(w * self.MAX_ROWS, self.max_rows) * H * 2
+        xs_bytes = 2 * self.max_rows * H * 2
         # greedy-pick exchange: [2][world][ax_cap] int32, one stage-1 table [rows, groups, 3] per rank and parity
         self.ax_cap = engine.max_seqs * K.argmax_groups(max(1, engine.cfg.vocab // w)) * 3
         ax_bytes = 2 * w * self.ax_cap * 4
@@ -154,6 +158,9 @@ class FusedComm(NcclComm):
                                                      c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P, c_int, c_int, _P,
                                                      _P, _P])
         K.register_signature("poot_tp_end_step", [_P, _P])
+        K.register_signature("poot_gemm_tiled_tp", [c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                    c_int, c_int, c_int, _P, _P, _P, _P, c_int, _P, _P, _P])
+        self._gemm_tiled = K.fn("poot_gemm_tiled_tp")
         self._begin = K.fn("poot_tp_begin_step")
         self._end = K.fn("poot_tp_end_step")
         self._norm = K.fn("poot_tp_norm")
@@ -161,17 +168,28 @@ class FusedComm(NcclComm):
 
     # ---- geometry -------------------------------------------------------------------------------------------
     def rows_for(self, T: int) -> int:
-        """Padded step rows (world * S, one of 16/32/64/128) or 0 when the step is too large for the fused path."""
+        """Padded step rows (world * S): one of 16/32/64/128 for the skinny kernels, whole 128-row tiles above that for
+        the tiled ones; 0 when the step is too large for the sharded program."""
         need = max(T, 8 * self.world)
         for r in (16, 32, 64, 128):
             if r >= need and r % (8 * self.world) == 0:
                 return r
-        return 0
+        r = (need + 127) // 128 * 128
+        return r if r <= self.max_rows else 0
 
     # ---- launches -------------------------------------------------------------------------------------------
     def begin_step(self) -> None:
         """First launch of a fused step: advances the epoch and starts the step's wait budget."""
         check(self._begin(self.epoch.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()), "tp_begin_step")
+
+    def gather_rows(self, idx: torch.Tensor, out: torch.Tensor, rows: int, S: int, ag_site: int) -> None:
+        """``out[b] = gathered rows[idx[b]]`` of ``ag_site`` once every rank's rows have landed (int64 ``idx``)."""
+        K.register_signature("poot_tp_gather_rows", [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, _P, _P, _P])
+        b = self.block
+        check(K.fn("poot_tp_gather_rows")(b.ptr(self.rank, self.off_xs), idx.data_ptr(), out.data_ptr(), rows, self.H,
+                                          self.world, self.rank, S, ag_site, self.ag_sites, self.epoch.data_ptr(),
+                                          b.ptr(self.rank, self.off_flags), K.status_word(self.device).data_ptr(),
+                                          K._stream()), "tp_gather_rows")
 
     def end_step(self) -> None:
         """Last launch of a fused step: clears the step deadline, so a later step that does not begin with
@@ -229,6 +247,14 @@ class FusedComm(NcclComm):
         ldo = out.stride(0) if out is not None else self.H
         b = self.block
         xptr = b.ptr(self.rank, self.off_xs) if ag_site >= 0 else x.data_ptr()
+        if self.world * S > self.MAX_ROWS:
+            # prefill-sized step: the tiled tcgen05 GEMM with the gathered operand and / or the scattered result
+            check(self._gemm_tiled(epi, xptr, W.data_ptr(), None if out is None else out.data_ptr(), N, Kd, ldx, ldo,
+                                   self.world, self.rank, S, ag_site, self.ag_sites, rs_site, self.rs_sites,
+                                   self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer, self.inbox_peer,
+                                   self.H, self.ticket.data_ptr(), K.status_word(self.device).data_ptr(), K._stream()),
+                  "gemm_tiled_tp")
+            return
         check(self._gemm(epi, xptr, W.data_ptr(), None if out is None else out.data_ptr(),
                          N, Kd, ldx, ldo, ck, self.world, self.rank, S, ag_site, self.ag_sites, rs_site, self.rs_sites,
                          self.epoch.data_ptr(), b.ptr(self.rank, self.off_flags), self.flags_peer, self.inbox_peer,

@@ -989,13 +989,19 @@ class DecoderEngine:
             pending_rs = rs
         self._count(2)
         comm.norm(w.final_norm, S, cfg.norm_eps, ag_site=ag, rs_site=pending_rs)
-        comm.gemm(K.EPI_F32, None, w.lm_head, self.logits_local[:R], S, ag_site=ag)
-        if B == T:
-            local = self.logits_local[:B]
-        else:
-            self._count()
+        if R > self.logits_local.shape[0]:
+            # prefill-sized step: only the sampling rows meet the head - picked out of the gathered rows once they landed
+            comm.gather_rows(self.logit_idx[:B], self.xl[:B], B, S, ag_site=ag)
             local = self.logits_sel[:B]
-            K.gather_rows(self.logits_local[:R], self.logit_idx[:B], local)
+            self._linear(self.xl[:B], w.lm_head, K.EPI_F32, local)
+        else:
+            comm.gemm(K.EPI_F32, None, w.lm_head, self.logits_local[:R], S, ag_site=ag)
+            if B == T:
+                local = self.logits_local[:B]
+            else:
+                self._count()
+                local = self.logits_sel[:B]
+                K.gather_rows(self.logits_local[:R], self.logit_idx[:B], local)
         self._sample(shape, local)
         self._count()
         comm.end_step()

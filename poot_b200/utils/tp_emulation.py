@@ -31,11 +31,12 @@ NO_DEADLINE_BUDGET_S = 1.0
 class EmulatedGroup:
     """What the ranks of one node share: every rank's flag block, inbox, gather buffer, exchange area, control block."""
 
-    def __init__(self, world: int, hidden: int, ax_cap: int = 4096):
+    def __init__(self, world: int, hidden: int, ax_cap: int = 4096, max_rows: int = MAX_ROWS):
         self.world, self.H, self.ax_cap = world, hidden, ax_cap
+        self.max_rows = max(MAX_ROWS, max_rows // 128 * 128)       # largest padded step of the sharded program
         self.flags = torch.zeros(world, 6, 8, dtype=torch.int64)
-        self.inbox = [torch.zeros(2, world, MAX_ROWS, hidden, dtype=torch.bfloat16) for _ in range(world)]
-        self.xs = [torch.zeros(2, MAX_ROWS, hidden, dtype=torch.bfloat16) for _ in range(world)]
+        self.inbox = [torch.zeros(2, world, self.max_rows, hidden, dtype=torch.bfloat16) for _ in range(world)]
+        self.xs = [torch.zeros(2, self.max_rows, hidden, dtype=torch.bfloat16) for _ in range(world)]
         self.ax = [torch.zeros(2, world, ax_cap, dtype=torch.int32) for _ in range(world)]
         # control blocks: first failure, detail, deadline (monotonic seconds; 0 = none), abort word, step budget
         self.ctl = [dict(code=0, detail=-1, deadline=0.0, abort=0, budget=5.0, gave_up=0) for _ in range(world)]
@@ -143,7 +144,8 @@ class EmulatedFusedComm:
         H = engine.cfg.hidden
         assert H == self.g.H
         self.H = H
-        self.s_max = MAX_ROWS // self.world
+        self.max_rows = max(MAX_ROWS, min(self.g.max_rows, engine.max_tokens // 128 * 128))
+        self.s_max = self.max_rows // self.world
         self.h_shard = torch.zeros(self.s_max, H, dtype=torch.bfloat16)
         L = engine.cfg.n_layers
         self.rs_sites, self.ag_sites = 2 * L, 2 * L + 1
@@ -159,7 +161,8 @@ class EmulatedFusedComm:
         for r in (16, 32, 64, 128):
             if r >= need and r % (8 * self.world) == 0:
                 return r
-        return 0
+        r = (need + 127) // 128 * 128
+        return r if r <= self.max_rows else 0
 
     def oneshot_ok(self, T: int) -> bool:
         return T <= 128 and T * (self.world - 1) <= 512
@@ -178,6 +181,12 @@ class EmulatedFusedComm:
 
     def end_step(self) -> None:
         self.g.ctl[self.rank]["deadline"] = 0.0
+
+    def gather_rows(self, idx, out, rows: int, S: int, ag_site: int) -> None:
+        target = self._target(ag_site, self.ag_sites)
+        ok = self.g.wait_all(self.rank, CH_AG, target, ag_site)
+        X = self.g.xs[self.rank][target & 1, :self.world * S]
+        out[:rows] = X[idx[:rows].long().clamp(0, self.world * S - 1)] if ok else 0
 
     def gemm_allreduce(self, x, W, rows: int, rs_site: int) -> None:
         y = E._bf(x[:rows].float() @ W.float().T)

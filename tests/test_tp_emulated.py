@@ -311,3 +311,58 @@ def test_sharded_expert_layer_equals_the_single_rank_layer_bit_for_bit(world):
     assert not errs, errs
     assert torch.equal(torch.cat([got[r] for r in range(world)], 0), want)
     assert want.float().abs().max().item() > 0.05
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("moe", [False, True])
+def test_prefill_sized_steps_ride_the_sharded_program(world, moe):
+    """A 200-token prefill (256 padded rows, 128 or 64 per rank) goes through the token-sharded program - tiled GEMMs with
+    the gathered operand and the scattered result on the device, the expert exchange when the model is routed - and the
+    decode steps after it through the skinny ones; no library collective in any step."""
+    extra = dict(n_experts=8, top_k=2, moe_ffn=128) if moe else {}
+    cfg = DecoderConfig(n_layers=2, hidden=256, n_heads=8, n_kv_heads=4, head_dim=64, ffn=512, vocab=4096, max_position=256,
+                        **extra)
+    g = torch.Generator().manual_seed(11)
+    prompts = torch.randint(0, cfg.vocab, (2, 100), generator=g, dtype=torch.int32)
+
+    def program(rank, w_world, comm, out):
+        w = random_weights(cfg, "cpu", seed=0, std=0.05, tp_rank=rank, tp_world=w_world,
+                           **(dict(ep_rank=rank, ep_world=w_world) if moe else {}))
+        eng = DecoderEngine(w, num_blocks=20, max_seqs=2, max_tokens=256, max_blocks_per_seq=8, comm=comm, device="cpu",
+                            use_graphs=False)
+        eng.tp_mode = "rs_ag"
+        s = FixedBatchSession(eng, 2, 128)
+        toks = [s.prefill_fast(prompts).clone()]
+        toks.append(s.decode(toks[-1][:, 0].tolist()).clone())
+        out[rank] = (torch.stack(toks), eng)
+
+    with emulated_kernels():
+        ref = {}
+        program(0, 1, None, ref)
+        group = EmulatedGroup(world, cfg.hidden, max_rows=256)
+        for c in group.ctl:
+            c["budget"] = 20.0
+        comms = [EmulatedFusedComm(r, group) for r in range(world)]
+        out, errs = {}, {}
+
+        def body(r):
+            try:
+                program(r, world, comms[r], out)
+            except Exception as e:
+                errs[r] = e
+        threads = [threading.Thread(target=body, args=(r,), daemon=True) for r in range(world)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=300)
+        assert not any(t.is_alive() for t in threads), "a rank thread did not finish"
+    assert not errs, errs
+    assert comms[0].rows_for(200) == 256 and comms[0].s_max == 256 // world
+    for r in range(world):
+        assert torch.equal(out[r][0], out[0][0]) and group.status(r) == (0, -1)
+        assert comms[r].library_collectives == 0
+    assert torch.equal(out[0][0][0, :, 0], ref[0][0][0, :, 0]), (out[0][0][:, :, 0], ref[0][0][:, :, 0])
+    kinds = [k for k, _, _ in comms[0].log]
+    L = cfg.n_layers
+    assert kinds.count("ag") == 2 * ((L + 1) if moe else (2 * L + 1))        # gathers: per attention (+ per dense FFN) + the head
+    assert kinds.count("epd") == (2 * L if moe else 0)
