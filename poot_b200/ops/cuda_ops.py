@@ -7,6 +7,7 @@ PyTorch fallback: a tensor that is not on a CUDA device is an error.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Optional
 
@@ -931,6 +932,25 @@ class QuantWeight:
 
 
 _dequant_scratch = {}
+# Decode batches of 5 to 128 rows over packed weights: the dequant-fused tensor-core kernel (the packed weight is read
+# once and never written back as bf16) instead of "decode the whole matrix to bf16, then the dense GEMM".  Opt-in
+# (POOT_QUANT_FUSED_GEMM=1) until the kernel has been checked on a device.
+QUANT_FUSED_GEMM = os.environ.get("POOT_QUANT_FUSED_GEMM", "0") not in ("", "0")
+_SIGS["poot_quant_gemm_skinny"] = [c_int, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P]
+
+
+def quant_gemm_skinny(x: torch.Tensor, W: "QuantWeight", epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
+                      resid: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x[M <= 128, K] @ dequant(W)^T`` with the block decode fused into the tcgen05 GEMM's weight stage."""
+    _need_cuda(x, W.packed)
+    M, Kd = x.shape
+    assert Kd == W.K and x.dtype == torch.bfloat16 and x.stride(1) == 1 and M <= 128
+    out = _out_for(epi, M, W.N, x.device, out)
+    check(_fn("poot_quant_gemm_skinny")(W.type_id, epi, _ptr(x), _ptr(W.packed), _ptr(out), _ptr(resid), M, W.N, Kd,
+                                        x.stride(0), out.stride(0), status_word(x.device).data_ptr(), _stream()),
+          "quant_gemm_skinny")
+    return out
+
 
 
 def quant_gemv(x: torch.Tensor, W: QuantWeight, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None,
@@ -1042,6 +1062,8 @@ def linear(x, W, epi: int = EPI_STORE, out: Optional[torch.Tensor] = None, resid
     if isinstance(W, QuantWeight):
         if x.shape[0] <= 4:
             return quant_gemv(x, W, epi, out, resid)
+        if x.shape[0] <= 128 and QUANT_FUSED_GEMM and epi in (EPI_STORE, EPI_F32, EPI_RESID, EPI_SWIGLU):
+            return quant_gemm_skinny(x, W, epi, out, resid)
         key = (W.device, W.N * W.K)
         buf = _dequant_scratch.get(key)
         if buf is None:
