@@ -57,7 +57,7 @@ class Program:
         return total
 
 
-PIPELINE = ["canonicalize", "cse", "rope_fusion", "flash_attention", "dce", "recognize_packed",
+PIPELINE = ["canonicalize", "cse", "rope_fusion", "flash_attention", "form_selection", "dce", "recognize_packed",
             "fold_dense_contractions", "fuse_contraction_epilogues", "fuse", "dce2"]
 
 
@@ -72,6 +72,9 @@ def run_passes(g: Graph, opt: CompileOptions, log: Dict[str, object], declines: 
             log[name] = passes.rope_fusion(g, declines)
         elif name == "flash_attention":
             log[name] = passes.flash_attention(g, declines) if opt.attention else 0
+        elif name == "form_selection":
+            from .selection import form_selection
+            log[name] = form_selection(g, declines)
         elif name in ("dce", "dce2"):
             log[name] = passes.dce(g)
         elif name == "recognize_packed":

@@ -103,7 +103,10 @@ def plan_eqn(g: Graph, k: int, e: Eqn, world: int = 1) -> Plan:
         if kernel is None:
             raise Refusal(k, op, dt, TARGET, f"no kernel for the {kind!r} recurrence")
         return Plan("dispatch", [kernel], f"{kind}: state carried per (sequence, head) in shared memory")
-    if op in ("block_top_k", "selected_attention", "packed_dequant", "all_to_all", "side_output"):
+    if op == "block_top_k":
+        # the exact radix select over each row's scores (ties at the cut: lowest position first)
+        return Plan("dispatch", ["poot_index_select"], f"k={e.attrs.get('k')} of {g.types[e.inputs[0]].shape[-1]} candidates")
+    if op in ("selected_attention", "packed_dequant", "all_to_all", "side_output"):
         raise Refusal(k, op, dt, TARGET, "no kernel family for this equation")
     raise Refusal(k, op, dt, TARGET, "unknown equation")
 

@@ -324,3 +324,68 @@ def test_hybrid_stacks_plan_their_recurrence_on_the_scan_kernels(kinds, extra, k
     odd = dataclasses.replace(scan, attrs={**scan.attrs, "family": "prefix_sum"})
     with pytest.raises(Refusal):
         plan_eqn(g, 0, odd)
+
+
+def test_form_selection_folds_the_rank_threshold_chain_and_leaves_near_misses_alone():
+    """``not(stable_descending_rank(score) >= k)`` becomes one ``block_top_k`` composite planned on the radix select; its
+    body is the composition, so the rewritten graph evaluates to the same bits.  A composition with another tie rule
+    (higher index first) is not the definition and stays as primitives."""
+    from poot_b200.ir import oplib as O
+    from poot_b200.ir.builder import Builder
+    from poot_b200.oracle.eval import eval_graph
+    from poot_b200.plan import passes
+    from poot_b200.plan.selection import form_selection
+    from poot_b200.tensor import DType
+
+    def graph(tie_lowest: bool, three_d: bool):
+        b = Builder()
+        shape = (2, 3, 16) if three_d else (6, 16)
+        s = b.slot("score", shape, DType.F32, "activation")
+        flat = b.reshape(s, (6, 16)) if three_d else s
+        if tie_lowest:
+            rank = O.stable_descending_rank(b, flat)
+        else:                                        # same chain, ties go to the HIGHER index
+            R, E = flat.shape
+            a = b.broadcast(b.reshape(flat, (R, E, 1)), (R, E, E))
+            o = b.broadcast(b.reshape(flat, (R, 1, E)), (R, E, E))
+            ie, io = b.iota((R, E, E), 1), b.iota((R, E, E), 2)
+            gt = b.binary("ge", o, a)
+            strictly = b.binary("and", gt, O.lnot(b, b.binary("ge", a, o)))
+            tie = b.binary("and", b.binary("and", gt, b.binary("ge", a, o)), O.lnot(b, b.binary("ge", ie, io)))
+            rank = b.cast(b.binary("or", strictly, tie), DType.I32).sum(-1)
+        if three_d:
+            rank = b.reshape(rank, shape)
+        keep = O.lnot(b, b.binary("ge", rank, b.broadcast(b.scalar(4, DType.I32), rank.shape)))
+        b.output(keep, "keep", "result")
+        return b.finish()
+
+    rng = np.random.default_rng(0)
+    for three_d in (False, True):
+        g = graph(True, three_d)
+        x = rng.standard_normal(g.types[g.inputs[0].value].shape).astype(np.float32)
+        x.reshape(-1, 16)[:, 3] = x.reshape(-1, 16)[:, 9]               # exact ties at possibly the cut
+        want = eval_graph(g, {"score": x}).outputs["keep"]
+        assert (want.reshape(-1, 16).sum(-1) == 4).all()
+        passes.canonicalize(g); passes.cse(g)
+        assert form_selection(g) == 1
+        sel = [e for e in g.eqns if e.op == "block_top_k"]
+        assert len(sel) == 1 and sel[0].attrs["k"] == 4 and sel[0].body is not None
+        g.validate()
+        assert np.array_equal(eval_graph(g, {"score": x}).outputs["keep"], want)
+        plans = plan_graph(g)
+        assert ["poot_index_select"] in [p.kernels for p in plans if p.kind == "dispatch"]
+    other = graph(False, False)
+    passes.canonicalize(other); passes.cse(other)
+    assert form_selection(other) == 0 and not any(e.op == "block_top_k" for e in other.eqns)
+
+
+def test_sparse_attention_family_compiles_with_its_selections_formed():
+    from tests.test_hf_parity import BASE, CASES
+    from poot_b200.models.model import StepSpec
+    from poot_b200.models.registry import Registry
+    hf = {k: v for k, v in {**BASE, **CASES["glm_moe_dsa"]}.items() if not k.startswith("_")}
+    m = Registry.builtin().resolve_hf(hf)
+    prog = compile_graph(m.trace(StepSpec(rows=1, tokens=4, capacity=32)))
+    ks = sorted(e.attrs["k"] for e in prog.graph.eqns if e.op == "block_top_k")
+    assert ks.count(m.cfg.index_topk) == m.cfg.n_layers              # one selection per layer's indexer
+    assert prog.log["form_selection"] == len(ks)
