@@ -6,6 +6,7 @@
 //    the D x D state of the (sequence, head) held in shared memory for the whole piece
 //    (crates/poot-graph-ir/src/ops/ssm.rs, crates/poot-kernelgen/src/scan.rs:1-8: "workgroup per (head, column block),
 //    state column in LDS");
+//  * kda_scan: the same rule with a decay per key channel (Kimi delta attention);
 //  * gated_rmsnorm: RMSNorm per head times SiLU(z);  sigmoid_mul: a *= sigmoid(g).
 //
 // A step names its sequence pieces in a table of (first row, rows, sequence row, first position); entries with zero rows
@@ -108,6 +109,64 @@ __global__ void __launch_bounds__(D) gdn_scan_kernel(const __nv_bfloat16* __rest
     }
     out[row * ((size_t)nv * D) + h * D + j] = __float2bfloat16(y);
     __syncthreads();                        // qs / ks are rewritten for the next row
+  }
+  for (int i = 0; i < D; ++i) St[(size_t)i * D + j] = S[i * D + j];
+}
+
+// Kimi delta attention: the same delta rule with a decay PER KEY CHANNEL.  Row i of the head's state decays by
+//   exp(lower_bound * sigmoid(exp(a_log[h]) * (f[h, i] + dt_bias[h, i])))
+// before the read; q, k, v come from the convolution as [T, 3 * heads * D] (q | k | v), `f` holds the raw output of the
+// low-rank gate projection [T, heads * D], beta the raw b projection at column b_col of `bm`.
+// grid (heads, pieces), block D threads: thread j owns column j of S[key i][value j] and computes the decay of row j.
+template <int D>
+__global__ void __launch_bounds__(D) kda_scan_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ f,
+                                                     const __nv_bfloat16* __restrict__ bm, int ldb, int b_col,
+                                                     const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                                     float lower_bound, float* __restrict__ state, int state_rows,
+                                                     const int* __restrict__ segs, __nv_bfloat16* __restrict__ out, int heads) {
+  extern __shared__ float sm[];
+  float* S = sm;                            // [D][D]
+  float* qs = S + D * D;
+  float* ks = qs + D;
+  float* ds = ks + D;                       // decay of each key channel for this row
+  float* red = ds + D;                      // [8]
+  pdl_wait(); pdl_launch();
+  const int s = blockIdx.y, h = blockIdx.x, j = threadIdx.x;
+  const int first = segs[4 * s], n = segs[4 * s + 1], seq = segs[4 * s + 2], pos0 = segs[4 * s + 3];
+  if (n <= 0 || seq < 0 || seq >= state_rows) return;
+  float* St = state + ((size_t)seq * heads + h) * D * D;
+  for (int i = 0; i < D; ++i) S[i * D + j] = pos0 == 0 ? 0.f : St[(size_t)i * D + j];
+  const size_t C = (size_t)heads * D;
+  const float rate = __expf(a_log[h]), bias = dt_bias[h * D + j];
+  const float qscale = rsqrtf((float)D);
+  for (int t = 0; t < n; ++t) {
+    const size_t row = (size_t)first + t;
+    const __nv_bfloat16* r = qkv + row * 3 * C;
+    const float qv = bf2f(r[h * D + j]), kv = bf2f(r[C + h * D + j]), vv = bf2f(r[2 * C + h * D + j]);
+    const float q2 = block_sum<D>(qv * qv, red);
+    const float k2 = block_sum<D>(kv * kv, red);
+    qs[j] = qv * rsqrtf(q2 + 1e-6f) * qscale;
+    ks[j] = kv * rsqrtf(k2 + 1e-6f);
+    const float gate = 1.f / (1.f + __expf(-rate * (bf2f(f[row * C + h * D + j]) + bias)));
+    ds[j] = __expf(lower_bound * gate);
+    __syncthreads();
+    const float b = bf2f(bm[row * ldb + b_col + h]);
+    const float beta = 1.f / (1.f + __expf(-b));
+    float kvm = 0.f;
+    for (int i = 0; i < D; ++i) {
+      const float sij = S[i * D + j] * ds[i];
+      S[i * D + j] = sij;
+      kvm += ks[i] * sij;
+    }
+    const float delta = (vv - kvm) * beta;
+    float y = 0.f;
+    for (int i = 0; i < D; ++i) {
+      const float sij = S[i * D + j] + ks[i] * delta;
+      S[i * D + j] = sij;
+      y += qs[i] * sij;
+    }
+    out[row * C + h * D + j] = __float2bfloat16(y);
+    __syncthreads();                        // qs / ks / ds are rewritten for the next row
   }
   for (int i = 0; i < D; ++i) St[(size_t)i * D + j] = S[i * D + j];
 }
@@ -225,6 +284,31 @@ POOT_API int poot_gdn_scan(const void* qkv, const void* ba, int ldb, int b_col, 
   if (nk < 1 || nv < nk || nv % nk || b_col < 0 || a_col < 0) return (int)cudaErrorInvalidValue;
   if (D == 128) return launch_gdn_scan<128>(qkv, ba, ldb, b_col, a_col, dt_bias, a_log, state, state_rows, segs, n_segs, out, nk, nv, s);
   if (D == 64) return launch_gdn_scan<64>(qkv, ba, ldb, b_col, a_col, dt_bias, a_log, state, state_rows, segs, n_segs, out, nk, nv, s);
+  return (int)cudaErrorInvalidValue;
+}
+
+template <int D>
+static int launch_kda_scan(const void* qkv, const void* f, const void* bm, int ldb, int b_col, const float* dt_bias, const float* a_log,
+                           float lower_bound, float* state, int state_rows, const int* segs, int n_segs, void* out, int heads,
+                           cudaStream_t s) {
+  constexpr size_t smem = ((size_t)D * D + 3 * D + 8) * sizeof(float);
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kda_scan_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  return launch_k(kda_scan_kernel<D>, dim3(heads, n_segs), dim3(D), smem, s, (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)f,
+                  (const __nv_bfloat16*)bm, ldb, b_col, dt_bias, a_log, lower_bound, state, state_rows, segs, (__nv_bfloat16*)out, heads);
+}
+
+POOT_API int poot_kda_scan(const void* qkv, const void* f, const void* bm, int ldb, int b_col, const float* dt_bias, const float* a_log,
+                           float lower_bound, float* state, int state_rows, const int* segs, int n_segs, void* out, int heads, int D,
+                           cudaStream_t s) {
+  if (n_segs == 0) return 0;
+  if (heads < 1 || b_col < 0 || !(lower_bound < 0.f)) return (int)cudaErrorInvalidValue;
+  if (D == 128) return launch_kda_scan<128>(qkv, f, bm, ldb, b_col, dt_bias, a_log, lower_bound, state, state_rows, segs, n_segs, out, heads, s);
+  if (D == 64) return launch_kda_scan<64>(qkv, f, bm, ldb, b_col, dt_bias, a_log, lower_bound, state, state_rows, segs, n_segs, out, heads, s);
   return (int)cudaErrorInvalidValue;
 }
 

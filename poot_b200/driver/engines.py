@@ -452,8 +452,28 @@ class OracleStepEngine:
     def last_logits(self, rows: int) -> np.ndarray:
         return self._logits[:rows]
 
+    # ---- recurrent state: snapshot / restore of sequence rows (speculative rollback), as on the device engine ---------
+    @property
+    def has_recurrent_state(self) -> bool:
+        return bool(getattr(self.model.cfg, "is_recurrent", False))
+
+    def snapshot_rows(self, rows) -> None:
+        """Keep a copy of the recurrent state (conv windows, scan carries) of the sequence rows ``rows``: folding a
+        token into it is not invertible, so a speculative round that rejects a draft restores the rows and replays
+        what it keeps (crates/poot-llm/src/driver/snapshot.rs:1-17)."""
+        rows = set(int(r) for r in rows)
+        self._shadow = {k: v.copy() for k, v in self.state.items() if isinstance(k, tuple) and k[0] in rows}
+        self._shadow_rows = rows
+
+    def restore_rows(self, rows) -> None:
+        if getattr(self, "_shadow", None) is None:
+            raise RuntimeError("restore_rows without a snapshot")
+        for k in [k for k in self.state if isinstance(k, tuple) and k[0] in self._shadow_rows]:
+            del self.state[k]                      # a state first written after the snapshot starts from zero again
+        self.state.update({k: v.copy() for k, v in self._shadow.items()})
+
     def copy_block(self, src: int, dst: int) -> None:
         b = self.block
         for name, pool in self.state.items():
-            if isinstance(name, str) and name.endswith(("k_pool", "v_pool")):
+            if isinstance(name, str) and name.endswith("_pool"):          # every paged pool: K/V, latent, indexer keys
                 pool[dst * b:(dst + 1) * b] = pool[src * b:(src + 1) * b]

@@ -141,14 +141,13 @@ class ModelHandle:
     def mtp_oracle_weights(self) -> Dict[str, np.ndarray]:
         """The multi-token-prediction layer as the one-layer model ``models.config.mtp_config`` describes: its block
         renamed to layer 0, its closing norm as ``final_norm``, the target's embedding and head."""
-        from ..models.config import mtp_config
         c = self.cfg
         if not self.has_mtp:
             raise KeyError(f"{self.source} stores no multi-token-prediction layer")
         tail = f"layers.{c.n_layers}."
         out = {"layers.0." + n[len(tail):]: w.to_f32() for n, w in self.canonical.items()
                if n.startswith(tail) and ".experts." not in n}
-        if mtp_config(c).moe_layer(0):
+        if self.model.mtp_model().cfg.moe_layer(0):
             src = {}
             self._stack_experts(src, tail)
             out.update({"layers.0." + k[len(tail):]: v for k, v in src.items()})

@@ -185,8 +185,8 @@ class Builder:
     def scan(self, family: str, operands: Sequence[Traced], chunk: int = 64):
         """A bounded recurrence over the sequence axis with one packed result ``[1, H, L + S, W]``: rows ``..L`` are the
         sequence output, rows ``L..`` the carried state (crates/poot-graph-ir/src/op.rs:1427-1435, 3084-3216).
-        ``delta_rule``: operands ``[q, k, v, g, beta, s_in]`` with q/k/v ``[1,H,L,D]``, g (log domain) and beta
-        ``[1,H,L,1]``, ``s_in[1,H,D,D]``.  ``ssd``: ``[x, b, c, delta, a, d, h_in]`` with ``x[1,H,L,P]``, b/c
+        ``delta_rule``: operands ``[q, k, v, g, beta, s_in]`` with q/k/v ``[1,H,L,D]``, g (log domain) ``[1,H,L,1]`` or,
+        with a decay per key channel, ``[1,H,L,D]``, beta ``[1,H,L,1]``, ``s_in[1,H,D,D]``.  ``ssd``: ``[x, b, c, delta, a, d, h_in]`` with ``x[1,H,L,P]``, b/c
         ``[1,H,L,N]``, ``delta[1,H,L,1]``, a/d ``[1,H,1,1]``, ``h_in[1,H,N,P]``.  Returns ``(y, state_out)``."""
         first = operands[0]
         _, H, L, Wd = first.shape

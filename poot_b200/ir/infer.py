@@ -151,7 +151,9 @@ def infer(op: str, attrs: Dict[str, Any], ins: List[TensorType], body=None) -> L
             raise GraphError(f"scan: family {fam!r}, lead operand {first.shape}")
         _, h, l, w = first.shape
         if fam == "delta_rule":
-            want = [(1, h, l, w), (1, h, l, w), (1, h, l, w), (1, h, l, 1), (1, h, l, 1), (1, h, w, w)]
+            # the log decay is one value per head and token, or one per key channel (a row of the state each)
+            decay = (1, h, l, w) if len(ins) > 3 and tuple(ins[3].shape) == (1, h, l, w) else (1, h, l, 1)
+            want = [(1, h, l, w), (1, h, l, w), (1, h, l, w), decay, (1, h, l, 1), (1, h, w, w)]
             rows = w
         else:
             n = ins[1].shape[3] if ins[1].rank == 4 else 0

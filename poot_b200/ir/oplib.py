@@ -277,6 +277,10 @@ def ffn_activation(b: Builder, gate: Traced, up: Optional[Traced], act: str = "s
                    alpha: float = 1.702) -> Traced:
     """``act(gate) * up`` for gated FFNs, ``act(gate)`` for plain ones.  ``limit > 0`` is the clamped form
     ``(min(up, limit) clamped below at -limit + 1) * g * sigmoid(alpha * g)`` with ``g = min(gate, limit)``."""
+    if act == "silu_clamped":
+        # silu(min(gate, limit)) * clamp(up, -limit, limit)   (components/ffn.rs ``Glu::ClampedSilu``)
+        lim = b.broadcast(b.scalar(limit, F32), gate.shape)
+        return swiglu(b, -b.binary("max", -gate, -lim), b.binary("max", -b.binary("max", -up, -lim), -lim))
     if limit > 0:
         lim = b.broadcast(b.scalar(limit, F32), gate.shape)
         g = -b.binary("max", -gate, -lim)

@@ -211,7 +211,7 @@ class LLM:
             require_mtp(cfg)
             check([Feature.DRAFT_MTP] + ([Feature.RECURRENT_STATE] if cfg.is_recurrent else []))
             mtp_weights, k = mtp
-            layer = Model(mtp_config(cfg))
+            layer = model.mtp_model()
             runner = OracleStepEngine(layer, mtp_weights, num_blocks, rows, step_prefill + rows, blocks_for(max_seq))
             llm.draft = MtpDraft(runner, k).attach(drv)
         return llm

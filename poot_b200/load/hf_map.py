@@ -282,6 +282,8 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
         p = f"layers.{l}."
         if cfg.family in ("qwen3next", "qwen38_27b") and _qwen3next_tensor(cfg, p, rest, w, canon):
             continue
+        if cfg.family == "glm53_flash" and _glm53_tensor(cfg, l, p, rest, w, canon):
+            continue
         if rest in table:
             canon[p + table[rest]] = w
             continue
@@ -360,6 +362,36 @@ def _qwen3next_tensor(cfg: DecoderConfig, p: str, rest: str, w: PackedWeight, ca
         a = w.to_f32()
         canon[p + "gdn_conv"] = f32_weight(p + "gdn_conv", a.reshape(a.shape[0], a.shape[-1]))
         return True
+    return False
+
+
+GLM53_SITE = {f"hc_{site}_{part}": f"hc_{site}_{part}" for site in ("attn", "ffn") for part in ("fn", "base", "scale")}
+GLM53_KDA = {"self_attn.q_proj.weight": "kda_q", "self_attn.k_proj.weight": "kda_k", "self_attn.v_proj.weight": "kda_v",
+             "self_attn.f_a_proj.weight": "kda_f_a", "self_attn.f_b_proj.weight": "kda_f_b", "self_attn.b_proj.weight": "kda_b",
+             "self_attn.g_a_proj.weight": "kda_g_a", "self_attn.g_b_proj.weight": "kda_g_b", "self_attn.A_log": "kda_a_log",
+             "self_attn.dt_bias": "kda_dt_bias", "self_attn.o_norm.weight": "kda_o_norm", "self_attn.o_proj.weight": "kda_o"}
+GLM53_POOL = {"self_attn.indexer.index_kpool_compress_gate": "idx_pool_gate", "self_attn.indexer.index_kpool_compress_ape": "idx_pool_bias"}
+
+
+def _glm53_tensor(cfg, l: int, p: str, rest: str, w: PackedWeight, canon: Dict[str, PackedWeight]) -> bool:
+    """Tensors GLM-5.3-Flash names its own way (crates/poot-models/src/architectures/glm53_flash/names.rs): the
+    hyper-connection sites, the delta-attention layer (whose projections share names with attention's) and the pooling
+    of the indexer.  The layer after the text stack is the multi-token-prediction block: latent attention."""
+    if rest in GLM53_SITE:
+        canon[p + GLM53_SITE[rest]] = w
+        return True
+    if rest in GLM53_POOL:
+        canon[p + GLM53_POOL[rest]] = w
+        return True
+    if l < cfg.n_layers and cfg.mixer_of(l) == "kda":
+        if rest in GLM53_KDA:
+            canon[p + GLM53_KDA[rest]] = w
+            return True
+        m = re.match(r"self_attn\.([qkv])_conv1d\.weight$", rest)
+        if m:                                            # [C, 1, K]
+            a = w.to_f32()
+            canon[p + "kda_conv_" + m.group(1)] = f32_weight(p + "kda_conv_" + m.group(1), a.reshape(a.shape[0], a.shape[-1]))
+            return True
     return False
 
 

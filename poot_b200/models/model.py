@@ -55,6 +55,11 @@ class Model:
     def __init__(self, cfg: DecoderConfig):
         self.cfg = cfg
 
+    def mtp_model(self) -> "Model":
+        """The checkpoint's multi-token-prediction layer as a one-block model of its own."""
+        from .config import mtp_config
+        return type(self)(mtp_config(self.cfg))
+
     def weight_shapes(self) -> Dict[str, tuple]:
         c = self.cfg
         H, D = c.hidden, c.head_dim

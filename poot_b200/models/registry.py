@@ -26,7 +26,8 @@ class FamilyEntry:
     gguf_archs: List[str]
     from_hf: Optional[Callable[[dict], DecoderConfig]]
     missing: Optional[str] = None     # capability that is not built when the family is refused
-    kind: str = "decoder"             # decoder (standard stack) | encoder (embeddings / rerank scores) | vlm (vision tower + decoder) | gemma4 (own tracer)
+    kind: str = "decoder"             # decoder (standard stack) | encoder (embeddings / rerank scores) | vlm (vision tower + decoder) | own (a tracer of its own)
+    tracer: Optional[str] = None      # kind "own": ``module:Class`` under ``models`` whose instances trace the family
 
 
 def _rope_params(c: dict, layer_type: Optional[str] = None) -> dict:
@@ -306,6 +307,64 @@ def _glm_moe_dsa(c):
     return cfg
 
 
+def _glm53(c):
+    """GLM-5.3-Flash (``glm5_next``: the text tower's header sits under ``text_config``; crates/poot-models/src/
+    architectures/glm53_flash/config.rs).  What the tracer does not implement is refused by name, not assumed."""
+    from .glm53 import Glm53Config
+    t = dict(c.get("text_config") or {})
+    if not t:
+        raise UnsupportedFamily("glm5_next header without text_config")
+    for k in ("eos_token_id", "bos_token_id", "tie_word_embeddings"):
+        if c.get(k) is not None:
+            t[k] = c[k]
+    for key, accepted in (("hidden_act", ("silu",)), ("scoring_func", ("sigmoid",)), ("topk_method", ("noaux_tc",))):
+        if t.get(key) is not None and t[key] not in accepted:
+            raise UnsupportedFamily(f"glm5_next {key} {t[key]!r}")
+    for key, supported in (("mla_use_nope", True), ("index_kpool_compress", True), ("index_kpool_always_select_tail", True),
+                           ("attention_bias", False)):
+        if t.get(key) is not None and bool(t[key]) != supported:
+            raise UnsupportedFamily(f"glm5_next with {key}={t[key]!r}")
+    L, H = int(t["num_hidden_layers"]), int(t["hidden_size"])
+    kinds = [{"linear_attention": "kda", "deepseek_sparse_attention": "dsa"}.get(k) for k in (t.get("layer_types") or [])]
+    ffns = list(t.get("mlp_layer_types") or [])
+    if len(kinds) != L or None in kinds or len(ffns) != L or any(f not in ("dense", "sparse") for f in ffns):
+        raise UnsupportedFamily(f"glm5_next layer schedule {t.get('layer_types')!r} / {t.get('mlp_layer_types')!r} for {L} layers")
+    mtp = int(t.get("num_nextn_predict_layers") or 0)
+    has_dsa = "dsa" in kinds or mtp > 0
+    if has_dsa and int(t.get("qk_rope_head_dim") or 0) != 0:
+        raise UnsupportedFamily("glm5_next with a rotary part in its latent attention")
+    if has_dsa and any(x != "full" for x in (t.get("indexer_types") or [])):
+        raise UnsupportedFamily(f"glm5_next indexer types {t.get('indexer_types')!r}")
+    lin = dict(t.get("linear_attn_config") or {})
+    if "kda" in kinds and not all(k in lin for k in ("num_heads", "head_dim", "short_conv_kernel_size", "gate_lower_bound")):
+        raise UnsupportedFamily("glm5_next linear-attention layers without a complete linear_attn_config")
+    lower = float(lin.get("gate_lower_bound", -5.0))
+    if not lower < 0:
+        raise UnsupportedFamily(f"glm5_next gate_lower_bound {lower}")
+    pool, topk = int(t.get("index_kpool") or 1), int(t.get("index_topk") or 0)
+    if has_dsa and (topk < 1 or topk % pool):
+        raise UnsupportedFamily(f"glm5_next index_topk {topk} is not a positive multiple of index_kpool {pool}")
+    sparse = "sparse" in ffns
+    inter = int(t.get("moe_intermediate_size") or 0)
+    return Glm53Config(
+        name="glm53_flash", family="glm53_flash", n_layers=L, hidden=H, n_heads=int(t.get("num_attention_heads") or 1),
+        n_kv_heads=int(t.get("num_attention_heads") or 1), head_dim=int(t.get("qk_nope_head_dim") or 0) or 1,
+        ffn=int(t.get("intermediate_size") or 0), vocab=int(t["vocab_size"]), norm_eps=float(t.get("rms_norm_eps", 1e-5)),
+        max_position=int(t["max_position_embeddings"]), tie_embeddings=bool(t.get("tie_word_embeddings", False)), pos="none",
+        layer_kinds=kinds, ffn_kinds=ffns, hc_mult=int(t["hc_mult"]), hc_eps=float(t.get("hc_eps", 1e-6)),
+        hc_iters=int(t["hc_sinkhorn_iters"]), kda_heads=int(lin.get("num_heads") or 0), kda_head_dim=int(lin.get("head_dim") or 0),
+        kda_conv=int(lin.get("short_conv_kernel_size") or 4), kda_lower_bound=lower,
+        q_lora_rank=int(t.get("q_lora_rank") or 0), kv_lora_rank=int(t.get("kv_lora_rank") or 0),
+        qk_nope_dim=int(t.get("qk_nope_head_dim") or 0), v_head_dim=int(t.get("v_head_dim") or 0),
+        index_n_heads=int(t.get("index_n_heads") or 0), index_head_dim=int(t.get("index_head_dim") or 0), index_topk=topk,
+        index_kpool=pool, n_experts=int(t.get("n_routed_experts") or 0) if sparse else 0,
+        top_k=int(t.get("num_experts_per_tok") or 0), moe_ffn=inter, n_shared_experts=int(t.get("n_shared_experts", 1)),
+        n_group=int(t.get("n_group") or 1), topk_group=int(t.get("topk_group") or 1),
+        routed_scale=float(t.get("routed_scaling_factor", 1.0)), norm_topk_prob=bool(t.get("norm_topk_prob", True)),
+        router="sigmoid", router_select_bias=True, swiglu_limit=float(t.get("swiglu_limit", 10.0)), mtp_layers=mtp,
+        bos_token=_token(t.get("bos_token_id"), 1), eos_token=_token(t.get("eos_token_id"), 2))
+
+
 def _deepseek2(c): return _deepseek(c, "deepseek2")
 def _deepseek3(c): return _deepseek(c, "deepseek3")
 
@@ -467,7 +526,7 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("bloom", ["bloom"], ["bloom"], _bloom),
     FamilyEntry("gemma3", ["gemma3", "gemma3_text"], ["gemma3"], _gemma3),
     FamilyEntry("gemma2", ["gemma2"], ["gemma2"], _gemma2),
-    FamilyEntry("gemma4", ["gemma4", "gemma4_text"], ["gemma4"], _gemma4, kind="gemma4"),
+    FamilyEntry("gemma4", ["gemma4", "gemma4_text"], ["gemma4"], _gemma4, kind="own", tracer="gemma4:Gemma4Model"),
     FamilyEntry("qwen3moe", ["qwen3_moe"], ["qwen3moe"], _qwen3moe),
     FamilyEntry("gpt_oss", ["gpt_oss"], ["gpt-oss"], _gpt_oss),
     FamilyEntry("olmoe", ["olmoe"], ["olmoe"], _olmoe),
@@ -482,10 +541,10 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("bert", ["bert"], ["bert"], _bert, kind="encoder"),
     FamilyEntry("idefics3", ["idefics3", "smolvlm"], [], _idefics3, kind="vlm"),
     FamilyEntry("qwen_vl", ["qwen2_5_vl"], [], _qwen_vl, kind="vlm"),
+    FamilyEntry("glm53_flash", ["glm5_next"], [], _glm53, kind="own", tracer="glm53:Glm53Model"),
     # families the reference ships whose mixers are not built here: refused by name
     FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
     FamilyEntry("qwen38", ["qwen4_exp"], ["qwen4exp"], None, "block-indexed sparse attention, hyper-connection residual streams, n-gram embeddings"),
-    FamilyEntry("glm53_flash", ["glm5_flash"], ["glm53"], None, "kimi delta attention, hyper-connection residual streams"),
 ]
 
 
@@ -510,9 +569,10 @@ class Registry:
                 if e.kind == "encoder":
                     from .encoder import EncoderModel
                     return EncoderModel(e.from_hf(config))
-                if e.kind == "gemma4":
-                    from .gemma4 import Gemma4Model
-                    return Gemma4Model(e.from_hf(config))
+                if e.kind == "own":
+                    import importlib
+                    mod, cls = e.tracer.split(":")
+                    return getattr(importlib.import_module("." + mod, __package__), cls)(e.from_hf(config))
                 if e.kind == "vlm":
                     from .vision import QwenVisionConfig, QwenVisionTower, VisionLanguageModel, VisionTower
                     text, vision, image_token = e.from_hf(config)

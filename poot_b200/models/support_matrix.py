@@ -45,6 +45,14 @@ SAMPLES = {
     "gemma4": dict(model_type="gemma4_text", head_dim=256, global_head_dim=512, hidden_size_per_layer_input=256, num_kv_shared_layers=2,
                    vocab_size_per_layer_input=32000, sliding_window=512,
                    layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "glm53_flash": dict(model_type="glm5_next", text_config=dict(
+        vocab_size=151552, hidden_size=2048, num_hidden_layers=4, num_nextn_predict_layers=1, max_position_embeddings=131072,
+        layer_types=["linear_attention", "linear_attention", "linear_attention", "deepseek_sparse_attention"],
+        mlp_layer_types=["dense", "sparse", "sparse", "sparse"],
+        linear_attn_config=dict(num_heads=32, head_dim=128, short_conv_kernel_size=4, gate_lower_bound=-5.0), hc_mult=4,
+        hc_sinkhorn_iters=20, num_attention_heads=32, q_lora_rank=1024, kv_lora_rank=512, qk_nope_head_dim=192, qk_rope_head_dim=0,
+        v_head_dim=128, index_n_heads=32, index_head_dim=128, index_topk=2048, index_kpool=4, intermediate_size=10240,
+        moe_intermediate_size=1536, n_routed_experts=128, num_experts_per_tok=8, n_shared_experts=1, routed_scaling_factor=2.5)),
     "bert": dict(model_type="bert", num_attention_heads=12, intermediate_size=3072, hidden_size=768),
     "idefics3": dict(model_type="idefics3", text_config=dict(model_type="llama", hidden_size=2048, num_hidden_layers=4,
                                                              num_attention_heads=32, num_key_value_heads=32, intermediate_size=8192,

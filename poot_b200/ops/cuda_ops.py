@@ -31,6 +31,7 @@ _SIGS = {
     "poot_causal_conv_silu": [_P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, _P],
     "poot_ssd_scan": [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "poot_gdn_scan": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
+    "poot_kda_scan": [_P, _P, _P, c_int, c_int, _P, _P, c_float, _P, c_int, _P, c_int, _P, c_int, c_int, _P],
     "poot_gated_rmsnorm": [_P, _P, c_int, c_int, _P, c_int, c_float, c_int, _P, c_int, c_int, c_int, _P],
     "poot_sigmoid_mul": [_P, _P, c_longlong, _P],
     "poot_add_bf16": [_P, _P, _P, c_longlong, _P],
@@ -780,6 +781,21 @@ def gdn_scan(qkv: torch.Tensor, ba: torch.Tensor, b_col: int, a_col: int, dt_bia
     assert state.dtype == torch.float32 and state.is_contiguous() and out.is_contiguous() and D in (64, 128)
     check(_fn("poot_gdn_scan")(_ptr(qkv), _ptr(ba), ba.stride(0), b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state),
                                state.shape[0], _ptr(segs), segs.shape[0], _ptr(out), nk, nv, D, _stream()), "gdn_scan")
+    return out
+
+
+def kda_scan(qkv: torch.Tensor, f: torch.Tensor, bm: torch.Tensor, b_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+             lower_bound: float, state: torch.Tensor, segs: torch.Tensor, out: torch.Tensor, heads: int, D: int) -> torch.Tensor:
+    """Kimi delta attention's recurrence over each sequence piece (crates/poot-models/src/components/kda.rs): the delta
+    rule of :func:`gdn_scan` with a decay per key channel.  ``qkv[T, 3 * heads * D]`` holds q | k | v after the
+    convolution, ``f[T, heads * D]`` the raw low-rank gate projection, ``bm[T, ld]`` the raw beta projection at column
+    ``b_col``; row ``i`` of a head's state decays by ``exp(lower_bound * sigmoid(exp(a_log[h]) * (f[h, i] + dt_bias[h, i])))``."""
+    _need_cuda(qkv, state)
+    assert qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and f.dtype == torch.bfloat16 and f.is_contiguous()
+    assert bm.dtype == torch.bfloat16 and bm.stride(1) == 1 and qkv.shape[1] == 3 * heads * D and f.shape[1] == heads * D
+    assert state.dtype == torch.float32 and state.is_contiguous() and out.is_contiguous() and D in (64, 128) and lower_bound < 0
+    check(_fn("poot_kda_scan")(_ptr(qkv), _ptr(f), _ptr(bm), bm.stride(0), b_col, _ptr(dt_bias), _ptr(a_log), float(lower_bound),
+                               _ptr(state), state.shape[0], _ptr(segs), segs.shape[0], _ptr(out), heads, D, _stream()), "kda_scan")
     return out
 
 

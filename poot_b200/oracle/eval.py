@@ -101,7 +101,7 @@ def _scan(family: str, ins) -> np.ndarray:
         s = s.copy()
         y = np.zeros((H, L, D), np.float32)
         for t in range(L):
-            s = s * np.exp(g[:, t])[:, :, None]
+            s = s * np.exp(g[:, t])[:, :, None]                 # g [H,1]: the whole state; [H,D]: row i by exp(g[i])
             kv = np.einsum("hk,hkv->hv", k[:, t], s)
             d = (v[:, t] - kv) * beta[:, t]
             s = (s + k[:, t][:, :, None] * d[:, None, :]).astype(np.float32)

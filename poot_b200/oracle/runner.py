@@ -33,7 +33,8 @@ class OracleSession:
 
     def __init__(self, model: Model, weights: Dict[str, np.ndarray], rows: int = 1, capacity: int = 64,
                  paged: bool = True, options: Optional[EvalOptions] = None, block_order: Optional[Sequence[int]] = None,
-                 world: int = 1, rank: int = 0, graph_transform=None):
+                 world: int = 1, rank: int = 0, graph_transform=None, logit_rows: str = "last"):
+        self.logit_rows = logit_rows               # "all": ``step`` returns the logits of every token of the step
         self.model, self.weights, self.rows, self.capacity, self.paged = model, weights, rows, capacity, paged
         self.options = options or EvalOptions(matmul_precision="exact")
         self.graphs: Dict[int, object] = {}
@@ -50,7 +51,7 @@ class OracleSession:
         key = (tokens, embeds, mrope) if mrope else (tokens, embeds)
         if key not in self.graphs:
             spec = StepSpec(rows=self.rows, tokens=tokens, capacity=self.capacity, paged=self.paged, world=self.world,
-                            embeds=embeds, mrope=mrope)
+                            embeds=embeds, mrope=mrope, logit_rows=self.logit_rows)
             g = self.model.trace(spec)
             self.graphs[key] = self.graph_transform(g) if self.graph_transform is not None else g
         return self.graphs[key]

@@ -100,6 +100,8 @@ def plan_eqn(g: Graph, k: int, e: Eqn, world: int = 1) -> Plan:
         # recurrence (N x P state per head); the state update and the output come out of one launch per layer
         kind = e.attrs.get("family")
         kernel = {"delta_rule": "poot_gdn_scan", "ssd": "poot_ssd_scan"}.get(kind)
+        if kind == "delta_rule" and g.types[e.inputs[3]].shape[-1] > 1:
+            kernel, kind = "poot_kda_scan", "delta_rule with a decay per key channel"
         if kernel is None:
             raise Refusal(k, op, dt, TARGET, f"no kernel for the {kind!r} recurrence")
         return Plan("dispatch", [kernel], f"{kind}: state carried per (sequence, head) in shared memory")

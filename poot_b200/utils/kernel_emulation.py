@@ -158,6 +158,30 @@ def gdn_scan(qkv, ba, b_col, a_col, dt_bias, a_log, state, segs, out, nk, nv, D)
     return out
 
 
+def kda_scan(qkv, f, bm, b_col, dt_bias, a_log, lower_bound, state, segs, out, heads, D):
+    C = heads * D
+    for first, n, seq, pos0 in segs.tolist():
+        if n == 0:
+            continue
+        S = torch.zeros(heads, D, D) if pos0 == 0 else state[seq].clone()
+        x = qkv[first:first + n].float()
+        unit = lambda t: t / torch.sqrt((t * t).sum(-1, keepdim=True) + 1e-6)
+        q = unit(x[:, :C].reshape(n, heads, D)) * (D ** -0.5)
+        k = unit(x[:, C:2 * C].reshape(n, heads, D))
+        v = x[:, 2 * C:].reshape(n, heads, D)
+        gate = torch.sigmoid(torch.exp(a_log.float())[None, :, None] * (f[first:first + n].float() + dt_bias.float()).reshape(n, heads, D))
+        decay = torch.exp(lower_bound * gate)
+        beta = torch.sigmoid(bm[first:first + n, b_col:b_col + heads].float())
+        for t in range(n):
+            S = S * decay[t][:, :, None]
+            kv = torch.einsum("hk,hkv->hv", k[t], S)
+            d = (v[t] - kv) * beta[t][:, None]
+            S = S + k[t][:, :, None] * d[:, None, :]
+            out[first + t] = _bf(torch.einsum("hk,hkv->hv", q[t], S).reshape(-1))
+        state[seq] = S
+    return out
+
+
 def gated_rmsnorm(y, z, z_col, w, eps, out, heads, D, gate_first=False):
     T = y.shape[0]
     yy = y.float().reshape(T, heads, D)
@@ -715,7 +739,7 @@ def emulated_kernels():
     from ..ops import moe_ops, suffix_ops
     table = {
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
-                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, replace_rows_=replace_rows_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, ssd_scan=ssd_scan,
+                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, replace_rows_=replace_rows_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, kda_scan=kda_scan, ssd_scan=ssd_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 bias_add_=bias_add_, bias_add_indexed_=bias_add_indexed_, scale_=scale_, gather_rows=gather_rows,
                 sigmoid_gate_rows_=sigmoid_gate_rows_,

@@ -392,6 +392,31 @@ def test_gdn_kernels_match_their_host_restatements(D):
     assert tol(got, want)
 
 
+@pytest.mark.xfail(strict=False, reason="new kernel: not yet run on a device")
+@pytest.mark.parametrize("D", [64, 128])
+def test_kda_scan_matches_its_host_restatement(D):
+    """The delta rule with a decay per key channel against the host restatement (itself checked against the graph
+    oracle's scan equation): outputs and carried states of pieces that start at zero and that continue."""
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.utils import kernel_emulation as emu
+    g = torch.Generator().manual_seed(1)
+    heads, rows, T = 3, 3, 21
+    C = heads * D
+    qkv = (torch.randn(T, 3 * C, generator=g) * 0.5).to(torch.bfloat16)
+    f = (torch.randn(T, C, generator=g)).to(torch.bfloat16)
+    bm = (torch.randn(T, heads + 5, generator=g)).to(torch.bfloat16)
+    segs = torch.tensor([[0, 8, 2, 0], [8, 1, 0, 5], [9, 12, 1, 16], [0, 0, 0, 0]], dtype=torch.int32)
+    state = torch.randn(rows, heads, D, D, generator=g) * 0.05
+    dt_bias, a_log = torch.randn(C, generator=g) * 0.3, torch.log(torch.rand(heads, generator=g) * 2 + 0.5)
+    s_ref, y_ref = state.clone(), torch.zeros(T, C, dtype=torch.bfloat16)
+    emu.kda_scan(qkv, f, bm, 2, dt_bias, a_log, -5.0, s_ref, segs, y_ref, heads, D)
+    s_dev, y = state.cuda(), torch.zeros(T, C, dtype=torch.bfloat16, device="cuda")
+    K.kda_scan(qkv.cuda(), f.cuda(), bm.cuda(), 2, dt_bias.cuda(), a_log.cuda(), -5.0, s_dev, segs.cuda(), y, heads, D)
+    K.check_status()
+    tol = lambda a, b: (a.float().cpu() - b.float()).abs().max().item() <= 0.02 * b.float().abs().max().item() + 2e-3
+    assert tol(y, y_ref) and tol(s_dev, s_ref)
+
+
 @pytest.mark.xfail(strict=False, reason="general attention kernel: not yet run on a device")
 @pytest.mark.parametrize("Dk,Dv,extras", [(256, 256, False), (192, 128, False), (64, 64, True)])
 def test_general_attention_matches_its_host_restatement(Dk, Dv, extras):
