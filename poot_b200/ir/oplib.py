@@ -306,7 +306,8 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
                select_bias: Optional[Traced] = None, n_group: int = 1, topk_group: int = 1, routed_scale: float = 1.0,
                act: str = "silu", limit: float = 0.0, alpha: float = 1.702, in_bias: Optional[Traced] = None,
                out_bias: Optional[Traced] = None, gated: bool = True, precision: str = "narrow",
-               router_x: Optional[Traced] = None, expert_scale: Optional[Traced] = None) -> Traced:
+               router_x: Optional[Traced] = None, expert_scale: Optional[Traced] = None,
+               route_ids: Optional[Traced] = None) -> Traced:
     """Routed experts in every variant the shipped families use (components/router.rs, ops/moe.rs).
 
     ``score``: ``softmax`` over all experts or ``sigmoid`` per expert.  Selection ranks ``score + select_bias`` (the
@@ -315,11 +316,24 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
     the selected experts, divided by their sum when ``renorm``, times ``routed_scale``.  Experts: ``w_in[E, 2F, H]``
     gate rows then up rows (+ ``in_bias[E, 2F]``), ``w_out[E, H, F]`` (+ ``out_bias[E, H]``); with ``gated=False``
     ``w_in[E, F, H]`` and the expert is ``down(act(up(x)))``.  ``router_x``: the router reads these rows instead of
-    the experts' input; ``expert_scale[E]`` multiplies the gate of each expert after the renormalisation."""
+    the experts' input; ``expert_scale[E]`` multiplies the gate of each expert after the renormalisation.
+    ``score="sqrtsoftplus"``: ``sqrt(softplus(logit))`` per expert (DeepSeek-V4).  ``route_ids[L, k]`` I32: the experts
+    come from a table instead of a ranking (a hash-routed layer); they are gated by their own scores, normalised over
+    the selection when ``renorm``, times ``routed_scale`` (architectures/deepseek4/moe.rs ``hash_routes``)."""
     L, H = x.shape
     E, F2, _ = w_in.shape
     F = F2 // 2 if gated else F2
     logits = linear(b, router_x if router_x is not None else x, router, router_bias, precision="exact")
+    scored = {"softmax": lambda t: softmax(b, t), "sigmoid": lambda t: sigmoid(b, t),
+              "sqrtsoftplus": lambda t: b.unary("sqrt", softplus_stable(b, t))}[score]
+    if route_ids is not None:
+        probs = canonical_router_scores(b, scored(logits))
+        flat_ids = b.reshape(route_ids, (L * k,))
+        sel = b.reshape(b.gather(b.reshape(probs, (L * E,)), b.reshape(b.iota((L, k), 0) * E, (L * k,)) + flat_ids, 0), (L, k))
+        if renorm:
+            sel = sel / b.broadcast(sel.sum(-1, keepdim=True), sel.shape)
+        gates = b.reshape(sel * routed_scale if routed_scale != 1.0 else sel, (L * k, 1))
+        return _experts(b, x, w_in, w_out, flat_ids, gates, k, act, limit, alpha, in_bias, out_bias, gated, precision)
     if score == "softmax" and renorm and select_bias is None and n_group == 1:
         # softmax over all, pick k, renormalise == softmax over the k selected logits
         scores = canonical_router_scores(b, logits)
@@ -330,7 +344,7 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
         ex = b.unary("exp", sel - b.broadcast(m, sel.shape)) * b.cast(keep, F32)
         gates_all = ex / b.broadcast(ex.sum(-1, keepdim=True), ex.shape)
     else:
-        probs = softmax(b, logits) if score == "softmax" else sigmoid(b, logits)
+        probs = scored(logits)
         choice = probs + b.broadcast(select_bias, probs.shape) if select_bias is not None else probs
         choice = canonical_router_scores(b, choice)
         if n_group > 1:
@@ -355,6 +369,16 @@ def moe_routed(b: Builder, x: Traced, router: Traced, w_in: Traced, w_out: Trace
     flat_ids = b.reshape(ids, (L * k,))
     gates = b.reshape(b.gather(b.reshape(gates_all, (L * E,)),
                                b.reshape(b.iota((L, k), 0) * E, (L * k,)) + flat_ids, 0), (L * k, 1))
+    return _experts(b, x, w_in, w_out, flat_ids, gates, k, act, limit, alpha, in_bias, out_bias, gated, precision)
+
+
+def _experts(b: Builder, x: Traced, w_in: Traced, w_out: Traced, flat_ids: Traced, gates: Traced, k: int, act: str,
+             limit: float, alpha: float, in_bias: Optional[Traced], out_bias: Optional[Traced], gated: bool,
+             precision: str) -> Traced:
+    """Every token through its ``k`` routed experts (``flat_ids[L * k]``, ``gates[L * k, 1]``) and their gated sum."""
+    L, H = x.shape
+    F2 = w_in.shape[1]
+    F = F2 // 2 if gated else F2
     xr = b.reshape(b.broadcast(b.reshape(x, (L, 1, H)), (L, k, H)), (L * k, H))
     gu = b.indexed_matmul(xr, b.transpose(w_in, (0, 2, 1)), flat_ids, precision)     # [L*k, 2F]
     if in_bias is not None:

@@ -251,6 +251,8 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
         return {**_map_qwen_vision(store), **map_checkpoint(text, store)}
     if cfg.family == "gemma4":
         return _map_gemma4(cfg, store)
+    if cfg.family == "deepseek4":
+        return _map_deepseek4(cfg, store)
     if cfg.family == "idefics3":
         text = replace(cfg, family="llama")
         return {**_map_vision(store), **map_checkpoint(text, _Renamed(store, "model.text_model.", "model."))}
@@ -393,6 +395,49 @@ def _glm53_tensor(cfg, l: int, p: str, rest: str, w: PackedWeight, canon: Dict[s
             canon[p + "kda_conv_" + m.group(1)] = f32_weight(p + "kda_conv_" + m.group(1), a.reshape(a.shape[0], a.shape[-1]))
             return True
     return False
+
+
+DEEPSEEK4_TOP = {"embed.weight": "embed", "norm.weight": "final_norm", "head.weight": "lm_head", "hc_head_fn": "hc_head_fn",
+                 "hc_head_base": "hc_head_base", "hc_head_scale": "hc_head_scale"}
+DEEPSEEK4_LAYER = {
+    "attn_norm.weight": "attn_norm", "ffn_norm.weight": "ffn_norm", "attn.q_norm.weight": "attn_q_a_norm",
+    "attn.kv_norm.weight": "attn_kv_norm", "attn.attn_sink": "attn_sinks", "attn.wq_a.weight": "attn_q_a", "attn.wq_b.weight": "attn_q_b",
+    "attn.wkv.weight": "attn_kv", "attn.wo_a.weight": "attn_o_a", "attn.wo_b.weight": "attn_o", "ffn.gate.weight": "ffn_router",
+    "ffn.gate.bias": "ffn_router_select_bias", "ffn.shared_experts.w1.weight": "shared_gate", "ffn.shared_experts.w3.weight": "shared_up",
+    "ffn.shared_experts.w2.weight": "shared_down", "attn.compressor.wkv.weight": "cmp_kv", "attn.compressor.wgate.weight": "cmp_gate",
+    "attn.compressor.ape": "cmp_bias", "attn.compressor.norm.weight": "cmp_norm", "attn.indexer.wq_b.weight": "idx_q",
+    "attn.indexer.weights_proj.weight": "idx_weights", "attn.indexer.compressor.wkv.weight": "idx_cmp_kv",
+    "attn.indexer.compressor.wgate.weight": "idx_cmp_gate", "attn.indexer.compressor.ape": "idx_cmp_bias",
+    "attn.indexer.compressor.norm.weight": "idx_cmp_norm",
+    **{f"hc_{site}_{part}": f"hc_{site}_{part}" for site in ("attn", "ffn") for part in ("fn", "base", "scale")}}
+
+
+def _map_deepseek4(cfg, store: WeightStore) -> Dict[str, PackedWeight]:
+    """DeepSeek-V4 tensors in the release's own naming (no ``model.`` prefix: ``embed.weight``, ``layers.N.attn.wq_a.weight``,
+    ``layers.N.ffn.experts.E.w1.weight``, ``head.weight``; crates/poot-models/src/architectures/deepseek4/names.rs).  A
+    hash-routed layer's token-to-experts table (``ffn.gate.tid2eid``, integers) is kept as exact small numbers."""
+    canon: Dict[str, PackedWeight] = {}
+    for n in store.names():
+        if n in DEEPSEEK4_TOP:
+            canon[DEEPSEEK4_TOP[n]] = store[n]
+            continue
+        m = re.match(r"layers\.(\d+)\.(.+)$", n)
+        if not m:
+            continue
+        p, rest = f"layers.{m.group(1)}.", m.group(2)
+        if rest in DEEPSEEK4_LAYER:
+            canon[p + DEEPSEEK4_LAYER[rest]] = store[n]
+        elif rest == "ffn.gate.tid2eid":
+            w = store[n]
+            raw = w.planar["__raw__"] if getattr(w, "planar", None) and "__raw__" in w.planar else w.to_f32()
+            if raw.min() < 0 or raw.max() >= cfg.n_experts:
+                raise CheckpointLayout(f"{n}: expert ids outside [0, {cfg.n_experts})")
+            canon[p + "ffn_hash_table"] = f32_weight(p + "ffn_hash_table", np.asarray(raw, np.float32))
+        else:
+            e = re.match(r"ffn\.experts\.(\d+)\.(w[123])\.weight$", rest)
+            if e:
+                canon[p + f"experts.{e.group(1)}.{EXPERT[e.group(2)]}"] = store[n]
+    return canon
 
 
 NEMOTRON_MIXER = {"mixer.dt_bias": "ssm_dt_bias", "mixer.A_log": "ssm_a_log", "mixer.D": "ssm_d", "mixer.conv1d.bias": "ssm_conv_bias",

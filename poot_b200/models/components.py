@@ -206,3 +206,50 @@ def pooled_dsa(b: Builder, x: Traced, W: Callable[[str], Traced], p: str, positi
     mask = pooled_keep(b, x, qr, W, p, positions, cached, ni, di, pool, pool_topk)
     a = O.attention_masked(b, q, b.slice(kv, 3, 0, qk), b.slice(kv, 3, qk, vd), mask, qk ** -0.5, 1, 0.0)
     return O.linear(b, b.reshape(b.transpose(a, (0, 2, 1, 3)), (L, n_heads * vd)), W(p + "attn_o"))
+
+
+# ---- interleaved rotary on the trailing channels -----------------------------------------------------------------------
+def rotate_tail(b: Builder, x: Traced, cos: Traced, sin: Traced, rot: int, inverse: bool = False) -> Traced:
+    """Rotate the trailing ``rot`` channels of ``x[R, heads, n, D]`` as INTERLEAVED pairs ``(x[2i], x[2i + 1])`` by the
+    angles of ``cos`` / ``sin`` (``[R, n, rot]`` rows of the duplicated-halves tables: entry ``i`` of the first half is
+    pair ``i``'s); the leading channels pass through.  ``inverse`` turns the other way, which undoes the rotation at
+    the same positions (crates/poot-models/src/architectures/deepseek4/sliding.rs ``rotate_tail``)."""
+    R, Hh, n, D = x.shape
+    half = rot // 2
+    tail = b.reshape(b.slice(x, 3, D - rot, rot), (R, Hh, n, half, 2))
+    a, c_ = b.reshape(b.slice(tail, 4, 0, 1), (R, Hh, n, half)), b.reshape(b.slice(tail, 4, 1, 1), (R, Hh, n, half))
+    co = b.broadcast(b.reshape(b.slice(cos, -1, 0, half), (R, 1, n, half)), a.shape)
+    si = b.broadcast(b.reshape(b.slice(sin, -1, 0, half), (R, 1, n, half)), a.shape)
+    if inverse:
+        si = -si
+    out = b.concat([b.reshape(a * co - c_ * si, (R, Hh, n, half, 1)), b.reshape(a * si + c_ * co, (R, Hh, n, half, 1))], 4)
+    out = b.reshape(out, (R, Hh, n, rot))
+    return b.concat([b.slice(x, 3, 0, D - rot), out], 3) if rot < D else out
+
+
+def pairwise_rank(b: Builder, s: Traced) -> Traced:
+    """``rank[..., i]`` = how many entries of the last axis are STRICTLY greater than entry ``i``: exact ties share a
+    rank, so a cut at ``k`` may keep more than ``k`` (the attention-side selectors' rule, unlike the router's stable
+    rank; crates/poot-models/src/components/sparse_top_k.rs)."""
+    shape = tuple(s.shape)
+    n = shape[-1]
+    mine = b.broadcast(b.reshape(s, shape + (1,)), shape + (n,))
+    other = b.broadcast(b.reshape(s, shape[:-1] + (1, n)), shape + (n,))
+    return b.cast(O.lnot(b, b.binary("ge", mine, other)), I32).sum(-1)
+
+
+def softmax_pool(b: Builder, kv: Traced, gate: Traced) -> Traced:
+    """``[R, windows, positions, channels] -> [R, windows, channels]``: per channel, the softmax of ``gate`` over a
+    window's positions weights its ``kv`` rows."""
+    w = b.transpose(O.softmax(b, b.transpose(gate, (0, 1, 3, 2))), (0, 1, 3, 2))
+    return (kv * w).sum(2)
+
+
+def paged_cache(b: Builder, name: str, rows_: Traced, slots: int, kv_dtype: DType, write_map: Traced, read_map: Traced) -> Traced:
+    """Write this step's rows ``[L, width]`` into the paged pool ``name`` (one head) and read the sequence's positions
+    back in order, through the storage dtype: ``[R, 1, cap, width]``."""
+    L, width = rows_.shape
+    pool_in = b.state(name, (slots, 1, width), kv_dtype, "blocked").cast(F32)
+    nxt = b.scatter_update(pool_in, write_map, b.reshape(rows_, (L, 1, width)))
+    b.output(nxt.cast(kv_dtype), name + ".next", "state_next", name)
+    return O.paged_view(b, nxt.cast(kv_dtype).cast(F32), read_map)

@@ -365,6 +365,51 @@ def _glm53(c):
         bos_token=_token(t.get("bos_token_id"), 1), eos_token=_token(t.get("eos_token_id"), 2))
 
 
+def _deepseek4(c):
+    """DeepSeek-V4 (``deepseek_v4``; crates/poot-models/src/architectures/deepseek4/config.rs).  The layer kinds come
+    from ``compress_ratios`` (0: window only; the sparse rate; the heavy rate); a router or a rotary scaling the tracer
+    does not implement is refused by name."""
+    from .deepseek4 import DeepseekV4Config
+    if c.get("scoring_func") not in (None, "sqrtsoftplus"):
+        raise UnsupportedFamily(f"deepseek_v4 scoring_func {c.get('scoring_func')!r}")
+    rs = c.get("rope_scaling") or {}
+    if (rs.get("rope_type") or rs.get("type") or "default") not in ("default", "none"):
+        raise UnsupportedFamily(f"deepseek_v4 rope_scaling {rs!r}")
+    L, H, nh, D = int(c["num_hidden_layers"]), int(c["hidden_size"]), int(c["num_attention_heads"]), int(c["head_dim"])
+    rot, groups = int(c["qk_rope_head_dim"]), int(c["o_groups"])
+    if rot > D or rot % 2:
+        raise UnsupportedFamily(f"deepseek_v4 qk_rope_head_dim {rot} for heads of {D}")
+    if (nh * D) % groups:
+        raise UnsupportedFamily(f"deepseek_v4 o_groups {groups} does not divide {nh * D}")
+    rates = dict(c.get("compress_rates") or {})
+    csa, hca = int(rates.get("compressed_sparse_attention", 4)), int(rates.get("heavily_compressed_attention", 128))
+    if csa < 1 or hca < 1 or csa == hca:
+        raise UnsupportedFamily(f"deepseek_v4 compress_rates {rates!r}")
+    ratios = list(c.get("compress_ratios") or [])
+    if len(ratios) < L:
+        raise UnsupportedFamily(f"deepseek_v4 compress_ratios names {len(ratios)} of {L} layers")
+    kinds = [{0: "sliding", csa: "csa", hca: "hca"}.get(int(r)) for r in ratios[:L]]
+    if None in kinds:
+        raise UnsupportedFamily(f"deepseek_v4 compress_ratios {ratios[:L]!r} outside 0 / {csa} / {hca}")
+    ni, di, topk = int(c.get("index_n_heads") or 0), int(c.get("index_head_dim") or 0), int(c.get("index_topk") or 0)
+    if "csa" in kinds and (ni < 1 or topk < 1 or di < rot):
+        raise UnsupportedFamily(f"deepseek_v4 indexer of {ni} heads of {di} keeping {topk}")
+    hashed = int(c.get("num_hash_layers") or 0)
+    if hashed > L:
+        raise UnsupportedFamily(f"deepseek_v4 num_hash_layers {hashed} exceeds {L} layers")
+    return DeepseekV4Config(
+        name="deepseek4", family="deepseek4", n_layers=L, hidden=H, n_heads=nh, n_kv_heads=1, head_dim=D, ffn=0,
+        vocab=int(c["vocab_size"]), norm_eps=float(c.get("rms_norm_eps", 1e-6)), max_position=int(c["max_position_embeddings"]),
+        rope_theta=float(c.get("rope_theta", 10000.0)), compress_rope_theta=float(c.get("compress_rope_theta", 160000.0)),
+        qk_rope_dim=rot, q_lora_rank=int(c["q_lora_rank"]), o_groups=groups, o_lora_rank=int(c["o_lora_rank"]),
+        sliding_window=int(c["sliding_window"]), attn_kinds=kinds, csa_rate=csa, hca_rate=hca, index_n_heads=ni, index_head_dim=di,
+        index_topk=topk, hc_mult=int(c["hc_mult"]), hc_eps=float(c.get("hc_eps", 1e-6)), hc_iters=int(c["hc_sinkhorn_iters"]),
+        n_experts=int(c["n_routed_experts"]), top_k=int(c["num_experts_per_tok"]), moe_ffn=int(c["moe_intermediate_size"]),
+        n_shared_experts=int(c.get("n_shared_experts", 1)), routed_scale=float(c.get("routed_scaling_factor", 1.0)),
+        router="sqrtsoftplus", router_select_bias=True, swiglu_limit=float(c.get("swiglu_limit", 10.0)), hash_layers=hashed,
+        attn_sinks=True, pos="rope", bos_token=_token(c.get("bos_token_id"), 1), eos_token=_token(c.get("eos_token_id"), 2))
+
+
 def _deepseek2(c): return _deepseek(c, "deepseek2")
 def _deepseek3(c): return _deepseek(c, "deepseek3")
 
@@ -542,8 +587,8 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("idefics3", ["idefics3", "smolvlm"], [], _idefics3, kind="vlm"),
     FamilyEntry("qwen_vl", ["qwen2_5_vl"], [], _qwen_vl, kind="vlm"),
     FamilyEntry("glm53_flash", ["glm5_next"], [], _glm53, kind="own", tracer="glm53:Glm53Model"),
+    FamilyEntry("deepseek4", ["deepseek_v4"], [], _deepseek4, kind="own", tracer="deepseek4:DeepseekV4Model"),
     # families the reference ships whose mixers are not built here: refused by name
-    FamilyEntry("deepseek4", ["deepseek_v4"], ["deepseek4"], None, "compressed attention"),
     FamilyEntry("qwen38", ["qwen4_exp"], ["qwen4exp"], None, "block-indexed sparse attention, hyper-connection residual streams, n-gram embeddings"),
 ]
 

@@ -53,6 +53,11 @@ SAMPLES = {
         hc_sinkhorn_iters=20, num_attention_heads=32, q_lora_rank=1024, kv_lora_rank=512, qk_nope_head_dim=192, qk_rope_head_dim=0,
         v_head_dim=128, index_n_heads=32, index_head_dim=128, index_topk=2048, index_kpool=4, intermediate_size=10240,
         moe_intermediate_size=1536, n_routed_experts=128, num_experts_per_tok=8, n_shared_experts=1, routed_scaling_factor=2.5)),
+    "deepseek4": dict(model_type="deepseek_v4", vocab_size=129280, hidden_size=4096, num_hidden_layers=4, num_attention_heads=64,
+                      head_dim=512, qk_rope_head_dim=64, q_lora_rank=1024, o_groups=8, o_lora_rank=1024, sliding_window=128,
+                      compress_ratios=[0, 4, 128, 4], index_n_heads=64, index_head_dim=128, index_topk=512, hc_mult=4,
+                      hc_sinkhorn_iters=20, n_routed_experts=256, num_experts_per_tok=6, moe_intermediate_size=2048,
+                      n_shared_experts=1, routed_scaling_factor=1.5, num_hash_layers=1, max_position_embeddings=1048576),
     "bert": dict(model_type="bert", num_attention_heads=12, intermediate_size=3072, hidden_size=768),
     "idefics3": dict(model_type="idefics3", text_config=dict(model_type="llama", hidden_size=2048, num_hidden_layers=4,
                                                              num_attention_heads=32, num_key_value_heads=32, intermediate_size=8192,
