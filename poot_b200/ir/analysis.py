@@ -103,6 +103,9 @@ def value_ranges(g: Graph) -> Dict[int, Interval]:
         elif op == "arg_top_k":
             n = g.types[e.inputs[0]].shape[-1]
             r[out] = (0, n - 1)
+        elif op == "ngram_hash":                 # every head's id lies in its own slice of the table
+            at = e.attrs
+            r[out] = (min(at["offsets"]), max(o + p_ - 1 for o, p_ in zip(at["offsets"], at["primes"])))
     return r
 
 

@@ -194,6 +194,18 @@ class Builder:
         out = self.emit("scan", list(operands), {"family": family, "chunk": chunk, "shape": (1, H, L + S, Wd)})[0]
         return self.slice(out, 2, 0, L), self.slice(out, 2, L, S)
 
+    def ngram_hash(self, window: Traced, context: int, multipliers, primes, offsets, heads_per_order: int, eos: int) -> Traced:
+        """Hashed n-gram ids of a token run: ``window[context + t]`` I32 is the ``context`` tokens before the run followed
+        by its ``t`` tokens; the result is ``[t, heads]`` I32 with ``heads = context * heads_per_order``.  For token
+        ``i`` (window index ``context + i``) the order-2 mix is ``m0 * s0 ^ m1 * s1`` over wrapping 64-bit words
+        (``s0`` the token, ``s1`` the one before it) and the order-3 mix xors ``m2 * s2``, where ``s2`` is the token two
+        back, or ``eos`` when ``s1`` is ``eos`` (a context that ends a segment hides what precedes it).  Head ``h`` of
+        order ``2 + h // heads_per_order`` is ``mix % primes[h] + offsets[h]`` (crates/poot-models/src/components/
+        ple.rs ``row_ids``).  One equation: 64-bit integer arithmetic is native on the device."""
+        return self.emit("ngram_hash", [window], {"context": int(context), "multipliers": tuple(int(m) for m in multipliers),
+                                                   "primes": tuple(int(p) for p in primes), "offsets": tuple(int(o) for o in offsets),
+                                                   "heads_per_order": int(heads_per_order), "eos": int(eos)})[0]
+
     def random_uniform(self, seed: Traced, cols: int) -> Traced:
         return self.emit("random_uniform", [seed], {"cols": cols})[0]
 

@@ -22,7 +22,7 @@ UNARY = ("neg", "exp", "log", "sqrt", "recip", "tanh", "erf", "not", "clz")
 BINARY = ("add", "sub", "mul", "div", "max", "ge", "geu", "remu", "and", "or", "xor", "shl", "shr")
 PRIMITIVES = UNARY + BINARY + (
     "select", "reduce", "broadcast", "cast", "reshape", "transpose", "slice", "concat", "iota", "gather",
-    "scatter_update", "matmul", "packed_dequant", "arg_top_k", "indexed_matmul", "dynamic_update_slice", "scan",
+    "scatter_update", "matmul", "packed_dequant", "arg_top_k", "indexed_matmul", "dynamic_update_slice", "scan", "ngram_hash",
     "random_uniform", "sample_token", "all_reduce", "all_gather", "all_to_all")
 COMPOSITES = ("packed_contraction", "packed_row_gather", "dense_contraction", "grouped_dense_contraction",
               "dense_row_gather", "contraction_epilogue", "expert_group", "fused", "fused_row", "side_output",

@@ -164,6 +164,17 @@ def infer(op: str, attrs: Dict[str, Any], ins: List[TensorType], body=None) -> L
         if tuple(attrs["shape"]) != (1, h, l + rows, w):
             raise GraphError("scan: packed shape does not match the operands")
         return [TensorType((1, h, l + rows, w), F32)]
+    if op == "ngram_hash":
+        (win,) = ins
+        ctx, per = attrs["context"], attrs["heads_per_order"]
+        heads = ctx * per
+        if win.dtype != I32 or win.rank != 1 or win.shape[0] <= ctx or ctx not in (1, 2) or per < 1:
+            raise GraphError(f"ngram_hash: window {win.shape} {win.dtype}, context {ctx}, {per} heads per order")
+        if len(attrs["multipliers"]) != ctx + 1 or len(attrs["primes"]) != heads or len(attrs["offsets"]) != heads:
+            raise GraphError("ngram_hash: one multiplier per n-gram position and one prime / offset per head")
+        if any(not 1 < p_ < 2 ** 32 for p_ in attrs["primes"]):
+            raise GraphError("ngram_hash: every head's modulus fits an unsigned 32-bit word")
+        return [TensorType((win.shape[0] - ctx, heads), I32)]
     if op == "random_uniform":
         (seed,) = ins
         return [TensorType(tuple(seed.shape) + (attrs["cols"],), F32)]

@@ -112,12 +112,28 @@ def causal_conv1d(b: Builder, x: Traced, state: Traced, w: Traced, bias: Optiona
     return y, b.slice(xp, 0, L, K - 1)
 
 
-def gated_rmsnorm(b: Builder, y: Traced, z: Traced, w: Traced, eps: float, gate_first: bool) -> Traced:
-    """RMSNorm over the last axis combined with a SiLU gate: ``norm(y * silu(z)) * w`` (Mamba2) or
-    ``norm(y) * w * silu(z)`` (gated delta net)."""
+def gated_rmsnorm(b: Builder, y: Traced, z: Traced, w: Traced, eps: float, gate_first: bool, gate_act: str = "silu") -> Traced:
+    """RMSNorm over the last axis combined with a gate: ``norm(y * silu(z)) * w`` (Mamba2) or ``norm(y) * w * act(z)``
+    (gated delta net; ``act`` is SiLU, or a sigmoid in Qwen3.8-Flash-Next)."""
+    act = {"silu": silu, "sigmoid": sigmoid}[gate_act]
     if gate_first:
-        return rmsnorm(b, y * silu(b, z), w, eps)
-    return rmsnorm(b, y, w, eps) * silu(b, z)
+        return rmsnorm(b, y * act(b, z), w, eps)
+    return rmsnorm(b, y, w, eps) * act(b, z)
+
+
+def causal_conv1d_dilated(b: Builder, x: Traced, state: Traced, w: Traced, dilation: int):
+    """Depthwise causal convolution whose taps are ``dilation`` positions apart: ``y[t] = sum_j w[:, j] *
+    xp[t + j * dilation]`` over ``xp = state ++ x`` with ``state[(K - 1) * dilation, C]`` the previous inputs, oldest
+    first.  Returns ``(y, next_state)`` (crates/poot-models/src/components/conv.rs)."""
+    L, C = x.shape
+    K = w.shape[1]
+    xp = b.concat([state, x], 0)
+    y = None
+    for j in range(K):
+        tap = b.broadcast(b.reshape(b.slice(w, 1, j, 1), (1, C)), (L, C))
+        term = b.slice(xp, 0, j * dilation, L) * tap
+        y = term if y is None else y + term
+    return y, b.slice(xp, 0, L, (K - 1) * dilation)
 
 
 def softcap(b: Builder, x: Traced, cap: float) -> Traced:

@@ -279,10 +279,15 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
             continue
         m = re.match(r"model\.(?:language_model\.)?layers\.(\d+)\.(.+)$", n)
         if not m:
+            top = re.match(r"model\.(?:language_model\.)?hyper_connection_mixer\.(.+)$", n) if cfg.hc_count else None
+            if top and _qwen38_gate("hc_final_", top.group(1)):
+                canon[_qwen38_gate("hc_final_", top.group(1))] = w
             continue
         l, rest = int(m.group(1)), m.group(2)
         p = f"layers.{l}."
-        if cfg.family in ("qwen3next", "qwen38_27b") and _qwen3next_tensor(cfg, p, rest, w, canon):
+        if cfg.family == "qwen38" and _qwen38_tensor(cfg, p, rest, w, canon):
+            continue
+        if cfg.family in ("qwen3next", "qwen38_27b", "qwen38") and _qwen3next_tensor(cfg, p, rest, w, canon):
             continue
         if cfg.family == "glm53_flash" and _glm53_tensor(cfg, l, p, rest, w, canon):
             continue
@@ -438,6 +443,46 @@ def _map_deepseek4(cfg, store: WeightStore) -> Dict[str, PackedWeight]:
             if e:
                 canon[p + f"experts.{e.group(1)}.{EXPERT[e.group(2)]}"] = store[n]
     return canon
+
+
+QWEN38_GATE = {"hc_norm.weight": "norm", "input_mix_weight_down": "down", "input_mix_weight_up": "up", "block_inject_weight": "inject"}
+QWEN38_PLE = {"ple.ple_embedding.ngram_embedding.weight": "ple_table", "ple.key_proj.weight": "ple_key", "ple.value_proj.weight": "ple_value",
+              "ple.norm_key.weight": "ple_key_norm", "ple.norm_query.weight": "ple_query_norm", "ple.norm_conv.weight": "ple_conv_norm"}
+
+
+def _qwen38_gate(stem: str, rest: str):
+    """``<gate>.<tensor>[.weight]`` of a hyper-connection gate -> canonical suffix."""
+    rest = rest[:-len(".weight")] if rest.endswith(".weight") and rest != "hc_norm.weight" else rest
+    return stem + QWEN38_GATE[rest] if rest in QWEN38_GATE else None
+
+
+def _qwen38_tensor(cfg, p: str, rest: str, w: PackedWeight, canon: Dict[str, PackedWeight]) -> bool:
+    """Tensors Qwen3.8-Flash-Next adds to the Qwen3.5 layer (crates/poot-models/src/architectures/qwen38/config.rs): the
+    two hyper-connection gates, the n-gram embedding block and the block indexer, whose query rows and key rows are
+    one fused projection, query rows first."""
+    for site, stem in (("attn_hyper_connection.", "hc_attn_"), ("mlp_hyper_connection.", "hc_ffn_")):
+        if rest.startswith(site):
+            name = _qwen38_gate(p + stem, rest[len(site):])
+            if name is not None:
+                canon[name] = w
+                return True
+    if rest in QWEN38_PLE:
+        canon[p + QWEN38_PLE[rest]] = w
+        return True
+    if rest == "ple.conv1d.weight":                        # [C, 1, K]
+        a = w.to_f32()
+        canon[p + "ple_conv"] = f32_weight(p + "ple_conv", a.reshape(a.shape[0], a.shape[-1]))
+        return True
+    if rest == "self_attn.indexer.index_qk_proj.weight":
+        nq = cfg.index_n_heads * cfg.index_head_dim
+        if w.shape[0] != nq + cfg.index_head_dim:
+            raise CheckpointLayout(f"{w.name}: {w.shape[0]} rows, expected {nq + cfg.index_head_dim} (queries | key)")
+        canon[p + "idx_q"], canon[p + "idx_k"] = w.rows(0, nq), w.rows(nq, cfg.index_head_dim)
+        return True
+    if rest in ("self_attn.indexer.q_layernorm.weight", "self_attn.indexer.k_layernorm.weight"):
+        canon[p + ("idx_q_norm" if ".q_" in rest else "idx_k_norm")] = w
+        return True
+    return False
 
 
 NEMOTRON_MIXER = {"mixer.dt_bias": "ssm_dt_bias", "mixer.A_log": "ssm_a_log", "mixer.D": "ssm_d", "mixer.conv1d.bias": "ssm_conv_bias",

@@ -119,6 +119,22 @@ class DecoderConfig:
     index_topk: int = 0                     # sparse attention: keys each query keeps, picked by the indexer (0: dense attention)
     index_n_heads: int = 0
     index_head_dim: int = 0
+    # gated hyper-connections (Qwen3.8-Flash-Next): the residual is ``hc_count`` parallel streams; every block reads a
+    # gated mean of their grouped norm and writes back into each stream with its own weight (0: one plain stream)
+    hc_count: int = 0
+    hc_lowrank: int = 0
+    index_ratio: int = 0                    # block indexer: positions per scored block (0: the per-position indexer)
+    index_budget: int = 0                   # block indexer: positions kept per query (``index_budget // index_ratio`` blocks)
+    gdn_gate_act: str = "silu"              # activation of the delta-net output gate: silu | sigmoid
+    # per-layer hashed n-gram embedding blocks in front of some layers, in ordinal order (``models/ngram.py``)
+    ple_layers: Optional[list] = None
+    ple_embed_dim: int = 0
+    ple_conv: int = 0
+    ngram_size: int = 0
+    heads_per_ngram: int = 0
+    ngram_vocab_base: int = 0
+    ngram_divisible_by: int = 1
+    ngram_seed: int = 1234
     mrope_sections: Optional[list] = None   # channel pairs of the time / row / column rotary streams (Qwen2.5-VL); None: one stream
     bos_token: int = 1
     eos_token: int = 2
@@ -164,6 +180,14 @@ class DecoderConfig:
     def shared_width(self) -> int:
         return self.shared_ffn or self.n_shared_experts * self.moe_ffn
 
+    def ple_tables(self, layer: int):
+        """Hash constants of the n-gram block in front of ``layer`` (``None``: the layer has none)."""
+        if not self.ple_layers or layer not in self.ple_layers:
+            return None
+        from .ngram import ngram_tables
+        return ngram_tables(self.ple_layers.index(layer), self.ngram_size, self.heads_per_ngram, self.ngram_vocab_base,
+                            self.ngram_divisible_by, self.ngram_seed, self.vocab)
+
     def uses_rope(self, layer: int) -> bool:
         return self.pos == "rope" and (self.rope_layers is None or bool(self.rope_layers[layer]))
 
@@ -205,6 +229,9 @@ class DecoderConfig:
         if self.ssm_heads and self.ssm_head_dim not in (32, 64, 128): g.append(f"Mamba2 head width {self.ssm_head_dim}")
         if self.ssm_heads and self.ssm_conv not in (2, 3, 4): g.append(f"conv width {self.ssm_conv}")
         if self.gdn_k_heads and self.gdn_head_dim not in (64, 128): g.append(f"delta-net head width {self.gdn_head_dim}")
+        if self.hc_count: g.append("gated hyper-connection residual streams")
+        if self.index_ratio: g.append("block-indexed sparse attention")
+        if self.ple_layers: g.append("hashed n-gram embedding blocks")
         if self.head_dim % 32 or not (32 <= self.head_dim <= 512): g.append(f"head_dim {self.head_dim}")
         return g
 

@@ -65,6 +65,15 @@ class Model:
         H, D = c.hidden, c.head_dim
         s = {"embed": (c.vocab, H), "final_norm": (H,)}
         norms = ["final_norm"]
+        S = c.hc_count
+        if S:
+            # gated hyper-connections: no plain norms; every gate has a grouped norm scale, a low-rank gate and, inside
+            # a layer, the per-stream injection projection; the closing gate collapses the streams into the head
+            del s["final_norm"]
+            norms = []
+            gate = lambda stem, inject: {stem + "norm": (S * H,), stem + "down": (c.hc_lowrank, S * H), stem + "up": (S * H, c.hc_lowrank),
+                                         **({stem + "inject": (S, S * H)} if inject else {})}
+            s.update(gate("hc_final_", False))
         if c.embed_norm:
             s["embed_norm"] = (H,)
             norms.append("embed_norm")
@@ -76,7 +85,15 @@ class Model:
         for l in range(c.n_layers):
             p = f"layers.{l}."
             kind, has_ffn = c.mixer_of(l), c.has_ffn(l)
-            if c.block in ("pre", "sandwich"):
+            if S:
+                s.update(gate(p + "hc_attn_", True))
+                s.update(gate(p + "hc_ffn_", True))
+                t_ = c.ple_tables(l)
+                if t_ is not None:
+                    s.update({p + "ple_table": (t_.rows, c.ple_embed_dim // len(t_.primes)), p + "ple_key": (S * H, c.ple_embed_dim),
+                              p + "ple_value": (H, c.ple_embed_dim), p + "ple_key_norm": (S * H,), p + "ple_query_norm": (S * H,),
+                              p + "ple_conv_norm": (S * H,), p + "ple_conv": (S * H, c.ple_conv)})
+            elif c.block in ("pre", "sandwich"):
                 if kind != "none":
                     s[p + "attn_norm"] = (H,)
                     norms.append(p + "attn_norm")
@@ -129,6 +146,9 @@ class Model:
                               p + "attn_k_norm": (c.kv_size if c.qk_norm_wide else D,)})
                 if c.attn_sinks:
                     s[p + "attn_sinks"] = (c.n_heads,)
+                if c.index_ratio:
+                    s.update({p + "idx_q": (c.index_n_heads * c.index_head_dim, H), p + "idx_k": (c.index_head_dim, H),
+                              p + "idx_q_norm": (c.index_head_dim,), p + "idx_k_norm": (c.index_head_dim,)})
             if not has_ffn:
                 continue
             if c.moe_layer(l):
@@ -202,6 +222,7 @@ class Model:
                 tag = "rope.local" if local else "rope"
                 ct = b.computed(tag + ".cos", (c.max_position, rot), F32, "rope_cos", (rot, theta, c.max_position, scaling))
                 st = b.computed(tag + ".sin", (c.max_position, rot), F32, "rope_sin", (rot, theta, c.max_position, scaling))
+                rope_tables.setdefault(("table",), (ct, st))
                 if not flat:
                     flat.append(b.reshape(positions, (R * T,)))
                 if spec.mrope and c.mrope_sections:
@@ -307,7 +328,7 @@ class Model:
                 k = O.rope(b, k, cos, sin, rot)
             K, V = kv_through_cache(p, k, v, D, D)
             qh = b.transpose(b.reshape(q, (R, T, hq, D)), (0, 2, 1, 3))
-            a = O.attention_biased(b, qh, K, V, mask_of(l), scale, hq // hkv, c.attn_softcap, head_bias,
+            a = O.attention_biased(b, qh, K, V, block_mask(l, x) if c.index_ratio else mask_of(l), scale, hq // hkv, c.attn_softcap, head_bias,
                                    W(p + "attn_sinks", (hq,)) if c.attn_sinks else None)
             a = b.reshape(b.transpose(a, (0, 2, 1, 3)), (R * T, hq * D))
             if c.attn_gate:
@@ -318,6 +339,50 @@ class Model:
             if c.out_bias:
                 o = o + b.broadcast(W(p + "attn_o_bias"), o.shape)
             return o
+
+        def block_mask(l: int, x: Traced) -> Traced:
+            """Block indexer (architectures/qwen38/qsa.rs): per-head queries (RMSNorm, partial rotary at the token's
+            position) score BLOCKS of ``index_ratio`` positions, ``sum_h relu(q_h . k_b) / sqrt(dim)``; a block's key is
+            the mean of its positions' raw keys, then RMSNorm, then rotary at the block's first position.  A block is
+            eligible once all of it is at or before the query; the ``index_budget // index_ratio`` best stay (equal
+            scores: the lower block) with all their positions.  The query's own unfinished block is always read,
+            unscored; a query on the last position of its block reads that block only if it is selected.  The raw keys
+            are cached per position (``idx_pool``) and the block keys recomputed from them."""
+            if not spec.paged or cap % c.index_ratio or c.window_of(l):
+                raise ValueError("the block indexer is traced over paged pools whose capacity is a whole number of blocks, without a window")
+            p = f"layers.{l}."
+            ni, di, ratio = c.index_n_heads, c.index_head_dim, c.index_ratio
+            nb = cap // ratio
+            cos, sin = rope_of(l)
+            q = O.rope(b, O.rmsnorm(b, b.reshape(O.linear(b, x, W(p + "idx_q")), (R * T, ni, di)), W(p + "idx_q_norm"), c.norm_eps), cos, sin, rot)
+            pool = b.state(p + "idx_pool", (spec.slots, 1, di), spec.kv_dtype, "blocked").cast(F32)
+            pool2 = b.scatter_update(pool, write_map, b.reshape(O.linear(b, x, W(p + "idx_k")), (R * T, 1, di)))
+            b.output(pool2.cast(spec.kv_dtype), p + "idx_pool.next", "state_next", p + "idx_pool")
+            raw = O.paged_view(b, pool2.cast(spec.kv_dtype).cast(F32), read_map)                      # [R, 1, cap, di]
+            pooled = b.reshape(raw, (R, nb, ratio, di)).sum(2) * (1.0 / ratio)
+            key = (c.rope_theta, "blocks", ratio, nb)
+            if key not in rope_tables:
+                ct, st = rope_tables[("table",)]
+                starts = b.iota((nb,), 0) * ratio
+                rope_tables[key] = tuple(b.reshape(b.broadcast(b.reshape(b.gather(t_, starts, 0), (1, nb, rot)), (R, nb, rot)), (R * nb, rot))
+                                         for t_ in (ct, st))
+            bc, bs = rope_tables[key]
+            kb = O.rope(b, b.reshape(O.rmsnorm(b, pooled, W(p + "idx_k_norm"), c.norm_eps), (R * nb, 1, di)), bc, bs, rot)
+            qh = b.transpose(b.reshape(q, (R, T, ni, di)), (0, 2, 1, 3))
+            kt = b.broadcast(b.reshape(b.transpose(b.reshape(kb, (R, nb, di)), (0, 2, 1)), (R, 1, di, nb)), (R, ni, di, nb))
+            score = O.relu(b, b.matmul(qh, kt, "exact")).sum(1) * (di ** -0.5)                        # [R, T, nb]
+            pos3 = lambda n: b.broadcast(b.reshape(positions, (R, T, 1)), (R, T, n))
+            eligible = b.binary("ge", pos3(nb), b.iota((R, T, nb), 2) * ratio + (ratio - 1))
+            score = b.select(eligible, O.canonical_router_scores(b, score), b.broadcast(b.scalar(-O.F32_MAX, F32), score.shape))
+            kept = min(c.index_budget // ratio, nb)
+            rank = b.reshape(O.stable_descending_rank(b, b.reshape(score, (R * T, nb))), (R, T, nb))
+            chosen = b.binary("and", O.lnot(b, b.binary("ge", rank, b.broadcast(b.scalar(kept, I32), rank.shape))), eligible)
+            spread = b.reshape(b.broadcast(b.reshape(chosen, (R, T, nb, 1)), (R, T, nb, ratio)), (R, T, cap))
+            slots_ = b.iota((R, T, cap), 2)
+            own_from = b.cast(eligible, I32).sum(-1, keepdim=True) * ratio                           # first position past the complete blocks
+            own = b.binary("and", b.binary("ge", slots_, b.broadcast(own_from, (R, T, cap))), b.binary("ge", pos3(cap), slots_))
+            keep = b.binary("or", spread, own)
+            return b.select(keep, b.broadcast(b.scalar(0.0, F32), (R, T, cap)), b.broadcast(b.scalar(O.MASK_HIDDEN, F32), (R, T, cap)))
 
         def sparse_mask(p: str, x: Traced, q_resid: Traced, cos: Traced, sin: Traced, mask: Traced) -> Traced:
             """Sparse attention indexer (components/dsa.rs): a light multi-head scorer over its own cached keys ranks the
@@ -485,11 +550,85 @@ class Model:
             b.output(b.concat(convs, 0) if R > 1 else convs[0], p + "conv_state.next", "state_next", p + "conv_state")
             b.output(b.concat(states, 0) if R > 1 else states[0], p + "gdn_state.next", "state_next", p + "gdn_state")
             y = b.concat(ys, 0) if R > 1 else ys[0]
-            out = O.gated_rmsnorm(b, y, z, W(p + "gdn_gate_norm_w"), c.norm_eps, gate_first=False)
+            out = O.gated_rmsnorm(b, y, z, W(p + "gdn_gate_norm_w"), c.norm_eps, gate_first=False, gate_act=c.gdn_gate_act)
             return O.linear(b, b.reshape(out, (R * T, nv * Dg)), W(p + "gdn_o"))
 
         mixers = {"attention": attention, "mamba": mamba, "gdn": gdn}
-        for l in range(c.n_layers):
+        S, L = c.hc_count, R * T
+
+        def grouped_norm(x: Traced, name: str) -> Traced:
+            """RMSNorm of each of the ``S`` runs of ``H`` values of ``x[L, S * H]`` by its own mean square, then one scale
+            over the whole row (components/ple.rs ``grouped_norm``)."""
+            g3 = b.reshape(x, (L, S, H))
+            den = b.unary("sqrt", (g3 * g3).sum(-1, keepdim=True) * (1.0 / H) + c.norm_eps)
+            return b.reshape(g3 / b.broadcast(den, g3.shape), (L, S * H)) * b.broadcast(W(name), (L, S * H))
+
+        def hc_read(xs: Traced, stem: str, inject: bool):
+            """A gate of the hyper-connections (architectures/qwen38/gated_residual.rs): the block's input is the mean
+            over the streams of ``sigmoid(up(silu(down(n) / S))) * n`` with ``n`` the grouped norm of the streams; the
+            weights that write the block's output back are ``2 * sigmoid(inject(n) / S)`` per stream."""
+            n = grouped_norm(xs, stem + "norm")
+            gate = O.sigmoid(b, O.linear(b, O.silu(b, O.linear(b, n, W(stem + "down")) * (1.0 / S)), W(stem + "up")))
+            x_in = b.reshape(gate * n, (L, S, H)).sum(1) * (1.0 / S)
+            return x_in, (O.sigmoid(b, O.linear(b, n, W(stem + "inject")) * (1.0 / S)) * 2.0 if inject else None)
+
+        def hc_write(xs: Traced, out: Traced, weights: Traced) -> Traced:
+            placed = b.broadcast(b.reshape(out, (L, 1, H)), (L, S, H)) * b.broadcast(b.reshape(weights, (L, S, 1)), (L, S, H))
+            return xs + b.reshape(placed, (L, S * H))
+
+        def ple(l: int, xs: Traced) -> Traced:
+            """Per-layer embedding block (components/ple.rs): hashed n-gram ids of the step's tokens (the ``ngram_size -
+            1`` tokens before the step are carried per sequence, xor-ed with the end-of-sequence id so that a zero
+            state reads as a sequence start) look up one table row per hash head; the rows' key, under a grouped norm,
+            gates their value into every stream by its agreement with the normed streams,
+            ``sigmoid(sign(g) * sqrt(max(|g|, 1e-6)))`` with ``g = key . query / sqrt(H)``; a dilated depthwise causal conv
+            of the normed result, through SiLU, is added to it."""
+            p = f"layers.{l}."
+            tb = c.ple_tables(l)
+            ctx, heads, dil, K = c.ngram_size - 1, len(tb.primes), c.ngram_size, c.ple_conv
+            hist = b.state(p + "ple_history", (R, ctx), I32, "recurrent")
+            eos = b.broadcast(b.scalar(c.eos_token, I32), (ctx,))
+            ids, nxt = [], []
+            for r in range(R):
+                win = b.concat([b.binary("xor", b.reshape(b.slice(hist, 0, r, 1), (ctx,)), eos), b.reshape(b.slice(tokens, 0, r, 1), (T,))], 0)
+                ids.append(b.ngram_hash(win, ctx, tb.multipliers, tb.primes, tb.offsets, c.heads_per_ngram, c.eos_token))
+                nxt.append(b.reshape(b.binary("xor", b.slice(win, 0, T, ctx), eos), (1, ctx)))
+            b.output(b.concat(nxt, 0) if R > 1 else nxt[0], p + "ple_history.next", "state_next", p + "ple_history")
+            ids = b.concat(ids, 0) if R > 1 else ids[0]                                           # [L, heads]
+            emb = b.reshape(b.gather(W(p + "ple_table"), b.reshape(ids, (L * heads,)), 0), (L, c.ple_embed_dim))
+            key = grouped_norm(O.linear(b, emb, W(p + "ple_key")), p + "ple_key_norm")
+            value = O.linear(b, emb, W(p + "ple_value"))
+            query = grouped_norm(xs, p + "ple_query_norm")
+            g_ = b.reshape(key * query, (L, S, H)).sum(-1, keepdim=True) * (H ** -0.5)           # [L, S, 1]
+            mag = b.unary("sqrt", b.binary("max", b.binary("max", g_, -g_), b.broadcast(b.scalar(1e-6, F32), g_.shape)))
+            zero = b.broadcast(b.scalar(0.0, F32), g_.shape)
+            sign = b.cast(b.binary("ge", g_, zero), F32) - b.cast(b.binary("ge", -g_, zero), F32)
+            gated = b.reshape(b.broadcast(O.sigmoid(b, mag * sign), (L, S, H)) * b.broadcast(b.reshape(value, (L, 1, H)), (L, S, H)), (L, S * H))
+            n = grouped_norm(gated, p + "ple_conv_norm")
+            win_in = b.state(p + "ple_conv_state", (R, (K - 1) * dil, S * H), F32, "recurrent")
+            ys, wins = [], []
+            for r in range(R):
+                y, ws = O.causal_conv1d_dilated(b, b.slice(n, 0, r * T, T), b.reshape(b.slice(win_in, 0, r, 1), ((K - 1) * dil, S * H)),
+                                                W(p + "ple_conv"), dil)
+                ys.append(y)
+                wins.append(b.reshape(ws, (1, (K - 1) * dil, S * H)))
+            b.output(b.concat(wins, 0) if R > 1 else wins[0], p + "ple_conv_state.next", "state_next", p + "ple_conv_state")
+            return gated + O.silu(b, b.concat(ys, 0) if R > 1 else ys[0])
+
+        if S:
+            if c.block != "pre" or c.residual_scale != 1.0:
+                raise ValueError("gated hyper-connections are traced for plain pre-gate blocks")
+            xs = b.reshape(b.broadcast(b.reshape(h, (L, 1, H)), (L, S, H)), (L, S * H))
+            for l in range(c.n_layers):
+                p = f"layers.{l}."
+                if c.ple_tables(l) is not None:
+                    xs = xs + ple(l, xs)                  # reads the raw streams, before the layer's first gate
+                x_in, wts = hc_read(xs, p + "hc_attn_", True)
+                xs = hc_write(xs, mixers[c.mixer_of(l)](l, x_in), wts)
+                x_in, wts = hc_read(xs, p + "hc_ffn_", True)
+                xs = hc_write(xs, ffn(l, x_in), wts)
+            h = hc_read(xs, "hc_final_", False)[0]        # the closing gate feeds the head directly: no final norm
+        for l in range(c.n_layers if not S else 0):
             p = f"layers.{l}."
             kind = c.mixer_of(l)
             if kind != "none":
@@ -508,7 +647,7 @@ class Model:
             h = b.reshape(b.slice(h, 1, T - 1, 1), (R, H))
         else:
             h = b.reshape(h, (R * T, H))
-        x = norm(h, "final_norm")
+        x = h if S else norm(h, "final_norm")
         if spec.carry or c.mtp_head:
             b.output(x, "hidden", "export")
         head = W("embed") if c.tie_embeddings else W("lm_head")

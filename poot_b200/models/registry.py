@@ -493,6 +493,62 @@ def _qwen35(c):
     return cfg
 
 
+def _qwen38(c):
+    """Qwen3.8-Flash-Next (``qwen4_exp``; crates/poot-models/src/architectures/qwen38/config.rs): the Qwen3-Next layer
+    (gated delta net or gated attention, routed experts with a gated shared expert) inside gated hyper-connections,
+    with a block indexer narrowing the full-attention layers and hashed n-gram embedding blocks in front of the layers
+    ``ple_layer_ids`` names (1-based)."""
+    t = dict(c.get("text_config") or {})
+    if not t:
+        raise UnsupportedFamily("qwen4_exp header without text_config")
+    for k in ("eos_token_id", "bos_token_id", "tie_word_embeddings"):
+        if k not in t and c.get(k) is not None:
+            t[k] = c[k]
+    for flag in ("attention_bias", "use_sliding_window"):
+        if t.get(flag):
+            raise UnsupportedFamily(f"qwen4_exp with {flag}")
+    if not t.get("layer_types") or len(t["layer_types"]) != t["num_hidden_layers"]:
+        raise UnsupportedFamily("qwen4_exp header without one layer_types entry per layer")
+    if t.get("partial_rotary_factor") is None:
+        raise UnsupportedFamily("qwen4_exp header without partial_rotary_factor")
+    if int(t.get("indexer_kv_heads", 1)) != 1:
+        raise UnsupportedFamily("qwen4_exp indexer_kv_heads other than 1 (the indexer shares one key per token)")
+    gate = t.get("output_gate_type") or t.get("hidden_act") or "silu"
+    if gate not in ("silu", "sigmoid"):
+        raise UnsupportedFamily(f"qwen4_exp output_gate_type {gate!r}")
+    cfg = _qwen3next(t)
+    ratio, budget = int(t.get("indexer_compress_ratio") or 0), int(t.get("indexer_budget") or 0)
+    ni, di = int(t.get("indexer_n_heads") or 0), int(t.get("indexer_head_dim") or 0)
+    if "attention" in cfg.layer_kinds:
+        if ratio < 1 or ratio & (ratio - 1):
+            raise UnsupportedFamily(f"qwen4_exp indexer_compress_ratio {ratio} is not a power of two")
+        if budget < ratio or ni < 1 or di < cfg.rot:
+            raise UnsupportedFamily(f"qwen4_exp indexer of {ni} heads of {di} with a budget of {budget} over blocks of {ratio}")
+    ids = list(t.get("ple_layer_ids") or [])
+    layers = [int(i) - 1 for i in ids]
+    if any(not 0 <= l < cfg.n_layers or cfg.layer_kinds[l] != "gdn" for l in layers) or len(set(layers)) != len(layers):
+        raise UnsupportedFamily(f"qwen4_exp ple_layer_ids {ids!r}: distinct linear-attention layers, counted from 1")
+    if layers:
+        n, per, emb = int(t.get("ngram_size") or 0), int(t.get("heads_per_ngram") or 0), int(t.get("ple_embed_dim") or 0)
+        if n not in (2, 3) or per < 1 or emb < 1 or emb % ((n - 1) * per) or int(t.get("ple_conv_kernel_size") or 0) < 2:
+            raise UnsupportedFamily(f"qwen4_exp n-gram block: order {n}, {per} heads per order, embedding {emb}, "
+                                    f"conv {t.get('ple_conv_kernel_size')}")
+        if t.get("ngram_vocab_size_base") is None:
+            raise UnsupportedFamily("qwen4_exp header without ngram_vocab_size_base")
+    streams, rank = int(t.get("hc_count") or 0), int(t.get("hc_lowrank") or 0)
+    if streams < 1 or rank < 1:
+        raise UnsupportedFamily(f"qwen4_exp hc_count {streams} / hc_lowrank {rank}")
+    cfg.family = cfg.name = "qwen38"
+    cfg.hc_count, cfg.hc_lowrank, cfg.gdn_gate_act = streams, rank, gate
+    cfg.index_ratio, cfg.index_budget, cfg.index_n_heads, cfg.index_head_dim = ratio, budget, ni, di
+    cfg.ple_layers = layers or None
+    if layers:
+        cfg.ple_embed_dim, cfg.ple_conv, cfg.ngram_size, cfg.heads_per_ngram = emb, int(t["ple_conv_kernel_size"]), n, per
+        cfg.ngram_vocab_base, cfg.ngram_divisible_by = int(t["ngram_vocab_size_base"]), int(t.get("make_ngram_vocab_size_divisible_by") or 1)
+        cfg.ngram_seed = int(t.get("seed", 1234))
+    return cfg
+
+
 def _idefics3(c):
     """Idefics3 / SmolVLM: a llama text stack behind a SigLIP-style vision tower and a pixel-shuffle connector."""
     from .vision import VisionConfig
@@ -588,8 +644,7 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("qwen_vl", ["qwen2_5_vl"], [], _qwen_vl, kind="vlm"),
     FamilyEntry("glm53_flash", ["glm5_next"], [], _glm53, kind="own", tracer="glm53:Glm53Model"),
     FamilyEntry("deepseek4", ["deepseek_v4"], [], _deepseek4, kind="own", tracer="deepseek4:DeepseekV4Model"),
-    # families the reference ships whose mixers are not built here: refused by name
-    FamilyEntry("qwen38", ["qwen4_exp"], ["qwen4exp"], None, "block-indexed sparse attention, hyper-connection residual streams, n-gram embeddings"),
+    FamilyEntry("qwen38", ["qwen4_exp"], [], _qwen38),
 ]
 
 

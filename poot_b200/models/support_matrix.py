@@ -58,6 +58,15 @@ SAMPLES = {
                       compress_ratios=[0, 4, 128, 4], index_n_heads=64, index_head_dim=128, index_topk=512, hc_mult=4,
                       hc_sinkhorn_iters=20, n_routed_experts=256, num_experts_per_tok=6, moe_intermediate_size=2048,
                       n_shared_experts=1, routed_scaling_factor=1.5, num_hash_layers=1, max_position_embeddings=1048576),
+    "qwen38": dict(model_type="qwen4_exp", text_config=dict(
+        vocab_size=151936, hidden_size=2048, num_hidden_layers=4, num_attention_heads=16, num_key_value_heads=2, head_dim=256,
+        partial_rotary_factor=0.25, max_position_embeddings=262144,
+        layer_types=["linear_attention", "linear_attention", "linear_attention", "full_attention"], linear_num_key_heads=16,
+        linear_num_value_heads=32, linear_key_head_dim=128, linear_value_head_dim=128, output_gate_type="sigmoid", num_experts=256,
+        num_experts_per_tok=8, moe_intermediate_size=512, shared_expert_intermediate_size=512, hc_count=4, hc_lowrank=32,
+        indexer_n_heads=16, indexer_head_dim=128, indexer_budget=2048, indexer_compress_ratio=64, ple_layer_ids=[1, 3],
+        ple_embed_dim=1024, ple_conv_kernel_size=4, ngram_size=3, heads_per_ngram=8, ngram_vocab_size_base=500000,
+        make_ngram_vocab_size_divisible_by=128, eos_token_id=151645)),
     "bert": dict(model_type="bert", num_attention_heads=12, intermediate_size=3072, hidden_size=768),
     "idefics3": dict(model_type="idefics3", text_config=dict(model_type="llama", hidden_size=2048, num_hidden_layers=4,
                                                              num_attention_heads=32, num_key_value_heads=32, intermediate_size=8192,

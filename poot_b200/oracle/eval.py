@@ -256,6 +256,19 @@ def _eval_eqn(g: Graph, e: Eqn, ins: List[np.ndarray], opt: EvalOptions) -> List
         if op == "packed_dequant":
             from ..quant import codec
             return [codec.dequantize(at["format"], ins[0], at["shape"])]
+        if op == "ngram_hash":
+            ctx, per, eos = at["context"], at["heads_per_order"], at["eos"]
+            win = ins[0].astype(np.int64).astype(np.uint64)
+            t = win.shape[0] - ctx
+            m = [np.uint64(v & 0xFFFFFFFFFFFFFFFF) for v in at["multipliers"]]
+            s0, s1 = win[ctx:ctx + t], win[ctx - 1:ctx - 1 + t]
+            with np.errstate(over="ignore"):
+                mix = [(s0 * m[0]) ^ (s1 * m[1])]
+                if ctx == 2:
+                    s2 = np.where(s1 == np.uint64(eos), np.uint64(eos), win[0:t])
+                    mix.append(mix[0] ^ (s2 * m[2]))
+            cols = [(mix[h // per] % np.uint64(at["primes"][h])).astype(np.int64) + at["offsets"][h] for h in range(ctx * per)]
+            return [np.stack(cols, 1).astype(np.int32)]
         if op == "arg_top_k":
             rank = ins[0]
             k = at["k"]

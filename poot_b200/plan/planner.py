@@ -105,6 +105,9 @@ def plan_eqn(g: Graph, k: int, e: Eqn, world: int = 1) -> Plan:
         if kernel is None:
             raise Refusal(k, op, dt, TARGET, f"no kernel for the {kind!r} recurrence")
         return Plan("dispatch", [kernel], f"{kind}: state carried per (sequence, head) in shared memory")
+    if op == "ngram_hash":
+        # wrapping 64-bit multiplies, xors and a remainder by a 32-bit prime per head: one thread per (token, head)
+        return Plan("dispatch", ["poot_ngram_hash"], f"{len(e.attrs['primes'])} heads over a window of {g.types[e.inputs[0]].shape[0]}")
     if op == "block_top_k":
         # the exact radix select over each row's scores (ties at the cut: lowest position first)
         return Plan("dispatch", ["poot_index_select"], f"k={e.attrs.get('k')} of {g.types[e.inputs[0]].shape[-1]} candidates")

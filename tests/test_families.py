@@ -105,16 +105,12 @@ def test_supported_family_traces_compiles_and_decodes(name):
 
 def test_refused_families_say_what_is_missing():
     reg = Registry.builtin()
-    for mt, word in (("qwen4_exp", "hyper-connection"),):
-        with pytest.raises(UnsupportedFamily) as e:
-            reg.resolve_hf({**BASE, "model_type": mt})
-        assert word in str(e.value)
     with pytest.raises(UnsupportedFamily):
         reg.resolve_hf({**BASE, "model_type": "never_heard_of_it"})
     with pytest.raises(UnsupportedFamily):
         reg.resolve_hf({"model_type": "mpt", "d_model": 64, "n_heads": 4, "n_layers": 2, "vocab_size": 200,
                         "attn_config": {"alibi": False}})
-    assert len(reg.listed()) == 29 and set(reg.listed()) - set(reg.supported()) == {"qwen38"}
+    assert len(reg.listed()) == 29 and set(reg.listed()) - set(reg.supported()) == set()              # every family the reference lists is traced
 
 
 def test_device_gaps_name_what_the_device_program_lacks():
