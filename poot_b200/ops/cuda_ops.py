@@ -31,6 +31,7 @@ _SIGS = {
     "poot_causal_conv_silu": [_P, c_int, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, _P],
     "poot_ssd_scan": [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, c_int, _P],
     "poot_gdn_scan": [_P, _P, c_int, c_int, c_int, _P, _P, _P, c_int, _P, c_int, _P, c_int, c_int, c_int, _P],
+    "poot_ngram_hash": [_P, _P, c_int, _P, c_int, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P, _P],
     "poot_kda_scan": [_P, _P, _P, c_int, c_int, _P, _P, c_float, _P, c_int, _P, c_int, _P, c_int, c_int, _P],
     "poot_gated_rmsnorm": [_P, _P, c_int, c_int, _P, c_int, c_float, c_int, _P, c_int, c_int, c_int, _P],
     "poot_sigmoid_mul": [_P, _P, c_longlong, _P],
@@ -782,6 +783,23 @@ def gdn_scan(qkv: torch.Tensor, ba: torch.Tensor, b_col: int, a_col: int, dt_bia
     check(_fn("poot_gdn_scan")(_ptr(qkv), _ptr(ba), ba.stride(0), b_col, a_col, _ptr(dt_bias), _ptr(a_log), _ptr(state),
                                state.shape[0], _ptr(segs), segs.shape[0], _ptr(out), nk, nv, D, _stream()), "gdn_scan")
     return out
+
+
+def ngram_hash(tokens: torch.Tensor, history: torch.Tensor, segs: torch.Tensor, mult: torch.Tensor, primes: torch.Tensor,
+               offsets: torch.Tensor, per_order: int, eos: int, vocab: int, ids: torch.Tensor) -> torch.Tensor:
+    """Hashed n-gram ids ``ids[T, heads]`` (int32) of the step's tokens, piece by piece (crates/poot-models/src/components/
+    ple.rs ``row_ids``): head ``h`` is ``((m0 * s0) ^ (m1 * s1) [^ (m2 * s2)]) % primes[h] + offsets[h]`` over wrapping
+    64-bit words.  ``history[rows, ctx]`` int32 holds each sequence's last ``ctx`` tokens xor-ed with ``eos`` (a piece at
+    position 0 ignores it) and is updated; ``mult`` is int64 holding the unsigned multipliers' bits, ``primes`` int32
+    holding unsigned moduli."""
+    _need_cuda(tokens, history)
+    ctx, heads = history.shape[1], ids.shape[1]
+    assert tokens.dtype == torch.int32 and history.dtype == torch.int32 and ids.dtype == torch.int32 and segs.dtype == torch.int32
+    assert mult.dtype == torch.int64 and mult.numel() == ctx + 1 and primes.dtype == torch.int32 and offsets.dtype == torch.int32
+    assert primes.numel() == heads == offsets.numel() and heads == ctx * per_order and ids.is_contiguous() and history.is_contiguous()
+    check(_fn("poot_ngram_hash")(_ptr(tokens), _ptr(history), history.shape[0], _ptr(segs), segs.shape[0], _ptr(mult), _ptr(primes),
+                                 _ptr(offsets), ctx, heads, per_order, eos, vocab, _ptr(ids), _stream()), "ngram_hash")
+    return ids
 
 
 def kda_scan(qkv: torch.Tensor, f: torch.Tensor, bm: torch.Tensor, b_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,

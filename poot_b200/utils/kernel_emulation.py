@@ -158,6 +158,31 @@ def gdn_scan(qkv, ba, b_col, a_col, dt_bias, a_log, state, segs, out, nk, nv, D)
     return out
 
 
+def ngram_hash(tokens, history, segs, mult, primes, offsets, per_order, eos, vocab, ids):
+    M = (1 << 64) - 1
+    ctx, heads = history.shape[1], ids.shape[1]
+    m = [int(v) & M for v in mult.tolist()]
+    pr = [int(v) & 0xFFFFFFFF for v in primes.tolist()]
+    off = offsets.tolist()
+    for first, n, seq, pos0 in segs.tolist():
+        if n == 0:
+            continue
+        before = [eos] * ctx if pos0 == 0 else [int(v) ^ eos for v in history[seq].tolist()]
+        toks = [t if 0 <= t < vocab else 0 for t in tokens[first:first + n].tolist()]
+        run = before + toks
+        for i in range(n):
+            s0, s1 = run[ctx + i], run[ctx + i - 1]
+            mix2 = ((s0 * m[0]) & M) ^ ((s1 * m[1]) & M)
+            for h in range(heads):
+                mix = mix2
+                if h >= per_order:
+                    s2 = eos if s1 == eos else run[ctx + i - 2]
+                    mix ^= (s2 * m[2]) & M
+                ids[first + i, h] = mix % pr[h] + off[h]
+        history[seq] = torch.tensor([v ^ eos for v in run[-ctx:]], dtype=history.dtype)
+    return ids
+
+
 def kda_scan(qkv, f, bm, b_col, dt_bias, a_log, lower_bound, state, segs, out, heads, D):
     C = heads * D
     for first, n, seq, pos0 in segs.tolist():
@@ -739,7 +764,7 @@ def emulated_kernels():
     from ..ops import moe_ops, suffix_ops
     table = {
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
-                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, replace_rows_=replace_rows_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, kda_scan=kda_scan, ssd_scan=ssd_scan,
+                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, replace_rows_=replace_rows_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, kda_scan=kda_scan, ngram_hash=ngram_hash, ssd_scan=ssd_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 bias_add_=bias_add_, bias_add_indexed_=bias_add_indexed_, scale_=scale_, gather_rows=gather_rows,
                 sigmoid_gate_rows_=sigmoid_gate_rows_,

@@ -393,6 +393,32 @@ def test_gdn_kernels_match_their_host_restatements(D):
 
 
 @pytest.mark.xfail(strict=False, reason="new kernel: not yet run on a device")
+def test_ngram_hash_matches_its_host_restatement():
+    """Ids and carried histories of pieces that start a sequence, continue one (one token: a decode step) and contain
+    an end-of-sequence id and an out-of-vocabulary token, against the host restatement in Python integers."""
+    from poot_b200.models.ngram import ngram_tables
+    from poot_b200.ops import cuda_ops as K
+    from poot_b200.utils import kernel_emulation as emu
+    g = torch.Generator().manual_seed(2)
+    vocab, eos, rows, T = 1000, 7, 3, 24
+    for order, per in ((3, 2), (2, 3)):
+        tb = ngram_tables(1, order, per, 5000, 64, 99, vocab)
+        ctx, heads = order - 1, len(tb.primes)
+        tokens = torch.randint(0, vocab, (T,), generator=g, dtype=torch.int32)
+        tokens[4], tokens[15] = eos, vocab + 5
+        segs = torch.tensor([[0, 9, 2, 0], [9, 1, 0, 5], [10, 14, 1, 16], [0, 0, 0, 0]], dtype=torch.int32)
+        hist = torch.randint(0, vocab, (rows, ctx), generator=g, dtype=torch.int32)
+        mult = torch.tensor([m - (1 << 64) if m >= 1 << 63 else m for m in tb.multipliers], dtype=torch.int64)
+        primes, offsets = torch.tensor(tb.primes, dtype=torch.int32), torch.tensor(tb.offsets, dtype=torch.int32)
+        h_ref, i_ref = hist.clone(), torch.zeros(T, heads, dtype=torch.int32)
+        emu.ngram_hash(tokens, h_ref, segs, mult, primes, offsets, per, eos, vocab, i_ref)
+        h_dev, ids = hist.cuda(), torch.zeros(T, heads, dtype=torch.int32, device="cuda")
+        K.ngram_hash(tokens.cuda(), h_dev, segs.cuda(), mult.cuda(), primes.cuda(), offsets.cuda(), per, eos, vocab, ids)
+        K.check_status()
+        assert torch.equal(ids.cpu(), i_ref) and torch.equal(h_dev.cpu(), h_ref)
+
+
+@pytest.mark.xfail(strict=False, reason="new kernel: not yet run on a device")
 @pytest.mark.parametrize("D", [64, 128])
 def test_kda_scan_matches_its_host_restatement(D):
     """The delta rule with a decay per key channel against the host restatement (itself checked against the graph

@@ -304,3 +304,29 @@ def test_checkpoint_in_the_family_names_loads_and_generates(tmp_path):
         logits = ref.token(want[-1])
     llm = LLM.oracle(str(tmp_path / "ckpt"), rows=2, max_seq=48, num_blocks=16, prefill_chunk=16)
     assert llm.generate_tokens(prompt, SamplingParams(max_tokens=7, temperature=0.0, ignore_eos=True)) == want
+
+
+def test_ngram_kernel_restatement_equals_the_hash_equation():
+    """The host restatement the device test compares the n-gram kernel with, against the graph's ``ngram_hash``
+    equation: pieces that start a sequence, continue one token at a time and carry the history between them."""
+    import torch
+    from poot_b200.ir.builder import Builder
+    from poot_b200.oracle.eval import eval_graph
+    from poot_b200.tensor import DType
+    from poot_b200.utils import kernel_emulation as emu
+    vocab, eos = 60, 59
+    tb = ngram_tables(1, 3, 2, 50, 16, 7, vocab)
+    toks = np.random.default_rng(0).integers(0, vocab, 11).astype(np.int32)
+    toks[3] = eos
+    b = Builder()
+    win = b.slot("w", (2 + 11,), DType.I32, "token")
+    b.output(b.ngram_hash(win, 2, tb.multipliers, tb.primes, tb.offsets, 2, eos), "ids")
+    want = eval_graph(b.finish(), {"w": np.concatenate([[eos, eos], toks]).astype(np.int32)}).outputs["ids"]
+    mult = torch.tensor([m - (1 << 64) if m >= 1 << 63 else m for m in tb.multipliers], dtype=torch.int64)
+    primes, offsets = torch.tensor(tb.primes, dtype=torch.int32), torch.tensor(tb.offsets, dtype=torch.int32)
+    hist, ids = torch.zeros(2, 2, dtype=torch.int32), torch.zeros(11, 4, dtype=torch.int32)
+    for first, n in ((0, 4), (4, 1), (5, 1), (6, 5)):                 # a prompt chunk, two decode steps, another chunk
+        emu.ngram_hash(torch.from_numpy(toks), hist, torch.tensor([[first, n, 1, first]], dtype=torch.int32), mult, primes, offsets, 2, eos,
+                       vocab, ids)
+    assert np.array_equal(ids.numpy(), want)
+    assert hist[1].tolist() == [int(toks[-2]) ^ eos, int(toks[-1]) ^ eos] and hist[0].tolist() == [0, 0]
