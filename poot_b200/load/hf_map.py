@@ -271,6 +271,7 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
     elif cfg.block == "sandwich":
         table.update(SANDWICH_BLOCK)
     canon: Dict[str, PackedWeight] = {}
+    mx_parts: Dict[str, Dict[str, np.ndarray]] = {}       # gpt-oss: a layer's MXFP4 expert operands, assembled once all are seen
     names = store.names()
     for n in names:
         w = store[n]
@@ -311,6 +312,11 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
             if half != cfg.ffn:
                 raise CheckpointLayout(f"{n}: {w.shape[0]} rows, expected {2 * cfg.ffn} (gate | up)")
             canon[p + "ffn_gate"], canon[p + "ffn_up"] = w.rows(0, half), w.rows(half, half)
+        elif cfg.family == "gpt_oss" and rest[len("mlp.experts."):] in MX_PARTS and rest.startswith("mlp.experts."):
+            raw = w.planar.get("__raw__") if w.planar else None
+            if raw is None:
+                raise CheckpointLayout(f"{n}: MXFP4 operands are stored as bytes, found {w.format}")
+            mx_parts.setdefault(p, {})[rest[len("mlp.experts."):]] = raw
         elif cfg.family == "gpt_oss" and rest.startswith("mlp.experts."):
             _gpt_oss_experts(cfg, p, rest, w, canon)
         elif rest in ("mlp.experts.gate_up_proj", "block_sparse_moe.input_linear.weight"):   # stacked [E, 2F, H]
@@ -323,6 +329,8 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
         elif rest in ("mlp.experts.down_proj", "block_sparse_moe.output_linear.weight"):     # stacked [E, H, F]
             for x in range(cfg.n_experts):
                 canon[p + f"experts.{x}.down"] = first_axis(w, x)
+    for p, parts in mx_parts.items():
+        _gpt_oss_mxfp4(cfg, p, parts, canon)
     if cfg.norm_offset != 0.0:
         for k in list(canon):
             if k.endswith("norm"):
@@ -549,6 +557,36 @@ def _gpt_oss_experts(cfg: DecoderConfig, p: str, rest: str, w: PackedWeight, can
             canon[p + f"experts.{x}.down"] = f32_weight(f"{p}experts.{x}.down", a[x].T)
     elif rest == "mlp.experts.down_proj_bias":
         canon[p + "experts_out_bias"] = f32_weight(p + "experts_out_bias", a)
+
+
+MX_PARTS = ("gate_up_proj_blocks", "gate_up_proj_scales", "down_proj_blocks", "down_proj_scales")
+
+
+def _gpt_oss_mxfp4(cfg: DecoderConfig, p: str, parts: Dict[str, np.ndarray], canon: Dict[str, PackedWeight]) -> None:
+    """The released gpt-oss checkpoints store the experts as MXFP4: ``*_blocks[E, rows, K / 32, 16]`` bytes of two 4-bit
+    E2M1 codes each (even element in the low nibble) and ``*_scales[E, rows, K / 32]`` E8M0 exponents, one per 32 values.
+    That is the planar ``E2M1_ROW32`` format row for row, so every expert becomes a packed weight without decoding a
+    value: gate rows are the even rows of ``gate_up``, up rows the odd ones; ``down`` is ``[H, F]`` as stored
+    (crates/poot-models/src/architectures/gpt_oss.rs)."""
+    missing = [k for k in MX_PARTS if k not in parts]
+    if missing:
+        raise CheckpointLayout(f"{p}mlp.experts: MXFP4 experts without {', '.join(missing)}")
+    E, F, H = cfg.n_experts, cfg.moe_ffn, cfg.hidden
+    for stem, rows, K in (("gate_up_proj", 2 * F, H), ("down_proj", H, F)):
+        blocks, scales = parts[stem + "_blocks"], parts[stem + "_scales"]
+        if blocks.dtype != np.uint8 or scales.dtype != np.uint8 or K % 32:
+            raise CheckpointLayout(f"{p}mlp.experts.{stem}: MXFP4 operands are bytes over rows of whole 32-value blocks")
+        if tuple(blocks.shape) != (E, rows, K // 32, 16) or tuple(scales.shape) != (E, rows, K // 32):
+            raise CheckpointLayout(f"{p}mlp.experts.{stem}: blocks {tuple(blocks.shape)} / scales {tuple(scales.shape)}, expected "
+                                   f"{(E, rows, K // 32, 16)} / {(E, rows, K // 32)}")
+    gu_b, gu_s = parts["gate_up_proj_blocks"].reshape(E, 2 * F, H // 2), parts["gate_up_proj_scales"]
+    dn_b, dn_s = parts["down_proj_blocks"].reshape(E, H, F // 2), parts["down_proj_scales"]
+    packed = lambda name, n, k, wt, sc: PackedWeight(name, "E2M1_ROW32", (n, k), np.zeros(0, np.uint8),
+                                                      planar={"weight": np.ascontiguousarray(wt), "weight_scale": np.ascontiguousarray(sc)})
+    for x in range(E):
+        canon[p + f"experts.{x}.gate"] = packed(f"{p}experts.{x}.gate", F, H, gu_b[x, 0::2], gu_s[x, 0::2])
+        canon[p + f"experts.{x}.up"] = packed(f"{p}experts.{x}.up", F, H, gu_b[x, 1::2], gu_s[x, 1::2])
+        canon[p + f"experts.{x}.down"] = packed(f"{p}experts.{x}.down", H, F, dn_b[x], dn_s[x])
 
 
 def _mla_halfsplit(cfg: DecoderConfig, canon: Dict[str, PackedWeight]) -> None:

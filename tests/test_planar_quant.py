@@ -156,3 +156,72 @@ def test_planar_gemv_and_dequant_match_the_host_codec(fmt, M):
     res = torch.randn(M, N).to(torch.bfloat16)
     got = K.planar_gemv(x.cuda(), W, K.EPI_RESID, resid=res.cuda()).float().cpu()
     assert (got - (want + res.float())).abs().max().item() <= 0.02 * max(1.0, want.abs().max().item())
+
+
+def test_gpt_oss_mxfp4_experts_are_assembled_without_decoding(tmp_path):
+    """The released gpt-oss layout: ``gate_up_proj_blocks[E, 2F, H / 32, 16]`` + ``_scales`` with gate / up rows
+    interleaved, ``down_proj_blocks[E, H, F / 32, 16]`` + ``_scales``.  Every expert loads as a packed E2M1 weight (the
+    stored bytes, re-viewed), the oracle's logits and greedy continuation equal the Hugging Face model over the decoded
+    experts, and a layer that lacks one of the four operands is refused by name."""
+    from safetensors.torch import save_file
+    from transformers import AutoConfig, AutoModelForCausalLM
+    from poot_b200 import LLM, SamplingParams
+    from poot_b200.driver.handle import ModelHandle
+    from poot_b200.load.hf_map import CheckpointLayout
+    E, F, H = 4, 64, 128
+    cfg = AutoConfig.for_model("gpt_oss", hidden_size=H, intermediate_size=F, num_hidden_layers=2, num_attention_heads=4,
+                               num_key_value_heads=2, head_dim=32, vocab_size=320, max_position_embeddings=128, num_local_experts=E,
+                               num_experts_per_tok=2, sliding_window=6, layer_types=["sliding_attention", "full_attention"],
+                               tie_word_embeddings=False)
+    torch.manual_seed(0)
+    m = AutoModelForCausalLM.from_config(cfg).float().eval()
+    with torch.no_grad():
+        for n_, p_ in m.named_parameters():
+            if "experts" in n_ or "router" in n_:
+                p_.normal_(0, 0.3)
+    m.save_pretrained(str(tmp_path), safe_serialization=True)
+    sd = {k: v.clone() for k, v in m.state_dict().items()}
+    out = {}
+    for k, v in sd.items():
+        if k.endswith("mlp.experts.gate_up_proj") or k.endswith("mlp.experts.down_proj"):
+            rows = v.numpy().transpose(0, 2, 1)                          # HF keeps [E, in, out]; the packed layout is [E, out, in]
+            packed = [codec.quantize_planar("E2M1_ROW32", np.ascontiguousarray(rows[e])) for e in range(E)]
+            n_out, n_in = rows.shape[1], rows.shape[2]
+            out[k + "_blocks"] = torch.from_numpy(np.stack([q["weight"].reshape(n_out, n_in // 32, 16) for q in packed]))
+            out[k + "_scales"] = torch.from_numpy(np.stack([q["weight_scale"].reshape(n_out, n_in // 32) for q in packed]))
+            deq = np.stack([codec.dequantize_planar("E2M1_ROW32", q) for q in packed]).transpose(0, 2, 1)
+            sd[k].copy_(torch.from_numpy(np.ascontiguousarray(deq)))
+        else:
+            out[k] = v
+    save_file(out, str(tmp_path / "model.safetensors"), metadata={"format": "pt"})
+    m.load_state_dict(sd)
+    h = ModelHandle.load(str(tmp_path))
+    g0 = h.canonical["layers.0.experts.1.gate"]
+    assert g0.format == "E2M1_ROW32" and g0.shape == (F, H) and h.canonical["layers.1.experts.3.down"].shape == (H, F)
+    stored = out["model.layers.0.mlp.experts.gate_up_proj_blocks"].numpy()
+    assert np.array_equal(g0.planar["weight"], stored[1, 0::2].reshape(F, H // 2))            # the stored bytes, re-viewed
+    assert np.array_equal(h.canonical["layers.0.experts.1.up"].planar["weight"], stored[1, 1::2].reshape(F, H // 2))
+    p = torch.randint(3, 320, (1, 17), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        want = m.generate(p, max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)[0, 17:].tolist()
+        want_logits = m(p).logits[0, -1].numpy()
+    llm = LLM.oracle(str(tmp_path), rows=1, max_seq=64, num_blocks=8, prefill_chunk=32)
+    assert llm.generate_tokens(p[0].tolist(), SamplingParams(max_tokens=6, ignore_eos=True)) == want
+    fresh = LLM.oracle(str(tmp_path), rows=1, max_seq=64, num_blocks=8, prefill_chunk=32)
+    fresh.generate_tokens(p[0].tolist(), SamplingParams(max_tokens=1, ignore_eos=True))
+    assert np.abs(fresh.driver.engine.last_logits(1)[0] - want_logits).max() <= 2e-4 * max(1.0, np.abs(want_logits).max())
+    # the device loader decodes the experts to bf16 (exact: an E2M1 code times a power of two); its program follows
+    from poot_b200.utils.kernel_emulation import emulated_kernels
+    with emulated_kernels():
+        dev = LLM.load(str(tmp_path), device="cpu", rows=1, max_seq=64, prefill_chunk=32, num_blocks=8)
+        dev.generate_tokens(p[0].tolist(), SamplingParams(max_tokens=1, ignore_eos=True))
+        got = dev.driver.engine.last_logits(1)[0]
+        got = got.float().numpy() if hasattr(got, "float") else np.asarray(got)
+    assert np.abs(got - want_logits).max() <= 0.03 and np.corrcoef(got, want_logits)[0, 1] > 0.999
+    del out["model.layers.1.mlp.experts.down_proj_scales"]
+    bad = tmp_path / "bad"
+    bad.mkdir()
+    save_file(out, str(bad / "model.safetensors"), metadata={"format": "pt"})
+    (bad / "config.json").write_text((tmp_path / "config.json").read_text())
+    with pytest.raises(CheckpointLayout, match="down_proj_scales"):
+        ModelHandle.load(str(bad))
