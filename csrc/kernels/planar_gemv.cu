@@ -12,6 +12,8 @@
 //
 // planar_gemv: y[m, n] = sum_k x[m, k] * w[n, k] for m < M <= 4 (decode), epilogues store / f32 / residual.
 // planar_dequant: the whole weight as bf16 [N, K] (larger steps multiply with the tiled GEMM over it).
+// planar_gemv_grouped: routed experts that stay packed (formats 0-2): one activation row per group against the
+// group's expert of a stack, optionally the gated activation of two stacks, biases and a per-group scale fused.
 // Row-major formats (0-2) take one warp per output row; the K-major int4 formats (3, 4) take one thread per output
 // column (GPTQ) or per word of eight columns (AWQ) with the K range cut over the warps of the CTA and summed in shared
 // memory in a fixed order, so results do not depend on scheduling.
@@ -117,6 +119,88 @@ planar_gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, int ldx, PlanarOps 
     const float v = warp_sum(acc[m]);
     if (lane == 0) store_epi(epi, out, resid, ldo, m, n, v);
   }
+}
+
+// ---- routed experts kept packed: one activation row per group, the group's expert read from stacked operands -------------
+// Group g multiplies activation row g / x_row_div (x_row_div > 0) or g with expert ids[g] (or g) of weights stacked as
+// [E, N, ...] per operand.  One warp per (group, output row).  With a second weight set the warp computes the gate row
+// and the up row of the same index and writes act(gate + b1, up + b2):
+//   act 1: silu(gate) * up          act 2: (clamp(up, -limit, limit) + 1) * g * sigmoid(alpha * g), g = min(gate, limit)
+// without one it writes (w x + b) * row_scale[g].  Biases are f32 [E, N].  A negative expert id leaves the group's row zero.
+struct GroupedOps {
+  const uint8_t* w;  const uint8_t* scale;       // gate (or the only) weight set
+  const uint8_t* w2; const uint8_t* scale2;      // up weight set, or null
+  const float* bias; const float* bias2;
+  size_t w_stride, scale_stride;                 // bytes per expert
+};
+
+template <int FMT>
+__device__ __forceinline__ float packed_row_dot(const uint8_t* wbase, const uint8_t* sbase, int n, int N, int K,
+                                                const __nv_bfloat16* __restrict__ xr, int lane) {
+  float acc = 0.f;
+  if (FMT == PF_E2M1_ROW32) {
+    const uint8_t* wr = wbase + (size_t)n * (K / 2);
+    const uint8_t* sr = sbase + (size_t)n * (K / 32);
+    for (int b = lane; b < K / 32; b += 32) {
+      const float s = e8m0_to_f32(sr[b]);
+      const uint4 pk = *reinterpret_cast<const uint4*>(wr + (size_t)b * 16);
+      const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        part += e2m1_to_f32((wd[i >> 3] >> (4 * (i & 7))) & 0xFu) * __bfloat162float(xr[b * 32 + i]);
+      acc += part * s;
+    }
+  } else {
+    const uint8_t* wr = wbase + (size_t)n * K;
+    const float* sc = reinterpret_cast<const float*>(sbase);
+    const int kb = (K + 127) / 128;
+    const float row_scale = FMT == PF_E4M3_CHANNEL ? sc[n] : 1.f;
+    for (int k0 = lane * 16; k0 < K; k0 += 32 * 16) {
+      const uint4 pk = *reinterpret_cast<const uint4*>(wr + k0);
+      const uint32_t wd[4] = {pk.x, pk.y, pk.z, pk.w};
+      const float s = FMT == PF_E4M3_BLOCK128 ? sc[(size_t)(n >> 7) * kb + (k0 >> 7)] : row_scale;
+      float part = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        part += e4m3_to_f32((wd[i >> 2] >> (8 * (i & 3))) & 0xFFu) * __bfloat162float(xr[k0 + i]);
+      acc += part * s;
+    }
+  }
+  return warp_sum(acc);
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(256)
+planar_gemv_grouped_kernel(const __nv_bfloat16* __restrict__ x, int ldx, int x_row_div, GroupedOps ops, int act, float alpha,
+                           float limit, const int* __restrict__ ids, const float* __restrict__ row_scale,
+                           __nv_bfloat16* __restrict__ out, int ldo, int E, int N, int K) {
+  pdl_wait(); pdl_launch();
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int g = blockIdx.y;
+  if (n >= N) return;
+  const int e = ids ? ids[g] : g;
+  if (e < 0 || e >= E) {                      // an unused slot (or an id outside the stack): the row reads as zero
+    if (lane == 0) out[(size_t)g * ldo + n] = __float2bfloat16(0.f);
+    return;
+  }
+  const __nv_bfloat16* xr = x + (size_t)(x_row_div > 0 ? g / x_row_div : g) * ldx;
+  float v = packed_row_dot<FMT>(ops.w + (size_t)e * ops.w_stride, ops.scale + (size_t)e * ops.scale_stride, n, N, K, xr, lane);
+  if (ops.bias) v += ops.bias[(size_t)e * N + n];
+  if (ops.w2) {
+    float u = packed_row_dot<FMT>(ops.w2 + (size_t)e * ops.w_stride, ops.scale2 + (size_t)e * ops.scale_stride, n, N, K, xr, lane);
+    if (ops.bias2) u += ops.bias2[(size_t)e * N + n];
+    if (act == 2) {
+      const float gt = fminf(v, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      v = (u + 1.f) * gt / (1.f + __expf(-alpha * gt));
+    } else {
+      v = silu(v) * u;
+    }
+  }
+  if (row_scale) v *= row_scale[g];
+  if (lane == 0) out[(size_t)g * ldo + n] = __float2bfloat16(v);
 }
 
 // ---- K-major int4 formats -------------------------------------------------------------------------------------------
@@ -283,6 +367,31 @@ POOT_API int poot_planar_gemv(int fmt, int epi, const void* x, int ldx, const vo
   }
 #undef ROWS
 #undef INT4
+}
+
+POOT_API int poot_planar_gemv_grouped(int fmt, const void* x, int ldx, int x_row_div, const void* w, const void* scale, const void* w2,
+                                      const void* scale2, const float* bias, const float* bias2, int act, float alpha, float limit,
+                                      const int* ids, const float* row_scale, void* out, int ldo, int groups, int E, int N, int K,
+                                      cudaStream_t s) {
+  if (groups == 0) return 0;
+  if (fmt < PF_E4M3_CHANNEL || fmt > PF_E2M1_ROW32 || w == nullptr || scale == nullptr || (w2 != nullptr) != (scale2 != nullptr))
+    return (int)cudaErrorInvalidValue;
+  if (N < 1 || E < 1 || x_row_div < 0 || (fmt == PF_E2M1_ROW32 ? K % 32 : K % 16) || (w2 != nullptr && (act < 1 || act > 2)) ||
+      (w2 == nullptr && bias2 != nullptr) || groups > 65535)
+    return (int)cudaErrorInvalidValue;
+  GroupedOps ops{(const uint8_t*)w, (const uint8_t*)scale, (const uint8_t*)w2, (const uint8_t*)scale2, bias, bias2, 0, 0};
+  const size_t kb = (size_t)(K + 127) / 128, nb = (size_t)(N + 127) / 128;
+  ops.w_stride = fmt == PF_E2M1_ROW32 ? (size_t)N * (K / 2) : (size_t)N * K;
+  ops.scale_stride = fmt == PF_E2M1_ROW32 ? (size_t)N * (K / 32) : fmt == PF_E4M3_CHANNEL ? (size_t)N * 4 : nb * kb * 4;
+  const dim3 grid((N + 7) / 8, groups), block(256);
+  const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
+#define GR(F) launch_k(planar_gemv_grouped_kernel<F>, grid, block, 0, s, xb, ldx, x_row_div, ops, act, alpha, limit, ids, row_scale, (__nv_bfloat16*)out, ldo, E, N, K)
+  switch (fmt) {
+    case PF_E4M3_CHANNEL: return GR(PF_E4M3_CHANNEL);
+    case PF_E4M3_BLOCK128: return GR(PF_E4M3_BLOCK128);
+    default: return GR(PF_E2M1_ROW32);
+  }
+#undef GR
 }
 
 POOT_API int poot_planar_dequant(int fmt, const void* w, const void* scale, const void* zeros, const int* g_idx, int group,

@@ -234,6 +234,41 @@ def mtp_device_weights(handle: ModelHandle, device, target=None):
     return share_tables(w, target) if target is not None else w
 
 
+def packed_experts(handle: ModelHandle, device, layers) -> dict:
+    """Layer -> ``PackedExperts`` for the layers of ``layers`` whose routed experts are all stored in one row-major
+    planar format (fp8 per channel or per 128 x 128 block, fp4 rows of 32): the stored operands go to the device as
+    they are, stacked per projection.  Layers stored otherwise are left out (their experts are decoded to bf16)."""
+    import torch
+    from ..ops import cuda_ops as K
+    c, canon = handle.cfg, handle.canonical
+    out = {}
+    if not (c.is_moe and c.gated_ffn and c.act == "silu"):
+        return out
+    for l in layers:
+        p = f"layers.{l}."
+        if not (c.has_ffn(l) and c.moe_layer(l)) or p + "experts.0.gate" not in canon:
+            continue
+        ws = [canon[p + f"experts.{e}.{r}"] for e in range(c.n_experts) for r in ("gate", "up", "down")]
+        fmt = ws[0].format
+        if fmt not in K.PACKED_EXPERT_FORMATS or any(w.format != fmt for w in ws):
+            continue
+        key = "weight_scale_inv" if fmt == "E4M3_BLOCK128" else "weight_scale"
+
+        def stack(role):
+            parts = [canon[p + f"experts.{e}.{role}"].planar for e in range(c.n_experts)]
+            codes = np.stack([np.ascontiguousarray(q["weight"]).view(np.uint8) for q in parts])
+            sc = np.stack([np.asarray(q[key]) for q in parts])
+            sc = sc if fmt == "E2M1_ROW32" else sc.astype(np.float32).reshape(c.n_experts, -1) if fmt == "E4M3_CHANNEL" else sc.astype(np.float32)
+            return torch.from_numpy(codes).to(device), torch.from_numpy(np.ascontiguousarray(sc)).to(device)
+        bias = {}
+        if c.expert_bias:
+            b, F = handle.f32(p + "experts_in_bias"), c.moe_ffn
+            f32dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(device)
+            bias = {"bias_gate": f32dev(b[:, :F]), "bias_up": f32dev(b[:, F:]), "bias_down": f32dev(handle.f32(p + "experts_out_bias"))}
+        out[l] = K.PackedExperts(fmt, stack("gate"), stack("up"), stack("down"), c.n_experts, c.moe_ffn, c.hidden, **bias)
+    return out
+
+
 def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int = 1, keep_packed: bool = True, stage=None):
     """Rank-local ``DecoderWeights``: fused QKV, interleaved gate/up, Megatron shares."""
     import torch
@@ -247,9 +282,12 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
     if not c.plain_block or c.router_select_bias or c.shared_width or c.first_dense_layers or c.dense_layers or c.n_group > 1 \
             or c.router != "softmax":
         # hybrid stacks and the less common layer variants go through the canonical-name builder (dense bf16)
-        from ..runtime.weights import from_named_tensors
-        named = {n: torch.from_numpy(np.ascontiguousarray(w.to_f32())) for n, w in canon.items()}
-        return from_named_tensors(c, named, device, tp_rank, tp_world, stage=stage)
+        from ..runtime.weights import StageSpec, from_named_tensors
+        st_ = stage or StageSpec.whole(c)
+        packed = packed_experts(handle, device, range(st_.l0, st_.l1)) if (keep_packed and tp_world == 1) else {}
+        skip = tuple(f"layers.{l}.experts." for l in packed)
+        named = {n: torch.from_numpy(np.ascontiguousarray(w.to_f32())) for n, w in canon.items() if not n.startswith(skip or ("\0",))}
+        return from_named_tensors(c, named, device, tp_rank, tp_world, stage=stage, packed_experts=packed)
     D = c.head_dim
     hq, hkv = c.n_heads // tp_world, max(c.n_kv_heads // tp_world, 1)
     k0 = tp_rank * hkv if c.n_kv_heads >= tp_world else tp_rank * c.n_kv_heads // tp_world
@@ -264,6 +302,7 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
     layers = []
     from ..runtime.weights import StageSpec
     st = stage or StageSpec.whole(c)
+    packed = packed_experts(handle, device, range(st.l0, st.l1)) if (keep_packed and tp_world == 1) else {}
     for l in range(st.l0, st.l1):
         p = f"layers.{l}."
         q, k, v = canon[p + "attn_q"], canon[p + "attn_k"], canon[p + "attn_v"]
@@ -300,13 +339,16 @@ def device_weights(handle: ModelHandle, device, tp_rank: int = 0, tp_world: int 
             L.router = dense(p + "ffn_router")
             if c.router_select_bias:
                 L.select_bias = torch.from_numpy(handle.f32(p + "ffn_router_select_bias")).to(device=device, dtype=torch.float32)
-            gus, downs = [], []
-            for e in range(c.n_experts):
-                g, u = handle.f32(p + f"experts.{e}.gate"), handle.f32(p + f"experts.{e}.up")
-                gus.append(torch.from_numpy(np.stack([g, u], 1).reshape(2 * g.shape[0], -1)))
-                downs.append(torch.from_numpy(handle.f32(p + f"experts.{e}.down")))
-            L.ex_wgu = torch.stack(gus).to(device=device, dtype=torch.bfloat16)
-            L.ex_wdown = torch.stack(downs).to(device=device, dtype=torch.bfloat16)
+            if l in packed:
+                L.ex_packed = packed[l]
+            else:
+                gus, downs = [], []
+                for e in range(c.n_experts):
+                    g, u = handle.f32(p + f"experts.{e}.gate"), handle.f32(p + f"experts.{e}.up")
+                    gus.append(torch.from_numpy(np.stack([g, u], 1).reshape(2 * g.shape[0], -1)))
+                    downs.append(torch.from_numpy(handle.f32(p + f"experts.{e}.down")))
+                L.ex_wgu = torch.stack(gus).to(device=device, dtype=torch.bfloat16)
+                L.ex_wdown = torch.stack(downs).to(device=device, dtype=torch.bfloat16)
         else:
             g, u, dn = canon[p + "ffn_gate"], canon[p + "ffn_up"], canon[p + "ffn_down"]
             F = g.shape[0] // tp_world

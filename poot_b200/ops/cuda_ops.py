@@ -1065,6 +1065,58 @@ def planar_gemv(x: torch.Tensor, W: PlanarWeight, epi: int = EPI_STORE, out: Opt
     return out
 
 
+_SIGS["poot_planar_gemv_grouped"] = [c_int, _P, c_int, c_int, _P, _P, _P, _P, _P, _P, c_int, c_float, c_float, _P, _P, _P, c_int,
+                                     c_int, c_int, c_int, c_int, _P]
+PACKED_EXPERT_FORMATS = ("E4M3_CHANNEL", "E4M3_BLOCK128", "E2M1_ROW32")
+
+
+class PackedExperts:
+    """A layer's routed experts resident as their checkpoint stores them: per projection (``gate``, ``up``, ``down``) one
+    stack of code tensors ``[E, N, K or K / 2]`` and one of scales (``[E, N]`` f32 per channel, ``[E, N / 128, K / 128]``
+    f32 per block, ``[E, N, K / 32]`` e8m0 bytes for fp4 rows of 32).  Optional f32 biases ``[E, N]`` per projection."""
+
+    def __init__(self, fmt: str, gate, up, down, E: int, F: int, H: int, bias_gate=None, bias_up=None, bias_down=None):
+        if fmt not in PACKED_EXPERT_FORMATS:
+            raise ValueError(f"{fmt}: experts stay packed in the row-major planar formats only")
+        self.fmt, self.type_id, self.E, self.F, self.H = fmt, PLANAR_DEVICE_FORMATS[fmt], E, F, H
+        self.gate, self.up, self.down = gate, up, down                   # (codes, scales) each
+        self.bias_gate, self.bias_up, self.bias_down = bias_gate, bias_up, bias_down
+        for (w, sc), (n, k) in ((gate, (F, H)), (up, (F, H)), (down, (H, F))):
+            assert w.dtype == torch.uint8 and w.is_contiguous() and sc.is_contiguous() and w.shape[0] == E and w.shape[1] == n
+            assert w.shape[2] == (k // 2 if fmt == "E2M1_ROW32" else k)
+
+    @property
+    def device(self):
+        return self.gate[0].device
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for pair in (self.gate, self.up, self.down) for t in pair)
+
+
+def planar_gemv_grouped(x: torch.Tensor, P: PackedExperts, which: str, ids: Optional[torch.Tensor], out: torch.Tensor, groups: int,
+                        x_row_div: int = 0, row_scale: Optional[torch.Tensor] = None, act: str = "silu", alpha: float = 1.702,
+                        limit: float = 0.0) -> torch.Tensor:
+    """One activation row per group against the group's expert, decoded inside the product.  ``which="in"``:
+    ``out[g] = act(gate_e(x) + b, up_e(x) + b)`` (SwiGLU, or the clamped form when ``limit > 0``) with ``x`` row
+    ``g // x_row_div``; ``which="out"``: ``out[g] = (down_e(x[g]) + b) * row_scale[g]``.  ``ids[g]`` names the expert
+    (negative: the row is zero)."""
+    _need_cuda(x, P.gate[0])
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and out.dtype == torch.bfloat16 and out.stride(1) == 1
+    assert ids is None or (ids.dtype == torch.int32 and ids.numel() >= groups)
+    if which == "in":
+        assert act == "silu" and x.shape[1] == P.H and out.shape[1] >= P.F
+        check(_fn("poot_planar_gemv_grouped")(P.type_id, _ptr(x), x.stride(0), x_row_div, _ptr(P.gate[0]), _ptr(P.gate[1]), _ptr(P.up[0]),
+                                              _ptr(P.up[1]), _ptr(P.bias_gate), _ptr(P.bias_up), 2 if limit > 0 else 1, float(alpha),
+                                              float(limit), _ptr(ids), None, _ptr(out), out.stride(0), groups, P.E, P.F, P.H, _stream()),
+              "planar_gemv_grouped")
+    else:
+        assert x.shape[1] == P.F and out.shape[1] >= P.H and (row_scale is None or row_scale.dtype == torch.float32)
+        check(_fn("poot_planar_gemv_grouped")(P.type_id, _ptr(x), x.stride(0), x_row_div, _ptr(P.down[0]), _ptr(P.down[1]), None, None,
+                                              _ptr(P.bias_down), None, 0, 0.0, 0.0, _ptr(ids), _ptr(row_scale), _ptr(out),
+                                              out.stride(0), groups, P.E, P.H, P.F, _stream()), "planar_gemv_grouped")
+    return out
+
+
 def planar_dequant(W: PlanarWeight, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The whole weight as bf16 ``[N, K]``."""
     _need_cuda(W.w)

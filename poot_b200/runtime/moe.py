@@ -28,8 +28,9 @@ def _buffers(eng):
     if getattr(eng, "_moe_buf", None) is None:
         c, dev = eng.cfg, eng.device
         T, E, k = eng.max_tokens, c.n_experts, c.top_k
-        e_local = next(L_.ex_wgu.shape[0] for L_ in eng.w.layers if L_.ex_wgu is not None)
+        e_local = next((L_.ex_wgu.shape[0] for L_ in eng.w.layers if L_.ex_wgu is not None), E)
         F, H = c.moe_ffn, c.hidden
+        any_packed = any(getattr(L_, "ex_packed", None) is not None for L_ in eng.w.layers)
         Tc = min(T, 128)
         G = max(e_local, min(T, E) * k)
         eng._moe_buf = {
@@ -41,6 +42,9 @@ def _buffers(eng):
             "gu": (torch.zeros(G * Tc * 2 * F, dtype=torch.bfloat16, device=dev)
                    if (c.expert_bias or c.swiglu_limit > 0 or c.act != "silu" or not c.gated_ffn) else None),
             "parts": torch.zeros(G * Tc * H, dtype=torch.bfloat16, device=dev),
+            # experts kept packed run one activation row per (token, slot) at every step size
+            "pact": torch.zeros(T * k, F, dtype=torch.bfloat16, device=dev) if any_packed else None,
+            "pparts": torch.zeros(T * k, H, dtype=torch.bfloat16, device=dev) if any_packed else None,
         }
     return eng._moe_buf
 
@@ -136,7 +140,10 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
     c = eng.cfg
     E, k, F, H = c.n_experts, c.top_k, c.moe_ffn, c.hidden
     buf = _buffers(eng)
-    e_local = L.ex_wgu.shape[0]
+    packed = getattr(L, "ex_packed", None)
+    if packed is not None and (ep is not None or getattr(eng, "expert_pool", None) is not None):
+        raise RuntimeError("experts kept packed run on one device without an expert pool")
+    e_local = L.ex_wgu.shape[0] if packed is None else E
     e0 = eng.w.ep_rank * e_local
     logits = buf["logits"][:T]
     eng._count(2)
@@ -157,6 +164,16 @@ def moe_forward(eng, l: int, L, x: torch.Tensor, T: int, ep=None, h=None):
     if pooled:
         eng._count()
         ids = _pool_sync(eng, l, L, ids)                    # expert ids -> pool rows; the layer below reads the pool
+    if packed is not None:
+        # the experts are read as stored: group g = (token, slot) multiplies the token's row with its expert's packed
+        # gate and up rows (bias and gated activation fused), then with the packed down rows scaled by the slot's gate
+        G = T * k
+        act, parts = buf["pact"][:G], buf["pparts"][:G]
+        eng._count(3)
+        K.planar_gemv_grouped(x, packed, "in", ids, act, G, x_row_div=k, limit=c.swiglu_limit, alpha=c.swiglu_alpha)
+        K.planar_gemv_grouped(act, packed, "out", ids, parts, G, row_scale=gates)
+        M.moe_combine(h, parts, h, T, H, G, H, per_token=k)
+        return None
     if ep is None and e_local == E and T * k <= E and not pooled:
         G = T * k                                             # one group per (token, slot)
         act = buf["act"][:G * F].view(G, F)

@@ -52,6 +52,7 @@ class LayerWeights:
     sh_wgu: Optional[torch.Tensor] = None   # always-on (shared) expert: interleaved gate/up rows, down projection
     sh_wdown: Optional[torch.Tensor] = None
     sh_gate: Optional[torch.Tensor] = None  # [8, hidden]: row 0 is the shared expert's sigmoid gate, the rest zero padding
+    ex_packed: Optional[object] = None      # ``ops.cuda_ops.PackedExperts``: the routed experts as stored (then ex_wgu / ex_wdown are unset)
     ex_wgu: Optional[torch.Tensor] = None   # [E_local, 2F, hidden]
     ex_wdown: Optional[torch.Tensor] = None  # [E_local, hidden, F]
     quant: Dict[str, object] = field(default_factory=dict)  # packed (GGUF block) weights by role
@@ -277,8 +278,11 @@ def random_weights(cfg: DecoderConfig, device, seed: int = 0, std: float = 0.02,
 
 
 def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], device, tp_rank: int = 0,
-                       tp_world: int = 1, dtype=torch.bfloat16, stage: Optional[StageSpec] = None) -> DecoderWeights:
-    """Build device weights from canonical names (``layers.{i}.attn_q`` ... as produced by the family name tables)."""
+                       tp_world: int = 1, dtype=torch.bfloat16, stage: Optional[StageSpec] = None,
+                       packed_experts: Optional[dict] = None) -> DecoderWeights:
+    """Build device weights from canonical names (``layers.{i}.attn_q`` ... as produced by the family name tables).
+    ``packed_experts``: layer index -> ``PackedExperts`` for layers whose routed experts stay as stored (their
+    ``experts.*`` tensors are then not read here)."""
     dev = torch.device(device)
 
     def get(name):
@@ -357,7 +361,7 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
                 L.select_bias = tensors[p + "ffn_router_select_bias"].to(device=dev, dtype=torch.float32).contiguous()
             if cfg.router_bias:
                 L.router_bias = tensors[p + "ffn_router_bias"].to(device=dev, dtype=torch.float32).contiguous()
-            if cfg.expert_bias:
+            if cfg.expert_bias and not (packed_experts and l in packed_experts):
                 b = get(p + "experts_in_bias")                       # [E, 2F]: gate half then up half
                 F_ = cfg.moe_ffn
                 L.ex_bgu = torch.stack([b[:, :F_], b[:, F_:]], dim=2).reshape(b.shape[0], 2 * F_).contiguous()
@@ -368,12 +372,16 @@ def from_named_tensors(cfg: DecoderConfig, tensors: Dict[str, torch.Tensor], dev
                 if cfg.shared_expert_gate:
                     L.sh_gate = torch.zeros(8, cfg.hidden, dtype=dtype, device=dev)
                     L.sh_gate[0] = get(p + "shared_expert_gate")[0]
-            gus, downs = [], []
-            for e in range(cfg.n_experts):
-                gus.append(interleave_gate_up(get(p + f"experts.{e}.gate"), get(p + f"experts.{e}.up")) if cfg.gated_ffn
-                           else get(p + f"experts.{e}.up"))
-                downs.append(get(p + f"experts.{e}.down"))
-            L.ex_wgu, L.ex_wdown = torch.stack(gus), torch.stack(downs)
+            if packed_experts and l in packed_experts:
+                L.ex_packed = packed_experts[l]           # the experts stay as stored; biases live on the packed object
+                L.ex_bgu = L.ex_bdown = None
+            else:
+                gus, downs = [], []
+                for e in range(cfg.n_experts):
+                    gus.append(interleave_gate_up(get(p + f"experts.{e}.gate"), get(p + f"experts.{e}.up")) if cfg.gated_ffn
+                               else get(p + f"experts.{e}.up"))
+                    downs.append(get(p + f"experts.{e}.down"))
+                L.ex_wgu, L.ex_wdown = torch.stack(gus), torch.stack(downs)
         elif cfg.gated_ffn:
             L.wgu = interleave_gate_up(shard_rows(get(p + "ffn_gate"), tp_rank, tp_world),
                                        shard_rows(get(p + "ffn_up"), tp_rank, tp_world))

@@ -319,6 +319,43 @@ def _planar_f32(W) -> torch.Tensor:
     return w
 
 
+def _packed_expert_f32(P, which: str, e: int) -> torch.Tensor:
+    cache = P.__dict__.setdefault("_emulated", {})
+    if (which, e) not in cache:
+        from ..quant import codec
+        w, sc = getattr(P, which)
+        key = "weight_scale_inv" if P.fmt == "E4M3_BLOCK128" else "weight_scale"
+        cache[(which, e)] = torch.from_numpy(codec.dequantize_planar(P.fmt, {"weight": w[e].cpu().numpy(), key: sc[e].cpu().numpy()}).astype("float32"))
+    return cache[(which, e)]
+
+
+def planar_gemv_grouped(x, P, which, ids, out, groups, x_row_div=0, row_scale=None, act="silu", alpha=1.702, limit=0.0):
+    for g in range(groups):
+        e = int(ids[g]) if ids is not None else g
+        if e < 0 or e >= P.E:
+            out[g, :(P.F if which == "in" else P.H)] = 0
+            continue
+        xr = x[g // x_row_div if x_row_div > 0 else g].float()
+        if which == "in":
+            gt, up = _packed_expert_f32(P, "gate", e) @ xr, _packed_expert_f32(P, "up", e) @ xr
+            if P.bias_gate is not None:
+                gt, up = gt + P.bias_gate[e].float(), up + P.bias_up[e].float()
+            if limit > 0:
+                gt, up = gt.clamp(max=limit), up.clamp(-limit, limit)
+                v = (up + 1.0) * gt * torch.sigmoid(alpha * gt)
+            else:
+                v = torch.nn.functional.silu(gt) * up
+            out[g, :P.F] = _bf(v)
+        else:
+            v = _packed_expert_f32(P, "down", e) @ xr
+            if P.bias_down is not None:
+                v = v + P.bias_down[e].float()
+            if row_scale is not None:
+                v = v * row_scale[g]
+            out[g, :P.H] = _bf(v)
+    return out
+
+
 def linear(x, W, epi=K.EPI_STORE, out=None, resid=None):
     if isinstance(W, K.QuantWeight):
         raise NotImplementedError("packed weights are not emulated")
@@ -764,7 +801,7 @@ def emulated_kernels():
     from ..ops import moe_ops, suffix_ops
     table = {
         K: dict(embed_gather=embed_gather, rmsnorm=rmsnorm, reduce_partials=reduce_partials, swiglu=swiglu, add=add,
-                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, replace_rows_=replace_rows_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, kda_scan=kda_scan, ngram_hash=ngram_hash, ssd_scan=ssd_scan,
+                gated_act=gated_act, softcap_=softcap_, layernorm=layernorm, act_=act_, replace_rows_=replace_rows_, causal_conv_silu=causal_conv_silu, gdn_scan=gdn_scan, kda_scan=kda_scan, ngram_hash=ngram_hash, planar_gemv_grouped=planar_gemv_grouped, ssd_scan=ssd_scan,
                 gated_rmsnorm=gated_rmsnorm, sigmoid_mul=sigmoid_mul,
                 bias_add_=bias_add_, bias_add_indexed_=bias_add_indexed_, scale_=scale_, gather_rows=gather_rows,
                 sigmoid_gate_rows_=sigmoid_gate_rows_,
