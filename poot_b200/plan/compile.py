@@ -57,7 +57,7 @@ class Program:
         return total
 
 
-PIPELINE = ["canonicalize", "cse", "rope_fusion", "flash_attention", "form_selection", "dce", "recognize_packed",
+PIPELINE = ["canonicalize", "cse", "rope_fusion", "flash_attention", "form_selection", "form_recurrent_blocks", "dce", "recognize_packed",
             "fold_dense_contractions", "fuse_contraction_epilogues", "fuse", "dce2"]
 
 
@@ -75,6 +75,9 @@ def run_passes(g: Graph, opt: CompileOptions, log: Dict[str, object], declines: 
         elif name == "form_selection":
             from .selection import form_selection
             log[name] = form_selection(g, declines)
+        elif name == "form_recurrent_blocks":
+            from .recurrent_forms import form_recurrent_blocks
+            log[name] = form_recurrent_blocks(g, declines) if any(e.op == "scan" for e in g.eqns) else {}
         elif name in ("dce", "dce2"):
             log[name] = passes.dce(g)
         elif name == "recognize_packed":

@@ -263,9 +263,17 @@ class MultiDevicePlan:
 
 
 def plan_tensor_parallel(cfg: DecoderConfig, topo: Topology, rows: int, num_blocks: int, step_tokens: int,
-                         comm: str = "fused", itemsize: int = 2) -> MultiDevicePlan:
+                         comm: str = "fused", itemsize: int = 2, program: str = "one_shot") -> MultiDevicePlan:
     """Placement, communication rows, accounting and FLOPs of one step of ``step_tokens`` tokens on the engine's
-    tensor-parallel (dense) or expert-parallel (routed) program over the devices of ``topo``."""
+    tensor-parallel (dense) or expert-parallel (routed) program over the devices of ``topo``.
+
+    ``program="one_shot"``: every rank holds every token; each projection that ends a block is an all-reduce.
+    ``program="rs_ag"``: the token-sharded program - a block's result is reduce-scattered into the rank's share of the
+    rows and all-gathered in front of the next block's first projection; a routed block exchanges rows instead: an
+    all-to-all that sends every (token, slot) row to the rank owning its expert and one that brings the results back
+    (``runtime/moe.py::moe_forward_sharded``, ``csrc/kernels/ep_exchange.cu``)."""
+    if program not in ("one_shot", "rs_ag"):
+        raise MultiDeviceError(f"unknown tensor-parallel program {program!r}")
     devs = [d.id for d in topo.devices]
     w = len(devs)
     H, D, L, V = cfg.hidden, cfg.head_dim, cfg.n_layers, cfg.vocab
@@ -300,9 +308,21 @@ def plan_tensor_parallel(cfg: DecoderConfig, topo: Topology, rows: int, num_bloc
     fused = comm == "fused" and T <= 128
     cm = Communication()
     prev: Tuple[int, ...] = ()
+    S = -(-T // w)                                  # a rank's share of the step's rows under the sharded program
     for l in range(L):
         for site in ("o_proj", "down_proj"):
-            if fused:
+            if program == "rs_ag":
+                if site == "down_proj" and cfg.moe_layer(l):
+                    # every (token, slot) row of the rank's share travels to its expert's rank and back
+                    out_rows = S * cfg.top_k * H * itemsize
+                    rid = cm.add("all_to_all", devs, out_rows, prev, fused_into=f"ep_dispatch[{l}]" if comm == "fused" else None)
+                    rid = cm.add("all_to_all", devs, out_rows, (rid,), fused_into=f"ep_combine[{l}]" if comm == "fused" else None)
+                    prev = (rid,)
+                    continue
+                gemm = "gemm_tiled_tp" if w * S > 128 else "gemm_skinny_tp"
+                rid = cm.add("reduce_scatter", devs, w * S * H * itemsize, prev, fused_into=f"{gemm}[{l}.{site}]" if comm == "fused" else None)
+                rid = cm.add("all_gather", devs, w * S * H * itemsize, (rid,), fused_into=f"{gemm}[{l}.{site}.next]" if comm == "fused" else None)
+            elif fused:
                 rid = cm.add("all_reduce", devs, T * H * itemsize, prev, fused_into=f"gemm_skinny_tp[{l}.{site}]")
             else:
                 rid = cm.add("all_reduce", devs, T * H * itemsize, prev, needs="peer_access")

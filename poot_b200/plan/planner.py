@@ -67,6 +67,10 @@ def plan_eqn(g: Graph, k: int, e: Eqn, world: int = 1) -> Plan:
         return Plan("dispatch", split, f"key={e.attrs.get('key')} n_rep={e.attrs.get('n_rep')}")
     if op == "fused_row" and e.attrs.get("kind") == "rmsnorm":
         return Plan("dispatch", ["poot_tp_norm" if world > 1 else "poot_rmsnorm"])
+    if op == "fused_row" and e.attrs.get("kind") == "causal_conv_silu":
+        return Plan("dispatch", ["poot_causal_conv_silu"], f"{e.attrs.get('taps')} taps, window carried per sequence")
+    if op == "fused_row" and e.attrs.get("kind") == "gated_rmsnorm":
+        return Plan("dispatch", ["poot_gated_rmsnorm"], f"gate {'before' if e.attrs.get('gate_first') else 'after'} the norm ({e.attrs.get('act')})")
     if op == "fused" and e.attrs.get("kind") == "swiglu":
         return Plan("none", note="runs in the gate/up contraction's epilogue (interleaved gate and up rows)")
     if op == "fused":

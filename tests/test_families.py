@@ -81,8 +81,13 @@ def test_supported_family_traces_compiles_and_decodes(name):
         # evaluates to the same logits
         from poot_b200.models.model import StepSpec
         prog = compile_graph(model.trace(StepSpec(rows=1, tokens=4, capacity=32)))
-        scans = [k for p in prog.plans if p.kind == "dispatch" for k in p.kernels if k in ("poot_gdn_scan", "poot_ssd_scan")]
-        assert len(scans) == sum(1 for k in cfg.layer_kinds if k in ("gdn", "mamba"))
+        kernels = [k for p in prog.plans if p.kind == "dispatch" for k in p.kernels]
+        scans = [k for k in kernels if k in ("poot_gdn_scan", "poot_ssd_scan")]
+        n_rec = sum(1 for k in cfg.layer_kinds if k in ("gdn", "mamba"))
+        assert len(scans) == n_rec
+        # the conv + SiLU in front of every scan and the gated norm behind it are one launch each as well
+        assert kernels.count("poot_causal_conv_silu") == n_rec and kernels.count("poot_gated_rmsnorm") == n_rec
+        assert prog.log["form_recurrent_blocks"] == {"causal_conv_silu": n_rec, "gated_rmsnorm": n_rec}
         rewritten = OracleSession(model, w, capacity=32, graph_transform=lambda g: compile_graph(g).graph).step(toks)
         assert np.allclose(rewritten, full, rtol=2e-5, atol=1e-5)
         return

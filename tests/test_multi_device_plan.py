@@ -99,3 +99,29 @@ def test_llama_70b_over_eight_devices_and_what_does_not_fit():
     assert not any(r.fused_into for r in lib.communication.rows)
     with pytest.raises(MultiDeviceError, match="do not divide"):
         plan_tensor_parallel(PRESETS["mixtral-8x7b"](), Topology.nvswitch(list(range(3)), 178 * GIB), 8, 64, 8)
+
+
+def test_sharded_program_plans_scatter_gather_pairs_and_expert_exchanges():
+    """The token-sharded program: a dense block ends in a reduce-scatter whose rows the next block's first projection
+    gathers; a routed block sends every (token, slot) row of the rank's share to its expert's rank and back as two
+    all-to-alls.  Their link bytes follow the rows that cross, and an unknown program is refused."""
+    from poot_b200.models.config import PRESETS
+    cfg = PRESETS["mixtral-8x7b"]()
+    topo = Topology.nvswitch(list(range(8)), 178 * GIB)
+    plan = plan_tensor_parallel(cfg, topo, rows=64, num_blocks=64 * 16, step_tokens=1024, program="rs_ag").validate()
+    kinds = [r.kind for r in plan.communication.rows]
+    L = cfg.n_layers
+    assert kinds.count("all_to_all") == 2 * L and kinds.count("reduce_scatter") == L and kinds.count("all_gather") == L + 1
+    S = 1024 // 8
+    a2a = next(r for r in plan.communication.rows if r.kind == "all_to_all")
+    assert a2a.bytes_per_rank == S * cfg.top_k * cfg.hidden * 2 and a2a.fused_into.startswith("ep_dispatch")
+    assert a2a.link_bytes() == a2a.bytes_per_rank * 7 // 8
+    rs = next(r for r in plan.communication.rows if r.kind == "reduce_scatter")
+    assert rs.fused_into.startswith("gemm_tiled_tp") and rs.bytes_per_rank == 1024 * cfg.hidden * 2
+    lib = plan_tensor_parallel(cfg, topo, 64, 64 * 16, 1024, comm="nccl", program="rs_ag")
+    assert all(r.fused_into is None for r in lib.communication.rows)
+    dense = plan_tensor_parallel(PRESETS["llama-3-8b"](), Topology.nvswitch([0, 1], 178 * GIB), 64, 64 * 16, 64, program="rs_ag")
+    assert [r.kind for r in dense.communication.rows].count("all_to_all") == 0
+    assert next(r for r in dense.communication.rows if r.kind == "reduce_scatter").fused_into.startswith("gemm_skinny_tp")
+    with pytest.raises(MultiDeviceError):
+        plan_tensor_parallel(cfg, topo, 64, 64 * 16, 64, program="ring")

@@ -389,3 +389,54 @@ def test_sparse_attention_family_compiles_with_its_selections_formed():
     ks = sorted(e.attrs["k"] for e in prog.graph.eqns if e.op == "block_top_k")
     assert ks.count(m.cfg.index_topk) == m.cfg.n_layers              # one selection per layer's indexer
     assert prog.log["form_selection"] == len(ks)
+
+
+def test_form_recurrent_blocks_matches_the_definitions_only():
+    """A causal conv + SiLU and a gated norm written with the tracer's own functions fold into their composites (the
+    rewritten graph evaluates to the same bits, the planner names their kernels); a conv whose taps run the other way
+    and a norm gated by another activation stay as primitives."""
+    from poot_b200.ir import oplib as O
+    from poot_b200.ir.builder import Builder
+    from poot_b200.oracle.eval import eval_graph
+    from poot_b200.plan import passes
+    from poot_b200.plan.recurrent_forms import form_recurrent_blocks
+    from poot_b200.tensor import DType
+    L, C, K, H, D = 5, 6, 3, 2, 3
+
+    def graph(flip: bool, gate: str):
+        b = Builder()
+        x, st, w = (b.slot(n, s, DType.F32, "activation") for n, s in (("x", (L, C)), ("st", (K - 1, C)), ("w", (C, K))))
+        y3, z3, nw = (b.slot(n, s, DType.F32, "activation") for n, s in (("y", (L, H, D)), ("z", (L, H, D)), ("nw", (D,))))
+        if flip:                                     # taps applied newest-first: not the definition
+            xp = b.concat([st, x], 0)
+            y = None
+            for k in range(K):
+                t = b.slice(xp, 0, K - 1 - k, L) * b.broadcast(b.reshape(b.slice(w, 1, k, 1), (1, C)), (L, C))
+                y = t if y is None else y + t
+            nxt = b.slice(xp, 0, L, K - 1)
+        else:
+            y, nxt = O.causal_conv1d(b, x, st, w)
+        b.output(O.silu(b, y), "conv"); b.output(nxt, "window")
+        n = O.rmsnorm(b, y3, nw, 1e-5) * (O.silu(b, z3) if gate == "silu" else b.unary("tanh", z3))
+        b.output(n, "norm")
+        return b.finish()
+
+    rng = np.random.default_rng(0)
+    feed = {n: rng.standard_normal(s).astype(np.float32) for n, s in
+            (("x", (L, C)), ("st", (K - 1, C)), ("w", (C, K)), ("y", (L, H, D)), ("z", (L, H, D)), ("nw", (D,)))}
+    g = graph(False, "silu")
+    want = eval_graph(g, feed).outputs
+    passes.canonicalize(g); passes.cse(g)
+    assert form_recurrent_blocks(g) == {"causal_conv_silu": 1, "gated_rmsnorm": 1}
+    g.validate()
+    kinds = sorted(e.attrs["kind"] for e in g.eqns if e.op == "fused_row")
+    assert kinds == ["causal_conv_silu", "gated_rmsnorm"]
+    conv = next(e for e in g.eqns if e.op == "fused_row" and e.attrs["kind"] == "causal_conv_silu")
+    assert conv.attrs["taps"] == K and len(conv.outputs) == 2           # the activation rows and the window it hands on
+    got = eval_graph(g, feed).outputs
+    assert all(np.array_equal(got[n], want[n]) for n in want)
+    ks = [k for p in plan_graph(g) if p.kind == "dispatch" for k in p.kernels]
+    assert "poot_causal_conv_silu" in ks and "poot_gated_rmsnorm" in ks
+    other = graph(True, "tanh")
+    passes.canonicalize(other); passes.cse(other)
+    assert form_recurrent_blocks(other) == {"causal_conv_silu": 0, "gated_rmsnorm": 0}
