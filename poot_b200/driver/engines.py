@@ -317,15 +317,25 @@ class OracleStepEngine:
     """
 
     def __init__(self, model, weights, num_blocks: int, max_seqs: int, max_tokens: int, max_blocks_per_seq: int,
-                 options=None, graph_transform=None, carry: bool = False):
+                 options=None, graph_transform=None, carry: bool = False, weight_formats=None):
         """``carry``: every step also keeps the closing-norm hidden state of each of its tokens (``last_hidden``), the
-        input of a multi-token-prediction layer; the graphs are then traced with a logit row at every position."""
+        input of a multi-token-prediction layer; the graphs are then traced with a logit row at every position.
+        ``weight_formats``: name -> block format of the weights that ``weights`` holds as packed bytes; the step graphs
+        declare them as stored, their contractions and row gathers are formed (``recognize_packed``) and evaluated by
+        the native loops, so a quantised checkpoint is served at its packed size."""
         from ..oracle.eval import EvalOptions
         from .kvcache import BLOCK
         self.model, self.weights = model, weights
         self.block = BLOCK
         self.num_blocks, self.max_seqs, self.max_tokens, self.max_blocks = num_blocks, max_seqs, max_tokens, max_blocks_per_seq
-        self.options = options or EvalOptions(matmul_precision="exact")
+        self.options = options or EvalOptions(matmul_precision="exact", native=bool(weight_formats))
+        self.weight_formats = tuple(sorted((weight_formats or {}).items()))
+        if self.weight_formats and graph_transform is None:
+            def graph_transform(g):
+                from ..plan import passes
+                g = g.copy()
+                passes.recognize_packed(g)
+                return g
         self.graph_transform = graph_transform
         self.block_tables = np.zeros((max_seqs, max_blocks_per_seq), np.int32)
         self.state = {}
@@ -345,7 +355,8 @@ class OracleStepEngine:
             from ..models.model import StepSpec
             g = self.model.trace(StepSpec(rows=1, tokens=tokens, capacity=capacity, paged=True,
                                           pool_slots=self.num_blocks * self.block, embeds=embeds, mrope=mrope,
-                                          carry=self.carry, logit_rows="all" if self.carry else "last"))
+                                          carry=self.carry, logit_rows="all" if self.carry else "last",
+                                          weight_formats=self.weight_formats))
             self.graphs[key] = self.graph_transform(g) if self.graph_transform is not None else g
         return self.graphs[key]
 

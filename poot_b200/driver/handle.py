@@ -100,10 +100,42 @@ class ModelHandle:
         out[p + "experts_in"] = gi
         out[p + "experts_out"] = np.stack([self.f32(p + f"experts.{e}.down") for e in range(c.n_experts)])
 
-    def oracle_weights(self) -> Dict[str, np.ndarray]:
-        """Every canonical weight decoded to f32 in the tracer's layout (experts stacked gate-then-up)."""
+    def packed_oracle_weights(self):
+        """``(weights, formats)`` for the oracle over packed weights: the 2-D weights the checkpoint stores in a GGUF
+        block format stay as their bytes (``formats[name]`` names the format), everything else is decoded to f32.
+        Families whose tracer declares every weight dense (their own tracers, routed experts) decode as usual."""
+        from ..quant.formats import FORMATS
+        out = self.oracle_weights(skip_packed=True)
+        formats = {}
+        if type(self.model).__name__ == "Model":
+            for n, w in self.canonical.items():
+                d = FORMATS[w.format]
+                if n not in out and d.storage == "blocks" and len(w.shape) == 2:
+                    out[n] = np.ascontiguousarray(w.payload).view(np.uint8).reshape(-1)
+                    formats[n] = w.format
+        for n, w in self.canonical.items():          # what the packed declaration does not cover is decoded after all
+            if n not in out and ".experts." not in n and not n.startswith("mtp.") and not n.startswith(f"layers.{self.cfg.n_layers}."):
+                out[n] = w.to_f32()
+        return out, formats
+
+    def oracle_weights(self, skip_packed: bool = False) -> Dict[str, np.ndarray]:
+        """Every canonical weight decoded to f32 in the tracer's layout (experts stacked gate-then-up).  ``skip_packed``
+        leaves out the 2-D weights stored in a quantised block format (``packed_oracle_weights`` keeps those as stored)."""
+        from ..quant.formats import FORMATS
         c = self.cfg
         out = {}
+        if skip_packed:
+            keep = lambda w: not (FORMATS[w.format].storage == "blocks" and w.format not in ("F32", "F16", "BF16") and len(w.shape) == 2)
+            tail = f"layers.{c.n_layers}."
+            for n, w in self.canonical.items():
+                if ".experts." not in n and not n.startswith(tail) and not n.startswith("mtp.") and keep(w):
+                    out[n] = w.to_f32()
+            for l in range(c.n_layers):
+                if c.has_ffn(l) and c.moe_layer(l):
+                    self._stack_experts(out, f"layers.{l}.")
+            if c.tie_embeddings:
+                out.pop("lm_head", None)
+            return out
         tail = f"layers.{c.n_layers}."          # a multi-token-prediction layer's block: ``mtp_oracle_weights``
         for n, w in self.canonical.items():
             if ".experts." not in n and not n.startswith(tail) and not n.startswith("mtp."):

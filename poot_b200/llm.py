@@ -160,7 +160,7 @@ class LLM:
 
     @staticmethod
     def oracle(path: str, rows: int = 4, max_seq: int = 512, num_blocks: int = 128, prefill_chunk: int = 64,
-               lora: Optional[str] = None, prefill_budget: Optional[int] = None, draft_mtp: int = 0) -> "LLM":
+               lora: Optional[str] = None, prefill_budget: Optional[int] = None, draft_mtp: int = 0, packed: bool = False) -> "LLM":
         """A checkpoint served by the CPU oracle: every supported family end to end on the host, in f32, through the
         same driver (paged K/V, prefix cache, sampling rules) as the device engine.  Slow; meant for checking a
         family or a checkpoint without a device."""
@@ -177,12 +177,20 @@ class LLM:
             if not handle.has_mtp:
                 raise Unavailable(Feature.DRAFT_MTP, f"{path} does not store the model's multi-token-prediction layer")
             mtp = (handle.mtp_oracle_weights(), draft_mtp)
+        if packed:
+            # quantised matrices stay as stored and are decoded inside the contractions by the native loops
+            if lora is not None or mtp is not None:
+                raise ValueError("the packed oracle serves a plain checkpoint (no adapter, no draft layer)")
+            weights, formats = handle.packed_oracle_weights()
+            return LLM.oracle_from(handle.model, weights, _tokenizer_for(handle), rows, max_seq, num_blocks, prefill_chunk, handle,
+                                   prefill_budget, weight_formats=formats)
         return LLM.oracle_from(handle.model, handle.oracle_weights(), _tokenizer_for(handle), rows, max_seq, num_blocks,
                                prefill_chunk, handle, prefill_budget, mtp=mtp)
 
     @staticmethod
     def oracle_from(model, weights, tokenizer=None, rows: int = 4, max_seq: int = 512, num_blocks: int = 128,
-                    prefill_chunk: int = 64, handle=None, prefill_budget: Optional[int] = None, mtp=None) -> "LLM":
+                    prefill_chunk: int = 64, handle=None, prefill_budget: Optional[int] = None, mtp=None,
+                    weight_formats=None) -> "LLM":
         """``mtp``: ``(weights of the multi-token-prediction layer, k)``: the layer drafts ``k`` tokens per round for a
         lone greedy sequence (``LLM.draft``); the model's configuration must store such a layer."""
         from .driver.engines import OracleStepEngine
@@ -190,7 +198,7 @@ class LLM:
         max_seq = min(max_seq, cfg.max_position)
         step_prefill = max(prefill_chunk, min(prefill_budget or 0, rows * prefill_chunk))
         eng = OracleStepEngine(model, weights, num_blocks, rows, step_prefill + rows, blocks_for(max_seq),
-                               carry=mtp is not None)
+                               carry=mtp is not None, weight_formats=weight_formats)
         tokenizer = tokenizer or ByteTokenizer(cfg.vocab, bos=cfg.bos_token, eos=cfg.eos_token)
         eos = getattr(tokenizer, "eos", None)
         # a prefix hit skips tokens; a recurrent layer's state after those tokens is not in the K/V cache, so recurrent

@@ -38,6 +38,8 @@ class StepSpec:
     #                               multi-token-prediction layer reads and a chain of its steps recycles
     embeds: bool = False          # rows of other modalities replace the embeddings of flagged tokens (image rows of a VLM)
     mrope: bool = False           # three rotary position streams (time, row, column) bind per token: ``rope_positions[3, R*T]``
+    weight_formats: tuple = ()    # ((weight name, block format), ..): those 2-D weights are declared as their packed bytes and
+    #                               decoded by a ``packed_dequant`` equation, so an evaluator or a planner sees them as stored
 
     @property
     def slots(self) -> int:
@@ -193,10 +195,17 @@ class Model:
         shapes = self.weight_shapes()
 
         consts: Dict[str, Traced] = {}
+        packed_as = dict(spec.weight_formats)
 
         def W(name: str, shape=None) -> Traced:
             if name not in consts:
-                consts[name] = b.const(name, shape or shapes[name], spec.weight_dtype).cast(F32)
+                shp = tuple(shape or shapes[name])
+                if name in packed_as and len(shp) == 2:
+                    from ..quant.formats import packed_nbytes
+                    raw = b.const(name, (packed_nbytes(packed_as[name], shp[0] * shp[1]),), DType.U8)
+                    consts[name] = b.packed_dequant(raw, packed_as[name], shp)
+                else:
+                    consts[name] = b.const(name, shp, spec.weight_dtype).cast(F32)
             return consts[name]
 
         def norm(x: Traced, name: str) -> Traced:

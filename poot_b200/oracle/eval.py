@@ -29,6 +29,7 @@ class EvalOptions:
     narrow_dtype: DType = DType.BF16
     collectives: Optional[Callable[[str, Eqn, List[np.ndarray]], np.ndarray]] = None   # rank-walk hook
     keep_intermediates: bool = False
+    native: bool = False          # contractions over packed weights, scans and rank-to-ids through the C++ loops (oracle/native.py)
 
 
 @dataclass
@@ -269,6 +270,9 @@ def _eval_eqn(g: Graph, e: Eqn, ins: List[np.ndarray], opt: EvalOptions) -> List
                     mix.append(mix[0] ^ (s2 * m[2]))
             cols = [(mix[h // per] % np.uint64(at["primes"][h])).astype(np.int64) + at["offsets"][h] for h in range(ctx * per)]
             return [np.stack(cols, 1).astype(np.int32)]
+        if op == "arg_top_k" and opt.native:
+            from . import native
+            return [native.arg_top_k(ins[0], at["k"])]
         if op == "arg_top_k":
             rank = ins[0]
             k = at["k"]
@@ -294,8 +298,32 @@ def _eval_eqn(g: Graph, e: Eqn, ins: List[np.ndarray], opt: EvalOptions) -> List
                     return [ins[0]]
                 raise EvalError(f"{op} needs a rank walk (world > 1)")
             return [opt.collectives(op, e, ins)]
+        if op == "scan" and opt.native:
+            from . import native
+            return [native.scan(at["family"], ins)]
         if op == "scan":
             return [_scan(at["family"], [np.asarray(x, np.float32) for x in ins])]
+        if opt.native and op == "packed_contraction" and len(ins) == 2:
+            # the composite's body is ``matmul(x, transpose(packed_dequant(p)))``: decode inside the product instead
+            from . import native
+            deq = next(b_ for b_ in e.body.eqns if b_.op == "packed_dequant")
+            prec = opt.matmul_precision or at.get("precision", "narrow")
+            packed_first = e.body.inputs[0].value == deq.inputs[0]
+            x, pk = (ins[1], ins[0]) if packed_first else (ins[0], ins[1])
+            if prec in ("exact", "narrow") and opt.narrow_dtype == DType.BF16:
+                return [native.packed_matmul(x, pk, at["format"], deq.attrs["shape"], prec == "narrow")]
+        if opt.native and op == "packed_row_gather" and len(ins) == 2:
+            # only the gathered rows are decoded (the body would expand the whole table first)
+            from ..quant import codec
+            from ..quant.formats import packed_nbytes
+            deq = next(b_ for b_ in e.body.eqns if b_.op == "packed_dequant")
+            gat = next(b_ for b_ in e.body.eqns if b_.op == "gather")
+            packed_first = e.body.inputs[0].value == deq.inputs[0]
+            pk, ids = (ins[0], ins[1]) if packed_first else (ins[1], ins[0])
+            N, K = deq.attrs["shape"]
+            if gat.attrs.get("axis", 0) == 0 and (ids.size == 0 or (ids.min() >= 0 and ids.max() < N)):
+                rows = np.ascontiguousarray(pk).view(np.uint8).reshape(N, packed_nbytes(at["format"], K))[ids.reshape(-1)]
+                return [codec.dequantize(at["format"], rows.reshape(-1), (ids.size, K)).reshape(tuple(ids.shape) + (K,))]
         if e.body is not None:
             sub_inputs = {bi.name: v for bi, v in zip(e.body.inputs, ins)}
             ev = eval_graph(e.body, sub_inputs, opt)

@@ -12,12 +12,12 @@ PKG = os.path.join(ROOT, "poot_b200")
 # a package may import the packages listed for it (and itself); lower layers never reach up
 LAYERS = {
     "tensor": set(), "target": {"tensor"}, "quant": {"tensor", "ops"}, "weights": {"tensor", "quant"},
-    "load": {"tensor", "quant", "weights", "models"}, "ir": {"tensor", "quant"}, "oracle": {"tensor", "quant", "ir", "models", "runtime"},
-    "models": {"tensor", "ir", "load"}, "plan": {"tensor", "ir", "quant", "target", "models", "oracle"},
+    "load": {"tensor", "quant", "weights", "models"}, "ir": {"tensor", "quant"}, "oracle": {"tensor", "quant", "ir", "models", "runtime", "ops"},
+    "models": {"tensor", "ir", "load", "quant"}, "plan": {"tensor", "ir", "quant", "target", "models", "oracle"},
     "ops": set(), "profile": {"target", "ops"}, "text": {"ops"},
     "runtime": {"models", "ops", "quant", "parallel", "tensor", "plan"}, "parallel": {"ops", "runtime"},
     "utils": {"ops", "oracle", "runtime", "models", "tensor", "plan", "quant"},
-    "driver": {"models", "runtime", "ops", "load", "quant", "ir", "oracle", "text", "tensor", "profile", "parallel"},
+    "driver": {"models", "runtime", "ops", "load", "quant", "ir", "oracle", "text", "tensor", "profile", "parallel", "plan"},
     "serve": {"driver", "text", "profile", "models", "parallel", "runtime", "ops", "load", "plan"}, "cli": {"driver", "text", "models"},
 }
 TOP = {"llm": None, "embed": None, "vlm": None, "build": None, "__init__": None}     # facades at the package root may import anything
