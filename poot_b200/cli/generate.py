@@ -110,7 +110,9 @@ def _open(a: GenerateArgs):
     if a.model.startswith("random:"):
         return LLM.random(a.model.split(":", 1)[1], rows=1, max_seq=ctx)
     if a.backend == "oracle":
-        return LLM.oracle(a.model, rows=1, max_seq=ctx, num_blocks=(ctx + 15) // 16 + 1, lora=a.lora)
+        # a GGUF's quantised matrices stay as stored: the evaluator decodes them inside its native contractions
+        return LLM.oracle(a.model, rows=1, max_seq=ctx, num_blocks=(ctx + 15) // 16 + 1, lora=a.lora,
+                          packed=a.model.endswith(".gguf") and not a.lora)
     return LLM.load(a.model, rows=1, max_seq=ctx, lora=a.lora)
 
 
