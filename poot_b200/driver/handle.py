@@ -9,6 +9,7 @@ GEMV stay packed (``QuantWeight``), every other stored format is expanded to bf1
 from __future__ import annotations
 
 import json
+import re
 import os
 from dataclasses import dataclass
 from typing import Dict, Optional
@@ -54,15 +55,27 @@ class ModelHandle:
         arch = store.metadata.get("general.architecture")
         model = registry.resolve_gguf(arch, store.metadata)
         canon = {}
+        fam = model.cfg.family
+        paired = fam in names.GGUF_PAIRED_QK
+        bias_parts = {}
         for n in store.names():
-            c = names.canonical_from_gguf(n)
+            c = names.canonical_from_gguf(n, fam)
             if c is None:
+                m = re.match(r"blk\.(\d+)\.ffn_(gate|up|down)_exps\.bias$", n)          # gpt-oss: one bias row per expert
+                if m:
+                    bias_parts.setdefault(int(m.group(1)), {})[m.group(2)] = store[n].to_f32()
                 continue
             w = store[n]
-            if arch == "llama" and c.endswith(("attn_q", "attn_k")) and len(w.shape) == 2:
+            if paired and c.endswith(("attn_q", "attn_k")) and len(w.shape) == 2:
                 heads = model.cfg.n_heads if c.endswith("attn_q") else model.cfg.n_kv_heads
                 w = _permute_rows(w, names.gguf_qk_row_order(w.shape[0], heads))
             canon[c] = w
+        for l, parts in bias_parts.items():
+            from ..load.hf_map import f32_weight
+            if {"gate", "up", "down"} - set(parts):
+                raise KeyError(f"blk.{l}: expert biases without {sorted({'gate', 'up', 'down'} - set(parts))}")
+            canon[f"layers.{l}.experts_in_bias"] = f32_weight(f"layers.{l}.experts_in_bias", np.concatenate([parts["gate"], parts["up"]], 1))
+            canon[f"layers.{l}.experts_out_bias"] = f32_weight(f"layers.{l}.experts_out_bias", parts["down"])
         if "lm_head" not in canon and "embed" in canon:
             model.cfg.tie_embeddings = True
         return ModelHandle(model, store, canon, path, "gguf", None)

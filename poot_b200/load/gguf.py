@@ -168,7 +168,8 @@ def read_gguf(path: str, check: bool = True) -> WeightStore:
             if t.offset % idx.alignment or lo + nbytes > raw.size:
                 raise GgufError(f"tensor {t.name!r} overruns the file or is misaligned")
             payload = raw[lo:lo + nbytes]
-            if len(t.shape) == 3 and FORMATS[fmt].storage == "blocks":
+            if len(t.shape) == 3 and (FORMATS[fmt].storage == "blocks" or t.name.endswith("_exps.weight")):
+                # a stacked expert tensor becomes one owner per expert, in any storage format
                 per = nbytes // t.shape[0]
                 for e in range(t.shape[0]):
                     store.add(PackedWeight(f"{t.name}#{e}", fmt, tuple(t.shape[1:]), payload[e * per:(e + 1) * per]))
@@ -232,6 +233,51 @@ def write_gguf(path: str, metadata: Dict[str, Any], tensors: List[PackedWeight],
 
 
 # ---- metadata -> configuration ---------------------------------------------------------------------------------
+def hf_header_from_gguf(arch: str, meta: Dict[str, Any], family: str) -> Dict[str, Any]:
+    """The Hugging Face style header a family's table reads, rebuilt from a GGUF's metadata keys (``<arch>.block_count``,
+    ``.embedding_length``, ... as llama.cpp's converter writes them), so one header table per family serves both
+    containers.  What a GGUF does not state takes the value llama.cpp's graph uses: Gemma's query scale is the head
+    width, gpt-oss slides on every even layer, SmolLM3 leaves every fourth layer without rotary positions."""
+    def g(key, default=None):
+        return meta.get(f"{arch}.{key}", default)
+
+    def one(v):
+        return v[0] if isinstance(v, (list, np.ndarray)) else v
+
+    H, nh = int(g("embedding_length")), int(g("attention.head_count"))
+    L = int(g("block_count"))
+    tokens = meta.get("tokenizer.ggml.tokens")
+    h: Dict[str, Any] = {
+        "hidden_size": H, "num_hidden_layers": L, "num_attention_heads": nh,
+        "num_key_value_heads": int(one(g("attention.head_count_kv", nh))), "head_dim": int(g("attention.key_length", H // nh)),
+        "intermediate_size": int(one(g("feed_forward_length", 4 * H))),
+        "vocab_size": int(g("vocab_size", len(tokens) if tokens is not None else 0)),
+        "rms_norm_eps": float(g("attention.layer_norm_rms_epsilon", 1e-6)), "rope_theta": float(g("rope.freq_base", 10000.0)),
+        "max_position_embeddings": int(g("context_length", 8192)), "tie_word_embeddings": False,
+        "bos_token_id": int(meta.get("tokenizer.ggml.bos_token_id", 1)), "eos_token_id": int(meta.get("tokenizer.ggml.eos_token_id", 2))}
+    if g("rope.scaling.type") in ("linear", "yarn"):
+        h["rope_scaling"] = {"rope_type": g("rope.scaling.type"), "factor": float(g("rope.scaling.factor", 1.0)),
+                             "original_max_position_embeddings": int(g("rope.scaling.original_context_length", 8192))}
+    if g("expert_count"):
+        h["num_local_experts"], h["num_experts_per_tok"] = int(g("expert_count")), int(g("expert_used_count", 0))
+        if g("expert_feed_forward_length"):
+            h["intermediate_size"] = int(g("expert_feed_forward_length"))
+    win = g("attention.sliding_window")
+    if family in ("gemma2", "gemma3"):
+        h.update({"sliding_window": int(win) if win else h["max_position_embeddings"], "query_pre_attn_scalar": h["head_dim"],
+                  "attn_logit_softcapping": g("attn_logit_softcapping"), "final_logit_softcapping": g("final_logit_softcapping"),
+                  "rope_local_base_freq": float(g("rope.freq_base_swa", 10000.0))})
+    elif family == "gpt_oss":
+        h.update({"sliding_window": int(win or 128), "attention_bias": True,
+                  "layer_types": ["sliding_attention" if l % 2 == 0 else "full_attention" for l in range(L)]})
+    elif family == "granite":
+        h.update({"embedding_multiplier": float(g("embedding_scale", 1.0)), "residual_multiplier": float(g("residual_scale", 1.0)),
+                  "logits_scaling": float(g("logit_scale", 1.0)), "attention_multiplier": g("attention.scale")})
+    elif family == "smollm3":
+        h["no_rope_layers"] = [int((l + 1) % 4 != 0) for l in range(L)]
+    return h
+
+
 def config_from_gguf_metadata(arch: str, meta: Dict[str, Any], family: str) -> DecoderConfig:
     def g(key, default=None):
         return meta.get(f"{arch}.{key}", default)

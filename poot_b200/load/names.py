@@ -57,13 +57,30 @@ def fused_hf_projection(name: str) -> Optional[Tuple[int, str]]:
     return int(m.group(1)), ("qkv" if m.group(2).endswith("qkv_proj") else "gate_up")
 
 
-def canonical_from_gguf(name: str) -> Optional[str]:
+# rows a family's GGUF carries beside (or in place of) the shared ones (crates/poot-models/src/names/gguf.rs): OLMo 2
+# stores the norms applied to each block's OUTPUT under the post-norm names; Gemma 2 / 3 have both pairs; gpt-oss names the
+# norm before its feed-forward block ``post_attention_norm`` and has sinks, an output bias and a biased router
+GGUF_FAMILY_LAYER = {
+    "olmo2": {"post_attention_norm.weight": "attn_post_norm", "post_ffw_norm.weight": "ffn_post_norm"},
+    "gemma2": {"post_attention_norm.weight": "attn_post_norm", "post_ffw_norm.weight": "ffn_post_norm"},
+    "gemma3": {"post_attention_norm.weight": "attn_post_norm", "post_ffw_norm.weight": "ffn_post_norm"},
+    "gpt_oss": {"post_attention_norm.weight": "ffn_norm", "attn_sinks.weight": "attn_sinks", "attn_output.bias": "attn_o_bias",
+                "ffn_gate_inp.bias": "ffn_router_bias"},
+}
+# families whose converter permutes Q / K rows for interleaved rotary pairs, read back half-split
+GGUF_PAIRED_QK = ("llama", "mixtral", "smollm3")
+
+
+def canonical_from_gguf(name: str, family: Optional[str] = None) -> Optional[str]:
     if name in GGUF_TOP:
         return GGUF_TOP[name]
     m = re.match(r"blk\.(\d+)\.([^#]+)(?:#(\d+))?$", name)
     if not m:
         return None
     l, rest, ex = m.group(1), m.group(2), m.group(3)
+    extra = GGUF_FAMILY_LAYER.get(family or "", {})
+    if rest in extra:
+        return f"layers.{l}.{extra[rest]}"
     if rest in GGUF_LAYER:
         return f"layers.{l}.{GGUF_LAYER[rest]}"
     if rest in GGUF_EXPERT and ex is not None:

@@ -622,7 +622,7 @@ SHIPPED: List[FamilyEntry] = [
     FamilyEntry("olmo2", ["olmo2"], ["olmo2"], _olmo2),
     FamilyEntry("phi3", ["phi3"], ["phi3"], _phi3),
     FamilyEntry("smollm3", ["smollm3"], ["smollm3"], _smollm3),
-    FamilyEntry("granite", ["granite", "granitemoe"], ["granite"], _granite),
+    FamilyEntry("granite", ["granite", "granitemoe"], ["granite", "granitemoe"], _granite),
     FamilyEntry("mpt", ["mpt"], ["mpt"], _mpt),
     FamilyEntry("bloom", ["bloom"], ["bloom"], _bloom),
     FamilyEntry("gemma3", ["gemma3", "gemma3_text"], ["gemma3"], _gemma3),
@@ -649,7 +649,9 @@ SHIPPED: List[FamilyEntry] = [
 
 
 # families whose GGUF metadata and tensor names the generic llama-style reader covers completely
-GGUF_FAMILIES = ("llama", "qwen2", "qwen3", "qwen3moe", "phi3")
+GGUF_FAMILIES = ("llama", "qwen2", "qwen3", "qwen3moe", "phi3", "olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss")
+# of those, the ones whose configuration is read by the family's own header table from a header rebuilt out of the GGUF keys
+GGUF_VIA_HEADER = ("olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss")
 
 
 class Registry:
@@ -692,6 +694,13 @@ class Registry:
                     # multipliers, router kinds) that only their Hugging Face header table reads here
                     raise UnsupportedFamily(f"family {e.name!r}: no GGUF header / tensor-name table; load the Hugging Face "
                                             "checkpoint directory (config.json + safetensors) instead")
+                if e.name in GGUF_VIA_HEADER:
+                    from ..load.gguf import hf_header_from_gguf
+                    cfg = e.from_hf(hf_header_from_gguf(arch, meta, e.name))
+                    cfg.name = str(meta.get("general.name", e.name))
+                    if e.name in ("gemma2", "gemma3"):
+                        cfg.norm_offset = 0.0           # llama.cpp's converter stores Gemma's norm scales with the one folded in
+                    return Model(cfg)
                 return Model(config_from_gguf_metadata(arch, meta, e.name))
         raise UnsupportedFamily(f"no family for GGUF architecture {arch!r}")
 

@@ -1,0 +1,169 @@
+"""GGUF checkpoints of the families beyond llama / qwen: a Hugging Face model is written out the way llama.cpp's
+converter lays a GGUF out (tensor names, Q / K rows permuted for the interleaved-rotary families, Gemma norm scales with
+the one folded in, experts stacked ``[E, out, in]``, gpt-oss's norm names, sinks and per-expert biases), loaded by its
+``general.architecture`` and evaluated: logits equal the Hugging Face forward."""
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from poot_b200.driver.handle import ModelHandle
+from poot_b200.load import gguf, names
+from poot_b200.models.model import StepSpec
+from poot_b200.oracle.runner import OracleSession
+from poot_b200.quant import codec
+from poot_b200.quant.weights import PackedWeight
+from tests.test_hf_parity import BASE, CASES, build
+
+ARCH = {"olmo2": "olmo2", "olmoe": "olmoe", "smollm3": "smollm3", "granite": "granite", "granitemoe": "granitemoe", "gemma2": "gemma2",
+        "gemma3": "gemma3", "gpt_oss": "gpt-oss"}
+LAYER = {"input_layernorm.weight": "attn_norm.weight", "post_attention_layernorm.weight": "ffn_norm.weight",
+         "self_attn.q_proj.weight": "attn_q.weight", "self_attn.k_proj.weight": "attn_k.weight", "self_attn.v_proj.weight": "attn_v.weight",
+         "self_attn.o_proj.weight": "attn_output.weight", "self_attn.q_norm.weight": "attn_q_norm.weight",
+         "self_attn.k_norm.weight": "attn_k_norm.weight", "mlp.gate_proj.weight": "ffn_gate.weight", "mlp.up_proj.weight": "ffn_up.weight",
+         "mlp.down_proj.weight": "ffn_down.weight", "self_attn.q_proj.bias": "attn_q.bias", "self_attn.k_proj.bias": "attn_k.bias",
+         "self_attn.v_proj.bias": "attn_v.bias", "self_attn.o_proj.bias": "attn_output.bias", "self_attn.sinks": "attn_sinks.weight",
+         "mlp.gate.weight": "ffn_gate_inp.weight", "mlp.router.weight": "ffn_gate_inp.weight", "mlp.router.bias": "ffn_gate_inp.bias",
+         "block_sparse_moe.router.layer.weight": "ffn_gate_inp.weight"}
+PER_FAMILY = {
+    "olmo2": {"post_attention_layernorm.weight": "post_attention_norm.weight", "post_feedforward_layernorm.weight": "post_ffw_norm.weight"},
+    "gemma": {"post_attention_layernorm.weight": "post_attention_norm.weight", "pre_feedforward_layernorm.weight": "ffn_norm.weight",
+              "post_feedforward_layernorm.weight": "post_ffw_norm.weight"},
+    "gpt_oss": {"post_attention_layernorm.weight": "post_attention_norm.weight"},
+}
+
+
+def _f32(name, a):
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    return PackedWeight(name, "F32", tuple(a.shape), a.view(np.uint8).reshape(-1))
+
+
+def _to_gguf(path, family, m, quantise=None):
+    """llama.cpp's layout of the Hugging Face model ``m``."""
+    c = m.config
+    arch = ARCH[family]
+    nh, nkv = c.num_attention_heads, c.num_key_value_heads
+    meta = {"general.architecture": arch, "general.name": family, f"{arch}.block_count": c.num_hidden_layers,
+            f"{arch}.embedding_length": c.hidden_size, f"{arch}.attention.head_count": nh, f"{arch}.attention.head_count_kv": nkv,
+            f"{arch}.feed_forward_length": c.intermediate_size, f"{arch}.attention.key_length": c.head_dim,
+            f"{arch}.rope.freq_base": float(getattr(c, "rope_theta", None) or (c.rope_parameters.get("rope_theta") if "rope_theta" in c.rope_parameters
+                                                                               else c.rope_parameters["full_attention"]["rope_theta"])),
+            f"{arch}.attention.layer_norm_rms_epsilon": float(c.rms_norm_eps), f"{arch}.context_length": c.max_position_embeddings,
+            f"{arch}.vocab_size": c.vocab_size, "tokenizer.ggml.bos_token_id": 1, "tokenizer.ggml.eos_token_id": 2}
+    experts = getattr(c, "num_local_experts", None) or getattr(c, "num_experts", None)
+    if experts:
+        meta[f"{arch}.expert_count"], meta[f"{arch}.expert_used_count"] = int(experts), int(c.num_experts_per_tok)
+    if family.startswith("gemma"):
+        meta[f"{arch}.attention.sliding_window"] = int(c.sliding_window)
+        if family == "gemma2":
+            meta[f"{arch}.attn_logit_softcapping"], meta[f"{arch}.final_logit_softcapping"] = float(c.attn_logit_softcapping), float(c.final_logit_softcapping)
+        else:
+            meta[f"{arch}.rope.freq_base_swa"] = float(c.rope_parameters["sliding_attention"]["rope_theta"])
+    if family == "gpt_oss":
+        meta[f"{arch}.attention.sliding_window"] = int(c.sliding_window)
+    if family.startswith("granite"):
+        meta.update({f"{arch}.embedding_scale": float(c.embedding_multiplier), f"{arch}.residual_scale": float(c.residual_multiplier),
+                     f"{arch}.logit_scale": float(c.logits_scaling), f"{arch}.attention.scale": float(c.attention_multiplier)})
+    paired = family == "smollm3"
+    gemma = family.startswith("gemma")
+    table = {**LAYER, **PER_FAMILY.get("gemma" if gemma else family, {})}
+    tensors = []
+    sd = {k: v.detach().float().numpy() for k, v in m.state_dict().items()}
+
+    def put(name, a):
+        if quantise and a.ndim == 2 and name.endswith(".weight") and "norm" not in name and a.shape[1] % 32 == 0 and "inp" not in name:
+            tensors.append(PackedWeight(name, quantise, tuple(a.shape), codec.quantize(quantise, np.ascontiguousarray(a, dtype=np.float32))))
+        else:
+            tensors.append(_f32(name, a))
+
+    for k, a in sd.items():
+        if k == "model.embed_tokens.weight":
+            put("token_embd.weight", a)
+        elif k == "model.norm.weight":
+            put("output_norm.weight", a + 1.0 if gemma else a)
+        elif k == "lm_head.weight":
+            if not getattr(c, "tie_word_embeddings", False):
+                put("output.weight", a)
+        else:
+            mm = re.match(r"model\.layers\.(\d+)\.(.+)$", k)
+            if not mm:
+                continue
+            b, rest = f"blk.{mm.group(1)}.", mm.group(2)
+            if rest in table:
+                if gemma and "norm" in rest:
+                    a = a + 1.0                                   # the converter folds the one in
+                if paired and rest in ("self_attn.q_proj.weight", "self_attn.k_proj.weight"):
+                    a = a[names.hf_to_gguf_qk_row_order(a.shape[0], nh if "q_proj" in rest else nkv)]
+                put(b + table[rest], a)
+            elif rest == "mlp.experts.gate_up_proj" and family == "gpt_oss":          # [E, H, 2F], gate / up columns alternating
+                put(b + "ffn_gate_exps.weight", a[:, :, 0::2].transpose(0, 2, 1))
+                put(b + "ffn_up_exps.weight", a[:, :, 1::2].transpose(0, 2, 1))
+            elif rest == "mlp.experts.gate_up_proj_bias":
+                put(b + "ffn_gate_exps.bias", a[:, 0::2]); put(b + "ffn_up_exps.bias", a[:, 1::2])
+            elif rest == "mlp.experts.down_proj" and family == "gpt_oss":             # [E, F, H]
+                put(b + "ffn_down_exps.weight", a.transpose(0, 2, 1))
+            elif rest == "mlp.experts.down_proj_bias":
+                put(b + "ffn_down_exps.bias", a)
+            elif rest == "mlp.experts.gate_up_proj":                                  # stacked [E, 2F, H]: gate rows, then up rows
+                F = a.shape[1] // 2
+                put(b + "ffn_gate_exps.weight", a[:, :F]); put(b + "ffn_up_exps.weight", a[:, F:])
+            elif rest == "mlp.experts.down_proj":                                     # stacked [E, H, F]
+                put(b + "ffn_down_exps.weight", a)
+            elif rest == "block_sparse_moe.input_linear.weight":                      # granitemoe: [E, 2F, H]
+                F = a.shape[1] // 2
+                put(b + "ffn_gate_exps.weight", a[:, :F]); put(b + "ffn_up_exps.weight", a[:, F:])
+            elif rest == "block_sparse_moe.output_linear.weight":
+                put(b + "ffn_down_exps.weight", a)
+            else:
+                e = re.match(r"mlp\.experts\.(\d+)\.(gate|up|down)_proj\.weight$", rest)
+                assert e, f"unmapped tensor {k}"
+                sd.setdefault(("stack", b, e.group(2)), {})[int(e.group(1))] = a
+    for key in [k for k in sd if isinstance(k, tuple)]:
+        _, b, role = key
+        put(b + f"ffn_{role}_exps.weight", np.stack([sd[key][i] for i in sorted(sd[key])]))
+    gguf.write_gguf(path, meta, tensors)
+
+
+FAMILY_CASES = ["olmo2", "olmoe", "smollm3", "granite", "granitemoe", "gemma2", "gemma3", "gpt_oss"]
+
+
+@pytest.mark.parametrize("family", FAMILY_CASES)
+def test_gguf_of_the_family_equals_the_hugging_face_forward(family, tmp_path):
+    case = dict(CASES["smollm3-nope-layer" if family == "smollm3" else family])
+    if family == "gemma2":
+        case["query_pre_attn_scalar"] = BASE["head_dim"]          # a GGUF carries no query scalar: it is the head width
+    if family == "gemma3":
+        case["query_pre_attn_scalar"] = BASE["head_dim"]
+        case["num_hidden_layers"], case["layer_types"] = 6, ["sliding_attention"] * 5 + ["full_attention"]   # the pattern a GGUF implies
+    if family == "gpt_oss":
+        case["sliding_window"] = 6
+    if family == "smollm3":
+        case["num_hidden_layers"], case["no_rope_layers"], case["no_rope_layer_interval"] = 4, [1, 1, 1, 0], 4
+    m, vocab = build(case)
+    toks = torch.randint(0, vocab, (1, 12), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = m(toks).logits[0].numpy()
+    path = str(tmp_path / f"{family}.gguf")
+    _to_gguf(path, family, m)
+    h = ModelHandle.load(path)
+    assert h.cfg.family == ("granite" if family == "granitemoe" else family) and h.kind == "gguf"
+    sess = OracleSession(h.model, h.oracle_weights(), capacity=32)
+    sess._graph = lambda T, embeds=False: h.model.trace(StepSpec(rows=1, tokens=T, capacity=32, logit_rows="all"))
+    got = sess.step(toks.numpy()).reshape(ref.shape)
+    err = np.abs(got - ref).max() / np.abs(ref).max()
+    assert err < 2e-5, err
+
+
+def test_quantised_gguf_of_a_new_family_generates_packed(tmp_path):
+    """A Q8_0 OLMoE GGUF through the packed oracle: the projections stay as stored and generation equals the oracle over
+    the decoded weights."""
+    from poot_b200.driver.sampler import SamplingParams
+    from poot_b200.llm import LLM
+    m, vocab = build({**CASES["olmoe"], "hidden_size": 128, "head_dim": 32, "intermediate_size": 64})
+    path = str(tmp_path / "olmoe-q8.gguf")
+    _to_gguf(path, "olmoe", m, quantise="Q8_0")
+    prompt = [int(t) for t in np.random.default_rng(0).integers(3, vocab, 18)]
+    p = SamplingParams(max_tokens=5, ignore_eos=True)
+    want = LLM.oracle(path, rows=1, max_seq=64, num_blocks=8, prefill_chunk=16).generate_tokens(prompt, p)
+    assert LLM.oracle(path, rows=1, max_seq=64, num_blocks=8, prefill_chunk=16, packed=True).generate_tokens(prompt, p) == want
