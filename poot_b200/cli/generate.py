@@ -96,7 +96,7 @@ def parse_generate(argv: List[str]) -> GenerateArgs:
         raise ValueError("sampling or context option out of range")
     if len(a.reverse_prompt) > 16:
         raise ValueError("at most 16 reverse prompts")
-    if a.backend not in ("auto", "b200", "cuda", "fake", "oracle"):
+    if a.backend not in ("auto", "b200", "cuda", "fake", "oracle", "graph"):
         raise ValueError(f"--backend {a.backend!r}: this build has one device backend (b200 / cuda / auto), the CPU "
                          "`oracle` and `fake`")
     return a
@@ -109,6 +109,10 @@ def _open(a: GenerateArgs):
     ctx = a.ctx_size or 4096
     if a.model.startswith("random:"):
         return LLM.random(a.model.split(":", 1)[1], rows=1, max_seq=ctx)
+    if a.backend == "graph":
+        # the general device executor: every traced family, equation by equation on the device
+        import torch
+        return LLM.graph(a.model, device="cuda" if torch.cuda.is_available() else "cpu", rows=1, max_seq=ctx, num_blocks=(ctx + 15) // 16 + 1)
     if a.backend == "oracle":
         # a GGUF's quantised matrices stay as stored: the evaluator decodes them inside its native contractions
         return LLM.oracle(a.model, rows=1, max_seq=ctx, num_blocks=(ctx + 15) // 16 + 1, lora=a.lora,

@@ -330,6 +330,7 @@ class OracleStepEngine:
         self.num_blocks, self.max_seqs, self.max_tokens, self.max_blocks = num_blocks, max_seqs, max_tokens, max_blocks_per_seq
         self.options = options or EvalOptions(matmul_precision="exact", native=bool(weight_formats))
         self.weight_formats = tuple(sorted((weight_formats or {}).items()))
+        self.spec_extra = {}                         # further StepSpec fields of this engine's graphs (weight storage type)
         if self.weight_formats and graph_transform is None:
             def graph_transform(g):
                 from ..plan import passes
@@ -349,21 +350,23 @@ class OracleStepEngine:
     def write_block_table(self, row: int, blocks) -> None:
         self.block_tables[row, :len(blocks)] = np.asarray(blocks, np.int32)
 
-    def _graph(self, tokens: int, capacity: int, embeds: bool = False, mrope: bool = False):
-        key = (tokens, capacity, embeds, mrope)
+    def _graph(self, tokens: int, capacity: int, embeds: bool = False, mrope: bool = False, all_rows: bool = False):
+        all_rows = all_rows or self.carry
+        key = (tokens, capacity, embeds, mrope, all_rows)
         if key not in self.graphs:
             from ..models.model import StepSpec
             g = self.model.trace(StepSpec(rows=1, tokens=tokens, capacity=capacity, paged=True,
                                           pool_slots=self.num_blocks * self.block, embeds=embeds, mrope=mrope,
-                                          carry=self.carry, logit_rows="all" if self.carry else "last",
-                                          weight_formats=self.weight_formats))
+                                          carry=self.carry, logit_rows="all" if all_rows else "last",
+                                          weight_formats=self.weight_formats, **self.spec_extra))
             self.graphs[key] = self.graph_transform(g) if self.graph_transform is not None else g
         return self.graphs[key]
 
     def _segment(self, row: int, tokens: np.ndarray, positions: np.ndarray, slots: np.ndarray, ctx: int,
                  embed_flags: Optional[np.ndarray] = None, embed_rows: Optional[np.ndarray] = None,
-                 rope_positions: Optional[np.ndarray] = None, carry: Optional[np.ndarray] = None):
-        """Logits of the segment's last token; with ``carry`` engines ``(logits, hidden)`` of every token."""
+                 rope_positions: Optional[np.ndarray] = None, carry: Optional[np.ndarray] = None, all_rows: bool = False):
+        """Logits of the segment's last token, or with ``all_rows`` (a verify step reads a logit row per token) of every
+        token; with ``carry`` engines ``(logits, hidden)`` of every token."""
         from ..oracle.eval import eval_graph
         blocks = max(1, -(-ctx // self.block))
         cap_blocks = 1
@@ -373,7 +376,7 @@ class OracleStepEngine:
         cap = cap_blocks * self.block
         embeds = embed_flags is not None and bool(embed_flags.any())
         mrope = rope_positions is not None and bool(getattr(self.model.cfg, "mrope_sections", None))
-        g = self._graph(len(tokens), cap, embeds, mrope)
+        g = self._graph(len(tokens), cap, embeds, mrope, all_rows)
         bt = self.block_tables[row, :cap_blocks].astype(np.int64)
         read = (bt[:, None] * self.block + np.arange(self.block)[None, :]).reshape(1, cap).astype(np.int32)
         inputs = {"tokens": tokens.reshape(1, -1).astype(np.int32), "positions": positions.reshape(1, -1).astype(np.int32),
@@ -395,16 +398,24 @@ class OracleStepEngine:
                 # paged pools are shared by every sequence; recurrent state (conv taps, scan carry) belongs to the row
                 key = (row, i.name) if getattr(i, "state_role", None) == "recurrent" else i.name
                 if key not in self.state or (isinstance(key, tuple) and fresh):
-                    self.state[key] = np.zeros(g.types[i.value].shape, dtype=np.float32)
+                    self.state[key] = self._new_state(g.types[i.value])
                 inputs[i.name] = self.state[key]
                 keys[i.name] = key
-        ev = eval_graph(g, inputs, self.options)
+        outputs = self._evaluate(g, inputs)
         for o in g.outputs:
             if o.role == "state_next":
-                self.state[keys[o.state_of]] = ev.outputs[o.name]
+                self.state[keys[o.state_of]] = outputs[o.name]
         if self.carry:
-            return ev.outputs["logits"], ev.outputs["hidden"]
-        return ev.outputs["logits"][0]
+            return outputs["logits"], outputs["hidden"]
+        return outputs["logits"] if all_rows else outputs["logits"][0]
+
+    # ---- where the step's values live (overridden by the device evaluator) ---------------------------------------------
+    def _new_state(self, ty):
+        return np.zeros(ty.shape, dtype=np.float32)
+
+    def _evaluate(self, g, inputs):
+        from ..oracle.eval import eval_graph
+        return eval_graph(g, inputs, self.options).outputs
 
     def run_step(self, inp: StepInputs):
         import time as _time
@@ -424,12 +435,15 @@ class OracleStepEngine:
             if int(inp.row_ctx[start]) > 0:       # padding tokens have no context and write nothing
                 ef = inp.embed_flags[start:end] if inp.embed_flags is not None else None
                 er = inp.embed_rows[start:end] if inp.embed_flags is not None else None
+                several = any(i in want for i in range(start, end - 1))          # a verify step: a logit row inside the segment
                 out = self._segment(row, inp.tokens[start:end], inp.positions[start:end], inp.slots[start:end],
                                     int(inp.row_ctx[end - 1]), ef, er,
                                     inp.rope_positions[:, start:end] if inp.rope_positions is not None else None,
-                                    inp.carry[start:end] if inp.carry is not None else None)
-                if self.carry:
-                    seg_logits, hidden[start:end] = out
+                                    inp.carry[start:end] if inp.carry is not None else None, all_rows=several)
+                if self.carry or several:
+                    seg_logits = out[0] if self.carry else out
+                    if self.carry:
+                        hidden[start:end] = out[1]
                     for i in range(start, end):
                         if i in want:
                             logits[want[i]] = seg_logits[i - start]
@@ -463,6 +477,9 @@ class OracleStepEngine:
     def last_logits(self, rows: int) -> np.ndarray:
         return self._logits[:rows]
 
+    def _copy(self, v):
+        return v.copy()
+
     # ---- recurrent state: snapshot / restore of sequence rows (speculative rollback), as on the device engine ---------
     @property
     def has_recurrent_state(self) -> bool:
@@ -473,7 +490,7 @@ class OracleStepEngine:
         token into it is not invertible, so a speculative round that rejects a draft restores the rows and replays
         what it keeps (crates/poot-llm/src/driver/snapshot.rs:1-17)."""
         rows = set(int(r) for r in rows)
-        self._shadow = {k: v.copy() for k, v in self.state.items() if isinstance(k, tuple) and k[0] in rows}
+        self._shadow = {k: self._copy(v) for k, v in self.state.items() if isinstance(k, tuple) and k[0] in rows}
         self._shadow_rows = rows
 
     def restore_rows(self, rows) -> None:
@@ -481,10 +498,76 @@ class OracleStepEngine:
             raise RuntimeError("restore_rows without a snapshot")
         for k in [k for k in self.state if isinstance(k, tuple) and k[0] in self._shadow_rows]:
             del self.state[k]                      # a state first written after the snapshot starts from zero again
-        self.state.update({k: v.copy() for k, v in self._shadow.items()})
+        self.state.update({k: self._copy(v) for k, v in self._shadow.items()})
 
     def copy_block(self, src: int, dst: int) -> None:
         b = self.block
         for name, pool in self.state.items():
             if isinstance(name, str) and name.endswith("_pool"):          # every paged pool: K/V, latent, indexer keys
                 pool[dst * b:(dst + 1) * b] = pool[src * b:(src + 1) * b]
+
+
+class GraphStepEngine(OracleStepEngine):
+    """The general device executor behind the driver: the family's traced step graphs evaluated with tensors on
+    ``device`` (``oracle/torch_eval.py``), weights uploaded once, paged pools and recurrent state resident there and
+    written in place.  Every family the registry traces runs through it, including those the hand-written engine has
+    no program for; one library or extension launch per equation, so it is launch-bound, and the logits come back to
+    the host for the driver's sampling rules (crates/poot-executor: a planned program walked equation by equation)."""
+
+    def __init__(self, model, weights, num_blocks: int, max_seqs: int, max_tokens: int, max_blocks_per_seq: int, device="cuda",
+                 weight_dtype=None, carry: bool = False):
+        import torch
+        super().__init__(model, weights, num_blocks, max_seqs, max_tokens, max_blocks_per_seq, carry=carry)
+        self.torch, self.device = torch, torch.device(device)
+        self.weight_dtype = weight_dtype or torch.float32
+        if self.weight_dtype == torch.bfloat16:       # the graphs declare the weights as stored and widen them where they are used
+            from ..tensor import DType
+            self.spec_extra = {"weight_dtype": DType.BF16}
+
+        def up(a):
+            t = torch.from_numpy(np.ascontiguousarray(a))
+            return t.to(self.device, dtype=self.weight_dtype if t.dtype.is_floating_point else t.dtype)
+        self.weights = {n: up(a) for n, a in weights.items()}
+        self._owners = {}
+
+    def _new_state(self, ty):
+        from ..oracle.torch_eval import StateTensor, torch_dtype
+        st = StateTensor(tuple(ty.shape), torch_dtype(ty.dtype), self.device)
+        self._owners[st.view.data_ptr()] = st
+        return st.view
+
+    def _copy(self, v):
+        return v.clone()
+
+    def _evaluate(self, g, inputs):
+        from ..oracle.torch_eval import eval_graph_torch, torch_dtype
+        torch = self.torch
+        feed, in_place = {}, {}
+        for i in g.inputs:
+            if i.name not in inputs:
+                continue
+            v = inputs[i.name]
+            want = torch_dtype(g.types[i.value].dtype)
+            if not isinstance(v, torch.Tensor):
+                v = torch.from_numpy(np.ascontiguousarray(v)).to(self.device)
+            feed[i.name] = v if v.dtype == want else v.to(want)
+            st = self._owners.get(feed[i.name].data_ptr()) if i.storage == "state" else None
+            if st is not None:
+                in_place[i.value] = st
+        out = eval_graph_torch(g, feed, self.device, in_place)
+        res = {}
+        for o in g.outputs:
+            v = out[o.name]
+            if o.role == "state_next":
+                if v.data_ptr() not in self._owners:            # a recurrent state: a fresh tensor each step
+                    v = v.contiguous()
+                res[o.name] = v
+            else:
+                res[o.name] = v.float().cpu().numpy()
+        return res
+
+    def copy_block(self, src: int, dst: int) -> None:
+        b = self.block
+        for name, pool in self.state.items():
+            if isinstance(name, str) and name.endswith("_pool"):
+                pool[dst * b:(dst + 1) * b].copy_(pool[src * b:(src + 1) * b])

@@ -188,6 +188,31 @@ class LLM:
                                prefill_chunk, handle, prefill_budget, mtp=mtp)
 
     @staticmethod
+    def graph(path: str, device: str = "cuda", rows: int = 4, max_seq: int = 512, num_blocks: int = 128, prefill_chunk: int = 64,
+              dtype: str = "bf16", prefill_budget: Optional[int] = None) -> "LLM":
+        """A checkpoint served by the general device executor: the family's step graphs evaluated equation by equation
+        with tensors on ``device`` (weights in ``dtype``, arithmetic in f32, pools resident and written in place).  Every
+        family the registry traces runs this way, including those without a hand-written device program; it is
+        launch-bound, so the hand-written engine (``LLM.load``) is the one to use where it has a program."""
+        import torch
+        from .driver.engines import GraphStepEngine
+        from .driver.handle import ModelHandle
+        handle = ModelHandle.load(path)
+        cfg = handle.cfg
+        max_seq = min(max_seq, cfg.max_position)
+        step_prefill = max(prefill_chunk, min(prefill_budget or 0, rows * prefill_chunk))
+        wd = {"bf16": torch.bfloat16, "f32": torch.float32}[dtype]
+        eng = GraphStepEngine(handle.model, handle.oracle_weights(), num_blocks, rows, step_prefill + rows, blocks_for(max_seq),
+                              device=device, weight_dtype=wd)
+        tokenizer = _tokenizer_for(handle)
+        eos = getattr(tokenizer, "eos", None)
+        from .driver.features import Feature, check
+        check([Feature.RECURRENT_STATE] if cfg.is_recurrent else [])
+        drv = Driver(eng, num_blocks, rows, max_seq, cfg.vocab, prefill_chunk=prefill_chunk, prefix_caching=not cfg.is_recurrent,
+                     eos_token=eos if eos is not None else cfg.eos_token, prefill_budget=step_prefill)
+        return LLM(cfg, drv, tokenizer, None, handle, None)
+
+    @staticmethod
     def oracle_from(model, weights, tokenizer=None, rows: int = 4, max_seq: int = 512, num_blocks: int = 128,
                     prefill_chunk: int = 64, handle=None, prefill_budget: Optional[int] = None, mtp=None,
                     weight_formats=None) -> "LLM":

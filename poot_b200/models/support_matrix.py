@@ -81,7 +81,7 @@ DEVICE_VERIFIED = {"llama", "qwen3"}
 
 def device_state(name: str, has_program: bool) -> str:
     if not has_program:
-        return "no"
+        return "general executor only"
     return "device-verified" if name in DEVICE_VERIFIED else "emulated only"
 
 
@@ -126,7 +126,8 @@ def render() -> str:
              "Hugging Face implementation.  `device`: the B200 engine has a kernel program for the family.  The `B200 engine`",
              "column says how far that program has been checked: `device-verified` = it ran on a B200 and matched the fp32",
              "restatement; `emulated only` = the engine's unmodified program ran on host restatements of the kernels and",
-             "matched the oracle and Hugging Face, but has not run on a device yet; `no` = no device program.  The last",
+             "matched the oracle and Hugging Face, but has not run on a device yet; `general executor only` = no hand-written",
+             "program: the family runs on the device through the general executor (`--backend graph`, one launch per equation).  The last",
              "column names what the device program lacks for a representative checkpoint of the family.", "",
              "| family | header `model_type` | runs on | GGUF | B200 engine | missing on the device |", "|---|---|---|---|---|---|"]
     for r in rows():
