@@ -27,11 +27,12 @@ def main(argv=None) -> int:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     comm = None
-    if cfg.backend not in ("b200", "cuda", "auto", "oracle"):
-        print(f"poot-serve: --backend {cfg.backend!r}: this build has the device backend (b200) and `oracle`", file=sys.stderr)
+    if cfg.backend not in ("b200", "cuda", "auto", "oracle", "graph"):
+        print(f"poot-serve: --backend {cfg.backend!r}: this build has the device backend (b200), the general device executor "
+              "(`graph`) and `oracle`", file=sys.stderr)
         return 2
-    if cfg.backend == "oracle" and world > 1:
-        print("poot-serve: the oracle backend runs in one process", file=sys.stderr)
+    if cfg.backend in ("oracle", "graph") and world > 1:
+        print(f"poot-serve: the {cfg.backend} backend runs in one process", file=sys.stderr)
         return 2
     pp = 1
     if world > 1:
@@ -75,6 +76,12 @@ def _open_model(cfg, rank: int, world: int, pp: int, comm, mtp_k: int):
                           kv_fraction=cfg.kv_fraction, tp_rank=rank if pp == 1 else 0, tp_world=world if pp == 1 else 1,
                           comm=comm, prefill_budget=cfg.prefill_budget or None, pp_rank=rank if pp > 1 else 0, pp_world=pp,
                           draft_mtp=mtp_k)
+    if cfg.backend == "graph":
+        # every traced family, equation by equation on the device (no adapter, no draft layer)
+        import torch
+        return LLM.graph(cfg.model, device="cuda" if torch.cuda.is_available() else "cpu", rows=cfg.rows, max_seq=cfg.max_seq,
+                         prefill_chunk=cfg.prefill_chunk, num_blocks=cfg.rows * ((cfg.max_seq + 15) // 16) + 8,
+                         prefill_budget=cfg.prefill_budget or None)
     if cfg.backend == "oracle":
         return LLM.oracle(cfg.model, rows=cfg.rows, max_seq=cfg.max_seq, prefill_chunk=cfg.prefill_chunk, lora=cfg.lora,
                           num_blocks=cfg.rows * ((cfg.max_seq + 15) // 16) + 8, prefill_budget=cfg.prefill_budget or None,

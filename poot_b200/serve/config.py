@@ -56,7 +56,7 @@ class ServeConfig:
     lora: Optional[str] = None           # PEFT adapter directory merged into the projections at load
     lora_slots: int = 0                  # > 0: resident adapters selected per request (POST /v1/lora_adapters, `model` = name)
     lora_max_rank: int = 64
-    backend: str = "b200"                # b200 (the device engine) | oracle (the CPU graph evaluator; every family, slow)
+    backend: str = "b200"                # b200 (the device engine) | graph (the general device executor; every family) | oracle (the CPU evaluator)
 
     def validate(self) -> None:
         def bound(name, lo, hi):
