@@ -423,3 +423,69 @@ def sample_head(b: Builder, logits: Traced, rule: str = "greedy", seed: Optional
     u = b.random_uniform(seed, logits.shape[-1])
     noise = -b.unary("log", -b.unary("log", u))
     return b.sample_token(rule, logits, noise, params, top_k if rule != "gumbel" else None)
+
+
+# ---- chunk-parallel gated delta rule ---------------------------------------------------------------------------------
+def delta_rule_chunked(b: Builder, q: Traced, k: Traced, v: Traced, g: Traced, beta: Traced, s_in: Traced, chunk: int = 64):
+    """The gated delta rule of the ``scan`` equation (one log decay per head and token) in its chunk-parallel form: the
+    same ``(y[1, H, L, D], state[1, H, D, D])`` out of matrix products over chunks of ``chunk`` tokens instead of one step
+    per token (crates/poot-graph-ir/src/ops/prefill.rs: the chunked linear-attention prefill).
+
+    Within a chunk, with ``G`` the running sum of the log decays, ``M[i, j] = beta_i (k_i . k_j) exp(G_i - G_j)`` for
+    ``j < i`` couples a token's correction to the earlier ones; ``T = (I + M)^-1`` undoes the coupling.  ``M`` is strictly
+    lower triangular, so with ``X = -M`` the inverse is the finite product ``(I + X)(I + X^2)(I + X^4)...`` -
+    ``log2(chunk)`` squarings, all matrix products.  Then per chunk, from the state ``S`` carried in:
+
+        ``v' = T (beta v) - T (beta k exp(G)) S``
+        ``y  = (q exp(G)) S + tril(q k^T exp(G_i - G_j)) v'``
+        ``S  = exp(G_last) S + (k exp(G_last - G))^T v'``
+
+    A ragged last chunk is padded with tokens that change nothing (zero key, value, beta and log decay)."""
+    _, H, L, D = q.shape
+    if tuple(g.shape) != (1, H, L, 1):
+        raise ValueError("the chunk-parallel form needs one log decay per head and token")
+    C = chunk
+    n = -(-L // C)
+    pad = n * C - L
+
+    def chunks(t: Traced, width: int) -> Traced:                      # [1, H, L, width] -> [H, n, C, width]
+        t = b.reshape(t, (H, L, width))
+        if pad:
+            t = b.concat([t, b.broadcast(b.scalar(0.0, F32), (H, pad, width))], 1)
+        return b.reshape(t, (H, n, C, width))
+
+    qc, kc, vc, gc, bc = chunks(q, D), chunks(k, D), chunks(v, D), chunks(g, 1), chunks(beta, 1)
+    row, col = b.iota((H, n, C, C), 2), b.iota((H, n, C, C), 3)
+    lower_incl = b.cast(b.binary("ge", row, col), F32)                 # j <= i
+    strictly = lower_incl - b.cast(b.binary("ge", col, row), F32) * lower_incl          # j < i
+    G = b.matmul(lower_incl, gc, "exact")                              # running sum of the log decays: [H, n, C, 1]
+    Gt = b.transpose(G, (0, 1, 3, 2))
+    # exp(G_i - G_j) only where j <= i (above the diagonal the difference is positive and may overflow)
+    decay = b.unary("exp", (b.broadcast(G, (H, n, C, C)) - b.broadcast(Gt, (H, n, C, C))) * lower_incl) * lower_incl
+    kb = kc * b.broadcast(bc, kc.shape)
+    X = -(b.matmul(kb, b.transpose(kc, (0, 1, 3, 2)), "exact") * decay * strictly)
+    eye = lower_incl * b.cast(b.binary("ge", col, row), F32)
+    T, P, span = eye + X, X, 1
+    while span * 2 < C:
+        P = b.matmul(P, P, "exact")
+        T = b.matmul(T, eye + P, "exact")
+        span *= 2
+    eG = b.unary("exp", G)
+    value = b.matmul(T, vc * b.broadcast(bc, vc.shape), "exact")       # T (beta v)
+    k_cum = b.matmul(T, kb * b.broadcast(eG, kb.shape), "exact")       # T (beta k exp(G))
+    qk = b.matmul(qc, b.transpose(kc, (0, 1, 3, 2)), "exact") * decay  # tril(q k^T exp(G_i - G_j)), diagonal kept
+    q_in = qc * b.broadcast(eG, qc.shape)
+    G_last = b.slice(G, 2, C - 1, 1)                                   # [H, n, 1, 1]
+    k_out = kc * b.broadcast(b.unary("exp", b.broadcast(G_last, G.shape) - G), kc.shape)
+    e_last = b.unary("exp", G_last)
+    S = b.reshape(s_in, (H, D, D))
+    ys = []
+    for c in range(n):
+        pick = lambda t: b.reshape(b.slice(t, 1, c, 1), (H,) + tuple(t.shape[2:]))
+        v_new = pick(value) - b.matmul(pick(k_cum), S, "exact")
+        ys.append(b.matmul(pick(q_in), S, "exact") + b.matmul(pick(qk), v_new, "exact"))
+        S = S * b.broadcast(pick(e_last), (H, D, D)) + b.matmul(b.transpose(pick(k_out), (0, 2, 1)), v_new, "exact")
+    y = b.concat(ys, 1) if n > 1 else ys[0]
+    if pad:
+        y = b.slice(y, 1, 0, L)
+    return b.reshape(y, (1, H, L, D)), b.reshape(S, (1, H, D, D))

@@ -38,6 +38,8 @@ class StepSpec:
     #                               multi-token-prediction layer reads and a chain of its steps recycles
     embeds: bool = False          # rows of other modalities replace the embeddings of flagged tokens (image rows of a VLM)
     mrope: bool = False           # three rotary position streams (time, row, column) bind per token: ``rope_positions[3, R*T]``
+    gdn_chunk: int = 0            # > 0: steps of more than one token run the gated delta rule in its chunk-parallel form
+    #                               (matrix products over chunks of this many tokens) instead of the per-token scan equation
     weight_formats: tuple = ()    # ((weight name, block format), ..): those 2-D weights are declared as their packed bytes and
     #                               decoded by a ``packed_dequant`` equation, so an evaluator or a planner sees them as stored
 
@@ -552,7 +554,10 @@ class Model:
                 k = O.repeat_kv(b, O.l2norm(b, heads(b.slice(y, 1, nk * Dg, nk * Dg), nk)), nv // nk)
                 v = heads(b.slice(y, 1, 2 * nk * Dg, nv * Dg), nv)
                 col = lambda t: b.reshape(b.transpose(b.slice(t, 0, r * T, T), (1, 0)), (1, nv, T, 1))
-                yo, so = b.scan("delta_rule", [q, k, v, col(g), col(beta), b.slice(s_in, 0, r, 1)])
+                if spec.gdn_chunk > 0 and T > 1:
+                    yo, so = O.delta_rule_chunked(b, q, k, v, col(g), col(beta), b.slice(s_in, 0, r, 1), spec.gdn_chunk)
+                else:
+                    yo, so = b.scan("delta_rule", [q, k, v, col(g), col(beta), b.slice(s_in, 0, r, 1)])
                 ys.append(b.reshape(b.transpose(yo, (0, 2, 1, 3)), (T, nv, Dg)))
                 convs.append(b.reshape(cs, (1, K - 1, C)))
                 states.append(so)

@@ -168,3 +168,54 @@ def test_supported_models_page_is_current():
     from poot_b200.models.support_matrix import render
     path = os.path.join(os.path.dirname(__file__), "..", "docs", "supported-models.md")
     assert open(path).read() == render()
+
+
+@pytest.mark.parametrize("L,C", [(13, 4), (64, 16), (7, 8)])
+def test_chunk_parallel_delta_rule_equals_the_scan_equation(L, C):
+    """The gated delta rule as matrix products over chunks (the coupling inside a chunk undone by ``log2(chunk)``
+    squarings of a strictly lower-triangular matrix) against the per-token scan, from a carried state, with a ragged
+    last chunk."""
+    from poot_b200.ir import oplib as O
+    from poot_b200.ir.builder import Builder
+    from poot_b200.oracle.eval import EvalOptions, eval_graph
+    from poot_b200.tensor import DType
+    rng = np.random.default_rng(L)
+    H, D = 3, 8
+    feed = {"q": rng.standard_normal((1, H, L, D)) * 0.4, "k": rng.standard_normal((1, H, L, D)), "v": rng.standard_normal((1, H, L, D)),
+            "g": -np.abs(rng.standard_normal((1, H, L, 1))) * 0.5, "beta": 1 / (1 + np.exp(-rng.standard_normal((1, H, L, 1)))),
+            "s": rng.standard_normal((1, H, D, D)) * 0.2}
+    feed["k"] /= np.linalg.norm(feed["k"], axis=-1, keepdims=True)
+    feed = {n: a.astype(np.float32) for n, a in feed.items()}
+    b = Builder()
+    ins = [b.slot(n, feed[n].shape, DType.F32, "activation") for n in ("q", "k", "v", "g", "beta", "s")]
+    y, s = b.scan("delta_rule", ins)
+    y2, s2 = O.delta_rule_chunked(b, *ins, chunk=C)
+    for n_, t in (("y", y), ("s", s), ("y2", y2), ("s2", s2)):
+        b.output(t, n_)
+    g = b.finish()
+    assert sum(1 for e in g.eqns if e.op == "scan") == 1                 # the chunked form has no recurrence equation
+    r = eval_graph(g, feed, EvalOptions(matmul_precision="exact")).outputs
+    assert np.abs(r["y"] - r["y2"]).max() <= 2e-6 and np.abs(r["s"] - r["s2"]).max() <= 2e-6
+
+
+def test_hybrid_prefill_through_the_chunk_parallel_form_equals_the_scan_form():
+    from poot_b200.models.model import StepSpec
+    from poot_b200.oracle.eval import EvalOptions, eval_graph
+    model = Registry.builtin().resolve_hf(header("qwen3next"))
+    w = random_weights_f32(model, seed=0, std=0.2)
+    toks = np.random.default_rng(1).integers(0, model.cfg.vocab, (1, 11)).astype(np.int32)
+    outs = []
+    for chunk in (0, 4):
+        g = model.trace(StepSpec(rows=1, tokens=11, capacity=16, gdn_chunk=chunk))
+        assert any(e.op == "scan" for e in g.eqns) == (chunk == 0)
+        feed = {"tokens": toks, "positions": np.arange(11, dtype=np.int32)[None], "read_map": np.arange(16, dtype=np.int32)[None],
+                "write_map": np.arange(11, dtype=np.int32)}
+        for i in g.inputs:
+            if i.storage == "const":
+                feed[i.name] = w[i.name]
+            elif i.storage == "state":
+                feed[i.name] = np.zeros(g.types[i.value].shape, np.float32)
+        outs.append(eval_graph(g, feed, EvalOptions(matmul_precision="exact")).outputs)
+    assert np.abs(outs[0]["logits"] - outs[1]["logits"]).max() <= 1e-4 * max(1.0, np.abs(outs[0]["logits"]).max())
+    state = next(n for n in outs[0] if n.endswith("gdn_state.next"))
+    assert np.abs(outs[0][state] - outs[1][state]).max() <= 1e-5
