@@ -529,6 +529,7 @@ class GraphStepEngine(OracleStepEngine):
             return t.to(self.device, dtype=self.weight_dtype if t.dtype.is_floating_point else t.dtype)
         self.weights = {n: up(a) for n, a in weights.items()}
         self._owners = {}
+        self._commit = {}
 
     def _new_state(self, ty):
         from ..oracle.torch_eval import StateTensor, torch_dtype
@@ -554,7 +555,11 @@ class GraphStepEngine(OracleStepEngine):
             st = self._owners.get(feed[i.name].data_ptr()) if i.storage == "state" else None
             if st is not None:
                 in_place[i.value] = st
-        out = eval_graph_torch(g, feed, self.device, in_place)
+        plan = self._commit.get(id(g))
+        if plan is None:                                  # which updates may overwrite their state: proven once per graph
+            from ..plan.state_commit import plan_state_commit
+            plan = self._commit[id(g)] = set(plan_state_commit(g).inplace)
+        out = eval_graph_torch(g, feed, self.device, in_place, donated=plan)
         res = {}
         for o in g.outputs:
             v = out[o.name]

@@ -149,3 +149,41 @@ def check_write_slots(write_map: np.ndarray) -> None:
     if live.size and np.unique(live).size != live.size:
         vals, counts = np.unique(live, return_counts=True)
         raise DuplicateWriteSlot(f"slot {int(vals[counts > 1][0])} is written {int(counts.max())} times in one step")
+
+
+# ---- numerics classes ---------------------------------------------------------------------------------------------------
+NUMERICS_ORDER = ("exact", "unfused", "reassociating", "narrowing")
+# comparison tolerance of a device result against the oracle, relative to max(|oracle element|, 1), by the strongest
+# property the compiled program exhibits (crates/poot-graph-ir/src/analysis/numerics.rs:83-96)
+TIER2_TOLERANCE = {"exact": 0.0, "unfused": 1e-4, "reassociating": 1e-3, "narrowing": 5e-3}
+_REASSOCIATING_OPS = {"attention", "rope", "fused", "fused_row", "contraction_epilogue", "dense_contraction", "grouped_dense_contraction",
+                      "expert_group", "block_top_k", "selected_attention"}
+_NARROWING_OPS = {"packed_contraction", "packed_row_gather", "packed_dequant"}
+_FLOAT_ARITHMETIC = {"add", "sub", "mul", "div", "max", "neg", "exp", "log", "sqrt", "recip", "tanh", "erf", "reduce", "matmul",
+                     "indexed_matmul", "scan", "all_reduce"}
+
+
+def implied_numerics(g: Graph) -> str:
+    """The strongest numerics property the graph's equations imply, in ``NUMERICS_ORDER``: ``exact`` (integer and
+    movement equations only), ``unfused`` (ordinary float arithmetic a device runs as written), ``reassociating`` (a
+    composite that reorders float arithmetic: fusion, tiling, flash attention, rope) or ``narrowing`` (a quantised
+    decode, a contraction whose operands are rounded to a 16-bit type, a float value stored narrower than f32).  It
+    describes how closely a device result can be expected to follow the oracle (``TIER2_TOLERANCE``), not whether a
+    rewrite is legal."""
+    rank = 0
+    for e in g.eqns:
+        out = g.types[e.outputs[0]] if e.outputs else None
+        r = 0
+        if e.op in _NARROWING_OPS or (e.op in ("matmul", "indexed_matmul", "dense_contraction", "packed_contraction", "attention")
+                                      and e.attrs.get("precision", "narrow") != "exact"):
+            r = 3
+        elif e.op == "cast" and e.attrs["dtype"].is_float and e.attrs["dtype"].size < 4:
+            r = 3
+        elif e.op in _REASSOCIATING_OPS:
+            r = 2
+        elif e.op in _FLOAT_ARITHMETIC and out is not None and out.dtype.is_float:
+            r = 1
+        if e.body is not None:
+            r = max(r, NUMERICS_ORDER.index(implied_numerics(e.body)))
+        rank = max(rank, r)
+    return NUMERICS_ORDER[rank]

@@ -49,9 +49,11 @@ def _erf(x):
     return torch.erf(x)
 
 
-def eval_graph_torch(g: Graph, inputs: Dict[str, torch.Tensor], device, in_place: Optional[Dict[int, StateTensor]] = None) -> Dict[str, torch.Tensor]:
+def eval_graph_torch(g: Graph, inputs: Dict[str, torch.Tensor], device, in_place: Optional[Dict[int, StateTensor]] = None,
+                     donated=None) -> Dict[str, torch.Tensor]:
     """Evaluate ``g`` over ``inputs`` (tensors on ``device``, computed constants are materialised here); returns the
-    outputs by name.  ``in_place``: graph value -> state tensor that a ``scatter_update`` of that value may overwrite."""
+    outputs by name.  ``in_place``: graph value -> state tensor behind it; ``donated``: indices of the equations the state
+    commit plan lets overwrite their state in place (``plan/state_commit.py``; ``None``: every update of a state tensor)."""
     from .eval import computed_constant
     env: Dict[int, torch.Tensor] = {}
     for i in g.inputs:
@@ -69,11 +71,11 @@ def eval_graph_torch(g: Graph, inputs: Dict[str, torch.Tensor], device, in_place
             raise ValueError(f"input {i.name!r}: shape {tuple(a.shape)}, graph expects {ty.shape}")
         env[i.value] = a
     owner = dict(in_place or {})
-    for e in g.eqns:
+    for k, e in enumerate(g.eqns):
         ins = [env[v] for v in e.inputs]
         if e.op == "cast" and e.inputs[0] in owner and ins[0].dtype == torch_dtype(e.attrs["dtype"]):
             owner[e.outputs[0]] = owner[e.inputs[0]]          # a cast to the pool's own type is the pool
-        outs = _eval(g, e, ins, device, owner)
+        outs = _eval(g, e, ins, device, owner if (donated is None or k in donated) else {})
         for o, val in zip(e.outputs, outs):
             env[o] = val
     return {o.name: env[o.value] for o in g.outputs}

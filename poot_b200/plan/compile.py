@@ -31,6 +31,24 @@ class Program:
     declines: List[tuple] = field(default_factory=list)
 
     @property
+    def numerics(self) -> str:
+        """The strongest numerics property of the compiled graph (``ir/analysis.py::implied_numerics``)."""
+        from ..ir.analysis import implied_numerics
+        return implied_numerics(self.graph)
+
+    @property
+    def tolerance(self) -> float:
+        """How closely a device result is expected to follow the oracle, relative to ``max(|oracle element|, 1)``."""
+        from ..ir.analysis import TIER2_TOLERANCE
+        return TIER2_TOLERANCE[self.numerics]
+
+    @property
+    def state_commit(self):
+        """Which state updates may overwrite their buffer and which are copied after the step (``plan/state_commit.py``)."""
+        from .state_commit import plan_state_commit
+        return plan_state_commit(self.graph)
+
+    @property
     def census(self) -> Dict[str, int]:
         return launch_census(self.plans)
 

@@ -440,3 +440,41 @@ def test_form_recurrent_blocks_matches_the_definitions_only():
     other = graph(True, "tanh")
     passes.canonicalize(other); passes.cse(other)
     assert form_recurrent_blocks(other) == {"causal_conv_silu": 0, "gated_rmsnorm": 0}
+
+
+def test_state_commit_plan_and_numerics_class():
+    """Paged pools whose only reader is their own update are overwritten in place; recurrent states (recomputed, not
+    updated) and a pool that something else still reads are copied after the step.  The numerics class is the strongest
+    property of the equations: exact for integer work, unfused for plain f32 arithmetic, reassociating once composites
+    are formed, narrowing when operands or storage are 16-bit."""
+    from poot_b200.ir.analysis import TIER2_TOLERANCE, implied_numerics
+    from poot_b200.ir.builder import Builder
+    from poot_b200.models.registry import Registry
+    from poot_b200.plan.state_commit import plan_state_commit
+    from poot_b200.tensor import DType
+    from tests.test_families import header
+    m = Registry.builtin().resolve_hf(header("qwen3next"))
+    g = m.trace(StepSpec(rows=1, tokens=4, capacity=32))
+    plan = plan_state_commit(g)
+    assert sorted(plan.inplace.values()) == ["layers.1.k_pool", "layers.1.v_pool", "layers.3.k_pool", "layers.3.v_pool"]
+    assert {a for a, _ in plan.copies} == {f"layers.{l}.{n}" for l in (0, 2) for n in ("conv_state", "gdn_state")}
+    prog = compile_graph(g)
+    assert sorted(prog.state_commit.inplace.values()) == sorted(plan.inplace.values())          # the rewrite keeps the donations
+    b = Builder()
+    pool = b.state("pool", (8, 1, 4), DType.F32, "blocked")
+    upd = b.slot("u", (2, 1, 4), DType.F32, "activation")
+    idx = b.slot("i", (2,), DType.I32, "write_map", range=(-1, 7))
+    nxt = b.scatter_update(pool, idx, upd)
+    b.output(nxt, "pool.next", "state_next", "pool")
+    b.output(pool * 2.0 + b.scalar(0.0, DType.F32), "old", "result")                            # the old contents are still read
+    late = plan_state_commit(b.finish())
+    assert not late.inplace and "read by another equation" in late.reasons["pool"]
+    i = Builder()
+    t = i.slot("t", (4,), DType.I32, "token")
+    i.output(i.binary("xor", t, i.broadcast(i.scalar(3, DType.I32), (4,))), "o")
+    assert implied_numerics(i.finish()) == "exact"
+    f = Builder()
+    x = f.slot("x", (4, 8), DType.F32, "activation")
+    f.output(f.matmul(x, f.transpose(x, (1, 0)), "exact") + 1.0, "o")
+    assert implied_numerics(f.finish()) == "unfused"
+    assert prog.numerics == "narrowing" and prog.tolerance == TIER2_TOLERANCE["narrowing"] == 5e-3
