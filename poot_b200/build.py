@@ -13,7 +13,9 @@ full build takes well under a minute.  Objects are rebuilt only when a source or
 from __future__ import annotations
 
 import concurrent.futures as cf
+import json
 import os
+import re
 import shutil
 import subprocess
 import sys
@@ -56,6 +58,57 @@ def _run(cmd, verbose):
     return r.stdout + r.stderr
 
 
+_ENTRY = re.compile(r"Compiling entry function '([^']+)' for 'sm_100a'")
+_SPILL = re.compile(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads")
+_USED = re.compile(r"Used (\d+) registers(?:, used (\d+) barriers)?(?:, (\d+) bytes smem)?")
+
+
+def parse_ptxas_info(text: str) -> dict:
+    """``ptxas -v`` output of one translation unit -> ``{mangled entry: {registers, barriers, static_smem, stack,
+    spill_stores, spill_loads}}``.  The static shared memory is what the kernel declares; a kernel that takes dynamic
+    shared memory gets the rest from its launcher."""
+    out, cur = {}, None
+    for line in text.splitlines():
+        m = _ENTRY.search(line)
+        if m:
+            cur = out.setdefault(m.group(1), {"registers": 0, "barriers": 0, "static_smem": 0, "stack": 0, "spill_stores": 0, "spill_loads": 0})
+            continue
+        if cur is None:
+            continue
+        m = _SPILL.search(line)
+        if m:
+            cur["stack"], cur["spill_stores"], cur["spill_loads"] = (int(x) for x in m.groups())
+            continue
+        m = _USED.search(line)
+        if m:
+            cur["registers"], cur["barriers"], cur["static_smem"] = int(m.group(1)), int(m.group(2) or 0), int(m.group(3) or 0)
+            cur = None
+    return out
+
+
+def _demangle(names) -> dict:
+    names = list(names)
+    tool = shutil.which("c++filt")
+    if not tool or not names:
+        return {n: n for n in names}
+    r = subprocess.run([tool], input="\n".join(names), capture_output=True, text=True)
+    plain = r.stdout.splitlines()
+    return dict(zip(names, plain)) if r.returncode == 0 and len(plain) == len(names) else {n: n for n in names}
+
+
+def write_resource_table(obj_dir: Path, out: Path) -> dict:
+    """Merge the per-object resource records into the table ``plan/register_feedback.py`` reads: one row per kernel
+    entry with its source file, the readable signature and what ``ptxas`` reported for it."""
+    rows = {}
+    for rec in sorted(obj_dir.glob("*.res.json")):
+        for mangled, r in json.loads(rec.read_text()).items():
+            rows[mangled] = {"source": rec.name[:-len(".res.json")] + ".cu", **r}
+    plain = _demangle(rows)
+    table = {"arch": "sm_100a", "kernels": [{"entry": m, "signature": plain[m], **r} for m, r in sorted(rows.items())]}
+    out.write_text(json.dumps(table, indent=0))
+    return table
+
+
 def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool = False,
                   debug_bounds: bool = False) -> Path:
     """``debug_bounds``: the checked flavour (``-DPOOT_DEBUG_BOUNDS``: every data-dependent index is compared with its
@@ -76,14 +129,15 @@ def build_kernels(verbose: bool = False, force: bool = False, ptxas_info: bool =
         o = obj_dir / (s.stem + ".o")
         objs.append(o)
         if force or _newer(o, [s, *headers]):
-            cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", str(src_dir), "-c", str(s), "-o", str(o)]
-            if ptxas_info:
-                cmd[1:1] = ["-Xptxas", "-v"]
-            jobs.append(cmd)
+            jobs.append([nvcc, "-Xptxas", "-v", *NVCC_FLAGS, *extra, "-I", str(src_dir), "-c", str(s), "-o", str(o)])
     logs = []
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
             logs = list(ex.map(lambda c: _run(c, verbose), jobs))
+        for cmd, log in zip(jobs, logs):          # what the compiler reported per entry, kept beside the object
+            Path(cmd[-1]).with_suffix(".res.json").write_text(json.dumps(parse_ptxas_info(log)))
+    if not debug_bounds and (jobs or force or not (LIB_DIR / "kernel_resources.json").exists()):
+        write_resource_table(obj_dir, LIB_DIR / "kernel_resources.json")
     if jobs or force or _newer(out, objs):
         _run([nvcc, "-shared", "-o", str(out), *map(str, objs), "-cudart", "static",
               "-gencode", "arch=compute_100a,code=sm_100a"], verbose)

@@ -78,6 +78,8 @@ def value_ranges(g: Graph) -> Dict[int, Interval]:
             r[out] = (min(x[0] for x in ins), max(x[1] for x in ins))
         elif op == "iota":
             r[out] = (0, e.attrs["shape"][e.attrs["axis"]] - 1)
+        elif op == "reduce" and e.attrs.get("kind", "sum") == "max" and ins[0] is not None:
+            r[out] = ins[0]
         elif op in ("add", "sub", "mul", "max") and ins[0] is not None and ins[1] is not None:
             a, b = ins
             if op == "add":

@@ -90,6 +90,11 @@ def computed_constant(kind: str, params: tuple, shape, dtype: DType) -> np.ndarr
         ang = np.arange(positions, dtype=np.float64)[:, None] * inv[None, :]
         t = (np.cos(ang) if kind == "rope_cos" else np.sin(ang)) * att
         return np.concatenate([t, t], axis=1).astype(np.float32).reshape(shape)   # duplicated halves
+    if kind == "iota":                                     # a folded ``iota`` equation: counts along one axis
+        ax = params[0]
+        view = [1] * len(shape)
+        view[ax] = shape[ax]
+        return np.broadcast_to(np.arange(shape[ax], dtype=_np_dtype(dtype)).reshape(view), shape).copy()
     raise EvalError(f"unknown computed constant {kind!r}")
 
 

@@ -75,8 +75,8 @@ class Program:
         return total
 
 
-PIPELINE = ["canonicalize", "cse", "rope_fusion", "flash_attention", "form_selection", "form_recurrent_blocks", "dce", "recognize_packed",
-            "fold_dense_contractions", "fuse_contraction_epilogues", "fuse", "dce2"]
+PIPELINE = ["canonicalize", "cse", "rope_fusion", "flash_attention", "form_selection", "form_recurrent_blocks", "dce", "fold_iota",
+            "recognize_packed", "fold_dense_contractions", "lower_nonlast_reduces", "fuse_contraction_epilogues", "fuse", "dce2"]
 
 
 def run_passes(g: Graph, opt: CompileOptions, log: Dict[str, object], declines: list) -> Graph:
@@ -98,6 +98,12 @@ def run_passes(g: Graph, opt: CompileOptions, log: Dict[str, object], declines: 
             log[name] = form_recurrent_blocks(g, declines) if any(e.op == "scan" for e in g.eqns) else {}
         elif name in ("dce", "dce2"):
             log[name] = passes.dce(g)
+        elif name == "fold_iota":
+            from .prepare import fold_iota
+            log[name] = fold_iota(g)
+        elif name == "lower_nonlast_reduces":
+            from .prepare import lower_nonlast_reduces
+            log[name] = lower_nonlast_reduces(g)
         elif name == "recognize_packed":
             log[name] = passes.recognize_packed(g)
         elif name == "fold_dense_contractions":

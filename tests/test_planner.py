@@ -478,3 +478,79 @@ def test_state_commit_plan_and_numerics_class():
     f.output(f.matmul(x, f.transpose(x, (1, 0)), "exact") + 1.0, "o")
     assert implied_numerics(f.finish()) == "unfused"
     assert prog.numerics == "narrowing" and prog.tolerance == TIER2_TOLERANCE["narrowing"] == 5e-3
+
+
+def test_fold_iota_and_lower_nonlast_reduces_keep_every_value():
+    """An iota becomes a computed constant (equal ones share it, the index range stays known); a reduce over an inner
+    or leading axis becomes a reduce over the last axis of a transposed view with bit-identical results."""
+    from poot_b200.ir.analysis import value_ranges
+    from poot_b200.ir.builder import Builder
+    from poot_b200.plan.prepare import fold_iota, lower_nonlast_reduces
+    from poot_b200.tensor import DType
+    b = Builder()
+    x = b.slot("x", (3, 5, 7), DType.F32, "activation")
+    i0, i1 = b.iota((3, 5, 7), 1), b.iota((3, 5, 7), 1)
+    f = b.cast(i0 + i1, DType.F32) * x
+    b.output(f.sum(0), "lead")
+    b.output(f.max(1, keepdim=True), "mid")
+    b.output(f.sum(2), "last")
+    b.output(b.gather(b.slot("t", (5, 2), DType.F32, "activation"), i0.max(2)), "rows")
+    g = b.finish()
+    xs = {"x": np.random.default_rng(0).standard_normal((3, 5, 7)).astype(np.float32),
+          "t": np.random.default_rng(1).standard_normal((5, 2)).astype(np.float32)}
+    want = eval_graph(g, xs).outputs
+    h = g.copy()
+    assert fold_iota(h) == 2 and not any(e.op == "iota" for e in h.eqns)
+    assert sum(1 for i in h.inputs if i.storage == "computed" and i.computed[0] == "iota") == 1
+    idx = next(e for e in h.eqns if e.op == "gather").inputs[1]
+    assert value_ranges(h)[idx] == (0, 4)                                  # the gather's index is still proven in range
+    assert lower_nonlast_reduces(h) == 2
+    h.validate()
+    for e in h.eqns:
+        if e.op == "reduce":
+            assert e.attrs["axis"] % h.types[e.inputs[0]].rank == h.types[e.inputs[0]].rank - 1
+    got = eval_graph(h, xs).outputs
+    for k in want:
+        assert got[k].shape == want[k].shape and np.array_equal(got[k], want[k]), k
+    assert lower_nonlast_reduces(h) == 0 and fold_iota(h) == 0              # idempotent
+    prog = compile_graph(Model(_cfg()).trace(StepSpec(rows=1, tokens=3, capacity=16)))
+    assert not any(e.op == "iota" for e in prog.graph.eqns) and prog.log["fold_iota"] >= 1
+
+
+def test_register_feedback_reads_the_build_and_chooses_without_spills():
+    """The kernel build records what the assembler reported per entry; the table gives a verdict per instantiation, an
+    occupancy figure over one SM's limits, and picks the cheapest instantiation that does not spill."""
+    from poot_b200.build import parse_ptxas_info
+    from poot_b200.plan.register_feedback import ResourceTable, Verdict
+    text = """ptxas info    : Compiling entry function '_Z1aPf' for 'sm_100a'
+ptxas info    : Function properties for _Z1aPf
+    16 bytes stack frame, 8 bytes spill stores, 12 bytes spill loads
+ptxas info    : Used 128 registers, used 1 barriers, 4096 bytes smem, 400 bytes cmem[0]
+ptxas info    : Compiling entry function '_Z1bPf' for 'sm_100a'
+ptxas info    : Function properties for _Z1bPf
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Used 40 registers"""
+    rows = parse_ptxas_info(text)
+    assert rows["_Z1aPf"] == {"registers": 128, "barriers": 1, "static_smem": 4096, "stack": 16, "spill_stores": 8, "spill_loads": 12}
+    assert rows["_Z1bPf"]["registers"] == 40 and rows["_Z1bPf"]["static_smem"] == 0
+    t = ResourceTable([{"entry": k, "signature": f"void poot::fam<{i}>(float*)", "source": "x.cu", **v} for i, (k, v) in enumerate(rows.items())])
+    a, b_ = t.verdict("_Z1aPf"), t.verdict("_Z1bPf")
+    assert a.kernel == "fam" and a.template == "<0>" and a.spills and not b_.spills
+    assert a.resident_ctas(128) == 4 and b_.resident_ctas(128) == 12        # 65536 / (128 * 128) and / (40 * 128)
+    assert b_.resident_ctas(128, dynamic_smem=100 * 1024) == 2 and b_.resident_ctas(128, dynamic_smem=228 * 1024) == 0
+    assert b_.resident_ctas(1024) == 1 and a.resident_ctas(1024) == 0        # 128 registers x 1024 threads do not fit
+    c = t.choose(t.instantiations("fam"), threads=128)
+    assert c.verdict is b_ and "without spills" in c.reason and c.rejected[0][0] == "_Z1aPf"
+    only = t.choose([a], threads=128)
+    assert only.verdict is a and "every candidate spills" in only.reason
+    with pytest.raises(ValueError):
+        t.choose([a], threads=1024)
+    built = ResourceTable.load()
+    assert len(built.by_entry) > 300
+    flash = built.instantiations("attn_flash_prefill_kernel")
+    assert flash and not flash[0].spills                                       # the tensor-core kernels keep their operands in registers
+    for name in ("gemm_tiled_kernel", "rmsnorm_kernel", "gdn_scan_kernel", "ssd_scan_kernel", "moe_align_kernel"):
+        for v in built.instantiations(name):
+            assert not v.spills, (name, v.template, v.spill_bytes)
+    # the instantiations with local-memory traffic are known ones: a new name here is a regression to look at
+    assert {v.kernel for v in built.spilling()} <= {"q80_gemv_kernel", "attn_paged_kernel", "planar_gemv_rows_kernel", "gemm_skinny_quant_kernel"}
