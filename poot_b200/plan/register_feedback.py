@@ -100,6 +100,9 @@ class ResourceTable:
     @classmethod
     def load(cls, path: Optional[str] = None) -> "ResourceTable":
         p = Path(path) if path else Path(__file__).resolve().parent.parent / "lib" / "kernel_resources.json"
+        if not p.exists() and path is None:               # the table is a product of the kernel build
+            from ..build import build_kernels
+            build_kernels()
         if not p.exists():
             raise FileNotFoundError(f"{p.name} is written by the kernel build (python -m poot_b200.build)")
         return cls(json.loads(p.read_text())["kernels"])
