@@ -58,12 +58,27 @@ class ModelHandle:
         fam = model.cfg.family
         paired = fam in names.GGUF_PAIRED_QK
         bias_parts = {}
+        latent_parts = {}
+        cfg = model.cfg
         for n in store.names():
             c = names.canonical_from_gguf(n, fam)
             if c is None:
                 m = re.match(r"blk\.(\d+)\.ffn_(gate|up|down)_exps\.bias$", n)          # gpt-oss: one bias row per expert
                 if m:
                     bias_parts.setdefault(int(m.group(1)), {})[m.group(2)] = store[n].to_f32()
+                m = re.match(r"blk\.(\d+)\.(attn_qkv)\.(weight|bias)$", n)
+                if m and m.group(2) + "." + m.group(3) in names.GGUF_FUSED_QKV:          # q rows | k rows | v rows
+                    from ..load.hf_map import f32_weight
+                    p, w = f"layers.{m.group(1)}.", store[n]
+                    nq, nk = cfg.n_heads * cfg.head_dim, cfg.n_kv_heads * cfg.head_dim
+                    if w.shape[0] != nq + 2 * nk:
+                        raise KeyError(f"{n}: {w.shape[0]} rows, expected {nq} + 2 x {nk}")
+                    suffix = "" if m.group(3) == "weight" else "_bias"
+                    for role, lo, cnt in (("attn_q", 0, nq), ("attn_k", nq, nk), ("attn_v", nq + nk, nk)):
+                        canon[p + role + suffix] = w.rows(lo, cnt) if suffix == "" else f32_weight(p + role + suffix, w.to_f32()[lo:lo + cnt])
+                m = re.match(r"blk\.(\d+)\.attn_(k|v)_b\.weight$", n)                    # the latent up-projection stored per head
+                if m and fam == "deepseek2":
+                    latent_parts.setdefault(int(m.group(1)), {})[m.group(2)] = store[n].to_f32()
                 continue
             w = store[n]
             if paired and c.endswith(("attn_q", "attn_k")) and len(w.shape) == 2:
@@ -76,6 +91,18 @@ class ModelHandle:
                 raise KeyError(f"blk.{l}: expert biases without {sorted({'gate', 'up', 'down'} - set(parts))}")
             canon[f"layers.{l}.experts_in_bias"] = f32_weight(f"layers.{l}.experts_in_bias", np.concatenate([parts["gate"], parts["up"]], 1))
             canon[f"layers.{l}.experts_out_bias"] = f32_weight(f"layers.{l}.experts_out_bias", parts["down"])
+        for l, parts in latent_parts.items():
+            # ``attn_k_b`` [heads, latent, nope] and ``attn_v_b`` [heads, value, latent] are the two halves of each head's
+            # rows of the up-projection the tracer reads as one matrix: nope rows (the key half transposed back), then value rows
+            from ..load.hf_map import f32_weight
+            if set(parts) != {"k", "v"}:
+                raise KeyError(f"blk.{l}: attn_k_b and attn_v_b come as a pair")
+            k_b = parts["k"].reshape(cfg.n_heads, cfg.kv_lora_rank, cfg.qk_nope_dim).transpose(0, 2, 1)
+            v_b = parts["v"].reshape(cfg.n_heads, cfg.v_head_dim, cfg.kv_lora_rank)
+            canon[f"layers.{l}.attn_kv_b"] = f32_weight(f"layers.{l}.attn_kv_b", np.concatenate([k_b, v_b], 1).reshape(-1, cfg.kv_lora_rank))
+        if fam == "deepseek2" and cfg.rope_interleaved:
+            from ..load.hf_map import _mla_halfsplit
+            _mla_halfsplit(cfg, canon)                         # the converter keeps the rotary pairs interleaved, like the source checkpoint
         if "lm_head" not in canon and "embed" in canon:
             model.cfg.tie_embeddings = True
         return ModelHandle(model, store, canon, path, "gguf", None)

@@ -247,6 +247,16 @@ def hf_header_from_gguf(arch: str, meta: Dict[str, Any], family: str) -> Dict[st
     H, nh = int(g("embedding_length")), int(g("attention.head_count"))
     L = int(g("block_count"))
     tokens = meta.get("tokenizer.ggml.tokens")
+    vocab = int(g("vocab_size", len(tokens) if tokens is not None else 0))
+    ids = {"bos_token_id": meta.get("tokenizer.ggml.bos_token_id"), "eos_token_id": meta.get("tokenizer.ggml.eos_token_id")}
+    if family == "mpt":                                  # the LayerNorm families keep their own header spelling
+        return {"d_model": H, "n_heads": nh, "n_layers": L, "vocab_size": vocab, "max_seq_len": int(g("context_length", 2048)),
+                "layer_norm_epsilon": float(g("attention.layer_norm_epsilon", 1e-5)), "expansion_ratio": int(one(g("feed_forward_length", 4 * H))) / H,
+                "no_bias": True, "attn_config": {"alibi": float(g("attention.max_alibi_bias", 8.0)) > 0.0, "alibi_bias_max": float(g("attention.max_alibi_bias", 8.0)),
+                                                 "clip_qkv": g("attention.clamp_kqv")}, **ids}
+    if family == "bloom":
+        return {"hidden_size": H, "n_head": nh, "n_layer": L, "vocab_size": vocab, "seq_length": int(g("context_length", 2048)),
+                "layer_norm_epsilon": float(g("attention.layer_norm_epsilon", 1e-5)), **ids}
     h: Dict[str, Any] = {
         "hidden_size": H, "num_hidden_layers": L, "num_attention_heads": nh,
         "num_key_value_heads": int(one(g("attention.head_count_kv", nh))), "head_dim": int(g("attention.key_length", H // nh)),
@@ -275,6 +285,28 @@ def hf_header_from_gguf(arch: str, meta: Dict[str, Any], family: str) -> Dict[st
                   "logits_scaling": float(g("logit_scale", 1.0)), "attention_multiplier": g("attention.scale")})
     elif family == "smollm3":
         h["no_rope_layers"] = [int((l + 1) % 4 != 0) for l in range(L)]
+    elif family == "minimax_m2":
+        rot = int(g("rope.dimension_count", h["head_dim"]))
+        if rot != h["head_dim"]:
+            h["partial_rotary_factor"] = rot / h["head_dim"]
+        if int(g("expert_gating_func", 2)) != 2:
+            raise ValueError(f"{arch}.expert_gating_func {g('expert_gating_func')}: this family's router is the sigmoid one (2)")
+    elif family == "deepseek2":
+        # converters that store the absorbed form describe the one shared latent head in ``key_length`` / ``value_length``
+        # and the per-head widths in the ``_mla`` keys; older files have the per-head widths in the plain keys
+        rope = int(g("rope.dimension_count"))
+        key = int(g("attention.key_length_mla", g("attention.key_length")))
+        if int(g("expert_gating_func", 1)) != 1:
+            raise ValueError(f"{arch}.expert_gating_func {g('expert_gating_func')}: DeepSeek-V2 routes by softmax (1)")
+        h.update({"q_lora_rank": int(g("attention.q_lora_rank", 0) or 0) or None, "kv_lora_rank": int(g("attention.kv_lora_rank")),
+                  "qk_rope_head_dim": rope, "qk_nope_head_dim": key - rope, "head_dim": key,
+                  "v_head_dim": int(g("attention.value_length_mla", g("attention.value_length"))), "num_key_value_heads": nh,
+                  "n_routed_experts": int(g("expert_count", 0) or 0), "num_experts_per_tok": int(g("expert_used_count", 0) or 0),
+                  "moe_intermediate_size": int(g("expert_feed_forward_length", 0) or 0), "n_shared_experts": int(g("expert_shared_count", 0) or 0),
+                  "first_k_dense_replace": int(g("leading_dense_block_count", 0) or 0), "routed_scaling_factor": float(g("expert_weights_scale", 1.0)),
+                  "norm_topk_prob": bool(g("expert_weights_norm", False)), "topk_method": "greedy"})
+        h.pop("num_local_experts", None)
+        h["intermediate_size"] = int(one(g("feed_forward_length", 4 * H)))
     return h
 
 

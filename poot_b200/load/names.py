@@ -66,12 +66,28 @@ GGUF_FAMILY_LAYER = {
     "gemma3": {"post_attention_norm.weight": "attn_post_norm", "post_ffw_norm.weight": "ffn_post_norm"},
     "gpt_oss": {"post_attention_norm.weight": "ffn_norm", "attn_sinks.weight": "attn_sinks", "attn_output.bias": "attn_o_bias",
                 "ffn_gate_inp.bias": "ffn_router_bias"},
+    "bloom": {"attn_norm.bias": "attn_norm_bias", "ffn_norm.bias": "ffn_norm_bias", "attn_output.bias": "attn_o_bias",
+              "ffn_up.bias": "ffn_up_bias", "ffn_down.bias": "ffn_down_bias"},
+    "minimax_m2": {"exp_probs_b.bias": "ffn_router_select_bias"},
+    "deepseek2": {"attn_q_a.weight": "attn_q_a", "attn_q_a_norm.weight": "attn_q_a_norm", "attn_q_b.weight": "attn_q_b",
+                  "attn_kv_a_mqa.weight": "attn_kv_a", "attn_kv_a_norm.weight": "attn_kv_a_norm", "attn_kv_b.weight": "attn_kv_b",
+                  "ffn_gate_shexp.weight": "shared_gate", "ffn_up_shexp.weight": "shared_up", "ffn_down_shexp.weight": "shared_down",
+                  "exp_probs_b.bias": "ffn_router_select_bias"},
 }
+# top-level rows of one family: BLOOM norms the embedding and its norms carry biases
+GGUF_FAMILY_TOP = {
+    "bloom": {"token_embd_norm.weight": "embed_norm", "token_embd_norm.bias": "embed_norm_bias", "output_norm.bias": "final_norm_bias"},
+}
+# fused rows a converter writes as one tensor: ``attn_qkv`` is q rows, then k rows, then v rows (llama.cpp regroups BLOOM's
+# per-head interleaving into these thirds when it converts)
+GGUF_FUSED_QKV = ("attn_qkv.weight", "attn_qkv.bias")
 # families whose converter permutes Q / K rows for interleaved rotary pairs, read back half-split
 GGUF_PAIRED_QK = ("llama", "mixtral", "smollm3")
 
 
 def canonical_from_gguf(name: str, family: Optional[str] = None) -> Optional[str]:
+    if name in GGUF_FAMILY_TOP.get(family or "", {}):
+        return GGUF_FAMILY_TOP[family][name]
     if name in GGUF_TOP:
         return GGUF_TOP[name]
     m = re.match(r"blk\.(\d+)\.([^#]+)(?:#(\d+))?$", name)

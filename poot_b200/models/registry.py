@@ -649,9 +649,10 @@ SHIPPED: List[FamilyEntry] = [
 
 
 # families whose GGUF metadata and tensor names the generic llama-style reader covers completely
-GGUF_FAMILIES = ("llama", "qwen2", "qwen3", "qwen3moe", "phi3", "olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss")
+GGUF_FAMILIES = ("llama", "qwen2", "qwen3", "qwen3moe", "phi3", "olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss",
+                 "mpt", "bloom", "minimax_m2", "deepseek2")
 # of those, the ones whose configuration is read by the family's own header table from a header rebuilt out of the GGUF keys
-GGUF_VIA_HEADER = ("olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss")
+GGUF_VIA_HEADER = ("olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss", "mpt", "bloom", "minimax_m2", "deepseek2")
 
 
 class Registry:

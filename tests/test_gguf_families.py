@@ -128,6 +128,187 @@ def _to_gguf(path, family, m, quantise=None):
 FAMILY_CASES = ["olmo2", "olmoe", "smollm3", "granite", "granitemoe", "gemma2", "gemma3", "gpt_oss"]
 
 
+def _put_all(path, meta, rows):
+    gguf.write_gguf(path, meta, [_f32(n, a) for n, a in rows])
+
+
+def _mpt_to_gguf(path, m):
+    c = m.config
+    meta = {"general.architecture": "mpt", "mpt.block_count": c.n_layers, "mpt.embedding_length": c.d_model, "mpt.attention.head_count": c.n_heads,
+            "mpt.feed_forward_length": 4 * c.d_model, "mpt.attention.layer_norm_epsilon": float(c.layer_norm_epsilon),
+            "mpt.attention.max_alibi_bias": float(c.attn_config.alibi_bias_max), "mpt.context_length": c.max_seq_len, "mpt.vocab_size": c.vocab_size}
+    table = {"norm_1.weight": "attn_norm.weight", "norm_2.weight": "ffn_norm.weight", "attn.Wqkv.weight": "attn_qkv.weight",
+             "attn.out_proj.weight": "attn_output.weight", "ffn.up_proj.weight": "ffn_up.weight", "ffn.down_proj.weight": "ffn_down.weight"}
+    rows = []
+    for k, v in m.state_dict().items():
+        a = v.detach().float().numpy()
+        mm = re.match(r"transformer\.blocks\.(\d+)\.(.+)$", k)
+        if k == "transformer.wte.weight":
+            rows.append(("token_embd.weight", a))
+        elif k == "transformer.norm_f.weight":
+            rows.append(("output_norm.weight", a))
+        elif mm:
+            rows.append((f"blk.{mm.group(1)}.{table[mm.group(2)]}", a))
+    _put_all(path, meta, rows)
+
+
+def _bloom_to_gguf(path, m):
+    c = m.config
+    nh, H = c.n_head, c.hidden_size
+    meta = {"general.architecture": "bloom", "bloom.block_count": c.n_layer, "bloom.embedding_length": H, "bloom.attention.head_count": nh,
+            "bloom.feed_forward_length": 4 * H, "bloom.attention.layer_norm_epsilon": float(c.layer_norm_epsilon), "bloom.vocab_size": c.vocab_size}
+    table = {"input_layernorm": "attn_norm", "post_attention_layernorm": "ffn_norm", "self_attention.dense": "attn_output",
+             "mlp.dense_h_to_4h": "ffn_up", "mlp.dense_4h_to_h": "ffn_down", "self_attention.query_key_value": "attn_qkv"}
+    top = {"transformer.word_embeddings.weight": "token_embd.weight", "transformer.word_embeddings_layernorm.weight": "token_embd_norm.weight",
+           "transformer.word_embeddings_layernorm.bias": "token_embd_norm.bias", "transformer.ln_f.weight": "output_norm.weight",
+           "transformer.ln_f.bias": "output_norm.bias"}
+    rows = []
+    for k, v in m.state_dict().items():
+        a = v.detach().float().numpy()
+        mm = re.match(r"transformer\.h\.(\d+)\.(.+)\.(weight|bias)$", k)
+        if k in top:
+            rows.append((top[k], a))
+        elif mm:
+            if mm.group(2) == "self_attention.query_key_value":      # the converter regroups [head][q | k | v] rows into thirds
+                a = a.reshape(nh, 3, H // nh, -1) if a.ndim == 2 else a.reshape(nh, 3, H // nh)
+                a = np.concatenate([a[:, i].reshape((H, -1) if a.ndim == 4 else (H,)) for i in range(3)], 0)
+            rows.append((f"blk.{mm.group(1)}.{table[mm.group(2)]}.{mm.group(3)}", a))
+    _put_all(path, meta, rows)
+
+
+def _minimax_to_gguf(path, m):
+    c = m.config
+    arch = "minimax-m2"
+    meta = {"general.architecture": arch, f"{arch}.block_count": c.num_hidden_layers, f"{arch}.embedding_length": c.hidden_size,
+            f"{arch}.attention.head_count": c.num_attention_heads, f"{arch}.attention.head_count_kv": c.num_key_value_heads,
+            f"{arch}.attention.key_length": c.head_dim, f"{arch}.feed_forward_length": c.intermediate_size,
+            f"{arch}.expert_feed_forward_length": c.intermediate_size, f"{arch}.expert_count": c.num_local_experts,
+            f"{arch}.expert_used_count": c.num_experts_per_tok, f"{arch}.expert_gating_func": 2,
+            f"{arch}.rope.dimension_count": int(getattr(c, "rotary_dim", None) or c.head_dim),
+            f"{arch}.rope.freq_base": float(c.rope_parameters["rope_theta"]), f"{arch}.attention.layer_norm_rms_epsilon": float(c.rms_norm_eps),
+            f"{arch}.context_length": c.max_position_embeddings, f"{arch}.vocab_size": c.vocab_size}
+    table = {**LAYER, "block_sparse_moe.gate.weight": "ffn_gate_inp.weight", "block_sparse_moe.e_score_correction_bias": "exp_probs_b.bias",
+             "mlp.gate.weight": "ffn_gate_inp.weight", "mlp.e_score_correction_bias": "exp_probs_b.bias"}
+    rows, stacks = [], {}
+    for k, v in m.state_dict().items():
+        a = v.detach().float().numpy()
+        mm = re.match(r"model\.layers\.(\d+)\.(.+)$", k)
+        if k == "model.embed_tokens.weight":
+            rows.append(("token_embd.weight", a))
+        elif k == "model.norm.weight":
+            rows.append(("output_norm.weight", a))
+        elif k == "lm_head.weight":
+            rows.append(("output.weight", a))
+        elif mm and mm.group(2) in table:
+            rows.append((f"blk.{mm.group(1)}.{table[mm.group(2)]}", a))
+        elif mm:
+            e = re.match(r"(?:block_sparse_moe|mlp)\.experts\.(\d+)\.(w1|w2|w3|gate_proj|up_proj|down_proj)\.weight$", mm.group(2))
+            if e:
+                role = {"w1": "gate", "w3": "up", "w2": "down", "gate_proj": "gate", "up_proj": "up", "down_proj": "down"}[e.group(2)]
+                stacks.setdefault((mm.group(1), role), {})[int(e.group(1))] = a
+            elif mm.group(2).endswith("experts.gate_up_proj"):
+                F = a.shape[1] // 2
+                rows += [(f"blk.{mm.group(1)}.ffn_gate_exps.weight", a[:, :F]), (f"blk.{mm.group(1)}.ffn_up_exps.weight", a[:, F:])]
+            elif mm.group(2).endswith("experts.down_proj"):
+                rows.append((f"blk.{mm.group(1)}.ffn_down_exps.weight", a))
+            else:
+                raise AssertionError(f"unmapped tensor {k}")
+    for (l, role), parts in stacks.items():
+        rows.append((f"blk.{l}.ffn_{role}_exps.weight", np.stack([parts[i] for i in sorted(parts)])))
+    _put_all(path, meta, rows)
+
+
+def _deepseek2_to_gguf(path, m, split_kv_b):
+    c = m.config
+    arch = "deepseek2"
+    nh, dn, dr, dv, r = c.num_attention_heads, c.qk_nope_head_dim, c.qk_rope_head_dim, c.v_head_dim, c.kv_lora_rank
+    meta = {"general.architecture": arch, f"{arch}.block_count": c.num_hidden_layers, f"{arch}.embedding_length": c.hidden_size,
+            f"{arch}.attention.head_count": nh, f"{arch}.attention.head_count_kv": 1 if split_kv_b else nh,
+            f"{arch}.feed_forward_length": c.intermediate_size, f"{arch}.expert_feed_forward_length": c.moe_intermediate_size,
+            f"{arch}.expert_count": c.n_routed_experts, f"{arch}.expert_used_count": c.num_experts_per_tok,
+            f"{arch}.expert_shared_count": c.n_shared_experts, f"{arch}.leading_dense_block_count": c.first_k_dense_replace,
+            f"{arch}.expert_weights_scale": float(c.routed_scaling_factor), f"{arch}.expert_weights_norm": bool(c.norm_topk_prob),
+            f"{arch}.expert_gating_func": 1, f"{arch}.attention.kv_lora_rank": r, f"{arch}.rope.dimension_count": dr,
+            f"{arch}.rope.freq_base": float(c.rope_parameters["rope_theta"]), f"{arch}.attention.layer_norm_rms_epsilon": float(c.rms_norm_eps),
+            f"{arch}.context_length": c.max_position_embeddings, f"{arch}.vocab_size": c.vocab_size}
+    if split_kv_b:      # the absorbed form: the plain keys describe the one latent head, the ``_mla`` keys the per-head widths
+        meta.update({f"{arch}.attention.key_length": r + dr, f"{arch}.attention.value_length": r,
+                     f"{arch}.attention.key_length_mla": dn + dr, f"{arch}.attention.value_length_mla": dv})
+    else:
+        meta.update({f"{arch}.attention.key_length": dn + dr, f"{arch}.attention.value_length": dv})
+    if c.q_lora_rank:
+        meta[f"{arch}.attention.q_lora_rank"] = c.q_lora_rank
+    table = {"input_layernorm.weight": "attn_norm.weight", "post_attention_layernorm.weight": "ffn_norm.weight",
+             "self_attn.q_proj.weight": "attn_q.weight", "self_attn.q_a_proj.weight": "attn_q_a.weight",
+             "self_attn.q_a_layernorm.weight": "attn_q_a_norm.weight", "self_attn.q_b_proj.weight": "attn_q_b.weight",
+             "self_attn.kv_a_proj_with_mqa.weight": "attn_kv_a_mqa.weight", "self_attn.kv_a_layernorm.weight": "attn_kv_a_norm.weight",
+             "self_attn.o_proj.weight": "attn_output.weight", "mlp.gate_proj.weight": "ffn_gate.weight", "mlp.up_proj.weight": "ffn_up.weight",
+             "mlp.down_proj.weight": "ffn_down.weight", "mlp.gate.weight": "ffn_gate_inp.weight",
+             "mlp.shared_experts.gate_proj.weight": "ffn_gate_shexp.weight", "mlp.shared_experts.up_proj.weight": "ffn_up_shexp.weight",
+             "mlp.shared_experts.down_proj.weight": "ffn_down_shexp.weight"}
+    rows, stacks = [], {}
+    for k, v in m.state_dict().items():
+        a = v.detach().float().numpy()
+        mm = re.match(r"model\.layers\.(\d+)\.(.+)$", k)
+        if k == "model.embed_tokens.weight":
+            rows.append(("token_embd.weight", a))
+        elif k == "model.norm.weight":
+            rows.append(("output_norm.weight", a))
+        elif k == "lm_head.weight":
+            rows.append(("output.weight", a))
+        elif mm and mm.group(2) in table:
+            rows.append((f"blk.{mm.group(1)}.{table[mm.group(2)]}", a))
+        elif mm and mm.group(2) == "self_attn.kv_b_proj.weight":
+            if split_kv_b:
+                kv = a.reshape(nh, dn + dv, r)
+                rows += [(f"blk.{mm.group(1)}.attn_k_b.weight", np.ascontiguousarray(kv[:, :dn].transpose(0, 2, 1))),
+                         (f"blk.{mm.group(1)}.attn_v_b.weight", np.ascontiguousarray(kv[:, dn:]))]
+            else:
+                rows.append((f"blk.{mm.group(1)}.attn_kv_b.weight", a))
+        elif mm:
+            e = re.match(r"mlp\.experts\.(\d+)\.(gate|up|down)_proj\.weight$", mm.group(2))
+            if e:
+                stacks.setdefault((mm.group(1), e.group(2)), {})[int(e.group(1))] = a
+            elif mm.group(2) == "mlp.experts.gate_up_proj":
+                F = a.shape[1] // 2
+                rows += [(f"blk.{mm.group(1)}.ffn_gate_exps.weight", a[:, :F]), (f"blk.{mm.group(1)}.ffn_up_exps.weight", a[:, F:])]
+            elif mm.group(2) == "mlp.experts.down_proj":
+                rows.append((f"blk.{mm.group(1)}.ffn_down_exps.weight", a))
+            else:
+                raise AssertionError(f"unmapped tensor {k}")
+    for (l, role), parts in stacks.items():
+        rows.append((f"blk.{l}.ffn_{role}_exps.weight", np.stack([parts[i] for i in sorted(parts)])))
+    _put_all(path, meta, rows)
+
+
+@pytest.mark.parametrize("family", ["mpt", "bloom", "minimax_m2", "deepseek2", "deepseek2-absorbed"])
+def test_gguf_of_the_families_with_their_own_layouts(family, tmp_path):
+    """MPT and BLOOM (LayerNorm stacks with a fused ``attn_qkv``, BLOOM's regrouped into thirds by the converter and with
+    biases everywhere), MiniMax-M2 (sigmoid router with ``exp_probs_b``, partial rotary) and DeepSeek-V2 (latent attention
+    rows; the up-projection stored whole or, in the absorbed form, as ``attn_k_b`` / ``attn_v_b`` per head)."""
+    name = family.split("-")[0]
+    m, vocab = build(CASES[name])
+    toks = torch.randint(0, vocab, (1, 12), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = m(toks).logits[0].numpy()
+    path = str(tmp_path / f"{family}.gguf")
+    if name == "mpt":
+        _mpt_to_gguf(path, m)
+    elif name == "bloom":
+        _bloom_to_gguf(path, m)
+    elif name == "minimax_m2":
+        _minimax_to_gguf(path, m)
+    else:
+        _deepseek2_to_gguf(path, m, split_kv_b=family.endswith("absorbed"))
+    h = ModelHandle.load(path)
+    assert h.cfg.family == name and h.kind == "gguf"
+    sess = OracleSession(h.model, h.oracle_weights(), capacity=32)
+    sess._graph = lambda T, embeds=False: h.model.trace(StepSpec(rows=1, tokens=T, capacity=32, logit_rows="all"))
+    got = sess.step(toks.numpy()).reshape(ref.shape)
+    err = np.abs(got - ref).max() / np.abs(ref).max()
+    assert err < 2e-5, err
+
+
 @pytest.mark.parametrize("family", FAMILY_CASES)
 def test_gguf_of_the_family_equals_the_hugging_face_forward(family, tmp_path):
     case = dict(CASES["smollm3-nope-layer" if family == "smollm3" else family])
