@@ -53,14 +53,41 @@ class ModelHandle:
             return ModelHandle(model, store, canon, path, "hf", path)
         store = gguf.read_gguf(path)
         arch = store.metadata.get("general.architecture")
-        model = registry.resolve_gguf(arch, store.metadata)
+        meta = store.metadata
+        if arch == "gemma4":
+            # what this family's header leaves to the tensor list: the global layers' rotary tail is NoPE where
+            # ``rope_freqs.weight`` divides a frequency away, a global layer without ``attn_v`` reads its value from the
+            # key projection, and ``output.weight`` is there only when the head is not the embedding
+            meta = dict(meta)
+            have = set(store.names())
+            if "rope_freqs.weight" in have:
+                f = store["rope_freqs.weight"].to_f32()
+                meta["tensors.rope_proportion"] = float((f == 1.0).sum()) / max(1, f.size)
+            local = [bool(x) for x in meta.get("gemma4.attention.sliding_window_pattern", [])]
+            meta["tensors.value_is_key"] = any(not loc and f"blk.{l}.attn_v.weight" not in have for l, loc in enumerate(local))
+            meta["tensors.has_output"] = "output.weight" in have
+        model = registry.resolve_gguf(arch, meta)
         canon = {}
+        stacked = {}
         fam = model.cfg.family
         paired = fam in names.GGUF_PAIRED_QK
         bias_parts = {}
         latent_parts = {}
         cfg = model.cfg
         for n in store.names():
+            m = re.match(r"blk\.(\d+)\.(.+)$", n)
+            if m and int(m.group(1)) >= cfg.n_layers:
+                continue                                       # blocks a converter appends after the stack (multi-token prediction)
+            x = re.match(r"blk\.(\d+)\.ffn_(gate_up|down)_exps\.weight#(\d+)$", n)
+            if x and fam == "gemma4":                          # this tracer reads the experts as the stacks the file holds
+                stacked.setdefault((int(x.group(1)), "experts_in" if x.group(2) == "gate_up" else "experts_out"), {})[int(x.group(3))] = store[n].to_f32()
+                continue
+            if n == "rope_freqs.weight":
+                continue
+            if m and fam == "qwen38_27b":
+                from ..load.hf_map import qwen35_gguf_tensor
+                if qwen35_gguf_tensor(cfg, f"layers.{m.group(1)}.", m.group(2), store[n], canon):
+                    continue
             c = names.canonical_from_gguf(n, fam)
             if c is None:
                 m = re.match(r"blk\.(\d+)\.ffn_(gate|up|down)_exps\.bias$", n)          # gpt-oss: one bias row per expert
@@ -91,6 +118,14 @@ class ModelHandle:
                 raise KeyError(f"blk.{l}: expert biases without {sorted({'gate', 'up', 'down'} - set(parts))}")
             canon[f"layers.{l}.experts_in_bias"] = f32_weight(f"layers.{l}.experts_in_bias", np.concatenate([parts["gate"], parts["up"]], 1))
             canon[f"layers.{l}.experts_out_bias"] = f32_weight(f"layers.{l}.experts_out_bias", parts["down"])
+        for (l, role), parts in stacked.items():
+            from ..load.hf_map import f32_weight
+            canon[f"layers.{l}.{role}"] = f32_weight(f"layers.{l}.{role}", np.stack([parts[e] for e in sorted(parts)]))
+        if fam == "gemma4":
+            for l in range(cfg.n_layers):                      # K/V of a layer that reads another layer's cache are stored and unused
+                for role in ("attn_k", "attn_v", "attn_k_norm"):
+                    if cfg.kv_source(l) is not None or (role == "attn_v" and cfg.value_is_key(l)):
+                        canon.pop(f"layers.{l}.{role}", None)
         for l, parts in latent_parts.items():
             # ``attn_k_b`` [heads, latent, nope] and ``attn_v_b`` [heads, value, latent] are the two halves of each head's
             # rows of the up-projection the tracer reads as one matrix: nope rows (the key half transposed back), then value rows

@@ -201,6 +201,8 @@ def _put_value(out: bytearray, v) -> None:
             out += struct.pack("<IQ", 8, len(v))
             for s in v:
                 _put_string(out, s)
+        elif v and isinstance(v[0], (bool, np.bool_)):
+            out += struct.pack("<IQ", 7, len(v)) + struct.pack(f"<{len(v)}?", *[bool(x) for x in v])
         elif v and isinstance(v[0], float):
             out += struct.pack("<IQ", 6, len(v)) + struct.pack(f"<{len(v)}f", *v)
         else:
@@ -254,6 +256,26 @@ def hf_header_from_gguf(arch: str, meta: Dict[str, Any], family: str) -> Dict[st
                 "layer_norm_epsilon": float(g("attention.layer_norm_epsilon", 1e-5)), "expansion_ratio": int(one(g("feed_forward_length", 4 * H))) / H,
                 "no_bias": True, "attn_config": {"alibi": float(g("attention.max_alibi_bias", 8.0)) > 0.0, "alibi_bias_max": float(g("attention.max_alibi_bias", 8.0)),
                                                  "clip_qkv": g("attention.clamp_kqv")}, **ids}
+    if family == "gemma4":
+        # per-layer facts come as arrays: which layers slide, and the K/V head count of each (local and global layers differ);
+        # ``tensors.*`` are facts read off the tensor list by the loader (a GGUF header does not state them)
+        local = [bool(x) for x in g("attention.sliding_window_pattern")]
+        kv = [int(x) for x in np.atleast_1d(g("attention.head_count_kv"))]
+        kv = kv * L if len(kv) == 1 else kv
+        kv_local = [n for n, loc in zip(kv, local) if loc] or kv
+        kv_global = [n for n, loc in zip(kv, local) if not loc]
+        experts = int(g("expert_count", 0) or 0)
+        return {"hidden_size": H, "num_hidden_layers": L, "num_attention_heads": nh, "num_key_value_heads": kv_local[0],
+                "num_global_key_value_heads": kv_global[0] if kv_global else 0, "head_dim": int(g("attention.key_length_swa", g("attention.key_length"))),
+                "global_head_dim": int(g("attention.key_length")), "intermediate_size": int(one(g("feed_forward_length"))), "vocab_size": vocab,
+                "rms_norm_eps": float(g("attention.layer_norm_rms_epsilon", 1e-6)), "max_position_embeddings": int(g("context_length", 131072)),
+                "layer_types": ["sliding_attention" if loc else "full_attention" for loc in local], "sliding_window": int(g("attention.sliding_window", 0) or 0),
+                "rope_parameters": {"full_attention": {"rope_type": "proportional", "rope_theta": float(g("rope.freq_base", 1e6)),
+                                                       "partial_rotary_factor": float(meta.get("tensors.rope_proportion", 1.0))},
+                                    "sliding_attention": {"rope_type": "default", "rope_theta": float(g("rope.freq_base_swa", 10000.0))}},
+                "final_logit_softcapping": g("final_logit_softcapping"), "attention_k_eq_v": bool(meta.get("tensors.value_is_key", False)),
+                "tie_word_embeddings": not meta.get("tensors.has_output", False), "enable_moe_block": experts > 0, "num_experts": experts,
+                "top_k_experts": int(g("expert_used_count", 0) or 0), "moe_intermediate_size": int(g("expert_feed_forward_length", 0) or 0), **ids}
     if family == "bloom":
         return {"hidden_size": H, "n_head": nh, "n_layer": L, "vocab_size": vocab, "seq_length": int(g("context_length", 2048)),
                 "layer_norm_epsilon": float(g("attention.layer_norm_epsilon", 1e-5)), **ids}
@@ -285,6 +307,18 @@ def hf_header_from_gguf(arch: str, meta: Dict[str, Any], family: str) -> Dict[st
                   "logits_scaling": float(g("logit_scale", 1.0)), "attention_multiplier": g("attention.scale")})
     elif family == "smollm3":
         h["no_rope_layers"] = [int((l + 1) % 4 != 0) for l in range(L)]
+    elif family == "qwen38_27b":
+        # the multi-token-prediction blocks a converter appends count in ``block_count`` and are not part of the stack
+        nextn = int(g("nextn_predict_layers", 0) or 0)
+        if nextn >= L:
+            raise ValueError(f"{arch}.nextn_predict_layers {nextn} leaves no block of {L} for the stack")
+        rot = int(g("rope.dimension_count", h["head_dim"]))
+        h.update({"num_hidden_layers": L - nextn, "linear_num_key_heads": int(g("ssm.group_count")), "linear_num_value_heads": int(g("ssm.time_step_rank")),
+                  "linear_key_head_dim": int(g("ssm.state_size")), "linear_value_head_dim": int(g("ssm.state_size")),
+                  "linear_conv_kernel_dim": int(g("ssm.conv_kernel", 4)), "full_attention_interval": int(g("full_attention_interval", 4)),
+                  "partial_rotary_factor": rot / h["head_dim"]})
+        if int(g("ssm.inner_size", h["linear_num_value_heads"] * h["linear_key_head_dim"])) != h["linear_num_value_heads"] * h["linear_key_head_dim"]:
+            raise ValueError(f"{arch}.ssm.inner_size is not value heads x head width")
     elif family == "minimax_m2":
         rot = int(g("rope.dimension_count", h["head_dim"]))
         if rot != h["head_dim"]:

@@ -380,6 +380,56 @@ def _qwen3next_tensor(cfg: DecoderConfig, p: str, rest: str, w: PackedWeight, ca
     return False
 
 
+def qwen35_gguf_tensor(cfg: DecoderConfig, p: str, rest: str, w: PackedWeight, canon: Dict[str, PackedWeight]) -> bool:
+    """llama.cpp's spelling of a Qwen3.5 layer (``general.architecture = qwen35``; crates/poot-models/src/architectures/
+    qwen38_27b.rs:19-23): one tensor per delta-net quantity (``attn_qkv`` = q | k | v rows, ``attn_gate`` = z, ``ssm_beta``,
+    ``ssm_alpha``), the value heads tiled over the key heads instead of grouped, ``ssm_a`` already ``-exp(A_log)``, the conv
+    kernel as ``[channels, taps]``; the attention layers' ``attn_q`` carries ``[head][query | gate]`` rows as the source does."""
+    from .names import gdn_grouped_heads
+    nk, nv, Dg, D = cfg.gdn_k_heads, cfg.gdn_v_heads, cfg.gdn_head_dim, cfg.head_dim
+    kd = nk * Dg
+    grouped = gdn_grouped_heads(nv, nk) if nk else None
+
+    def untile(a: np.ndarray, block: int) -> np.ndarray:
+        """Rows of ``a`` in runs of ``block`` per value head, put back from tiled to grouped order."""
+        t = a.reshape(nv, block, -1)
+        out = np.empty_like(t)
+        out[grouped] = t
+        return out.reshape(a.shape)
+
+    if rest == "attn_q.weight" and w.shape[0] == 2 * cfg.n_heads * D:
+        a = w.to_f32().reshape(cfg.n_heads, 2, D, -1)
+        canon[p + "attn_q"] = f32_weight(p + "attn_q", a[:, 0].reshape(cfg.n_heads * D, -1))
+        canon[p + "attn_gate"] = f32_weight(p + "attn_gate", a[:, 1].reshape(cfg.n_heads * D, -1))
+        return True
+    if rest == "attn_qkv.weight":
+        if w.shape[0] != 2 * kd + nv * Dg:
+            raise CheckpointLayout(f"{p}{rest}: {w.shape[0]} rows, expected {2 * kd + nv * Dg}")
+        canon[p + "gdn_q"], canon[p + "gdn_k"] = w.rows(0, kd), w.rows(kd, kd)
+        canon[p + "gdn_v"] = f32_weight(p + "gdn_v", untile(w.rows(2 * kd, nv * Dg).to_f32(), Dg))
+        return True
+    per_head = {"attn_gate.weight": ("gdn_z", Dg), "ssm_beta.weight": ("gdn_b", 1), "ssm_alpha.weight": ("gdn_a", 1), "ssm_dt.bias": ("gdn_dt_bias", 1)}
+    if rest in per_head:
+        role, block = per_head[rest]
+        canon[p + role] = f32_weight(p + role, untile(w.to_f32(), block))
+        return True
+    if rest == "ssm_a":
+        a = w.to_f32()
+        if not (a < 0).all():
+            raise CheckpointLayout(f"{p}ssm_a holds -exp(A_log): every value is negative")
+        canon[p + "gdn_a_log"] = f32_weight(p + "gdn_a_log", untile(np.log(-a.astype(np.float64)).astype(np.float32), 1))
+        return True
+    if rest == "ssm_conv1d.weight":
+        a = w.to_f32().reshape(2 * kd + nv * Dg, -1)
+        canon[p + "gdn_conv"] = f32_weight(p + "gdn_conv", np.concatenate([a[:2 * kd], untile(a[2 * kd:], Dg)], 0))
+        return True
+    if rest == "ssm_out.weight":                           # [hidden, value channels]: the columns follow the value heads
+        a = w.to_f32()
+        canon[p + "gdn_o"] = f32_weight(p + "gdn_o", np.ascontiguousarray(untile(np.ascontiguousarray(a.T), Dg).T))
+        return True
+    return False
+
+
 GLM53_SITE = {f"hc_{site}_{part}": f"hc_{site}_{part}" for site in ("attn", "ffn") for part in ("fn", "base", "scale")}
 GLM53_KDA = {"self_attn.q_proj.weight": "kda_q", "self_attn.k_proj.weight": "kda_k", "self_attn.v_proj.weight": "kda_v",
              "self_attn.f_a_proj.weight": "kda_f_a", "self_attn.f_b_proj.weight": "kda_f_b", "self_attn.b_proj.weight": "kda_b",

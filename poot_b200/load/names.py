@@ -69,6 +69,10 @@ GGUF_FAMILY_LAYER = {
     "bloom": {"attn_norm.bias": "attn_norm_bias", "ffn_norm.bias": "ffn_norm_bias", "attn_output.bias": "attn_o_bias",
               "ffn_up.bias": "ffn_up_bias", "ffn_down.bias": "ffn_down_bias"},
     "minimax_m2": {"exp_probs_b.bias": "ffn_router_select_bias"},
+    "qwen38_27b": {"post_attention_norm.weight": "ffn_norm", "ssm_norm.weight": "gdn_gate_norm_w"},
+    "gemma4": {"post_attention_norm.weight": "attn_post_norm", "post_ffw_norm.weight": "ffn_post_norm", "layer_output_scale.weight": "layer_scalar",
+               "ffn_pre_norm_2.weight": "ffn_norm_2", "ffn_post_norm_1.weight": "ffn_post_norm_1", "ffn_post_norm_2.weight": "ffn_post_norm_2",
+               "ffn_gate_inp.scale": "ffn_router_scale", "ffn_down_exps.scale": "ffn_expert_scale"},
     "deepseek2": {"attn_q_a.weight": "attn_q_a", "attn_q_a_norm.weight": "attn_q_a_norm", "attn_q_b.weight": "attn_q_b",
                   "attn_kv_a_mqa.weight": "attn_kv_a", "attn_kv_a_norm.weight": "attn_kv_a_norm", "attn_kv_b.weight": "attn_kv_b",
                   "ffn_gate_shexp.weight": "shared_gate", "ffn_up_shexp.weight": "shared_up", "ffn_down_shexp.weight": "shared_down",
@@ -116,3 +120,12 @@ def hf_to_gguf_qk_row_order(n_rows: int, n_heads: int) -> np.ndarray:
     hd = n_rows // n_heads
     idx = np.arange(n_rows).reshape(n_heads, 2, hd // 2)
     return idx.transpose(0, 2, 1).reshape(-1)
+
+
+def gdn_grouped_heads(n_value_heads: int, n_key_heads: int) -> np.ndarray:
+    """llama.cpp stores a gated delta net's value heads tiled over the key heads: position ``t`` holds the head that the
+    source checkpoint, which groups value heads by key head, has at ``(t % key_heads) * rep + t // key_heads``
+    (crates/poot-models/src/components/gdn_names.rs:283-297).  Returns that index per tiled position."""
+    rep = n_value_heads // n_key_heads
+    t = np.arange(n_value_heads)
+    return (t % n_key_heads) * rep + t // n_key_heads

@@ -650,9 +650,9 @@ SHIPPED: List[FamilyEntry] = [
 
 # families whose GGUF metadata and tensor names the generic llama-style reader covers completely
 GGUF_FAMILIES = ("llama", "qwen2", "qwen3", "qwen3moe", "phi3", "olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss",
-                 "mpt", "bloom", "minimax_m2", "deepseek2")
+                 "mpt", "bloom", "minimax_m2", "deepseek2", "qwen38_27b", "gemma4")
 # of those, the ones whose configuration is read by the family's own header table from a header rebuilt out of the GGUF keys
-GGUF_VIA_HEADER = ("olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss", "mpt", "bloom", "minimax_m2", "deepseek2")
+GGUF_VIA_HEADER = ("olmo2", "olmoe", "smollm3", "granite", "gemma2", "gemma3", "gpt_oss", "mpt", "bloom", "minimax_m2", "deepseek2", "qwen38_27b", "gemma4")
 
 
 class Registry:
@@ -699,8 +699,12 @@ class Registry:
                     from ..load.gguf import hf_header_from_gguf
                     cfg = e.from_hf(hf_header_from_gguf(arch, meta, e.name))
                     cfg.name = str(meta.get("general.name", e.name))
-                    if e.name in ("gemma2", "gemma3"):
-                        cfg.norm_offset = 0.0           # llama.cpp's converter stores Gemma's norm scales with the one folded in
+                    if e.name in ("gemma2", "gemma3", "qwen38_27b"):
+                        cfg.norm_offset = 0.0           # llama.cpp's converter stores these norm scales with the one folded in
+                    if e.kind == "own":
+                        import importlib
+                        mod, cls = e.tracer.split(":")
+                        return getattr(importlib.import_module("." + mod, __package__), cls)(cfg)
                     return Model(cfg)
                 return Model(config_from_gguf_metadata(arch, meta, e.name))
         raise UnsupportedFamily(f"no family for GGUF architecture {arch!r}")

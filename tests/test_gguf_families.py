@@ -281,6 +281,143 @@ def _deepseek2_to_gguf(path, m, split_kv_b):
     _put_all(path, meta, rows)
 
 
+def _qwen35_to_gguf(path, m, nextn):
+    """llama.cpp's ``qwen35`` layout: the delta-net quantities one tensor each with the value heads tiled over the key
+    heads, ``ssm_a = -exp(A_log)``, every ``1 + w`` norm with the one folded in, and (``nextn``) one more block after the stack."""
+    c = m.config
+    arch = "qwen35"
+    nk, nv, Dg, K = c.linear_num_key_heads, c.linear_num_value_heads, c.linear_key_head_dim, c.linear_conv_kernel_dim
+    H, L, rep, kd = c.hidden_size, c.num_hidden_layers, nv // nk, nk * Dg
+    tiled = [(t % nk) * rep + t // nk for t in range(nv)]                 # the grouped head each tiled position holds
+
+    def tile(a, block):
+        return a.reshape(nv, block, -1)[tiled].reshape(a.shape)
+
+    rp = c.rope_parameters
+    meta = {"general.architecture": arch, f"{arch}.block_count": L + (1 if nextn else 0), f"{arch}.embedding_length": H,
+            f"{arch}.attention.head_count": c.num_attention_heads, f"{arch}.attention.head_count_kv": c.num_key_value_heads,
+            f"{arch}.attention.key_length": c.head_dim, f"{arch}.feed_forward_length": c.intermediate_size,
+            f"{arch}.rope.freq_base": float(rp["rope_theta"]), f"{arch}.rope.dimension_count": int(c.head_dim * rp.get("partial_rotary_factor", 1.0)),
+            f"{arch}.attention.layer_norm_rms_epsilon": float(c.rms_norm_eps), f"{arch}.context_length": c.max_position_embeddings,
+            f"{arch}.vocab_size": c.vocab_size, f"{arch}.ssm.inner_size": nv * Dg, f"{arch}.ssm.state_size": Dg, f"{arch}.ssm.group_count": nk,
+            f"{arch}.ssm.time_step_rank": nv, f"{arch}.ssm.conv_kernel": K, f"{arch}.full_attention_interval": 2}
+    if nextn:
+        meta[f"{arch}.nextn_predict_layers"] = 1
+    sd = {k: v.detach().float().numpy() for k, v in m.state_dict().items()}
+    rows = [("token_embd.weight", sd["model.embed_tokens.weight"]), ("output_norm.weight", sd["model.norm.weight"] + 1.0),
+            ("output.weight", sd["lm_head.weight"])]
+    for l in range(L):
+        hf, b = f"model.layers.{l}.", f"blk.{l}."
+        rows += [(b + "attn_norm.weight", sd[hf + "input_layernorm.weight"] + 1.0),
+                 (b + "post_attention_norm.weight", sd[hf + "post_attention_layernorm.weight"] + 1.0)]
+        if hf + "self_attn.q_proj.weight" in sd:
+            for gg, name in (("attn_q", "q_proj"), ("attn_k", "k_proj"), ("attn_v", "v_proj"), ("attn_output", "o_proj")):
+                rows.append((b + gg + ".weight", sd[hf + f"self_attn.{name}.weight"]))
+            rows += [(b + "attn_q_norm.weight", sd[hf + "self_attn.q_norm.weight"] + 1.0), (b + "attn_k_norm.weight", sd[hf + "self_attn.k_norm.weight"] + 1.0)]
+        else:
+            la = hf + "linear_attn."
+            qkv = sd[la + "in_proj_qkv.weight"]
+            conv = sd[la + "conv1d.weight"].reshape(2 * kd + nv * Dg, K)
+            rows += [(b + "attn_qkv.weight", np.concatenate([qkv[:2 * kd], tile(qkv[2 * kd:], Dg)], 0)),
+                     (b + "attn_gate.weight", tile(sd[la + "in_proj_z.weight"], Dg)), (b + "ssm_beta.weight", tile(sd[la + "in_proj_b.weight"], 1)),
+                     (b + "ssm_alpha.weight", tile(sd[la + "in_proj_a.weight"], 1)), (b + "ssm_dt.bias", tile(sd[la + "dt_bias"], 1)),
+                     (b + "ssm_a", tile(-np.exp(sd[la + "A_log"]), 1)),
+                     (b + "ssm_conv1d.weight", np.concatenate([conv[:2 * kd], tile(conv[2 * kd:], Dg)], 0)),
+                     (b + "ssm_norm.weight", sd[la + "norm.weight"]),
+                     (b + "ssm_out.weight", np.ascontiguousarray(tile(np.ascontiguousarray(sd[la + "out_proj.weight"].T), Dg).T))]
+        for gg, name in (("ffn_gate", "gate_proj"), ("ffn_up", "up_proj"), ("ffn_down", "down_proj")):
+            rows.append((b + gg + ".weight", sd[hf + f"mlp.{name}.weight"]))
+    if nextn:                                                              # never read: it is not part of the stack
+        rows += [(f"blk.{L}.attn_norm.weight", np.ones(H, np.float32)), (f"blk.{L}.nextn.eh_proj.weight", np.ones((H, 2 * H), np.float32)),
+                 (f"blk.{L}.attn_qkv.weight", np.ones((3, H), np.float32))]
+    _put_all(path, meta, rows)
+
+
+GEMMA4_LAYER = {"input_layernorm.weight": "attn_norm.weight", "post_attention_layernorm.weight": "post_attention_norm.weight",
+                "pre_feedforward_layernorm.weight": "ffn_norm.weight", "post_feedforward_layernorm.weight": "post_ffw_norm.weight",
+                "layer_scalar": "layer_output_scale.weight", "self_attn.q_proj.weight": "attn_q.weight", "self_attn.k_proj.weight": "attn_k.weight",
+                "self_attn.v_proj.weight": "attn_v.weight", "self_attn.o_proj.weight": "attn_output.weight", "self_attn.q_norm.weight": "attn_q_norm.weight",
+                "self_attn.k_norm.weight": "attn_k_norm.weight", "mlp.gate_proj.weight": "ffn_gate.weight", "mlp.up_proj.weight": "ffn_up.weight",
+                "mlp.down_proj.weight": "ffn_down.weight", "pre_feedforward_layernorm_2.weight": "ffn_pre_norm_2.weight",
+                "post_feedforward_layernorm_1.weight": "ffn_post_norm_1.weight", "post_feedforward_layernorm_2.weight": "ffn_post_norm_2.weight",
+                "router.proj.weight": "ffn_gate_inp.weight", "router.scale": "ffn_gate_inp.scale", "router.per_expert_scale": "ffn_down_exps.scale",
+                "experts.gate_up_proj": "ffn_gate_up_exps.weight", "experts.down_proj": "ffn_down_exps.weight"}
+
+
+def _gemma4_to_gguf(path, m):
+    """llama.cpp's ``gemma4`` layout: per-layer K/V head counts and sliding flags as arrays, the two head widths, no ``attn_v``
+    on a global layer that reads its value from the key projection, and the global layers' rotary tail as ``rope_freqs.weight``
+    (ones over the rotated pairs, 1e30 over the rest)."""
+    c = m.config
+    arch = "gemma4"
+    local = [t == "sliding_attention" for t in c.layer_types]
+    rp = c.rope_parameters
+    meta = {"general.architecture": arch, f"{arch}.block_count": c.num_hidden_layers, f"{arch}.embedding_length": c.hidden_size,
+            f"{arch}.feed_forward_length": c.intermediate_size, f"{arch}.context_length": c.max_position_embeddings,
+            f"{arch}.attention.head_count": c.num_attention_heads,
+            f"{arch}.attention.head_count_kv": [int(c.num_key_value_heads if loc else (c.num_global_key_value_heads or c.num_key_value_heads)) for loc in local],
+            f"{arch}.attention.sliding_window_pattern": local, f"{arch}.attention.sliding_window": c.sliding_window,
+            f"{arch}.attention.key_length": c.global_head_dim, f"{arch}.attention.key_length_swa": c.head_dim,
+            f"{arch}.rope.freq_base": float(rp["full_attention"]["rope_theta"]), f"{arch}.rope.freq_base_swa": float(rp["sliding_attention"]["rope_theta"]),
+            f"{arch}.attention.layer_norm_rms_epsilon": float(c.rms_norm_eps), f"{arch}.vocab_size": c.vocab_size}
+    if c.final_logit_softcapping:
+        meta[f"{arch}.final_logit_softcapping"] = float(c.final_logit_softcapping)
+    if c.enable_moe_block:
+        meta.update({f"{arch}.expert_count": c.num_experts, f"{arch}.expert_used_count": c.top_k_experts,
+                     f"{arch}.expert_feed_forward_length": c.moe_intermediate_size})
+    pairs = c.global_head_dim // 2
+    rotated = int(pairs * rp["full_attention"].get("partial_rotary_factor", 1.0))
+    rows = [("rope_freqs.weight", np.array([1.0] * rotated + [1e30] * (pairs - rotated), np.float32))]
+    for k, v in m.state_dict().items():
+        a = v.detach().float().numpy()
+        mm = re.match(r"model\.layers\.(\d+)\.(.+)$", k)
+        if k == "model.embed_tokens.weight":
+            rows.append(("token_embd.weight", a))
+        elif k == "model.norm.weight":
+            rows.append(("output_norm.weight", a))
+        elif mm:
+            l = int(mm.group(1))
+            if mm.group(2) == "self_attn.v_proj.weight" and c.attention_k_eq_v and not local[l]:
+                continue
+            rows.append((f"blk.{l}.{GEMMA4_LAYER[mm.group(2)]}", a))
+    _put_all(path, meta, rows)
+
+
+@pytest.mark.parametrize("case", ["gemma4-value-is-key", "gemma4-moe"])
+def test_gemma4_gguf_equals_the_hugging_face_forward(case, tmp_path):
+    m, vocab = build(CASES[case])
+    toks = torch.randint(0, vocab, (1, 12), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = m(toks).logits[0].numpy()
+    path = str(tmp_path / "gemma4.gguf")
+    _gemma4_to_gguf(path, m)
+    h = ModelHandle.load(path)
+    assert h.cfg.family == "gemma4" and h.cfg.k_eq_v == bool(m.config.attention_k_eq_v) and h.cfg.tie_embeddings
+    sess = OracleSession(h.model, h.oracle_weights(), capacity=32)
+    sess._graph = lambda T, embeds=False: h.model.trace(StepSpec(rows=1, tokens=T, capacity=32, logit_rows="all"))
+    got = sess.step(toks.numpy()).reshape(ref.shape)
+    err = np.abs(got - ref).max() / np.abs(ref).max()
+    assert err < 2e-5, err
+
+
+@pytest.mark.parametrize("nextn", [False, True])
+def test_qwen35_gguf_equals_the_hugging_face_forward(nextn, tmp_path):
+    m, vocab = build(CASES["qwen3_5"])
+    toks = torch.randint(0, vocab, (1, 12), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = m(toks).logits[0].numpy()
+    path = str(tmp_path / "qwen35.gguf")
+    _qwen35_to_gguf(path, m, nextn)
+    h = ModelHandle.load(path)
+    assert h.cfg.family == "qwen38_27b" and h.cfg.n_layers == m.config.num_hidden_layers and h.cfg.norm_offset == 0.0
+    assert not any(k.startswith(f"layers.{h.cfg.n_layers}.") for k in h.canonical)
+    sess = OracleSession(h.model, h.oracle_weights(), capacity=32)
+    sess._graph = lambda T, embeds=False: h.model.trace(StepSpec(rows=1, tokens=T, capacity=32, logit_rows="all"))
+    got = sess.step(toks.numpy()).reshape(ref.shape)
+    err = np.abs(got - ref).max() / np.abs(ref).max()
+    assert err < 1e-4, err
+
+
 @pytest.mark.parametrize("family", ["mpt", "bloom", "minimax_m2", "deepseek2", "deepseek2-absorbed"])
 def test_gguf_of_the_families_with_their_own_layouts(family, tmp_path):
     """MPT and BLOOM (LayerNorm stacks with a fused ``attn_qkv``, BLOOM's regrouped into thirds by the converter and with
