@@ -44,7 +44,13 @@ def main_caption(argv: List[str]) -> int:
     try:
         from PIL import Image
         image = Image.open(args.image)
-        image.load()
+        if getattr(image, "n_frames", 1) > 1 and image.format == "PNG":
+            # an animated PNG is a clip: the front end samples its frames (families without a video path refuse it)
+            from ..models.image_prep import read_apng
+            with open(args.image, "rb") as fh:
+                image = read_apng(fh.read())
+        else:
+            image.load()
     except Exception as e:                                  # unreadable or undecodable file
         print(f"error: decode {args.image}: {e}", file=sys.stderr)
         return 1

@@ -13,7 +13,7 @@ import json
 import math
 import os
 from dataclasses import dataclass, field
-from typing import List, Tuple
+from typing import List, Optional, Tuple
 
 import numpy as np
 
@@ -207,7 +207,8 @@ def smart_resize(h: int, w: int, factor: int, min_pixels: int, max_pixels: int) 
 @dataclass
 class QwenImages:
     patches: np.ndarray                 # [sum t*h*w, C * temporal * patch * patch] f32
-    grids: List[Tuple[int, int, int]]   # (t, h, w) patches of every image
+    grids: List[Tuple[int, int, int]]   # (t, h, w) patches of every image or video, in prompt order
+    seconds: Optional[List[Optional[float]]] = None   # per grid: seconds one temporal step covers (None: a still image)
 
     def rows(self, merge: int) -> List[int]:
         return [t * h * w // (merge * merge) for t, h, w in self.grids]
@@ -227,3 +228,110 @@ def qwen_preprocess(img, prep: QwenImagePrep) -> QwenImages:
     x = np.broadcast_to(a[None], (tp, 3, hb, wb)).reshape(1, tp, 3, gh // m, m, p, gw // m, m, p)
     x = x.transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)
     return QwenImages(np.ascontiguousarray(x).reshape(gh * gw, 3 * tp * p * p), [(1, gh, gw)])
+
+
+# ---- Qwen2.5-VL video ----------------------------------------------------------------------------------------------
+MAX_VIDEO_FRAMES = 16 * 1024
+
+
+@dataclass
+class VideoClip:
+    """Decoded frames of one clip with what frame sampling needs to know about the source."""
+    frames: list                         # PIL images, source order
+    fps: float                           # average source rate: frames / duration
+    timestamps: List[float] = field(default_factory=list)    # start of each frame in seconds
+
+
+@dataclass
+class QwenVideoPrep:
+    """Frame sampling and per-frame pixel budget of the video half of the processor (crates/poot-models/src/multimodal/
+    qwen_vl/processor/video_sampling.rs, preprocess.rs): frames are taken uniformly at ``fps`` per second of source,
+    between ``min_frames`` and ``max_frames`` and a whole number of temporal steps."""
+    fps: float = 2.0
+    min_frames: int = 4
+    max_frames: int = 768
+    min_pixels: int = 128 * 28 * 28
+    max_pixels: int = 768 * 28 * 28
+
+    @staticmethod
+    def from_dir(path: str, patch: int, merge: int) -> "QwenVideoPrep":
+        """Defaults scaled to the tower's merged cell, overridden by ``video_preprocessor_config.json`` where the
+        checkpoint directory has one."""
+        p = QwenVideoPrep(min_pixels=128 * (patch * merge) ** 2, max_pixels=768 * (patch * merge) ** 2)
+        f = os.path.join(path, "video_preprocessor_config.json")
+        if os.path.exists(f):
+            with open(f) as fh:
+                c = json.load(fh)
+            size = c.get("size") or {}
+            p.min_pixels = int(c.get("min_pixels") or size.get("shortest_edge") or p.min_pixels)
+            p.max_pixels = int(c.get("max_pixels") or size.get("longest_edge") or p.max_pixels)
+            p.fps = float(c.get("fps") or p.fps)
+            p.min_frames, p.max_frames = int(c.get("min_frames") or p.min_frames), int(c.get("max_frames") or p.max_frames)
+        if not (p.fps > 0 and 0 < p.min_frames <= p.max_frames and 0 < p.min_pixels <= p.max_pixels):
+            raise ValueError(f"video preprocessing limits do not make sense: {p}")
+        return p
+
+
+def sample_video_frames(n_frames: int, source_fps: float, prep: QwenVideoPrep, temporal: int = 2) -> List[int]:
+    """Indices of the frames the processor keeps: ``n_frames / source_fps * fps`` of them, clamped to ``[min_frames,
+    max_frames]`` and to the clip's length, rounded down to whole temporal steps, spaced uniformly from frame 0."""
+    if n_frames <= 0:
+        raise ValueError("a video must hold at least one frame")
+    if n_frames > MAX_VIDEO_FRAMES:
+        raise ValueError(f"a video of {n_frames} frames; at most {MAX_VIDEO_FRAMES} are read")
+    if not (math.isfinite(source_fps) and source_fps > 0):
+        raise ValueError(f"source frame rate must be positive and finite, got {source_fps}")
+    want = n_frames / source_fps * prep.fps
+    want = min(min(max(want, prep.min_frames), prep.max_frames), n_frames)
+    want = int(math.floor(want / temporal) * temporal)
+    if want <= 0:                        # a clip shorter than one temporal step: every frame, padded by the caller
+        return list(range(n_frames))
+    return [int(x) for x in np.arange(0, n_frames, n_frames / want).astype(np.int64)[:want]]
+
+
+def qwen_preprocess_video(clip: VideoClip, prep: QwenImagePrep, video: Optional[QwenVideoPrep] = None):
+    """``(QwenImages with one (t, h, w) grid, seconds one temporal step covers)`` for one clip: sample, resize every kept
+    frame to one size within the per-frame pixel budget, normalise, and lay ``temporal`` consecutive frames into each
+    patch row (an odd tail repeats the last frame)."""
+    from PIL import Image
+    video = video or QwenVideoPrep()
+    keep = sample_video_frames(len(clip.frames), clip.fps, video, prep.temporal)
+    frames = [clip.frames[i].convert("RGB") for i in keep]
+    while len(frames) % prep.temporal:
+        frames.append(frames[-1])
+    w, h = frames[0].size
+    if any(f.size != (w, h) for f in frames):
+        raise ValueError("the frames of one video differ in size")
+    hb, wb = smart_resize(h, w, prep.patch * prep.merge, video.min_pixels, video.max_pixels)
+    mean, std = np.asarray(prep.mean, np.float32)[:, None, None], np.asarray(prep.std, np.float32)[:, None, None]
+    a = np.stack([(np.asarray(f.resize((wb, hb), Image.BICUBIC), dtype=np.float32).transpose(2, 0, 1) * np.float32(prep.rescale) - mean) / std
+                  for f in frames])
+    p, m, tp = prep.patch, prep.merge, prep.temporal
+    gt, gh, gw = len(frames) // tp, hb // p, wb // p
+    x = a.reshape(gt, tp, 3, gh // m, m, p, gw // m, m, p).transpose(0, 3, 6, 4, 7, 2, 1, 5, 8)
+    # the rate the kept frames stand for: kept frames over the clip's duration
+    sampled_fps = len(keep) / (len(clip.frames) / clip.fps)
+    return QwenImages(np.ascontiguousarray(x).reshape(gt * gh * gw, 3 * tp * p * p), [(gt, gh, gw)]), prep.temporal / sampled_fps
+
+
+def read_apng(data: bytes, max_pixels: int = 32 * 1024 * 1024) -> VideoClip:
+    """An animated PNG as a clip (crates/poot-llm/src/multimodal/apng.rs): one animation cycle, every frame composed onto
+    the canvas, the frame delays kept as timestamps; the source rate is frames over duration.  A still PNG is a
+    one-frame clip at one frame per second."""
+    import io
+    from PIL import Image, ImageSequence
+    img = Image.open(io.BytesIO(data))
+    if img.format != "PNG":
+        raise ValueError(f"a video is read from an animated PNG, not {img.format}")
+    n = int(getattr(img, "n_frames", 1))
+    if n > MAX_VIDEO_FRAMES or n * img.size[0] * img.size[1] > max_pixels:
+        raise ValueError(f"an animation of {n} frames of {img.size[0]}x{img.size[1]} is over the decode budget")
+    frames, stamps, t = [], [], 0.0
+    for f in ImageSequence.Iterator(img):
+        frames.append(f.convert("RGB").copy())
+        stamps.append(t)
+        t += float(f.info.get("duration", 0.0) or 0.0) / 1000.0
+    if t <= 0.0:
+        t = float(len(frames))           # no delays stated: one frame per second
+        stamps = [float(i) for i in range(len(frames))]
+    return VideoClip(frames, len(frames) / t, stamps)

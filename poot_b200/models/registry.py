@@ -594,7 +594,8 @@ def _qwen_vl(c):
                               patch=v.get("patch_size", 14), temporal=v.get("temporal_patch_size", 2),
                               merge=v.get("spatial_merge_size", 2), window=v.get("window_size", 112),
                               full_layers=tuple(v.get("fullatt_block_indexes", (7, 15, 23, 31))),
-                              out_hidden=v.get("out_hidden_size", text.hidden), act=act)
+                              out_hidden=v.get("out_hidden_size", text.hidden), act=act,
+                              video_token=int(c.get("video_token_id", -1)), tokens_per_second=float(v.get("tokens_per_second", 2)))
     if vision.out_hidden != text.hidden:
         raise UnsupportedFamily("qwen2_5_vl: the merger's output width differs from the text width")
     return text, vision, int(c.get("image_token_id", 151655))

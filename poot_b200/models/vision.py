@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import math
 from dataclasses import dataclass
-from typing import Dict
+from typing import Dict, Optional
 
 import numpy as np
 
@@ -179,6 +179,8 @@ class QwenVisionConfig:
     act: str = "silu"
     norm_eps: float = 1e-6
     rope_theta: float = 10000.0
+    video_token: int = -1                  # id of the video placeholder (-1: the checkpoint names none)
+    tokens_per_second: float = 2.0         # time positions per second of video
 
     @property
     def patch_dim(self) -> int:
@@ -281,20 +283,43 @@ class QwenVisionTower:
         return b.finish()
 
 
-def mrope_positions(tokens, image_token: int, grids, merge: int) -> np.ndarray:
-    """Rotary position streams ``[3, len(tokens)]`` (time, row, column) of a prompt whose runs of ``image_token`` stand
-    for the images of ``grids = [(t, h, w), ...]`` patches (multimodal/mrope.rs; ``get_rope_index``): text tokens count
-    up with three equal values; an image starting at ``s`` gives ``(s, s + row, s + column)`` per merged cell; the text
-    after it continues at ``s + max(rows, columns)`` of merged cells."""
+def mrope_positions(tokens, image_token: int, grids, merge: int, video_token: Optional[int] = None, seconds_per_step=None,
+                    tokens_per_second: float = 2.0) -> np.ndarray:
+    """Rotary position streams ``[3, len(tokens)]`` (time, row, column) of a prompt whose runs of ``image_token`` (or
+    ``video_token``) stand for the media of ``grids = [(t, h, w), ...]`` patches, in prompt order (multimodal/mrope.rs;
+    ``get_rope_index``): text tokens count up with three equal values; an image starting at ``s`` gives ``(s, s + row,
+    s + column)`` per merged cell and the text after it continues at ``s + max(rows, columns)`` of merged cells.  A video
+    (``seconds_per_step[i]`` is the time one temporal step of grid ``i`` covers, ``None`` for an image) advances its time
+    stream by ``floor(step * seconds * tokens_per_second)`` per temporal step, and the text continues after the largest
+    position of any stream."""
     toks = np.asarray(tokens).reshape(-1)
     out = np.zeros((3, len(toks)), dtype=np.int32)
     i, nxt, image = 0, 0, 0
+    secs = list(seconds_per_step) if seconds_per_step is not None else [None] * len(grids)
     while i < len(toks):
+        if video_token is not None and toks[i] == video_token:
+            if image >= len(grids) or secs[image] is None:
+                raise ValueError("a video run in the prompt without a video at that place")
+            t, h, w = grids[image]
+            lh, lw = h // merge, w // merge
+            n = t * lh * lw
+            if len(toks[i:i + n]) != n or not np.all(toks[i:i + n] == video_token):
+                raise ValueError(f"video {image}: the prompt holds fewer than {n} video tokens in a run")
+            step = np.floor(np.arange(t) * float(secs[image]) * float(tokens_per_second)).astype(np.int64)
+            out[0, i:i + n] = nxt + np.repeat(step, lh * lw)
+            out[1, i:i + n] = nxt + np.tile(np.repeat(np.arange(lh), lw), t)
+            out[2, i:i + n] = nxt + np.tile(np.tile(np.arange(lw), lh), t)
+            nxt = int(out[:, i:i + n].max()) + 1
+            i += n
+            image += 1
+            continue
         if toks[i] != image_token:
             out[:, i] = nxt
             nxt += 1
             i += 1
             continue
+        if image < len(grids) and secs[image] is not None:
+            raise ValueError(f"medium {image} is a video but the prompt holds an image run there")
         if image >= len(grids):
             raise ValueError("more image runs in the prompt than images")
         t, h, w = grids[image]

@@ -428,15 +428,15 @@ def make_handler(state: ServerState):
             for the job (``self._embeds``).  ``None`` when no message holds an image."""
             self._embeds = self._rope = None
             has = any(isinstance(m, dict) and isinstance(m.get("content"), list) and
-                      any(isinstance(p, dict) and p.get("type") in ("image_url", "image") for p in m["content"]) for m in msgs)
+                      any(isinstance(p, dict) and p.get("type") in ("image_url", "image", "video_url", "video") for p in m["content"]) for m in msgs)
             if not has:
                 return None
             if state.vision is None:
                 raise ApiError(400, "the served model takes no images: it has no vision front end", param="messages")
             try:
-                if any(isinstance(p, dict) and p.get("type") == "image" for m in msgs if isinstance(m.get("content"), list)
+                if any(isinstance(p, dict) and p.get("type") in ("image", "video") for m in msgs if isinstance(m.get("content"), list)
                        for p in m["content"]):
-                    raise ValueError("image parts are sent as image_url with a data: URL")
+                    raise ValueError("image and video parts are sent as image_url / video_url with a data: URL")
                 ids, pixels = state.vision.prepare_messages(msgs, state.chat_template)
                 self._embeds = state.vision.image_inputs(ids, pixels)
                 self._rope = state.vision.rope_inputs(ids, pixels)

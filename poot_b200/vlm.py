@@ -15,7 +15,8 @@ from typing import Callable, List, Optional, Sequence
 import numpy as np
 
 from .driver.handle import ModelHandle
-from .models.image_prep import ImagePrep, QwenImagePrep, QwenImages, image_prompt, preprocess, qwen_preprocess
+from .models.image_prep import (ImagePrep, QwenImagePrep, QwenImages, QwenVideoPrep, VideoClip, image_prompt, preprocess, qwen_preprocess,
+                                qwen_preprocess_video, read_apng)
 from .models.vision import QwenVisionTower, mrope_positions, patchify, position_ids, qwen_vision_inputs
 from .oracle.eval import EvalOptions, eval_graph
 from .driver.sampler import SamplingParams
@@ -36,11 +37,39 @@ QWEN_VL_TEMPLATE = ("{% for message in messages %}{% if loop.first and message['
                     "You are a helpful assistant.<|im_end|>\n{% endif %}<|im_start|>{{ message['role'] }}\n"
                     "{% if message['content'] is string %}{{ message['content'] }}{% else %}{% for part in message['content'] %}"
                     "{% if part['type'] == 'image' %}<|vision_start|><|image_pad|><|vision_end|>"
+                    "{% elif part['type'] == 'video' %}<|vision_start|><|video_pad|><|vision_end|>"
                     "{% elif part['type'] == 'text' %}{{ part['text'] }}{% endif %}{% endfor %}{% endif %}<|im_end|>\n{% endfor %}"
                     "{% if add_generation_prompt %}<|im_start|>assistant\n{% endif %}")
 
+VIDEO_TOKEN = "<|video_pad|>"
 MAX_IMAGE_BYTES = 32 * 1024 * 1024
 MAX_IMAGE_PIXELS = 64 * 1024 * 1024
+MAX_VIDEO_BYTES = 64 * 1024 * 1024
+
+
+def video_clip(src) -> VideoClip:
+    """A video part's payload as a clip: a ``VideoClip``, a list of PIL frames (taken as one frame per second), the bytes
+    of an animated PNG, or a ``data:image/apng;base64,`` (or ``image/png``) URL of one.  Nothing is fetched."""
+    import base64
+    import binascii
+    if isinstance(src, VideoClip):
+        return src
+    if isinstance(src, (list, tuple)) and src:
+        return VideoClip(list(src), 1.0, [float(i) for i in range(len(src))])
+    if isinstance(src, (bytes, bytearray)):
+        return read_apng(bytes(src))
+    if not isinstance(src, str) or not src.startswith("data:"):
+        raise ValueError("a video is a data: URL of an animated PNG (base64); remote URLs are not fetched")
+    head, sep, payload = src[5:].partition(",")
+    if not sep or not head.endswith(";base64") or head.split(";")[0] not in ("image/apng", "image/png", "video/apng"):
+        raise ValueError("a video URL must be data:image/apng;base64,...")
+    if len(payload) > MAX_VIDEO_BYTES * 4 // 3 + 4:
+        raise ValueError("video payload exceeds the size limit")
+    try:
+        raw = base64.b64decode(payload, validate=True)
+    except (binascii.Error, ValueError):
+        raise ValueError("video payload is not valid base64") from None
+    return read_apng(raw)
 
 
 def image_from_data_url(url):
@@ -91,6 +120,7 @@ class VisionLLM:
         if self.qwen:
             vc = self.vision.cfg
             self.prep = QwenImagePrep.from_dir(handle.source, vc.patch, vc.merge, vc.temporal)
+            self.video_prep = QwenVideoPrep.from_dir(handle.source, vc.patch, vc.merge)
         else:
             self.prep = ImagePrep.from_dir(handle.source, self.vision.cfg.image_size)
         self._towers = {}
@@ -187,8 +217,8 @@ class VisionLLM:
     # ---- prompt ----------------------------------------------------------------------------------------------------
     def prepare(self, question: str, image) -> tuple:
         """``(prompt tokens, frames)`` for one user turn holding ``image`` (a PIL image) and ``question``."""
-        return self.prepare_messages([{"role": "user", "content": [{"type": "image", "image": image},
-                                                                  {"type": "text", "text": question}]}])
+        part = {"type": "video", "video": image} if isinstance(image, VideoClip) else {"type": "image", "image": image}
+        return self.prepare_messages([{"role": "user", "content": [part, {"type": "text", "text": question}]}])
 
     def prepare_messages(self, messages: List[dict], template: Optional[str] = None) -> tuple:
         """Chat messages whose contents hold image parts -> ``(prompt tokens, frames of every image in order)``.
@@ -213,28 +243,41 @@ class VisionLLM:
                 elif kind == "image":
                     images.append(part.get("image"))
                     parts.append({"type": "image"})
+                elif kind in ("video", "video_url") and self.qwen:
+                    images.append(video_clip(part.get("video") if kind == "video" else (part.get("video_url") or {}).get("url")))
+                    parts.append({"type": "video"})
                 else:
-                    raise ValueError(f"content part of type {kind!r}: text and image_url parts are read")
+                    raise ValueError(f"content part of type {kind!r}: text and image_url parts are read" +
+                                     (", and video / video_url parts (an animated PNG)" if self.qwen else ""))
             shaped.append({**m, "content": parts})
         default = QWEN_VL_TEMPLATE if self.qwen else VLM_TEMPLATE
         text = render_chat(shaped, template or self.template or default, family=self.handle.cfg.family, keep_parts=True)
-        pieces = text.split(self.prep.image_token)
+        import re
+        marks = [self.prep.image_token] + ([VIDEO_TOKEN] if self.qwen else [])
+        cut = re.split("(" + "|".join(re.escape(t) for t in marks) + ")", text)
+        pieces, written = cut[0::2], cut[1::2]
         if len(pieces) != len(images) + 1:
             raise ValueError(f"the template wrote {len(pieces) - 1} image placeholders for {len(images)} images")
-        out, frames, grids = pieces[0], [], []
-        for img, tail in zip(images, pieces[1:]):
+        out, frames, grids, seconds = pieces[0], [], [], []
+        for img, mark, tail in zip(images, written, pieces[1:]):
             if self.qwen:
-                one = qwen_preprocess(img, self.prep)
+                if isinstance(img, VideoClip) != (mark == VIDEO_TOKEN):
+                    raise ValueError("the template wrote an image placeholder for a video part (or the reverse)")
+                if isinstance(img, VideoClip):
+                    one, sec = qwen_preprocess_video(img, self.prep, self.video_prep)
+                else:
+                    one, sec = qwen_preprocess(img, self.prep), None
                 frames.append(one.patches)
                 grids += one.grids
-                out += self.prep.image_token * one.rows(self.vision.cfg.merge)[0] + tail
+                seconds.append(sec)
+                out += mark * one.rows(self.vision.cfg.merge)[0] + tail
             else:
                 fr = preprocess(img, self.prep)
                 frames.append(fr.pixels)
                 out += image_prompt(self.prep, fr.rows, fr.cols, self.vision.cfg.rows_per_image) + tail
         pixels = np.concatenate(frames, 0) if frames else None
         if self.qwen and frames:
-            pixels = QwenImages(pixels, grids)
+            pixels = QwenImages(pixels, grids, seconds if any(x is not None for x in seconds) else None)
         return self.tokenizer.encode(out, add_bos=False), pixels
 
     # ---- generation ------------------------------------------------------------------------------------------------
@@ -245,12 +288,12 @@ class VisionLLM:
     def prefill(self, sess: OracleSession, tokens: Sequence[int], pixels: Optional[np.ndarray]) -> np.ndarray:
         """Feed the whole prompt; returns the last position's logits ``[1, vocab]``."""
         toks = np.asarray(tokens, dtype=np.int32).reshape(1, -1)
-        flags = (toks[0] == self.model.image_token).astype(np.int32)
+        flags = self._media(toks[0]).astype(np.int32)
         none = pixels is None or (not self.qwen and len(pixels) == 0)
         rope = None
         if self.qwen:
             # three rotary streams per token; the decode steps after this prompt continue at ``index + rope_delta``
-            rope = mrope_positions(toks[0], self.model.image_token, [] if none else pixels.grids, self.vision.cfg.merge)
+            rope = self._mrope(toks[0], None if none else pixels)
             self.rope_delta = int(rope.max()) + 1 - toks.shape[1]
         if none:
             if flags.any():
@@ -267,7 +310,7 @@ class VisionLLM:
         """``(positions, rows)`` for ``Driver.open(..., embeds=)``: the prompt's image-token positions and the rows the
         frames give, checked to agree in number."""
         toks = np.asarray(tokens, dtype=np.int64).reshape(-1)
-        at = np.nonzero(toks == self.model.image_token)[0]
+        at = np.nonzero(self._media(toks))[0]
         if pixels is None or (not self.qwen and len(pixels) == 0):
             if len(at):
                 raise ValueError("the prompt holds image tokens but no image was given")
@@ -282,8 +325,20 @@ class VisionLLM:
         (``None`` for families with one position per token)."""
         if not self.qwen:
             return None
+        return self._mrope(np.asarray(tokens).reshape(-1), pixels)
+
+    def _media(self, toks: np.ndarray) -> np.ndarray:
+        """Which prompt positions take a row of the vision tower: image placeholders and, for Qwen, video placeholders."""
+        at = toks == self.model.image_token
+        if self.qwen and self.vision.cfg.video_token >= 0:
+            at = at | (toks == self.vision.cfg.video_token)
+        return at
+
+    def _mrope(self, toks: np.ndarray, pixels) -> np.ndarray:
+        c = self.vision.cfg
         grids = [] if pixels is None else pixels.grids
-        return mrope_positions(np.asarray(tokens).reshape(-1), self.model.image_token, grids, self.vision.cfg.merge)
+        return mrope_positions(toks, self.model.image_token, grids, c.merge, video_token=c.video_token if c.video_token >= 0 else None,
+                               seconds_per_step=None if pixels is None else pixels.seconds, tokens_per_second=c.tokens_per_second)
 
     def generate(self, tokens: Sequence[int], pixels: Optional[np.ndarray], max_new: int = 64,
                  eos: Optional[Sequence[int]] = None, on_token: Optional[Callable[[int], None]] = None) -> List[int]:

@@ -329,6 +329,8 @@ def qwen_checkpoint(tmp_path_factory):
     with open(os.path.join(d, "preprocessor_config.json"), "w") as f:
         json.dump({"size": {"shortest_edge": 16 * 16, "longest_edge": 8 * 8 * 40}, "patch_size": 4, "merge_size": 2,
                    "temporal_patch_size": 2}, f)
+    with open(os.path.join(d, "video_preprocessor_config.json"), "w") as f:
+        json.dump({"size": {"shortest_edge": 8 * 8, "longest_edge": 8 * 8 * 12}, "fps": 2.0, "min_frames": 4, "max_frames": 16}, f)
     return d, hf, ids
 
 
@@ -518,3 +520,105 @@ def test_qwen_vl_images_on_the_emulated_device_engine(tmp_path):
             break
         agree += 1
     assert agree >= 2, (got, want)
+
+
+def _apng(frames, ms):
+    import io
+    buf = io.BytesIO()
+    frames[0].save(buf, format="PNG", save_all=True, append_images=frames[1:], duration=ms, loop=0)
+    return buf.getvalue()
+
+
+def test_video_frame_sampling_and_time_positions():
+    """Uniform sampling at two frames per second of source, clamped and cut to whole temporal steps; a video's time
+    stream advances by ``floor(step * seconds per step * positions per second)`` and the text continues past it."""
+    from poot_b200.models.image_prep import QwenVideoPrep, sample_video_frames
+    from poot_b200.models.vision import mrope_positions
+    p = QwenVideoPrep()
+    assert sample_video_frames(30, 10.0, p) == [0, 5, 10, 15, 20, 25]            # 3 s at 2 per second
+    assert sample_video_frames(100, 50.0, p) == [0, 25, 50, 75]                  # 2 s would be 4 frames: the minimum
+    assert sample_video_frames(3, 1.0, p) == [0, 1]                               # never more than the clip, whole steps only
+    assert sample_video_frames(1, 1.0, p) == [0]
+    assert len(sample_video_frames(16 * 1024, 1.0, QwenVideoPrep(max_frames=768))) == 768
+    for bad in (0.0, float("nan"), float("inf"), -1.0):
+        with pytest.raises(ValueError):
+            sample_video_frames(10, bad, p)
+    with pytest.raises(ValueError):
+        sample_video_frames(0, 1.0, p)
+    V, I = 98, 99
+    # three temporal steps of 2 x 2 merged cells, two seconds per step, 25 positions per second: 0, 50, 100
+    pos = mrope_positions([7] + [V] * 12 + [8, 9], I, [(3, 4, 4)], 2, video_token=V, seconds_per_step=[2.0], tokens_per_second=25)
+    assert pos[0].tolist() == [0] + [1] * 4 + [51] * 4 + [101] * 4 + [102, 103]
+    assert pos[1].tolist() == [0] + [1, 1, 2, 2] * 3 + [102, 103]
+    assert pos[2].tolist() == [0] + [1, 2, 1, 2] * 3 + [102, 103]
+    # an image and a video in one prompt, each at its own kind of run
+    both = mrope_positions([I] * 4 + [5] + [V] * 8, I, [(1, 4, 4), (2, 4, 4)], 2, video_token=V, seconds_per_step=[None, 0.5], tokens_per_second=2)
+    assert both[0].tolist() == [0] * 4 + [2] + [3] * 4 + [4] * 4
+    with pytest.raises(ValueError, match="is a video"):
+        mrope_positions([I] * 8, I, [(2, 4, 4)], 2, video_token=V, seconds_per_step=[1.0])
+    with pytest.raises(ValueError, match="without a video"):
+        mrope_positions([V] * 4, I, [(1, 4, 4)], 2, video_token=V, seconds_per_step=[None])
+
+
+def test_qwen_vl_video_rows_and_logits(qwen_checkpoint):
+    """A clip through the front end: an animated PNG is sampled, patched two frames per temporal step and written as
+    video placeholders; the tower's rows equal ``transformers``' video features, and with the same position streams the
+    logits equal its forward."""
+    from PIL import Image
+    from poot_b200.models.image_prep import read_apng
+    d, hf, ids = qwen_checkpoint
+    vlm = VisionLLM.load(d)
+    VID = ids["<|video_pad|>"]
+    assert vlm.vision.cfg.video_token == VID and vlm.vision.cfg.tokens_per_second == 1.0
+    rng = np.random.default_rng(0)
+    frames = [Image.fromarray(rng.integers(0, 255, (24, 32, 3), dtype=np.uint8)) for _ in range(10)]
+    data = _apng(frames, 250)                                                 # 4 frames per second: 2.5 s, five kept
+    clip = read_apng(data)
+    assert len(clip.frames) == 10 and abs(clip.fps - 4.0) < 1e-9 and clip.timestamps[:3] == [0.0, 0.25, 0.5]
+    import base64
+    url = "data:image/apng;base64," + base64.b64encode(data).decode()
+    tokens, pixels = vlm.prepare_messages([{"role": "user", "content": [{"type": "video_url", "video_url": {"url": url}},
+                                                                        {"type": "text", "text": "what moves?"}]}])
+    (t, h, w), = pixels.grids
+    assert t == 2 and pixels.seconds is not None and abs(pixels.seconds[0] - 2 / (4 / 2.5)) < 1e-9      # 4 kept frames over 2.5 s
+    n = t * h * w // 4
+    assert tokens.count(VID) == n and tokens.count(ids["<|image_pad|>"]) == 0
+    with torch.no_grad():
+        want_rows = hf.model.visual(torch.tensor(pixels.patches), grid_thw=torch.tensor(pixels.grids)).pooler_output.numpy()
+    rows = vlm.encode_images(pixels)
+    assert rows.shape == (n, 64) and np.abs(rows - want_rows).max() < 1e-5
+    rope = vlm.rope_inputs(tokens, pixels)
+    first = tokens.index(VID)
+    step = int(np.floor(pixels.seconds[0] * 1.0))
+    assert rope[0, first] == first and rope[0, first + n - 1] == first + step                       # the second temporal step is later in time
+    ids_t = torch.tensor([tokens])
+    with torch.no_grad():
+        out = hf(input_ids=ids_t, pixel_values_videos=torch.tensor(pixels.patches), video_grid_thw=torch.tensor(pixels.grids),
+                 attention_mask=torch.ones_like(ids_t), position_ids=torch.tensor(rope)[:, None, :].long())
+    want = out.logits[0, -1].numpy()
+    got = vlm.prefill(vlm._session(len(tokens)), tokens, pixels)[0]
+    assert np.abs(got - want).max() <= 2e-5 * max(1.0, np.abs(want).max())
+    # through the serving driver: the video rows ride the same embedding path as image rows
+    served = VisionLLM.load(d, backend="oracle", rows=2, max_seq=256, prefill_chunk=16, num_blocks=48)
+    assert served.generate(tokens, pixels, max_new=4) == vlm.generate(tokens, pixels, max_new=4)
+    with pytest.raises(ValueError, match="data: URL"):
+        vlm.prepare_messages([{"role": "user", "content": [{"type": "video_url", "video_url": {"url": "https://example.com/a.png"}}]}])
+
+
+def test_qwen_caption_command_takes_an_animated_png(qwen_checkpoint, tmp_path, capsys):
+    from PIL import Image
+    from poot_b200.cli.caption import main_caption
+    d, hf, ids = qwen_checkpoint
+    rng = np.random.default_rng(1)
+    frames = [Image.fromarray(rng.integers(0, 255, (16, 24, 3), dtype=np.uint8)) for _ in range(8)]
+    path = str(tmp_path / "clip.png")
+    with open(path, "wb") as f:
+        f.write(_apng(frames, 500))
+    assert main_caption([d, path, "what moves?", "-n", "4", "--backend", "oracle"]) == 0
+    out = capsys.readouterr().out.rstrip("\n")
+    vlm = VisionLLM.load(d)
+    from poot_b200.models.image_prep import read_apng
+    tokens, pixels = vlm.prepare("what moves?", read_apng(open(path, "rb").read()))
+    assert pixels.grids[0][0] == 4 and tokens.count(ids["<|video_pad|>"]) > 0          # 4 s at two frames per second, two per step
+    want = vlm.generate(tokens, pixels, max_new=4, eos=[vlm.handle.cfg.eos_token])
+    assert out == vlm.tokenizer.decode(want)
