@@ -331,6 +331,8 @@ def map_checkpoint(cfg: DecoderConfig, store: WeightStore) -> Dict[str, PackedWe
                 canon[p + f"experts.{x}.down"] = first_axis(w, x)
     for p, parts in mx_parts.items():
         _gpt_oss_mxfp4(cfg, p, parts, canon)
+    if cfg.family == "qwen38":
+        _join_table_shards(canon)
     if cfg.norm_offset != 0.0:
         for k in list(canon):
             if k.endswith("norm"):
@@ -514,6 +516,39 @@ def _qwen38_gate(stem: str, rest: str):
     return stem + QWEN38_GATE[rest] if rest in QWEN38_GATE else None
 
 
+def _join_table_shards(canon: Dict[str, PackedWeight]) -> None:
+    """An n-gram table stored as ``shard_0, shard_1, ...`` (consecutive row ranges of E4M3 codes) with one ``weight_scale``
+    becomes one table that stays at a byte per value: fp8 codes with the scale repeated per row, which is the
+    per-channel fp8 format the row gather already reads.  The reference keeps the shards apart and selects among one
+    gather per shard because a single buffer of its devices cannot hold the table (crates/poot-models/src/components/
+    ple.rs:24-28); one allocation of this device can."""
+    stems = sorted({k.split("#")[0] for k in canon if "ple_table#" in k})
+    for stem in stems:
+        parts = {k.split("#")[1]: canon.pop(k) for k in [k for k in canon if k.startswith(stem + "#")]}
+        scale = parts.pop("scale", None)
+        if scale is None:
+            raise CheckpointLayout(f"{stem}: table shards without their weight_scale")
+        order = sorted(parts, key=int)
+        if order != [str(i) for i in range(len(order))]:
+            raise CheckpointLayout(f"{stem}: shards {order} do not count up from 0")
+        codes = []
+        for i in order:
+            w = parts[i]
+            raw = (w.planar or {}).get("__raw__")
+            if raw is None or raw.dtype.itemsize != 1 or raw.ndim != 2:
+                raise CheckpointLayout(f"{stem}.shard_{i}: expected a matrix of fp8 codes")
+            if codes and raw.shape[1] != codes[0].shape[1]:
+                raise CheckpointLayout(f"{stem}.shard_{i}: {raw.shape[1]} columns, the first shard has {codes[0].shape[1]}")
+            codes.append(raw.view(np.uint8))
+        sraw = (scale.planar or {}).get("__raw__")
+        sval = np.asarray(sraw if sraw is not None else scale.to_f32(), np.float32).reshape(-1)
+        if sval.size != 1:
+            raise CheckpointLayout(f"{stem}: one scale for the whole table, got {sval.size}")
+        table = np.concatenate(codes, 0)
+        canon[stem] = PackedWeight(stem, "E4M3_CHANNEL", tuple(table.shape), np.zeros(0, np.uint8),
+                                   planar={"weight": table, "weight_scale": np.full(table.shape[0], sval[0], np.float32)})
+
+
 def _qwen38_tensor(cfg, p: str, rest: str, w: PackedWeight, canon: Dict[str, PackedWeight]) -> bool:
     """Tensors Qwen3.8-Flash-Next adds to the Qwen3.5 layer (crates/poot-models/src/architectures/qwen38/config.rs): the
     two hyper-connection gates, the n-gram embedding block and the block indexer, whose query rows and key rows are
@@ -526,6 +561,10 @@ def _qwen38_tensor(cfg, p: str, rest: str, w: PackedWeight, canon: Dict[str, Pac
                 return True
     if rest in QWEN38_PLE:
         canon[p + QWEN38_PLE[rest]] = w
+        return True
+    sh = re.match(r"ple\.ple_embedding\.ngram_embedding\.(?:shard_(\d+)\.weight|(weight_scale))$", rest)
+    if sh:                                                 # the table as numbered E4M3 row-range shards under one scale
+        canon[p + ("ple_table#scale" if sh.group(2) else f"ple_table#{int(sh.group(1))}")] = w
         return True
     if rest == "ple.conv1d.weight":                        # [C, 1, K]
         a = w.to_f32()

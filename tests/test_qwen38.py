@@ -330,3 +330,49 @@ def test_ngram_kernel_restatement_equals_the_hash_equation():
                        vocab, ids)
     assert np.array_equal(ids.numpy(), want)
     assert hist[1].tolist() == [int(toks[-2]) ^ eos, int(toks[-1]) ^ eos] and hist[0].tolist() == [0, 0]
+
+
+def test_sharded_fp8_ngram_table_loads_as_one_table(tmp_path):
+    """The release stores an n-gram table as numbered E4M3 row-range shards under one scale: they load as one table at a
+    byte per value whose decoded rows are ``code * scale``, and the model generates what it generates over those rows."""
+    import torch
+    from safetensors import safe_open
+    from safetensors.torch import save_file
+    from poot_b200.driver.handle import ModelHandle
+    from poot_b200.load.hf_map import CheckpointLayout
+    from poot_b200.quant.codec import e4m3_bits_to_f32
+    model = Registry.builtin().resolve_hf(_header())
+    w = _weights(model, seed=6)
+    _write_checkpoint(tmp_path / "ckpt", w, model.cfg)
+    path = str(tmp_path / "ckpt" / "model.safetensors")
+    with safe_open(path, "pt") as f:
+        tensors = {k: f.get_tensor(k) for k in f.keys()}
+    scale = np.float32(0.03125)
+    want = {}
+    for k in [k for k in tensors if k.endswith("ngram_embedding.weight")]:
+        t = tensors.pop(k)
+        codes = (t / float(scale)).to(torch.float8_e4m3fn)
+        cuts = [0, 1, t.shape[0] // 2, t.shape[0]]                     # a one-row shard, then two uneven ones
+        for i, (lo, hi) in enumerate(zip(cuts[:-1], cuts[1:])):
+            tensors[k.replace(".weight", f".shard_{i}.weight")] = codes[lo:hi].contiguous()
+        tensors[k.replace(".weight", ".weight_scale")] = torch.tensor([float(scale)])
+        layer = int(k.split("layers.")[1].split(".")[0])
+        want[f"layers.{layer}.ple_table"] = e4m3_bits_to_f32(codes.view(torch.uint8).numpy()) * scale
+    assert want
+    save_file(tensors, path, metadata={"format": "pt"})
+    h = ModelHandle.load(str(tmp_path / "ckpt"))
+    for name, rows in want.items():
+        pw = h.canonical[name]
+        assert pw.format == "E4M3_CHANNEL" and pw.planar["weight"].dtype == np.uint8 and pw.planar["weight"].nbytes == rows.size
+        assert np.array_equal(pw.to_f32(), rows)
+    got = h.oracle_weights()
+    assert all(np.array_equal(got[n], want[n]) for n in want)
+    # a missing scale, or shards that do not count up from 0, are refused by name
+    bad = {k: v for k, v in tensors.items() if not k.endswith("ngram_embedding.weight_scale")}
+    save_file(bad, path, metadata={"format": "pt"})
+    with pytest.raises(CheckpointLayout, match="weight_scale"):
+        ModelHandle.load(str(tmp_path / "ckpt"))
+    gap = {k: v for k, v in tensors.items() if ".shard_1." not in k}
+    save_file(gap, path, metadata={"format": "pt"})
+    with pytest.raises(CheckpointLayout, match="count up"):
+        ModelHandle.load(str(tmp_path / "ckpt"))
