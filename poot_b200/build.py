@@ -60,7 +60,8 @@ def _run(cmd, verbose):
 
 _ENTRY = re.compile(r"Compiling entry function '([^']+)' for 'sm_100a'")
 _SPILL = re.compile(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads")
-_USED = re.compile(r"Used (\d+) registers(?:, used (\d+) barriers)?(?:, (\d+) bytes smem)?")
+_USED = re.compile(r"Used (\d+) registers(?:, used (\d+) barriers)?")
+_SMEM = re.compile(r"(\d+) bytes smem")
 
 
 def parse_ptxas_info(text: str) -> dict:
@@ -81,7 +82,8 @@ def parse_ptxas_info(text: str) -> dict:
             continue
         m = _USED.search(line)
         if m:
-            cur["registers"], cur["barriers"], cur["static_smem"] = int(m.group(1)), int(m.group(2) or 0), int(m.group(3) or 0)
+            sm = _SMEM.search(line)               # a stack-size note may stand between the barriers and the shared memory
+            cur["registers"], cur["barriers"], cur["static_smem"] = int(m.group(1)), int(m.group(2) or 0), int(sm.group(1)) if sm else 0
             cur = None
     return out
 

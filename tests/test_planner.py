@@ -525,7 +525,7 @@ def test_register_feedback_reads_the_build_and_chooses_without_spills():
     text = """ptxas info    : Compiling entry function '_Z1aPf' for 'sm_100a'
 ptxas info    : Function properties for _Z1aPf
     16 bytes stack frame, 8 bytes spill stores, 12 bytes spill loads
-ptxas info    : Used 128 registers, used 1 barriers, 4096 bytes smem, 400 bytes cmem[0]
+ptxas info    : Used 128 registers, used 1 barriers, 16 bytes cumulative stack size, 4096 bytes smem, 400 bytes cmem[0]
 ptxas info    : Compiling entry function '_Z1bPf' for 'sm_100a'
 ptxas info    : Function properties for _Z1bPf
     0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
