@@ -144,3 +144,28 @@ class ResourceTable:
         best = min(fits, key=lambda v: (v.spill_bytes, cost(v)))
         rejected += [(v.entry, f"spills {v.spill_bytes} B per thread") for v in fits if v is not best]
         return Choice(best, f"every candidate spills; this one moves the fewest bytes ({best.spill_bytes} B per thread)", tuple(rejected))
+
+
+# planner kernel name -> library entry, where stripping ``poot_`` and adding ``_kernel`` does not give it
+ENTRY_OF = {"poot_rope_kv_write": "rope_kv_kernel", "poot_gemm_skinny_grouped": "gemm_skinny_kernel", "poot_gemm_grouped_tiled": "gemm_bf16_tcgen05_kernel",
+            "poot_quant_gemv": "quant_gemv_kernel", "poot_quant_row_gather": "quant_row_gather_kernel", "poot_tp_norm": "tp_norm_kernel",
+            "poot_index_select": "index_select_kernel", "poot_planar_gemv": "planar_gemv_rows_kernel", "poot_cast": "cast_f32_bf16_kernel"}
+
+
+def plan_resources(program, table: Optional[ResourceTable] = None) -> Dict[str, dict]:
+    """The kernel choice record of a compiled program: for every kernel its plans dispatch, the library entry behind it,
+    how many instantiations were built, the most registers any of them takes and the ones that spill
+    (crates/poot-graph-plan/src/planner/choice.rs: the reference records ``Generated | Imported | NoDispatch`` beside
+    each plan; every kernel here is a built one, so the record is what the build says about it).  A planner name with no
+    entry in the library (``movement``, ``elementwise``: done by the consumer or by a library copy) maps to ``None``."""
+    table = table or ResourceTable.load()
+    out: Dict[str, dict] = {}
+    for name, launches in sorted(program.census.items()):
+        entry = ENTRY_OF.get(name, (name[len("poot_"):] if name.startswith("poot_") else name) + "_kernel")
+        vs = table.instantiations(entry)
+        if not vs:
+            out[name] = None
+            continue
+        out[name] = {"entry": entry, "launches": launches, "instantiations": len(vs), "max_registers": max(v.registers for v in vs),
+                     "max_static_smem": max(v.static_smem for v in vs), "spilling": [v.template or v.entry for v in vs if v.spills]}
+    return out

@@ -554,3 +554,17 @@ ptxas info    : Used 40 registers"""
             assert not v.spills, (name, v.template, v.spill_bytes)
     # the instantiations with local-memory traffic are known ones: a new name here is a regression to look at
     assert {v.kernel for v in built.spilling()} <= {"q80_gemv_kernel", "attn_paged_kernel", "planar_gemv_rows_kernel", "gemm_skinny_quant_kernel"}
+
+
+def test_kernel_choice_record_of_a_compiled_program():
+    """Every kernel the flagship decode plan dispatches has an entry in the built library, with what the build says of it."""
+    from poot_b200.models.config import PRESETS
+    from poot_b200.plan.register_feedback import plan_resources
+    for preset in ("tiny-llama", "mixtral-8x7b"):
+        cfg = PRESETS[preset]()
+        cfg.n_layers = 2
+        prog = compile_graph(Model(cfg).trace(StepSpec(rows=1, tokens=1, capacity=64)))
+        rec = plan_resources(prog)
+        assert set(rec) == set(prog.census) and all(v is not None for v in rec.values()), {k for k, v in rec.items() if v is None}
+        assert rec["poot_rmsnorm"]["entry"] == "rmsnorm_kernel" and rec["poot_rmsnorm"]["spilling"] == []
+        assert rec["poot_attn_paged"]["max_registers"] <= 128 and rec["poot_attn_paged"]["launches"] == 2
