@@ -5,7 +5,7 @@ import sys
 
 from .generate import main_generate
 
-USAGE = "usage: poot {generate|caption|embed} [options]   (generate --help lists the llama-cli compatible flags)"
+USAGE = "usage: poot {generate|caption|embed|plan} [options]   (generate --help lists the llama-cli compatible flags)"
 
 
 def main(argv=None) -> int:
@@ -19,6 +19,9 @@ def main(argv=None) -> int:
     if cmd == "embed":
         from .embed import main_embed
         return main_embed(rest)
+    if cmd == "plan":
+        from .plan import main_plan
+        return main_plan(rest)
     if cmd == "caption":
         from .caption import main_caption
         return main_caption(rest)

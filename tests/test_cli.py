@@ -64,3 +64,23 @@ def test_commands():
     assert main([]) == 2 and main(["--help"]) == 0
     assert main(["caption", "-m", "x"]) == 2 and main(["embed", "-m", "x"]) == 2 and main(["nope"]) == 2
     assert main(["generate", "-m", "fake", "--no-chat-template", "-p", "a", "-n", "2", "--no-show-timings"]) == 0
+
+
+def test_plan_command_reports_the_compiled_step(tmp_path, capsys):
+    """``poot plan`` compiles one step from the checkpoint's header alone and prints census, digest, numerics class,
+    state commit and what the build says of each dispatched kernel; ``--json`` gives the same as one object."""
+    import json
+    from poot_b200.cli.__main__ import main
+    from tests.test_families import header
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps({**header("qwen3next"), "model_type": "qwen3_next"}))
+    assert main(["plan", str(d), "--tokens", "4", "--capacity", "32"]) == 0
+    out = capsys.readouterr().out
+    assert "qwen3next: 1 x 4 tokens" in out and "numerics narrowing" in out and "poot_gdn_scan" in out
+    assert "state written in place: layers.1.k_pool" in out and "state copied after the step: layers.0.conv_state" in out
+    assert main(["plan", str(d), "--json"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["family"] == "qwen3next" and rep["census"]["poot_gdn_scan"] == 2 and rep["numerics"]["tolerance"] == 5e-3
+    assert rep["kernels"]["poot_gdn_scan"]["entry"] == "gdn_scan_kernel" and rep["kernels"]["poot_gdn_scan"]["spilling"] == []
+    assert main(["plan", str(tmp_path / "missing")]) == 1
