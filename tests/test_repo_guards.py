@@ -18,7 +18,7 @@ LAYERS = {
     "runtime": {"models", "ops", "quant", "parallel", "tensor", "plan"}, "parallel": {"ops", "runtime"},
     "utils": {"ops", "oracle", "runtime", "models", "tensor", "plan", "quant"},
     "driver": {"models", "runtime", "ops", "load", "quant", "ir", "oracle", "text", "tensor", "profile", "parallel", "plan"},
-    "serve": {"driver", "text", "profile", "models", "parallel", "runtime", "ops", "load", "plan"}, "cli": {"driver", "text", "models"},
+    "serve": {"driver", "text", "profile", "models", "parallel", "runtime", "ops", "load", "plan"}, "cli": {"driver", "text", "models", "plan", "load"},
 }
 TOP = {"llm": None, "embed": None, "vlm": None, "build": None, "__init__": None}     # facades at the package root may import anything
 
